@@ -1,0 +1,52 @@
+"""Mixture-of-Depths token router (reference: moe_arch/model/mod.py:18-171)."""
+from __future__ import annotations
+
+from typing import Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+
+
+class MoDRouter(nn.Module):
+    """Scalar router ``Linear(d, 1)`` choosing ``k = int(S * capacity)`` tokens per
+    sequence; the kept indices are returned ascending and the output weights are a
+    softmax over the kept logits.  A small MLP is trained with BCE to predict the
+    selection from detached inputs (the causal-sampling predictor); that BCE, times
+    ``mod_load_balance_loss_weight``, is the layer's auxiliary loss.
+    """
+
+    def __init__(self, config):
+        super().__init__()
+        self.d_model = config.d_model
+        self.capacity_factor = config.mod_capacity_factor
+        self.router = nn.Linear(config.d_model, 1, bias=False)
+        h = config.mod_router_hidden_dim
+        self.aux_router = nn.Sequential(
+            nn.Linear(config.d_model, h, bias=False), nn.SiLU(), nn.Linear(h, 1, bias=False))
+        self.aux_loss_weight = config.mod_load_balance_loss_weight
+        self.aux_loss = 0.0
+
+    def num_selected(self, seq_len: int) -> int:
+        return max(1, min(seq_len, int(seq_len * self.capacity_factor)))
+
+    def forward(self, hidden_states: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+        B, S, _ = hidden_states.shape
+        if S == 0:
+            e_i = torch.zeros(B, 0, dtype=torch.long, device=hidden_states.device)
+            e_f = hidden_states.new_zeros(B, 0)
+            return e_i, e_f, e_f, e_i
+        logits = self.router(hidden_states).squeeze(-1)
+        k = self.num_selected(S)
+        sorted_idx, weights, topk_idx = ops.mod_route(logits, k)
+        if self.training:
+            targets = torch.zeros(B, S, device=logits.device, dtype=hidden_states.dtype)
+            targets.scatter_(1, topk_idx, 1.0)
+            aux_logits = self.aux_router(hidden_states.detach()).squeeze(-1)
+            self.aux_loss = self.aux_loss_weight * F.binary_cross_entropy_with_logits(
+                aux_logits, targets, reduction="mean")
+        else:
+            self.aux_loss = 0.0
+        return sorted_idx, weights, logits, topk_idx

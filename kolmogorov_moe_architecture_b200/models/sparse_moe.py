@@ -1,0 +1,116 @@
+"""``sparse`` and ``expert_parallel`` MoE implementations
+(reference: moe_arch/model/sparse_moe.py:292-652).
+
+The reference's expert-parallel layer exchanges tokens with plain c10d
+``all_to_all_single`` calls, which autograd does not see, so its experts, router
+and inputs receive no language-model gradient through the exchange
+(sparse_moe.py:540-603).  Here dispatch and combine are differentiable
+(:mod:`..parallel.ep`), and the expert parameters are marked so the data-parallel
+sharder leaves them out of its shard group.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+
+
+class SparseGroupedExpertsPyTorch(nn.Module):
+    """Stacked SwiGLU experts, truncated-normal init (std = 1/sqrt(3 fan_in), cut at 2 std)."""
+
+    def __init__(self, n_experts: int, d_model: int, d_ff: int, activation: str = "swiglu",
+                 moe_dtype: str = "bf16"):
+        super().__init__()
+        self.n_experts, self.d_model, self.d_ff, self.moe_dtype = n_experts, d_model, d_ff, moe_dtype
+        self.w1 = nn.Parameter(torch.empty(n_experts, d_model, d_ff))
+        self.w2 = nn.Parameter(torch.empty(n_experts, d_model, d_ff))
+        self.w3 = nn.Parameter(torch.empty(n_experts, d_ff, d_model))
+        for w in (self.w1, self.w2, self.w3):
+            std = math.sqrt(1.0 / 3.0) / math.sqrt(w.shape[1])
+            nn.init.trunc_normal_(w, mean=0.0, std=std, a=-2 * std, b=2 * std)
+
+    def forward(self, x: torch.Tensor, expert_indices: torch.Tensor, expert_weights: torch.Tensor,
+                keep: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return ops.grouped_swiglu(x, self.w1, self.w2, self.w3, expert_indices, expert_weights,
+                                  keep, self.moe_dtype)
+
+
+SparseGroupedExperts = SparseGroupedExpertsPyTorch
+
+
+def get_sparse_experts(n_experts: int, d_model: int, d_ff: int, use_triton: bool = False, **kw) -> nn.Module:
+    """Factory kept for API parity (sparse_moe.py:659-687); there is one implementation."""
+    return SparseGroupedExpertsPyTorch(n_experts, d_model, d_ff, **kw)
+
+
+class ExpertParallelMoE(nn.Module):
+    """Experts block-partitioned over the ranks of ``process_group``.
+
+    Router: a single ``Linear(d, E)``; top-k is taken on the *logits* and the weights
+    are a softmax over those k logits (sparse_moe.py:456,490-493) - this differs from
+    ``Router`` and is kept so checkpoints keyed ``expert_parallel_layer.*`` behave the
+    same.  Aux loss: ``w_lb * E * sum_i c_i P_i + w_z * mean(lse^2)`` with c_i the mean
+    number of slots per token routed to expert i (so it sums to top_k).
+    """
+
+    def __init__(self, config, layer_idx: int, process_group=None):
+        super().__init__()
+        self.config, self.layer_idx, self.process_group = config, layer_idx, process_group
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized():
+            self.world_size = dist.get_world_size(process_group)
+            self.rank = dist.get_rank(process_group)
+        else:
+            self.world_size, self.rank = 1, 0
+        self.n_experts, self.top_k = config.n_experts, config.moe_top_k
+        self.d_model, self.d_ff = config.d_model, config.d_ff_expert
+        assert self.n_experts % self.world_size == 0, (
+            f"n_experts ({self.n_experts}) must be divisible by world_size ({self.world_size})")
+        self.n_local_experts = self.n_experts // self.world_size
+        self.expert_start_idx = self.rank * self.n_local_experts
+        self.expert_end_idx = self.expert_start_idx + self.n_local_experts
+        self.router = nn.Linear(config.d_model, config.n_experts, bias=False)
+        self.local_experts = SparseGroupedExpertsPyTorch(
+            self.n_local_experts, config.d_model, config.d_ff_expert,
+            moe_dtype=getattr(config, "moe_dtype", "bf16"))
+        for p in self.local_experts.parameters():
+            p._kmoe_expert_parallel = True          # excluded from data-parallel sharding/averaging
+        self.capacity_factor = config.moe_capacity_factor
+        self.drop_tokens = getattr(config, "moe_drop_tokens", False)
+        self.aux_loss = 0.0
+        self.last_expert_counts = None
+
+    def _compute_aux_loss(self, logits: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+        probs = F.softmax(logits, dim=-1)
+        c = F.one_hot(idx, self.n_experts).float().sum(dim=1).mean(dim=0)
+        lb = self.n_experts * (c * probs.mean(dim=0)).sum()
+        z = torch.logsumexp(logits, dim=-1).pow(2).mean()
+        return self.config.moe_load_balance_loss_weight * lb + self.config.moe_router_z_loss_weight * z
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        B, S, d = x.shape
+        xf = x.reshape(-1, d)
+        logits = self.router(xf)
+        topv, idx = torch.topk(logits, self.top_k, dim=-1)
+        w = F.softmax(topv, dim=-1)
+        if self.training:
+            self.aux_loss = self._compute_aux_loss(logits, idx)
+        else:
+            self.aux_loss = 0.0
+        with torch.no_grad():
+            self.last_expert_counts = torch.bincount(idx.reshape(-1), minlength=self.n_experts)
+        keep = None
+        if self.drop_tokens:
+            cap = int(math.ceil(self.capacity_factor * idx.numel() / self.n_experts))
+            keep = ops.capacity_keep_mask(idx, self.n_experts, cap)
+        if self.world_size == 1:
+            return self.local_experts(xf, idx, w, keep).reshape(B, S, d)
+        from ..parallel.ep import expert_parallel_ffn
+        out = expert_parallel_ffn(xf, idx, w, self.local_experts, self.n_experts,
+                                  self.process_group, keep=keep)
+        return out.reshape(B, S, d)

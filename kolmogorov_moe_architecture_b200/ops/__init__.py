@@ -1,0 +1,94 @@
+"""Hot-op dispatch.
+
+Every function here takes the CUDA kernel path for CUDA tensors and the
+plain-PyTorch definition in :mod:`.eager` for CPU tensors.  On a CUDA tensor
+the compiled extension is mandatory: a missing ``_C`` library raises instead
+of silently falling back, unless ``KMOE_ALLOW_EAGER=1`` is set.
+"""
+from __future__ import annotations
+
+import os
+
+from . import eager
+from .loader import ext_available, load_ext, require_ext  # noqa: F401
+
+
+def _use_cuda(t) -> bool:
+    if not t.is_cuda:
+        return False
+    if ext_available():
+        return True
+    if os.environ.get("KMOE_ALLOW_EAGER", "0") == "1":
+        return False
+    require_ext()
+    return True
+
+
+def rmsnorm(x, weight, eps):
+    if _use_cuda(x):
+        from . import cuda_ops
+        return cuda_ops.rmsnorm(x, weight, eps)
+    return eager.rmsnorm(x, weight, eps)
+
+
+def rope_apply(x, cos, sin):
+    if _use_cuda(x):
+        from . import cuda_ops
+        return cuda_ops.rope_apply(x, cos, sin)
+    return eager.rope_apply(x, cos, sin)
+
+
+def swiglu(gate, up):
+    if _use_cuda(gate):
+        from . import cuda_ops
+        return cuda_ops.swiglu(gate, up)
+    return eager.swiglu(gate, up)
+
+
+def attention(q, k, v, causal=True, attn_mask=None, dropout_p=0.0, training=False):
+    if attn_mask is None and not (dropout_p > 0.0 and training) and _use_cuda(q):
+        from . import cuda_ops
+        return cuda_ops.attention(q, k, v, causal)
+    return eager.attention(q, k, v, causal, attn_mask, dropout_p, training)
+
+
+def causal_conv1d(x, weight, bias, activation=True):
+    if _use_cuda(x):
+        from . import cuda_ops
+        return cuda_ops.causal_conv1d(x, weight, bias, activation)
+    return eager.causal_conv1d(x, weight, bias, activation)
+
+
+def selective_scan(u, delta, A, Bm, Cm, D, z, delta_bias, delta_softplus=True):
+    if _use_cuda(u):
+        from . import cuda_ops
+        return cuda_ops.selective_scan(u, delta, A, Bm, Cm, D, z, delta_bias, delta_softplus)
+    return eager.selective_scan(u, delta, A, Bm, Cm, D, z, delta_bias, delta_softplus)
+
+
+def grouped_swiglu(x, w1, w2, w3, idx, weights, keep=None, moe_dtype="bf16"):
+    if _use_cuda(x):
+        from . import cuda_ops
+        return cuda_ops.grouped_swiglu(x, w1, w2, w3, idx, weights, keep, moe_dtype)
+    return eager.grouped_swiglu(x, w1, w2, w3, idx, weights, keep)
+
+
+def mtp_cross_entropy(hidden, head_weights, labels, weights, ignore_index=-100):
+    if _use_cuda(hidden):
+        from . import cuda_ops
+        return cuda_ops.mtp_cross_entropy(hidden, head_weights, labels, weights, ignore_index)
+    return eager.mtp_cross_entropy(hidden, head_weights, labels, weights, ignore_index)
+
+
+def newton_schulz(matrix, iters=5):
+    if _use_cuda(matrix):
+        from . import cuda_ops
+        return cuda_ops.newton_schulz(matrix, iters)
+    return eager.newton_schulz(matrix, iters)
+
+
+topk_softmax_route = eager.topk_softmax_route
+moe_aux_loss = eager.moe_aux_loss
+capacity_keep_mask = eager.capacity_keep_mask
+mod_route = eager.mod_route
+rope_tables = eager.rope_tables
