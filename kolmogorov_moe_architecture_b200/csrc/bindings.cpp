@@ -1,0 +1,284 @@
+// PyTorch operator registrations (namespace torch.ops.kmoe) over the C launch API in
+// kmoe_api.h.  This is the only translation unit that includes torch headers.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include "kmoe_api.h"
+
+namespace {
+
+using at::Tensor;
+using OptT = c10::optional<Tensor>;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+inline void check(int rc, const char* what) { TORCH_CHECK(rc == 0, "kmoe::", what, " failed with code ", rc); }
+inline const void* ptr_or_null(const OptT& t) { return (t.has_value() && t->defined()) ? t->data_ptr() : nullptr; }
+inline void need_bf16(const Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16, n, " must be a CUDA bf16 tensor");
+}
+inline void need_f32(const Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous(), n,
+              " must be a contiguous CUDA fp32 tensor");
+}
+// row stride of a (..., C) tensor whose last dim is dense and whose leading dims collapse to rows
+inline long long row_stride(const Tensor& t) {
+  TORCH_CHECK(t.stride(-1) == 1, "last dimension must be contiguous");
+  long long ld = t.stride(-2);
+  for (int i = t.dim() - 3; i >= 0; --i)
+    TORCH_CHECK(t.size(i) == 1 || t.stride(i) == t.stride(i + 1) * t.size(i + 1), "leading dims must collapse");
+  return ld;
+}
+
+// ------------------------------------------------------------------------ GEMM
+void gemm(const Tensor& A, const Tensor& B, const OptT& B2, Tensor C, const OptT& D, const OptT& G, const OptT& U,
+          int64_t mode, int64_t epilogue, int64_t M, int64_t N, int64_t K, int64_t groups, int64_t a_major,
+          int64_t b_major, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, int64_t a_gs, int64_t b_gs,
+          int64_t c_gs, const OptT& tile_group, const OptT& num_m_tiles, const OptT& k_begin, const OptT& k_len,
+          double alpha, double beta, const OptT& row_scale, Tensor status) {
+  c10::cuda::CUDAGuard guard(A.device());
+  need_bf16(A, "A");
+  need_bf16(B, "B");
+  KmoeGemmDesc d{};
+  d.A = A.data_ptr(); d.B = B.data_ptr(); d.B2 = ptr_or_null(B2); d.C = C.data_ptr();
+  d.D = ptr_or_null(D); d.G_out = const_cast<void*>(ptr_or_null(G)); d.U_out = const_cast<void*>(ptr_or_null(U));
+  d.mode = (int)mode; d.epilogue = (int)epilogue; d.M = (int)M; d.N = (int)N; d.K = (int)K; d.groups = (int)groups;
+  d.a_major = (int)a_major; d.b_major = (int)b_major;
+  d.lda = lda; d.ldb = ldb; d.ldc = ldc; d.ldd = ldd; d.a_gstride = a_gs; d.b_gstride = b_gs; d.c_gstride = c_gs;
+  d.tile_group = (const int*)ptr_or_null(tile_group); d.num_m_tiles = (const int*)ptr_or_null(num_m_tiles);
+  d.k_begin = (const int*)ptr_or_null(k_begin); d.k_len = (const int*)ptr_or_null(k_len);
+  d.out_f32 = C.scalar_type() == at::kFloat ? 1 : 0;
+  TORCH_CHECK(d.out_f32 || C.scalar_type() == at::kBFloat16, "C must be bf16 or fp32");
+  if (D.has_value() && D->defined()) TORCH_CHECK(D->scalar_type() == C.scalar_type(), "D must have C's dtype");
+  d.alpha = (float)alpha; d.beta = (float)beta; d.row_scale = (const float*)ptr_or_null(row_scale);
+  TORCH_CHECK(status.scalar_type() == at::kInt && status.is_cuda(), "status must be a CUDA int32 tensor");
+  d.status = status.data_ptr<int>();
+  d.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  check(kmoe_gemm(&d, cur_stream()), "gemm");
+}
+
+// ----------------------------------------------------------------- row kernels
+std::tuple<Tensor, Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_bf16(x, "x"); need_bf16(w, "w");
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous());
+  const int d = x.size(-1);
+  const int rows = x.numel() / d;
+  Tensor y = at::empty_like(x);
+  Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  check(kmoe_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), rows, d, (float)eps,
+                         cur_stream()), "rmsnorm_fwd");
+  return {y, rstd};
+}
+
+std::tuple<Tensor, Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const Tensor& dy, const Tensor& rstd) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_bf16(x, "x"); need_bf16(dy, "dy"); need_f32(rstd, "rstd");
+  TORCH_CHECK(x.is_contiguous() && dy.is_contiguous());
+  const int d = x.size(-1);
+  const int rows = x.numel() / d;
+  Tensor dx = at::empty_like(x);
+  Tensor dw = at::empty({d}, x.options().dtype(at::kFloat));
+  Tensor partial = at::empty({kmoe_rmsnorm_bwd_num_partials(rows), d}, x.options().dtype(at::kFloat));
+  check(kmoe_rmsnorm_bwd(x.data_ptr(), w.data_ptr(), dy.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(), nullptr,
+                         dw.data_ptr<float>(), partial.data_ptr<float>(), rows, d, cur_stream()), "rmsnorm_bwd");
+  return {dx, dw};
+}
+
+Tensor rope(const Tensor& x, const Tensor& cs, const Tensor& sn, bool transpose) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_bf16(x, "x"); need_f32(cs, "cos"); need_f32(sn, "sin");
+  TORCH_CHECK(x.dim() == 4 && x.is_contiguous(), "x must be contiguous [B,S,H,D]");
+  const int B = x.size(0), S = x.size(1), H = x.size(2), D = x.size(3);
+  long long bstride = 0;
+  if (cs.dim() == 3 && cs.size(0) > 1) bstride = (long long)S * D;
+  TORCH_CHECK(cs.size(-1) == D && cs.size(-2) == S, "cos/sin must be [S,D] or [B,S,D]");
+  Tensor out = at::empty_like(x);
+  check(kmoe_rope(x.data_ptr(), cs.data_ptr<float>(), sn.data_ptr<float>(), out.data_ptr(), B, S, H, D, bstride,
+                  transpose ? 1 : 0, cur_stream()), "rope");
+  return out;
+}
+
+Tensor swiglu_fwd(const Tensor& g, const Tensor& u) {
+  c10::cuda::CUDAGuard guard(g.device());
+  need_bf16(g, "gate"); need_bf16(u, "up");
+  const int cols = g.size(-1);
+  const long long rows = g.numel() / cols;
+  Tensor g2 = g.dim() == 1 ? g.unsqueeze(0) : g, u2 = u.dim() == 1 ? u.unsqueeze(0) : u;
+  Tensor h = at::empty(g.sizes(), g.options());
+  check(kmoe_swiglu_fwd(g2.data_ptr(), u2.data_ptr(), h.data_ptr(), rows, cols, row_stride(g2), row_stride(u2),
+                        cur_stream()), "swiglu_fwd");
+  return h;
+}
+
+std::tuple<Tensor, Tensor> swiglu_bwd(const Tensor& g, const Tensor& u, const Tensor& dh) {
+  c10::cuda::CUDAGuard guard(g.device());
+  need_bf16(g, "gate"); need_bf16(u, "up"); need_bf16(dh, "dh");
+  TORCH_CHECK(dh.is_contiguous());
+  const int cols = g.size(-1);
+  const long long rows = g.numel() / cols;
+  Tensor g2 = g.dim() == 1 ? g.unsqueeze(0) : g, u2 = u.dim() == 1 ? u.unsqueeze(0) : u;
+  Tensor dg = at::empty(g.sizes(), g.options()), du = at::empty(g.sizes(), g.options());
+  check(kmoe_swiglu_bwd(g2.data_ptr(), u2.data_ptr(), dh.data_ptr(), dg.data_ptr(), du.data_ptr(), rows, cols,
+                        row_stride(g2), row_stride(u2), cols, cur_stream()), "swiglu_bwd");
+  return {dg, du};
+}
+
+// ------------------------------------------------------------------------ Mamba
+Tensor conv1d_fwd(const Tensor& x, const Tensor& w, const OptT& bias, bool act) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_bf16(x, "x"); need_f32(w, "w");
+  TORCH_CHECK(x.dim() == 3 && w.dim() == 2 && w.size(1) == 4, "x [B,S,C], w [C,4]");
+  const int B = x.size(0), S = x.size(1), C = x.size(2);
+  Tensor y = at::empty({B, S, C}, x.options());
+  check(kmoe_conv1d_fwd(x.data_ptr(), w.data_ptr<float>(), (const float*)ptr_or_null(bias), y.data_ptr(), B, S, C,
+                        row_stride(x), act ? 1 : 0, cur_stream()), "conv1d_fwd");
+  return y;
+}
+
+std::tuple<Tensor, Tensor, Tensor> conv1d_bwd(const Tensor& x, const Tensor& w, const OptT& bias, const Tensor& dy,
+                                              bool act) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_bf16(x, "x"); need_bf16(dy, "dy"); need_f32(w, "w");
+  TORCH_CHECK(dy.is_contiguous());
+  const int B = x.size(0), S = x.size(1), C = x.size(2);
+  Tensor dx = at::empty({B, S, C}, x.options());
+  Tensor dw = at::zeros({C, 4}, w.options());
+  Tensor db = at::zeros({C}, w.options());
+  check(kmoe_conv1d_bwd(x.data_ptr(), w.data_ptr<float>(), (const float*)ptr_or_null(bias), dy.data_ptr(),
+                        dx.data_ptr(), dw.data_ptr<float>(), db.data_ptr<float>(), B, S, C, row_stride(x),
+                        act ? 1 : 0, cur_stream()), "conv1d_bwd");
+  return {dx, dw, db};
+}
+
+std::tuple<Tensor, Tensor> scan_fwd(const Tensor& u, const Tensor& delta, const OptT& z, const Tensor& A,
+                                    const Tensor& Bm, const Tensor& Cm, const OptT& D, const OptT& dt_bias,
+                                    bool softplus, bool save) {
+  c10::cuda::CUDAGuard guard(u.device());
+  need_bf16(u, "u"); need_bf16(delta, "delta"); need_f32(A, "A"); need_f32(Bm, "B"); need_f32(Cm, "C");
+  TORCH_CHECK(u.is_contiguous() && delta.is_contiguous() && u.dim() == 3);
+  const int B = u.size(0), S = u.size(1), C = u.size(2), N = A.size(1);
+  Tensor out = at::empty_like(u);
+  const int nch = (S + kmoe_scan_chunk() - 1) / kmoe_scan_chunk();
+  Tensor ckpt = save ? at::empty({B, nch, N, C}, A.options()) : at::empty({0}, A.options());
+  const bool has_z = z.has_value() && z->defined();
+  if (has_z) need_bf16(*z, "z");
+  check(kmoe_scan_fwd(u.data_ptr(), delta.data_ptr(), has_z ? z->data_ptr() : nullptr, A.data_ptr<float>(),
+                      Bm.data_ptr<float>(), Cm.data_ptr<float>(), (const float*)ptr_or_null(D),
+                      (const float*)ptr_or_null(dt_bias), out.data_ptr(), save ? ckpt.data_ptr<float>() : nullptr, B,
+                      S, C, N, has_z ? row_stride(*z) : 0, softplus ? 1 : 0, cur_stream()), "scan_fwd");
+  return {out, ckpt};
+}
+
+std::vector<Tensor> scan_bwd(const Tensor& u, const Tensor& delta, const OptT& z, const Tensor& A, const Tensor& Bm,
+                             const Tensor& Cm, const OptT& D, const OptT& dt_bias, const Tensor& dout,
+                             const Tensor& ckpt, bool softplus) {
+  c10::cuda::CUDAGuard guard(u.device());
+  need_bf16(dout, "dout");
+  TORCH_CHECK(dout.is_contiguous());
+  const int B = u.size(0), S = u.size(1), C = u.size(2), N = A.size(1);
+  const bool has_z = z.has_value() && z->defined();
+  Tensor du = at::empty_like(u), dd = at::empty_like(u);
+  Tensor dz = has_z ? at::empty({B, S, C}, u.options()) : at::empty({0}, u.options());
+  auto f32 = A.options();
+  Tensor dA = at::zeros({C, N}, f32), dB = at::zeros({B, S, N}, f32), dC = at::zeros({B, S, N}, f32);
+  Tensor dD = at::zeros({C}, f32), dbias = at::zeros({C}, f32);
+  check(kmoe_scan_bwd(u.data_ptr(), delta.data_ptr(), has_z ? z->data_ptr() : nullptr, A.data_ptr<float>(),
+                      Bm.data_ptr<float>(), Cm.data_ptr<float>(), (const float*)ptr_or_null(D),
+                      (const float*)ptr_or_null(dt_bias), dout.data_ptr(), ckpt.data_ptr<float>(), du.data_ptr(),
+                      dd.data_ptr(), has_z ? dz.data_ptr() : nullptr, C, dA.data_ptr<float>(), dB.data_ptr<float>(),
+                      dC.data_ptr<float>(), dD.data_ptr<float>(), dbias.data_ptr<float>(), B, S, C, N,
+                      has_z ? row_stride(*z) : 0, softplus ? 1 : 0, cur_stream()), "scan_bwd");
+  return {du, dd, dz, dA, dB, dC, dD, dbias};
+}
+
+// -------------------------------------------------------------------------- MoE
+std::vector<Tensor> moe_plan(const Tensor& idx, const OptT& keep, int64_t E, int64_t expert_base) {
+  c10::cuda::CUDAGuard guard(idx.device());
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kLong && idx.is_contiguous(), "idx must be contiguous int64");
+  const int n = idx.numel();
+  const int max_rows = kmoe_moe_max_rows(n, (int)E);
+  auto i32 = idx.options().dtype(at::kInt);
+  Tensor pos = at::empty({n}, i32), row_src = at::empty({max_rows}, i32), counts = at::empty({E}, i32);
+  Tensor offsets = at::empty({E + 1}, i32), tile_group = at::empty({max_rows / 128}, i32), meta = at::empty({2}, i32);
+  const unsigned char* kp = nullptr;
+  Tensor k8;
+  if (keep.has_value() && keep->defined()) {
+    k8 = keep->to(at::kByte).contiguous();
+    kp = k8.data_ptr<unsigned char>();
+  }
+  check(kmoe_moe_plan((const long long*)idx.data_ptr<int64_t>(), kp, n, (int)E, max_rows, (int)expert_base,
+                      pos.data_ptr<int>(), row_src.data_ptr<int>(), counts.data_ptr<int>(), offsets.data_ptr<int>(),
+                      tile_group.data_ptr<int>(), meta.data_ptr<int>(), cur_stream()), "moe_plan");
+  return {pos, row_src, counts, offsets, tile_group, meta};
+}
+
+Tensor moe_gather_rows(const Tensor& src, const Tensor& row_src, const OptT& assign_scale, const Tensor& meta,
+                       int64_t div) {
+  c10::cuda::CUDAGuard guard(src.device());
+  need_bf16(src, "src");
+  TORCH_CHECK(src.is_contiguous() && src.dim() == 2);
+  const int max_rows = row_src.numel(), d = src.size(1);
+  Tensor dst = at::empty({max_rows, d}, src.options());
+  check(kmoe_moe_gather_rows(src.data_ptr(), row_src.data_ptr<int>(), (const float*)ptr_or_null(assign_scale),
+                             meta.data_ptr<int>(), dst.data_ptr(), max_rows, d, (int)div, cur_stream()),
+        "moe_gather_rows");
+  return dst;
+}
+
+Tensor moe_combine(const Tensor& Y, const Tensor& pos, const OptT& w, int64_t T, int64_t k) {
+  c10::cuda::CUDAGuard guard(Y.device());
+  need_bf16(Y, "Y");
+  TORCH_CHECK(Y.is_contiguous());
+  const int d = Y.size(1);
+  Tensor out = at::empty({T, d}, Y.options());
+  check(kmoe_moe_combine(Y.data_ptr(), pos.data_ptr<int>(), (const float*)ptr_or_null(w), out.data_ptr(), (int)T,
+                         (int)k, d, cur_stream()), "moe_combine");
+  return out;
+}
+
+Tensor moe_combine_dw(const Tensor& Y, const Tensor& dout, const Tensor& pos, int64_t k) {
+  c10::cuda::CUDAGuard guard(Y.device());
+  need_bf16(Y, "Y"); need_bf16(dout, "dout");
+  TORCH_CHECK(Y.is_contiguous() && dout.is_contiguous());
+  const int n = pos.numel(), d = Y.size(1);
+  Tensor dw = at::empty({n}, Y.options().dtype(at::kFloat));
+  check(kmoe_moe_combine_dw(Y.data_ptr(), dout.data_ptr(), pos.data_ptr<int>(), dw.data_ptr<float>(), n, (int)k, d,
+                            cur_stream()), "moe_combine_dw");
+  return dw;
+}
+
+// ------------------------------------------------------------------------- loss
+Tensor ce_fwd_bwd(Tensor logits, const Tensor& labels, const Tensor& grad_scale, int64_t ignore_index,
+                  bool write_grad) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  need_bf16(logits, "logits"); need_f32(grad_scale, "grad_scale");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1);
+  TORCH_CHECK(labels.scalar_type() == at::kLong && labels.is_contiguous() && labels.numel() == logits.size(0));
+  Tensor loss_rows = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+  check(kmoe_ce_fwd_bwd(logits.data_ptr(), (const long long*)labels.data_ptr<int64_t>(), loss_rows.data_ptr<float>(),
+                        grad_scale.data_ptr<float>(), (int)logits.size(0), (int)logits.size(1), logits.stride(0),
+                        ignore_index, write_grad ? 1 : 0, cur_stream()), "ce_fwd_bwd");
+  return loss_rows;
+}
+
+}  // namespace
+
+TORCH_LIBRARY(kmoe, m) {
+  m.def("gemm", &gemm);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rope", &rope);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("conv1d_fwd", &conv1d_fwd);
+  m.def("conv1d_bwd", &conv1d_bwd);
+  m.def("scan_fwd", &scan_fwd);
+  m.def("scan_bwd", &scan_bwd);
+  m.def("moe_plan", &moe_plan);
+  m.def("moe_gather_rows", &moe_gather_rows);
+  m.def("moe_combine", &moe_combine);
+  m.def("moe_combine_dw", &moe_combine_dw);
+  m.def("ce_fwd_bwd", &ce_fwd_bwd);
+}

@@ -1,0 +1,261 @@
+// Bandwidth-bound row kernels: RMSNorm fwd/bwd, rotate-half RoPE, SwiGLU fwd/bwd.
+// bf16 in/out, fp32 math, 16-byte vector accesses.  One warp per row for the
+// normalisation kernels (a 2048-wide row is 8 x uint4 per lane).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "kmoe_api.h"
+#include "ptx.cuh"
+
+namespace kmoe {
+
+__device__ __forceinline__ void unpack8(const uint4& r, float* v) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(p[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* v) {
+  uint4 o;
+  o.x = pack_bf16(v[0], v[1]);
+  o.y = pack_bf16(v[2], v[3]);
+  o.z = pack_bf16(v[4], v[5]);
+  o.w = pack_bf16(v[6], v[7]);
+  return o;
+}
+
+// ------------------------------------------------------------------- RMSNorm
+// y = w * x * rsqrt(mean(x^2) + eps); optionally res_out = x (+ residual) is fused by the caller.
+__global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int d,
+                                   float eps) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
+    const __nv_bfloat16* xr = x + (size_t)row * d;
+    float ss = 0.f;
+    for (int c = lane * 8; c < d; c += 256) {
+      float v[8];
+      unpack8(*reinterpret_cast<const uint4*>(xr + c), v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / d + eps);
+    if (lane == 0 && rstd != nullptr) rstd[row] = r;
+    __nv_bfloat16* yr = y + (size_t)row * d;
+    for (int c = lane * 8; c < d; c += 256) {
+      float v[8], g[8];
+      unpack8(*reinterpret_cast<const uint4*>(xr + c), v);
+      unpack8(*reinterpret_cast<const uint4*>(w + c), g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = v[i] * r * g[i];
+      *reinterpret_cast<uint4*>(yr + c) = pack8(v);
+    }
+  }
+}
+
+// dx = rstd * (w dy) - x * rstd^3 * mean(w dy x);  dw partial sums per block into `partial` [gridDim.x, d].
+__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                   const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
+                                   __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int d) {
+  extern __shared__ float s_dw[];  // d floats
+  for (int c = threadIdx.x; c < d; c += blockDim.x) s_dw[c] = 0.f;
+  __syncthreads();
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
+    const __nv_bfloat16* xr = x + (size_t)row * d;
+    const __nv_bfloat16* gr = dy + (size_t)row * d;
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int c = lane * 8; c < d; c += 256) {
+      float xv[8], gv[8], wv[8];
+      unpack8(*reinterpret_cast<const uint4*>(xr + c), xv);
+      unpack8(*reinterpret_cast<const uint4*>(gr + c), gv);
+      unpack8(*reinterpret_cast<const uint4*>(w + c), wv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dot += gv[i] * wv[i] * xv[i];
+    }
+    dot = warp_sum(dot);
+    const float coef = dot * r * r * r / d;
+    __nv_bfloat16* dxr = dx + (size_t)row * d;
+    for (int c = lane * 8; c < d; c += 256) {
+      float xv[8], gv[8], wv[8], o[8];
+      unpack8(*reinterpret_cast<const uint4*>(xr + c), xv);
+      unpack8(*reinterpret_cast<const uint4*>(gr + c), gv);
+      unpack8(*reinterpret_cast<const uint4*>(w + c), wv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        o[i] = gv[i] * wv[i] * r - xv[i] * coef;
+        atomicAdd(&s_dw[c + i], gv[i] * xv[i] * r);
+      }
+      *reinterpret_cast<uint4*>(dxr + c) = pack8(o);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < d; c += blockDim.x) partial[(size_t)blockIdx.x * d + c] = s_dw[c];
+}
+
+__global__ void colsum_partials_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out_bf16,
+                                       float* __restrict__ out_f32, int nparts, int d) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * d + c];
+  if (out_bf16 != nullptr) out_bf16[c] = __float2bfloat16(s);
+  if (out_f32 != nullptr) out_f32[c] = s;
+}
+
+// ---------------------------------------------------------------------- RoPE
+// x: [B, S, H, D] bf16 ; cos/sin: fp32 [*, S, D] with batch stride cs_bstride (0 = shared).
+// out = x * cos + rotate_half(x) * sin ; `sign` = -1 gives the transpose (the backward).
+__global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ cs,
+                            const float* __restrict__ sn, __nv_bfloat16* __restrict__ out, int B, int S, int H, int D,
+                            long long cs_bstride, float sign) {
+  const int half = D / 2;
+  const int vec_per_head = half / 8;
+  const long long total = (long long)B * S * H * vec_per_head;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(i % vec_per_head);
+    long long t = i / vec_per_head;
+    const int h = (int)(t % H);
+    t /= H;
+    const int s = (int)(t % S);
+    const int b = (int)(t / S);
+    const size_t base = (((size_t)b * S + s) * H + h) * D + v * 8;
+    const size_t cbase = (size_t)b * cs_bstride + (size_t)s * D + v * 8;
+    float x1[8], x2[8], o1[8], o2[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + base), x1);
+    unpack8(*reinterpret_cast<const uint4*>(x + base + half), x2);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float c1 = cs[cbase + j], c2 = cs[cbase + half + j];
+      const float s1 = sign * sn[cbase + j], s2 = sign * sn[cbase + half + j];
+      // forward: o1 = x1 c1 - x2 s1 ; o2 = x2 c2 + x1 s2.  transpose: o1 = x1 c1 + x2 s2 ; o2 = x2 c2 - x1 s1
+      if (sign > 0.f) {
+        o1[j] = x1[j] * c1 - x2[j] * s1;
+        o2[j] = x2[j] * c2 + x1[j] * s2;
+      } else {
+        o1[j] = x1[j] * c1 - x2[j] * s2;
+        o2[j] = x2[j] * c2 + x1[j] * s1;
+      }
+    }
+    *reinterpret_cast<uint4*>(out + base) = pack8(o1);
+    *reinterpret_cast<uint4*>(out + base + half) = pack8(o2);
+  }
+}
+
+// -------------------------------------------------------------------- SwiGLU
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
+                                  __nv_bfloat16* __restrict__ h, long long rows, int cols, long long ldg,
+                                  long long ldu) {
+  const int vpr = cols / 8;
+  const long long total = rows * vpr;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vpr;
+    const int c = (int)(i % vpr) * 8;
+    float gv[8], uv[8];
+    unpack8(*reinterpret_cast<const uint4*>(g + r * ldg + c), gv);
+    unpack8(*reinterpret_cast<const uint4*>(u + r * ldu + c), uv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) gv[j] = silu_f(gv[j]) * uv[j];
+    *reinterpret_cast<uint4*>(h + r * cols + c) = pack8(gv);
+  }
+}
+
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
+                                  const __nv_bfloat16* __restrict__ dh, __nv_bfloat16* __restrict__ dg,
+                                  __nv_bfloat16* __restrict__ du, long long rows, int cols, long long ldg,
+                                  long long ldu, long long ldo) {
+  const int vpr = cols / 8;
+  const long long total = rows * vpr;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vpr;
+    const int c = (int)(i % vpr) * 8;
+    float gv[8], uv[8], dv[8], og[8], ou[8];
+    unpack8(*reinterpret_cast<const uint4*>(g + r * ldg + c), gv);
+    unpack8(*reinterpret_cast<const uint4*>(u + r * ldu + c), uv);
+    unpack8(*reinterpret_cast<const uint4*>(dh + r * cols + c), dv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = 1.f / (1.f + __expf(-gv[j]));
+      og[j] = dv[j] * uv[j] * sg * (1.f + gv[j] * (1.f - sg));
+      ou[j] = dv[j] * gv[j] * sg;
+    }
+    *reinterpret_cast<uint4*>(dg + r * ldo + c) = pack8(og);
+    *reinterpret_cast<uint4*>(du + r * ldo + c) = pack8(ou);
+  }
+}
+
+static inline int grid_for(long long work, int block, int sms = 148) {
+  long long g = (work + block - 1) / block;
+  long long cap = (long long)sms * 16;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace kmoe
+
+using namespace kmoe;
+
+extern "C" int kmoe_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int d, float eps,
+                                cudaStream_t st) {
+  if (d % 8) return -1;
+  const int block = 256, wpb = block / 32;
+  int grid = (rows + wpb - 1) / wpb;
+  if (grid > 148 * 8) grid = 148 * 8;
+  rmsnorm_fwd_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
+                                             rstd, rows, d, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_rmsnorm_bwd_num_partials(int rows) {
+  const int wpb = 8;
+  int grid = (rows + wpb - 1) / wpb;
+  return grid > 296 ? 296 : grid;
+}
+
+// `partial` is scratch of kmoe_rmsnorm_bwd_num_partials(rows) * d floats.
+extern "C" int kmoe_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx,
+                                void* dw_bf16, float* dw_f32, float* partial, int rows, int d, cudaStream_t st) {
+  if (d % 8) return -1;
+  const int block = 256;
+  const int grid = kmoe_rmsnorm_bwd_num_partials(rows);
+  rmsnorm_bwd_kernel<<<grid, block, d * sizeof(float), st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                                             (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx,
+                                                             partial, rows, d);
+  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, (__nv_bfloat16*)dw_bf16, dw_f32, grid, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_rope(const void* x, const float* cs, const float* sn, void* out, int B, int S, int H, int D,
+                         long long cs_bstride, int transpose, cudaStream_t st) {
+  if (D % 16) return -1;
+  const long long total = (long long)B * S * H * (D / 16);
+  rope_kernel<<<grid_for(total, 256), 256, 0, st>>>((const __nv_bfloat16*)x, cs, sn, (__nv_bfloat16*)out, B, S, H, D,
+                                                    cs_bstride, transpose ? -1.f : 1.f);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_swiglu_fwd(const void* g, const void* u, void* h, long long rows, int cols, long long ldg,
+                               long long ldu, cudaStream_t st) {
+  if (cols % 8 || ldg % 8 || ldu % 8) return -1;
+  swiglu_fwd_kernel<<<grid_for(rows * (cols / 8), 256), 256, 0, st>>>(
+      (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (__nv_bfloat16*)h, rows, cols, ldg, ldu);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_swiglu_bwd(const void* g, const void* u, const void* dh, void* dg, void* du, long long rows,
+                               int cols, long long ldg, long long ldu, long long ldo, cudaStream_t st) {
+  if (cols % 8 || ldg % 8 || ldu % 8 || ldo % 8) return -1;
+  swiglu_bwd_kernel<<<grid_for(rows * (cols / 8), 256), 256, 0, st>>>(
+      (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (const __nv_bfloat16*)dh, (__nv_bfloat16*)dg,
+      (__nv_bfloat16*)du, rows, cols, ldg, ldu, ldo);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

@@ -1,0 +1,529 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a.
+//
+//   warp 0      : TMA producer  (cp.async.bulk.tensor -> 128B-swizzled smem ring, mbarrier tx counts)
+//   warp 1      : MMA issuer    (tcgen05.mma 128 x BN x 16, accumulators in TMEM, double buffered)
+//   warps 2..5  : epilogue      (tcgen05.ld -> registers -> fused epilogue -> global)
+//
+// One CTA per SM walks a static tile list, so the epilogue of tile i overlaps the
+// main loop of tile i+1.  Operands may be K-major or MN-major (the MMA reads either
+// from swizzled smem), which covers forward, dgrad and wgrad without transposes.
+// Three tile schedules: dense, grouped along M (expert-sorted rows padded to 128
+// per expert, tile->expert table and live tile count read from device memory: no
+// host synchronisation), and batched (independent GEMMs, optionally with a ragged
+// reduction range per group: the wgrad of the experts).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "kmoe_api.h"
+#include "ptx.cuh"
+
+namespace kmoe {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int NUM_THREADS = 192;
+
+struct GemmArgs {
+  void* C;
+  const void* D;
+  void* G_out;
+  void* U_out;
+  int mode, epilogue;
+  int M, N, K, groups;
+  long long ldc, ldd, c_gstride;
+  int a_grouped, b_grouped;
+  const int* tile_group;
+  const int* num_m_tiles;
+  const int* k_begin;
+  const int* k_len;
+  int out_f32;
+  float alpha, beta;
+  const float* row_scale;
+  int* status;
+};
+
+struct Tile {
+  int m_tile, n_tile, g_a, g_b, g_c, k0, k_blocks;
+};
+
+__device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Maps a linear work index to a tile. Returns false past the end.
+template <int BN>
+__device__ __forceinline__ bool get_tile(const GemmArgs& a, int idx, int num_m, int num_n, Tile& t) {
+  const int n_out = (a.epilogue == KMOE_EPI_SWIGLU) ? BN / 2 : BN;
+  (void)n_out;
+  int per_group = num_m * num_n;
+  int g = 0, local = idx;
+  if (a.mode == KMOE_GEMM_BATCHED) {
+    g = idx / per_group;
+    local = idx - g * per_group;
+    if (g >= a.groups) return false;
+  } else if (idx >= per_group) {
+    return false;
+  }
+  // supertile of 8 m-tiles: neighbouring CTAs share B tiles and a narrow band of A
+  const int GM = 8;
+  int band = local / (GM * num_n);
+  int first_m = band * GM;
+  int gsz = min(num_m - first_m, GM);
+  int r = local - band * GM * num_n;
+  t.m_tile = first_m + r % gsz;
+  t.n_tile = r / gsz;
+  t.k0 = 0;
+  t.k_blocks = ceil_div(a.K, BK);
+  if (a.mode == KMOE_GEMM_GROUPED_M) {
+    int e = a.tile_group[t.m_tile];
+    t.g_a = 0;
+    t.g_b = e;
+    t.g_c = 0;
+  } else if (a.mode == KMOE_GEMM_BATCHED) {
+    t.g_a = a.a_grouped ? g : 0;
+    t.g_b = a.b_grouped ? g : 0;
+    t.g_c = g;
+    if (a.k_begin != nullptr) {
+      t.k0 = a.k_begin[g];
+      t.k_blocks = ceil_div(a.k_len[g], BK);
+    }
+  } else {
+    t.g_a = t.g_b = t.g_c = 0;
+  }
+  return true;
+}
+
+template <typename T>
+__device__ __forceinline__ void store8(T* dst, const float* v);
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* dst, const float* v) {
+  uint4 o;
+  o.x = pack_bf16(v[0], v[1]);
+  o.y = pack_bf16(v[2], v[3]);
+  o.z = pack_bf16(v[4], v[5]);
+  o.w = pack_bf16(v[6], v[7]);
+  *reinterpret_cast<uint4*>(dst) = o;
+}
+template <>
+__device__ __forceinline__ void store8<float>(float* dst, const float* v) {
+  *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* src, float* v) {
+  uint4 r = *reinterpret_cast<const uint4*>(src);
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(p[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void load8(const float* src, float* v) {
+  float4 a = *reinterpret_cast<const float4*>(src);
+  float4 b = *reinterpret_cast<const float4*>(src + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+// Writes one 32-column chunk of one row: out = alpha*scale*acc + beta*D
+template <typename T>
+__device__ __forceinline__ void epilogue_store_chunk(const GemmArgs& a, const uint32_t (&acc)[32], bool have_acc,
+                                                     long long row_off_c, long long row_off_d, int col, float scale) {
+  T* C = reinterpret_cast<T*>(a.C);
+  const T* D = reinterpret_cast<const T*>(a.D);
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    if (col + j >= a.N) break;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = have_acc ? __uint_as_float(acc[j + i]) * scale : 0.f;
+    if (D != nullptr) {
+      float d[8];
+      load8(D + row_off_d + col + j, d);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += a.beta * d[i];
+    }
+    store8<T>(C + row_off_c + col + j, v);
+  }
+}
+
+template <int BN, int A_MAJOR, int B_MAJOR>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmB2, const GemmArgs args, const int stages) {
+  constexpr int B_STAGE_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators
+  constexpr uint32_t IDESC = make_idesc_f16(BM, BN, /*bf16*/ 1, A_MAJOR, B_MAJOR);
+  constexpr int MAX_STAGES = 8;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[MAX_STAGES];
+  __shared__ uint64_t empty_bar[MAX_STAGES];
+  __shared__ uint64_t tmem_full[2];
+  __shared__ uint64_t tmem_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);  // one arrival per epilogue warp
+    }
+    mbar_fence_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  const bool swiglu = args.epilogue == KMOE_EPI_SWIGLU;
+  const int n_per_tile = swiglu ? BN / 2 : BN;  // output columns per tile
+  int num_m = ceil_div(args.M, BM);
+  if (args.mode == KMOE_GEMM_GROUPED_M) num_m = min(num_m, *args.num_m_tiles);
+  const int num_n = ceil_div(args.N, n_per_tile);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (elect_one()) {
+      int s = 0;
+      uint32_t ph = 0;
+      Tile t;
+      for (int idx = blockIdx.x; get_tile<BN>(args, idx, num_m, num_n, t); idx += gridDim.x) {
+        for (int kb = 0; kb < t.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+            atomicExch(args.status, 1);
+            goto teardown;
+          }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          const int k = t.k0 + kb * BK;
+          if (A_MAJOR == KMOE_MAJOR_K)
+            tma_load_4d(sa, &tmA, &full_bar[s], k, t.m_tile * BM, 0, t.g_a);
+          else
+            tma_load_4d(sa, &tmA, &full_bar[s], 0, k, t.m_tile * (BM / 64), t.g_a);
+          if (!swiglu) {
+            if (B_MAJOR == KMOE_MAJOR_K)
+              tma_load_4d(sb, &tmB, &full_bar[s], k, t.n_tile * BN, 0, t.g_b);
+            else
+              tma_load_4d(sb, &tmB, &full_bar[s], 0, k, t.n_tile * (BN / 64), t.g_b);
+          } else {
+            constexpr int HB = BN / 2;
+            if (B_MAJOR == KMOE_MAJOR_K) {
+              tma_load_4d(sb, &tmB, &full_bar[s], k, t.n_tile * HB, 0, t.g_b);
+              tma_load_4d(sb + B_STAGE_BYTES / 2, &tmB2, &full_bar[s], k, t.n_tile * HB, 0, t.g_b);
+            } else {
+              tma_load_4d(sb, &tmB, &full_bar[s], 0, k, t.n_tile * (HB / 64), t.g_b);
+              tma_load_4d(sb + B_STAGE_BYTES / 2, &tmB2, &full_bar[s], 0, k, t.n_tile * (HB / 64), t.g_b);
+            }
+          }
+          if (++s == stages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      Tile t;
+      for (int idx = blockIdx.x; get_tile<BN>(args, idx, num_m, num_n, t); idx += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_ph = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1)) {
+          atomicExch(args.status, 2);
+          goto teardown;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < t.k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[s], ph)) {
+            atomicExch(args.status, 3);
+            goto teardown;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4) {
+            // K-major: 16 bf16 = 32 B along the swizzled row. MN-major: 16 k-rows of 128 B.
+            const uint32_t a_off = (A_MAJOR == KMOE_MAJOR_K) ? k4 * 32 : k4 * 16 * 128;
+            const uint32_t b_off = (B_MAJOR == KMOE_MAJOR_K) ? k4 * 32 : k4 * 16 * 128;
+            const uint64_t adesc = make_smem_desc_sw128(sa + a_off, (A_MAJOR == KMOE_MAJOR_K) ? 16 : BK * 128, 1024);
+            const uint64_t bdesc = make_smem_desc_sw128(sb + b_off, (B_MAJOR == KMOE_MAJOR_K) ? 16 : BK * 128, 1024);
+            umma_f16(d_tmem, adesc, bdesc, IDESC, (kb > 0 || k4 > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);  // frees the smem stage once these MMAs retire
+          if (++s == stages) { s = 0; ph ^= 1; }
+        }
+        if (t.k_blocks > 0)
+          umma_commit(&tmem_full[acc]);
+        else
+          mbar_arrive(&tmem_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int it = 0;
+    Tile t;
+    for (int idx = blockIdx.x; get_tile<BN>(args, idx, num_m, num_n, t); idx += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_ph = (it >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_ph)) {
+        if (lane == 0) atomicExch(args.status, 4);
+        goto teardown;
+      }
+      tc_fence_after();
+      const bool have_acc = t.k_blocks > 0;
+      const int row = t.m_tile * BM + q * 32 + lane;
+      const bool row_ok = row < args.M;
+      const long long coff = (long long)t.g_c * args.c_gstride + (long long)row * args.ldc;
+      const long long doff = (long long)t.g_c * args.c_gstride + (long long)row * args.ldd;
+      float scale = args.alpha;
+      if (args.row_scale != nullptr && row_ok) scale *= args.row_scale[row];
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      if (!swiglu) {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          if (have_acc) {
+            tmem_ld_32x32(t_row + c, r);
+            tmem_ld_wait();
+          }
+          const int col = t.n_tile * BN + c;
+          if (row_ok && col < args.N) {
+            if (args.out_f32)
+              epilogue_store_chunk<float>(args, r, have_acc, coff, doff, col, scale);
+            else
+              epilogue_store_chunk<__nv_bfloat16>(args, r, have_acc, coff, doff, col, scale);
+          }
+        }
+      } else {
+        constexpr int HB = BN / 2;
+        __nv_bfloat16* H = reinterpret_cast<__nv_bfloat16*>(args.C);
+        __nv_bfloat16* G = reinterpret_cast<__nv_bfloat16*>(args.G_out);
+        __nv_bfloat16* U = reinterpret_cast<__nv_bfloat16*>(args.U_out);
+#pragma unroll 1
+        for (int c = 0; c < HB; c += 32) {
+          uint32_t g[32], u[32];
+          if (have_acc) {
+            tmem_ld_32x32(t_row + c, g);
+            tmem_ld_32x32(t_row + HB + c, u);
+            tmem_ld_wait();
+          }
+          const int col = t.n_tile * HB + c;
+          if (row_ok && col < args.N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col + j >= args.N) break;
+              float gv[8], uv[8], hv[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                gv[i] = have_acc ? __uint_as_float(g[j + i]) : 0.f;
+                uv[i] = have_acc ? __uint_as_float(u[j + i]) : 0.f;
+                hv[i] = silu_f(gv[i]) * uv[i] * scale;
+              }
+              store8<__nv_bfloat16>(H + coff + col + j, hv);
+              if (G != nullptr) store8<__nv_bfloat16>(G + coff + col + j, gv);
+              if (U != nullptr) store8<__nv_bfloat16>(U + coff + col + j, uv);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+teardown:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+using TmapKey = std::tuple<const void*, int, long long, long long, long long, long long, int, int>;
+static std::map<TmapKey, CUtensorMap> g_tmap_cache;
+static std::mutex g_tmap_mutex;
+
+// Operand tensor map (bf16, 128B swizzle), always rank 4 so one TMA instruction form serves all cases.
+//   K-major : dims {K, rows, 1, G}       box {64, tile_rows, 1, 1}
+//   MN-major: dims {64, K, rows/64, G}   box {64, 64, tile_rows/64, 1}   (memory is [K][rows], rows contiguous)
+static int make_operand_tmap(CUtensorMap* out, const void* base, int major, long long rows, long long K,
+                             long long ld, long long gstride, int groups, int tile_rows) {
+  TmapKey key{base, major, rows, K, ld, gstride, groups, tile_rows};
+  {
+    std::lock_guard<std::mutex> lk(g_tmap_mutex);
+    auto it = g_tmap_cache.find(key);
+    if (it != g_tmap_cache.end()) {
+      *out = it->second;
+      return 0;
+    }
+  }
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return -10;
+  cuuint64_t dims[4];
+  cuuint64_t strides[3];
+  cuuint32_t box[4];
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const long long gs = (groups > 1 && gstride > 0) ? gstride : (major == KMOE_MAJOR_K ? rows * ld : K * ld);
+  const int G = (groups > 1 && gstride > 0) ? groups : 1;
+  if (major == KMOE_MAJOR_K) {
+    dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)rows; dims[2] = 1; dims[3] = (cuuint64_t)G;
+    strides[0] = (cuuint64_t)ld * 2; strides[1] = (cuuint64_t)rows * ld * 2; strides[2] = (cuuint64_t)gs * 2;
+    box[0] = BK; box[1] = (cuuint32_t)tile_rows; box[2] = 1; box[3] = 1;
+  } else {
+    if (rows % 64 != 0) return -11;
+    dims[0] = 64; dims[1] = (cuuint64_t)K; dims[2] = (cuuint64_t)(rows / 64); dims[3] = (cuuint64_t)G;
+    strides[0] = (cuuint64_t)ld * 2; strides[1] = 128; strides[2] = (cuuint64_t)gs * 2;
+    box[0] = 64; box[1] = BK; box[2] = (cuuint32_t)(tile_rows / 64); box[3] = 1;
+  }
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] % 16 != 0) return -12;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return -13;
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -14;
+  {
+    std::lock_guard<std::mutex> lk(g_tmap_mutex);
+    if (g_tmap_cache.size() > 4096) g_tmap_cache.clear();
+    g_tmap_cache[key] = *out;
+  }
+  return 0;
+}
+
+template <int BN, int AM, int BMj>
+static int launch_variant(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const GemmArgs& args,
+                          int grid, cudaStream_t stream) {
+  constexpr int stage_bytes = A_STAGE_BYTES + BN * BK * 2;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > 8) stages = 8;
+  const int smem = stages * stage_bytes + 1024;
+  auto kern = umma_gemm_kernel<BN, AM, BMj>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -20;
+    attr_set = true;
+  }
+  kern<<<grid, NUM_THREADS, smem, stream>>>(tA, tB, tB2, args, stages);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+}  // namespace kmoe
+
+extern "C" void kmoe_gemm_clear_tensormap_cache(void) {
+  std::lock_guard<std::mutex> lk(kmoe::g_tmap_mutex);
+  kmoe::g_tmap_cache.clear();
+}
+
+extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
+  using namespace kmoe;
+  if (d->K % 8 != 0 || d->N % 8 != 0) return -1;
+  if (d->K <= 0 || d->M <= 0 || d->N <= 0) return -2;
+  const bool swiglu = d->epilogue == KMOE_EPI_SWIGLU;
+  // narrow outputs use the 128-wide tile so more CTAs get work
+  const int n_tiles_256 = (d->N + (swiglu ? 127 : 255)) / (swiglu ? 128 : 256);
+  const long long m_tiles = (d->M + BM - 1) / BM;
+  const long long groups = d->mode == KMOE_GEMM_BATCHED ? d->groups : 1;
+  int sms = d->num_sms;
+  if (sms <= 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const bool use256 = swiglu || (m_tiles * n_tiles_256 * groups >= sms && d->N >= 256);
+  const int BN = use256 ? 256 : 128;
+  const int b_box_rows = swiglu ? BN / 2 : BN;
+
+  GemmArgs a;
+  a.C = d->C; a.D = d->D; a.G_out = d->G_out; a.U_out = d->U_out;
+  a.mode = d->mode; a.epilogue = d->epilogue;
+  a.M = d->M; a.N = d->N; a.K = d->K; a.groups = d->groups;
+  a.ldc = d->ldc; a.ldd = d->ldd ? d->ldd : d->ldc; a.c_gstride = d->c_gstride;
+  a.a_grouped = d->a_gstride != 0; a.b_grouped = d->b_gstride != 0;
+  a.tile_group = d->tile_group; a.num_m_tiles = d->num_m_tiles;
+  a.k_begin = d->k_begin; a.k_len = d->k_len;
+  a.out_f32 = d->out_f32; a.alpha = d->alpha; a.beta = d->beta;
+  a.row_scale = d->row_scale; a.status = d->status;
+
+  // The reduction extent seen by TMA: ragged batched GEMMs index a shared [sum K, rows] buffer.
+  long long k_extent_a = d->K, k_extent_b = d->K;
+  if (d->mode == KMOE_GEMM_BATCHED && d->k_begin != nullptr) {
+    k_extent_a = d->a_gstride == 0 ? (long long)d->K : d->K;
+    k_extent_b = k_extent_a;
+  }
+  const int a_groups = (d->mode == KMOE_GEMM_BATCHED && d->a_gstride != 0) ? d->groups : 1;
+  const int b_groups = d->b_gstride != 0 ? d->groups : 1;
+  CUtensorMap tA, tB, tB2;
+  int rc = make_operand_tmap(&tA, d->A, d->a_major, d->M, k_extent_a, d->lda, d->a_gstride, a_groups, BM);
+  if (rc) return rc;
+  rc = make_operand_tmap(&tB, d->B, d->b_major, d->N, k_extent_b, d->ldb, d->b_gstride, b_groups, b_box_rows);
+  if (rc) return rc;
+  if (swiglu) {
+    rc = make_operand_tmap(&tB2, d->B2, d->b_major, d->N, k_extent_b, d->ldb, d->b_gstride, b_groups, b_box_rows);
+    if (rc) return rc;
+  } else {
+    tB2 = tB;
+  }
+  const int n_per_tile = swiglu ? BN / 2 : BN;
+  long long total = m_tiles * ((d->N + n_per_tile - 1) / n_per_tile) * groups;
+  int grid = (int)(total < sms ? total : sms);
+  if (grid < 1) grid = 1;
+
+#define KMOE_LAUNCH(BN_, AM_, BM_) return launch_variant<BN_, AM_, BM_>(tA, tB, tB2, a, grid, stream)
+  if (BN == 256) {
+    if (d->a_major == 0 && d->b_major == 0) KMOE_LAUNCH(256, 0, 0);
+    if (d->a_major == 0 && d->b_major == 1) KMOE_LAUNCH(256, 0, 1);
+    if (d->a_major == 1 && d->b_major == 0) KMOE_LAUNCH(256, 1, 0);
+    KMOE_LAUNCH(256, 1, 1);
+  } else {
+    if (d->a_major == 0 && d->b_major == 0) KMOE_LAUNCH(128, 0, 0);
+    if (d->a_major == 0 && d->b_major == 1) KMOE_LAUNCH(128, 0, 1);
+    if (d->a_major == 1 && d->b_major == 0) KMOE_LAUNCH(128, 1, 0);
+    KMOE_LAUNCH(128, 1, 1);
+  }
+#undef KMOE_LAUNCH
+}

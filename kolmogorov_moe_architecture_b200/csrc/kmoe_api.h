@@ -1,0 +1,92 @@
+// C launch interface of the CUDA kernels.  Everything takes raw device pointers
+// and a stream; the PyTorch bindings (bindings.cpp) and any other host can call
+// these directly.  All functions return 0 on success or a negative error code.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ------------------------------------------------------------------ tcgen05 GEMM
+// C[M,N] = alpha * A[M,K] * B[N,K]^T (+ beta * D), bf16 operands, fp32 accumulation in TMEM.
+enum { KMOE_GEMM_DENSE = 0, KMOE_GEMM_GROUPED_M = 1, KMOE_GEMM_BATCHED = 2 };
+enum { KMOE_EPI_STORE = 0, KMOE_EPI_SWIGLU = 1 };
+enum { KMOE_MAJOR_K = 0, KMOE_MAJOR_MN = 1 };
+
+typedef struct KmoeGemmDesc {
+  const void* A;        // bf16. K-major: [rows, K] (lda); MN-major: [K, rows] (lda)
+  const void* B;        // bf16. K-major: [N, K] (ldb);    MN-major: [K, N] (ldb)
+  const void* B2;       // SWIGLU epilogue only: second weight (same layout as B)
+  void* C;              // bf16 or fp32 output, row-major [M, N] (ldc)
+  const void* D;        // optional addend with C's type and ldd
+  void* G_out;          // SWIGLU only, optional: pre-activation gate, [M, N] bf16 (ldc)
+  void* U_out;          // SWIGLU only, optional: up projection
+  int mode;             // KMOE_GEMM_*
+  int epilogue;         // KMOE_EPI_*
+  int M, N, K;          // per-group dims. GROUPED_M: M = rows of the whole padded buffer
+  int groups;           // GROUPED_M: number of B groups; BATCHED: number of independent GEMMs
+  int a_major, b_major;
+  long long lda, ldb, ldc, ldd;
+  long long a_gstride, b_gstride, c_gstride;  // elements between groups (0 = shared)
+  // GROUPED_M: m-tile i covers rows [128 i, 128 i + 128) of A and C and uses B group tile_group[i];
+  // *num_m_tiles (device) tiles are live.
+  const int* tile_group;
+  const int* num_m_tiles;
+  // BATCHED, optional ragged reduction range per group, in elements of K (multiples of 64).
+  const int* k_begin;
+  const int* k_len;
+  int out_f32;
+  float alpha, beta;
+  const float* row_scale;  // optional per-row multiplier applied to the product
+  int* status;             // device int; non-zero after the launch = a bounded wait expired
+  int num_sms;             // 0 = query
+} KmoeGemmDesc;
+
+int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream);
+void kmoe_gemm_clear_tensormap_cache(void);
+
+// ------------------------------------------------------------ row kernels (bf16 data, fp32 math)
+int kmoe_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int d, float eps, cudaStream_t st);
+int kmoe_rmsnorm_bwd_num_partials(int rows);
+int kmoe_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx, void* dw_bf16,
+                     float* dw_f32, float* partial, int rows, int d, cudaStream_t st);
+int kmoe_rope(const void* x, const float* cs, const float* sn, void* out, int B, int S, int H, int D,
+              long long cs_bstride, int transpose, cudaStream_t st);
+int kmoe_swiglu_fwd(const void* g, const void* u, void* h, long long rows, int cols, long long ldg, long long ldu,
+                    cudaStream_t st);
+int kmoe_swiglu_bwd(const void* g, const void* u, const void* dh, void* dg, void* du, long long rows, int cols,
+                    long long ldg, long long ldu, long long ldo, cudaStream_t st);
+
+// --------------------------------------------------------------------------- Mamba
+int kmoe_conv1d_fwd(const void* x, const float* w, const float* bias, void* y, int B, int S, int C, long long ldx,
+                    int act, cudaStream_t st);
+int kmoe_conv1d_bwd(const void* x, const float* w, const float* bias, const void* dy, void* dx, float* dw,
+                    float* dbias, int B, int S, int C, long long ldx, int act, cudaStream_t st);
+int kmoe_scan_chunk(void);
+int kmoe_scan_fwd(const void* u, const void* delta, const void* z, const float* A, const float* Bm, const float* Cm,
+                  const float* D, const float* dt_bias, void* out, float* ckpt, int B, int S, int C, int N,
+                  long long ldz, int softplus, cudaStream_t st);
+int kmoe_scan_bwd(const void* u, const void* delta, const void* z, const float* A, const float* Bm, const float* Cm,
+                  const float* D, const float* dt_bias, const void* dout, const float* ckpt, void* du, void* ddelta,
+                  void* dz, long long lddz, float* dA, float* dB, float* dC, float* dD, float* dbias, int B, int S,
+                  int C, int N, long long ldz, int softplus, cudaStream_t st);
+
+// ------------------------------------------------------------------- MoE bookkeeping
+int kmoe_moe_max_rows(int n_assign, int E);
+int kmoe_moe_plan(const long long* idx, const unsigned char* keep, int n, int E, int max_rows, int expert_base,
+                  int* pos, int* row_src, int* counts, int* offsets, int* tile_group, int* meta, cudaStream_t st);
+int kmoe_moe_gather_rows(const void* src, const int* row_src, const float* assign_scale, const int* meta, void* dst,
+                         int max_rows, int d, int div, cudaStream_t st);
+int kmoe_moe_combine(const void* Y, const int* pos, const float* w, void* out, int T, int k, int d, cudaStream_t st);
+int kmoe_moe_combine_dw(const void* Y, const void* dout, const int* pos, float* dw, int n, int k, int d,
+                        cudaStream_t st);
+
+// ---------------------------------------------------------------------------- loss
+int kmoe_ce_fwd_bwd(void* logits, const long long* labels, float* loss_rows, const float* grad_scale, int R, int V,
+                    long long ld, long long ignore_index, int write_grad, cudaStream_t st);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,227 @@
+// Token-choice MoE bookkeeping without host synchronisation.
+//
+// Layout ("padded expert-major"): the assignments of expert e occupy rows
+// [off[e], off[e] + cnt[e]) of a [max_rows, d] buffer, with off[e] a multiple of 128,
+// so a 128-row GEMM tile never spans two experts; rows between cnt[e] and the next
+// multiple of 128 are zero.  Within an expert, rows keep (token, slot) order - the
+// sort is stable, so results are deterministic.  max_rows = T*k + E*127 rounded up
+// is a static bound, which keeps every buffer shape fixed across steps.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "kmoe_api.h"
+#include "ptx.cuh"
+
+namespace kmoe {
+
+constexpr int PLAN_THREADS = 256;
+constexpr int ROW_TILE = 128;
+
+// Single-block stable counting sort of n = T*k assignments over E experts.
+//   idx      [n] int64 expert of each assignment (flat (token, slot) order)
+//   keep     [n] bool/uint8 or null: 0 = dropped assignment
+//   pos      [n] int32  row of the assignment in the padded layout, -1 if dropped
+//   row_src  [max_rows] int32 flat assignment index feeding each row, -1 for padding
+//   counts   [E] int32 ; offsets [E+1] int32 (padded) ; tile_group [max_rows/128] ; meta[0] = live m-tiles,
+//   meta[1] = live padded rows
+__global__ void __launch_bounds__(PLAN_THREADS)
+moe_plan_kernel(const long long* __restrict__ idx, const unsigned char* __restrict__ keep, int n, int E, int max_rows,
+                int expert_base, int* __restrict__ pos, int* __restrict__ row_src, int* __restrict__ counts,
+                int* __restrict__ offsets, int* __restrict__ tile_group, int* __restrict__ meta) {
+  extern __shared__ int sh[];     // hist[PLAN_THREADS][E] then off[E+1]
+  int* hist = sh;
+  int* off = sh + PLAN_THREADS * E;
+  const int tid = threadIdx.x;
+  const int seg = (n + PLAN_THREADS - 1) / PLAN_THREADS;
+  const int lo = min(tid * seg, n), hi = min(lo + seg, n);
+  for (int e = 0; e < E; ++e) hist[tid * E + e] = 0;
+  for (int i = tid; i < max_rows; i += PLAN_THREADS) row_src[i] = -1;
+  for (int i = lo; i < hi; ++i) {
+    const int e = (int)idx[i] - expert_base;
+    if (e >= 0 && e < E && (keep == nullptr || keep[i])) hist[tid * E + e]++;
+  }
+  __syncthreads();
+  // exclusive scan over threads, one expert per thread
+  for (int e = tid; e < E; e += PLAN_THREADS) {
+    int run = 0;
+    for (int t = 0; t < PLAN_THREADS; ++t) {
+      const int v = hist[t * E + e];
+      hist[t * E + e] = run;
+      run += v;
+    }
+    counts[e] = run;
+    off[e] = run;  // temporarily the count
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      const int cnt = off[e];
+      off[e] = run;
+      offsets[e] = run;
+      const int nt = (cnt + ROW_TILE - 1) / ROW_TILE;
+      for (int j = 0; j < nt; ++j) tile_group[tiles + j] = e;
+      tiles += nt;
+      run += nt * ROW_TILE;
+    }
+    off[E] = run;
+    offsets[E] = run;
+    meta[0] = tiles;
+    meta[1] = run;
+    for (int j = tiles; j < max_rows / ROW_TILE; ++j) tile_group[j] = 0;
+  }
+  __syncthreads();
+  for (int i = lo; i < hi; ++i) {
+    const int e = (int)idx[i] - expert_base;
+    int p = -1;
+    if (e >= 0 && e < E && (keep == nullptr || keep[i])) {
+      p = off[e] + hist[tid * E + e]++;
+      if (p < max_rows) row_src[p] = i; else p = -1;
+    }
+    pos[i] = p;
+  }
+}
+
+// dst[row] = scale(row) * src[row_src[row] / div]  (zero for padding rows), rows < meta[1].
+//   row_scale: optional fp32 per *assignment* multiplier (indexed by row_src), used by the
+//   backward of the combine: dY[row] = w[assignment] * dout[token].
+__global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ row_src,
+                                       const float* __restrict__ assign_scale, const int* __restrict__ meta,
+                                       __nv_bfloat16* __restrict__ dst, int max_rows, int d, int div) {
+  const int live_rows = min(meta[1], max_rows);
+  const int vec = d / 8;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < live_rows; row += warps) {
+    const int a = row_src[row];
+    uint4* drow = reinterpret_cast<uint4*>(dst + (size_t)row * d);
+    if (a < 0) {
+      for (int v = lane; v < vec; v += 32) drow[v] = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    const uint4* srow = reinterpret_cast<const uint4*>(src + (size_t)(a / div) * d);
+    if (assign_scale == nullptr) {
+      for (int v = lane; v < vec; v += 32) drow[v] = srow[v];
+    } else {
+      const float s = assign_scale[a];
+      for (int v = lane; v < vec; v += 32) {
+        uint4 r = srow[v];
+        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 f = __bfloat1622float2(p[i]);
+          p[i] = __floats2bfloat162_rn(f.x * s, f.y * s);
+        }
+        drow[v] = r;
+      }
+    }
+  }
+}
+
+// out[t] = sum_k w[t,k] * Y[pos[t,k]]   (pos < 0 skipped; w null = 1).  One warp per token.
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ Y, const int* __restrict__ pos,
+                                   const float* __restrict__ w, __nv_bfloat16* __restrict__ out, int T, int k, int d) {
+  const int vec = d / 8;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < T; t += warps) {
+    for (int v = lane; v < vec; v += 32) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int j = 0; j < k; ++j) {
+        const int p = pos[t * k + j];
+        if (p < 0) continue;
+        const float s = w ? w[t * k + j] : 1.f;
+        uint4 r = *reinterpret_cast<const uint4*>(Y + (size_t)p * d + v * 8);
+        const __nv_bfloat162* q = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 f = __bfloat1622float2(q[i]);
+          acc[2 * i] += s * f.x;
+          acc[2 * i + 1] += s * f.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16(acc[0], acc[1]);
+      o.y = pack_bf16(acc[2], acc[3]);
+      o.z = pack_bf16(acc[4], acc[5]);
+      o.w = pack_bf16(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(out + (size_t)t * d + v * 8) = o;
+    }
+  }
+}
+
+// dw[t,k] = <dout[t], Y[pos[t,k]]>.  One warp per assignment.
+__global__ void moe_combine_dw_kernel(const __nv_bfloat16* __restrict__ Y, const __nv_bfloat16* __restrict__ dout,
+                                      const int* __restrict__ pos, float* __restrict__ dw, int n, int k, int d) {
+  const int vec = d / 8;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int a = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; a < n; a += warps) {
+    const int p = pos[a];
+    float s = 0.f;
+    if (p >= 0) {
+      const uint4* yr = reinterpret_cast<const uint4*>(Y + (size_t)p * d);
+      const uint4* gr = reinterpret_cast<const uint4*>(dout + (size_t)(a / k) * d);
+      for (int v = lane; v < vec; v += 32) {
+        uint4 r1 = yr[v], r2 = gr[v];
+        const __nv_bfloat162* q1 = reinterpret_cast<const __nv_bfloat162*>(&r1);
+        const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(&r2);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 f1 = __bfloat1622float2(q1[i]), f2 = __bfloat1622float2(q2[i]);
+          s += f1.x * f2.x + f1.y * f2.y;
+        }
+      }
+    }
+    s = warp_sum(s);
+    if (lane == 0) dw[a] = s;
+  }
+}
+
+}  // namespace kmoe
+
+using namespace kmoe;
+
+extern "C" int kmoe_moe_max_rows(int n_assign, int E) {
+  const int r = n_assign + E * (ROW_TILE - 1);
+  return (r + ROW_TILE - 1) / ROW_TILE * ROW_TILE;
+}
+
+extern "C" int kmoe_moe_plan(const long long* idx, const unsigned char* keep, int n, int E, int max_rows,
+                             int expert_base, int* pos, int* row_src, int* counts, int* offsets, int* tile_group,
+                             int* meta, cudaStream_t st) {
+  const size_t smem = ((size_t)PLAN_THREADS * E + E + 1) * sizeof(int);
+  if (smem > 200 * 1024) return -1;
+  static size_t attr_set = 0;
+  if (smem > 48 * 1024 && smem > attr_set) {
+    if (cudaFuncSetAttribute(moe_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return -3;
+    attr_set = smem;
+  }
+  moe_plan_kernel<<<1, PLAN_THREADS, smem, st>>>(idx, keep, n, E, max_rows, expert_base, pos, row_src, counts,
+                                                 offsets, tile_group, meta);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_moe_gather_rows(const void* src, const int* row_src, const float* assign_scale, const int* meta,
+                                    void* dst, int max_rows, int d, int div, cudaStream_t st) {
+  if (d % 8) return -1;
+  moe_gather_rows_kernel<<<148 * 4, 256, 0, st>>>((const __nv_bfloat16*)src, row_src, assign_scale, meta,
+                                                  (__nv_bfloat16*)dst, max_rows, d, div);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_moe_combine(const void* Y, const int* pos, const float* w, void* out, int T, int k, int d,
+                                cudaStream_t st) {
+  if (d % 8) return -1;
+  moe_combine_kernel<<<148 * 4, 256, 0, st>>>((const __nv_bfloat16*)Y, pos, w, (__nv_bfloat16*)out, T, k, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_moe_combine_dw(const void* Y, const void* dout, const int* pos, float* dw, int n, int k, int d,
+                                   cudaStream_t st) {
+  if (d % 8) return -1;
+  moe_combine_dw_kernel<<<148 * 4, 256, 0, st>>>((const __nv_bfloat16*)Y, (const __nv_bfloat16*)dout, pos, dw, n, k,
+                                                 d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

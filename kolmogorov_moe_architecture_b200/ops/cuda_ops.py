@@ -1,0 +1,449 @@
+"""CUDA implementations of the hot ops: autograd wrappers over ``torch.ops.kmoe``.
+
+Kernels work on bf16 activations with fp32 accumulation.  A call whose dtype or
+shape a kernel does not cover (fp32 activations, a dimension that is not a
+multiple of the kernel's vector / tile granularity) is evaluated by the PyTorch
+definition in :mod:`.eager`; ``KMOE_STRICT=1`` turns that into an error, which
+the GPU tests set so that a kernel path cannot be skipped unnoticed.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+
+from . import eager
+from .loader import require_ext
+
+require_ext()
+K = torch.ops.kmoe
+
+DENSE, GROUPED_M, BATCHED = 0, 1, 2
+EPI_STORE, EPI_SWIGLU = 0, 1
+MAJ_K, MAJ_MN = 0, 1
+
+_STATUS = {}
+LAUNCHES = {"count": 0}       # number of kernels of this library launched (bench accounting)
+
+
+def _strict() -> bool:
+    return os.environ.get("KMOE_STRICT", "0") == "1"
+
+
+def _fallback(name: str, why: str):
+    if _strict():
+        raise RuntimeError(f"kmoe.{name}: no CUDA kernel for this call ({why}) and KMOE_STRICT=1")
+
+
+def status_tensor(device) -> torch.Tensor:
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    t = _STATUS.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+        _STATUS[key] = t
+    return t
+
+
+def check_status(device=None) -> None:
+    """Raise if any kernel since the last check gave up on a bounded wait.  Synchronises."""
+    for key, t in list(_STATUS.items()):
+        v = int(t.item())
+        if v != 0:
+            t.zero_()
+            raise RuntimeError(f"kmoe kernel on cuda:{key} reported wait-timeout status {v}")
+
+
+def _count(n: int = 1):
+    LAUNCHES["count"] += n
+
+
+# ---------------------------------------------------------------------- GEMM
+def gemm(A, B, C, *, M, N, Kd, mode=DENSE, epi=EPI_STORE, groups=1, a_major=MAJ_K, b_major=MAJ_K,
+         lda, ldb, ldc, ldd=0, a_gs=0, b_gs=0, c_gs=0, B2=None, D=None, G=None, U=None,
+         tile_group=None, num_m_tiles=None, k_begin=None, k_len=None, alpha=1.0, beta=0.0, row_scale=None):
+    K.gemm(A, B, B2, C, D, G, U, mode, epi, M, N, Kd, groups, a_major, b_major, lda, ldb, ldc, ldd,
+           a_gs, b_gs, c_gs, tile_group, num_m_tiles, k_begin, k_len, alpha, beta, row_scale,
+           status_tensor(A.device))
+    _count()
+    return C
+
+
+def mm_nt(a: torch.Tensor, b: torch.Tensor, out=None, out_dtype=None, D=None, alpha=1.0, beta=0.0):
+    """a [M,K] @ b[N,K]^T -> [M,N]."""
+    M, Kd = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or a.dtype, device=a.device)
+    return gemm(a, b, out, M=M, N=N, Kd=Kd, lda=a.stride(0), ldb=b.stride(0), ldc=out.stride(0),
+                ldd=D.stride(0) if D is not None else 0, D=D, alpha=alpha, beta=beta)
+
+
+def mm_nn(a: torch.Tensor, b: torch.Tensor, out=None, out_dtype=None, D=None, alpha=1.0, beta=0.0):
+    """a [M,K] @ b[K,N] -> [M,N]  (b is read MN-major; N % 64 == 0)."""
+    M, Kd = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or a.dtype, device=a.device)
+    return gemm(a, b, out, M=M, N=N, Kd=Kd, b_major=MAJ_MN, lda=a.stride(0), ldb=b.stride(0),
+                ldc=out.stride(0), ldd=D.stride(0) if D is not None else 0, D=D, alpha=alpha, beta=beta)
+
+
+def mm_tn(a: torch.Tensor, b: torch.Tensor, out=None, out_dtype=None, D=None, alpha=1.0, beta=0.0):
+    """a[K,M]^T @ b[K,N] -> [M,N]  (both read MN-major; M, N % 64 == 0)."""
+    Kd, M = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or a.dtype, device=a.device)
+    return gemm(a, b, out, M=M, N=N, Kd=Kd, a_major=MAJ_MN, b_major=MAJ_MN, lda=a.stride(0),
+                ldb=b.stride(0), ldc=out.stride(0), ldd=D.stride(0) if D is not None else 0, D=D,
+                alpha=alpha, beta=beta)
+
+
+def _bf16(t: torch.Tensor) -> bool:
+    return t.dtype == torch.bfloat16
+
+
+# ------------------------------------------------------------------- RMSNorm
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        xc = x.contiguous()
+        y, rstd = K.rmsnorm_fwd(xc, w.contiguous(), eps)
+        _count()
+        ctx.save_for_backward(xc, w, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rstd = ctx.saved_tensors
+        dx, dw = K.rmsnorm_bwd(x, w.contiguous(), dy.contiguous(), rstd)
+        _count(2)
+        return dx, dw.to(w.dtype), None
+
+
+def rmsnorm(x, weight, eps):
+    if not (_bf16(x) and _bf16(weight) and x.shape[-1] % 8 == 0):
+        _fallback("rmsnorm", f"dtype {x.dtype}/{weight.dtype}")
+        return eager.rmsnorm(x, weight, eps)
+    return _RMSNorm.apply(x, weight, eps)
+
+
+# ---------------------------------------------------------------------- RoPE
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        ctx.save_for_backward(cos, sin)
+        _count()
+        return K.rope(x.contiguous(), cos, sin, False)
+
+    @staticmethod
+    def backward(ctx, g):
+        cos, sin = ctx.saved_tensors
+        _count()
+        return K.rope(g.contiguous(), cos, sin, True), None, None
+
+
+def rope_apply(x, cos, sin):
+    if not (_bf16(x) and x.dim() == 4 and x.shape[-1] % 16 == 0):
+        _fallback("rope", f"dtype {x.dtype}")
+        return eager.rope_apply(x, cos, sin)
+    return _Rope.apply(x, cos.float().contiguous(), sin.float().contiguous())
+
+
+# -------------------------------------------------------------------- SwiGLU
+def _rows_ok(t: torch.Tensor) -> bool:
+    if t.stride(-1) != 1 or t.dim() < 2:
+        return False
+    if t.stride(-2) % 8:
+        return False
+    for i in range(t.dim() - 3, -1, -1):
+        if t.size(i) != 1 and t.stride(i) != t.stride(i + 1) * t.size(i + 1):
+            return False
+    return True
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, g, u):
+        ctx.save_for_backward(g, u)
+        _count()
+        return K.swiglu_fwd(g, u)
+
+    @staticmethod
+    def backward(ctx, dh):
+        g, u = ctx.saved_tensors
+        _count()
+        dg, du = K.swiglu_bwd(g, u, dh.contiguous())
+        return dg, du
+
+
+def swiglu(gate, up):
+    if not (_bf16(gate) and _bf16(up) and gate.shape[-1] % 8 == 0):
+        _fallback("swiglu", f"dtype {gate.dtype}")
+        return eager.swiglu(gate, up)
+    if not _rows_ok(gate):
+        gate = gate.contiguous()
+    if not _rows_ok(up):
+        up = up.contiguous()
+    return _SwiGLU.apply(gate, up)
+
+
+# --------------------------------------------------------------------- Mamba
+class _Conv1d(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, act):
+        wf = w.float().contiguous()
+        bf = b.float().contiguous() if b is not None else None
+        ctx.save_for_backward(x, wf, bf)
+        ctx.act, ctx.wdt, ctx.bdt = act, w.dtype, (b.dtype if b is not None else None)
+        _count()
+        return K.conv1d_fwd(x, wf, bf, act)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, wf, bf = ctx.saved_tensors
+        dx, dw, db = K.conv1d_bwd(x, wf, bf, dy.contiguous(), ctx.act)
+        _count()
+        return dx, dw.to(ctx.wdt), (db.to(ctx.bdt) if bf is not None else None), None
+
+
+def causal_conv1d(x, weight, bias, activation=True):
+    if not (_bf16(x) and weight.shape[1] == 4 and x.dim() == 3):
+        _fallback("causal_conv1d", f"dtype {x.dtype} width {weight.shape[1]}")
+        return eager.causal_conv1d(x, weight, bias, activation)
+    if not _rows_ok(x):
+        x = x.contiguous()
+    return _Conv1d.apply(x, weight, bias, bool(activation))
+
+
+class _Scan(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, u, delta, A, Bm, Cm, D, z, dt_bias, softplus):
+        Af = A.float().contiguous()
+        Bf, Cf = Bm.float().contiguous(), Cm.float().contiguous()
+        Df = D.float().contiguous() if D is not None else None
+        bf = dt_bias.float().contiguous() if dt_bias is not None else None
+        need = any(ctx.needs_input_grad)
+        out, ckpt = K.scan_fwd(u, delta, z, Af, Bf, Cf, Df, bf, softplus, need)
+        _count()
+        ctx.save_for_backward(u, delta, z, Af, Bf, Cf, Df, bf, ckpt)
+        ctx.softplus = softplus
+        ctx.dtypes = (A.dtype, Bm.dtype, Cm.dtype, D.dtype if D is not None else None,
+                      dt_bias.dtype if dt_bias is not None else None)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        u, delta, z, Af, Bf, Cf, Df, bf, ckpt = ctx.saved_tensors
+        du, dd, dz, dA, dB, dC, dD, dbias = K.scan_bwd(u, delta, z, Af, Bf, Cf, Df, bf, dout.contiguous(),
+                                                       ckpt, ctx.softplus)
+        _count()
+        a_dt, b_dt, c_dt, d_dt, bias_dt = ctx.dtypes
+        return (du, dd, dA.to(a_dt), dB.to(b_dt), dC.to(c_dt), dD.to(d_dt) if Df is not None else None,
+                dz if z is not None else None, dbias.to(bias_dt) if bf is not None else None, None)
+
+
+def selective_scan(u, delta, A, Bm, Cm, D, z, delta_bias, delta_softplus=True):
+    if not (_bf16(u) and _bf16(delta) and A.shape[1] == 16 and (z is None or _bf16(z))):
+        _fallback("selective_scan", f"dtype {u.dtype} d_state {A.shape[1]}")
+        return eager.selective_scan(u, delta, A, Bm, Cm, D, z, delta_bias, delta_softplus)
+    u, delta = u.contiguous(), delta.contiguous()
+    if z is not None and not _rows_ok(z):
+        z = z.contiguous()
+    return _Scan.apply(u, delta, A, Bm, Cm, D, z, delta_bias, bool(delta_softplus))
+
+
+# ----------------------------------------------------------------- attention
+def attention(q, k, v, causal=True):
+    from . import attention_cuda
+    return attention_cuda.attention(q, k, v, causal)
+
+
+# ------------------------------------------------------------- MoE experts
+class _GroupedSwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w1, w2, w3, idx, weights, keep):
+        T, d = x.shape
+        E, _, f = w1.shape
+        k = idx.shape[1]
+        idx_flat = idx.reshape(-1).contiguous()
+        pos, row_src, counts, offsets, tile_group, meta = K.moe_plan(idx_flat, keep.reshape(-1) if keep is not None else None, E, 0)
+        max_rows = row_src.numel()
+        xc = x.contiguous()
+        Xp = K.moe_gather_rows(xc, row_src, None, meta, k)
+        H = torch.empty(max_rows, f, dtype=x.dtype, device=x.device)
+        G, U = torch.empty_like(H), torch.empty_like(H)
+        nmt = meta[0:1]
+        gemm(Xp, w1, H, B2=w2, G=G, U=U, mode=GROUPED_M, epi=EPI_SWIGLU, M=max_rows, N=f, Kd=d, groups=E,
+             b_major=MAJ_MN, lda=d, ldb=f, ldc=f, b_gs=d * f, tile_group=tile_group, num_m_tiles=nmt)
+        Y = torch.empty(max_rows, d, dtype=x.dtype, device=x.device)
+        gemm(H, w3, Y, mode=GROUPED_M, M=max_rows, N=d, Kd=f, groups=E, b_major=MAJ_MN, lda=f, ldb=d, ldc=d,
+             b_gs=f * d, tile_group=tile_group, num_m_tiles=nmt)
+        wf = weights.reshape(-1).float().contiguous()
+        out = K.moe_combine(Y, pos, wf, T, k)
+        _count(3)
+        ctx.save_for_backward(Xp, G, U, Y, w1, w2, w3, wf, pos, row_src, offsets, tile_group, meta)
+        ctx.dims = (T, d, E, f, k, max_rows)
+        ctx.wdtype = weights.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        Xp, G, U, Y, w1, w2, w3, wf, pos, row_src, offsets, tile_group, meta = ctx.saved_tensors
+        T, d, E, f, k, max_rows = ctx.dims
+        dout = dout.contiguous()
+        nmt = meta[0:1]
+        dYp = K.moe_gather_rows(dout, row_src, wf, meta, k)
+        dwts = K.moe_combine_dw(Y, dout, pos, k).view(T, k).to(ctx.wdtype)
+        dH = torch.empty(max_rows, f, dtype=dout.dtype, device=dout.device)
+        gemm(dYp, w3, dH, mode=GROUPED_M, M=max_rows, N=f, Kd=d, groups=E, lda=d, ldb=d, ldc=f, b_gs=f * d,
+             tile_group=tile_group, num_m_tiles=nmt)
+        dG, dU = K.swiglu_bwd(G, U, dH)
+        dXp = torch.empty(max_rows, d, dtype=dout.dtype, device=dout.device)
+        gemm(dG, w1, dXp, mode=GROUPED_M, M=max_rows, N=d, Kd=f, groups=E, lda=f, ldb=f, ldc=d, b_gs=d * f,
+             tile_group=tile_group, num_m_tiles=nmt)
+        gemm(dU, w2, dXp, D=dXp, beta=1.0, mode=GROUPED_M, M=max_rows, N=d, Kd=f, groups=E, lda=f, ldb=f,
+             ldc=d, ldd=d, b_gs=d * f, tile_group=tile_group, num_m_tiles=nmt)
+        dx = K.moe_combine(dXp, pos, None, T, k)
+        # weight gradients: per expert, reduction over that expert's (padded) row range
+        kb = offsets[:E].contiguous()
+        kl = (offsets[1:] - offsets[:E]).contiguous()
+        H = K.swiglu_fwd(G, U)
+        dw1 = torch.empty_like(w1)
+        dw2 = torch.empty_like(w2)
+        dw3 = torch.empty_like(w3)
+        common = dict(mode=BATCHED, groups=E, a_major=MAJ_MN, b_major=MAJ_MN, Kd=max_rows, k_begin=kb, k_len=kl)
+        gemm(Xp, dG, dw1, M=d, N=f, lda=d, ldb=f, ldc=f, c_gs=d * f, **common)
+        gemm(Xp, dU, dw2, M=d, N=f, lda=d, ldb=f, ldc=f, c_gs=d * f, **common)
+        gemm(H, dYp, dw3, M=f, N=d, lda=f, ldb=d, ldc=d, c_gs=f * d, **common)
+        _count(5)
+        return dx, dw1, dw2, dw3, None, dwts, None
+
+
+def grouped_swiglu(x, w1, w2, w3, idx, weights, keep=None, moe_dtype="bf16"):
+    T, d = x.shape
+    f = w1.shape[2]
+    ok = _bf16(x) and _bf16(w1) and d % 64 == 0 and f % 64 == 0
+    if not ok:
+        _fallback("grouped_swiglu", f"dtype {x.dtype}/{w1.dtype} d={d} f={f}")
+        return eager.grouped_swiglu(x, w1, w2, w3, idx, weights, keep)
+    if moe_dtype == "mxfp8":
+        from . import mxfp8
+        return mxfp8.grouped_swiglu_mxfp8(x, w1, w2, w3, idx, weights, keep)
+    return _GroupedSwiGLU.apply(x, w1.contiguous(), w2.contiguous(), w3.contiguous(), idx, weights, keep)
+
+
+# -------------------------------------------------------- LM head + MTP loss
+class _MTPLoss(torch.autograd.Function):
+    """Per head: logits chunk = H W^T (tcgen05 GEMM) -> CE kernel writes d logits in place ->
+    dH += dlogits W and dW = dlogits^T H.  Gradients are produced during forward (scaled
+    for an upstream gradient of 1) and rescaled in backward."""
+
+    @staticmethod
+    def forward(ctx, hidden, labels, weights, ignore_index, chunk_rows, *head_weights):
+        B, S, d = hidden.shape
+        R = B * S
+        h2 = hidden.reshape(R, d).contiguous()
+        need_grad = ctx.needs_input_grad[0] or any(ctx.needs_input_grad[5:])
+        dH = torch.zeros_like(h2) if need_grad else None
+        dWs: List[Optional[torch.Tensor]] = []
+        per = []
+        for i, W in enumerate(head_weights):
+            V = W.shape[0]
+            shift = i + 1
+            if shift >= S:
+                per.append(torch.zeros((), dtype=torch.float32, device=hidden.device))
+                dWs.append(None)
+                continue
+            lab = torch.full((B, S), ignore_index, dtype=torch.long, device=hidden.device)
+            lab[:, : S - shift] = labels[:, shift:]
+            lab = lab.reshape(R)
+            n_valid = (lab != ignore_index).sum().clamp(min=1).float()
+            gscale = (float(weights[i]) / n_valid).reshape(1).contiguous()
+            Wc = W.contiguous()
+            dW = torch.zeros_like(Wc) if need_grad else None
+            loss_sum = torch.zeros((), dtype=torch.float32, device=hidden.device)
+            for r0 in range(0, R, chunk_rows):
+                r1 = min(R, r0 + chunk_rows)
+                hc = h2[r0:r1]
+                logits = mm_nt(hc, Wc)
+                rows = K.ce_fwd_bwd(logits, lab[r0:r1].contiguous(), gscale, ignore_index, need_grad)
+                _count()
+                loss_sum = loss_sum + rows.sum()
+                if need_grad:
+                    mm_nn(logits, Wc, out=dH[r0:r1], D=dH[r0:r1], beta=1.0)
+                    mm_tn(logits, hc, out=dW, D=dW, beta=1.0)
+            per.append(loss_sum / n_valid)
+            dWs.append(dW)
+        per_t = torch.stack(per)
+        wt = torch.tensor(list(weights), dtype=torch.float32, device=hidden.device)
+        total = (per_t * wt).sum()
+        ctx.shape = (B, S, d)
+        ctx.n_heads = len(head_weights)
+        saved = [dH if dH is not None else torch.empty(0, device=hidden.device)]
+        saved += [w if w is not None else torch.empty(0, device=hidden.device) for w in dWs]
+        ctx.save_for_backward(*saved)
+        ctx.need_grad = need_grad
+        ctx.mark_non_differentiable(per_t)
+        return total, per_t
+
+    @staticmethod
+    def backward(ctx, g_total, _g_per):
+        saved = ctx.saved_tensors
+        dH, dWs = saved[0], saved[1:]
+        B, S, d = ctx.shape
+        gh = (dH * g_total.to(dH.dtype)).view(B, S, d) if dH.numel() else None
+        gws = [(w * g_total.to(w.dtype)) if w.numel() else None for w in dWs]
+        return (gh, None, None, None, None, *gws)
+
+
+def mtp_cross_entropy(hidden, head_weights: Sequence[torch.Tensor], labels, weights, ignore_index=-100,
+                      chunk_rows: int = 8192):
+    d = hidden.shape[-1]
+    V = head_weights[0].shape[0]
+    ok = _bf16(hidden) and all(_bf16(w) for w in head_weights) and d % 64 == 0 and V % 64 == 0
+    if not ok:
+        _fallback("mtp_cross_entropy", f"dtype {hidden.dtype} d={d} V={V}")
+        return eager.mtp_cross_entropy(hidden, head_weights, labels, weights, ignore_index)
+    return _MTPLoss.apply(hidden, labels, tuple(weights), ignore_index, chunk_rows, *head_weights)
+
+
+# ------------------------------------------------------------ Newton-Schulz
+@torch.no_grad()
+def newton_schulz(matrix: torch.Tensor, iters: int = 5) -> torch.Tensor:
+    """Batched cubic Newton-Schulz on the tcgen05 GEMM: per iteration one Gram product and
+    one product with the fused ``1.5 Y - 0.5 (G Y)`` epilogue.  bf16 operands, fp32
+    accumulation; the Frobenius normalisation is done in fp32."""
+    squeeze = matrix.dim() == 2
+    Y = matrix.unsqueeze(0) if squeeze else matrix
+    b, m, n = Y.shape
+    if m % 64 or n % 64:
+        _fallback("newton_schulz", f"shape {tuple(matrix.shape)}")
+        return eager.newton_schulz(matrix, iters)
+    Yf = Y.float()
+    norms = Yf.reshape(b, -1).norm(dim=1).view(b, 1, 1)
+    Ya = (Yf / (norms + 1e-7)).to(torch.bfloat16).contiguous()
+    Yb = torch.empty_like(Ya)
+    wide = m <= n
+    g = m if wide else n
+    Gm = torch.empty(b, g, g, dtype=torch.bfloat16, device=Y.device)
+    for _ in range(iters):
+        if wide:
+            # G = Y Y^T  (A, B K-major over n)
+            gemm(Ya, Ya, Gm, mode=BATCHED, groups=b, M=m, N=m, Kd=n, lda=n, ldb=n, ldc=m,
+                 a_gs=m * n, b_gs=m * n, c_gs=m * m)
+            # Y' = 1.5 Y - 0.5 G Y   (B = Y read MN-major)
+            gemm(Gm, Ya, Yb, D=Ya, alpha=-0.5, beta=1.5, mode=BATCHED, groups=b, M=m, N=n, Kd=m,
+                 b_major=MAJ_MN, lda=m, ldb=n, ldc=n, ldd=n, a_gs=m * m, b_gs=m * n, c_gs=m * n)
+        else:
+            # G = Y^T Y  (both MN-major over m)
+            gemm(Ya, Ya, Gm, mode=BATCHED, groups=b, M=n, N=n, Kd=m, a_major=MAJ_MN, b_major=MAJ_MN,
+                 lda=n, ldb=n, ldc=n, a_gs=m * n, b_gs=m * n, c_gs=n * n)
+            # Y' = 1.5 Y - 0.5 Y G   (G symmetric: read K-major)
+            gemm(Ya, Gm, Yb, D=Ya, alpha=-0.5, beta=1.5, mode=BATCHED, groups=b, M=m, N=n, Kd=n,
+                 lda=n, ldb=n, ldc=n, ldd=n, a_gs=m * n, b_gs=n * n, c_gs=m * n)
+        Ya, Yb = Yb, Ya
+    out = Ya.to(matrix.dtype)
+    return out.squeeze(0) if squeeze else out
