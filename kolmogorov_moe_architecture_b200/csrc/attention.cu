@@ -1,0 +1,753 @@
+// Causal grouped-query flash attention for sm_100a: tcgen05 MMAs with TMEM accumulators,
+// TMA-fed 128B-swizzled shared memory, online softmax in registers.
+//
+// Layouts: q, o, do, dq [B, S, H, D]; k, v, dk, dv [B, S, Hkv, D] (bf16, contiguous);
+// lse [B, H, S] fp32 (natural log).  Query head h reads KV head h / (H / Hkv) directly -
+// K and V are never expanded to H heads.
+//
+// Forward, one CTA per (128-query block, head, batch):
+//   warp 4   TMA producer: Q once, then K_j / V_j into a 2-stage ring
+//   warp 5   MMA issuer:   S_j = Q K_j^T (double-buffered in TMEM), PV_j = P_j V_j
+//   warps 0-3 (thread = query row): S_j from TMEM -> scale, causal mask, running max/sum,
+//            P_j as bf16 into swizzled smem (A operand of the PV MMA), then
+//            O = O * alpha + PV_j with O kept in registers.
+// Backward is two kernels of the same structure: dQ (loop over KV blocks for a query
+// block) and dK/dV (loop over query blocks of all heads of the group for a KV block);
+// both recompute P from the saved lse, so no atomics and the result is deterministic.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include <mutex>
+
+#include "kmoe_api.h"
+#include "ptx.cuh"
+#include "tmap_host.h"
+
+namespace kmoe {
+
+constexpr int ATT_BLK = 128;             // query rows per CTA and keys per step
+constexpr int PANEL_BYTES = ATT_BLK * 128;  // one 64-column bf16 panel of a 128-row tile
+constexpr int ATT_THREADS = 192;
+
+struct AttnArgs {
+  int B, S, H, Hkv;
+  float scale_log2;  // softmax scale * log2(e)
+  __nv_bfloat16* out;
+  float* lse;
+  int* status;
+};
+
+// Byte offset of the 16-byte chunk holding (row, col..col+7) in a K-major 128B-swizzled tile
+// made of 64-column panels.
+__device__ __forceinline__ uint32_t swz_kmajor(int row, int col) {
+  const int panel = col >> 6;
+  const int chunk = (col & 63) >> 3;
+  return panel * PANEL_BYTES + row * 128 + ((chunk ^ (row & 7)) << 4);
+}
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
+  constexpr int NP = D / 64;                      // panels per tile
+  constexpr int TILE_BYTES = NP * PANEL_BYTES;    // Q, K, V tiles
+  constexpr uint32_t IDESC_S = make_idesc_f16(128, ATT_BLK, 1, KMOE_MAJOR_K, KMOE_MAJOR_K);
+  constexpr uint32_t IDESC_PV = make_idesc_f16(128, D, 1, KMOE_MAJOR_K, KMOE_MAJOR_MN);
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t COL_S0 = 0, COL_PV = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + TILE_BYTES;            // 2 stages
+  uint8_t* sV = sK + 2 * TILE_BYTES;        // 2 stages
+  uint8_t* sP = sV + 2 * TILE_BYTES;        // 128 x 128 bf16
+  __shared__ uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_free[2], p_full, pv_full;
+  __shared__ uint32_t tmem_slot;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = gridDim.x - 1 - blockIdx.x;  // heavy (late) query blocks first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hkv = h / (a.H / a.Hkv);
+  const int q0 = qb * ATT_BLK;
+  const int nblk = qb + 1;                    // causal: KV blocks 0..qb
+
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1);
+      mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 128);
+    }
+    mbar_init(&p_full, 128);
+    mbar_init(&pv_full, 1);
+    mbar_fence_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  if (warp == 5) {
+    tmem_alloc(&tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 4) {
+    if (elect_one()) {
+      mbar_expect_tx(&q_full, TILE_BYTES);
+#pragma unroll
+      for (int p = 0; p < NP; ++p) tma_load_4d(sQ + p * PANEL_BYTES, &tmQ, &q_full, p * 64, h, q0, b);
+      for (int j = 0; j < nblk; ++j) {
+        const int st = j & 1;
+        const uint32_t par = ((j >> 1) & 1) ^ 1;
+        if (!mbar_wait(&k_empty[st], par)) { atomicExch(a.status, 11); goto teardown; }
+        mbar_expect_tx(&k_full[st], TILE_BYTES);
+#pragma unroll
+        for (int p = 0; p < NP; ++p)
+          tma_load_4d(sK + st * TILE_BYTES + p * PANEL_BYTES, &tmK, &k_full[st], p * 64, hkv, j * ATT_BLK, b);
+        if (!mbar_wait(&v_empty[st], par)) { atomicExch(a.status, 12); goto teardown; }
+        mbar_expect_tx(&v_full[st], TILE_BYTES);
+#pragma unroll
+        for (int p = 0; p < NP; ++p)
+          tma_load_4d(sV + st * TILE_BYTES + p * PANEL_BYTES, &tmV, &v_full[st], p * 64, hkv, j * ATT_BLK, b);
+      }
+    }
+  } else if (warp == 5) {
+    if (elect_one()) {
+      auto issue_S = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait(&k_full[st], (j >> 1) & 1)) return false;
+        if (!mbar_wait(&s_free[st], ((j >> 1) & 1) ^ 1)) return false;
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * TILE_BYTES);
+#pragma unroll
+        for (int k4 = 0; k4 < D / 16; ++k4) {
+          const uint32_t off = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;
+          umma_f16(tmem + COL_S0 + st * ATT_BLK, make_smem_desc_sw128(qa + off, 16, 1024),
+                   make_smem_desc_sw128(ka + off, 16, 1024), IDESC_S, k4 > 0);
+        }
+        umma_commit(&s_full[st]);
+        umma_commit(&k_empty[st]);
+        return true;
+      };
+      if (!mbar_wait(&q_full, 0)) { atomicExch(a.status, 13); goto teardown; }
+      if (!issue_S(0)) { atomicExch(a.status, 14); goto teardown; }
+      for (int j = 0; j < nblk; ++j) {
+        if (j + 1 < nblk && !issue_S(j + 1)) { atomicExch(a.status, 15); goto teardown; }
+        const int st = j & 1;
+        if (!mbar_wait(&v_full[st], (j >> 1) & 1)) { atomicExch(a.status, 16); goto teardown; }
+        if (!mbar_wait(&p_full, j & 1)) { atomicExch(a.status, 17); goto teardown; }
+        tc_fence_after();
+        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + st * TILE_BYTES);
+#pragma unroll
+        for (int k4 = 0; k4 < ATT_BLK / 16; ++k4) {
+          const uint32_t aoff = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;   // P: K-major over keys
+          const uint32_t boff = k4 * 16 * 128;                              // V: MN-major, 16 key rows
+          umma_f16(tmem + COL_PV, make_smem_desc_sw128(pa + aoff, 16, 1024),
+                   make_smem_desc_sw128(va + boff, PANEL_BYTES, 1024), IDESC_PV, k4 > 0);
+        }
+        umma_commit(&pv_full);
+        umma_commit(&v_empty[st]);
+      }
+    }
+  } else {
+    // ----------------------------------------------------------- softmax warps
+    const int r = warp * 32 + lane;                 // query row within the block
+    const int qi = q0 + r;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    float m = -INFINITY, l = 0.f;
+    float O[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) O[i] = 0.f;
+    for (int j = 0; j < nblk; ++j) {
+      const int st = j & 1;
+      if (!mbar_wait(&s_full[st], (j >> 1) & 1)) { if (lane == 0) atomicExch(a.status, 18); goto teardown; }
+      tc_fence_after();
+      const uint32_t ts = tmem + lane_base + COL_S0 + st * ATT_BLK;
+      const int k0 = j * ATT_BLK;
+      const bool need_mask = (j == qb) || (k0 + ATT_BLK > a.S);
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < ATT_BLK; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(ts + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]);
+          if (need_mask && (k0 + c + i > qi || k0 + c + i >= a.S)) s = -INFINITY;
+          mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = fmaxf(m, mx * a.scale_log2);
+      const float alpha = exp2f(m - m_new);
+      float rs = 0.f;
+      // pass 2: probabilities -> swizzled smem
+#pragma unroll 1
+      for (int c = 0; c < ATT_BLK; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(ts + c, v);
+        tmem_ld_wait();
+        float p[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]);
+          const bool dead = need_mask && (k0 + c + i > qi || k0 + c + i >= a.S);
+          p[i] = dead ? 0.f : exp2f(s * a.scale_log2 - m_new);
+          rs += p[i];
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 o;
+          o.x = pack_bf16(p[i], p[i + 1]); o.y = pack_bf16(p[i + 2], p[i + 3]);
+          o.z = pack_bf16(p[i + 4], p[i + 5]); o.w = pack_bf16(p[i + 6], p[i + 7]);
+          *reinterpret_cast<uint4*>(sP + swz_kmajor(r, c + i)) = o;
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&s_free[st]);
+      l = l * alpha + rs;
+      m = m_new;
+      fence_async_smem();
+      mbar_arrive(&p_full);
+      if (!mbar_wait(&pv_full, j & 1)) { if (lane == 0) atomicExch(a.status, 19); goto teardown; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem + lane_base + COL_PV + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) O[c + i] = O[c + i] * alpha + __uint_as_float(v[i]);
+      }
+      tc_fence_before();
+    }
+    if (qi < a.S) {
+      const float inv = 1.f / l;
+      __nv_bfloat16* orow = a.out + (((size_t)b * a.S + qi) * a.H + h) * D;
+#pragma unroll
+      for (int c = 0; c < D; c += 8) {
+        uint4 o;
+        o.x = pack_bf16(O[c] * inv, O[c + 1] * inv); o.y = pack_bf16(O[c + 2] * inv, O[c + 3] * inv);
+        o.z = pack_bf16(O[c + 4] * inv, O[c + 5] * inv); o.w = pack_bf16(O[c + 6] * inv, O[c + 7] * inv);
+        *reinterpret_cast<uint4*>(orow + c) = o;
+      }
+      a.lse[((size_t)b * a.H + h) * a.S + qi] = (m + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+
+teardown:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+}  // namespace kmoe
+
+// ------------------------------------------------------------------- backward
+namespace kmoe {
+
+constexpr int BWD_SUB = 64;                       // keys (dQ kernel) / queries (dK/dV kernel) per step
+constexpr int SUBPANEL_BYTES = BWD_SUB * 128;     // 64 rows x 64 bf16 columns
+
+struct AttnBwdArgs {
+  int B, S, H, Hkv;
+  float scale, scale_log2;
+  const float* lse;     // [B,H,S]
+  const float* delta;   // [B,H,S]  rowsum(dO * O)
+  __nv_bfloat16* dq;    // [B,S,H,D]
+  __nv_bfloat16* dk;    // [B,S,Hkv,D]
+  __nv_bfloat16* dv;
+  int* status;
+};
+
+// delta[b,h,s] = sum_d dO * O.  One warp per (b,s,h) row.
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                  float* __restrict__ delta, int B, int S, int H, int D) {
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long rows = (long long)B * S * H;
+  for (long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5; row < rows; row += warps) {
+    const int h = (int)(row % H);
+    const long long bs = row / H;
+    const int s_ = (int)(bs % S);
+    const int b = (int)(bs / S);
+    float acc = 0.f;
+    for (int c = lane * 8; c < D; c += 256) {
+      uint4 r1 = *reinterpret_cast<const uint4*>(o + row * D + c);
+      uint4 r2 = *reinterpret_cast<const uint4*>(d_o + row * D + c);
+      const __nv_bfloat162* p1 = reinterpret_cast<const __nv_bfloat162*>(&r1);
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&r2);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 f1 = __bfloat1622float2(p1[i]), f2 = __bfloat1622float2(p2[i]);
+        acc += f1.x * f2.x + f1.y * f2.y;
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) delta[((size_t)b * H + h) * S + s_] = acc;
+  }
+}
+
+// 16-byte chunk offset inside a [rows x 64] K-major swizzled panel
+__device__ __forceinline__ uint32_t swz64(int row, int col) { return row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4); }
+
+// dQ for one (128-query block, head, batch): dQ = sum_j dS_j K_j, dS = P * (dO V^T - delta) * scale
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                   const AttnBwdArgs a) {
+  constexpr int NP = D / 64;
+  constexpr int QTILE = NP * PANEL_BYTES;       // 128 rows
+  constexpr int KTILE = NP * SUBPANEL_BYTES;    // 64 rows
+  constexpr uint32_t IDESC_S = make_idesc_f16(128, BWD_SUB, 1, KMOE_MAJOR_K, KMOE_MAJOR_K);
+  constexpr uint32_t IDESC_DQ = make_idesc_f16(128, D, 1, KMOE_MAJOR_K, KMOE_MAJOR_MN);
+  constexpr uint32_t TMEM_COLS = 256, COL_S = 0, COL_DP = 64, COL_DQ = 128;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sdO = sQ + QTILE;
+  uint8_t* sK = sdO + QTILE;          // 2 stages
+  uint8_t* sV = sK + 2 * KTILE;       // 2 stages
+  uint8_t* sdS = sV + 2 * KTILE;      // 128 x 64 bf16
+  __shared__ uint64_t qdo_full, k_full[2], v_full[2], k_empty[2], v_empty[2], sdp_full, ds_full, ds_free, dq_full;
+  __shared__ uint32_t tmem_slot;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hkv = h / (a.H / a.Hkv);
+  const int q0 = qb * ATT_BLK;
+  const int kmax = min(q0 + ATT_BLK, a.S);
+  const int nblk = (kmax + BWD_SUB - 1) / BWD_SUB;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&qdo_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1);
+    }
+    mbar_init(&sdp_full, 1); mbar_init(&ds_full, 128); mbar_init(&ds_free, 1); mbar_init(&dq_full, 1);
+    mbar_fence_init();
+  }
+  if (warp == 5) { tmem_alloc(&tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 4) {
+    if (elect_one()) {
+      mbar_expect_tx(&qdo_full, 2 * QTILE);
+#pragma unroll
+      for (int p = 0; p < NP; ++p) {
+        tma_load_4d(sQ + p * PANEL_BYTES, &tmQ, &qdo_full, p * 64, h, q0, b);
+        tma_load_4d(sdO + p * PANEL_BYTES, &tmdO, &qdo_full, p * 64, h, q0, b);
+      }
+      for (int j = 0; j < nblk; ++j) {
+        const int st = j & 1;
+        const uint32_t par = ((j >> 1) & 1) ^ 1;
+        if (!mbar_wait(&k_empty[st], par)) { atomicExch(a.status, 21); goto teardown; }
+        mbar_expect_tx(&k_full[st], KTILE);
+#pragma unroll
+        for (int p = 0; p < NP; ++p)
+          tma_load_4d(sK + st * KTILE + p * SUBPANEL_BYTES, &tmK, &k_full[st], p * 64, hkv, j * BWD_SUB, b);
+        if (!mbar_wait(&v_empty[st], par)) { atomicExch(a.status, 22); goto teardown; }
+        mbar_expect_tx(&v_full[st], KTILE);
+#pragma unroll
+        for (int p = 0; p < NP; ++p)
+          tma_load_4d(sV + st * KTILE + p * SUBPANEL_BYTES, &tmV, &v_full[st], p * 64, hkv, j * BWD_SUB, b);
+      }
+    }
+  } else if (warp == 5) {
+    if (elect_one()) {
+      if (!mbar_wait(&qdo_full, 0)) { atomicExch(a.status, 23); goto teardown; }
+      for (int j = 0; j < nblk; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_full[st], ph) || !mbar_wait(&v_full[st], ph)) { atomicExch(a.status, 24); goto teardown; }
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ), da = smem_u32(sdO);
+        const uint32_t ka = smem_u32(sK + st * KTILE), va = smem_u32(sV + st * KTILE);
+#pragma unroll
+        for (int k4 = 0; k4 < D / 16; ++k4) {
+          const uint32_t aoff = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;
+          const uint32_t boff = (k4 >> 2) * SUBPANEL_BYTES + (k4 & 3) * 32;
+          umma_f16(tmem + COL_S, make_smem_desc_sw128(qa + aoff, 16, 1024), make_smem_desc_sw128(ka + boff, 16, 1024),
+                   IDESC_S, k4 > 0);
+        }
+#pragma unroll
+        for (int k4 = 0; k4 < D / 16; ++k4) {
+          const uint32_t aoff = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;
+          const uint32_t boff = (k4 >> 2) * SUBPANEL_BYTES + (k4 & 3) * 32;
+          umma_f16(tmem + COL_DP, make_smem_desc_sw128(da + aoff, 16, 1024), make_smem_desc_sw128(va + boff, 16, 1024),
+                   IDESC_S, k4 > 0);
+        }
+        umma_commit(&sdp_full);
+        umma_commit(&v_empty[st]);
+        if (!mbar_wait(&ds_full, j & 1)) { atomicExch(a.status, 25); goto teardown; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(sdS);
+#pragma unroll
+        for (int k4 = 0; k4 < BWD_SUB / 16; ++k4)
+          umma_f16(tmem + COL_DQ, make_smem_desc_sw128(sa + k4 * 32, 16, 1024),
+                   make_smem_desc_sw128(ka + k4 * 16 * 128, SUBPANEL_BYTES, 1024), IDESC_DQ, (j > 0 || k4 > 0));
+        umma_commit(&ds_free);
+        umma_commit(&k_empty[st]);
+      }
+      umma_commit(&dq_full);
+    }
+  } else {
+    const int r = warp * 32 + lane;
+    const int qi = q0 + r;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const bool row_ok = qi < a.S;
+    const size_t stat = ((size_t)b * a.H + h) * a.S + (row_ok ? qi : 0);
+    const float lse2 = a.lse[stat] * 1.4426950408889634f;
+    const float dlt = a.delta[stat];
+    for (int j = 0; j < nblk; ++j) {
+      if (!mbar_wait(&sdp_full, j & 1)) { if (lane == 0) atomicExch(a.status, 26); goto teardown; }
+      tc_fence_after();
+      const int k0 = j * BWD_SUB;
+      uint32_t ds_packed[BWD_SUB / 2];
+#pragma unroll
+      for (int c = 0; c < BWD_SUB; c += 32) {
+        uint32_t sv[32], dv_[32];
+        tmem_ld_32x32(tmem + lane_base + COL_S + c, sv);
+        tmem_ld_32x32(tmem + lane_base + COL_DP + c, dv_);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float v2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int kj = k0 + c + i + e;
+            const bool dead = (kj > qi) || (kj >= a.S) || !row_ok;
+            const float p = dead ? 0.f : exp2f(__uint_as_float(sv[i + e]) * a.scale_log2 - lse2);
+            v2[e] = p * (__uint_as_float(dv_[i + e]) - dlt) * a.scale;
+          }
+          ds_packed[(c + i) >> 1] = pack_bf16(v2[0], v2[1]);
+        }
+      }
+      tc_fence_before();
+      if (!mbar_wait(&ds_free, (j & 1) ^ 1)) { if (lane == 0) atomicExch(a.status, 27); goto teardown; }
+#pragma unroll
+      for (int c = 0; c < BWD_SUB; c += 8)
+        *reinterpret_cast<uint4*>(sdS + swz64(r, c)) =
+            make_uint4(ds_packed[c / 2], ds_packed[c / 2 + 1], ds_packed[c / 2 + 2], ds_packed[c / 2 + 3]);
+      fence_async_smem();
+      mbar_arrive(&ds_full);
+    }
+    if (!mbar_wait(&dq_full, 0)) { if (lane == 0) atomicExch(a.status, 28); goto teardown; }
+    tc_fence_after();
+    __nv_bfloat16* drow = a.dq + (((size_t)b * a.S + (row_ok ? qi : 0)) * a.H + h) * D;
+#pragma unroll
+    for (int c = 0; c < D; c += 32) {
+      uint32_t v[32];
+      tmem_ld_32x32(tmem + lane_base + COL_DQ + c, v);
+      tmem_ld_wait();
+      if (row_ok) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8)
+          *reinterpret_cast<uint4*>(drow + c + i) =
+              make_uint4(pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1])),
+                         pack_bf16(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])),
+                         pack_bf16(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5])),
+                         pack_bf16(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7])));
+      }
+    }
+    tc_fence_before();
+  }
+teardown:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+// dK, dV for one (128-key block, KV head, batch): loops over the query heads of the group and the
+// 64-query blocks at or after the key block.
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                    const AttnBwdArgs a) {
+  constexpr int NP = D / 64;
+  constexpr int KTILE = NP * PANEL_BYTES;       // 128 key rows
+  constexpr int QTILE = NP * SUBPANEL_BYTES;    // 64 query rows
+  constexpr uint32_t IDESC_ST = make_idesc_f16(128, BWD_SUB, 1, KMOE_MAJOR_K, KMOE_MAJOR_K);
+  constexpr uint32_t IDESC_ACC = make_idesc_f16(128, D, 1, KMOE_MAJOR_K, KMOE_MAJOR_MN);
+  constexpr uint32_t TMEM_COLS = 512, COL_ST = 0, COL_DPT = 64, COL_DV = 128, COL_DK = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + KTILE;
+  uint8_t* sQ = sV + KTILE;            // 2 stages
+  uint8_t* sdO = sQ + 2 * QTILE;       // 2 stages
+  uint8_t* sPT = sdO + 2 * QTILE;      // 128 x 64
+  uint8_t* sdST = sPT + ATT_BLK * 128; // 128 x 64
+  __shared__ uint64_t kv_full, q_full[2], q_empty[2], st_full, pds_full, pds_free, acc_full;
+  __shared__ uint32_t tmem_slot;
+  __shared__ float s_lse[BWD_SUB], s_delta[BWD_SUB];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int G = a.H / a.Hkv;
+  const int k0 = kb * ATT_BLK;
+  const int qblk0 = k0 / BWD_SUB;
+  const int qblk1 = (a.S + BWD_SUB - 1) / BWD_SUB;
+  const int per_head = qblk1 - qblk0;
+  const int niter = per_head * G;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&kv_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
+    mbar_init(&st_full, 1); mbar_init(&pds_full, 128); mbar_init(&pds_free, 1); mbar_init(&acc_full, 1);
+    mbar_fence_init();
+  }
+  if (warp == 5) { tmem_alloc(&tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 4) {
+    if (elect_one()) {
+      mbar_expect_tx(&kv_full, 2 * KTILE);
+#pragma unroll
+      for (int p = 0; p < NP; ++p) {
+        tma_load_4d(sK + p * PANEL_BYTES, &tmK, &kv_full, p * 64, hkv, k0, b);
+        tma_load_4d(sV + p * PANEL_BYTES, &tmV, &kv_full, p * 64, hkv, k0, b);
+      }
+      for (int it = 0; it < niter; ++it) {
+        const int st = it & 1;
+        const int h = hkv * G + it / per_head;
+        const int qrow = (qblk0 + it % per_head) * BWD_SUB;
+        if (!mbar_wait(&q_empty[st], ((it >> 1) & 1) ^ 1)) { atomicExch(a.status, 31); goto teardown; }
+        mbar_expect_tx(&q_full[st], 2 * QTILE);
+#pragma unroll
+        for (int p = 0; p < NP; ++p) {
+          tma_load_4d(sQ + st * QTILE + p * SUBPANEL_BYTES, &tmQ, &q_full[st], p * 64, h, qrow, b);
+          tma_load_4d(sdO + st * QTILE + p * SUBPANEL_BYTES, &tmdO, &q_full[st], p * 64, h, qrow, b);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (elect_one()) {
+      if (!mbar_wait(&kv_full, 0)) { atomicExch(a.status, 32); goto teardown; }
+      for (int it = 0; it < niter; ++it) {
+        const int st = it & 1;
+        if (!mbar_wait(&q_full[st], (it >> 1) & 1)) { atomicExch(a.status, 33); goto teardown; }
+        tc_fence_after();
+        const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+        const uint32_t qa = smem_u32(sQ + st * QTILE), da = smem_u32(sdO + st * QTILE);
+#pragma unroll
+        for (int k4 = 0; k4 < D / 16; ++k4) {
+          const uint32_t aoff = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;
+          const uint32_t boff = (k4 >> 2) * SUBPANEL_BYTES + (k4 & 3) * 32;
+          umma_f16(tmem + COL_ST, make_smem_desc_sw128(ka + aoff, 16, 1024), make_smem_desc_sw128(qa + boff, 16, 1024),
+                   IDESC_ST, k4 > 0);
+        }
+#pragma unroll
+        for (int k4 = 0; k4 < D / 16; ++k4) {
+          const uint32_t aoff = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;
+          const uint32_t boff = (k4 >> 2) * SUBPANEL_BYTES + (k4 & 3) * 32;
+          umma_f16(tmem + COL_DPT, make_smem_desc_sw128(va + aoff, 16, 1024),
+                   make_smem_desc_sw128(da + boff, 16, 1024), IDESC_ST, k4 > 0);
+        }
+        umma_commit(&st_full);
+        if (!mbar_wait(&pds_full, it & 1)) { atomicExch(a.status, 34); goto teardown; }
+        tc_fence_after();
+        const uint32_t pa = smem_u32(sPT), sa = smem_u32(sdST);
+#pragma unroll
+        for (int k4 = 0; k4 < BWD_SUB / 16; ++k4) {
+          umma_f16(tmem + COL_DV, make_smem_desc_sw128(pa + k4 * 32, 16, 1024),
+                   make_smem_desc_sw128(da + k4 * 16 * 128, SUBPANEL_BYTES, 1024), IDESC_ACC, (it > 0 || k4 > 0));
+          umma_f16(tmem + COL_DK, make_smem_desc_sw128(sa + k4 * 32, 16, 1024),
+                   make_smem_desc_sw128(qa + k4 * 16 * 128, SUBPANEL_BYTES, 1024), IDESC_ACC, (it > 0 || k4 > 0));
+        }
+        umma_commit(&pds_free);
+        umma_commit(&q_empty[st]);
+      }
+      umma_commit(&acc_full);
+    }
+  } else {
+    const int r = warp * 32 + lane;     // key row
+    const int kj = k0 + r;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    for (int it = 0; it < niter; ++it) {
+      const int h = hkv * G + it / per_head;
+      const int qrow = (qblk0 + it % per_head) * BWD_SUB;
+      // stage lse / delta of the 64 queries (previous iteration's readers are past their loop:
+      // they arrived on pds_full after their last read, and this point is after waiting st_full)
+      if (!mbar_wait(&st_full, it & 1)) { if (lane == 0) atomicExch(a.status, 35); goto teardown; }
+      tc_fence_after();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (r < BWD_SUB) {
+        const int qi = qrow + r;
+        const size_t si = ((size_t)b * a.H + h) * a.S + (qi < a.S ? qi : 0);
+        s_lse[r] = a.lse[si] * 1.4426950408889634f;
+        s_delta[r] = a.delta[si];
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      uint32_t pt[BWD_SUB / 2], dst[BWD_SUB / 2];
+#pragma unroll
+      for (int c = 0; c < BWD_SUB; c += 32) {
+        uint32_t sv[32], dv_[32];
+        tmem_ld_32x32(tmem + lane_base + COL_ST + c, sv);
+        tmem_ld_32x32(tmem + lane_base + COL_DPT + c, dv_);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float pv[2], dv2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int qi = qrow + c + i + e;
+            const bool dead = (kj > qi) || (qi >= a.S) || (kj >= a.S);
+            pv[e] = dead ? 0.f : exp2f(__uint_as_float(sv[i + e]) * a.scale_log2 - s_lse[c + i + e]);
+            dv2[e] = pv[e] * (__uint_as_float(dv_[i + e]) - s_delta[c + i + e]) * a.scale;
+          }
+          pt[(c + i) >> 1] = pack_bf16(pv[0], pv[1]);
+          dst[(c + i) >> 1] = pack_bf16(dv2[0], dv2[1]);
+        }
+      }
+      tc_fence_before();
+      if (!mbar_wait(&pds_free, (it & 1) ^ 1)) { if (lane == 0) atomicExch(a.status, 36); goto teardown; }
+#pragma unroll
+      for (int c = 0; c < BWD_SUB; c += 8) {
+        *reinterpret_cast<uint4*>(sPT + swz64(r, c)) = make_uint4(pt[c / 2], pt[c / 2 + 1], pt[c / 2 + 2], pt[c / 2 + 3]);
+        *reinterpret_cast<uint4*>(sdST + swz64(r, c)) =
+            make_uint4(dst[c / 2], dst[c / 2 + 1], dst[c / 2 + 2], dst[c / 2 + 3]);
+      }
+      fence_async_smem();
+      mbar_arrive(&pds_full);
+    }
+    if (!mbar_wait(&acc_full, 0)) { if (lane == 0) atomicExch(a.status, 37); goto teardown; }
+    tc_fence_after();
+    const bool row_ok = kj < a.S;
+    const size_t off = (((size_t)b * a.S + (row_ok ? kj : 0)) * a.Hkv + hkv) * D;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      __nv_bfloat16* drow = (which == 0 ? a.dv : a.dk) + off;
+      const uint32_t col0 = which == 0 ? COL_DV : COL_DK;
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem + lane_base + col0 + c, v);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8)
+            *reinterpret_cast<uint4*>(drow + c + i) =
+                make_uint4(pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1])),
+                           pack_bf16(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])),
+                           pack_bf16(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5])),
+                           pack_bf16(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7])));
+        }
+      }
+    }
+    tc_fence_before();
+  }
+teardown:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+}  // namespace kmoe
+
+// ------------------------------------------------------------------ host side
+namespace kmoe {
+
+// [B, S, Hx, D] bf16 tensor viewed as dims {D, Hx, S, B}; box = 64 columns of one head for `rows` positions.
+static int make_bshd_tmap(CUtensorMap* out, const void* base, int B, int S, int Hx, int D, int rows) {
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)Hx, (cuuint64_t)S, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)Hx * D * 2, (cuuint64_t)S * Hx * D * 2};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)rows, 1};
+  return encode_bf16_4d(out, base, dims, strides, box);
+}
+
+template <int D>
+static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a,
+                           cudaStream_t st) {
+  constexpr int tile = (D / 64) * PANEL_BYTES;
+  const int smem = tile * 5 + ATT_BLK * ATT_BLK * 2 + 1024;
+  auto kern = attn_fwd_kernel<D>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -20;
+    attr = true;
+  }
+  dim3 grid((a.S + ATT_BLK - 1) / ATT_BLK, a.H, a.B);
+  kern<<<grid, ATT_THREADS, smem, st>>>(tq, tk, tv, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+}  // namespace kmoe
+
+extern "C" int kmoe_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int H,
+                             int Hkv, int D, float scale, int* status, cudaStream_t st) {
+  using namespace kmoe;
+  if (D != 64 && D != 128) return -1;
+  if (H % Hkv) return -2;
+  CUtensorMap tq, tk, tv;
+  int rc = make_bshd_tmap(&tq, q, B, S, H, D, ATT_BLK);
+  if (rc) return rc;
+  if ((rc = make_bshd_tmap(&tk, k, B, S, Hkv, D, ATT_BLK))) return rc;
+  if ((rc = make_bshd_tmap(&tv, v, B, S, Hkv, D, ATT_BLK))) return rc;
+  AttnArgs a{B, S, H, Hkv, scale * 1.4426950408889634f, (__nv_bfloat16*)out, lse, status};
+  return D == 128 ? launch_attn_fwd<128>(tq, tk, tv, a, st) : launch_attn_fwd<64>(tq, tk, tv, a, st);
+}
+
+namespace kmoe {
+template <int D>
+static int launch_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, const AttnBwdArgs& a,
+                           cudaStream_t st) {
+  CUtensorMap tq128, tdo128, tk64, tv64, tq64, tdo64, tk128, tv128;
+  int rc;
+  if ((rc = make_bshd_tmap(&tq128, q, a.B, a.S, a.H, D, 128))) return rc;
+  if ((rc = make_bshd_tmap(&tdo128, d_o, a.B, a.S, a.H, D, 128))) return rc;
+  if ((rc = make_bshd_tmap(&tk64, k, a.B, a.S, a.Hkv, D, 64))) return rc;
+  if ((rc = make_bshd_tmap(&tv64, v, a.B, a.S, a.Hkv, D, 64))) return rc;
+  if ((rc = make_bshd_tmap(&tq64, q, a.B, a.S, a.H, D, 64))) return rc;
+  if ((rc = make_bshd_tmap(&tdo64, d_o, a.B, a.S, a.H, D, 64))) return rc;
+  if ((rc = make_bshd_tmap(&tk128, k, a.B, a.S, a.Hkv, D, 128))) return rc;
+  if ((rc = make_bshd_tmap(&tv128, v, a.B, a.S, a.Hkv, D, 128))) return rc;
+  constexpr int NP = D / 64;
+  const int smem_dq = 2 * NP * PANEL_BYTES + 4 * NP * SUBPANEL_BYTES + ATT_BLK * 128 + 1024;
+  const int smem_dkv = 2 * NP * PANEL_BYTES + 4 * NP * SUBPANEL_BYTES + 2 * ATT_BLK * 128 + 1024;
+  auto k1 = attn_bwd_dq_kernel<D>;
+  auto k2 = attn_bwd_dkv_kernel<D>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq) != cudaSuccess) return -20;
+    if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dkv) != cudaSuccess) return -20;
+    attr = true;
+  }
+  const int nb = (a.S + ATT_BLK - 1) / ATT_BLK;
+  k1<<<dim3(nb, a.H, a.B), ATT_THREADS, smem_dq, st>>>(tq128, tdo128, tk64, tv64, a);
+  k2<<<dim3(nb, a.Hkv, a.B), ATT_THREADS, smem_dkv, st>>>(tq64, tdo64, tk128, tv128, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+}  // namespace kmoe
+
+// delta is scratch of B*H*S floats.
+extern "C" int kmoe_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                             const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int H,
+                             int Hkv, int D, float scale, int* status, cudaStream_t st) {
+  using namespace kmoe;
+  if (D != 64 && D != 128) return -1;
+  if (H % Hkv) return -2;
+  attn_delta_kernel<<<148 * 4, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, B, S, H, D);
+  AttnBwdArgs a{B, S, H, Hkv, scale, scale * 1.4426950408889634f, lse, delta, (__nv_bfloat16*)dq,
+                (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, status};
+  return D == 128 ? launch_attn_bwd<128>(q, k, v, d_o, a, st) : launch_attn_bwd<64>(q, k, v, d_o, a, st);
+}

@@ -249,6 +249,33 @@ Tensor moe_combine_dw(const Tensor& Y, const Tensor& dout, const Tensor& pos, in
   return dw;
 }
 
+// -------------------------------------------------------------------- attention
+std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale, Tensor status) {
+  c10::cuda::CUDAGuard guard(q.device());
+  need_bf16(q, "q"); need_bf16(k, "k"); need_bf16(v, "v");
+  TORCH_CHECK(q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && q.dim() == 4);
+  const int B = q.size(0), S = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
+  Tensor out = at::empty_like(q);
+  Tensor lse = at::empty({B, H, S}, q.options().dtype(at::kFloat));
+  check(kmoe_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), B, S, H, Hkv,
+                      D, (float)scale, status.data_ptr<int>(), cur_stream()), "attn_fwd");
+  return {out, lse};
+}
+
+std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
+                                            const Tensor& d_o, const Tensor& lse, double scale, Tensor status) {
+  c10::cuda::CUDAGuard guard(q.device());
+  need_bf16(d_o, "do");
+  TORCH_CHECK(d_o.is_contiguous() && o.is_contiguous());
+  const int B = q.size(0), S = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
+  Tensor dq = at::empty_like(q), dk = at::empty_like(k), dv = at::empty_like(v);
+  Tensor delta = at::empty({B, H, S}, lse.options());
+  check(kmoe_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr<float>(),
+                      delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, H, Hkv, D,
+                      (float)scale, status.data_ptr<int>(), cur_stream()), "attn_bwd");
+  return {dq, dk, dv};
+}
+
 // ------------------------------------------------------------------------- loss
 Tensor ce_fwd_bwd(Tensor logits, const Tensor& labels, const Tensor& grad_scale, int64_t ignore_index,
                   bool write_grad) {
@@ -281,4 +308,6 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("moe_combine", &moe_combine);
   m.def("moe_combine_dw", &moe_combine_dw);
   m.def("ce_fwd_bwd", &ce_fwd_bwd);
+  m.def("attn_fwd", &attn_fwd);
+  m.def("attn_bwd", &attn_bwd);
 }

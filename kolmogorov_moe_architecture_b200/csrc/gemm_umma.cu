@@ -21,6 +21,7 @@
 
 #include "kmoe_api.h"
 #include "ptx.cuh"
+#include "tmap_host.h"
 
 namespace kmoe {
 
@@ -367,23 +368,6 @@ teardown:
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
-
 using TmapKey = std::tuple<const void*, int, long long, long long, long long, long long, int, int>;
 static std::map<TmapKey, CUtensorMap> g_tmap_cache;
 static std::mutex g_tmap_mutex;
@@ -402,12 +386,9 @@ static int make_operand_tmap(CUtensorMap* out, const void* base, int major, long
       return 0;
     }
   }
-  EncodeTiledFn enc = get_encode_fn();
-  if (enc == nullptr) return -10;
   cuuint64_t dims[4];
   cuuint64_t strides[3];
   cuuint32_t box[4];
-  cuuint32_t estr[4] = {1, 1, 1, 1};
   const long long gs = (groups > 1 && gstride > 0) ? gstride : (major == KMOE_MAJOR_K ? rows * ld : K * ld);
   const int G = (groups > 1 && gstride > 0) ? groups : 1;
   if (major == KMOE_MAJOR_K) {
@@ -420,13 +401,8 @@ static int make_operand_tmap(CUtensorMap* out, const void* base, int major, long
     strides[0] = (cuuint64_t)ld * 2; strides[1] = 128; strides[2] = (cuuint64_t)gs * 2;
     box[0] = 64; box[1] = BK; box[2] = (cuuint32_t)(tile_rows / 64); box[3] = 1;
   }
-  for (int i = 0; i < 3; ++i)
-    if (strides[i] % 16 != 0) return -12;
-  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return -13;
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return -14;
+  const int rc = encode_bf16_4d(out, base, dims, strides, box);
+  if (rc) return rc;
   {
     std::lock_guard<std::mutex> lk(g_tmap_mutex);
     if (g_tmap_cache.size() > 4096) g_tmap_cache.clear();

@@ -83,6 +83,14 @@ int kmoe_moe_combine(const void* Y, const int* pos, const float* w, void* out, i
 int kmoe_moe_combine_dw(const void* Y, const void* dout, const int* pos, float* dw, int n, int k, int d,
                         cudaStream_t st);
 
+// ----------------------------------------------------------------------- attention
+// Causal GQA flash attention. q/out/dq [B,S,H,D], k/v/dk/dv [B,S,Hkv,D] bf16; lse, delta [B,H,S] fp32; D in {64,128}.
+int kmoe_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int H, int Hkv,
+                  int D, float scale, int* status, cudaStream_t st);
+int kmoe_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                  float* delta, void* dq, void* dk, void* dv, int B, int S, int H, int Hkv, int D, float scale,
+                  int* status, cudaStream_t st);
+
 // ---------------------------------------------------------------------------- loss
 int kmoe_ce_fwd_bwd(void* logits, const long long* labels, float* loss_rows, const float* grad_scale, int R, int V,
                     long long ld, long long ignore_index, int write_grad, cudaStream_t st);

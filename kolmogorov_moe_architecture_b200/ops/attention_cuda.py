@@ -1,12 +1,39 @@
-"""Causal GQA attention on CUDA tensors."""
+"""Causal GQA flash attention on CUDA tensors (tcgen05 kernels in csrc/attention.cu)."""
 from __future__ import annotations
 
+import math
+
 import torch
-import torch.nn.functional as F
+
+from . import eager
+
+
+class _FlashAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale):
+        from . import cuda_ops
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        out, lse = torch.ops.kmoe.attn_fwd(q, k, v, scale, cuda_ops.status_tensor(q.device))
+        cuda_ops._count()
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.scale = scale
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        from . import cuda_ops
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = torch.ops.kmoe.attn_bwd(q, k, v, out, d_out.contiguous(), lse, ctx.scale,
+                                             cuda_ops.status_tensor(q.device))
+        cuda_ops._count(3)
+        return dq, dk, dv, None
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True) -> torch.Tensor:
-    """q (B,S,H,D); k, v (B,S,Hkv,D) -> (B,S,H,D)."""
-    out = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
-                                         is_causal=causal, enable_gqa=True)
-    return out.transpose(1, 2).contiguous()
+    """q (B,S,H,D); k, v (B,S,Hkv,D) -> (B,S,H,D).  bf16, D in {64, 128}, causal."""
+    from . import cuda_ops
+    D = q.shape[-1]
+    if not (causal and q.dtype == torch.bfloat16 and D in (64, 128)):
+        cuda_ops._fallback("attention", f"dtype {q.dtype} head_dim {D} causal {causal}")
+        return eager.attention(q, k, v, causal)
+    return _FlashAttn.apply(q, k, v, 1.0 / math.sqrt(D))

@@ -195,3 +195,21 @@ def test_model_step_bf16_matches_eager():
     o2 = ref(ids, labels=ids, return_logits=False)
     assert abs(out["lm_loss"].item() - o2["lm_loss"].item()) < 0.05
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,D", [(1, 128, 2, 1, 64), (2, 200, 4, 2, 128), (1, 512, 4, 1, 128),
+                                         (2, 333, 2, 2, 64)])
+def test_flash_attention_fwd_bwd(B, S, H, Hkv, D):
+    ops, c, eager = _mods()
+    q, k, v = _bf(B, S, H, D, grad=True), _bf(B, S, Hkv, D, grad=True), _bf(B, S, Hkv, D, grad=True)
+    out = ops.attention(q, k, v, causal=True)
+    go = _bf(B, S, H, D)
+    out.backward(go)
+    c.check_status()
+    qr, kr, vr = _f32_leaf(q), _f32_leaf(k), _f32_leaf(v)
+    ref = eager.attention(qr, kr, vr, True)
+    ref.backward(go.float())
+    assert _rel(out, ref) < 2e-2
+    assert _rel(q.grad, qr.grad) < 3e-2, "dq"
+    assert _rel(k.grad, kr.grad) < 3e-2, "dk"
+    assert _rel(v.grad, vr.grad) < 3e-2, "dv"
