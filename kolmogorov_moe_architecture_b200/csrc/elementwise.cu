@@ -58,13 +58,10 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
   }
 }
 
-// dx = rstd * (w dy) - x * rstd^3 * mean(w dy x);  dw partial sums per block into `partial` [gridDim.x, d].
+// dx = rstd * (w dy) - x * rstd^3 * mean(w dy x).  One warp per row.
 __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                    const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
-                                   __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int d) {
-  extern __shared__ float s_dw[];  // d floats
-  for (int c = threadIdx.x; c < d; c += blockDim.x) s_dw[c] = 0.f;
-  __syncthreads();
+                                   __nv_bfloat16* __restrict__ dx, int rows, int d) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
@@ -89,15 +86,38 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __
       unpack8(*reinterpret_cast<const uint4*>(gr + c), gv);
       unpack8(*reinterpret_cast<const uint4*>(w + c), wv);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        o[i] = gv[i] * wv[i] * r - xv[i] * coef;
-        atomicAdd(&s_dw[c + i], gv[i] * xv[i] * r);
-      }
+      for (int i = 0; i < 8; ++i) o[i] = gv[i] * wv[i] * r - xv[i] * coef;
       *reinterpret_cast<uint4*>(dxr + c) = pack8(o);
     }
   }
+}
+
+// Column sums of dy * x * rstd over a slice of the rows: partial[blockIdx.y][c].
+// Block = 32 column-vectors (256 columns) x 8 row lanes.
+__global__ void rmsnorm_dw_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                                  const float* __restrict__ rstd, float* __restrict__ partial, int rows, int d) {
+  __shared__ float red[8][256];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 256 + tx * 8;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (c < d) {
+    for (int row = blockIdx.y * 8 + ty; row < rows; row += gridDim.y * 8) {
+      float xv[8], gv[8];
+      unpack8(*reinterpret_cast<const uint4*>(x + (size_t)row * d + c), xv);
+      unpack8(*reinterpret_cast<const uint4*>(dy + (size_t)row * d + c), gv);
+      const float r = rstd[row];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += gv[i] * xv[i] * r;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[ty][tx * 8 + i] = acc[i];
   __syncthreads();
-  for (int c = threadIdx.x; c < d; c += blockDim.x) partial[(size_t)blockIdx.x * d + c] = s_dw[c];
+  const int col = threadIdx.x;  // 256 threads, one column each
+  float s_ = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s_ += red[j][col];
+  if (blockIdx.x * 256 + col < d) partial[(size_t)blockIdx.y * d + blockIdx.x * 256 + col] = s_;
 }
 
 __global__ void colsum_partials_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out_bf16,
@@ -216,21 +236,23 @@ extern "C" int kmoe_rmsnorm_fwd(const void* x, const void* w, void* y, float* rs
 }
 
 extern "C" int kmoe_rmsnorm_bwd_num_partials(int rows) {
-  const int wpb = 8;
-  int grid = (rows + wpb - 1) / wpb;
-  return grid > 296 ? 296 : grid;
+  int r = (rows + 63) / 64;
+  return r > 64 ? 64 : (r < 1 ? 1 : r);
 }
 
 // `partial` is scratch of kmoe_rmsnorm_bwd_num_partials(rows) * d floats.
 extern "C" int kmoe_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx,
                                 void* dw_bf16, float* dw_f32, float* partial, int rows, int d, cudaStream_t st) {
   if (d % 8) return -1;
-  const int block = 256;
-  const int grid = kmoe_rmsnorm_bwd_num_partials(rows);
-  rmsnorm_bwd_kernel<<<grid, block, d * sizeof(float), st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
-                                                             (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx,
-                                                             partial, rows, d);
-  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, (__nv_bfloat16*)dw_bf16, dw_f32, grid, d);
+  const int block = 256, wpb = block / 32;
+  int grid = (rows + wpb - 1) / wpb;
+  if (grid > 148 * 8) grid = 148 * 8;
+  rmsnorm_bwd_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                             (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, rows, d);
+  const int parts = kmoe_rmsnorm_bwd_num_partials(rows);
+  rmsnorm_dw_kernel<<<dim3((d + 255) / 256, parts), 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
+                                                                  rstd, partial, rows, d);
+  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, (__nv_bfloat16*)dw_bf16, dw_f32, parts, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

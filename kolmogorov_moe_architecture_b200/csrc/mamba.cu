@@ -3,11 +3,9 @@
 // tensor is a column slice of a fused projection); the small per-channel parameters
 // (conv taps, bias, A, D, dt bias) and the per-step B/C vectors are fp32.
 //
-// Scan mapping: one thread per channel holding the N (=16) states in registers;
-// consecutive threads own consecutive channels so every per-step load is coalesced.
-// The 16 state recurrences are independent, which gives the ILP that hides the
-// fma/ex2 latency at the low occupancy this mapping has.  Forward stores the state at
-// every CHUNK-th step; backward replays one chunk at a time from that checkpoint into
+// Scan: a CTA owns 32 channels, a thread one channel and 4 of the N (=16) states; inputs
+// are staged through shared memory with double-buffered cp.async.  Forward stores the state
+// at every CHUNK-th step; backward replays one chunk at a time from that checkpoint into
 // shared memory and then walks it in reverse.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -19,7 +17,6 @@ namespace kmoe {
 
 constexpr int SCAN_N = 16;      // state size
 constexpr int SCAN_CHUNK = 16;  // checkpoint interval
-constexpr int SCAN_THREADS = 64;
 
 __device__ __forceinline__ float bf2f(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
@@ -27,7 +24,6 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf
 
 // ------------------------------------------------------------------ conv1d
 // y[b,t,c] = act(bias[c] + sum_j w[c,j] * x[b, t-(W-1)+j, c]),  W = 4
-constexpr int CONV_W = 4;
 constexpr int CONV_T = 64;  // time steps per thread
 
 __global__ void conv1d_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
@@ -99,8 +95,7 @@ __global__ void conv1d_bwd_kernel(const __nv_bfloat16* __restrict__ x, const flo
     x0 = x1; x1 = x2; x2 = x3;
     p0 = p1; p1 = p2; p2 = p3;
   }
-  // dx for the first three steps of this chunk needs dpre of t0..t0+2 only through later taps; the loop
-  // above starts its dpre window empty, which is exact because dx[td >= t0] never reads dpre[< t0].
+  // the dpre window starts empty, which is exact: dx[td >= t0] never reads dpre[< t0]
   atomicAdd(&dw[c * 4 + 0], aw0);
   atomicAdd(&dw[c * 4 + 1], aw1);
   atomicAdd(&dw[c * 4 + 2], aw2);
@@ -123,250 +118,284 @@ struct ScanArgs {
   int softplus;
 };
 
-__global__ void __launch_bounds__(SCAN_THREADS)
+// Thread mapping of both scan kernels: a CTA of 128 threads owns 32 consecutive channels;
+// thread = (channel, group of 4 states).  Inputs are staged through shared memory with
+// cp.async, double buffered, so the global-memory latency of tile k+1 hides behind the
+// recurrence of tile k; all global traffic is in full 64-byte rows.
+constexpr int SCAN_CH = 32;   // channels per CTA
+constexpr int SCAN_SG = 4;    // states per thread
+constexpr int FWD_T = 32;     // steps per forward stage
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const uint32_t d = smem_u32(dst);
+  const int sz = valid ? 16 : 0;   // src-size 0 zero-fills the destination
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+struct __align__(16) FwdStage {
+  __nv_bfloat16 u[FWD_T][SCAN_CH], dt[FWD_T][SCAN_CH], z[FWD_T][SCAN_CH];
+  float B[FWD_T][SCAN_N], C[FWD_T][SCAN_N];
+};
+
+__global__ void __launch_bounds__(SCAN_CH * SCAN_SG)
 scan_fwd_kernel(ScanArgs a, __nv_bfloat16* __restrict__ out, float* __restrict__ ckpt /*[B, S/CHUNK, N, C]*/) {
-  const int c = blockIdx.x * SCAN_THREADS + threadIdx.x;
-  const int b = blockIdx.y;
-  if (c >= a.C) return;
-  float An[SCAN_N], h[SCAN_N];
+  __shared__ FwdStage st[2];
+  __shared__ __align__(16) __nv_bfloat16 ytile[FWD_T][SCAN_CH];
+  const int tid = threadIdx.x, ch = tid >> 2, sg = tid & 3;
+  const int c0 = blockIdx.x * SCAN_CH, c = c0 + ch, b = blockIdx.y;
+  const bool has_z = a.z != nullptr;
+  float An[SCAN_SG], h[SCAN_SG];
 #pragma unroll
-  for (int n = 0; n < SCAN_N; ++n) {
-    An[n] = a.A[c * SCAN_N + n] * 1.4426950408889634f;  // exp(x) = 2^(x log2 e)
-    h[n] = 0.f;
+  for (int j = 0; j < SCAN_SG; ++j) {
+    An[j] = a.A[c * SCAN_N + sg * SCAN_SG + j] * 1.4426950408889634f;
+    h[j] = 0.f;
   }
   const float Dc = a.D ? a.D[c] : 0.f;
   const float bias = a.dt_bias ? a.dt_bias[c] : 0.f;
-  const size_t base = (size_t)b * a.S * a.C + c;
-  const __nv_bfloat16* up = a.u + base;
-  const __nv_bfloat16* dp = a.delta + base;
-  const __nv_bfloat16* zp = a.z ? a.z + (size_t)b * a.S * a.ldz + c : nullptr;
-  const float* Bp = a.Bm + (size_t)b * a.S * SCAN_N;
-  const float* Cp = a.Cm + (size_t)b * a.S * SCAN_N;
-  __nv_bfloat16* op = out + base;
   const int nchunks = (a.S + SCAN_CHUNK - 1) / SCAN_CHUNK;
-  for (int ch = 0; ch < nchunks; ++ch) {
-    if (ckpt != nullptr) {
-      float* ck = ckpt + (((size_t)b * nchunks + ch) * SCAN_N) * a.C + c;
+  const int ntiles = (a.S + FWD_T - 1) / FWD_T;
+  const int lrow = tid >> 2, lpart = tid & 3;
+
+  auto load_tile = [&](int s, int tile) {
+    const int t = tile * FWD_T + lrow;
+    const bool ok = t < a.S;
+    const size_t tt = (size_t)b * a.S + (ok ? t : a.S - 1);
+    cp_async16(&st[s].u[lrow][lpart * 8], a.u + tt * a.C + c0 + lpart * 8, ok);
+    cp_async16(&st[s].dt[lrow][lpart * 8], a.delta + tt * a.C + c0 + lpart * 8, ok);
+    if (has_z) cp_async16(&st[s].z[lrow][lpart * 8], a.z + tt * a.ldz + c0 + lpart * 8, ok);
+    cp_async16(&st[s].B[lrow][lpart * 4], a.Bm + tt * SCAN_N + lpart * 4, ok);
+    cp_async16(&st[s].C[lrow][lpart * 4], a.Cm + tt * SCAN_N + lpart * 4, ok);
+  };
+
+  load_tile(0, 0);
+  cp_async_commit();
+  for (int tile = 0; tile < ntiles; ++tile) {
+    const int s = tile & 1;
+    if (tile + 1 < ntiles) load_tile(s ^ 1, tile + 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+#pragma unroll 4
+    for (int i = 0; i < FWD_T; ++i) {
+      const int t = tile * FWD_T + i;
+      if (ckpt != nullptr && (i % SCAN_CHUNK) == 0 && t < a.S) {
+        float* ck = ckpt + (((size_t)b * nchunks + t / SCAN_CHUNK) * SCAN_N + sg * SCAN_SG) * a.C + c;
 #pragma unroll
-      for (int n = 0; n < SCAN_N; ++n) ck[(size_t)n * a.C] = h[n];
-    }
-    const int t0 = ch * SCAN_CHUNK;
-    float uu[SCAN_CHUNK], dd[SCAN_CHUNK], zz[SCAN_CHUNK];
-#pragma unroll
-    for (int i = 0; i < SCAN_CHUNK; ++i) {
-      const int t = t0 + i;
-      const bool ok = t < a.S;
-      uu[i] = ok ? bf2f(up[(size_t)t * a.C]) : 0.f;
-      dd[i] = ok ? bf2f(dp[(size_t)t * a.C]) : 0.f;
-      zz[i] = (ok && zp) ? bf2f(zp[(size_t)t * a.ldz]) : 0.f;
-    }
-#pragma unroll
-    for (int i = 0; i < SCAN_CHUNK; ++i) {
-      const int t = t0 + i;
-      if (t >= a.S) break;
-      float dt = dd[i] + bias;
-      if (a.softplus) dt = softplus_f(dt);
-      const float4* B4 = reinterpret_cast<const float4*>(Bp + (size_t)t * SCAN_N);
-      const float4* C4 = reinterpret_cast<const float4*>(Cp + (size_t)t * SCAN_N);
-      float Bv[SCAN_N], Cv[SCAN_N];
-#pragma unroll
-      for (int q = 0; q < SCAN_N / 4; ++q) {
-        const float4 bq = __ldg(B4 + q), cq = __ldg(C4 + q);
-        Bv[4 * q] = bq.x; Bv[4 * q + 1] = bq.y; Bv[4 * q + 2] = bq.z; Bv[4 * q + 3] = bq.w;
-        Cv[4 * q] = cq.x; Cv[4 * q + 1] = cq.y; Cv[4 * q + 2] = cq.z; Cv[4 * q + 3] = cq.w;
+        for (int j = 0; j < SCAN_SG; ++j) ck[(size_t)j * a.C] = h[j];
       }
-      const float dtu = dt * uu[i];
+      const float uu = bf2f(st[s].u[i][ch]);
+      float dt = bf2f(st[s].dt[i][ch]) + bias;
+      if (a.softplus) dt = softplus_f(dt);
+      const float4 Bq = *reinterpret_cast<const float4*>(&st[s].B[i][sg * SCAN_SG]);
+      const float4 Cq = *reinterpret_cast<const float4*>(&st[s].C[i][sg * SCAN_SG]);
+      const float Bv[4] = {Bq.x, Bq.y, Bq.z, Bq.w}, Cv[4] = {Cq.x, Cq.y, Cq.z, Cq.w};
+      const float dtu = dt * uu;
       float y = 0.f;
 #pragma unroll
-      for (int n = 0; n < SCAN_N; ++n) {
-        h[n] = exp2f(dt * An[n]) * h[n] + dtu * Bv[n];
-        y += Cv[n] * h[n];
+      for (int j = 0; j < SCAN_SG; ++j) {
+        h[j] = exp2f(dt * An[j]) * h[j] + dtu * Bv[j];
+        y += Cv[j] * h[j];
       }
-      y += Dc * uu[i];
-      if (zp) y *= silu_f(zz[i]);
-      op[(size_t)t * a.C] = __float2bfloat16(y);
+      y += __shfl_xor_sync(0xffffffffu, y, 1);
+      y += __shfl_xor_sync(0xffffffffu, y, 2);
+      y += Dc * uu;
+      if (has_z) y *= silu_f(bf2f(st[s].z[i][ch]));
+      if (sg == 0) ytile[i][ch] = __float2bfloat16(y);
+    }
+    __syncthreads();
+    {
+      const int t = tile * FWD_T + lrow;
+      if (t < a.S)
+        *reinterpret_cast<uint4*>(out + ((size_t)b * a.S + t) * a.C + c0 + lpart * 8) =
+            *reinterpret_cast<const uint4*>(&ytile[lrow][lpart * 8]);
     }
   }
+  cp_async_wait<0>();
 }
 
-// Sum `v[0..15]` across the 32 lanes; lane l (< 16) ends with the total of element l.
-__device__ __forceinline__ float warp_reduce_scatter16(float (&v)[SCAN_N], int lane) {
-  // step 1: lanes exchange halves of the 16 values with lane^16
-  float r8[8];
-  {
-    const bool hi = lane & 16;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float send = hi ? v[i] : v[i + 8];
-      const float keep = hi ? v[i + 8] : v[i];
-      r8[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-    }
-  }  // lanes with bit4=0 hold elements 0..7, bit4=1 hold 8..15
-  float r4[4];
-  {
-    const bool hi = lane & 8;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float send = hi ? r8[i] : r8[i + 4];
-      const float keep = hi ? r8[i + 4] : r8[i];
-      r4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-    }
-  }
-  float r2[2];
-  {
-    const bool hi = lane & 4;
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const float send = hi ? r4[i] : r4[i + 2];
-      const float keep = hi ? r4[i + 2] : r4[i];
-      r2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-    }
-  }
-  float r1;
-  {
-    const bool hi = lane & 2;
-    const float send = hi ? r2[0] : r2[1];
-    const float keep = hi ? r2[1] : r2[0];
-    r1 = keep + __shfl_xor_sync(0xffffffffu, send, 2);
-  }
-  r1 += __shfl_xor_sync(0xffffffffu, r1, 1);
-  // element index held by this lane: bit4 -> 8, bit3 -> 4, bit2 -> 2, bit1 -> 1
-  return r1;
-}
-__device__ __forceinline__ int reduce_scatter16_index(int lane) {
-  return ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
-}
+struct __align__(16) BwdStage {
+  __nv_bfloat16 u[SCAN_CHUNK][SCAN_CH], dt[SCAN_CHUNK][SCAN_CH], z[SCAN_CHUNK][SCAN_CH], go[SCAN_CHUNK][SCAN_CH];
+  float B[SCAN_CHUNK][SCAN_N], C[SCAN_CHUNK][SCAN_N];
+};
 
-__global__ void __launch_bounds__(SCAN_THREADS)
+__global__ void __launch_bounds__(SCAN_CH * SCAN_SG)
 scan_bwd_kernel(ScanArgs a, const __nv_bfloat16* __restrict__ dout, const float* __restrict__ ckpt,
                 __nv_bfloat16* __restrict__ du, __nv_bfloat16* __restrict__ ddelta, __nv_bfloat16* __restrict__ dz,
                 long long lddz, float* __restrict__ dA, float* __restrict__ dB, float* __restrict__ dC,
                 float* __restrict__ dD, float* __restrict__ dbias) {
-  extern __shared__ float hs[];  // [SCAN_CHUNK + 1][SCAN_N][SCAN_THREADS]; slot 0 = state before the chunk
-  const int tid = threadIdx.x;
-  const int lane = tid & 31;
-  const int c = blockIdx.x * SCAN_THREADS + tid;
-  const int b = blockIdx.y;
-  const bool live = c < a.C;
-  const int cc = live ? c : a.C - 1;
-  float An[SCAN_N], g[SCAN_N], dAacc[SCAN_N];
+  __shared__ BwdStage st[2];
+  extern __shared__ float4 hs_raw[];  // [SCAN_CHUNK + 1][128]; slot 0 = state before the chunk
+  float4 (*hs)[SCAN_CH * SCAN_SG] = reinterpret_cast<float4 (*)[SCAN_CH * SCAN_SG]>(hs_raw);
+  __shared__ float dBs[SCAN_CHUNK][SCAN_N], dCs[SCAN_CHUNK][SCAN_N];
+  __shared__ __align__(16) __nv_bfloat16 du_t[SCAN_CHUNK][SCAN_CH], dd_t[SCAN_CHUNK][SCAN_CH], dz_t[SCAN_CHUNK][SCAN_CH];
+  const int tid = threadIdx.x, lane = tid & 31, ch = tid >> 2, sg = tid & 3;
+  const int c0 = blockIdx.x * SCAN_CH, c = c0 + ch, b = blockIdx.y;
+  const bool has_z = a.z != nullptr;
+  float An[SCAN_SG], g[SCAN_SG], dAacc[SCAN_SG];
 #pragma unroll
-  for (int n = 0; n < SCAN_N; ++n) {
-    An[n] = a.A[cc * SCAN_N + n];
-    g[n] = 0.f;
-    dAacc[n] = 0.f;
+  for (int j = 0; j < SCAN_SG; ++j) {
+    An[j] = a.A[c * SCAN_N + sg * SCAN_SG + j];
+    g[j] = 0.f;
+    dAacc[j] = 0.f;
   }
-  const float Dc = a.D ? a.D[cc] : 0.f;
-  const float bias = a.dt_bias ? a.dt_bias[cc] : 0.f;
+  const float Dc = a.D ? a.D[c] : 0.f;
+  const float bias = a.dt_bias ? a.dt_bias[c] : 0.f;
   float dDacc = 0.f, dbacc = 0.f;
-  const size_t base = (size_t)b * a.S * a.C + cc;
-  const __nv_bfloat16* up = a.u + base;
-  const __nv_bfloat16* dp = a.delta + base;
-  const __nv_bfloat16* zp = a.z ? a.z + (size_t)b * a.S * a.ldz + cc : nullptr;
-  const __nv_bfloat16* gp = dout + base;
-  const float* Bp = a.Bm + (size_t)b * a.S * SCAN_N;
-  const float* Cp = a.Cm + (size_t)b * a.S * SCAN_N;
   const int nchunks = (a.S + SCAN_CHUNK - 1) / SCAN_CHUNK;
-#define HS(t, n) hs[((t) * SCAN_N + (n)) * SCAN_THREADS + tid]
-  for (int ch = nchunks - 1; ch >= 0; --ch) {
-    const int t0 = ch * SCAN_CHUNK;
-    const int len = min(SCAN_CHUNK, a.S - t0);
-    const float* ck = ckpt + (((size_t)b * nchunks + ch) * SCAN_N) * a.C + cc;
-    float h[SCAN_N];
-#pragma unroll
-    for (int n = 0; n < SCAN_N; ++n) {
-      h[n] = ck[(size_t)n * a.C];
-      HS(0, n) = h[n];
+  for (int i = tid; i < SCAN_CHUNK * SCAN_N; i += blockDim.x) {
+    (&dBs[0][0])[i] = 0.f;
+    (&dCs[0][0])[i] = 0.f;
+  }
+
+  // 6 arrays x 64 sixteen-byte pieces per stage; each thread copies three of them
+  const int lrow = (tid & 63) >> 2, lpart = tid & 3, lhalf = tid >> 6;
+  auto load_chunk = [&](int s, int chunk) {
+    const int t = chunk * SCAN_CHUNK + lrow;
+    const bool ok = t < a.S;
+    const size_t tt = (size_t)b * a.S + (ok ? t : a.S - 1);
+    if (lhalf == 0) {
+      cp_async16(&st[s].u[lrow][lpart * 8], a.u + tt * a.C + c0 + lpart * 8, ok);
+      cp_async16(&st[s].go[lrow][lpart * 8], dout + tt * a.C + c0 + lpart * 8, ok);
+      cp_async16(&st[s].B[lrow][lpart * 4], a.Bm + tt * SCAN_N + lpart * 4, ok);
+    } else {
+      cp_async16(&st[s].dt[lrow][lpart * 8], a.delta + tt * a.C + c0 + lpart * 8, ok);
+      if (has_z) cp_async16(&st[s].z[lrow][lpart * 8], a.z + tt * a.ldz + c0 + lpart * 8, ok);
+      cp_async16(&st[s].C[lrow][lpart * 4], a.Cm + tt * SCAN_N + lpart * 4, ok);
     }
-    float uu[SCAN_CHUNK], dt_[SCAN_CHUNK];
-    // replay forward, keeping every state of the chunk
+  };
+
+  load_chunk(0, nchunks - 1);
+  cp_async_commit();
+  int s = 0;
+  for (int chk = nchunks - 1; chk >= 0; --chk, s ^= 1) {
+    if (chk > 0) load_chunk(s ^ 1, chk - 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int t0 = chk * SCAN_CHUNK;
+    const int len = min(SCAN_CHUNK, a.S - t0);
+    float h[SCAN_SG];
+    {
+      const float* ck = ckpt + (((size_t)b * nchunks + chk) * SCAN_N + sg * SCAN_SG) * a.C + c;
+#pragma unroll
+      for (int j = 0; j < SCAN_SG; ++j) h[j] = ck[(size_t)j * a.C];
+      hs[0][tid] = make_float4(h[0], h[1], h[2], h[3]);
+    }
+    float uu[SCAN_CHUNK], dtv[SCAN_CHUNK];
+    // replay the chunk forward, keeping every state
 #pragma unroll
     for (int i = 0; i < SCAN_CHUNK; ++i) {
-      if (i >= len) break;
-      const int t = t0 + i;
-      uu[i] = bf2f(up[(size_t)t * a.C]);
-      float dt = bf2f(dp[(size_t)t * a.C]) + bias;
+      uu[i] = bf2f(st[s].u[i][ch]);
+      float dt = bf2f(st[s].dt[i][ch]) + bias;
       if (a.softplus) dt = softplus_f(dt);
-      dt_[i] = dt;
-      const float4* B4 = reinterpret_cast<const float4*>(Bp + (size_t)t * SCAN_N);
+      dtv[i] = dt;
+      const float4 Bq = *reinterpret_cast<const float4*>(&st[s].B[i][sg * SCAN_SG]);
+      const float Bv[4] = {Bq.x, Bq.y, Bq.z, Bq.w};
       const float dtu = dt * uu[i];
 #pragma unroll
-      for (int q = 0; q < SCAN_N / 4; ++q) {
-        const float4 bq = __ldg(B4 + q);
-        const float bv[4] = {bq.x, bq.y, bq.z, bq.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int n = 4 * q + j;
-          h[n] = __expf(dt * An[n]) * h[n] + dtu * bv[j];
-          HS(i + 1, n) = h[n];
-        }
-      }
+      for (int j = 0; j < SCAN_SG; ++j) h[j] = __expf(dt * An[j]) * h[j] + dtu * Bv[j];
+      hs[i + 1][tid] = make_float4(h[0], h[1], h[2], h[3]);
     }
     // reverse sweep
 #pragma unroll
     for (int i = SCAN_CHUNK - 1; i >= 0; --i) {
-      if (i >= len) continue;
-      const int t = t0 + i;
-      const float dt = dt_[i], u = uu[i];
-      const float go = live ? bf2f(gp[(size_t)t * a.C]) : 0.f;
-      const float4* B4 = reinterpret_cast<const float4*>(Bp + (size_t)t * SCAN_N);
-      const float4* C4 = reinterpret_cast<const float4*>(Cp + (size_t)t * SCAN_N);
-      float Bv[SCAN_N], Cv[SCAN_N];
+      if (i >= len) continue;           // uniform across the CTA
+      const float dt = dtv[i], u = uu[i];
+      const float go = bf2f(st[s].go[i][ch]);
+      const float4 Bq = *reinterpret_cast<const float4*>(&st[s].B[i][sg * SCAN_SG]);
+      const float4 Cq = *reinterpret_cast<const float4*>(&st[s].C[i][sg * SCAN_SG]);
+      const float Bv[4] = {Bq.x, Bq.y, Bq.z, Bq.w}, Cv[4] = {Cq.x, Cq.y, Cq.z, Cq.w};
+      const float4 hc4 = hs[i + 1][tid], hp4 = hs[i][tid];
+      const float hc[4] = {hc4.x, hc4.y, hc4.z, hc4.w}, hp[4] = {hp4.x, hp4.y, hp4.z, hp4.w};
+      float dy = go, dzv = 0.f;
+      if (has_z) {
+        float yp = 0.f;
 #pragma unroll
-      for (int q = 0; q < SCAN_N / 4; ++q) {
-        const float4 bq = __ldg(B4 + q), cq = __ldg(C4 + q);
-        Bv[4 * q] = bq.x; Bv[4 * q + 1] = bq.y; Bv[4 * q + 2] = bq.z; Bv[4 * q + 3] = bq.w;
-        Cv[4 * q] = cq.x; Cv[4 * q + 1] = cq.y; Cv[4 * q + 2] = cq.z; Cv[4 * q + 3] = cq.w;
+        for (int j = 0; j < SCAN_SG; ++j) yp += Cv[j] * hc[j];
+        yp += __shfl_xor_sync(0xffffffffu, yp, 1);
+        yp += __shfl_xor_sync(0xffffffffu, yp, 2);
+        yp += Dc * u;
+        const float zv = bf2f(st[s].z[i][ch]);
+        const float sgm = sigmoid_f(zv);
+        dzv = go * yp * sgm * (1.f + zv * (1.f - sgm));
+        dy = go * zv * sgm;
       }
-      // y before gating (needed for dz)
-      float ypre = Dc * u;
+      float ddt = 0.f, du_p = 0.f;
+      float dBv[SCAN_SG], dCv[SCAN_SG];
 #pragma unroll
-      for (int n = 0; n < SCAN_N; ++n) ypre += Cv[n] * HS(i + 1, n);
-      float dy = go;
-      if (zp) {
-        const float zv = bf2f(zp[(size_t)t * a.ldz]);
-        const float sg = sigmoid_f(zv);
-        if (live) dz[(size_t)b * a.S * lddz + (size_t)t * lddz + cc] = __float2bfloat16(go * ypre * sg * (1.f + zv * (1.f - sg)));
-        dy = go * zv * sg;
+      for (int j = 0; j < SCAN_SG; ++j) {
+        dCv[j] = dy * hc[j];
+        g[j] += Cv[j] * dy;
+        const float dA_t = __expf(dt * An[j]);
+        const float gh = g[j] * hp[j] * dA_t;
+        ddt += gh * An[j] + g[j] * Bv[j] * u;
+        dAacc[j] += gh * dt;
+        dBv[j] = g[j] * dt * u;
+        du_p += g[j] * dt * Bv[j];
+        g[j] *= dA_t;
       }
-      dDacc += dy * u;
-      float du_v = dy * Dc;
-      float ddt = 0.f;
-      float dBv[SCAN_N], dCv[SCAN_N];
-#pragma unroll
-      for (int n = 0; n < SCAN_N; ++n) {
-        const float hprev = HS(i, n);
-        const float hcur = HS(i + 1, n);
-        dCv[n] = dy * hcur;
-        g[n] += Cv[n] * dy;                       // adjoint of h_t
-        const float dA_t = __expf(dt * An[n]);
-        const float gh = g[n] * hprev * dA_t;     // d/d(dt*A)
-        ddt += gh * An[n] + g[n] * Bv[n] * u;
-        dAacc[n] += gh * dt;
-        dBv[n] = g[n] * dt * u;
-        du_v += g[n] * dt * Bv[n];
-        g[n] *= dA_t;                             // carry to step t-1
-      }
+      ddt += __shfl_xor_sync(0xffffffffu, ddt, 1);
+      ddt += __shfl_xor_sync(0xffffffffu, ddt, 2);
+      du_p += __shfl_xor_sync(0xffffffffu, du_p, 1);
+      du_p += __shfl_xor_sync(0xffffffffu, du_p, 2);
       float dd = ddt;
-      if (a.softplus) dd *= sigmoid_f(bf2f(dp[(size_t)t * a.C]) + bias);
-      dbacc += dd;
-      if (live) {
-        du[base + (size_t)t * a.C] = __float2bfloat16(du_v);
-        ddelta[base + (size_t)t * a.C] = __float2bfloat16(dd);
+      if (a.softplus) dd *= sigmoid_f(bf2f(st[s].dt[i][ch]) + bias);
+      if (sg == 0) {
+        dDacc += dy * u;
+        dbacc += dd;
+        du_t[i][ch] = __float2bfloat16(du_p + dy * Dc);
+        dd_t[i][ch] = __float2bfloat16(dd);
+        dz_t[i][ch] = __float2bfloat16(dzv);
       }
-      const float sB = warp_reduce_scatter16(dBv, lane);
-      const float sC = warp_reduce_scatter16(dCv, lane);
-      if ((lane & 1) == 0) {
-        const int n = reduce_scatter16_index(lane);
-        atomicAdd(&dB[((size_t)b * a.S + t) * SCAN_N + n], sB);
-        atomicAdd(&dC[((size_t)b * a.S + t) * SCAN_N + n], sC);
+      // sum dB, dC over the 8 channels of this warp (lanes with equal sg), then over warps in smem
+#pragma unroll
+      for (int j = 0; j < SCAN_SG; ++j) {
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          dBv[j] += __shfl_xor_sync(0xffffffffu, dBv[j], o);
+          dCv[j] += __shfl_xor_sync(0xffffffffu, dCv[j], o);
+        }
+      }
+      if (lane < 4) {
+#pragma unroll
+        for (int j = 0; j < SCAN_SG; ++j) {
+          atomicAdd(&dBs[i][sg * SCAN_SG + j], dBv[j]);
+          atomicAdd(&dCs[i][sg * SCAN_SG + j], dCv[j]);
+        }
       }
     }
+    __syncthreads();
+    // flush the chunk: coalesced du / ddelta / dz rows, and the channel-summed dB / dC
+    if (tid < 64) {
+      const int t = t0 + lrow;
+      if (t < a.S) {
+        const size_t o = ((size_t)b * a.S + t) * a.C + c0 + lpart * 8;
+        *reinterpret_cast<uint4*>(du + o) = *reinterpret_cast<const uint4*>(&du_t[lrow][lpart * 8]);
+        *reinterpret_cast<uint4*>(ddelta + o) = *reinterpret_cast<const uint4*>(&dd_t[lrow][lpart * 8]);
+        if (has_z)
+          *reinterpret_cast<uint4*>(dz + ((size_t)b * a.S + t) * lddz + c0 + lpart * 8) =
+              *reinterpret_cast<const uint4*>(&dz_t[lrow][lpart * 8]);
+      }
+    }
+    for (int i = tid; i < SCAN_CHUNK * SCAN_N; i += blockDim.x) {
+      const int row = i / SCAN_N;
+      if (row < len) {
+        const size_t o = ((size_t)b * a.S + t0 + row) * SCAN_N + (i % SCAN_N);
+        atomicAdd(&dB[o], (&dBs[0][0])[i]);
+        atomicAdd(&dC[o], (&dCs[0][0])[i]);
+      }
+      (&dBs[0][0])[i] = 0.f;
+      (&dCs[0][0])[i] = 0.f;
+    }
+    __syncthreads();
   }
-#undef HS
-  if (live) {
+  cp_async_wait<0>();
 #pragma unroll
-    for (int n = 0; n < SCAN_N; ++n) atomicAdd(&dA[c * SCAN_N + n], dAacc[n]);
+  for (int j = 0; j < SCAN_SG; ++j) atomicAdd(&dA[c * SCAN_N + sg * SCAN_SG + j], dAacc[j]);
+  if (sg == 0) {
     if (dD) atomicAdd(&dD[c], dDacc);
     if (dbias) atomicAdd(&dbias[c], dbacc);
   }
@@ -399,8 +428,9 @@ extern "C" int kmoe_scan_fwd(const void* u, const void* delta, const void* z, co
   if (N != SCAN_N) return -1;
   ScanArgs a{(const __nv_bfloat16*)u, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)z, A, Bm, Cm, D, dt_bias,
              S, C, ldz, softplus};
-  dim3 grid((C + SCAN_THREADS - 1) / SCAN_THREADS, B);
-  scan_fwd_kernel<<<grid, SCAN_THREADS, 0, st>>>(a, (__nv_bfloat16*)out, ckpt);
+  if (C % SCAN_CH || (z != nullptr && ldz % 8)) return -4;
+  dim3 grid(C / SCAN_CH, B);
+  scan_fwd_kernel<<<grid, SCAN_CH * SCAN_SG, 0, st>>>(a, (__nv_bfloat16*)out, ckpt);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -413,16 +443,17 @@ extern "C" int kmoe_scan_bwd(const void* u, const void* delta, const void* z, co
   if (N != SCAN_N) return -1;
   ScanArgs a{(const __nv_bfloat16*)u, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)z, A, Bm, Cm, D, dt_bias,
              S, C, ldz, softplus};
-  const int smem = (SCAN_CHUNK + 1) * SCAN_N * SCAN_THREADS * sizeof(float);
+  if (C % SCAN_CH || (z != nullptr && (ldz % 8 || lddz % 8))) return -4;
+  dim3 grid(C / SCAN_CH, B);
+  const int hs_bytes = (SCAN_CHUNK + 1) * SCAN_CH * SCAN_SG * sizeof(float4);
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, hs_bytes) != cudaSuccess)
       return -3;
     attr = true;
   }
-  dim3 grid((C + SCAN_THREADS - 1) / SCAN_THREADS, B);
-  scan_bwd_kernel<<<grid, SCAN_THREADS, smem, st>>>(a, (const __nv_bfloat16*)dout, ckpt, (__nv_bfloat16*)du,
-                                                    (__nv_bfloat16*)ddelta, (__nv_bfloat16*)dz, lddz, dA, dB, dC, dD,
-                                                    dbias);
+  scan_bwd_kernel<<<grid, SCAN_CH * SCAN_SG, hs_bytes, st>>>(a, (const __nv_bfloat16*)dout, ckpt, (__nv_bfloat16*)du,
+                                                     (__nv_bfloat16*)ddelta, (__nv_bfloat16*)dz, lddz, dA, dB, dC,
+                                                     dD, dbias);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
