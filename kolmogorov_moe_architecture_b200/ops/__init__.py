@@ -67,6 +67,8 @@ def selective_scan(u, delta, A, Bm, Cm, D, z, delta_bias, delta_softplus=True):
 
 
 def grouped_swiglu(x, w1, w2, w3, idx, weights, keep=None, moe_dtype="bf16"):
+    if x.shape[0] == 0:
+        return x * 0
     if _use_cuda(x):
         from . import cuda_ops
         return cuda_ops.grouped_swiglu(x, w1, w2, w3, idx, weights, keep, moe_dtype)
