@@ -281,3 +281,44 @@ extern "C" int kmoe_swiglu_bwd(const void* g, const void* u, const void* dh, voi
       (__nv_bfloat16*)du, rows, cols, ldg, ldu, ldo);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+// ------------------------------------------------- allocation-free RMSNorm backward
+// See kmoe_noalloc.h.  The scratch lives in the device image; host code must not pass the
+// symbol itself to a kernel (on the host it is only a stand-in), so its device address is
+// looked up once per device and cached.
+#include "kmoe_noalloc.h"
+
+namespace kmoe {
+constexpr int NOALLOC_PARTS = 64;
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_PARTS * KMOE_NOALLOC_MAX_D];
+static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+}  // namespace kmoe
+
+extern "C" int kmoe_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy, const float* rstd, void* dx,
+                                        float* dw_f32, int rows, int d, cudaStream_t st) {
+  if (rows < 1 || d < 8 || d % 8 != 0 || d > KMOE_NOALLOC_MAX_D) return KMOE_NOALLOC_E_SIZE;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return KMOE_NOALLOC_E_SYMBOL;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // first call on this device: resolve the array's device address (device `dev` is current)
+    float* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_noalloc_scratch) != cudaSuccess || p == nullptr)
+      return KMOE_NOALLOC_E_SYMBOL;
+    g_noalloc_ptr[dev] = p;
+  }
+  float* partial = g_noalloc_ptr[dev];
+  const int block = 256, wpb = block / 32;
+  int grid = (rows + wpb - 1) / wpb;
+  if (grid > 148 * 8) grid = 148 * 8;
+  rmsnorm_bwd_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                             (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, rows, d);
+  int parts = kmoe_rmsnorm_bwd_num_partials(rows);
+  if (parts > NOALLOC_PARTS) parts = NOALLOC_PARTS;
+  // every partial row that is summed below is fully written by rmsnorm_dw_kernel first, so nothing
+  // left over from an earlier call is ever read and no clearing pass is needed
+  rmsnorm_dw_kernel<<<dim3((d + 255) / 256, parts), 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
+                                                                  rstd, partial, rows, d);
+  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, nullptr, dw_f32, parts, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : KMOE_NOALLOC_E_LAUNCH;
+}
