@@ -39,6 +39,8 @@ def parse_args():
     ap.add_argument("--mamba-moe-mode", default="moe_ffn", choices=["moe_ffn", "routing_mamba"])
     ap.add_argument("--optimizer", default="muon", choices=["muon", "adamw"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--transport", default=None, choices=[None, "p2p", "nccl"],
+                    help="gradient/parameter collectives: own NVLink peer kernels (default when available) or NCCL")
     return ap.parse_args()
 
 
@@ -118,7 +120,6 @@ def max_over_ranks(x: float, world: int) -> float:
 def run_ours(args):
     import kolmogorov_moe_architecture_b200 as kmoe
     from kolmogorov_moe_architecture_b200.training.engine import TrainEngine
-    from kolmogorov_moe_architecture_b200.training.optim_factory import build_optimizer
     from kolmogorov_moe_architecture_b200.ops import cuda_ops
 
     world, rank, local = dist_setup(args)
@@ -134,13 +135,9 @@ def run_ours(args):
     with torch.device(dev):
         model = kmoe.MoETransformer(cfg, verbose=(rank == 0)).to(torch.bfloat16)
     n_params = sum(p.numel() for p in model.parameters())
-    dp = None
-    if world > 1:
-        from kolmogorov_moe_architecture_b200.parallel.zero import ShardedDataParallel
-        dp = ShardedDataParallel(model, optimizer_kind=args.optimizer)
-        optimizer = dp.optimizer
-    else:
-        optimizer = build_optimizer(model, kind=args.optimizer)
+    from kolmogorov_moe_architecture_b200.parallel.zero import ShardedDataParallel
+    dp = ShardedDataParallel(model, optimizer_kind=args.optimizer, transport=args.transport)
+    optimizer = dp.optimizer
     engine = TrainEngine(model, optimizer, grad_clip=1.0, dp=dp, device=dev)
 
     B, S = args.micro_batch, args.seq_len
@@ -194,7 +191,7 @@ def run_ours(args):
             "config": {"model": "5B hybrid MoE (32L d2048 16/4 heads, 16 experts top-2 x16 MoE layers, "
                                 "Mamba d_state16, MoD 0.75, 4-token MTP, vocab 50304)",
                        "params_b": round(n_params / 1e9, 3), "global_batch": B * world, "seq_len": S,
-                       "parallelism": f"dp{world}" + ("-zero1" if world > 1 else ""),
+                       "parallelism": f"dp{world}" + (f"-zero1-{dp.transport}" if world > 1 else ""),
                        "optimizer": args.optimizer, "mamba_moe_mode": args.mamba_moe_mode,
                        "l2": "inputs+weights (>11 GB) exceed L2 between iterations",
                        "peak_mem_gb": round(peak_gb, 1), "valid_config": valid},

@@ -290,6 +290,37 @@ Tensor ce_fwd_bwd(Tensor logits, const Tensor& labels, const Tensor& grad_scale,
   return loss_rows;
 }
 
+// ------------------------------------------------------------- peer-to-peer collectives
+void p2p_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t world, int64_t epoch, double timeout_s,
+                 Tensor status) {
+  c10::cuda::CUDAGuard guard(status.device());
+  check(kmoe_p2p_barrier((const long long*)flag_ptrs.data(), (int)rank, (int)world, (int)epoch, timeout_s,
+                         status.data_ptr<int>(), cur_stream()), "p2p_barrier");
+}
+
+void p2p_reduce_scatter(std::vector<int64_t> grad_ptrs, int64_t rank, int64_t world, int64_t off, int64_t n,
+                        const OptT& sq_out) {
+  check(kmoe_p2p_reduce_scatter((const long long*)grad_ptrs.data(), (int)rank, (int)world, off, n,
+                                (float*)const_cast<void*>(ptr_or_null(sq_out)), cur_stream()), "p2p_reduce_scatter");
+}
+
+void p2p_adamw_allgather(std::vector<int64_t> param_ptrs, const Tensor& grad, Tensor m, Tensor v, int64_t rank,
+                         int64_t world, int64_t off, int64_t n, double lr, double beta1, double beta2, double eps,
+                         double wd, int64_t step, const OptT& clip_coef) {
+  c10::cuda::CUDAGuard guard(grad.device());
+  need_bf16(grad, "grad"); need_f32(m, "m"); need_f32(v, "v");
+  TORCH_CHECK(m.numel() >= n && v.numel() >= n, "moment buffers too small");
+  check(kmoe_p2p_adamw_allgather((const long long*)param_ptrs.data(), grad.data_ptr(), m.data_ptr<float>(),
+                                 v.data_ptr<float>(), (int)rank, (int)world, off, n, (float)lr, (float)beta1,
+                                 (float)beta2, (float)eps, (float)wd, (int)step, (const float*)ptr_or_null(clip_coef),
+                                 cur_stream()), "p2p_adamw_allgather");
+}
+
+void p2p_allgather(std::vector<int64_t> buf_ptrs, int64_t rank, int64_t world, int64_t off, int64_t n) {
+  check(kmoe_p2p_allgather((const long long*)buf_ptrs.data(), (int)rank, (int)world, off, n, cur_stream()),
+        "p2p_allgather");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(kmoe, m) {
@@ -310,4 +341,8 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("ce_fwd_bwd", &ce_fwd_bwd);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
+  m.def("p2p_barrier", &p2p_barrier);
+  m.def("p2p_reduce_scatter", &p2p_reduce_scatter);
+  m.def("p2p_adamw_allgather", &p2p_adamw_allgather);
+  m.def("p2p_allgather", &p2p_allgather);
 }

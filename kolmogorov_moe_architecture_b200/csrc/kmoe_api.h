@@ -91,6 +91,17 @@ int kmoe_attn_bwd(const void* q, const void* k, const void* v, const void* o, co
                   float* delta, void* dq, void* dk, void* dv, int B, int S, int H, int Hkv, int D, float scale,
                   int* status, cudaStream_t st);
 
+// ------------------------------------------- collectives over NVLink peer pointers
+// `*_ptrs`: device addresses (as integers) of the same symmetric buffer on every rank, indexed by rank.
+int kmoe_p2p_barrier(const long long* flag_ptrs, int rank, int world, int epoch, double timeout_s, int* status,
+                     cudaStream_t st);
+int kmoe_p2p_reduce_scatter(const long long* grad_ptrs, int rank, int world, long long off, long long n,
+                            float* sq_out, cudaStream_t st);
+int kmoe_p2p_adamw_allgather(const long long* param_ptrs, const void* grad, float* m, float* v, int rank, int world,
+                             long long off, long long n, float lr, float beta1, float beta2, float eps, float wd,
+                             int step, const float* clip_coef, cudaStream_t st);
+int kmoe_p2p_allgather(const long long* buf_ptrs, int rank, int world, long long off, long long n, cudaStream_t st);
+
 // ---------------------------------------------------------------------------- loss
 int kmoe_ce_fwd_bwd(void* logits, const long long* labels, float* loss_rows, const float* grad_scale, int R, int V,
                     long long ld, long long ignore_index, int write_grad, cudaStream_t st);

@@ -13,10 +13,16 @@ Ownership is per tensor, not per flat byte range: every parameter (2-D matrices 
 expert stacks included) belongs to exactly one rank, so Muon's Newton-Schulz runs on whole
 matrices on the owner with no gather, and each rank orthogonalises only its share of the
 matrices.  Rank r's tensors are packed into segment r of two flat buffers (parameters and
-gradients) whose segments have equal size; ``reduce_scatter_tensor`` then hands each owner
-the averaged gradients of exactly its tensors, and ``all_gather_into_tensor`` publishes the
-updated tensors.  On CUDA with peer access the same two steps run as this library's own
-kernels over NVLink peer pointers (:mod:`.p2p`), fused with the AdamW update.
+gradients) whose segments have equal size, AdamW-updated tensors first and Muon-updated
+matrices after them.
+
+Three transports for the two collectives:
+* ``p2p`` (CUDA ranks with peer access): the buffers live in symmetric memory and this
+  library's kernels do the work over NVLink peer pointers - the reduce-scatter is fused
+  with the squared-norm reduction for clipping, and the AdamW update is fused with the
+  all-gather (the kernel stores each new parameter into every rank's buffer).
+* ``nccl``: ``reduce_scatter_tensor`` / ``all_gather_into_tensor``.
+* ``gloo`` (CPU tests): all-reduce + slice, all-gather.
 
 Gradient accumulation needs no ``no_sync`` bookkeeping: gradients accumulate locally in the
 flat buffer and are reduced once, when the step is taken.
@@ -50,18 +56,59 @@ def assign_owners(numels: List[int], world: int) -> List[int]:
     return owner
 
 
+def is_muon_param(name: str, p: torch.Tensor) -> bool:
+    nl = name.lower()
+    return p.dim() == 2 and ".weight" in nl and not any(t in nl for t in _EXCLUDE)
+
+
+class FusedAdamW:
+    """AdamW over one contiguous range of a flat bf16 buffer with fp32 moments, run by the
+    ``p2p_adamw_allgather`` kernel: clip coefficient read on the device, result stored into
+    every buffer in ``param_ptrs`` (all ranks under p2p, only this rank otherwise)."""
+
+    def __init__(self, flat_param, flat_grad, start: int, n: int, lr, betas=(0.9, 0.95), eps=1e-8,
+                 weight_decay=0.01):
+        self.flat_param, self.flat_grad, self.start, self.n = flat_param, flat_grad, start, n
+        self.m = torch.zeros(n, dtype=torch.float32, device=flat_param.device)
+        self.v = torch.zeros(n, dtype=torch.float32, device=flat_param.device)
+        self.param_groups = [dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay, params=[])]
+        self.step_count = 0
+
+    def step(self, param_ptrs: List[int], rank: int, clip_coef: Optional[torch.Tensor]):
+        from ..ops import cuda_ops
+        g = self.param_groups[0]
+        self.step_count += 1
+        torch.ops.kmoe.p2p_adamw_allgather(param_ptrs, self.flat_grad, self.m, self.v, rank, len(param_ptrs),
+                                           self.start, self.n, g["lr"], g["betas"][0], g["betas"][1], g["eps"],
+                                           g["weight_decay"], self.step_count, clip_coef)
+        cuda_ops._count()
+
+    def state_dict(self):
+        return {"m": self.m, "v": self.v, "step": self.step_count,
+                "hyper": {k: v for k, v in self.param_groups[0].items() if k != "params"}}
+
+    def load_state_dict(self, sd):
+        self.m.copy_(sd["m"])
+        self.v.copy_(sd["v"])
+        self.step_count = sd["step"]
+
+
 class ShardedDataParallel:
     def __init__(self, model: torch.nn.Module, optimizer_kind: str = "muon", group=None,
                  lr: float = 1e-3, adamw_lr: float = 3e-4, momentum: float = 0.95,
-                 weight_decay: float = 0.01, newton_iters: int = 5, use_p2p: Optional[bool] = None,
-                 broadcast_from_rank0: bool = True, expert_params: bool = False, grad_scale: float = 1.0):
+                 weight_decay: float = 0.01, newton_iters: int = 5, transport: Optional[str] = None,
+                 broadcast_from_rank0: bool = True, expert_params: bool = False, grad_scale: float = 1.0,
+                 fused_adamw: Optional[bool] = None):
         """``expert_params=False``: all parameters except expert-parallel ones (``group`` = every
         data-parallel rank).  ``expert_params=True``: only the expert-parallel tensors, with
         ``group`` the ranks that hold replicas of the same experts and ``grad_scale = 1/ep``
-        (an expert's gradient already sums the losses of the ep ranks that sent it tokens)."""
+        (an expert's gradient already sums the losses of the ep ranks that sent it tokens).
+        ``transport``: ``p2p`` | ``nccl`` | ``gloo`` | None (= p2p when available)."""
         self.model, self.group = model, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.grad_scale = grad_scale
+        self.kind = optimizer_kind
         named: List[Tuple[str, torch.nn.Parameter]] = []
         seen = set()
         for n, p in model.named_parameters():
@@ -74,109 +121,146 @@ class ShardedDataParallel:
         dtype, device = named[0][1].dtype, named[0][1].device
         assert all(p.dtype == dtype for _, p in named), "parameters must share one dtype"
         self.dtype, self.device = dtype, device
+        muon_flag = [optimizer_kind == "muon" and is_muon_param(n, p) for n, p in named]
         owners = assign_owners([p.numel() for _, p in named], self.world)
+        # segment layout: AdamW tensors first, Muon matrices after them
         offsets = [0] * self.world
-        self.slots: List[Tuple[int, int]] = []          # (owner, offset in segment)
-        for (n, p), r in zip(named, owners):
-            self.slots.append((r, offsets[r]))
-            offsets[r] += _round_up(p.numel(), _ALIGN)
-        self.seg = _round_up(max(offsets) if offsets else _ALIGN, _ALIGN)
+        self.slots: List[Optional[Tuple[int, int]]] = [None] * len(named)
+        for want_muon in (False, True):
+            if want_muon:
+                self.adamw_end = list(offsets)
+            for i, ((n, p), r) in enumerate(zip(named, owners)):
+                if muon_flag[i] == want_muon:
+                    self.slots[i] = (r, offsets[r])
+                    offsets[r] += _round_up(p.numel(), _ALIGN)
+        self.used = list(offsets)
+        self.seg = _round_up(max(offsets), _ALIGN)
         total = self.seg * self.world
-        self.use_p2p = False
-        if use_p2p is None:
-            use_p2p = False
-        self.flat_param, self.flat_grad, self.p2p = self._alloc(total, use_p2p)
+
+        self.transport = self._pick_transport(transport)
+        self.p2p = None
+        if self.transport == "p2p":
+            from .p2p import SymmetricBuffers
+            self.p2p = SymmetricBuffers(total, dtype, device, group)
+            self.flat_param, self.flat_grad = self.p2p.param, self.p2p.grad
+        else:
+            self.flat_param = torch.zeros(total, dtype=dtype, device=device)
+            self.flat_grad = torch.zeros(total, dtype=dtype, device=device)
         with torch.no_grad():
             for (n, p), (r, off) in zip(named, self.slots):
-                view = self.flat_param[r * self.seg + off: r * self.seg + off + p.numel()].view_as(p)
+                a = r * self.seg + off
+                view = self.flat_param[a: a + p.numel()].view_as(p)
                 view.copy_(p.data)
                 p.data = view
-                p.grad = self.flat_grad[r * self.seg + off: r * self.seg + off + p.numel()].view_as(p)
+                p.grad = self.flat_grad[a: a + p.numel()].view_as(p)
         if broadcast_from_rank0 and self.world > 1:
             dist.broadcast(self.flat_param, src=dist.get_global_rank(group, 0) if group is not None else 0,
                            group=group)
         self.owned = [(n, p) for (n, p), (r, _) in zip(named, self.slots) if r == self.rank]
-        self.optimizer = self._build_optimizer(optimizer_kind, lr, adamw_lr, momentum, weight_decay, newton_iters)
-        self._sync = True
-        self.grad_scale = grad_scale
+        self.owned_muon = [(n, p) for i, ((n, p), (r, _)) in enumerate(zip(named, self.slots))
+                           if r == self.rank and muon_flag[i]]
+        self.owned_adamw = [(n, p) for i, ((n, p), (r, _)) in enumerate(zip(named, self.slots))
+                            if r == self.rank and not muon_flag[i]]
+        if fused_adamw is None:
+            fused_adamw = device.type == "cuda" and dtype == torch.bfloat16
+        self.fused: Optional[FusedAdamW] = None
+        self.muon: Optional[Muon] = None
+        self.adamw = None
+        my_adamw_n = self.adamw_end[self.rank] if optimizer_kind == "muon" else self.used[self.rank]
+        if optimizer_kind == "muon" and self.owned_muon:
+            self.muon = Muon([p for _, p in self.owned_muon], lr=lr, momentum=momentum, weight_decay=weight_decay,
+                             newton_iters=newton_iters)
+        if fused_adamw and my_adamw_n > 0:
+            self.fused = FusedAdamW(self.flat_param, self.flat_grad, self.rank * self.seg, my_adamw_n, adamw_lr,
+                                    weight_decay=weight_decay)
+        elif self.owned_adamw:
+            self.adamw = make_adamw([p for _, p in self.owned_adamw], adamw_lr, weight_decay=weight_decay)
+        self.optimizer = _PoolOptimizer(self)
+        self._clip: Optional[torch.Tensor] = None
+        self._sq = torch.zeros(1, dtype=torch.float32, device=device)
 
     # ------------------------------------------------------------------ set-up
-    def _alloc(self, total: int, use_p2p: bool):
-        if use_p2p and self.device.type == "cuda" and self.world > 1:
+    def _pick_transport(self, want: Optional[str]) -> str:
+        if self.world == 1:
+            return "local"
+        backend = dist.get_backend(self.group)
+        if want in ("nccl", "gloo"):
+            return want
+        if self.device.type == "cuda" and want in (None, "p2p"):
             try:
-                from .p2p import SymmetricBuffers
-                sb = SymmetricBuffers(total, self.dtype, self.device, self.group)
-                self.use_p2p = True
-                return sb.param, sb.grad, sb
-            except Exception as e:  # pragma: no cover - needs multi-GPU peer access
-                if self.rank == 0:
-                    print(f"[zero] symmetric memory unavailable ({e}); using NCCL collectives")
-        fp = torch.zeros(total, dtype=self.dtype, device=self.device)
-        fg = torch.zeros(total, dtype=self.dtype, device=self.device)
-        return fp, fg, None
-
-    def _build_optimizer(self, kind, lr, adamw_lr, momentum, wd, iters):
-        if kind == "adamw":
-            ps = [p for _, p in self.owned]
-            return make_adamw(ps, adamw_lr, weight_decay=wd) if ps else None
-        muon_p, adamw_p = [], []
-        for n, p in self.owned:
-            nl = n.lower()
-            is_w = ".weight" in nl and not any(t in nl for t in _EXCLUDE)
-            (muon_p if (is_w and p.dim() == 2) else adamw_p).append(p)
-        muon = Muon(muon_p, lr=lr, momentum=momentum, weight_decay=wd, newton_iters=iters) if muon_p else None
-        adamw = make_adamw(adamw_p, adamw_lr, weight_decay=wd) if adamw_p else None
-        return HybridOptimizer(muon, adamw)
+                from .p2p import p2p_available
+                if p2p_available(self.device):
+                    return "p2p"
+            except Exception:
+                pass
+            if want == "p2p":
+                raise RuntimeError("p2p transport requested but symmetric memory is unavailable")
+        return "nccl" if backend == "nccl" else "gloo"
 
     # -------------------------------------------------------------------- step
     def set_sync(self, flag: bool) -> None:
-        self._sync = flag
+        pass
 
     def own_slice(self, flat: torch.Tensor) -> torch.Tensor:
         return flat[self.rank * self.seg: (self.rank + 1) * self.seg]
 
-    def _reduce_gradients(self) -> None:
-        if self.world == 1:
-            return
-        if self.use_p2p:
-            self.p2p.reduce_scatter_mean(self.rank, self.seg)
-            return
-        backend = dist.get_backend(self.group)
-        if backend == "nccl":
+    def reduce(self) -> None:
+        """Average gradients over the group into their owners' segments."""
+        self._sq_valid = False
+        if self.transport == "p2p":
+            self.p2p.barrier()
+            self._sq.zero_()
+            self.p2p.reduce_scatter_mean(self.rank * self.seg, self.seg, self._sq)
+            self._sq_valid = self.grad_scale == 1.0
+        elif self.transport == "nccl":
             dist.reduce_scatter_tensor(self.own_slice(self.flat_grad), self.flat_grad, op=dist.ReduceOp.AVG,
                                        group=self.group)
-        else:
+        elif self.transport == "gloo":
             dist.all_reduce(self.flat_grad, group=self.group)
             self.flat_grad.div_(self.world)
-
-    def _publish_parameters(self) -> None:
-        if self.world == 1:
-            return
-        if self.use_p2p:
-            self.p2p.all_gather_params(self.rank, self.seg)
-            return
-        dist.all_gather_into_tensor(self.flat_param, self.own_slice(self.flat_param).clone()
-                                    if dist.get_backend(self.group) != "nccl" else self.own_slice(self.flat_param),
-                                    group=self.group)
-
-    def reduce(self) -> None:
-        self._reduce_gradients()
         if self.grad_scale != 1.0:
             self.own_slice(self.flat_grad).mul_(self.grad_scale)
 
     def owned_sq_norm(self) -> torch.Tensor:
+        if getattr(self, "_sq_valid", False):
+            return self._sq[0]
         return self.own_slice(self.flat_grad).float().pow(2).sum()
 
     def scale_owned(self, coef: torch.Tensor) -> None:
-        g = self.own_slice(self.flat_grad)
-        g.mul_(coef.to(g.dtype))
+        """Apply the clip coefficient: the fused AdamW kernel reads it from the device; only
+        the gradients of the other optimizers are rescaled in memory."""
+        self._clip = coef.reshape(1).float().contiguous()
+        a0 = self.rank * self.seg
+        if self.fused is not None:
+            lo = a0 + self.fused.n
+        else:
+            lo = a0
+        hi = a0 + self.used[self.rank]
+        if hi > lo:
+            self.flat_grad[lo:hi].mul_(coef.to(self.flat_grad.dtype))
 
-    def finish(self, optimizer=None) -> None:
-        opt = optimizer if optimizer is not None else self.optimizer
-        if opt is not None:
-            opt.step()
-        self._publish_parameters()
+    def finish(self) -> None:
+        a0 = self.rank * self.seg
+        ptrs = self.p2p.param_ptrs if self.transport == "p2p" else [self.flat_param.data_ptr()]
+        prank = self.rank if self.transport == "p2p" else 0
+        if self.fused is not None:
+            self.fused.step(ptrs, prank, self._clip)
+        if self.adamw is not None:
+            self.adamw.step()
+        if self.muon is not None:
+            self.muon.step()
+        if self.transport == "p2p":
+            lo = a0 + (self.fused.n if self.fused is not None else 0)
+            hi = a0 + self.used[self.rank]
+            if hi > lo:
+                self.p2p.all_gather_range(lo, _round_up(hi - lo, 8))
+            self.p2p.barrier()
+        elif self.transport == "nccl":
+            dist.all_gather_into_tensor(self.flat_param, self.own_slice(self.flat_param), group=self.group)
+        elif self.transport == "gloo":
+            dist.all_gather_into_tensor(self.flat_param, self.own_slice(self.flat_param).clone(), group=self.group)
         self.flat_grad.zero_()
+        self._clip = None
 
     def reduce_clip_and_step(self, optimizer=None, max_norm: Optional[float] = 1.0) -> torch.Tensor:
         """Reduce gradients to their owners, clip by the global norm, update the owned
@@ -191,12 +275,45 @@ class ShardedDataParallel:
     def optimizer_state_dict(self) -> Dict:
         """State of this rank's shard plus the names it covers (for sharded checkpoints)."""
         return {"rank": self.rank, "world": self.world, "owned": self.owned_names(),
-                "state": self.optimizer.state_dict() if self.optimizer is not None else None}
+                "fused_adamw": self.fused.state_dict() if self.fused is not None else None,
+                "adamw": self.adamw.state_dict() if self.adamw is not None else None,
+                "muon": self.muon.state_dict() if self.muon is not None else None}
 
     def load_optimizer_state_dict(self, sd: Dict) -> None:
         assert sd["owned"] == self.owned_names(), "optimizer shard does not match this rank's ownership"
-        if self.optimizer is not None and sd["state"] is not None:
-            self.optimizer.load_state_dict(sd["state"])
+        if self.fused is not None and sd.get("fused_adamw") is not None:
+            self.fused.load_state_dict(sd["fused_adamw"])
+        if self.adamw is not None and sd.get("adamw") is not None:
+            self.adamw.load_state_dict(sd["adamw"])
+        if self.muon is not None and sd.get("muon") is not None:
+            self.muon.load_state_dict(sd["muon"])
+
+
+class _PoolOptimizer:
+    """Optimizer-shaped view of a pool (``param_groups`` for LR schedulers, state dicts)."""
+
+    def __init__(self, pool: ShardedDataParallel):
+        self.pool = pool
+
+    @property
+    def param_groups(self):
+        out = []
+        for o in (self.pool.muon, self.pool.adamw, self.pool.fused):
+            if o is not None:
+                out.extend(o.param_groups)
+        return out
+
+    def state_dict(self):
+        return self.pool.optimizer_state_dict()
+
+    def load_state_dict(self, sd):
+        self.pool.load_optimizer_state_dict(sd)
+
+    def zero_grad(self, set_to_none: bool = False):
+        self.pool.flat_grad.zero_()
+
+    def step(self):
+        raise RuntimeError("step through ShardedDataParallel.reduce_clip_and_step")
 
 
 class ParallelPlan:
@@ -208,28 +325,23 @@ class ParallelPlan:
         self.optimizer = pools[0].optimizer
 
     def set_sync(self, flag: bool) -> None:
-        for p in self.pools:
-            p.set_sync(flag)
+        pass
 
     def reduce_clip_and_step(self, optimizer=None, max_norm: Optional[float] = 1.0) -> torch.Tensor:
         for p in self.pools:
             p.reduce()
-        sq = sum(p.owned_sq_norm() for p in self.pools)
+        sq = sum(p.owned_sq_norm() for p in self.pools).reshape(1).clone()
         if dist.is_initialized() and dist.get_world_size(self.norm_group) > 1:
             dist.all_reduce(sq, group=self.norm_group)
-        total = sq.sqrt()
+        total = sq.sqrt()[0]
         if max_norm is not None and max_norm > 0:
             coef = (max_norm / (total + 1e-6)).clamp(max=1.0)
             for p in self.pools:
                 p.scale_owned(coef)
-        for i, p in enumerate(self.pools):
-            p.finish(optimizer if (optimizer is not None and i == 0 and len(self.pools) == 1) else None)
+        for p in self.pools:
+            p.finish()
         return total
 
     @property
     def param_groups(self):
-        out = []
-        for p in self.pools:
-            if p.optimizer is not None:
-                out.extend(p.optimizer.param_groups)
-        return out
+        return [g for p in self.pools for g in p.optimizer.param_groups]

@@ -1,0 +1,57 @@
+"""Multi-GPU checks (run only where at least 2 GPUs are visible): the peer-to-peer transport
+of the sharded data-parallel step against the NCCL transport, as child processes."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["KMOE_ROOT"])
+from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig, MoETransformer
+from kolmogorov_moe_architecture_b200.ops import cuda_ops
+from kolmogorov_moe_architecture_b200.parallel.zero import ShardedDataParallel
+from kolmogorov_moe_architecture_b200.training.engine import TrainEngine
+rank = int(os.environ["RANK"]); torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+cfg = AdvancedMoEConfig(vocab_size=512, d_model=128, n_layers=2, n_heads=2, n_kv_heads=1, head_dim=64, d_ff=256,
+                        d_ff_expert=128, n_experts=4, moe_layers=(1,), mamba_layers=(1,), max_seq_len=64,
+                        n_pred_tokens=2, aux_loss_weights=(1.0, 0.5), mamba_moe_mode="moe_ffn", dropout=0.0,
+                        attention_dropout=0.0, residual_dropout=0.0)
+out = {}
+for transport in ("nccl", "p2p"):
+    torch.manual_seed(0)
+    model = MoETransformer(cfg, verbose=False).cuda().to(torch.bfloat16)
+    dp = ShardedDataParallel(model, optimizer_kind="muon", lr=2e-3, adamw_lr=2e-3, transport=transport)
+    eng = TrainEngine(model, dp.optimizer, grad_clip=1.0, dp=dp)
+    g = torch.Generator().manual_seed(5 + rank)
+    for s in range(3):
+        eng.step(torch.randint(0, 512, (2, 64), generator=g).cuda())
+    cuda_ops.check_status()
+    out[transport] = torch.cat([p.detach().float().flatten() for p in model.parameters()])
+err = (out["nccl"] - out["p2p"]).abs().max().item()
+ref = out["nccl"].abs().max().item()
+# replicas must agree bit for bit after the all-gather
+mine = out["p2p"].clone(); other = mine.clone(); dist.broadcast(other, 0)
+assert torch.equal(mine, other), "ranks diverged"
+assert err < 2e-2 * ref, (err, ref)
+if rank == 0: print("MULTI_OK", err)
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_p2p_transport_matches_nccl_2gpus(tmp_path):
+    f = tmp_path / "worker.py"
+    f.write_text(WORKER)
+    env = dict(os.environ, KMOE_ROOT=ROOT, NCCL_NVLS_ENABLE="0", KMOE_STRICT="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29581", str(f)],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "MULTI_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
