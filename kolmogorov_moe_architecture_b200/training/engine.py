@@ -78,6 +78,28 @@ class TrainEngine:
         loss.backward()
         return out
 
+    def _forward_backward_scaled(self, ids, labels, attention_mask, accum: int):
+        """One micro-batch whose loss is divided by ``accum`` (for callers that drive the
+        accumulation themselves, like ``Trainer``)."""
+        self.model.train()
+        saved, self.grad_accum = self.grad_accum, accum
+        try:
+            am = None if attention_mask is None else self._to_device(attention_mask)
+            return self._forward_backward(ids, labels, am)
+        finally:
+            self.grad_accum = saved
+
+    def apply_update(self):
+        """Clip, step the optimizer (through the data-parallel plan when attached) and clear gradients."""
+        if self.dp is not None:
+            return self.dp.reduce_clip_and_step(self.optimizer, self.grad_clip)
+        gnorm = None
+        if self.grad_clip:
+            gnorm = clip_grad_norm_device(list(self.model.parameters()), self.grad_clip)
+        self.optimizer.step()
+        self.optimizer.zero_grad(set_to_none=True)
+        return gnorm
+
     def step(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None,
              attention_mask: Optional[torch.Tensor] = None) -> StepStats:
         """``input_ids``: (grad_accum * micro_batch, S) or (micro_batch, S)."""
@@ -97,19 +119,13 @@ class TrainEngine:
             ld, lm = out["loss"].detach(), out["lm_loss"].detach()
             loss_acc = ld if loss_acc is None else loss_acc + ld
             lm_acc = lm if lm_acc is None else lm_acc + lm
-        gnorm = None
-        if self.dp is not None:
-            gnorm = self.dp.reduce_clip_and_step(self.optimizer, self.grad_clip)
-        else:
-            if self.grad_clip:
-                gnorm = clip_grad_norm_device(list(self.model.parameters()), self.grad_clip)
-            self.optimizer.step()
-            self.optimizer.zero_grad(set_to_none=True)
+        gnorm = self.apply_update()
         if self.lr_scheduler is not None:
             self.lr_scheduler.step()
         self.global_step += 1
         ntok = ids.numel()
         self.tokens_seen += ntok
         n = len(chunks)
-        return StepStats(loss_acc / n, lm_acc / n, out["aux_loss"], gnorm, ntok,
+        aux = out["aux_loss"].detach() if torch.is_tensor(out["aux_loss"]) else out["aux_loss"]
+        return StepStats(loss_acc / n, lm_acc / n, aux, gnorm, ntok,
                          out.get("multitoken_loss_dict"))

@@ -1,0 +1,365 @@
+"""The training loop shared by the command-line entrypoints.
+
+Each entrypoint (``train.py``, ``train_distributed.py``, ``train_custom.py``, ``scripts/train.py``)
+parses its own flags - kept from the reference's scripts - into a :class:`RunSpec` and calls
+:func:`run_training`.  What a spec selects:
+
+* weight regime: ``bf16`` weights (train.py:508-509) or fp32 master weights with bf16 autocast
+  (scripts/train.py); fp16 weights are accepted for parity.
+* optimizer family: ``combined`` (Muon on ndim >= 2 + AdamW groups, train.py:566-705), ``hybrid``
+  (name-based Muon + AdamW, muon_optimizer.py:468-616), ``muon8bit_all`` (train_custom.py:1035-1049),
+  ``adamw`` (decay / no-decay groups).
+* parallelism: one process, or torchrun with the sharded data-parallel plan (+ expert parallelism
+  when the model config says ``moe_implementation: expert_parallel``).
+* checkpoint format B (single file) or C (directory, newest three kept), sharded when distributed.
+* data: synthetic ids, streaming text, packed documents with cross-document label masking.
+
+Unlike the reference's distributed script the loop seeds every rank, clips with the global norm
+across shards, does not shift labels twice, and can resume.
+"""
+from __future__ import annotations
+
+import math
+import os
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, Optional
+
+import torch
+
+from ..config import AdvancedMoEConfig
+from ..data import (DolmaStreamingDataset, PackedDocumentDataset, PinnedPrefetcher, SyntheticTokenDataset,
+                    TokenizerWrapper, document_attention_mask)
+from ..models.transformer import MoETransformer
+from ..parallel import mesh as pmesh
+from ..utils.config_io import load_yaml, model_config_strict, model_config_tolerant, section
+from ..utils.fault import InterruptGuard, StepWatchdog, check_router_collapse
+from ..utils.logging import MetricLogger
+from ..utils.profiling import PhaseTimer
+from . import checkpoint as ckpt
+from .engine import TrainEngine
+from .lr_schedule import CosineScheduleWithWarmup
+from .muon_optimizer import CombinedOptimizer, Muon8bit, get_muon_optimizer
+from .optim_factory import make_adamw
+
+
+@dataclass
+class RunSpec:
+    config_path: str
+    steps: Optional[int] = None
+    batch_size: Optional[int] = None
+    seq_len: Optional[int] = None
+    grad_accum: Optional[int] = None
+    strict_config: bool = False
+    weights: str = "bf16"                  # bf16 | fp16 | fp32_autocast
+    optimizer_family: str = "auto"         # auto | combined | hybrid | muon8bit_all | adamw
+    checkpoint_format: str = "B"           # B | C
+    checkpoint_dir: Optional[str] = None
+    save_interval: Optional[int] = None
+    resume: Optional[str] = None
+    data_mode: str = "auto"                # auto | synthetic | streaming | packed
+    document_mask: bool = False
+    grad_checkpoint: bool = False
+    compile: bool = False
+    wandb: bool = False
+    wandb_project: str = "Kolmogorov-Testing"
+    wandb_run: Optional[str] = None
+    lr_scale: float = 1.0
+    gpu: Optional[int] = None
+    balanced_routing: bool = False
+    collapse_check_interval: int = 0
+    collapse_entropy_threshold: float = 0.7
+    reallocate: bool = False
+    entropy_threshold: float = 0.85
+    constant_lr: bool = False              # train.py trains at a fixed LR (no scheduler)
+    profile: bool = False
+    debug: bool = False
+    debug_interval: int = 100
+    use_lr_schedule: bool = True
+    step_deadline_s: float = 0.0           # > 0 arms the step watchdog
+    transport: Optional[str] = None
+    jsonl: Optional[str] = None
+    extra: Dict[str, Any] = field(default_factory=dict)
+
+
+def _build_optimizer(spec: RunSpec, model, opt_cfg, train_cfg):
+    fam = spec.optimizer_family
+    kind = opt_cfg.get("type", "adamw")
+    if fam == "auto":
+        fam = "combined" if kind == "muon" else "adamw"
+    s = spec.lr_scale
+    wd = opt_cfg.get("weight_decay", train_cfg.get("weight_decay", 0.01))
+    if fam == "combined":
+        adamw_lr = opt_cfg.get("adamw_lr", 3e-4) * s
+        norm_lr = opt_cfg.get("norm_lr")
+        return CombinedOptimizer(model, muon_lr=opt_cfg.get("muon_lr", 0.02) * s, adamw_lr=adamw_lr,
+                                 momentum=opt_cfg.get("momentum", 0.95), weight_decay=wd,
+                                 nesterov=opt_cfg.get("nesterov", True), backend=opt_cfg.get("backend", "newton"),
+                                 newton_iters=opt_cfg.get("newton_iters", 5),
+                                 norm_lr=(norm_lr * s) if norm_lr is not None else None,
+                                 betas=tuple(opt_cfg.get("adamw_betas", (0.9, 0.95))))
+    if fam == "hybrid":
+        return get_muon_optimizer(model, lr=train_cfg.get("max_lr", 1e-3) * s, momentum=opt_cfg.get("momentum", 0.95),
+                                  weight_decay=wd)
+    if fam == "muon8bit_all":
+        return Muon8bit(model.parameters(), lr=train_cfg.get("max_lr", 1e-3) * s, momentum=opt_cfg.get("momentum", 0.95),
+                        weight_decay=wd)
+    decay, no_decay = [], []
+    for n, p in model.named_parameters():
+        if p.requires_grad:
+            (no_decay if (p.dim() < 2 or "norm" in n or "bias" in n) else decay).append(p)
+    lr = train_cfg.get("max_lr", opt_cfg.get("adamw_lr", 3e-4)) * s
+    on_cuda = next(model.parameters()).is_cuda
+    return torch.optim.AdamW([{"params": decay, "weight_decay": wd}, {"params": no_decay, "weight_decay": 0.0}],
+                             lr=lr, betas=tuple(opt_cfg.get("adamw_betas", (0.9, 0.95))), fused=on_cuda)
+
+
+def _documents(tokenizer, max_examples):
+    from ..data.dolma_dataset import _open_first_available
+    ds = _open_first_available("train", True)
+    if ds is None:
+        return None
+
+    def gen():
+        for i, ex in enumerate(ds):
+            if max_examples and i >= max_examples:
+                return
+            t = ex.get("text", "")
+            if t:
+                enc = tokenizer.encode(t, truncation=False)
+                yield enc["input_ids"] if isinstance(enc, dict) else enc
+    return gen()
+
+
+def _make_loader(spec, cfg, data_cfg, batch, rank, world):
+    from torch.utils.data import DataLoader
+    mode = spec.data_mode
+    tok = None
+    if mode in ("auto", "streaming", "packed"):
+        tok = TokenizerWrapper(data_cfg.get("tokenizer_name", "gpt2"), vocab_size=None, verbose=(rank == 0))
+    if mode == "packed" or (mode == "auto" and spec.checkpoint_format == "C"):
+        docs = _documents(tok, data_cfg.get("max_examples"))
+        if docs is not None:
+            ds = PackedDocumentDataset(docs, cfg.max_seq_len, tok.eos_token_id, cfg.n_pred_tokens)
+            return DataLoader(ds, batch_size=batch), "packed"
+    if mode in ("auto", "streaming"):
+        ds = DolmaStreamingDataset(tok, cfg.max_seq_len, cfg.n_pred_tokens, "train", True, cfg.vocab_size,
+                                   rank=rank, world_size=world)
+        if ds.dataset is not None:
+            return DataLoader(ds, batch_size=batch), "streaming"
+    ds = SyntheticTokenDataset(cfg.vocab_size, cfg.max_seq_len, seed=1234, rank=rank, low=1)
+    return DataLoader(ds, batch_size=batch), "synthetic"
+
+
+def run_training(spec: RunSpec) -> Dict[str, Any]:
+    mesh = pmesh.init_distributed(ep_size=1) if int(os.environ.get("WORLD_SIZE", "1")) > 1 else pmesh.Mesh(
+        1, 0, spec.gpu or 0, 1, 1)
+    rank, world = mesh.rank, mesh.world
+    is_main = rank == 0
+    use_cuda = torch.cuda.is_available()
+    device = torch.device("cuda", mesh.local_rank if world > 1 else (spec.gpu or 0)) if use_cuda else torch.device("cpu")
+    if use_cuda:
+        torch.cuda.set_device(device)
+    y = load_yaml(spec.config_path)
+    train_cfg, opt_cfg, data_cfg = section(y, "training"), section(y, "optimizer"), section(y, "data")
+    over = {}
+    if spec.balanced_routing:
+        over["moe_balanced_routing"] = True
+    cfg: AdvancedMoEConfig = (model_config_strict(y, **over) if spec.strict_config
+                              else model_config_tolerant(y, seq_len=spec.seq_len, **over))
+    if spec.seq_len and spec.strict_config:
+        cfg.max_seq_len = spec.seq_len
+    if cfg.moe_implementation == "expert_parallel" and world > 1 and cfg.ep_size == 1:
+        cfg.ep_size = math.gcd(world, cfg.n_experts)
+    if cfg.ep_size > 1 and world > 1:
+        mesh = pmesh.make_mesh(cfg.ep_size)
+    torch.manual_seed(1234)                                    # identical initial weights on every rank
+    model = MoETransformer(cfg, verbose=is_main)
+    if cfg.ep_size > 1 and mesh.ep_group is not None:
+        for m in model.modules():
+            if hasattr(m, "expert_parallel_layer") and m.expert_parallel_layer is not None:
+                m.expert_parallel_layer.process_group = mesh.ep_group
+    wdtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32_autocast": torch.float32}[spec.weights]
+    model = model.to(device).to(wdtype)
+    if spec.grad_checkpoint:
+        model.gradient_checkpointing_enable()
+    start_step, tokens_seen, losses = 0, 0, []
+    resume = spec.resume or train_cfg.get("resume_from")
+    if resume and not os.path.isdir(resume):
+        _, ck = ckpt.load_model_state(model, resume, map_location=device)
+        start_step = ck.get("step", ck.get("global_step", 0)) if isinstance(ck, dict) else 0
+        tokens_seen = ck.get("total_tokens", ck.get("tokens_seen", 0)) if isinstance(ck, dict) else 0
+    if spec.reallocate:
+        from tools.reallocate_experts import reallocate_model_experts
+        reallocate_model_experts(model, entropy_threshold=spec.entropy_threshold, verbose=is_main)
+
+    dp = None
+    if world > 1:
+        from ..parallel.zero import ParallelPlan, ShardedDataParallel
+        okind = "muon" if opt_cfg.get("type", "adamw") == "muon" else "adamw"
+        pools = [ShardedDataParallel(model, optimizer_kind=okind, lr=opt_cfg.get("muon_lr", 1e-3) * spec.lr_scale,
+                                     adamw_lr=opt_cfg.get("adamw_lr", 3e-4) * spec.lr_scale,
+                                     momentum=opt_cfg.get("momentum", 0.95),
+                                     weight_decay=opt_cfg.get("weight_decay", 0.01),
+                                     newton_iters=opt_cfg.get("newton_iters", 5), transport=spec.transport)]
+        if cfg.ep_size > 1 and any(getattr(p, "_kmoe_expert_parallel", False) for p in model.parameters()):
+            pools.append(ShardedDataParallel(model, optimizer_kind="adamw", group=mesh.expert_dp_group,
+                                             adamw_lr=opt_cfg.get("adamw_lr", 3e-4) * spec.lr_scale,
+                                             weight_decay=opt_cfg.get("weight_decay", 0.01), expert_params=True,
+                                             grad_scale=1.0 / cfg.ep_size, broadcast_from_rank0=False,
+                                             transport="nccl" if use_cuda else "gloo"))
+        dp = ParallelPlan(pools)
+        optimizer = dp
+    else:
+        optimizer = _build_optimizer(spec, model, opt_cfg, train_cfg)
+        if resume and not os.path.isdir(resume) and isinstance(ck, dict) and ck.get("optimizer_state_dict") is not None:
+            try:
+                optimizer.load_state_dict(ck["optimizer_state_dict"])
+            except Exception as e:
+                if is_main:
+                    print(f"optimizer state not restored: {e}")
+
+    batch = spec.batch_size or train_cfg["batch_size"]
+    accum = spec.grad_accum or train_cfg["gradient_accumulation_steps"]
+    tokens_per_step = batch * cfg.max_seq_len * world * accum
+    total_steps = spec.steps or max(1, train_cfg["total_tokens"] // tokens_per_step)
+    sched = None
+    if spec.use_lr_schedule and not spec.constant_lr:
+        max_lr = train_cfg["max_lr"] * spec.lr_scale
+        sched = CosineScheduleWithWarmup(optimizer, min(train_cfg["warmup_steps"], max(total_steps - 1, 1)),
+                                         total_steps, max_lr, max_lr * train_cfg["min_lr_ratio"],
+                                         preserve_ratios=True)
+        sched.current_step = start_step
+    amp = torch.bfloat16 if (spec.weights == "fp32_autocast" and use_cuda) else None
+    engine = TrainEngine(model, optimizer, sched, train_cfg["gradient_clip_norm"], accum, amp, dp, device)
+    engine.global_step, engine.tokens_seen = start_step, tokens_seen
+    if resume and os.path.isdir(resume):
+        st = (ckpt.load_sharded(resume, model, dp.pools[0], rank, device) if dp is not None
+              else ckpt.load_format_c(resume, model, optimizer, device))
+        engine.global_step = start_step = st.get("step", 0)
+        engine.tokens_seen = st.get("tokens_seen", 0)
+
+    loader, data_kind = _make_loader(spec, cfg, data_cfg, batch * accum, rank, world)
+    it = iter(PinnedPrefetcher(loader, depth=4, pin=use_cuda))
+    cdir = spec.checkpoint_dir or train_cfg["checkpoint_dir"]
+    if spec.checkpoint_format == "B":
+        cdir = os.path.join(cdir, os.path.splitext(os.path.basename(spec.config_path))[0])
+    save_every = spec.save_interval if spec.save_interval is not None else train_cfg["save_interval"]
+    logger = MetricLogger(spec.jsonl, spec.wandb, spec.wandb_project, spec.wandb_run, y, rank=rank)
+    timer = PhaseTimer(enabled=spec.profile, device=device)
+    dog = StepWatchdog(spec.step_deadline_s, lambda idle: print(f"[watchdog] no step for {idle:.0f}s on rank {rank}",
+                                                                flush=True)).start() if spec.step_deadline_s > 0 else None
+    if is_main:
+        print(f"training: {total_steps} steps, {tokens_per_step:,} tokens/step, data={data_kind}, world={world}, "
+              f"ep={cfg.ep_size}, weights={spec.weights}")
+
+    def save(step: int, suffix: Optional[str] = None):
+        state = {"step": step, "tokens_seen": engine.tokens_seen, "config_path": spec.config_path}
+        if dp is not None:
+            ckpt.save_sharded(cdir, step, model, dp.pools[0], state, rank)
+        elif spec.checkpoint_format == "C":
+            ckpt.save_format_c(cdir, step, model, optimizer, state)
+        else:
+            ckpt.save_format_b(os.path.join(cdir, ckpt.format_b_name(step, suffix)), model, optimizer, step, 0, 0,
+                               losses, engine.tokens_seen, spec.config_path)
+
+    log_every = train_cfg["log_interval"]
+    t_last, tok_last = time.time(), engine.tokens_seen
+    last_stats = None
+    with InterruptGuard() as guard:
+        step = start_step
+        while step < total_steps:
+            with timer.phase("data"):
+                b = next(it)
+            am = None
+            if spec.document_mask and "doc_ids" in b:
+                am = document_attention_mask(b["doc_ids"].to(device))
+            with timer.phase("step"):
+                if am is not None:
+                    last_stats = _step_with_mask(engine, b, am)
+                else:
+                    last_stats = engine.step(b["input_ids"], b.get("labels"))
+            step += 1
+            if dog is not None:
+                dog.beat()
+            if step % log_every == 0 or step == total_steps:
+                lv = last_stats.loss_value()
+                losses.append(lv)
+                now = time.time()
+                tps = (engine.tokens_seen - tok_last) * world / max(now - t_last, 1e-9)
+                t_last, tok_last = now, engine.tokens_seen
+                rec = {"loss": lv, "lm_loss": float(last_stats.lm_loss), "lr": optimizer.param_groups[0]["lr"],
+                       "aux_loss": float(last_stats.aux_loss) if torch.is_tensor(last_stats.aux_loss) else 0.0,
+                       "grad_norm": float(last_stats.grad_norm) if last_stats.grad_norm is not None else None,
+                       "tokens_seen": engine.tokens_seen * world, "tokens_per_sec": tps}
+                if use_cuda:
+                    rec["mem_allocated_gb"] = torch.cuda.memory_allocated() / 2**30
+                    rec["mem_reserved_gb"] = torch.cuda.memory_reserved() / 2**30
+                for k, v in (last_stats.per_head or {}).items():
+                    rec[f"mt_{k}"] = float(v)
+                if spec.profile:
+                    rec.update({f"time_{k}_ms": v for k, v in timer.summary(reduce_max=world > 1).items()})
+                    timer.reset()
+                logger.log(rec, step=step)
+                if is_main:
+                    print(f"Step {step}/{total_steps} | Loss: {lv:.4f} | LR: {rec['lr']:.2e} | Tok/s: {tps:,.0f}", flush=True)
+            if spec.collapse_check_interval and step % spec.collapse_check_interval == 0:
+                stats, collapsed, summary = check_router_collapse(model, entropy_threshold=spec.collapse_entropy_threshold)
+                if stats:
+                    logger.log({"router/avg_entropy": sum(s["entropy"] for s in stats.values()) / len(stats),
+                                "router/max_usage": max(s["max_usage"] for s in stats.values()),
+                                "router/collapsed_layers": len(collapsed)}, step=step)
+                if is_main and collapsed:
+                    print(f"  [router] {summary}")
+            if save_every and step % save_every == 0 and step < total_steps:
+                save(step)
+            if guard.requested:
+                if is_main:
+                    print(f"signal {guard.signum}: saving checkpoint at step {step} and stopping")
+                save(step, "interrupted")
+                break
+        else:
+            save(step, "final")
+    if dog is not None:
+        dog.stop()
+    logger.close()
+    if use_cuda:
+        from ..ops import cuda_ops
+        cuda_ops.check_status()
+    out = {"steps": step, "final_loss": losses[-1] if losses else None, "tokens_seen": engine.tokens_seen * world,
+           "checkpoint_dir": cdir}
+    if world > 1:
+        pmesh.destroy()
+    return out
+
+
+def _step_with_mask(engine: TrainEngine, b, am):
+    """A step with an explicit additive attention mask (document-masked packing)."""
+    engine.model.train()
+    ids = engine._to_device(b["input_ids"])
+    lab = engine._to_device(b.get("labels", b["input_ids"]))
+    out = _forward_masked(engine.model, ids, lab, am)
+    out["loss"].backward()
+    g = engine.apply_update()
+    if engine.lr_scheduler is not None:
+        engine.lr_scheduler.step()
+    engine.global_step += 1
+    engine.tokens_seen += ids.numel()
+    from .engine import StepStats
+    return StepStats(out["loss"].detach(), out["lm_loss"].detach(), out["aux_loss"], g, ids.numel(),
+                     out.get("multitoken_loss_dict"))
+
+
+def _forward_masked(model, ids, labels, add_mask):
+    """Forward with a (B,1,S,S) additive mask passed straight to the attention layers."""
+    h = model.token_embedding(ids)
+    aux = 0.0
+    add_mask = add_mask.to(h.dtype).clamp(min=torch.finfo(h.dtype).min)
+    for layer in model.layers:
+        h = layer(h, attention_mask=add_mask, position_ids=None)
+        if model.training:
+            aux = aux + layer.aux_loss
+    h = model.final_norm(h)
+    lm, info = model.multitoken_loss.from_hidden(h, [hd.weight for hd in model.lm_heads], labels)
+    loss = lm + aux if (model.training and torch.is_tensor(aux)) else lm
+    return {"loss": loss, "lm_loss": lm, "aux_loss": aux, "multitoken_loss_dict": info}

@@ -1,0 +1,88 @@
+"""HuggingFace-Trainer entrypoint (counterpart of the reference's ``train_production.py``).
+
+    python train_production.py --config configs/training_500m_hf.yaml [--max_steps N] [--synthetic]
+
+The model is wrapped by ``MoEModelWrapper``; HF owns the loop, logging and ``checkpoint-N/``
+directories (``save_total_limit=3``); the optimizer is the hybrid Muon/AdamW or AdamW and the
+schedule the cosine-with-warm-up of this library.  ``mixed_precision.fp8: true`` selects the
+block-scaled fp8 expert GEMMs (``moe_dtype: mxfp8``) instead of the reference's torchao swap.
+"""
+import argparse
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", type=str, required=True)
+    ap.add_argument("--resume_from_checkpoint", type=str, default=None)
+    ap.add_argument("--max_steps", type=int, default=None)
+    ap.add_argument("--synthetic", action="store_true")
+    ap.add_argument("--output_dir", type=str, default=None)
+    a = ap.parse_args(argv)
+    import importlib.util
+    if importlib.util.find_spec("accelerate") is None:
+        # HF Trainer cannot be constructed without `accelerate`; run the same recipe (hybrid optimizer,
+        # cosine schedule with warm-up, checkpoint-N directories with the newest three kept) on the native loop.
+        print("accelerate is not installed: running the HF recipe on the native training loop")
+        from kolmogorov_moe_architecture_b200.training.runner import RunSpec, run_training
+        return run_training(RunSpec(config_path=a.config, steps=a.max_steps, strict_config=True,
+                                    weights="fp32_autocast", optimizer_family="hybrid", checkpoint_format="C",
+                                    checkpoint_dir=a.output_dir, resume=a.resume_from_checkpoint,
+                                    data_mode="synthetic" if a.synthetic else "streaming"))
+    import torch
+    from torch.utils.data import Dataset
+    from transformers import TrainingArguments
+    from kolmogorov_moe_architecture_b200 import MoETransformer
+    from kolmogorov_moe_architecture_b200.training.hf import MoEModelWrapper, make_hf_classes
+    from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml, model_config_strict, section
+    y = load_yaml(a.config)
+    tc, oc, dc = section(y, "training"), section(y, "optimizer"), section(y, "data")
+    mp = y.get("mixed_precision") or {}
+    over = {"moe_dtype": "mxfp8"} if mp.get("fp8") else {}
+    cfg = model_config_strict(y, **over)
+    model = MoEModelWrapper(MoETransformer(cfg))
+    MoETrainer, TrueLoss = make_hf_classes()
+
+    class Rows(Dataset):
+        def __init__(self, n, seed):
+            g = torch.Generator().manual_seed(seed)
+            self.x = torch.randint(1, cfg.vocab_size, (n, cfg.max_seq_len), generator=g)
+
+        def __len__(self):
+            return self.x.shape[0]
+
+        def __getitem__(self, i):
+            return {"input_ids": self.x[i], "labels": self.x[i]}
+
+    if a.synthetic:
+        train_ds, eval_ds = Rows(256, 0), Rows(16, 1)
+    else:
+        from kolmogorov_moe_architecture_b200.data import DolmaStreamingDataset, TokenizerWrapper
+        tok = TokenizerWrapper(dc.get("tokenizer_name", "gpt2"))
+        train_ds = DolmaStreamingDataset(tok, cfg.max_seq_len, cfg.n_pred_tokens, "train", True, cfg.vocab_size)
+        eval_ds = None
+    steps = a.max_steps or max(1, tc["total_tokens"] // (tc["batch_size"] * cfg.max_seq_len *
+                                                          tc["gradient_accumulation_steps"]))
+    cuda = torch.cuda.is_available()
+    args = TrainingArguments(
+        output_dir=a.output_dir or tc["checkpoint_dir"], max_steps=steps,
+        per_device_train_batch_size=tc["batch_size"], gradient_accumulation_steps=tc["gradient_accumulation_steps"],
+        learning_rate=tc["max_lr"], warmup_steps=min(tc["warmup_steps"], max(steps - 1, 0)),
+        max_grad_norm=tc["gradient_clip_norm"], logging_steps=tc["log_interval"], save_steps=tc["save_interval"],
+        save_total_limit=3, bf16=bool(mp.get("bf16", cuda)) and cuda, report_to=[], remove_unused_columns=False,
+        dataloader_num_workers=0, use_cpu=not cuda)
+    trainer = MoETrainer(oc, tc, tc["log_interval"], model=model, args=args, train_dataset=train_ds,
+                         eval_dataset=eval_ds, callbacks=[TrueLoss(tc["gradient_accumulation_steps"])])
+    try:
+        trainer.train(resume_from_checkpoint=a.resume_from_checkpoint)
+    except KeyboardInterrupt:
+        print("interrupted: the newest checkpoint-N directory holds the last saved state")
+    return trainer
+
+
+if __name__ == "__main__":
+    main()
