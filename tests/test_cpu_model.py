@@ -1,0 +1,153 @@
+"""CPU tests of the model, losses, routing rules, generation and gradient flow."""
+import math
+
+import pytest
+import torch
+
+import kolmogorov_moe_architecture_b200 as kmoe
+from kolmogorov_moe_architecture_b200 import ops
+from kolmogorov_moe_architecture_b200.ops import eager
+
+
+def _tiny(**kw):
+    base = dict(vocab_size=200, d_model=64, n_layers=4, n_heads=4, n_kv_heads=2, head_dim=16, d_ff=128,
+                d_ff_expert=64, n_experts=4, moe_layers=(1, 2), mamba_layers=(1,), max_seq_len=32, n_pred_tokens=2,
+                aux_loss_weights=(1.0, 0.5), dropout=0.0, attention_dropout=0.0, residual_dropout=0.0,
+                device="cpu", dtype="float32")
+    base.update(kw)
+    return kmoe.AdvancedMoEConfig(**base)
+
+
+@pytest.mark.parametrize("mode", ["routing_mamba", "moe_ffn"])
+def test_forward_shapes_loss_composition_and_eval_aux(mode):
+    cfg = _tiny(mamba_moe_mode=mode)
+    m = kmoe.MoETransformer(cfg, verbose=False)
+    ids = torch.randint(0, 200, (2, 32))
+    m.train()
+    out = m(ids, labels=ids)
+    assert out["logits"].shape == (2, 32, 200) and len(out["logits_list"]) == 2
+    assert torch.allclose(out["loss"], out["lm_loss"] + out["aux_loss"])
+    out2 = m(ids, labels=ids, return_logits=False)
+    assert torch.allclose(out2["lm_loss"], out["lm_loss"], atol=1e-5)
+    m.eval()
+    ev = m(ids, labels=ids)
+    assert ev["aux_loss"] == 0.0 and torch.allclose(ev["loss"], ev["lm_loss"])
+    kinds = [(l.mixer_kind, l.ffn_kind) for l in m.layers]
+    assert kinds[1] == (("routing_mamba", "dense") if mode == "routing_mamba" else ("mamba", "moe"))
+
+
+@pytest.mark.parametrize("mod", [True, False])
+def test_every_parameter_gets_a_gradient(mod):
+    m = kmoe.MoETransformer(_tiny(mod_enabled=mod, mamba_moe_mode="moe_ffn"), verbose=False)
+    m.train()
+    ids = torch.randint(0, 200, (2, 32))
+    m(ids, labels=ids, return_logits=False)["loss"].backward()
+    missing = [n for n, p in m.named_parameters() if p.grad is None or not torch.isfinite(p.grad).all()]
+    assert not missing, missing
+    zero = [n for n, p in m.named_parameters() if p.grad.abs().sum() == 0]
+    assert not zero, zero
+
+
+def test_state_dict_schema():
+    m = kmoe.MoETransformer(_tiny(), verbose=False)
+    keys = set(m.state_dict())
+    for k in ["token_embedding.embedding.weight", "layers.0.seq_layer.q_proj.weight", "layers.0.ffn.w1.weight",
+              "layers.0.ffn_mod_router.router.weight", "layers.0.ffn_mod_router.aux_router.2.weight",
+              "layers.1.seq_layer.experts.0.mamba.mamba.in_proj.weight", "layers.1.seq_layer.router.0.weight",
+              "layers.2.ffn.router.router.0.weight", "layers.2.ffn.grouped_experts.w3", "final_norm.weight",
+              "lm_heads.0.weight", "lm_heads.1.weight"]:
+        assert k in keys, k
+    assert m.lm_heads[0].weight is m.token_embedding.embedding.weight
+    assert m.state_dict()["layers.2.ffn.grouped_experts.w1"].shape == (4, 64, 64)
+    assert not any("cos_cached" in k or "inv_freq" in k for k in keys)
+
+
+def test_generate_length_and_sampling_filters():
+    m = kmoe.MoETransformer(_tiny(), verbose=False).eval()
+    ids = torch.randint(0, 200, (2, 5))
+    out = m.generate(ids, max_new_tokens=4, temperature=0.8, top_k=10, top_p=0.9)
+    assert out.shape == (2, 9) and torch.equal(out[:, :5], ids)
+
+
+def test_mod_router_rule():
+    from kolmogorov_moe_architecture_b200.models.mod import MoDRouter
+    r = MoDRouter(_tiny(mod_capacity_factor=0.75)).train()
+    x = torch.randn(3, 16, 64)
+    idx, w, logits, topk = r(x)
+    assert idx.shape == (3, 12) and torch.all(idx[:, 1:] > idx[:, :-1])
+    assert torch.allclose(w.sum(-1), torch.ones(3), atol=1e-5)
+    assert torch.allclose(w, torch.softmax(torch.gather(logits, 1, idx), -1), atol=1e-6)
+    assert r.aux_loss > 0
+    assert r.num_selected(1) == 1
+
+
+def test_router_weights_and_balanced_capacity():
+    from kolmogorov_moe_architecture_b200.models.moe import Router
+    r = Router(_tiny())
+    w, idx, logits = r(torch.randn(2, 16, 64))
+    assert torch.allclose(w.sum(-1), torch.ones(2, 16), atol=1e-5) and idx.shape == (2, 16, 2)
+    rb = Router(_tiny(moe_balanced_routing=True))
+    wb, ib, _ = rb(torch.randn(4, 32, 64))
+    assert torch.all(ib[..., 0] != ib[..., 1])
+    counts = torch.bincount(ib.reshape(-1), minlength=4)
+    assert counts.max() <= 2 * (4 * 32 * 2 // 4)
+
+
+def test_capacity_drop_policy():
+    idx = torch.tensor([[0, 1], [0, 1], [0, 2], [0, 1]])
+    keep = eager.capacity_keep_mask(idx, 4, 2)
+    assert keep.tolist() == [[True, True], [True, True], [False, True], [False, False]]
+    x, w = torch.randn(4, 8), torch.full((4, 2), 0.5)
+    w1, w2, w3 = torch.randn(4, 8, 6), torch.randn(4, 8, 6), torch.randn(4, 6, 8)
+    out = eager.grouped_swiglu(x, w1, w2, w3, idx, w, keep)
+    assert out[3].abs().sum() == 0
+
+
+def test_expert_choice_capacity():
+    from kolmogorov_moe_architecture_b200.models.moe import ExpertChoiceRouter
+    r = ExpertChoiceRouter(_tiny(moe_capacity_factor=1.25))
+    w, tok, _, cap = r(torch.randn(2, 16, 64))
+    assert cap == math.ceil(16 * 1.25 / 4) and tok.shape == (2, 4, cap)
+    assert torch.allclose(w.sum(-1), torch.ones(2, 4), atol=1e-4)
+
+
+def test_selective_scan_matches_closed_form_for_constant_inputs():
+    B, S, C, N = 1, 6, 2, 16
+    u, dt = torch.ones(B, S, C), torch.full((B, S, C), 0.5)
+    A = -torch.ones(C, N)
+    Bm, Cm = torch.ones(B, S, N), torch.ones(B, S, N)
+    y = eager.selective_scan(u, dt, A, Bm, Cm, None, None, None, delta_softplus=False)
+    a, h, ref = math.exp(-0.5), 0.0, []
+    for _ in range(S):
+        h = a * h + 0.5
+        ref.append(N * h)
+    assert torch.allclose(y[0, :, 0], torch.tensor(ref), atol=1e-5)
+
+
+def test_causal_conv_is_causal():
+    x = torch.randn(1, 10, 4)
+    w, b = torch.randn(4, 4), torch.randn(4)
+    y1 = eager.causal_conv1d(x, w, b, True)
+    x2 = x.clone(); x2[:, 7:] += 1.0
+    y2 = eager.causal_conv1d(x2, w, b, True)
+    assert torch.allclose(y1[:, :7], y2[:, :7])
+
+
+def test_attention_gqa_equals_expanded_heads():
+    q, k, v = torch.randn(2, 9, 4, 8), torch.randn(2, 9, 2, 8), torch.randn(2, 9, 2, 8)
+    a = eager.attention(q, k, v)
+    b = eager.attention(q, k.repeat_interleave(2, 2), v.repeat_interleave(2, 2))
+    assert torch.allclose(a, b, atol=1e-6)
+
+
+def test_count_parameters_and_presets():
+    m = kmoe.MoETransformer(_tiny(mamba_moe_mode="moe_ffn"), verbose=False)
+    c = m.count_parameters()
+    assert c["total"] == sum(p.numel() for p in m.parameters()) and 0 < c["active"] < c["total"]
+    assert kmoe.get_3b_config().n_experts == 64 and kmoe.get_test_config().n_layers == 4
+    b = kmoe.get_bench_5b_config()
+    assert len(b.moe_layers) == 16 and len(b.mamba_layers) == 8 and b.vocab_size == 50304
+    d = b.to_dict(); d2 = kmoe.AdvancedMoEConfig.from_dict(d)
+    assert d2.moe_layers == b.moe_layers
+    with pytest.raises(TypeError):
+        kmoe.AdvancedMoEConfig.from_dict({"not_a_field": 1})

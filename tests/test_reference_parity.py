@@ -1,0 +1,130 @@
+"""Numerical parity with the reference implementation (imported from ``baseline/_ref`` when it is
+installed there): same weights + same input => same loss, gradients and optimizer steps."""
+import contextlib
+import os as _os
+_os.environ.setdefault("MOE_DISABLE_COMPILE", "1")   # the reference torch.compile()s its expert-choice body
+import io
+import os
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref")
+pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "moe_arch")),
+                                reason="reference package not installed under baseline/_ref")
+
+
+@pytest.fixture(scope="module")
+def ref():
+    saved = {k: v for k, v in sys.modules.items() if k == "moe_arch" or k.startswith("moe_arch.")}
+    for k in saved:
+        del sys.modules[k]
+    sys.path.insert(0, REF)
+    with contextlib.redirect_stdout(io.StringIO()):
+        import moe_arch.model.config as rc
+        import moe_arch.model.transformer as rt
+        import moe_arch.training.losses as rl
+        import moe_arch.training.lr_schedule as rs
+        import moe_arch.training.muon_optimizer as rm
+    yield {"config": rc, "transformer": rt, "losses": rl, "sched": rs, "muon": rm}
+    sys.path.remove(REF)
+    for k in [k for k in sys.modules if k == "moe_arch" or k.startswith("moe_arch.")]:
+        del sys.modules[k]
+    sys.modules.update(saved)
+
+
+KW = dict(vocab_size=512, d_model=64, n_layers=4, n_heads=4, n_kv_heads=1, head_dim=16, d_ff=128, d_ff_expert=96,
+          n_experts=4, moe_top_k=2, moe_layers=(1, 2), mamba_layers=(1,), max_seq_len=32, n_pred_tokens=4,
+          aux_loss_weights=(1.0, 0.5, 0.3, 0.2), dropout=0.0, attention_dropout=0.0, residual_dropout=0.0,
+          use_flash_attention=False, device="cpu", dtype="float32")
+
+
+def test_config_defaults_match(ref):
+    from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig
+    a, b = AdvancedMoEConfig(), ref["config"].AdvancedMoEConfig()
+    for k, v in b.to_dict().items():
+        assert getattr(a, k) == v, k
+    assert a.count_parameters() == b.count_parameters()
+
+
+@pytest.mark.parametrize("routing,mod", [("token_choice", True), ("expert_choice", False)])
+def test_model_loss_and_grads_match(ref, routing, mod):
+    from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig, MoETransformer
+    kw = dict(KW, moe_routing=routing, mod_enabled=mod)
+    torch.manual_seed(0)
+    with contextlib.redirect_stdout(io.StringIO()):
+        rmodel = ref["transformer"].MoETransformer(ref["config"].AdvancedMoEConfig(**kw))
+    ours = MoETransformer(AdvancedMoEConfig(mamba_impl="simple", **kw), verbose=False)
+    missing, unexpected = ours.load_state_dict(rmodel.state_dict(), strict=True)
+    assert not missing and not unexpected
+    ids = torch.randint(0, 512, (2, 32), generator=torch.Generator().manual_seed(1))
+    rmodel.train(); ours.train()
+    with contextlib.redirect_stdout(io.StringIO()):
+        ro = rmodel(ids, labels=ids)
+    oo = ours(ids, labels=ids, return_logits=False)
+    assert torch.allclose(oo["lm_loss"], ro["lm_loss"], atol=1e-5), (oo["lm_loss"], ro["lm_loss"])
+    assert torch.allclose(oo["loss"], ro["loss"], atol=1e-5)
+    ro["loss"].backward(); oo["loss"].backward()
+    rg = dict(rmodel.named_parameters())
+    for n, p in ours.named_parameters():
+        if rg[n].grad is None:
+            assert p.grad is None or p.grad.abs().max() == 0, n
+        else:
+            assert torch.allclose(p.grad, rg[n].grad, atol=2e-5, rtol=1e-3), n
+    rmodel.eval(); ours.eval()
+    with torch.no_grad(), contextlib.redirect_stdout(io.StringIO()):
+        assert torch.allclose(ours(ids)["logits"], rmodel(ids)["logits"], atol=1e-4)
+
+
+def test_mtp_loss_matches(ref):
+    from kolmogorov_moe_architecture_b200.training.losses import MultiTokenPredictionLoss
+    g = torch.Generator().manual_seed(0)
+    logits = [torch.randn(2, 16, 50, generator=g) for _ in range(3)]
+    labels = torch.randint(0, 50, (2, 16), generator=g)
+    mask = torch.ones(2, 16, dtype=torch.long); mask[0, 10:] = 0
+    with contextlib.redirect_stdout(io.StringIO()):
+        r = ref["losses"].MultiTokenPredictionLoss(3, (1.0, 0.5, 0.25))
+    o = MultiTokenPredictionLoss(3, (1.0, 0.5, 0.25))
+    a, _ = o(logits, labels, attention_mask=mask)
+    b, _ = r(logits, labels, attention_mask=mask)
+    assert torch.allclose(a, b, atol=1e-6)
+
+
+@pytest.mark.parametrize("cls", ["Muon", "Muon8bit"])
+def test_muon_steps_match(ref, cls):
+    from kolmogorov_moe_architecture_b200.training import muon_optimizer as mo
+    g = torch.Generator().manual_seed(0)
+    shapes = [(24, 40), (40, 24), (3, 16, 24), (17,)]
+    pa = [torch.randn(*s, generator=g).requires_grad_(True) for s in shapes]
+    pb = [p.detach().clone().requires_grad_(True) for p in pa]
+    with contextlib.redirect_stdout(io.StringIO()):
+        oa = getattr(mo, cls)(pa, lr=1e-2)
+        ob = getattr(ref["muon"], cls)(pb, lr=1e-2)
+    for _ in range(3):
+        for x, y in zip(pa, pb):
+            gr = torch.randn(*x.shape, generator=g)
+            x.grad, y.grad = gr.clone(), gr.clone()
+        oa.step(); ob.step()
+    for x, y in zip(pa, pb):
+        assert torch.allclose(x, y, atol=1e-5), x.shape
+
+
+def test_newton_schulz_orthogonality():
+    from kolmogorov_moe_architecture_b200.ops import eager
+    m = torch.randn(32, 64, generator=torch.Generator().manual_seed(0))
+    q = eager.newton_schulz(m, 10)
+    assert (q @ q.T - torch.eye(32)).abs().max() < 0.1
+
+
+def test_schedule_matches(ref):
+    from kolmogorov_moe_architecture_b200.training.lr_schedule import CosineScheduleWithWarmup
+    p = [torch.zeros(1, requires_grad=True)]
+    oa, ob = torch.optim.SGD(p, lr=1.0), torch.optim.SGD(p, lr=1.0)
+    with contextlib.redirect_stdout(io.StringIO()):
+        r = ref["sched"].CosineScheduleWithWarmup(ob, 5, 50, 1e-3, 1e-4)
+    o = CosineScheduleWithWarmup(oa, 5, 50, 1e-3, 1e-4)
+    for _ in range(60):
+        assert abs(o.step() - r.step()) < 1e-12
+    assert o.state_dict() == r.state_dict()
