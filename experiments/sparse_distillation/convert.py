@@ -1,0 +1,95 @@
+"""Swap the dense FFNs of a model for trained MoE layers (counterpart of the reference's
+``Experiments/sparse_distillation/convert.py``)."""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+import torch.nn as nn
+
+from .distill import DistillationConfig, MoEDistillationLayer
+from .hooks import find_ffn_modules
+
+
+def _set_submodule(root: nn.Module, path: str, new: nn.Module) -> None:
+    parts = path.split(".")
+    parent = root
+    for p in parts[:-1]:
+        parent = getattr(parent, p) if not p.isdigit() else parent[int(p)]
+    if parts[-1].isdigit():
+        parent[int(parts[-1])] = new
+    else:
+        setattr(parent, parts[-1], new)
+
+
+def replace_ffn_with_moe(model: nn.Module, moe_layers: Dict[str, nn.Module]) -> nn.Module:
+    for i, (name, _) in enumerate(find_ffn_modules(model)):
+        if str(i) in moe_layers:
+            _set_submodule(model, name, moe_layers[str(i)])
+    return model
+
+
+class SparseModelWrapper(nn.Module):
+    """The converted model plus helpers: routing statistics of the last forward and parameter counts."""
+
+    def __init__(self, model: nn.Module, moe_paths: Dict[int, str]):
+        super().__init__()
+        self.model, self.moe_paths = model, moe_paths
+
+    def forward(self, *a, **kw):
+        return self.model(*a, **kw)
+
+    def moe_modules(self):
+        mods = dict(self.model.named_modules())
+        return {i: mods[p] for i, p in self.moe_paths.items()}
+
+    def routing_stats(self) -> Dict[int, Dict[str, float]]:
+        out = {}
+        for i, m in self.moe_modules().items():
+            c = getattr(m, "_last_expert_counts", None)
+            if c is not None:
+                u = c.float() / c.sum().clamp(min=1)
+                out[i] = {"max_usage": float(u.max()), "dead": int((u == 0).sum()),
+                          "entropy": float(-(u * torch.log(u + 1e-10)).sum() / torch.log(torch.tensor(float(len(u)))))}
+        return out
+
+    def count_parameters(self) -> Dict[str, int]:
+        total = sum(p.numel() for p in self.model.parameters())
+        expert = sum(p.numel() for m in self.moe_modules().values() for p in m.experts.parameters())
+        frac = next(iter(self.moe_modules().values())).top_k / next(iter(self.moe_modules().values())).n_experts \
+            if self.moe_paths else 1.0
+        return {"total": total, "expert": expert, "active": int(total - expert * (1 - frac))}
+
+
+def infer_layer_dims(state: Dict[str, torch.Tensor]):
+    """(n_experts, d_model, d_ff) from a saved MoE layer's ``experts.w1`` shape."""
+    w1 = state["experts.w1"]
+    return w1.shape[0], w1.shape[1], w1.shape[2]
+
+
+def convert_to_sparse(model: nn.Module, distilled_path: Optional[str] = None, trainer=None,
+                      random_init: bool = False) -> SparseModelWrapper:
+    """Build the sparse model from a ``SparseDistillationTrainer`` or from its ``save()`` file.
+    ``random_init=True`` keeps the architecture but re-initialises the experts (a control)."""
+    if trainer is not None:
+        layers = {k: v for k, v in trainer.get_moe_layers().items()}
+    else:
+        ck = torch.load(distilled_path, map_location="cpu", weights_only=False)
+        cfg = DistillationConfig(**ck["config"])
+        layers = {}
+        for k, sd in ck["layers"].items():
+            E, d, f = infer_layer_dims(sd)
+            top_k = ck.get("dims", {}).get(k, (d, f, E, cfg.moe_top_k))[3]
+            layer = MoEDistillationLayer(d, f, cfg, n_experts=E, top_k=top_k)
+            layer.load_state_dict(sd)
+            layers[k] = layer
+    if random_init:
+        for layer in layers.values():
+            for p in layer.experts.parameters():
+                nn.init.normal_(p, std=0.02)
+    paths = {i: name for i, (name, _) in enumerate(find_ffn_modules(model)) if str(i) in layers}
+    p0 = next(model.parameters())
+    for layer in layers.values():
+        layer.to(p0.device).to(p0.dtype)
+    replace_ffn_with_moe(model, layers)
+    return SparseModelWrapper(model, paths)

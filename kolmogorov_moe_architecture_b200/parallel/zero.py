@@ -224,7 +224,8 @@ class ShardedDataParallel:
     def owned_sq_norm(self) -> torch.Tensor:
         if getattr(self, "_sq_valid", False):
             return self._sq[0]
-        return self.own_slice(self.flat_grad).float().pow(2).sum()
+        # fused fp32-accumulating reduction: no fp32 copy of the gradient segment is materialised
+        return torch.linalg.vector_norm(self.own_slice(self.flat_grad), dtype=torch.float32).pow(2)
 
     def scale_owned(self, coef: torch.Tensor) -> None:
         """Apply the clip coefficient: the fused AdamW kernel reads it from the device; only

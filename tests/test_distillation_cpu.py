@@ -1,0 +1,89 @@
+"""Sparse distillation pipeline on a toy transformer (CPU)."""
+import torch
+
+from experiments.sparse_distillation.convert import convert_to_sparse
+from experiments.sparse_distillation.distill import (DistillationConfig, MoEDistillationLayer,
+                                                     SparseDistillationTrainer, cluster_quality, kmeans)
+from experiments.sparse_distillation.dynamic_experts import (DynamicExpertLayer, interpolate_expert_weights,
+                                                             reallocate_expert_layer)
+from experiments.sparse_distillation.example_usage import ToyLM
+from experiments.sparse_distillation.generate_config import choose_layer_config
+from experiments.sparse_distillation.hooks import FFNActivationCache, find_ffn_modules
+
+
+def _cfg(**kw):
+    base = dict(n_experts=4, moe_top_k=2, data_free=True, data_free_steps=30, data_free_seq_len=32,
+                data_free_batch_size=2, cluster_samples=512, router_train_steps=20, log_interval=0,
+                learning_rate=2e-3)
+    base.update(kw)
+    return DistillationConfig(**base)
+
+
+def test_hooks_capture_ffn_io():
+    torch.manual_seed(0)
+    m = ToyLM()
+    assert len(find_ffn_modules(m)) == 2
+    with FFNActivationCache(m) as c:
+        m(torch.randint(0, 256, (2, 8)))
+    assert c.inputs[0].shape == (2, 8, 64) and c.outputs[1].shape == (2, 8, 64)
+
+
+def test_init_from_dense_makes_experts_tile_the_dense_ffn():
+    torch.manual_seed(0)
+    m = ToyLM()
+    layer = MoEDistillationLayer(64, 64, _cfg())
+    assert layer.init_from_dense_ffn(m.blocks[0].mlp, noise=0.0)
+    assert torch.allclose(layer.experts.w1[1], m.blocks[0].mlp.gate_proj.weight[64:128].t())
+
+
+def test_data_free_distillation_reduces_error_and_converts():
+    torch.manual_seed(0)
+    m = ToyLM().eval()
+    tr = SparseDistillationTrainer(m, _cfg(), device="cpu")
+    hist = tr.distill(steps=40)
+    assert sum(hist[0][-5:]) < sum(hist[0][:5])
+    ev = tr.evaluate(2)
+    assert ev[0]["cosine"] > 0.5
+    sparse = convert_to_sparse(m, trainer=tr)
+    out = sparse(torch.randint(0, 256, (2, 16)))
+    assert out["logits"].shape == (2, 16, 256)
+    assert set(sparse.routing_stats()) == {0, 1}
+
+
+def test_empirical_and_dynamic_and_expert_choice_modes_run():
+    torch.manual_seed(0)
+    for kw in (dict(empirical_routing=True, supervised_routing=False), dict(dynamic_experts=True, reallocate_every_n_steps=5, min_d_ff=16),
+               dict(moe_routing="expert_choice", supervised_routing=False)):
+        tr = SparseDistillationTrainer(ToyLM().eval(), _cfg(**kw), device="cpu")
+        hist = tr.distill(steps=8)
+        assert all(torch.isfinite(torch.tensor(v)).all() for v in hist.values())
+
+
+def test_save_load_roundtrip(tmp_path):
+    torch.manual_seed(0)
+    m = ToyLM().eval()
+    tr = SparseDistillationTrainer(m, _cfg(), device="cpu")
+    tr.save(str(tmp_path / "d.pt"))
+    sparse = convert_to_sparse(ToyLM().eval(), distilled_path=str(tmp_path / "d.pt"))
+    assert sparse.count_parameters()["active"] < sparse.count_parameters()["total"]
+
+
+def test_kmeans_and_quality_and_layer_config():
+    g = torch.Generator().manual_seed(0)
+    x = torch.cat([torch.randn(100, 8, generator=g) + 6 * i for i in range(3)])
+    assign, cent = kmeans(x, 3)
+    q = cluster_quality(x, assign, cent)
+    assert q["silhouette"] > 0.5 and q["balance"] > 0.9
+    cfg = choose_layer_config({"4": {"silhouette": 0.2, "balance": 0.9}, "8": {"silhouette": 0.4, "balance": 0.9}}, 1024)
+    assert cfg["n_experts"] == 8 and cfg["d_ff_expert"] == 256 and cfg["top_k"] == 1
+
+
+def test_dynamic_expert_resize():
+    w1, w2, w3 = torch.randn(8, 32), torch.randn(8, 32), torch.randn(32, 8)
+    a, b, c = interpolate_expert_weights(w1, w2, w3, 16)
+    assert a.shape == (8, 16) and c.shape == (16, 8)
+    a, b, c = interpolate_expert_weights(w1, w2, w3, 48)
+    assert a.shape == (8, 48) and c.shape == (48, 8)
+    layer = reallocate_expert_layer(DynamicExpertLayer(8, [32, 32]), {0: 48, 1: 16})
+    out = layer(torch.randn(5, 8), torch.tensor([[0], [1], [0], [1], [0]]), torch.ones(5, 1))
+    assert out.shape == (5, 8) and layer.d_ffs == [48, 16]

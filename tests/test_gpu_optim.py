@@ -17,6 +17,7 @@ def _tiny(dtype=torch.bfloat16):
 
 
 def test_fused_adamw_kernel_matches_torch():
+    from kolmogorov_moe_architecture_b200.ops import cuda_ops  # noqa: F401  (loads the extension)
     n = 4096 + 128
     torch.manual_seed(1)
     p0 = torch.randn(n, device="cuda").to(torch.bfloat16)
