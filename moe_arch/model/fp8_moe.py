@@ -1,0 +1,1 @@
+from kolmogorov_moe_architecture_b200.models.fp8_moe import FP8GroupedExperts, FP8Linear, FP8MoELayer, is_fp8_available  # noqa: F401

@@ -1,0 +1,1 @@
+from kolmogorov_moe_architecture_b200.models.fused_moe import FusedSparseMoE, OptimizedGroupedExperts  # noqa: F401

@@ -1,0 +1,1 @@
+from kolmogorov_moe_architecture_b200.models.mod import MoDRouter  # noqa: F401

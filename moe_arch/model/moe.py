@@ -1,0 +1,1 @@
+from kolmogorov_moe_architecture_b200.models.moe import ExpertChoiceRouter, GroupedExperts, GroupedExpertsExpertChoice, MoELayer, Router  # noqa: F401
