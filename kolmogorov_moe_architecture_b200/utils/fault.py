@@ -104,6 +104,27 @@ class HeartbeatMonitor:
         except Exception:
             return None
 
+    def wait_all(self, step: int, timeout_s: Optional[float] = None, poll_s: float = 0.01) -> List[int]:
+        """Host-side agreement before a step's collectives: publish ``step``, then wait until every
+        other rank has published a value >= ``step`` or has marked itself as leaving.  Returns the ranks
+        that left or did not show up within the timeout; an empty list means it is safe to launch."""
+        self.beat(step)
+        deadline = time.monotonic() + (self.timeout_s if timeout_s is None else timeout_s)
+        pending = [r for r in range(self.world) if r != self.rank]
+        gone: List[int] = []
+        while pending:
+            for r in list(pending):
+                v = self._read(r)
+                if v == -1:
+                    gone.append(r)
+                    pending.remove(r)
+                elif v is not None and v >= step:
+                    pending.remove(r)
+            if not pending or time.monotonic() > deadline:
+                break
+            time.sleep(poll_s)
+        return sorted(gone + pending)
+
     def dead_ranks(self, step: int) -> List[int]:
         now = time.monotonic()
         dead = []
