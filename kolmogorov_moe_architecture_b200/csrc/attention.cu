@@ -5,12 +5,12 @@
 // lse [B, H, S] fp32 (natural log).  Query head h reads KV head h / (H / Hkv) directly -
 // K and V are never expanded to H heads.
 //
-// Forward, one CTA per (128-query block, head, batch):
+// Forward, one CTA per (128-query block, head, batch), two CTAs per SM, 64 keys per step:
 //   warp 4   TMA producer: Q once, then K_j / V_j into a 2-stage ring
-//   warp 5   MMA issuer:   S_j = Q K_j^T (double-buffered in TMEM), PV_j = P_j V_j
+//   warp 5   MMA issuer:   S_j = Q K_j^T (double-buffered in TMEM), O += P_j V_j (O lives in TMEM)
 //   warps 0-3 (thread = query row): S_j from TMEM -> scale, causal mask, running max/sum,
-//            P_j as bf16 into swizzled smem (A operand of the PV MMA), then
-//            O = O * alpha + PV_j with O kept in registers.
+//            P_j as bf16 into swizzled smem (A operand of the PV MMA); O is rescaled in TMEM only
+//            when the row maximum grew by more than 2^8.
 // Backward is two kernels of the same structure: dQ (loop over KV blocks for a query
 // block) and dK/dV (loop over query blocks of all heads of the group for a KV block);
 // both recompute P from the saved lse, so no atomics and the result is deterministic.
@@ -47,23 +47,36 @@ __device__ __forceinline__ uint32_t swz_kmajor(int row, int col) {
   return panel * PANEL_BYTES + row * 128 + ((chunk ^ (row & 7)) << 4);
 }
 
+// 16-byte chunk offset inside a [rows x 64] K-major swizzled panel
+__device__ __forceinline__ uint32_t swz64(int row, int col) { return row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4); }
+
+constexpr int FWD_BN = 64;                         // keys per forward step
+constexpr int FWD_KPANEL = FWD_BN * 128;           // 64 key rows x 64 bf16 columns
+constexpr float RESCALE_THRESHOLD = 8.0f;          // log2 units: rescale O only when the row max grew by > 2^8
+
+// Forward.  O stays in TMEM across the whole KV loop (the PV MMA accumulates into it); the running
+// maximum used for the exponent is only advanced - and O rescaled in place - when the true row
+// maximum has grown by more than RESCALE_THRESHOLD, so most steps never touch O.  64-key steps keep
+// the footprint at 112 KB of shared memory and 256 TMEM columns: two CTAs share an SM and the
+// softmax of one overlaps the MMAs of the other.
 template <int D>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+__global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
-  constexpr int NP = D / 64;                      // panels per tile
-  constexpr int TILE_BYTES = NP * PANEL_BYTES;    // Q, K, V tiles
-  constexpr uint32_t IDESC_S = make_idesc_f16(128, ATT_BLK, 1, KMOE_MAJOR_K, KMOE_MAJOR_K);
+  constexpr int NP = D / 64;
+  constexpr int QTILE = NP * PANEL_BYTES;       // 128 query rows
+  constexpr int KTILE = NP * FWD_KPANEL;        // 64 key rows
+  constexpr uint32_t IDESC_S = make_idesc_f16(128, FWD_BN, 1, KMOE_MAJOR_K, KMOE_MAJOR_K);
   constexpr uint32_t IDESC_PV = make_idesc_f16(128, D, 1, KMOE_MAJOR_K, KMOE_MAJOR_MN);
-  constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t COL_S0 = 0, COL_PV = 256;
+  constexpr uint32_t TMEM_COLS = 256;
+  constexpr uint32_t COL_S0 = 0, COL_O = 128;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + TILE_BYTES;            // 2 stages
-  uint8_t* sV = sK + 2 * TILE_BYTES;        // 2 stages
-  uint8_t* sP = sV + 2 * TILE_BYTES;        // 128 x 128 bf16
+  uint8_t* sK = sQ + QTILE;             // 2 stages
+  uint8_t* sV = sK + 2 * KTILE;         // 2 stages
+  uint8_t* sP = sV + 2 * KTILE;         // 128 x 64 bf16, one K-major panel
   __shared__ uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_free[2], p_full, pv_full;
   __shared__ uint32_t tmem_slot;
 
@@ -72,7 +85,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int h = blockIdx.y, b = blockIdx.z;
   const int hkv = h / (a.H / a.Hkv);
   const int q0 = qb * ATT_BLK;
-  const int nblk = qb + 1;                    // causal: KV blocks 0..qb
+  const int kmax = min(q0 + ATT_BLK, a.S);
+  const int nblk = (kmax + FWD_BN - 1) / FWD_BN;
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
@@ -97,22 +111,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (warp == 4) {
     if (elect_one()) {
-      mbar_expect_tx(&q_full, TILE_BYTES);
+      mbar_expect_tx(&q_full, QTILE);
 #pragma unroll
       for (int p = 0; p < NP; ++p) tma_load_4d(sQ + p * PANEL_BYTES, &tmQ, &q_full, p * 64, h, q0, b);
       for (int j = 0; j < nblk; ++j) {
         const int st = j & 1;
         const uint32_t par = ((j >> 1) & 1) ^ 1;
         if (!mbar_wait(&k_empty[st], par)) { atomicExch(a.status, 11); goto teardown; }
-        mbar_expect_tx(&k_full[st], TILE_BYTES);
+        mbar_expect_tx(&k_full[st], KTILE);
 #pragma unroll
         for (int p = 0; p < NP; ++p)
-          tma_load_4d(sK + st * TILE_BYTES + p * PANEL_BYTES, &tmK, &k_full[st], p * 64, hkv, j * ATT_BLK, b);
+          tma_load_4d(sK + st * KTILE + p * FWD_KPANEL, &tmK, &k_full[st], p * 64, hkv, j * FWD_BN, b);
         if (!mbar_wait(&v_empty[st], par)) { atomicExch(a.status, 12); goto teardown; }
-        mbar_expect_tx(&v_full[st], TILE_BYTES);
+        mbar_expect_tx(&v_full[st], KTILE);
 #pragma unroll
         for (int p = 0; p < NP; ++p)
-          tma_load_4d(sV + st * TILE_BYTES + p * PANEL_BYTES, &tmV, &v_full[st], p * 64, hkv, j * ATT_BLK, b);
+          tma_load_4d(sV + st * KTILE + p * FWD_KPANEL, &tmV, &v_full[st], p * 64, hkv, j * FWD_BN, b);
       }
     }
   } else if (warp == 5) {
@@ -122,12 +136,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(&k_full[st], (j >> 1) & 1)) return false;
         if (!mbar_wait(&s_free[st], ((j >> 1) & 1) ^ 1)) return false;
         tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * TILE_BYTES);
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * KTILE);
 #pragma unroll
         for (int k4 = 0; k4 < D / 16; ++k4) {
-          const uint32_t off = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;
-          umma_f16(tmem + COL_S0 + st * ATT_BLK, make_smem_desc_sw128(qa + off, 16, 1024),
-                   make_smem_desc_sw128(ka + off, 16, 1024), IDESC_S, k4 > 0);
+          const uint32_t aoff = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;
+          const uint32_t boff = (k4 >> 2) * FWD_KPANEL + (k4 & 3) * 32;
+          umma_f16(tmem + COL_S0 + st * FWD_BN, make_smem_desc_sw128(qa + aoff, 16, 1024),
+                   make_smem_desc_sw128(ka + boff, 16, 1024), IDESC_S, k4 > 0);
         }
         umma_commit(&s_full[st]);
         umma_commit(&k_empty[st]);
@@ -141,14 +156,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(&v_full[st], (j >> 1) & 1)) { atomicExch(a.status, 16); goto teardown; }
         if (!mbar_wait(&p_full, j & 1)) { atomicExch(a.status, 17); goto teardown; }
         tc_fence_after();
-        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + st * TILE_BYTES);
+        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + st * KTILE);
 #pragma unroll
-        for (int k4 = 0; k4 < ATT_BLK / 16; ++k4) {
-          const uint32_t aoff = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;   // P: K-major over keys
-          const uint32_t boff = k4 * 16 * 128;                              // V: MN-major, 16 key rows
-          umma_f16(tmem + COL_PV, make_smem_desc_sw128(pa + aoff, 16, 1024),
-                   make_smem_desc_sw128(va + boff, PANEL_BYTES, 1024), IDESC_PV, k4 > 0);
-        }
+        for (int k4 = 0; k4 < FWD_BN / 16; ++k4)
+          umma_f16(tmem + COL_O, make_smem_desc_sw128(pa + k4 * 32, 16, 1024),
+                   make_smem_desc_sw128(va + k4 * 16 * 128, FWD_KPANEL, 1024), IDESC_PV, (j > 0 || k4 > 0));
         umma_commit(&pv_full);
         umma_commit(&v_empty[st]);
       }
@@ -158,86 +170,91 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int r = warp * 32 + lane;                 // query row within the block
     const int qi = q0 + r;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    float m = -INFINITY, l = 0.f;
-    float O[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) O[i] = 0.f;
+    float m_used = -INFINITY, l = 0.f;
     for (int j = 0; j < nblk; ++j) {
       const int st = j & 1;
       if (!mbar_wait(&s_full[st], (j >> 1) & 1)) { if (lane == 0) atomicExch(a.status, 18); goto teardown; }
       tc_fence_after();
-      const uint32_t ts = tmem + lane_base + COL_S0 + st * ATT_BLK;
-      const int k0 = j * ATT_BLK;
-      const bool need_mask = (j == qb) || (k0 + ATT_BLK > a.S);
-      // pass 1: row maximum
+      const uint32_t ts = tmem + lane_base + COL_S0 + st * FWD_BN;
+      const int k0 = j * FWD_BN;
+      const bool need_mask = (k0 + FWD_BN > q0) || (k0 + FWD_BN > a.S);
+      uint32_t sv[FWD_BN];
+      {
+        uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[0]);
+        uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[32]);
+        tmem_ld_32x32(ts, lo);
+        tmem_ld_32x32(ts + 32, hi);
+        tmem_ld_wait();
+      }
+      tc_fence_before();
+      mbar_arrive(&s_free[st]);          // S_j is in registers: its TMEM buffer may be overwritten
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < ATT_BLK; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(ts + c, v);
-        tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]);
-          if (need_mask && (k0 + c + i > qi || k0 + c + i >= a.S)) s = -INFINITY;
-          mx = fmaxf(mx, s);
-        }
+      for (int i = 0; i < FWD_BN; ++i) {
+        float s = __uint_as_float(sv[i]) * a.scale_log2;
+        if (need_mask && (k0 + i > qi || k0 + i >= a.S)) s = -INFINITY;
+        sv[i] = __float_as_uint(s);
+        mx = fmaxf(mx, s);
       }
-      const float m_new = fmaxf(m, mx * a.scale_log2);
-      const float alpha = exp2f(m - m_new);
+      const bool grow = mx > m_used + RESCALE_THRESHOLD;      // always true on the first step
+      const float m_new = grow ? mx : m_used;
+      const float alpha = grow ? exp2f(m_used - m_new) : 1.f;
       float rs = 0.f;
-      // pass 2: probabilities -> swizzled smem
-#pragma unroll 1
-      for (int c = 0; c < ATT_BLK; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(ts + c, v);
-        tmem_ld_wait();
-        float p[32];
+      uint32_t pk[FWD_BN / 2];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]);
-          const bool dead = need_mask && (k0 + c + i > qi || k0 + c + i >= a.S);
-          p[i] = dead ? 0.f : exp2f(s * a.scale_log2 - m_new);
-          rs += p[i];
-        }
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          uint4 o;
-          o.x = pack_bf16(p[i], p[i + 1]); o.y = pack_bf16(p[i + 2], p[i + 3]);
-          o.z = pack_bf16(p[i + 4], p[i + 5]); o.w = pack_bf16(p[i + 6], p[i + 7]);
-          *reinterpret_cast<uint4*>(sP + swz_kmajor(r, c + i)) = o;
-        }
+      for (int i = 0; i < FWD_BN; i += 2) {
+        const float p0 = exp2f(__uint_as_float(sv[i]) - m_new), p1 = exp2f(__uint_as_float(sv[i + 1]) - m_new);
+        rs += p0 + p1;
+        pk[i >> 1] = pack_bf16(p0, p1);
       }
-      tc_fence_before();
-      mbar_arrive(&s_free[st]);
       l = l * alpha + rs;
-      m = m_new;
+      m_used = m_new;
+      if (j > 0) {
+        // PV_{j-1} must have retired before P is overwritten or O is rescaled
+        if (!mbar_wait(&pv_full, (j - 1) & 1)) { if (lane == 0) atomicExch(a.status, 19); goto teardown; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+          for (int c = 0; c < D; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem + lane_base + COL_O + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32(tmem + lane_base + COL_O + c, v);
+          }
+          tmem_st_wait();
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < FWD_BN; c += 8)
+        *reinterpret_cast<uint4*>(sP + swz64(r, c)) = make_uint4(pk[c / 2], pk[c / 2 + 1], pk[c / 2 + 2], pk[c / 2 + 3]);
       fence_async_smem();
-      mbar_arrive(&p_full);
-      if (!mbar_wait(&pv_full, j & 1)) { if (lane == 0) atomicExch(a.status, 19); goto teardown; }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < D; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem + lane_base + COL_PV + c, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) O[c + i] = O[c + i] * alpha + __uint_as_float(v[i]);
-      }
       tc_fence_before();
+      mbar_arrive(&p_full);
     }
-    if (qi < a.S) {
-      const float inv = 1.f / l;
-      __nv_bfloat16* orow = a.out + (((size_t)b * a.S + qi) * a.H + h) * D;
+    if (!mbar_wait(&pv_full, (nblk - 1) & 1)) { if (lane == 0) atomicExch(a.status, 20); goto teardown; }
+    tc_fence_after();
+    const bool row_ok = qi < a.S;
+    const float inv = 1.f / l;
+    __nv_bfloat16* orow = a.out + (((size_t)b * a.S + (row_ok ? qi : 0)) * a.H + h) * D;
 #pragma unroll
-      for (int c = 0; c < D; c += 8) {
-        uint4 o;
-        o.x = pack_bf16(O[c] * inv, O[c + 1] * inv); o.y = pack_bf16(O[c + 2] * inv, O[c + 3] * inv);
-        o.z = pack_bf16(O[c + 4] * inv, O[c + 5] * inv); o.w = pack_bf16(O[c + 6] * inv, O[c + 7] * inv);
-        *reinterpret_cast<uint4*>(orow + c) = o;
+    for (int c = 0; c < D; c += 32) {
+      uint32_t v[32];
+      tmem_ld_32x32(tmem + lane_base + COL_O + c, v);
+      tmem_ld_wait();
+      if (row_ok) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8)
+          *reinterpret_cast<uint4*>(orow + c + i) =
+              make_uint4(pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv),
+                         pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv),
+                         pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv),
+                         pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv));
       }
-      a.lse[((size_t)b * a.H + h) * a.S + qi] = (m + log2f(l)) * 0.6931471805599453f;
     }
+    if (row_ok) a.lse[((size_t)b * a.H + h) * a.S + qi] = (m_used + log2f(l)) * 0.6931471805599453f;
+    tc_fence_before();
   }
 
 teardown:
@@ -296,8 +313,6 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
   }
 }
 
-// 16-byte chunk offset inside a [rows x 64] K-major swizzled panel
-__device__ __forceinline__ uint32_t swz64(int row, int col) { return row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4); }
 
 // dQ for one (128-query block, head, batch): dQ = sum_j dS_j K_j, dS = P * (dO V^T - delta) * scale
 template <int D>
@@ -678,8 +693,8 @@ static int make_bshd_tmap(CUtensorMap* out, const void* base, int B, int S, int 
 template <int D>
 static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a,
                            cudaStream_t st) {
-  constexpr int tile = (D / 64) * PANEL_BYTES;
-  const int smem = tile * 5 + ATT_BLK * ATT_BLK * 2 + 1024;
+  constexpr int NP = D / 64;
+  const int smem = NP * PANEL_BYTES + 4 * NP * FWD_KPANEL + ATT_BLK * 128 + 1024;
   auto kern = attn_fwd_kernel<D>;
   static bool attr = false;
   if (!attr) {
@@ -701,8 +716,8 @@ extern "C" int kmoe_attn_fwd(const void* q, const void* k, const void* v, void* 
   CUtensorMap tq, tk, tv;
   int rc = make_bshd_tmap(&tq, q, B, S, H, D, ATT_BLK);
   if (rc) return rc;
-  if ((rc = make_bshd_tmap(&tk, k, B, S, Hkv, D, ATT_BLK))) return rc;
-  if ((rc = make_bshd_tmap(&tv, v, B, S, Hkv, D, ATT_BLK))) return rc;
+  if ((rc = make_bshd_tmap(&tk, k, B, S, Hkv, D, FWD_BN))) return rc;
+  if ((rc = make_bshd_tmap(&tv, v, B, S, Hkv, D, FWD_BN))) return rc;
   AttnArgs a{B, S, H, Hkv, scale * 1.4426950408889634f, (__nv_bfloat16*)out, lse, status};
   return D == 128 ? launch_attn_fwd<128>(tq, tk, tv, a, st) : launch_attn_fwd<64>(tq, tk, tv, a, st);
 }

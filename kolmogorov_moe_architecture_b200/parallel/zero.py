@@ -177,6 +177,7 @@ class ShardedDataParallel:
             self.adamw = make_adamw([p for _, p in self.owned_adamw], adamw_lr, weight_decay=weight_decay)
         self.optimizer = _PoolOptimizer(self)
         self._clip: Optional[torch.Tensor] = None
+        self._side_stream = None
         self._sq = torch.zeros(1, dtype=torch.float32, device=device)
 
     # ------------------------------------------------------------------ set-up
@@ -244,12 +245,24 @@ class ShardedDataParallel:
         a0 = self.rank * self.seg
         ptrs = self.p2p.param_ptrs if self.transport == "p2p" else [self.flat_param.data_ptr()]
         prank = self.rank if self.transport == "p2p" else 0
-        if self.fused is not None:
+        # The fused AdamW kernel is HBM-bound and Muon's Newton-Schulz is tensor-core-bound: run them
+        # on two streams so they overlap (they touch disjoint ranges of the flat buffers).
+        side = None
+        if self.fused is not None and self.muon is not None and self.device.type == "cuda":
+            if self._side_stream is None:
+                self._side_stream = torch.cuda.Stream(device=self.device)
+            side = self._side_stream
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                self.fused.step(ptrs, prank, self._clip)
+        elif self.fused is not None:
             self.fused.step(ptrs, prank, self._clip)
         if self.adamw is not None:
             self.adamw.step()
         if self.muon is not None:
             self.muon.step()
+        if side is not None:
+            torch.cuda.current_stream(self.device).wait_stream(side)
         if self.transport == "p2p":
             lo = a0 + (self.fused.n if self.fused is not None else 0)
             hi = a0 + self.used[self.rank]

@@ -18,7 +18,6 @@ batched call instead of one Python-level iteration per parameter.
 from __future__ import annotations
 
 import os
-from collections import defaultdict
 from typing import Dict, Iterable, List, Optional
 
 import torch
@@ -65,54 +64,91 @@ class Muon(Optimizer):
     def _newton_schulz_orthogonalize_batched(matrices: torch.Tensor, num_iters: int = 5) -> torch.Tensor:
         return ops.newton_schulz(matrices, num_iters)
 
+    def _bucket_state(self, group_idx: int, params):
+        """Momentum of all >=2-D parameters of equal matrix shape lives in one stacked tensor
+        (``state[p]['momentum_buffer']`` is a view of its slice), so momentum update, Newton-Schulz
+        and write-back are a handful of launches per shape instead of several per parameter."""
+        key = (group_idx, tuple(id(p) for p in params))
+        cache = self.__dict__.setdefault("_buckets", {})
+        if key in cache:
+            return cache[key]
+        buckets = {}
+        for p in params:
+            mb = _as_matrix_batch(p)
+            buckets.setdefault((mb.shape[1], mb.shape[2], p.dtype, p.device), []).append(p)
+        out = []
+        for (m, n, dt, dev), ps in buckets.items():
+            counts = [_as_matrix_batch(p).shape[0] for p in ps]
+            stacked = torch.zeros(sum(counts), m, n, dtype=dt, device=dev)
+            off = 0
+            views = []
+            for p, c in zip(ps, counts):
+                v = stacked[off: off + c].view(p.shape)
+                st = self.state[p]
+                if "momentum_buffer" in st:                 # state loaded from a checkpoint
+                    v.copy_(st["momentum_buffer"])
+                st["momentum_buffer"] = v
+                views.append(v)
+                off += c
+            out.append((stacked, ps, views))
+        cache[key] = out
+        return out
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = None
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
-        for group in self.param_groups:
+        for gi, group in enumerate(self.param_groups):
             lr, mu, wd = group["lr"], group["momentum"], group["weight_decay"]
             nesterov, backend, iters = group["nesterov"], group["backend"], group["newton_iters"]
             standard = group.get("standard_muon", False)
-            buckets: Dict[tuple, List[torch.Tensor]] = defaultdict(list)
-            pending = []
-            for p in group["params"]:
-                if p.grad is None:
-                    continue
-                g = p.grad
-                if wd != 0:
-                    p.mul_(1 - lr * wd)
+            live = [p for p in group["params"] if p.grad is not None]
+            if not live:
+                continue
+            if wd != 0:
+                torch._foreach_mul_(live, 1 - lr * wd)
+            vecs = [p for p in live if p.dim() < 2]
+            mats = [p for p in live if p.dim() >= 2]
+            for p in vecs:
                 st = self.state[p]
                 if "momentum_buffer" not in st:
-                    st["momentum_buffer"] = torch.zeros_like(g)
-                buf = st["momentum_buffer"]
-                buf.mul_(mu).add_(g)
-                if p.dim() >= 2:
-                    if backend == "qr" and p.dim() != 3:
-                        src = (g.add(buf, alpha=mu) if nesterov else buf) if standard else buf
-                        o = _qr_orthogonalize(src.reshape(src.shape[0], -1)).reshape(buf.shape)
-                        self._apply(p, g, buf, o, lr, mu, nesterov, standard)
-                    else:
-                        src = (g.add(buf, alpha=mu) if nesterov else buf) if standard else buf
-                        mb = _as_matrix_batch(src)
-                        buckets[(mb.shape[1], mb.shape[2], mb.dtype, mb.device)].append(mb)
-                        pending.append((p, g, buf, mb.shape[0]))
-                else:
-                    p.add_(g.add(buf, alpha=mu) if nesterov else buf, alpha=-lr)
-            # one batched Newton-Schulz per distinct matrix shape
-            results: Dict[tuple, List[torch.Tensor]] = {}
-            for key, mats in buckets.items():
-                stacked = torch.cat(mats, dim=0) if len(mats) > 1 else mats[0]
-                ortho = ops.newton_schulz(stacked, iters)
-                results[key] = list(torch.split(ortho, [m.shape[0] for m in mats], dim=0))
-            cursor: Dict[tuple, int] = defaultdict(int)
-            for p, g, buf, _nb in pending:
-                mb = _as_matrix_batch(buf)
-                key = (mb.shape[1], mb.shape[2], mb.dtype, mb.device)
-                o = results[key][cursor[key]].reshape(buf.shape)
-                cursor[key] += 1
-                self._apply(p, g, buf, o, lr, mu, nesterov, standard)
+                    st["momentum_buffer"] = torch.zeros_like(p.grad)
+            if vecs:
+                bufs = [self.state[p]["momentum_buffer"] for p in vecs]
+                grads = [p.grad for p in vecs]
+                torch._foreach_mul_(bufs, mu)
+                torch._foreach_add_(bufs, grads)
+                upd = torch._foreach_add(grads, bufs, alpha=mu) if nesterov else bufs
+                torch._foreach_add_(vecs, upd, alpha=-lr)
+            if not mats:
+                continue
+            if backend == "qr":
+                for p in mats:
+                    st = self.state[p]
+                    if "momentum_buffer" not in st:
+                        st["momentum_buffer"] = torch.zeros_like(p.grad)
+                    buf, g = st["momentum_buffer"], p.grad
+                    buf.mul_(mu).add_(g)
+                    src = (g.add(buf, alpha=mu) if nesterov else buf) if standard else buf
+                    mb = _as_matrix_batch(src)
+                    o = torch.stack([_qr_orthogonalize(x) for x in mb]).reshape(buf.shape)
+                    self._apply(p, g, buf, o, lr, mu, nesterov, standard)
+                continue
+            for stacked, ps, views in self._bucket_state(gi, mats):
+                grads = [p.grad for p in ps]
+                stacked.mul_(mu)
+                torch._foreach_add_(views, grads)
+                if standard:
+                    src = torch.cat([_as_matrix_batch(g.add(v, alpha=mu) if nesterov else v) for g, v in zip(grads, views)])
+                    ortho = ops.newton_schulz(src, iters)
+                    outs = torch.split(ortho, [_as_matrix_batch(p).shape[0] for p in ps])
+                    torch._foreach_add_(ps, [o.reshape(p.shape).to(p.dtype) for o, p in zip(outs, ps)], alpha=-lr)
+                    continue
+                stacked.copy_(ops.newton_schulz(stacked, iters))     # the orthogonal factor replaces the momentum
+                upd = torch._foreach_add(grads, views, alpha=mu) if nesterov else views
+                torch._foreach_add_(ps, upd, alpha=-lr)
         return loss
 
     @staticmethod

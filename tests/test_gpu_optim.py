@@ -20,7 +20,7 @@ def test_fused_adamw_kernel_matches_torch():
     from kolmogorov_moe_architecture_b200.ops import cuda_ops  # noqa: F401  (loads the extension)
     n = 4096 + 128
     torch.manual_seed(1)
-    p0 = torch.randn(n, device="cuda").to(torch.bfloat16)
+    p0 = (0.1 * torch.randn(n, device="cuda")).to(torch.bfloat16)
     ref_p = p0.float().clone().requires_grad_(True)
     opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1, eps=1e-8)
     flat_p, flat_g = p0.clone(), torch.zeros_like(p0)
@@ -35,7 +35,7 @@ def test_fused_adamw_kernel_matches_torch():
         ref_p.grad = g.float() * 0.5
         opt.step()
     err = (flat_p.float() - ref_p.detach()).abs().max().item()
-    assert err < 2e-2, err          # bf16 parameter rounding per step
+    assert err < 5e-3, err          # bf16 parameter rounding (ulp 1e-3 at 0.25) over three steps
 
 
 def test_sharded_pool_single_gpu_trains():
