@@ -321,6 +321,96 @@ void p2p_allgather(std::vector<int64_t> buf_ptrs, int64_t rank, int64_t world, i
         "p2p_allgather");
 }
 
+// ------------------------------------------------------------- routing decisions
+std::vector<Tensor> route_topk_fwd(const Tensor& logits, int64_t k) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  need_f32(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous());
+  const int64_t T = logits.size(0), E = logits.size(1);
+  auto of = logits.options();
+  Tensor w = at::empty({T, k}, of), idx = at::empty({T, k}, of.dtype(at::kLong)), lse = at::empty({T}, of);
+  Tensor acc = at::zeros({2 * E + 1}, of);   // [0,E) sum of probabilities, [E,2E) counts, [2E] sum lse^2
+  float* a = acc.data_ptr<float>();
+  check(kmoe_route_topk_fwd(logits.data_ptr<float>(), (int)T, (int)E, (int)k, w.data_ptr<float>(),
+                            (long long*)idx.data_ptr<int64_t>(), lse.data_ptr<float>(), a, a + E, a + 2 * E,
+                            cur_stream()), "route_topk_fwd");
+  return {w, idx, lse, acc};
+}
+
+Tensor route_topk_bwd(const Tensor& logits, const Tensor& lse, const Tensor& idx, const Tensor& w, const OptT& dw,
+                      const Tensor& acc, const OptT& d_aux, double w_lb, double w_z) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t T = logits.size(0), E = logits.size(1), k = idx.size(1);
+  Tensor dl = at::empty_like(logits);
+  check(kmoe_route_topk_bwd(logits.data_ptr<float>(), lse.data_ptr<float>(), (const long long*)idx.data_ptr<int64_t>(),
+                            w.data_ptr<float>(), (const float*)ptr_or_null(dw), acc.data_ptr<float>() + E,
+                            (const float*)ptr_or_null(d_aux), (float)w_lb, (float)w_z, (int)T, (int)E, (int)k,
+                            dl.data_ptr<float>(), cur_stream()), "route_topk_bwd");
+  return dl;
+}
+
+// scores: contiguous fp32; (rows, S) when rows_inner == rows, or (outer, S, rows_inner) for column-wise rows
+std::vector<Tensor> seq_topk_fwd(const Tensor& scores, int64_t row_stride, int64_t col_stride, int64_t rows_inner,
+                                 int64_t outer_stride, int64_t rows, int64_t S, int64_t k, int64_t mode) {
+  c10::cuda::CUDAGuard guard(scores.device());
+  need_f32(scores, "scores");
+  TORCH_CHECK(scores.is_contiguous());
+  auto of = scores.options();
+  Tensor idx = at::empty({rows, k}, of.dtype(at::kLong)), w = at::empty({rows, k}, of), stat = at::empty({rows, 3}, of);
+  check(kmoe_seq_topk_fwd(scores.data_ptr<float>(), row_stride, col_stride, (int)rows_inner, outer_stride, (int)rows,
+                          (int)S, (int)k, (int)mode, (long long*)idx.data_ptr<int64_t>(), w.data_ptr<float>(),
+                          stat.data_ptr<float>(), cur_stream()), "seq_topk_fwd");
+  return {idx, w, stat};
+}
+
+Tensor seq_topk_bwd(const Tensor& scores, int64_t row_stride, int64_t col_stride, int64_t rows_inner,
+                    int64_t outer_stride, int64_t rows, int64_t S, int64_t k, int64_t mode, const Tensor& idx,
+                    const Tensor& w, const Tensor& dw, const Tensor& stat) {
+  c10::cuda::CUDAGuard guard(scores.device());
+  need_f32(dw, "dw");
+  TORCH_CHECK(dw.is_contiguous());
+  Tensor ds = at::empty_like(scores);
+  check(kmoe_seq_topk_bwd(scores.data_ptr<float>(), row_stride, col_stride, (int)rows_inner, outer_stride, (int)rows,
+                          (int)S, (int)k, (int)mode, (const long long*)idx.data_ptr<int64_t>(), w.data_ptr<float>(),
+                          dw.data_ptr<float>(), stat.data_ptr<float>(), ds.data_ptr<float>(), cur_stream()),
+        "seq_topk_bwd");
+  return ds;
+}
+
+// ------------------------------------------------------------- expert-parallel exchange
+void ep_dispatch(const Tensor& src, const Tensor& row_src, const OptT& assign_scale, const Tensor& offsets,
+                 const Tensor& counts, std::vector<int64_t> recv_ptrs, std::vector<int64_t> meta_ptrs, int64_t rank,
+                 int64_t world, int64_t E, int64_t cap, int64_t div) {
+  c10::cuda::CUDAGuard guard(src.device());
+  need_bf16(src, "src");
+  TORCH_CHECK(src.dim() == 2 && src.is_contiguous());
+  check(kmoe_ep_dispatch(src.data_ptr(), row_src.data_ptr<int>(), (const float*)ptr_or_null(assign_scale),
+                         offsets.data_ptr<int>(), counts.data_ptr<int>(), (const long long*)recv_ptrs.data(),
+                         (const long long*)meta_ptrs.data(), (int)rank, (int)world, (int)E, cap, (int)src.size(1),
+                         (int)div, (int)row_src.numel(), cur_stream()), "ep_dispatch");
+}
+
+std::vector<Tensor> ep_recv_plan(const Tensor& meta_in, int64_t n_local, int64_t world, int64_t max_rows) {
+  c10::cuda::CUDAGuard guard(meta_in.device());
+  auto o = meta_in.options().dtype(at::kInt);
+  Tensor slot_dst = at::empty({n_local * world}, o), offsets = at::empty({n_local + 1}, o);
+  Tensor tile_group = at::empty({max_rows / 128}, o), out_meta = at::empty({2}, o);
+  check(kmoe_ep_recv_plan(meta_in.data_ptr<int>(), (int)n_local, (int)world, (int)max_rows, slot_dst.data_ptr<int>(),
+                          offsets.data_ptr<int>(), tile_group.data_ptr<int>(), out_meta.data_ptr<int>(),
+                          cur_stream()), "ep_recv_plan");
+  return {slot_dst, offsets, tile_group, out_meta};
+}
+
+void ep_move(const Tensor& slots, Tensor packed, const Tensor& meta_in, const Tensor& slot_dst, const Tensor& offsets,
+             std::vector<int64_t> ret_ptrs, int64_t rank, int64_t n_local, int64_t world, int64_t cap, int64_t dir) {
+  c10::cuda::CUDAGuard guard(packed.device());
+  need_bf16(packed, "packed");
+  TORCH_CHECK(packed.dim() == 2 && packed.is_contiguous());
+  check(kmoe_ep_move(slots.data_ptr(), packed.data_ptr(), meta_in.data_ptr<int>(), slot_dst.data_ptr<int>(),
+                     offsets.data_ptr<int>(), (const long long*)ret_ptrs.data(), (int)rank, (int)n_local, (int)world,
+                     cap, (int)packed.size(1), (int)packed.size(0), (int)dir, cur_stream()), "ep_move");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(kmoe, m) {
@@ -345,4 +435,11 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("p2p_reduce_scatter", &p2p_reduce_scatter);
   m.def("p2p_adamw_allgather", &p2p_adamw_allgather);
   m.def("p2p_allgather", &p2p_allgather);
+  m.def("route_topk_fwd", &route_topk_fwd);
+  m.def("route_topk_bwd", &route_topk_bwd);
+  m.def("seq_topk_fwd", &seq_topk_fwd);
+  m.def("seq_topk_bwd", &seq_topk_bwd);
+  m.def("ep_dispatch", &ep_dispatch);
+  m.def("ep_recv_plan", &ep_recv_plan);
+  m.def("ep_move", &ep_move);
 }

@@ -201,3 +201,149 @@ extern "C" int kmoe_p2p_allgather(const long long* buf_ptrs, int rank, int world
   p2p_allgather_kernel<<<148 * 8, 256, 0, st>>>(make_ptrs(buf_ptrs, world), rank, world, off, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+// =====================================================================================
+// Expert-parallel token exchange over peer pointers.
+//
+// Source side: the local plan (moe_route.cu) lays the assignments of ALL experts out in a padded
+// expert-major order; `ep_dispatch` reads each assignment's row straight from the token matrix
+// (the permute) and stores it into the owning rank's receive buffer (the all-to-all) in one pass:
+//     recv[dest][(e_local * world + src) * cap + j]   <-  x[token of the j-th assignment to expert e]
+// together with the per-(expert, source) counts and the source's row offsets.  Expert side:
+// `ep_recv_plan` turns the counts into a padded expert-major layout, `ep_compact` gathers the slots
+// into it, the grouped GEMMs run on that, and `ep_return` stores every result row back into the
+// source rank's buffer at the position its local plan expects, so the weighted top-k un-permute
+// is the ordinary local combine.  No host synchronisation, no NCCL.
+namespace kmoe {
+
+// one warp per padded source row
+__global__ void ep_dispatch_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ row_src,
+                                   const float* __restrict__ assign_scale, const int* __restrict__ offsets,
+                                   const int* __restrict__ counts, PeerPtrs recv, PeerPtrs recv_meta, int rank,
+                                   int world, int E, int n_local, long long cap, int d, int div, int max_rows) {
+  const int vec = d / 8;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  // publish counts and offsets: meta[dest][(e_local * world + rank) * 2 + {0,1}]
+  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < E; e += gridDim.x * blockDim.x) {
+    int* m = reinterpret_cast<int*>(recv_meta.p[e / n_local]) + ((e % n_local) * world + rank) * 2;
+    m[0] = min(counts[e], (int)cap);      // rows beyond the slot capacity are dropped
+    m[1] = offsets[e];
+  }
+  const int live_rows = min(offsets[E], max_rows);
+  for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < live_rows; row += warps) {
+    const int a = row_src[row];
+    if (a < 0) continue;                       // padding rows are not sent
+    int e = 0;                                 // expert whose segment holds this row (E is small)
+    while (e + 1 < E && offsets[e + 1] <= row) ++e;
+    const int j = row - offsets[e];
+    if (j >= cap) continue;
+    const int dest = e / n_local;
+    __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(recv.p[dest]) +
+                          (((long long)(e % n_local) * world + rank) * cap + j) * d;
+    const uint4* srow = reinterpret_cast<const uint4*>(src + (size_t)(div > 0 ? a / div : row) * d);
+    const float s = assign_scale ? assign_scale[a] : 1.f;
+    for (int v = lane; v < vec; v += 32) {
+      uint4 r = srow[v];
+      if (assign_scale) {
+        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 f = __bfloat1622float2(p[i]);
+          p[i] = __floats2bfloat162_rn(f.x * s, f.y * s);
+        }
+      }
+      reinterpret_cast<uint4*>(drow)[v] = r;
+    }
+  }
+}
+
+// Single block.  meta_in: [n_local * world][2] = (count, source offset).  Outputs:
+//   slot_dst [n_local*world]   first row of each (expert, source) slot in the compacted layout
+//   offsets  [n_local+1]       padded expert offsets ; tile_group ; out_meta = {live tiles, live rows}
+__global__ void ep_recv_plan_kernel(const int* __restrict__ meta_in, int n_local, int world, int max_rows,
+                                    int* __restrict__ slot_dst, int* __restrict__ offsets,
+                                    int* __restrict__ tile_group, int* __restrict__ out_meta) {
+  if (threadIdx.x != 0) return;
+  int run = 0, tiles = 0;
+  for (int e = 0; e < n_local; ++e) {
+    offsets[e] = run;
+    int cnt = 0;
+    for (int s = 0; s < world; ++s) {
+      slot_dst[e * world + s] = run + cnt;
+      cnt += meta_in[(e * world + s) * 2];
+    }
+    const int nt = (cnt + 127) / 128;
+    for (int j = 0; j < nt && tiles + j < max_rows / 128; ++j) tile_group[tiles + j] = e;
+    tiles += nt;
+    run += nt * 128;
+  }
+  offsets[n_local] = run;
+  for (int j = tiles; j < max_rows / 128; ++j) tile_group[j] = 0;
+  out_meta[0] = min(tiles, max_rows / 128);
+  out_meta[1] = min(run, max_rows);
+}
+
+// dir = 0: compact  (slots of the local receive buffer -> expert-major padded rows, padding zeroed)
+// dir = 1: return   (expert-major rows -> the source rank's buffer at its own padded position)
+__global__ void ep_move_kernel(const __nv_bfloat16* __restrict__ slots, __nv_bfloat16* __restrict__ packed,
+                               const int* __restrict__ meta_in, const int* __restrict__ slot_dst,
+                               const int* __restrict__ offsets, PeerPtrs ret, int rank, int n_local, int world,
+                               long long cap, int d, int max_rows, int dir) {
+  const int vec = d / 8;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int live_rows = min(offsets[n_local], max_rows);
+  const int nslots = n_local * world;
+  for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < live_rows; row += warps) {
+    // find the slot containing this packed row
+    int sl = -1, j = 0;
+    for (int q = 0; q < nslots; ++q) {
+      const int b0 = slot_dst[q], c = meta_in[q * 2];
+      if (row >= b0 && row < b0 + c) { sl = q; j = row - b0; break; }
+    }
+    uint4* prow = reinterpret_cast<uint4*>(packed + (size_t)row * d);
+    if (dir == 0) {
+      if (sl < 0) {
+        for (int v = lane; v < vec; v += 32) prow[v] = make_uint4(0, 0, 0, 0);
+      } else {
+        const uint4* srow = reinterpret_cast<const uint4*>(slots + ((long long)sl * cap + j) * d);
+        for (int v = lane; v < vec; v += 32) prow[v] = srow[v];
+      }
+    } else if (sl >= 0) {
+      const int src_rank = sl % world;
+      const int src_off = meta_in[sl * 2 + 1];
+      uint4* drow = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(ret.p[src_rank]) +
+                                             (size_t)(src_off + j) * d);
+      for (int v = lane; v < vec; v += 32) drow[v] = prow[v];
+    }
+  }
+}
+
+}  // namespace kmoe
+
+extern "C" int kmoe_ep_dispatch(const void* src, const int* row_src, const float* assign_scale, const int* offsets,
+                                const int* counts, const long long* recv_ptrs, const long long* meta_ptrs, int rank,
+                                int world, int E, long long cap, int d, int div, int max_rows, cudaStream_t st) {
+  if (world > MAX_RANKS || d % 8 || E % world) return -1;
+  ep_dispatch_kernel<<<148 * 4, 256, 0, st>>>((const __nv_bfloat16*)src, row_src, assign_scale, offsets, counts,
+                                              make_ptrs(recv_ptrs, world), make_ptrs(meta_ptrs, world), rank, world, E,
+                                              E / world, cap, d, div, max_rows);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_ep_recv_plan(const int* meta_in, int n_local, int world, int max_rows, int* slot_dst,
+                                 int* offsets, int* tile_group, int* out_meta, cudaStream_t st) {
+  ep_recv_plan_kernel<<<1, 32, 0, st>>>(meta_in, n_local, world, max_rows, slot_dst, offsets, tile_group, out_meta);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_ep_move(const void* slots, void* packed, const int* meta_in, const int* slot_dst,
+                            const int* offsets, const long long* ret_ptrs, int rank, int n_local, int world,
+                            long long cap, int d, int max_rows, int dir, cudaStream_t st) {
+  if (world > MAX_RANKS || d % 8) return -1;
+  ep_move_kernel<<<148 * 4, 256, 0, st>>>((const __nv_bfloat16*)slots, (__nv_bfloat16*)packed, meta_in, slot_dst,
+                                          offsets, make_ptrs(ret_ptrs, world), rank, n_local, world, cap, d, max_rows,
+                                          dir);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

@@ -102,6 +102,43 @@ int kmoe_p2p_adamw_allgather(const long long* param_ptrs, const void* grad, floa
                              int step, const float* clip_coef, cudaStream_t st);
 int kmoe_p2p_allgather(const long long* buf_ptrs, int rank, int world, long long off, long long n, cudaStream_t st);
 
+// Expert-parallel token exchange.  E experts are split evenly over `world` ranks (expert e lives on rank
+// e / (E / world)).  The receive buffer of a rank holds (E / world) * world slots of `cap` rows; slot
+// (e_local, src) belongs to source rank src.  `meta` holds (count, source row offset) per slot.
+//   dispatch : rows of `src` selected by the local plan (row_src, offsets, counts over all E experts) are
+//              stored into the owners' receive buffers; div > 0: source row = assignment / div (token
+//              matrix), div == 0: source row = padded row; assign_scale (optional) multiplies each row.
+//   recv_plan: counts -> padded expert-major layout of the received rows (offsets, tile_group, out_meta).
+//   move     : dir 0 gathers the slots into that layout; dir 1 stores layout rows back into the source
+//              ranks' return buffers at the rows their own plan assigned.
+int kmoe_ep_dispatch(const void* src, const int* row_src, const float* assign_scale, const int* offsets,
+                     const int* counts, const long long* recv_ptrs, const long long* meta_ptrs, int rank, int world,
+                     int E, long long cap, int d, int div, int max_rows, cudaStream_t st);
+int kmoe_ep_recv_plan(const int* meta_in, int n_local, int world, int max_rows, int* slot_dst, int* offsets,
+                      int* tile_group, int* out_meta, cudaStream_t st);
+int kmoe_ep_move(const void* slots, void* packed, const int* meta_in, const int* slot_dst, const int* offsets,
+                 const long long* ret_ptrs, int rank, int n_local, int world, long long cap, int d, int max_rows,
+                 int dir, cudaStream_t st);
+
+// ---------------------------------------------------------------------------- routing decisions
+// Token choice: softmax over E experts -> top-k -> renormalise; also accumulates (atomically, into
+// zero-initialised buffers) sum_t p[t, e], the number of assignments per expert and sum_t lse_t^2.
+int kmoe_route_topk_fwd(const float* logits, int T, int E, int k, float* w, long long* idx, float* lse, float* p_sum,
+                        float* counts, float* z_sum, cudaStream_t st);
+int kmoe_route_topk_bwd(const float* logits, const float* lse, const long long* idx, const float* w, const float* dw,
+                        const float* counts, const float* d_aux, float w_lb, float w_z, int T, int E, int k,
+                        float* dlogits, cudaStream_t st);
+// Per-row top-k of a strided score matrix; row r starts at (r / rows_inner) * outer_stride +
+// (r % rows_inner) * row_stride and its S entries are col_stride apart.  mode 0: k largest scores,
+// indices ascending, softmax over the kept scores.  mode 1: softmax over the row, k largest
+// probabilities (descending), renormalised; stat (rows, 3) keeps (max, denominator, kept mass).
+int kmoe_seq_topk_fwd(const float* scores, long long row_stride, long long col_stride, int rows_inner,
+                      long long outer_stride, int rows, int S, int k, int mode, long long* idx, float* w, float* stat,
+                      cudaStream_t st);
+int kmoe_seq_topk_bwd(const float* scores, long long row_stride, long long col_stride, int rows_inner,
+                      long long outer_stride, int rows, int S, int k, int mode, const long long* idx, const float* w,
+                      const float* dw, const float* stat, float* dscores, cudaStream_t st);
+
 // ---------------------------------------------------------------------------- loss
 int kmoe_ce_fwd_bwd(void* logits, const long long* labels, float* loss_rows, const float* grad_scale, int R, int V,
                     long long ld, long long ignore_index, int write_grad, cudaStream_t st);

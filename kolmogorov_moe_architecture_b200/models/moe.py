@@ -33,6 +33,10 @@ class Router(nn.Module):
         super().__init__()
         self.d_model, self.n_experts, self.top_k = config.d_model, config.n_experts, config.moe_top_k
         self.balanced_routing = getattr(config, "moe_balanced_routing", False)
+        # (load-balance weight, z-loss weight) of the auxiliary loss computed with the routing pass
+        self.aux_weights = (getattr(config, "moe_load_balance_loss_weight", 0.0),
+                            getattr(config, "moe_router_z_loss_weight", 0.0))
+        self.last_aux, self.last_counts = None, None
         self.router = nn.Sequential(nn.Linear(config.d_model, 128, bias=False), nn.SiLU(),
                                     nn.Linear(128, config.n_experts, bias=False))
 
@@ -68,7 +72,9 @@ class Router(nn.Module):
             probs = F.softmax(logits, dim=-1).reshape(-1, self.n_experts)
             w, idx = self._balanced_topk_assignment(probs, self.top_k)
             return w.view(B, S, self.top_k), idx.view(B, S, self.top_k), logits
-        w, idx = ops.topk_softmax_route(logits, self.top_k)
+        # one pass: softmax -> top-k -> renormalise, plus the auxiliary-loss sums and expert counts
+        w_lb, w_z = self.aux_weights if self.training else (0.0, 0.0)
+        w, idx, self.last_aux, self.last_counts = ops.route_topk(logits, self.top_k, w_lb, w_z)
         return w, idx, logits
 
 
@@ -87,9 +93,7 @@ class ExpertChoiceRouter(nn.Module):
         S = hidden_states.shape[1]
         capacity = min(S, int(math.ceil(S * self.capacity_factor / self.n_experts)))
         logits = self.router(hidden_states)
-        probs = F.softmax(logits.transpose(1, 2), dim=-1)            # (B, E, S)
-        w, tok = torch.topk(probs, capacity, dim=-1)
-        w = w / (w.sum(dim=-1, keepdim=True) + 1e-9)
+        w, tok = ops.expert_choice_route(logits, capacity)            # (B, E, C) each
         return w, tok, logits, capacity
 
 
@@ -232,13 +236,15 @@ class MoELayer(nn.Module):
             keep = ops.capacity_keep_mask(idx_f, self.n_experts, cap)
             self.last_drop_count = (~keep).sum()
         out = self.grouped_experts(hidden_states.reshape(-1, d), idx_f, w_f, keep).view(B, S, d)
-        with torch.no_grad():
-            self.last_expert_counts = torch.bincount(idx_f.reshape(-1), minlength=self.n_experts)
-        if self.training:
-            self.aux_loss = ops.moe_aux_loss(logits, idx, self.n_experts,
-                                             self.load_balance_loss_weight, self.router_z_loss_weight)
-        else:
-            self.aux_loss = 0.0
+        if self.router.last_counts is not None:
+            self.last_expert_counts = self.router.last_counts.detach()
+            self.aux_loss = self.router.last_aux if self.training else 0.0
+            self.router.last_aux = self.router.last_counts = None
+        else:                                   # balanced assignment: separate passes
+            with torch.no_grad():
+                self.last_expert_counts = torch.bincount(idx_f.reshape(-1), minlength=self.n_experts)
+            self.aux_loss = ops.moe_aux_loss(logits, idx, self.n_experts, self.load_balance_loss_weight,
+                                             self.router_z_loss_weight) if self.training else 0.0
         return out
 
     def _forward_expert_choice(self, hidden_states: torch.Tensor) -> torch.Tensor:

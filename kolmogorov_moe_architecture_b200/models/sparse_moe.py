@@ -84,6 +84,9 @@ class ExpertParallelMoE(nn.Module):
         self.drop_tokens = getattr(config, "moe_drop_tokens", False)
         self.aux_loss = 0.0
         self.last_expert_counts = None
+        # "auto": peer-pointer kernels when available, else all_to_all; "p2p" / "all_to_all" force one
+        import os
+        self.transport = os.environ.get("KMOE_EP_TRANSPORT", "auto")
 
     def _compute_aux_loss(self, logits: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
         probs = F.softmax(logits, dim=-1)
@@ -110,6 +113,16 @@ class ExpertParallelMoE(nn.Module):
             keep = ops.capacity_keep_mask(idx, self.n_experts, cap)
         if self.world_size == 1:
             return self.local_experts(xf, idx, w, keep).reshape(B, S, d)
+        le = self.local_experts
+        if self.transport != "all_to_all" and le.moe_dtype == "bf16":
+            from ..parallel import ep_p2p
+            if ep_p2p.fused_available(xf, le.w1):
+                # permute + exchange fused over NVLink peer pointers; no host read, no NCCL
+                out = ep_p2p.expert_parallel_ffn_fused(xf, idx, w, le.w1, le.w2, le.w3, self.n_experts,
+                                                       self.process_group, keep=keep)
+                return out.reshape(B, S, d)
+            if self.transport == "p2p":
+                raise RuntimeError("expert-parallel transport 'p2p' needs CUDA bf16 tensors and peer access")
         from ..parallel.ep import expert_parallel_ffn
         out = expert_parallel_ffn(xf, idx, w, self.local_experts, self.n_experts,
                                   self.process_group, keep=keep)

@@ -89,8 +89,29 @@ def newton_schulz(matrix, iters=5):
     return eager.newton_schulz(matrix, iters)
 
 
+def route_topk(logits, k, w_lb=0.0, w_z=0.0):
+    """Router tail: (weights, indices, aux_loss, assignments per expert)."""
+    if _use_cuda(logits):
+        from . import cuda_ops
+        return cuda_ops.route_topk(logits, k, w_lb, w_z)
+    return eager.route_topk(logits, k, w_lb, w_z)
+
+
+def mod_route(logits, k):
+    if _use_cuda(logits):
+        from . import cuda_ops
+        return cuda_ops.mod_route(logits, k)
+    return eager.mod_route(logits, k)
+
+
+def expert_choice_route(logits, capacity):
+    if _use_cuda(logits):
+        from . import cuda_ops
+        return cuda_ops.expert_choice_route(logits, capacity)
+    return eager.expert_choice_route(logits, capacity)
+
+
 topk_softmax_route = eager.topk_softmax_route
 moe_aux_loss = eager.moe_aux_loss
 capacity_keep_mask = eager.capacity_keep_mask
-mod_route = eager.mod_route
 rope_tables = eager.rope_tables

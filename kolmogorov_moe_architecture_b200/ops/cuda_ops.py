@@ -335,6 +335,92 @@ def grouped_swiglu(x, w1, w2, w3, idx, weights, keep=None, moe_dtype="bf16"):
     return _GroupedSwiGLU.apply(x, w1.contiguous(), w2.contiguous(), w3.contiguous(), idx, weights, keep)
 
 
+# -------------------------------------------------------- routing decisions
+class _RouteTopK(torch.autograd.Function):
+    """softmax over experts -> top-k -> renormalise, with the auxiliary loss
+    ``w_lb * E * sum_e f_e P_e + w_z * mean(lse^2)`` from the same pass."""
+
+    @staticmethod
+    def forward(ctx, logits, k, w_lb, w_z):
+        shape = logits.shape
+        E = shape[-1]
+        lf = logits.reshape(-1, E).float().contiguous()
+        T = lf.shape[0]
+        w, idx, lse, acc = K.route_topk_fwd(lf, k)
+        _count()
+        aux = (w_lb * E / (float(T) * T * k)) * (acc[:E] * acc[E:2 * E]).sum() + (w_z / T) * acc[2 * E]
+        ctx.save_for_backward(lf, lse, idx, w, acc)
+        ctx.meta = (shape, logits.dtype, k, w_lb, w_z)
+        ctx.mark_non_differentiable(idx)
+        return w.view(*shape[:-1], k).to(logits.dtype), idx.view(*shape[:-1], k), aux, acc[E:2 * E]
+
+    @staticmethod
+    def backward(ctx, dw, _didx, daux, _dcounts):
+        lf, lse, idx, w, acc = ctx.saved_tensors
+        shape, dtype, k, w_lb, w_z = ctx.meta
+        dwf = dw.reshape(-1, k).float().contiguous() if dw is not None else None
+        da = daux.reshape(1).float().contiguous() if daux is not None else None
+        dl = K.route_topk_bwd(lf, lse, idx, w, dwf, acc, da, w_lb, w_z)
+        _count()
+        return dl.view(shape).to(dtype), None, None, None
+
+
+def route_topk(logits, k, w_lb=0.0, w_z=0.0):
+    """Returns (weights, indices, aux_loss, counts_per_expert)."""
+    E = logits.shape[-1]
+    if E > 128 or k > 8:
+        _fallback("route_topk", f"E={E} k={k}")
+        return eager.route_topk(logits, k, w_lb, w_z)
+    return _RouteTopK.apply(logits, k, float(w_lb), float(w_z))
+
+
+class _SeqTopK(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, scores, k, mode):
+        sf = scores.float().contiguous()
+        if mode == 0:                       # (B, S): rows are contiguous
+            B, S = sf.shape
+            geo = (S, 1, B, 0, B, S)
+        else:                               # (B, S, E): one row per (b, e), entries E apart
+            B, S, E = sf.shape
+            geo = (1, E, E, S * E, B * E, S)
+        idx, w, stat = K.seq_topk_fwd(sf, *geo, k, mode)
+        _count()
+        ctx.save_for_backward(sf, idx, w, stat)
+        ctx.meta = (geo, k, mode, scores.dtype)
+        ctx.mark_non_differentiable(idx)
+        if mode == 0:
+            return idx, w.to(scores.dtype)
+        return idx.view(B, E, k), w.view(B, E, k).to(scores.dtype)
+
+    @staticmethod
+    def backward(ctx, _didx, dw):
+        sf, idx, w, stat = ctx.saved_tensors
+        geo, k, mode, dtype = ctx.meta
+        ds = K.seq_topk_bwd(sf, *geo, k, mode, idx, w, dw.reshape(-1, k).float().contiguous(), stat)
+        _count()
+        return ds.to(dtype), None, None
+
+
+def mod_route(logits, k):
+    """(B, S) logits -> (ascending indices of the k largest, softmax over them, the same indices)."""
+    if logits.shape[-1] > 16384:
+        _fallback("mod_route", f"S={logits.shape[-1]}")
+        return eager.mod_route(logits, k)
+    idx, w = _SeqTopK.apply(logits, k, 0)
+    return idx, w, idx
+
+
+def expert_choice_route(logits, capacity):
+    """(B, S, E) logits -> (weights (B, E, C), token indices (B, E, C)): softmax over tokens,
+    the C most probable tokens per expert, renormalised."""
+    if logits.shape[1] > 16384:
+        _fallback("expert_choice_route", f"S={logits.shape[1]}")
+        return eager.expert_choice_route(logits, capacity)
+    idx, w = _SeqTopK.apply(logits, capacity, 1)
+    return w, idx
+
+
 # -------------------------------------------------------- LM head + MTP loss
 class _MTPLoss(torch.autograd.Function):
     """Per head: logits chunk = H W^T (tcgen05 GEMM) -> CE kernel writes d logits in place ->

@@ -133,6 +133,22 @@ def moe_aux_loss(logits: torch.Tensor, idx: torch.Tensor, n_experts: int,
     return w_lb * lb + w_z * z
 
 
+def route_topk(logits: torch.Tensor, top_k: int, w_lb: float = 0.0, w_z: float = 0.0):
+    """Router tail in one call: (weights, indices, aux_loss, counts_per_expert)."""
+    w, idx = topk_softmax_route(logits, top_k)
+    E = logits.shape[-1]
+    aux = moe_aux_loss(logits.float(), idx, E, w_lb, w_z)
+    counts = torch.bincount(idx.reshape(-1), minlength=E).float()
+    return w, idx, aux, counts
+
+
+def expert_choice_route(logits: torch.Tensor, capacity: int):
+    """(B, S, E) -> softmax over tokens, per-expert top-C, renormalised (reference: moe.py:494-530)."""
+    probs = F.softmax(logits.transpose(1, 2), dim=-1)
+    w, tok = torch.topk(probs, capacity, dim=-1)
+    return w / (w.sum(dim=-1, keepdim=True) + 1e-9), tok
+
+
 def capacity_keep_mask(idx: torch.Tensor, n_experts: int, capacity: int) -> torch.Tensor:
     """Drop policy for token-choice with capacity: for each expert keep the first
     ``capacity`` assignments in (token, slot) order; later ones are dropped and

@@ -1,0 +1,213 @@
+"""Expert-parallel SwiGLU FFN whose token exchange runs over NVLink peer pointers.
+
+One autograd function covers the whole layer on both sides of the exchange:
+
+    source rank                                      expert rank
+    -----------                                      -----------
+    plan (stable counting sort over all E experts)
+    dispatch: token rows -> owner's receive slots    (permute and all-to-all in one kernel)
+    ------------------------ flag barrier ------------------------
+                                                     recv_plan: slot counts -> padded expert-major layout
+                                                     compact slots -> Xp
+                                                     grouped GEMM 1 (+SwiGLU epilogue), grouped GEMM 2
+                                                     return: Y rows -> source's buffer, at the row its
+                                                             own plan gave the assignment
+    ------------------------ flag barrier ------------------------
+    weighted top-k combine (local)
+
+Backward is the same pipeline with ``w * dout`` rows travelling out, the dgrad GEMMs on the
+expert rank, and ``dXp`` rows travelling back; weight gradients never leave the expert rank.
+Counts, offsets and tile tables stay on the device - there is no host read and no NCCL call
+in either direction (the all-to-all transport in :mod:`.ep` needs one host read per layer).
+
+Buffers are symmetric-memory allocations sized for the worst case (every token of every rank
+routed to one rank) and shared by all layers of a model: a layer's receive buffer is free
+again once the rank has compacted it, which the second barrier of the layer orders before any
+peer's next dispatch.
+
+The kernels are in ``csrc/comm.cu`` (``ep_dispatch``, ``ep_recv_plan``, ``ep_move``).  The
+reference exchanges rows with ``all_to_all_single`` and a host-side loop
+(moe_arch/model/sparse_moe.py:540-603).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .p2p import _group_name
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class EPBuffers:
+    """Symmetric receive / return / meta / flag buffers for one (tokens, top_k, d_model, E) shape."""
+
+    def __init__(self, T: int, k: int, d: int, E: int, dtype, device, group=None, cap: Optional[int] = None,
+                 barrier_timeout_s: float = 30.0):
+        import torch.distributed._symmetric_memory as symm
+        from ..ops import cuda_ops
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        assert E % self.world == 0
+        self.T, self.k, self.d, self.E = T, k, d, E
+        self.n_local = E // self.world
+        # top-k picks distinct experts, so one source sends an expert at most T rows
+        self.cap = int(cap) if cap is not None else T
+        n_slots = self.n_local * self.world
+        self.max_rows_src = _round_up(T * k + E * 127, 128)
+        self.max_rows_exp = _round_up(min(n_slots * self.cap, self.world * T * k) + self.n_local * 127, 128)
+        name = _group_name(group)
+        if hasattr(symm, "enable_symm_mem_for_group"):
+            try:
+                symm.enable_symm_mem_for_group(name)
+            except Exception:
+                pass
+        self.recv = symm.empty((n_slots * self.cap, d), dtype=dtype, device=device)
+        self.ret = symm.empty((self.max_rows_src, d), dtype=dtype, device=device)
+        self.meta = symm.empty(n_slots * 2, dtype=torch.int32, device=device)
+        self.flags = symm.empty(64, dtype=torch.int32, device=device)
+        self.meta.zero_()
+        self.flags.zero_()
+        torch.cuda.synchronize(device)
+        hs = [symm.rendezvous(t, name) for t in (self.recv, self.ret, self.meta, self.flags)]
+        self._h = hs
+        self.recv_ptrs = [int(p) for p in hs[0].buffer_ptrs]
+        self.ret_ptrs = [int(p) for p in hs[1].buffer_ptrs]
+        self.meta_ptrs = [int(p) for p in hs[2].buffer_ptrs]
+        self.flag_ptrs = [int(p) for p in hs[3].buffer_ptrs]
+        self.epoch = 0
+        self.timeout_s = barrier_timeout_s
+        self.status = cuda_ops.status_tensor(device)
+        dist.barrier(group=group)
+
+    def barrier(self) -> None:
+        from ..ops import cuda_ops
+        self.epoch += 1
+        torch.ops.kmoe.p2p_barrier(self.flag_ptrs, self.rank, self.world, self.epoch, self.timeout_s, self.status)
+        cuda_ops._count()
+
+    def bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.recv, self.ret, self.meta, self.flags))
+
+
+_CACHE: Dict[Tuple, EPBuffers] = {}
+
+
+def get_buffers(T: int, k: int, d: int, E: int, dtype, device, group=None) -> EPBuffers:
+    key = (T, k, d, E, dtype, str(device), _group_name(group))
+    buf = _CACHE.get(key)
+    if buf is None:
+        buf = EPBuffers(T, k, d, E, dtype, device, group)
+        _CACHE[key] = buf
+    return buf
+
+
+def release_buffers() -> None:
+    """Drop the cached symmetric buffers (all ranks of the group must call it together)."""
+    _CACHE.clear()
+
+
+class _EPFusedFFN(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w1, w2, w3, idx, weights, keep, buf: EPBuffers):
+        from ..ops import cuda_ops as C
+        K = torch.ops.kmoe
+        T, d = x.shape
+        nl, _, f = w1.shape
+        k = idx.shape[1]
+        E, ws = buf.E, buf.world
+        idx_flat = idx.reshape(-1).contiguous()
+        pos, row_src, counts, offsets, _tg, _meta = K.moe_plan(
+            idx_flat, keep.reshape(-1) if keep is not None else None, E, 0)
+        assert row_src.numel() <= buf.max_rows_src
+        xc = x.contiguous()
+        K.ep_dispatch(xc, row_src, None, offsets, counts, buf.recv_ptrs, buf.meta_ptrs, buf.rank, ws, E, buf.cap, k)
+        buf.barrier()
+        R = buf.max_rows_exp
+        meta_in = buf.meta.clone()
+        slot_dst, offs_l, tile_group, meta_l = K.ep_recv_plan(meta_in, nl, ws, R)
+        Xp = torch.empty(R, d, dtype=x.dtype, device=x.device)
+        K.ep_move(buf.recv, Xp, meta_in, slot_dst, offs_l, buf.ret_ptrs, buf.rank, nl, ws, buf.cap, 0)
+        H = torch.empty(R, f, dtype=x.dtype, device=x.device)
+        G, U = torch.empty_like(H), torch.empty_like(H)
+        nmt = meta_l[0:1]
+        C.gemm(Xp, w1, H, B2=w2, G=G, U=U, mode=C.GROUPED_M, epi=C.EPI_SWIGLU, M=R, N=f, Kd=d, groups=nl,
+               b_major=C.MAJ_MN, lda=d, ldb=f, ldc=f, b_gs=d * f, tile_group=tile_group, num_m_tiles=nmt)
+        Y = torch.empty(R, d, dtype=x.dtype, device=x.device)
+        C.gemm(H, w3, Y, mode=C.GROUPED_M, M=R, N=d, Kd=f, groups=nl, b_major=C.MAJ_MN, lda=f, ldb=d, ldc=d,
+               b_gs=f * d, tile_group=tile_group, num_m_tiles=nmt)
+        K.ep_move(buf.recv, Y, meta_in, slot_dst, offs_l, buf.ret_ptrs, buf.rank, nl, ws, buf.cap, 1)
+        buf.barrier()
+        wf = weights.reshape(-1).float().contiguous()
+        out = K.moe_combine(buf.ret, pos, wf, T, k)
+        # the return buffer is reused by the next layer; keep this layer's rows for d(loss)/d(weights)
+        Yret = buf.ret[: row_src.numel()].clone() if ctx.needs_input_grad[5] else None
+        C._count(7)
+        ctx.save_for_backward(Xp, G, U, w1, w2, w3, wf, pos, row_src, counts, offsets, meta_in, slot_dst, offs_l,
+                              tile_group, meta_l, Yret if Yret is not None else torch.empty(0, device=x.device))
+        ctx.buf = buf
+        ctx.dims = (T, d, nl, f, k, R)
+        ctx.wdtype = weights.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from ..ops import cuda_ops as C
+        K = torch.ops.kmoe
+        (Xp, G, U, w1, w2, w3, wf, pos, row_src, counts, offsets, meta_in, slot_dst, offs_l, tile_group, meta_l,
+         Yret) = ctx.saved_tensors
+        buf = ctx.buf
+        T, d, nl, f, k, R = ctx.dims
+        E, ws = buf.E, buf.world
+        dout = dout.contiguous()
+        nmt = meta_l[0:1]
+        # w * dout rows travel to the expert ranks (permute, scale and exchange in one kernel)
+        K.ep_dispatch(dout, row_src, wf, offsets, counts, buf.recv_ptrs, buf.meta_ptrs, buf.rank, ws, E, buf.cap, k)
+        buf.barrier()
+        dYp = torch.empty(R, d, dtype=dout.dtype, device=dout.device)
+        K.ep_move(buf.recv, dYp, meta_in, slot_dst, offs_l, buf.ret_ptrs, buf.rank, nl, ws, buf.cap, 0)
+        dH = torch.empty(R, f, dtype=dout.dtype, device=dout.device)
+        C.gemm(dYp, w3, dH, mode=C.GROUPED_M, M=R, N=f, Kd=d, groups=nl, lda=d, ldb=d, ldc=f, b_gs=f * d,
+               tile_group=tile_group, num_m_tiles=nmt)
+        dG, dU = K.swiglu_bwd(G, U, dH)
+        dXp = torch.empty(R, d, dtype=dout.dtype, device=dout.device)
+        C.gemm(dG, w1, dXp, mode=C.GROUPED_M, M=R, N=d, Kd=f, groups=nl, lda=f, ldb=f, ldc=d, b_gs=d * f,
+               tile_group=tile_group, num_m_tiles=nmt)
+        C.gemm(dU, w2, dXp, D=dXp, beta=1.0, mode=C.GROUPED_M, M=R, N=d, Kd=f, groups=nl, lda=f, ldb=f,
+               ldc=d, ldd=d, b_gs=d * f, tile_group=tile_group, num_m_tiles=nmt)
+        K.ep_move(buf.recv, dXp, meta_in, slot_dst, offs_l, buf.ret_ptrs, buf.rank, nl, ws, buf.cap, 1)
+        buf.barrier()
+        dx = K.moe_combine(buf.ret, pos, None, T, k)
+        dwts = None
+        if Yret.numel():
+            dwts = K.moe_combine_dw(Yret, dout, pos, k).view(T, k).to(ctx.wdtype)
+        kb = offs_l[:nl].contiguous()
+        kl = (offs_l[1:] - offs_l[:nl]).contiguous()
+        H = K.swiglu_fwd(G, U)
+        dw1, dw2, dw3 = torch.empty_like(w1), torch.empty_like(w2), torch.empty_like(w3)
+        common = dict(mode=C.BATCHED, groups=nl, a_major=C.MAJ_MN, b_major=C.MAJ_MN, Kd=R, k_begin=kb, k_len=kl)
+        C.gemm(Xp, dG, dw1, M=d, N=f, lda=d, ldb=f, ldc=f, c_gs=d * f, **common)
+        C.gemm(Xp, dU, dw2, M=d, N=f, lda=d, ldb=f, ldc=f, c_gs=d * f, **common)
+        C.gemm(H, dYp, dw3, M=f, N=d, lda=f, ldb=d, ldc=d, c_gs=f * d, **common)
+        C._count(8)
+        return dx, dw1, dw2, dw3, None, dwts, None, None
+
+
+def fused_available(x: torch.Tensor, w1: torch.Tensor) -> bool:
+    from .p2p import p2p_available
+    d, f = w1.shape[1], w1.shape[2]
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w1.dtype == torch.bfloat16 and d % 64 == 0 and f % 64 == 0
+            and p2p_available(x.device))
+
+
+def expert_parallel_ffn_fused(x, idx, weights, w1, w2, w3, n_experts: int, group=None, keep=None):
+    """x (T, d) bf16; idx, weights (T, k) with global expert ids; w* are this rank's expert weights
+    (E / world, d, f) / (E / world, f, d).  Every rank of the group must call it with the same T."""
+    T, d = x.shape
+    buf = get_buffers(T, idx.shape[1], d, n_experts, x.dtype, x.device, group)
+    return _EPFusedFFN.apply(x, w1.contiguous(), w2.contiguous(), w3.contiguous(), idx, weights, keep, buf)

@@ -213,3 +213,52 @@ def test_flash_attention_fwd_bwd(B, S, H, Hkv, D):
     assert _rel(q.grad, qr.grad) < 3e-2, "dq"
     assert _rel(k.grad, kr.grad) < 3e-2, "dk"
     assert _rel(v.grad, vr.grad) < 3e-2, "dv"
+
+
+@pytest.mark.parametrize("T,E,k", [(777, 16, 2), (64, 8, 1), (1500, 64, 4)])
+def test_route_topk_fwd_bwd(T, E, k):
+    ops, c, eager = _mods()
+    torch.manual_seed(3)
+    logits = (torch.randn(T, E, device="cuda") * 2).requires_grad_(True)
+    w, idx, aux, counts = ops.route_topk(logits, k, 0.01, 0.001)
+    gw = torch.randn(T, k, device="cuda")
+    (w * gw).sum().add(aux * 3.0).backward()
+    lr = logits.detach().clone().requires_grad_(True)
+    wr, idxr, auxr, countsr = eager.route_topk(lr, k, 0.01, 0.001)
+    (wr * gw).sum().add(auxr * 3.0).backward()
+    assert torch.equal(idx, idxr)
+    assert torch.allclose(counts, countsr)
+    assert torch.allclose(w, wr, atol=1e-5) and torch.allclose(aux, auxr, rtol=1e-4, atol=1e-6)
+    assert torch.allclose(logits.grad, lr.grad, atol=2e-5, rtol=1e-3)
+
+
+@pytest.mark.parametrize("B,S,k", [(3, 2048, 1536), (2, 100, 37), (1, 5, 5)])
+def test_mod_route_fwd_bwd(B, S, k):
+    ops, c, eager = _mods()
+    torch.manual_seed(4)
+    logits = torch.randn(B, S, device="cuda").requires_grad_(True)
+    sidx, w, _ = ops.mod_route(logits, k)
+    gw = torch.randn(B, k, device="cuda")
+    (w * gw).sum().backward()
+    lr = logits.detach().clone().requires_grad_(True)
+    sidxr, wr, _ = eager.mod_route(lr, k)
+    (wr * gw).sum().backward()
+    assert torch.equal(sidx, sidxr)
+    assert torch.allclose(w, wr, atol=1e-6, rtol=1e-4)
+    assert torch.allclose(logits.grad, lr.grad, atol=1e-6, rtol=1e-3)
+
+
+@pytest.mark.parametrize("B,S,E,C", [(2, 2048, 16, 160), (3, 50, 4, 13)])
+def test_expert_choice_route_fwd_bwd(B, S, E, C):
+    ops, c, eager = _mods()
+    torch.manual_seed(5)
+    logits = torch.randn(B, S, E, device="cuda").requires_grad_(True)
+    w, tok = ops.expert_choice_route(logits, C)
+    gw = torch.randn(B, E, C, device="cuda")
+    (w * gw).sum().backward()
+    lr = logits.detach().clone().requires_grad_(True)
+    wr, tokr = eager.expert_choice_route(lr, C)
+    (wr * gw).sum().backward()
+    assert torch.equal(tok, tokr)
+    assert torch.allclose(w, wr, atol=1e-6, rtol=1e-4)
+    assert torch.allclose(logits.grad, lr.grad, atol=1e-7, rtol=2e-3)
