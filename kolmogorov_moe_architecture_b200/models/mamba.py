@@ -130,23 +130,18 @@ class RoutingMamba(nn.Module):
 
     def _route(self, hidden_states: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         logits = self.router(hidden_states)
-        w, idx = ops.topk_softmax_route(logits, self.top_k)
+        w_lb, w_z = (self.load_balance_loss_weight, self.router_z_loss_weight) if self.training else (0.0, 0.0)
+        w, idx, self._aux, self._counts = ops.route_topk(logits, self.top_k, w_lb, w_z)
         return w, idx, logits
 
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
         w, idx, logits = self._route(hidden_states)
         mix = torch.zeros(*hidden_states.shape[:2], self.n_experts, dtype=w.dtype, device=w.device)
         mix = mix.scatter_add(-1, idx, w)                       # (B, S, E), differentiable in w
-        used = torch.zeros(self.n_experts, dtype=torch.bool, device=w.device)
-        used[idx.reshape(-1)] = True
-        used = used.tolist()                                    # one host read for all experts
+        used = (self._counts > 0).tolist()                      # one host read for all experts
         out = torch.zeros_like(hidden_states)
         for e, expert in enumerate(self.experts):
             if used[e]:
                 out = out + mix[..., e:e + 1].to(hidden_states.dtype) * expert(hidden_states)
-        if self.training:
-            self.aux_loss = ops.moe_aux_loss(logits, idx, self.n_experts,
-                                             self.load_balance_loss_weight, self.router_z_loss_weight)
-        else:
-            self.aux_loss = 0.0
+        self.aux_loss = self._aux if self.training else 0.0
         return out
