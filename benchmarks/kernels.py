@@ -115,6 +115,42 @@ def bench_moe(rows):
     c.check_status()
 
 
+def bench_mxfp8(rows):
+    """Block-scaled fp8 GEMM alone (operands already quantised), the quantisers, and the expert FFN on it.
+    Fractions are against the bf16 cuBLAS peak, so 1.0 means "as fast as a perfect bf16 GEMM"."""
+    from kolmogorov_moe_architecture_b200 import ops
+    from kolmogorov_moe_architecture_b200.ops import cuda_ops as c, eager, mxfp8 as mx
+    for (M, N, K) in [(8192, 8192, 2048), (12288, 2816, 2048), (8192, 8192, 8192)]:
+        a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+        aq, sa = mx.quant_rows(a)
+        bq, sb = mx.quant_rows(b)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        report(rows, f"gemm mxfp8 {M}x{N}x{K}", timeit(lambda: mx.gemm_mx(aq, sa, bq, sb, out, M=M, N=N, K=K)),
+               2.0 * M * N * K)
+        report(rows, f"quant_rows {M}x{K}", timeit(lambda: mx.quant_rows(a)), None, M * K * 3.0)
+        report(rows, f"quant_cols {M}x{K}", timeit(lambda: mx.quant_cols(a)), None, M * K * 3.0)
+    T, d, f, E, k = 6144, 2048, 2816, 16, 2
+    x = (torch.randn(T, d, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    w1 = (torch.randn(E, d, f, device="cuda") * 0.02).to(torch.bfloat16).requires_grad_(True)
+    w2 = (torch.randn(E, d, f, device="cuda") * 0.02).to(torch.bfloat16).requires_grad_(True)
+    w3 = (torch.randn(E, f, d, device="cuda") * 0.02).to(torch.bfloat16).requires_grad_(True)
+    logits = torch.randn(T, E, device="cuda") + torch.log(1.0 / torch.arange(1, E + 1, device="cuda").float())
+    wts, idx = eager.topk_softmax_route(logits, k)
+    go = torch.randn(T, d, device="cuda").to(torch.bfloat16)
+    fl_f = 2.0 * T * k * 3 * d * f
+    for dt in ("mxfp8", "bf16"):
+        def fwd():
+            return ops.grouped_swiglu(x, w1, w2, w3, idx, wts, None, dt)
+
+        def fwdbwd():
+            fwd().backward(go)
+            x.grad = w1.grad = w2.grad = w3.grad = None
+        report(rows, f"moe_ffn {dt} fwd (5B layer)", timeit(fwd), fl_f)
+        report(rows, f"moe_ffn {dt} fwd+bwd (5B layer)", timeit(fwdbwd), 3 * fl_f)
+    c.check_status()
+
+
 def bench_attn(rows):
     from kolmogorov_moe_architecture_b200 import ops
     from kolmogorov_moe_architecture_b200.ops import cuda_ops as c
@@ -204,11 +240,11 @@ def bench_norm(rows):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--which", default="gemm,moe,attn,scan,ce,norm")
+    ap.add_argument("--which", default="gemm,moe,mxfp8,attn,scan,ce,norm")
     ap.add_argument("--out", default=None)
     a = ap.parse_args()
     rows = []
-    table = {"gemm": bench_gemm, "moe": bench_moe, "attn": bench_attn, "scan": bench_scan, "ce": bench_ce,
+    table = {"gemm": bench_gemm, "moe": bench_moe, "mxfp8": bench_mxfp8, "attn": bench_attn, "scan": bench_scan, "ce": bench_ce,
              "norm": bench_norm}
     for k in a.which.split(","):
         table[k](rows)

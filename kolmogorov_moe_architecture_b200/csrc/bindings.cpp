@@ -321,6 +321,66 @@ void p2p_allgather(std::vector<int64_t> buf_ptrs, int64_t rank, int64_t world, i
         "p2p_allgather");
 }
 
+// ------------------------------------------------------------- MXFP8
+// x: (..., C) bf16 with collapsing leading dims -> (q e4m3 same shape, scale chunks uint8)
+std::vector<Tensor> mx_quant_rows(const Tensor& x, const OptT& x2, const OptT& live_rows) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_bf16(x, "x");
+  TORCH_CHECK(x.dim() >= 2);
+  const long long ld = row_stride(x);
+  const int64_t C = x.size(-1), rows = x.numel() / C;
+  if (x2.has_value() && x2->defined()) {
+    need_bf16(*x2, "x2");
+    TORCH_CHECK(x2->sizes() == x.sizes() && row_stride(*x2) == ld, "x2 must match x");
+  }
+  Tensor q = at::empty(x.sizes(), x.options().dtype(at::kFloat8_e4m3fn));
+  Tensor sf = at::zeros({kmoe_mx_sf_bytes(rows, C)}, x.options().dtype(at::kByte));
+  check(kmoe_mx_quant_rows(x.data_ptr(), ptr_or_null(x2), rows, (int)C, ld, q.data_ptr(), sf.data_ptr(),
+                           (const int*)ptr_or_null(live_rows), cur_stream()), "mx_quant_rows");
+  return {q, sf};
+}
+
+// x: (R, C) or (G, R, C) bf16 contiguous -> (q e4m3 (G, C, R), scale chunks)
+std::vector<Tensor> mx_quant_cols(const Tensor& x, const OptT& live_rows) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_bf16(x, "x");
+  TORCH_CHECK(x.is_contiguous() && (x.dim() == 2 || x.dim() == 3));
+  const int64_t G = x.dim() == 3 ? x.size(0) : 1, R = x.size(-2), C = x.size(-1);
+  Tensor q = x.dim() == 3 ? at::empty({G, C, R}, x.options().dtype(at::kFloat8_e4m3fn))
+                          : at::empty({C, R}, x.options().dtype(at::kFloat8_e4m3fn));
+  Tensor sf = at::zeros({kmoe_mx_sf_bytes(G * C, R)}, x.options().dtype(at::kByte));
+  check(kmoe_mx_quant_cols(x.data_ptr(), (int)G, R, (int)C, C, R * C, q.data_ptr(), sf.data_ptr(),
+                           (const int*)ptr_or_null(live_rows), cur_stream()), "mx_quant_cols");
+  return {q, sf};
+}
+
+void gemm_mxfp8(const Tensor& A, const Tensor& sfa, const Tensor& B, const Tensor& sfb, Tensor C, const OptT& D,
+                int64_t mode, int64_t M, int64_t N, int64_t K, int64_t groups, bool a_grouped, bool b_grouped,
+                int64_t ldc, int64_t ldd, int64_t c_gs, const OptT& tile_group, const OptT& num_m_tiles,
+                const OptT& k_begin, const OptT& k_len, double alpha, double beta, Tensor status) {
+  c10::cuda::CUDAGuard guard(A.device());
+  TORCH_CHECK(A.scalar_type() == at::kFloat8_e4m3fn && B.scalar_type() == at::kFloat8_e4m3fn && A.is_contiguous() &&
+              B.is_contiguous(), "A and B must be contiguous float8_e4m3fn tensors");
+  TORCH_CHECK(sfa.scalar_type() == at::kByte && sfb.scalar_type() == at::kByte);
+  TORCH_CHECK(sfa.numel() >= kmoe_mx_sf_bytes((a_grouped ? groups : 1) * M, K), "A scale buffer too small");
+  TORCH_CHECK(sfb.numel() >= kmoe_mx_sf_bytes((b_grouped ? groups : 1) * N, K), "B scale buffer too small");
+  KmoeMxGemmDesc d{};
+  d.A = A.data_ptr(); d.B = B.data_ptr(); d.sfa = sfa.data_ptr(); d.sfb = sfb.data_ptr();
+  d.C = C.data_ptr(); d.D = ptr_or_null(D);
+  d.mode = (int)mode; d.M = (int)M; d.N = (int)N; d.K = (int)K; d.groups = (int)groups;
+  d.a_grouped = a_grouped; d.b_grouped = b_grouped;
+  d.ldc = ldc; d.ldd = ldd; d.c_gstride = c_gs;
+  d.tile_group = (const int*)ptr_or_null(tile_group); d.num_m_tiles = (const int*)ptr_or_null(num_m_tiles);
+  d.k_begin = (const int*)ptr_or_null(k_begin); d.k_len = (const int*)ptr_or_null(k_len);
+  d.out_f32 = C.scalar_type() == at::kFloat ? 1 : 0;
+  TORCH_CHECK(d.out_f32 || C.scalar_type() == at::kBFloat16, "C must be bf16 or fp32");
+  if (D.has_value() && D->defined()) TORCH_CHECK(D->scalar_type() == C.scalar_type(), "D must have C's dtype");
+  d.alpha = (float)alpha; d.beta = (float)beta;
+  d.status = status.data_ptr<int>();
+  d.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  check(kmoe_gemm_mxfp8(&d, cur_stream()), "gemm_mxfp8");
+}
+
 // ------------------------------------------------------------- routing decisions
 std::vector<Tensor> route_topk_fwd(const Tensor& logits, int64_t k) {
   c10::cuda::CUDAGuard guard(logits.device());
@@ -435,6 +495,9 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("p2p_reduce_scatter", &p2p_reduce_scatter);
   m.def("p2p_adamw_allgather", &p2p_adamw_allgather);
   m.def("p2p_allgather", &p2p_allgather);
+  m.def("mx_quant_rows", &mx_quant_rows);
+  m.def("mx_quant_cols", &mx_quant_cols);
+  m.def("gemm_mxfp8", &gemm_mxfp8);
   m.def("route_topk_fwd", &route_topk_fwd);
   m.def("route_topk_bwd", &route_topk_bwd);
   m.def("seq_topk_fwd", &seq_topk_fwd);

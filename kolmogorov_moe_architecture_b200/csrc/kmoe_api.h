@@ -47,6 +47,42 @@ typedef struct KmoeGemmDesc {
 int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream);
 void kmoe_gemm_clear_tensormap_cache(void);
 
+// ------------------------------------------------------------ MXFP8 (e4m3 + e8m0 1x32 block scales)
+// Scale factors live in 512-byte chunks, one per (128 operand rows, 128 reduction elements):
+//   chunk = (row / 128) * (K / 128) + k / 128,  byte = (row % 32) * 16 + ((row % 128) / 32) * 4 + (k % 128) / 32
+// which is the arrangement the block-scaled tensor-core instruction expects in tensor memory.
+long long kmoe_mx_sf_bytes(long long rows, long long K);
+// x (rows, C) bf16 -> q (rows, C) e4m3, reduction along C (C % 128 == 0).  x2 != NULL: quantise silu(x) * x2.
+// live_rows (device, optional): only the first *live_rows rows are processed.
+int kmoe_mx_quant_rows(const void* x, const void* x2, long long rows, int C, long long ld, void* q, void* sf,
+                       const int* live_rows, cudaStream_t st);
+// x (groups, R, C) bf16 -> q (groups, C, R) e4m3, reduction along R (R % 128 == 0); scale rows are (group, c).
+int kmoe_mx_quant_cols(const void* x, int groups, long long R, int C, long long ld, long long g_stride, void* q,
+                       void* sf, const int* live_rows, cudaStream_t st);
+
+typedef struct KmoeMxGemmDesc {
+  const void* A;        // e4m3 [M, K] (or [groups, M, K] when a_grouped), K contiguous
+  const void* B;        // e4m3 [N, K] (or [groups, N, K] when b_grouped)
+  const void* sfa;      // scale chunks of A / B in the arrangement above
+  const void* sfb;
+  void* C;              // bf16 or fp32 [M, N] (ldc)
+  const void* D;        // optional addend (C's type, ldd)
+  int mode;             // KMOE_GEMM_DENSE / GROUPED_M / BATCHED
+  int M, N, K, groups;  // K % 128 == 0
+  int a_grouped, b_grouped;
+  long long ldc, ldd, c_gstride;
+  const int* tile_group;
+  const int* num_m_tiles;
+  const int* k_begin;   // BATCHED: optional ragged reduction range per group (multiples of 128)
+  const int* k_len;
+  int out_f32;
+  float alpha, beta;
+  int* status;
+  int num_sms;
+} KmoeMxGemmDesc;
+int kmoe_gemm_mxfp8(const KmoeMxGemmDesc* d, cudaStream_t stream);
+void kmoe_mxfp8_clear_tensormap_cache(void);
+
 // ------------------------------------------------------------ row kernels (bf16 data, fp32 math)
 int kmoe_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int d, float eps, cudaStream_t st);
 int kmoe_rmsnorm_bwd_num_partials(int rows);

@@ -242,6 +242,9 @@ class ShardedDataParallel:
             self.flat_grad[lo:hi].mul_(coef.to(self.flat_grad.dtype))
 
     def finish(self) -> None:
+        # parameters are rewritten through raw pointers below: drop derived copies (quantised weights)
+        from ..ops import mxfp8
+        mxfp8.invalidate_weight_cache()
         a0 = self.rank * self.seg
         ptrs = self.p2p.param_ptrs if self.transport == "p2p" else [self.flat_param.data_ptr()]
         prank = self.rank if self.transport == "p2p" else 0
