@@ -1,6 +1,6 @@
 """Small single-kernel workloads for Nsight Compute captures.
 
-    python benchmarks/ncu_cases.py --case gemm|moe|attn|scan|adamw|ce [--launches 4]
+    python benchmarks/ncu_cases.py --case gemm|moe|attn|scan|adamw|ce|mxfp8 [--launches 4]
 
 Each case holds well under 2 GB on the device, uses operands larger than L2 where the kernel is
 bandwidth-sensitive, and launches the kernel of interest a handful of times so that
@@ -64,6 +64,14 @@ def main():
         gs = torch.full((1,), 1.0 / R, device="cuda")
         for _ in range(n):
             torch.ops.kmoe.ce_fwd_bwd(logits, labels, gs, -100, True)
+    elif a.case == "mxfp8":
+        from kolmogorov_moe_architecture_b200.ops import mxfp8 as mx
+        M, N, K = 8192, 8192, 2048
+        aq, sa = mx.quant_rows(bf(M, K, sc=1.0))
+        bq, sb = mx.quant_rows(bf(N, K, sc=1.0))
+        out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        for _ in range(n):
+            mx.gemm_mx(aq, sa, bq, sb, out, M=M, N=N, K=K)
     else:
         raise SystemExit(f"unknown case {a.case}")
     torch.cuda.synchronize()
