@@ -36,7 +36,7 @@ void gemm(const Tensor& A, const Tensor& B, const OptT& B2, Tensor C, const OptT
           int64_t mode, int64_t epilogue, int64_t M, int64_t N, int64_t K, int64_t groups, int64_t a_major,
           int64_t b_major, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, int64_t a_gs, int64_t b_gs,
           int64_t c_gs, const OptT& tile_group, const OptT& num_m_tiles, const OptT& k_begin, const OptT& k_len,
-          double alpha, double beta, const OptT& row_scale, Tensor status) {
+          double alpha, double beta, const OptT& row_scale, const OptT& row_ptr, Tensor status) {
   c10::cuda::CUDAGuard guard(A.device());
   need_bf16(A, "A");
   need_bf16(B, "B");
@@ -52,6 +52,11 @@ void gemm(const Tensor& A, const Tensor& B, const OptT& B2, Tensor C, const OptT
   TORCH_CHECK(d.out_f32 || C.scalar_type() == at::kBFloat16, "C must be bf16 or fp32");
   if (D.has_value() && D->defined()) TORCH_CHECK(D->scalar_type() == C.scalar_type(), "D must have C's dtype");
   d.alpha = (float)alpha; d.beta = (float)beta; d.row_scale = (const float*)ptr_or_null(row_scale);
+  if (row_ptr.has_value() && row_ptr->defined()) {
+    TORCH_CHECK(row_ptr->scalar_type() == at::kLong && row_ptr->is_contiguous() && row_ptr->numel() >= M &&
+                epilogue == KMOE_EPI_STORE, "row_ptr: int64, one entry per output row, plain store epilogue");
+    d.c_row_ptr = (const long long*)row_ptr->data_ptr<int64_t>();
+  }
   TORCH_CHECK(status.scalar_type() == at::kInt && status.is_cuda(), "status must be a CUDA int32 tensor");
   d.status = status.data_ptr<int>();
   d.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
@@ -462,13 +467,15 @@ std::vector<Tensor> ep_recv_plan(const Tensor& meta_in, int64_t n_local, int64_t
 }
 
 void ep_move(const Tensor& slots, Tensor packed, const Tensor& meta_in, const Tensor& slot_dst, const Tensor& offsets,
-             std::vector<int64_t> ret_ptrs, int64_t rank, int64_t n_local, int64_t world, int64_t cap, int64_t dir) {
+             std::vector<int64_t> ret_ptrs, int64_t rank, int64_t n_local, int64_t world, int64_t cap, int64_t dir,
+             const OptT& row_ptr_out) {
   c10::cuda::CUDAGuard guard(packed.device());
   need_bf16(packed, "packed");
   TORCH_CHECK(packed.dim() == 2 && packed.is_contiguous());
   check(kmoe_ep_move(slots.data_ptr(), packed.data_ptr(), meta_in.data_ptr<int>(), slot_dst.data_ptr<int>(),
                      offsets.data_ptr<int>(), (const long long*)ret_ptrs.data(), (int)rank, (int)n_local, (int)world,
-                     cap, (int)packed.size(1), (int)packed.size(0), (int)dir, cur_stream()), "ep_move");
+                     cap, (int)packed.size(1), (int)packed.size(0), (int)dir,
+                     (long long*)const_cast<void*>(ptr_or_null(row_ptr_out)), cur_stream()), "ep_move");
 }
 
 }  // namespace

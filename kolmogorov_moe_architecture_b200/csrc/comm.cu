@@ -289,7 +289,7 @@ __global__ void ep_recv_plan_kernel(const int* __restrict__ meta_in, int n_local
 __global__ void ep_move_kernel(const __nv_bfloat16* __restrict__ slots, __nv_bfloat16* __restrict__ packed,
                                const int* __restrict__ meta_in, const int* __restrict__ slot_dst,
                                const int* __restrict__ offsets, PeerPtrs ret, int rank, int n_local, int world,
-                               long long cap, int d, int max_rows, int dir) {
+                               long long cap, int d, int max_rows, int dir, long long* __restrict__ row_ptr_out) {
   const int vec = d / 8;
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -303,6 +303,13 @@ __global__ void ep_move_kernel(const __nv_bfloat16* __restrict__ slots, __nv_bfl
       if (row >= b0 && row < b0 + c) { sl = q; j = row - b0; break; }
     }
     uint4* prow = reinterpret_cast<uint4*>(packed + (size_t)row * d);
+    if (dir == 0 && row_ptr_out != nullptr && lane == 0) {
+      long long addr = 0;
+      if (sl >= 0)
+        addr = reinterpret_cast<long long>(reinterpret_cast<__nv_bfloat16*>(ret.p[sl % world]) +
+                                           (size_t)(meta_in[sl * 2 + 1] + j) * d);
+      row_ptr_out[row] = addr;
+    }
     if (dir == 0) {
       if (sl < 0) {
         for (int v = lane; v < vec; v += 32) prow[v] = make_uint4(0, 0, 0, 0);
@@ -340,10 +347,10 @@ extern "C" int kmoe_ep_recv_plan(const int* meta_in, int n_local, int world, int
 
 extern "C" int kmoe_ep_move(const void* slots, void* packed, const int* meta_in, const int* slot_dst,
                             const int* offsets, const long long* ret_ptrs, int rank, int n_local, int world,
-                            long long cap, int d, int max_rows, int dir, cudaStream_t st) {
+                            long long cap, int d, int max_rows, int dir, long long* row_ptr_out, cudaStream_t st) {
   if (world > MAX_RANKS || d % 8) return -1;
   ep_move_kernel<<<148 * 4, 256, 0, st>>>((const __nv_bfloat16*)slots, (__nv_bfloat16*)packed, meta_in, slot_dst,
                                           offsets, make_ptrs(ret_ptrs, world), rank, n_local, world, cap, d, max_rows,
-                                          dir);
+                                          dir, row_ptr_out);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

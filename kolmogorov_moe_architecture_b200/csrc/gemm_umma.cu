@@ -46,6 +46,7 @@ struct GemmArgs {
   int out_f32;
   float alpha, beta;
   const float* row_scale;
+  const long long* row_ptr;   // optional: address of each output row (may be peer memory); 0 = row not stored
   int* status;
 };
 
@@ -134,8 +135,10 @@ __device__ __forceinline__ void load8(const float* src, float* v) {
 // Writes one 32-column chunk of one row: out = alpha*scale*acc + beta*D
 template <typename T>
 __device__ __forceinline__ void epilogue_store_chunk(const GemmArgs& a, const uint32_t (&acc)[32], bool have_acc,
-                                                     long long row_off_c, long long row_off_d, int col, float scale) {
-  T* C = reinterpret_cast<T*>(a.C);
+                                                     long long row_off_c, long long row_off_d, int col, float scale,
+                                                     long long row_addr) {
+  // row_addr != 0: the row's own base address (possibly on a peer GPU) replaces C + row offset
+  T* C = row_addr ? reinterpret_cast<T*>(row_addr) - row_off_c : reinterpret_cast<T*>(a.C);
   const T* D = reinterpret_cast<const T*>(a.D);
 #pragma unroll
   for (int j = 0; j < 32; j += 8) {
@@ -304,6 +307,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       float scale = args.alpha;
       if (args.row_scale != nullptr && row_ok) scale *= args.row_scale[row];
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      long long row_addr = 0;
+      bool store_ok = row_ok;
+      if (args.row_ptr != nullptr && row_ok) {
+        row_addr = args.row_ptr[row];
+        store_ok = row_addr != 0;
+      }
       if (!swiglu) {
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
@@ -313,11 +322,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tmem_ld_wait();
           }
           const int col = t.n_tile * BN + c;
-          if (row_ok && col < args.N) {
+          if (store_ok && col < args.N) {
             if (args.out_f32)
-              epilogue_store_chunk<float>(args, r, have_acc, coff, doff, col, scale);
+              epilogue_store_chunk<float>(args, r, have_acc, coff, doff, col, scale, row_addr);
             else
-              epilogue_store_chunk<__nv_bfloat16>(args, r, have_acc, coff, doff, col, scale);
+              epilogue_store_chunk<__nv_bfloat16>(args, r, have_acc, coff, doff, col, scale, row_addr);
           }
         }
       } else {
@@ -463,7 +472,7 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
   a.tile_group = d->tile_group; a.num_m_tiles = d->num_m_tiles;
   a.k_begin = d->k_begin; a.k_len = d->k_len;
   a.out_f32 = d->out_f32; a.alpha = d->alpha; a.beta = d->beta;
-  a.row_scale = d->row_scale; a.status = d->status;
+  a.row_scale = d->row_scale; a.row_ptr = d->c_row_ptr; a.status = d->status;
 
   // The reduction extent seen by TMA: ragged batched GEMMs index a shared [sum K, rows] buffer.
   long long k_extent_a = d->K, k_extent_b = d->K;

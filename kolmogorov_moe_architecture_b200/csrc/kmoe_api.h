@@ -40,6 +40,9 @@ typedef struct KmoeGemmDesc {
   int out_f32;
   float alpha, beta;
   const float* row_scale;  // optional per-row multiplier applied to the product
+  // optional (STORE epilogue): device array with the address of every output row, which may lie in a
+  // peer GPU's memory; 0 skips the row.  Replaces C + row * ldc; D is still read at its usual place.
+  const long long* c_row_ptr;
   int* status;             // device int; non-zero after the launch = a bounded wait expired
   int num_sms;             // 0 = query
 } KmoeGemmDesc;
@@ -152,9 +155,11 @@ int kmoe_ep_dispatch(const void* src, const int* row_src, const float* assign_sc
                      int E, long long cap, int d, int div, int max_rows, cudaStream_t st);
 int kmoe_ep_recv_plan(const int* meta_in, int n_local, int world, int max_rows, int* slot_dst, int* offsets,
                       int* tile_group, int* out_meta, cudaStream_t st);
+// row_ptr_out (optional, dir 0): for every packed row the address of its place in the source rank's return
+// buffer (0 for padding) - the table a GEMM epilogue uses to store its rows straight to the peers.
 int kmoe_ep_move(const void* slots, void* packed, const int* meta_in, const int* slot_dst, const int* offsets,
                  const long long* ret_ptrs, int rank, int n_local, int world, long long cap, int d, int max_rows,
-                 int dir, cudaStream_t st);
+                 int dir, long long* row_ptr_out, cudaStream_t st);
 
 // ---------------------------------------------------------------------------- routing decisions
 // Token choice: softmax over E experts -> top-k -> renormalise; also accumulates (atomically, into

@@ -62,9 +62,12 @@ def _count(n: int = 1):
 # ---------------------------------------------------------------------- GEMM
 def gemm(A, B, C, *, M, N, Kd, mode=DENSE, epi=EPI_STORE, groups=1, a_major=MAJ_K, b_major=MAJ_K,
          lda, ldb, ldc, ldd=0, a_gs=0, b_gs=0, c_gs=0, B2=None, D=None, G=None, U=None,
-         tile_group=None, num_m_tiles=None, k_begin=None, k_len=None, alpha=1.0, beta=0.0, row_scale=None):
+         tile_group=None, num_m_tiles=None, k_begin=None, k_len=None, alpha=1.0, beta=0.0, row_scale=None,
+         row_ptr=None):
+    """``row_ptr`` (int64, one address per output row, 0 = skip) redirects each output row, e.g. into a
+    peer GPU's buffer; ``C`` then only supplies the dtype."""
     K.gemm(A, B, B2, C, D, G, U, mode, epi, M, N, Kd, groups, a_major, b_major, lda, ldb, ldc, ldd,
-           a_gs, b_gs, c_gs, tile_group, num_m_tiles, k_begin, k_len, alpha, beta, row_scale,
+           a_gs, b_gs, c_gs, tile_group, num_m_tiles, k_begin, k_len, alpha, beta, row_scale, row_ptr,
            status_tensor(A.device))
     _count()
     return C

@@ -8,10 +8,11 @@ One autograd function covers the whole layer on both sides of the exchange:
     dispatch: token rows -> owner's receive slots    (permute and all-to-all in one kernel)
     ------------------------ flag barrier ------------------------
                                                      recv_plan: slot counts -> padded expert-major layout
-                                                     compact slots -> Xp
-                                                     grouped GEMM 1 (+SwiGLU epilogue), grouped GEMM 2
-                                                     return: Y rows -> source's buffer, at the row its
-                                                             own plan gave the assignment
+                                                     compact slots -> Xp (+ table: packed row -> address
+                                                             of its place in the source's return buffer)
+                                                     grouped GEMM 1 (+SwiGLU epilogue)
+                                                     grouped GEMM 2 whose epilogue stores every row
+                                                             through that table into the source rank
     ------------------------ flag barrier ------------------------
     weighted top-k combine (local)
 
@@ -25,7 +26,8 @@ routed to one rank) and shared by all layers of a model: a layer's receive buffe
 again once the rank has compacted it, which the second barrier of the layer orders before any
 peer's next dispatch.
 
-The kernels are in ``csrc/comm.cu`` (``ep_dispatch``, ``ep_recv_plan``, ``ep_move``).  The
+The kernels are in ``csrc/comm.cu`` (``ep_dispatch``, ``ep_recv_plan``, ``ep_move``) and the
+row-pointer epilogue of ``csrc/gemm_umma.cu``.  The
 reference exchanges rows with ``all_to_all_single`` and a host-side loop
 (moe_arch/model/sparse_moe.py:540-603).
 """
@@ -132,24 +134,27 @@ class _EPFusedFFN(torch.autograd.Function):
         meta_in = buf.meta.clone()
         slot_dst, offs_l, tile_group, meta_l = K.ep_recv_plan(meta_in, nl, ws, R)
         Xp = torch.empty(R, d, dtype=x.dtype, device=x.device)
-        K.ep_move(buf.recv, Xp, meta_in, slot_dst, offs_l, buf.ret_ptrs, buf.rank, nl, ws, buf.cap, 0)
+        # row_ptr: where each packed row's result belongs in its source rank's return buffer
+        row_ptr = torch.empty(R, dtype=torch.int64, device=x.device)
+        K.ep_move(buf.recv, Xp, meta_in, slot_dst, offs_l, buf.ret_ptrs, buf.rank, nl, ws, buf.cap, 0, row_ptr)
         H = torch.empty(R, f, dtype=x.dtype, device=x.device)
         G, U = torch.empty_like(H), torch.empty_like(H)
         nmt = meta_l[0:1]
         C.gemm(Xp, w1, H, B2=w2, G=G, U=U, mode=C.GROUPED_M, epi=C.EPI_SWIGLU, M=R, N=f, Kd=d, groups=nl,
                b_major=C.MAJ_MN, lda=d, ldb=f, ldc=f, b_gs=d * f, tile_group=tile_group, num_m_tiles=nmt)
-        Y = torch.empty(R, d, dtype=x.dtype, device=x.device)
-        C.gemm(H, w3, Y, mode=C.GROUPED_M, M=R, N=d, Kd=f, groups=nl, b_major=C.MAJ_MN, lda=f, ldb=d, ldc=d,
-               b_gs=f * d, tile_group=tile_group, num_m_tiles=nmt)
-        K.ep_move(buf.recv, Y, meta_in, slot_dst, offs_l, buf.ret_ptrs, buf.rank, nl, ws, buf.cap, 1)
+        # GEMM 2 with the combine's transfer in its epilogue: every output row is stored straight into the
+        # source rank's return buffer over NVLink (Xp only lends its dtype here)
+        C.gemm(H, w3, Xp, mode=C.GROUPED_M, M=R, N=d, Kd=f, groups=nl, b_major=C.MAJ_MN, lda=f, ldb=d, ldc=d,
+               b_gs=f * d, tile_group=tile_group, num_m_tiles=nmt, row_ptr=row_ptr)
         buf.barrier()
         wf = weights.reshape(-1).float().contiguous()
         out = K.moe_combine(buf.ret, pos, wf, T, k)
         # the return buffer is reused by the next layer; keep this layer's rows for d(loss)/d(weights)
         Yret = buf.ret[: row_src.numel()].clone() if ctx.needs_input_grad[5] else None
-        C._count(7)
+        C._count(6)
         ctx.save_for_backward(Xp, G, U, w1, w2, w3, wf, pos, row_src, counts, offsets, meta_in, slot_dst, offs_l,
-                              tile_group, meta_l, Yret if Yret is not None else torch.empty(0, device=x.device))
+                              tile_group, meta_l, Yret if Yret is not None else torch.empty(0, device=x.device),
+                              row_ptr)
         ctx.buf = buf
         ctx.dims = (T, d, nl, f, k, R)
         ctx.wdtype = weights.dtype
@@ -160,7 +165,7 @@ class _EPFusedFFN(torch.autograd.Function):
         from ..ops import cuda_ops as C
         K = torch.ops.kmoe
         (Xp, G, U, w1, w2, w3, wf, pos, row_src, counts, offsets, meta_in, slot_dst, offs_l, tile_group, meta_l,
-         Yret) = ctx.saved_tensors
+         Yret, row_ptr) = ctx.saved_tensors
         buf = ctx.buf
         T, d, nl, f, k, R = ctx.dims
         E, ws = buf.E, buf.world
@@ -170,7 +175,7 @@ class _EPFusedFFN(torch.autograd.Function):
         K.ep_dispatch(dout, row_src, wf, offsets, counts, buf.recv_ptrs, buf.meta_ptrs, buf.rank, ws, E, buf.cap, k)
         buf.barrier()
         dYp = torch.empty(R, d, dtype=dout.dtype, device=dout.device)
-        K.ep_move(buf.recv, dYp, meta_in, slot_dst, offs_l, buf.ret_ptrs, buf.rank, nl, ws, buf.cap, 0)
+        K.ep_move(buf.recv, dYp, meta_in, slot_dst, offs_l, buf.ret_ptrs, buf.rank, nl, ws, buf.cap, 0, None)
         dH = torch.empty(R, f, dtype=dout.dtype, device=dout.device)
         C.gemm(dYp, w3, dH, mode=C.GROUPED_M, M=R, N=f, Kd=d, groups=nl, lda=d, ldb=d, ldc=f, b_gs=f * d,
                tile_group=tile_group, num_m_tiles=nmt)
@@ -178,9 +183,9 @@ class _EPFusedFFN(torch.autograd.Function):
         dXp = torch.empty(R, d, dtype=dout.dtype, device=dout.device)
         C.gemm(dG, w1, dXp, mode=C.GROUPED_M, M=R, N=d, Kd=f, groups=nl, lda=f, ldb=f, ldc=d, b_gs=d * f,
                tile_group=tile_group, num_m_tiles=nmt)
+        # second dgrad GEMM adds the first one's local result and stores the sum into the source ranks
         C.gemm(dU, w2, dXp, D=dXp, beta=1.0, mode=C.GROUPED_M, M=R, N=d, Kd=f, groups=nl, lda=f, ldb=f,
-               ldc=d, ldd=d, b_gs=d * f, tile_group=tile_group, num_m_tiles=nmt)
-        K.ep_move(buf.recv, dXp, meta_in, slot_dst, offs_l, buf.ret_ptrs, buf.rank, nl, ws, buf.cap, 1)
+               ldc=d, ldd=d, b_gs=d * f, tile_group=tile_group, num_m_tiles=nmt, row_ptr=row_ptr)
         buf.barrier()
         dx = K.moe_combine(buf.ret, pos, None, T, k)
         dwts = None
