@@ -243,17 +243,26 @@ __global__ void ep_dispatch_kernel(const __nv_bfloat16* __restrict__ src, const 
                           (((long long)(e % n_local) * world + rank) * cap + j) * d;
     const uint4* srow = reinterpret_cast<const uint4*>(src + (size_t)(div > 0 ? a / div : row) * d);
     const float s = assign_scale ? assign_scale[a] : 1.f;
-    for (int v = lane; v < vec; v += 32) {
-      uint4 r = srow[v];
-      if (assign_scale) {
-        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&r);
+    // four 16-byte loads in flight per lane before the (possibly remote) stores
+    for (int v0 = lane; v0 < vec; v0 += 128) {
+      uint4 r[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float2 f = __bfloat1622float2(p[i]);
-          p[i] = __floats2bfloat162_rn(f.x * s, f.y * s);
+      for (int u = 0; u < 4; ++u)
+        if (v0 + 32 * u < vec) r[u] = srow[v0 + 32 * u];
+      if (assign_scale) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&r[u]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float2 f = __bfloat1622float2(p[i]);
+            p[i] = __floats2bfloat162_rn(f.x * s, f.y * s);
+          }
         }
       }
-      reinterpret_cast<uint4*>(drow)[v] = r;
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v0 + 32 * u < vec) reinterpret_cast<uint4*>(drow)[v0 + 32 * u] = r[u];
     }
   }
 }
@@ -315,7 +324,15 @@ __global__ void ep_move_kernel(const __nv_bfloat16* __restrict__ slots, __nv_bfl
         for (int v = lane; v < vec; v += 32) prow[v] = make_uint4(0, 0, 0, 0);
       } else {
         const uint4* srow = reinterpret_cast<const uint4*>(slots + ((long long)sl * cap + j) * d);
-        for (int v = lane; v < vec; v += 32) prow[v] = srow[v];
+        for (int v0 = lane; v0 < vec; v0 += 128) {
+          uint4 r[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (v0 + 32 * u < vec) r[u] = srow[v0 + 32 * u];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (v0 + 32 * u < vec) prow[v0 + 32 * u] = r[u];
+        }
       }
     } else if (sl >= 0) {
       const int src_rank = sl % world;
@@ -333,7 +350,7 @@ extern "C" int kmoe_ep_dispatch(const void* src, const int* row_src, const float
                                 const int* counts, const long long* recv_ptrs, const long long* meta_ptrs, int rank,
                                 int world, int E, long long cap, int d, int div, int max_rows, cudaStream_t st) {
   if (world > MAX_RANKS || d % 8 || E % world) return -1;
-  ep_dispatch_kernel<<<148 * 4, 256, 0, st>>>((const __nv_bfloat16*)src, row_src, assign_scale, offsets, counts,
+  ep_dispatch_kernel<<<148 * 8, 256, 0, st>>>((const __nv_bfloat16*)src, row_src, assign_scale, offsets, counts,
                                               make_ptrs(recv_ptrs, world), make_ptrs(meta_ptrs, world), rank, world, E,
                                               E / world, cap, d, div, max_rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;

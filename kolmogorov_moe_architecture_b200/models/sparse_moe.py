@@ -60,8 +60,11 @@ class ExpertParallelMoE(nn.Module):
 
     def __init__(self, config, layer_idx: int, process_group=None):
         super().__init__()
-        self.config, self.layer_idx, self.process_group = config, layer_idx, process_group
         import torch.distributed as dist
+        if process_group is None and dist.is_available() and dist.is_initialized():
+            from ..parallel.mesh import default_ep_group
+            process_group = default_ep_group()
+        self.config, self.layer_idx, self.process_group = config, layer_idx, process_group
         if dist.is_available() and dist.is_initialized():
             self.world_size = dist.get_world_size(process_group)
             self.rank = dist.get_rank(process_group)

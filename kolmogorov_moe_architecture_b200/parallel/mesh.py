@@ -64,6 +64,15 @@ def init_distributed(backend: Optional[str] = None, ep_size: int = 1, timeout_s:
     return make_mesh(ep_size, with_control_group=with_control_group)
 
 
+# Expert-parallel group of the most recent mesh; expert-parallel layers built afterwards split their
+# experts over it (None = the world group, the reference's only choice).
+_DEFAULT_EP = [None]
+
+
+def default_ep_group():
+    return _DEFAULT_EP[0]
+
+
 def make_mesh(ep_size: int = 1, with_control_group: bool = False) -> Mesh:
     world, rank = dist.get_world_size(), dist.get_rank()
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
@@ -80,6 +89,7 @@ def make_mesh(ep_size: int = 1, with_control_group: bool = False) -> Mesh:
             if e == rank % ep_size:
                 expert_dp_group = grp
     control = dist.new_group(backend="gloo") if with_control_group else None
+    _DEFAULT_EP[0] = ep_group
     return Mesh(world, rank, local, ep_size, dp, dist.group.WORLD, ep_group, expert_dp_group, control)
 
 
