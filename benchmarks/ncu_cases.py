@@ -56,7 +56,7 @@ def main():
         m, v = torch.zeros(N_, device="cuda"), torch.zeros(N_, device="cuda")
         coef = torch.ones(1, device="cuda")
         for s in range(1, n + 1):
-            torch.ops.kmoe.p2p_adamw_allgather([p.data_ptr()], g, m, v, 0, 1, 0, N_, 3e-4, 0.9, 0.95, 1e-8, 0.01, s, coef)
+            torch.ops.kmoe.p2p_adamw_allgather([p.data_ptr()], g, m, v, 0, 1, 0, N_, 3e-4, 0.9, 0.95, 1e-8, 0.01, s, coef, 0)
     elif a.case == "ce":
         R, V = 2048, 50304
         logits = bf(R, V, sc=1.0)

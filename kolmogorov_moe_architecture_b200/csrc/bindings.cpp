@@ -105,7 +105,7 @@ Tensor rope(const Tensor& x, const Tensor& cs, const Tensor& sn, bool transpose)
   return out;
 }
 
-Tensor swiglu_fwd(const Tensor& g, const Tensor& u) {
+Tensor swiglu_fwd(const Tensor& g, const Tensor& u, const OptT& live_rows) {
   c10::cuda::CUDAGuard guard(g.device());
   need_bf16(g, "gate"); need_bf16(u, "up");
   const int cols = g.size(-1);
@@ -113,11 +113,11 @@ Tensor swiglu_fwd(const Tensor& g, const Tensor& u) {
   Tensor g2 = g.dim() == 1 ? g.unsqueeze(0) : g, u2 = u.dim() == 1 ? u.unsqueeze(0) : u;
   Tensor h = at::empty(g.sizes(), g.options());
   check(kmoe_swiglu_fwd(g2.data_ptr(), u2.data_ptr(), h.data_ptr(), rows, cols, row_stride(g2), row_stride(u2),
-                        cur_stream()), "swiglu_fwd");
+                        (const int*)ptr_or_null(live_rows), cur_stream()), "swiglu_fwd");
   return h;
 }
 
-std::tuple<Tensor, Tensor> swiglu_bwd(const Tensor& g, const Tensor& u, const Tensor& dh) {
+std::tuple<Tensor, Tensor> swiglu_bwd(const Tensor& g, const Tensor& u, const Tensor& dh, const OptT& live_rows) {
   c10::cuda::CUDAGuard guard(g.device());
   need_bf16(g, "gate"); need_bf16(u, "up"); need_bf16(dh, "dh");
   TORCH_CHECK(dh.is_contiguous());
@@ -126,7 +126,8 @@ std::tuple<Tensor, Tensor> swiglu_bwd(const Tensor& g, const Tensor& u, const Te
   Tensor g2 = g.dim() == 1 ? g.unsqueeze(0) : g, u2 = u.dim() == 1 ? u.unsqueeze(0) : u;
   Tensor dg = at::empty(g.sizes(), g.options()), du = at::empty(g.sizes(), g.options());
   check(kmoe_swiglu_bwd(g2.data_ptr(), u2.data_ptr(), dh.data_ptr(), dg.data_ptr(), du.data_ptr(), rows, cols,
-                        row_stride(g2), row_stride(u2), cols, cur_stream()), "swiglu_bwd");
+                        row_stride(g2), row_stride(u2), cols, (const int*)ptr_or_null(live_rows), cur_stream()),
+        "swiglu_bwd");
   return {dg, du};
 }
 
@@ -304,25 +305,27 @@ void p2p_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t world, in
 }
 
 void p2p_reduce_scatter(std::vector<int64_t> grad_ptrs, int64_t rank, int64_t world, int64_t off, int64_t n,
-                        const OptT& sq_out) {
+                        const OptT& sq_out, int64_t mc_ptr) {
   check(kmoe_p2p_reduce_scatter((const long long*)grad_ptrs.data(), (int)rank, (int)world, off, n,
-                                (float*)const_cast<void*>(ptr_or_null(sq_out)), cur_stream()), "p2p_reduce_scatter");
+                                (float*)const_cast<void*>(ptr_or_null(sq_out)), mc_ptr, cur_stream()),
+        "p2p_reduce_scatter");
 }
 
 void p2p_adamw_allgather(std::vector<int64_t> param_ptrs, const Tensor& grad, Tensor m, Tensor v, int64_t rank,
                          int64_t world, int64_t off, int64_t n, double lr, double beta1, double beta2, double eps,
-                         double wd, int64_t step, const OptT& clip_coef) {
+                         double wd, int64_t step, const OptT& clip_coef, int64_t mc_ptr) {
   c10::cuda::CUDAGuard guard(grad.device());
   need_bf16(grad, "grad"); need_f32(m, "m"); need_f32(v, "v");
   TORCH_CHECK(m.numel() >= n && v.numel() >= n, "moment buffers too small");
   check(kmoe_p2p_adamw_allgather((const long long*)param_ptrs.data(), grad.data_ptr(), m.data_ptr<float>(),
                                  v.data_ptr<float>(), (int)rank, (int)world, off, n, (float)lr, (float)beta1,
                                  (float)beta2, (float)eps, (float)wd, (int)step, (const float*)ptr_or_null(clip_coef),
-                                 cur_stream()), "p2p_adamw_allgather");
+                                 mc_ptr, cur_stream()), "p2p_adamw_allgather");
 }
 
-void p2p_allgather(std::vector<int64_t> buf_ptrs, int64_t rank, int64_t world, int64_t off, int64_t n) {
-  check(kmoe_p2p_allgather((const long long*)buf_ptrs.data(), (int)rank, (int)world, off, n, cur_stream()),
+void p2p_allgather(std::vector<int64_t> buf_ptrs, int64_t rank, int64_t world, int64_t off, int64_t n,
+                   int64_t mc_ptr) {
+  check(kmoe_p2p_allgather((const long long*)buf_ptrs.data(), (int)rank, (int)world, off, n, mc_ptr, cur_stream()),
         "p2p_allgather");
 }
 

@@ -11,6 +11,9 @@
 //                      fp32 moments) whose result is stored into every rank's parameter
 //                      buffer - the update and the all-gather are one kernel.
 //   allgather          copy of an owned range into every rank's buffer (used after Muon).
+// Each of the three takes an optional NVLink-switch multicast address of the same buffer: the reduction
+// then happens inside the switch (multimem.ld_reduce, one load instead of `world`) and the publication is
+// one multimem.st instead of `world` stores, which cuts the bytes through each GPU's port by ~world.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -28,6 +31,22 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
+}
+
+// NVLink-switch (NVLS) multicast: one address that stands for the same offset in every rank's buffer.
+// ld_reduce returns the sum over all ranks, formed in the switch with fp32 accumulation; st writes to all ranks.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(mc_addr)
+               : "memory");
+  return r;
+}
+__device__ __forceinline__ void multimem_st_16B(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
 }
 
 // flags[r] on every rank is written by rank r.  One CTA; thread r handles peer r.
@@ -64,8 +83,9 @@ __device__ __forceinline__ void acc8(const uint4& r, float* a) {
 }
 
 // out[i] = (1/world) * sum_r grads[r][off + i], i in [0, n); sq_out += sum out^2 (fp32 atomics per CTA)
+// mc != null: the sum comes from one multicast load per 16 bytes instead of `world` peer loads.
 __global__ void p2p_reduce_scatter_kernel(PeerPtrs grads, int rank, int world, long long off, long long n,
-                                          float* __restrict__ sq_out) {
+                                          float* __restrict__ sq_out, const void* mc) {
   const long long nvec = n / 8;
   const float inv = 1.f / world;
   float sq = 0.f;
@@ -73,10 +93,14 @@ __global__ void p2p_reduce_scatter_kernel(PeerPtrs grads, int rank, int world, l
   for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec;
        v += (long long)gridDim.x * blockDim.x) {
     float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int r = 0; r < world; ++r) {
-      const int src = (rank + r) % world;     // stagger peers so ranks do not all hit the same one
-      const uint4 x = *(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[src]) + off) + v);
-      acc8(x, a);
+    if (mc != nullptr) {
+      acc8(multimem_ld_reduce_bf16x8(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(mc) + off) + v), a);
+    } else {
+      for (int r = 0; r < world; ++r) {
+        const int src = (rank + r) % world;     // stagger peers so ranks do not all hit the same one
+        const uint4 x = *(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[src]) + off) + v);
+        acc8(x, a);
+      }
     }
     uint4 o;
 #pragma unroll
@@ -106,7 +130,7 @@ struct AdamArgs {
 // AdamW on [off, off+n) of the owner's gradient/parameter segment; new parameters go to every rank.
 __global__ void p2p_adamw_allgather_kernel(PeerPtrs params, const __nv_bfloat16* __restrict__ grad, float* __restrict__ m,
                                            float* __restrict__ v2, int rank, int world, long long off, long long n,
-                                           AdamArgs h) {
+                                           AdamArgs h, void* mc) {
   const long long nvec = n / 8;
   const float cc = h.clip_coef ? *h.clip_coef : 1.f;
   const __nv_bfloat16* own = reinterpret_cast<const __nv_bfloat16*>(params.p[rank]) + off;
@@ -139,20 +163,28 @@ __global__ void p2p_adamw_allgather_kernel(PeerPtrs params, const __nv_bfloat16*
     *reinterpret_cast<float4*>(v2 + i * 8 + 4) = make_float4(sv[4], sv[5], sv[6], sv[7]);
     uint4 o;
     o.x = pack_bf16(pv[0], pv[1]); o.y = pack_bf16(pv[2], pv[3]); o.z = pack_bf16(pv[4], pv[5]); o.w = pack_bf16(pv[6], pv[7]);
-    for (int r = 0; r < world; ++r) {
-      const int dst = (rank + r) % world;
-      *(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.p[dst]) + off) + i) = o;
+    if (mc != nullptr) {
+      multimem_st_16B(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(mc) + off) + i, o);
+    } else {
+      for (int r = 0; r < world; ++r) {
+        const int dst = (rank + r) % world;
+        *(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.p[dst]) + off) + i) = o;
+      }
     }
   }
 }
 
 // Copy [off, off+n) of this rank's buffer into every other rank's buffer.
-__global__ void p2p_allgather_kernel(PeerPtrs bufs, int rank, int world, long long off, long long n) {
+__global__ void p2p_allgather_kernel(PeerPtrs bufs, int rank, int world, long long off, long long n, void* mc) {
   const long long nvec = n / 8;
   const uint4* own = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(bufs.p[rank]) + off);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
     const uint4 x = own[i];
+    if (mc != nullptr) {                      // one store reaches every rank (this one included: same value)
+      multimem_st_16B(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(mc) + off) + i, x);
+      continue;
+    }
     for (int r = 1; r < world; ++r) {
       const int dst = (rank + r) % world;
       *(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(bufs.p[dst]) + off) + i) = x;
@@ -179,26 +211,29 @@ extern "C" int kmoe_p2p_barrier(const long long* flag_ptrs, int rank, int world,
 }
 
 extern "C" int kmoe_p2p_reduce_scatter(const long long* grad_ptrs, int rank, int world, long long off, long long n,
-                                       float* sq_out, cudaStream_t st) {
+                                       float* sq_out, long long mc_ptr, cudaStream_t st) {
   if (world > MAX_RANKS || n % 8 || off % 8) return -1;
-  p2p_reduce_scatter_kernel<<<148 * 8, 256, 0, st>>>(make_ptrs(grad_ptrs, world), rank, world, off, n, sq_out);
+  p2p_reduce_scatter_kernel<<<148 * 8, 256, 0, st>>>(make_ptrs(grad_ptrs, world), rank, world, off, n, sq_out,
+                                                     reinterpret_cast<const void*>(mc_ptr));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 extern "C" int kmoe_p2p_adamw_allgather(const long long* param_ptrs, const void* grad, float* m, float* v, int rank,
                                         int world, long long off, long long n, float lr, float beta1, float beta2,
-                                        float eps, float wd, int step, const float* clip_coef, cudaStream_t st) {
+                                        float eps, float wd, int step, const float* clip_coef, long long mc_ptr,
+                                        cudaStream_t st) {
   if (world > MAX_RANKS || n % 8 || off % 8) return -1;
   AdamArgs h{lr, beta1, beta2, eps, wd, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step), clip_coef};
   p2p_adamw_allgather_kernel<<<148 * 8, 256, 0, st>>>(make_ptrs(param_ptrs, world), (const __nv_bfloat16*)grad, m, v,
-                                                      rank, world, off, n, h);
+                                                      rank, world, off, n, h, reinterpret_cast<void*>(mc_ptr));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 extern "C" int kmoe_p2p_allgather(const long long* buf_ptrs, int rank, int world, long long off, long long n,
-                                  cudaStream_t st) {
+                                  long long mc_ptr, cudaStream_t st) {
   if (world > MAX_RANKS || n % 8 || off % 8) return -1;
-  p2p_allgather_kernel<<<148 * 8, 256, 0, st>>>(make_ptrs(buf_ptrs, world), rank, world, off, n);
+  p2p_allgather_kernel<<<148 * 8, 256, 0, st>>>(make_ptrs(buf_ptrs, world), rank, world, off, n,
+                                                reinterpret_cast<void*>(mc_ptr));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -173,8 +173,9 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, const float* __
 // -------------------------------------------------------------------- SwiGLU
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
                                   __nv_bfloat16* __restrict__ h, long long rows, int cols, long long ldg,
-                                  long long ldu) {
+                                  long long ldu, const int* __restrict__ live_rows) {
   const int vpr = cols / 8;
+  if (live_rows != nullptr) rows = min(rows, (long long)*live_rows);   // rows past the live count hold no data
   const long long total = rows * vpr;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -192,8 +193,9 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ g, const __n
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
                                   const __nv_bfloat16* __restrict__ dh, __nv_bfloat16* __restrict__ dg,
                                   __nv_bfloat16* __restrict__ du, long long rows, int cols, long long ldg,
-                                  long long ldu, long long ldo) {
+                                  long long ldu, long long ldo, const int* __restrict__ live_rows) {
   const int vpr = cols / 8;
+  if (live_rows != nullptr) rows = min(rows, (long long)*live_rows);
   const long long total = rows * vpr;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -266,19 +268,20 @@ extern "C" int kmoe_rope(const void* x, const float* cs, const float* sn, void* 
 }
 
 extern "C" int kmoe_swiglu_fwd(const void* g, const void* u, void* h, long long rows, int cols, long long ldg,
-                               long long ldu, cudaStream_t st) {
+                               long long ldu, const int* live_rows, cudaStream_t st) {
   if (cols % 8 || ldg % 8 || ldu % 8) return -1;
   swiglu_fwd_kernel<<<grid_for(rows * (cols / 8), 256), 256, 0, st>>>(
-      (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (__nv_bfloat16*)h, rows, cols, ldg, ldu);
+      (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (__nv_bfloat16*)h, rows, cols, ldg, ldu, live_rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 extern "C" int kmoe_swiglu_bwd(const void* g, const void* u, const void* dh, void* dg, void* du, long long rows,
-                               int cols, long long ldg, long long ldu, long long ldo, cudaStream_t st) {
+                               int cols, long long ldg, long long ldu, long long ldo, const int* live_rows,
+                               cudaStream_t st) {
   if (cols % 8 || ldg % 8 || ldu % 8 || ldo % 8) return -1;
   swiglu_bwd_kernel<<<grid_for(rows * (cols / 8), 256), 256, 0, st>>>(
       (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (const __nv_bfloat16*)dh, (__nv_bfloat16*)dg,
-      (__nv_bfloat16*)du, rows, cols, ldg, ldu, ldo);
+      (__nv_bfloat16*)du, rows, cols, ldg, ldu, ldo, live_rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

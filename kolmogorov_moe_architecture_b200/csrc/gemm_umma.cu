@@ -173,6 +173,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __shared__ uint64_t tmem_full[2];
   __shared__ uint64_t tmem_empty[2];
   __shared__ uint32_t tmem_base_slot;
+  __shared__ __align__(16) __nv_bfloat16 peer_stage[4][32][72];   // per epilogue warp: 32 rows x 64 columns (+pad)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -309,11 +310,54 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
       long long row_addr = 0;
       bool store_ok = row_ok;
-      if (args.row_ptr != nullptr && row_ok) {
-        row_addr = args.row_ptr[row];
+      if (args.row_ptr != nullptr) {
+        row_addr = row_ok ? args.row_ptr[row] : 0;
         store_ok = row_addr != 0;
       }
-      if (!swiglu) {
+      if (!swiglu && args.row_ptr != nullptr) {
+        // Rows go to individual addresses, possibly on peer GPUs.  A lane holds one row, so a direct store
+        // would emit 32 scattered 16-byte writes per instruction; the 64-column slab is staged in shared
+        // memory instead and written back with 8 lanes per row: four full 128-byte lines per instruction.
+        __nv_bfloat16(*stg)[72] = peer_stage[q];
+        const __nv_bfloat16* Dp = reinterpret_cast<const __nv_bfloat16*>(args.D);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 64) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            if (have_acc) {
+              tmem_ld_32x32(t_row + c + h * 32, r);
+              tmem_ld_wait();
+            }
+            const int col = t.n_tile * BN + c + h * 32;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = have_acc ? __uint_as_float(r[j + i]) * scale : 0.f;
+              if (Dp != nullptr && row_ok && col + j < args.N) {
+                float d[8];
+                load8(Dp + doff + col + j, d);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] += args.beta * d[i];
+              }
+              store8<__nv_bfloat16>(&stg[lane][h * 32 + j], v);
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + (lane >> 3);
+            const int cc = (lane & 7) * 8;
+            const long long addr = __shfl_sync(0xffffffffu, row_addr, rr);
+            const int gcol = t.n_tile * BN + c + cc;
+            if (addr != 0 && gcol < args.N)
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(addr) + gcol) =
+                  *reinterpret_cast<const uint4*>(&stg[rr][cc]);
+          }
+          __syncwarp();
+        }
+      } else if (!swiglu) {
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           uint32_t r[32];
@@ -424,7 +468,7 @@ template <int BN, int AM, int BMj>
 static int launch_variant(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const GemmArgs& args,
                           int grid, cudaStream_t stream) {
   constexpr int stage_bytes = A_STAGE_BYTES + BN * BK * 2;
-  int stages = (200 * 1024) / stage_bytes;
+  int stages = (196 * 1024) / stage_bytes;      // leaves room for the 18 KB static staging buffer
   if (stages > 8) stages = 8;
   const int smem = stages * stage_bytes + 1024;
   auto kern = umma_gemm_kernel<BN, AM, BMj>;
@@ -448,6 +492,7 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
   using namespace kmoe;
   if (d->K % 8 != 0 || d->N % 8 != 0) return -1;
   if (d->K <= 0 || d->M <= 0 || d->N <= 0) return -2;
+  if (d->c_row_ptr != nullptr && (d->out_f32 || d->epilogue != KMOE_EPI_STORE)) return -3;
   const bool swiglu = d->epilogue == KMOE_EPI_SWIGLU;
   // narrow outputs use the 128-wide tile so more CTAs get work
   const int n_tiles_256 = (d->N + (swiglu ? 127 : 255)) / (swiglu ? 128 : 256);

@@ -93,10 +93,11 @@ int kmoe_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* 
                      float* dw_f32, float* partial, int rows, int d, cudaStream_t st);
 int kmoe_rope(const void* x, const float* cs, const float* sn, void* out, int B, int S, int H, int D,
               long long cs_bstride, int transpose, cudaStream_t st);
+// live_rows (device, optional): only the first min(rows, *live_rows) rows are processed.
 int kmoe_swiglu_fwd(const void* g, const void* u, void* h, long long rows, int cols, long long ldg, long long ldu,
-                    cudaStream_t st);
+                    const int* live_rows, cudaStream_t st);
 int kmoe_swiglu_bwd(const void* g, const void* u, const void* dh, void* dg, void* du, long long rows, int cols,
-                    long long ldg, long long ldu, long long ldo, cudaStream_t st);
+                    long long ldg, long long ldu, long long ldo, const int* live_rows, cudaStream_t st);
 
 // --------------------------------------------------------------------------- Mamba
 int kmoe_conv1d_fwd(const void* x, const float* w, const float* bias, void* y, int B, int S, int C, long long ldx,
@@ -134,12 +135,14 @@ int kmoe_attn_bwd(const void* q, const void* k, const void* v, const void* o, co
 // `*_ptrs`: device addresses (as integers) of the same symmetric buffer on every rank, indexed by rank.
 int kmoe_p2p_barrier(const long long* flag_ptrs, int rank, int world, int epoch, double timeout_s, int* status,
                      cudaStream_t st);
+// mc_ptr: multicast (NVLink switch) address of the same symmetric buffer, or 0 to use plain peer accesses.
 int kmoe_p2p_reduce_scatter(const long long* grad_ptrs, int rank, int world, long long off, long long n,
-                            float* sq_out, cudaStream_t st);
+                            float* sq_out, long long mc_ptr, cudaStream_t st);
 int kmoe_p2p_adamw_allgather(const long long* param_ptrs, const void* grad, float* m, float* v, int rank, int world,
                              long long off, long long n, float lr, float beta1, float beta2, float eps, float wd,
-                             int step, const float* clip_coef, cudaStream_t st);
-int kmoe_p2p_allgather(const long long* buf_ptrs, int rank, int world, long long off, long long n, cudaStream_t st);
+                             int step, const float* clip_coef, long long mc_ptr, cudaStream_t st);
+int kmoe_p2p_allgather(const long long* buf_ptrs, int rank, int world, long long off, long long n, long long mc_ptr,
+                       cudaStream_t st);
 
 // Expert-parallel token exchange.  E experts are split evenly over `world` ranks (expert e lives on rank
 // e / (E / world)).  The receive buffer of a rank holds (E / world) * world slots of `cap` rows; slot

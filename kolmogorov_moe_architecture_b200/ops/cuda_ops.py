@@ -172,13 +172,13 @@ class _SwiGLU(torch.autograd.Function):
     def forward(ctx, g, u):
         ctx.save_for_backward(g, u)
         _count()
-        return K.swiglu_fwd(g, u)
+        return K.swiglu_fwd(g, u, None)
 
     @staticmethod
     def backward(ctx, dh):
         g, u = ctx.saved_tensors
         _count()
-        dg, du = K.swiglu_bwd(g, u, dh.contiguous())
+        dg, du = K.swiglu_bwd(g, u, dh.contiguous(), None)
         return dg, du
 
 
@@ -303,7 +303,7 @@ class _GroupedSwiGLU(torch.autograd.Function):
         dH = torch.empty(max_rows, f, dtype=dout.dtype, device=dout.device)
         gemm(dYp, w3, dH, mode=GROUPED_M, M=max_rows, N=f, Kd=d, groups=E, lda=d, ldb=d, ldc=f, b_gs=f * d,
              tile_group=tile_group, num_m_tiles=nmt)
-        dG, dU = K.swiglu_bwd(G, U, dH)
+        dG, dU = K.swiglu_bwd(G, U, dH, meta[1:2])
         dXp = torch.empty(max_rows, d, dtype=dout.dtype, device=dout.device)
         gemm(dG, w1, dXp, mode=GROUPED_M, M=max_rows, N=d, Kd=f, groups=E, lda=f, ldb=f, ldc=d, b_gs=d * f,
              tile_group=tile_group, num_m_tiles=nmt)
@@ -313,7 +313,7 @@ class _GroupedSwiGLU(torch.autograd.Function):
         # weight gradients: per expert, reduction over that expert's (padded) row range
         kb = offsets[:E].contiguous()
         kl = (offsets[1:] - offsets[:E]).contiguous()
-        H = K.swiglu_fwd(G, U)
+        H = K.swiglu_fwd(G, U, meta[1:2])
         dw1 = torch.empty_like(w1)
         dw2 = torch.empty_like(w2)
         dw3 = torch.empty_like(w3)

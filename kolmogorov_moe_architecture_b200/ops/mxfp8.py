@@ -205,7 +205,7 @@ class _GroupedSwiGLUMX(torch.autograd.Function):
         W3r, s3r = _weight_quant(w3, "rows")                  # (E, f, d): reduction over d
         dH = torch.empty(R, f, dtype=dout.dtype, device=dout.device)
         gemm_mx(dYq, sdY, W3r, s3r, dH, M=R, N=f, K=d, **grp)
-        dG, dU = K.swiglu_bwd(G, U, dH)
+        dG, dU = K.swiglu_bwd(G, U, dH, live)
         dGq, sdG = quant_rows(dG, live_rows=live)
         dUq, sdU = quant_rows(dU, live_rows=live)
         W1r, s1r = _weight_quant(w1, "rows")                  # (E, d, f): reduction over f
@@ -217,7 +217,7 @@ class _GroupedSwiGLUMX(torch.autograd.Function):
         # weight gradients: reduction over each expert's (padded) token rows
         kb = offsets[:E].contiguous()
         kl = (offsets[1:] - offsets[:E]).contiguous()
-        H = K.swiglu_fwd(G, U)
+        H = K.swiglu_fwd(G, U, live)
         XT, sXT = quant_cols(Xp, live_rows=live)              # (d, R)
         dGT, sdGT = quant_cols(dG, live_rows=live)            # (f, R)
         dUT, sdUT = quant_cols(dU, live_rows=live)

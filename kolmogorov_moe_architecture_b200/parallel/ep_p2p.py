@@ -38,7 +38,7 @@ from typing import Dict, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-from .p2p import _group_name
+from .p2p import _group_name, peer_ptrs
 
 
 def _round_up(x: int, m: int) -> int:
@@ -78,10 +78,10 @@ class EPBuffers:
         torch.cuda.synchronize(device)
         hs = [symm.rendezvous(t, name) for t in (self.recv, self.ret, self.meta, self.flags)]
         self._h = hs
-        self.recv_ptrs = [int(p) for p in hs[0].buffer_ptrs]
-        self.ret_ptrs = [int(p) for p in hs[1].buffer_ptrs]
-        self.meta_ptrs = [int(p) for p in hs[2].buffer_ptrs]
-        self.flag_ptrs = [int(p) for p in hs[3].buffer_ptrs]
+        self.recv_ptrs = peer_ptrs(hs[0], self.recv, self.rank)
+        self.ret_ptrs = peer_ptrs(hs[1], self.ret, self.rank)
+        self.meta_ptrs = peer_ptrs(hs[2], self.meta, self.rank)
+        self.flag_ptrs = peer_ptrs(hs[3], self.flags, self.rank)
         self.epoch = 0
         self.timeout_s = barrier_timeout_s
         self.status = cuda_ops.status_tensor(device)
@@ -179,7 +179,7 @@ class _EPFusedFFN(torch.autograd.Function):
         dH = torch.empty(R, f, dtype=dout.dtype, device=dout.device)
         C.gemm(dYp, w3, dH, mode=C.GROUPED_M, M=R, N=f, Kd=d, groups=nl, lda=d, ldb=d, ldc=f, b_gs=f * d,
                tile_group=tile_group, num_m_tiles=nmt)
-        dG, dU = K.swiglu_bwd(G, U, dH)
+        dG, dU = K.swiglu_bwd(G, U, dH, meta_l[1:2])      # buffers are worst-case sized: touch live rows only
         dXp = torch.empty(R, d, dtype=dout.dtype, device=dout.device)
         C.gemm(dG, w1, dXp, mode=C.GROUPED_M, M=R, N=d, Kd=f, groups=nl, lda=f, ldb=f, ldc=d, b_gs=d * f,
                tile_group=tile_group, num_m_tiles=nmt)
@@ -193,7 +193,7 @@ class _EPFusedFFN(torch.autograd.Function):
             dwts = K.moe_combine_dw(Yret, dout, pos, k).view(T, k).to(ctx.wdtype)
         kb = offs_l[:nl].contiguous()
         kl = (offs_l[1:] - offs_l[:nl]).contiguous()
-        H = K.swiglu_fwd(G, U)
+        H = K.swiglu_fwd(G, U, meta_l[1:2])
         dw1, dw2, dw3 = torch.empty_like(w1), torch.empty_like(w2), torch.empty_like(w3)
         common = dict(mode=C.BATCHED, groups=nl, a_major=C.MAJ_MN, b_major=C.MAJ_MN, Kd=R, k_begin=kb, k_len=kl)
         C.gemm(Xp, dG, dw1, M=d, N=f, lda=d, ldb=f, ldc=f, c_gs=d * f, **common)

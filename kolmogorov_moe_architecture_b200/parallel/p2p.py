@@ -4,12 +4,15 @@ Buffers are allocated with ``torch.distributed._symmetric_memory`` (CUDA VMM all
 whose handles are exchanged at rendezvous and mapped into every rank of the group), which
 gives each rank a device pointer to every peer's copy.  The collectives themselves are this
 library's kernels (``csrc/comm.cu``): plain 16-byte loads and stores through those peer
-pointers over NVLink, never TMA multicast.  Cross-rank ordering uses a flag barrier whose
+pointers over NVLink, never TMA multicast; on an NVSwitch system the reduce-scatter and the
+parameter publication use the switch instead (``multimem.ld_reduce`` / ``multimem.st`` on the
+buffers' multicast addresses), which moves ~1/world of the bytes through each GPU's port.  Cross-rank ordering uses a flag barrier whose
 wait is bounded by a wall-clock limit; on expiry the kernel sets the status word that
 ``ops.cuda_ops.check_status`` reports, and the context stays usable.
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional
 
 import torch
@@ -29,6 +32,26 @@ def p2p_available(device) -> bool:
 def _group_name(group) -> str:
     g = group if group is not None else dist.group.WORLD
     return g.group_name
+
+
+def _delta(handle, tensor, rank: int) -> int:
+    """Byte offset of ``tensor`` inside its symmetric allocation (the allocator may sub-allocate)."""
+    return int(tensor.data_ptr()) - int(handle.buffer_ptrs[rank])
+
+
+def peer_ptrs(handle, tensor, rank: int) -> List[int]:
+    """Device address of ``tensor``'s counterpart on every rank."""
+    d = _delta(handle, tensor, rank)
+    return [int(p) + d for p in handle.buffer_ptrs]
+
+
+def multicast_ptr(handle, tensor, rank: int) -> int:
+    """NVLink-switch multicast address of ``tensor`` (0 when the fabric offers none)."""
+    try:
+        base = int(handle.multicast_ptr or 0)
+    except Exception:
+        base = 0
+    return base + _delta(handle, tensor, rank) if base else 0
 
 
 class SymmetricBuffers:
@@ -54,9 +77,18 @@ class SymmetricBuffers:
         self.flags.zero_()
         torch.cuda.synchronize(device)
         self._h = [symm.rendezvous(t, name) for t in (self.param, self.grad, self.flags)]
-        self.param_ptrs: List[int] = [int(p) for p in self._h[0].buffer_ptrs]
-        self.grad_ptrs: List[int] = [int(p) for p in self._h[1].buffer_ptrs]
-        self.flag_ptrs: List[int] = [int(p) for p in self._h[2].buffer_ptrs]
+        self.param_ptrs: List[int] = peer_ptrs(self._h[0], self.param, self.rank)
+        self.grad_ptrs: List[int] = peer_ptrs(self._h[1], self.grad, self.rank)
+        self.flag_ptrs: List[int] = peer_ptrs(self._h[2], self.flags, self.rank)
+        # NVLink-switch multicast addresses of the two big buffers (0 = not available / switched off).
+        # The switch path pays off once several peers would otherwise be read one by one: default on from
+        # 4 ranks (at 2 ranks it moves the same bytes and measured slower).  KMOE_MULTIMEM=1/0 forces it;
+        # NCCL_NVLS_ENABLE=0 keeps every kernel on plain peer loads and stores.
+        want = os.environ.get("KMOE_MULTIMEM", "auto")
+        use_mc = (self.world > 1 and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0"
+                  and (want == "1" or (want == "auto" and self.world >= 4)))
+        self.param_mc: int = multicast_ptr(self._h[0], self.param, self.rank) if use_mc else 0
+        self.grad_mc: int = multicast_ptr(self._h[1], self.grad, self.rank) if use_mc else 0
         self.epoch = 0
         self.timeout_s = barrier_timeout_s
         self.status = cuda_ops.status_tensor(device)
@@ -70,10 +102,10 @@ class SymmetricBuffers:
 
     def reduce_scatter_mean(self, off: int, n: int, sq_out: Optional[torch.Tensor]) -> None:
         from ..ops import cuda_ops
-        torch.ops.kmoe.p2p_reduce_scatter(self.grad_ptrs, self.rank, self.world, off, n, sq_out)
+        torch.ops.kmoe.p2p_reduce_scatter(self.grad_ptrs, self.rank, self.world, off, n, sq_out, self.grad_mc)
         cuda_ops._count()
 
     def all_gather_range(self, off: int, n: int) -> None:
         from ..ops import cuda_ops
-        torch.ops.kmoe.p2p_allgather(self.param_ptrs, self.rank, self.world, off, n)
+        torch.ops.kmoe.p2p_allgather(self.param_ptrs, self.rank, self.world, off, n, self.param_mc)
         cuda_ops._count()

@@ -74,13 +74,13 @@ class FusedAdamW:
         self.param_groups = [dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay, params=[])]
         self.step_count = 0
 
-    def step(self, param_ptrs: List[int], rank: int, clip_coef: Optional[torch.Tensor]):
+    def step(self, param_ptrs: List[int], rank: int, clip_coef: Optional[torch.Tensor], mc_ptr: int = 0):
         from ..ops import cuda_ops
         g = self.param_groups[0]
         self.step_count += 1
         torch.ops.kmoe.p2p_adamw_allgather(param_ptrs, self.flat_grad, self.m, self.v, rank, len(param_ptrs),
                                            self.start, self.n, g["lr"], g["betas"][0], g["betas"][1], g["eps"],
-                                           g["weight_decay"], self.step_count, clip_coef)
+                                           g["weight_decay"], self.step_count, clip_coef, mc_ptr)
         cuda_ops._count()
 
     def state_dict(self):
@@ -248,6 +248,7 @@ class ShardedDataParallel:
         a0 = self.rank * self.seg
         ptrs = self.p2p.param_ptrs if self.transport == "p2p" else [self.flat_param.data_ptr()]
         prank = self.rank if self.transport == "p2p" else 0
+        mc = self.p2p.param_mc if self.transport == "p2p" else 0
         # The fused AdamW kernel is HBM-bound and Muon's Newton-Schulz is tensor-core-bound: run them
         # on two streams so they overlap (they touch disjoint ranges of the flat buffers).
         side = None
@@ -257,9 +258,9 @@ class ShardedDataParallel:
             side = self._side_stream
             side.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(side):
-                self.fused.step(ptrs, prank, self._clip)
+                self.fused.step(ptrs, prank, self._clip, mc)
         elif self.fused is not None:
-            self.fused.step(ptrs, prank, self._clip)
+            self.fused.step(ptrs, prank, self._clip, mc)
         if self.adamw is not None:
             self.adamw.step()
         if self.muon is not None:

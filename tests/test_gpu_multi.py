@@ -41,16 +41,28 @@ ref = out["nccl"].abs().max().item()
 mine = out["p2p"].clone(); other = mine.clone(); dist.broadcast(other, 0)
 assert torch.equal(mine, other), "ranks diverged"
 assert err < 2e-2 * ref, (err, ref)
-if rank == 0: print("MULTI_OK", err)
+want_mc = os.environ.get("KMOE_EXPECT_MULTIMEM") == "1"
+if want_mc:
+    assert dp.p2p.grad_mc != 0 and dp.p2p.param_mc != 0, "no multicast address on this fabric"
+else:
+    assert dp.p2p.grad_mc == 0
+if rank == 0: print("MULTI_OK", err, "multimem" if want_mc else "peer")
 dist.destroy_process_group()
 '''
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_p2p_transport_matches_nccl_2gpus(tmp_path):
+@pytest.mark.parametrize("multimem", [False, True])
+def test_p2p_transport_matches_nccl_2gpus(tmp_path, multimem):
+    """Plain peer loads/stores, and the NVLink-switch path (multimem.ld_reduce / multimem.st)."""
     f = tmp_path / "worker.py"
     f.write_text(WORKER)
-    env = dict(os.environ, KMOE_ROOT=ROOT, NCCL_NVLS_ENABLE="0", KMOE_STRICT="1")
+    env = dict(os.environ, KMOE_ROOT=ROOT, KMOE_STRICT="1")
+    if multimem:
+        env.pop("NCCL_NVLS_ENABLE", None)
+        env.update(KMOE_MULTIMEM="1", KMOE_EXPECT_MULTIMEM="1")
+    else:
+        env.update(NCCL_NVLS_ENABLE="0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29581", str(f)],
                        env=env, capture_output=True, text=True, timeout=600)

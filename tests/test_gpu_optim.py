@@ -31,7 +31,7 @@ def test_fused_adamw_kernel_matches_torch():
         g = torch.randn(n, device="cuda").to(torch.bfloat16)
         flat_g.copy_(g)
         torch.ops.kmoe.p2p_adamw_allgather([flat_p.data_ptr()], flat_g, m, v, 0, 1, 0, n, 1e-2, 0.9, 0.95, 1e-8, 0.1,
-                                           step, coef)
+                                           step, coef, 0)
         ref_p.grad = g.float() * 0.5
         opt.step()
     err = (flat_p.float() - ref_p.detach()).abs().max().item()
