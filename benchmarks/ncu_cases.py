@@ -1,6 +1,6 @@
 """Small single-kernel workloads for Nsight Compute captures.
 
-    python benchmarks/ncu_cases.py --case gemm|moe|attn|scan|adamw|ce|mxfp8 [--launches 4]
+    python benchmarks/ncu_cases.py --case gemm|moe|attn|scan|adamw|ce|mxfp8|ep_dispatch|ep_gemm2 [--launches 4]
 
 Each case holds well under 2 GB on the device, uses operands larger than L2 where the kernel is
 bandwidth-sensitive, and launches the kernel of interest a handful of times so that
@@ -64,6 +64,37 @@ def main():
         gs = torch.full((1,), 1.0 / R, device="cuda")
         for _ in range(n):
             torch.ops.kmoe.ce_fwd_bwd(logits, labels, gs, -100, True)
+    elif a.case in ("ep_dispatch", "ep_gemm2"):
+        # the expert-parallel kernels in a one-rank group (the "peer" pointers are this GPU's own buffers), so a
+        # single process can be profiled: dispatch (permute + exchange) and GEMM 2 with the row-pointer epilogue
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29711")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+        from kolmogorov_moe_architecture_b200.parallel import ep_p2p
+        K = torch.ops.kmoe
+        T, d, f, E, k = 16384, 2048, 4096, 16, 2
+        x = bf(T, d, sc=1.0)
+        wts, idx = eager.topk_softmax_route(torch.randn(T, E, device="cuda"), k)
+        buf = ep_p2p.get_buffers(T, k, d, E, torch.bfloat16, x.device, None)
+        pos, row_src, counts, offsets, _tg, _m = K.moe_plan(idx.reshape(-1).contiguous(), None, E, 0)
+        for _ in range(n):
+            K.ep_dispatch(x, row_src, None, offsets, counts, buf.recv_ptrs, buf.meta_ptrs, 0, 1, E, buf.cap, k)
+        buf.barrier()
+        meta_in = buf.meta.clone()
+        R = buf.max_rows_exp
+        slot_dst, offs_l, tile_group, meta_l = K.ep_recv_plan(meta_in, E, 1, R)
+        Xp = torch.empty(R, d, dtype=torch.bfloat16, device="cuda")
+        row_ptr = torch.empty(R, dtype=torch.int64, device="cuda")
+        K.ep_move(buf.recv, Xp, meta_in, slot_dst, offs_l, buf.ret_ptrs, 0, E, 1, buf.cap, 0, row_ptr)
+        H, w3 = bf(R, f, sc=1.0), bf(E, f, d)
+        for _ in range(n):
+            c.gemm(H, w3, Xp, mode=c.GROUPED_M, M=R, N=d, Kd=f, groups=E, b_major=c.MAJ_MN, lda=f, ldb=d, ldc=d,
+                   b_gs=f * d, tile_group=tile_group, num_m_tiles=meta_l[0:1], row_ptr=row_ptr)
+        torch.cuda.synchronize()
+        c.check_status()
+        ep_p2p.release_buffers()
+        dist.destroy_process_group()
     elif a.case == "mxfp8":
         from kolmogorov_moe_architecture_b200.ops import mxfp8 as mx
         M, N, K = 8192, 8192, 2048

@@ -36,7 +36,8 @@ void gemm(const Tensor& A, const Tensor& B, const OptT& B2, Tensor C, const OptT
           int64_t mode, int64_t epilogue, int64_t M, int64_t N, int64_t K, int64_t groups, int64_t a_major,
           int64_t b_major, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, int64_t a_gs, int64_t b_gs,
           int64_t c_gs, const OptT& tile_group, const OptT& num_m_tiles, const OptT& k_begin, const OptT& k_len,
-          double alpha, double beta, const OptT& row_scale, const OptT& row_ptr, Tensor status) {
+          double alpha, double beta, const OptT& row_scale, const OptT& row_ptr, const OptT& alpha_dev,
+          const OptT& beta_dev, Tensor status) {
   c10::cuda::CUDAGuard guard(A.device());
   need_bf16(A, "A");
   need_bf16(B, "B");
@@ -56,6 +57,17 @@ void gemm(const Tensor& A, const Tensor& B, const OptT& B2, Tensor C, const OptT
     TORCH_CHECK(row_ptr->scalar_type() == at::kLong && row_ptr->is_contiguous() && row_ptr->numel() >= M &&
                 epilogue == KMOE_EPI_STORE, "row_ptr: int64, one entry per output row, plain store epilogue");
     d.c_row_ptr = (const long long*)row_ptr->data_ptr<int64_t>();
+  }
+  const int64_t n_groups = mode == KMOE_GEMM_BATCHED ? groups : 1;
+  if (alpha_dev.has_value() && alpha_dev->defined()) {
+    need_f32(*alpha_dev, "alpha_dev");
+    TORCH_CHECK(alpha_dev->numel() >= n_groups);
+    d.alpha_dev = alpha_dev->data_ptr<float>();
+  }
+  if (beta_dev.has_value() && beta_dev->defined()) {
+    need_f32(*beta_dev, "beta_dev");
+    TORCH_CHECK(beta_dev->numel() >= n_groups);
+    d.beta_dev = beta_dev->data_ptr<float>();
   }
   TORCH_CHECK(status.scalar_type() == at::kInt && status.is_cuda(), "status must be a CUDA int32 tensor");
   d.status = status.data_ptr<int>();
@@ -329,6 +341,27 @@ void p2p_allgather(std::vector<int64_t> buf_ptrs, int64_t rank, int64_t world, i
         "p2p_allgather");
 }
 
+// ------------------------------------------------------------- Muon elementwise passes
+void muon_momentum(Tensor buf, const Tensor& grad_ptrs, Tensor sumsq, double mu) {
+  c10::cuda::CUDAGuard guard(buf.device());
+  need_bf16(buf, "buf"); need_f32(sumsq, "sumsq");
+  TORCH_CHECK(buf.is_contiguous() && buf.dim() == 3 && grad_ptrs.scalar_type() == at::kLong &&
+              grad_ptrs.numel() == buf.size(0) && sumsq.numel() == buf.size(0));
+  check(kmoe_muon_momentum(buf.data_ptr(), (const long long*)grad_ptrs.data_ptr<int64_t>(), sumsq.data_ptr<float>(),
+                           (int)buf.size(0), buf.size(1) * buf.size(2), (float)mu, cur_stream()), "muon_momentum");
+}
+
+void muon_apply(Tensor buf, const Tensor& ortho, const Tensor& grad_ptrs, const Tensor& param_ptrs, double lr,
+                double mu, double wd, bool nesterov) {
+  c10::cuda::CUDAGuard guard(buf.device());
+  need_bf16(buf, "buf"); need_bf16(ortho, "ortho");
+  TORCH_CHECK(buf.is_contiguous() && ortho.is_contiguous() && buf.sizes() == ortho.sizes() && buf.dim() == 3);
+  TORCH_CHECK(grad_ptrs.numel() == buf.size(0) && param_ptrs.numel() == buf.size(0));
+  check(kmoe_muon_apply(buf.data_ptr(), ortho.data_ptr(), (const long long*)grad_ptrs.data_ptr<int64_t>(),
+                        (const long long*)param_ptrs.data_ptr<int64_t>(), (int)buf.size(0), buf.size(1) * buf.size(2),
+                        (float)lr, (float)mu, (float)wd, nesterov ? 1 : 0, cur_stream()), "muon_apply");
+}
+
 // ------------------------------------------------------------- MXFP8
 // x: (..., C) bf16 with collapsing leading dims -> (q e4m3 same shape, scale chunks uint8)
 std::vector<Tensor> mx_quant_rows(const Tensor& x, const OptT& x2, const OptT& live_rows) {
@@ -505,6 +538,8 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("p2p_reduce_scatter", &p2p_reduce_scatter);
   m.def("p2p_adamw_allgather", &p2p_adamw_allgather);
   m.def("p2p_allgather", &p2p_allgather);
+  m.def("muon_momentum", &muon_momentum);
+  m.def("muon_apply", &muon_apply);
   m.def("mx_quant_rows", &mx_quant_rows);
   m.def("mx_quant_cols", &mx_quant_cols);
   m.def("gemm_mxfp8", &gemm_mxfp8);

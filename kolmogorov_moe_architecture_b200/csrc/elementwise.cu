@@ -325,3 +325,96 @@ extern "C" int kmoe_rmsnorm_bwd_noalloc(const void* x, const void* w, const void
   colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, nullptr, dw_f32, parts, d);
   return cudaGetLastError() == cudaSuccess ? 0 : KMOE_NOALLOC_E_LAUNCH;
 }
+
+// ------------------------------------------------- Muon: momentum update and parameter update, one pass each
+// (the orthogonalisation between them is the batched Newton-Schulz GEMM loop).  grid.y = matrix index.
+namespace kmoe {
+
+__global__ void muon_momentum_kernel(__nv_bfloat16* __restrict__ buf, const long long* __restrict__ grad_ptrs,
+                                     float* __restrict__ sumsq, long long numel, float mu) {
+  const int mi = blockIdx.y;
+  __nv_bfloat16* b = buf + (long long)mi * numel;
+  const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(grad_ptrs[mi]);
+  const long long nvec = numel / 8;
+  float sq = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float bv[8], gv[8];
+    unpack8(*(reinterpret_cast<const uint4*>(b) + i), bv);
+    unpack8(*(reinterpret_cast<const uint4*>(g) + i), gv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) bv[j] = mu * bv[j] + gv[j];
+    const uint4 o = pack8(bv);
+    *(reinterpret_cast<uint4*>(b) + i) = o;
+    float rv[8];
+    unpack8(o, rv);                      // the norm of what is stored (bf16-rounded), as the GEMMs will see it
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sq += rv[j] * rv[j];
+  }
+  sq = warp_sum(sq);
+  __shared__ float s[32];
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? s[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) atomicAdd(&sumsq[mi], t);
+  }
+}
+
+__global__ void muon_apply_kernel(__nv_bfloat16* __restrict__ buf, const __nv_bfloat16* __restrict__ ortho,
+                                  const long long* __restrict__ grad_ptrs, const long long* __restrict__ param_ptrs,
+                                  long long numel, float lr, float mu, float wd, int nesterov) {
+  const int mi = blockIdx.y;
+  __nv_bfloat16* b = buf + (long long)mi * numel;
+  const __nv_bfloat16* o = ortho + (long long)mi * numel;
+  const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(grad_ptrs[mi]);
+  __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(param_ptrs[mi]);
+  const long long nvec = numel / 8;
+  const float decay = 1.f - lr * wd;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const uint4 ov = *(reinterpret_cast<const uint4*>(o) + i);
+    float of[8], gf[8], pf[8];
+    unpack8(ov, of);
+    unpack8(*(reinterpret_cast<const uint4*>(p) + i), pf);
+    if (nesterov) {
+      unpack8(*(reinterpret_cast<const uint4*>(g) + i), gf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        // same rounding points as the unfused sequence: p*decay -> bf16, g + mu*o -> bf16, then the update
+        const float pd = __bfloat162float(__float2bfloat16(pf[j] * decay));
+        const float up = __bfloat162float(__float2bfloat16(gf[j] + mu * of[j]));
+        pf[j] = pd - lr * up;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) pf[j] = __bfloat162float(__float2bfloat16(pf[j] * decay)) - lr * of[j];
+    }
+    *(reinterpret_cast<uint4*>(p) + i) = pack8(pf);
+    *(reinterpret_cast<uint4*>(b) + i) = ov;
+  }
+}
+
+}  // namespace kmoe
+
+extern "C" int kmoe_muon_momentum(void* buf, const long long* grad_ptrs, float* sumsq, int n_mat, long long numel,
+                                  float mu, cudaStream_t st) {
+  if (numel % 8 || n_mat <= 0 || n_mat > 65535) return -1;
+  const long long per = (numel / 8 + 255) / 256;
+  const long long cap = 2368 / n_mat > 64 ? 2368 / n_mat : 64;      // ~16 CTAs per SM over all matrices
+  dim3 grid((unsigned)(per < cap ? per : cap), n_mat);
+  kmoe::muon_momentum_kernel<<<grid, 256, 0, st>>>((__nv_bfloat16*)buf, grad_ptrs, sumsq, numel, mu);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_muon_apply(void* buf, const void* ortho, const long long* grad_ptrs, const long long* param_ptrs,
+                               int n_mat, long long numel, float lr, float mu, float wd, int nesterov, cudaStream_t st) {
+  if (numel % 8 || n_mat <= 0 || n_mat > 65535) return -1;
+  const long long per = (numel / 8 + 255) / 256;
+  const long long cap = 2368 / n_mat > 64 ? 2368 / n_mat : 64;
+  dim3 grid((unsigned)(per < cap ? per : cap), n_mat);
+  kmoe::muon_apply_kernel<<<grid, 256, 0, st>>>((__nv_bfloat16*)buf, (const __nv_bfloat16*)ortho, grad_ptrs, param_ptrs,
+                                                numel, lr, mu, wd, nesterov);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

@@ -46,6 +46,8 @@ struct GemmArgs {
   int out_f32;
   float alpha, beta;
   const float* row_scale;
+  const float* alpha_dev;     // optional per-group multipliers of alpha / beta (BATCHED: index = group)
+  const float* beta_dev;
   const long long* row_ptr;   // optional: address of each output row (may be peer memory); 0 = row not stored
   int* status;
 };
@@ -136,7 +138,7 @@ __device__ __forceinline__ void load8(const float* src, float* v) {
 template <typename T>
 __device__ __forceinline__ void epilogue_store_chunk(const GemmArgs& a, const uint32_t (&acc)[32], bool have_acc,
                                                      long long row_off_c, long long row_off_d, int col, float scale,
-                                                     long long row_addr) {
+                                                     float beta, long long row_addr) {
   // row_addr != 0: the row's own base address (possibly on a peer GPU) replaces C + row offset
   T* C = row_addr ? reinterpret_cast<T*>(row_addr) - row_off_c : reinterpret_cast<T*>(a.C);
   const T* D = reinterpret_cast<const T*>(a.D);
@@ -150,7 +152,7 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmArgs& a, const ui
       float d[8];
       load8(D + row_off_d + col + j, d);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] += a.beta * d[i];
+      for (int i = 0; i < 8; ++i) v[i] += beta * d[i];
     }
     store8<T>(C + row_off_c + col + j, v);
   }
@@ -306,6 +308,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const long long coff = (long long)t.g_c * args.c_gstride + (long long)row * args.ldc;
       const long long doff = (long long)t.g_c * args.c_gstride + (long long)row * args.ldd;
       float scale = args.alpha;
+      float beta = args.beta;
+      if (args.alpha_dev != nullptr) scale *= args.alpha_dev[t.g_c];
+      if (args.beta_dev != nullptr) beta *= args.beta_dev[t.g_c];
       if (args.row_scale != nullptr && row_ok) scale *= args.row_scale[row];
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
       long long row_addr = 0;
@@ -339,7 +344,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 float d[8];
                 load8(Dp + doff + col + j, d);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] += args.beta * d[i];
+                for (int i = 0; i < 8; ++i) v[i] += beta * d[i];
               }
               store8<__nv_bfloat16>(&stg[lane][h * 32 + j], v);
             }
@@ -368,9 +373,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int col = t.n_tile * BN + c;
           if (store_ok && col < args.N) {
             if (args.out_f32)
-              epilogue_store_chunk<float>(args, r, have_acc, coff, doff, col, scale, row_addr);
+              epilogue_store_chunk<float>(args, r, have_acc, coff, doff, col, scale, beta, row_addr);
             else
-              epilogue_store_chunk<__nv_bfloat16>(args, r, have_acc, coff, doff, col, scale, row_addr);
+              epilogue_store_chunk<__nv_bfloat16>(args, r, have_acc, coff, doff, col, scale, beta, row_addr);
           }
         }
       } else {
@@ -518,6 +523,7 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
   a.k_begin = d->k_begin; a.k_len = d->k_len;
   a.out_f32 = d->out_f32; a.alpha = d->alpha; a.beta = d->beta;
   a.row_scale = d->row_scale; a.row_ptr = d->c_row_ptr; a.status = d->status;
+  a.alpha_dev = d->alpha_dev; a.beta_dev = d->beta_dev;
 
   // The reduction extent seen by TMA: ragged batched GEMMs index a shared [sum K, rows] buffer.
   long long k_extent_a = d->K, k_extent_b = d->K;

@@ -43,12 +43,26 @@ typedef struct KmoeGemmDesc {
   // optional (STORE epilogue): device array with the address of every output row, which may lie in a
   // peer GPU's memory; 0 skips the row.  Replaces C + row * ldc; D is still read at its usual place.
   const long long* c_row_ptr;
+  // optional device arrays, one entry per group of a BATCHED GEMM (entry 0 otherwise): alpha and beta are
+  // multiplied by them, so scalars computed on the device (e.g. 1 / norm) need no separate pass.
+  const float* alpha_dev;
+  const float* beta_dev;
   int* status;             // device int; non-zero after the launch = a bounded wait expired
   int num_sms;             // 0 = query
 } KmoeGemmDesc;
 
 int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream);
 void kmoe_gemm_clear_tensormap_cache(void);
+
+// ------------------------------------------------------------ Muon elementwise passes
+// `n_mat` matrices of `numel` bf16 elements each.  buf: stacked momentum (n_mat, numel); grad_ptrs / param_ptrs:
+// device arrays with the address of each matrix's gradient / parameter.
+//   momentum: buf = mu * buf + grad ; sumsq[i] += sum(buf_i^2)      (sumsq zeroed by the caller)
+//   apply   : param = param * (1 - lr * wd) - lr * (nesterov ? grad + mu * ortho : ortho) ; buf = ortho
+int kmoe_muon_momentum(void* buf, const long long* grad_ptrs, float* sumsq, int n_mat, long long numel, float mu,
+                       cudaStream_t st);
+int kmoe_muon_apply(void* buf, const void* ortho, const long long* grad_ptrs, const long long* param_ptrs, int n_mat,
+                    long long numel, float lr, float mu, float wd, int nesterov, cudaStream_t st);
 
 // ------------------------------------------------------------ MXFP8 (e4m3 + e8m0 1x32 block scales)
 // Scale factors live in 512-byte chunks, one per (128 operand rows, 128 reduction elements):

@@ -82,10 +82,11 @@ def mtp_cross_entropy(hidden, head_weights, labels, weights, ignore_index=-100):
     return eager.mtp_cross_entropy(hidden, head_weights, labels, weights, ignore_index)
 
 
-def newton_schulz(matrix, iters=5):
+def newton_schulz(matrix, iters=5, sumsq=None):
+    """``sumsq``: optional squared Frobenius norms already on the device (see ``cuda_ops.newton_schulz``)."""
     if _use_cuda(matrix):
         from . import cuda_ops
-        return cuda_ops.newton_schulz(matrix, iters)
+        return cuda_ops.newton_schulz(matrix, iters, sumsq)
     return eager.newton_schulz(matrix, iters)
 
 

@@ -63,12 +63,13 @@ def _count(n: int = 1):
 def gemm(A, B, C, *, M, N, Kd, mode=DENSE, epi=EPI_STORE, groups=1, a_major=MAJ_K, b_major=MAJ_K,
          lda, ldb, ldc, ldd=0, a_gs=0, b_gs=0, c_gs=0, B2=None, D=None, G=None, U=None,
          tile_group=None, num_m_tiles=None, k_begin=None, k_len=None, alpha=1.0, beta=0.0, row_scale=None,
-         row_ptr=None):
+         row_ptr=None, alpha_dev=None, beta_dev=None):
     """``row_ptr`` (int64, one address per output row, 0 = skip) redirects each output row, e.g. into a
-    peer GPU's buffer; ``C`` then only supplies the dtype."""
+    peer GPU's buffer; ``C`` then only supplies the dtype.  ``alpha_dev`` / ``beta_dev`` (fp32, one entry
+    per group of a batched GEMM) multiply alpha / beta with values that live on the device."""
     K.gemm(A, B, B2, C, D, G, U, mode, epi, M, N, Kd, groups, a_major, b_major, lda, ldb, ldc, ldd,
            a_gs, b_gs, c_gs, tile_group, num_m_tiles, k_begin, k_len, alpha, beta, row_scale, row_ptr,
-           status_tensor(A.device))
+           alpha_dev, beta_dev, status_tensor(A.device))
     _count()
     return C
 
@@ -501,38 +502,54 @@ def mtp_cross_entropy(hidden, head_weights: Sequence[torch.Tensor], labels, weig
 
 # ------------------------------------------------------------ Newton-Schulz
 @torch.no_grad()
-def newton_schulz(matrix: torch.Tensor, iters: int = 5) -> torch.Tensor:
+def newton_schulz(matrix: torch.Tensor, iters: int = 5, sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Batched cubic Newton-Schulz on the tcgen05 GEMM: per iteration one Gram product and
-    one product with the fused ``1.5 Y - 0.5 (G Y)`` epilogue.  bf16 operands, fp32
-    accumulation; the Frobenius normalisation is done in fp32."""
+    one product with the fused ``1.5 Y - 0.5 (G Y)`` epilogue.  bf16 operands, fp32 accumulation.
+
+    ``sumsq`` (fp32, one entry per matrix: its squared Frobenius norm, already on the device) removes the
+    normalisation passes: the first iteration runs on the unnormalised bf16 input and folds
+    ``s = 1 / (norm + 1e-7)`` into the GEMM epilogues (``G = s^2 X X^T``, ``Y1 = 1.5 s X - 0.5 s G X``)."""
     squeeze = matrix.dim() == 2
     Y = matrix.unsqueeze(0) if squeeze else matrix
     b, m, n = Y.shape
     if m % 64 or n % 64:
         # vectors and odd-sized matrices (e.g. the (1, d) MoD router) are negligible work
         return eager.newton_schulz(matrix, iters)
-    Yf = Y.float()
-    norms = Yf.reshape(b, -1).norm(dim=1).view(b, 1, 1)
-    Ya = (Yf / (norms + 1e-7)).to(torch.bfloat16).contiguous()
+    s1 = s2 = None
+    if sumsq is not None and matrix.dtype == torch.bfloat16 and Y.is_contiguous() and iters > 0:
+        s1 = (1.0 / (sumsq.float().sqrt() + 1e-7)).contiguous()
+        s2 = (s1 * s1).contiguous()
+        Ya = Y
+    else:
+        Yf = Y.float()
+        norms = Yf.reshape(b, -1).norm(dim=1).view(b, 1, 1)
+        Ya = (Yf / (norms + 1e-7)).to(torch.bfloat16).contiguous()
     Yb = torch.empty_like(Ya)
+    Yc = torch.empty_like(Ya) if s1 is not None else None        # never write into the caller's tensor
     wide = m <= n
     g = m if wide else n
     Gm = torch.empty(b, g, g, dtype=torch.bfloat16, device=Y.device)
-    for _ in range(iters):
+    for it in range(iters):
+        first = it == 0 and s1 is not None
+        ga = dict(alpha_dev=s2) if first else {}
+        ya = dict(alpha_dev=s1, beta_dev=s1) if first else {}
         if wide:
             # G = Y Y^T  (A, B K-major over n)
             gemm(Ya, Ya, Gm, mode=BATCHED, groups=b, M=m, N=m, Kd=n, lda=n, ldb=n, ldc=m,
-                 a_gs=m * n, b_gs=m * n, c_gs=m * m)
+                 a_gs=m * n, b_gs=m * n, c_gs=m * m, **ga)
             # Y' = 1.5 Y - 0.5 G Y   (B = Y read MN-major)
             gemm(Gm, Ya, Yb, D=Ya, alpha=-0.5, beta=1.5, mode=BATCHED, groups=b, M=m, N=n, Kd=m,
-                 b_major=MAJ_MN, lda=m, ldb=n, ldc=n, ldd=n, a_gs=m * m, b_gs=m * n, c_gs=m * n)
+                 b_major=MAJ_MN, lda=m, ldb=n, ldc=n, ldd=n, a_gs=m * m, b_gs=m * n, c_gs=m * n, **ya)
         else:
             # G = Y^T Y  (both MN-major over m)
             gemm(Ya, Ya, Gm, mode=BATCHED, groups=b, M=n, N=n, Kd=m, a_major=MAJ_MN, b_major=MAJ_MN,
-                 lda=n, ldb=n, ldc=n, a_gs=m * n, b_gs=m * n, c_gs=n * n)
+                 lda=n, ldb=n, ldc=n, a_gs=m * n, b_gs=m * n, c_gs=n * n, **ga)
             # Y' = 1.5 Y - 0.5 Y G   (G symmetric: read K-major)
             gemm(Ya, Gm, Yb, D=Ya, alpha=-0.5, beta=1.5, mode=BATCHED, groups=b, M=m, N=n, Kd=n,
-                 lda=n, ldb=n, ldc=n, ldd=n, a_gs=m * n, b_gs=n * n, c_gs=m * n)
-        Ya, Yb = Yb, Ya
+                 lda=n, ldb=n, ldc=n, ldd=n, a_gs=m * n, b_gs=n * n, c_gs=m * n, **ya)
+        if first:
+            Ya, Yb = Yb, Yc
+        else:
+            Ya, Yb = Yb, Ya
     out = Ya.to(matrix.dtype)
     return out.squeeze(0) if squeeze else out

@@ -94,6 +94,38 @@ class Muon(Optimizer):
         cache[key] = out
         return out
 
+    @staticmethod
+    def _fused_ok(stacked, ps, standard) -> bool:
+        """The fused kernels cover the default rule on CUDA bf16 matrices whose sides are multiples of 64."""
+        if standard or not stacked.is_cuda or stacked.dtype != torch.bfloat16:
+            return False
+        if os.environ.get("KMOE_MUON_FUSED", "1") == "0":
+            return False
+        if stacked.shape[1] % 64 or stacked.shape[2] % 64:
+            return False
+        from ..ops import ext_available
+        return ext_available() and all(p.is_contiguous() and p.grad.is_contiguous() and p.grad.dtype == torch.bfloat16
+                                       for p in ps)
+
+    def _bucket_ptrs(self, stacked, ps):
+        """Device arrays with the address of every matrix's gradient and parameter (rebuilt only when an
+        address changes, e.g. after ``zero_grad(set_to_none=True)``)."""
+        numel_b = stacked.shape[1] * stacked.shape[2] * stacked.element_size()
+        sig = tuple((p.grad.data_ptr(), p.data_ptr()) for p in ps)
+        cache = self.__dict__.setdefault("_ptr_cache", {})
+        hit = cache.get(id(stacked))
+        if hit is not None and hit[0] == sig:
+            return hit[1], hit[2]
+        gl, pl = [], []
+        for p in ps:
+            for e in range(_as_matrix_batch(p).shape[0]):
+                gl.append(p.grad.data_ptr() + e * numel_b)
+                pl.append(p.data_ptr() + e * numel_b)
+        gp = torch.tensor(gl, dtype=torch.int64).to(stacked.device)
+        pp = torch.tensor(pl, dtype=torch.int64).to(stacked.device)
+        cache[id(stacked)] = (sig, gp, pp)
+        return gp, pp
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = None
@@ -107,10 +139,15 @@ class Muon(Optimizer):
             live = [p for p in group["params"] if p.grad is not None]
             if not live:
                 continue
-            if wd != 0:
-                torch._foreach_mul_(live, 1 - lr * wd)
             vecs = [p for p in live if p.dim() < 2]
             mats = [p for p in live if p.dim() >= 2]
+            buckets = self._bucket_state(gi, mats) if (mats and backend != "qr") else []
+            fused = [self._fused_ok(stacked, ps, standard) for stacked, ps, _ in buckets]
+            in_fused = {id(p) for (b, ok) in zip(buckets, fused) if ok for p in b[1]}
+            if wd != 0:
+                decay = [p for p in live if id(p) not in in_fused]      # fused buckets decay inside their kernel
+                if decay:
+                    torch._foreach_mul_(decay, 1 - lr * wd)
             for p in vecs:
                 st = self.state[p]
                 if "momentum_buffer" not in st:
@@ -136,8 +173,19 @@ class Muon(Optimizer):
                     o = torch.stack([_qr_orthogonalize(x) for x in mb]).reshape(buf.shape)
                     self._apply(p, g, buf, o, lr, mu, nesterov, standard)
                 continue
-            for stacked, ps, views in self._bucket_state(gi, mats):
+            for (stacked, ps, views), ok in zip(buckets, fused):
                 grads = [p.grad for p in ps]
+                if ok:
+                    # two elementwise passes in total: momentum (+ squared norms) before, parameter update after;
+                    # the normalisation is folded into the first Newton-Schulz GEMMs
+                    gp, pp = self._bucket_ptrs(stacked, ps)
+                    sumsq = torch.zeros(stacked.shape[0], dtype=torch.float32, device=stacked.device)
+                    torch.ops.kmoe.muon_momentum(stacked, gp, sumsq, mu)
+                    ortho = ops.newton_schulz(stacked, iters, sumsq=sumsq)
+                    torch.ops.kmoe.muon_apply(stacked, ortho.contiguous(), gp, pp, lr, mu, wd, bool(nesterov))
+                    from ..ops import cuda_ops
+                    cuda_ops._count(2)
+                    continue
                 stacked.mul_(mu)
                 torch._foreach_add_(views, grads)
                 if standard:

@@ -51,3 +51,33 @@ def test_sharded_pool_single_gpu_trains():
     cuda_ops.check_status()
     assert losses[-1] < losses[0], losses
     assert all(torch.isfinite(p).all() for p in model.parameters())
+
+
+def test_muon_fused_kernels_match_unfused(monkeypatch):
+    """Momentum / normalisation-in-GEMM / parameter-update kernels against the sequence of torch ops
+    they replace (same optimizer class, fused path switched off), over 2-D and stacked 3-D parameters."""
+    from kolmogorov_moe_architecture_b200.ops import cuda_ops  # noqa: F401  (loads the extension)
+    from kolmogorov_moe_architecture_b200.training.muon_optimizer import Muon
+
+    def run(fused: bool):
+        monkeypatch.setenv("KMOE_MUON_FUSED", "1" if fused else "0")
+        torch.manual_seed(0)
+        ps = [torch.nn.Parameter((torch.randn(256, 512, device="cuda") * 0.05).bfloat16()),
+              torch.nn.Parameter((torch.randn(512, 128, device="cuda") * 0.05).bfloat16()),
+              torch.nn.Parameter((torch.randn(3, 256, 512, device="cuda") * 0.05).bfloat16()),
+              torch.nn.Parameter((torch.randn(256, 512, device="cuda") * 0.05).bfloat16())]
+        opt = Muon(ps, lr=2e-2, momentum=0.9, weight_decay=0.1)
+        g = torch.Generator(device="cuda").manual_seed(1)
+        for _ in range(3):
+            for p in ps:
+                p.grad = (torch.randn(p.shape, device="cuda", generator=g) * 0.1).bfloat16()
+            opt.step()
+        bufs = [opt.state[p]["momentum_buffer"].float().clone() for p in ps]
+        return [p.detach().float().clone() for p in ps], bufs
+
+    pf, bf_ = run(True)
+    pu, bu = run(False)
+    for a, b in zip(pf, pu):
+        assert (a - b).abs().max().item() < 4e-3 * max(b.abs().max().item(), 1e-3) + 2e-4
+    for a, b in zip(bf_, bu):
+        assert (a - b).norm().item() < 3e-2 * b.norm().item()
