@@ -317,9 +317,10 @@ void p2p_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t world, in
 }
 
 void p2p_reduce_scatter(std::vector<int64_t> grad_ptrs, int64_t rank, int64_t world, int64_t off, int64_t n,
-                        const OptT& sq_out, int64_t mc_ptr) {
+                        const OptT& sq_out, int64_t mc_ptr, int64_t max_blocks) {
   check(kmoe_p2p_reduce_scatter((const long long*)grad_ptrs.data(), (int)rank, (int)world, off, n,
-                                (float*)const_cast<void*>(ptr_or_null(sq_out)), mc_ptr, cur_stream()),
+                                (float*)const_cast<void*>(ptr_or_null(sq_out)), mc_ptr, (int)max_blocks,
+                                cur_stream()),
         "p2p_reduce_scatter");
 }
 

@@ -84,32 +84,58 @@ __device__ __forceinline__ void acc8(const uint4& r, float* a) {
 
 // out[i] = (1/world) * sum_r grads[r][off + i], i in [0, n); sq_out += sum out^2 (fp32 atomics per CTA)
 // mc != null: the sum comes from one multicast load per 16 bytes instead of `world` peer loads.
+// Each thread keeps RS_UNROLL independent 16-byte loads in flight (per peer), so that a small grid running
+// beside the backward pass still covers the NVLink latency.
+constexpr int RS_UNROLL = 4;
 __global__ void p2p_reduce_scatter_kernel(PeerPtrs grads, int rank, int world, long long off, long long n,
                                           float* __restrict__ sq_out, const void* mc) {
   const long long nvec = n / 8;
   const float inv = 1.f / world;
   float sq = 0.f;
   __nv_bfloat16* own = reinterpret_cast<__nv_bfloat16*>(grads.p[rank]) + off;
-  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec;
-       v += (long long)gridDim.x * blockDim.x) {
-    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long v0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; v0 < nvec; v0 += stride * RS_UNROLL) {
+    float a[RS_UNROLL][8];
+#pragma unroll
+    for (int u = 0; u < RS_UNROLL; ++u)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a[u][i] = 0.f;
     if (mc != nullptr) {
-      acc8(multimem_ld_reduce_bf16x8(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(mc) + off) + v), a);
+      uint4 x[RS_UNROLL];
+#pragma unroll
+      for (int u = 0; u < RS_UNROLL; ++u)
+        if (v0 + u * stride < nvec)
+          x[u] = multimem_ld_reduce_bf16x8(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(mc) + off) +
+                                           v0 + u * stride);
+#pragma unroll
+      for (int u = 0; u < RS_UNROLL; ++u)
+        if (v0 + u * stride < nvec) acc8(x[u], a[u]);
     } else {
       for (int r = 0; r < world; ++r) {
         const int src = (rank + r) % world;     // stagger peers so ranks do not all hit the same one
-        const uint4 x = *(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[src]) + off) + v);
-        acc8(x, a);
+        const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[src]) + off);
+        uint4 x[RS_UNROLL];
+#pragma unroll
+        for (int u = 0; u < RS_UNROLL; ++u)
+          if (v0 + u * stride < nvec) x[u] = sp[v0 + u * stride];
+#pragma unroll
+        for (int u = 0; u < RS_UNROLL; ++u)
+          if (v0 + u * stride < nvec) acc8(x[u], a[u]);
       }
     }
-    uint4 o;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      a[i] *= inv;
-      sq += a[i] * a[i];
+    for (int u = 0; u < RS_UNROLL; ++u) {
+      if (v0 + u * stride >= nvec) continue;
+      uint4 o;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        a[u][i] *= inv;
+        sq += a[u][i] * a[u][i];
+      }
+      o.x = pack_bf16(a[u][0], a[u][1]); o.y = pack_bf16(a[u][2], a[u][3]);
+      o.z = pack_bf16(a[u][4], a[u][5]); o.w = pack_bf16(a[u][6], a[u][7]);
+      *(reinterpret_cast<uint4*>(own) + v0 + u * stride) = o;
     }
-    o.x = pack_bf16(a[0], a[1]); o.y = pack_bf16(a[2], a[3]); o.z = pack_bf16(a[4], a[5]); o.w = pack_bf16(a[6], a[7]);
-    *(reinterpret_cast<uint4*>(own) + v) = o;
   }
   sq = warp_sum(sq);
   __shared__ float s[32];
@@ -211,9 +237,11 @@ extern "C" int kmoe_p2p_barrier(const long long* flag_ptrs, int rank, int world,
 }
 
 extern "C" int kmoe_p2p_reduce_scatter(const long long* grad_ptrs, int rank, int world, long long off, long long n,
-                                       float* sq_out, long long mc_ptr, cudaStream_t st) {
+                                       float* sq_out, long long mc_ptr, int max_blocks, cudaStream_t st) {
   if (world > MAX_RANKS || n % 8 || off % 8) return -1;
-  p2p_reduce_scatter_kernel<<<148 * 8, 256, 0, st>>>(make_ptrs(grad_ptrs, world), rank, world, off, n, sq_out,
+  if (n == 0) return 0;
+  const int blocks = max_blocks > 0 ? max_blocks : 148 * 8;
+  p2p_reduce_scatter_kernel<<<blocks, 256, 0, st>>>(make_ptrs(grad_ptrs, world), rank, world, off, n, sq_out,
                                                      reinterpret_cast<const void*>(mc_ptr));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

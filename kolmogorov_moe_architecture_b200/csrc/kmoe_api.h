@@ -151,7 +151,7 @@ int kmoe_p2p_barrier(const long long* flag_ptrs, int rank, int world, int epoch,
                      cudaStream_t st);
 // mc_ptr: multicast (NVLink switch) address of the same symmetric buffer, or 0 to use plain peer accesses.
 int kmoe_p2p_reduce_scatter(const long long* grad_ptrs, int rank, int world, long long off, long long n,
-                            float* sq_out, long long mc_ptr, cudaStream_t st);
+                            float* sq_out, long long mc_ptr, int max_blocks /*0 = whole device*/, cudaStream_t st);
 int kmoe_p2p_adamw_allgather(const long long* param_ptrs, const void* grad, float* m, float* v, int rank, int world,
                              long long off, long long n, float lr, float beta1, float beta2, float eps, float wd,
                              int step, const float* clip_coef, long long mc_ptr, cudaStream_t st);

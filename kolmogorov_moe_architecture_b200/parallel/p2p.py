@@ -90,19 +90,25 @@ class SymmetricBuffers:
         self.param_mc: int = multicast_ptr(self._h[0], self.param, self.rank) if use_mc else 0
         self.grad_mc: int = multicast_ptr(self._h[1], self.grad, self.rank) if use_mc else 0
         self.epoch = 0
+        self.epochs = [0, 0, 0, 0]          # one counter per barrier channel (16 flag words each)
         self.timeout_s = barrier_timeout_s
         self.status = cuda_ops.status_tensor(device)
         dist.barrier(group=group)
 
-    def barrier(self) -> None:
+    def barrier(self, channel: int = 0) -> None:
+        """Flag barrier on the current stream.  Barriers issued on different streams must use different
+        channels: each channel has its own flag words and epoch counter, so the order in which the
+        streams' kernels actually run does not matter."""
         from ..ops import cuda_ops
-        self.epoch += 1
-        torch.ops.kmoe.p2p_barrier(self.flag_ptrs, self.rank, self.world, self.epoch, self.timeout_s, self.status)
+        self.epochs[channel] += 1
+        ptrs = [p + channel * 64 for p in self.flag_ptrs]
+        torch.ops.kmoe.p2p_barrier(ptrs, self.rank, self.world, self.epochs[channel], self.timeout_s, self.status)
         cuda_ops._count()
 
-    def reduce_scatter_mean(self, off: int, n: int, sq_out: Optional[torch.Tensor]) -> None:
+    def reduce_scatter_mean(self, off: int, n: int, sq_out: Optional[torch.Tensor], max_blocks: int = 0) -> None:
         from ..ops import cuda_ops
-        torch.ops.kmoe.p2p_reduce_scatter(self.grad_ptrs, self.rank, self.world, off, n, sq_out, self.grad_mc)
+        torch.ops.kmoe.p2p_reduce_scatter(self.grad_ptrs, self.rank, self.world, off, n, sq_out, self.grad_mc,
+                                          max_blocks)
         cuda_ops._count()
 
     def all_gather_range(self, off: int, n: int) -> None:

@@ -29,6 +29,8 @@ flat buffer and are reduced once, when the step is taken.
 """
 from __future__ import annotations
 
+import os
+
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -123,13 +125,17 @@ class ShardedDataParallel:
         self.dtype, self.device = dtype, device
         muon_flag = [optimizer_kind == "muon" and is_muon_param(n, p) for n, p in named]
         owners = assign_owners([p.numel() for _, p in named], self.world)
-        # segment layout: AdamW tensors first, Muon matrices after them
+        # segment layout: AdamW tensors first, Muon matrices after them; inside each part the tensors
+        # are placed in reverse module order, which is the order their gradients are finished by the
+        # backward pass - so "everything from the output down to layer l" is a prefix of both parts
+        # and can be reduced while the backward pass is still working on the earlier layers
         offsets = [0] * self.world
         self.slots: List[Optional[Tuple[int, int]]] = [None] * len(named)
         for want_muon in (False, True):
             if want_muon:
                 self.adamw_end = list(offsets)
-            for i, ((n, p), r) in enumerate(zip(named, owners)):
+            for i in reversed(range(len(named))):
+                (n, p), r = named[i], owners[i]
                 if muon_flag[i] == want_muon:
                     self.slots[i] = (r, offsets[r])
                     offsets[r] += _round_up(p.numel(), _ALIGN)
@@ -179,6 +185,86 @@ class ShardedDataParallel:
         self._clip: Optional[torch.Tensor] = None
         self._side_stream = None
         self._sq = torch.zeros(1, dtype=torch.float32, device=device)
+        self._sync = True
+        self._setup_overlap(named, muon_flag, int(os.environ.get("KMOE_RS_CHUNKS", "6")))
+
+    # ------------------------------------------------ reduce-scatter overlapped with the backward pass
+    def _setup_overlap(self, named, muon_flag, n_chunks: int) -> None:
+        """Split the tensors, in the order the backward pass finishes them, into ``n_chunks`` groups of
+        about equal size.  For this rank every group is one range of its AdamW part and one of its Muon
+        part; a group is reduced (own kernel, side stream) as soon as its last gradient has been
+        accumulated on every rank, while the backward pass continues below it."""
+        self._chunks: List[List[Tuple[int, int]]] = []
+        self._chunk_of: Dict[int, int] = {}
+        self._pending: List[int] = []
+        self._launched = 0
+        self._rs_stream = None
+        # measured at 2 GPUs the overlap costs more than the 4 ms it hides, so it is on from 4 ranks
+        # (KMOE_RS_OVERLAP=1/0 forces it)
+        want = os.environ.get("KMOE_RS_OVERLAP", "auto")
+        if self.transport != "p2p" or n_chunks <= 1 or want == "0" or (want == "auto" and self.world < 4):
+            return
+        order = list(reversed(range(len(named))))                      # backward completion order
+        total = sum(named[i][1].numel() for i in order)
+        bounds, acc, k = [], 0, 0
+        group_of = {}
+        for i in order:
+            group_of[i] = k
+            acc += named[i][1].numel()
+            if acc >= total * (k + 1) / n_chunks and k < n_chunks - 1:
+                k += 1
+        n_groups = max(group_of.values()) + 1
+        ranges: List[List[Tuple[int, int]]] = [[] for _ in range(n_groups)]
+        for want_muon in (False, True):
+            lo = [None] * n_groups
+            hi = [None] * n_groups
+            for i in order:
+                r, off = self.slots[i]
+                if r != self.rank or muon_flag[i] != want_muon:
+                    continue
+                g = group_of[i]
+                a = r * self.seg + off
+                b = a + _round_up(named[i][1].numel(), _ALIGN)
+                lo[g] = a if lo[g] is None else min(lo[g], a)
+                hi[g] = b if hi[g] is None else max(hi[g], b)
+            for g in range(n_groups):
+                if lo[g] is not None:
+                    ranges[g].append((lo[g], hi[g] - lo[g]))
+        self._chunks = ranges
+        self._group_sizes = [0] * n_groups
+        for i in range(len(named)):
+            self._group_sizes[group_of[i]] += 1
+            self._chunk_of[id(named[i][1])] = group_of[i]
+            named[i][1].register_post_accumulate_grad_hook(self._grad_ready)
+        self._pending = list(self._group_sizes)
+        self._rs_stream = torch.cuda.Stream(device=self.device)
+
+    def _grad_ready(self, p) -> None:
+        if not self._sync or not self._chunks:
+            return
+        g = self._chunk_of.get(id(p))
+        if g is None:
+            return
+        self._pending[g] -= 1
+        while self._launched < len(self._chunks) and self._pending[self._launched] <= 0:
+            self._launch_chunk(self._launched)
+            self._launched += 1
+
+    def _launch_chunk(self, g: int) -> None:
+        """Side stream: wait for the gradients enqueued so far, meet the other ranks, reduce this rank's
+        ranges of the group (mean over ranks, squared norm accumulated for clipping)."""
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self._rs_stream):
+            self._rs_stream.wait_event(ev)
+            self.p2p.barrier(channel=1)
+            for off, n in self._chunks[g]:
+                self.p2p.reduce_scatter_mean(off, n, self._sq, max_blocks=self._rs_blocks(g))
+
+    def _rs_blocks(self, g: int) -> int:
+        # while the backward pass is running the reduction gets a fraction of the SMs; the last group
+        # (nothing left to overlap with) gets the whole device
+        return 0 if g == len(self._chunks) - 1 else 48
 
     # ------------------------------------------------------------------ set-up
     def _pick_transport(self, want: Optional[str]) -> str:
@@ -200,7 +286,8 @@ class ShardedDataParallel:
 
     # -------------------------------------------------------------------- step
     def set_sync(self, flag: bool) -> None:
-        pass
+        """False while accumulating micro-batches: gradients are only reduced after the last one."""
+        self._sync = bool(flag)
 
     def own_slice(self, flat: torch.Tensor) -> torch.Tensor:
         return flat[self.rank * self.seg: (self.rank + 1) * self.seg]
@@ -208,7 +295,14 @@ class ShardedDataParallel:
     def reduce(self) -> None:
         """Average gradients over the group into their owners' segments."""
         self._sq_valid = False
-        if self.transport == "p2p":
+        if self.transport == "p2p" and self._chunks:
+            # groups whose last gradient arrived during the backward pass are already reduced (or in flight)
+            while self._launched < len(self._chunks):
+                self._launch_chunk(self._launched)
+                self._launched += 1
+            torch.cuda.current_stream(self.device).wait_stream(self._rs_stream)
+            self._sq_valid = self.grad_scale == 1.0
+        elif self.transport == "p2p":
             self.p2p.barrier()
             self._sq.zero_()
             self.p2p.reduce_scatter_mean(self.rank * self.seg, self.seg, self._sq)
@@ -279,6 +373,10 @@ class ShardedDataParallel:
             dist.all_gather_into_tensor(self.flat_param, self.own_slice(self.flat_param).clone(), group=self.group)
         self.flat_grad.zero_()
         self._clip = None
+        if self._chunks:                                  # re-arm the overlapped reduction for the next backward
+            self._sq.zero_()
+            self._pending = list(self._group_sizes)
+            self._launched = 0
 
     def reduce_clip_and_step(self, optimizer=None, max_norm: Optional[float] = 1.0) -> torch.Tensor:
         """Reduce gradients to their owners, clip by the global norm, update the owned
@@ -343,7 +441,8 @@ class ParallelPlan:
         self.optimizer = pools[0].optimizer
 
     def set_sync(self, flag: bool) -> None:
-        pass
+        for p in self.pools:
+            p.set_sync(flag)
 
     def reduce_clip_and_step(self, optimizer=None, max_norm: Optional[float] = 1.0) -> torch.Tensor:
         for p in self.pools:
