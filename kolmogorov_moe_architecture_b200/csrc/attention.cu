@@ -325,7 +325,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   constexpr int KTILE = NP * SUBPANEL_BYTES;    // 64 rows
   constexpr uint32_t IDESC_S = make_idesc_f16(128, BWD_SUB, 1, KMOE_MAJOR_K, KMOE_MAJOR_K);
   constexpr uint32_t IDESC_DQ = make_idesc_f16(128, D, 1, KMOE_MAJOR_K, KMOE_MAJOR_MN);
-  constexpr uint32_t TMEM_COLS = 256, COL_S = 0, COL_DP = 64, COL_DQ = 128;
+  // S and dP are double buffered in TMEM (buffer = block parity): the MMAs of block j+1 run while the
+  // threads turn block j into dS, and the dQ MMA of block j runs under the softmax of block j+1.
+  constexpr uint32_t TMEM_COLS = 512, COL_S = 0, COL_DP = 64, COL_BUF = 128, COL_DQ = 256;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -334,7 +336,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint8_t* sK = sdO + QTILE;          // 2 stages
   uint8_t* sV = sK + 2 * KTILE;       // 2 stages
   uint8_t* sdS = sV + 2 * KTILE;      // 128 x 64 bf16
-  __shared__ uint64_t qdo_full, k_full[2], v_full[2], k_empty[2], v_empty[2], sdp_full, ds_full, ds_free, dq_full;
+  __shared__ uint64_t qdo_full, k_full[2], v_full[2], k_empty[2], v_empty[2], sdp_full[2], ds_full, ds_free, dq_full;
   __shared__ uint32_t tmem_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -350,7 +352,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1);
     }
-    mbar_init(&sdp_full, 1); mbar_init(&ds_full, 128); mbar_init(&ds_free, 1); mbar_init(&dq_full, 1);
+    mbar_init(&sdp_full[0], 1); mbar_init(&sdp_full[1], 1);
+    mbar_init(&ds_full, 128); mbar_init(&ds_free, 1); mbar_init(&dq_full, 1);
     mbar_fence_init();
   }
   if (warp == 5) { tmem_alloc(&tmem_slot, TMEM_COLS); tmem_relinquish(); }
@@ -385,32 +388,42 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   } else if (warp == 5) {
     if (elect_one()) {
       if (!mbar_wait(&qdo_full, 0)) { atomicExch(a.status, 23); goto teardown; }
-      for (int j = 0; j < nblk; ++j) {
+      const uint32_t qa = smem_u32(sQ), da = smem_u32(sdO);
+      // S_j = Q K_j^T and dP_j = dO V_j^T into TMEM buffer j & 1
+      auto issue_sdp = [&](int j) -> bool {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_full[st], ph) || !mbar_wait(&v_full[st], ph)) { atomicExch(a.status, 24); goto teardown; }
+        if (!mbar_wait(&k_full[st], ph) || !mbar_wait(&v_full[st], ph)) return false;
         tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), da = smem_u32(sdO);
         const uint32_t ka = smem_u32(sK + st * KTILE), va = smem_u32(sV + st * KTILE);
+        const uint32_t tb = tmem + st * COL_BUF;
 #pragma unroll
         for (int k4 = 0; k4 < D / 16; ++k4) {
           const uint32_t aoff = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;
           const uint32_t boff = (k4 >> 2) * SUBPANEL_BYTES + (k4 & 3) * 32;
-          umma_f16(tmem + COL_S, make_smem_desc_sw128(qa + aoff, 16, 1024), make_smem_desc_sw128(ka + boff, 16, 1024),
+          umma_f16(tb + COL_S, make_smem_desc_sw128(qa + aoff, 16, 1024), make_smem_desc_sw128(ka + boff, 16, 1024),
                    IDESC_S, k4 > 0);
         }
 #pragma unroll
         for (int k4 = 0; k4 < D / 16; ++k4) {
           const uint32_t aoff = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;
           const uint32_t boff = (k4 >> 2) * SUBPANEL_BYTES + (k4 & 3) * 32;
-          umma_f16(tmem + COL_DP, make_smem_desc_sw128(da + aoff, 16, 1024), make_smem_desc_sw128(va + boff, 16, 1024),
+          umma_f16(tb + COL_DP, make_smem_desc_sw128(da + aoff, 16, 1024), make_smem_desc_sw128(va + boff, 16, 1024),
                    IDESC_S, k4 > 0);
         }
-        umma_commit(&sdp_full);
+        umma_commit(&sdp_full[st]);
         umma_commit(&v_empty[st]);
+        return true;
+      };
+      if (nblk > 0 && !issue_sdp(0)) { atomicExch(a.status, 24); goto teardown; }
+      for (int j = 0; j < nblk; ++j) {
+        const int st = j & 1;
+        // buffer (j+1)&1 was last read for block j-1, whose dS arrival was awaited in the previous iteration
+        if (j + 1 < nblk && !issue_sdp(j + 1)) { atomicExch(a.status, 24); goto teardown; }
         if (!mbar_wait(&ds_full, j & 1)) { atomicExch(a.status, 25); goto teardown; }
         tc_fence_after();
         const uint32_t sa = smem_u32(sdS);
+        const uint32_t ka = smem_u32(sK + st * KTILE);
 #pragma unroll
         for (int k4 = 0; k4 < BWD_SUB / 16; ++k4)
           umma_f16(tmem + COL_DQ, make_smem_desc_sw128(sa + k4 * 32, 16, 1024),
@@ -429,15 +442,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const float lse2 = a.lse[stat] * 1.4426950408889634f;
     const float dlt = a.delta[stat];
     for (int j = 0; j < nblk; ++j) {
-      if (!mbar_wait(&sdp_full, j & 1)) { if (lane == 0) atomicExch(a.status, 26); goto teardown; }
+      if (!mbar_wait(&sdp_full[j & 1], (j >> 1) & 1)) { if (lane == 0) atomicExch(a.status, 26); goto teardown; }
+      const uint32_t tbuf = tmem + lane_base + (j & 1) * COL_BUF;
       tc_fence_after();
       const int k0 = j * BWD_SUB;
       uint32_t ds_packed[BWD_SUB / 2];
 #pragma unroll
       for (int c = 0; c < BWD_SUB; c += 32) {
         uint32_t sv[32], dv_[32];
-        tmem_ld_32x32(tmem + lane_base + COL_S + c, sv);
-        tmem_ld_32x32(tmem + lane_base + COL_DP + c, dv_);
+        tmem_ld_32x32(tbuf + COL_S + c, sv);
+        tmem_ld_32x32(tbuf + COL_DP + c, dv_);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -499,7 +513,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr int QTILE = NP * SUBPANEL_BYTES;    // 64 query rows
   constexpr uint32_t IDESC_ST = make_idesc_f16(128, BWD_SUB, 1, KMOE_MAJOR_K, KMOE_MAJOR_K);
   constexpr uint32_t IDESC_ACC = make_idesc_f16(128, D, 1, KMOE_MAJOR_K, KMOE_MAJOR_MN);
-  constexpr uint32_t TMEM_COLS = 512, COL_ST = 0, COL_DPT = 64, COL_DV = 128, COL_DK = 256;
+  // S^T and dP^T are double buffered in TMEM (buffer = iteration parity) so that the MMAs of iteration it+1
+  // run while the threads turn iteration it into P^T / dS^T, and the dV / dK MMAs run under the next softmax.
+  constexpr uint32_t TMEM_COLS = 512, COL_ST = 0, COL_DPT = 64, COL_BUF = 128, COL_DV = 256, COL_DK = 384;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -509,7 +525,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint8_t* sdO = sQ + 2 * QTILE;       // 2 stages
   uint8_t* sPT = sdO + 2 * QTILE;      // 128 x 64
   uint8_t* sdST = sPT + ATT_BLK * 128; // 128 x 64
-  __shared__ uint64_t kv_full, q_full[2], q_empty[2], st_full, pds_full, pds_free, acc_full;
+  __shared__ uint64_t kv_full, q_full[2], q_empty[2], st_full[2], pds_full, pds_free, acc_full;
   __shared__ uint32_t tmem_slot;
   __shared__ float s_lse[BWD_SUB], s_delta[BWD_SUB];
 
@@ -525,7 +541,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(&kv_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
-    mbar_init(&st_full, 1); mbar_init(&pds_full, 128); mbar_init(&pds_free, 1); mbar_init(&acc_full, 1);
+    mbar_init(&st_full[0], 1); mbar_init(&st_full[1], 1);
+    mbar_init(&pds_full, 128); mbar_init(&pds_free, 1); mbar_init(&acc_full, 1);
     mbar_fence_init();
   }
   if (warp == 5) { tmem_alloc(&tmem_slot, TMEM_COLS); tmem_relinquish(); }
@@ -558,29 +575,40 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   } else if (warp == 5) {
     if (elect_one()) {
       if (!mbar_wait(&kv_full, 0)) { atomicExch(a.status, 32); goto teardown; }
-      for (int it = 0; it < niter; ++it) {
+      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+      // S^T = K Q^T and dP^T = V dO^T of iteration `it` into TMEM buffer it & 1
+      auto issue_st = [&](int it) -> bool {
         const int st = it & 1;
-        if (!mbar_wait(&q_full[st], (it >> 1) & 1)) { atomicExch(a.status, 33); goto teardown; }
+        if (!mbar_wait(&q_full[st], (it >> 1) & 1)) return false;
         tc_fence_after();
-        const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
         const uint32_t qa = smem_u32(sQ + st * QTILE), da = smem_u32(sdO + st * QTILE);
+        const uint32_t tb = tmem + st * COL_BUF;
 #pragma unroll
         for (int k4 = 0; k4 < D / 16; ++k4) {
           const uint32_t aoff = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;
           const uint32_t boff = (k4 >> 2) * SUBPANEL_BYTES + (k4 & 3) * 32;
-          umma_f16(tmem + COL_ST, make_smem_desc_sw128(ka + aoff, 16, 1024), make_smem_desc_sw128(qa + boff, 16, 1024),
+          umma_f16(tb + COL_ST, make_smem_desc_sw128(ka + aoff, 16, 1024), make_smem_desc_sw128(qa + boff, 16, 1024),
                    IDESC_ST, k4 > 0);
         }
 #pragma unroll
         for (int k4 = 0; k4 < D / 16; ++k4) {
           const uint32_t aoff = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;
           const uint32_t boff = (k4 >> 2) * SUBPANEL_BYTES + (k4 & 3) * 32;
-          umma_f16(tmem + COL_DPT, make_smem_desc_sw128(va + aoff, 16, 1024),
+          umma_f16(tb + COL_DPT, make_smem_desc_sw128(va + aoff, 16, 1024),
                    make_smem_desc_sw128(da + boff, 16, 1024), IDESC_ST, k4 > 0);
         }
-        umma_commit(&st_full);
+        umma_commit(&st_full[st]);
+        return true;
+      };
+      if (niter > 0 && !issue_st(0)) { atomicExch(a.status, 33); goto teardown; }
+      for (int it = 0; it < niter; ++it) {
+        const int st = it & 1;
+        // TMEM buffer (it+1)&1 was last read for iteration it-1, whose P^T/dS^T arrival was awaited last time;
+        // the Q/dO stage (it+1)&1 is handed back by q_empty after the accumulation MMAs of iteration it-1
+        if (it + 1 < niter && !issue_st(it + 1)) { atomicExch(a.status, 33); goto teardown; }
         if (!mbar_wait(&pds_full, it & 1)) { atomicExch(a.status, 34); goto teardown; }
         tc_fence_after();
+        const uint32_t qa = smem_u32(sQ + st * QTILE), da = smem_u32(sdO + st * QTILE);
         const uint32_t pa = smem_u32(sPT), sa = smem_u32(sdST);
 #pragma unroll
         for (int k4 = 0; k4 < BWD_SUB / 16; ++k4) {
@@ -603,7 +631,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int qrow = (qblk0 + it % per_head) * BWD_SUB;
       // stage lse / delta of the 64 queries (previous iteration's readers are past their loop:
       // they arrived on pds_full after their last read, and this point is after waiting st_full)
-      if (!mbar_wait(&st_full, it & 1)) { if (lane == 0) atomicExch(a.status, 35); goto teardown; }
+      if (!mbar_wait(&st_full[it & 1], (it >> 1) & 1)) { if (lane == 0) atomicExch(a.status, 35); goto teardown; }
+      const uint32_t tbuf = tmem + lane_base + (it & 1) * COL_BUF;
       tc_fence_after();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (r < BWD_SUB) {
@@ -617,8 +646,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
       for (int c = 0; c < BWD_SUB; c += 32) {
         uint32_t sv[32], dv_[32];
-        tmem_ld_32x32(tmem + lane_base + COL_ST + c, sv);
-        tmem_ld_32x32(tmem + lane_base + COL_DPT + c, dv_);
+        tmem_ld_32x32(tbuf + COL_ST + c, sv);
+        tmem_ld_32x32(tbuf + COL_DPT + c, dv_);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
