@@ -36,6 +36,8 @@ __global__ void route_topk_fwd_kernel(const float* __restrict__ logits, int T, i
   __syncthreads();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   float z = 0.f;
+  float my_p[ROUTE_MAX_E];
+  int my_sel[ROUTE_MAX_K];
   if (t < T) {
     const float* row = logits + (size_t)t * E;
     float mx = -CUDART_INF_F;
@@ -65,9 +67,22 @@ __global__ void route_topk_fwd_kernel(const float* __restrict__ logits, int T, i
     for (int j = 0; j < k; ++j) {
       w_out[(size_t)t * k + j] = pv[j] / s;
       idx_out[(size_t)t * k + j] = sel[j];
-      atomicAdd(&s_c[sel[j]], 1.f);
     }
-    for (int e = 0; e < E; ++e) atomicAdd(&s_p[e], __expf(row[e] - mx) * inv);
+    for (int j = 0; j < ROUTE_MAX_K; ++j) my_sel[j] = j < k ? sel[j] : -1;
+    for (int e = 0; e < E; ++e) my_p[e] = __expf(row[e] - mx) * inv;
+  }
+  // per-expert sums: reduce inside the warp first, so shared memory sees one atomic per warp and expert
+  // instead of one per token and expert
+  for (int e = 0; e < E; ++e) {
+    const float ps = warp_sum(t < T ? my_p[e] : 0.f);
+    int hit = 0;
+#pragma unroll
+    for (int j = 0; j < ROUTE_MAX_K; ++j) hit += (t < T && my_sel[j] == e) ? 1 : 0;
+    const float cs = warp_sum((float)hit);
+    if ((threadIdx.x & 31) == 0) {
+      if (ps != 0.f) atomicAdd(&s_p[e], ps);
+      if (cs != 0.f) atomicAdd(&s_c[e], cs);
+    }
   }
   z = warp_sum(z);
   if ((threadIdx.x & 31) == 0 && z != 0.f) atomicAdd(z_sum, z);
