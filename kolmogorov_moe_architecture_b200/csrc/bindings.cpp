@@ -342,6 +342,59 @@ void p2p_allgather(std::vector<int64_t> buf_ptrs, int64_t rank, int64_t world, i
         "p2p_allgather");
 }
 
+// ------------------------------------------------------------- mixture-of-depths rows
+static void check_idx(const Tensor& idx) {
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kLong && idx.is_contiguous() && idx.dim() == 2,
+              "idx must be a contiguous (B, k) int64 CUDA tensor");
+}
+
+Tensor rows_gather(const Tensor& src, const Tensor& idx) {
+  c10::cuda::CUDAGuard guard(src.device());
+  need_bf16(src, "src"); check_idx(idx);
+  TORCH_CHECK(src.is_contiguous() && src.dim() == 3);
+  const int B = src.size(0), S = src.size(1), d = src.size(2), k = idx.size(1);
+  Tensor out = at::empty({B, k, d}, src.options());
+  check(kmoe_rows_gather(src.data_ptr(), (const long long*)idx.data_ptr<int64_t>(), out.data_ptr(), B, S, k, d,
+                         cur_stream()), "rows_gather");
+  return out;
+}
+
+Tensor rows_scatter(const Tensor& src, const Tensor& idx, int64_t S) {
+  c10::cuda::CUDAGuard guard(src.device());
+  need_bf16(src, "src"); check_idx(idx);
+  TORCH_CHECK(src.is_contiguous() && src.dim() == 3);
+  const int B = src.size(0), k = src.size(1), d = src.size(2);
+  Tensor out = at::empty({B, S, d}, src.options());
+  check(kmoe_rows_scatter(src.data_ptr(), (const long long*)idx.data_ptr<int64_t>(), out.data_ptr(), B, (int)S, k, d,
+                          cur_stream()), "rows_scatter");
+  return out;
+}
+
+Tensor mod_combine_fwd(const Tensor& res, const Tensor& proc, const Tensor& w, const Tensor& idx) {
+  c10::cuda::CUDAGuard guard(res.device());
+  need_bf16(res, "res"); need_bf16(proc, "proc"); need_f32(w, "w"); check_idx(idx);
+  TORCH_CHECK(res.is_contiguous() && proc.is_contiguous() && res.dim() == 3 && proc.dim() == 3);
+  const int B = res.size(0), S = res.size(1), d = res.size(2), k = proc.size(1);
+  Tensor out = at::empty_like(res);
+  check(kmoe_mod_combine_fwd(res.data_ptr(), proc.data_ptr(), w.data_ptr<float>(),
+                             (const long long*)idx.data_ptr<int64_t>(), out.data_ptr(), B, S, k, d, cur_stream()),
+        "mod_combine_fwd");
+  return out;
+}
+
+std::tuple<Tensor, Tensor> mod_combine_bwd(const Tensor& dout, const Tensor& proc, const Tensor& w, const Tensor& idx) {
+  c10::cuda::CUDAGuard guard(dout.device());
+  need_bf16(dout, "dout"); need_bf16(proc, "proc"); need_f32(w, "w"); check_idx(idx);
+  TORCH_CHECK(dout.is_contiguous() && proc.is_contiguous());
+  const int B = dout.size(0), S = dout.size(1), d = dout.size(2), k = proc.size(1);
+  Tensor dproc = at::empty_like(proc);
+  Tensor dw = at::empty({B, k}, w.options());
+  check(kmoe_mod_combine_bwd(dout.data_ptr(), proc.data_ptr(), w.data_ptr<float>(),
+                             (const long long*)idx.data_ptr<int64_t>(), dproc.data_ptr(), dw.data_ptr<float>(), B, S,
+                             k, d, cur_stream()), "mod_combine_bwd");
+  return {dproc, dw};
+}
+
 // ------------------------------------------------------------- Muon elementwise passes
 void muon_momentum(Tensor buf, const Tensor& grad_ptrs, Tensor sumsq, double mu) {
   c10::cuda::CUDAGuard guard(buf.device());
@@ -539,6 +592,10 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("p2p_reduce_scatter", &p2p_reduce_scatter);
   m.def("p2p_adamw_allgather", &p2p_adamw_allgather);
   m.def("p2p_allgather", &p2p_allgather);
+  m.def("rows_gather", &rows_gather);
+  m.def("rows_scatter", &rows_scatter);
+  m.def("mod_combine_fwd", &mod_combine_fwd);
+  m.def("mod_combine_bwd", &mod_combine_bwd);
   m.def("muon_momentum", &muon_momentum);
   m.def("muon_apply", &muon_apply);
   m.def("mx_quant_rows", &mx_quant_rows);

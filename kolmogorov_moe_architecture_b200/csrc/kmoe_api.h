@@ -197,6 +197,15 @@ int kmoe_seq_topk_bwd(const float* scores, long long row_stride, long long col_s
                       long long outer_stride, int rows, int S, int k, int mode, const long long* idx, const float* w,
                       const float* dw, const float* stat, float* dscores, cudaStream_t st);
 
+// ---------------------------------------------------------------------------- mixture-of-depths rows
+// idx (B, k) int64, ascending per row, unique.  src/res/out/dout (B, S, d), proc/dproc (B, k, d), w/dw (B, k).
+int kmoe_rows_gather(const void* src, const long long* idx, void* out, int B, int S, int k, int d, cudaStream_t st);
+int kmoe_rows_scatter(const void* src, const long long* idx, void* out, int B, int S, int k, int d, cudaStream_t st);
+int kmoe_mod_combine_fwd(const void* res, const void* proc, const float* w, const long long* idx, void* out, int B,
+                         int S, int k, int d, cudaStream_t st);
+int kmoe_mod_combine_bwd(const void* dout, const void* proc, const float* w, const long long* idx, void* dproc,
+                         float* dw, int B, int S, int k, int d, cudaStream_t st);
+
 // ---------------------------------------------------------------------------- loss
 int kmoe_ce_fwd_bwd(void* logits, const long long* labels, float* loss_rows, const float* grad_scale, int R, int V,
                     long long ld, long long ignore_index, int write_grad, cudaStream_t st);

@@ -1,0 +1,174 @@
+// Mixture-of-depths data movement: the router keeps k of S tokens per sequence (indices ascending); the kept
+// rows are gathered, run through the FFN, weighted and added back onto the residual stream.
+//   rows_gather       out[b, j, :] = src[b, idx[b, j], :]
+//   rows_scatter      out[b, t, :] = src[b, j, :] if idx[b, j] == t else 0          (backward of the gather)
+//   combine_fwd       out[b, t, :] = res[b, t, :] + (w[b, j] * proc[b, j, :] if idx[b, j] == t)
+//   combine_bwd       dproc[b, j, :] = w[b, j] * dout[b, idx[b, j], :] ;  dw[b, j] = <dout[b, idx[b, j], :], proc[b, j, :]>
+// One warp per row, 16-byte lanes; the inverse map token -> slot is a binary search in the sorted index row,
+// so every output is written exactly once and nothing is zero-filled or accumulated afterwards.
+// reference: moe_arch/model/layers.py:148-185 (gather, multiply, scatter_add_ into zeros, residual add).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "kmoe_api.h"
+#include "ptx.cuh"
+
+namespace kmoe {
+
+__device__ __forceinline__ int find_slot(const long long* __restrict__ row_idx, int k, int t) {
+  int lo = 0, hi = k;                         // first position with idx >= t
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (row_idx[mid] < t) lo = mid + 1; else hi = mid;
+  }
+  return (lo < k && row_idx[lo] == t) ? lo : -1;
+}
+
+__global__ void rows_gather_kernel(const __nv_bfloat16* __restrict__ src, const long long* __restrict__ idx,
+                                   __nv_bfloat16* __restrict__ out, int B, int S, int k, int d) {
+  const int vec = d / 8, lane = threadIdx.x & 31;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < (long long)B * k; r += warps) {
+    const int b = (int)(r / k);
+    const long long t = idx[r];
+    const uint4* s = reinterpret_cast<const uint4*>(src + ((long long)b * S + t) * d);
+    uint4* o = reinterpret_cast<uint4*>(out + r * d);
+    for (int v = lane; v < vec; v += 32) o[v] = s[v];
+  }
+}
+
+__global__ void rows_scatter_kernel(const __nv_bfloat16* __restrict__ src, const long long* __restrict__ idx,
+                                    __nv_bfloat16* __restrict__ out, int B, int S, int k, int d) {
+  const int vec = d / 8, lane = threadIdx.x & 31;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < (long long)B * S; r += warps) {
+    const int b = (int)(r / S), t = (int)(r % S);
+    const int j = find_slot(idx + (long long)b * k, k, t);
+    uint4* o = reinterpret_cast<uint4*>(out + r * d);
+    if (j < 0) {
+      for (int v = lane; v < vec; v += 32) o[v] = make_uint4(0, 0, 0, 0);
+    } else {
+      const uint4* s = reinterpret_cast<const uint4*>(src + ((long long)b * k + j) * d);
+      for (int v = lane; v < vec; v += 32) o[v] = s[v];
+    }
+  }
+}
+
+__device__ __forceinline__ void unpack8f(const uint4& r, float* v) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(p[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+__global__ void mod_combine_fwd_kernel(const __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ proc,
+                                       const float* __restrict__ w, const long long* __restrict__ idx,
+                                       __nv_bfloat16* __restrict__ out, int B, int S, int k, int d) {
+  const int vec = d / 8, lane = threadIdx.x & 31;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < (long long)B * S; r += warps) {
+    const int b = (int)(r / S), t = (int)(r % S);
+    const int j = find_slot(idx + (long long)b * k, k, t);
+    const uint4* rs = reinterpret_cast<const uint4*>(res + r * d);
+    uint4* o = reinterpret_cast<uint4*>(out + r * d);
+    if (j < 0) {
+      for (int v = lane; v < vec; v += 32) o[v] = rs[v];
+    } else {
+      const float wj = w[(long long)b * k + j];
+      const uint4* ps = reinterpret_cast<const uint4*>(proc + ((long long)b * k + j) * d);
+      for (int v = lane; v < vec; v += 32) {
+        float a[8], p[8];
+        unpack8f(rs[v], a);
+        unpack8f(ps[v], p);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          // the weighted row is rounded to bf16 before the add, as the unfused multiply produced a bf16 tensor
+          a[i] += __bfloat162float(__float2bfloat16(wj * p[i]));
+        }
+        uint4 q;
+        q.x = pack_bf16(a[0], a[1]); q.y = pack_bf16(a[2], a[3]); q.z = pack_bf16(a[4], a[5]); q.w = pack_bf16(a[6], a[7]);
+        o[v] = q;
+      }
+    }
+  }
+}
+
+__global__ void mod_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ proc,
+                                       const float* __restrict__ w, const long long* __restrict__ idx,
+                                       __nv_bfloat16* __restrict__ dproc, float* __restrict__ dw, int B, int S, int k,
+                                       int d) {
+  const int vec = d / 8, lane = threadIdx.x & 31;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < (long long)B * k; r += warps) {
+    const int b = (int)(r / k);
+    const long long t = idx[r];
+    const float wj = w[r];
+    const uint4* gs = reinterpret_cast<const uint4*>(dout + ((long long)b * S + t) * d);
+    const uint4* ps = reinterpret_cast<const uint4*>(proc + r * d);
+    uint4* o = reinterpret_cast<uint4*>(dproc + r * d);
+    float dot = 0.f;
+    for (int v = lane; v < vec; v += 32) {
+      float g[8], p[8];
+      unpack8f(gs[v], g);
+      unpack8f(ps[v], p);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        dot += g[i] * p[i];
+        g[i] *= wj;
+      }
+      uint4 q;
+      q.x = pack_bf16(g[0], g[1]); q.y = pack_bf16(g[2], g[3]); q.z = pack_bf16(g[4], g[5]); q.w = pack_bf16(g[6], g[7]);
+      o[v] = q;
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) dw[r] = dot;
+  }
+}
+
+static int grid_rows(long long rows) {
+  const long long want = (rows + 7) / 8;           // 8 warps per 256-thread CTA
+  return (int)(want < 148 * 16 ? (want > 0 ? want : 1) : 148 * 16);
+}
+
+}  // namespace kmoe
+
+using namespace kmoe;
+
+extern "C" int kmoe_rows_gather(const void* src, const long long* idx, void* out, int B, int S, int k, int d,
+                                cudaStream_t st) {
+  if (d % 8) return -1;
+  if (B * (long long)k == 0) return 0;
+  rows_gather_kernel<<<grid_rows((long long)B * k), 256, 0, st>>>((const __nv_bfloat16*)src, idx, (__nv_bfloat16*)out,
+                                                                  B, S, k, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_rows_scatter(const void* src, const long long* idx, void* out, int B, int S, int k, int d,
+                                 cudaStream_t st) {
+  if (d % 8) return -1;
+  if (B * (long long)S == 0) return 0;
+  rows_scatter_kernel<<<grid_rows((long long)B * S), 256, 0, st>>>((const __nv_bfloat16*)src, idx, (__nv_bfloat16*)out,
+                                                                   B, S, k, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_mod_combine_fwd(const void* res, const void* proc, const float* w, const long long* idx, void* out,
+                                    int B, int S, int k, int d, cudaStream_t st) {
+  if (d % 8) return -1;
+  if (B * (long long)S == 0) return 0;
+  mod_combine_fwd_kernel<<<grid_rows((long long)B * S), 256, 0, st>>>(
+      (const __nv_bfloat16*)res, (const __nv_bfloat16*)proc, w, idx, (__nv_bfloat16*)out, B, S, k, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_mod_combine_bwd(const void* dout, const void* proc, const float* w, const long long* idx,
+                                    void* dproc, float* dw, int B, int S, int k, int d, cudaStream_t st) {
+  if (d % 8) return -1;
+  if (B * (long long)k == 0) return 0;
+  mod_combine_bwd_kernel<<<grid_rows((long long)B * k), 256, 0, st>>>(
+      (const __nv_bfloat16*)dout, (const __nv_bfloat16*)proc, w, idx, (__nv_bfloat16*)dproc, dw, B, S, k, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

@@ -17,6 +17,7 @@ import torch.nn as nn
 from .attention import GroupedQueryAttention
 from .embeddings import get_norm_layer
 from .ffn import get_ffn_module
+from .. import ops
 from .mamba import MambaBlock, RoutingMamba
 from .mod import MoDRouter
 from .moe import MoELayer
@@ -47,13 +48,12 @@ class TransformerBlock(nn.Module):
         self.residual_dropout = nn.Dropout(config.residual_dropout)
         self.aux_loss = 0.0
 
-    def _ffn_with_mod(self, h: torch.Tensor):
+    def _ffn_with_mod(self, h: torch.Tensor, residual: torch.Tensor):
+        """Kept tokens go through the FFN; their weighted outputs are added onto the residual stream
+        (gather -> FFN -> residual + scatter(w * out), each a single pass)."""
         sorted_idx, weights, _logits, _topk = self.ffn_mod_router(h)
-        d = h.shape[-1]
-        gather_idx = sorted_idx.unsqueeze(-1).expand(-1, -1, d)
-        picked = torch.gather(h, 1, gather_idx)
-        processed = self.ffn(picked) * weights.unsqueeze(-1).to(h.dtype)
-        out = torch.zeros_like(h).scatter_add(1, gather_idx, processed)
+        picked = ops.mod_gather(h, sorted_idx)
+        out = ops.mod_combine(residual, self.ffn(picked), weights, sorted_idx)
         return out, self.ffn_mod_router.aux_loss
 
     def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
@@ -69,12 +69,15 @@ class TransformerBlock(nn.Module):
             aux = aux + self.seq_layer.aux_loss
 
         h = self.ffn_norm(hidden_states)
-        if self.use_mod and self.training:
-            ffn_out, mod_aux = self._ffn_with_mod(h)
+        if self.use_mod and self.training and self.residual_dropout.p == 0.0:
+            hidden_states, mod_aux = self._ffn_with_mod(h, hidden_states)
             aux = aux + mod_aux
+        elif self.use_mod and self.training:
+            delta, mod_aux = self._ffn_with_mod(h, torch.zeros_like(hidden_states))
+            aux = aux + mod_aux
+            hidden_states = hidden_states + self.residual_dropout(delta)
         else:
-            ffn_out = self.ffn(h)
-        hidden_states = hidden_states + self.residual_dropout(ffn_out)
+            hidden_states = hidden_states + self.residual_dropout(self.ffn(h))
         if self.ffn_kind == "moe" and self.training:
             aux = aux + self.ffn.aux_loss
 

@@ -105,6 +105,20 @@ def mod_route(logits, k):
     return eager.mod_route(logits, k)
 
 
+def mod_gather(h, idx):
+    if _use_cuda(h):
+        from . import cuda_ops
+        return cuda_ops.mod_gather(h, idx)
+    return eager.mod_gather(h, idx)
+
+
+def mod_combine(res, proc, w, idx):
+    if _use_cuda(res):
+        from . import cuda_ops
+        return cuda_ops.mod_combine(res, proc, w, idx)
+    return eager.mod_combine(res, proc, w, idx)
+
+
 def expert_choice_route(logits, capacity):
     if _use_cuda(logits):
         from . import cuda_ops

@@ -425,6 +425,57 @@ def expert_choice_route(logits, capacity):
     return w, idx
 
 
+# -------------------------------------------------------- mixture-of-depths rows
+class _ModGather(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, idx):
+        ctx.save_for_backward(idx)
+        ctx.S = h.shape[1]
+        _count()
+        return K.rows_gather(h.contiguous(), idx)
+
+    @staticmethod
+    def backward(ctx, g):
+        (idx,) = ctx.saved_tensors
+        _count()
+        return K.rows_scatter(g.contiguous(), idx, ctx.S), None
+
+
+class _ModCombine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, res, proc, w, idx):
+        wf = w.float().contiguous()
+        procc = proc.contiguous()
+        ctx.save_for_backward(procc, wf, idx)
+        ctx.wdtype = w.dtype
+        _count()
+        return K.mod_combine_fwd(res.contiguous(), procc, wf, idx)
+
+    @staticmethod
+    def backward(ctx, g):
+        proc, wf, idx = ctx.saved_tensors
+        g = g.contiguous()
+        dproc, dw = K.mod_combine_bwd(g, proc, wf, idx)
+        _count()
+        return g, dproc, dw.to(ctx.wdtype), None
+
+
+def mod_gather(h, idx):
+    """h (B, S, d), idx (B, k) ascending -> (B, k, d)."""
+    if not _bf16(h) or h.shape[-1] % 8:
+        _fallback("mod_gather", f"dtype {h.dtype} d={h.shape[-1]}")
+        return eager.mod_gather(h, idx)
+    return _ModGather.apply(h, idx.contiguous())
+
+
+def mod_combine(res, proc, w, idx):
+    """res + scatter(w * proc) along the sequence: (B, S, d)."""
+    if not (_bf16(res) and _bf16(proc)) or res.shape[-1] % 8:
+        _fallback("mod_combine", f"dtype {res.dtype}/{proc.dtype} d={res.shape[-1]}")
+        return eager.mod_combine(res, proc, w, idx)
+    return _ModCombine.apply(res, proc, w, idx.contiguous())
+
+
 # -------------------------------------------------------- LM head + MTP loss
 class _MTPLoss(torch.autograd.Function):
     """Per head: logits chunk = H W^T (tcgen05 GEMM) -> CE kernel writes d logits in place ->

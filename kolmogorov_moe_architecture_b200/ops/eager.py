@@ -192,6 +192,19 @@ def mod_route(logits: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor,
     return sidx, w, topi
 
 
+def mod_gather(h: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    """Rows of h (B, S, d) at the kept positions idx (B, k) -> (B, k, d)."""
+    return torch.gather(h, 1, idx.unsqueeze(-1).expand(-1, -1, h.shape[-1]))
+
+
+def mod_combine(res: torch.Tensor, proc: torch.Tensor, w: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    """res + scatter of the weighted processed rows back to their positions
+    (reference: moe_arch/model/layers.py:160-185)."""
+    gi = idx.unsqueeze(-1).expand(-1, -1, res.shape[-1])
+    upd = proc * w.unsqueeze(-1).to(proc.dtype)
+    return res + torch.zeros_like(res).scatter_add(1, gi, upd)
+
+
 # ----------------------------------------------------------------------- loss
 def mtp_cross_entropy(hidden: torch.Tensor, head_weights, labels: torch.Tensor,
                       weights, ignore_index: int = -100) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -262,3 +262,27 @@ def test_expert_choice_route_fwd_bwd(B, S, E, C):
     assert torch.equal(tok, tokr)
     assert torch.allclose(w, wr, atol=1e-6, rtol=1e-4)
     assert torch.allclose(logits.grad, lr.grad, atol=1e-7, rtol=2e-3)
+
+
+@pytest.mark.parametrize("B,S,k,d", [(3, 64, 48, 256), (2, 2048, 1536, 512), (1, 7, 1, 64)])
+def test_mod_gather_combine_fwd_bwd(B, S, k, d):
+    """Mixture-of-depths row movement: gather of the kept rows and residual + scatter(w * processed)."""
+    ops, c, eager = _mods()
+    torch.manual_seed(6)
+    h = _bf(B, S, d, grad=True)
+    res = _bf(B, S, d, grad=True)
+    idx = torch.stack([torch.randperm(S, device="cuda")[:k].sort().values for _ in range(B)])
+    w = torch.rand(B, k, device="cuda").bfloat16().requires_grad_(True)
+    lin = _bf(d, d, scale=0.05)
+    picked = ops.mod_gather(h, idx)
+    proc = picked @ lin
+    out = ops.mod_combine(res, proc, w, idx)
+    g = _bf(B, S, d)
+    out.backward(g)
+    hr, rr, wr = _f32_leaf(h), _f32_leaf(res), _f32_leaf(w)
+    pr = eager.mod_gather(hr, idx)
+    outr = eager.mod_combine(rr, pr @ lin.float(), wr, idx)
+    outr.backward(g.float())
+    assert torch.equal(picked.float(), pr.detach())
+    assert _rel(out, outr) < 1e-2
+    assert _rel(h.grad, hr.grad) < 2e-2 and _rel(res.grad, rr.grad) < 1e-6 and _rel(w.grad, wr.grad) < 2e-2
