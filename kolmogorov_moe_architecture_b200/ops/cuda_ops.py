@@ -55,6 +55,28 @@ def check_status(device=None) -> None:
             raise RuntimeError(f"kmoe kernel on cuda:{key} reported wait-timeout status {v}")
 
 
+# Destinations for weight gradients, registered by the sharded data-parallel wrapper: parameter address ->
+# (weak reference to the parameter, its slice of the flat gradient buffer, commit callback).  An op whose
+# backward produces a weight gradient with a GEMM can write it straight to the destination and return None.
+_GRAD_SINKS: dict = {}
+
+
+def register_grad_sink(param, view, commit) -> None:
+    import weakref
+    _GRAD_SINKS[param.data_ptr()] = (weakref.ref(param), view, commit)
+
+
+def grad_sink(w):
+    """(destination, commit) when ``w`` has a registered destination and no gradient yet this step."""
+    hit = _GRAD_SINKS.get(w.data_ptr())
+    if hit is None:
+        return None
+    p = hit[0]()
+    if p is None or p.grad is not None or hit[1].shape != w.shape:
+        return None
+    return hit[1], (lambda: hit[2](p))
+
+
 def _count(n: int = 1):
     LAUNCHES["count"] += n
 
@@ -315,14 +337,18 @@ class _GroupedSwiGLU(torch.autograd.Function):
         kb = offsets[:E].contiguous()
         kl = (offsets[1:] - offsets[:E]).contiguous()
         H = K.swiglu_fwd(G, U, meta[1:2])
-        dw1 = torch.empty_like(w1)
-        dw2 = torch.empty_like(w2)
-        dw3 = torch.empty_like(w3)
+        # weight gradients go straight to their place in the flat gradient buffer when one is registered
+        sinks = [grad_sink(w) for w in (w1, w2, w3)]
+        dw1, dw2, dw3 = [s[0] if s is not None else torch.empty_like(w) for s, w in zip(sinks, (w1, w2, w3))]
         common = dict(mode=BATCHED, groups=E, a_major=MAJ_MN, b_major=MAJ_MN, Kd=max_rows, k_begin=kb, k_len=kl)
         gemm(Xp, dG, dw1, M=d, N=f, lda=d, ldb=f, ldc=f, c_gs=d * f, **common)
         gemm(Xp, dU, dw2, M=d, N=f, lda=d, ldb=f, ldc=f, c_gs=d * f, **common)
         gemm(H, dYp, dw3, M=f, N=d, lda=f, ldb=d, ldc=d, c_gs=f * d, **common)
         _count(5)
+        for s_ in sinks:
+            if s_ is not None:
+                s_[1]()
+        dw1, dw2, dw3 = [None if s_ is not None else g for s_, g in zip(sinks, (dw1, dw2, dw3))]
         return dx, dw1, dw2, dw3, None, dwts, None
 
 

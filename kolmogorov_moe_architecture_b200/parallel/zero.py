@@ -159,6 +159,7 @@ class ShardedDataParallel:
                 view.copy_(p.data)
                 p.data = view
                 p.grad = self.flat_grad[a: a + p.numel()].view_as(p)
+        self._setup_grad_landing()
         if broadcast_from_rank0 and self.world > 1:
             dist.broadcast(self.flat_param, src=dist.get_global_rank(group, 0) if group is not None else 0,
                            group=group)
@@ -187,6 +188,56 @@ class ShardedDataParallel:
         self._sq = torch.zeros(1, dtype=torch.float32, device=device)
         self._sync = True
         self._setup_overlap(named, muon_flag, int(os.environ.get("KMOE_RS_CHUNKS", "6")))
+
+    # ------------------------------------------------ gradients land in the flat buffer without an add
+    def _setup_grad_landing(self) -> None:
+        """With ``p.grad`` pointing into the flat buffer autograd *adds* every new gradient to it, which
+        costs a zero-fill of the buffer plus a read-modify-write per tensor per step.  Instead ``p.grad``
+        starts each step as None: autograd then hands over the freshly computed gradient, and a
+        post-accumulate hook copies it to the tensor's place in the flat buffer (one read, one write)
+        and points ``p.grad`` there, so further micro-batches accumulate in place.  Ops that can write
+        their weight gradient straight into the flat buffer ask ``ops.cuda_ops.grad_sink`` for the
+        destination and skip even the copy."""
+        self._views: Dict[int, torch.Tensor] = {}
+        self._touched: set = set()
+        self._landing = self.device.type == "cuda" and os.environ.get("KMOE_GRAD_LANDING", "1") != "0"
+        if not self._landing:
+            return
+        from ..ops import cuda_ops
+        for (n, p) in self.named:
+            self._views[id(p)] = p.grad
+            p.grad = None
+            p.register_post_accumulate_grad_hook(self._land)
+            cuda_ops.register_grad_sink(p, self._views[id(p)], self._sink_commit)
+
+    def _land(self, p) -> None:
+        v = self._views[id(p)]
+        if p.grad is not None and p.grad.data_ptr() != v.data_ptr():
+            v.copy_(p.grad)
+            p.grad = v
+        self._touched.add(id(p))
+
+    def _sink_commit(self, p) -> None:
+        """An op wrote this parameter's gradient directly into the flat buffer."""
+        p.grad = self._views[id(p)]
+        self._touched.add(id(p))
+        self._grad_ready(p)
+
+    def _clear_grads(self) -> None:
+        if self._landing:
+            for (_, p) in self.named:
+                p.grad = None
+            self._touched.clear()
+        else:
+            self.flat_grad.zero_()
+
+    def _zero_untouched(self) -> None:
+        """Parameters that received no gradient this step still hold last step's values in the buffer."""
+        if self._landing and len(self._touched) != len(self.named):
+            for (_, p) in self.named:
+                if id(p) not in self._touched:
+                    self._views[id(p)].zero_()
+                    p.grad = self._views[id(p)]
 
     # ------------------------------------------------ reduce-scatter overlapped with the backward pass
     def _setup_overlap(self, named, muon_flag, n_chunks: int) -> None:
@@ -294,6 +345,7 @@ class ShardedDataParallel:
 
     def reduce(self) -> None:
         """Average gradients over the group into their owners' segments."""
+        self._zero_untouched()
         self._sq_valid = False
         if self.transport == "p2p" and self._chunks:
             # groups whose last gradient arrived during the backward pass are already reduced (or in flight)
@@ -371,7 +423,7 @@ class ShardedDataParallel:
             dist.all_gather_into_tensor(self.flat_param, self.own_slice(self.flat_param), group=self.group)
         elif self.transport == "gloo":
             dist.all_gather_into_tensor(self.flat_param, self.own_slice(self.flat_param).clone(), group=self.group)
-        self.flat_grad.zero_()
+        self._clear_grads()
         self._clip = None
         if self._chunks:                                  # re-arm the overlapped reduction for the next backward
             self._sq.zero_()
@@ -426,7 +478,7 @@ class _PoolOptimizer:
         self.pool.load_optimizer_state_dict(sd)
 
     def zero_grad(self, set_to_none: bool = False):
-        self.pool.flat_grad.zero_()
+        self.pool._clear_grads()
 
     def step(self):
         raise RuntimeError("step through ShardedDataParallel.reduce_clip_and_step")
