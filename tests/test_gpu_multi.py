@@ -52,12 +52,14 @@ dist.destroy_process_group()
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("multimem", [False, True])
-def test_p2p_transport_matches_nccl_2gpus(tmp_path, multimem):
-    """Plain peer loads/stores, and the NVLink-switch path (multimem.ld_reduce / multimem.st)."""
+@pytest.mark.parametrize("multimem,overlap", [(False, False), (True, False), (False, True)])
+def test_p2p_transport_matches_nccl_2gpus(tmp_path, multimem, overlap):
+    """Plain peer loads/stores, the NVLink-switch path (multimem.ld_reduce / multimem.st), and the
+    reduce-scatter issued in groups on a side stream while the backward pass is still running."""
     f = tmp_path / "worker.py"
     f.write_text(WORKER)
-    env = dict(os.environ, KMOE_ROOT=ROOT, KMOE_STRICT="1")
+    env = dict(os.environ, KMOE_ROOT=ROOT, KMOE_STRICT="1", KMOE_RS_OVERLAP="1" if overlap else "0",
+               KMOE_RS_CHUNKS="3")
     if multimem:
         env.pop("NCCL_NVLS_ENABLE", None)
         env.update(KMOE_MULTIMEM="1", KMOE_EXPECT_MULTIMEM="1")
