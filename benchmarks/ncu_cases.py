@@ -1,6 +1,6 @@
 """Small single-kernel workloads for Nsight Compute captures.
 
-    python benchmarks/ncu_cases.py --case gemm|moe|attn|scan|adamw|ce|mxfp8|ep_dispatch|ep_gemm2 [--launches 4]
+    python benchmarks/ncu_cases.py --case gemm|moe|attn|scan|adamw|ce|mxfp8|mod|ep_dispatch|ep_gemm2 [--launches 4]
 
 Each case holds well under 2 GB on the device, uses operands larger than L2 where the kernel is
 bandwidth-sensitive, and launches the kernel of interest a handful of times so that
@@ -95,6 +95,13 @@ def main():
         c.check_status()
         ep_p2p.release_buffers()
         dist.destroy_process_group()
+    elif a.case == "mod":
+        B, S, k, d = 4, 2048, 1536, 2048
+        h, res = bf(B, S, d, sc=1.0).requires_grad_(True), bf(B, S, d, sc=1.0).requires_grad_(True)
+        idx = torch.stack([torch.randperm(S, device="cuda")[:k].sort().values for _ in range(B)])
+        w = torch.rand(B, k, device="cuda").to(torch.bfloat16).requires_grad_(True)
+        for _ in range(n):
+            ops.mod_combine(res, ops.mod_gather(h, idx), w, idx).backward(bf(B, S, d, sc=1.0))
     elif a.case == "mxfp8":
         from kolmogorov_moe_architecture_b200.ops import mxfp8 as mx
         M, N, K = 8192, 8192, 2048
