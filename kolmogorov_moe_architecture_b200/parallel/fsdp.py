@@ -1,0 +1,326 @@
+"""Parameter-sharded data parallelism (ZeRO-3 / FULL_SHARD), the regime of the reference's
+``train_distributed.py`` (reference: train_distributed.py:275-333 wraps every ``TransformerBlock`` in
+FSDP FULL_SHARD with bf16 all-gather / reduce-scatter, optional CPU offload, AdamW only).
+
+The default data-parallel plan of this framework (:mod:`.zero`) keeps the bf16 parameters replicated
+and shards only gradients and optimizer state, which is the faster choice while the model fits in a
+GPU.  This module is the memory-lean alternative for models that do not fit:
+
+* a *unit* is one ``TransformerBlock`` (plus one root unit for embeddings, final norm and heads);
+  its parameters are laid out back to back in one flat vector, padded to a multiple of the world size;
+  each rank keeps 1/world of it (the *shard*) plus fp32 AdamW moments for that shard - optionally in
+  pinned host memory (``cpu_offload``);
+* before a unit runs (forward, and again before its backward) its flat vector is all-gathered into
+  one of two rotating device buffers and the module's parameters are pointed at views of it; after
+  the unit's forward, and after its gradients are complete, the parameters are released again;
+* when the last gradient of a unit arrives, the unit's gradients are flattened, reduce-scattered
+  (mean) into the rank's gradient shard, and dropped;
+* the step clips by the global norm of all gradient shards and runs AdamW on the shards.
+
+Muon needs whole matrices on one rank and is therefore offered by the replicated plan only, as in the
+reference, whose distributed launcher is AdamW-only (train_distributed.py:336-397).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class _Unit:
+    def __init__(self, name: str, module: Optional[torch.nn.Module], params: List[torch.nn.Parameter],
+                 names: List[str]):
+        self.name, self.module, self.params, self.names = name, module, params, names
+        self.offsets: List[int] = []
+        self.total = 0
+        self.padded = 0
+        self.shard: Optional[torch.Tensor] = None          # this rank's slice of the flat parameters
+        self.grad_shard: Optional[torch.Tensor] = None     # accumulated, reduced gradient slice
+        self.m: Optional[torch.Tensor] = None              # AdamW moments (fp32)
+        self.v: Optional[torch.Tensor] = None
+        self.gathered = False
+        self.buffer: Optional[torch.Tensor] = None
+        self.pending = 0
+        self.reduced = False
+
+
+class FullyShardedDataParallel:
+    """``model`` must already be on its device in its training dtype.  ``unit_cls``: module class whose
+    instances become units (default: the framework's ``TransformerBlock``)."""
+
+    def __init__(self, model: torch.nn.Module, group=None, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
+                 weight_decay: float = 0.01, unit_cls=None, cpu_offload: bool = False,
+                 broadcast_from_rank0: bool = True):
+        if unit_cls is None:
+            from ..models.layers import TransformerBlock
+            unit_cls = TransformerBlock
+        self.model, self.group = model, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.cpu_offload = cpu_offload
+        first = next(p for p in model.parameters() if p.requires_grad)
+        self.device, self.dtype = first.device, first.dtype
+        self.backend = dist.get_backend(group) if dist.is_initialized() else "none"
+        self.hyper = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
+        self.step_count = 0
+        self._in_backward = False
+
+        # ---- units
+        seen = set()
+        self.units: List[_Unit] = []
+        for mname, mod in model.named_modules():
+            if isinstance(mod, unit_cls):
+                ps, ns = [], []
+                for n, p in mod.named_parameters():
+                    if p.requires_grad and id(p) not in seen:
+                        assert not getattr(p, "_kmoe_expert_parallel", False), \
+                            "expert-parallel tensors are not supported by the parameter-sharded plan"
+                        seen.add(id(p))
+                        ps.append(p)
+                        ns.append(f"{mname}.{n}")
+                if ps:
+                    self.units.append(_Unit(mname, mod, ps, ns))
+        rp, rn = [], []
+        for n, p in model.named_parameters():
+            if p.requires_grad and id(p) not in seen:
+                seen.add(id(p))
+                rp.append(p)
+                rn.append(n)
+        self.root = _Unit("", None, rp, rn) if rp else None
+        all_units = self.units + ([self.root] if self.root else [])
+        align = 8 * self.world
+        for u in all_units:
+            off = 0
+            for p in u.params:
+                assert p.dtype == self.dtype, "parameters must share one dtype"
+                p._kmoe_shape, p._kmoe_numel = tuple(p.shape), p.numel()
+                u.offsets.append(off)
+                off += _round_up(p.numel(), 8)
+            u.total, u.padded = off, _round_up(off, align)
+        # ---- buffers: two rotating ones for the block units, a permanent one for the root unit
+        big = max([u.padded for u in self.units], default=0)
+        self._pool = [torch.zeros(big, dtype=self.dtype, device=self.device) for _ in range(2 if self.units else 0)]
+        self._grad_buf = torch.zeros(max([u.padded for u in all_units]), dtype=self.dtype, device=self.device)
+        for i, u in enumerate(self.units):
+            u.buffer = self._pool[i % 2][: u.padded]
+        if self.root:
+            self.root.buffer = torch.zeros(self.root.padded, dtype=self.dtype, device=self.device)
+        self._placeholder = torch.empty(0, dtype=self.dtype, device=self.device)
+        # ---- shards from the initial parameters (rank 0's values when asked to broadcast)
+        store = torch.device("cpu") if cpu_offload else self.device
+        for u in all_units:
+            flat = torch.zeros(u.padded, dtype=self.dtype, device=self.device)
+            for p, off in zip(u.params, u.offsets):
+                flat[off: off + p.numel()].copy_(p.data.reshape(-1))
+            if broadcast_from_rank0 and self.world > 1:
+                dist.broadcast(flat, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+            chunk = u.padded // self.world
+            sl = flat[self.rank * chunk: (self.rank + 1) * chunk]
+            u.shard = sl.to(store).clone()
+            if cpu_offload and torch.cuda.is_available():
+                u.shard = u.shard.pin_memory()
+            u.grad_shard = torch.zeros(chunk, dtype=torch.float32, device=store)
+            u.m = torch.zeros(chunk, dtype=torch.float32, device=store)
+            u.v = torch.zeros(chunk, dtype=torch.float32, device=store)
+            for p in u.params:
+                p.data = self._placeholder
+                p.grad = None
+            del flat
+        # ---- hooks
+        for u in self.units:
+            u.module.register_forward_pre_hook(lambda m, a, u=u: self._gather(u))
+            u.module.register_forward_hook(lambda m, a, o, u=u: self._after_forward(u))
+            u.module.register_full_backward_pre_hook(lambda m, g, u=u: self._before_backward(u))
+        model.register_forward_pre_hook(lambda m, a: self._begin_forward())
+        for u in all_units:
+            for p in u.params:
+                p.register_post_accumulate_grad_hook(lambda p, u=u: self._grad_arrived(u))
+        self.optimizer = _ShardOptimizer(self)
+        self._arm()
+
+    # ------------------------------------------------------------------ gather / release
+    def _gather(self, u: _Unit) -> None:
+        if u.gathered:
+            return
+        shard = u.shard.to(self.device, non_blocking=True) if u.shard.device != self.device else u.shard
+        out = u.buffer.data                     # alias with its own version counter: autograd never sees the write
+        if self.world > 1:
+            dist.all_gather_into_tensor(out, shard.contiguous(), group=self.group)
+        else:
+            out.copy_(shard)
+        for p, off in zip(u.params, u.offsets):
+            p.data = u.buffer[off: off + p._kmoe_numel].view(p._kmoe_shape)
+        u.gathered = True
+        from ..ops import mxfp8
+        mxfp8.invalidate_weight_cache()         # the same addresses now hold another unit's weights
+
+    def _release(self, u: _Unit) -> None:
+        if not u.gathered or u is self.root:
+            return
+        for p in u.params:
+            p.data = self._placeholder
+        u.gathered = False
+
+    def _begin_forward(self) -> None:
+        self._in_backward = False
+        if self.root is not None:
+            self._gather(self.root)
+
+    def _after_forward(self, u: _Unit) -> None:
+        # a forward that runs inside the backward pass (activation recomputation) keeps the unit for its
+        # backward; otherwise the buffer goes to the unit two positions on, and this unit's backward
+        # gathers it again into the same addresses (which tensors saved by autograd still point at)
+        if not self._in_backward:
+            self._release(u)
+
+    def _before_backward(self, u: _Unit) -> None:
+        self._in_backward = True
+        # the other unit of this buffer may still be resident
+        for o in self.units:
+            if o is not u and o.gathered and o.buffer.data_ptr() == u.buffer.data_ptr():
+                self._release(o)
+        self._gather(u)
+
+    # ------------------------------------------------------------------ gradients
+    def _grad_arrived(self, u: _Unit) -> None:
+        u.pending -= 1
+        if u.pending <= 0 and not u.reduced and u is not self.root:
+            self._reduce_unit(u)
+            self._release(u)
+
+    def _reduce_unit(self, u: _Unit) -> None:
+        """Flatten the unit's gradients, average them over the ranks, keep this rank's slice."""
+        g = self._grad_buf[: u.padded]
+        g.zero_()
+        for p, off in zip(u.params, u.offsets):
+            if p.grad is not None:
+                g[off: off + p._kmoe_numel].copy_(p.grad.reshape(-1))
+                p.grad = None
+        chunk = u.padded // self.world
+        if self.world == 1:
+            red = g
+        elif self.backend == "nccl":
+            red = torch.empty(chunk, dtype=g.dtype, device=g.device)
+            dist.reduce_scatter_tensor(red, g, op=dist.ReduceOp.AVG, group=self.group)
+        else:                                   # gloo has no reduce-scatter
+            dist.all_reduce(g, group=self.group)
+            red = g[self.rank * chunk: (self.rank + 1) * chunk] / self.world
+        u.grad_shard.add_(red.to(u.grad_shard.device, non_blocking=False).float())
+        u.reduced = True
+
+    # ------------------------------------------------------------------ step
+    def set_sync(self, flag: bool) -> None:
+        pass                                    # every micro-batch is reduced, like the reference's FSDP use
+
+    def _arm(self) -> None:
+        for u in self.units + ([self.root] if self.root else []):
+            u.pending = len(u.params)
+            u.reduced = False
+
+    def reduce_clip_and_step(self, optimizer=None, max_norm: Optional[float] = 1.0) -> torch.Tensor:
+        all_units = self.units + ([self.root] if self.root else [])
+        for u in all_units:                     # the root unit, and units with parameters that got no gradient
+            if not u.reduced:
+                self._reduce_unit(u)
+                self._release(u)
+        sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for u in all_units:
+            sq += u.grad_shard.pow(2).sum().to(self.device)
+        if self.world > 1:
+            dist.all_reduce(sq, group=self.group)
+        total = sq.sqrt()[0]
+        coef = 1.0
+        if max_norm is not None and max_norm > 0:
+            coef = (max_norm / (total + 1e-6)).clamp(max=1.0)
+        self.step_count += 1
+        h = self.hyper
+        b1, b2 = h["betas"]
+        bc1, bc2 = 1 - b1 ** self.step_count, 1 - b2 ** self.step_count
+        for u in all_units:
+            c = coef.to(u.grad_shard.device) if torch.is_tensor(coef) else coef
+            g = u.grad_shard * c
+            u.m.mul_(b1).add_(g, alpha=1 - b1)
+            u.v.mul_(b2).addcmul_(g, g, value=1 - b2)
+            p32 = u.shard.float()
+            p32.mul_(1 - h["lr"] * h["weight_decay"])
+            p32.addcdiv_(u.m / bc1, (u.v / bc2).sqrt_().add_(h["eps"]), value=-h["lr"])
+            u.shard.copy_(p32.to(u.shard.dtype))
+            u.grad_shard.zero_()
+        if self.root is not None:               # new values: the root unit is gathered again at the next forward
+            self.root.gathered = False
+        self._arm()
+        return total
+
+    # ------------------------------------------------------------------ whole-model access
+    def full_state_dict(self, to_cpu: bool = True) -> Dict[str, torch.Tensor]:
+        """Every parameter in full, gathered unit by unit (call on all ranks)."""
+        out: Dict[str, torch.Tensor] = {}
+        for u in self.units + ([self.root] if self.root else []):
+            was = u.gathered
+            self._gather(u)
+            for p, n in zip(u.params, u.names):
+                t = p.data.detach().clone()
+                out[n] = t.cpu() if to_cpu else t
+            if not was:
+                self._release(u)
+        # tied parameters appear under every name they have in the model (e.g. lm_heads.0 = embedding)
+        primary = {id(p): n for u in self.units + ([self.root] if self.root else []) for p, n in zip(u.params, u.names)}
+        for n, p in self.model.named_parameters(remove_duplicate=False):
+            if n not in out and id(p) in primary:
+                out[n] = out[primary[id(p)]]
+        return out
+
+    def load_full_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
+        for u in self.units + ([self.root] if self.root else []):
+            flat = torch.zeros(u.padded, dtype=self.dtype, device=self.device)
+            for p, n, off in zip(u.params, u.names, u.offsets):
+                flat[off: off + p._kmoe_numel].copy_(sd[n].reshape(-1).to(self.device, self.dtype))
+            chunk = u.padded // self.world
+            u.shard.copy_(flat[self.rank * chunk: (self.rank + 1) * chunk].to(u.shard.device))
+            u.gathered = False if u is self.root else u.gathered
+
+    def shard_state_dict(self) -> Dict:
+        return {"rank": self.rank, "world": self.world, "step": self.step_count,
+                "units": {u.name: {"shard": u.shard, "m": u.m, "v": u.v}
+                          for u in self.units + ([self.root] if self.root else [])}}
+
+    def load_shard_state_dict(self, sd: Dict) -> None:
+        assert sd["world"] == self.world and sd["rank"] == self.rank, "shard file belongs to another rank layout"
+        self.step_count = sd["step"]
+        for u in self.units + ([self.root] if self.root else []):
+            s = sd["units"][u.name]
+            u.shard.copy_(s["shard"])
+            u.m.copy_(s["m"])
+            u.v.copy_(s["v"])
+
+    def param_bytes_per_rank(self) -> int:
+        es = torch.empty(0, dtype=self.dtype).element_size()
+        return sum(u.shard.numel() for u in self.units + ([self.root] if self.root else [])) * es
+
+
+class _ShardOptimizer:
+    """Optimizer-shaped handle (``param_groups`` for LR schedulers, state dicts)."""
+
+    def __init__(self, plan: FullyShardedDataParallel):
+        self.plan = plan
+        self.param_groups = [plan.hyper]
+        plan.hyper.setdefault("params", [])
+
+    def state_dict(self):
+        return self.plan.shard_state_dict()
+
+    def load_state_dict(self, sd):
+        self.plan.load_shard_state_dict(sd)
+
+    def zero_grad(self, set_to_none: bool = True):
+        for u in self.plan.units + ([self.plan.root] if self.plan.root else []):
+            u.grad_shard.zero_()
+
+    def step(self):
+        raise RuntimeError("step through FullyShardedDataParallel.reduce_clip_and_step")

@@ -167,6 +167,40 @@ def load_sharded(d: str, model, dp, rank: int, map_location="cpu") -> Dict:
     return torch.load(ts, map_location=map_location, weights_only=False) if os.path.exists(ts) else {}
 
 
+def save_param_sharded(root: str, step: int, plan, training_state: Dict, rank: int, keep: int = 3) -> str:
+    """Checkpoint of the parameter-sharded plan: every rank helps gather the full parameters (rank 0
+    writes them as an ordinary ``model.pt``) and writes its own shards with their AdamW moments."""
+    import torch.distributed as dist
+    d = os.path.join(root, f"checkpoint-{step}")
+    os.makedirs(d, exist_ok=True)
+    full = plan.full_state_dict(to_cpu=True)
+    if rank == 0:
+        _atomic_save(full, os.path.join(d, "model.pt"))
+        _atomic_save(training_state, os.path.join(d, "training_state.pt"))
+    _atomic_save(plan.shard_state_dict(), os.path.join(d, f"shards-rank{rank}.pt"))
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+    if rank == 0:
+        prune_checkpoints(root, keep)
+    return d
+
+
+def load_param_sharded(d: str, plan, rank: int) -> Dict:
+    """Restores shards and moments when the file of this rank matches the current layout, otherwise the
+    parameters alone from ``model.pt`` (any world size)."""
+    f = os.path.join(d, f"shards-rank{rank}.pt")
+    done = False
+    if os.path.exists(f):
+        sd = torch.load(f, map_location="cpu", weights_only=False)
+        if sd.get("world") == plan.world and sd.get("rank") == plan.rank:
+            plan.load_shard_state_dict(sd)
+            done = True
+    if not done:
+        plan.load_full_state_dict(torch.load(os.path.join(d, "model.pt"), map_location="cpu", weights_only=False))
+    ts = os.path.join(d, "training_state.pt")
+    return torch.load(ts, map_location="cpu", weights_only=False) if os.path.exists(ts) else {}
+
+
 def _atomic_save(obj, path: str) -> None:
     os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
     tmp = path + ".tmp"

@@ -79,6 +79,8 @@ class RunSpec:
     step_deadline_s: float = 0.0           # > 0 arms the step watchdog
     transport: Optional[str] = None
     jsonl: Optional[str] = None
+    shard_params: bool = False             # ZeRO-3 / FULL_SHARD plan (AdamW) instead of replicated parameters
+    cpu_offload: bool = False              # with shard_params: shards and optimizer state in pinned host memory
     extra: Dict[str, Any] = field(default_factory=dict)
 
 
@@ -194,7 +196,19 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
         reallocate_model_experts(model, entropy_threshold=spec.entropy_threshold, verbose=is_main)
 
     dp = None
-    if world > 1:
+    if spec.shard_params:
+        # the reference's train_distributed.py regime: parameters sharded per block, AdamW on the shards
+        from ..parallel.fsdp import FullyShardedDataParallel
+        assert cfg.ep_size == 1, "the parameter-sharded plan does not combine with expert parallelism"
+        dp = FullyShardedDataParallel(model, lr=opt_cfg.get("adamw_lr", train_cfg.get("max_lr", 3e-4)) * spec.lr_scale,
+                                      betas=tuple(opt_cfg.get("adamw_betas", (0.9, 0.95))),
+                                      weight_decay=opt_cfg.get("weight_decay", train_cfg.get("weight_decay", 0.01)),
+                                      cpu_offload=spec.cpu_offload)
+        optimizer = dp.optimizer
+        if is_main:
+            print(f"parameter-sharded plan: {dp.param_bytes_per_rank() / 2**20:.1f} MiB of parameters per rank"
+                  f"{' (host memory)' if spec.cpu_offload else ''}")
+    elif world > 1:
         from ..parallel.zero import ParallelPlan, ShardedDataParallel
         okind = "muon" if opt_cfg.get("type", "adamw") == "muon" else "adamw"
         pools = [ShardedDataParallel(model, optimizer_kind=okind, lr=opt_cfg.get("muon_lr", 1e-3) * spec.lr_scale,
@@ -234,8 +248,11 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
     engine = TrainEngine(model, optimizer, sched, train_cfg["gradient_clip_norm"], accum, amp, dp, device)
     engine.global_step, engine.tokens_seen = start_step, tokens_seen
     if resume and os.path.isdir(resume):
-        st = (ckpt.load_sharded(resume, model, dp.pools[0], rank, device) if dp is not None
-              else ckpt.load_format_c(resume, model, optimizer, device))
+        if spec.shard_params:
+            st = ckpt.load_param_sharded(resume, dp, rank)
+        else:
+            st = (ckpt.load_sharded(resume, model, dp.pools[0], rank, device) if dp is not None
+                  else ckpt.load_format_c(resume, model, optimizer, device))
         engine.global_step = start_step = st.get("step", 0)
         engine.tokens_seen = st.get("tokens_seen", 0)
 
@@ -255,7 +272,9 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
 
     def save(step: int, suffix: Optional[str] = None):
         state = {"step": step, "tokens_seen": engine.tokens_seen, "config_path": spec.config_path}
-        if dp is not None:
+        if spec.shard_params:
+            ckpt.save_param_sharded(cdir, step, dp, state, rank)
+        elif dp is not None:
             ckpt.save_sharded(cdir, step, model, dp.pools[0], state, rank)
         elif spec.checkpoint_format == "C":
             ckpt.save_format_c(cdir, step, model, optimizer, state)

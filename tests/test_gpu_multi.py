@@ -142,3 +142,60 @@ def test_expert_parallel_fused_exchange_2gpus(tmp_path):
                         "--master-addr", "127.0.0.1", "--master-port", "29583", str(f)],
                        env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "EP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+FSDP_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["KMOE_ROOT"])
+from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig, MoETransformer
+from kolmogorov_moe_architecture_b200.ops import cuda_ops
+from kolmogorov_moe_architecture_b200.parallel.zero import ShardedDataParallel
+from kolmogorov_moe_architecture_b200.parallel.fsdp import FullyShardedDataParallel
+from kolmogorov_moe_architecture_b200.training.engine import TrainEngine
+rank = int(os.environ["RANK"]); torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+cfg = AdvancedMoEConfig(vocab_size=512, d_model=128, n_layers=4, n_heads=2, n_kv_heads=1, head_dim=64, d_ff=256,
+                        d_ff_expert=128, n_experts=4, moe_layers=(1, 2), mamba_layers=(1,), max_seq_len=64,
+                        n_pred_tokens=2, aux_loss_weights=(1.0, 0.5), mamba_moe_mode="moe_ffn", dropout=0.0,
+                        attention_dropout=0.0, residual_dropout=0.0)
+out, losses = {}, {}
+for kind in ("replicated", "sharded"):
+    torch.manual_seed(0)
+    model = MoETransformer(cfg, verbose=False).cuda().to(torch.bfloat16)
+    n_full = sum(p.numel() for p in model.parameters())
+    if kind == "replicated":
+        dp = ShardedDataParallel(model, optimizer_kind="adamw", adamw_lr=2e-3, transport="nccl")
+    else:
+        dp = FullyShardedDataParallel(model, lr=2e-3)
+        assert all(p.numel() == 0 for p in model.parameters())
+        assert dp.param_bytes_per_rank() <= 0.55 * n_full * 2
+    eng = TrainEngine(model, dp.optimizer, grad_clip=1.0, dp=dp)
+    g = torch.Generator().manual_seed(5 + rank)
+    ls = []
+    for s in range(3):
+        ls.append(eng.step(torch.randint(0, 512, (2, 64), generator=g).cuda()).loss_value())
+    cuda_ops.check_status()
+    losses[kind] = ls
+    if kind == "replicated":
+        out[kind] = {n: p.detach().float().clone() for n, p in model.named_parameters()}
+    else:
+        out[kind] = {n: t.float().cuda() for n, t in dp.full_state_dict().items()}
+err = max((out["replicated"][n] - out["sharded"][n]).abs().max().item() for n in out["replicated"])
+ref = max(t.abs().max().item() for t in out["replicated"].values())
+assert max(abs(a - b) for a, b in zip(losses["replicated"], losses["sharded"])) < 5e-2, losses
+assert err < 3e-2 * ref, (err, ref)
+if rank == 0: print("FSDP_OK", err, losses)
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_param_sharded_plan_matches_replicated_2gpus(tmp_path):
+    """ZeRO-3 style plan (parameters gathered per block into two rotating buffers) against the replicated plan."""
+    f = tmp_path / "fsdp_worker.py"
+    f.write_text(FSDP_WORKER)
+    env = dict(os.environ, KMOE_ROOT=ROOT, NCCL_NVLS_ENABLE="0", KMOE_STRICT="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29585", str(f)],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "FSDP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]

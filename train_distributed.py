@@ -2,9 +2,11 @@
 
     torchrun --nproc_per_node=8 train_distributed.py --config configs/training_4.5b.yaml
 
-One process per GPU over NCCL.  Parameters are replicated in bf16; reduced gradients and
+One process per GPU over NCCL.  By default parameters are replicated in bf16; reduced gradients and
 optimizer state are sharded by whole tensors (one reduce-scatter and one all-gather per step,
 run by this library's NVLink peer kernels when peer access is available, NCCL otherwise).
+``--shard-params`` selects the reference's regime instead (parameters sharded per block, gathered
+around each block's forward and backward, AdamW on the shards, optional ``--cpu-offload``).
 ``moe_implementation: expert_parallel`` in the YAML shards the experts over an expert-parallel
 group with differentiable dispatch/combine.  Adds what the reference's script lacks: seeding,
 global-norm clipping across shards, Muon, sharded checkpoints and ``--resume``.
@@ -20,7 +22,11 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description="Distributed MoE Training")
     ap.add_argument("--config", type=str, required=True)
     ap.add_argument("--resume", type=str, default=None)
-    ap.add_argument("--cpu-offload", action="store_true", help="accepted for compatibility (parameters stay on the GPU)")
+    ap.add_argument("--shard-params", action="store_true",
+                    help="shard the parameters per block over the ranks (ZeRO-3 / FULL_SHARD, AdamW) instead of "
+                         "replicating them; for models that do not fit one GPU")
+    ap.add_argument("--cpu-offload", action="store_true",
+                    help="with --shard-params: keep the shards and optimizer state in pinned host memory")
     ap.add_argument("--no-activation-checkpointing", action="store_true")
     ap.add_argument("--activation-checkpointing", action="store_true",
                     help="recompute blocks in backward (off by default: 180 GB of HBM holds the activations)")
@@ -38,7 +44,8 @@ def main(argv=None):
     spec = RunSpec(config_path=a.config, steps=a.steps, resume=a.resume, weights="bf16", checkpoint_format="C",
                    checkpoint_dir=a.checkpoint_dir, grad_checkpoint=a.activation_checkpointing,
                    data_mode="synthetic" if a.synthetic else "streaming", debug=a.debug, debug_interval=a.debug_interval,
-                   transport=a.transport, jsonl=a.jsonl)
+                   transport=a.transport, jsonl=a.jsonl, shard_params=a.shard_params or a.cpu_offload,
+                   cpu_offload=a.cpu_offload)
     return run_training(spec)
 
 
