@@ -37,6 +37,9 @@ struct AttnArgs {
   __nv_bfloat16* out;
   float* lse;
   int* status;
+  // optional (B, S): first position of the packed document that contains each position; a query then sees
+  // only keys k with doc_start[q] <= k <= q (block-diagonal causal mask of packed sequences)
+  const int* doc_start;
 };
 
 // Byte offset of the 16-byte chunk holding (row, col..col+7) in a K-major 128B-swizzled tile
@@ -171,13 +174,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int qi = q0 + r;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     float m_used = -INFINITY, l = 0.f;
+    const int qstart = (a.doc_start != nullptr && qi < a.S) ? a.doc_start[(size_t)b * a.S + qi] : 0;
     for (int j = 0; j < nblk; ++j) {
       const int st = j & 1;
       if (!mbar_wait(&s_full[st], (j >> 1) & 1)) { if (lane == 0) atomicExch(a.status, 18); goto teardown; }
       tc_fence_after();
       const uint32_t ts = tmem + lane_base + COL_S0 + st * FWD_BN;
       const int k0 = j * FWD_BN;
-      const bool need_mask = (k0 + FWD_BN > q0) || (k0 + FWD_BN > a.S);
+      const bool need_mask = (k0 + FWD_BN > q0) || (k0 + FWD_BN > a.S) || (k0 < qstart);
       uint32_t sv[FWD_BN];
       {
         uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[0]);
@@ -192,18 +196,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
       for (int i = 0; i < FWD_BN; ++i) {
         float s = __uint_as_float(sv[i]) * a.scale_log2;
-        if (need_mask && (k0 + i > qi || k0 + i >= a.S)) s = -INFINITY;
+        if (need_mask && (k0 + i > qi || k0 + i >= a.S || k0 + i < qstart)) s = -INFINITY;
         sv[i] = __float_as_uint(s);
         mx = fmaxf(mx, s);
       }
       const bool grow = mx > m_used + RESCALE_THRESHOLD;      // always true on the first step
       const float m_new = grow ? mx : m_used;
       const float alpha = grow ? exp2f(m_used - m_new) : 1.f;
+      // a row that has not met a visible key yet (its document starts in a later block) has m_new = -inf
+      const float m_exp = (m_new == -INFINITY) ? 0.f : m_new;
       float rs = 0.f;
       uint32_t pk[FWD_BN / 2];
 #pragma unroll
       for (int i = 0; i < FWD_BN; i += 2) {
-        const float p0 = exp2f(__uint_as_float(sv[i]) - m_new), p1 = exp2f(__uint_as_float(sv[i + 1]) - m_new);
+        const float p0 = exp2f(__uint_as_float(sv[i]) - m_exp), p1 = exp2f(__uint_as_float(sv[i + 1]) - m_exp);
         rs += p0 + p1;
         pk[i >> 1] = pack_bf16(p0, p1);
       }
@@ -283,6 +289,7 @@ struct AttnBwdArgs {
   __nv_bfloat16* dk;    // [B,S,Hkv,D]
   __nv_bfloat16* dv;
   int* status;
+  const int* doc_start;  // optional (B, S), see AttnArgs
 };
 
 // delta[b,h,s] = sum_d dO * O.  One warp per (b,s,h) row.
@@ -441,6 +448,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const size_t stat = ((size_t)b * a.H + h) * a.S + (row_ok ? qi : 0);
     const float lse2 = a.lse[stat] * 1.4426950408889634f;
     const float dlt = a.delta[stat];
+    const int qstart = (a.doc_start != nullptr && row_ok) ? a.doc_start[(size_t)b * a.S + qi] : 0;
     for (int j = 0; j < nblk; ++j) {
       if (!mbar_wait(&sdp_full[j & 1], (j >> 1) & 1)) { if (lane == 0) atomicExch(a.status, 26); goto teardown; }
       const uint32_t tbuf = tmem + lane_base + (j & 1) * COL_BUF;
@@ -459,7 +467,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int kj = k0 + c + i + e;
-            const bool dead = (kj > qi) || (kj >= a.S) || !row_ok;
+            const bool dead = (kj > qi) || (kj >= a.S) || !row_ok || (kj < qstart);
             const float p = dead ? 0.f : exp2f(__uint_as_float(sv[i + e]) * a.scale_log2 - lse2);
             v2[e] = p * (__uint_as_float(dv_[i + e]) - dlt) * a.scale;
           }
@@ -528,6 +536,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __shared__ uint64_t kv_full, q_full[2], q_empty[2], st_full[2], pds_full, pds_free, acc_full;
   __shared__ uint32_t tmem_slot;
   __shared__ float s_lse[BWD_SUB], s_delta[BWD_SUB];
+  __shared__ int s_start[BWD_SUB];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kb = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
@@ -640,6 +649,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const size_t si = ((size_t)b * a.H + h) * a.S + (qi < a.S ? qi : 0);
         s_lse[r] = a.lse[si] * 1.4426950408889634f;
         s_delta[r] = a.delta[si];
+        s_start[r] = (a.doc_start != nullptr && qi < a.S) ? a.doc_start[(size_t)b * a.S + qi] : 0;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       uint32_t pt[BWD_SUB / 2], dst[BWD_SUB / 2];
@@ -655,7 +665,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int qi = qrow + c + i + e;
-            const bool dead = (kj > qi) || (qi >= a.S) || (kj >= a.S);
+            const bool dead = (kj > qi) || (qi >= a.S) || (kj >= a.S) || (kj < s_start[c + i + e]);
             pv[e] = dead ? 0.f : exp2f(__uint_as_float(sv[i + e]) * a.scale_log2 - s_lse[c + i + e]);
             dv2[e] = pv[e] * (__uint_as_float(dv_[i + e]) - s_delta[c + i + e]) * a.scale;
           }
@@ -738,7 +748,7 @@ static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
 }  // namespace kmoe
 
 extern "C" int kmoe_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int H,
-                             int Hkv, int D, float scale, int* status, cudaStream_t st) {
+                             int Hkv, int D, float scale, const int* doc_start, int* status, cudaStream_t st) {
   using namespace kmoe;
   if (D != 64 && D != 128) return -1;
   if (H % Hkv) return -2;
@@ -747,7 +757,7 @@ extern "C" int kmoe_attn_fwd(const void* q, const void* k, const void* v, void* 
   if (rc) return rc;
   if ((rc = make_bshd_tmap(&tk, k, B, S, Hkv, D, FWD_BN))) return rc;
   if ((rc = make_bshd_tmap(&tv, v, B, S, Hkv, D, FWD_BN))) return rc;
-  AttnArgs a{B, S, H, Hkv, scale * 1.4426950408889634f, (__nv_bfloat16*)out, lse, status};
+  AttnArgs a{B, S, H, Hkv, scale * 1.4426950408889634f, (__nv_bfloat16*)out, lse, status, doc_start};
   return D == 128 ? launch_attn_fwd<128>(tq, tk, tv, a, st) : launch_attn_fwd<64>(tq, tk, tv, a, st);
 }
 
@@ -786,12 +796,12 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
 // delta is scratch of B*H*S floats.
 extern "C" int kmoe_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
                              const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int H,
-                             int Hkv, int D, float scale, int* status, cudaStream_t st) {
+                             int Hkv, int D, float scale, const int* doc_start, int* status, cudaStream_t st) {
   using namespace kmoe;
   if (D != 64 && D != 128) return -1;
   if (H % Hkv) return -2;
   attn_delta_kernel<<<148 * 4, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, B, S, H, D);
   AttnBwdArgs a{B, S, H, Hkv, scale, scale * 1.4426950408889634f, lse, delta, (__nv_bfloat16*)dq,
-                (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, status};
+                (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, status, doc_start};
   return D == 128 ? launch_attn_bwd<128>(q, k, v, d_o, a, st) : launch_attn_bwd<64>(q, k, v, d_o, a, st);
 }

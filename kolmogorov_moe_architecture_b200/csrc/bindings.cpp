@@ -268,7 +268,15 @@ Tensor moe_combine_dw(const Tensor& Y, const Tensor& dout, const Tensor& pos, in
 }
 
 // -------------------------------------------------------------------- attention
-std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale, Tensor status) {
+static const int* doc_ptr(const OptT& doc_start, int64_t B, int64_t S) {
+  if (!doc_start.has_value() || !doc_start->defined()) return nullptr;
+  TORCH_CHECK(doc_start->is_cuda() && doc_start->scalar_type() == at::kInt && doc_start->is_contiguous() &&
+              doc_start->numel() == B * S, "doc_start must be a contiguous (B, S) int32 CUDA tensor");
+  return doc_start->data_ptr<int>();
+}
+
+std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale,
+                                    const OptT& doc_start, Tensor status) {
   c10::cuda::CUDAGuard guard(q.device());
   need_bf16(q, "q"); need_bf16(k, "k"); need_bf16(v, "v");
   TORCH_CHECK(q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && q.dim() == 4);
@@ -276,12 +284,13 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
   Tensor out = at::empty_like(q);
   Tensor lse = at::empty({B, H, S}, q.options().dtype(at::kFloat));
   check(kmoe_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), B, S, H, Hkv,
-                      D, (float)scale, status.data_ptr<int>(), cur_stream()), "attn_fwd");
+                      D, (float)scale, doc_ptr(doc_start, B, S), status.data_ptr<int>(), cur_stream()), "attn_fwd");
   return {out, lse};
 }
 
 std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
-                                            const Tensor& d_o, const Tensor& lse, double scale, Tensor status) {
+                                            const Tensor& d_o, const Tensor& lse, double scale, const OptT& doc_start,
+                                            Tensor status) {
   c10::cuda::CUDAGuard guard(q.device());
   need_bf16(d_o, "do");
   TORCH_CHECK(d_o.is_contiguous() && o.is_contiguous());
@@ -290,7 +299,7 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& q, const Tensor& k, co
   Tensor delta = at::empty({B, H, S}, lse.options());
   check(kmoe_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr<float>(),
                       delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, H, Hkv, D,
-                      (float)scale, status.data_ptr<int>(), cur_stream()), "attn_bwd");
+                      (float)scale, doc_ptr(doc_start, B, S), status.data_ptr<int>(), cur_stream()), "attn_bwd");
   return {dq, dk, dv};
 }
 

@@ -139,11 +139,13 @@ int kmoe_moe_combine_dw(const void* Y, const void* dout, const int* pos, float* 
 
 // ----------------------------------------------------------------------- attention
 // Causal GQA flash attention. q/out/dq [B,S,H,D], k/v/dk/dv [B,S,Hkv,D] bf16; lse, delta [B,H,S] fp32; D in {64,128}.
+// doc_start (optional, (B, S) int32): first position of the packed document containing each position; a query
+// then attends to keys doc_start[q] <= k <= q only (causal attention that does not cross document boundaries).
 int kmoe_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int H, int Hkv,
-                  int D, float scale, int* status, cudaStream_t st);
+                  int D, float scale, const int* doc_start, int* status, cudaStream_t st);
 int kmoe_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
                   float* delta, void* dq, void* dk, void* dv, int B, int S, int H, int Hkv, int D, float scale,
-                  int* status, cudaStream_t st);
+                  const int* doc_start, int* status, cudaStream_t st);
 
 // ------------------------------------------- collectives over NVLink peer pointers
 // `*_ptrs`: device addresses (as integers) of the same symmetric buffer on every rank, indexed by rank.

@@ -140,6 +140,34 @@ def document_attention_mask(doc_ids: torch.Tensor) -> torch.Tensor:
     return torch.zeros(ok.shape, dtype=torch.float32, device=doc_ids.device).masked_fill(~ok, float("-inf"))[:, None]
 
 
+class PackedDocs:
+    """Document boundaries of a packed batch, for attention that must not cross documents.
+
+    Pass an instance as ``attention_mask`` to ``MoETransformer``: on CUDA the flash-attention kernels apply the
+    boundaries directly (each query row only needs the first position of its document), so packed
+    training keeps the fast path; elsewhere it becomes the additive mask of ``document_attention_mask``.
+    The reference builds the dense (B, 1, S, S) mask and falls off its flash path (train_custom.py:429-463)."""
+
+    def __init__(self, doc_ids: Optional[torch.Tensor] = None, doc_start: Optional[torch.Tensor] = None):
+        from ..ops import eager
+        assert (doc_ids is None) != (doc_start is None), "give document ids or start positions"
+        self.doc_start = eager.doc_start_from_ids(doc_ids) if doc_start is None else doc_start.to(torch.int32)
+
+    @property
+    def device(self):
+        return self.doc_start.device
+
+    def to(self, device, non_blocking: bool = False) -> "PackedDocs":
+        return PackedDocs(doc_start=self.doc_start.to(device, non_blocking=non_blocking))
+
+    def chunk(self, n: int, dim: int = 0):
+        return [PackedDocs(doc_start=t) for t in self.doc_start.chunk(n, dim=dim)]
+
+    def dense_mask(self, dtype=torch.float32) -> torch.Tensor:
+        from ..ops import eager
+        return eager.doc_start_to_mask(self.doc_start, dtype)
+
+
 class DolmaMemoryMappedDataset(Dataset):
     def __init__(self, data_path: str, seq_len: int = 2048, n_pred_tokens: int = 4, vocab_size: int = 50257):
         super().__init__()

@@ -38,6 +38,10 @@ class GroupedQueryAttention(nn.Module):
         k = self.k_proj(hidden_states).view(B, S, self.n_kv_heads, self.head_dim)
         v = self.v_proj(hidden_states).view(B, S, self.n_kv_heads, self.head_dim)
         q, k = self.rope(q, k, position_ids)
+        if hasattr(attention_mask, "doc_start"):            # packed documents: boundaries, not a dense mask
+            out = ops.attention(q, k, v, causal=True, dropout_p=self.attention_dropout, training=self.training,
+                                doc_start=attention_mask.doc_start)
+            return self.o_proj(out.reshape(B, S, self.n_heads * self.head_dim))
         if attention_mask is not None and attention_mask.dim() == 2:
             m = attention_mask[:, None, None, :].to(q.dtype)
             attention_mask = (1.0 - m) * torch.finfo(q.dtype).min

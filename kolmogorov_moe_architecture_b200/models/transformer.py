@@ -72,7 +72,11 @@ class MoETransformer(nn.Module):
         """Embedding + blocks + final norm. Returns (hidden, summed aux loss)."""
         h = self.token_embedding(input_ids)
         add_mask = None
-        if attention_mask is not None:
+        if hasattr(attention_mask, "doc_start"):            # PackedDocs: handed to the attention layers as is
+            add_mask = attention_mask
+        elif attention_mask is not None and attention_mask.dim() == 4:    # already additive (B, 1, S, S)
+            add_mask = attention_mask.to(h.dtype).clamp(min=torch.finfo(h.dtype).min)
+        elif attention_mask is not None:
             add_mask = (1.0 - attention_mask[:, None, None, :].to(h.dtype)) * torch.finfo(h.dtype).min
         aux = 0.0
         for layer in self.layers:
@@ -91,6 +95,8 @@ class MoETransformer(nn.Module):
                 position_ids: Optional[torch.Tensor] = None, labels: Optional[torch.Tensor] = None,
                 return_logits: bool = True) -> Dict[str, torch.Tensor]:
         hidden, aux = self.forward_hidden(input_ids, attention_mask, position_ids)
+        if hasattr(attention_mask, "doc_start") or (attention_mask is not None and attention_mask.dim() == 4):
+            attention_mask = None                           # attention structure, not a padding mask for the loss
         loss = lm_loss = None
         info: Dict[str, torch.Tensor] = {}
         logits_list = None

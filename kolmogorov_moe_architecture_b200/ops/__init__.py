@@ -45,10 +45,15 @@ def swiglu(gate, up):
     return eager.swiglu(gate, up)
 
 
-def attention(q, k, v, causal=True, attn_mask=None, dropout_p=0.0, training=False):
+def attention(q, k, v, causal=True, attn_mask=None, dropout_p=0.0, training=False, doc_start=None):
+    """``doc_start`` (B, S): packed-document boundaries (see ``eager.doc_start_from_ids``); on CUDA the flash
+    kernels apply them directly, elsewhere they become an additive mask."""
     if attn_mask is None and not (dropout_p > 0.0 and training) and _use_cuda(q):
         from . import cuda_ops
-        return cuda_ops.attention(q, k, v, causal)
+        return cuda_ops.attention(q, k, v, causal, doc_start)
+    if doc_start is not None:
+        dm = eager.doc_start_to_mask(doc_start, q.dtype)
+        attn_mask = dm if attn_mask is None else attn_mask + dm
     return eager.attention(q, k, v, causal, attn_mask, dropout_p, training)
 
 
@@ -130,3 +135,5 @@ topk_softmax_route = eager.topk_softmax_route
 moe_aux_loss = eager.moe_aux_loss
 capacity_keep_mask = eager.capacity_keep_mask
 rope_tables = eager.rope_tables
+doc_start_from_ids = eager.doc_start_from_ids
+doc_start_to_mask = eager.doc_start_to_mask

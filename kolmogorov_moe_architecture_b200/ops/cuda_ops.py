@@ -282,9 +282,9 @@ def selective_scan(u, delta, A, Bm, Cm, D, z, delta_bias, delta_softplus=True):
 
 
 # ----------------------------------------------------------------- attention
-def attention(q, k, v, causal=True):
+def attention(q, k, v, causal=True, doc_start=None):
     from . import attention_cuda
-    return attention_cuda.attention(q, k, v, causal)
+    return attention_cuda.attention(q, k, v, causal, doc_start)
 
 
 # ------------------------------------------------------------- MoE experts

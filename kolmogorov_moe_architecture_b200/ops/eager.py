@@ -70,6 +70,24 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
     return torch.matmul(p, vh).transpose(1, 2).contiguous()   # B,S,H,D
 
 
+def doc_start_from_ids(doc_ids: torch.Tensor) -> torch.Tensor:
+    """(B, S) document ids of a packed batch (constant inside a document) -> (B, S) int32 position of the first
+    token of each position's document."""
+    B, S = doc_ids.shape
+    pos = torch.arange(S, device=doc_ids.device).expand(B, S)
+    change = torch.ones(B, S, dtype=torch.bool, device=doc_ids.device)
+    change[:, 1:] = doc_ids[:, 1:] != doc_ids[:, :-1]
+    return torch.cummax(torch.where(change, pos, torch.zeros_like(pos)), dim=1).values.to(torch.int32)
+
+
+def doc_start_to_mask(doc_start: torch.Tensor, dtype=torch.float32) -> torch.Tensor:
+    """Additive (B, 1, S, S) mask equivalent to ``doc_start``: key k is hidden from query q when k < doc_start[q]."""
+    B, S = doc_start.shape
+    k = torch.arange(S, device=doc_start.device).view(1, 1, S)
+    hidden = k < doc_start.view(B, S, 1)
+    return torch.zeros(B, 1, S, S, dtype=dtype, device=doc_start.device).masked_fill(hidden.unsqueeze(1), float("-inf"))
+
+
 # ---------------------------------------------------------------------- mamba
 def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
                   activation: bool = True) -> torch.Tensor:

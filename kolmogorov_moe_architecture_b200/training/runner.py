@@ -29,7 +29,7 @@ import torch
 
 from ..config import AdvancedMoEConfig
 from ..data import (DolmaStreamingDataset, PackedDocumentDataset, PinnedPrefetcher, SyntheticTokenDataset,
-                    TokenizerWrapper, document_attention_mask)
+                    TokenizerWrapper, PackedDocs, document_attention_mask)
 from ..models.transformer import MoETransformer
 from ..parallel import mesh as pmesh
 from ..utils.config_io import load_yaml, model_config_strict, model_config_tolerant, section
@@ -292,10 +292,11 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
                 b = next(it)
             am = None
             if spec.document_mask and "doc_ids" in b:
-                am = document_attention_mask(b["doc_ids"].to(device))
+                # boundaries instead of a dense (B, 1, S, S) mask: attention stays on the flash kernels
+                am = PackedDocs(doc_ids=b["doc_ids"].to(device))
             with timer.phase("step"):
                 if am is not None:
-                    last_stats = _step_with_mask(engine, b, am)
+                    last_stats = engine.step(b["input_ids"], b.get("labels"), attention_mask=am)
                 else:
                     last_stats = engine.step(b["input_ids"], b.get("labels"))
             step += 1

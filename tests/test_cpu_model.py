@@ -151,3 +151,23 @@ def test_count_parameters_and_presets():
     assert d2.moe_layers == b.moe_layers
     with pytest.raises(TypeError):
         kmoe.AdvancedMoEConfig.from_dict({"not_a_field": 1})
+
+
+def test_packed_docs_equals_dense_document_mask():
+    """Document boundaries passed as ``PackedDocs`` give the same model output as the dense block-diagonal mask."""
+    import kolmogorov_moe_architecture_b200 as kmoe
+    from kolmogorov_moe_architecture_b200.data import PackedDocs, document_attention_mask
+    cfg = kmoe.get_tiny_debug_config(vocab_size=128, d_model=64, n_heads=2, n_kv_heads=1, head_dim=32, d_ff=128,
+                                     d_ff_expert=64, max_seq_len=24, n_pred_tokens=2, aux_loss_weights=(1.0, 0.5))
+    torch.manual_seed(0)
+    m = kmoe.MoETransformer(cfg, verbose=False).eval()
+    ids = torch.randint(0, 128, (2, 24))
+    doc_ids = torch.tensor([[0] * 5 + [1] * 10 + [2] * 9, [3] * 24])
+    pd = PackedDocs(doc_ids=doc_ids)
+    assert pd.doc_start[0].tolist() == [0] * 5 + [5] * 10 + [15] * 9 and pd.doc_start[1].tolist() == [0] * 24
+    with torch.no_grad():
+        a = m(ids, attention_mask=pd)["logits"]
+        b = m(ids, attention_mask=document_attention_mask(doc_ids))["logits"]
+        c = m(ids)["logits"]
+    assert torch.allclose(a, b, atol=1e-5)
+    assert not torch.allclose(a[0], c[0], atol=1e-3) and torch.allclose(a[1], c[1], atol=1e-5)

@@ -286,3 +286,27 @@ def test_mod_gather_combine_fwd_bwd(B, S, k, d):
     assert torch.equal(picked.float(), pr.detach())
     assert _rel(out, outr) < 1e-2
     assert _rel(h.grad, hr.grad) < 2e-2 and _rel(res.grad, rr.grad) < 1e-6 and _rel(w.grad, wr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,D", [(2, 384, 4, 2, 128), (1, 200, 2, 1, 64)])
+def test_flash_attention_packed_documents(B, S, H, Hkv, D):
+    """Document boundaries applied inside the flash kernels (forward, dQ, dK/dV) against eager attention with
+    the dense block-diagonal mask; documents start in the middle of key blocks and span several of them."""
+    ops, c, eager = _mods()
+    torch.manual_seed(8)
+    q, k, v = _bf(B, S, H, D, grad=True), _bf(B, S, Hkv, D, grad=True), _bf(B, S, Hkv, D, grad=True)
+    cuts = [[0, 37, 101, 270], [0, 150]][:B] if B > 1 else [[0, 5, 77, 140]]
+    doc_ids = torch.zeros(B, S, dtype=torch.long, device="cuda")
+    for b, cs in enumerate(cuts):
+        for i, s0 in enumerate(cs):
+            doc_ids[b, s0:] = i
+    ds = eager.doc_start_from_ids(doc_ids)
+    out = ops.attention(q, k, v, causal=True, doc_start=ds)
+    g = _bf(B, S, H, D)
+    out.backward(g)
+    c.check_status()
+    qr, kr, vr = _f32_leaf(q), _f32_leaf(k), _f32_leaf(v)
+    outr = eager.attention(qr, kr, vr, True, eager.doc_start_to_mask(ds))
+    outr.backward(g.float())
+    assert _rel(out, outr) < 2e-2
+    assert _rel(q.grad, qr.grad) < 3e-2 and _rel(k.grad, kr.grad) < 3e-2 and _rel(v.grad, vr.grad) < 3e-2
