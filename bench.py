@@ -42,6 +42,8 @@ def parse_args():
     ap.add_argument("--ep-size", type=int, default=1,
                     help="expert-parallel group size (experts split over it; dense parameters stay data-parallel)")
     ap.add_argument("--moe-dtype", default="bf16", choices=["bf16", "mxfp8"], help="expert GEMM number format")
+    ap.add_argument("--shard-params", action="store_true",
+                    help="parameter-sharded plan (ZeRO-3 / FULL_SHARD, AdamW) instead of replicated parameters")
     ap.add_argument("--transport", default=None, choices=[None, "p2p", "nccl"],
                     help="gradient/parameter collectives: own NVLink peer kernels (default when available) or NCCL")
     return ap.parse_args()
@@ -146,8 +148,13 @@ def run_ours(args):
         model = kmoe.MoETransformer(cfg, verbose=(rank == 0)).to(torch.bfloat16)
     n_params = sum(p.numel() for p in model.parameters())
     from kolmogorov_moe_architecture_b200.parallel.zero import ParallelPlan, ShardedDataParallel
-    dp = ShardedDataParallel(model, optimizer_kind=args.optimizer, transport=args.transport)
-    transport = dp.transport
+    if args.shard_params:
+        from kolmogorov_moe_architecture_b200.parallel.fsdp import FullyShardedDataParallel
+        dp = FullyShardedDataParallel(model, lr=3e-4)
+        transport = "full-shard-nccl"
+    else:
+        dp = ShardedDataParallel(model, optimizer_kind=args.optimizer, transport=args.transport)
+        transport = dp.transport
     if mesh is not None:
         experts = ShardedDataParallel(model, optimizer_kind="adamw", group=mesh.expert_dp_group, expert_params=True,
                                       grad_scale=1.0 / args.ep_size, broadcast_from_rank0=False, transport="nccl")
@@ -197,7 +204,9 @@ def run_ours(args):
                "d2h_bytes_per_step": 4, "ms_per_step": ms2 / args.steps, "last_loss": last}
     peak_gb = torch.cuda.max_memory_allocated() / 2**30
     if rank == 0:
-        valid = args.layers == 32 and B == 4 and S == 2048 and args.moe_dtype == "bf16"
+        valid = args.layers == 32 and B == 4 and S == 2048 and args.moe_dtype == "bf16" and not args.shard_params
+        if args.shard_params:
+            args.optimizer = "adamw (sharded)"
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -206,7 +215,8 @@ def run_ours(args):
             "config": {"model": "5B hybrid MoE (32L d2048 16/4 heads, 16 experts top-2 x16 MoE layers, "
                                 "Mamba d_state16, MoD 0.75, 4-token MTP, vocab 50304)",
                        "params_b": round(n_params / 1e9, 3), "global_batch": B * world, "seq_len": S,
-                       "parallelism": (f"dp{world}" + (f"-zero1-{transport}" if world > 1 else "")
+                       "parallelism": (f"dp{world}" + (f"-{transport}" if args.shard_params else
+                                                       (f"-zero1-{transport}" if world > 1 else ""))
                                        + (f"-ep{args.ep_size}-p2p" if args.ep_size > 1 else "")),
                        "moe_dtype": args.moe_dtype,
                        "optimizer": args.optimizer, "mamba_moe_mode": args.mamba_moe_mode,
