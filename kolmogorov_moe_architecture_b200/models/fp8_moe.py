@@ -17,7 +17,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import eager
-from ..ops.mxfp8 import fake_quant_mx, grouped_swiglu_mxfp8
+from ..ops.mxfp8 import fake_quant_mx, grouped_swiglu_mxfp8, linear_mx
 
 FP8_E4M3 = torch.float8_e4m3fn
 FP8_E5M2 = torch.float8_e5m2
@@ -45,7 +45,7 @@ class FP8Linear(nn.Module):
         nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return F.linear(fake_quant_mx(x, -1), fake_quant_mx(self.weight, -1), self.bias)
+        return linear_mx(x, self.weight, self.bias)
 
 
 class FP8GroupedExperts(nn.Module):

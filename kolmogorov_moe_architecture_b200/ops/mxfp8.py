@@ -125,6 +125,50 @@ def mm_mx(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return gemm_mx(aq, sa, bq, sb, torch.empty(M, N, dtype=torch.bfloat16, device=a.device), M=M, N=N, K=K)
 
 
+class _LinearMX(torch.autograd.Function):
+    """y = x W^T with all three GEMMs (forward, dgrad, wgrad) on the block-scaled fp8 path.
+    x (M, in), W (out, in); M, in and out multiples of 128."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        M, K = x.shape
+        N = w.shape[0]
+        xq, sx = quant_rows(x.contiguous())
+        wq, sw = _weight_quant(w, "rows")                      # (out, in): reduction over in
+        y = gemm_mx(xq, sx, wq, sw, torch.empty(M, N, dtype=x.dtype, device=x.device), M=M, N=N, K=K)
+        ctx.save_for_backward(x, w)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        M, K = x.shape
+        N = w.shape[0]
+        dy = dy.contiguous()
+        dyq, sdy = quant_rows(dy)                              # reduction over out
+        wT, swT = _weight_quant(w, "cols")                     # (in, out): reduction over out
+        dx = gemm_mx(dyq, sdy, wT, swT, torch.empty(M, K, dtype=dy.dtype, device=dy.device), M=M, N=K, K=N)
+        dyT, sdyT = quant_cols(dy)                             # (out, M): reduction over tokens
+        xT, sxT = quant_cols(x.contiguous())                   # (in, M)
+        dw = gemm_mx(dyT, sdyT, xT, sxT, torch.empty(N, K, dtype=w.dtype, device=w.device), M=N, N=K, K=M)
+        return dx, dw
+
+
+def linear_mx(x: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
+    """``F.linear`` with MXFP8 operands.  Uses the tensor-core path for CUDA bf16 inputs whose token count and
+    feature sizes are multiples of 128, fake-quantised operands with a bf16 multiply otherwise."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    ok = (x2.is_cuda and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x2.shape[0] % 128 == 0
+          and x2.shape[1] % 128 == 0 and w.shape[0] % 128 == 0 and x2.shape[0] > 0)
+    if ok:
+        y = _LinearMX.apply(x2, w)
+    else:
+        y = torch.nn.functional.linear(fake_quant_mx(x2, -1), fake_quant_mx(w, -1))
+    y = y.reshape(*lead, w.shape[0])
+    return y if bias is None else y + bias
+
+
 # Quantised copies of the expert weights are kept until the weights change, so a step with several
 # micro-batches (or forward + backward of one) quantises each orientation once.  A copy is valid while the
 # tensor's autograd version and the global epoch are unchanged; code that rewrites parameters through raw
