@@ -398,7 +398,8 @@ class ShardedDataParallel:
         # The fused AdamW kernel is HBM-bound and Muon's Newton-Schulz is tensor-core-bound: run them
         # on two streams so they overlap (they touch disjoint ranges of the flat buffers).
         side = None
-        if self.fused is not None and self.muon is not None and self.device.type == "cuda":
+        if (self.fused is not None and self.muon is not None and self.device.type == "cuda"
+                and os.environ.get("KMOE_OPT_OVERLAP", "1") != "0"):
             if self._side_stream is None:
                 self._side_stream = torch.cuda.Stream(device=self.device)
             side = self._side_stream
