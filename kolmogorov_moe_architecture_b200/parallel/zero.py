@@ -147,7 +147,20 @@ class ShardedDataParallel:
         self.p2p = None
         if self.transport == "p2p":
             from .p2p import SymmetricBuffers
-            self.p2p = SymmetricBuffers(total, dtype, device, group)
+            try:
+                self.p2p = SymmetricBuffers(total, dtype, device, group)
+            except Exception as e:                      # no peer mapping on this machine: use the library collectives
+                if transport == "p2p":
+                    raise
+                print(f"[kmoe] symmetric-memory set-up failed ({type(e).__name__}: {e}); using NCCL collectives", flush=True)
+                self.p2p = None
+            # every rank must take the same branch
+            flag = torch.tensor([1.0 if self.p2p is not None else 0.0], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+            if flag.item() == 0.0:
+                self.p2p = None
+                self.transport = "nccl" if dist.get_backend(group) == "nccl" else "gloo"
+        if self.transport == "p2p":
             self.flat_param, self.flat_grad = self.p2p.param, self.p2p.grad
         else:
             self.flat_param = torch.zeros(total, dtype=dtype, device=device)
