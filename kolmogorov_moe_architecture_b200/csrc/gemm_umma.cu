@@ -15,6 +15,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -48,12 +49,14 @@ struct GemmArgs {
   const float* row_scale;
   const float* alpha_dev;     // optional per-group multipliers of alpha / beta (BATCHED: index = group)
   const float* beta_dev;
+  int sym_upper;              // C is symmetric (A == B): compute only tiles that touch the upper triangle
   const long long* row_ptr;   // optional: address of each output row (may be peer memory); 0 = row not stored
   int* status;
 };
 
 struct Tile {
   int m_tile, n_tile, g_a, g_b, g_c, k0, k_blocks;
+  bool skip;   // symmetric output: the tile lies entirely below the diagonal and is filled by mirroring
 };
 
 __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
@@ -65,23 +68,42 @@ __device__ __forceinline__ bool get_tile(const GemmArgs& a, int idx, int num_m, 
   (void)n_out;
   int per_group = num_m * num_n;
   int g = 0, local = idx;
-  if (a.mode == KMOE_GEMM_BATCHED) {
-    g = idx / per_group;
-    local = idx - g * per_group;
-    if (g >= a.groups) return false;
-  } else if (idx >= per_group) {
-    return false;
+  if (a.sym_upper) {
+    // enumerate only the tiles that touch the upper triangle, row by row, so that the work is spread evenly
+    int kept = 0;
+    for (int m = 0; m < num_m; ++m) kept += num_n - min(num_n, (m * BM) / BN);
+    g = idx / kept;
+    local = idx - g * kept;
+    if (g >= (a.mode == KMOE_GEMM_BATCHED ? a.groups : 1)) return false;
+    int m = 0;
+    while (true) {
+      const int km = num_n - min(num_n, (m * BM) / BN);
+      if (local < km) break;
+      local -= km;
+      ++m;
+    }
+    t.m_tile = m;
+    t.n_tile = min(num_n, (m * BM) / BN) + local;
+  } else {
+    if (a.mode == KMOE_GEMM_BATCHED) {
+      g = idx / per_group;
+      local = idx - g * per_group;
+      if (g >= a.groups) return false;
+    } else if (idx >= per_group) {
+      return false;
+    }
+    // supertile of 8 m-tiles: neighbouring CTAs share B tiles and a narrow band of A
+    const int GM = 8;
+    int band = local / (GM * num_n);
+    int first_m = band * GM;
+    int gsz = min(num_m - first_m, GM);
+    int r = local - band * GM * num_n;
+    t.m_tile = first_m + r % gsz;
+    t.n_tile = r / gsz;
   }
-  // supertile of 8 m-tiles: neighbouring CTAs share B tiles and a narrow band of A
-  const int GM = 8;
-  int band = local / (GM * num_n);
-  int first_m = band * GM;
-  int gsz = min(num_m - first_m, GM);
-  int r = local - band * GM * num_n;
-  t.m_tile = first_m + r % gsz;
-  t.n_tile = r / gsz;
   t.k0 = 0;
   t.k_blocks = ceil_div(a.K, BK);
+  t.skip = false;
   if (a.mode == KMOE_GEMM_GROUPED_M) {
     int e = a.tile_group[t.m_tile];
     t.g_a = 0;
@@ -215,6 +237,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t ph = 0;
       Tile t;
       for (int idx = blockIdx.x; get_tile<BN>(args, idx, num_m, num_n, t); idx += gridDim.x) {
+        if (t.skip) continue;
         for (int kb = 0; kb < t.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
             atomicExch(args.status, 1);
@@ -254,9 +277,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t ph = 0;
       int it = 0;
       Tile t;
-      for (int idx = blockIdx.x; get_tile<BN>(args, idx, num_m, num_n, t); idx += gridDim.x, ++it) {
+      for (int idx = blockIdx.x; get_tile<BN>(args, idx, num_m, num_n, t); idx += gridDim.x) {
+        if (t.skip) continue;                  // `it` counts computed tiles only (it drives the barrier phases)
         const int acc = it & 1;
         const uint32_t acc_ph = (it >> 1) & 1;
+        ++it;
         if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1)) {
           atomicExch(args.status, 2);
           goto teardown;
@@ -294,9 +319,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
     Tile t;
-    for (int idx = blockIdx.x; get_tile<BN>(args, idx, num_m, num_n, t); idx += gridDim.x, ++it) {
+    for (int idx = blockIdx.x; get_tile<BN>(args, idx, num_m, num_n, t); idx += gridDim.x) {
+      if (t.skip) continue;
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
+      ++it;
       if (!mbar_wait(&tmem_full[acc], acc_ph)) {
         if (lane == 0) atomicExch(args.status, 4);
         goto teardown;
@@ -425,6 +452,21 @@ teardown:
   }
 }
 
+// Fills the tiles that a symmetric GEMM skipped: C[g][i][j] = C[g][j][i] for every 32x32 block that lies in a
+// tile entirely below the diagonal.  grid = (n/32, n/32, groups), block = (32, 8).
+__global__ void sym_mirror_kernel(__nv_bfloat16* __restrict__ C, int n, long long ldc, long long gstride, int bn) {
+  const int bx = blockIdx.x, by = blockIdx.y;
+  const int mt = (by * 32) / BM, nt = (bx * 32) / bn;
+  if ((nt + 1) * bn > mt * BM) return;                      // destination was computed
+  __shared__ __nv_bfloat16 tile[32][33];
+  __nv_bfloat16* Cg = C + (long long)blockIdx.z * gstride;
+  for (int r = threadIdx.y; r < 32; r += 8)                  // source block: rows 32*bx.., cols 32*by..
+    tile[r][threadIdx.x] = Cg[(long long)(bx * 32 + r) * ldc + by * 32 + threadIdx.x];
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += 8)
+    Cg[(long long)(by * 32 + r) * ldc + bx * 32 + threadIdx.x] = tile[threadIdx.x][r];
+}
+
 // ------------------------------------------------------------------ host side
 using TmapKey = std::tuple<const void*, int, long long, long long, long long, long long, int, int>;
 static std::map<TmapKey, CUtensorMap> g_tmap_cache;
@@ -524,6 +566,10 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
   a.out_f32 = d->out_f32; a.alpha = d->alpha; a.beta = d->beta;
   a.row_scale = d->row_scale; a.row_ptr = d->c_row_ptr; a.status = d->status;
   a.alpha_dev = d->alpha_dev; a.beta_dev = d->beta_dev;
+  a.sym_upper = d->sym_upper;
+  if (d->sym_upper && (d->M != d->N || swiglu || d->mode == KMOE_GEMM_GROUPED_M || d->out_f32 || d->N % 32 ||
+                       d->D != nullptr))
+    return -4;
 
   // The reduction extent seen by TMA: ragged batched GEMMs index a shared [sum K, rows] buffer.
   long long k_extent_a = d->K, k_extent_b = d->K;
@@ -546,20 +592,35 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
   }
   const int n_per_tile = swiglu ? BN / 2 : BN;
   long long total = m_tiles * ((d->N + n_per_tile - 1) / n_per_tile) * groups;
+  if (d->sym_upper) {
+    const long long nn = (d->N + BN - 1) / BN;
+    long long kept = 0;
+    for (long long m = 0; m < m_tiles; ++m) kept += nn - std::min<long long>(nn, (m * BM) / BN);
+    total = kept * groups;
+  }
   int grid = (int)(total < sms ? total : sms);
   if (grid < 1) grid = 1;
 
-#define KMOE_LAUNCH(BN_, AM_, BM_) return launch_variant<BN_, AM_, BM_>(tA, tB, tB2, a, grid, stream)
+  int lrc = 0;
+#define KMOE_LAUNCH(BN_, AM_, BM_) lrc = launch_variant<BN_, AM_, BM_>(tA, tB, tB2, a, grid, stream)
   if (BN == 256) {
     if (d->a_major == 0 && d->b_major == 0) KMOE_LAUNCH(256, 0, 0);
-    if (d->a_major == 0 && d->b_major == 1) KMOE_LAUNCH(256, 0, 1);
-    if (d->a_major == 1 && d->b_major == 0) KMOE_LAUNCH(256, 1, 0);
-    KMOE_LAUNCH(256, 1, 1);
+    else if (d->a_major == 0 && d->b_major == 1) KMOE_LAUNCH(256, 0, 1);
+    else if (d->a_major == 1 && d->b_major == 0) KMOE_LAUNCH(256, 1, 0);
+    else KMOE_LAUNCH(256, 1, 1);
   } else {
     if (d->a_major == 0 && d->b_major == 0) KMOE_LAUNCH(128, 0, 0);
-    if (d->a_major == 0 && d->b_major == 1) KMOE_LAUNCH(128, 0, 1);
-    if (d->a_major == 1 && d->b_major == 0) KMOE_LAUNCH(128, 1, 0);
-    KMOE_LAUNCH(128, 1, 1);
+    else if (d->a_major == 0 && d->b_major == 1) KMOE_LAUNCH(128, 0, 1);
+    else if (d->a_major == 1 && d->b_major == 0) KMOE_LAUNCH(128, 1, 0);
+    else KMOE_LAUNCH(128, 1, 1);
   }
 #undef KMOE_LAUNCH
+  if (lrc) return lrc;
+  if (d->sym_upper) {
+    // the tiles below the diagonal were skipped: mirror them from the computed upper part
+    dim3 mg((unsigned)(d->N / 32), (unsigned)(d->N / 32), (unsigned)groups);
+    sym_mirror_kernel<<<mg, dim3(32, 8), 0, stream>>>((__nv_bfloat16*)d->C, d->N, d->ldc, d->c_gstride, BN);
+    if (cudaGetLastError() != cudaSuccess) return -22;
+  }
+  return 0;
 }

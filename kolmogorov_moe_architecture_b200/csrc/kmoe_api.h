@@ -47,6 +47,9 @@ typedef struct KmoeGemmDesc {
   // multiplied by them, so scalars computed on the device (e.g. 1 / norm) need no separate pass.
   const float* alpha_dev;
   const float* beta_dev;
+  // C = A A^T style products (M == N, A and B the same operand, bf16 output, no addend): tiles entirely below
+  // the diagonal are not computed but mirrored from the upper part afterwards.
+  int sym_upper;
   int* status;             // device int; non-zero after the launch = a bounded wait expired
   int num_sms;             // 0 = query
 } KmoeGemmDesc;

@@ -85,13 +85,15 @@ def _count(n: int = 1):
 def gemm(A, B, C, *, M, N, Kd, mode=DENSE, epi=EPI_STORE, groups=1, a_major=MAJ_K, b_major=MAJ_K,
          lda, ldb, ldc, ldd=0, a_gs=0, b_gs=0, c_gs=0, B2=None, D=None, G=None, U=None,
          tile_group=None, num_m_tiles=None, k_begin=None, k_len=None, alpha=1.0, beta=0.0, row_scale=None,
-         row_ptr=None, alpha_dev=None, beta_dev=None):
+         row_ptr=None, alpha_dev=None, beta_dev=None, sym_upper=False):
     """``row_ptr`` (int64, one address per output row, 0 = skip) redirects each output row, e.g. into a
     peer GPU's buffer; ``C`` then only supplies the dtype.  ``alpha_dev`` / ``beta_dev`` (fp32, one entry
-    per group of a batched GEMM) multiply alpha / beta with values that live on the device."""
+    per group of a batched GEMM) multiply alpha / beta with values that live on the device.  ``sym_upper``:
+    the product is symmetric (A and B are the same operand, M == N): tiles below the diagonal are mirrored
+    instead of computed."""
     K.gemm(A, B, B2, C, D, G, U, mode, epi, M, N, Kd, groups, a_major, b_major, lda, ldb, ldc, ldd,
            a_gs, b_gs, c_gs, tile_group, num_m_tiles, k_begin, k_len, alpha, beta, row_scale, row_ptr,
-           alpha_dev, beta_dev, status_tensor(A.device))
+           alpha_dev, beta_dev, sym_upper, status_tensor(A.device))
     _count()
     return C
 
@@ -613,14 +615,14 @@ def newton_schulz(matrix: torch.Tensor, iters: int = 5, sumsq: Optional[torch.Te
         if wide:
             # G = Y Y^T  (A, B K-major over n)
             gemm(Ya, Ya, Gm, mode=BATCHED, groups=b, M=m, N=m, Kd=n, lda=n, ldb=n, ldc=m,
-                 a_gs=m * n, b_gs=m * n, c_gs=m * m, **ga)
+                 a_gs=m * n, b_gs=m * n, c_gs=m * m, sym_upper=True, **ga)
             # Y' = 1.5 Y - 0.5 G Y   (B = Y read MN-major)
             gemm(Gm, Ya, Yb, D=Ya, alpha=-0.5, beta=1.5, mode=BATCHED, groups=b, M=m, N=n, Kd=m,
                  b_major=MAJ_MN, lda=m, ldb=n, ldc=n, ldd=n, a_gs=m * m, b_gs=m * n, c_gs=m * n, **ya)
         else:
             # G = Y^T Y  (both MN-major over m)
             gemm(Ya, Ya, Gm, mode=BATCHED, groups=b, M=n, N=n, Kd=m, a_major=MAJ_MN, b_major=MAJ_MN,
-                 lda=n, ldb=n, ldc=n, a_gs=m * n, b_gs=m * n, c_gs=n * n, **ga)
+                 lda=n, ldb=n, ldc=n, a_gs=m * n, b_gs=m * n, c_gs=n * n, sym_upper=True, **ga)
             # Y' = 1.5 Y - 0.5 Y G   (G symmetric: read K-major)
             gemm(Ya, Gm, Yb, D=Ya, alpha=-0.5, beta=1.5, mode=BATCHED, groups=b, M=m, N=n, Kd=n,
                  lda=n, ldb=n, ldc=n, ldd=n, a_gs=m * n, b_gs=n * n, c_gs=m * n, **ya)

@@ -104,3 +104,21 @@ def test_grouped_m_swiglu():
         _close(U[t * 128:(t + 1) * 128], u)
         _close(H[t * 128:(t + 1) * 128], torch.nn.functional.silu(g) * u, tol=3e-2)
     assert H[5 * 128:].abs().max().item() == 0.0   # tiles past the live count are untouched
+
+
+@pytest.mark.parametrize("b,m,n", [(3, 512, 320), (1, 2048, 1024), (2, 192, 192)])
+def test_symmetric_gram_skips_and_mirrors(b, m, n):
+    """A A^T with ``sym_upper``: tiles below the diagonal are mirrored, the result equals the full product."""
+    from kolmogorov_moe_architecture_b200.ops import cuda_ops as c
+    torch.manual_seed(2)
+    a = (torch.randn(b, m, n, device="cuda") * 0.1).to(torch.bfloat16)
+    full = torch.empty(b, m, m, dtype=torch.bfloat16, device="cuda")
+    sym = torch.full((b, m, m), 7.0, dtype=torch.bfloat16, device="cuda")
+    kw = dict(mode=c.BATCHED, groups=b, M=m, N=m, Kd=n, lda=n, ldb=n, ldc=m, a_gs=m * n, b_gs=m * n, c_gs=m * m)
+    c.gemm(a, a, full, **kw)
+    c.gemm(a, a, sym, sym_upper=True, **kw)
+    c.check_status()
+    ref = a.float() @ a.float().transpose(1, 2)
+    assert (full.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
+    assert torch.equal(torch.triu(sym), torch.triu(full))
+    assert torch.equal(sym, sym.transpose(1, 2))
