@@ -179,6 +179,27 @@ def bench_attn(rows):
     c.check_status()
 
 
+def bench_attn_docs(rows):
+    """Packed documents (mean length 512) on the flash kernels against the same call without boundaries."""
+    from kolmogorov_moe_architecture_b200 import ops
+    from kolmogorov_moe_architecture_b200.ops import eager
+    B, S, H, Hkv, D = 4, 2048, 16, 4, 128
+    q = torch.randn(B, S, H, D, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    k = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    v = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    go = torch.randn(B, S, H, D, device="cuda").to(torch.bfloat16)
+    doc_ids = torch.arange(S, device="cuda").div(512, rounding_mode="floor").expand(B, S).contiguous()
+    ds = eager.doc_start_from_ids(doc_ids)
+
+    def run(doc):
+        o = ops.attention(q, k, v, doc_start=doc)
+        o.backward(go)
+        q.grad = k.grad = v.grad = None
+    fl = 3.5 * 4.0 * B * H * S * S * D / 2
+    report(rows, "kmoe.attention fwd+bwd B=4, 4 packed documents of 512", timeit(lambda: run(ds)), fl / 4)
+    report(rows, "kmoe.attention fwd+bwd B=4, one document", timeit(lambda: run(None)), fl)
+
+
 def bench_scan(rows):
     from kolmogorov_moe_architecture_b200 import ops
     for B in (4, 8):
@@ -244,7 +265,7 @@ def main():
     ap.add_argument("--out", default=None)
     a = ap.parse_args()
     rows = []
-    table = {"gemm": bench_gemm, "moe": bench_moe, "mxfp8": bench_mxfp8, "attn": bench_attn, "scan": bench_scan, "ce": bench_ce,
+    table = {"gemm": bench_gemm, "moe": bench_moe, "mxfp8": bench_mxfp8, "attn": bench_attn, "attn_docs": bench_attn_docs, "scan": bench_scan, "ce": bench_ce,
              "norm": bench_norm}
     for k in a.which.split(","):
         table[k](rows)
