@@ -310,3 +310,21 @@ def test_flash_attention_packed_documents(B, S, H, Hkv, D):
     outr.backward(g.float())
     assert _rel(out, outr) < 2e-2
     assert _rel(q.grad, qr.grad) < 3e-2 and _rel(k.grad, kr.grad) < 3e-2 and _rel(v.grad, vr.grad) < 3e-2
+
+
+def test_attention_and_routing_are_bitwise_deterministic():
+    """No atomics on these paths: the same call twice gives identical bits (forward and gradients)."""
+    ops, c, eager = _mods()
+    torch.manual_seed(9)
+    q, k, v = _bf(2, 300, 4, 128, grad=True), _bf(2, 300, 2, 128, grad=True), _bf(2, 300, 2, 128, grad=True)
+    g = _bf(2, 300, 4, 128)
+    runs = []
+    for _ in range(2):
+        q.grad = k.grad = v.grad = None
+        o = ops.attention(q, k, v)
+        o.backward(g)
+        runs.append([o.detach().clone(), q.grad.clone(), k.grad.clone(), v.grad.clone()])
+    assert all(torch.equal(a, b) for a, b in zip(*runs))
+    logits = torch.randn(4, 512, device="cuda")
+    a1, a2 = ops.mod_route(logits, 300), ops.mod_route(logits, 300)
+    assert torch.equal(a1[0], a2[0]) and torch.equal(a1[1], a2[1])
