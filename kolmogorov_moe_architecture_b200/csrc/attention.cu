@@ -89,7 +89,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int hkv = h / (a.H / a.Hkv);
   const int q0 = qb * ATT_BLK;
   const int kmax = min(q0 + ATT_BLK, a.S);
-  const int nblk = (kmax + FWD_BN - 1) / FWD_BN;
+  // packed documents: key blocks that end before the document of the block's first query are invisible to
+  // every row of the block (document starts do not decrease along the sequence) and are not visited at all
+  const int jlo = a.doc_start != nullptr ? a.doc_start[(size_t)b * a.S + q0] / FWD_BN : 0;
+  const int nblk = (kmax + FWD_BN - 1) / FWD_BN - jlo;       // j below counts visited blocks; key block = jlo + j
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
@@ -124,12 +127,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_expect_tx(&k_full[st], KTILE);
 #pragma unroll
         for (int p = 0; p < NP; ++p)
-          tma_load_4d(sK + st * KTILE + p * FWD_KPANEL, &tmK, &k_full[st], p * 64, hkv, j * FWD_BN, b);
+          tma_load_4d(sK + st * KTILE + p * FWD_KPANEL, &tmK, &k_full[st], p * 64, hkv, (jlo + j) * FWD_BN, b);
         if (!mbar_wait(&v_empty[st], par)) { atomicExch(a.status, 12); goto teardown; }
         mbar_expect_tx(&v_full[st], KTILE);
 #pragma unroll
         for (int p = 0; p < NP; ++p)
-          tma_load_4d(sV + st * KTILE + p * FWD_KPANEL, &tmV, &v_full[st], p * 64, hkv, j * FWD_BN, b);
+          tma_load_4d(sV + st * KTILE + p * FWD_KPANEL, &tmV, &v_full[st], p * 64, hkv, (jlo + j) * FWD_BN, b);
       }
     }
   } else if (warp == 5) {
@@ -180,7 +183,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!mbar_wait(&s_full[st], (j >> 1) & 1)) { if (lane == 0) atomicExch(a.status, 18); goto teardown; }
       tc_fence_after();
       const uint32_t ts = tmem + lane_base + COL_S0 + st * FWD_BN;
-      const int k0 = j * FWD_BN;
+      const int k0 = (jlo + j) * FWD_BN;
       const bool need_mask = (k0 + FWD_BN > q0) || (k0 + FWD_BN > a.S) || (k0 < qstart);
       uint32_t sv[FWD_BN];
       {
@@ -352,7 +355,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int hkv = h / (a.H / a.Hkv);
   const int q0 = qb * ATT_BLK;
   const int kmax = min(q0 + ATT_BLK, a.S);
-  const int nblk = (kmax + BWD_SUB - 1) / BWD_SUB;
+  const int jlo = a.doc_start != nullptr ? a.doc_start[(size_t)b * a.S + q0] / BWD_SUB : 0;   // see the forward kernel
+  const int nblk = (kmax + BWD_SUB - 1) / BWD_SUB - jlo;
 
   if (threadIdx.x == 0) {
     mbar_init(&qdo_full, 1);
@@ -384,12 +388,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_expect_tx(&k_full[st], KTILE);
 #pragma unroll
         for (int p = 0; p < NP; ++p)
-          tma_load_4d(sK + st * KTILE + p * SUBPANEL_BYTES, &tmK, &k_full[st], p * 64, hkv, j * BWD_SUB, b);
+          tma_load_4d(sK + st * KTILE + p * SUBPANEL_BYTES, &tmK, &k_full[st], p * 64, hkv, (jlo + j) * BWD_SUB, b);
         if (!mbar_wait(&v_empty[st], par)) { atomicExch(a.status, 22); goto teardown; }
         mbar_expect_tx(&v_full[st], KTILE);
 #pragma unroll
         for (int p = 0; p < NP; ++p)
-          tma_load_4d(sV + st * KTILE + p * SUBPANEL_BYTES, &tmV, &v_full[st], p * 64, hkv, j * BWD_SUB, b);
+          tma_load_4d(sV + st * KTILE + p * SUBPANEL_BYTES, &tmV, &v_full[st], p * 64, hkv, (jlo + j) * BWD_SUB, b);
       }
     }
   } else if (warp == 5) {
@@ -453,7 +457,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (!mbar_wait(&sdp_full[j & 1], (j >> 1) & 1)) { if (lane == 0) atomicExch(a.status, 26); goto teardown; }
       const uint32_t tbuf = tmem + lane_base + (j & 1) * COL_BUF;
       tc_fence_after();
-      const int k0 = j * BWD_SUB;
+      const int k0 = (jlo + j) * BWD_SUB;
       uint32_t ds_packed[BWD_SUB / 2];
 #pragma unroll
       for (int c = 0; c < BWD_SUB; c += 32) {
@@ -544,7 +548,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int k0 = kb * ATT_BLK;
   const int qblk0 = k0 / BWD_SUB;
   const int qblk1 = (a.S + BWD_SUB - 1) / BWD_SUB;
-  const int per_head = qblk1 - qblk0;
+  int per_head = qblk1 - qblk0;
+  if (a.doc_start != nullptr) {
+    // packed documents: once a query block starts in a document that begins after this key block's last key,
+    // it and all later query blocks cannot see the block (document starts do not decrease along the sequence)
+    const int klast = min(k0 + ATT_BLK, a.S) - 1;
+    for (int i = 1; i < per_head; ++i) {
+      if (a.doc_start[(size_t)b * a.S + (qblk0 + i) * BWD_SUB] > klast) { per_head = i; break; }
+    }
+  }
   const int niter = per_head * G;
 
   if (threadIdx.x == 0) {
