@@ -122,7 +122,8 @@ class ExpertParallelMoE(nn.Module):
             if ep_p2p.fused_available(xf, le.w1):
                 # permute + exchange fused over NVLink peer pointers; no host read, no NCCL
                 out = ep_p2p.expert_parallel_ffn_fused(xf, idx, w, le.w1, le.w2, le.w3, self.n_experts,
-                                                       self.process_group, keep=keep)
+                                                       self.process_group, keep=keep,
+                                                       slot_cap=cap if keep is not None else None)
                 return out.reshape(B, S, d)
             if self.transport == "p2p":
                 raise RuntimeError("expert-parallel transport 'p2p' needs CUDA bf16 tensors and peer access")

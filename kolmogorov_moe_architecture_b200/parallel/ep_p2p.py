@@ -100,11 +100,11 @@ class EPBuffers:
 _CACHE: Dict[Tuple, EPBuffers] = {}
 
 
-def get_buffers(T: int, k: int, d: int, E: int, dtype, device, group=None) -> EPBuffers:
-    key = (T, k, d, E, dtype, str(device), _group_name(group))
+def get_buffers(T: int, k: int, d: int, E: int, dtype, device, group=None, cap: Optional[int] = None) -> EPBuffers:
+    key = (T, k, d, E, dtype, str(device), _group_name(group), cap)
     buf = _CACHE.get(key)
     if buf is None:
-        buf = EPBuffers(T, k, d, E, dtype, device, group)
+        buf = EPBuffers(T, k, d, E, dtype, device, group, cap=cap)
         _CACHE[key] = buf
     return buf
 
@@ -210,9 +210,13 @@ def fused_available(x: torch.Tensor, w1: torch.Tensor) -> bool:
             and p2p_available(x.device))
 
 
-def expert_parallel_ffn_fused(x, idx, weights, w1, w2, w3, n_experts: int, group=None, keep=None):
+def expert_parallel_ffn_fused(x, idx, weights, w1, w2, w3, n_experts: int, group=None, keep=None,
+                              slot_cap: Optional[int] = None):
     """x (T, d) bf16; idx, weights (T, k) with global expert ids; w* are this rank's expert weights
-    (E / world, d, f) / (E / world, f, d).  Every rank of the group must call it with the same T."""
+    (E / world, d, f) / (E / world, f, d).  Every rank of the group must call it with the same T.
+    ``slot_cap``: upper bound on the assignments one rank sends to one expert (the capacity when ``keep``
+    enforces one); it sizes the receive slots and the expert-side buffers, which default to the worst case T."""
     T, d = x.shape
-    buf = get_buffers(T, idx.shape[1], d, n_experts, x.dtype, x.device, group)
+    cap = None if slot_cap is None else min(int(slot_cap), T)
+    buf = get_buffers(T, idx.shape[1], d, n_experts, x.dtype, x.device, group, cap)
     return _EPFusedFFN.apply(x, w1.contiguous(), w2.contiguous(), w3.contiguous(), idx, weights, keep, buf)

@@ -88,9 +88,11 @@ g2 = torch.Generator().manual_seed(10 + rank)
 x0 = torch.randn(T, d, generator=g2); logits = torch.randn(T, E, generator=g2)
 logits[:, 3] += 1.5                                   # skewed load
 wts0, idx = torch.softmax(logits, -1).topk(k, dim=-1)
-keep = torch.rand(T, k, generator=g2) > 0.1
 dout = torch.randn(T, d, generator=g2).cuda().bfloat16()
-idx = idx.cuda(); keep = keep.cuda()
+idx = idx.cuda()
+cap = T * k // E                                      # capacity factor 1.0: the skewed expert really drops
+keep = ops.capacity_keep_mask(idx, E, cap)
+assert int((~keep).sum()) > 0
 res = {}
 for mode in ("fused", "a2a", "oracle"):
     x = x0.cuda().bfloat16().requires_grad_(True)
@@ -110,7 +112,8 @@ for mode in ("fused", "a2a", "oracle"):
         if mode == "fused":
             for rep in range(2):                      # twice: buffers and epochs are reused across layers
                 for t in [x, wts] + ws_: t.grad = None
-                out = ep_p2p.expert_parallel_ffn_fused(x, idx, wts, ws_[0], ws_[1], ws_[2], E, None, keep)
+                out = ep_p2p.expert_parallel_ffn_fused(x, idx, wts, ws_[0], ws_[1], ws_[2], E, None, keep,
+                                                       slot_cap=cap if rep == 1 else None)   # capacity-sized slots
                 out.backward(dout)
         else:
             fn = lambda xx, ii, ww, kk: ops.grouped_swiglu(xx, ws_[0], ws_[1], ws_[2], ii, ww, kk)
