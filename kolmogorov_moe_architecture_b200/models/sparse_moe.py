@@ -121,10 +121,16 @@ class ExpertParallelMoE(nn.Module):
             from ..parallel import ep_p2p
             if ep_p2p.fused_available(xf, le.w1):
                 # permute + exchange fused over NVLink peer pointers; no host read, no NCCL
-                out = ep_p2p.expert_parallel_ffn_fused(xf, idx, w, le.w1, le.w2, le.w3, self.n_experts,
-                                                       self.process_group, keep=keep,
-                                                       slot_cap=cap if keep is not None else None)
-                return out.reshape(B, S, d)
+                try:
+                    out = ep_p2p.expert_parallel_ffn_fused(xf, idx, w, le.w1, le.w2, le.w3, self.n_experts,
+                                                           self.process_group, keep=keep,
+                                                           slot_cap=cap if keep is not None else None)
+                    return out.reshape(B, S, d)
+                except ep_p2p.EPUnavailable as e:
+                    if self.transport == "p2p":
+                        raise
+                    print(f"[kmoe] peer-pointer expert exchange unavailable ({e}); using all_to_all", flush=True)
+                    self.transport = "all_to_all"
             if self.transport == "p2p":
                 raise RuntimeError("expert-parallel transport 'p2p' needs CUDA bf16 tensors and peer access")
         from ..parallel.ep import expert_parallel_ffn

@@ -97,6 +97,10 @@ class EPBuffers:
         return sum(t.numel() * t.element_size() for t in (self.recv, self.ret, self.meta, self.flags))
 
 
+class EPUnavailable(RuntimeError):
+    """The symmetric buffers of the peer-pointer transport could not be set up on this machine."""
+
+
 _CACHE: Dict[Tuple, EPBuffers] = {}
 
 
@@ -104,7 +108,10 @@ def get_buffers(T: int, k: int, d: int, E: int, dtype, device, group=None, cap: 
     key = (T, k, d, E, dtype, str(device), _group_name(group), cap)
     buf = _CACHE.get(key)
     if buf is None:
-        buf = EPBuffers(T, k, d, E, dtype, device, group, cap=cap)
+        try:
+            buf = EPBuffers(T, k, d, E, dtype, device, group, cap=cap)
+        except Exception as e:
+            raise EPUnavailable(f"{type(e).__name__}: {e}") from e
         _CACHE[key] = buf
     return buf
 
