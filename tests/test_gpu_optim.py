@@ -81,3 +81,25 @@ def test_muon_fused_kernels_match_unfused(monkeypatch):
         assert (a - b).abs().max().item() < 4e-3 * max(b.abs().max().item(), 1e-3) + 2e-4
     for a, b in zip(bf_, bu):
         assert (a - b).norm().item() < 3e-2 * b.norm().item()
+
+
+def test_barrier_wait_runs_out_and_reports_status():
+    """Failure detection on the device without faulting it: a flag barrier whose peer never arrives gives up
+    after its wall-clock limit, records a status code that the host turns into an exception, and leaves the
+    context usable."""
+    import time
+    from kolmogorov_moe_architecture_b200.ops import cuda_ops
+    cuda_ops.check_status()
+    mine = torch.zeros(64, dtype=torch.int32, device="cuda")      # this rank's flag words
+    absent = torch.zeros(64, dtype=torch.int32, device="cuda")    # stands in for a peer that never writes
+    status = cuda_ops.status_tensor(torch.device("cuda"))
+    t0 = time.time()
+    torch.ops.kmoe.p2p_barrier([mine.data_ptr(), absent.data_ptr()], 0, 2, 1, 0.05, status)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 5.0
+    assert int(absent[0]) == 1                                    # the arrival was published to the "peer"
+    with pytest.raises(RuntimeError, match="wait-timeout status 101"):
+        cuda_ops.check_status()
+    cuda_ops.check_status()                                       # cleared by the report
+    x = torch.ones(1024, device="cuda")
+    assert float((x * 2).sum()) == 2048.0                         # the context still works
