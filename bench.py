@@ -150,8 +150,8 @@ def run_ours(args):
     from kolmogorov_moe_architecture_b200.parallel.zero import ParallelPlan, ShardedDataParallel
     if args.shard_params:
         from kolmogorov_moe_architecture_b200.parallel.fsdp import FullyShardedDataParallel
-        dp = FullyShardedDataParallel(model, lr=3e-4)
-        transport = "full-shard-nccl"
+        dp = FullyShardedDataParallel(model, lr=3e-4, transport=args.transport)
+        transport = f"full-shard-{dp.transport}" + ("-overlap" if dp.overlap else "")
     else:
         dp = ShardedDataParallel(model, optimizer_kind=args.optimizer, transport=args.transport)
         transport = dp.transport

@@ -32,7 +32,7 @@ def _worker(rank, world, tmp):
     rdp = ShardedDataParallel(ref, optimizer_kind="adamw", adamw_lr=1e-2, weight_decay=0.01)
     reng = TrainEngine(ref, rdp.optimizer, grad_clip=1.0, dp=rdp)
     n_full = sum(p.numel() for p in model.parameters())
-    plan = FullyShardedDataParallel(model, lr=1e-2, weight_decay=0.01)
+    plan = FullyShardedDataParallel(model, lr=1e-2, weight_decay=0.01, overlap=(tmp.endswith("prefetch")))
     assert all(p.numel() == 0 for p in model.parameters()), "parameters must be released outside their unit"
     assert plan.param_bytes_per_rank() < 0.6 * n_full * 4
     eng = TrainEngine(model, plan.optimizer, grad_clip=1.0, dp=plan)
@@ -42,6 +42,8 @@ def _worker(rank, world, tmp):
         a = eng.step(ids[rank * 2: rank * 2 + 2])
         b = reng.step(ids[rank * 2: rank * 2 + 2])
         assert abs(a.loss_value() - b.loss_value()) < 1e-3, (step, a.loss_value(), b.loss_value())
+    if plan.overlap:     # per step: every block but the first ahead of its forward, every block but the last ahead of its backward
+        assert plan.early_gathers == 3 * 2 * (len(plan.units) - 1) + 3, plan.early_gathers
     full = plan.full_state_dict()
     rs = dict(ref.named_parameters(remove_duplicate=False))
     worst = max((full[n] - rs[n].detach()).abs().max().item() for n in full)
@@ -62,6 +64,13 @@ def _worker(rank, world, tmp):
 
 def test_fsdp_two_ranks_follow_single_process(tmp_path):
     run_ranks(_worker, 2, str(tmp_path))
+
+
+def test_fsdp_with_early_gathers_follows_single_process(tmp_path):
+    """Same check with the next unit's gather issued ahead of its use (buffer-free bookkeeping)."""
+    d = tmp_path / "prefetch"
+    d.mkdir()
+    run_ranks(_worker, 2, str(d))
 
 
 def _ckpt_worker(rank, world, tmp):

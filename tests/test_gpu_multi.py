@@ -162,14 +162,17 @@ cfg = AdvancedMoEConfig(vocab_size=512, d_model=128, n_layers=4, n_heads=2, n_kv
                         n_pred_tokens=2, aux_loss_weights=(1.0, 0.5), mamba_moe_mode="moe_ffn", dropout=0.0,
                         attention_dropout=0.0, residual_dropout=0.0)
 out, losses = {}, {}
-for kind in ("replicated", "sharded"):
+variants = {"replicated": None, "nccl": dict(transport="nccl", overlap=False),
+            "nccl-overlap": dict(transport="nccl", overlap=True), "p2p-overlap": dict(transport="p2p", overlap=True)}
+for kind, kw in variants.items():
     torch.manual_seed(0)
     model = MoETransformer(cfg, verbose=False).cuda().to(torch.bfloat16)
     n_full = sum(p.numel() for p in model.parameters())
-    if kind == "replicated":
+    if kw is None:
         dp = ShardedDataParallel(model, optimizer_kind="adamw", adamw_lr=2e-3, transport="nccl")
     else:
-        dp = FullyShardedDataParallel(model, lr=2e-3)
+        dp = FullyShardedDataParallel(model, lr=2e-3, **kw)
+        assert dp.transport == kw["transport"] and dp.overlap == kw["overlap"]
         assert all(p.numel() == 0 for p in model.parameters())
         assert dp.param_bytes_per_rank() <= 0.55 * n_full * 2
     eng = TrainEngine(model, dp.optimizer, grad_clip=1.0, dp=dp)
@@ -179,14 +182,24 @@ for kind in ("replicated", "sharded"):
         ls.append(eng.step(torch.randint(0, 512, (2, 64), generator=g).cuda()).loss_value())
     cuda_ops.check_status()
     losses[kind] = ls
-    if kind == "replicated":
+    if kw is None:
         out[kind] = {n: p.detach().float().clone() for n, p in model.named_parameters()}
     else:
         out[kind] = {n: t.float().cuda() for n, t in dp.full_state_dict().items()}
-err = max((out["replicated"][n] - out["sharded"][n]).abs().max().item() for n in out["replicated"])
+        assert dp.early_gathers == (3 * (2 * (len(dp.units) - 1) + 1) if kw["overlap"] else 0)
 ref = max(t.abs().max().item() for t in out["replicated"].values())
-assert max(abs(a - b) for a, b in zip(losses["replicated"], losses["sharded"])) < 5e-2, losses
-assert err < 3e-2 * ref, (err, ref)
+err = 0.0
+for kind in variants:
+    if kind == "replicated":
+        continue
+    e = max((out["replicated"][n] - out[kind][n]).abs().max().item() for n in out["replicated"])
+    assert max(abs(a - b) for a, b in zip(losses["replicated"], losses[kind])) < 5e-2, (kind, losses)
+    assert e < 3e-2 * ref, (kind, e, ref)
+    err = max(err, e)
+# the variants of the sharded plan do the same arithmetic: a race on a buffer would show up here
+for kind in ("nccl-overlap", "p2p-overlap"):
+    d = max((out["nccl"][n] - out[kind][n]).abs().max().item() for n in out["nccl"])
+    assert d < 5e-3 * ref, (kind, d, ref)
 if rank == 0: print("FSDP_OK", err, losses)
 dist.destroy_process_group()
 '''
@@ -194,7 +207,8 @@ dist.destroy_process_group()
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_param_sharded_plan_matches_replicated_2gpus(tmp_path):
-    """ZeRO-3 style plan (parameters gathered per block into two rotating buffers) against the replicated plan."""
+    """ZeRO-3 style plan (parameters gathered per block into two rotating buffers) against the replicated plan:
+    library collectives, the same with gathers and reduce-scatters on side streams, and the peer-memory transport."""
     f = tmp_path / "fsdp_worker.py"
     f.write_text(FSDP_WORKER)
     env = dict(os.environ, KMOE_ROOT=ROOT, NCCL_NVLS_ENABLE="0", KMOE_STRICT="1")
