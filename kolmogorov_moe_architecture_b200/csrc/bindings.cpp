@@ -347,8 +347,13 @@ void p2p_adamw_allgather(std::vector<int64_t> param_ptrs, const Tensor& grad, Te
 }
 
 void p2p_allgather(std::vector<int64_t> buf_ptrs, int64_t rank, int64_t world, int64_t off, int64_t n,
-                   int64_t mc_ptr) {
-  check(kmoe_p2p_allgather((const long long*)buf_ptrs.data(), (int)rank, (int)world, off, n, mc_ptr, cur_stream()),
+                   int64_t mc_ptr, const OptT& src, int64_t max_blocks) {
+  if (src.has_value()) {
+    need_bf16(*src, "src");
+    TORCH_CHECK(src->is_contiguous() && src->numel() >= n, "src too small or not contiguous");
+  }
+  check(kmoe_p2p_allgather((const long long*)buf_ptrs.data(), (int)rank, (int)world, off, n, mc_ptr,
+                           ptr_or_null(src), (int)max_blocks, cur_stream()),
         "p2p_allgather");
 }
 

@@ -16,6 +16,7 @@
 // one multimem.st instead of `world` stores, which cuts the bytes through each GPU's port by ~world.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <cstdint>
 
 #include "kmoe_api.h"
 #include "ptx.cuh"
@@ -200,20 +201,36 @@ __global__ void p2p_adamw_allgather_kernel(PeerPtrs params, const __nv_bfloat16*
   }
 }
 
-// Copy [off, off+n) of this rank's buffer into every other rank's buffer.
-__global__ void p2p_allgather_kernel(PeerPtrs bufs, int rank, int world, long long off, long long n, void* mc) {
+// Copy n elements into [off, off+n) of every rank's buffer.  src == null: the source is this rank's own
+// buffer at the same offset (which is then left alone); otherwise `src` (e.g. a parameter shard) is also
+// stored into this rank's buffer.  AG_UNROLL loads are in flight per thread, so a small grid that runs
+// beside compute kernels still fills the link.
+constexpr int AG_UNROLL = 4;
+__global__ void p2p_allgather_kernel(PeerPtrs bufs, int rank, int world, long long off, long long n, void* mc,
+                                     const __nv_bfloat16* __restrict__ src) {
   const long long nvec = n / 8;
-  const uint4* own = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(bufs.p[rank]) + off);
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
-       i += (long long)gridDim.x * blockDim.x) {
-    const uint4 x = own[i];
-    if (mc != nullptr) {                      // one store reaches every rank (this one included: same value)
-      multimem_st_16B(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(mc) + off) + i, x);
-      continue;
-    }
-    for (int r = 1; r < world; ++r) {
-      const int dst = (rank + r) % world;
-      *(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(bufs.p[dst]) + off) + i) = x;
+  const uint4* from = src != nullptr
+                          ? reinterpret_cast<const uint4*>(src)
+                          : reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(bufs.p[rank]) + off);
+  const int first = src != nullptr ? 0 : 1;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * AG_UNROLL) {
+    uint4 x[AG_UNROLL];
+#pragma unroll
+    for (int u = 0; u < AG_UNROLL; ++u)
+      if (i0 + u * stride < nvec) x[u] = from[i0 + u * stride];
+#pragma unroll
+    for (int u = 0; u < AG_UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) continue;
+      if (mc != nullptr) {                    // one store reaches every rank (this one included)
+        multimem_st_16B(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(mc) + off) + i, x[u]);
+        continue;
+      }
+      for (int r = first; r < world; ++r) {
+        const int dst = (rank + r) % world;
+        *(reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(bufs.p[dst]) + off) + i) = x[u];
+      }
     }
   }
 }
@@ -258,10 +275,12 @@ extern "C" int kmoe_p2p_adamw_allgather(const long long* param_ptrs, const void*
 }
 
 extern "C" int kmoe_p2p_allgather(const long long* buf_ptrs, int rank, int world, long long off, long long n,
-                                  long long mc_ptr, cudaStream_t st) {
-  if (world > MAX_RANKS || n % 8 || off % 8) return -1;
-  p2p_allgather_kernel<<<148 * 8, 256, 0, st>>>(make_ptrs(buf_ptrs, world), rank, world, off, n,
-                                                reinterpret_cast<void*>(mc_ptr));
+                                  long long mc_ptr, const void* src, int max_blocks, cudaStream_t st) {
+  if (world > MAX_RANKS || n % 8 || off % 8 || (reinterpret_cast<uintptr_t>(src) & 15)) return -1;
+  if (n == 0) return 0;
+  const int blocks = max_blocks > 0 ? max_blocks : 148 * 8;
+  p2p_allgather_kernel<<<blocks, 256, 0, st>>>(make_ptrs(buf_ptrs, world), rank, world, off, n,
+                                               reinterpret_cast<void*>(mc_ptr), (const __nv_bfloat16*)src);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

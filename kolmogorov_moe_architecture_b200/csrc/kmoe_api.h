@@ -160,8 +160,9 @@ int kmoe_p2p_reduce_scatter(const long long* grad_ptrs, int rank, int world, lon
 int kmoe_p2p_adamw_allgather(const long long* param_ptrs, const void* grad, float* m, float* v, int rank, int world,
                              long long off, long long n, float lr, float beta1, float beta2, float eps, float wd,
                              int step, const float* clip_coef, long long mc_ptr, cudaStream_t st);
+// src (optional): read the n elements from there instead of this rank's own buffer, and store them into it too.
 int kmoe_p2p_allgather(const long long* buf_ptrs, int rank, int world, long long off, long long n, long long mc_ptr,
-                       cudaStream_t st);
+                       const void* src, int max_blocks /*0 = whole device*/, cudaStream_t st);
 
 // Expert-parallel token exchange.  E experts are split evenly over `world` ranks (expert e lives on rank
 // e / (E / world)).  The receive buffer of a rank holds (E / world) * world slots of `cap` rows; slot

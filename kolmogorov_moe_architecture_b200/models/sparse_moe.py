@@ -117,14 +117,15 @@ class ExpertParallelMoE(nn.Module):
         if self.world_size == 1:
             return self.local_experts(xf, idx, w, keep).reshape(B, S, d)
         le = self.local_experts
-        if self.transport != "all_to_all" and le.moe_dtype == "bf16":
+        if self.transport != "all_to_all" and le.moe_dtype in ("bf16", "mxfp8"):
             from ..parallel import ep_p2p
-            if ep_p2p.fused_available(xf, le.w1):
+            if ep_p2p.fused_available(xf, le.w1, le.moe_dtype):
                 # permute + exchange fused over NVLink peer pointers; no host read, no NCCL
                 try:
                     out = ep_p2p.expert_parallel_ffn_fused(xf, idx, w, le.w1, le.w2, le.w3, self.n_experts,
                                                            self.process_group, keep=keep,
-                                                           slot_cap=cap if keep is not None else None)
+                                                           slot_cap=cap if keep is not None else None,
+                                                           moe_dtype=le.moe_dtype)
                     return out.reshape(B, S, d)
                 except ep_p2p.EPUnavailable as e:
                     if self.transport == "p2p":

@@ -210,20 +210,127 @@ class _EPFusedFFN(torch.autograd.Function):
         return dx, dw1, dw2, dw3, None, dwts, None, None
 
 
-def fused_available(x: torch.Tensor, w1: torch.Tensor) -> bool:
+class _EPFusedFFNMX(torch.autograd.Function):
+    """Same exchange, expert GEMMs (forward, dgrad, wgrad) on the block-scaled fp8 path (e4m3 values, one
+    e8m0 scale per 32 elements along the reduction, fp32 accumulation, bf16 results).  Rows cross NVLink in
+    bf16 and are quantised on the expert rank, where each operand is quantised once per orientation; the
+    second GEMM's rows go back to their source ranks with the return kernel instead of a GEMM epilogue."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w2, w3, idx, weights, keep, buf: EPBuffers):
+        from ..ops import cuda_ops as C
+        from ..ops import mxfp8 as MX
+        K = torch.ops.kmoe
+        T, d = x.shape
+        nl, _, f = w1.shape
+        k = idx.shape[1]
+        E, ws = buf.E, buf.world
+        pos, row_src, counts, offsets, _tg, _meta = K.moe_plan(
+            idx.reshape(-1).contiguous(), keep.reshape(-1) if keep is not None else None, E, 0)
+        assert row_src.numel() <= buf.max_rows_src
+        K.ep_dispatch(x.contiguous(), row_src, None, offsets, counts, buf.recv_ptrs, buf.meta_ptrs, buf.rank, ws, E,
+                      buf.cap, k)
+        buf.barrier()
+        R = buf.max_rows_exp
+        meta_in = buf.meta.clone()
+        slot_dst, offs_l, tile_group, meta_l = K.ep_recv_plan(meta_in, nl, ws, R)
+        nmt, live = meta_l[0:1], meta_l[1:2]
+        Xp = torch.empty(R, d, dtype=x.dtype, device=x.device)
+        K.ep_move(buf.recv, Xp, meta_in, slot_dst, offs_l, buf.ret_ptrs, buf.rank, nl, ws, buf.cap, 0, None)
+        grp = dict(mode=C.GROUPED_M, groups=nl, b_grouped=True, tile_group=tile_group, num_m_tiles=nmt)
+        Xq, sX = MX.quant_rows(Xp, live_rows=live)
+        W1q, s1 = MX._weight_quant(w1, "cols")
+        W2q, s2 = MX._weight_quant(w2, "cols")
+        G = torch.empty(R, f, dtype=x.dtype, device=x.device)
+        U = torch.empty_like(G)
+        MX.gemm_mx(Xq, sX, W1q, s1, G, M=R, N=f, K=d, **grp)
+        MX.gemm_mx(Xq, sX, W2q, s2, U, M=R, N=f, K=d, **grp)
+        Hq, sH = MX.quant_rows(G, U, live_rows=live)          # SwiGLU fused into the quantiser
+        W3q, s3 = MX._weight_quant(w3, "cols")
+        Y = torch.empty(R, d, dtype=x.dtype, device=x.device)
+        MX.gemm_mx(Hq, sH, W3q, s3, Y, M=R, N=d, K=f, **grp)
+        K.ep_move(buf.recv, Y, meta_in, slot_dst, offs_l, buf.ret_ptrs, buf.rank, nl, ws, buf.cap, 1, None)
+        buf.barrier()
+        wf = weights.reshape(-1).float().contiguous()
+        out = K.moe_combine(buf.ret, pos, wf, T, k)
+        Yret = buf.ret[: row_src.numel()].clone() if ctx.needs_input_grad[5] else None
+        C._count(6)
+        ctx.save_for_backward(Xp, G, U, w1, w2, w3, wf, pos, row_src, counts, offsets, meta_in, slot_dst, offs_l,
+                              tile_group, meta_l, Yret if Yret is not None else torch.empty(0, device=x.device))
+        ctx.buf = buf
+        ctx.dims = (T, d, nl, f, k, R)
+        ctx.wdtype = weights.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from ..ops import cuda_ops as C
+        from ..ops import mxfp8 as MX
+        K = torch.ops.kmoe
+        (Xp, G, U, w1, w2, w3, wf, pos, row_src, counts, offsets, meta_in, slot_dst, offs_l, tile_group, meta_l,
+         Yret) = ctx.saved_tensors
+        buf = ctx.buf
+        T, d, nl, f, k, R = ctx.dims
+        E, ws = buf.E, buf.world
+        dout = dout.contiguous()
+        nmt, live = meta_l[0:1], meta_l[1:2]
+        grp = dict(mode=C.GROUPED_M, groups=nl, b_grouped=True, tile_group=tile_group, num_m_tiles=nmt)
+        K.ep_dispatch(dout, row_src, wf, offsets, counts, buf.recv_ptrs, buf.meta_ptrs, buf.rank, ws, E, buf.cap, k)
+        buf.barrier()
+        dYp = torch.empty(R, d, dtype=dout.dtype, device=dout.device)
+        K.ep_move(buf.recv, dYp, meta_in, slot_dst, offs_l, buf.ret_ptrs, buf.rank, nl, ws, buf.cap, 0, None)
+        dYq, sdY = MX.quant_rows(dYp, live_rows=live)
+        W3r, s3r = MX._weight_quant(w3, "rows")
+        dH = torch.empty(R, f, dtype=dout.dtype, device=dout.device)
+        MX.gemm_mx(dYq, sdY, W3r, s3r, dH, M=R, N=f, K=d, **grp)
+        dG, dU = K.swiglu_bwd(G, U, dH, live)
+        dGq, sdG = MX.quant_rows(dG, live_rows=live)
+        dUq, sdU = MX.quant_rows(dU, live_rows=live)
+        W1r, s1r = MX._weight_quant(w1, "rows")
+        W2r, s2r = MX._weight_quant(w2, "rows")
+        dXp = torch.empty(R, d, dtype=dout.dtype, device=dout.device)
+        MX.gemm_mx(dGq, sdG, W1r, s1r, dXp, M=R, N=d, K=f, **grp)
+        MX.gemm_mx(dUq, sdU, W2r, s2r, dXp, D=dXp, beta=1.0, M=R, N=d, K=f, **grp)
+        K.ep_move(buf.recv, dXp, meta_in, slot_dst, offs_l, buf.ret_ptrs, buf.rank, nl, ws, buf.cap, 1, None)
+        buf.barrier()
+        dx = K.moe_combine(buf.ret, pos, None, T, k)
+        dwts = None
+        if Yret.numel():
+            dwts = K.moe_combine_dw(Yret, dout, pos, k).view(T, k).to(ctx.wdtype)
+        kb = offs_l[:nl].contiguous()
+        kl = (offs_l[1:] - offs_l[:nl]).contiguous()
+        H = K.swiglu_fwd(G, U, live)
+        XT, sXT = MX.quant_cols(Xp, live_rows=live)
+        dGT, sdGT = MX.quant_cols(dG, live_rows=live)
+        dUT, sdUT = MX.quant_cols(dU, live_rows=live)
+        HT, sHT = MX.quant_cols(H, live_rows=live)
+        dYT, sdYT = MX.quant_cols(dYp, live_rows=live)
+        dw1, dw2, dw3 = torch.empty_like(w1), torch.empty_like(w2), torch.empty_like(w3)
+        bat = dict(mode=C.BATCHED, groups=nl, k_begin=kb, k_len=kl, K=R)
+        MX.gemm_mx(XT, sXT, dGT, sdGT, dw1, M=d, N=f, c_gs=d * f, **bat)
+        MX.gemm_mx(XT, sXT, dUT, sdUT, dw2, M=d, N=f, c_gs=d * f, **bat)
+        MX.gemm_mx(HT, sHT, dYT, sdYT, dw3, M=f, N=d, c_gs=f * d, **bat)
+        C._count(8)
+        return dx, dw1, dw2, dw3, None, dwts, None, None
+
+
+def fused_available(x: torch.Tensor, w1: torch.Tensor, moe_dtype: str = "bf16") -> bool:
     from .p2p import p2p_available
     d, f = w1.shape[1], w1.shape[2]
-    return (x.is_cuda and x.dtype == torch.bfloat16 and w1.dtype == torch.bfloat16 and d % 64 == 0 and f % 64 == 0
-            and p2p_available(x.device))
+    gran = 128 if moe_dtype == "mxfp8" else 64
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w1.dtype == torch.bfloat16 and d % gran == 0
+            and f % gran == 0 and p2p_available(x.device))
 
 
 def expert_parallel_ffn_fused(x, idx, weights, w1, w2, w3, n_experts: int, group=None, keep=None,
-                              slot_cap: Optional[int] = None):
+                              slot_cap: Optional[int] = None, moe_dtype: str = "bf16"):
     """x (T, d) bf16; idx, weights (T, k) with global expert ids; w* are this rank's expert weights
     (E / world, d, f) / (E / world, f, d).  Every rank of the group must call it with the same T.
     ``slot_cap``: upper bound on the assignments one rank sends to one expert (the capacity when ``keep``
-    enforces one); it sizes the receive slots and the expert-side buffers, which default to the worst case T."""
+    enforces one); it sizes the receive slots and the expert-side buffers, which default to the worst case T.
+    ``moe_dtype="mxfp8"`` runs the expert GEMMs block-scaled in fp8 (d and f multiples of 128)."""
     T, d = x.shape
     cap = None if slot_cap is None else min(int(slot_cap), T)
     buf = get_buffers(T, idx.shape[1], d, n_experts, x.dtype, x.device, group, cap)
-    return _EPFusedFFN.apply(x, w1.contiguous(), w2.contiguous(), w3.contiguous(), idx, weights, keep, buf)
+    fn = _EPFusedFFNMX if moe_dtype == "mxfp8" else _EPFusedFFN
+    return fn.apply(x, w1.contiguous(), w2.contiguous(), w3.contiguous(), idx, weights, keep, buf)

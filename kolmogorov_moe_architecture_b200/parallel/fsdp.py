@@ -158,8 +158,12 @@ class FullyShardedDataParallel:
         else:
             self._pool = [torch.zeros(big, dtype=self.dtype, device=self.device) for _ in range(2 if big else 0)]
             self._grad_bufs = [torch.zeros(big, dtype=self.dtype, device=self.device) for _ in range(2 if big else 0)]
+        # grids of the two peer kernels while they run beside compute kernels (0 = whole device)
+        self._ag_blocks = int(os.environ.get("KMOE_FSDP_AG_BLOCKS", "32")) if self.overlap else 0
+        self._rs_blocks = int(os.environ.get("KMOE_FSDP_RS_BLOCKS", "148"))
+        self._p2p_rs = os.environ.get("KMOE_FSDP_P2P_RS", "1") != "0"
         self._red_bufs = ([torch.empty(big // self.world, dtype=self.dtype, device=self.device) for _ in range(2)]
-                          if self._sym is None and self.backend == "nccl" and big else None)
+                          if (self._sym is None or not self._p2p_rs) and self.backend == "nccl" and big else None)
         self._rs_done = [None, None]
         self._rs_slot = 0
         for i, u in enumerate(self.units):
@@ -238,12 +242,12 @@ class FullyShardedDataParallel:
             if self.world == 1:
                 out.copy_(shard)
             elif self._sym is not None and u is not self.root:
-                # own slice locally, then pushed into every peer's buffer; the first barrier says that every
-                # rank is done with what the buffer held before, the second that every push has landed
-                out[self.rank * chunk: (self.rank + 1) * chunk].copy_(shard)
+                # one kernel stores this rank's shard into every rank's buffer (its own included); the first
+                # barrier says that every rank is done with what the buffer held before, the second that
+                # every store has landed
                 off = u.slot * self._big + self.rank * chunk
                 self._sym.barrier(2)
-                self._sym.all_gather_range(off, chunk)
+                self._sym.all_gather_range(off, chunk, src=shard, max_blocks=self._ag_blocks)
                 self._sym.barrier(2)
             else:
                 dist.all_gather_into_tensor(out, shard.contiguous(), group=self.group)
@@ -352,10 +356,10 @@ class FullyShardedDataParallel:
         with self._side(side):
             if self.world == 1:
                 red = g
-            elif self._sym is not None and slot >= 0:
+            elif self._sym is not None and slot >= 0 and self._p2p_rs:
                 off = slot * self._big + self.rank * chunk
                 self._sym.barrier(3)                       # every rank's gradients are in place
-                self._sym.reduce_scatter_mean(off, chunk, None, 48 if side is not None else 0)   # small grid beside the backward pass
+                self._sym.reduce_scatter_mean(off, chunk, None, self._rs_blocks if side is not None else 0)
                 self._sym.barrier(3)                       # every rank has read what it needs from this buffer
                 red = g[self.rank * chunk: (self.rank + 1) * chunk]
             elif self.backend == "nccl":

@@ -114,7 +114,9 @@ class SymmetricBuffers:
                                           max_blocks)
         cuda_ops._count()
 
-    def all_gather_range(self, off: int, n: int) -> None:
+    def all_gather_range(self, off: int, n: int, src: Optional[torch.Tensor] = None, max_blocks: int = 0) -> None:
+        """Publish ``n`` elements at ``off`` of the parameter buffer to every rank: this rank's own copy of
+        the range, or ``src`` (a bf16 vector outside the buffer, also stored into this rank's copy)."""
         from ..ops import cuda_ops
-        torch.ops.kmoe.p2p_allgather(self.param_ptrs, self.rank, self.world, off, n, self.param_mc)
+        torch.ops.kmoe.p2p_allgather(self.param_ptrs, self.rank, self.world, off, n, self.param_mc, src, max_blocks)
         cuda_ops._count()
