@@ -21,6 +21,10 @@ expert rank, and ``dXp`` rows travelling back; weight gradients never leave the 
 Counts, offsets and tile tables stay on the device - there is no host read and no NCCL call
 in either direction (the all-to-all transport in :mod:`.ep` needs one host read per layer).
 
+With ``moe_dtype="mxfp8"`` the expert rank quantises the compacted rows (e4m3, one e8m0 scale per 32
+elements along each GEMM's reduction) and runs the block-scaled GEMMs of ``csrc/gemm_mxfp8.cu``; rows
+travel in bf16 both ways and the second GEMM's rows go back with the return kernel.
+
 Buffers are symmetric-memory allocations sized for the worst case (every token of every rank
 routed to one rank) and shared by all layers of a model: a layer's receive buffer is free
 again once the rank has compacted it, which the second barrier of the layer orders before any
