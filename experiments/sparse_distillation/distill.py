@@ -396,28 +396,63 @@ class SparseDistillationTrainer:
         out = ffn(x.to(dev))
         return (out[0] if isinstance(out, tuple) else out).to(self.device)
 
-    def _cluster_ffn_outputs(self, i: int, n_clusters: int):
-        xs, ys = [], []
-        n = 0
-        while n < self.cfg.cluster_samples:
-            x = self._random_inputs()
-            xs.append(x.reshape(-1, self.d_model))
-            ys.append(self._teacher(i, x).reshape(-1, self.d_model))
+    @torch.no_grad()
+    def _collect_ffn_activations_from_data(self, batches, i: int, max_samples: int = 10000):
+        """(inputs, outputs) of dense FFN ``i`` on real batches, flattened to (N, d_model) on the host
+        (reference: Experiments/sparse_distillation/distill.py:1261-1319).  A batch is a tensor of input
+        ids, a tuple whose first entry is one, or a dict with ``input_ids`` (and optionally
+        ``attention_mask``)."""
+        xs, ys, n = [], [], 0
+        dev = next(self.model.parameters()).device
+        self.model.eval()
+        for b in batches:
+            if n >= max_samples:
+                break
+            kw = {}
+            if isinstance(b, dict):
+                ids = b.get("input_ids", b.get("tokens"))
+                if b.get("attention_mask") is not None:
+                    kw["attention_mask"] = b["attention_mask"].to(dev)
+            else:
+                ids = b[0] if isinstance(b, (list, tuple)) else b
+            with FFNActivationCache(self.model, layers=[i]) as cache:
+                self.model(ids.to(dev), **kw)
+            xs.append(cache.inputs[i].reshape(-1, self.d_model).float().cpu())
+            ys.append(cache.outputs[i].reshape(-1, self.d_model).float().cpu())
             n += xs[-1].shape[0]
-        X, Y = torch.cat(xs)[: self.cfg.cluster_samples], torch.cat(ys)[: self.cfg.cluster_samples]
+        if not xs:
+            raise ValueError(f"no activations collected for layer {i}")
+        return torch.cat(xs)[:max_samples], torch.cat(ys)[:max_samples]
+
+    def _cluster_ffn_outputs(self, i: int, n_clusters: int, batches=None):
+        """Spherical k-means of the dense FFN's outputs: on activations from ``batches`` when given,
+        otherwise on its responses to random unit-norm inputs scaled by sqrt(d)."""
+        if batches is not None:
+            X, Y = self._collect_ffn_activations_from_data(batches, i, self.cfg.cluster_samples)
+            X, Y = X.to(self.dtype), Y.to(self.dtype)
+        else:
+            xs, ys = [], []
+            n = 0
+            while n < self.cfg.cluster_samples:
+                x = self._random_inputs()
+                xs.append(x.reshape(-1, self.d_model))
+                ys.append(self._teacher(i, x).reshape(-1, self.d_model))
+                n += xs[-1].shape[0]
+            X, Y = torch.cat(xs)[: self.cfg.cluster_samples], torch.cat(ys)[: self.cfg.cluster_samples]
         assign, cent = kmeans(Y, n_clusters, spherical=True)
         return X, Y, assign, cent
 
-    def analyze_cluster_quality(self, i: int, ks=(4, 8, 16)) -> Dict[int, Dict[str, float]]:
+    def analyze_cluster_quality(self, i: int, ks=(4, 8, 16), batches=None) -> Dict[int, Dict[str, float]]:
         out = {}
+        batches = list(batches) if batches is not None else None
         for k in ks:
-            _, Y, assign, cent = self._cluster_ffn_outputs(i, k)
+            _, Y, assign, cent = self._cluster_ffn_outputs(i, k, batches)
             out[k] = cluster_quality(F.normalize(Y.float(), dim=-1), assign, cent)
         return out
 
-    def _train_router_supervised(self, i: int, steps: Optional[int] = None) -> float:
+    def _train_router_supervised(self, i: int, steps: Optional[int] = None, batches=None) -> float:
         layer = self.moe_layers[str(i)].to(self.device).train()
-        X, _, assign, _ = self._cluster_ffn_outputs(i, layer.n_experts)
+        X, _, assign, _ = self._cluster_ffn_outputs(i, layer.n_experts, batches)
         params = list(layer.router.parameters()) + ([layer.expert_bias] if layer.expert_bias is not None else [])
         opt = torch.optim.AdamW(params, lr=self.cfg.learning_rate * 10)
         last = 0.0

@@ -1,4 +1,4 @@
 from .dolma_dataset import (DolmaMemoryMappedDataset, DolmaStreamingDataset, PackedDocumentDataset,
-                            PinnedPrefetcher, SyntheticTokenDataset, document_attention_mask, PackedDocs, get_dataloaders,
+                            PinnedPrefetcher, ThreadedPrefetcher, SyntheticTokenDataset, document_attention_mask, PackedDocs, get_dataloaders,
                             write_token_file)
 from .tokenizer import ByteTokenizer, TokenizerWrapper

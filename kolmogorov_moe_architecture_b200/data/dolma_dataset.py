@@ -262,3 +262,24 @@ class PinnedPrefetcher:
                 self.q.get_nowait()
         except queue.Empty:
             pass
+
+
+class ThreadedPrefetcher(PinnedPrefetcher):
+    """``PinnedPrefetcher`` with the constructor and behaviour of the reference's custom-training
+    prefetcher (reference: train_custom.py:519-594): ``buffer_size`` batches are produced ahead by a
+    background thread and every batch handed out is already on ``device`` (the copy from pinned
+    memory is asynchronous, so it overlaps the step that is still running)."""
+
+    def __init__(self, dataloader: Iterable, device, buffer_size: int = 3):
+        self.device = torch.device(device)
+        super().__init__(dataloader, depth=buffer_size, pin=self.device.type == "cuda")
+
+    def _to_device(self, batch):
+        if isinstance(batch, dict):
+            return {k: self._to_device(v) for k, v in batch.items()}
+        if torch.is_tensor(batch):
+            return batch.to(self.device, non_blocking=True)
+        return batch
+
+    def __next__(self):
+        return self._to_device(super().__next__())

@@ -195,3 +195,11 @@ def test_yaml_loaders(tmp_path):
         load_yaml(str(tmp_path / "bad.yaml"))
     with pytest.raises(TypeError):
         model_config_strict({"model": {"no_such_field": 1}})
+
+
+def test_threaded_prefetcher_yields_batches_on_the_device_in_order():
+    from kolmogorov_moe_architecture_b200.data import ThreadedPrefetcher
+    batches = [{"input_ids": torch.full((2, 4), i), "n": i} for i in range(7)]
+    got = list(ThreadedPrefetcher(batches, "cpu", buffer_size=2))
+    assert [b["n"] for b in got] == list(range(7))
+    assert all(torch.equal(b["input_ids"], torch.full((2, 4), b["n"])) for b in got)

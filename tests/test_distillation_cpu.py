@@ -87,3 +87,21 @@ def test_dynamic_expert_resize():
     layer = reallocate_expert_layer(DynamicExpertLayer(8, [32, 32]), {0: 48, 1: 16})
     out = layer(torch.randn(5, 8), torch.tensor([[0], [1], [0], [1], [0]]), torch.ones(5, 1))
     assert out.shape == (5, 8) and layer.d_ffs == [48, 16]
+
+
+def test_router_supervision_from_real_activations():
+    """Clusters of the dense FFN's outputs on real batches supervise the router: its loss against the
+    cluster labels falls, and the collected activations are the hooked layer's own input/output."""
+    torch.manual_seed(0)
+    m = ToyLM().eval()
+    tr = SparseDistillationTrainer(m, _cfg(cluster_samples=256), device="cpu")
+    batches = [{"input_ids": torch.randint(0, 256, (4, 16))} for _ in range(6)]
+    X, Y = tr._collect_ffn_activations_from_data(batches, 1, max_samples=200)
+    assert X.shape == Y.shape == (200, 64)
+    with torch.no_grad():
+        assert torch.allclose(m.blocks[1].mlp(X[:8]), Y[:8], atol=1e-5)
+    first = tr._train_router_supervised(1, steps=1, batches=batches)
+    last = tr._train_router_supervised(1, steps=60, batches=batches)
+    assert last < first
+    q = tr.analyze_cluster_quality(0, ks=(2, 4), batches=batches)
+    assert set(q) == {2, 4}
