@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import math
 import os
-from typing import Dict, Iterable, Optional
+from typing import Dict, Iterable, List, Optional
 
 import torch
 import torch.nn.functional as F
@@ -14,34 +14,176 @@ import torch.nn.functional as F
 from .convert import SparseModelWrapper
 
 
-def accumulate_routing_stats(wrapper: SparseModelWrapper, batches: Iterable[torch.Tensor]) -> Dict[int, Dict[str, float]]:
-    acc: Dict[int, torch.Tensor] = {}
+def _layer_stats(counts: torch.Tensor) -> Dict[str, object]:
+    """Balance figures of one layer from its per-expert assignment counts."""
+    counts = counts.float().cpu()
+    E = counts.numel()
+    tot = float(counts.sum())
+    if tot <= 0:
+        return {"n_experts": E, "total_tokens": 0}
+    u = counts / tot
+    ent = float(-(u * torch.log(u + 1e-10)).sum())
+    srt, _ = torch.sort(u)
+    idx = torch.arange(1, E + 1, dtype=torch.float32)
+    gini = float(((2 * idx - E - 1) * srt).sum() / E)               # 0 = uniform, 1 - 1/E = one expert
+    meaningful = int((u > 0.1 / E).sum())                            # at least a tenth of the uniform share
+    return {"n_experts": E, "total_tokens": int(tot), "expert_counts": counts.tolist(), "expert_fracs": u.tolist(),
+            "entropy": ent, "normalized_entropy": ent / math.log(E) if E > 1 else 0.0, "gini": gini,
+            "min_frac": float(u.min()), "max_frac": float(u.max()), "imbalance": float(u.max() * E),
+            "active_experts": int((counts > 0).sum()), "meaningful_experts": meaningful,
+            "collapsed": meaningful < 0.5 * E}
+
+
+def _summarise(per_layer: Dict[int, Dict[str, object]], verbose: bool) -> Dict[str, object]:
+    live = {i: s for i, s in per_layer.items() if s.get("total_tokens", 0) > 0}
+    agg: Dict[str, object] = {}
+    if live:
+        ne = [s["normalized_entropy"] for s in live.values()]
+        agg = {"mean_normalized_entropy": sum(ne) / len(ne), "min_normalized_entropy": min(ne),
+               "worst_max_frac": max(s["max_frac"] for s in live.values()),
+               "mean_active_experts": sum(s["active_experts"] for s in live.values()) / len(live),
+               "collapsed_layers": [i for i, s in live.items() if s["collapsed"]]}
+    if verbose:
+        for i, s in sorted(live.items()):
+            flag = "  COLLAPSED" if s["collapsed"] else ""
+            print(f"  layer {i:3d}: entropy {s['normalized_entropy']:.3f}  gini {s['gini']:.3f}  "
+                  f"max {s['max_frac']:.3f}  min {s['min_frac']:.4f}  active {s['active_experts']}/{s['n_experts']}{flag}")
+        if agg:
+            print(f"  mean entropy {agg['mean_normalized_entropy']:.3f}, collapsed layers: {agg['collapsed_layers'] or 'none'}")
+    return {"per_layer": per_layer, "aggregate": agg}
+
+
+def _moe_dict(moe_layers) -> Dict[int, torch.nn.Module]:
+    if isinstance(moe_layers, SparseModelWrapper):
+        return moe_layers.moe_modules()
+    return {int(k): v for k, v in moe_layers.items()}
+
+
+def compute_routing_stats(moe_layers, verbose: bool = True) -> Dict[str, object]:
+    """Load balance of every MoE layer in the LAST forward pass: entropy (normalised by log E), Gini, min /
+    max share, active experts, and a collapse flag (fewer than half of the experts get a tenth of the uniform
+    share).  ``moe_layers``: a ``SparseModelWrapper`` or a mapping layer index -> MoE layer
+    (reference: Experiments/sparse_distillation/finetune_eval.py:67-209)."""
+    per = {}
+    for i, m in sorted(_moe_dict(moe_layers).items()):
+        c = getattr(m, "_last_expert_counts", None)
+        per[i] = _layer_stats(c) if c is not None else {"n_experts": m.n_experts, "total_tokens": 0}
+    return _summarise(per, verbose)
+
+
+def reset_routing_stats(moe_layers) -> None:
+    for m in _moe_dict(moe_layers).values():
+        m._accumulated_counts = None
+
+
+def start_routing_accumulation(moe_layers) -> None:
+    """From now on ``accumulate_routing_stats`` adds each forward's counts to a running total."""
+    reset_routing_stats(moe_layers)
+    for m in _moe_dict(moe_layers).values():
+        m._accumulate_routing = True
+
+
+def stop_routing_accumulation(moe_layers) -> None:
+    for m in _moe_dict(moe_layers).values():
+        m._accumulate_routing = False
+
+
+def accumulate_routing_stats(moe_layers, batches: Optional[Iterable[torch.Tensor]] = None):
+    """Without ``batches``: fold the last forward's counts into the running totals of the layers that are
+    accumulating (call after each forward).  With ``batches`` (wrapper only): run them and return the
+    accumulated per-layer summary - the one-call form."""
+    if batches is not None:
+        return _accumulate_over(moe_layers, batches)
+    for m in _moe_dict(moe_layers).values():
+        if getattr(m, "_accumulate_routing", False) and getattr(m, "_last_expert_counts", None) is not None:
+            c = m._last_expert_counts.detach().float().cpu()
+            acc = getattr(m, "_accumulated_counts", None)
+            m._accumulated_counts = c if acc is None else acc + c
+
+
+def compute_routing_stats_accumulated(moe_layers, verbose: bool = True) -> Dict[str, object]:
+    """Same figures as ``compute_routing_stats`` over everything accumulated since
+    ``start_routing_accumulation`` (reference: finetune_eval.py:251-385)."""
+    per = {}
+    for i, m in sorted(_moe_dict(moe_layers).items()):
+        c = getattr(m, "_accumulated_counts", None)
+        per[i] = _layer_stats(c) if c is not None else {"n_experts": m.n_experts, "total_tokens": 0}
+    return _summarise(per, verbose)
+
+
+def _accumulate_over(wrapper: SparseModelWrapper, batches: Iterable[torch.Tensor]) -> Dict[int, Dict[str, float]]:
+    start_routing_accumulation(wrapper)
     wrapper.model.eval()
     with torch.no_grad():
         for ids in batches:
             wrapper(ids)
-            for i, m in wrapper.moe_modules().items():
-                c = m._last_expert_counts.float().cpu()
-                acc[i] = c if i not in acc else acc[i] + c
+            accumulate_routing_stats(wrapper)
+    stop_routing_accumulation(wrapper)
     out = {}
-    for i, c in acc.items():
-        u = c / c.sum().clamp(min=1)
-        out[i] = {"entropy": float(-(u * torch.log(u + 1e-10)).sum() / math.log(max(len(u), 2))),
-                  "max_usage": float(u.max()), "min_usage": float(u.min()), "dead": int((u == 0).sum())}
+    for i, st in compute_routing_stats_accumulated(wrapper, verbose=False)["per_layer"].items():
+        if st.get("total_tokens", 0) > 0:
+            out[i] = {"entropy": st["normalized_entropy"], "max_usage": st["max_frac"], "min_usage": st["min_frac"],
+                      "dead": st["n_experts"] - st["active_experts"], "gini": st["gini"]}
     return out
 
 
+def _logits(out, logits_of=None):
+    if logits_of is not None:
+        return logits_of(out)
+    return out["logits"] if isinstance(out, dict) else getattr(out, "logits", out)
+
+
+def _ids_of(batch):
+    if isinstance(batch, dict):
+        return batch.get("input_ids", batch.get("tokens"))
+    return batch[0] if isinstance(batch, (list, tuple)) else batch
+
+
 @torch.no_grad()
+def compute_perplexity(model, batches: Iterable, logits_of=None, pad_token_id: Optional[int] = None,
+                       max_batches: Optional[int] = None, accumulate_routing: bool = False) -> float:
+    """Token-weighted next-token perplexity.  Positions whose target is ``pad_token_id`` do not count;
+    ``accumulate_routing`` (model = ``SparseModelWrapper``) folds every batch's expert counts into the
+    layers' running totals (reference: finetune_eval.py:388-464)."""
+    tot, n = 0.0, 0
+    was_training = getattr(model, "training", False)
+    model.eval()
+    if accumulate_routing:
+        start_routing_accumulation(model)
+    for bi, batch in enumerate(batches):
+        if max_batches is not None and bi >= max_batches:
+            break
+        ids = _ids_of(batch)
+        logits = _logits(model(ids), logits_of)
+        tgt = ids[:, 1:].reshape(-1)
+        if pad_token_id is not None:
+            tgt = tgt.masked_fill(tgt == pad_token_id, -100)
+        k = int((tgt != -100).sum())
+        if k == 0:
+            continue
+        loss = F.cross_entropy(logits[:, :-1].reshape(-1, logits.shape[-1]).float(), tgt, ignore_index=-100)
+        tot, n = tot + float(loss) * k, n + k
+        if accumulate_routing:
+            accumulate_routing_stats(model)
+    if accumulate_routing:
+        stop_routing_accumulation(model)
+    if was_training:
+        model.train()
+    return math.exp(min(tot / max(n, 1), 50.0))
+
+
 def perplexity(model, batches: Iterable[torch.Tensor], logits_of=None) -> float:
     """Next-token perplexity; ``logits_of(output)`` extracts (B, S, V) logits from the model output."""
-    tot, n = 0.0, 0
-    for ids in batches:
-        out = model(ids)
-        logits = logits_of(out) if logits_of else (out["logits"] if isinstance(out, dict) else getattr(out, "logits", out))
-        loss = F.cross_entropy(logits[:, :-1].reshape(-1, logits.shape[-1]).float(), ids[:, 1:].reshape(-1))
-        k = ids[:, 1:].numel()
-        tot, n = tot + float(loss) * k, n + k
-    return math.exp(min(tot / max(n, 1), 50.0))
+    return compute_perplexity(model, batches, logits_of)
+
+
+def compare_dense(dense_model, wrapper: SparseModelWrapper, batches, logits_of=None,
+                  pad_token_id: Optional[int] = None) -> Dict[str, float]:
+    """Perplexity of the original dense model against the converted sparse one on the same batches."""
+    batches = list(batches)
+    d = compute_perplexity(dense_model, batches, logits_of, pad_token_id)
+    s_ = compute_perplexity(wrapper, batches, logits_of, pad_token_id)
+    return {"dense_ppl": d, "sparse_ppl": s_, "ratio": s_ / d if d > 0 else float("inf")}
 
 
 def freeze_all_but_moe(wrapper: SparseModelWrapper) -> int:
@@ -55,45 +197,179 @@ def freeze_all_but_moe(wrapper: SparseModelWrapper) -> int:
     return n
 
 
-def finetune(wrapper: SparseModelWrapper, batches: Iterable[torch.Tensor], steps: int, lr: float = 1e-5,
+def aux_losses(wrapper: SparseModelWrapper, lb_weight: float, z_weight: float) -> torch.Tensor:
+    """Load-balance (E * sum_e f_e P_e) and z (mean logsumexp^2) terms from the router logits each MoE
+    layer cached in the forward pass that just ran."""
+    total = None
+    for m in wrapper.moe_modules().values():
+        rl, c = getattr(m, "_last_router_logits", None), getattr(m, "_last_expert_counts", None)
+        if rl is None:
+            continue
+        t = 0.0
+        if lb_weight > 0 and c is not None and m.routing == "token_choice":
+            E = rl.shape[-1]
+            P = F.softmax(rl.reshape(-1, E).float(), -1).mean(0)
+            t = t + lb_weight * E * ((c.float() / c.sum().clamp(min=1)) * P).sum()
+        if z_weight > 0:
+            t = t + z_weight * torch.logsumexp(rl.float(), -1).pow(2).mean()
+        if torch.is_tensor(t):
+            total = t if total is None else total + t
+    return total if total is not None else torch.zeros((), device=next(wrapper.model.parameters()).device)
+
+
+def _save(path: str, wrapper: SparseModelWrapper, opt, step: int, ppl: float, with_optimizer: bool) -> None:
+    os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
+    moe = {str(i): m.state_dict() for i, m in wrapper.moe_modules().items()}
+    ck = {"model": wrapper.model.state_dict(), "moe_layers": moe, "step": step, "ppl": ppl}
+    if with_optimizer:
+        ck["optimizer"] = opt.state_dict()
+    torch.save(ck, path)
+
+
+def load_finetuned(wrapper: SparseModelWrapper, path: str, optimizer=None) -> int:
+    """Load weights saved by ``finetune`` (and the optimizer state when one is passed: resume).  Returns
+    the step the file was written at."""
+    ck = torch.load(path, map_location="cpu", weights_only=False)
+    wrapper.model.load_state_dict(ck["model"])
+    if optimizer is not None and "optimizer" in ck:
+        optimizer.load_state_dict(ck["optimizer"])
+    return int(ck.get("step", 0))
+
+
+def finetune(wrapper: SparseModelWrapper, batches: Iterable, steps: int, lr: float = 1e-5,
              lb_weight: float = 0.01, z_weight: float = 0.001, moe_only: bool = True, out_dir: Optional[str] = None,
-             eval_batches=None, logits_of=None) -> Dict[str, float]:
+             eval_batches=None, logits_of=None, eval_every: Optional[int] = None, lr_schedule: bool = False,
+             resume: Optional[str] = None, pad_token_id: Optional[int] = None, max_grad_norm: float = 1.0,
+             log_every: int = 0) -> Dict[str, object]:
+    """Language-model fine-tuning of the converted model: cross-entropy plus the routers' auxiliary losses,
+    gradient clipping, constant LR or cosine decay to 10 %, evaluation every ``eval_every`` steps with
+    ``latest_checkpoint.pt`` (with optimizer state, for ``resume``) and ``best_checkpoint.pt`` under
+    ``out_dir`` (reference: finetune_eval.py:498-693)."""
     if moe_only:
         freeze_all_but_moe(wrapper)
     params = [p for p in wrapper.model.parameters() if p.requires_grad]
     opt = torch.optim.AdamW(params, lr=lr, weight_decay=0.0)
-    best = float("inf")
+    start = load_finetuned(wrapper, resume, opt) if resume else 0
+    eval_every = eval_every or max(steps // 4, 1)
+    best, last = float("inf"), 0.0
+    history: List[Dict[str, float]] = []
     wrapper.model.train()
     it = iter(batches)
-    last = 0.0
-    for s in range(steps):
+    for s in range(start, steps):
         try:
-            ids = next(it)
+            batch = next(it)
         except StopIteration:
             it = iter(batches)
-            ids = next(it)
-        out = wrapper(ids)
-        logits = logits_of(out) if logits_of else (out["logits"] if isinstance(out, dict) else getattr(out, "logits", out))
-        loss = F.cross_entropy(logits[:, :-1].reshape(-1, logits.shape[-1]).float(), ids[:, 1:].reshape(-1))
-        for m in wrapper.moe_modules().values():
-            rl, c = m._last_router_logits, m._last_expert_counts
-            if rl is not None and m.routing == "token_choice":
-                E = rl.shape[-1]
-                P = F.softmax(rl.reshape(-1, E).float(), -1).mean(0)
-                loss = loss + lb_weight * E * ((c.float() / c.sum().clamp(min=1)) * P).sum()
-            if rl is not None:
-                loss = loss + z_weight * torch.logsumexp(rl.float(), -1).pow(2).mean()
+            batch = next(it)
+        if lr_schedule:
+            for g in opt.param_groups:
+                g["lr"] = lr * (0.1 + 0.9 * 0.5 * (1 + math.cos(math.pi * s / max(steps, 1))))
+        ids = _ids_of(batch)
+        logits = _logits(wrapper(ids), logits_of)
+        tgt = ids[:, 1:].reshape(-1)
+        if pad_token_id is not None:
+            tgt = tgt.masked_fill(tgt == pad_token_id, -100)
+        lm = F.cross_entropy(logits[:, :-1].reshape(-1, logits.shape[-1]).float(), tgt, ignore_index=-100)
+        loss = lm + aux_losses(wrapper, lb_weight, z_weight)
         opt.zero_grad(set_to_none=True)
         loss.backward()
-        torch.nn.utils.clip_grad_norm_(params, 1.0)
+        torch.nn.utils.clip_grad_norm_(params, max_grad_norm)
         opt.step()
-        last = float(loss)
-        if out_dir and eval_batches is not None and (s + 1) % max(steps // 4, 1) == 0:
-            os.makedirs(out_dir, exist_ok=True)
-            ppl = perplexity(wrapper, eval_batches, logits_of)
+        last = float(loss.detach())
+        if log_every and (s + 1) % log_every == 0:
+            print(f"step {s + 1}/{steps}  loss {last:.4f}  lm {float(lm.detach()):.4f}", flush=True)
+        if eval_batches is not None and ((s + 1) % eval_every == 0 or s + 1 == steps):
+            ppl = compute_perplexity(wrapper, eval_batches, logits_of, pad_token_id)
             wrapper.model.train()
-            torch.save({"model": wrapper.model.state_dict(), "step": s + 1, "ppl": ppl}, os.path.join(out_dir, "latest_checkpoint.pt"))
+            history.append({"step": s + 1, "ppl": ppl, "loss": last})
+            if out_dir:
+                _save(os.path.join(out_dir, "latest_checkpoint.pt"), wrapper, opt, s + 1, ppl, True)
             if ppl < best:
                 best = ppl
-                torch.save({"model": wrapper.model.state_dict(), "step": s + 1, "ppl": ppl}, os.path.join(out_dir, "best_checkpoint.pt"))
-    return {"final_loss": last, "best_ppl": best}
+                if out_dir:
+                    _save(os.path.join(out_dir, "best_checkpoint.pt"), wrapper, opt, s + 1, ppl, False)
+    return {"final_loss": last, "best_ppl": best, "history": history}
+
+
+def _token_batches(a, vocab: int, n: int, seed: int):
+    """Batches of token ids: a ``.bin`` file of uint16 ids when ``--data`` names one, otherwise random ids
+    from a seed (there is no dataset download in this script)."""
+    g = torch.Generator().manual_seed(seed)
+    if a.data:
+        import numpy as np
+        arr = np.memmap(a.data, dtype=np.uint16, mode="r")
+        n_seq = (len(arr) - 1) // a.seq_len
+        pick = torch.randperm(n_seq, generator=g)[: n * a.batch_size].tolist()
+        rows = [torch.from_numpy(np.asarray(arr[i * a.seq_len: (i + 1) * a.seq_len], dtype=np.int64)) for i in pick]
+        return [torch.stack(rows[i: i + a.batch_size]).to(a.device) for i in range(0, len(rows) - a.batch_size + 1, a.batch_size)]
+    return [torch.randint(0, vocab, (a.batch_size, a.seq_len), generator=g).to(a.device) for _ in range(n)]
+
+
+def main(argv=None):
+    """Fine-tune and/or evaluate a distilled checkpoint:
+
+        python -m experiments.sparse_distillation.finetune_eval --model toy --checkpoint out/distilled_moe.pt \\
+            [--eval_only] [--compare_dense] [--random_init] [--moe_only] [--lr_schedule] [--resume latest.pt]
+    """
+    import argparse
+    import copy
+    import json
+    from .convert import convert_to_sparse
+    ap = argparse.ArgumentParser(description="fine-tune and evaluate a sparse (distilled) model")
+    ap.add_argument("--model", default="toy", help="'toy' or a local Hugging Face model directory")
+    ap.add_argument("--checkpoint", required=True, help="file written by SparseDistillationTrainer.save")
+    ap.add_argument("--data", default=None, help="uint16 token file; random tokens when absent")
+    ap.add_argument("--seq_len", type=int, default=64)
+    ap.add_argument("--batch_size", type=int, default=4)
+    ap.add_argument("--max_steps", type=int, default=100)
+    ap.add_argument("--eval_every", type=int, default=None)
+    ap.add_argument("--eval_batches", type=int, default=8)
+    ap.add_argument("--lr", type=float, default=1e-4)
+    ap.add_argument("--moe_only", action="store_true")
+    ap.add_argument("--lr_schedule", action="store_true")
+    ap.add_argument("--load_balance_weight", type=float, default=0.01)
+    ap.add_argument("--z_loss_weight", type=float, default=0.001)
+    ap.add_argument("--resume", default=None, help="latest_checkpoint.pt of an earlier run (with optimizer state)")
+    ap.add_argument("--load_finetuned", default=None, help="weights of an earlier run, no optimizer state")
+    ap.add_argument("--eval_only", action="store_true")
+    ap.add_argument("--compare_dense", action="store_true")
+    ap.add_argument("--random_init", action="store_true", help="control: random experts instead of distilled ones")
+    ap.add_argument("--output", default=None)
+    ap.add_argument("--device", default="cpu")
+    a = ap.parse_args(argv)
+    if a.model == "toy":
+        from .example_usage import ToyLM
+        torch.manual_seed(0)
+        model, vocab = ToyLM(), 256
+    else:
+        from transformers import AutoModelForCausalLM
+        model = AutoModelForCausalLM.from_pretrained(a.model, local_files_only=True)
+        vocab = model.config.vocab_size
+    model.to(a.device)
+    dense = copy.deepcopy(model).eval() if a.compare_dense else None
+    wrapper = convert_to_sparse(model, distilled_path=a.checkpoint, random_init=a.random_init)
+    if a.load_finetuned:
+        load_finetuned(wrapper, a.load_finetuned)
+    train_b = _token_batches(a, vocab, max(a.max_steps, 1), seed=1)
+    eval_b = _token_batches(a, vocab, a.eval_batches, seed=2)
+    report: Dict[str, object] = {"parameters": wrapper.count_parameters()}
+    report["ppl_before"] = compute_perplexity(wrapper, eval_b, accumulate_routing=True)
+    report["routing_before"] = compute_routing_stats_accumulated(wrapper, verbose=False)["aggregate"]
+    if not a.eval_only:
+        report["finetune"] = finetune(wrapper, train_b, a.max_steps, lr=a.lr, lb_weight=a.load_balance_weight,
+                                      z_weight=a.z_loss_weight, moe_only=a.moe_only, out_dir=a.output,
+                                      eval_batches=eval_b, eval_every=a.eval_every, lr_schedule=a.lr_schedule,
+                                      resume=a.resume)
+        report["ppl_after"] = compute_perplexity(wrapper, eval_b, accumulate_routing=True)
+        report["routing_after"] = compute_routing_stats_accumulated(wrapper, verbose=False)["aggregate"]
+    if dense is not None:
+        report["dense_ppl"] = compute_perplexity(dense, eval_b)
+    print(json.dumps(report, indent=1, default=str))
+    if a.output:
+        os.makedirs(a.output, exist_ok=True)
+        json.dump(report, open(os.path.join(a.output, "finetune_report.json"), "w"), indent=1, default=str)
+    return report
+
+
+if __name__ == "__main__":
+    main()

@@ -105,3 +105,30 @@ def test_router_supervision_from_real_activations():
     assert last < first
     q = tr.analyze_cluster_quality(0, ks=(2, 4), batches=batches)
     assert set(q) == {2, 4}
+
+
+def test_finetune_eval_cli_and_routing_statistics(tmp_path):
+    """Distil, save, then run the fine-tune/evaluate command line on the saved file: routing statistics over
+    several batches, perplexity before/after, best and latest checkpoints, resume from the latest one."""
+    from experiments.sparse_distillation import finetune_eval as fe
+    torch.manual_seed(0)
+    m = ToyLM().eval()
+    tr = SparseDistillationTrainer(m, _cfg(), device="cpu")
+    tr.distill(steps=10)
+    ck = str(tmp_path / "distilled.pt")
+    tr.save(ck)
+    out = str(tmp_path / "ft")
+    rep = fe.main(["--checkpoint", ck, "--max_steps", "8", "--eval_every", "4", "--moe_only", "--compare_dense",
+                   "--output", out, "--seq_len", "16", "--eval_batches", "2", "--lr", "1e-3"])
+    # random tokens carry nothing to learn: perplexity stays near the vocabulary size, for dense and sparse alike
+    assert abs(rep["ppl_after"] - rep["ppl_before"]) < 0.05 * rep["ppl_before"]
+    assert 100 < rep["dense_ppl"] < 600 and [h["step"] for h in rep["finetune"]["history"]] == [4, 8]
+    assert 0.0 < rep["routing_before"]["mean_normalized_entropy"] <= 1.0
+    assert (tmp_path / "ft" / "best_checkpoint.pt").exists() and (tmp_path / "ft" / "latest_checkpoint.pt").exists()
+    rep2 = fe.main(["--checkpoint", ck, "--max_steps", "10", "--resume", out + "/latest_checkpoint.pt", "--moe_only",
+                    "--seq_len", "16", "--eval_batches", "2"])
+    assert len(rep2["finetune"]["history"]) >= 1 and rep2["finetune"]["history"][0]["step"] > 8
+    # per-layer figures from hand-made counts
+    st = fe._layer_stats(torch.tensor([10.0, 10.0, 0.0, 0.0]))
+    assert st["active_experts"] == 2 and abs(st["normalized_entropy"] - 0.5) < 1e-3 and not st["collapsed"]
+    assert fe._layer_stats(torch.tensor([100.0, 0.0, 0.0, 0.0]))["collapsed"]
