@@ -2,11 +2,40 @@
 reference's ``Experiments/sparse_distillation/dynamic_experts.py``)."""
 from __future__ import annotations
 
-from typing import Dict, List
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
 
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
+
+
+@dataclass
+class DynamicExpertConfig:
+    """When and by how much expert widths change (reference: dynamic_experts.py:33-51)."""
+    reallocate_every_n_steps: int = 500
+    growth_factor: float = 1.25
+    shrink_factor: float = 0.8
+    min_d_ff: int = 256
+    max_d_ff: int = 8192
+    top_k_grow: int = 2                 # the experts with the highest loss grow
+    top_k_shrink: int = 2               # the ones with the lowest loss shrink
+    maintain_param_budget: bool = True  # rescale all widths so that the total stays what it was
+    round_to: int = 8                   # widths stay multiples of this (vector loads, tensor-core tiles)
+
+
+@dataclass
+class ExpertStats:
+    """Running reconstruction loss of one expert since the last reallocation."""
+    expert_idx: int
+    d_ff: int
+    total_loss: float = 0.0
+    token_count: int = 0
+
+    @property
+    def avg_loss(self) -> float:
+        return self.total_loss / max(self.token_count, 1)
 
 
 class DynamicExpertLayer(nn.Module):
@@ -25,6 +54,24 @@ class DynamicExpertLayer(nn.Module):
 
     def expert(self, e: int, x: torch.Tensor) -> torch.Tensor:
         return (F.silu(x @ self.w1[e]) * (x @ self.w2[e])) @ self.w3[e]
+
+    def forward_expert(self, x: torch.Tensor, expert_idx: int) -> torch.Tensor:
+        return self.expert(expert_idx, x)
+
+    def get_expert_params(self, e: int) -> int:
+        return 3 * self.d_model * self.d_ffs[e]
+
+    def get_total_params(self) -> int:
+        return sum(self.get_expert_params(e) for e in range(self.n_experts))
+
+    def get_avg_active_params(self, top_k: int = 2, usage: Optional[torch.Tensor] = None) -> float:
+        """Expected expert parameters touched per token: ``top_k`` times the mean expert size, weighted by
+        the experts' token shares when ``usage`` is given (wide experts that are rarely picked cost little)."""
+        sizes = torch.tensor([float(self.get_expert_params(e)) for e in range(self.n_experts)])
+        if usage is None:
+            return float(top_k * sizes.mean())
+        u = usage.float().cpu()
+        return float(top_k * (sizes * u / u.sum().clamp(min=1e-12)).sum())
 
     def forward(self, x: torch.Tensor, idx: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         out = torch.zeros_like(x)
@@ -51,18 +98,34 @@ def interpolate_expert_weights(w1, w2, w3, new_f: int):
 
 
 class DynamicExpertTracker:
-    """Exponential moving average of the per-expert reconstruction loss and token share."""
+    """Per-expert loss bookkeeping for width reallocation.  Two views are kept: an exponential moving
+    average of loss and token share (``update`` / ``plan``: grow where loss x share is largest), and plain
+    sums since the last reallocation (``update_stats`` / ``compute_reallocation``, the reference's scheme:
+    dynamic_experts.py:241-345 - rank by mean loss, grow the worst, shrink the best, optionally rescale all
+    widths so the layer's parameter count stays put)."""
 
-    def __init__(self, n_experts: int, momentum: float = 0.99):
+    def __init__(self, n_experts: int, momentum: float = 0.99, initial_d_ff: Optional[int] = None,
+                 d_model: Optional[int] = None, config: Optional[DynamicExpertConfig] = None):
+        self.n_experts, self.d_model = n_experts, d_model
+        self.config = config or DynamicExpertConfig()
         self.loss = torch.zeros(n_experts)
         self.share = torch.zeros(n_experts)
         self.momentum, self.steps = momentum, 0
+        self.expert_stats: Dict[int, ExpertStats] = {e: ExpertStats(e, initial_d_ff or 0) for e in range(n_experts)}
+        self.step_count = 0
+        self.reallocation_history: List[Dict] = []
 
+    # ---- moving averages
     def update(self, per_expert_loss: torch.Tensor, counts: torch.Tensor):
         m = self.momentum if self.steps else 0.0
         self.loss = m * self.loss + (1 - m) * per_expert_loss.detach().float().cpu()
         self.share = m * self.share + (1 - m) * (counts.float() / counts.sum().clamp(min=1)).cpu()
         self.steps += 1
+        self.step_count += 1
+        for e in range(self.n_experts):
+            n = int(counts[e])
+            self.expert_stats[e].total_loss += float(per_expert_loss[e]) * n
+            self.expert_stats[e].token_count += n
 
     def plan(self, d_ffs: List[int], top_k_grow=2, top_k_shrink=2, growth=1.25, shrink=0.8, lo=256, hi=8192) -> Dict[int, int]:
         order = torch.argsort(self.loss * self.share, descending=True).tolist()
@@ -73,6 +136,71 @@ class DynamicExpertTracker:
             if e not in plan:
                 plan[e] = max(lo, int(d_ffs[e] * shrink) // 8 * 8)
         return {e: f for e, f in plan.items() if f != d_ffs[e]}
+
+    # ---- sums since the last reallocation
+    def update_stats(self, expert_outputs: Dict[int, torch.Tensor], targets: Dict[int, torch.Tensor]) -> None:
+        """``expert_outputs[e]`` / ``targets[e]``: (n_e, d_model) rows routed to expert e and what they should be."""
+        for e, out in expert_outputs.items():
+            if e in targets and out.numel():
+                self.expert_stats[e].total_loss += float(F.mse_loss(out.float(), targets[e].float(), reduction="sum"))
+                self.expert_stats[e].token_count += out.shape[0]
+        self.step_count += 1
+
+    def set_widths(self, d_ffs: List[int]) -> None:
+        for e, f in enumerate(d_ffs):
+            self.expert_stats[e].d_ff = int(f)
+
+    def should_reallocate(self) -> bool:
+        return self.step_count > 0 and self.step_count % self.config.reallocate_every_n_steps == 0
+
+    def compute_reallocation(self) -> Dict[int, int]:
+        """New width for every expert (unchanged ones included)."""
+        c = self.config
+        rnd = lambda f: max(c.round_to, int(f) // c.round_to * c.round_to)
+        ranked = sorted(self.expert_stats.values(), key=lambda s: s.avg_loss, reverse=True)
+        new = {s.expert_idx: s.d_ff for s in ranked}
+        grow = ranked[: c.top_k_grow]
+        for s in grow:
+            new[s.expert_idx] = min(rnd(s.d_ff * c.growth_factor), c.max_d_ff)
+        for s in ranked[::-1][: c.top_k_shrink]:
+            if s not in grow:
+                new[s.expert_idx] = max(rnd(s.d_ff * c.shrink_factor), c.min_d_ff)
+        if c.maintain_param_budget:
+            before, after = sum(s.d_ff for s in ranked), sum(new.values())
+            if after != before and after > 0:
+                k = before / after                      # parameters are linear in the width
+                new = {e: min(max(rnd(f * k), c.min_d_ff), c.max_d_ff) for e, f in new.items()}
+        self.reallocation_history.append({"step": self.step_count, "d_ff": dict(new),
+                                          "avg_loss": {s.expert_idx: s.avg_loss for s in ranked}})
+        return new
+
+    def reset_stats(self) -> None:
+        for s in self.expert_stats.values():
+            s.total_loss, s.token_count = 0.0, 0
+
+    def get_report(self) -> str:
+        d = self.d_model or 1
+        ranked = sorted(self.expert_stats.values(), key=lambda s: s.avg_loss, reverse=True)
+        total = sum(3 * d * s.d_ff for s in ranked) or 1
+        lines = ["expert statistics (highest loss first):"]
+        for s in ranked:
+            p = 3 * d * s.d_ff
+            lines.append(f"  expert {s.expert_idx:2d}: d_ff {s.d_ff:5d}  avg loss {s.avg_loss:.6f}  tokens {s.token_count}"
+                         f"  params {p:,} ({100 * p / total:.1f} %)")
+        w = [s.d_ff for s in ranked]
+        lines.append(f"  total params {total:,}; d_ff min {min(w)} max {max(w)} mean {sum(w) / len(w):.0f}")
+        return "\n".join(lines)
+
+
+def print_active_params_report(layers: Dict[int, DynamicExpertLayer], top_k: int = 2,
+                               usage: Optional[Dict[int, torch.Tensor]] = None) -> Dict[int, Dict[str, float]]:
+    """Total and expected-active expert parameters per layer (reference: dynamic_experts.py:421-446)."""
+    out = {}
+    for i, layer in sorted(layers.items()):
+        act = layer.get_avg_active_params(top_k, usage.get(i) if usage else None)
+        out[i] = {"total": layer.get_total_params(), "active": act, "widths": list(layer.d_ffs)}
+        print(f"  layer {i}: total {out[i]['total']:,}  active/token {act:,.0f}  widths {min(layer.d_ffs)}..{max(layer.d_ffs)}")
+    return out
 
 
 @torch.no_grad()

@@ -132,3 +132,30 @@ def test_finetune_eval_cli_and_routing_statistics(tmp_path):
     st = fe._layer_stats(torch.tensor([10.0, 10.0, 0.0, 0.0]))
     assert st["active_experts"] == 2 and abs(st["normalized_entropy"] - 0.5) < 1e-3 and not st["collapsed"]
     assert fe._layer_stats(torch.tensor([100.0, 0.0, 0.0, 0.0]))["collapsed"]
+
+
+def test_dynamic_expert_tracker_reallocation_keeps_the_budget():
+    from experiments.sparse_distillation.dynamic_experts import (DynamicExpertConfig, DynamicExpertTracker,
+                                                                 print_active_params_report)
+    torch.manual_seed(0)
+    cfg = DynamicExpertConfig(reallocate_every_n_steps=2, min_d_ff=16, max_d_ff=512, top_k_grow=1, top_k_shrink=1)
+    layer = DynamicExpertLayer(32, [64, 64, 64, 64])
+    tr = DynamicExpertTracker(4, initial_d_ff=64, d_model=32, config=cfg)
+    x = torch.randn(40, 32)
+    for step in range(2):
+        outs = {e: layer.forward_expert(x[e * 10:(e + 1) * 10], e) for e in range(4)}
+        tgts = {e: outs[e].detach() + (3.0 if e == 2 else 0.1 * (e + 1)) for e in range(4)}   # expert 2 is the worst
+        tr.update_stats(outs, tgts)
+    assert tr.should_reallocate()
+    new = tr.compute_reallocation()
+    assert new[2] == max(new.values()) and new[0] == min(new.values())
+    assert abs(sum(new.values()) - 4 * 64) <= 4 * cfg.round_to and all(f % cfg.round_to == 0 for f in new.values())
+    before = layer.get_total_params()
+    reallocate_expert_layer(layer, {e: f for e, f in new.items() if f != layer.d_ffs[e]})
+    tr.set_widths(layer.d_ffs)
+    tr.reset_stats()
+    assert abs(layer.get_total_params() - before) <= 3 * 32 * 4 * cfg.round_to
+    assert "expert  2" in tr.get_report() and tr.expert_stats[2].token_count == 0
+    rep = print_active_params_report({0: layer}, top_k=2, usage={0: torch.tensor([1.0, 1.0, 0.0, 0.0])})
+    assert rep[0]["active"] == 2 * 0.5 * (layer.get_expert_params(0) + layer.get_expert_params(1))
+    assert layer(x, torch.randint(0, 4, (40, 2)), torch.rand(40, 2)).shape == x.shape
