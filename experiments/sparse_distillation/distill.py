@@ -260,6 +260,8 @@ class SparseDistillationTrainer:
         assert self.ffn, "no FFN modules found in the model"
         self.d_model, self.d_ff_dense, self.dtype = self._infer_dimensions()
         self.layer_cfg = json.load(open(config.layer_config_path)) if config.layer_config_path else {}
+        if isinstance(self.layer_cfg.get("layers"), dict):      # file written by generate_config.compute_layer_config
+            self.layer_cfg = self.layer_cfg["layers"]
         self.moe_layers = nn.ModuleDict()
         self._create_moe_layers()
         self.optimizers: Dict[int, torch.optim.Optimizer] = {}

@@ -159,3 +159,22 @@ def test_dynamic_expert_tracker_reallocation_keeps_the_budget():
     rep = print_active_params_report({0: layer}, top_k=2, usage={0: torch.tensor([1.0, 1.0, 0.0, 0.0])})
     assert rep[0]["active"] == 2 * 0.5 * (layer.get_expert_params(0) + layer.get_expert_params(1))
     assert layer(x, torch.randint(0, 4, (40, 2)), torch.rand(40, 2)).shape == x.shape
+
+
+def test_compute_layer_config_holds_the_ratios(tmp_path):
+    import json
+    from experiments.sparse_distillation.generate_config import compute_layer_config, main
+    analysis = {"d_model": 64, "d_ff": 1024, "layers": {
+        "0": {"n_experts": 8, "balance": 0.9, "silhouette": 0.2},
+        "1": {"n_experts": 2, "balance": 0.8, "all_results": {"2": {"balance": 0.8}, "4": {"balance": 0.5}, "16": {"balance": 0.7}}},
+        "2": {"n_experts": 2, "balance": 0.8}}}
+    cfg = compute_layer_config(analysis, 3.0, 0.25, min_experts=4, verbose=False)
+    L = cfg["layers"]
+    assert L["0"] == {"n_experts": 8, "d_ff_expert": 384, "top_k": 1, "balance": 0.9, "silhouette": 0.2}
+    assert L["1"]["n_experts"] == 16 and L["1"]["balance"] == 0.7 and L["1"]["d_ff_expert"] == 192
+    assert L["2"]["n_experts"] == 4 and L["2"]["d_ff_expert"] == 768
+    assert abs(cfg["stats"]["actual_expansion_ratio"] - 3.0) < 1e-6
+    f = tmp_path / "a.json"
+    f.write_text(json.dumps(analysis))
+    out = main(["--analysis", str(f), "--output", str(tmp_path / "o.json")])
+    assert json.load(open(tmp_path / "o.json"))["layers"] == out["layers"]
