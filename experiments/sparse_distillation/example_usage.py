@@ -55,6 +55,15 @@ def main(argv=None):
     ap.add_argument("--top_k", type=int, default=2)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--analyze_clusters", action="store_true")
+    ap.add_argument("--routing", default="token_choice", choices=["token_choice", "expert_choice"])
+    ap.add_argument("--d_ff_expert", type=float, default=None, help="width (>4) or fraction of the dense width (<=4)")
+    ap.add_argument("--layer_config", default=None, help="per-layer configuration written by generate_config")
+    ap.add_argument("--mode", default="data_free",
+                    choices=["data_free", "parallel", "sequential", "empirical", "dynamic"],
+                    help="training mode; 'parallel' and 'sequential' train on token batches through the model")
+    ap.add_argument("--router_mlp", action="store_true")
+    ap.add_argument("--no_expert_bias", action="store_true")
+    ap.add_argument("--lr", type=float, default=1e-3)
     ap.add_argument("--output_dir", default="sparse_distillation_output")
     ap.add_argument("--device", default="cpu")
     a = ap.parse_args(argv)
@@ -66,15 +75,26 @@ def main(argv=None):
         from transformers import AutoModelForCausalLM
         model = AutoModelForCausalLM.from_pretrained(a.model)
     model.to(a.device).eval()
-    cfg = DistillationConfig(n_experts=a.n_experts, moe_top_k=a.top_k, data_free=True, data_free_steps=a.steps,
+    dff = None if a.d_ff_expert is None else (int(a.d_ff_expert) if a.d_ff_expert > 4 else float(a.d_ff_expert))
+    cfg = DistillationConfig(n_experts=a.n_experts, moe_top_k=a.top_k, moe_routing=a.routing, d_ff_expert=dff,
+                             layer_config_path=a.layer_config, data_free=a.mode == "data_free",
+                             sequential_layers=a.mode == "sequential", empirical_routing=a.mode == "empirical",
+                             dynamic_experts=a.mode == "dynamic", router_mlp=a.router_mlp,
+                             use_expert_bias=not a.no_expert_bias, data_free_steps=a.steps,
                              data_free_seq_len=64, cluster_samples=2048, router_train_steps=min(200, a.steps),
-                             log_interval=0, learning_rate=1e-3)
+                             reallocate_every_n_steps=max(a.steps // 4, 1), min_d_ff=16,
+                             log_interval=0, learning_rate=a.lr)
     trainer = SparseDistillationTrainer(model, cfg, device=a.device)
     if a.analyze_clusters:
         analysis = {str(i): {str(k): v for k, v in trainer.analyze_cluster_quality(i, ks=(4, 8)).items()}
                     for i in range(len(trainer.ffn))}
         json.dump(analysis, open(os.path.join(a.output_dir, "cluster_analysis.json"), "w"), indent=2)
-    hist = trainer.distill(steps=a.steps)
+    batches = None
+    if a.mode in ("parallel", "sequential"):
+        vocab = 256 if a.model == "toy" else model.config.vocab_size
+        g = torch.Generator().manual_seed(0)
+        batches = [torch.randint(0, vocab, (2, 64), generator=g) for _ in range(a.steps)]
+    hist = trainer.distill(batches, steps=a.steps)
     ev = trainer.evaluate(2)
     trainer.save(os.path.join(a.output_dir, "distilled_moe.pt"))
     sparse = convert_to_sparse(model, trainer=trainer)
