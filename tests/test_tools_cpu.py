@@ -1,0 +1,127 @@
+"""The evaluation, analysis and diagnosis command lines run end to end on CPU on a tiny model."""
+import json
+import os
+import sys
+
+import pytest
+import torch
+import yaml
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+@pytest.fixture(scope="module")
+def tiny(tmp_path_factory):
+    """A small YAML config (same schema as configs/*.yaml) and a checkpoint of a model built from it."""
+    d = tmp_path_factory.mktemp("tools")
+    cfg = yaml.safe_load(open(os.path.join(ROOT, "configs", "test.yaml")))
+    cfg["model"].update(d_model=64, d_ff=128, d_ff_expert=64, head_dim=16, n_heads=4, n_kv_heads=2,
+                        max_seq_len=64, vocab_size=300, moe_layers=[1, 2, 3])
+    cfg_path = str(d / "tiny.yaml")
+    yaml.safe_dump(cfg, open(cfg_path, "w"))
+    from kolmogorov_moe_architecture_b200 import MoETransformer
+    from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml, model_config_tolerant
+    torch.manual_seed(0)
+    model = MoETransformer(model_config_tolerant(load_yaml(cfg_path)), verbose=False)
+    ck_path = str(d / "ck.pt")
+    torch.save({"model_state_dict": model.state_dict(), "global_step": 3, "tokens_seen": 123}, ck_path)
+    return {"dir": str(d), "config": cfg_path, "checkpoint": ck_path}
+
+
+def test_evaluate_perplexity_synthetic(tiny):
+    from eval import evaluate_perplexity as ev
+    out = os.path.join(tiny["dir"], "results.md")
+    ev.main(["--checkpoint", tiny["checkpoint"], "--config", tiny["config"], "--device", "cpu", "--synthetic",
+             "--tokens", "2000", "--seq-len", "32", "--stride", "16", "--output", out])
+    assert os.path.exists(out) and os.path.exists(out.replace(".md", ".json"))
+    res = json.load(open(out.replace(".md", ".json")))
+    text = json.dumps(res)
+    assert "perplexity" in text
+    # strided windows cover the stream with the requested overlap
+    w = ev.windows(list(range(100)), 32, 16)
+    assert all(len(x) == 32 for x in w) and w[1][0] == 16
+
+
+def test_diagnose_training_reports_every_section(tiny):
+    from tools import diagnose_training as dt
+    rep = dt.main(["--checkpoint", tiny["checkpoint"], "--config", tiny["config"], "--device", "cpu", "--synthetic",
+                   "--eval-batches", "2"])
+    assert set(rep) >= {"router", "routing_in_model", "movement", "trainability", "evaluation", "gradients", "verdict"}
+    assert rep["trainability"]["trainable"] == rep["trainability"]["total"]
+    assert abs(rep["evaluation"]["lm_loss"] - rep["evaluation"]["uniform_loss"]) < 1.0   # untrained model
+    assert rep["routing_in_model"] and all(0.0 <= s["gini"] <= 1.0 for s in rep["routing_in_model"].values())
+    # the checkpoint is the seed-0 initialisation itself: nothing has moved
+    assert max(rep["movement"].values()) < 1e-6
+    assert any("did not move" in line for line in rep["verdict"])
+    assert dt.calculate_gini([1, 1, 1, 1]) == 0.0 and dt.calculate_gini([0, 0, 0, 8]) == 0.75
+
+
+def test_reallocate_experts_copies_w123_and_resets_routers(tiny):
+    """A layer whose router has collapsed gets its experts from a healthy layer (the stacked w1/w2/w3 tensors
+    are what is copied) and every router is re-initialised; the optimizer state is dropped."""
+    from tools import reallocate_experts as re_
+    from eval.evaluate_perplexity import load_model
+    model, _ = load_model(tiny["checkpoint"], tiny["config"], "cpu", dtype=torch.float32)
+    moe_layers = [i for i, l in enumerate(model.layers) if hasattr(l.ffn, "grouped_experts")]
+    assert len(moe_layers) >= 2
+    sick = model.layers[moe_layers[0]].ffn
+    with torch.no_grad():                                      # collapse: every token prefers expert 0
+        last = sick.router.router[2].weight
+        last.zero_()
+        last[0].fill_(5.0)
+        sick.router.router[0].weight.normal_(0.0, 1.0)       # large hidden activations: silu ~ relu >= 0
+    bad_ck = os.path.join(tiny["dir"], "collapsed.pt")
+    torch.save({"model_state_dict": model.state_dict(), "optimizer_state_dict": {"x": 1}}, bad_ck)
+    out = os.path.join(tiny["dir"], "reallocated.pt")
+    info = re_.reallocate_experts(bad_ck, tiny["config"], out, "cpu")
+    assert moe_layers[0] in info["collapsed"] and info["source"] in info["healthy"]
+    ck = torch.load(out, map_location="cpu", weights_only=False)
+    assert "optimizer_state_dict" not in ck
+    sd = ck["model_state_dict"]
+    a, b = f"layers.{moe_layers[0]}.ffn.grouped_experts.w1", f"layers.{info['source']}.ffn.grouped_experts.w1"
+    assert torch.equal(sd[a], sd[b])
+    assert not torch.equal(sd[f"layers.{moe_layers[0]}.ffn.router.router.2.weight"], last)
+
+
+def test_param_calculator_matches_the_model(tiny):
+    from tools import param_calculator as pc
+    from kolmogorov_moe_architecture_b200 import MoETransformer
+    from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml, model_config_tolerant
+    cfg = model_config_tolerant(load_yaml(tiny["config"]))
+    r = pc.analyze(cfg, world=2)
+    n = sum(p.numel() for p in MoETransformer(cfg, verbose=False).parameters())
+    total = next(v for k, v in r.items() if "total" in k and isinstance(v, (int, float)))
+    assert abs(total - n) <= 0.02 * n, (total, n)
+    found = pc.design(5e9, 1.5e9, tol=0.3, limit=3)
+    assert isinstance(found, list)
+
+
+def test_plateau_memory_debug_and_active_param_tools(tiny, capsys):
+    import analyze_active_params
+    import check_memory
+    import debug_training
+    import diagnose_memory
+    import diagnose_plateau
+    rep = diagnose_plateau.main(["--config", tiny["config"], "--checkpoint", tiny["checkpoint"], "--device", "cpu",
+                                 "--batches", "2"])
+    assert rep, "router hooks recorded nothing"
+    rows = check_memory.main(["--config", tiny["config"], "--seq-len", "32"])
+    assert [r[0] for r in rows][:2] == ["start", "model"] and len(rows) >= 6
+    assert diagnose_memory.main(["--config", tiny["config"], "--seq-len", "32"])
+    info = debug_training.inspect(tiny["checkpoint"], top=3)
+    assert info["non_finite"] == [] and info["n_tensors"] > 10 and info["meta"]["global_step"] == 3
+    analyze_active_params.main(["--preset", "test"])
+    assert "active" in capsys.readouterr().out.lower()
+
+
+def test_expert_choice_scatter_benchmark_variants_agree():
+    from tools import benchmark_expert_choice as bec
+    torch.manual_seed(0)
+    B, E, C, S, d = 2, 3, 4, 10, 8
+    w_out = torch.randn(B, E, C, d)
+    idx = torch.randint(0, S, (B, E, C))
+    a = bec.scatter_loop(torch.zeros(B, S, d), w_out, idx)
+    b = bec.scatter_vectorised(torch.zeros(B, S, d), w_out, idx)
+    assert torch.allclose(a, b, atol=1e-6)
+    bec.main(["--device", "cpu"])

@@ -43,6 +43,101 @@ def gradient_flow(model, ids) -> dict:
     return gradient_census(model)
 
 
+def calculate_gini(values) -> float:
+    """Gini coefficient of non-negative values (0 = all equal, -> 1 = one holds everything)."""
+    v = torch.as_tensor(values, dtype=torch.float64).flatten().clamp(min=0).sort().values
+    n, tot = v.numel(), float(v.sum())
+    if n == 0 or tot == 0:
+        return 0.0
+    idx = torch.arange(1, n + 1, dtype=torch.float64)
+    return float(((2 * idx - n - 1) * v).sum() / (n * tot))
+
+
+@torch.no_grad()
+def analyze_router_collapse(model, n_samples: int = 8, seq_len: int = 64, device: str = "cpu", generator=None) -> dict:
+    """Expert usage through the WHOLE model on token batches (``check_router_collapse`` probes each router
+    alone with random hidden states): per MoE layer the usage entropy, Gini, dead experts and the share of
+    the busiest expert, from the counts each layer records in its forward pass
+    (reference: tools/diagnose_training.py:113-233)."""
+    import math
+    cfg = model.config
+    was = model.training
+    model.eval()
+    totals = {}
+    for _ in range(n_samples):
+        ids = torch.randint(0, cfg.vocab_size, (1, min(seq_len, cfg.max_seq_len)), generator=generator).to(device)
+        model(ids, return_logits=False)
+        for i, layer in enumerate(model.layers):
+            c = getattr(getattr(layer, "ffn", None), "last_expert_counts", None)
+            if c is None:
+                c = getattr(getattr(getattr(layer, "ffn", None), "expert_parallel_layer", None), "last_expert_counts", None)
+            if c is not None:
+                totals[i] = totals.get(i, 0) + c.detach().float().cpu()
+    if was:
+        model.train()
+    out = {}
+    for i, c in totals.items():
+        u = c / c.sum().clamp(min=1)
+        E = u.numel()
+        ent = float(-(u * torch.log(u + 1e-10)).sum()) / (math.log(E) if E > 1 else 1.0)
+        out[i] = {"entropy": ent, "gini": calculate_gini(c), "dead_experts": int((c == 0).sum()),
+                  "max_usage": float(u.max()), "is_collapsed": ent < 0.7 or float(u.max()) > 0.5}
+    return out
+
+
+@torch.no_grad()
+def run_evaluation(model, cfg, n_batches: int = 8, device: str = "cpu", data: str = None, batch_size: int = 2,
+                   seq_len: int = None) -> dict:
+    """Mean loss / perplexity of head 0 (next token) and of the full multi-token objective over batches from a
+    uint16 token file, or over random tokens when there is none - where a trained model should sit near
+    ln(vocab) and a broken one far above (reference: tools/diagnose_training.py:354-467)."""
+    import math
+    import numpy as np
+    S = seq_len or min(256, cfg.max_seq_len)
+    g = torch.Generator().manual_seed(0)
+    arr = np.memmap(data, dtype=np.uint16, mode="r") if data else None
+    was = model.training
+    model.eval()
+    tot, lm, n = 0.0, 0.0, 0
+    for _ in range(n_batches):
+        if arr is not None:
+            starts = torch.randint(0, len(arr) - S - 1, (batch_size,), generator=g).tolist()
+            ids = torch.stack([torch.from_numpy(np.asarray(arr[s: s + S], dtype=np.int64)) for s in starts])
+        else:
+            ids = torch.randint(0, cfg.vocab_size, (batch_size, S), generator=g)
+        ids = ids.to(device)
+        out = model(ids, labels=ids, return_logits=False)
+        tot += float(out["loss"])
+        lm += float(out.get("lm_loss", out["loss"]))
+        n += 1
+    if was:
+        model.train()
+    mean = lm / max(n, 1)
+    return {"loss": tot / max(n, 1), "lm_loss": mean, "perplexity": math.exp(min(mean, 50.0)),
+            "uniform_loss": math.log(cfg.vocab_size), "batches": n, "source": data or "random tokens"}
+
+
+def verdict(report: dict) -> list:
+    """Plain-language findings from the collected figures."""
+    issues = []
+    bad = [i for i, s in report.get("routing_in_model", {}).items() if s["is_collapsed"]]
+    if report.get("collapsed") or bad:
+        issues.append(f"router collapse in layers {sorted(set(list(report.get('collapsed', [])) + bad))}")
+    still = [k for k, v in report.get("movement", {}).items() if v < 1e-4]
+    if still:
+        issues.append(f"{len(still)} components did not move from their initialisation: {still[:5]}")
+    tr = report.get("trainability", {})
+    if tr and tr["trainable"] < tr["total"]:
+        issues.append(f"{tr['total'] - tr['trainable']:,} parameters are frozen")
+    ev = report.get("evaluation")
+    if ev and ev["lm_loss"] > ev["uniform_loss"] * 1.05 and ev["source"] != "random tokens":
+        issues.append(f"loss on data {ev['lm_loss']:.3f} is above the uniform-prediction loss {ev['uniform_loss']:.3f}")
+    for k, v in report.get("gradients", {}).items():
+        if isinstance(v, dict) and (v.get("nan_or_inf", 0) or v.get("no_grad", 0)):
+            issues.append(f"gradients of '{k}': {v.get('nan_or_inf', 0)} non-finite, {v.get('no_grad', 0)} missing")
+    return issues or ["no problem found"]
+
+
 @torch.no_grad()
 def greedy_sample(model, prompt_ids, n: int = 20):
     model.eval()
@@ -59,6 +154,8 @@ def main(argv=None):
     ap.add_argument("--config", required=True)
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--synthetic", action="store_true")
+    ap.add_argument("--data", default=None, help="uint16 token file for the evaluation pass")
+    ap.add_argument("--eval-batches", type=int, default=8)
     a = ap.parse_args(argv)
     from eval.evaluate_perplexity import load_model
     from kolmogorov_moe_architecture_b200.utils.fault import check_router_collapse
@@ -67,15 +164,26 @@ def main(argv=None):
     print("[router]", summary)
     for i, s in stats.items():
         print(f"  layer {i}: entropy {s['entropy']:.3f} max_usage {s['max_usage']:.3f}")
+    in_model = analyze_router_collapse(model, device=a.device)
+    for i, s in in_model.items():
+        print(f"  layer {i} (through the model): entropy {s['entropy']:.3f} gini {s['gini']:.3f} dead {s['dead_experts']}")
     mv = parameter_movement(model, cfg)
     print("[movement] least moved:", sorted(mv.items(), key=lambda kv: kv[1])[:5])
     tr = trainability(model)
     print(f"[trainable] {tr['trainable']:,} of {tr['total']:,}; frozen tensors: {len(tr['frozen_tensors'])}")
+    ev = run_evaluation(model, cfg, a.eval_batches, a.device, None if a.synthetic else a.data)
+    print(f"[eval] {ev['source']}: loss {ev['lm_loss']:.4f} (uniform {ev['uniform_loss']:.4f}) ppl {ev['perplexity']:.1f}")
     ids = torch.randint(0, cfg.vocab_size, (2, min(64, cfg.max_seq_len)), device=a.device)
-    for k, v in gradient_flow(model, ids).items():
+    grads = gradient_flow(model, ids)
+    for k, v in grads.items():
         print(f"[grad] {k}: {v}")
     print("[sample]", greedy_sample(model, ids[:1, :8], 12)[0].tolist())
-    return {"router": stats, "collapsed": collapsed, "movement": mv, "trainability": tr}
+    report = {"router": stats, "collapsed": collapsed, "routing_in_model": in_model, "movement": mv,
+              "trainability": tr, "evaluation": ev, "gradients": grads}
+    report["verdict"] = verdict(report)
+    for line in report["verdict"]:
+        print("[verdict]", line)
+    return report
 
 
 if __name__ == "__main__":
