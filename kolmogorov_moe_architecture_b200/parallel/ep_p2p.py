@@ -42,7 +42,7 @@ from typing import Dict, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-from .p2p import _group_name, peer_ptrs
+from .p2p import _group_name, enable_group, peer_ptrs
 
 
 def _round_up(x: int, m: int) -> int:
@@ -68,11 +68,7 @@ class EPBuffers:
         self.max_rows_src = _round_up(T * k + E * 127, 128)
         self.max_rows_exp = _round_up(min(n_slots * self.cap, self.world * T * k) + self.n_local * 127, 128)
         name = _group_name(group)
-        if hasattr(symm, "enable_symm_mem_for_group"):
-            try:
-                symm.enable_symm_mem_for_group(name)
-            except Exception:
-                pass
+        enable_group(name)
         self.recv = symm.empty((n_slots * self.cap, d), dtype=dtype, device=device)
         self.ret = symm.empty((self.max_rows_src, d), dtype=dtype, device=device)
         self.meta = symm.empty(n_slots * 2, dtype=torch.int32, device=device)

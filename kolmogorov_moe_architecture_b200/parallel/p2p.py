@@ -34,6 +34,20 @@ def _group_name(group) -> str:
     return g.group_name
 
 
+def enable_group(name: str) -> None:
+    """Older releases of the symmetric-memory module want a group registered before its first allocation;
+    newer ones do it themselves and only warn about the call."""
+    import warnings
+    import torch.distributed._symmetric_memory as symm
+    if hasattr(symm, "enable_symm_mem_for_group"):
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            try:
+                symm.enable_symm_mem_for_group(name)
+            except Exception:
+                pass
+
+
 def _delta(handle, tensor, rank: int) -> int:
     """Byte offset of ``tensor`` inside its symmetric allocation (the allocator may sub-allocate)."""
     return int(tensor.data_ptr()) - int(handle.buffer_ptrs[rank])
@@ -64,11 +78,7 @@ class SymmetricBuffers:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         name = _group_name(group)
-        if hasattr(symm, "enable_symm_mem_for_group"):
-            try:
-                symm.enable_symm_mem_for_group(name)
-            except Exception:
-                pass
+        enable_group(name)
         self.param = symm.empty(total, dtype=dtype, device=device)
         self.grad = symm.empty(total, dtype=dtype, device=device)
         self.flags = symm.empty(64, dtype=torch.int32, device=device)
