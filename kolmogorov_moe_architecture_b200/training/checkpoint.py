@@ -18,13 +18,17 @@ Formats (all hold the model under the key schema of the reference, so files inte
 prefixed by ``_orig_mod.`` / ``module.`` / ``model.``).  ``save_sharded`` writes one
 optimizer-state file per rank next to a single model file, all ranks taking part, so no
 rank skips a collective (the reference's format-C writer returns early on non-main ranks
-before a collective gather, train_custom.py:780-781).
+before a collective gather, train_custom.py:780-781).  With an ``AsyncCheckpointWriter`` the
+sharded saves only copy the state to pinned host memory on the training thread; files are written
+in the background and a checkpoint directory becomes valid when every rank's marker is in it.
 """
 from __future__ import annotations
 
+import copy
 import os
 import re
 import shutil
+import threading
 from typing import Any, Dict, Optional
 
 import torch
@@ -119,11 +123,15 @@ def save_format_c(root, step, model, optimizer, training_state: Dict, keep: int 
     return d
 
 
-def prune_checkpoints(root: str, keep: int = 3) -> None:
+def prune_checkpoints(root: str, keep: int = 3, world: Optional[int] = None) -> None:
+    """Keep the newest ``keep`` checkpoint directories.  With ``world`` (background saves) only complete
+    directories count towards ``keep`` and incomplete ones are left alone: another rank may still be
+    writing into them."""
     ds = []
     for name in os.listdir(root):
         m = re.fullmatch(r"checkpoint-(\d+)", name)
-        if m and os.path.isdir(os.path.join(root, name)):
+        d = os.path.join(root, name)
+        if m and os.path.isdir(d) and (world is None or checkpoint_complete(d, world)):
             ds.append((int(m.group(1)), name))
     for _, name in sorted(ds)[:-keep] if keep > 0 else []:
         shutil.rmtree(os.path.join(root, name), ignore_errors=True)
@@ -140,16 +148,24 @@ def load_format_c(d: str, model, optimizer=None, map_location="cpu") -> Dict:
 
 
 # ---------------------------------------------------------- sharded (ZeRO) save
-def save_sharded(root: str, step: int, model, dp, training_state: Dict, rank: int, keep: int = 3) -> str:
+def save_sharded(root: str, step: int, model, dp, training_state: Dict, rank: int, keep: int = 3,
+                 writer: Optional["AsyncCheckpointWriter"] = None, world: Optional[int] = None) -> str:
     """Rank 0 writes ``model.pt`` (parameters are replicated) and ``training_state.pt``; every rank
-    writes ``optimizer-rank{r}.pt`` with the state of the tensors it owns."""
+    writes ``optimizer-rank{r}.pt`` with the state of the tensors it owns.  ``writer``: write in the
+    background (no barrier; the directory is valid once all ``world`` markers exist)."""
     import torch.distributed as dist
     d = os.path.join(root, f"checkpoint-{step}")
     os.makedirs(d, exist_ok=True)
+    files: Dict[str, Any] = {os.path.join(d, f"optimizer-rank{rank}.pt"): dp.optimizer_state_dict()}
     if rank == 0:
-        _atomic_save(unwrap_model(model).state_dict(), os.path.join(d, "model.pt"))
-        _atomic_save(training_state, os.path.join(d, "training_state.pt"))
-    _atomic_save(dp.optimizer_state_dict(), os.path.join(d, f"optimizer-rank{rank}.pt"))
+        files[os.path.join(d, "model.pt")] = unwrap_model(model).state_dict()
+        files[os.path.join(d, "training_state.pt")] = training_state
+    if writer is not None:
+        w = world or (dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1)
+        writer.submit(files, d, rank, then=(lambda: prune_checkpoints(root, keep, world=w)) if rank == 0 else None)
+        return d
+    for path, obj in files.items():
+        _atomic_save(obj, path)
     if dist.is_available() and dist.is_initialized():
         dist.barrier()
     if rank == 0:
@@ -167,17 +183,25 @@ def load_sharded(d: str, model, dp, rank: int, map_location="cpu") -> Dict:
     return torch.load(ts, map_location=map_location, weights_only=False) if os.path.exists(ts) else {}
 
 
-def save_param_sharded(root: str, step: int, plan, training_state: Dict, rank: int, keep: int = 3) -> str:
+def save_param_sharded(root: str, step: int, plan, training_state: Dict, rank: int, keep: int = 3,
+                       writer: Optional["AsyncCheckpointWriter"] = None) -> str:
     """Checkpoint of the parameter-sharded plan: every rank helps gather the full parameters (rank 0
-    writes them as an ordinary ``model.pt``) and writes its own shards with their AdamW moments."""
+    writes them as an ordinary ``model.pt``) and writes its own shards with their AdamW moments.
+    ``writer``: the files are written in the background (the gather itself stays collective)."""
     import torch.distributed as dist
     d = os.path.join(root, f"checkpoint-{step}")
     os.makedirs(d, exist_ok=True)
     full = plan.full_state_dict(to_cpu=True)
+    files: Dict[str, Any] = {os.path.join(d, f"shards-rank{rank}.pt"): plan.shard_state_dict()}
     if rank == 0:
-        _atomic_save(full, os.path.join(d, "model.pt"))
-        _atomic_save(training_state, os.path.join(d, "training_state.pt"))
-    _atomic_save(plan.shard_state_dict(), os.path.join(d, f"shards-rank{rank}.pt"))
+        files[os.path.join(d, "model.pt")] = full
+        files[os.path.join(d, "training_state.pt")] = training_state
+    if writer is not None:
+        writer.submit(files, d, rank,
+                      then=(lambda: prune_checkpoints(root, keep, world=plan.world)) if rank == 0 else None)
+        return d
+    for path, obj in files.items():
+        _atomic_save(obj, path)
     if dist.is_available() and dist.is_initialized():
         dist.barrier()
     if rank == 0:
@@ -199,6 +223,86 @@ def load_param_sharded(d: str, plan, rank: int) -> Dict:
         plan.load_full_state_dict(torch.load(os.path.join(d, "model.pt"), map_location="cpu", weights_only=False))
     ts = os.path.join(d, "training_state.pt")
     return torch.load(ts, map_location="cpu", weights_only=False) if os.path.exists(ts) else {}
+
+
+def snapshot_to_host(obj):
+    """Deep copy of a (nested) state object with every tensor on the host.  Device tensors are copied
+    into pinned memory without blocking the host; the caller synchronises once before reading them."""
+    if torch.is_tensor(obj):
+        if obj.device.type == "cuda":
+            dst = torch.empty(obj.shape, dtype=obj.dtype, device="cpu", pin_memory=True)
+            dst.copy_(obj.detach(), non_blocking=True)
+            return dst
+        return obj.detach().clone()
+    if isinstance(obj, dict):
+        return type(obj)((k, snapshot_to_host(v)) for k, v in obj.items())
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(snapshot_to_host(v) for v in obj)
+    return copy.deepcopy(obj)
+
+
+class AsyncCheckpointWriter:
+    """Checkpoint files written off the training thread.
+
+    ``submit`` copies the state to (pinned) host memory - the only part the training loop waits for, one
+    device-to-host pass - and a background thread serialises it, each file through a temporary name, and
+    finally drops a ``complete-rank{r}`` marker into the checkpoint directory.  A directory counts as a
+    checkpoint only when every rank's marker is there (``checkpoint_complete``), so a job killed in the
+    middle of a save resumes from the previous one.  One save is in flight at a time: a second ``submit``
+    first waits for the first.  An error in the writer thread is raised by the next ``submit`` / ``wait``."""
+
+    def __init__(self):
+        self._thread: Optional[threading.Thread] = None
+        self._error: Optional[BaseException] = None
+
+    def wait(self) -> None:
+        if self._thread is not None:
+            self._thread.join()
+            self._thread = None
+        if self._error is not None:
+            e, self._error = self._error, None
+            raise RuntimeError(f"asynchronous checkpoint write failed: {e!r}") from e
+
+    def submit(self, files: Dict[str, Any], directory: str, rank: int, then=None) -> None:
+        """``files``: path -> state object.  ``then`` runs in the writer thread after the marker exists."""
+        self.wait()
+        host = {path: snapshot_to_host(obj) for path, obj in files.items()}
+        if torch.cuda.is_available():
+            torch.cuda.current_stream().synchronize()
+
+        def run():
+            try:
+                for path, obj in host.items():
+                    _atomic_save(obj, path)
+                with open(os.path.join(directory, f"complete-rank{rank}"), "w") as f:
+                    f.write("ok")
+                if then is not None:
+                    then()
+            except BaseException as e:       # surfaced by wait()
+                self._error = e
+
+        self._thread = threading.Thread(target=run, daemon=False)
+        self._thread.start()
+
+
+def checkpoint_complete(d: str, world: int) -> bool:
+    """Every rank finished writing into ``d`` (directories written synchronously carry no markers and
+    count as complete once ``training_state.pt`` exists)."""
+    marks = [n for n in os.listdir(d) if n.startswith("complete-rank")] if os.path.isdir(d) else []
+    if marks:
+        return all(os.path.exists(os.path.join(d, f"complete-rank{r}")) for r in range(world))
+    return os.path.exists(os.path.join(d, "training_state.pt"))
+
+
+def latest_complete_checkpoint(root: str, world: int = 1) -> Optional[str]:
+    best = None
+    if os.path.isdir(root):
+        for name in os.listdir(root):
+            m = re.fullmatch(r"checkpoint-(\d+)", name)
+            d = os.path.join(root, name)
+            if m and checkpoint_complete(d, world) and (best is None or int(m.group(1)) > best[0]):
+                best = (int(m.group(1)), d)
+    return best[1] if best else None
 
 
 def _atomic_save(obj, path: str) -> None:

@@ -81,6 +81,7 @@ class RunSpec:
     jsonl: Optional[str] = None
     shard_params: bool = False             # ZeRO-3 / FULL_SHARD plan (AdamW) instead of replicated parameters
     cpu_offload: bool = False              # with shard_params: shards and optimizer state in pinned host memory
+    async_checkpoint: bool = False         # sharded saves: copy to pinned memory, write files in the background
     extra: Dict[str, Any] = field(default_factory=dict)
 
 
@@ -247,6 +248,12 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
     amp = torch.bfloat16 if (spec.weights == "fp32_autocast" and use_cuda) else None
     engine = TrainEngine(model, optimizer, sched, train_cfg["gradient_clip_norm"], accum, amp, dp, device)
     engine.global_step, engine.tokens_seen = start_step, tokens_seen
+    if resume and os.path.isdir(resume) and not os.path.exists(os.path.join(resume, "model.pt")):
+        # a checkpoint root: continue from the newest directory that every rank finished writing
+        found = ckpt.latest_complete_checkpoint(resume, world)
+        if found is None:
+            raise FileNotFoundError(f"no complete checkpoint under {resume}")
+        resume = found
     if resume and os.path.isdir(resume):
         if spec.shard_params:
             st = ckpt.load_param_sharded(resume, dp, rank)
@@ -270,12 +277,14 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
         print(f"training: {total_steps} steps, {tokens_per_step:,} tokens/step, data={data_kind}, world={world}, "
               f"ep={cfg.ep_size}, weights={spec.weights}")
 
+    writer = ckpt.AsyncCheckpointWriter() if spec.async_checkpoint else None
+
     def save(step: int, suffix: Optional[str] = None):
         state = {"step": step, "tokens_seen": engine.tokens_seen, "config_path": spec.config_path}
         if spec.shard_params:
-            ckpt.save_param_sharded(cdir, step, dp, state, rank)
+            ckpt.save_param_sharded(cdir, step, dp, state, rank, writer=writer)
         elif dp is not None:
-            ckpt.save_sharded(cdir, step, model, dp.pools[0], state, rank)
+            ckpt.save_sharded(cdir, step, model, dp.pools[0], state, rank, writer=writer, world=world)
         elif spec.checkpoint_format == "C":
             ckpt.save_format_c(cdir, step, model, optimizer, state)
         else:
@@ -340,6 +349,8 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
                 break
         else:
             save(step, "final")
+    if writer is not None:
+        writer.wait()                          # the last save must be on disk before the job reports success
     if dog is not None:
         dog.stop()
     logger.close()

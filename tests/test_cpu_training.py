@@ -203,3 +203,42 @@ def test_threaded_prefetcher_yields_batches_on_the_device_in_order():
     got = list(ThreadedPrefetcher(batches, "cpu", buffer_size=2))
     assert [b["n"] for b in got] == list(range(7))
     assert all(torch.equal(b["input_ids"], torch.full((2, 4), b["n"])) for b in got)
+
+
+def test_async_checkpoint_writer_markers_pruning_and_errors(tmp_path):
+    """Background sharded saves: the state is snapshotted at submit time, a directory is a checkpoint only
+    when every rank's marker is in it, pruning ignores incomplete directories, writer errors surface."""
+    from kolmogorov_moe_architecture_b200.training import checkpoint as ck
+
+    class FakePlan:                      # what save_sharded needs from a data-parallel plan
+        def __init__(self, v):
+            self.t = torch.full((4,), float(v))
+
+        def optimizer_state_dict(self):
+            return {"m": self.t}
+
+    root = str(tmp_path)
+    model = torch.nn.Linear(3, 2)
+    w0, w1 = ck.AsyncCheckpointWriter(), ck.AsyncCheckpointWriter()
+    for step in (10, 20, 30):
+        plan0, plan1 = FakePlan(step), FakePlan(step + 1)
+        d = ck.save_sharded(root, step, model, plan0, {"step": step}, rank=0, keep=2, writer=w0, world=2)
+        plan0.t.zero_()                  # training goes on: the file must hold the value at submit time
+        w0.wait()
+        assert not ck.checkpoint_complete(d, 2)
+        if step < 30:                    # rank 1 never finishes the last one
+            ck.save_sharded(root, step, model, plan1, {"step": step}, rank=1, keep=2, writer=w1, world=2)
+            w1.wait()
+            assert ck.checkpoint_complete(d, 2)
+        assert torch.equal(torch.load(os.path.join(d, "optimizer-rank0.pt"))["m"], torch.full((4,), float(step)))
+    assert ck.latest_complete_checkpoint(root, 2).endswith("checkpoint-20")
+    ck.prune_checkpoints(root, keep=1, world=2)
+    left = sorted(n for n in os.listdir(root) if n.startswith("checkpoint-"))
+    assert left == ["checkpoint-20", "checkpoint-30"]           # 10 pruned, incomplete 30 left alone
+    st = ck.load_sharded(os.path.join(root, "checkpoint-20"), torch.nn.Linear(3, 2),
+                         type("P", (), {"load_optimizer_state_dict": lambda self, sd: None})(), rank=0)
+    assert st["step"] == 20
+    bad = ck.AsyncCheckpointWriter()
+    bad.submit({os.path.join(root, "x.pt"): {"f": lambda: 0}}, root, 0)      # a lambda cannot be pickled
+    with pytest.raises(RuntimeError, match="asynchronous checkpoint write failed"):
+        bad.wait()

@@ -1,0 +1,99 @@
+"""Every training entry point runs a few steps on CPU from a YAML config, writes the checkpoint layout its
+counterpart in the reference writes, and resumes from it."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+import yaml
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+@pytest.fixture(scope="module")
+def tiny_cfg(tmp_path_factory):
+    d = tmp_path_factory.mktemp("entry")
+    cfg = yaml.safe_load(open(os.path.join(ROOT, "configs", "test.yaml")))
+    cfg["model"].update(d_model=64, d_ff=128, d_ff_expert=64, head_dim=16, n_heads=4, n_kv_heads=2,
+                        max_seq_len=32, vocab_size=300)
+    cfg["training"].update(checkpoint_dir=str(d / "from_yaml"), save_interval=2, log_interval=1,
+                           gradient_accumulation_steps=1, batch_size=2)
+    path = str(d / "tiny.yaml")
+    yaml.safe_dump(cfg, open(path, "w"))
+    return {"dir": str(d), "config": path}
+
+
+def test_train_py_format_b_checkpoints_and_resume(tiny_cfg):
+    import train
+    ck = os.path.join(tiny_cfg["dir"], "b")
+    out = train.main(["--config", tiny_cfg["config"], "--steps", "4", "--batch-size", "2", "--seq-len", "32",
+                      "--grad-accum", "1", "--synthetic", "--checkpoint-dir", ck, "--save-interval", "2"])
+    assert out["steps"] == 4 and out["final_loss"] is not None
+    files = sorted(os.listdir(os.path.join(ck, "tiny")))
+    assert files == ["checkpoint-2.pt", "checkpoint-4-final.pt"]
+    sd = torch.load(os.path.join(ck, "tiny", "checkpoint-2.pt"), map_location="cpu", weights_only=False)
+    assert {"step", "model_state_dict", "optimizer_state_dict", "total_tokens", "config_path"} <= set(sd)
+    assert isinstance(sd["optimizer_state_dict"], list) and len(sd["optimizer_state_dict"]) == 2   # Muon + AdamW
+    out2 = train.main(["--config", tiny_cfg["config"], "--steps", "5", "--batch-size", "2", "--seq-len", "32",
+                       "--grad-accum", "1", "--synthetic", "--checkpoint-dir", ck, "--save-interval", "0",
+                       "--resume", os.path.join(ck, "tiny", "checkpoint-2.pt")])
+    assert out2["steps"] == 5
+
+
+def test_train_custom_format_c_and_scripts_train_format_a(tiny_cfg):
+    import train_custom
+    ck = os.path.join(tiny_cfg["dir"], "c")
+    out = train_custom.main(["--config", tiny_cfg["config"], "--steps", "4", "--batch-size", "2", "--synthetic",
+                             "--checkpoint-dir", ck])
+    assert out["steps"] == 4
+    dirs = sorted(n for n in os.listdir(ck) if n.startswith("checkpoint-"))
+    assert dirs and set(os.listdir(os.path.join(ck, dirs[-1]))) >= {"model.pt", "optimizer.pt", "training_state.pt"}
+    out = train_custom.main(["--config", tiny_cfg["config"], "--steps", "5", "--batch-size", "2", "--synthetic",
+                             "--checkpoint-dir", ck, "--resume", os.path.join(ck, dirs[-1])])
+    assert out["steps"] == 5
+    sys.path.insert(0, os.path.join(ROOT, "scripts"))
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("scripts_train", os.path.join(ROOT, "scripts", "train.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.main(["--config", tiny_cfg["config"], "--max_steps", "3", "--device", "cpu", "--synthetic"])
+
+
+def test_train_production_native_fallback(tiny_cfg):
+    import train_production
+    out = train_production.main(["--config", tiny_cfg["config"], "--max_steps", "3", "--synthetic",
+                                 "--output_dir", os.path.join(tiny_cfg["dir"], "hf")])
+    assert out is None or out.get("steps", 3) == 3
+
+
+def _torchrun(args, port):
+    env = dict(os.environ, PYTHONPATH=ROOT, KMOE_OFFLINE="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port),
+                        os.path.join(ROOT, "train_distributed.py")] + args,
+                       env=env, capture_output=True, text=True, timeout=900, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    return r.stdout
+
+
+@pytest.mark.parametrize("sharded", [False, True])
+def test_train_distributed_two_ranks_background_checkpoints_and_resume(tiny_cfg, sharded):
+    """Two gloo ranks: replicated-parameter plan and parameter-sharded plan, checkpoints written in the
+    background with completion markers, then a second launch that resumes from the checkpoint root."""
+    ck = os.path.join(tiny_cfg["dir"], "dist_sharded" if sharded else "dist")
+    extra = ["--shard-params"] if sharded else []
+    out = _torchrun(["--config", tiny_cfg["config"], "--steps", "4", "--synthetic", "--checkpoint-dir", ck,
+                     "--async-checkpoint"] + extra, 29711 + int(sharded))
+    assert "Step 4/4" in out
+    from kolmogorov_moe_architecture_b200.training import checkpoint as ckpt
+    last = ckpt.latest_complete_checkpoint(ck, world=2)
+    assert last is not None and last.endswith("checkpoint-4")
+    names = set(os.listdir(last))
+    per_rank = "shards-rank{}.pt" if sharded else "optimizer-rank{}.pt"
+    assert {"model.pt", "training_state.pt", "complete-rank0", "complete-rank1",
+            per_rank.format(0), per_rank.format(1)} <= names
+    out = _torchrun(["--config", tiny_cfg["config"], "--steps", "6", "--synthetic", "--checkpoint-dir", ck,
+                     "--resume", ck] + extra, 29713 + int(sharded))
+    assert "Step 5/6" in out and "Step 4/6" not in out

@@ -39,13 +39,15 @@ def main(argv=None):
     ap.add_argument("--transport", default=None, choices=[None, "p2p", "nccl"])
     ap.add_argument("--checkpoint-dir", type=str, default=None)
     ap.add_argument("--jsonl", type=str, default=None)
+    ap.add_argument("--async-checkpoint", action="store_true",
+                    help="copy checkpoint state to pinned host memory and write the files in the background")
     a = ap.parse_args(argv)
     from kolmogorov_moe_architecture_b200.training.runner import RunSpec, run_training
     spec = RunSpec(config_path=a.config, steps=a.steps, resume=a.resume, weights="bf16", checkpoint_format="C",
                    checkpoint_dir=a.checkpoint_dir, grad_checkpoint=a.activation_checkpointing,
                    data_mode="synthetic" if a.synthetic else "streaming", debug=a.debug, debug_interval=a.debug_interval,
                    transport=a.transport, jsonl=a.jsonl, shard_params=a.shard_params or a.cpu_offload,
-                   cpu_offload=a.cpu_offload)
+                   cpu_offload=a.cpu_offload, async_checkpoint=a.async_checkpoint)
     return run_training(spec)
 
 
