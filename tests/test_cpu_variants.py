@@ -1,0 +1,143 @@
+"""Alternative MoE layer classes, the native-kernel call interface, and the small utilities (metric sink,
+phase timer, roofline reporter, tokenizer wrapper) on CPU."""
+import json
+import os
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+import kolmogorov_moe_architecture_b200 as kmoe
+from kolmogorov_moe_architecture_b200.ops import eager
+
+
+def _route(T, E, k, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    w, idx = torch.softmax(torch.randn(T, E, generator=g), -1).topk(k, dim=-1)
+    return idx, w / w.sum(-1, keepdim=True)
+
+
+def test_alternative_expert_classes_compute_the_same_function():
+    """OptimizedGroupedExperts and the benchmark classes of triton_moe are the one grouped path under
+    other names: same weights -> same output as the eager definition."""
+    from kolmogorov_moe_architecture_b200.models.fused_moe import FusedSparseMoE, OptimizedGroupedExperts
+    from kolmogorov_moe_architecture_b200.models.triton_moe import (BatchedMoE, BatchedMoEOptimized,
+                                                                    TritonGroupedExperts, TritonGroupedExpertsFused,
+                                                                    sort_tokens_by_expert)
+    torch.manual_seed(0)
+    T, d, f, E, k = 24, 16, 32, 4, 2
+    x = torch.randn(T, d)
+    idx, w = _route(T, E, k)
+    for cls in (OptimizedGroupedExperts, TritonGroupedExperts, TritonGroupedExpertsFused, BatchedMoE, BatchedMoEOptimized):
+        m = cls(E, d, f)
+        want = eager.grouped_swiglu(x, m.w1, m.w2, m.w3, idx, w)
+        assert torch.allclose(m(x, idx, w), want, atol=1e-5), cls.__name__
+    tok, ids, order, starts, ends = sort_tokens_by_expert(idx, E)
+    flat = idx.reshape(-1)
+    assert torch.equal(ids, flat[order]) and torch.equal(ids, ids.sort().values)      # expert ids ascending
+    assert torch.equal(tok, order // k) and int(ends[-1]) == T * k
+    assert all(bool((ids[s:e] == i).all()) for i, (s, e) in enumerate(zip(starts.tolist(), ends.tolist())))
+    layer = FusedSparseMoE(d, f, E, top_k=k)
+    y = layer(torch.randn(2, 6, d))
+    assert y.shape == (2, 6, d) and torch.isfinite(y).all()
+    y.sum().backward()
+    assert all(p.grad is not None for p in layer.parameters())
+
+
+def test_fp8_layers_follow_the_mx_number_format_on_cpu():
+    """FP8Linear / FP8GroupedExperts / FP8MoELayer: on CPU the block-scaled format is emulated, so the result
+    is the exact-arithmetic result of the quantised operands and stays near the bf16 layer."""
+    from kolmogorov_moe_architecture_b200.models.fp8_moe import (FP8GroupedExperts, FP8Linear, FP8MoELayer,
+                                                                 is_fp8_available)
+    from kolmogorov_moe_architecture_b200.ops.mxfp8 import fake_quant_mx
+    assert is_fp8_available() in (True, False)
+    torch.manual_seed(0)
+    lin = FP8Linear(64, 32).float()
+    x = torch.randn(5, 64)
+    want = fake_quant_mx(x) @ fake_quant_mx(lin.weight).t()
+    got = lin(x)
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-4)
+    assert (got - x @ lin.weight.t()).abs().max() < 0.1 * (x @ lin.weight.t()).abs().max()
+    assert {"input_scale", "weight_scale", "input_amax_history"} <= set(lin.state_dict())     # reference's buffer names
+    ex = FP8GroupedExperts(4, 64, 64).float()
+    idx, w = _route(12, 4, 2)
+    xe = torch.randn(12, 64)
+    ref = eager.grouped_swiglu(xe, ex.w1, ex.w2, ex.w3, idx, w)
+    out = ex(xe, idx, w)
+    assert (out - ref).abs().max() < 0.15 * ref.abs().max() + 1e-3
+    layer = FP8MoELayer(64, 64, 4, top_k=2).float().train()
+    y = layer(torch.randn(2, 8, 64))
+    assert y.shape == (2, 8, 64) and float(layer.aux_loss) > 0
+
+
+def test_native_kernel_interface_on_sorted_rows():
+    """``grouped_swiglu_forward`` / ``grouped_swiglu_with_grad`` / ``GroupedSwiGLUFunction`` on expert-sorted
+    rows with segment bounds (the calling convention of the reference's extension)."""
+    from kolmogorov_moe_architecture_b200 import kernels as K
+    torch.manual_seed(0)
+    E, d, f = 3, 8, 16
+    counts = [5, 0, 7]
+    ids = torch.cat([torch.full((c,), e) for e, c in enumerate(counts)])
+    ends = torch.tensor(counts).cumsum(0)
+    starts = ends - torch.tensor(counts)
+    x = torch.randn(sum(counts), d, requires_grad=True)
+    W = [torch.randn(E, d, f, requires_grad=True), torch.randn(E, d, f, requires_grad=True),
+         torch.randn(E, f, d, requires_grad=True)]
+    want = torch.cat([(F.silu(x[s:t] @ W[0][e]) * (x[s:t] @ W[1][e])) @ W[2][e]
+                      for e, (s, t) in enumerate(zip(starts.tolist(), ends.tolist()))])
+    got = K.grouped_swiglu_forward(x.detach(), W[0].detach(), W[1].detach(), W[2].detach(), ids, starts, ends)
+    assert torch.allclose(got, want, atol=1e-5)
+    out = K.GroupedSwiGLUFunction.apply(x, *W, ids, starts, ends)
+    assert torch.allclose(out, want, atol=1e-5)
+    g_ref = torch.autograd.grad(want.sum(), [x] + W, retain_graph=True)
+    g_got = torch.autograd.grad(out.sum(), [x] + W)
+    assert all(torch.allclose(a, b, atol=1e-4) for a, b in zip(g_got, g_ref))
+    assert K.is_kernel_available() in (True, False)
+    import moe_arch.kernels as shim                        # the reference's import path resolves to the same module
+    assert shim.grouped_swiglu_forward is K.grouped_swiglu_forward
+
+
+def test_metric_logger_phase_timer_and_roofline(tmp_path):
+    from kolmogorov_moe_architecture_b200.utils.logging import MetricLogger
+    from kolmogorov_moe_architecture_b200.utils.profiling import PhaseTimer, measured_peaks, nvtx_range, roofline
+    path = str(tmp_path / "m" / "metrics.jsonl")
+    lg = MetricLogger(path)
+    lg.log({"loss": torch.tensor(1.5), "lr": 1e-3, "router/avg_entropy": 0.9}, step=7)
+    lg.close()
+    MetricLogger(path, rank=1).log({"loss": 0.0}, step=8)          # other ranks write nothing
+    rows = [json.loads(l) for l in open(path)]
+    assert len(rows) == 1 and rows[0]["step"] == 7 and rows[0]["loss"] == 1.5 and "time" in rows[0]
+    t = PhaseTimer(enabled=True, device=torch.device("cpu"))
+    for _ in range(3):
+        with t.phase("fwd"):
+            sum(range(1000))
+        with t.phase("bwd"), nvtx_range("bwd"):
+            sum(range(1000))
+    s = t.summary()
+    assert set(s) >= {"fwd", "bwd"} and all(v >= 0 for v in s.values())
+    off = PhaseTimer(enabled=False)
+    with off.phase("x"):
+        pass
+    assert off.summary() == {}
+    pk = measured_peaks()
+    assert pk["kind"] in ("measured", "fallback") and pk["hbm_bytes_s"] > 1e12
+    r = roofline(1e-3, flops=pk["bf16_flops"] * 0.5e-3, hbm_bytes=pk["hbm_bytes_s"] * 0.25e-3)
+    assert abs(r["achieved_fraction"] - 0.5) < 1e-6                  # compute is the binding limit here
+    r = roofline(1e-3, nvlink_bytes=770e9 * 0.8e-3)
+    assert abs(r["achieved_fraction"] - 0.8) < 1e-6
+
+
+def test_tokenizer_wrapper_with_the_offline_byte_tokenizer(monkeypatch):
+    """No tokenizer files are reachable here: the wrapper falls back to the byte tokenizer and keeps the
+    Hugging Face calling convention (pad = its own id, batches padded to the longest row)."""
+    from kolmogorov_moe_architecture_b200.data import ByteTokenizer, TokenizerWrapper
+    monkeypatch.setenv("HF_HUB_OFFLINE", "1")
+    w = TokenizerWrapper("no-such-tokenizer-anywhere", verbose=False)
+    assert isinstance(w.tokenizer, ByteTokenizer) and w.vocab_size == 258 and w.pad_token_id == 257
+    one = w.encode("héllo wörld")
+    assert one["input_ids"][-1] == w.eos_token_id and w.decode(one["input_ids"]) == "héllo wörld"
+    batch = w.encode(["ab", "abcdef"], padding=True, return_tensors="pt")
+    assert batch["input_ids"].shape == (2, 7) and batch["attention_mask"][0].tolist() == [1, 1, 1, 0, 0, 0, 0]
+    assert w.batch_decode(batch["input_ids"]) == ["ab", "abcdef"]
+    with pytest.raises(Exception):
+        TokenizerWrapper("no-such-tokenizer-anywhere", allow_byte_fallback=False, verbose=False)
