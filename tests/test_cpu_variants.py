@@ -141,3 +141,70 @@ def test_tokenizer_wrapper_with_the_offline_byte_tokenizer(monkeypatch):
     assert w.batch_decode(batch["input_ids"]) == ["ab", "abcdef"]
     with pytest.raises(Exception):
         TokenizerWrapper("no-such-tokenizer-anywhere", allow_byte_fallback=False, verbose=False)
+
+
+def _tiny_model():
+    cfg = kmoe.get_tiny_debug_config(vocab_size=128, d_model=32, n_heads=2, n_kv_heads=1, head_dim=16, d_ff=64,
+                                     d_ff_expert=32, max_seq_len=16, n_pred_tokens=2, aux_loss_weights=(1.0, 0.5))
+    torch.manual_seed(0)
+    return kmoe.MoETransformer(cfg, verbose=False), cfg
+
+
+def test_library_trainer_loop_eval_and_format_a_checkpoints(tmp_path):
+    """``Trainer``: accumulation keyed on the micro-step counter, metric names of the reference, evaluation,
+    ``checkpoint_step_{N}.pt`` / ``checkpoint_final.pt`` and resume of the counters."""
+    from kolmogorov_moe_architecture_b200.training.lr_schedule import CosineScheduleWithWarmup
+    from kolmogorov_moe_architecture_b200.training.trainer import Trainer
+    model, cfg = _tiny_model()
+    g = torch.Generator().manual_seed(1)
+    data = [{"input_ids": (t := torch.randint(0, 128, (2, 16), generator=g)), "labels": t} for _ in range(5)]
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    sched = CosineScheduleWithWarmup(opt, 2, 20, 1e-3, 1e-4, 0.0)
+    jl = str(tmp_path / "log.jsonl")
+    tr = Trainer(model, opt, sched, data, data[:2], {"run_name": "t"}, device="cpu", use_amp=False,
+                 gradient_accumulation_steps=2, checkpoint_dir=str(tmp_path / "ck"), log_interval=1, eval_interval=3,
+                 save_interval=3, jsonl_path=jl, verbose=False)    # updates fall on odd micro-steps (1, 3, 5, ...)
+    tr.train(max_steps=9)
+    names = sorted(os.listdir(tmp_path / "ck"))
+    assert "checkpoint_final.pt" in names and any(n.startswith("checkpoint_step_") for n in names)
+    rows = [json.loads(l) for l in open(jl)]
+    train_rows = [r for r in rows if "loss" in r and "eval_loss" not in r]
+    assert train_rows and {"lm_loss", "aux_loss", "lr", "grad_norm", "tokens_seen", "tokens_per_sec"} <= set(train_rows[0])
+    assert any(k.startswith("mt_") for k in train_rows[0])
+    assert any("eval_ppl" in r for r in rows)
+    assert tr.epoch >= 1                                           # five batches, nine micro-steps: the loader wrapped
+    ev = tr.evaluate(num_batches=2)
+    assert ev["eval_ppl"] > 1.0
+    model2, _ = _tiny_model()
+    opt2 = torch.optim.AdamW(model2.parameters(), lr=1e-3)
+    tr2 = Trainer(model2, opt2, CosineScheduleWithWarmup(opt2, 2, 20, 1e-3, 1e-4, 0.0), data, None, {}, device="cpu",
+                  use_amp=False, checkpoint_dir=str(tmp_path / "ck2"), verbose=False)
+    tr2.load_checkpoint(str(tmp_path / "ck" / "checkpoint_final.pt"))
+    assert (tr2.global_step, tr2.tokens_seen) == (tr.global_step, tr.tokens_seen)
+    assert all(torch.equal(a, b) for a, b in zip(model.state_dict().values(), model2.state_dict().values()))
+
+
+def test_hf_wrapper_signature_and_prefixed_checkpoint_keys(tmp_path):
+    from kolmogorov_moe_architecture_b200.training import checkpoint as ck
+    from kolmogorov_moe_architecture_b200.training.hf import MoEModelWrapper, make_hf_classes
+    model, cfg = _tiny_model()
+    w = MoEModelWrapper(model)
+    ids = torch.randint(0, 128, (2, 16))
+    out = w(input_ids=ids, labels=ids)
+    assert set(out) == {"loss"} and out["loss"].requires_grad            # no logits materialised with labels
+    out = w(input_ids=ids)
+    assert out["logits"].shape == (2, 16, 128)
+    assert all(k.startswith("model.") for k in w.state_dict())
+    path = str(tmp_path / "pytorch_model.bin")
+    torch.save(w.state_dict(), path)
+    fresh, _ = _tiny_model()
+    with torch.no_grad():
+        for p in fresh.parameters():
+            p.add_(1.0)
+    ck.load_model_state(fresh, path)                                      # the prefix is stripped on load
+    assert all(torch.equal(a, b) for a, b in zip(model.state_dict().values(), fresh.state_dict().values()))
+    MoETrainer, Callback = make_hf_classes()
+    logs = {"loss": 8.0}
+    Callback(4).on_log(None, None, None, logs=logs)
+    assert logs["true_loss"] == 2.0 and logs["accumulated_loss"] == 8.0
+    assert hasattr(MoETrainer, "create_optimizer") and hasattr(MoETrainer, "compute_loss")
