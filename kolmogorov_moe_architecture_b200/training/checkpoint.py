@@ -148,17 +148,40 @@ def load_format_c(d: str, model, optimizer=None, map_location="cpu") -> Dict:
 
 
 # ---------------------------------------------------------- sharded (ZeRO) save
+def _expert_parallel_names(model) -> list:
+    return [n for n, p in unwrap_model(model).named_parameters() if getattr(p, "_kmoe_expert_parallel", False)]
+
+
+def _pools(dp):
+    """(pool of the replicated parameters, pool of the expert-parallel tensors or None)."""
+    pools = getattr(dp, "pools", None)
+    if pools is None:
+        return dp, None
+    return pools[0], (pools[1] if len(pools) > 1 else None)
+
+
 def save_sharded(root: str, step: int, model, dp, training_state: Dict, rank: int, keep: int = 3,
-                 writer: Optional["AsyncCheckpointWriter"] = None, world: Optional[int] = None) -> str:
-    """Rank 0 writes ``model.pt`` (parameters are replicated) and ``training_state.pt``; every rank
-    writes ``optimizer-rank{r}.pt`` with the state of the tensors it owns.  ``writer``: write in the
-    background (no barrier; the directory is valid once all ``world`` markers exist)."""
+                 writer: Optional["AsyncCheckpointWriter"] = None, world: Optional[int] = None,
+                 ep_rank: int = 0, ep_size: int = 1) -> str:
+    """Rank 0 writes ``model.pt`` (the replicated parameters) and ``training_state.pt``; every rank writes
+    ``optimizer-rank{r}.pt`` with the state of the tensors it owns.  Under expert parallelism the expert
+    tensors differ from rank to rank: they are left out of ``model.pt`` and every rank writes its own
+    ``experts-rank{r}.pt`` (its experts, their optimizer state, and its place ``ep_rank`` of ``ep_size``).
+    ``dp``: one pool or a ``ParallelPlan``.  ``writer``: write in the background (no barrier; the directory
+    is valid once all ``world`` markers exist)."""
     import torch.distributed as dist
     d = os.path.join(root, f"checkpoint-{step}")
     os.makedirs(d, exist_ok=True)
-    files: Dict[str, Any] = {os.path.join(d, f"optimizer-rank{rank}.pt"): dp.optimizer_state_dict()}
+    main_pool, expert_pool = _pools(dp)
+    files: Dict[str, Any] = {os.path.join(d, f"optimizer-rank{rank}.pt"): main_pool.optimizer_state_dict()}
+    sd = unwrap_model(model).state_dict()
+    ep_names = _expert_parallel_names(model)
+    if ep_names:
+        files[os.path.join(d, f"experts-rank{rank}.pt")] = {
+            "ep_rank": ep_rank, "ep_size": ep_size, "params": {n: sd[n] for n in ep_names},
+            "optimizer": expert_pool.optimizer_state_dict() if expert_pool is not None else None}
     if rank == 0:
-        files[os.path.join(d, "model.pt")] = unwrap_model(model).state_dict()
+        files[os.path.join(d, "model.pt")] = {k: v for k, v in sd.items() if k not in set(ep_names)}
         files[os.path.join(d, "training_state.pt")] = training_state
     if writer is not None:
         w = world or (dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1)
@@ -173,14 +196,50 @@ def save_sharded(root: str, step: int, model, dp, training_state: Dict, rank: in
     return d
 
 
-def load_sharded(d: str, model, dp, rank: int, map_location="cpu") -> Dict:
-    unwrap_model(model).load_state_dict(torch.load(os.path.join(d, "model.pt"), map_location=map_location,
-                                                   weights_only=False))
+def load_sharded(d: str, model, dp, rank: int, map_location="cpu", ep_rank: int = 0, ep_size: int = 1) -> Dict:
+    base = unwrap_model(model)
+    main_pool, expert_pool = _pools(dp)
+    ep_names = _expert_parallel_names(model)
+    sd = torch.load(os.path.join(d, "model.pt"), map_location=map_location, weights_only=False)
+    missing, unexpected = base.load_state_dict(sd, strict=False)
+    lost = [k for k in missing if k not in set(ep_names)]
+    assert not lost and not unexpected, f"model.pt does not match the model: missing {lost[:5]}, unexpected {list(unexpected)[:5]}"
+    if ep_names and not all(n in sd for n in ep_names):
+        f = os.path.join(d, f"experts-rank{rank}.pt")
+        if not os.path.exists(f):
+            raise FileNotFoundError(f"{f}: this rank's experts are not in the checkpoint (written with another world size?)")
+        ex = torch.load(f, map_location=map_location, weights_only=False)
+        assert (ex["ep_rank"], ex["ep_size"]) == (ep_rank, ep_size), \
+            f"expert file holds shard {ex['ep_rank']} of {ex['ep_size']}, this rank is {ep_rank} of {ep_size}"
+        params = dict(base.named_parameters())
+        with torch.no_grad():
+            for n, t in ex["params"].items():
+                params[n].copy_(t)
+        if expert_pool is not None and ex.get("optimizer") is not None:
+            expert_pool.load_optimizer_state_dict(ex["optimizer"])
     f = os.path.join(d, f"optimizer-rank{rank}.pt")
     if os.path.exists(f):
-        dp.load_optimizer_state_dict(torch.load(f, map_location=map_location, weights_only=False))
+        main_pool.load_optimizer_state_dict(torch.load(f, map_location=map_location, weights_only=False))
     ts = os.path.join(d, "training_state.pt")
     return torch.load(ts, map_location=map_location, weights_only=False) if os.path.exists(ts) else {}
+
+
+def consolidate_expert_checkpoint(d: str) -> Dict[str, torch.Tensor]:
+    """One full state dict from an expert-parallel checkpoint directory: ``model.pt`` plus the expert
+    tensors of shards 0..ep_size-1 concatenated along the expert dimension (what a model built with
+    ``ep_size = 1`` and the same ``moe_implementation`` loads)."""
+    sd = dict(torch.load(os.path.join(d, "model.pt"), map_location="cpu", weights_only=False))
+    shards: Dict[int, Dict[str, torch.Tensor]] = {}
+    ep_size = 1
+    for name in sorted(os.listdir(d)):
+        if re.fullmatch(r"experts-rank\d+\.pt", name):
+            ex = torch.load(os.path.join(d, name), map_location="cpu", weights_only=False)
+            ep_size = ex["ep_size"]
+            shards.setdefault(ex["ep_rank"], ex["params"])      # replicas of a shard are identical
+    assert sorted(shards) == list(range(ep_size)), f"expert shards present: {sorted(shards)} of {ep_size}"
+    for n in shards.get(0, {}):
+        sd[n] = torch.cat([shards[r][n] for r in range(ep_size)], dim=0)
+    return sd
 
 
 def save_param_sharded(root: str, step: int, plan, training_state: Dict, rank: int, keep: int = 3,

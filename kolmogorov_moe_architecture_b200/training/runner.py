@@ -258,7 +258,8 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
         if spec.shard_params:
             st = ckpt.load_param_sharded(resume, dp, rank)
         else:
-            st = (ckpt.load_sharded(resume, model, dp.pools[0], rank, device) if dp is not None
+            st = (ckpt.load_sharded(resume, model, dp, rank, device, ep_rank=mesh.ep_rank, ep_size=mesh.ep)
+                  if dp is not None
                   else ckpt.load_format_c(resume, model, optimizer, device))
         engine.global_step = start_step = st.get("step", 0)
         engine.tokens_seen = st.get("tokens_seen", 0)
@@ -284,7 +285,8 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
         if spec.shard_params:
             ckpt.save_param_sharded(cdir, step, dp, state, rank, writer=writer)
         elif dp is not None:
-            ckpt.save_sharded(cdir, step, model, dp.pools[0], state, rank, writer=writer, world=world)
+            ckpt.save_sharded(cdir, step, model, dp, state, rank, writer=writer, world=world,
+                              ep_rank=mesh.ep_rank, ep_size=mesh.ep)
         elif spec.checkpoint_format == "C":
             ckpt.save_format_c(cdir, step, model, optimizer, state)
         else:

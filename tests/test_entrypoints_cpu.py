@@ -97,3 +97,38 @@ def test_train_distributed_two_ranks_background_checkpoints_and_resume(tiny_cfg,
     out = _torchrun(["--config", tiny_cfg["config"], "--steps", "6", "--synthetic", "--checkpoint-dir", ck,
                      "--resume", ck] + extra, 29713 + int(sharded))
     assert "Step 5/6" in out and "Step 4/6" not in out
+
+
+def test_expert_parallel_checkpoint_keeps_every_ranks_experts(tiny_cfg):
+    """Experts split over two ranks: each rank's experts and their optimizer state go to its own file, the
+    job resumes from them, and the directory consolidates into one state dict for a model with all experts
+    on one rank."""
+    cfg = yaml.safe_load(open(tiny_cfg["config"]))
+    cfg["model"].update(moe_implementation="expert_parallel", ep_size=2, moe_layers=[1, 2, 3])
+    path = os.path.join(tiny_cfg["dir"], "tiny_ep.yaml")
+    yaml.safe_dump(cfg, open(path, "w"))
+    ck = os.path.join(tiny_cfg["dir"], "dist_ep")
+    _torchrun(["--config", path, "--steps", "4", "--synthetic", "--checkpoint-dir", ck, "--async-checkpoint"], 29715)
+    from kolmogorov_moe_architecture_b200.training import checkpoint as ckpt
+    last = ckpt.latest_complete_checkpoint(ck, world=2)
+    assert {"experts-rank0.pt", "experts-rank1.pt", "model.pt"} <= set(os.listdir(last))
+    e0 = torch.load(os.path.join(last, "experts-rank0.pt"), weights_only=False)
+    e1 = torch.load(os.path.join(last, "experts-rank1.pt"), weights_only=False)
+    assert (e0["ep_rank"], e1["ep_rank"], e0["ep_size"]) == (0, 1, 2) and e0["optimizer"] is not None
+    name = next(iter(e0["params"]))
+    assert "local_experts" in name and not torch.equal(e0["params"][name], e1["params"][name])
+    model_sd = torch.load(os.path.join(last, "model.pt"), weights_only=False)
+    assert not any("local_experts" in k for k in model_sd)
+    full = ckpt.consolidate_expert_checkpoint(last)
+    assert full[name].shape[0] == 2 * e0["params"][name].shape[0]
+    assert torch.equal(full[name][: e0["params"][name].shape[0]], e0["params"][name])
+    # a single-process model with all experts local loads the consolidated state
+    import kolmogorov_moe_architecture_b200 as kmoe
+    from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml, model_config_tolerant
+    y = load_yaml(path)
+    y["model"]["ep_size"] = 1
+    one = kmoe.MoETransformer(model_config_tolerant(y), verbose=False)
+    missing, unexpected = one.load_state_dict(full, strict=False)
+    assert not unexpected and not [k for k in missing if "local_experts" in k]
+    out = _torchrun(["--config", path, "--steps", "6", "--synthetic", "--checkpoint-dir", ck, "--resume", ck], 29716)
+    assert "Step 5/6" in out and "Step 4/6" not in out
