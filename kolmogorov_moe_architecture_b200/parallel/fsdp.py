@@ -30,6 +30,13 @@ preceding one in the backward pass) is issued on a side stream as soon as its bu
 reduce-scatter of a finished unit runs on a second side stream, so that both hide behind the compute
 of the neighbouring unit.  ``KMOE_FSDP_OVERLAP=0`` keeps everything on the compute stream.
 
+Expert parallelism.  Tensors already split over an expert-parallel group (``_kmoe_expert_parallel``) are
+not sharded again: they stay resident, and a second pool (``zero.ShardedDataParallel(expert_params=True)``
+over the ranks that hold the same experts) reduces and steps them.  ``zero.ParallelPlan([this plan, that
+pool])`` drives both through ``reduce / owned_sq_norm / scale_owned / finish`` with one global-norm clip -
+the combination the reference cannot run (its expert-parallel layer has no backward and clashes with its
+FSDP wrapping, moe_arch/model/sparse_moe.py:540-603).
+
 Muon needs whole matrices on one rank and is therefore offered by the replicated plan only, as in the
 reference, whose distributed launcher is AdamW-only (train_distributed.py:336-397).
 """
@@ -99,16 +106,16 @@ class FullyShardedDataParallel:
                 ps, ns = [], []
                 for n, p in mod.named_parameters():
                     if p.requires_grad and id(p) not in seen:
-                        assert not getattr(p, "_kmoe_expert_parallel", False), \
-                            "expert-parallel tensors are not supported by the parameter-sharded plan"
                         seen.add(id(p))
+                        if getattr(p, "_kmoe_expert_parallel", False):
+                            continue            # already split over the expert-parallel group: its own pool steps it
                         ps.append(p)
                         ns.append(f"{mname}.{n}")
                 if ps:
                     self.units.append(_Unit(mname, mod, ps, ns))
         rp, rn = [], []
         for n, p in model.named_parameters():
-            if p.requires_grad and id(p) not in seen:
+            if p.requires_grad and id(p) not in seen and not getattr(p, "_kmoe_expert_parallel", False):
                 seen.add(id(p))
                 rp.append(p)
                 rn.append(n)
@@ -396,22 +403,39 @@ class FullyShardedDataParallel:
         require_ext()                           # a GPU run without the extension is an error, not a slow path
         return True
 
-    def reduce_clip_and_step(self, optimizer=None, max_norm: Optional[float] = 1.0) -> torch.Tensor:
-        all_units = self.units + ([self.root] if self.root else [])
-        for u in all_units:                     # the root unit, and units with parameters that got no gradient
-            if not u.reduced:
+    # The step in the four phases a ``ParallelPlan`` drives (so that this plan and the pool of the
+    # expert-parallel tensors clip by one global norm): reduce, owned_sq_norm, scale_owned, finish.
+    def reduce(self) -> None:
+        for u in self.units + ([self.root] if self.root else []):     # the root unit, and units whose
+            if not u.reduced:                                          # parameters got no gradient
                 self._reduce_unit(u)
                 self._release(u)
         if self._rs_stream is not None:
             torch.cuda.current_stream(self.device).wait_stream(self._rs_stream)
+
+    def owned_sq_norm(self) -> torch.Tensor:
+        all_units = self.units + ([self.root] if self.root else [])
         norms = torch._foreach_norm([u.grad_shard for u in all_units])
-        sq = torch.stack([n.to(self.device) for n in norms]).pow(2).sum().reshape(1)
+        return torch.stack([n.to(self.device) for n in norms]).pow(2).sum()
+
+    def scale_owned(self, coef) -> None:
+        self._coef = coef
+
+    def reduce_clip_and_step(self, optimizer=None, max_norm: Optional[float] = 1.0) -> torch.Tensor:
+        self.reduce()
+        sq = self.owned_sq_norm().reshape(1)
         if self.world > 1:
             dist.all_reduce(sq, group=self.group)
         total = sq.sqrt()[0]
-        coef = None
+        self._coef = None
         if max_norm is not None and max_norm > 0:
-            coef = (max_norm / (total + 1e-6)).clamp(max=1.0)
+            self._coef = (max_norm / (total + 1e-6)).clamp(max=1.0)
+        self.finish()
+        return total
+
+    def finish(self) -> None:
+        all_units = self.units + ([self.root] if self.root else [])
+        coef, self._coef = getattr(self, "_coef", None), None
         self.step_count += 1
         h = self.hyper
         b1, b2 = h["betas"]
@@ -441,7 +465,6 @@ class FullyShardedDataParallel:
                 u.grad_shard.zero_()
         self._drop_all()                        # new values: everything is gathered again at its next use
         self._arm()
-        return total
 
     # ------------------------------------------------------------------ whole-model access
     def full_state_dict(self, to_cpu: bool = True) -> Dict[str, torch.Tensor]:

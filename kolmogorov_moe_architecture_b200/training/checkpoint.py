@@ -160,6 +160,26 @@ def _pools(dp):
     return pools[0], (pools[1] if len(pools) > 1 else None)
 
 
+def _expert_file(sd, ep_names, expert_pool, ep_rank: int, ep_size: int) -> Dict[str, Any]:
+    return {"ep_rank": ep_rank, "ep_size": ep_size, "params": {n: sd[n] for n in ep_names},
+            "optimizer": expert_pool.optimizer_state_dict() if expert_pool is not None else None}
+
+
+def _load_expert_file(d: str, rank: int, base, expert_pool, ep_rank: int, ep_size: int, map_location="cpu") -> None:
+    f = os.path.join(d, f"experts-rank{rank}.pt")
+    if not os.path.exists(f):
+        raise FileNotFoundError(f"{f}: this rank's experts are not in the checkpoint (written with another world size?)")
+    ex = torch.load(f, map_location=map_location, weights_only=False)
+    assert (ex["ep_rank"], ex["ep_size"]) == (ep_rank, ep_size), \
+        f"expert file holds shard {ex['ep_rank']} of {ex['ep_size']}, this rank is {ep_rank} of {ep_size}"
+    params = dict(base.named_parameters())
+    with torch.no_grad():
+        for n, t in ex["params"].items():
+            params[n].copy_(t)
+    if expert_pool is not None and ex.get("optimizer") is not None:
+        expert_pool.load_optimizer_state_dict(ex["optimizer"])
+
+
 def save_sharded(root: str, step: int, model, dp, training_state: Dict, rank: int, keep: int = 3,
                  writer: Optional["AsyncCheckpointWriter"] = None, world: Optional[int] = None,
                  ep_rank: int = 0, ep_size: int = 1) -> str:
@@ -177,9 +197,7 @@ def save_sharded(root: str, step: int, model, dp, training_state: Dict, rank: in
     sd = unwrap_model(model).state_dict()
     ep_names = _expert_parallel_names(model)
     if ep_names:
-        files[os.path.join(d, f"experts-rank{rank}.pt")] = {
-            "ep_rank": ep_rank, "ep_size": ep_size, "params": {n: sd[n] for n in ep_names},
-            "optimizer": expert_pool.optimizer_state_dict() if expert_pool is not None else None}
+        files[os.path.join(d, f"experts-rank{rank}.pt")] = _expert_file(sd, ep_names, expert_pool, ep_rank, ep_size)
     if rank == 0:
         files[os.path.join(d, "model.pt")] = {k: v for k, v in sd.items() if k not in set(ep_names)}
         files[os.path.join(d, "training_state.pt")] = training_state
@@ -205,18 +223,7 @@ def load_sharded(d: str, model, dp, rank: int, map_location="cpu", ep_rank: int 
     lost = [k for k in missing if k not in set(ep_names)]
     assert not lost and not unexpected, f"model.pt does not match the model: missing {lost[:5]}, unexpected {list(unexpected)[:5]}"
     if ep_names and not all(n in sd for n in ep_names):
-        f = os.path.join(d, f"experts-rank{rank}.pt")
-        if not os.path.exists(f):
-            raise FileNotFoundError(f"{f}: this rank's experts are not in the checkpoint (written with another world size?)")
-        ex = torch.load(f, map_location=map_location, weights_only=False)
-        assert (ex["ep_rank"], ex["ep_size"]) == (ep_rank, ep_size), \
-            f"expert file holds shard {ex['ep_rank']} of {ex['ep_size']}, this rank is {ep_rank} of {ep_size}"
-        params = dict(base.named_parameters())
-        with torch.no_grad():
-            for n, t in ex["params"].items():
-                params[n].copy_(t)
-        if expert_pool is not None and ex.get("optimizer") is not None:
-            expert_pool.load_optimizer_state_dict(ex["optimizer"])
+        _load_expert_file(d, rank, base, expert_pool, ep_rank, ep_size, map_location)
     f = os.path.join(d, f"optimizer-rank{rank}.pt")
     if os.path.exists(f):
         main_pool.load_optimizer_state_dict(torch.load(f, map_location=map_location, weights_only=False))
@@ -243,21 +250,28 @@ def consolidate_expert_checkpoint(d: str) -> Dict[str, torch.Tensor]:
 
 
 def save_param_sharded(root: str, step: int, plan, training_state: Dict, rank: int, keep: int = 3,
-                       writer: Optional["AsyncCheckpointWriter"] = None) -> str:
+                       writer: Optional["AsyncCheckpointWriter"] = None, ep_rank: int = 0, ep_size: int = 1) -> str:
     """Checkpoint of the parameter-sharded plan: every rank helps gather the full parameters (rank 0
-    writes them as an ordinary ``model.pt``) and writes its own shards with their AdamW moments.
-    ``writer``: the files are written in the background (the gather itself stays collective)."""
+    writes them as an ordinary ``model.pt``) and writes its own shards with their AdamW moments; under
+    expert parallelism also its ``experts-rank{r}.pt``.  ``plan``: the sharded plan or a ``ParallelPlan``
+    of it and the expert pool.  ``writer``: files are written in the background (the gather itself stays
+    collective)."""
     import torch.distributed as dist
     d = os.path.join(root, f"checkpoint-{step}")
     os.makedirs(d, exist_ok=True)
-    full = plan.full_state_dict(to_cpu=True)
-    files: Dict[str, Any] = {os.path.join(d, f"shards-rank{rank}.pt"): plan.shard_state_dict()}
+    fsdp, expert_pool = _pools(plan)
+    full = fsdp.full_state_dict(to_cpu=True)
+    files: Dict[str, Any] = {os.path.join(d, f"shards-rank{rank}.pt"): fsdp.shard_state_dict()}
+    ep_names = _expert_parallel_names(fsdp.model)
+    if ep_names:
+        esd = {n: p.detach() for n, p in unwrap_model(fsdp.model).named_parameters() if n in set(ep_names)}
+        files[os.path.join(d, f"experts-rank{rank}.pt")] = _expert_file(esd, ep_names, expert_pool, ep_rank, ep_size)
     if rank == 0:
         files[os.path.join(d, "model.pt")] = full
         files[os.path.join(d, "training_state.pt")] = training_state
     if writer is not None:
         writer.submit(files, d, rank,
-                      then=(lambda: prune_checkpoints(root, keep, world=plan.world)) if rank == 0 else None)
+                      then=(lambda: prune_checkpoints(root, keep, world=fsdp.world)) if rank == 0 else None)
         return d
     for path, obj in files.items():
         _atomic_save(obj, path)
@@ -268,18 +282,21 @@ def save_param_sharded(root: str, step: int, plan, training_state: Dict, rank: i
     return d
 
 
-def load_param_sharded(d: str, plan, rank: int) -> Dict:
+def load_param_sharded(d: str, plan, rank: int, ep_rank: int = 0, ep_size: int = 1) -> Dict:
     """Restores shards and moments when the file of this rank matches the current layout, otherwise the
-    parameters alone from ``model.pt`` (any world size)."""
+    parameters alone from ``model.pt`` (any world size); experts from this rank's expert file."""
+    fsdp, expert_pool = _pools(plan)
     f = os.path.join(d, f"shards-rank{rank}.pt")
     done = False
     if os.path.exists(f):
         sd = torch.load(f, map_location="cpu", weights_only=False)
-        if sd.get("world") == plan.world and sd.get("rank") == plan.rank:
-            plan.load_shard_state_dict(sd)
+        if sd.get("world") == fsdp.world and sd.get("rank") == fsdp.rank:
+            fsdp.load_shard_state_dict(sd)
             done = True
     if not done:
-        plan.load_full_state_dict(torch.load(os.path.join(d, "model.pt"), map_location="cpu", weights_only=False))
+        fsdp.load_full_state_dict(torch.load(os.path.join(d, "model.pt"), map_location="cpu", weights_only=False))
+    if _expert_parallel_names(fsdp.model):
+        _load_expert_file(d, rank, unwrap_model(fsdp.model), expert_pool, ep_rank, ep_size)
     ts = os.path.join(d, "training_state.pt")
     return torch.load(ts, map_location="cpu", weights_only=False) if os.path.exists(ts) else {}
 

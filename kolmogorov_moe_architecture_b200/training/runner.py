@@ -200,7 +200,6 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
     if spec.shard_params:
         # the reference's train_distributed.py regime: parameters sharded per block, AdamW on the shards
         from ..parallel.fsdp import FullyShardedDataParallel
-        assert cfg.ep_size == 1, "the parameter-sharded plan does not combine with expert parallelism"
         dp = FullyShardedDataParallel(model, lr=opt_cfg.get("adamw_lr", train_cfg.get("max_lr", 3e-4)) * spec.lr_scale,
                                       betas=tuple(opt_cfg.get("adamw_betas", (0.9, 0.95))),
                                       weight_decay=opt_cfg.get("weight_decay", train_cfg.get("weight_decay", 0.01)),
@@ -209,6 +208,16 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
         if is_main:
             print(f"parameter-sharded plan: {dp.param_bytes_per_rank() / 2**20:.1f} MiB of parameters per rank"
                   f"{' (host memory)' if spec.cpu_offload else ''}")
+        if cfg.ep_size > 1 and any(getattr(p, "_kmoe_expert_parallel", False) for p in model.parameters()):
+            # experts are already split over the expert-parallel group; their replicas form a second pool
+            from ..parallel.zero import ParallelPlan, ShardedDataParallel
+            experts = ShardedDataParallel(model, optimizer_kind="adamw", group=mesh.expert_dp_group,
+                                          adamw_lr=opt_cfg.get("adamw_lr", 3e-4) * spec.lr_scale,
+                                          weight_decay=opt_cfg.get("weight_decay", 0.01), expert_params=True,
+                                          grad_scale=1.0 / cfg.ep_size, broadcast_from_rank0=False,
+                                          transport="nccl" if use_cuda else "gloo")
+            dp = ParallelPlan([dp, experts])
+            optimizer = dp
     elif world > 1:
         from ..parallel.zero import ParallelPlan, ShardedDataParallel
         okind = "muon" if opt_cfg.get("type", "adamw") == "muon" else "adamw"
@@ -256,7 +265,7 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
         resume = found
     if resume and os.path.isdir(resume):
         if spec.shard_params:
-            st = ckpt.load_param_sharded(resume, dp, rank)
+            st = ckpt.load_param_sharded(resume, dp, rank, ep_rank=mesh.ep_rank, ep_size=mesh.ep)
         else:
             st = (ckpt.load_sharded(resume, model, dp, rank, device, ep_rank=mesh.ep_rank, ep_size=mesh.ep)
                   if dp is not None
@@ -283,7 +292,7 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
     def save(step: int, suffix: Optional[str] = None):
         state = {"step": step, "tokens_seen": engine.tokens_seen, "config_path": spec.config_path}
         if spec.shard_params:
-            ckpt.save_param_sharded(cdir, step, dp, state, rank, writer=writer)
+            ckpt.save_param_sharded(cdir, step, dp, state, rank, writer=writer, ep_rank=mesh.ep_rank, ep_size=mesh.ep)
         elif dp is not None:
             ckpt.save_sharded(cdir, step, model, dp, state, rank, writer=writer, world=world,
                               ep_rank=mesh.ep_rank, ep_size=mesh.ep)

@@ -132,3 +132,11 @@ def test_expert_parallel_checkpoint_keeps_every_ranks_experts(tiny_cfg):
     assert not unexpected and not [k for k in missing if "local_experts" in k]
     out = _torchrun(["--config", path, "--steps", "6", "--synthetic", "--checkpoint-dir", ck, "--resume", ck], 29716)
     assert "Step 5/6" in out and "Step 4/6" not in out
+    # the same split of the experts under the parameter-sharded plan for the dense parameters
+    ck2 = os.path.join(tiny_cfg["dir"], "dist_ep_sharded")
+    _torchrun(["--config", path, "--steps", "4", "--synthetic", "--checkpoint-dir", ck2, "--shard-params"], 29717)
+    last = ckpt.latest_complete_checkpoint(ck2, world=2)
+    assert {"experts-rank0.pt", "experts-rank1.pt", "shards-rank0.pt", "shards-rank1.pt", "model.pt"} <= set(os.listdir(last))
+    out = _torchrun(["--config", path, "--steps", "5", "--synthetic", "--checkpoint-dir", ck2, "--shard-params",
+                     "--resume", ck2], 29718)
+    assert "Step 5/5" in out and "Step 4/5" not in out

@@ -125,3 +125,50 @@ def test_fsdp_cpu_offload_single_process():
     for _ in range(5):
         l1 = e.step(ids).loss_value()
     assert l1 < l0
+
+
+def _ep_worker(rank, world, tmp):
+    """Dense parameters sharded per block, experts split over the expert-parallel group: same losses and
+    parameters as the replicated-parameter plan with the same expert pool, one global-norm clip over both."""
+    import kolmogorov_moe_architecture_b200 as kmoe
+    from kolmogorov_moe_architecture_b200.parallel import mesh as pmesh
+    from kolmogorov_moe_architecture_b200.parallel.fsdp import FullyShardedDataParallel
+    from kolmogorov_moe_architecture_b200.parallel.zero import ParallelPlan, ShardedDataParallel
+    from kolmogorov_moe_architecture_b200.training.engine import TrainEngine
+    mesh = pmesh.make_mesh(2)
+    cfg = kmoe.get_tiny_debug_config(vocab_size=256, d_model=64, n_heads=2, n_kv_heads=1, head_dim=32, d_ff=128,
+                                     d_ff_expert=64, max_seq_len=32, n_pred_tokens=2, aux_loss_weights=(1.0, 0.5),
+                                     mamba_moe_mode="moe_ffn", mod_capacity_factor=1.0,
+                                     moe_implementation="expert_parallel", ep_size=2)
+
+    def build(sharded):
+        torch.manual_seed(0)
+        m = kmoe.MoETransformer(cfg, verbose=False)
+        n_ep = sum(p.numel() for p in m.parameters() if getattr(p, "_kmoe_expert_parallel", False))
+        assert n_ep > 0
+        experts = ShardedDataParallel(m, optimizer_kind="adamw", group=mesh.expert_dp_group, adamw_lr=1e-2,
+                                      weight_decay=0.01, expert_params=True, grad_scale=0.5, broadcast_from_rank0=False)
+        dense = (FullyShardedDataParallel(m, lr=1e-2, weight_decay=0.01, overlap=True) if sharded
+                 else ShardedDataParallel(m, optimizer_kind="adamw", adamw_lr=1e-2, weight_decay=0.01))
+        plan = ParallelPlan([dense, experts])
+        return m, dense, TrainEngine(m, plan, grad_clip=0.5, dp=plan)
+
+    ma, _, ea = build(False)
+    mb, fsdp, eb = build(True)
+    assert all(p.numel() > 0 for p in mb.parameters() if getattr(p, "_kmoe_expert_parallel", False))
+    assert all(p.numel() == 0 for p in mb.parameters() if not getattr(p, "_kmoe_expert_parallel", False))
+    g = torch.Generator().manual_seed(11 + rank)
+    for step in range(3):
+        ids = torch.randint(0, 256, (2, 32), generator=g)
+        la, lb = ea.step(ids).loss_value(), eb.step(ids).loss_value()
+        assert abs(la - lb) < 1e-3, (step, la, lb)
+    full = fsdp.full_state_dict()
+    ref = dict(ma.named_parameters(remove_duplicate=False))
+    assert max((full[n] - ref[n].detach()).abs().max().item() for n in full) < 2e-3
+    for (n, pa), (_, pb) in zip(ma.named_parameters(), mb.named_parameters()):
+        if getattr(pa, "_kmoe_expert_parallel", False):
+            assert torch.allclose(pa, pb, atol=2e-3), n
+
+
+def test_sharded_dense_parameters_with_expert_parallel_experts(tmp_path):
+    run_ranks(_ep_worker, 2, str(tmp_path))
