@@ -226,7 +226,13 @@ def load_sharded(d: str, model, dp, rank: int, map_location="cpu", ep_rank: int 
         _load_expert_file(d, rank, base, expert_pool, ep_rank, ep_size, map_location)
     f = os.path.join(d, f"optimizer-rank{rank}.pt")
     if os.path.exists(f):
-        main_pool.load_optimizer_state_dict(torch.load(f, map_location=map_location, weights_only=False))
+        osd = torch.load(f, map_location=map_location, weights_only=False)
+        same = not isinstance(osd, dict) or osd.get("world") in (None, getattr(main_pool, "world", None))
+        if same:
+            main_pool.load_optimizer_state_dict(osd)
+        else:           # written by a job of another size: parameters carry over, optimizer moments start fresh
+            print(f"[checkpoint] {os.path.basename(f)} was written by {osd.get('world')} ranks; "
+                  f"optimizer state of rank {rank} starts fresh", flush=True)
     ts = os.path.join(d, "training_state.pt")
     return torch.load(ts, map_location=map_location, weights_only=False) if os.path.exists(ts) else {}
 

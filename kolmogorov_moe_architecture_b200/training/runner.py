@@ -302,6 +302,7 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
             ckpt.save_format_b(os.path.join(cdir, ckpt.format_b_name(step, suffix)), model, optimizer, step, 0, 0,
                                losses, engine.tokens_seen, spec.config_path)
 
+    injector = _fault_from_env()
     log_every = train_cfg["log_interval"]
     t_last, tok_last = time.time(), engine.tokens_seen
     last_stats = None
@@ -322,6 +323,8 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
             step += 1
             if dog is not None:
                 dog.beat()
+            if injector is not None:
+                injector(rank, step)           # host-side failure between steps (tests of restart / resume)
             if step % log_every == 0 or step == total_steps:
                 lv = last_stats.loss_value()
                 losses.append(lv)
@@ -373,6 +376,34 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
     if world > 1:
         pmesh.destroy()
     return out
+
+
+def _fault_from_env():
+    """``KMOE_FAULT_INJECT=rank:step:kind`` (kind = raise | exit | stall) makes that rank fail on the host
+    right after that step, with no kernel or collective of its own in flight.  With ``KMOE_FAULT_ONCE=<file>``
+    the failure happens only while the file does not exist (it is created first), so a restarted job runs
+    through."""
+    spec = os.environ.get("KMOE_FAULT_INJECT")
+    if not spec:
+        return None
+    from ..utils.fault import FaultInjector
+    r, s_, kind = (spec.split(":") + ["raise"])[:3]
+    inj = FaultInjector(int(r), int(s_), kind)
+    once = os.environ.get("KMOE_FAULT_ONCE")
+
+    def fire(rank: int, step: int) -> None:
+        if rank != inj.rank or step != inj.step:
+            return
+        if once:
+            if os.path.exists(once):
+                return
+            with open(once, "w") as f:
+                f.write(f"rank {rank} step {step}\n")
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()           # nothing of this rank is in flight when it leaves
+        inj.maybe_fail(rank, step)
+
+    return fire
 
 
 def _step_with_mask(engine: TrainEngine, b, am):

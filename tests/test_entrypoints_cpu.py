@@ -140,3 +140,32 @@ def test_expert_parallel_checkpoint_keeps_every_ranks_experts(tiny_cfg):
     out = _torchrun(["--config", path, "--steps", "5", "--synthetic", "--checkpoint-dir", ck2, "--shard-params",
                      "--resume", ck2], 29718)
     assert "Step 5/5" in out and "Step 4/5" not in out
+
+
+def test_elastic_launcher_restarts_from_the_newest_complete_checkpoint(tiny_cfg):
+    """Rank 1 exits on the host after step 3 (once); the launcher starts the job again, which resumes from
+    checkpoint-2 and runs to the end.  A second scenario shrinks to one process after two failures."""
+    import elastic_launch
+    ck = os.path.join(tiny_cfg["dir"], "elastic")
+    marker = os.path.join(tiny_cfg["dir"], "failed_once")
+    env = dict(os.environ, PYTHONPATH=ROOT, KMOE_OFFLINE="1", KMOE_FAULT_INJECT="1:3:exit", KMOE_FAULT_ONCE=marker)
+    lines = []
+    rc = elastic_launch.supervise(2, ["train_distributed.py", "--config", tiny_cfg["config"], "--steps", "6",
+                                      "--synthetic"], ck, max_restarts=2, port=29741, env=env, log=lines.append)
+    assert rc == 0, lines
+    assert os.path.exists(marker)
+    assert any("starting fresh" in l for l in lines) and any("resuming from checkpoint-2" in l for l in lines)
+    assert any("finished after 1 restart" in l for l in lines)
+    from kolmogorov_moe_architecture_b200.training import checkpoint as ckpt
+    assert ckpt.latest_complete_checkpoint(ck, world=2).endswith("checkpoint-6")
+    # a rank that fails every time: two failures at two processes, then one process finishes the job
+    ck2 = os.path.join(tiny_cfg["dir"], "elastic_shrink")
+    env2 = dict(os.environ, PYTHONPATH=ROOT, KMOE_OFFLINE="1", KMOE_FAULT_INJECT="1:3:exit")
+    lines = []
+    rc = elastic_launch.supervise(2, ["train_distributed.py", "--config", tiny_cfg["config"], "--steps", "6",
+                                      "--synthetic"], ck2, max_restarts=3, port=29751, shrink=True, env=env2,
+                                  log=lines.append, backoff_s=0.1)
+    assert rc == 0, lines
+    assert any("continuing with 1 processes" in l for l in lines)
+    cmd = elastic_launch.build_command(4, 29500, ["t.py", "--resume", "old", "--checkpoint-dir=x", "--steps", "3"], "ck", "ck")
+    assert cmd[-4:] == ["--checkpoint-dir", "ck", "--resume", "ck"] and "old" not in cmd and "--steps" in cmd
