@@ -93,6 +93,10 @@ def test_param_calculator_matches_the_model(tiny):
     n = sum(p.numel() for p in MoETransformer(cfg, verbose=False).parameters())
     total = next(v for k, v in r.items() if "total" in k and isinstance(v, (int, float)))
     assert abs(total - n) <= 0.02 * n, (total, n)
+    rep = pc.print_report(cfg, world=2)
+    b = rep["breakdown"]
+    assert b["total"] == n and b["experts"] > 0 and b["mamba"] > 0 and b["mod_router"] > 0 and "other" not in b
+    assert pc.format_params(5.87e9) == "5.87B" and pc.format_params(1500) == "1.50K"
     found = pc.design(5e9, 1.5e9, tol=0.3, limit=3)
     assert isinstance(found, list)
 

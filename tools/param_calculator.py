@@ -37,6 +37,76 @@ def analyze(cfg, world: int = 8, micro_batch: int = 4, optimizer: str = "muon") 
             "per_gpu_total_gb": (w + g + opt / world + act) / 2**30, "layers": c}
 
 
+def format_params(n: float) -> str:
+    for unit, div in (("B", 1e9), ("M", 1e6), ("K", 1e3)):
+        if abs(n) >= div:
+            return f"{n / div:.2f}{unit}"
+    return str(int(n))
+
+
+def breakdown(cfg) -> dict:
+    """Exact parameter counts by kind of tensor (embedding, heads, attention, Mamba mixers, norms, dense FFN,
+    routers, experts, MoD routers), counted on a meta-device instance so the categories follow the modules the
+    model really builds (Mamba layers, RoutingMamba experts and MoD routers included)."""
+    from kolmogorov_moe_architecture_b200 import MoETransformer
+    with torch.device("meta"):
+        m = MoETransformer(cfg, verbose=False)
+    out = dict.fromkeys(("embedding", "lm_heads", "attention", "mamba", "norms", "dense_ffn", "router", "experts",
+                         "mod_router"), 0)
+    tied = set()
+    for name, p in m.named_parameters():
+        n = p.numel()
+        if name.startswith("token_embedding"):
+            out["embedding"] += n
+        elif name.startswith("lm_heads"):
+            out["lm_heads"] += n
+        elif "norm" in name.split(".")[-2] or name.startswith("final_norm"):
+            out["norms"] += n
+        elif "mod_router" in name:
+            out["mod_router"] += n
+        elif ".seq_layer." in name:
+            mixer = name.split(".seq_layer.")[1]
+            if mixer.split(".")[0] in ("q_proj", "k_proj", "v_proj", "o_proj"):
+                out["attention"] += n
+            elif mixer.startswith("router"):
+                out["router"] += n
+            else:
+                out["mamba"] += n
+        elif ".ffn." in name:
+            tail = name.split(".ffn.")[1]
+            if "router" in tail:
+                out["router"] += n
+            elif "experts" in tail:
+                out["experts"] += n
+            else:
+                out["dense_ffn"] += n
+        else:
+            out.setdefault("other", 0)
+            out["other"] += n
+    out["total"] = sum(v for k, v in out.items() if k != "total")
+    return out
+
+
+def print_report(cfg, world: int = 8, micro_batch: int = 4, optimizer: str = "muon") -> dict:
+    r, b = analyze(cfg, world, micro_batch, optimizer), breakdown(cfg)
+    n_moe = len([i for i in range(cfg.n_layers) if i in set(cfg.moe_layers)]) if cfg.moe_layers is not None else cfg.n_layers
+    print("=" * 64)
+    print("configuration")
+    print(f"  vocab {cfg.vocab_size:,}  d_model {cfg.d_model}  layers {cfg.n_layers} ({n_moe} MoE, {len(cfg.mamba_layers or ())} Mamba)")
+    print(f"  heads {cfg.n_heads} / kv {cfg.n_kv_heads} x {cfg.head_dim}  d_ff {cfg.d_ff}  experts {cfg.n_experts} x d_ff {cfg.d_ff_expert}, top-{cfg.moe_top_k}")
+    print("parameters by kind")
+    for k in ("embedding", "lm_heads", "attention", "mamba", "norms", "dense_ffn", "router", "experts", "mod_router"):
+        print(f"  {k:12s} {format_params(b[k]):>10s}  {100 * b[k] / max(b['total'], 1):5.1f} %")
+    print(f"  {'total':12s} {format_params(r['total']):>10s}  ({r['total']:,}; tied head counted once)")
+    print(f"  {'active':12s} {format_params(r['active']):>10s}  sparsity {100 * r['sparsity']:.1f} %")
+    print(f"memory per GPU, bf16 weights and gradients replicated, optimizer state over {world} ranks ({optimizer})")
+    print(f"  weights {r['weights_gb']:.2f} GB  gradients {r['grads_gb']:.2f} GB  optimizer {r['optimizer_gb_per_rank']:.2f} GB"
+          f"  activations (no recompute, micro-batch {micro_batch}) {r['activations_gb_no_recompute']:.2f} GB")
+    print(f"  total {r['per_gpu_total_gb']:.2f} GB of 180 GB")
+    print("=" * 64)
+    return {"analysis": r, "breakdown": b}
+
+
 def design(target_total: float, target_active: float, tol: float = 0.1, limit: int = 10):
     from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig
     out = []
@@ -73,7 +143,4 @@ if __name__ == "__main__":
         from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig
         from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml, model_config_tolerant
         cfg = model_config_tolerant(load_yaml(a.config)) if a.config else AdvancedMoEConfig()
-        r = analyze(cfg, a.world)
-        for k, v in r.items():
-            if k != "layers":
-                print(f"{k:32s} {v:,.3f}" if isinstance(v, float) else f"{k:32s} {v:,}")
+        print_report(cfg, a.world)
