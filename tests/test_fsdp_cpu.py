@@ -168,6 +168,14 @@ def _ep_worker(rank, world, tmp):
     for (n, pa), (_, pb) in zip(ma.named_parameters(), mb.named_parameters()):
         if getattr(pa, "_kmoe_expert_parallel", False):
             assert torch.allclose(pa, pb, atol=2e-3), n
+    # checkpoint of both pools, restored into a freshly built job: the next step gives the same loss
+    from kolmogorov_moe_architecture_b200.training import checkpoint as ckpt
+    d = ckpt.save_param_sharded(tmp, 3, eb.dp, {"step": 3}, rank, ep_rank=mesh.ep_rank, ep_size=2)
+    mc, _, ec = build(True)
+    st = ckpt.load_param_sharded(d, ec.dp, rank, ep_rank=mesh.ep_rank, ep_size=2)
+    assert st["step"] == 3
+    ids = torch.randint(0, 256, (2, 32), generator=g)
+    assert abs(eb.step(ids).loss_value() - ec.step(ids).loss_value()) < 1e-4
 
 
 def test_sharded_dense_parameters_with_expert_parallel_experts(tmp_path):
