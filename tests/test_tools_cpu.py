@@ -129,3 +129,28 @@ def test_expert_choice_scatter_benchmark_variants_agree():
     b = bec.scatter_vectorised(torch.zeros(B, S, d), w_out, idx)
     assert torch.allclose(a, b, atol=1e-6)
     bec.main(["--device", "cpu"])
+
+
+def test_bench_clock_sampler_parses_nvidia_smi_lines_and_flags():
+    """The benchmark's clock record: median SM clock under load, maximum clock, and the throttle reasons that
+    were active in any sample; the argument defaults are the contract's (1 GPU, >= 3 warm-up steps)."""
+    import bench
+    s = bench.ClockSampler(0)
+    s.proc = type("P", (), {"terminate": lambda self: None})()
+    s.lines = ["0, 1965, 1965, 950.1, 0x0000000000000004, Not Active, Not Active, Not Active, Active",
+               "0, 1890, 1965, 990.0, 0x0000000000000004, Not Active, Not Active, Not Active, Active",
+               "0, 1920, 1965, 980.0, 0x0000000000000000, Not Active, Not Active, Not Active, Not Active",
+               "garbage line", "0, [N/A], 1965, 1, 0, Not Active, Not Active, Not Active, Not Active"]
+    out = s.stop()
+    assert out == {"sm_mhz": 1920.0, "sm_max_mhz": 1965.0, "samples": 3, "reasons": ["sw_power_cap"]}
+    s.lines = ["0, 1200, 1965, 500, 0x8, Active, Active, Not Active, Not Active"]
+    assert s.stop()["reasons"] == ["hw_slowdown", "hw_thermal_slowdown"]
+    none = bench.ClockSampler(0).stop()
+    assert none["sm_mhz"] is None
+    import sys
+    argv, sys.argv = sys.argv, ["bench.py"]
+    try:
+        a = bench.parse_args()
+    finally:
+        sys.argv = argv
+    assert (a.gpus, a.impl, a.micro_batch, a.seq_len, a.layers) == (1, "ours", 4, 2048, 32) and a.warmup >= 3
