@@ -306,6 +306,8 @@ class FullyShardedDataParallel:
             self.root.gathered, self.root.inflight, self.root.ready = False, False, None
 
     def _begin_forward(self) -> None:
+        if self._in_backward:                   # a new micro-batch: its gradients are reduced and added again
+            self._arm()
         self._in_backward = False
         if self.root is not None:
             self._gather(self.root)

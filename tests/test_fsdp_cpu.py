@@ -180,3 +180,34 @@ def _ep_worker(rank, world, tmp):
 
 def test_sharded_dense_parameters_with_expert_parallel_experts(tmp_path):
     run_ranks(_ep_worker, 2, str(tmp_path))
+
+
+def _accum_worker(rank, world, tmp):
+    """Two micro-batches per step: each one's gradients are reduced and added to the shards (the sharded plan
+    against the replicated plan with the same accumulation)."""
+    import kolmogorov_moe_architecture_b200 as kmoe
+    from kolmogorov_moe_architecture_b200.parallel.fsdp import FullyShardedDataParallel
+    from kolmogorov_moe_architecture_b200.parallel.zero import ShardedDataParallel
+    from kolmogorov_moe_architecture_b200.training.engine import TrainEngine
+    cfg = _tiny_cfg()
+    torch.manual_seed(0)
+    a = kmoe.MoETransformer(cfg, verbose=False)
+    b = kmoe.MoETransformer(cfg, verbose=False)
+    b.load_state_dict(a.state_dict())
+    pa = ShardedDataParallel(a, optimizer_kind="adamw", adamw_lr=1e-2, weight_decay=0.01)
+    pb = FullyShardedDataParallel(b, lr=1e-2, weight_decay=0.01, overlap=True)
+    ea = TrainEngine(a, pa.optimizer, grad_clip=1.0, grad_accum=2, dp=pa)
+    eb = TrainEngine(b, pb.optimizer, grad_clip=1.0, grad_accum=2, dp=pb)
+    g = torch.Generator().manual_seed(7 + rank)
+    for step in range(3):
+        ids = torch.randint(0, 256, (4, 32), generator=g)          # two micro-batches of two sequences
+        la, lb = ea.step(ids).loss_value(), eb.step(ids).loss_value()
+        assert abs(la - lb) < 1e-3, (step, la, lb)
+    full = pb.full_state_dict()
+    ref = dict(a.named_parameters(remove_duplicate=False))
+    assert max((full[n] - ref[n].detach()).abs().max().item() for n in full) < 2e-3
+    assert all(p.numel() == 0 for p in b.layers.parameters())      # every block is released again
+
+
+def test_fsdp_gradient_accumulation_reduces_every_micro_batch(tmp_path):
+    run_ranks(_accum_worker, 2, str(tmp_path))
