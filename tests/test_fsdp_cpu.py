@@ -211,3 +211,32 @@ def _accum_worker(rank, world, tmp):
 
 def test_fsdp_gradient_accumulation_reduces_every_micro_batch(tmp_path):
     run_ranks(_accum_worker, 2, str(tmp_path))
+
+
+def _recompute_worker(rank, world, tmp):
+    """Activation recomputation: a block's forward runs again inside the backward pass, with its parameters
+    gathered for it and kept until its gradients are reduced."""
+    import kolmogorov_moe_architecture_b200 as kmoe
+    from kolmogorov_moe_architecture_b200.parallel.fsdp import FullyShardedDataParallel
+    from kolmogorov_moe_architecture_b200.parallel.zero import ShardedDataParallel
+    from kolmogorov_moe_architecture_b200.training.engine import TrainEngine
+    cfg = _tiny_cfg()
+    cfg.use_gradient_checkpointing = True
+    torch.manual_seed(0)
+    a = kmoe.MoETransformer(cfg, verbose=False)
+    b = kmoe.MoETransformer(cfg, verbose=False)
+    b.load_state_dict(a.state_dict())
+    pa = ShardedDataParallel(a, optimizer_kind="adamw", adamw_lr=1e-2, weight_decay=0.01)
+    pb = FullyShardedDataParallel(b, lr=1e-2, weight_decay=0.01, overlap=True)
+    ea = TrainEngine(a, pa.optimizer, grad_clip=1.0, dp=pa)
+    eb = TrainEngine(b, pb.optimizer, grad_clip=1.0, dp=pb)
+    g = torch.Generator().manual_seed(9 + rank)
+    for step in range(3):
+        ids = torch.randint(0, 256, (2, 32), generator=g)
+        la, lb = ea.step(ids).loss_value(), eb.step(ids).loss_value()
+        assert abs(la - lb) < 1e-3, (step, la, lb)
+    assert all(p.numel() == 0 for p in b.layers.parameters())
+
+
+def test_fsdp_with_activation_recomputation(tmp_path):
+    run_ranks(_recompute_worker, 2, str(tmp_path))
