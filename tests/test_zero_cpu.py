@@ -17,17 +17,17 @@ def _data(world):
     return torch.randint(0, 128, (3, 2 * world, 32), generator=g)     # steps x global batch x seq
 
 
-def _worker(rank, world, kind, ref_state):
+def _worker(rank, world, kind, ref_state, accum=1):
     from kolmogorov_moe_architecture_b200 import MoETransformer
     from kolmogorov_moe_architecture_b200.parallel.zero import ShardedDataParallel
     from kolmogorov_moe_architecture_b200.training.engine import TrainEngine
     torch.manual_seed(0)
     model = MoETransformer(_cfg(), verbose=False)
     dp = ShardedDataParallel(model, optimizer_kind=kind, lr=1e-2, adamw_lr=1e-2)
-    eng = TrainEngine(model, dp.optimizer, grad_clip=1.0, dp=dp)
+    eng = TrainEngine(model, dp.optimizer, grad_clip=1.0, grad_accum=accum, dp=dp)
     data = _data(world)
     for s in range(3):
-        eng.step(data[s, 2 * rank: 2 * rank + 2])
+        eng.step(data[s, 2 * rank: 2 * rank + 2])       # with accum = 2: two micro-batches of one sequence
     sd = model.state_dict()
     for k, v in ref_state.items():
         assert torch.allclose(sd[k], v, atol=5e-4, rtol=1e-3), (k, (sd[k] - v).abs().max())
@@ -54,6 +54,12 @@ def _reference(kind, world):
 
 def test_zero_matches_single_process_adamw_2ranks():
     run_ranks(_worker, 2, "adamw", _reference("adamw", 2))
+
+
+def test_zero_with_gradient_accumulation_reduces_once_per_step():
+    """Micro-batches of equal size: accumulating two of them is the same step as one batch of both, and the
+    ranks exchange gradients only after the last one."""
+    run_ranks(_worker, 2, "adamw", _reference("adamw", 2), 2)
 
 
 def test_zero_matches_single_process_muon_3ranks():
