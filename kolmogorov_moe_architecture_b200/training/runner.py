@@ -281,6 +281,9 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
     save_every = spec.save_interval if spec.save_interval is not None else train_cfg["save_interval"]
     logger = MetricLogger(spec.jsonl, spec.wandb, spec.wandb_project, spec.wandb_run, y, rank=rank)
     timer = PhaseTimer(enabled=spec.profile, device=device)
+    if spec.profile and os.environ.get("KMOE_NVTX_BLOCKS", "0") == "1":
+        from ..utils.profiling import annotate_blocks
+        annotate_blocks(model)                 # per-layer ranges for a timeline capture
     dog = StepWatchdog(spec.step_deadline_s, lambda idle: print(f"[watchdog] no step for {idle:.0f}s on rank {rank}",
                                                                 flush=True)).start() if spec.step_deadline_s > 0 else None
     if is_main:

@@ -4,6 +4,8 @@
   events on the compute stream, reduced as max over ranks; the host-clock ``TimingStats`` of the
   reference (train_custom.py:597-640) without the device synchronisations inside the step.
 * ``nvtx_range``  - context manager adding an NVTX range (no-op when CUDA is absent).
+* ``annotate_blocks`` - NVTX ranges around every transformer block's forward and backward (and around
+  its sequence mixer and FFN), so a timeline shows which layer a kernel belongs to.
 * ``device_timed``- run a callable K times between CUDA events with barrier + synchronize on both
   sides; returns milliseconds per call (max over ranks).
 * ``roofline``    - achieved / peak against the measured peaks file.
@@ -30,6 +32,47 @@ def nvtx_range(name: str):
     finally:
         if on:
             torch.cuda.nvtx.range_pop()
+
+
+class BlockAnnotations:
+    """Handle returned by ``annotate_blocks``: ``remove()`` takes the hooks off again; ``events`` counts
+    the ranges opened (forward, backward) - also without a GPU, where the ranges themselves are no-ops."""
+
+    def __init__(self):
+        self.handles = []
+        self.events = {"forward": 0, "backward": 0}
+
+    def remove(self) -> None:
+        for h in self.handles:
+            h.remove()
+        self.handles.clear()
+
+
+def annotate_blocks(model, parts=("seq_layer", "ffn")) -> BlockAnnotations:
+    """Forward ranges ``L{i}`` / ``L{i}.seq_layer`` / ``L{i}.ffn`` and backward ranges ``L{i}.bwd`` on every
+    block of ``model.layers``.  The backward range opens when the block's output gradient is ready and
+    closes when its input gradient has been produced."""
+    ann = BlockAnnotations()
+    on = torch.cuda.is_available()
+
+    def push(name, kind):
+        ann.events[kind] += 1
+        if on:
+            torch.cuda.nvtx.range_push(name)
+
+    def pop():
+        if on:
+            torch.cuda.nvtx.range_pop()
+
+    base = getattr(model, "_orig_mod", model)
+    for i, layer in enumerate(base.layers):
+        mods = [(f"L{i}", layer)] + [(f"L{i}.{p}", getattr(layer, p)) for p in parts if getattr(layer, p, None) is not None]
+        for name, m in mods:
+            ann.handles.append(m.register_forward_pre_hook(lambda mod, a, n=name: push(n, "forward")))
+            ann.handles.append(m.register_forward_hook(lambda mod, a, o: pop()))
+        ann.handles.append(layer.register_full_backward_pre_hook(lambda mod, g, n=f"L{i}.bwd": push(n, "backward")))
+        ann.handles.append(layer.register_full_backward_hook(lambda mod, gi, go: pop()))
+    return ann
 
 
 class PhaseTimer:

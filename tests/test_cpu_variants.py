@@ -208,3 +208,17 @@ def test_hf_wrapper_signature_and_prefixed_checkpoint_keys(tmp_path):
     Callback(4).on_log(None, None, None, logs=logs)
     assert logs["true_loss"] == 2.0 and logs["accumulated_loss"] == 8.0
     assert hasattr(MoETrainer, "create_optimizer") and hasattr(MoETrainer, "compute_loss")
+
+
+def test_block_annotations_open_a_range_per_block_and_direction():
+    from kolmogorov_moe_architecture_b200.utils.profiling import annotate_blocks
+    model, cfg = _tiny_model()
+    ann = annotate_blocks(model)
+    ids = torch.randint(0, 128, (2, 16))
+    model.train()
+    model(ids, labels=ids, return_logits=False)["loss"].backward()
+    L = len(model.layers)
+    assert ann.events == {"forward": 3 * L, "backward": L}       # block + mixer + FFN forward, block backward
+    ann.remove()
+    model(ids, labels=ids, return_logits=False)["loss"].backward()
+    assert ann.events == {"forward": 3 * L, "backward": L}
