@@ -222,8 +222,9 @@ class FullyShardedDataParallel:
             from .p2p import p2p_available
             if p2p_available(self.device):
                 return "p2p"
-            if transport == "p2p":
-                raise RuntimeError("p2p transport asked for, but symmetric memory is not available")
+        if transport == "p2p":
+            raise RuntimeError("p2p transport asked for: it needs bf16 parameters on GPUs of an NCCL group "
+                               "with symmetric memory")
         return self.backend
 
     @contextlib.contextmanager
