@@ -50,6 +50,8 @@ def main():
     ap.add_argument("--top-k", type=int, default=2)
     ap.add_argument("--capacity-factor", type=float, default=1.25,
                     help="each source rank keeps at most cf * tokens * k / E assignments per expert (0 = no dropping)")
+    ap.add_argument("--moe-dtype", default="bf16", choices=["bf16", "mxfp8"],
+                    help="number format of the expert GEMMs (rows cross NVLink in bf16 either way)")
     ap.add_argument("--out", default=None)
     a = ap.parse_args()
     rank, ws = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -79,14 +81,14 @@ def main():
         x.grad = w1.grad = w2.grad = w3.grad = wts.grad = None
 
     def fused():
-        ep_p2p.expert_parallel_ffn_fused(x, idx, wts, w1, w2, w3, E, None, keep).backward(go)
+        ep_p2p.expert_parallel_ffn_fused(x, idx, wts, w1, w2, w3, E, None, keep, moe_dtype=a.moe_dtype).backward(go)
         clear()
 
     def fused_fwd():
         with torch.no_grad():
-            ep_p2p.expert_parallel_ffn_fused(x, idx, wts, w1, w2, w3, E, None, keep)
+            ep_p2p.expert_parallel_ffn_fused(x, idx, wts, w1, w2, w3, E, None, keep, moe_dtype=a.moe_dtype)
 
-    local_fn = lambda xx, ii, ww, kk: ops.grouped_swiglu(xx, w1, w2, w3, ii, ww, kk)
+    local_fn = lambda xx, ii, ww, kk: ops.grouped_swiglu(xx, w1, w2, w3, ii, ww, kk, a.moe_dtype)
 
     def a2a():
         ep.expert_parallel_ffn(x, idx, wts, local_fn, E, None, keep=keep).backward(go)
@@ -101,7 +103,7 @@ def main():
     dist.all_reduce(kept_t)
     flops_fwd = 2.0 * (kept_t.item() / ws) * 3 * d * f   # mean per rank; the busiest rank does more (see live rows)
     res = {"world": ws, "tokens_per_rank": T, "d_model": d, "d_ff": f, "experts": E, "top_k": k,
-           "capacity_factor": a.capacity_factor, "kept_assignments_mean_per_rank": kept_t.item() / ws}
+           "capacity_factor": a.capacity_factor, "moe_dtype": a.moe_dtype, "kept_assignments_mean_per_rank": kept_t.item() / ws}
     for name, fn, mult in (("fused_p2p fwd", fused_fwd, 1), ("fused_p2p fwd+bwd", fused, 3),
                            ("all_to_all fwd", a2a_fwd, 1), ("all_to_all fwd+bwd", a2a, 3)):
         ms = timed(fn)
