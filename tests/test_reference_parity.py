@@ -128,3 +128,47 @@ def test_schedule_matches(ref):
     for _ in range(60):
         assert abs(o.step() - r.step()) < 1e-12
     assert o.state_dict() == r.state_dict()
+
+
+@pytest.mark.parametrize("fsdp_mode", [False, True])
+def test_hybrid_optimizer_partition_matches(ref, fsdp_mode, monkeypatch):
+    """Which tensors go to Muon and which to AdamW: the reference decides by name and dimension, and by name
+    alone when it believes it runs distributed (it looks at WORLD_SIZE / LOCAL_RANK)."""
+    from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig, MoETransformer
+    from kolmogorov_moe_architecture_b200.training.muon_optimizer import split_muon_params
+    for k in ("WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(k, raising=False)
+    if fsdp_mode:
+        monkeypatch.setenv("WORLD_SIZE", "2")
+    torch.manual_seed(0)
+    with contextlib.redirect_stdout(io.StringIO()):
+        rmodel = ref["transformer"].MoETransformer(ref["config"].AdvancedMoEConfig(**KW))
+        ropt = ref["muon"].get_muon_optimizer(rmodel, lr=1e-3)
+    ours = MoETransformer(AdvancedMoEConfig(mamba_impl="simple", **KW), verbose=False)
+    rnames = {id(p): n for n, p in rmodel.named_parameters()}
+    ref_muon = {rnames[id(p)] for g in ropt.muon_opt.param_groups for p in g["params"]}
+    ref_adam = {rnames[id(p)] for g in ropt.adamw_opt.param_groups for p in g["params"]}
+    mu, ad = split_muon_params(ours, fsdp_mode=fsdp_mode)
+    onames = {id(p): n for n, p in ours.named_parameters()}
+    assert {onames[id(p)] for p in mu} == ref_muon
+    assert {onames[id(p)] for p in ad} == ref_adam
+
+
+def test_memory_mapped_dataset_matches(ref, tmp_path):
+    """Same ``.bin`` file, same samples: fixed strides of ``seq_len + n_pred_tokens`` tokens, labels equal to
+    the inputs (the model shifts them itself)."""
+    import numpy as np
+    from kolmogorov_moe_architecture_b200.data import DolmaMemoryMappedDataset, write_token_file
+    with contextlib.redirect_stdout(io.StringIO()):
+        import moe_arch.data.dolma_dataset as rd
+    path = str(tmp_path / "train.bin")
+    toks = np.random.default_rng(0).integers(0, 50000, size=1000)
+    write_token_file(path, toks)
+    with contextlib.redirect_stdout(io.StringIO()):
+        r = rd.DolmaMemoryMappedDataset(path, seq_len=32, n_pred_tokens=4)
+    o = DolmaMemoryMappedDataset(path, seq_len=32, n_pred_tokens=4)
+    assert len(o) == len(r) == 1000 // 36
+    for i in (0, 5, len(o) - 1):
+        a, b = o[i], r[i]
+        assert torch.equal(a["input_ids"], b["input_ids"]) and torch.equal(a["labels"], b["labels"])
+        assert a["input_ids"].dtype == torch.int64 and a["input_ids"].shape == (32,)
