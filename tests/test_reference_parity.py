@@ -172,3 +172,24 @@ def test_memory_mapped_dataset_matches(ref, tmp_path):
         a, b = o[i], r[i]
         assert torch.equal(a["input_ids"], b["input_ids"]) and torch.equal(a["labels"], b["labels"])
         assert a["input_ids"].dtype == torch.int64 and a["input_ids"].shape == (32,)
+
+
+def test_expert_parallel_layer_single_process_matches(ref):
+    """``ExpertParallelMoE`` with all experts on one rank: same router rule (softmax over the top-k logits),
+    same experts, same auxiliary loss as the reference layer."""
+    from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig
+    from kolmogorov_moe_architecture_b200.models.sparse_moe import ExpertParallelMoE
+    with contextlib.redirect_stdout(io.StringIO()):
+        import moe_arch.model.sparse_moe as rsm
+        torch.manual_seed(0)
+        r = rsm.ExpertParallelMoE(ref["config"].AdvancedMoEConfig(**dict(KW, moe_implementation="expert_parallel")), 1)
+    o = ExpertParallelMoE(AdvancedMoEConfig(**dict(KW, moe_implementation="expert_parallel")), 1)
+    missing, unexpected = o.load_state_dict(r.state_dict(), strict=True)
+    assert not missing and not unexpected
+    x = torch.randn(2, 16, 64, generator=torch.Generator().manual_seed(2))
+    r.train(); o.train()
+    with contextlib.redirect_stdout(io.StringIO()):
+        yr = r(x)
+    yo = o(x)
+    assert torch.allclose(yo, yr, atol=1e-5), (yo - yr).abs().max()
+    assert abs(float(o.aux_loss) - float(r.aux_loss)) < 1e-6
