@@ -193,3 +193,34 @@ def test_expert_parallel_layer_single_process_matches(ref):
     yo = o(x)
     assert torch.allclose(yo, yr, atol=1e-5), (yo - yr).abs().max()
     assert abs(float(o.aux_loss) - float(r.aux_loss)) < 1e-6
+
+
+def test_stand_alone_moe_layer_variants_match(ref):
+    """The stand-alone layer classes of ``fused_moe.py`` and ``triton_moe.py`` that run without a GPU: same
+    state dict keys, same outputs."""
+    from kolmogorov_moe_architecture_b200.models import fused_moe as of, triton_moe as ot
+    with contextlib.redirect_stdout(io.StringIO()):
+        import moe_arch.model.fused_moe as rf
+        import moe_arch.model.triton_moe as rt
+    torch.manual_seed(0)
+    T, d, f, E, k = 20, 16, 32, 4, 2
+    x = torch.randn(T, d)
+    w, idx = torch.softmax(torch.randn(T, E), -1).topk(k, dim=-1)
+    w = w / w.sum(-1, keepdim=True)
+    for rcls, ocls in ((rf.OptimizedGroupedExperts, of.OptimizedGroupedExperts), (rt.BatchedMoE, ot.BatchedMoE),
+                       (rt.BatchedMoEOptimized, ot.BatchedMoEOptimized)):
+        with contextlib.redirect_stdout(io.StringIO()):
+            r = rcls(E, d, f)
+        o = ocls(E, d, f)
+        assert not any(o.load_state_dict(r.state_dict(), strict=True))
+        with contextlib.redirect_stdout(io.StringIO()):
+            yr = r(x, idx, w)
+        assert torch.allclose(o(x, idx, w), yr, atol=1e-5), rcls.__name__
+    with contextlib.redirect_stdout(io.StringIO()):
+        r = rf.FusedSparseMoE(d, f, E, k)
+    o = of.FusedSparseMoE(d, f, E, k)
+    assert not any(o.load_state_dict(r.state_dict(), strict=True))
+    xb = torch.randn(2, 10, d)
+    with contextlib.redirect_stdout(io.StringIO()):
+        yr = r(xb)
+    assert torch.allclose(o(xb), yr, atol=1e-5)
