@@ -154,3 +154,29 @@ def test_bench_clock_sampler_parses_nvidia_smi_lines_and_flags():
     finally:
         sys.argv = argv
     assert (a.gpus, a.impl, a.micro_batch, a.seq_len, a.layers) == (1, "ours", 4, 2048, 32) and a.warmup >= 3
+
+
+def test_every_shipped_config_builds_a_model_on_the_meta_device():
+    """All YAML files under configs/ (the Accelerate launcher file aside) go through both loaders and describe
+    a model that can be instantiated; every one has the training sections the entry points read."""
+    import glob
+    from kolmogorov_moe_architecture_b200 import MoETransformer
+    from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml, model_config_tolerant, section
+    paths = sorted(p for p in glob.glob(os.path.join(ROOT, "configs", "*.yaml")) if not p.endswith("fsdp_config.yaml"))
+    assert len(paths) >= 18
+    for p in paths:
+        y = load_yaml(p)
+        cfg = model_config_tolerant(y)
+        with torch.device("meta"):
+            m = MoETransformer(cfg, verbose=False)
+        c = m.count_parameters()
+        assert c["total"] > 0 and 0 < c["active"] <= c["total"], p
+        tr = section(y, "training")
+        assert {"batch_size", "gradient_accumulation_steps", "max_lr", "warmup_steps"} <= set(tr), p
+        assert section(y, "optimizer").get("type", "adamw") in ("muon", "adamw", "adam"), p
+    big = model_config_tolerant(load_yaml(os.path.join(ROOT, "configs", "bench_5b_hybrid.yaml")))
+    with torch.device("meta"):
+        n = sum(p.numel() for p in MoETransformer(big, verbose=False).parameters())
+    assert abs(n - 5.87e9) < 0.01e9
+    acc = yaml.safe_load(open(os.path.join(ROOT, "configs", "fsdp_config.yaml")))
+    assert acc["distributed_type"] == "FSDP" and acc["fsdp_config"]["fsdp_sharding_strategy"] == "FULL_SHARD"
