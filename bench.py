@@ -17,7 +17,6 @@ import os
 import subprocess
 import sys
 import threading
-import time
 
 import torch
 

@@ -2,8 +2,7 @@
 reference's ``Experiments/sparse_distillation/dynamic_experts.py``)."""
 from __future__ import annotations
 
-import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional
 
 import torch

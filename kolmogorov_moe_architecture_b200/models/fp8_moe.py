@@ -10,14 +10,12 @@ buffers) are kept so reference checkpoints load.
 from __future__ import annotations
 
 import math
-from typing import Optional
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from ..ops import eager
-from ..ops.mxfp8 import fake_quant_mx, grouped_swiglu_mxfp8, linear_mx
+from ..ops.mxfp8 import grouped_swiglu_mxfp8, linear_mx
 
 FP8_E4M3 = torch.float8_e4m3fn
 FP8_E5M2 = torch.float8_e5m2

@@ -12,7 +12,6 @@ import os
 from typing import List, Optional, Sequence
 
 import torch
-import torch.nn.functional as F
 
 from . import eager
 from .loader import require_ext

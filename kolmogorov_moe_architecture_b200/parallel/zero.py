@@ -36,7 +36,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-from ..training.muon_optimizer import _EXCLUDE, HybridOptimizer, Muon
+from ..training.muon_optimizer import _EXCLUDE, Muon
 from ..training.optim_factory import make_adamw
 
 _ALIGN = 128   # elements; keeps every tensor 256-byte aligned inside a segment

@@ -18,7 +18,7 @@ batched call instead of one Python-level iteration per parameter.
 from __future__ import annotations
 
 import os
-from typing import Dict, Iterable, List, Optional
+from typing import Optional
 
 import torch
 from torch.optim import Optimizer

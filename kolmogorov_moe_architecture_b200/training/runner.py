@@ -29,7 +29,7 @@ import torch
 
 from ..config import AdvancedMoEConfig
 from ..data import (DolmaStreamingDataset, PackedDocumentDataset, PinnedPrefetcher, SyntheticTokenDataset,
-                    TokenizerWrapper, PackedDocs, document_attention_mask)
+                    TokenizerWrapper, PackedDocs)
 from ..models.transformer import MoETransformer
 from ..parallel import mesh as pmesh
 from ..utils.config_io import load_yaml, model_config_strict, model_config_tolerant, section
@@ -40,7 +40,6 @@ from . import checkpoint as ckpt
 from .engine import TrainEngine
 from .lr_schedule import CosineScheduleWithWarmup
 from .muon_optimizer import CombinedOptimizer, Muon8bit, get_muon_optimizer
-from .optim_factory import make_adamw
 
 
 @dataclass

@@ -2,7 +2,6 @@
 replicated-parameter plan (same ranks, same data, AdamW) step for step; parameters are released between
 uses; full and sharded state round-trips."""
 import os
-import sys
 
 import torch
 
