@@ -1,6 +1,6 @@
 """Small single-kernel workloads for Nsight Compute captures.
 
-    python benchmarks/ncu_cases.py --case gemm|moe|attn|scan|adamw|ce|mxfp8|mod|ep_dispatch|ep_gemm2 [--launches 4]
+    python benchmarks/ncu_cases.py --case gemm|moe|attn|scan|adamw|allgather|ce|mxfp8|mod|ep_dispatch|ep_gemm2 [--launches 4]
 
 Each case holds well under 2 GB on the device, uses operands larger than L2 where the kernel is
 bandwidth-sensitive, and launches the kernel of interest a handful of times so that
@@ -57,6 +57,14 @@ def main():
         coef = torch.ones(1, device="cuda")
         for s in range(1, n + 1):
             torch.ops.kmoe.p2p_adamw_allgather([p.data_ptr()], g, m, v, 0, 1, 0, N_, 3e-4, 0.9, 0.95, 1e-8, 0.01, s, coef, 0)
+    elif a.case == "allgather":
+        # the parameter-gather kernel of the sharded plan in a one-rank "group": it reads a shard and stores it
+        # into the gather buffer (with more ranks the same stores go to every peer's buffer)
+        N_ = 256 * 2**20
+        shard, buf = bf(N_), torch.empty(N_, dtype=torch.bfloat16, device="cuda")
+        for blocks in (32, 0)[: max(1, min(2, n))]:
+            for _ in range(max(1, n // 2)):
+                torch.ops.kmoe.p2p_allgather([buf.data_ptr()], 0, 1, 0, N_, 0, shard, blocks)
     elif a.case == "ce":
         R, V = 2048, 50304
         logits = bf(R, V, sc=1.0)
