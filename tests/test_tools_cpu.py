@@ -47,13 +47,13 @@ def test_diagnose_training_reports_every_section(tiny):
     from tools import diagnose_training as dt
     rep = dt.main(["--checkpoint", tiny["checkpoint"], "--config", tiny["config"], "--device", "cpu", "--synthetic",
                    "--eval-batches", "2"])
-    assert set(rep) >= {"router", "routing_in_model", "movement", "trainability", "evaluation", "gradients", "verdict"}
+    assert set(rep) >= {"router", "routing_in_model", "movement", "trainability", "evaluation", "gradients", "findings"}
     assert rep["trainability"]["trainable"] == rep["trainability"]["total"]
     assert abs(rep["evaluation"]["lm_loss"] - rep["evaluation"]["uniform_loss"]) < 1.0   # untrained model
     assert rep["routing_in_model"] and all(0.0 <= s["gini"] <= 1.0 for s in rep["routing_in_model"].values())
     # the checkpoint is the seed-0 initialisation itself: nothing has moved
     assert max(rep["movement"].values()) < 1e-6
-    assert any("did not move" in line for line in rep["verdict"])
+    assert any("did not move" in line for line in rep["findings"])
     assert dt.calculate_gini([1, 1, 1, 1]) == 0.0 and dt.calculate_gini([0, 0, 0, 8]) == 0.75
 
 

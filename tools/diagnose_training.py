@@ -117,7 +117,7 @@ def run_evaluation(model, cfg, n_batches: int = 8, device: str = "cpu", data: st
             "uniform_loss": math.log(cfg.vocab_size), "batches": n, "source": data or "random tokens"}
 
 
-def verdict(report: dict) -> list:
+def findings(report: dict) -> list:
     """Plain-language findings from the collected figures."""
     issues = []
     bad = [i for i, s in report.get("routing_in_model", {}).items() if s["is_collapsed"]]
@@ -180,9 +180,9 @@ def main(argv=None):
     print("[sample]", greedy_sample(model, ids[:1, :8], 12)[0].tolist())
     report = {"router": stats, "collapsed": collapsed, "routing_in_model": in_model, "movement": mv,
               "trainability": tr, "evaluation": ev, "gradients": grads}
-    report["verdict"] = verdict(report)
-    for line in report["verdict"]:
-        print("[verdict]", line)
+    report["findings"] = findings(report)
+    for line in report["findings"]:
+        print("[finding]", line)
     return report
 
 
