@@ -1,0 +1,91 @@
+"""Properties of the routing definitions in ``ops/eager.py`` - the oracles the routing kernels are compared
+against - checked on generated shapes and values."""
+import math
+
+import torch
+from hypothesis import given, settings, strategies as st
+
+from kolmogorov_moe_architecture_b200.ops import eager
+
+SET = settings(max_examples=40, deadline=None)
+
+
+@SET
+@given(T=st.integers(1, 60), E=st.integers(2, 9), k=st.integers(1, 3), seed=st.integers(0, 10_000))
+def test_token_choice_weights_sum_to_one_and_pick_distinct_largest(T, E, k, seed):
+    k = min(k, E)
+    logits = torch.randn(T, E, generator=torch.Generator().manual_seed(seed))
+    w, idx = eager.topk_softmax_route(logits, k)
+    assert w.shape == idx.shape == (T, k)
+    assert torch.allclose(w.sum(-1), torch.ones(T), atol=1e-5) and (w > 0).all()
+    assert all(len(set(r)) == k for r in idx.tolist())                      # distinct experts per token
+    kth = logits.gather(1, idx).min(-1).values
+    not_picked = torch.ones(T, E, dtype=torch.bool).scatter_(1, idx, False)
+    assert (logits.masked_fill(~not_picked, -math.inf).max(-1).values <= kth + 1e-6).all()
+    _, _, aux, counts = eager.route_topk(logits, k, 1.0, 0.0)
+    assert int(counts.sum()) == T * k and float(aux) >= 0.0
+
+
+@SET
+@given(T=st.integers(1, 80), E=st.integers(1, 8), k=st.integers(1, 3), cap=st.integers(0, 30), seed=st.integers(0, 10_000))
+def test_capacity_mask_keeps_the_first_assignments_of_each_expert(T, E, k, cap, seed):
+    idx = torch.randint(0, E, (T, k), generator=torch.Generator().manual_seed(seed))
+    keep = eager.capacity_keep_mask(idx, E, cap)
+    flat, kf = idx.reshape(-1), keep.reshape(-1)
+    for e in range(E):
+        pos = (flat == e).nonzero().flatten()
+        assert int(kf[pos].sum()) == min(cap, pos.numel())
+        assert kf[pos[:cap]].all() and not kf[pos[cap:]].any()             # lowest (token, slot) order first
+
+
+@SET
+@given(B=st.integers(1, 4), S=st.integers(2, 40), frac=st.floats(0.1, 1.0), seed=st.integers(0, 10_000))
+def test_mod_router_keeps_k_tokens_in_order_with_softmax_weights(B, S, frac, seed):
+    k = max(1, min(S, int(S * frac)))
+    logits = torch.randn(B, S, generator=torch.Generator().manual_seed(seed))
+    sidx, w, topi = eager.mod_route(logits, k)
+    assert sidx.shape == w.shape == (B, k)
+    assert (sidx[:, 1:] > sidx[:, :-1]).all()                              # ascending, distinct positions
+    assert torch.equal(sidx.sort(-1).values, topi.sort(-1).values)
+    assert torch.allclose(w, torch.softmax(logits.gather(1, sidx), -1), atol=1e-6)
+    dropped = torch.ones(B, S, dtype=torch.bool).scatter_(1, sidx, False)
+    if k < S:
+        assert (logits.masked_fill(~dropped, -math.inf).max(-1).values <= logits.gather(1, sidx).min(-1).values).all()
+    # combine: positions that were not kept pass the residual through unchanged
+    d = 3
+    res = torch.randn(B, S, d)
+    proc = torch.randn(B, k, d)
+    out = eager.mod_combine(res, proc, w, sidx)
+    assert torch.equal(out[dropped], res[dropped])
+    assert torch.allclose(eager.mod_gather(out - res, sidx), proc * w.unsqueeze(-1), atol=1e-6)
+
+
+@SET
+@given(B=st.integers(1, 3), S=st.integers(2, 30), E=st.integers(1, 5), cf=st.floats(0.5, 2.0), seed=st.integers(0, 10_000))
+def test_expert_choice_each_expert_takes_its_capacity(B, S, E, cf, seed):
+    cap = min(S, int(math.ceil(S * cf / E)))
+    logits = torch.randn(B, S, E, generator=torch.Generator().manual_seed(seed))
+    w, tok = eager.expert_choice_route(logits, cap)
+    assert w.shape == tok.shape == (B, E, cap)
+    assert torch.allclose(w.sum(-1), torch.ones(B, E), atol=1e-4)
+    assert all(len(set(r)) == cap for b in tok.tolist() for r in b)        # an expert takes a token once
+    probs = torch.softmax(logits.transpose(1, 2), -1)
+    kth = probs.gather(2, tok).min(-1).values
+    rest = probs.scatter(2, tok, -1.0).max(-1).values
+    assert (rest <= kth + 1e-7).all()
+
+
+@SET
+@given(T=st.integers(1, 40), E=st.integers(2, 6), seed=st.integers(0, 10_000))
+def test_dropped_assignments_contribute_nothing(T, E, seed):
+    g = torch.Generator().manual_seed(seed)
+    d, f, k = 8, 12, 2
+    x = torch.randn(T, d, generator=g)
+    w1, w2, w3 = torch.randn(E, d, f, generator=g), torch.randn(E, d, f, generator=g), torch.randn(E, f, d, generator=g)
+    wts, idx = eager.topk_softmax_route(torch.randn(T, E, generator=g), k)
+    keep = eager.capacity_keep_mask(idx, E, max(1, T * k // (2 * E)))
+    out = eager.grouped_swiglu(x, w1, w2, w3, idx, wts, keep)
+    ref = eager.grouped_swiglu(x, w1, w2, w3, idx, wts * keep, None)       # zero weight == dropped, no renormalising
+    assert torch.allclose(out, ref, atol=1e-5)
+    all_dropped = ~keep.any(-1)
+    assert torch.equal(out[all_dropped], torch.zeros_like(out[all_dropped]))
