@@ -1,4 +1,4 @@
-"""Properties of the routing definitions in ``ops/eager.py`` - the oracles the routing kernels are compared
+"""Properties of the routing definitions in ``ops/eager.py`` and of the MXFP8 rounding emulation - the oracles the kernels are compared
 against - checked on generated shapes and values."""
 import math
 
@@ -89,3 +89,40 @@ def test_dropped_assignments_contribute_nothing(T, E, seed):
     assert torch.allclose(out, ref, atol=1e-5)
     all_dropped = ~keep.any(-1)
     assert torch.equal(out[all_dropped], torch.zeros_like(out[all_dropped]))
+
+
+@SET
+@given(R=st.integers(1, 6), K=st.integers(1, 100), scale=st.floats(1e-6, 1e4), dim=st.sampled_from([-1, 0]),
+       seed=st.integers(0, 10_000))
+def test_mx_rounding_is_a_projection_with_bounded_error(R, K, scale, dim, seed):
+    """Block-scaled e4m3 (one power-of-two scale per 32 elements): quantising twice changes nothing more,
+    the scale exponent follows the block maximum, the element error is within half an e4m3 step (values
+    above 448 scales saturate), zero blocks stay zero, and the gradient passes straight through."""
+    from kolmogorov_moe_architecture_b200.ops.mxfp8 import dequantize_mx, fake_quant_mx, quantize_mx
+    x = torch.randn(R, K, generator=torch.Generator().manual_seed(seed)) * scale
+    x[0, : min(K, 32)] = 0.0 if dim == -1 else x[0, : min(K, 32)]
+    once = fake_quant_mx(x, dim)
+    assert torch.equal(fake_quant_mx(once, dim), once)
+    q, e = quantize_mx(x, dim)
+    assert q.dtype == torch.float8_e4m3fn and q.shape == x.shape and e.dtype == torch.int8
+    xm = x.movedim(dim, -1)
+    nb = (xm.shape[-1] + 31) // 32
+    assert e.shape[-1] == nb
+    for b in range(nb):
+        blk = xm[..., 32 * b: 32 * b + 32]
+        amax = blk.abs().amax(-1)
+        live = amax > 2.0 ** -100
+        want = torch.floor(torch.log2(amax.clamp(min=2.0 ** -127))) - 8
+        assert torch.equal(e[..., b].float()[live], want.clamp(-127, 127)[live])
+        sc = torch.exp2(e[..., b].float()).unsqueeze(-1)
+        got = once.movedim(dim, -1)[..., 32 * b: 32 * b + 32]
+        err = (got - blk).abs()
+        inside = blk.abs() <= 448.0 * sc                 # 3 mantissa bits; below 2^-6 of the scale a fixed step
+        assert (err[inside] <= torch.maximum(2.0 ** -4 * blk.abs(), 2.0 ** -10 * sc.expand_as(blk))[inside]).all()
+        assert torch.equal(got[~inside].abs(), (448.0 * sc.expand_as(blk))[~inside])     # saturates, never overflows
+    assert torch.equal(dequantize_mx(q, e, dim, torch.float32), once)
+    if dim == -1:
+        assert torch.equal(once[0, : min(K, 32)], torch.zeros(min(K, 32)))
+    xg = x.clone().requires_grad_(True)
+    fake_quant_mx(xg, dim).sum().backward()
+    assert torch.equal(xg.grad, torch.ones_like(x))
