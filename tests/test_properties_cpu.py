@@ -126,3 +126,60 @@ def test_mx_rounding_is_a_projection_with_bounded_error(R, K, scale, dim, seed):
     xg = x.clone().requires_grad_(True)
     fake_quant_mx(xg, dim).sum().backward()
     assert torch.equal(xg.grad, torch.ones_like(x))
+
+
+@SET
+@given(m=st.integers(2, 24), n=st.integers(2, 24), b=st.integers(1, 3), seed=st.integers(0, 10_000))
+def test_newton_schulz_moves_singular_values_towards_one(m, n, b, seed):
+    """Wide, tall and batched inputs: the iteration keeps the singular vectors and pushes every singular
+    value of the normalised matrix up towards 1 without overshooting, so the result is closer to an
+    orthogonal factor after every additional step."""
+    x = torch.randn(b, m, n, generator=torch.Generator().manual_seed(seed), dtype=torch.float64)
+    y0 = x / x.reshape(b, -1).norm(dim=1).view(b, 1, 1)
+    prev = torch.linalg.svdvals(y0)
+    for iters in (1, 3, 6):
+        y = eager.newton_schulz(x, iters)
+        assert y.shape == x.shape
+        sv = torch.linalg.svdvals(y)
+        assert (sv <= 1.0 + 1e-9).all() and (sv >= prev - 1e-9).all()
+        prev = sv
+    one = eager.newton_schulz(x[0], 6)
+    assert torch.allclose(one, y[0], atol=1e-12)                       # 2-D input = batch of one
+    u, s, vh = torch.linalg.svd(y0[0], full_matrices=False)
+    recon = u @ torch.diag(torch.linalg.svdvals(one)) @ vh
+    assert torch.allclose(recon, one, atol=1e-8)                       # same singular vectors
+
+
+@SET
+@given(n=st.integers(1, 5000), scale=st.floats(1e-4, 1e3), seed=st.integers(0, 10_000))
+def test_int8_block_quantisation_error_is_half_a_step_of_the_block_maximum(n, scale, seed):
+    from kolmogorov_moe_architecture_b200.training.muon_optimizer import Muon8bit
+    t = torch.randn(n, generator=torch.Generator().manual_seed(seed)) * scale
+    q, scales, shape, numel = Muon8bit._quantize_to_8bit(t, block_size=256)
+    back = Muon8bit._dequantize_from_8bit(q, scales, shape, numel)
+    assert q.dtype == torch.int8 and back.shape == t.shape and scales.shape[0] == (n + 255) // 256
+    bound = (scales / 127 * 0.5 * (1 + 1e-5)).expand(-1, 256).flatten()[:n]
+    assert ((back - t).abs() <= bound).all()
+    assert int(q.abs().max()) <= 127
+
+
+@SET
+@given(B=st.integers(1, 3), S=st.integers(1, 24), ndocs=st.integers(1, 5), seed=st.integers(0, 10_000))
+def test_document_boundaries_and_mask_agree(B, S, ndocs, seed):
+    """``doc_start`` is the first position of each token's document; the additive mask built from it hides
+    exactly the keys of earlier documents (causality itself is the attention's job)."""
+    g = torch.Generator().manual_seed(seed)
+    cuts = torch.sort(torch.randint(0, S, (B, ndocs - 1), generator=g), dim=1).values if ndocs > 1 else torch.zeros(B, 0, dtype=torch.long)
+    doc_ids = torch.zeros(B, S, dtype=torch.long)
+    for b in range(B):
+        for c in cuts[b].tolist():
+            doc_ids[b, c:] += 1
+    ds = eager.doc_start_from_ids(doc_ids)
+    assert ds.dtype == torch.int32 and (ds <= torch.arange(S)).all()
+    for b in range(B):
+        for t in range(S):
+            s0 = int(ds[b, t])
+            assert (doc_ids[b, s0: t + 1] == doc_ids[b, t]).all() and (s0 == 0 or doc_ids[b, s0 - 1] != doc_ids[b, t])
+    mask = eager.doc_start_to_mask(ds)
+    same_or_later_doc = doc_ids.unsqueeze(2) <= doc_ids.unsqueeze(1)          # key's document is not an earlier one
+    assert torch.equal(mask[:, 0] == 0, same_or_later_doc)
