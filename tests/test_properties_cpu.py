@@ -183,3 +183,38 @@ def test_document_boundaries_and_mask_agree(B, S, ndocs, seed):
     mask = eager.doc_start_to_mask(ds)
     same_or_later_doc = doc_ids.unsqueeze(2) <= doc_ids.unsqueeze(1)          # key's document is not an earlier one
     assert torch.equal(mask[:, 0] == 0, same_or_later_doc)
+
+
+@SET
+@given(B=st.integers(1, 3), S=st.integers(1, 12), n_heads=st.integers(1, 4), V=st.integers(2, 9), seed=st.integers(0, 10_000))
+def test_multi_token_loss_scores_head_i_against_the_token_i_plus_one_ahead(B, S, n_heads, V, seed):
+    """Head i (0-based) at position t is scored against labels[t + i + 1]; ignored targets do not count; heads
+    that have no target inside the sequence contribute zero; a head whose logits put all mass on its targets
+    has zero loss."""
+    g = torch.Generator().manual_seed(seed)
+    d = V                                                      # hidden = one-hot of a token: logits are readable
+    labels = torch.randint(0, V, (B, S), generator=g)
+    heads = [torch.eye(V) * 50.0 for _ in range(n_heads)]
+    w = [1.0 / n_heads] * n_heads
+    for i in range(n_heads):                                   # hidden state that is exactly right for head i
+        hidden = torch.zeros(B, S, d)
+        if i + 1 < S:
+            hidden[:, : S - i - 1] = torch.nn.functional.one_hot(labels[:, i + 1:], V).float()
+        total, per = eager.mtp_cross_entropy(hidden, heads, labels, w)
+        assert per.shape == (n_heads,) and float(per[i]) < 1e-6
+        assert abs(float(total) - float((per * torch.tensor(w)).sum())) < 1e-6
+        for j in range(n_heads):
+            if j + 1 >= S:
+                assert float(per[j]) == 0.0
+    hidden = torch.randn(B, S, d, generator=g)
+    _, per = eager.mtp_cross_entropy(hidden, heads, labels, w)
+    masked = labels.clone()
+    masked[:, ::2] = -100
+    _, per_m = eager.mtp_cross_entropy(hidden, heads, masked, w)
+    i = 0
+    if S > 1:
+        keep = masked[:, 1:] != -100
+        if keep.any():
+            logits = hidden[:, : S - 1] @ heads[0].t()
+            want = torch.nn.functional.cross_entropy(logits[keep], labels[:, 1:][keep])
+            assert abs(float(per_m[i]) - float(want)) < 1e-4
