@@ -68,6 +68,20 @@ class TrainEngine:
             return t
         return t.to(self.device, non_blocking=True)
 
+    def _check_ids(self, input_ids: torch.Tensor) -> None:
+        """Token ids that are still on the host are range-checked there (a few microseconds): an id outside
+        the vocabulary would otherwise surface as a device-side assertion in the embedding lookup, which
+        costs the process its CUDA context."""
+        if input_ids.device.type != "cpu" or input_ids.numel() == 0:
+            return
+        cfg = getattr(getattr(self.model, "_orig_mod", self.model), "config", None)
+        vocab = getattr(cfg, "vocab_size", None)
+        if vocab is None:
+            return
+        lo, hi = int(input_ids.min()), int(input_ids.max())
+        if lo < 0 or hi >= vocab:
+            raise ValueError(f"token ids must lie in [0, {vocab}); the batch has values from {lo} to {hi}")
+
     def _forward_backward(self, ids: torch.Tensor, labels: torch.Tensor, attention_mask=None):
         if self.autocast_dtype is not None and self.device.type == "cuda":
             with torch.autocast("cuda", dtype=self.autocast_dtype):
@@ -104,6 +118,7 @@ class TrainEngine:
              attention_mask: Optional[torch.Tensor] = None) -> StepStats:
         """``input_ids``: (grad_accum * micro_batch, S) or (micro_batch, S)."""
         self.model.train()
+        self._check_ids(input_ids)
         ids = self._to_device(input_ids)
         lab = ids if labels is None else self._to_device(labels)
         am = None if attention_mask is None else self._to_device(attention_mask)

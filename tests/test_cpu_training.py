@@ -242,3 +242,15 @@ def test_async_checkpoint_writer_markers_pruning_and_errors(tmp_path):
     bad.submit({os.path.join(root, "x.pt"): {"f": lambda: 0}}, root, 0)      # a lambda cannot be pickled
     with pytest.raises(RuntimeError, match="asynchronous checkpoint write failed"):
         bad.wait()
+
+
+def test_engine_rejects_token_ids_outside_the_vocabulary_on_the_host():
+    _, m = _model()
+    eng = TrainEngine(m, torch.optim.AdamW(m.parameters(), lr=1e-3))
+    V = m.config.vocab_size
+    ok = torch.randint(0, V, (2, 16))
+    eng.step(ok)
+    for bad in (ok.clone().index_put_((torch.tensor(0), torch.tensor(3)), torch.tensor(V)),
+                ok.clone().index_put_((torch.tensor(1), torch.tensor(0)), torch.tensor(-1))):
+        with pytest.raises(ValueError, match="token ids must lie in"):
+            eng.step(bad)
