@@ -148,20 +148,30 @@ class PackedDocs:
     training keeps the fast path; elsewhere it becomes the additive mask of ``document_attention_mask``.
     The reference builds the dense (B, 1, S, S) mask and falls off its flash path (train_custom.py:429-463)."""
 
-    def __init__(self, doc_ids: Optional[torch.Tensor] = None, doc_start: Optional[torch.Tensor] = None):
+    def __init__(self, doc_ids: Optional[torch.Tensor] = None, doc_start: Optional[torch.Tensor] = None,
+                 _checked: bool = False):
         from ..ops import eager
         assert (doc_ids is None) != (doc_start is None), "give document ids or start positions"
-        self.doc_start = eager.doc_start_from_ids(doc_ids) if doc_start is None else doc_start.to(torch.int32)
+        if doc_start is None:
+            self.doc_start = eager.doc_start_from_ids(doc_ids)
+        elif _checked:
+            self.doc_start = doc_start
+        else:
+            # start positions from outside: a start is neither negative nor after its own position (the
+            # attention kernels index key blocks with it)
+            ds = doc_start.to(torch.int32)
+            pos = torch.arange(ds.shape[-1], device=ds.device, dtype=torch.int32)
+            self.doc_start = torch.minimum(ds.clamp(min=0), pos.expand_as(ds))
 
     @property
     def device(self):
         return self.doc_start.device
 
     def to(self, device, non_blocking: bool = False) -> "PackedDocs":
-        return PackedDocs(doc_start=self.doc_start.to(device, non_blocking=non_blocking))
+        return PackedDocs(doc_start=self.doc_start.to(device, non_blocking=non_blocking), _checked=True)
 
     def chunk(self, n: int, dim: int = 0):
-        return [PackedDocs(doc_start=t) for t in self.doc_start.chunk(n, dim=dim)]
+        return [PackedDocs(doc_start=t, _checked=True) for t in self.doc_start.chunk(n, dim=dim)]
 
     def dense_mask(self, dtype=torch.float32) -> torch.Tensor:
         from ..ops import eager
