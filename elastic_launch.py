@@ -12,6 +12,9 @@ directory carrying all ranks' completion markers (or written synchronously) and 
 over.  The reference has no restart logic: a failed rank ends the run (reference: train_distributed.py:747-1095
 has no checkpointing at all; train.py:211-225 only saves on SIGINT / SIGTERM in a single process).
 
+The children run with ``NCCL_NVLS_ENABLE=0`` and ``KMOE_MULTIMEM=0`` unless the caller's environment sets them:
+a rank that can die should not be bound to an NVLink multicast object.
+
 ``--shrink`` lets a restart use fewer processes (halving, not below ``--min-nproc``) after two failures in a
 row at the same size; the replicated-parameter plan and the parameter-sharded plan both reload ``model.pt``
 at any world size (optimizer shards are reused only when the layout matches).
@@ -57,6 +60,12 @@ def supervise(nproc: int, script_args: List[str], checkpoint_dir: str, max_resta
               shrink: bool = False, min_nproc: int = 1, backoff_s: float = 1.0, env=None, log=print) -> int:
     """Returns the exit code of the last attempt (0 = the job finished)."""
     from kolmogorov_moe_architecture_b200.training.checkpoint import latest_complete_checkpoint
+    if env is None:
+        env = dict(os.environ)
+    # a job that may lose a rank keeps off the NVLink switch's multicast objects: a process that dies while its
+    # memory is bound to one can fault the other ranks' GPUs; plain peer loads and stores have no such coupling
+    env.setdefault("NCCL_NVLS_ENABLE", "0")
+    env.setdefault("KMOE_MULTIMEM", "0")
     attempt, fails_at_size = 0, 0
     while True:
         found = latest_complete_checkpoint(checkpoint_dir, world=nproc) if os.path.isdir(checkpoint_dir) else None
