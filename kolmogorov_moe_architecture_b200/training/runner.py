@@ -384,10 +384,14 @@ def _fault_from_env():
     """``KMOE_FAULT_INJECT=rank:step:kind`` (kind = raise | exit | stall) makes that rank fail on the host
     right after that step, with no kernel or collective of its own in flight.  With ``KMOE_FAULT_ONCE=<file>``
     the failure happens only while the file does not exist (it is created first), so a restarted job runs
-    through."""
+    through.  On GPUs the switch multicast must be off (``NCCL_NVLS_ENABLE=0``, which this library's kernels obey
+    too)."""
     spec = os.environ.get("KMOE_FAULT_INJECT")
     if not spec:
         return None
+    if torch.cuda.is_available() and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0":
+        # a rank that leaves while its buffers are bound to an NVLink multicast object can fault its peers' GPUs
+        raise RuntimeError("KMOE_FAULT_INJECT on GPUs needs NCCL_NVLS_ENABLE=0 (plain peer loads and stores only)")
     from ..utils.fault import FaultInjector
     r, s_, kind = (spec.split(":") + ["raise"])[:3]
     inj = FaultInjector(int(r), int(s_), kind)
