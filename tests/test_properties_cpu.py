@@ -218,3 +218,58 @@ def test_multi_token_loss_scores_head_i_against_the_token_i_plus_one_ahead(B, S,
             logits = hidden[:, : S - 1] @ heads[0].t()
             want = torch.nn.functional.cross_entropy(logits[keep], labels[:, 1:][keep])
             assert abs(float(per_m[i]) - float(want)) < 1e-4
+
+
+def _get_tile(idx, num_m, num_n, groups, batched, sym_upper, BM=128, BN=256):
+    """The work-index -> tile mapping of the persistent GEMM (``get_tile`` in csrc/gemm_umma.cu), restated."""
+    per_group = num_m * num_n
+    if sym_upper:
+        first = [min(num_n, (m * BM) // BN) for m in range(num_m)]
+        kept = sum(num_n - f for f in first)
+        g, local = divmod(idx, kept)
+        if g >= (groups if batched else 1):
+            return None
+        m = 0
+        while local >= num_n - first[m]:
+            local -= num_n - first[m]
+            m += 1
+        return g, m, first[m] + local
+    g, local = 0, idx
+    if batched:
+        g, local = divmod(idx, per_group)
+        if g >= groups:
+            return None
+    elif idx >= per_group:
+        return None
+    GM = 8
+    band = local // (GM * num_n)
+    first_m = band * GM
+    gsz = min(num_m - first_m, GM)
+    r = local - band * GM * num_n
+    return g, first_m + r % gsz, r // gsz
+
+
+@SET
+@given(num_m=st.integers(1, 40), num_n=st.integers(1, 12), groups=st.integers(1, 4), batched=st.booleans(),
+       grid=st.integers(1, 148))
+def test_gemm_tile_scheduler_visits_every_tile_exactly_once(num_m, num_n, groups, batched, grid):
+    """Persistent CTAs stride the work index by the grid size: together they cover every (group, m, n) tile
+    once, in bands of eight m-tiles; the symmetric variant covers exactly the tiles that touch the upper
+    triangle (the rest is mirrored afterwards)."""
+    G = groups if batched else 1
+    seen = []
+    for cta in range(grid):
+        idx = cta
+        while (t := _get_tile(idx, num_m, num_n, groups, batched, False)) is not None:
+            seen.append(t)
+            idx += grid
+    assert len(seen) == len(set(seen)) == G * num_m * num_n
+    assert set(seen) == {(g, m, n) for g in range(G) for m in range(num_m) for n in range(num_n)}
+    # symmetric product: BM = 128 rows against BN = 256 columns
+    seen = []
+    idx = 0
+    while (t := _get_tile(idx, num_m, num_n, groups, batched, True)) is not None:
+        seen.append(t)
+        idx += 1
+    want = {(g, m, n) for g in range(G) for m in range(num_m) for n in range(num_n) if (n + 1) * 256 > m * 128}
+    assert len(seen) == len(set(seen)) and set(seen) == want
