@@ -273,3 +273,21 @@ def test_gemm_tile_scheduler_visits_every_tile_exactly_once(num_m, num_n, groups
         idx += 1
     want = {(g, m, n) for g in range(G) for m in range(num_m) for n in range(num_n) if (n + 1) * 256 > m * 128}
     assert len(seen) == len(set(seen)) and set(seen) == want
+
+
+@SET
+@given(rows=st.integers(1, 300), kchunks=st.integers(1, 4), seed=st.integers(0, 10_000))
+def test_mx_scale_chunk_layout_round_trip(rows, kchunks, seed):
+    """Scale bytes are stored in 512-byte chunks per 128 rows x 128 reduction elements, byte
+    (row % 32) * 16 + (row % 128) / 32 * 4 + (k / 32) % 4 inside the chunk (the arrangement the tensor core
+    reads from tensor memory); ``decode_scale_chunks`` undoes exactly that placement."""
+    from kolmogorov_moe_architecture_b200.ops.mxfp8 import decode_scale_chunks
+    K = 128 * kchunks
+    exps = torch.randint(-20, 20, (rows, K // 32), generator=torch.Generator().manual_seed(seed))
+    rb = (rows + 127) // 128
+    sf = torch.zeros(rb * kchunks * 512, dtype=torch.uint8)
+    for r in range(rows):
+        for kg in range(K // 32):
+            chunk = (r // 128) * kchunks + kg // 4
+            sf[chunk * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + kg % 4] = int(exps[r, kg]) + 127
+    assert torch.equal(decode_scale_chunks(sf, rows, K), exps.to(torch.int32))
