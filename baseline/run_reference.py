@@ -8,6 +8,15 @@ copied beside it in ``baseline/_ref/ref_scripts``), driven through its own publi
 * N GPUs - the regime of the reference's ``train_distributed.py``: the same model wrapped by
   its own ``wrap_model_with_fsdp`` (FULL_SHARD, bf16, activation checkpointing), same optimizer.
 
+``--mamba-moe-mode`` selects what a layer listed in both ``moe_layers`` and ``mamba_layers``
+becomes.  ``routing_mamba`` is the stock reference (RoutingMamba + dense FFN,
+moe_arch/model/layers.py:58-82).  ``moe_ffn`` (the default of ``bench.py``, the layer the
+benchmark names: Mamba mixer + MoE FFN) cannot be expressed by the reference's config, so
+those layers are built by ``MambaMoEBlock`` below: a subclass of the reference's
+``TransformerBlock`` that composes the reference's own unmodified ``MambaBlock`` and
+``MoELayer`` and inherits its ``forward`` untouched.  Both arms then hold the same
+parameter count (``params_b``).
+
 Nothing from this repository's package is imported here.  The same JSON line as the other
 arm is printed, with ``"impl": "reference"``; if the reference cannot be imported or run,
 ``{"impl": "reference", "unavailable": "<reason>"}`` is printed instead and the exit code is 0.
@@ -44,6 +53,51 @@ def _import_reference():
     return AdvancedMoEConfig, MoETransformer, get_muon_optimizer
 
 
+def _mamba_moe_block_factory():
+    """``TransformerBlock`` factory for ``--mamba-moe-mode moe_ffn``.
+
+    A layer in both lists is first built by the reference's own constructor as a Mamba layer
+    without MoE (``MambaBlock`` + dense FFN), then its FFN is replaced by the reference's
+    ``MoELayer`` and ``use_moe`` is switched on, which is all the inherited ``forward``
+    (moe_arch/model/layers.py:96-207) needs to run the mixer, the MoD routing and the MoE
+    auxiliary loss.  Every other layer is the stock block."""
+    import dataclasses
+    from moe_arch.model.layers import TransformerBlock
+    from moe_arch.model.moe import MoELayer
+    from moe_arch.model.mamba import MambaBlock
+
+    class MambaMoEBlock(TransformerBlock):
+        def __init__(self, config, layer_idx):
+            plain = dataclasses.replace(
+                config, moe_layers=tuple(i for i in config.moe_layers if i != layer_idx))
+            super().__init__(plain, layer_idx)
+            assert isinstance(self.seq_layer, MambaBlock)
+            self.config = config
+            self.use_moe = True
+            self.ffn = MoELayer(config, layer_idx)
+
+    def make(config, layer_idx):
+        both = config.mamba_enabled and layer_idx in config.mamba_layers and layer_idx in config.moe_layers
+        return (MambaMoEBlock if both else TransformerBlock)(config, layer_idx)
+
+    return make, TransformerBlock
+
+
+def _build_model(MoETransformer, cfg, mode: str):
+    """Stock ``MoETransformer(cfg)``; for ``moe_ffn`` the name ``TransformerBlock`` that its
+    constructor looks up (moe_arch/model/transformer.py:56-59) is pointed at the factory
+    above for the duration of the call.  No reference file is edited."""
+    if mode == "routing_mamba":
+        return MoETransformer(cfg)
+    import moe_arch.model.transformer as ref_tf
+    make, stock = _mamba_moe_block_factory()
+    ref_tf.TransformerBlock = make
+    try:
+        return MoETransformer(cfg)
+    finally:
+        ref_tf.TransformerBlock = stock
+
+
 def run_reference(args):
     if not os.path.isdir(os.path.join(REF, "moe_arch")):
         return _unavailable("baseline/_ref/moe_arch is missing (reference not installed)")
@@ -55,7 +109,7 @@ def run_reference(args):
 
 
 def _run(args):
-    from bench import ClockSampler, barrier, dist_setup, max_over_ranks
+    from bench import ClockSampler, barrier, dist_setup, max_over_ranks, metric_name, workload_config
     AdvancedMoEConfig, MoETransformer, get_muon_optimizer = _import_reference()
     world, rank, local = dist_setup(args)
     dev = torch.device("cuda", local)
@@ -65,22 +119,24 @@ def _run(args):
         moe_layers=tuple(i for i in range(L) if i % 4 in (1, 2)),
         mamba_layers=tuple(i for i in range(L) if i % 4 == 1),
         dropout=0.0, attention_dropout=0.0, residual_dropout=0.0)
+    mode = getattr(args, "mamba_moe_mode", "moe_ffn")
     torch.manual_seed(0)
     if rank != 0:
         sys.stdout = open(os.devnull, "w")
     ckpt = world > 1
     if world == 1:
-        model = MoETransformer(cfg).to(dev).to(torch.bfloat16)
+        model = _build_model(MoETransformer, cfg, mode).to(dev).to(torch.bfloat16)
         model.train()
         regime = "train.py single-GPU regime: bf16 weights, no activation checkpointing"
     else:
         from train_distributed import wrap_model_with_fsdp
         with torch.device(dev):
-            model = MoETransformer(cfg)
+            model = _build_model(MoETransformer, cfg, mode)
+        n_params_unwrapped = sum(p.numel() for p in model.parameters())
         model = wrap_model_with_fsdp(model, rank, use_bf16=True, cpu_offload=False, activation_checkpointing=True)
         model.train()
         regime = "train_distributed.py regime: FSDP FULL_SHARD bf16 + activation checkpointing"
-    n_params = sum(p.numel() for p in model.parameters())
+    n_params = n_params_unwrapped if ckpt else sum(p.numel() for p in model.parameters())
     os.environ.setdefault("WORLD_SIZE", str(world))
     optimizer = get_muon_optimizer(model, lr=1e-3)
     sys.stdout = sys.__stdout__
@@ -127,19 +183,22 @@ def _run(args):
     if rank == 0:
         mamba = "mamba_ssm" if _has_mamba_ssm() else "SimpleSSM fallback (mamba_ssm not installed)"
         print(json.dumps({
-            "metric": METRIC, "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+            "metric": metric_name(args), "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "impl": "reference", "clocks": clocks,
             "e2e": {"value": tokens / (ms2 / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": B * S * 8,
                     "d2h_bytes_per_step": 4, "ms_per_step": ms2 / args.steps, "last_loss": last},
-            "config": {"model": "reference MoETransformer, same AdvancedMoEConfig fields as the other arm "
-                                "(a layer in both moe_layers and mamba_layers is RoutingMamba + dense FFN there)",
-                       "params_b": round(n_params * (world if ckpt else 1) / 1e9, 3) if not ckpt else None,
-                       "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}",
-                       "regime": regime, "mamba": mamba, "optimizer": "get_muon_optimizer (Muon8bit + AdamW)",
+            "config": workload_config(args, world, L == 32 and B == 4 and S == 2048),
+            "detail": {"params_b": round(n_params / 1e9, 3),
                        "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
-                       "valid_config": L == 32 and B == 4 and S == 2048}}), flush=True)
+                       "model": ("reference MoETransformer; Mamba+MoE layers = the reference's own MambaBlock + "
+                                 "MoELayer composed by a harness-side TransformerBlock subclass"
+                                 if mode == "moe_ffn" else
+                                 "stock reference MoETransformer (a layer in both moe_layers and mamba_layers "
+                                 "is RoutingMamba + dense FFN)"),
+                       "regime": regime, "mamba": mamba,
+                       "optimizer": "get_muon_optimizer (Muon8bit + AdamW)"}}), flush=True)
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()

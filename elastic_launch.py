@@ -12,12 +12,18 @@ directory carrying all ranks' completion markers (or written synchronously) and 
 over.  The reference has no restart logic: a failed rank ends the run (reference: train_distributed.py:747-1095
 has no checkpointing at all; train.py:211-225 only saves on SIGINT / SIGTERM in a single process).
 
-The children run with ``NCCL_NVLS_ENABLE=0`` and ``KMOE_MULTIMEM=0`` unless the caller's environment sets them:
-a rank that can die should not be bound to an NVLink multicast object.
+The children run with ``NCCL_NVLS_ENABLE=0``, ``KMOE_MULTIMEM=0`` and ``TORCH_SYMM_MEM_DISABLE_MULTICAST=1`` unless
+the caller's environment sets them: a rank that can die should not be bound to an NVLink multicast object.  The
+first two keep NCCL and this library's kernels off the multicast address; the third stops torch's
+symmetric-memory allocator (which backs the peer buffers of the ``p2p`` transport) from creating and binding a
+multicast object at rendezvous in the first place.
 
 ``--shrink`` lets a restart use fewer processes (halving, not below ``--min-nproc``) after two failures in a
 row at the same size; the replicated-parameter plan and the parameter-sharded plan both reload ``model.pt``
-at any world size (optimizer shards are reused only when the layout matches).
+at any world size (optimizer shards are reused only when the layout matches).  A checkpoint written under expert
+parallelism holds each rank's experts in its own file and loads only at the same size, so ``--shrink`` is
+refused for such a job (the size is kept) with a message naming ``consolidate_expert_checkpoint`` as the way
+to move it to another size by hand.
 """
 from __future__ import annotations
 
@@ -66,12 +72,12 @@ def supervise(nproc: int, script_args: List[str], checkpoint_dir: str, max_resta
     # memory is bound to one can fault the other ranks' GPUs; plain peer loads and stores have no such coupling
     env.setdefault("NCCL_NVLS_ENABLE", "0")
     env.setdefault("KMOE_MULTIMEM", "0")
+    env.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     attempt, fails_at_size = 0, 0
     while True:
+        # completeness is judged by each directory's own manifest (its writer count), so a checkpoint written
+        # by a larger job is found by a smaller one too
         found = latest_complete_checkpoint(checkpoint_dir, world=nproc) if os.path.isdir(checkpoint_dir) else None
-        if found is None and os.path.isdir(checkpoint_dir):
-            # a checkpoint written by a larger job is complete for this one too if its own markers say so
-            found = _latest_any_world(checkpoint_dir)
         cmd = build_command(nproc, port + attempt, script_args, checkpoint_dir, checkpoint_dir if found else None)
         log(f"[elastic] attempt {attempt + 1}: {nproc} processes, "
             f"{'resuming from ' + os.path.basename(found) if found else 'starting fresh'}")
@@ -87,25 +93,28 @@ def supervise(nproc: int, script_args: List[str], checkpoint_dir: str, max_resta
             return rc
         fails_at_size += 1
         if shrink and fails_at_size >= 2 and nproc // 2 >= min_nproc:
-            nproc, fails_at_size = nproc // 2, 0
-            log(f"[elastic] two failures in a row: continuing with {nproc} processes")
+            if _has_expert_shards(checkpoint_dir):
+                log("[elastic] --shrink refused: the checkpoints hold per-rank expert shards (expert parallelism), "
+                    "which load only at the size that wrote them; keeping "
+                    f"{nproc} processes (training.checkpoint.consolidate_expert_checkpoint merges the shards "
+                    "for a job of another size)")
+                fails_at_size = 0
+            else:
+                nproc, fails_at_size = nproc // 2, 0
+                log(f"[elastic] two failures in a row: continuing with {nproc} processes")
         time.sleep(backoff_s)
 
 
-def _latest_any_world(root: str) -> Optional[str]:
+def _has_expert_shards(root: str) -> bool:
     import re
-    best = None
+    if not os.path.isdir(root):
+        return False
     for name in os.listdir(root):
-        m = re.fullmatch(r"checkpoint-(\d+)", name)
         d = os.path.join(root, name)
-        if not m or not os.path.isdir(d):
-            continue
-        marks = [n for n in os.listdir(d) if n.startswith("complete-rank")]
-        writers = len([n for n in os.listdir(d) if n.startswith(("optimizer-rank", "shards-rank"))])
-        done = (len(marks) == writers and writers > 0) if marks else os.path.exists(os.path.join(d, "training_state.pt"))
-        if done and (best is None or int(m.group(1)) > best[0]):
-            best = (int(m.group(1)), d)
-    return best[1] if best else None
+        if re.fullmatch(r"checkpoint-(\d+)", name) and os.path.isdir(d):
+            if any(re.fullmatch(r"experts-rank\d+\.pt", n) for n in os.listdir(d)):
+                return True
+    return False
 
 
 def main(argv=None) -> int:

@@ -49,9 +49,6 @@ def strip_prefixes(sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
         changed = True
         while changed:
             changed = False
-            for p in _PREFIXES:
-                if k.startswith(p) and not k.startswith("model.layers") is False:
-                    pass
             for p in ("_orig_mod.", "module."):
                 if k.startswith(p):
                     k, changed = k[len(p):], True
@@ -180,6 +177,47 @@ def _load_expert_file(d: str, rank: int, base, expert_pool, ep_rank: int, ep_siz
         expert_pool.load_optimizer_state_dict(ex["optimizer"])
 
 
+MANIFEST = "manifest.json"
+
+
+def _write_manifest(d: str, mode: str, world: int, files) -> None:
+    """Rank 0 writes this before any other file of a multi-rank checkpoint: who writes into the
+    directory and which files must exist.  ``checkpoint_complete`` trusts a directory only when
+    every rank named here has dropped its marker."""
+    import json
+    tmp = os.path.join(d, MANIFEST + ".tmp")
+    with open(tmp, "w") as f:
+        json.dump({"mode": mode, "world": int(world), "files": sorted(files),
+                   "markers": [f"complete-rank{r}" for r in range(int(world))]}, f)
+    os.replace(tmp, os.path.join(d, MANIFEST))
+
+
+def read_manifest(d: str) -> Optional[Dict[str, Any]]:
+    import json
+    try:
+        with open(os.path.join(d, MANIFEST)) as f:
+            return json.load(f)
+    except (OSError, ValueError):
+        return None
+
+
+def _mark_complete(d: str, rank: int) -> None:
+    with open(os.path.join(d, f"complete-rank{rank}"), "w") as f:
+        f.write("ok")
+
+
+def _expected_files(kind: str, world: int, has_experts: bool):
+    names = ["model.pt", "training_state.pt"] + [f"{kind}-rank{r}.pt" for r in range(world)]
+    if has_experts:
+        names += [f"experts-rank{r}.pt" for r in range(world)]
+    return names
+
+
+def _world_size(world: Optional[int] = None) -> int:
+    import torch.distributed as dist
+    return world or (dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1)
+
+
 def save_sharded(root: str, step: int, model, dp, training_state: Dict, rank: int, keep: int = 3,
                  writer: Optional["AsyncCheckpointWriter"] = None, world: Optional[int] = None,
                  ep_rank: int = 0, ep_size: int = 1) -> str:
@@ -198,19 +236,21 @@ def save_sharded(root: str, step: int, model, dp, training_state: Dict, rank: in
     ep_names = _expert_parallel_names(model)
     if ep_names:
         files[os.path.join(d, f"experts-rank{rank}.pt")] = _expert_file(sd, ep_names, expert_pool, ep_rank, ep_size)
+    w = _world_size(world)
     if rank == 0:
+        _write_manifest(d, "sharded", w, _expected_files("optimizer", w, bool(ep_names)))
         files[os.path.join(d, "model.pt")] = {k: v for k, v in sd.items() if k not in set(ep_names)}
         files[os.path.join(d, "training_state.pt")] = training_state
     if writer is not None:
-        w = world or (dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1)
         writer.submit(files, d, rank, then=(lambda: prune_checkpoints(root, keep, world=w)) if rank == 0 else None)
         return d
     for path, obj in files.items():
         _atomic_save(obj, path)
+    _mark_complete(d, rank)                  # after this rank's last file; the directory counts once all are there
     if dist.is_available() and dist.is_initialized():
         dist.barrier()
     if rank == 0:
-        prune_checkpoints(root, keep)
+        prune_checkpoints(root, keep, world=w)
     return d
 
 
@@ -225,6 +265,12 @@ def load_sharded(d: str, model, dp, rank: int, map_location="cpu", ep_rank: int 
     if ep_names and not all(n in sd for n in ep_names):
         _load_expert_file(d, rank, base, expert_pool, ep_rank, ep_size, map_location)
     f = os.path.join(d, f"optimizer-rank{rank}.pt")
+    man = read_manifest(d)
+    if not os.path.exists(f) and man is not None and man.get("world") == getattr(main_pool, "world", None):
+        # same job size, so this rank's moments must be there: resuming without them would silently
+        # restart the optimizer on one rank only
+        raise FileNotFoundError(f"{f}: optimizer state of rank {rank} is missing from a checkpoint written by "
+                                f"{man.get('world')} ranks (incomplete checkpoint?)")
     if os.path.exists(f):
         osd = torch.load(f, map_location=map_location, weights_only=False)
         same = not isinstance(osd, dict) or osd.get("world") in (None, getattr(main_pool, "world", None))
@@ -273,6 +319,7 @@ def save_param_sharded(root: str, step: int, plan, training_state: Dict, rank: i
         esd = {n: p.detach() for n, p in unwrap_model(fsdp.model).named_parameters() if n in set(ep_names)}
         files[os.path.join(d, f"experts-rank{rank}.pt")] = _expert_file(esd, ep_names, expert_pool, ep_rank, ep_size)
     if rank == 0:
+        _write_manifest(d, "param_sharded", fsdp.world, _expected_files("shards", fsdp.world, bool(ep_names)))
         files[os.path.join(d, "model.pt")] = full
         files[os.path.join(d, "training_state.pt")] = training_state
     if writer is not None:
@@ -281,10 +328,11 @@ def save_param_sharded(root: str, step: int, plan, training_state: Dict, rank: i
         return d
     for path, obj in files.items():
         _atomic_save(obj, path)
+    _mark_complete(d, rank)
     if dist.is_available() and dist.is_initialized():
         dist.barrier()
     if rank == 0:
-        prune_checkpoints(root, keep)
+        prune_checkpoints(root, keep, world=fsdp.world)
     return d
 
 
@@ -356,8 +404,7 @@ class AsyncCheckpointWriter:
             try:
                 for path, obj in host.items():
                     _atomic_save(obj, path)
-                with open(os.path.join(directory, f"complete-rank{rank}"), "w") as f:
-                    f.write("ok")
+                _mark_complete(directory, rank)
                 if then is not None:
                     then()
             except BaseException as e:       # surfaced by wait()
@@ -368,12 +415,24 @@ class AsyncCheckpointWriter:
 
 
 def checkpoint_complete(d: str, world: int) -> bool:
-    """Every rank finished writing into ``d`` (directories written synchronously carry no markers and
-    count as complete once ``training_state.pt`` exists)."""
-    marks = [n for n in os.listdir(d) if n.startswith("complete-rank")] if os.path.isdir(d) else []
-    if marks:
-        return all(os.path.exists(os.path.join(d, f"complete-rank{r}")) for r in range(world))
-    return os.path.exists(os.path.join(d, "training_state.pt"))
+    """Whether ``d`` holds a finished checkpoint.
+
+    A multi-rank directory starts with rank 0's manifest (its writer count and expected files) and is
+    complete when every rank named there has dropped its ``complete-rank{r}`` marker - each rank's
+    last write - and every expected file exists.  The writer count comes from the manifest, not from
+    ``world``: a job restarted on fewer ranks must still recognise what the larger job wrote.
+    A directory with per-rank files or markers but no manifest is a save that rank 0 has not begun
+    (or one cut off before the manifest): incomplete.  A directory without any per-rank file is the
+    single-writer layout (``save_format_c``), whose last file is ``training_state.pt``."""
+    if not os.path.isdir(d):
+        return False
+    names = set(os.listdir(d))
+    man = read_manifest(d)
+    if man is not None:
+        return all(m in names for m in man.get("markers", [])) and all(f in names for f in man.get("files", []))
+    if any(re.fullmatch(r"(complete-rank\d+|(optimizer|shards|experts)-rank\d+\.pt(\.tmp)?)", n) for n in names):
+        return False
+    return "training_state.pt" in names
 
 
 def latest_complete_checkpoint(root: str, world: int = 1) -> Optional[str]:

@@ -19,7 +19,9 @@ class CosineScheduleWithWarmup:
         self.max_lr, self.min_lr, self.warmup_init_lr = max_lr, min_lr, warmup_init_lr
         self.current_step = 0
         self.preserve_ratios = preserve_ratios
-        self._base_lrs = [g["lr"] for g in optimizer.param_groups]
+        # ``initial_lr`` travels with the optimizer's state dict, so a scheduler built on a restored
+        # optimizer (whose ``lr`` is already scaled) still sees each group's base rate
+        self._base_lrs = [g.setdefault("initial_lr", g["lr"]) for g in optimizer.param_groups]
 
     def get_lr(self, step: Optional[int] = None) -> float:
         s = self.current_step if step is None else step
@@ -32,6 +34,11 @@ class CosineScheduleWithWarmup:
 
     def step(self) -> float:
         self.current_step += 1
+        return self.apply()
+
+    def apply(self) -> float:
+        """Write the rate of ``current_step`` into the param groups without advancing (used after a
+        resume, so the first step after it runs at the rate the uninterrupted run would use)."""
         lr = self.get_lr()
         self._last_lr = []
         for g, base in zip(self.optimizer.param_groups, self._base_lrs):

@@ -133,7 +133,25 @@ def _documents(tokenizer, max_examples):
     return gen()
 
 
-def _make_loader(spec, cfg, data_cfg, batch, rank, world):
+class _SkipFirst:
+    """An iterable that drops the first ``n`` batches of ``loader`` (resume: the batches consumed
+    before the checkpoint are not replayed; the reference stores and restores ``data_idx`` for
+    the same purpose, train.py:195, 811, 869)."""
+
+    def __init__(self, loader, n: int):
+        self.loader, self.n = loader, int(n)
+
+    def __iter__(self):
+        import itertools
+        return itertools.islice(iter(self.loader), self.n, None)
+
+
+def _make_loader(spec, cfg, data_cfg, batch, rank, world, skip_batches: int = 0):
+    loader, kind = _make_loader_from_start(spec, cfg, data_cfg, batch, rank, world)
+    return (_SkipFirst(loader, skip_batches) if skip_batches > 0 else loader), kind
+
+
+def _make_loader_from_start(spec, cfg, data_cfg, batch, rank, world):
     from torch.utils.data import DataLoader
     mode = spec.data_mode
     tok = None
@@ -185,12 +203,13 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
     model = model.to(device).to(wdtype)
     if spec.grad_checkpoint:
         model.gradient_checkpointing_enable()
-    start_step, tokens_seen, losses = 0, 0, []
+    start_step, tokens_seen, losses, data_idx = 0, 0, [], None
     resume = spec.resume or train_cfg.get("resume_from")
     if resume and not os.path.isdir(resume):
         _, ck = ckpt.load_model_state(model, resume, map_location=device)
         start_step = ck.get("step", ck.get("global_step", 0)) if isinstance(ck, dict) else 0
         tokens_seen = ck.get("total_tokens", ck.get("tokens_seen", 0)) if isinstance(ck, dict) else 0
+        data_idx = ck.get("data_idx") if isinstance(ck, dict) else None
     if spec.reallocate:
         from tools.reallocate_experts import reallocate_model_experts
         reallocate_model_experts(model, entropy_threshold=spec.entropy_threshold, verbose=is_main)
@@ -271,8 +290,18 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
                   else ckpt.load_format_c(resume, model, optimizer, device))
         engine.global_step = start_step = st.get("step", 0)
         engine.tokens_seen = st.get("tokens_seen", 0)
-
-    loader, data_kind = _make_loader(spec, cfg, data_cfg, batch * accum, rank, world)
+        data_idx = st.get("data_idx")
+        if sched is not None:
+            if st.get("lr_scheduler") is not None:
+                sched.load_state_dict(st["lr_scheduler"])
+            sched.current_step = start_step        # warm-up and cosine phase continue, they do not restart
+            sched.apply()
+    elif sched is not None and start_step:
+        sched.apply()
+    # one loader batch feeds one optimizer step; a checkpoint from before ``data_idx`` existed
+    # (or one that stored 0) falls back to the step count
+    consumed = data_idx if data_idx else start_step
+    loader, data_kind = _make_loader(spec, cfg, data_cfg, batch * accum, rank, world, skip_batches=consumed)
     it = iter(PinnedPrefetcher(loader, depth=4, pin=use_cuda))
     cdir = spec.checkpoint_dir or train_cfg["checkpoint_dir"]
     if spec.checkpoint_format == "B":
@@ -292,7 +321,9 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
     writer = ckpt.AsyncCheckpointWriter() if spec.async_checkpoint else None
 
     def save(step: int, suffix: Optional[str] = None):
-        state = {"step": step, "tokens_seen": engine.tokens_seen, "config_path": spec.config_path}
+        state = {"step": step, "tokens_seen": engine.tokens_seen, "config_path": spec.config_path,
+                 "data_idx": batches_consumed,
+                 "lr_scheduler": sched.state_dict() if sched is not None else None}
         if spec.shard_params:
             ckpt.save_param_sharded(cdir, step, dp, state, rank, writer=writer, ep_rank=mesh.ep_rank, ep_size=mesh.ep)
         elif dp is not None:
@@ -301,18 +332,20 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
         elif spec.checkpoint_format == "C":
             ckpt.save_format_c(cdir, step, model, optimizer, state)
         else:
-            ckpt.save_format_b(os.path.join(cdir, ckpt.format_b_name(step, suffix)), model, optimizer, step, 0, 0,
-                               losses, engine.tokens_seen, spec.config_path)
+            ckpt.save_format_b(os.path.join(cdir, ckpt.format_b_name(step, suffix)), model, optimizer, step, 0,
+                               batches_consumed, losses, engine.tokens_seen, spec.config_path)
 
-    injector = _fault_from_env()
+    injector = _fault_from_env(spec.transport)
     log_every = train_cfg["log_interval"]
     t_last, tok_last = time.time(), engine.tokens_seen
     last_stats = None
+    batches_consumed = consumed
     with InterruptGuard() as guard:
         step = start_step
         while step < total_steps:
             with timer.phase("data"):
                 b = next(it)
+            batches_consumed += 1
             am = None
             if spec.document_mask and "doc_ids" in b:
                 # boundaries instead of a dense (B, 1, S, S) mask: attention stays on the flash kernels
@@ -380,18 +413,32 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
     return out
 
 
-def _fault_from_env():
+def fault_injection_refusal(env, transport: Optional[str]) -> Optional[str]:
+    """Why host-side fault injection may not run on GPUs with this environment (None = it may).  A rank that
+    leaves while its memory is bound to an NVLink multicast object can fault its peers' GPUs."""
+    if env.get("NCCL_NVLS_ENABLE", "1") != "0":
+        return "KMOE_FAULT_INJECT on GPUs needs NCCL_NVLS_ENABLE=0 (plain peer loads and stores only)"
+    if transport not in ("nccl", "gloo") and env.get("TORCH_SYMM_MEM_DISABLE_MULTICAST", "0") != "1":
+        return ("KMOE_FAULT_INJECT on GPUs needs TORCH_SYMM_MEM_DISABLE_MULTICAST=1 (or --transport nccl): the "
+                "symmetric-memory rendezvous of the p2p transport otherwise binds the buffers to a multicast object")
+    return None
+
+
+def _fault_from_env(transport: Optional[str] = None):
     """``KMOE_FAULT_INJECT=rank:step:kind`` (kind = raise | exit | stall) makes that rank fail on the host
     right after that step, with no kernel or collective of its own in flight.  With ``KMOE_FAULT_ONCE=<file>``
     the failure happens only while the file does not exist (it is created first), so a restarted job runs
-    through.  On GPUs the switch multicast must be off (``NCCL_NVLS_ENABLE=0``, which this library's kernels obey
-    too)."""
+    through.  On GPUs nothing of the job may be bound to an NVLink multicast object: ``NCCL_NVLS_ENABLE=0`` (NCCL;
+    this library's kernels obey it too) and either ``TORCH_SYMM_MEM_DISABLE_MULTICAST=1`` (torch's symmetric-memory
+    allocator, which backs the ``p2p`` transport's buffers, otherwise creates and binds one at rendezvous) or a
+    transport that allocates no symmetric memory (``transport`` = ``nccl`` / ``gloo``)."""
     spec = os.environ.get("KMOE_FAULT_INJECT")
     if not spec:
         return None
-    if torch.cuda.is_available() and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0":
-        # a rank that leaves while its buffers are bound to an NVLink multicast object can fault its peers' GPUs
-        raise RuntimeError("KMOE_FAULT_INJECT on GPUs needs NCCL_NVLS_ENABLE=0 (plain peer loads and stores only)")
+    if torch.cuda.is_available():
+        refusal = fault_injection_refusal(os.environ, transport)
+        if refusal:
+            raise RuntimeError(refusal)
     from ..utils.fault import FaultInjector
     r, s_, kind = (spec.split(":") + ["raise"])[:3]
     inj = FaultInjector(int(r), int(s_), kind)
@@ -410,35 +457,3 @@ def _fault_from_env():
         inj.maybe_fail(rank, step)
 
     return fire
-
-
-def _step_with_mask(engine: TrainEngine, b, am):
-    """A step with an explicit additive attention mask (document-masked packing)."""
-    engine.model.train()
-    ids = engine._to_device(b["input_ids"])
-    lab = engine._to_device(b.get("labels", b["input_ids"]))
-    out = _forward_masked(engine.model, ids, lab, am)
-    out["loss"].backward()
-    g = engine.apply_update()
-    if engine.lr_scheduler is not None:
-        engine.lr_scheduler.step()
-    engine.global_step += 1
-    engine.tokens_seen += ids.numel()
-    from .engine import StepStats
-    return StepStats(out["loss"].detach(), out["lm_loss"].detach(), out["aux_loss"], g, ids.numel(),
-                     out.get("multitoken_loss_dict"))
-
-
-def _forward_masked(model, ids, labels, add_mask):
-    """Forward with a (B,1,S,S) additive mask passed straight to the attention layers."""
-    h = model.token_embedding(ids)
-    aux = 0.0
-    add_mask = add_mask.to(h.dtype).clamp(min=torch.finfo(h.dtype).min)
-    for layer in model.layers:
-        h = layer(h, attention_mask=add_mask, position_ids=None)
-        if model.training:
-            aux = aux + layer.aux_loss
-    h = model.final_norm(h)
-    lm, info = model.multitoken_loss.from_hidden(h, [hd.weight for hd in model.lm_heads], labels)
-    loss = lm + aux if (model.training and torch.is_tensor(aux)) else lm
-    return {"loss": loss, "lm_loss": lm, "aux_loss": aux, "multitoken_loss_dict": info}

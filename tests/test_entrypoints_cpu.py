@@ -174,3 +174,119 @@ def test_elastic_launcher_restarts_from_the_newest_complete_checkpoint(tiny_cfg,
     assert elastic_launch.supervise(2, ["t.py"], ck, max_restarts=1, log=lines.append, backoff_s=0.0) == 3
     cmd = elastic_launch.build_command(4, 29500, ["t.py", "--resume", "old", "--checkpoint-dir=x", "--steps", "3"], "ck", "ck")
     assert cmd[-4:] == ["--checkpoint-dir", "ck", "--resume", "ck"] and "old" not in cmd and "--steps" in cmd
+
+
+def _records(path):
+    import json
+    return {r["step"]: r for r in map(json.loads, open(path)) if "loss" in r}
+
+
+@pytest.mark.parametrize("fmt", ["B", "C"])
+def test_resume_continues_schedule_and_data(tiny_cfg, fmt):
+    """After a resume the learning rate and the loss of the next steps equal those of the run that was
+    never interrupted: the schedule continues at the saved step and the consumed batches are not replayed."""
+    from kolmogorov_moe_architecture_b200.training.runner import RunSpec, run_training
+    base = os.path.join(tiny_cfg["dir"], f"resume_{fmt}")
+    common = dict(config_path=tiny_cfg["config"], steps=6, batch_size=2, data_mode="synthetic",
+                  checkpoint_format=fmt, save_interval=3, optimizer_family="adamw")
+    run_training(RunSpec(checkpoint_dir=os.path.join(base, "a"), jsonl=os.path.join(base, "a.jsonl"), **common))
+    cdir = os.path.join(base, "a") if fmt == "C" else os.path.join(base, "a", "tiny")
+    ck = os.path.join(cdir, "checkpoint-3" if fmt == "C" else "checkpoint-3.pt")
+    assert os.path.exists(ck)
+    run_training(RunSpec(checkpoint_dir=os.path.join(base, "b"), jsonl=os.path.join(base, "b.jsonl"), resume=ck,
+                         **common))
+    full, tail = _records(os.path.join(base, "a.jsonl")), _records(os.path.join(base, "b.jsonl"))
+    assert sorted(tail) == [4, 5, 6]
+    lrs = [full[s]["lr"] for s in range(1, 7)]
+    assert len(set(lrs)) == 6, "the warm-up should move the rate at every step of this run"
+    for s in (4, 5, 6):
+        assert tail[s]["lr"] == pytest.approx(full[s]["lr"], rel=1e-12), (s, tail[s]["lr"], full[s]["lr"])
+        assert tail[s]["loss"] == pytest.approx(full[s]["loss"], rel=1e-5), (s, tail[s]["loss"], full[s]["loss"])
+    saved = torch.load(ck if fmt == "B" else os.path.join(ck, "training_state.pt"), map_location="cpu",
+                       weights_only=False)
+    assert saved["data_idx"] == 3
+
+
+def test_checkpoint_completeness_rules(tmp_path):
+    """A directory is a checkpoint only when every writer named in rank 0's manifest has finished."""
+    from kolmogorov_moe_architecture_b200.training import checkpoint as ck
+    d = tmp_path / "checkpoint-5"
+    d.mkdir()
+    # rank 0 has written its state, no rank has dropped a marker yet (killed in that window)
+    ck._write_manifest(str(d), "sharded", 2, ck._expected_files("optimizer", 2, False))
+    for n in ("model.pt", "training_state.pt", "optimizer-rank0.pt"):
+        (d / n).write_bytes(b"x")
+    assert not ck.checkpoint_complete(str(d), 2)
+    ck._mark_complete(str(d), 0)
+    assert not ck.checkpoint_complete(str(d), 2)            # rank 1 still writing
+    (d / "optimizer-rank1.pt").write_bytes(b"x")
+    ck._mark_complete(str(d), 1)
+    assert ck.checkpoint_complete(str(d), 2)
+    assert ck.checkpoint_complete(str(d), 1)                # a smaller job recognises it too
+    # per-rank files without a manifest: rank 0 has not begun
+    e = tmp_path / "checkpoint-7"
+    e.mkdir()
+    (e / "optimizer-rank1.pt").write_bytes(b"x")
+    (e / "training_state.pt").write_bytes(b"x")
+    assert not ck.checkpoint_complete(str(e), 2)
+    # single-writer layout (format C)
+    f = tmp_path / "checkpoint-9"
+    f.mkdir()
+    (f / "model.pt").write_bytes(b"x")
+    assert not ck.checkpoint_complete(str(f), 1)
+    (f / "training_state.pt").write_bytes(b"x")
+    assert ck.checkpoint_complete(str(f), 1)
+    assert ck.latest_complete_checkpoint(str(tmp_path), 2).endswith("checkpoint-9")
+    # pruning never deletes on the strength of an unfinished directory
+    ck.prune_checkpoints(str(tmp_path), keep=1, world=2)
+    assert sorted(os.listdir(tmp_path)) == ["checkpoint-7", "checkpoint-9"]
+
+
+def test_missing_optimizer_shard_is_an_error_at_the_same_world_size(tmp_path):
+    from kolmogorov_moe_architecture_b200.training import checkpoint as ck
+
+    class Pool:
+        world = 2
+        def load_optimizer_state_dict(self, sd):
+            raise AssertionError("not reached")
+
+    model = torch.nn.Linear(4, 4)
+    d = tmp_path / "checkpoint-1"
+    d.mkdir()
+    torch.save(model.state_dict(), d / "model.pt")
+    torch.save({"step": 1}, d / "training_state.pt")
+    ck._write_manifest(str(d), "sharded", 2, ck._expected_files("optimizer", 2, False))
+    with pytest.raises(FileNotFoundError, match="optimizer state of rank 1"):
+        ck.load_sharded(str(d), model, Pool(), rank=1)
+    # written by a job of another size: parameters carry over, moments start fresh
+    ck._write_manifest(str(d), "sharded", 4, ck._expected_files("optimizer", 4, False))
+    assert ck.load_sharded(str(d), model, Pool(), rank=1)["step"] == 1
+
+
+def test_elastic_launcher_environment_and_shrink_refusal(tmp_path, monkeypatch):
+    import elastic_launch
+    from kolmogorov_moe_architecture_b200.training.runner import fault_injection_refusal
+    seen = {}
+
+    def fake_call(cmd, env=None, cwd=None):
+        seen.setdefault("envs", []).append(dict(env))
+        seen.setdefault("cmds", []).append(cmd)
+        return 1
+    monkeypatch.setattr(elastic_launch.subprocess, "call", fake_call)
+    d = tmp_path / "ck" / "checkpoint-2"
+    d.mkdir(parents=True)
+    (d / "experts-rank0.pt").write_bytes(b"x")
+    logs = []
+    rc = elastic_launch.supervise(4, ["train_distributed.py"], str(tmp_path / "ck"), max_restarts=3, shrink=True,
+                                  backoff_s=0.0, env={}, log=logs.append)
+    assert rc == 1
+    env = seen["envs"][0]
+    assert env["NCCL_NVLS_ENABLE"] == "0" and env["KMOE_MULTIMEM"] == "0"
+    assert env["TORCH_SYMM_MEM_DISABLE_MULTICAST"] == "1"
+    assert all("--nproc-per-node=4" in c for c in seen["cmds"]), "expert-parallel checkpoints keep the job size"
+    assert any("--shrink refused" in m for m in logs)
+    # the injector's own guard
+    assert "NCCL_NVLS_ENABLE" in fault_injection_refusal({}, None)
+    assert "TORCH_SYMM_MEM_DISABLE_MULTICAST" in fault_injection_refusal({"NCCL_NVLS_ENABLE": "0"}, "p2p")
+    assert fault_injection_refusal({"NCCL_NVLS_ENABLE": "0"}, "nccl") is None
+    assert fault_injection_refusal({"NCCL_NVLS_ENABLE": "0", "TORCH_SYMM_MEM_DISABLE_MULTICAST": "1"}, None) is None

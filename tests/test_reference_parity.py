@@ -224,3 +224,33 @@ def test_stand_alone_moe_layer_variants_match(ref):
     with contextlib.redirect_stdout(io.StringIO()):
         yr = r(xb)
     assert torch.allclose(o(xb), yr, atol=1e-5)
+
+
+def test_reference_arm_builds_the_benchmark_layer(ref):
+    """The benchmark's reference arm in ``moe_ffn`` mode (Mamba mixer + MoE FFN composed from the
+    reference's own classes) holds exactly the parameters of this framework's model in that mode,
+    loads into it strictly, and gives the same loss."""
+    from baseline.run_reference import _build_model
+    from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig, MoETransformer
+    kw = dict(KW, mod_enabled=True)
+    torch.manual_seed(0)
+    with contextlib.redirect_stdout(io.StringIO()):
+        rmodel = _build_model(ref["transformer"].MoETransformer, ref["config"].AdvancedMoEConfig(**kw), "moe_ffn")
+        stock = _build_model(ref["transformer"].MoETransformer, ref["config"].AdvancedMoEConfig(**kw), "routing_mamba")
+    assert type(rmodel.layers[1]).__name__ == "MambaMoEBlock"
+    assert type(rmodel.layers[1].seq_layer).__name__ == "MambaBlock"
+    assert type(rmodel.layers[1].ffn).__name__ == "MoELayer"
+    assert type(stock.layers[1].seq_layer).__name__ == "RoutingMamba"
+    assert ref["transformer"].TransformerBlock.__name__ == "TransformerBlock"      # lookup restored
+    ours = MoETransformer(AdvancedMoEConfig(mamba_impl="simple", mamba_moe_mode="moe_ffn", **kw), verbose=False)
+    n_ref = sum(p.numel() for p in rmodel.parameters())
+    assert n_ref == sum(p.numel() for p in ours.parameters())
+    assert n_ref != sum(p.numel() for p in stock.parameters())
+    missing, unexpected = ours.load_state_dict(rmodel.state_dict(), strict=True)
+    assert not missing and not unexpected
+    ids = torch.randint(0, 512, (2, 32), generator=torch.Generator().manual_seed(1))
+    rmodel.train(); ours.train()
+    with contextlib.redirect_stdout(io.StringIO()):
+        ro = rmodel(ids, labels=ids)
+    oo = ours(ids, labels=ids, return_logits=False)
+    assert torch.allclose(oo["loss"], ro["loss"], atol=1e-5), (oo["loss"], ro["loss"])
