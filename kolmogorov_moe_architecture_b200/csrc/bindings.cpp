@@ -148,11 +148,15 @@ std::tuple<Tensor, Tensor> swiglu_bwd(const Tensor& g, const Tensor& u, const Te
 Tensor conv1d_fwd(const Tensor& x, const Tensor& w, const OptT& bias, bool act) {
   c10::cuda::CUDAGuard guard(x.device());
   need_bf16(x, "x"); need_f32(w, "w");
-  TORCH_CHECK(x.dim() == 3 && w.dim() == 2 && w.size(1) == 4, "x [B,S,C], w [C,4]");
+  // w [C,4], or [G,C,4] with G parameter sets: batch entries [g*B/G, (g+1)*B/G) use set g (bias [G,C] then)
+  TORCH_CHECK(x.dim() == 3 && (w.dim() == 2 || w.dim() == 3) && w.size(-1) == 4 && w.is_contiguous(),
+              "x [B,S,C], w [C,4] or [G,C,4]");
   const int B = x.size(0), S = x.size(1), C = x.size(2);
+  const int G = w.dim() == 3 ? (int)w.size(0) : 1;
+  TORCH_CHECK(w.size(-2) == C && B % G == 0, "w does not match x");
   Tensor y = at::empty({B, S, C}, x.options());
   check(kmoe_conv1d_fwd(x.data_ptr(), w.data_ptr<float>(), (const float*)ptr_or_null(bias), y.data_ptr(), B, S, C,
-                        row_stride(x), act ? 1 : 0, cur_stream()), "conv1d_fwd");
+                        row_stride(x), act ? 1 : 0, G, cur_stream()), "conv1d_fwd");
   return y;
 }
 
@@ -162,12 +166,14 @@ std::tuple<Tensor, Tensor, Tensor> conv1d_bwd(const Tensor& x, const Tensor& w, 
   need_bf16(x, "x"); need_bf16(dy, "dy"); need_f32(w, "w");
   TORCH_CHECK(dy.is_contiguous());
   const int B = x.size(0), S = x.size(1), C = x.size(2);
+  const int G = w.dim() == 3 ? (int)w.size(0) : 1;
+  TORCH_CHECK(w.is_contiguous() && w.size(-2) == C && B % G == 0, "w does not match x");
   Tensor dx = at::empty({B, S, C}, x.options());
-  Tensor dw = at::zeros({C, 4}, w.options());
-  Tensor db = at::zeros({C}, w.options());
+  Tensor dw = at::zeros_like(w);
+  Tensor db = w.dim() == 3 ? at::zeros({G, C}, w.options()) : at::zeros({C}, w.options());
   check(kmoe_conv1d_bwd(x.data_ptr(), w.data_ptr<float>(), (const float*)ptr_or_null(bias), dy.data_ptr(),
                         dx.data_ptr(), dw.data_ptr<float>(), db.data_ptr<float>(), B, S, C, row_stride(x),
-                        act ? 1 : 0, cur_stream()), "conv1d_bwd");
+                        act ? 1 : 0, G, cur_stream()), "conv1d_bwd");
   return {dx, dw, db};
 }
 
@@ -176,8 +182,11 @@ std::tuple<Tensor, Tensor> scan_fwd(const Tensor& u, const Tensor& delta, const 
                                     bool softplus, bool save) {
   c10::cuda::CUDAGuard guard(u.device());
   need_bf16(u, "u"); need_bf16(delta, "delta"); need_f32(A, "A"); need_f32(Bm, "B"); need_f32(Cm, "C");
-  TORCH_CHECK(u.is_contiguous() && delta.is_contiguous() && u.dim() == 3);
-  const int B = u.size(0), S = u.size(1), C = u.size(2), N = A.size(1);
+  // A [C,N], or [G,C,N] with G parameter sets over the batch (D, dt_bias [G,C] then)
+  TORCH_CHECK(u.is_contiguous() && delta.is_contiguous() && u.dim() == 3 && A.is_contiguous());
+  const int B = u.size(0), S = u.size(1), C = u.size(2), N = A.size(-1);
+  const int G = A.dim() == 3 ? (int)A.size(0) : 1;
+  TORCH_CHECK(A.size(-2) == C && B % G == 0, "A does not match u");
   Tensor out = at::empty_like(u);
   const int nch = (S + kmoe_scan_chunk() - 1) / kmoe_scan_chunk();
   Tensor ckpt = save ? at::empty({B, nch, N, C}, A.options()) : at::empty({0}, A.options());
@@ -186,7 +195,7 @@ std::tuple<Tensor, Tensor> scan_fwd(const Tensor& u, const Tensor& delta, const 
   check(kmoe_scan_fwd(u.data_ptr(), delta.data_ptr(), has_z ? z->data_ptr() : nullptr, A.data_ptr<float>(),
                       Bm.data_ptr<float>(), Cm.data_ptr<float>(), (const float*)ptr_or_null(D),
                       (const float*)ptr_or_null(dt_bias), out.data_ptr(), save ? ckpt.data_ptr<float>() : nullptr, B,
-                      S, C, N, has_z ? row_stride(*z) : 0, softplus ? 1 : 0, cur_stream()), "scan_fwd");
+                      S, C, N, has_z ? row_stride(*z) : 0, softplus ? 1 : 0, G, cur_stream()), "scan_fwd");
   return {out, ckpt};
 }
 
@@ -196,19 +205,22 @@ std::vector<Tensor> scan_bwd(const Tensor& u, const Tensor& delta, const OptT& z
   c10::cuda::CUDAGuard guard(u.device());
   need_bf16(dout, "dout");
   TORCH_CHECK(dout.is_contiguous());
-  const int B = u.size(0), S = u.size(1), C = u.size(2), N = A.size(1);
+  const int B = u.size(0), S = u.size(1), C = u.size(2), N = A.size(-1);
+  const int G = A.dim() == 3 ? (int)A.size(0) : 1;
+  TORCH_CHECK(A.is_contiguous() && A.size(-2) == C && B % G == 0, "A does not match u");
   const bool has_z = z.has_value() && z->defined();
   Tensor du = at::empty_like(u), dd = at::empty_like(u);
   Tensor dz = has_z ? at::empty({B, S, C}, u.options()) : at::empty({0}, u.options());
   auto f32 = A.options();
-  Tensor dA = at::zeros({C, N}, f32), dB = at::zeros({B, S, N}, f32), dC = at::zeros({B, S, N}, f32);
-  Tensor dD = at::zeros({C}, f32), dbias = at::zeros({C}, f32);
+  Tensor dA = at::zeros_like(A), dB = at::zeros({B, S, N}, f32), dC = at::zeros({B, S, N}, f32);
+  Tensor dD = A.dim() == 3 ? at::zeros({G, C}, f32) : at::zeros({C}, f32);
+  Tensor dbias = at::zeros_like(dD);
   check(kmoe_scan_bwd(u.data_ptr(), delta.data_ptr(), has_z ? z->data_ptr() : nullptr, A.data_ptr<float>(),
                       Bm.data_ptr<float>(), Cm.data_ptr<float>(), (const float*)ptr_or_null(D),
                       (const float*)ptr_or_null(dt_bias), dout.data_ptr(), ckpt.data_ptr<float>(), du.data_ptr(),
                       dd.data_ptr(), has_z ? dz.data_ptr() : nullptr, C, dA.data_ptr<float>(), dB.data_ptr<float>(),
                       dC.data_ptr<float>(), dD.data_ptr<float>(), dbias.data_ptr<float>(), B, S, C, N,
-                      has_z ? row_stride(*z) : 0, softplus ? 1 : 0, cur_stream()), "scan_bwd");
+                      has_z ? row_stride(*z) : 0, softplus ? 1 : 0, G, cur_stream()), "scan_bwd");
   return {du, dd, dz, dA, dB, dC, dD, dbias};
 }
 

@@ -117,18 +117,20 @@ int kmoe_swiglu_bwd(const void* g, const void* u, const void* dh, void* dg, void
                     long long ldg, long long ldu, long long ldo, const int* live_rows, cudaStream_t st);
 
 // --------------------------------------------------------------------------- Mamba
+// groups: number of parameter sets stacked along the first dimension of w / bias (A, D, dt_bias for the scan);
+// batch entries [g * B / groups, (g + 1) * B / groups) use set g.  1 = one set for the whole batch.
 int kmoe_conv1d_fwd(const void* x, const float* w, const float* bias, void* y, int B, int S, int C, long long ldx,
-                    int act, cudaStream_t st);
+                    int act, int groups, cudaStream_t st);
 int kmoe_conv1d_bwd(const void* x, const float* w, const float* bias, const void* dy, void* dx, float* dw,
-                    float* dbias, int B, int S, int C, long long ldx, int act, cudaStream_t st);
+                    float* dbias, int B, int S, int C, long long ldx, int act, int groups, cudaStream_t st);
 int kmoe_scan_chunk(void);
 int kmoe_scan_fwd(const void* u, const void* delta, const void* z, const float* A, const float* Bm, const float* Cm,
                   const float* D, const float* dt_bias, void* out, float* ckpt, int B, int S, int C, int N,
-                  long long ldz, int softplus, cudaStream_t st);
+                  long long ldz, int softplus, int groups, cudaStream_t st);
 int kmoe_scan_bwd(const void* u, const void* delta, const void* z, const float* A, const float* Bm, const float* Cm,
                   const float* D, const float* dt_bias, const void* dout, const float* ckpt, void* du, void* ddelta,
                   void* dz, long long lddz, float* dA, float* dB, float* dC, float* dD, float* dbias, int B, int S,
-                  int C, int N, long long ldz, int softplus, cudaStream_t st);
+                  int C, int N, long long ldz, int softplus, int groups, cudaStream_t st);
 
 // ------------------------------------------------------------------- MoE bookkeeping
 int kmoe_moe_max_rows(int n_assign, int E);

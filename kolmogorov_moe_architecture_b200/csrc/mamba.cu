@@ -28,13 +28,14 @@ constexpr int CONV_T = 64;  // time steps per thread
 
 __global__ void conv1d_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
                                   const float* __restrict__ bias, __nv_bfloat16* __restrict__ y, int S, int C,
-                                  long long ldx, int act) {
+                                  long long ldx, int act, int bpg) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
   const int b = blockIdx.z;
   const int t0 = blockIdx.y * CONV_T;
-  const float w0 = w[c * 4 + 0], w1 = w[c * 4 + 1], w2 = w[c * 4 + 2], w3 = w[c * 4 + 3];
-  const float bs = bias ? bias[c] : 0.f;
+  const int pc = (b / bpg) * C + c;   // parameter row: batch entries [g*bpg, (g+1)*bpg) use parameter set g
+  const float w0 = w[pc * 4 + 0], w1 = w[pc * 4 + 1], w2 = w[pc * 4 + 2], w3 = w[pc * 4 + 3];
+  const float bs = bias ? bias[pc] : 0.f;
   const __nv_bfloat16* xb = x + (size_t)b * S * ldx + c;
   __nv_bfloat16* yb = y + (size_t)b * S * C + c;
   float x0 = t0 >= 3 ? bf2f(xb[(size_t)(t0 - 3) * ldx]) : 0.f;
@@ -55,13 +56,14 @@ __global__ void conv1d_fwd_kernel(const __nv_bfloat16* __restrict__ x, const flo
 __global__ void conv1d_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
                                   const float* __restrict__ bias, const __nv_bfloat16* __restrict__ dy,
                                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, float* __restrict__ dbias,
-                                  int S, int C, long long ldx, int act) {
+                                  int S, int C, long long ldx, int act, int bpg) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
   const int b = blockIdx.z;
   const int t0 = blockIdx.y * CONV_T;
-  const float w0 = w[c * 4 + 0], w1 = w[c * 4 + 1], w2 = w[c * 4 + 2], w3 = w[c * 4 + 3];
-  const float bs = bias ? bias[c] : 0.f;
+  const int pc = (b / bpg) * C + c;
+  const float w0 = w[pc * 4 + 0], w1 = w[pc * 4 + 1], w2 = w[pc * 4 + 2], w3 = w[pc * 4 + 3];
+  const float bs = bias ? bias[pc] : 0.f;
   const __nv_bfloat16* xb = x + (size_t)b * S * ldx + c;
   const __nv_bfloat16* gb = dy + (size_t)b * S * C + c;
   __nv_bfloat16* dxb = dx + (size_t)b * S * C + c;
@@ -96,11 +98,11 @@ __global__ void conv1d_bwd_kernel(const __nv_bfloat16* __restrict__ x, const flo
     p0 = p1; p1 = p2; p2 = p3;
   }
   // the dpre window starts empty, which is exact: dx[td >= t0] never reads dpre[< t0]
-  atomicAdd(&dw[c * 4 + 0], aw0);
-  atomicAdd(&dw[c * 4 + 1], aw1);
-  atomicAdd(&dw[c * 4 + 2], aw2);
-  atomicAdd(&dw[c * 4 + 3], aw3);
-  if (dbias) atomicAdd(&dbias[c], ab);
+  atomicAdd(&dw[pc * 4 + 0], aw0);
+  atomicAdd(&dw[pc * 4 + 1], aw1);
+  atomicAdd(&dw[pc * 4 + 2], aw2);
+  atomicAdd(&dw[pc * 4 + 3], aw3);
+  if (dbias) atomicAdd(&dbias[pc], ab);
 }
 
 // ----------------------------------------------------------- selective scan
@@ -116,6 +118,8 @@ struct ScanArgs {
   int S, C;
   long long ldz;
   int softplus;
+  int bpg;                     // batch entries per parameter set: A, D, dt_bias (and their gradients) of
+                               // batch entry b are rows (b / bpg) * C + c
 };
 
 // Thread mapping of both scan kernels: a CTA of 128 threads owns 32 consecutive channels;
@@ -146,15 +150,16 @@ scan_fwd_kernel(ScanArgs a, __nv_bfloat16* __restrict__ out, float* __restrict__
   __shared__ __align__(16) __nv_bfloat16 ytile[FWD_T][SCAN_CH];
   const int tid = threadIdx.x, ch = tid >> 2, sg = tid & 3;
   const int c0 = blockIdx.x * SCAN_CH, c = c0 + ch, b = blockIdx.y;
+  const int pc = (b / a.bpg) * a.C + c;   // row of this channel's parameters
   const bool has_z = a.z != nullptr;
   float An[SCAN_SG], h[SCAN_SG];
 #pragma unroll
   for (int j = 0; j < SCAN_SG; ++j) {
-    An[j] = a.A[c * SCAN_N + sg * SCAN_SG + j] * 1.4426950408889634f;
+    An[j] = a.A[pc * SCAN_N + sg * SCAN_SG + j] * 1.4426950408889634f;
     h[j] = 0.f;
   }
-  const float Dc = a.D ? a.D[c] : 0.f;
-  const float bias = a.dt_bias ? a.dt_bias[c] : 0.f;
+  const float Dc = a.D ? a.D[pc] : 0.f;
+  const float bias = a.dt_bias ? a.dt_bias[pc] : 0.f;
   const int nchunks = (a.S + SCAN_CHUNK - 1) / SCAN_CHUNK;
   const int ntiles = (a.S + FWD_T - 1) / FWD_T;
   const int lrow = tid >> 2, lpart = tid & 3;
@@ -233,16 +238,17 @@ scan_bwd_kernel(ScanArgs a, const __nv_bfloat16* __restrict__ dout, const float*
   __shared__ __align__(16) __nv_bfloat16 du_t[SCAN_CHUNK][SCAN_CH], dd_t[SCAN_CHUNK][SCAN_CH], dz_t[SCAN_CHUNK][SCAN_CH];
   const int tid = threadIdx.x, lane = tid & 31, ch = tid >> 2, sg = tid & 3;
   const int c0 = blockIdx.x * SCAN_CH, c = c0 + ch, b = blockIdx.y;
+  const int pc = (b / a.bpg) * a.C + c;   // row of this channel's parameters and of their gradients
   const bool has_z = a.z != nullptr;
   float An[SCAN_SG], g[SCAN_SG], dAacc[SCAN_SG];
 #pragma unroll
   for (int j = 0; j < SCAN_SG; ++j) {
-    An[j] = a.A[c * SCAN_N + sg * SCAN_SG + j];
+    An[j] = a.A[pc * SCAN_N + sg * SCAN_SG + j];
     g[j] = 0.f;
     dAacc[j] = 0.f;
   }
-  const float Dc = a.D ? a.D[c] : 0.f;
-  const float bias = a.dt_bias ? a.dt_bias[c] : 0.f;
+  const float Dc = a.D ? a.D[pc] : 0.f;
+  const float bias = a.dt_bias ? a.dt_bias[pc] : 0.f;
   float dDacc = 0.f, dbacc = 0.f;
   const int nchunks = (a.S + SCAN_CHUNK - 1) / SCAN_CHUNK;
   for (int i = tid; i < SCAN_CHUNK * SCAN_N; i += blockDim.x) {
@@ -394,10 +400,10 @@ scan_bwd_kernel(ScanArgs a, const __nv_bfloat16* __restrict__ dout, const float*
   }
   cp_async_wait<0>();
 #pragma unroll
-  for (int j = 0; j < SCAN_SG; ++j) atomicAdd(&dA[c * SCAN_N + sg * SCAN_SG + j], dAacc[j]);
+  for (int j = 0; j < SCAN_SG; ++j) atomicAdd(&dA[pc * SCAN_N + sg * SCAN_SG + j], dAacc[j]);
   if (sg == 0) {
-    if (dD) atomicAdd(&dD[c], dDacc);
-    if (dbias) atomicAdd(&dbias[c], dbacc);
+    if (dD) atomicAdd(&dD[pc], dDacc);
+    if (dbias) atomicAdd(&dbias[pc], dbacc);
   }
 }
 
@@ -406,17 +412,21 @@ scan_bwd_kernel(ScanArgs a, const __nv_bfloat16* __restrict__ dout, const float*
 using namespace kmoe;
 
 extern "C" int kmoe_conv1d_fwd(const void* x, const float* w, const float* bias, void* y, int B, int S, int C,
-                               long long ldx, int act, cudaStream_t st) {
+                               long long ldx, int act, int groups, cudaStream_t st) {
+  if (groups < 1 || B % groups) return -1;
   dim3 grid((C + 127) / 128, (S + CONV_T - 1) / CONV_T, B);
-  conv1d_fwd_kernel<<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, w, bias, (__nv_bfloat16*)y, S, C, ldx, act);
+  conv1d_fwd_kernel<<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, w, bias, (__nv_bfloat16*)y, S, C, ldx, act,
+                                          B / groups);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 extern "C" int kmoe_conv1d_bwd(const void* x, const float* w, const float* bias, const void* dy, void* dx, float* dw,
-                               float* dbias, int B, int S, int C, long long ldx, int act, cudaStream_t st) {
+                               float* dbias, int B, int S, int C, long long ldx, int act, int groups,
+                               cudaStream_t st) {
+  if (groups < 1 || B % groups) return -1;
   dim3 grid((C + 127) / 128, (S + CONV_T - 1) / CONV_T, B);
   conv1d_bwd_kernel<<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, w, bias, (const __nv_bfloat16*)dy,
-                                          (__nv_bfloat16*)dx, dw, dbias, S, C, ldx, act);
+                                          (__nv_bfloat16*)dx, dw, dbias, S, C, ldx, act, B / groups);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -424,25 +434,25 @@ extern "C" int kmoe_scan_chunk(void) { return SCAN_CHUNK; }
 
 extern "C" int kmoe_scan_fwd(const void* u, const void* delta, const void* z, const float* A, const float* Bm,
                              const float* Cm, const float* D, const float* dt_bias, void* out, float* ckpt, int B,
-                             int S, int C, int N, long long ldz, int softplus, cudaStream_t st) {
-  if (N != SCAN_N) return -1;
+                             int S, int C, int N, long long ldz, int softplus, int groups, cudaStream_t st) {
+  if (N != SCAN_N || groups < 1 || B % groups) return -1;
   ScanArgs a{(const __nv_bfloat16*)u, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)z, A, Bm, Cm, D, dt_bias,
-             S, C, ldz, softplus};
+             S, C, ldz, softplus, B / groups};
   if (C % SCAN_CH || (z != nullptr && ldz % 8)) return -4;
   dim3 grid(C / SCAN_CH, B);
   scan_fwd_kernel<<<grid, SCAN_CH * SCAN_SG, 0, st>>>(a, (__nv_bfloat16*)out, ckpt);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-// dA [C,N], dB/dC [B,S,N], dD [C], dbias [C] are fp32 and must be zeroed by the caller.
+// dA [G,C,N], dB/dC [B,S,N], dD [G,C], dbias [G,C] (G = groups) are fp32 and must be zeroed by the caller.
 extern "C" int kmoe_scan_bwd(const void* u, const void* delta, const void* z, const float* A, const float* Bm,
                              const float* Cm, const float* D, const float* dt_bias, const void* dout,
                              const float* ckpt, void* du, void* ddelta, void* dz, long long lddz, float* dA, float* dB,
                              float* dC, float* dD, float* dbias, int B, int S, int C, int N, long long ldz,
-                             int softplus, cudaStream_t st) {
-  if (N != SCAN_N) return -1;
+                             int softplus, int groups, cudaStream_t st) {
+  if (N != SCAN_N || groups < 1 || B % groups) return -1;
   ScanArgs a{(const __nv_bfloat16*)u, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)z, A, Bm, Cm, D, dt_bias,
-             S, C, ldz, softplus};
+             S, C, ldz, softplus, B / groups};
   if (C % SCAN_CH || (z != nullptr && (ldz % 8 || lddz % 8))) return -4;
   dim3 grid(C / SCAN_CH, B);
   const int hs_bytes = (SCAN_CHUNK + 1) * SCAN_CH * SCAN_SG * sizeof(float4);

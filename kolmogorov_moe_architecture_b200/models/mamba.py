@@ -77,6 +77,30 @@ class SimpleSSM(nn.Module):
         return self.out_proj(ops.swiglu(z, x))
 
 
+def mamba_forward_batched(mixers, hidden_states: torch.Tensor) -> torch.Tensor:
+    """All of ``mixers`` (``Mamba`` modules of equal shape) on the same (B, S, d) input in one pass:
+    returns (U, B, S, d).  The projections are batched GEMMs over the stacked weights; convolution and
+    scan run once on the (U * B, S, C) stack, each slice of B batch entries with its own mixer's
+    parameters (the ops take (U, C, ...) parameter sets).  Same arithmetic as calling the mixers one by one."""
+    m0 = mixers[0]
+    U = len(mixers)
+    B, S, d = hidden_states.shape
+    C, N, R = m0.d_inner, m0.d_state, m0.dt_rank
+    st = lambda f: torch.stack([f(m) for m in mixers])
+    x2 = hidden_states.reshape(1, B * S, d)
+    xz = torch.matmul(x2, st(lambda m: m.in_proj.weight).transpose(1, 2)).reshape(U * B, S, 2 * C)
+    x, z = xz[..., :C], xz[..., C:]
+    x = ops.causal_conv1d(x, st(lambda m: m.conv1d.weight.squeeze(1)), st(lambda m: m.conv1d.bias), activation=True)
+    x_dbl = torch.bmm(x.reshape(U, B * S, C), st(lambda m: m.x_proj.weight).transpose(1, 2))
+    dt, Bm, Cm = torch.split(x_dbl, [R, N, N], dim=-1)
+    delta = torch.bmm(dt, st(lambda m: m.dt_proj.weight).transpose(1, 2)).reshape(U * B, S, C)
+    A = -torch.exp(st(lambda m: m.A_log).float())
+    y = ops.selective_scan(x, delta, A, Bm.reshape(U * B, S, N), Cm.reshape(U * B, S, N),
+                           st(lambda m: m.D).float(), z, st(lambda m: m.dt_proj.bias).float(), delta_softplus=True)
+    out = torch.bmm(y.reshape(U, B * S, C), st(lambda m: m.out_proj.weight).transpose(1, 2))
+    return out.reshape(U, B, S, d)
+
+
 class MambaBlock(nn.Module):
     """Holds the mixer under the attribute ``mamba`` (state-dict prefix ``mamba.``)."""
 
@@ -127,6 +151,9 @@ class RoutingMamba(nn.Module):
         self.load_balance_loss_weight = config.moe_load_balance_loss_weight
         self.router_z_loss_weight = config.moe_router_z_loss_weight
         self.aux_loss = 0.0
+        # one batched pass over the selected experts instead of one pass per expert
+        import os
+        self.batched = os.environ.get("KMOE_ROM_BATCHED", "1") != "0"
 
     def _route(self, hidden_states: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         logits = self.router(hidden_states)
@@ -139,9 +166,15 @@ class RoutingMamba(nn.Module):
         mix = torch.zeros(*hidden_states.shape[:2], self.n_experts, dtype=w.dtype, device=w.device)
         mix = mix.scatter_add(-1, idx, w)                       # (B, S, E), differentiable in w
         used = (self._counts > 0).tolist()                      # one host read for all experts
-        out = torch.zeros_like(hidden_states)
-        for e, expert in enumerate(self.experts):
-            if used[e]:
-                out = out + mix[..., e:e + 1].to(hidden_states.dtype) * expert(hidden_states)
+        sel = [e for e in range(self.n_experts) if used[e]]
+        mixers = [self.experts[e].mamba.mamba for e in sel]
+        if self.batched and sel and all(isinstance(m, Mamba) for m in mixers):
+            ys = mamba_forward_batched(mixers, hidden_states)                       # (U, B, S, d)
+            wsel = mix[..., sel].permute(2, 0, 1).unsqueeze(-1).to(hidden_states.dtype)
+            out = (wsel * ys).sum(0)
+        else:
+            out = torch.zeros_like(hidden_states)
+            for e in sel:
+                out = out + mix[..., e:e + 1].to(hidden_states.dtype) * self.experts[e](hidden_states)
         self.aux_loss = self._aux if self.training else 0.0
         return out

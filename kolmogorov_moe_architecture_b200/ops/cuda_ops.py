@@ -237,8 +237,8 @@ class _Conv1d(torch.autograd.Function):
 
 
 def causal_conv1d(x, weight, bias, activation=True):
-    if not (_bf16(x) and weight.shape[1] == 4 and x.dim() == 3):
-        _fallback("causal_conv1d", f"dtype {x.dtype} width {weight.shape[1]}")
+    if not (_bf16(x) and weight.shape[-1] == 4 and x.dim() == 3):
+        _fallback("causal_conv1d", f"dtype {x.dtype} width {weight.shape[-1]}")
         return eager.causal_conv1d(x, weight, bias, activation)
     if not _rows_ok(x):
         x = x.contiguous()
@@ -273,8 +273,8 @@ class _Scan(torch.autograd.Function):
 
 
 def selective_scan(u, delta, A, Bm, Cm, D, z, delta_bias, delta_softplus=True):
-    if not (_bf16(u) and _bf16(delta) and A.shape[1] == 16 and (z is None or _bf16(z))):
-        _fallback("selective_scan", f"dtype {u.dtype} d_state {A.shape[1]}")
+    if not (_bf16(u) and _bf16(delta) and A.shape[-1] == 16 and (z is None or _bf16(z))):
+        _fallback("selective_scan", f"dtype {u.dtype} d_state {A.shape[-1]}")
         return eager.selective_scan(u, delta, A, Bm, Cm, D, z, delta_bias, delta_softplus)
     u, delta = u.contiguous(), delta.contiguous()
     if z is not None and not _rows_ok(z):

@@ -91,7 +91,13 @@ def doc_start_to_mask(doc_start: torch.Tensor, dtype=torch.float32) -> torch.Ten
 # ---------------------------------------------------------------------- mamba
 def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
                   activation: bool = True) -> torch.Tensor:
-    """Depthwise causal conv over time. x (B, S, C) channels-last; weight (C, W)."""
+    """Depthwise causal conv over time. x (B, S, C) channels-last; weight (C, W), or (G, C, W) with G
+    parameter sets: batch entries [g B/G, (g+1) B/G) use set g (bias (G, C) then)."""
+    if weight.dim() == 3:
+        G = weight.shape[0]
+        parts = x.chunk(G, dim=0)
+        return torch.cat([causal_conv1d(parts[g], weight[g], bias[g] if bias is not None else None, activation)
+                          for g in range(G)], dim=0)
     C, W = weight.shape
     y = F.conv1d(x.transpose(1, 2), weight.unsqueeze(1), bias, padding=W - 1, groups=C)[..., : x.shape[1]]
     y = y.transpose(1, 2)
@@ -105,8 +111,16 @@ def selective_scan(u: torch.Tensor, delta: torch.Tensor, A: torch.Tensor, Bm: to
 
     u, delta, z: (B, S, C); A: (C, N); Bm, Cm: (B, S, N); D, delta_bias: (C,).
     h_t = exp(delta_t A) h_{t-1} + delta_t B_t u_t ;  y_t = <C_t, h_t> + D u_t ;
-    y_t *= silu(z_t).  Evaluated sequentially in fp32.
+    y_t *= silu(z_t).  Evaluated sequentially in fp32.  A (G, C, N) with D, delta_bias (G, C): G parameter
+    sets over consecutive slices of the batch.
     """
+    if A.dim() == 3:
+        G = A.shape[0]
+        sl = lambda t: t.chunk(G, dim=0) if t is not None else [None] * G
+        us, ds, bs, cs, zs = sl(u), sl(delta), sl(Bm), sl(Cm), sl(z)
+        return torch.cat([selective_scan(us[g], ds[g], A[g], bs[g], cs[g], D[g] if D is not None else None, zs[g],
+                                         delta_bias[g] if delta_bias is not None else None, delta_softplus)
+                          for g in range(G)], dim=0)
     dt = delta.float()
     if delta_bias is not None:
         dt = dt + delta_bias.float()

@@ -181,3 +181,26 @@ def test_packed_docs_sanitises_start_positions_given_from_outside():
     assert p.to("cpu").doc_start.tolist() == p.doc_start.tolist() and len(p.chunk(1)) == 1
     ids = torch.tensor([[7, 7, 8, 8, 8, 9]])
     assert PackedDocs(doc_ids=ids).doc_start.tolist() == [[0, 0, 2, 2, 2, 5]]
+
+
+def test_routing_mamba_batched_pass_equals_one_pass_per_expert():
+    """All selected Mamba experts in one stacked pass (grouped convolution / scan parameters, batched
+    projections) against the loop over experts: outputs, input gradient and every parameter gradient."""
+    from kolmogorov_moe_architecture_b200.models.mamba import RoutingMamba
+    cfg = kmoe.get_tiny_debug_config(vocab_size=128, d_model=32, n_heads=2, n_kv_heads=1, head_dim=16, d_ff=64,
+                                     d_ff_expert=32, max_seq_len=16, n_pred_tokens=1, aux_loss_weights=(1.0,))
+    torch.manual_seed(0)
+    m = RoutingMamba(cfg, 1).train()
+    x = torch.randn(2, 16, 32, requires_grad=True)
+    res = {}
+    for flag in (False, True):
+        m.batched = flag
+        m.zero_grad()
+        x.grad = None
+        y = m(x)
+        (y * torch.arange(32.0)).sum().backward()
+        res[flag] = (y.detach().clone(), x.grad.clone(),
+                     {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None})
+    a, b = res[False], res[True]
+    assert torch.allclose(a[0], b[0], atol=1e-5) and torch.allclose(a[1], b[1], atol=1e-5)
+    assert set(a[2]) == set(b[2]) and all(torch.allclose(a[2][n], b[2][n], atol=1e-5) for n in a[2])

@@ -113,6 +113,69 @@ def test_selective_scan(S, C):
         assert _rel(a.grad, b.grad) < 4e-2, name
 
 
+def test_conv_and_scan_with_parameter_sets_over_the_batch():
+    """(G, C, ...) parameters: every slice of B / G batch entries uses its own set, forward and all gradients
+    (the fp32 definition applies the sets slice by slice)."""
+    ops, c, eager = _mods()
+    G, Bg, S, C, N = 3, 2, 45, 96, 16
+    B = G * Bg
+    xz = _bf(B, S, 2 * C, grad=True)
+    w = torch.randn(G, C, 4, device="cuda", requires_grad=True)
+    b = torch.randn(G, C, device="cuda", requires_grad=True)
+    y = ops.causal_conv1d(xz[..., :C], w, b, True)
+    go = _bf(B, S, C)
+    y.backward(go)
+    xr, wr, br = _f32_leaf(xz), _f32_leaf(w), _f32_leaf(b)
+    yr = eager.causal_conv1d(xr[..., :C], wr, br, True)
+    yr.backward(go.float())
+    assert _rel(y, yr) < 1e-2 and _rel(xz.grad, xr.grad) < 2e-2
+    assert _rel(w.grad, wr.grad) < 2e-2 and _rel(b.grad, br.grad) < 2e-2
+    u = _bf(B, S, C, grad=True)
+    delta = _bf(B, S, C, scale=0.5, grad=True)
+    z2 = _bf(B, S, 2 * C, grad=True)
+    A = (-torch.exp(torch.randn(G, C, N, device="cuda") * 0.5)).requires_grad_(True)
+    Bm, Cm = _bf(B, S, N, grad=True), _bf(B, S, N, grad=True)
+    D = torch.randn(G, C, device="cuda", requires_grad=True)
+    bias = torch.randn(G, C, device="cuda", requires_grad=True)
+    y = ops.selective_scan(u, delta, A, Bm, Cm, D, z2[..., C:], bias, True)
+    y.backward(go)
+    ur, dr, Ar, Br, Cr, Dr, zr, bir = [_f32_leaf(t) for t in (u, delta, A, Bm, Cm, D, z2, bias)]
+    yr = eager.selective_scan(ur, dr, Ar, Br, Cr, Dr, zr[..., C:], bir, True)
+    yr.backward(go.float())
+    assert _rel(y, yr) < 2e-2
+    for name, a_, b_ in [("u", u, ur), ("delta", delta, dr), ("A", A, Ar), ("B", Bm, Br), ("C", Cm, Cr),
+                         ("D", D, Dr), ("z", z2, zr), ("bias", bias, bir)]:
+        assert _rel(a_.grad, b_.grad) < 4e-2, name
+    # the sets really differ per slice: swapping two sets changes those slices only
+    with torch.no_grad():
+        A2 = A.detach().clone()
+        A2[[0, 1]] = A2[[1, 0]]
+        y2 = ops.selective_scan(u, delta, A2, Bm, Cm, D, z2[..., C:], bias, True)
+    assert torch.equal(y2[2 * Bg:], y.detach()[2 * Bg:]) and not torch.equal(y2[:Bg], y.detach()[:Bg])
+
+
+def test_routing_mamba_batched_pass_on_the_kernels():
+    import kolmogorov_moe_architecture_b200 as kmoe
+    from kolmogorov_moe_architecture_b200.models.mamba import RoutingMamba
+    cfg = kmoe.get_tiny_debug_config(vocab_size=128, d_model=128, n_heads=2, n_kv_heads=1, head_dim=64, d_ff=256,
+                                     d_ff_expert=128, max_seq_len=64, n_pred_tokens=1, aux_loss_weights=(1.0,))
+    torch.manual_seed(0)
+    m = RoutingMamba(cfg, 1).cuda().to(torch.bfloat16).train()
+    x = _bf(2, 64, 128, grad=True)
+    go = _bf(2, 64, 128)
+    res = {}
+    for flag in (False, True):
+        m.batched = flag
+        m.zero_grad()
+        x.grad = None
+        y = m(x)
+        y.backward(go)
+        res[flag] = (y.detach().float(), x.grad.float(), {n: p.grad.float() for n, p in m.named_parameters() if p.grad is not None})
+    a, b = res[False], res[True]
+    assert _rel(b[0], a[0]) < 2e-2 and _rel(b[1], a[1]) < 3e-2
+    assert set(a[2]) == set(b[2]) and all(_rel(b[2][n], a[2][n]) < 5e-2 for n in a[2])
+
+
 @pytest.mark.parametrize("T,E,k,drop", [(300, 4, 2, False), (64, 8, 2, False), (513, 4, 1, True)])
 def test_grouped_swiglu_fwd_bwd(T, E, k, drop):
     ops, c, eager = _mods()
