@@ -137,8 +137,10 @@ class RoutingMamba(nn.Module):
     outputs are mixed per token with the routing weights.  The per-token mixing
     weight of expert e is ``sum_k w[t,k] * [idx[t,k] == e]``, computed for all
     experts at once with a scatter instead of the reference's Python loops over
-    ``unique(experts)`` x ``top_k`` (mamba.py:266-304); experts nobody selected are
-    skipped without a host round trip per expert by reading the usage mask once.
+    ``unique(experts)`` x ``top_k`` (mamba.py:266-304).  With selective-scan experts all
+    experts run in one stacked pass (one convolution and one scan launch for the layer, no
+    host read); the per-expert loop remains for the ``SimpleSSM`` experts, where experts
+    nobody selected are skipped by reading the usage mask once.
     """
 
     def __init__(self, config, layer_idx: int):
@@ -165,14 +167,15 @@ class RoutingMamba(nn.Module):
         w, idx, logits = self._route(hidden_states)
         mix = torch.zeros(*hidden_states.shape[:2], self.n_experts, dtype=w.dtype, device=w.device)
         mix = mix.scatter_add(-1, idx, w)                       # (B, S, E), differentiable in w
-        used = (self._counts > 0).tolist()                      # one host read for all experts
-        sel = [e for e in range(self.n_experts) if used[e]]
-        mixers = [self.experts[e].mamba.mamba for e in sel]
-        if self.batched and sel and all(isinstance(m, Mamba) for m in mixers):
-            ys = mamba_forward_batched(mixers, hidden_states)                       # (U, B, S, d)
-            wsel = mix[..., sel].permute(2, 0, 1).unsqueeze(-1).to(hidden_states.dtype)
-            out = (wsel * ys).sum(0)
+        mixers = [ex.mamba.mamba for ex in self.experts]
+        if self.batched and all(isinstance(m, Mamba) for m in mixers):
+            # every expert runs (an expert nobody selected is mixed in with weight 0, the value the
+            # reference's skip gives), so no usage mask has to reach the host
+            ys = mamba_forward_batched(mixers, hidden_states)                       # (E, B, S, d)
+            out = (mix.permute(2, 0, 1).unsqueeze(-1).to(hidden_states.dtype) * ys).sum(0)
         else:
+            used = (self._counts > 0).tolist()                  # one host read for all experts
+            sel = [e for e in range(self.n_experts) if used[e]]
             out = torch.zeros_like(hidden_states)
             for e in sel:
                 out = out + mix[..., e:e + 1].to(hidden_states.dtype) * self.experts[e](hidden_states)
