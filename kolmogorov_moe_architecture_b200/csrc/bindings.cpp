@@ -104,6 +104,37 @@ std::tuple<Tensor, Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const T
   return {dx, dw};
 }
 
+Tensor rowdot_fwd(const Tensor& x, const Tensor& w) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_bf16(x, "x"); need_bf16(w, "w");
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous());
+  const int d = x.size(-1);
+  const int rows = x.numel() / d;
+  TORCH_CHECK(w.numel() == d, "w must hold one row of d weights");
+  Tensor y = at::empty({rows}, x.options());
+  check(kmoe_rowdot_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rows, d, cur_stream()), "rowdot_fwd");
+  return y;
+}
+
+// dw goes to `dw_out` (bf16, d elements) when given, else a new tensor is returned
+std::tuple<Tensor, Tensor> rowdot_bwd(const Tensor& x, const Tensor& w, const Tensor& dy, bool need_dx,
+                                      const c10::optional<Tensor>& dw_out) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_bf16(x, "x"); need_bf16(w, "w"); need_bf16(dy, "dy");
+  TORCH_CHECK(x.is_contiguous() && dy.is_contiguous() && w.is_contiguous());
+  const int d = x.size(-1);
+  const int rows = x.numel() / d;
+  TORCH_CHECK(dy.numel() == rows);
+  Tensor dx = need_dx ? at::empty_like(x) : Tensor();
+  Tensor dw = (dw_out.has_value() && dw_out->defined()) ? *dw_out : at::empty({d}, x.options());
+  need_bf16(dw, "dw");
+  TORCH_CHECK(dw.is_contiguous() && dw.numel() == d);
+  Tensor partial = at::empty({kmoe_rmsnorm_bwd_num_partials(rows), d}, x.options().dtype(at::kFloat));
+  check(kmoe_rowdot_bwd(x.data_ptr(), w.data_ptr(), dy.data_ptr(), need_dx ? dx.data_ptr() : nullptr, dw.data_ptr(),
+                        nullptr, partial.data_ptr<float>(), rows, d, cur_stream()), "rowdot_bwd");
+  return {need_dx ? dx : at::empty({0}, x.options()), dw};
+}
+
 Tensor rope(const Tensor& x, const Tensor& cs, const Tensor& sn, bool transpose) {
   c10::cuda::CUDAGuard guard(x.device());
   need_bf16(x, "x"); need_f32(cs, "cos"); need_f32(sn, "sin");
@@ -602,6 +633,8 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("rope", &rope);
+  m.def("rowdot_fwd", &rowdot_fwd);
+  m.def("rowdot_bwd", &rowdot_bwd);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("conv1d_fwd", &conv1d_fwd);

@@ -130,6 +130,72 @@ __global__ void colsum_partials_kernel(const float* __restrict__ partial, __nv_b
   if (out_f32 != nullptr) out_f32[c] = s;
 }
 
+// ------------------------------------------------- Linear with one output column
+// y[row] = sum_c x[row, c] * w[c]   (the mixture-of-depths scorer and the last layer of its
+// auxiliary predictor: nn.Linear(d, 1)).  One warp per row.
+__global__ void rowdot_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                  __nv_bfloat16* __restrict__ y, int rows, int d) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
+    const __nv_bfloat16* xr = x + (size_t)row * d;
+    float s = 0.f;
+    for (int c = lane * 8; c < d; c += 256) {
+      float v[8], g[8];
+      unpack8(*reinterpret_cast<const uint4*>(xr + c), v);
+      unpack8(*reinterpret_cast<const uint4*>(w + c), g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += v[i] * g[i];
+    }
+    s = warp_sum(s);
+    if (lane == 0) y[row] = __float2bfloat16(s);
+  }
+}
+
+// dx[row, c] = dy[row] * w[c]
+__global__ void rowdot_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ w,
+                                 __nv_bfloat16* __restrict__ dx, int rows, int d) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
+    const float g = __bfloat162float(dy[row]);
+    __nv_bfloat16* dxr = dx + (size_t)row * d;
+    for (int c = lane * 8; c < d; c += 256) {
+      float v[8];
+      unpack8(*reinterpret_cast<const uint4*>(w + c), v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] *= g;
+      *reinterpret_cast<uint4*>(dxr + c) = pack8(v);
+    }
+  }
+}
+
+// partial[blockIdx.y][c] = sum over a slice of the rows of dy[row] * x[row, c]
+__global__ void rowdot_dw_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                                 float* __restrict__ partial, int rows, int d) {
+  __shared__ float red[8][256];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 256 + tx * 8;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (c < d) {
+    for (int row = blockIdx.y * 8 + ty; row < rows; row += gridDim.y * 8) {
+      float xv[8];
+      unpack8(*reinterpret_cast<const uint4*>(x + (size_t)row * d + c), xv);
+      const float g = __bfloat162float(dy[row]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += g * xv[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[ty][tx * 8 + i] = acc[i];
+  __syncthreads();
+  const int col = threadIdx.x;
+  float s_ = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s_ += red[j][col];
+  if (blockIdx.x * 256 + col < d) partial[(size_t)blockIdx.y * d + blockIdx.x * 256 + col] = s_;
+}
+
 // ---------------------------------------------------------------------- RoPE
 // x: [B, S, H, D] bf16 ; cos/sin: fp32 [*, S, D] with batch stride cs_bstride (0 = shared).
 // out = x * cos + rotate_half(x) * sin ; `sign` = -1 gives the transpose (the backward).
@@ -254,6 +320,32 @@ extern "C" int kmoe_rmsnorm_bwd(const void* x, const void* w, const void* dy, co
   const int parts = kmoe_rmsnorm_bwd_num_partials(rows);
   rmsnorm_dw_kernel<<<dim3((d + 255) / 256, parts), 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
                                                                   rstd, partial, rows, d);
+  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, (__nv_bfloat16*)dw_bf16, dw_f32, parts, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_rowdot_fwd(const void* x, const void* w, void* y, int rows, int d, cudaStream_t st) {
+  if (d % 8) return -1;
+  const int block = 256, wpb = block / 32;
+  int grid = (rows + wpb - 1) / wpb;
+  if (grid > 148 * 8) grid = 148 * 8;
+  rowdot_fwd_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rows, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// `partial` is scratch of kmoe_rmsnorm_bwd_num_partials(rows) * d floats; dw may be bf16 and/or fp32.
+extern "C" int kmoe_rowdot_bwd(const void* x, const void* w, const void* dy, void* dx, void* dw_bf16, float* dw_f32,
+                               float* partial, int rows, int d, cudaStream_t st) {
+  if (d % 8) return -1;
+  const int block = 256, wpb = block / 32;
+  int grid = (rows + wpb - 1) / wpb;
+  if (grid > 148 * 8) grid = 148 * 8;
+  if (dx != nullptr)
+    rowdot_dx_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)w, (__nv_bfloat16*)dx,
+                                             rows, d);
+  const int parts = kmoe_rmsnorm_bwd_num_partials(rows);
+  rowdot_dw_kernel<<<dim3((d + 255) / 256, parts), 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
+                                                                 partial, rows, d);
   colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, (__nv_bfloat16*)dw_bf16, dw_f32, parts, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -106,6 +106,10 @@ void kmoe_mxfp8_clear_tensormap_cache(void);
 // ------------------------------------------------------------ row kernels (bf16 data, fp32 math)
 int kmoe_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int d, float eps, cudaStream_t st);
 int kmoe_rmsnorm_bwd_num_partials(int rows);
+/* nn.Linear(d, 1): y[row] = x[row, :] . w ; backward gives dx (optional) and dw (bf16 and/or fp32). */
+int kmoe_rowdot_fwd(const void* x, const void* w, void* y, int rows, int d, cudaStream_t st);
+int kmoe_rowdot_bwd(const void* x, const void* w, const void* dy, void* dx, void* dw_bf16, float* dw_f32,
+                    float* partial, int rows, int d, cudaStream_t st);
 int kmoe_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx, void* dw_bf16,
                      float* dw_f32, float* partial, int rows, int d, cudaStream_t st);
 int kmoe_rope(const void* x, const float* cs, const float* sn, void* out, int B, int S, int H, int D,

@@ -12,6 +12,7 @@ import torch
 import torch.nn as nn
 
 from .. import ops
+from .linear import Linear
 from .embeddings import RotaryPositionalEmbedding
 
 
@@ -22,10 +23,10 @@ class GroupedQueryAttention(nn.Module):
         self.n_heads, self.n_kv_heads, self.head_dim = config.n_heads, config.n_kv_heads, config.head_dim
         self.n_groups = self.n_heads // self.n_kv_heads
         assert self.d_model == self.n_heads * self.head_dim, "d_model must equal n_heads * head_dim"
-        self.q_proj = nn.Linear(self.d_model, self.n_heads * self.head_dim, bias=False)
-        self.k_proj = nn.Linear(self.d_model, self.n_kv_heads * self.head_dim, bias=False)
-        self.v_proj = nn.Linear(self.d_model, self.n_kv_heads * self.head_dim, bias=False)
-        self.o_proj = nn.Linear(self.n_heads * self.head_dim, self.d_model, bias=False)
+        self.q_proj = Linear(self.d_model, self.n_heads * self.head_dim, bias=False)
+        self.k_proj = Linear(self.d_model, self.n_kv_heads * self.head_dim, bias=False)
+        self.v_proj = Linear(self.d_model, self.n_kv_heads * self.head_dim, bias=False)
+        self.o_proj = Linear(self.n_heads * self.head_dim, self.d_model, bias=False)
         self.rope = RotaryPositionalEmbedding(self.head_dim, config.max_seq_len, config.rope_theta,
                                               config.rope_scaling)
         self.attention_dropout = config.attention_dropout

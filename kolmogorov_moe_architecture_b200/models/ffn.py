@@ -6,6 +6,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
+from .linear import Linear
 
 
 class SwiGLU(nn.Module):
@@ -13,20 +14,20 @@ class SwiGLU(nn.Module):
 
     def __init__(self, d_model: int, d_ff: int, dropout: float = 0.0):
         super().__init__()
-        self.w1 = nn.Linear(d_model, d_ff, bias=False)
-        self.w2 = nn.Linear(d_model, d_ff, bias=False)
-        self.w3 = nn.Linear(d_ff, d_model, bias=False)
+        self.w1 = Linear(d_model, d_ff, bias=False)
+        self.w2 = Linear(d_model, d_ff, bias=False)
+        self.w3 = Linear(d_ff, d_model, bias=False)
         self.dropout = nn.Dropout(dropout)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.dropout(self.w3(ops.swiglu(self.w1(x), self.w2(x))))
+        return self.dropout(ops.dense_swiglu(x, self.w1.weight, self.w2.weight, self.w3.weight))
 
 
 class StandardFFN(nn.Module):
     def __init__(self, d_model: int, d_ff: int, activation: str = "gelu", dropout: float = 0.0):
         super().__init__()
-        self.w1 = nn.Linear(d_model, d_ff, bias=False)
-        self.w2 = nn.Linear(d_ff, d_model, bias=False)
+        self.w1 = Linear(d_model, d_ff, bias=False)
+        self.w2 = Linear(d_ff, d_model, bias=False)
         self.act = {"gelu": F.gelu, "silu": F.silu, "relu": F.relu}[activation]
         self.dropout = nn.Dropout(dropout)
 

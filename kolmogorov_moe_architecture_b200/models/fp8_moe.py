@@ -16,6 +16,7 @@ import torch.nn as nn
 
 from ..ops import eager
 from ..ops.mxfp8 import grouped_swiglu_mxfp8, linear_mx
+from .linear import Linear
 
 FP8_E4M3 = torch.float8_e4m3fn
 FP8_E5M2 = torch.float8_e5m2
@@ -69,7 +70,7 @@ class FP8MoELayer(nn.Module):
     def __init__(self, d_model: int, d_ff: int, n_experts: int, top_k: int = 2):
         super().__init__()
         self.d_model, self.d_ff, self.n_experts, self.top_k = d_model, d_ff, n_experts, top_k
-        self.router = nn.Linear(d_model, n_experts, bias=False)
+        self.router = Linear(d_model, n_experts, bias=False)
         self.experts = FP8GroupedExperts(n_experts, d_model, d_ff)
         self.aux_loss = 0.0
 

@@ -18,6 +18,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
+from .linear import Linear
 
 
 class Mamba(nn.Module):
@@ -31,11 +32,11 @@ class Mamba(nn.Module):
         self.d_model, self.d_state, self.d_conv, self.expand = d_model, d_state, d_conv, expand
         self.d_inner = expand * d_model
         self.dt_rank = math.ceil(d_model / 16)
-        self.in_proj = nn.Linear(d_model, 2 * self.d_inner, bias=False)
+        self.in_proj = Linear(d_model, 2 * self.d_inner, bias=False)
         self.conv1d = nn.Conv1d(self.d_inner, self.d_inner, kernel_size=d_conv, groups=self.d_inner,
                                 padding=d_conv - 1, bias=True)
-        self.x_proj = nn.Linear(self.d_inner, self.dt_rank + 2 * d_state, bias=False)
-        self.dt_proj = nn.Linear(self.dt_rank, self.d_inner, bias=True)
+        self.x_proj = Linear(self.d_inner, self.dt_rank + 2 * d_state, bias=False)
+        self.dt_proj = Linear(self.dt_rank, self.d_inner, bias=True)
         std = self.dt_rank ** -0.5
         nn.init.uniform_(self.dt_proj.weight, -std, std)
         dt = torch.exp(torch.rand(self.d_inner) * (math.log(dt_max) - math.log(dt_min))
@@ -45,7 +46,7 @@ class Mamba(nn.Module):
         A = torch.arange(1, d_state + 1, dtype=torch.float32).repeat(self.d_inner, 1)
         self.A_log = nn.Parameter(torch.log(A))
         self.D = nn.Parameter(torch.ones(self.d_inner))
-        self.out_proj = nn.Linear(self.d_inner, d_model, bias=False)
+        self.out_proj = Linear(self.d_inner, d_model, bias=False)
 
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
         xz = self.in_proj(hidden_states)
@@ -53,7 +54,7 @@ class Mamba(nn.Module):
         x = ops.causal_conv1d(x, self.conv1d.weight.squeeze(1), self.conv1d.bias, activation=True)
         x_dbl = self.x_proj(x)
         dt, Bm, Cm = torch.split(x_dbl, [self.dt_rank, self.d_state, self.d_state], dim=-1)
-        delta = F.linear(dt, self.dt_proj.weight)          # bias is added inside the scan
+        delta = ops.linear(dt, self.dt_proj.weight)          # bias is added inside the scan
         A = -torch.exp(self.A_log.float())
         y = ops.selective_scan(x, delta, A, Bm, Cm, self.D.float(), z,
                                self.dt_proj.bias.float(), delta_softplus=True)
@@ -66,9 +67,9 @@ class SimpleSSM(nn.Module):
 
     def __init__(self, d_model: int, d_inner: int):
         super().__init__()
-        self.in_proj = nn.Linear(d_model, d_inner * 2, bias=False)
+        self.in_proj = Linear(d_model, d_inner * 2, bias=False)
         self.conv1d = nn.Conv1d(d_inner, d_inner, kernel_size=4, padding=3, groups=d_inner)
-        self.out_proj = nn.Linear(d_inner, d_model, bias=False)
+        self.out_proj = Linear(d_inner, d_model, bias=False)
         self.act = nn.SiLU()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -148,8 +149,8 @@ class RoutingMamba(nn.Module):
         self.config, self.layer_idx = config, layer_idx
         self.n_experts, self.top_k, self.d_model = config.n_experts, config.moe_top_k, config.d_model
         self.experts = nn.ModuleList([MambaExpert(config) for _ in range(config.n_experts)])
-        self.router = nn.Sequential(nn.Linear(config.d_model, 128, bias=False), nn.SiLU(),
-                                    nn.Linear(128, config.n_experts, bias=False))
+        self.router = nn.Sequential(Linear(config.d_model, 128, bias=False), nn.SiLU(),
+                                    Linear(128, config.n_experts, bias=False))
         self.load_balance_loss_weight = config.moe_load_balance_loss_weight
         self.router_z_loss_weight = config.moe_router_z_loss_weight
         self.aux_loss = 0.0

@@ -8,6 +8,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
+from .linear import Linear
 
 
 class MoDRouter(nn.Module):
@@ -22,10 +23,10 @@ class MoDRouter(nn.Module):
         super().__init__()
         self.d_model = config.d_model
         self.capacity_factor = config.mod_capacity_factor
-        self.router = nn.Linear(config.d_model, 1, bias=False)
+        self.router = Linear(config.d_model, 1, bias=False)
         h = config.mod_router_hidden_dim
         self.aux_router = nn.Sequential(
-            nn.Linear(config.d_model, h, bias=False), nn.SiLU(), nn.Linear(h, 1, bias=False))
+            Linear(config.d_model, h, bias=False), nn.SiLU(), Linear(h, 1, bias=False))
         self.aux_loss_weight = config.mod_load_balance_loss_weight
         self.aux_loss = 0.0
 

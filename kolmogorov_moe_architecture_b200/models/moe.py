@@ -17,6 +17,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
+from .linear import Linear
 
 
 def _init_stacked(w: torch.Tensor) -> None:
@@ -37,8 +38,8 @@ class Router(nn.Module):
         self.aux_weights = (getattr(config, "moe_load_balance_loss_weight", 0.0),
                             getattr(config, "moe_router_z_loss_weight", 0.0))
         self.last_aux, self.last_counts = None, None
-        self.router = nn.Sequential(nn.Linear(config.d_model, 128, bias=False), nn.SiLU(),
-                                    nn.Linear(128, config.n_experts, bias=False))
+        self.router = nn.Sequential(Linear(config.d_model, 128, bias=False), nn.SiLU(),
+                                    Linear(128, config.n_experts, bias=False))
 
     @staticmethod
     def _balanced_topk_assignment(probs: torch.Tensor, top_k: int) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -86,8 +87,8 @@ class ExpertChoiceRouter(nn.Module):
         super().__init__()
         self.d_model, self.n_experts = config.d_model, config.n_experts
         self.capacity_factor = config.moe_capacity_factor
-        self.router = nn.Sequential(nn.Linear(config.d_model, 128, bias=False), nn.SiLU(),
-                                    nn.Linear(128, config.n_experts, bias=False))
+        self.router = nn.Sequential(Linear(config.d_model, 128, bias=False), nn.SiLU(),
+                                    Linear(128, config.n_experts, bias=False))
 
     def forward(self, hidden_states: torch.Tensor):
         S = hidden_states.shape[1]

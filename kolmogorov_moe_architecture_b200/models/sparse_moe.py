@@ -18,6 +18,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
+from .linear import Linear
 
 
 class SparseGroupedExpertsPyTorch(nn.Module):
@@ -77,7 +78,7 @@ class ExpertParallelMoE(nn.Module):
         self.n_local_experts = self.n_experts // self.world_size
         self.expert_start_idx = self.rank * self.n_local_experts
         self.expert_end_idx = self.expert_start_idx + self.n_local_experts
-        self.router = nn.Linear(config.d_model, config.n_experts, bias=False)
+        self.router = Linear(config.d_model, config.n_experts, bias=False)
         self.local_experts = SparseGroupedExpertsPyTorch(
             self.n_local_experts, config.d_model, config.d_ff_expert,
             moe_dtype=getattr(config, "moe_dtype", "bf16"))

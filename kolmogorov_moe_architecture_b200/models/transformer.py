@@ -18,6 +18,7 @@ from ..config import AdvancedMoEConfig
 from ..training.losses import MultiTokenPredictionLoss
 from .embeddings import TokenEmbedding, get_norm_layer
 from .layers import TransformerBlock
+from .linear import Linear
 
 
 def _numel(module_or_params) -> int:
@@ -33,7 +34,7 @@ class MoETransformer(nn.Module):
         self.token_embedding = TokenEmbedding(config)
         self.layers = nn.ModuleList([TransformerBlock(config, i) for i in range(config.n_layers)])
         self.final_norm = get_norm_layer(config)
-        self.lm_heads = nn.ModuleList([nn.Linear(config.d_model, config.vocab_size, bias=False)
+        self.lm_heads = nn.ModuleList([Linear(config.d_model, config.vocab_size, bias=False)
                                        for _ in range(config.n_pred_tokens)])
         self.tie_word_embeddings = getattr(config, "tie_word_embeddings", True)
         if self.tie_word_embeddings:

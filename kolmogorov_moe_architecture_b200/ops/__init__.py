@@ -24,6 +24,24 @@ def _use_cuda(t) -> bool:
     return True
 
 
+def linear(x, weight, bias=None):
+    """``F.linear``; bf16 CUDA tensors go through this library's tcgen05 GEMM (forward, dx and dW)."""
+    if _use_cuda(x):
+        from . import cuda_ops
+        return cuda_ops.linear(x, weight, bias)
+    import torch.nn.functional as F
+    return F.linear(x, weight, bias)
+
+
+def dense_swiglu(x, w1, w2, w3):
+    """``w3(silu(w1 x) * (w2 x))`` with ``nn.Linear``-layout weights (reference: moe_arch/model/ffn.py:44-64)."""
+    if _use_cuda(x):
+        from . import cuda_ops
+        return cuda_ops.dense_swiglu(x, w1, w2, w3)
+    import torch.nn.functional as F
+    return F.linear(eager.swiglu(F.linear(x, w1), F.linear(x, w2)), w3)
+
+
 def rmsnorm(x, weight, eps):
     if _use_cuda(x):
         from . import cuda_ops

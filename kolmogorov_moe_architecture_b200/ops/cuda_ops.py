@@ -132,6 +132,141 @@ def _bf16(t: torch.Tensor) -> bool:
     return t.dtype == torch.bfloat16
 
 
+# -------------------------------------------------------------------- Linear
+def _linear_ok(x2: torch.Tensor, w: torch.Tensor) -> bool:
+    """Shapes the GEMM covers for all three products of a linear layer: the input width is a whole number
+    of 64-element swizzle atoms (the weight is read MN-major for dx, the activations for dW), the output
+    width and the row count are multiples of 8 (16-byte rows for TMA)."""
+    out_f, in_f = w.shape
+    return (_bf16(x2) and _bf16(w) and w.is_contiguous() and in_f % 64 == 0 and out_f % 8 == 0
+            and x2.shape[0] % 8 == 0 and x2.shape[0] > 0)
+
+
+def _wgrad(dy: torch.Tensor, x2: torch.Tensor, w: torch.Tensor):
+    """dW = dy^T x2 into the weight's slot of the flat gradient buffer when one is registered (returns None
+    then), else into a new tensor."""
+    out_f, in_f = w.shape
+    T = x2.shape[0]
+    sink = grad_sink(w)
+    dst = sink[0] if sink is not None else torch.empty_like(w)
+    if out_f % 64 == 0:
+        mm_tn(dy, x2, out=dst)
+    else:
+        # dy is too narrow to be read MN-major (rows of whole 64-element atoms): use its transpose, K-major
+        dyT = dy.t().contiguous()
+        gemm(dyT, x2, dst, M=out_f, N=in_f, Kd=T, a_major=MAJ_K, b_major=MAJ_MN, lda=T, ldb=x2.stride(0),
+             ldc=dst.stride(0))
+    if sink is not None:
+        sink[1]()
+        return None
+    return dst
+
+
+class _Linear(torch.autograd.Function):
+    """y = x W^T on the tcgen05 GEMM; dx = dy W and dW = dy^T x read the same tensors in the other major, so
+    nothing is transposed in memory."""
+
+    @staticmethod
+    def forward(ctx, x2, w):
+        ctx.save_for_backward(x2, w)
+        return mm_nt(x2, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        if not _rows_ok(dy):
+            dy = dy.contiguous()
+        dx = mm_nn(dy, w) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(dy, x2, w) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+class _RowDot(torch.autograd.Function):
+    """nn.Linear(d, 1) (a dot product per row)."""
+
+    @staticmethod
+    def forward(ctx, x2, w):
+        ctx.save_for_backward(x2, w)
+        _count()
+        return K.rowdot_fwd(x2, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        sink = grad_sink(w)
+        dst = sink[0].view(-1) if sink is not None else None
+        dx, dw = K.rowdot_bwd(x2, w, dy.contiguous(), ctx.needs_input_grad[0], dst)
+        _count(3)
+        if sink is not None:
+            sink[1]()
+        return (dx if ctx.needs_input_grad[0] else None), (None if sink is not None else dw.view_as(w))
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``F.linear`` on this library's GEMM.  Layers whose input is narrower than one 64-element swizzle atom
+    (or not a multiple of it) are left to the library GEMM; none of the 5B model's layers is."""
+    in_f = weight.shape[1]
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, in_f)
+    if not _rows_ok(x2):
+        x2 = x2.contiguous()
+    if weight.shape[0] == 1 and _bf16(x2) and _bf16(weight) and in_f % 8 == 0 and x2.is_contiguous() and x2.shape[0] > 0:
+        y = _RowDot.apply(x2, weight.contiguous()).view(*lead, 1)
+    elif _linear_ok(x2, weight):
+        y = _Linear.apply(x2, weight).view(*lead, weight.shape[0])
+    else:
+        return torch.nn.functional.linear(x, weight, bias)
+    return y if bias is None else y + bias
+
+
+class _DenseSwiGLU(torch.autograd.Function):
+    """w3(silu(w1 x) * (w2 x)) with gate and up in one GEMM whose epilogue applies SwiGLU (one tile holds 128
+    gate and 128 up columns), the same kernels the experts use with a single group."""
+
+    @staticmethod
+    def forward(ctx, x2, w1, w2, w3):
+        T, d = x2.shape
+        f = w1.shape[0]
+        H = torch.empty(T, f, dtype=x2.dtype, device=x2.device)
+        G, U = torch.empty_like(H), torch.empty_like(H)
+        gemm(x2, w1, H, B2=w2, G=G, U=U, epi=EPI_SWIGLU, M=T, N=f, Kd=d, lda=x2.stride(0), ldb=d, ldc=f)
+        y = mm_nt(H, w3)
+        ctx.save_for_backward(x2, G, U, w1, w2, w3)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, G, U, w1, w2, w3 = ctx.saved_tensors
+        if not _rows_ok(dy):
+            dy = dy.contiguous()
+        dH = mm_nn(dy, w3)
+        dG, dU = K.swiglu_bwd(G, U, dH, None)
+        _count()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = mm_nn(dG, w1)
+            mm_nn(dU, w2, out=dx, D=dx, beta=1.0)
+        H = K.swiglu_fwd(G, U, None)
+        _count()
+        dw1 = _wgrad(dG, x2, w1)
+        dw2 = _wgrad(dU, x2, w2)
+        dw3 = _wgrad(dy, H, w3)
+        return dx, dw1, dw2, dw3
+
+
+def dense_swiglu(x, w1, w2, w3):
+    d, f = w1.shape[1], w1.shape[0]
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, d)
+    if not _rows_ok(x2):
+        x2 = x2.contiguous()
+    ok = (_linear_ok(x2, w1) and _linear_ok(x2, w2) and _bf16(w3) and w3.is_contiguous()
+          and f % 64 == 0 and d % 64 == 0)
+    if not ok:
+        return linear(swiglu(linear(x, w1), linear(x, w2)), w3)
+    return _DenseSwiGLU.apply(x2, w1, w2, w3).view(*lead, d)
+
+
 # ------------------------------------------------------------------- RMSNorm
 class _RMSNorm(torch.autograd.Function):
     @staticmethod

@@ -19,7 +19,12 @@ def _bf(*shape, scale=1.0, grad=False):
 
 
 def _rel(a, b):
-    return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6)).item()
+    """Worst element of |a - b| / (|b| + rms(b)): a relative error where the reference is large and an
+    absolute one, in units of the reference's typical magnitude, where it is small.  (Dividing by the
+    largest reference value instead would let an op that is wrong on its small outputs pass.)"""
+    a, b = a.float(), b.float()
+    rms = b.pow(2).mean().sqrt() + 1e-12
+    return ((a - b).abs() / (b.abs() + rms)).max().item()
 
 
 def _f32_leaf(t):
@@ -391,3 +396,71 @@ def test_attention_and_routing_are_bitwise_deterministic():
     logits = torch.randn(4, 512, device="cuda")
     a1, a2 = ops.mod_route(logits, 300), ops.mod_route(logits, 300)
     assert torch.equal(a1[0], a2[0]) and torch.equal(a1[1], a2[1])
+
+
+@pytest.mark.parametrize("T,din,dout", [(256, 128, 192), (200, 256, 40), (64, 64, 16), (1024, 512, 1024)])
+def test_linear_fwd_bwd(T, din, dout):
+    """ops.linear (tcgen05 GEMM for y, dx and dW) against F.linear in fp32; dout = 40 / 16 takes the
+    transposed-dy weight-gradient path, T = 200 a ragged last row tile."""
+    ops, c, eager = _mods()
+    x = _bf(2, T // 2, din, grad=True)
+    w = _bf(dout, din, scale=din ** -0.5, grad=True)
+    n0 = c.LAUNCHES["count"]
+    y = ops.linear(x, w)
+    g = _bf(2, T // 2, dout)
+    y.backward(g)
+    assert c.LAUNCHES["count"] - n0 == 3, "forward, dx and dW must each be one launch of the library's GEMM"
+    xr, wr = _f32_leaf(x), _f32_leaf(w)
+    yr = F.linear(xr, wr)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 1e-2 and _rel(x.grad, xr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
+
+
+def test_linear_strided_input_and_bias():
+    ops, c, eager = _mods()
+    xz = _bf(4, 32, 2 * 128, grad=True)
+    x = xz[..., 128:]                                   # row stride 256, width 128
+    w, b = _bf(64, 128, scale=0.1, grad=True), _bf(64, grad=True)
+    y = ops.linear(x, w, b)
+    g = _bf(4, 32, 64)
+    y.backward(g)
+    r, wr, br = _f32_leaf(xz), _f32_leaf(w), _f32_leaf(b)
+    yr = F.linear(r[..., 128:], wr, br)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 1e-2 and _rel(xz.grad, r.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
+    assert _rel(b.grad, br.grad) < 1e-2
+
+
+def test_linear_single_output_column():
+    """nn.Linear(d, 1): the mixture-of-depths scorer."""
+    ops, c, eager = _mods()
+    x, w = _bf(3, 50, 256, grad=True), _bf(1, 256, scale=0.06, grad=True)
+    y = ops.linear(x, w)
+    assert y.shape == (3, 50, 1)
+    g = _bf(3, 50, 1)
+    y.backward(g)
+    xr, wr = _f32_leaf(x), _f32_leaf(w)
+    yr = F.linear(xr, wr)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 1e-2 and _rel(x.grad, xr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
+    # input that needs no gradient (the auxiliary predictor sees detached activations)
+    w2 = w.detach().clone().requires_grad_(True)
+    ops.linear(x.detach(), w2).backward(g)
+    assert _rel(w2.grad, wr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("T,d,f", [(256, 128, 256), (520, 256, 704)])
+def test_dense_swiglu_fwd_bwd(T, d, f):
+    ops, c, eager = _mods()
+    x = _bf(T, d, grad=True)
+    w1, w2 = _bf(f, d, scale=d ** -0.5, grad=True), _bf(f, d, scale=d ** -0.5, grad=True)
+    w3 = _bf(d, f, scale=f ** -0.5, grad=True)
+    y = ops.dense_swiglu(x, w1, w2, w3)
+    g = _bf(T, d)
+    y.backward(g)
+    xr, r1, r2, r3 = (_f32_leaf(t) for t in (x, w1, w2, w3))
+    yr = F.linear(F.silu(F.linear(xr, r1)) * F.linear(xr, r2), r3)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 2e-2 and _rel(x.grad, xr.grad) < 2e-2
+    for a, b in ((w1, r1), (w2, r2), (w3, r3)):
+        assert _rel(a.grad, b.grad) < 2e-2
