@@ -352,7 +352,7 @@ def test_mod_gather_combine_fwd_bwd(B, S, k, d):
     outr = eager.mod_combine(rr, pr @ lin.float(), wr, idx)
     outr.backward(g.float())
     assert torch.equal(picked.float(), pr.detach())
-    assert _rel(out, outr) < 1e-2
+    assert _rel(out, outr) < 1.5e-2     # `proc` is rounded to bf16 before the combine on this side only
     assert _rel(h.grad, hr.grad) < 2e-2 and _rel(res.grad, rr.grad) < 1e-6 and _rel(w.grad, wr.grad) < 2e-2
 
 
