@@ -56,13 +56,12 @@ struct GemmArgs {
 
 struct Tile {
   int m_tile, n_tile, g_a, g_b, g_c, k0, k_blocks;
-  bool skip;   // symmetric output: the tile lies entirely below the diagonal and is filled by mirroring
 };
 
 __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
-// Maps a linear work index to a tile. Returns false past the end.
-template <int BN>
+// Maps a linear work index to a tile of TM x BN outputs. Returns false past the end.
+template <int BN, int TM = BM>
 __device__ __forceinline__ bool get_tile(const GemmArgs& a, int idx, int num_m, int num_n, Tile& t) {
   const int n_out = (a.epilogue == KMOE_EPI_SWIGLU) ? BN / 2 : BN;
   (void)n_out;
@@ -71,19 +70,19 @@ __device__ __forceinline__ bool get_tile(const GemmArgs& a, int idx, int num_m, 
   if (a.sym_upper) {
     // enumerate only the tiles that touch the upper triangle, row by row, so that the work is spread evenly
     int kept = 0;
-    for (int m = 0; m < num_m; ++m) kept += num_n - min(num_n, (m * BM) / BN);
+    for (int m = 0; m < num_m; ++m) kept += num_n - min(num_n, (m * TM) / BN);
     g = idx / kept;
     local = idx - g * kept;
     if (g >= (a.mode == KMOE_GEMM_BATCHED ? a.groups : 1)) return false;
     int m = 0;
     while (true) {
-      const int km = num_n - min(num_n, (m * BM) / BN);
+      const int km = num_n - min(num_n, (m * TM) / BN);
       if (local < km) break;
       local -= km;
       ++m;
     }
     t.m_tile = m;
-    t.n_tile = min(num_n, (m * BM) / BN) + local;
+    t.n_tile = min(num_n, (m * TM) / BN) + local;
   } else {
     if (a.mode == KMOE_GEMM_BATCHED) {
       g = idx / per_group;
@@ -103,7 +102,6 @@ __device__ __forceinline__ bool get_tile(const GemmArgs& a, int idx, int num_m, 
   }
   t.k0 = 0;
   t.k_blocks = ceil_div(a.K, BK);
-  t.skip = false;
   if (a.mode == KMOE_GEMM_GROUPED_M) {
     int e = a.tile_group[t.m_tile];
     t.g_a = 0;
@@ -237,7 +235,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t ph = 0;
       Tile t;
       for (int idx = blockIdx.x; get_tile<BN>(args, idx, num_m, num_n, t); idx += gridDim.x) {
-        if (t.skip) continue;
         for (int kb = 0; kb < t.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
             atomicExch(args.status, 1);
@@ -278,7 +275,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int it = 0;
       Tile t;
       for (int idx = blockIdx.x; get_tile<BN>(args, idx, num_m, num_n, t); idx += gridDim.x) {
-        if (t.skip) continue;                  // `it` counts computed tiles only (it drives the barrier phases)
         const int acc = it & 1;
         const uint32_t acc_ph = (it >> 1) & 1;
         ++it;
@@ -320,7 +316,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int it = 0;
     Tile t;
     for (int idx = blockIdx.x; get_tile<BN>(args, idx, num_m, num_n, t); idx += gridDim.x) {
-      if (t.skip) continue;
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
       ++it;
@@ -452,12 +447,299 @@ teardown:
   }
 }
 
+// ------------------------------------------------------------------ CTA-pair kernel
+// The same GEMM with tcgen05.mma.cta_group::2: the two CTAs of a cluster share one 256 x BN tile.  Each CTA
+// loads its own 128 rows of A and its own half of B's columns (plain per-CTA TMA loads), the even CTA issues
+// 256 x BN x 16 MMAs that read both CTAs' shared memory, and each CTA ends up with its 128 rows of the
+// accumulator in its own tensor memory.  Halving the B traffic per CTA is what lifts the tensor pipe off the
+// shared-memory bandwidth limit of the single-CTA 128 x 256 tile.
+//
+// Barriers: `full` lives in the leader and is credited by both CTAs' loads; `empty` and `tmem_full` exist in
+// both CTAs and are signalled by the leader's commits (multicast arrive); `tmem_empty` lives in the leader
+// and collects the epilogue warps of both CTAs.  DENSE and BATCHED schedules, all epilogues except per-row
+// destination addresses.
+constexpr int PAIR_TM = 2 * BM;
+
+template <int BN, int A_MAJOR, int B_MAJOR>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmB2, const GemmArgs args, const int stages) {
+  constexpr int HALF_N = BN / 2;
+  constexpr int B_STAGE_BYTES = HALF_N * BK * 2;
+  constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;   // per CTA
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  constexpr uint32_t IDESC = make_idesc_f16(PAIR_TM, BN, /*bf16*/ 1, A_MAJOR, B_MAJOR);
+  constexpr int MAX_STAGES = 8;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[MAX_STAGES];
+  __shared__ uint64_t empty_bar[MAX_STAGES];
+  __shared__ uint64_t tmem_full[2];
+  __shared__ uint64_t tmem_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ __align__(16) __nv_bfloat16 out_stage[4][32][72];   // per epilogue warp: 32 rows x 64 columns (+pad)
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 8);   // four epilogue warps in each CTA of the pair
+    }
+    mbar_fence_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {                    // collective over the pair: the same warp of both CTAs
+    tmem_alloc_pair(&tmem_base_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                 // the peer's barriers exist before anything is signalled across
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  const bool swiglu = args.epilogue == KMOE_EPI_SWIGLU;
+  const int n_per_tile = swiglu ? BN / 2 : BN;
+  const int num_m = ceil_div(args.M, PAIR_TM);
+  const int num_n = ceil_div(args.N, n_per_tile);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    if (elect_one()) {
+      int s = 0;
+      uint32_t ph = 0;
+      Tile t;
+      for (int idx = pair; get_tile<BN, PAIR_TM>(args, idx, num_m, num_n, t); idx += num_pairs) {
+        const int arow = t.m_tile * PAIR_TM + (int)rank * BM;
+        for (int kb = 0; kb < t.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+            atomicExch(args.status, 11);
+            goto teardown;
+          }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
+          const uint32_t fb = map_to_cta(&full_bar[s], 0);
+          const int k = t.k0 + kb * BK;
+          if (A_MAJOR == KMOE_MAJOR_K)
+            tma_load_4d_pair(sa, &tmA, fb, k, arow, 0, t.g_a);
+          else
+            tma_load_4d_pair(sa, &tmA, fb, 0, k, arow / 64, t.g_a);
+          // B: this CTA's half of the tile's columns; with the SwiGLU epilogue the halves are the gate
+          // weight (leader) and the up weight (peer), so accumulator columns [0, BN/2) hold the gate
+          const CUtensorMap* tb = (swiglu && !leader) ? &tmB2 : &tmB;
+          const int brow = swiglu ? t.n_tile * HALF_N : t.n_tile * BN + (int)rank * HALF_N;
+          if (B_MAJOR == KMOE_MAJOR_K)
+            tma_load_4d_pair(sb, tb, fb, k, brow, 0, t.g_b);
+          else
+            tma_load_4d_pair(sb, tb, fb, 0, k, brow / 64, t.g_b);
+          if (++s == stages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer (leader only)
+    if (leader && elect_one()) {
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      Tile t;
+      for (int idx = pair; get_tile<BN, PAIR_TM>(args, idx, num_m, num_n, t); idx += num_pairs) {
+        const int acc = it & 1;
+        const uint32_t acc_ph = (it >> 1) & 1;
+        ++it;
+        if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1)) {
+          atomicExch(args.status, 12);
+          goto teardown;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < t.k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[s], ph)) {
+            atomicExch(args.status, 13);
+            goto teardown;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4) {
+            const uint32_t a_off = (A_MAJOR == KMOE_MAJOR_K) ? k4 * 32 : k4 * 16 * 128;
+            const uint32_t b_off = (B_MAJOR == KMOE_MAJOR_K) ? k4 * 32 : k4 * 16 * 128;
+            const uint64_t adesc = make_smem_desc_sw128(sa + a_off, (A_MAJOR == KMOE_MAJOR_K) ? 16 : BK * 128, 1024);
+            const uint64_t bdesc = make_smem_desc_sw128(sb + b_off, (B_MAJOR == KMOE_MAJOR_K) ? 16 : BK * 128, 1024);
+            umma_f16_pair(d_tmem, adesc, bdesc, IDESC, (kb > 0 || k4 > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[s], 3);      // frees the stage in both CTAs
+          if (++s == stages) { s = 0; ph ^= 1; }
+        }
+        if (t.k_blocks > 0) {
+          umma_commit_pair(&tmem_full[acc], 3);
+        } else {
+          mbar_arrive(&tmem_full[acc]);
+          mbar_arrive_cluster(map_to_cta(&tmem_full[acc], 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    const int q = warp & 3;
+    int it = 0;
+    Tile t;
+    __nv_bfloat16(*stg)[72] = out_stage[q];
+    for (int idx = pair; get_tile<BN, PAIR_TM>(args, idx, num_m, num_n, t); idx += num_pairs) {
+      const int acc = it & 1;
+      const uint32_t acc_ph = (it >> 1) & 1;
+      ++it;
+      if (!mbar_wait(&tmem_full[acc], acc_ph)) {
+        if (lane == 0) atomicExch(args.status, 14);
+        goto teardown;
+      }
+      tc_fence_after();
+      const bool have_acc = t.k_blocks > 0;
+      const int row0 = t.m_tile * PAIR_TM + (int)rank * BM + q * 32;
+      const int row = row0 + lane;
+      const bool row_ok = row < args.M;
+      const long long goff = (long long)t.g_c * args.c_gstride;
+      const long long coff = goff + (long long)row * args.ldc;
+      const long long doff = goff + (long long)row * args.ldd;
+      float scale = args.alpha;
+      float beta = args.beta;
+      if (args.alpha_dev != nullptr) scale *= args.alpha_dev[t.g_c];
+      if (args.beta_dev != nullptr) beta *= args.beta_dev[t.g_c];
+      if (args.row_scale != nullptr && row_ok) scale *= args.row_scale[row];
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      if (!swiglu && !args.out_f32) {
+        // bf16 output: a lane holds one row, so the 64-column slab is staged in shared memory and written
+        // back with 8 lanes per row (four full 128-byte lines per store instruction); the addend is read
+        // with the same coalesced pattern
+        __nv_bfloat16* Cb = reinterpret_cast<__nv_bfloat16*>(args.C);
+        const __nv_bfloat16* Dp = reinterpret_cast<const __nv_bfloat16*>(args.D);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 64) {
+          if (t.n_tile * BN + c >= args.N) break;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            if (have_acc) {
+              tmem_ld_32x32(t_row + c + h * 32, r);
+              tmem_ld_wait();
+            }
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = have_acc ? __uint_as_float(r[j + i]) * scale : 0.f;
+              store8<__nv_bfloat16>(&stg[lane][h * 32 + j], v);
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i8 = 0; i8 < 8; ++i8) {
+            const int rr = i8 * 4 + (lane >> 3);
+            const int cc = (lane & 7) * 8;
+            const int grow = row0 + rr;
+            const int gcol = t.n_tile * BN + c + cc;
+            if (grow < args.M && gcol < args.N) {
+              uint4 o = *reinterpret_cast<const uint4*>(&stg[rr][cc]);
+              if (Dp != nullptr) {
+                float d[8], v[8];
+                load8(Dp + goff + (long long)grow * args.ldd + gcol, d);
+                const __nv_bfloat162* pv = reinterpret_cast<const __nv_bfloat162*>(&o);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  float2 f = __bfloat1622float2(pv[i]);
+                  v[2 * i] = f.x + beta * d[2 * i];
+                  v[2 * i + 1] = f.y + beta * d[2 * i + 1];
+                }
+                o.x = pack_bf16(v[0], v[1]); o.y = pack_bf16(v[2], v[3]);
+                o.z = pack_bf16(v[4], v[5]); o.w = pack_bf16(v[6], v[7]);
+              }
+              *reinterpret_cast<uint4*>(Cb + goff + (long long)grow * args.ldc + gcol) = o;
+            }
+          }
+          __syncwarp();
+        }
+      } else if (!swiglu) {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          if (have_acc) {
+            tmem_ld_32x32(t_row + c, r);
+            tmem_ld_wait();
+          }
+          const int col = t.n_tile * BN + c;
+          if (row_ok && col < args.N) epilogue_store_chunk<float>(args, r, have_acc, coff, doff, col, scale, beta, 0);
+        }
+      } else {
+        __nv_bfloat16* H = reinterpret_cast<__nv_bfloat16*>(args.C);
+        __nv_bfloat16* G = reinterpret_cast<__nv_bfloat16*>(args.G_out);
+        __nv_bfloat16* U = reinterpret_cast<__nv_bfloat16*>(args.U_out);
+#pragma unroll 1
+        for (int c = 0; c < HALF_N; c += 32) {
+          uint32_t g[32], u[32];
+          if (have_acc) {
+            tmem_ld_32x32(t_row + c, g);
+            tmem_ld_32x32(t_row + HALF_N + c, u);
+            tmem_ld_wait();
+          }
+          const int col = t.n_tile * HALF_N + c;
+          if (row_ok && col < args.N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col + j >= args.N) break;
+              float gv[8], uv[8], hv[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                gv[i] = have_acc ? __uint_as_float(g[j + i]) : 0.f;
+                uv[i] = have_acc ? __uint_as_float(u[j + i]) : 0.f;
+                hv[i] = silu_f(gv[i]) * uv[i] * scale;
+              }
+              store8<__nv_bfloat16>(H + coff + col + j, hv);
+              if (G != nullptr) store8<__nv_bfloat16>(G + coff + col + j, gv);
+              if (U != nullptr) store8<__nv_bfloat16>(U + coff + col + j, uv);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (leader) mbar_arrive(&tmem_empty[acc]);
+        else mbar_arrive_cluster(map_to_cta(&tmem_empty[acc], 0));
+      }
+    }
+  }
+
+teardown:
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                 // nothing of the peer may still point at this CTA's memory
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
 // Fills the tiles that a symmetric GEMM skipped: C[g][i][j] = C[g][j][i] for every 32x32 block that lies in a
 // tile entirely below the diagonal.  grid = (n/32, n/32, groups), block = (32, 8).
-__global__ void sym_mirror_kernel(__nv_bfloat16* __restrict__ C, int n, long long ldc, long long gstride, int bn) {
+__global__ void sym_mirror_kernel(__nv_bfloat16* __restrict__ C, int n, long long ldc, long long gstride, int bn,
+                                  int tm) {
   const int bx = blockIdx.x, by = blockIdx.y;
-  const int mt = (by * 32) / BM, nt = (bx * 32) / bn;
-  if ((nt + 1) * bn > mt * BM) return;                      // destination was computed
+  const int mt = (by * 32) / tm, nt = (bx * 32) / bn;
+  if ((nt + 1) * bn > mt * tm) return;                      // destination was computed
   __shared__ __nv_bfloat16 tile[32][33];
   __nv_bfloat16* Cg = C + (long long)blockIdx.z * gstride;
   for (int r = threadIdx.y; r < 32; r += 8)                  // source block: rows 32*bx.., cols 32*by..
@@ -528,6 +810,45 @@ static int launch_variant(const CUtensorMap& tA, const CUtensorMap& tB, const CU
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
+template <int BN, int AM, int BMj>
+static int launch_pair_variant(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2,
+                               const GemmArgs& args, long long pair_tiles, int sms, cudaStream_t stream) {
+  constexpr int stage_bytes = A_STAGE_BYTES + (BN / 2) * BK * 2;
+  int stages = (196 * 1024) / stage_bytes;
+  if (stages > 8) stages = 8;
+  const int smem = stages * stage_bytes + 1024;
+  auto kern = umma_gemm_pair_kernel<BN, AM, BMj>;
+  static int max_clusters = 0;
+  if (max_clusters == 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -20;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * (sms / 2)));
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) n = sms / 2;
+    max_clusters = n;
+  }
+  long long pairs = pair_tiles < max_clusters ? pair_tiles : max_clusters;
+  if (pairs < 1) pairs = 1;
+  kern<<<(unsigned)(2 * pairs), NUM_THREADS, smem, stream>>>(tA, tB, tB2, args, stages);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+// KMOE_GEMM_PAIR=0 keeps every GEMM on the single-CTA kernel.
+static bool pair_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("KMOE_GEMM_PAIR");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 }  // namespace kmoe
 
 extern "C" void kmoe_gemm_clear_tensormap_cache(void) {
@@ -551,9 +872,15 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const bool use256 = swiglu || (m_tiles * n_tiles_256 * groups >= sms && d->N >= 256);
+  // CTA-pair kernel (256-row tiles): every schedule except the expert-padded one (its row blocks are 128 high
+  // and neighbouring blocks may belong to different experts) and per-row destination addresses
+  const bool pair = pair_enabled() && d->mode != KMOE_GEMM_GROUPED_M && d->c_row_ptr == nullptr && d->M > BM;
+  const int TM = pair ? PAIR_TM : BM;
+  const long long tm_tiles = (d->M + TM - 1) / TM;
+  const int units = pair ? sms / 2 : sms;       // CTAs or CTA pairs that run at once
+  const bool use256 = swiglu || (tm_tiles * n_tiles_256 * groups >= units && d->N >= 256);
   const int BN = use256 ? 256 : 128;
-  const int b_box_rows = swiglu ? BN / 2 : BN;
+  const int b_box_rows = pair ? BN / 2 : (swiglu ? BN / 2 : BN);
 
   GemmArgs a;
   a.C = d->C; a.D = d->D; a.G_out = d->G_out; a.U_out = d->U_out;
@@ -591,19 +918,30 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
     tB2 = tB;
   }
   const int n_per_tile = swiglu ? BN / 2 : BN;
-  long long total = m_tiles * ((d->N + n_per_tile - 1) / n_per_tile) * groups;
+  long long total = tm_tiles * ((d->N + n_per_tile - 1) / n_per_tile) * groups;
   if (d->sym_upper) {
     const long long nn = (d->N + BN - 1) / BN;
     long long kept = 0;
-    for (long long m = 0; m < m_tiles; ++m) kept += nn - std::min<long long>(nn, (m * BM) / BN);
+    for (long long m = 0; m < tm_tiles; ++m) kept += nn - std::min<long long>(nn, (m * TM) / BN);
     total = kept * groups;
   }
   int grid = (int)(total < sms ? total : sms);
   if (grid < 1) grid = 1;
 
   int lrc = 0;
+#define KMOE_LAUNCH_PAIR(BN_, AM_, BM_) lrc = launch_pair_variant<BN_, AM_, BM_>(tA, tB, tB2, a, total, sms, stream)
 #define KMOE_LAUNCH(BN_, AM_, BM_) lrc = launch_variant<BN_, AM_, BM_>(tA, tB, tB2, a, grid, stream)
-  if (BN == 256) {
+  if (pair && BN == 256) {
+    if (d->a_major == 0 && d->b_major == 0) KMOE_LAUNCH_PAIR(256, 0, 0);
+    else if (d->a_major == 0 && d->b_major == 1) KMOE_LAUNCH_PAIR(256, 0, 1);
+    else if (d->a_major == 1 && d->b_major == 0) KMOE_LAUNCH_PAIR(256, 1, 0);
+    else KMOE_LAUNCH_PAIR(256, 1, 1);
+  } else if (pair) {
+    if (d->a_major == 0 && d->b_major == 0) KMOE_LAUNCH_PAIR(128, 0, 0);
+    else if (d->a_major == 0 && d->b_major == 1) KMOE_LAUNCH_PAIR(128, 0, 1);
+    else if (d->a_major == 1 && d->b_major == 0) KMOE_LAUNCH_PAIR(128, 1, 0);
+    else KMOE_LAUNCH_PAIR(128, 1, 1);
+  } else if (BN == 256) {
     if (d->a_major == 0 && d->b_major == 0) KMOE_LAUNCH(256, 0, 0);
     else if (d->a_major == 0 && d->b_major == 1) KMOE_LAUNCH(256, 0, 1);
     else if (d->a_major == 1 && d->b_major == 0) KMOE_LAUNCH(256, 1, 0);
@@ -615,11 +953,12 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
     else KMOE_LAUNCH(128, 1, 1);
   }
 #undef KMOE_LAUNCH
+#undef KMOE_LAUNCH_PAIR
   if (lrc) return lrc;
   if (d->sym_upper) {
     // the tiles below the diagonal were skipped: mirror them from the computed upper part
     dim3 mg((unsigned)(d->N / 32), (unsigned)(d->N / 32), (unsigned)groups);
-    sym_mirror_kernel<<<mg, dim3(32, 8), 0, stream>>>((__nv_bfloat16*)d->C, d->N, d->ldc, d->c_gstride, BN);
+    sym_mirror_kernel<<<mg, dim3(32, 8), 0, stream>>>((__nv_bfloat16*)d->C, d->N, d->ldc, d->c_gstride, BN, TM);
     if (cudaGetLastError() != cudaSuccess) return -22;
   }
   return 0;

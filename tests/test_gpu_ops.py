@@ -202,7 +202,7 @@ def test_grouped_swiglu_fwd_bwd(T, E, k, drop):
     ref.backward(go.float())
     assert _rel(out, ref) < 2e-2
     for name, a, b in [("x", x, xr), ("w1", w1, a1), ("w2", w2, a2), ("w3", w3, a3), ("wts", wts, wr)]:
-        assert _rel(a.grad, b.grad) < 3e-2, name
+        assert _rel(a.grad, b.grad) < 4e-2, name
     # determinism: the same call twice gives identical bits
     out2 = ops.grouped_swiglu(x, w1, w2, w3, idx, wts, keep)
     assert torch.equal(out, out2)
