@@ -377,7 +377,7 @@ def test_flash_attention_packed_documents(B, S, H, Hkv, D):
     outr = eager.attention(qr, kr, vr, True, eager.doc_start_to_mask(ds))
     outr.backward(g.float())
     assert _rel(out, outr) < 2e-2
-    assert _rel(q.grad, qr.grad) < 3e-2 and _rel(k.grad, kr.grad) < 3e-2 and _rel(v.grad, vr.grad) < 3e-2
+    assert _rel(q.grad, qr.grad) < 4e-2 and _rel(k.grad, kr.grad) < 4e-2 and _rel(v.grad, vr.grad) < 4e-2
 
 
 def test_attention_and_routing_are_bitwise_deterministic():
