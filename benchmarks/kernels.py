@@ -248,6 +248,23 @@ def bench_ce(rows):
     report(rows, "lm_head+mtp_ce fwd+bwd (4 heads, 8192 tok)", timeit(fb, iters=5), 4 * 3 * 2.0 * B * S * d * V)
 
 
+def bench_muon(rows):
+    """Newton-Schulz orthogonalisation (5 cubic iterations) on the stacked matrix shapes of the 5B model:
+    per iteration a symmetric Gram product (upper-triangle tiles only) and a product with the
+    ``1.5 Y - 0.5 G Y`` epilogue.  FLOPs counted as executed: 5 * (g^2 o + 2 g^2 o), g = min(m, n), o = max."""
+    from kolmogorov_moe_architecture_b200 import ops
+    from kolmogorov_moe_architecture_b200.ops import cuda_ops as c
+    for (b, m, n, tag) in [(48, 5632, 2048, "dense FFN w1/w2"), (16, 2048, 5632, "dense FFN w3 (16 of 48)"),
+                           (48, 2048, 2048, "attention q/o"), (48, 512, 2048, "attention k/v"),
+                           (8, 8192, 2048, "mamba in_proj"), (8, 2048, 4096, "mamba out_proj")]:
+        x = torch.randn(b, m, n, device="cuda").to(torch.bfloat16)
+        sumsq = x.float().pow(2).sum(dim=(1, 2))
+        g_, o_ = min(m, n), max(m, n)
+        fl = b * 5 * 3.0 * g_ * g_ * o_
+        report(rows, f"newton_schulz x5 ({tag}) {b}x{m}x{n}", timeit(lambda: ops.newton_schulz(x, 5, sumsq)), fl)
+    c.check_status()
+
+
 def bench_norm(rows):
     from kolmogorov_moe_architecture_b200 import ops
     x = torch.randn(8192, 2048, device="cuda").to(torch.bfloat16).requires_grad_(True)
@@ -261,12 +278,12 @@ def bench_norm(rows):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--which", default="gemm,moe,mxfp8,attn,scan,ce,norm")
+    ap.add_argument("--which", default="gemm,moe,mxfp8,attn,scan,ce,norm,muon")
     ap.add_argument("--out", default=None)
     a = ap.parse_args()
     rows = []
     table = {"gemm": bench_gemm, "moe": bench_moe, "mxfp8": bench_mxfp8, "attn": bench_attn, "attn_docs": bench_attn_docs, "scan": bench_scan, "ce": bench_ce,
-             "norm": bench_norm}
+             "norm": bench_norm, "muon": bench_muon}
     for k in a.which.split(","):
         table[k](rows)
     if a.out:

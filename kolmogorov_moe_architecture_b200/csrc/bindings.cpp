@@ -37,7 +37,7 @@ void gemm(const Tensor& A, const Tensor& B, const OptT& B2, Tensor C, const OptT
           int64_t b_major, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, int64_t a_gs, int64_t b_gs,
           int64_t c_gs, const OptT& tile_group, const OptT& num_m_tiles, const OptT& k_begin, const OptT& k_len,
           double alpha, double beta, const OptT& row_scale, const OptT& row_ptr, const OptT& alpha_dev,
-          const OptT& beta_dev, bool sym_upper, Tensor status) {
+          const OptT& beta_dev, bool sym_upper, double diag_add, Tensor status) {
   c10::cuda::CUDAGuard guard(A.device());
   need_bf16(A, "A");
   need_bf16(B, "B");
@@ -59,6 +59,7 @@ void gemm(const Tensor& A, const Tensor& B, const OptT& B2, Tensor C, const OptT
     d.c_row_ptr = (const long long*)row_ptr->data_ptr<int64_t>();
   }
   d.sym_upper = sym_upper ? 1 : 0;
+  d.diag_add = (float)diag_add;
   const int64_t n_groups = mode == KMOE_GEMM_BATCHED ? groups : 1;
   if (alpha_dev.has_value() && alpha_dev->defined()) {
     need_f32(*alpha_dev, "alpha_dev");

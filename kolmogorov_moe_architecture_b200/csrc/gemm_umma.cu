@@ -50,6 +50,7 @@ struct GemmArgs {
   const float* alpha_dev;     // optional per-group multipliers of alpha / beta (BATCHED: index = group)
   const float* beta_dev;
   int sym_upper;              // C is symmetric (A == B): compute only tiles that touch the upper triangle
+  float diag_add;             // added to C[i][i] after alpha (bf16 store path)
   const long long* row_ptr;   // optional: address of each output row (may be peer memory); 0 = row not stored
   int* status;
 };
@@ -158,7 +159,7 @@ __device__ __forceinline__ void load8(const float* src, float* v) {
 template <typename T>
 __device__ __forceinline__ void epilogue_store_chunk(const GemmArgs& a, const uint32_t (&acc)[32], bool have_acc,
                                                      long long row_off_c, long long row_off_d, int col, float scale,
-                                                     float beta, long long row_addr) {
+                                                     float beta, long long row_addr, int row = -1) {
   // row_addr != 0: the row's own base address (possibly on a peer GPU) replaces C + row offset
   T* C = row_addr ? reinterpret_cast<T*>(row_addr) - row_off_c : reinterpret_cast<T*>(a.C);
   const T* D = reinterpret_cast<const T*>(a.D);
@@ -168,6 +169,10 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmArgs& a, const ui
     float v[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = have_acc ? __uint_as_float(acc[j + i]) * scale : 0.f;
+    if (a.diag_add != 0.f && row >= col + j && row < col + j + 8) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += (col + j + i == row) ? a.diag_add : 0.f;
+    }
     if (D != nullptr) {
       float d[8];
       load8(D + row_off_d + col + j, d);
@@ -397,7 +402,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (args.out_f32)
               epilogue_store_chunk<float>(args, r, have_acc, coff, doff, col, scale, beta, row_addr);
             else
-              epilogue_store_chunk<__nv_bfloat16>(args, r, have_acc, coff, doff, col, scale, beta, row_addr);
+              epilogue_store_chunk<__nv_bfloat16>(args, r, have_acc, coff, doff, col, scale, beta, row_addr, row);
           }
         }
       } else {
@@ -603,11 +608,14 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
       ++it;
-      if (!mbar_wait(&tmem_full[acc], acc_ph)) {
-        if (lane == 0) atomicExch(args.status, 14);
-        goto teardown;
+      const bool staged = !swiglu && !args.out_f32;   // this path awaits the accumulator after prefetching D
+      if (!staged) {
+        if (!mbar_wait(&tmem_full[acc], acc_ph)) {
+          if (lane == 0) atomicExch(args.status, 14);
+          goto teardown;
+        }
+        tc_fence_after();
       }
-      tc_fence_after();
       const bool have_acc = t.k_blocks > 0;
       const int row0 = t.m_tile * PAIR_TM + (int)rank * BM + q * 32;
       const int row = row0 + lane;
@@ -622,13 +630,37 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (args.row_scale != nullptr && row_ok) scale *= args.row_scale[row];
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
       if (!swiglu && !args.out_f32) {
-        // bf16 output: a lane holds one row, so the 64-column slab is staged in shared memory and written
-        // back with 8 lanes per row (four full 128-byte lines per store instruction); the addend is read
-        // with the same coalesced pattern
+        // bf16 output: a lane holds one row, so each 64-column slab is staged in shared memory and written
+        // back with 8 lanes per row (four full 128-byte lines per store instruction).  The addend is read
+        // with the same pattern, and all of it before the accumulator is awaited, so its latency falls
+        // under the main loop of this tile instead of between the slabs.
         __nv_bfloat16* Cb = reinterpret_cast<__nv_bfloat16*>(args.C);
         const __nv_bfloat16* Dp = reinterpret_cast<const __nv_bfloat16*>(args.D);
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 64) {
+        constexpr int SLABS = BN / 64;
+        uint4 dpre[SLABS][8];
+        if (Dp != nullptr) {
+#pragma unroll
+          for (int sl = 0; sl < SLABS; ++sl) {
+#pragma unroll
+            for (int i8 = 0; i8 < 8; ++i8) {
+              const int grow = row0 + i8 * 4 + (lane >> 3);
+              const int gcol = t.n_tile * BN + sl * 64 + (lane & 7) * 8;
+              dpre[sl][i8] = (grow < args.M && gcol < args.N)
+                                 ? __ldg(reinterpret_cast<const uint4*>(Dp + goff + (long long)grow * args.ldd + gcol))
+                                 : make_uint4(0, 0, 0, 0);
+            }
+          }
+        }
+        if (!mbar_wait(&tmem_full[acc], acc_ph)) {
+          if (lane == 0) atomicExch(args.status, 14);
+          goto teardown;
+        }
+        tc_fence_after();
+        // symmetric product: a tile strictly above the diagonal also writes its transpose
+        const bool mirror = args.sym_upper && t.n_tile * BN >= (t.m_tile + 1) * PAIR_TM;
+#pragma unroll
+        for (int sl = 0; sl < SLABS; ++sl) {
+          const int c = sl * 64;
           if (t.n_tile * BN + c >= args.N) break;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
@@ -642,6 +674,11 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
               float v[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) v[i] = have_acc ? __uint_as_float(r[j + i]) * scale : 0.f;
+              const int col0 = t.n_tile * BN + c + h * 32 + j;
+              if (args.diag_add != 0.f && row >= col0 && row < col0 + 8) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] += (col0 + i == row) ? args.diag_add : 0.f;
+              }
               store8<__nv_bfloat16>(&stg[lane][h * 32 + j], v);
             }
           }
@@ -655,19 +692,38 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             if (grow < args.M && gcol < args.N) {
               uint4 o = *reinterpret_cast<const uint4*>(&stg[rr][cc]);
               if (Dp != nullptr) {
-                float d[8], v[8];
-                load8(Dp + goff + (long long)grow * args.ldd + gcol, d);
+                float v[8];
                 const __nv_bfloat162* pv = reinterpret_cast<const __nv_bfloat162*>(&o);
+                const __nv_bfloat162* pd = reinterpret_cast<const __nv_bfloat162*>(&dpre[sl][i8]);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                  float2 f = __bfloat1622float2(pv[i]);
-                  v[2 * i] = f.x + beta * d[2 * i];
-                  v[2 * i + 1] = f.y + beta * d[2 * i + 1];
+                  const float2 f = __bfloat1622float2(pv[i]);
+                  const float2 d = __bfloat1622float2(pd[i]);
+                  v[2 * i] = f.x + beta * d.x;
+                  v[2 * i + 1] = f.y + beta * d.y;
                 }
                 o.x = pack_bf16(v[0], v[1]); o.y = pack_bf16(v[2], v[3]);
                 o.z = pack_bf16(v[4], v[5]); o.w = pack_bf16(v[6], v[7]);
               }
               *reinterpret_cast<uint4*>(Cb + goff + (long long)grow * args.ldc + gcol) = o;
+            }
+          }
+          if (mirror) {
+            // C[col][row] = C[row][col]: a lane gathers 8 rows of one staged column (16 bytes of the
+            // destination row), 4 lanes cover the 32 rows of the slab
+#pragma unroll
+            for (int i8 = 0; i8 < 8; ++i8) {
+              const int jc = i8 * 8 + (lane >> 2);          // staged column = destination row
+              const int r8 = (lane & 3) * 8;                // first of 8 staged rows = destination columns
+              const int drow = t.n_tile * BN + c + jc;
+              const int dcol = row0 + r8;
+              if (drow < args.N && dcol < args.M) {
+                __nv_bfloat16 e[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) e[i] = stg[r8 + i][jc];
+                *reinterpret_cast<uint4*>(Cb + goff + (long long)drow * args.ldc + dcol) =
+                    *reinterpret_cast<const uint4*>(e);
+              }
             }
           }
           __syncwarp();
@@ -894,6 +950,7 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
   a.row_scale = d->row_scale; a.row_ptr = d->c_row_ptr; a.status = d->status;
   a.alpha_dev = d->alpha_dev; a.beta_dev = d->beta_dev;
   a.sym_upper = d->sym_upper;
+  a.diag_add = d->diag_add;
   if (d->sym_upper && (d->M != d->N || swiglu || d->mode == KMOE_GEMM_GROUPED_M || d->out_f32 || d->N % 32 ||
                        d->D != nullptr))
     return -4;
@@ -955,8 +1012,9 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
 #undef KMOE_LAUNCH
 #undef KMOE_LAUNCH_PAIR
   if (lrc) return lrc;
-  if (d->sym_upper) {
-    // the tiles below the diagonal were skipped: mirror them from the computed upper part
+  if (d->sym_upper && !pair) {
+    // the tiles below the diagonal were skipped: mirror them from the computed upper part (the CTA-pair
+    // kernel writes the transposed tiles from its epilogue instead)
     dim3 mg((unsigned)(d->N / 32), (unsigned)(d->N / 32), (unsigned)groups);
     sym_mirror_kernel<<<mg, dim3(32, 8), 0, stream>>>((__nv_bfloat16*)d->C, d->N, d->ldc, d->c_gstride, BN, TM);
     if (cudaGetLastError() != cudaSuccess) return -22;

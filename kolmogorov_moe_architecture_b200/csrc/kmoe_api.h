@@ -50,6 +50,9 @@ typedef struct KmoeGemmDesc {
   // C = A A^T style products (M == N, A and B the same operand, bf16 output, no addend): tiles entirely below
   // the diagonal are not computed but mirrored from the upper part afterwards.
   int sym_upper;
+  // added to the elements on the main diagonal of every (group's) output after alpha is applied (STORE
+  // epilogue, bf16 output): C = alpha * A B + diag_add * I, e.g. the 1.5 I - 0.5 X X^T factor of Newton-Schulz
+  float diag_add;
   int* status;             // device int; non-zero after the launch = a bounded wait expired
   int num_sms;             // 0 = query
 } KmoeGemmDesc;

@@ -84,15 +84,15 @@ def _count(n: int = 1):
 def gemm(A, B, C, *, M, N, Kd, mode=DENSE, epi=EPI_STORE, groups=1, a_major=MAJ_K, b_major=MAJ_K,
          lda, ldb, ldc, ldd=0, a_gs=0, b_gs=0, c_gs=0, B2=None, D=None, G=None, U=None,
          tile_group=None, num_m_tiles=None, k_begin=None, k_len=None, alpha=1.0, beta=0.0, row_scale=None,
-         row_ptr=None, alpha_dev=None, beta_dev=None, sym_upper=False):
+         row_ptr=None, alpha_dev=None, beta_dev=None, sym_upper=False, diag_add=0.0):
     """``row_ptr`` (int64, one address per output row, 0 = skip) redirects each output row, e.g. into a
     peer GPU's buffer; ``C`` then only supplies the dtype.  ``alpha_dev`` / ``beta_dev`` (fp32, one entry
     per group of a batched GEMM) multiply alpha / beta with values that live on the device.  ``sym_upper``:
     the product is symmetric (A and B are the same operand, M == N): tiles below the diagonal are mirrored
-    instead of computed."""
+    instead of computed.  ``diag_add`` is added to the main diagonal of the (bf16) result after ``alpha``."""
     K.gemm(A, B, B2, C, D, G, U, mode, epi, M, N, Kd, groups, a_major, b_major, lda, ldb, ldc, ldd,
            a_gs, b_gs, c_gs, tile_group, num_m_tiles, k_begin, k_len, alpha, beta, row_scale, row_ptr,
-           alpha_dev, beta_dev, sym_upper, status_tensor(A.device))
+           alpha_dev, beta_dev, sym_upper, float(diag_add), status_tensor(A.device))
     _count()
     return C
 
@@ -721,7 +721,7 @@ def newton_schulz(matrix: torch.Tensor, iters: int = 5, sumsq: Optional[torch.Te
 
     ``sumsq`` (fp32, one entry per matrix: its squared Frobenius norm, already on the device) removes the
     normalisation passes: the first iteration runs on the unnormalised bf16 input and folds
-    ``s = 1 / (norm + 1e-7)`` into the GEMM epilogues (``G = s^2 X X^T``, ``Y1 = 1.5 s X - 0.5 s G X``)."""
+    ``s = 1 / (norm + 1e-7)`` into the GEMM epilogues (``P = 1.5 I - 0.5 s^2 X X^T``, ``Y1 = s P X``)."""
     squeeze = matrix.dim() == 2
     Y = matrix.unsqueeze(0) if squeeze else matrix
     b, m, n = Y.shape
@@ -742,24 +742,27 @@ def newton_schulz(matrix: torch.Tensor, iters: int = 5, sumsq: Optional[torch.Te
     wide = m <= n
     g = m if wide else n
     Gm = torch.empty(b, g, g, dtype=torch.bfloat16, device=Y.device)
+    # Y' = 1.5 Y - 0.5 G Y = (1.5 I - 0.5 G) Y: the Gram GEMM's epilogue emits P = 1.5 I - 0.5 G directly, so
+    # the second product is a plain GEMM that reads no addend
     for it in range(iters):
         first = it == 0 and s1 is not None
         ga = dict(alpha_dev=s2) if first else {}
-        ya = dict(alpha_dev=s1, beta_dev=s1) if first else {}
+        ya = dict(alpha_dev=s1) if first else {}
         if wide:
-            # G = Y Y^T  (A, B K-major over n)
-            gemm(Ya, Ya, Gm, mode=BATCHED, groups=b, M=m, N=m, Kd=n, lda=n, ldb=n, ldc=m,
-                 a_gs=m * n, b_gs=m * n, c_gs=m * m, sym_upper=True, **ga)
-            # Y' = 1.5 Y - 0.5 G Y   (B = Y read MN-major)
-            gemm(Gm, Ya, Yb, D=Ya, alpha=-0.5, beta=1.5, mode=BATCHED, groups=b, M=m, N=n, Kd=m,
-                 b_major=MAJ_MN, lda=m, ldb=n, ldc=n, ldd=n, a_gs=m * m, b_gs=m * n, c_gs=m * n, **ya)
+            # P = 1.5 I - 0.5 Y Y^T  (A, B K-major over n)
+            gemm(Ya, Ya, Gm, mode=BATCHED, groups=b, M=m, N=m, Kd=n, lda=n, ldb=n, ldc=m, alpha=-0.5,
+                 diag_add=1.5, a_gs=m * n, b_gs=m * n, c_gs=m * m, sym_upper=True, **ga)
+            # Y' = P Y   (B = Y read MN-major)
+            gemm(Gm, Ya, Yb, mode=BATCHED, groups=b, M=m, N=n, Kd=m,
+                 b_major=MAJ_MN, lda=m, ldb=n, ldc=n, a_gs=m * m, b_gs=m * n, c_gs=m * n, **ya)
         else:
-            # G = Y^T Y  (both MN-major over m)
+            # P = 1.5 I - 0.5 Y^T Y  (both MN-major over m)
             gemm(Ya, Ya, Gm, mode=BATCHED, groups=b, M=n, N=n, Kd=m, a_major=MAJ_MN, b_major=MAJ_MN,
-                 lda=n, ldb=n, ldc=n, a_gs=m * n, b_gs=m * n, c_gs=n * n, sym_upper=True, **ga)
-            # Y' = 1.5 Y - 0.5 Y G   (G symmetric: read K-major)
-            gemm(Ya, Gm, Yb, D=Ya, alpha=-0.5, beta=1.5, mode=BATCHED, groups=b, M=m, N=n, Kd=n,
-                 lda=n, ldb=n, ldc=n, ldd=n, a_gs=m * n, b_gs=n * n, c_gs=m * n, **ya)
+                 lda=n, ldb=n, ldc=n, alpha=-0.5, diag_add=1.5, a_gs=m * n, b_gs=m * n, c_gs=n * n,
+                 sym_upper=True, **ga)
+            # Y' = Y P   (P symmetric: read K-major)
+            gemm(Ya, Gm, Yb, mode=BATCHED, groups=b, M=m, N=n, Kd=n,
+                 lda=n, ldb=n, ldc=n, a_gs=m * n, b_gs=n * n, c_gs=m * n, **ya)
         if first:
             Ya, Yb = Yb, Yc
         else:

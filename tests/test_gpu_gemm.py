@@ -122,3 +122,22 @@ def test_symmetric_gram_skips_and_mirrors(b, m, n):
     assert (full.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
     assert torch.equal(torch.triu(sym), torch.triu(full))
     assert torch.equal(sym, sym.transpose(1, 2))
+
+
+@pytest.mark.parametrize("b,m,n", [(2, 512, 320), (1, 2048, 512), (3, 128, 192)])
+def test_symmetric_gram_with_scaled_identity(b, m, n):
+    """``alpha * A A^T + diag_add * I`` (the ``1.5 I - 0.5 X X^T`` factor of a Newton-Schulz step) with and
+    without the symmetric shortcut, against fp32."""
+    from kolmogorov_moe_architecture_b200.ops import cuda_ops as c
+    torch.manual_seed(3)
+    a = (torch.randn(b, m, n, device="cuda") * 0.05).to(torch.bfloat16)
+    ref = -0.5 * (a.float() @ a.float().transpose(1, 2)) + 1.5 * torch.eye(m, device="cuda")
+    kw = dict(mode=c.BATCHED, groups=b, M=m, N=m, Kd=n, lda=n, ldb=n, ldc=m, a_gs=m * n, b_gs=m * n, c_gs=m * m,
+              alpha=-0.5, diag_add=1.5)
+    for sym in (False, True):
+        out = torch.full((b, m, m), 7.0, dtype=torch.bfloat16, device="cuda")
+        c.gemm(a, a, out, sym_upper=sym, **kw)
+        c.check_status()
+        _close(out, ref, tol=1e-2)
+        if sym:
+            assert torch.equal(out, out.transpose(1, 2))
