@@ -37,7 +37,7 @@ void gemm(const Tensor& A, const Tensor& B, const OptT& B2, Tensor C, const OptT
           int64_t b_major, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, int64_t a_gs, int64_t b_gs,
           int64_t c_gs, const OptT& tile_group, const OptT& num_m_tiles, const OptT& k_begin, const OptT& k_len,
           double alpha, double beta, const OptT& row_scale, const OptT& row_ptr, const OptT& alpha_dev,
-          const OptT& beta_dev, bool sym_upper, double diag_add, Tensor status) {
+          const OptT& beta_dev, bool sym_upper, double diag_add, int64_t k_split, Tensor status) {
   c10::cuda::CUDAGuard guard(A.device());
   need_bf16(A, "A");
   need_bf16(B, "B");
@@ -60,6 +60,7 @@ void gemm(const Tensor& A, const Tensor& B, const OptT& B2, Tensor C, const OptT
   }
   d.sym_upper = sym_upper ? 1 : 0;
   d.diag_add = (float)diag_add;
+  d.k_split = (int)k_split;
   const int64_t n_groups = mode == KMOE_GEMM_BATCHED ? groups : 1;
   if (alpha_dev.has_value() && alpha_dev->defined()) {
     need_f32(*alpha_dev, "alpha_dev");
@@ -174,6 +175,21 @@ std::tuple<Tensor, Tensor> swiglu_bwd(const Tensor& g, const Tensor& u, const Te
                         row_stride(g2), row_stride(u2), cols, (const int*)ptr_or_null(live_rows), cur_stream()),
         "swiglu_bwd");
   return {dg, du};
+}
+
+// dG and dU side by side in one (rows, 2 * cols) buffer: the [dG | dU] operand of a split-reduction GEMM
+Tensor swiglu_bwd_cat(const Tensor& g, const Tensor& u, const Tensor& dh, const OptT& live_rows) {
+  c10::cuda::CUDAGuard guard(g.device());
+  need_bf16(g, "gate"); need_bf16(u, "up"); need_bf16(dh, "dh");
+  TORCH_CHECK(dh.is_contiguous() && g.dim() == 2);
+  const int cols = g.size(-1);
+  const long long rows = g.numel() / cols;
+  Tensor out = at::empty({rows, 2 * (long long)cols}, g.options());
+  char* base = reinterpret_cast<char*>(out.data_ptr());
+  check(kmoe_swiglu_bwd(g.data_ptr(), u.data_ptr(), dh.data_ptr(), base, base + 2LL * cols, rows, cols, row_stride(g),
+                        row_stride(u), 2LL * cols, (const int*)ptr_or_null(live_rows), cur_stream()),
+        "swiglu_bwd_cat");
+  return out;
 }
 
 // ------------------------------------------------------------------------ Mamba
@@ -638,6 +654,7 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("rowdot_bwd", &rowdot_bwd);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("swiglu_bwd_cat", &swiglu_bwd_cat);
   m.def("conv1d_fwd", &conv1d_fwd);
   m.def("conv1d_bwd", &conv1d_bwd);
   m.def("scan_fwd", &scan_fwd);

@@ -51,6 +51,7 @@ struct GemmArgs {
   const float* beta_dev;
   int sym_upper;              // C is symmetric (A == B): compute only tiles that touch the upper triangle
   float diag_add;             // added to C[i][i] after alpha (bf16 store path)
+  int k_split;                // > 0: reduction elements [k_split, K) of B come from the second tensor map
   const long long* row_ptr;   // optional: address of each output row (may be peer memory); 0 = row not stored
   int* status;
 };
@@ -254,10 +255,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           else
             tma_load_4d(sa, &tmA, &full_bar[s], 0, k, t.m_tile * (BM / 64), t.g_a);
           if (!swiglu) {
+            const bool second = args.k_split > 0 && k >= args.k_split;
+            const CUtensorMap* tb = second ? &tmB2 : &tmB;
+            const int kb2 = second ? k - args.k_split : k;
             if (B_MAJOR == KMOE_MAJOR_K)
-              tma_load_4d(sb, &tmB, &full_bar[s], k, t.n_tile * BN, 0, t.g_b);
+              tma_load_4d(sb, tb, &full_bar[s], kb2, t.n_tile * BN, 0, t.g_b);
             else
-              tma_load_4d(sb, &tmB, &full_bar[s], 0, k, t.n_tile * (BN / 64), t.g_b);
+              tma_load_4d(sb, tb, &full_bar[s], 0, kb2, t.n_tile * (BN / 64), t.g_b);
           } else {
             constexpr int HB = BN / 2;
             if (B_MAJOR == KMOE_MAJOR_K) {
@@ -544,12 +548,14 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             tma_load_4d_pair(sa, &tmA, fb, 0, k, arow / 64, t.g_a);
           // B: this CTA's half of the tile's columns; with the SwiGLU epilogue the halves are the gate
           // weight (leader) and the up weight (peer), so accumulator columns [0, BN/2) hold the gate
-          const CUtensorMap* tb = (swiglu && !leader) ? &tmB2 : &tmB;
+          const bool second = !swiglu && args.k_split > 0 && k >= args.k_split;
+          const CUtensorMap* tb = ((swiglu && !leader) || second) ? &tmB2 : &tmB;
+          const int kb2 = second ? k - args.k_split : k;
           const int brow = swiglu ? t.n_tile * HALF_N : t.n_tile * BN + (int)rank * HALF_N;
           if (B_MAJOR == KMOE_MAJOR_K)
-            tma_load_4d_pair(sb, tb, fb, k, brow, 0, t.g_b);
+            tma_load_4d_pair(sb, tb, fb, kb2, brow, 0, t.g_b);
           else
-            tma_load_4d_pair(sb, tb, fb, 0, k, brow / 64, t.g_b);
+            tma_load_4d_pair(sb, tb, fb, 0, kb2, brow / 64, t.g_b);
           if (++s == stages) { s = 0; ph ^= 1; }
         }
       }
@@ -917,6 +923,9 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
   if (d->K % 8 != 0 || d->N % 8 != 0) return -1;
   if (d->K <= 0 || d->M <= 0 || d->N <= 0) return -2;
   if (d->c_row_ptr != nullptr && (d->out_f32 || d->epilogue != KMOE_EPI_STORE)) return -3;
+  if (d->k_split != 0 && (d->k_split % BK || d->k_split <= 0 || d->k_split >= d->K || d->B2 == nullptr ||
+                          d->epilogue != KMOE_EPI_STORE || d->k_begin != nullptr))
+    return -5;
   const bool swiglu = d->epilogue == KMOE_EPI_SWIGLU;
   // narrow outputs use the 128-wide tile so more CTAs get work
   const int n_tiles_256 = (d->N + (swiglu ? 127 : 255)) / (swiglu ? 128 : 256);
@@ -951,6 +960,7 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
   a.alpha_dev = d->alpha_dev; a.beta_dev = d->beta_dev;
   a.sym_upper = d->sym_upper;
   a.diag_add = d->diag_add;
+  a.k_split = d->k_split;
   if (d->sym_upper && (d->M != d->N || swiglu || d->mode == KMOE_GEMM_GROUPED_M || d->out_f32 || d->N % 32 ||
                        d->D != nullptr))
     return -4;
@@ -966,9 +976,14 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
   CUtensorMap tA, tB, tB2;
   int rc = make_operand_tmap(&tA, d->A, d->a_major, d->M, k_extent_a, d->lda, d->a_gstride, a_groups, BM);
   if (rc) return rc;
+  if (d->k_split > 0) k_extent_b = d->k_split;
   rc = make_operand_tmap(&tB, d->B, d->b_major, d->N, k_extent_b, d->ldb, d->b_gstride, b_groups, b_box_rows);
   if (rc) return rc;
-  if (swiglu) {
+  if (d->k_split > 0) {
+    rc = make_operand_tmap(&tB2, d->B2, d->b_major, d->N, d->K - d->k_split, d->ldb, d->b_gstride, b_groups,
+                           b_box_rows);
+    if (rc) return rc;
+  } else if (swiglu) {
     rc = make_operand_tmap(&tB2, d->B2, d->b_major, d->N, k_extent_b, d->ldb, d->b_gstride, b_groups, b_box_rows);
     if (rc) return rc;
   } else {

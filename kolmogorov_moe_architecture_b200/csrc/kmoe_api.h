@@ -53,6 +53,10 @@ typedef struct KmoeGemmDesc {
   // added to the elements on the main diagonal of every (group's) output after alpha is applied (STORE
   // epilogue, bf16 output): C = alpha * A B + diag_add * I, e.g. the 1.5 I - 0.5 X X^T factor of Newton-Schulz
   float diag_add;
+  // STORE epilogue, optional: the reduction is the concatenation of two B operands, elements [0, k_split) from
+  // B and [k_split, K) from B2 (same layout, ldb and group stride; k_split a multiple of 64), while A is one
+  // [M, K] operand.  C = A[:, :k_split] B^T + A[:, k_split:] B2^T in one pass, e.g. dX = [dG | dU] [W1 ; W2].
+  int k_split;
   int* status;             // device int; non-zero after the launch = a bounded wait expired
   int num_sms;             // 0 = query
 } KmoeGemmDesc;

@@ -84,15 +84,17 @@ def _count(n: int = 1):
 def gemm(A, B, C, *, M, N, Kd, mode=DENSE, epi=EPI_STORE, groups=1, a_major=MAJ_K, b_major=MAJ_K,
          lda, ldb, ldc, ldd=0, a_gs=0, b_gs=0, c_gs=0, B2=None, D=None, G=None, U=None,
          tile_group=None, num_m_tiles=None, k_begin=None, k_len=None, alpha=1.0, beta=0.0, row_scale=None,
-         row_ptr=None, alpha_dev=None, beta_dev=None, sym_upper=False, diag_add=0.0):
+         row_ptr=None, alpha_dev=None, beta_dev=None, sym_upper=False, diag_add=0.0, k_split=0):
     """``row_ptr`` (int64, one address per output row, 0 = skip) redirects each output row, e.g. into a
     peer GPU's buffer; ``C`` then only supplies the dtype.  ``alpha_dev`` / ``beta_dev`` (fp32, one entry
     per group of a batched GEMM) multiply alpha / beta with values that live on the device.  ``sym_upper``:
     the product is symmetric (A and B are the same operand, M == N): tiles below the diagonal are mirrored
-    instead of computed.  ``diag_add`` is added to the main diagonal of the (bf16) result after ``alpha``."""
+    instead of computed.  ``diag_add`` is added to the main diagonal of the (bf16) result after ``alpha``.
+    ``k_split`` > 0 (with ``B2``): the reduction is split, elements [0, k_split) multiply ``B`` and the rest
+    ``B2``: ``C = A[:, :k_split] B^T + A[:, k_split:] B2^T`` in one pass."""
     K.gemm(A, B, B2, C, D, G, U, mode, epi, M, N, Kd, groups, a_major, b_major, lda, ldb, ldc, ldd,
            a_gs, b_gs, c_gs, tile_group, num_m_tiles, k_begin, k_len, alpha, beta, row_scale, row_ptr,
-           alpha_dev, beta_dev, sym_upper, float(diag_add), status_tensor(A.device))
+           alpha_dev, beta_dev, sym_upper, float(diag_add), int(k_split), status_tensor(A.device))
     _count()
     return C
 
@@ -240,12 +242,16 @@ class _DenseSwiGLU(torch.autograd.Function):
         if not _rows_ok(dy):
             dy = dy.contiguous()
         dH = mm_nn(dy, w3)
-        dG, dU = K.swiglu_bwd(G, U, dH, None)
+        T, f = dH.shape
+        d = w1.shape[1]
+        dGU = K.swiglu_bwd_cat(G, U, dH, None)              # [dG | dU], one (T, 2f) operand
+        dG, dU = dGU[:, :f], dGU[:, f:]
         _count()
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = mm_nn(dG, w1)
-            mm_nn(dU, w2, out=dx, D=dx, beta=1.0)
+            # dx = dG W1 + dU W2 as one GEMM whose reduction runs over [dG | dU] and [W1 ; W2]
+            dx = torch.empty(T, d, dtype=dy.dtype, device=dy.device)
+            gemm(dGU, w1, dx, B2=w2, M=T, N=d, Kd=2 * f, k_split=f, b_major=MAJ_MN, lda=2 * f, ldb=d, ldc=d)
         H = K.swiglu_fwd(G, U, None)
         _count()
         dw1 = _wgrad(dG, x2, w1)
@@ -462,12 +468,12 @@ class _GroupedSwiGLU(torch.autograd.Function):
         dH = torch.empty(max_rows, f, dtype=dout.dtype, device=dout.device)
         gemm(dYp, w3, dH, mode=GROUPED_M, M=max_rows, N=f, Kd=d, groups=E, lda=d, ldb=d, ldc=f, b_gs=f * d,
              tile_group=tile_group, num_m_tiles=nmt)
-        dG, dU = K.swiglu_bwd(G, U, dH, meta[1:2])
+        dGU = K.swiglu_bwd_cat(G, U, dH, meta[1:2])          # [dG | dU], one (rows, 2f) operand
+        dG, dU = dGU[:, :f], dGU[:, f:]
         dXp = torch.empty(max_rows, d, dtype=dout.dtype, device=dout.device)
-        gemm(dG, w1, dXp, mode=GROUPED_M, M=max_rows, N=d, Kd=f, groups=E, lda=f, ldb=f, ldc=d, b_gs=d * f,
-             tile_group=tile_group, num_m_tiles=nmt)
-        gemm(dU, w2, dXp, D=dXp, beta=1.0, mode=GROUPED_M, M=max_rows, N=d, Kd=f, groups=E, lda=f, ldb=f,
-             ldc=d, ldd=d, b_gs=d * f, tile_group=tile_group, num_m_tiles=nmt)
+        # dXp = dG W1^T + dU W2^T in one grouped GEMM: the reduction runs over [dG | dU] and [W1 | W2]
+        gemm(dGU, w1, dXp, B2=w2, mode=GROUPED_M, M=max_rows, N=d, Kd=2 * f, k_split=f, groups=E, lda=2 * f,
+             ldb=f, ldc=d, b_gs=d * f, tile_group=tile_group, num_m_tiles=nmt)
         dx = K.moe_combine(dXp, pos, None, T, k)
         # weight gradients: per expert, reduction over that expert's (padded) row range
         kb = offsets[:E].contiguous()
@@ -477,8 +483,8 @@ class _GroupedSwiGLU(torch.autograd.Function):
         sinks = [grad_sink(w) for w in (w1, w2, w3)]
         dw1, dw2, dw3 = [s[0] if s is not None else torch.empty_like(w) for s, w in zip(sinks, (w1, w2, w3))]
         common = dict(mode=BATCHED, groups=E, a_major=MAJ_MN, b_major=MAJ_MN, Kd=max_rows, k_begin=kb, k_len=kl)
-        gemm(Xp, dG, dw1, M=d, N=f, lda=d, ldb=f, ldc=f, c_gs=d * f, **common)
-        gemm(Xp, dU, dw2, M=d, N=f, lda=d, ldb=f, ldc=f, c_gs=d * f, **common)
+        gemm(Xp, dG, dw1, M=d, N=f, lda=d, ldb=2 * f, ldc=f, c_gs=d * f, **common)
+        gemm(Xp, dU, dw2, M=d, N=f, lda=d, ldb=2 * f, ldc=f, c_gs=d * f, **common)
         gemm(H, dYp, dw3, M=f, N=d, lda=f, ldb=d, ldc=d, c_gs=f * d, **common)
         _count(5)
         for s_ in sinks:
