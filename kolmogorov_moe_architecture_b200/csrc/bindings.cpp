@@ -225,9 +225,9 @@ std::tuple<Tensor, Tensor, Tensor> conv1d_bwd(const Tensor& x, const Tensor& w, 
   return {dx, dw, db};
 }
 
-std::tuple<Tensor, Tensor> scan_fwd(const Tensor& u, const Tensor& delta, const OptT& z, const Tensor& A,
-                                    const Tensor& Bm, const Tensor& Cm, const OptT& D, const OptT& dt_bias,
-                                    bool softplus, bool save) {
+std::tuple<Tensor, Tensor, Tensor> scan_fwd(const Tensor& u, const Tensor& delta, const OptT& z, const Tensor& A,
+                                            const Tensor& Bm, const Tensor& Cm, const OptT& D, const OptT& dt_bias,
+                                            bool softplus, bool save) {
   c10::cuda::CUDAGuard guard(u.device());
   need_bf16(u, "u"); need_bf16(delta, "delta"); need_f32(A, "A"); need_f32(Bm, "B"); need_f32(Cm, "C");
   // A [C,N], or [G,C,N] with G parameter sets over the batch (D, dt_bias [G,C] then)
@@ -238,18 +238,21 @@ std::tuple<Tensor, Tensor> scan_fwd(const Tensor& u, const Tensor& delta, const 
   Tensor out = at::empty_like(u);
   const int nch = (S + kmoe_scan_chunk() - 1) / kmoe_scan_chunk();
   Tensor ckpt = save ? at::empty({B, nch, N, C}, A.options()) : at::empty({0}, A.options());
+  const int P = kmoe_scan_segments(B, S, C);
+  Tensor seg = P > 1 ? at::empty({B, P, N + 1, C}, A.options()) : at::empty({0}, A.options());
   const bool has_z = z.has_value() && z->defined();
   if (has_z) need_bf16(*z, "z");
   check(kmoe_scan_fwd(u.data_ptr(), delta.data_ptr(), has_z ? z->data_ptr() : nullptr, A.data_ptr<float>(),
                       Bm.data_ptr<float>(), Cm.data_ptr<float>(), (const float*)ptr_or_null(D),
-                      (const float*)ptr_or_null(dt_bias), out.data_ptr(), save ? ckpt.data_ptr<float>() : nullptr, B,
-                      S, C, N, has_z ? row_stride(*z) : 0, softplus ? 1 : 0, G, cur_stream()), "scan_fwd");
-  return {out, ckpt};
+                      (const float*)ptr_or_null(dt_bias), out.data_ptr(), save ? ckpt.data_ptr<float>() : nullptr,
+                      P > 1 ? seg.data_ptr<float>() : nullptr, B, S, C, N, has_z ? row_stride(*z) : 0,
+                      softplus ? 1 : 0, G, cur_stream()), "scan_fwd");
+  return {out, ckpt, seg};
 }
 
 std::vector<Tensor> scan_bwd(const Tensor& u, const Tensor& delta, const OptT& z, const Tensor& A, const Tensor& Bm,
                              const Tensor& Cm, const OptT& D, const OptT& dt_bias, const Tensor& dout,
-                             const Tensor& ckpt, bool softplus) {
+                             const Tensor& ckpt, const Tensor& seg, bool softplus) {
   c10::cuda::CUDAGuard guard(u.device());
   need_bf16(dout, "dout");
   TORCH_CHECK(dout.is_contiguous());
@@ -263,9 +266,13 @@ std::vector<Tensor> scan_bwd(const Tensor& u, const Tensor& delta, const OptT& z
   Tensor dA = at::zeros_like(A), dB = at::zeros({B, S, N}, f32), dC = at::zeros({B, S, N}, f32);
   Tensor dD = A.dim() == 3 ? at::zeros({G, C}, f32) : at::zeros({C}, f32);
   Tensor dbias = at::zeros_like(dD);
+  const int P = kmoe_scan_segments(B, S, C);
+  TORCH_CHECK(P == 1 || seg.numel() == (int64_t)B * P * (N + 1) * C, "segment scratch of the forward pass expected");
+  Tensor gseg = P > 1 ? at::empty({B, P, N, C}, f32) : at::empty({0}, f32);
   check(kmoe_scan_bwd(u.data_ptr(), delta.data_ptr(), has_z ? z->data_ptr() : nullptr, A.data_ptr<float>(),
                       Bm.data_ptr<float>(), Cm.data_ptr<float>(), (const float*)ptr_or_null(D),
-                      (const float*)ptr_or_null(dt_bias), dout.data_ptr(), ckpt.data_ptr<float>(), du.data_ptr(),
+                      (const float*)ptr_or_null(dt_bias), dout.data_ptr(), ckpt.data_ptr<float>(),
+                      P > 1 ? seg.data_ptr<float>() : nullptr, P > 1 ? gseg.data_ptr<float>() : nullptr, du.data_ptr(),
                       dd.data_ptr(), has_z ? dz.data_ptr() : nullptr, C, dA.data_ptr<float>(), dB.data_ptr<float>(),
                       dC.data_ptr<float>(), dD.data_ptr<float>(), dbias.data_ptr<float>(), B, S, C, N,
                       has_z ? row_stride(*z) : 0, softplus ? 1 : 0, G, cur_stream()), "scan_bwd");

@@ -134,14 +134,21 @@ int kmoe_conv1d_fwd(const void* x, const float* w, const float* bias, void* y, i
                     int act, int groups, cudaStream_t st);
 int kmoe_conv1d_bwd(const void* x, const float* w, const float* bias, const void* dy, void* dx, float* dw,
                     float* dbias, int B, int S, int C, long long ldx, int act, int groups, cudaStream_t st);
+// Selective scan.  The sequence is processed in kmoe_scan_segments(B, S, C) parallel segments.
+//   ckpt (forward, optional): [B, ceil(S / kmoe_scan_chunk()), N, C] floats, the state before every chunk.
+//   seg  (required when there is more than one segment): [B, segments, N + 1, C] floats of scratch that the
+//        backward pass reads again;  gseg: [B, segments, N, C] floats of scratch for the backward pass.
+//   C % 8 == 0, N == 16.
 int kmoe_scan_chunk(void);
+int kmoe_scan_segments(int B, int S, int C);
 int kmoe_scan_fwd(const void* u, const void* delta, const void* z, const float* A, const float* Bm, const float* Cm,
-                  const float* D, const float* dt_bias, void* out, float* ckpt, int B, int S, int C, int N,
-                  long long ldz, int softplus, int groups, cudaStream_t st);
+                  const float* D, const float* dt_bias, void* out, float* ckpt, float* seg, int B, int S, int C,
+                  int N, long long ldz, int softplus, int groups, cudaStream_t st);
 int kmoe_scan_bwd(const void* u, const void* delta, const void* z, const float* A, const float* Bm, const float* Cm,
-                  const float* D, const float* dt_bias, const void* dout, const float* ckpt, void* du, void* ddelta,
-                  void* dz, long long lddz, float* dA, float* dB, float* dC, float* dD, float* dbias, int B, int S,
-                  int C, int N, long long ldz, int softplus, int groups, cudaStream_t st);
+                  const float* D, const float* dt_bias, const void* dout, const float* ckpt, const float* seg,
+                  float* gseg, void* du, void* ddelta, void* dz, long long lddz, float* dA, float* dB, float* dC,
+                  float* dD, float* dbias, int B, int S, int C, int N, long long ldz, int softplus, int groups,
+                  cudaStream_t st);
 
 // ------------------------------------------------------------------- MoE bookkeeping
 int kmoe_moe_max_rows(int n_assign, int E);

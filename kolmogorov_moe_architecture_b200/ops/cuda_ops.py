@@ -394,9 +394,9 @@ class _Scan(torch.autograd.Function):
         Df = D.float().contiguous() if D is not None else None
         bf = dt_bias.float().contiguous() if dt_bias is not None else None
         need = any(ctx.needs_input_grad)
-        out, ckpt = K.scan_fwd(u, delta, z, Af, Bf, Cf, Df, bf, softplus, need)
-        _count()
-        ctx.save_for_backward(u, delta, z, Af, Bf, Cf, Df, bf, ckpt)
+        out, ckpt, seg = K.scan_fwd(u, delta, z, Af, Bf, Cf, Df, bf, softplus, need)
+        _count(2 if seg.numel() else 1)
+        ctx.save_for_backward(u, delta, z, Af, Bf, Cf, Df, bf, ckpt, seg)
         ctx.softplus = softplus
         ctx.dtypes = (A.dtype, Bm.dtype, Cm.dtype, D.dtype if D is not None else None,
                       dt_bias.dtype if dt_bias is not None else None)
@@ -404,10 +404,10 @@ class _Scan(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
-        u, delta, z, Af, Bf, Cf, Df, bf, ckpt = ctx.saved_tensors
+        u, delta, z, Af, Bf, Cf, Df, bf, ckpt, seg = ctx.saved_tensors
         du, dd, dz, dA, dB, dC, dD, dbias = K.scan_bwd(u, delta, z, Af, Bf, Cf, Df, bf, dout.contiguous(),
-                                                       ckpt, ctx.softplus)
-        _count()
+                                                       ckpt, seg, ctx.softplus)
+        _count(2 if seg.numel() else 1)
         a_dt, b_dt, c_dt, d_dt, bias_dt = ctx.dtypes
         return (du, dd, dA.to(a_dt), dB.to(b_dt), dC.to(c_dt), dD.to(d_dt) if Df is not None else None,
                 dz if z is not None else None, dbias.to(bias_dt) if bf is not None else None, None)
