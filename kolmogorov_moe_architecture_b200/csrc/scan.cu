@@ -141,7 +141,7 @@ scan_fwd_kernel(ScanArgs a, __nv_bfloat16* __restrict__ out, float* __restrict__
       const float dtu = dt * uu;
       const float4* Bq = reinterpret_cast<const float4*>(&st[s].B[i][0]);
       const float4* Cq = reinterpret_cast<const float4*>(&st[s].C[i][0]);
-      float y = 0.f;
+      float ys[4] = {0.f, 0.f, 0.f, 0.f};                // four partial sums: no 16-long dependent chain
 #pragma unroll
       for (int n4 = 0; n4 < 4; ++n4) {
         const float4 bq = Bq[n4];
@@ -155,13 +155,13 @@ scan_fwd_kernel(ScanArgs a, __nv_bfloat16* __restrict__ out, float* __restrict__
         for (int j = 0; j < 4; ++j) {
           const int n = n4 * 4 + j;
           h[n] = s_ex2(dt * An[n]) * h[n] + dtu * bv[j];
-          if (MODE == 1) y += cv[j] * h[n];
+          if (MODE == 1) ys[j] += cv[j] * h[n];
         }
       }
       if (MODE == 0) {
         sdt += dt;
       } else {
-        y += Dc * uu;
+        float y = (ys[0] + ys[1]) + (ys[2] + ys[3]) + Dc * uu;
         if (has_z) {
           const float zv = s_bf2f(st[s].z[i][tid]);
           y *= zv * s_sigmoid(zv);
@@ -414,16 +414,17 @@ scan_bwd_kernel(ScanArgs a, const __nv_bfloat16* __restrict__ dout, const float*
       }
       float dy = go, dzv = 0.f;
       if (has_z) {
-        float yp = Dc * u;
+        float yq[4] = {Dc * u, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int n = 0; n < SN; ++n) yp += Cv[n] * hc[n];
+        for (int n = 0; n < SN; ++n) yq[n & 3] += Cv[n] * hc[n];
+        const float yp = (yq[0] + yq[1]) + (yq[2] + yq[3]);
         const float zv = s_bf2f(sm.st[s].z[i][tid]);
         const float sgm = s_sigmoid(zv);
         dzv = go * yp * sgm * (1.f + zv * (1.f - sgm));
         dy = go * zv * sgm;
       }
       const float dtu = dt * u;
-      float sA = 0.f, sB = 0.f;                       // sum_n g h_prev a A2[n],  sum_n g B[n]
+      float sAq[4] = {0.f, 0.f, 0.f, 0.f}, sBq[4] = {0.f, 0.f, 0.f, 0.f};   // partial sums over the states
       float vals[2 * SN];
 #pragma unroll
       for (int n = 0; n < SN; ++n) {
@@ -431,12 +432,14 @@ scan_bwd_kernel(ScanArgs a, const __nv_bfloat16* __restrict__ dout, const float*
         const float gn = g[n] + Cv[n] * dy;            // dL/dh_t
         const float an = s_ex2(dt * An[n]);
         const float gh = gn * hp[n] * an;
-        sA += gh * An[n];
-        sB += gn * Bv[n];
+        sAq[n & 3] += gh * An[n];
+        sBq[n & 3] += gn * Bv[n];
         dAacc[n] += gh * dt;
         vals[n] = gn * dtu;                            // dB
         g[n] = gn * an;                                // handed to step t-1
       }
+      const float sA = (sAq[0] + sAq[1]) + (sAq[2] + sAq[3]);   // sum_n g h_prev a A2[n]
+      const float sB = (sBq[0] + sBq[1]) + (sBq[2] + sBq[3]);   // sum_n g B[n]
       float dd = sA * LN2 + u * sB;
       if (a.softplus) dd *= s_sigmoid(s_bf2f(sm.st[s].dt[i][tid]) + bias);
       dDacc += dy * u;
@@ -452,11 +455,11 @@ scan_bwd_kernel(ScanArgs a, const __nv_bfloat16* __restrict__ dout, const float*
           *reinterpret_cast<float4*>(row + k4 * 4) =
               make_float4(vals[k4 * 4], vals[k4 * 4 + 1], vals[k4 * 4 + 2], vals[k4 * 4 + 3]);
         __syncwarp();
-        float sum = 0.f;
+        float sq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int r = 0; r < 32; ++r) sum += sm.tr[warp][r][lane];
+        for (int r = 0; r < 32; ++r) sq[r & 3] += sm.tr[warp][r][lane];
         __syncwarp();
-        atomicAdd(&sm.acc[i][lane], sum);
+        atomicAdd(&sm.acc[i][lane], (sq[0] + sq[1]) + (sq[2] + sq[3]));
       }
 #pragma unroll
       for (int n = 0; n < SN; ++n) hc[n] = hp[n];
