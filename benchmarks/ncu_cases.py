@@ -4,7 +4,8 @@
 
 Each case holds well under 2 GB on the device, uses operands larger than L2 where the kernel is
 bandwidth-sensitive, and launches the kernel of interest a handful of times so that
-``ncu -k regex:<kernel> -s 2 -c 1`` captures a warm launch and the program then ends by itself.
+``ncu --clock-control none -k regex:<kernel> -s 2 -c 1 ...`` captures a warm launch and the program then
+ends by itself (one process, one GPU; without ``--clock-control none`` ncu would lock the GPU clocks).
 """
 import argparse
 import os

@@ -62,6 +62,10 @@ class TrainEngine:
         self.device = device or next(model.parameters()).device
         self.global_step = 0
         self.tokens_seen = 0
+        # optional instruments, all off by default:
+        self.timer = None            # a utils.profiling.PhaseTimer: forward / backward / optimizer phases
+        self.before_update = []      # callables(model) run after the last backward, before clipping and the update
+        self.token_weights = None    # (S,) weights: the loss becomes the position-weighted next-token loss
 
     def _to_device(self, t: torch.Tensor) -> torch.Tensor:
         if t.device == self.device:
@@ -82,14 +86,38 @@ class TrainEngine:
         if lo < 0 or hi >= vocab:
             raise ValueError(f"token ids must lie in [0, {vocab}); the batch has values from {lo} to {hi}")
 
+    def _phase(self, name: str):
+        import contextlib
+        return self.timer.phase(name) if self.timer is not None else contextlib.nullcontext()
+
+    def _weighted_loss(self, out, labels):
+        """Position-weighted next-token loss of the first head (reference: train_custom.py:715-752, which
+        replaces the model's loss by this one when token weighting is on)."""
+        import torch.nn.functional as F
+        logits = out["logits"][0] if isinstance(out["logits"], (list, tuple)) else out["logits"]
+        if logits.dim() == 4:
+            logits = logits[..., 0, :]
+        sl, tl = logits[..., :-1, :], labels[..., 1:]
+        ce = F.cross_entropy(sl.reshape(-1, sl.size(-1)).float(), tl.reshape(-1), reduction="none",
+                             ignore_index=-100).view(tl.shape)
+        w = self.token_weights[: ce.shape[1]].to(ce.device).unsqueeze(0)
+        return (ce * w).sum() / (tl != -100).sum().clamp(min=1)
+
     def _forward_backward(self, ids: torch.Tensor, labels: torch.Tensor, attention_mask=None):
-        if self.autocast_dtype is not None and self.device.type == "cuda":
-            with torch.autocast("cuda", dtype=self.autocast_dtype):
-                out = self.model(ids, attention_mask=attention_mask, labels=labels, return_logits=False)
-        else:
-            out = self.model(ids, attention_mask=attention_mask, labels=labels, return_logits=False)
-        loss = out["loss"] / self.grad_accum
-        loss.backward()
+        want_logits = self.token_weights is not None
+        with self._phase("forward"):
+            if self.autocast_dtype is not None and self.device.type == "cuda":
+                with torch.autocast("cuda", dtype=self.autocast_dtype):
+                    out = self.model(ids, attention_mask=attention_mask, labels=labels, return_logits=want_logits)
+            else:
+                out = self.model(ids, attention_mask=attention_mask, labels=labels, return_logits=want_logits)
+            if want_logits:
+                out = dict(out)
+                out["loss"] = self._weighted_loss(out, labels)
+                out.pop("logits", None)
+            loss = out["loss"] / self.grad_accum
+        with self._phase("backward"):
+            loss.backward()
         return out
 
     def _forward_backward_scaled(self, ids, labels, attention_mask, accum: int):
@@ -134,7 +162,10 @@ class TrainEngine:
             ld, lm = out["loss"].detach(), out["lm_loss"].detach()
             loss_acc = ld if loss_acc is None else loss_acc + ld
             lm_acc = lm if lm_acc is None else lm_acc + lm
-        gnorm = self.apply_update()
+        for fn in self.before_update:
+            fn(self.model)
+        with self._phase("optimizer"):
+            gnorm = self.apply_update()
         if self.lr_scheduler is not None:
             self.lr_scheduler.step()
         self.global_step += 1

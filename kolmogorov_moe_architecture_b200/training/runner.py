@@ -72,8 +72,10 @@ class RunSpec:
     entropy_threshold: float = 0.85
     constant_lr: bool = False              # train.py trains at a fixed LR (no scheduler)
     profile: bool = False
-    debug: bool = False
+    debug: bool = False                    # gradient-flow table, router statistics and stuck-norm check
     debug_interval: int = 100
+    use_8bit_optimizer: bool = False       # bitsandbytes AdamW8bit when installed (one process, AdamW family)
+    token_weight_decay: float = 0.0        # > 0: later positions weigh more in the loss (train_custom.py:690-707)
     use_lr_schedule: bool = True
     step_deadline_s: float = 0.0           # > 0 arms the step watchdog
     transport: Optional[str] = None
@@ -112,6 +114,15 @@ def _build_optimizer(spec: RunSpec, model, opt_cfg, train_cfg):
             (no_decay if (p.dim() < 2 or "norm" in n or "bias" in n) else decay).append(p)
     lr = train_cfg.get("max_lr", opt_cfg.get("adamw_lr", 3e-4)) * s
     on_cuda = next(model.parameters()).is_cuda
+    if spec.use_8bit_optimizer:
+        # reference: train_distributed.py:368-383 - AdamW8bit when bitsandbytes is there, else plain AdamW
+        try:
+            import bitsandbytes as bnb
+            print("Using 8-bit AdamW (4x memory savings for optimizer states)")
+            return bnb.optim.AdamW8bit([{"params": decay, "weight_decay": wd}, {"params": no_decay, "weight_decay": 0.0}],
+                                       lr=lr, betas=tuple(opt_cfg.get("adamw_betas", (0.9, 0.95))), eps=1e-8)
+        except ImportError:
+            print("Warning: bitsandbytes not available, falling back to standard AdamW")
     return torch.optim.AdamW([{"params": decay, "weight_decay": wd}, {"params": no_decay, "weight_decay": 0.0}],
                              lr=lr, betas=tuple(opt_cfg.get("adamw_betas", (0.9, 0.95))), fused=on_cuda)
 
@@ -275,6 +286,17 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
     amp = torch.bfloat16 if (spec.weights == "fp32_autocast" and use_cuda) else None
     engine = TrainEngine(model, optimizer, sched, train_cfg["gradient_clip_norm"], accum, amp, dp, device)
     engine.global_step, engine.tokens_seen = start_step, tokens_seen
+    if spec.use_8bit_optimizer and dp is not None and is_main:
+        print("--8bit-optimizer: ignored under the sharded plans (optimizer state is already split over the "
+              f"{world} ranks and kept in fp32 by their fused update kernels)")
+    twd = spec.token_weight_decay or (train_cfg.get("token_weight_decay", 0.0)
+                                      if train_cfg.get("use_token_weights", False) else 0.0)
+    if twd > 0:
+        pos = torch.arange(cfg.max_seq_len, dtype=torch.float32, device=device)
+        w = 1.0 + twd * pos / cfg.max_seq_len
+        engine.token_weights = w / w.mean()
+        if is_main:
+            print(f"  Token weighting: enabled (decay={twd})")
     if resume and os.path.isdir(resume) and not os.path.exists(os.path.join(resume, "model.pt")):
         # a checkpoint root: continue from the newest directory that every rank finished writing
         found = ckpt.latest_complete_checkpoint(resume, world)
@@ -309,11 +331,31 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
     save_every = spec.save_interval if spec.save_interval is not None else train_cfg["save_interval"]
     logger = MetricLogger(spec.jsonl, spec.wandb, spec.wandb_project, spec.wandb_run, y, rank=rank)
     timer = PhaseTimer(enabled=spec.profile, device=device)
+    if spec.profile:
+        engine.timer = timer                   # forward / backward / optimizer next to data / step
+    watch = None
+    if spec.debug:
+        from ..utils.fault import NormWatch, format_flow_report, gradient_flow_report
+        watch = NormWatch(model)
+        if is_main:
+            print(f"DEBUG MODE: diagnostics every {spec.debug_interval} steps; gradient statistics are summed "
+                  f"over the {world} rank(s) with one all-reduce")
+
+        def _flow(m):
+            # first step and then every debug_interval-th: which parameter groups received gradients
+            if engine.global_step == start_step or (engine.global_step + 1) % spec.debug_interval == 0:
+                rep = gradient_flow_report(m)
+                if is_main:
+                    print(format_flow_report(rep, world), flush=True)
+        engine.before_update.append(_flow)
     if spec.profile and os.environ.get("KMOE_NVTX_BLOCKS", "0") == "1":
         from ..utils.profiling import annotate_blocks
         annotate_blocks(model)                 # per-layer ranges for a timeline capture
     dog = StepWatchdog(spec.step_deadline_s, lambda idle: print(f"[watchdog] no step for {idle:.0f}s on rank {rank}",
                                                                 flush=True)).start() if spec.step_deadline_s > 0 else None
+    if spec.compile and is_main:
+        print("--compile: accepted for command-line compatibility and not used (the hot operations are this "
+              "library's fused CUDA kernels; nothing is traced)")
     if is_main:
         print(f"training: {total_steps} steps, {tokens_per_step:,} tokens/step, data={data_kind}, world={world}, "
               f"ep={cfg.ep_size}, weights={spec.weights}")
@@ -381,6 +423,13 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
                 logger.log(rec, step=step)
                 if is_main:
                     print(f"Step {step}/{total_steps} | Loss: {lv:.4f} | LR: {rec['lr']:.2e} | Tok/s: {tps:,.0f}", flush=True)
+            if spec.debug and step % spec.debug_interval == 0:
+                stats, collapsed, summary = check_router_collapse(model, entropy_threshold=spec.collapse_entropy_threshold)
+                stuck = watch.stuck(model) if watch is not None else []
+                if is_main:
+                    print(f"  [debug step {step}] router: {summary}; "
+                          f"norm weights still at their initial value: {len(stuck)}"
+                          + (f" (e.g. {stuck[0]})" if stuck else ""), flush=True)
             if spec.collapse_check_interval and step % spec.collapse_check_interval == 0:
                 stats, collapsed, summary = check_router_collapse(model, entropy_threshold=spec.collapse_entropy_threshold)
                 if stats:

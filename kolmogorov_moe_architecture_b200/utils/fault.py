@@ -227,6 +227,82 @@ def gradient_census(model) -> Dict[str, Dict[str, float]]:
     return groups
 
 
+_FLOW_GROUPS = ("attention", "embeddings", "expert_weights", "lm_head", "mod_router", "moe_router", "norms", "other")
+
+
+def _flow_group(name: str) -> str:
+    """Parameter categories of the distributed launcher's gradient-flow check
+    (reference: train_distributed.py:975-996)."""
+    n = name.lower()
+    if "mod_router" in n:
+        return "mod_router"
+    if "lm_head" in n:
+        return "lm_head"
+    if ".ffn.router" in n or ("moe" in n and "router" in n) or ".router." in n:
+        return "moe_router"
+    if "grouped_experts" in n or "local_experts" in n or (".ffn." in n and any(f".{w}" in n for w in ("w1", "w2", "w3"))):
+        return "expert_weights"
+    if "embed" in n:
+        return "embeddings"
+    if "norm" in n:
+        return "norms"
+    if any(k in n for k in ("q_proj", "k_proj", "v_proj", "o_proj", "qkv_proj")) or ("seq_layer" in n and "ffn" not in n):
+        return "attention"
+    return "other"
+
+
+@torch.no_grad()
+def gradient_flow_report(model, group=None) -> Dict[str, Dict[str, float]]:
+    """Per category: tensors, tensors that received a gradient, gradient norm; summed over the ranks of
+    ``group`` with ONE all-reduce (the reference issues one all-reduce for the table and one for the
+    counters, train_distributed.py:1005-1020).  Reads ``p.grad``, so it belongs between the backward pass
+    and the optimizer update (``TrainEngine.before_update``)."""
+    import torch.distributed as dist
+    stats = {g: [0.0, 0.0, 0.0] for g in _FLOW_GROUPS}
+    dev = None
+    sq_terms = {g: [] for g in _FLOW_GROUPS}
+    for name, p in model.named_parameters():
+        if not p.requires_grad:
+            continue
+        dev = dev or p.device
+        st = stats[_flow_group(name)]
+        st[0] += 1
+        if p.grad is not None:
+            st[1] += 1
+            sq_terms[_flow_group(name)].append(p.grad)
+    vec = torch.zeros(len(_FLOW_GROUPS) * 3, dtype=torch.float64, device=dev or "cpu")
+    for i, g in enumerate(_FLOW_GROUPS):
+        vec[3 * i], vec[3 * i + 1] = stats[g][0], stats[g][1]
+        if sq_terms[g]:
+            norms = torch._foreach_norm(sq_terms[g], 2.0)
+            vec[3 * i + 2] = torch.stack([x.double() for x in norms]).pow(2).sum()
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        v32 = vec.float() if vec.device.type == "cuda" else vec
+        dist.all_reduce(v32, group=group)
+        vec = v32.double()
+    out = {}
+    host = vec.tolist()                              # the one host read of the report
+    for i, g in enumerate(_FLOW_GROUPS):
+        if host[3 * i] > 0:
+            out[g] = {"tensors": int(host[3 * i]), "with_grad": int(host[3 * i + 1]),
+                      "norm": math.sqrt(max(host[3 * i + 2], 0.0))}
+    return out
+
+
+def format_flow_report(rep: Dict[str, Dict[str, float]], world: int = 1) -> str:
+    tot = sum(r["tensors"] for r in rep.values())
+    got = sum(r["with_grad"] for r in rep.values())
+    lines = [f"Gradient flow summary (aggregated across {world} ranks):",
+             f"  Total trainable params: {tot}", f"  Params with gradients: {got}",
+             f"  Params without gradients: {tot - got}", "By module:"]
+    for g, r in rep.items():
+        ok = "ok" if r["with_grad"] == r["tensors"] else "MISSING"
+        lines.append(f"  {g:20s}: {r['with_grad']:3d}/{r['tensors']:3d} grads, norm={r['norm']:.6f} {ok}")
+    lines.append("All parameters received gradients!" if got == tot
+                 else f"{tot - got} parameters did not receive gradients (this can make training plateau)")
+    return "\n".join(lines)
+
+
 class NormWatch:
     """Reports normalisation weights that are still exactly at their initial value after training steps."""
 

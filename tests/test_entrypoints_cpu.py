@@ -290,3 +290,31 @@ def test_elastic_launcher_environment_and_shrink_refusal(tmp_path, monkeypatch):
     assert "TORCH_SYMM_MEM_DISABLE_MULTICAST" in fault_injection_refusal({"NCCL_NVLS_ENABLE": "0"}, "p2p")
     assert fault_injection_refusal({"NCCL_NVLS_ENABLE": "0"}, "nccl") is None
     assert fault_injection_refusal({"NCCL_NVLS_ENABLE": "0", "TORCH_SYMM_MEM_DISABLE_MULTICAST": "1"}, None) is None
+
+
+def test_debug_mode_profile_phases_and_token_weighting(tiny_cfg, capsys):
+    """``--debug`` prints the gradient-flow table (every category got gradients) and the router / stuck-norm
+    line; ``--profile`` reports forward / backward / optimizer next to data / step; token weighting changes
+    the loss that is optimised."""
+    from kolmogorov_moe_architecture_b200.training.runner import RunSpec, run_training
+    base = os.path.join(tiny_cfg["dir"], "dbg")
+    common = dict(config_path=tiny_cfg["config"], steps=3, batch_size=2, data_mode="synthetic", checkpoint_format="C",
+                  save_interval=0, optimizer_family="adamw")
+    run_training(RunSpec(checkpoint_dir=os.path.join(base, "a"), jsonl=os.path.join(base, "a.jsonl"), debug=True,
+                         debug_interval=2, profile=True, use_8bit_optimizer=True, compile=True, **common))
+    out = capsys.readouterr().out
+    assert "Gradient flow summary (aggregated across 1 ranks)" in out
+    assert "All parameters received gradients!" in out and "MISSING" not in out
+    for group in ("attention", "expert_weights", "moe_router", "mod_router", "lm_head", "norms", "embeddings"):
+        assert f"  {group}" in out, group
+    assert "[debug step 2] router:" in out and "norm weights still at their initial value" in out
+    assert "bitsandbytes not available, falling back to standard AdamW" in out or "Using 8-bit AdamW" in out
+    assert "--compile: accepted" in out
+    rec = _records(os.path.join(base, "a.jsonl"))[3]
+    for k in ("time_data_ms", "time_step_ms", "time_forward_ms", "time_backward_ms", "time_optimizer_ms"):
+        assert rec[k] >= 0.0, k
+    run_training(RunSpec(checkpoint_dir=os.path.join(base, "b"), jsonl=os.path.join(base, "b.jsonl"),
+                         token_weight_decay=2.0, **common))
+    plain, weighted = _records(os.path.join(base, "a.jsonl")), _records(os.path.join(base, "b.jsonl"))
+    assert weighted[1]["loss"] != pytest.approx(plain[1]["loss"], rel=1e-6)
+    assert abs(weighted[1]["loss"] - plain[1]["lm_loss"]) < 1.0      # still a next-token loss near ln(vocab)

@@ -29,6 +29,10 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--synthetic", action="store_true")
     ap.add_argument("--checkpoint-dir", type=str, default=None)
+    ap.add_argument("--jsonl", type=str, default=None, help="also write metrics to this JSONL file")
+    ap.add_argument("--token-weight-decay", type=float, default=0.0,
+                    help="> 0: weigh later positions more in the loss (also: training.use_token_weights / "
+                         "training.token_weight_decay in the config)")
     a = ap.parse_args(argv)
     from kolmogorov_moe_architecture_b200.training.runner import RunSpec, run_training
     from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml, section
@@ -38,7 +42,8 @@ def main(argv=None):
                        "type") == "muon" else "adamw", checkpoint_format="C", checkpoint_dir=a.checkpoint_dir,
                    data_mode="synthetic" if a.synthetic else ("streaming" if a.no_packing else "packed"),
                    document_mask=bool(data.get("use_document_attention_mask")), wandb=a.wandb, gpu=a.gpu,
-                   profile=a.profile, compile=a.compile)
+                   profile=a.profile, compile=a.compile, jsonl=a.jsonl,
+                   token_weight_decay=a.token_weight_decay)
     return run_training(spec)
 
 

@@ -47,7 +47,8 @@ def main(argv=None):
                    checkpoint_dir=a.checkpoint_dir, grad_checkpoint=a.activation_checkpointing,
                    data_mode="synthetic" if a.synthetic else "streaming", debug=a.debug, debug_interval=a.debug_interval,
                    transport=a.transport, jsonl=a.jsonl, shard_params=a.shard_params or a.cpu_offload,
-                   cpu_offload=a.cpu_offload, async_checkpoint=a.async_checkpoint)
+                   cpu_offload=a.cpu_offload, async_checkpoint=a.async_checkpoint,
+                   use_8bit_optimizer=a.use_8bit_optimizer)
     return run_training(spec)
 
 
