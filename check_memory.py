@@ -1,5 +1,5 @@
 """GPU memory by phase for one training step of a configuration (counterpart of the reference's
-``check_memory.py`` / ``diagnose_memory.py``): allocated / reserved / peak after model creation,
+``check_memory.py``): allocated / reserved / peak after model creation,
 forward, backward and the optimizer step.
 
     python check_memory.py --config configs/training_1.5b.yaml [--batch-size 4] [--seq-len 2048]

@@ -112,7 +112,9 @@ def test_plateau_memory_debug_and_active_param_tools(tiny, capsys):
     assert rep, "router hooks recorded nothing"
     rows = check_memory.main(["--config", tiny["config"], "--seq-len", "32"])
     assert [r[0] for r in rows][:2] == ["start", "model"] and len(rows) >= 6
-    assert diagnose_memory.main(["--config", tiny["config"], "--seq-len", "32"])
+    rep = diagnose_memory.main([tiny["config"], "--seq-len", "32", "--steps", "6", "--accum", "2"])
+    assert rep["opt_steps"] == 3 and rep["leak"] is False
+    assert diagnose_memory.growth_per_step([1.0, 2.0, 2.5, 3.0, 3.5]) == pytest.approx(0.5)
     info = debug_training.inspect(tiny["checkpoint"], top=3)
     assert info["non_finite"] == [] and info["n_tensors"] > 10 and info["meta"]["global_step"] == 3
     analyze_active_params.main(["--preset", "test"])
