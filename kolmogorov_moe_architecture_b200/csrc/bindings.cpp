@@ -300,6 +300,32 @@ std::vector<Tensor> moe_plan(const Tensor& idx, const OptT& keep, int64_t E, int
   return {pos, row_src, counts, offsets, tile_group, meta};
 }
 
+Tensor moe_capacity_mask(const Tensor& idx, int64_t E, int64_t cap) {
+  c10::cuda::CUDAGuard guard(idx.device());
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kLong && idx.is_contiguous(), "idx must be contiguous int64");
+  Tensor keep = at::empty(idx.sizes(), idx.options().dtype(at::kBool));
+  if (idx.numel() > 0)
+    check(kmoe_moe_capacity_mask((const long long*)idx.data_ptr<int64_t>(), (int)idx.numel(), (int)E, (int)cap,
+                                 (unsigned char*)keep.data_ptr(), cur_stream()), "moe_capacity_mask");
+  return keep;
+}
+
+// expert indices [T, k] of the balanced assignment (non-differentiable; weights are gathered by the caller)
+Tensor moe_balanced_assign(const Tensor& probs, int64_t k, int64_t cap) {
+  c10::cuda::CUDAGuard guard(probs.device());
+  need_f32(probs, "probs");
+  TORCH_CHECK(probs.dim() == 2);
+  const int T = probs.size(0), E = probs.size(1);
+  Tensor taken = at::zeros({T, E}, probs.options().dtype(at::kByte));
+  Tensor counts = at::zeros({k + 1, E}, probs.options().dtype(at::kInt));
+  Tensor sel = at::empty({T, k}, probs.options().dtype(at::kLong));
+  if (T > 0)
+    check(kmoe_moe_balanced_assign(probs.data_ptr<float>(), taken.data_ptr<unsigned char>(), counts.data_ptr<int>(),
+                                   (long long*)sel.data_ptr<int64_t>(), T, E, (int)k, (int)cap, cur_stream()),
+          "moe_balanced_assign");
+  return sel;
+}
+
 Tensor moe_gather_rows(const Tensor& src, const Tensor& row_src, const OptT& assign_scale, const Tensor& meta,
                        int64_t div) {
   c10::cuda::CUDAGuard guard(src.device());
@@ -498,6 +524,33 @@ void muon_apply(Tensor buf, const Tensor& ortho, const Tensor& grad_ptrs, const 
                         (float)lr, (float)mu, (float)wd, nesterov ? 1 : 0, cur_stream()), "muon_apply");
 }
 
+// int8 block-quantised momentum (Muon8bit): returns (q [blocks, block] int8, scales [blocks, 1] fp32)
+std::tuple<Tensor, Tensor> q8_quant(const Tensor& x, int64_t block) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && (x.scalar_type() == at::kFloat || x.scalar_type() == at::kBFloat16),
+              "x must be a contiguous CUDA fp32 or bf16 tensor");
+  const int64_t n = x.numel(), nb = (n + block - 1) / block;
+  Tensor q = at::empty({nb, block}, x.options().dtype(at::kChar));
+  Tensor sc = at::empty({nb, 1}, x.options().dtype(at::kFloat));
+  check(kmoe_q8_quant(x.data_ptr(), x.scalar_type() == at::kBFloat16, (signed char*)q.data_ptr(), sc.data_ptr<float>(),
+                      n, (int)block, cur_stream()), "q8_quant");
+  return {q, sc};
+}
+
+// mu * dequant(q, scales) + g, shaped and typed like g
+Tensor q8_momentum(const Tensor& q, const Tensor& scales, const Tensor& g, double mu) {
+  c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(g.is_cuda() && g.is_contiguous() && (g.scalar_type() == at::kFloat || g.scalar_type() == at::kBFloat16));
+  TORCH_CHECK(q.scalar_type() == at::kChar && q.is_contiguous() && q.dim() == 2 && q.numel() >= g.numel());
+  need_f32(scales, "scales");
+  TORCH_CHECK(scales.numel() == q.size(0));
+  Tensor out = at::empty_like(g);
+  check(kmoe_q8_momentum((const signed char*)q.data_ptr(), scales.data_ptr<float>(), g.data_ptr(),
+                         g.scalar_type() == at::kBFloat16, out.data_ptr(), g.numel(), (int)q.size(1), (float)mu,
+                         cur_stream()), "q8_momentum");
+  return out;
+}
+
 // ------------------------------------------------------------- MXFP8
 // x: (..., C) bf16 with collapsing leading dims -> (q e4m3 same shape, scale chunks uint8)
 std::vector<Tensor> mx_quant_rows(const Tensor& x, const OptT& x2, const OptT& live_rows) {
@@ -667,6 +720,8 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("scan_fwd", &scan_fwd);
   m.def("scan_bwd", &scan_bwd);
   m.def("moe_plan", &moe_plan);
+  m.def("moe_capacity_mask", &moe_capacity_mask);
+  m.def("moe_balanced_assign", &moe_balanced_assign);
   m.def("moe_gather_rows", &moe_gather_rows);
   m.def("moe_combine", &moe_combine);
   m.def("moe_combine_dw", &moe_combine_dw);
@@ -683,6 +738,8 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("mod_combine_bwd", &mod_combine_bwd);
   m.def("muon_momentum", &muon_momentum);
   m.def("muon_apply", &muon_apply);
+  m.def("q8_quant", &q8_quant);
+  m.def("q8_momentum", &q8_momentum);
   m.def("mx_quant_rows", &mx_quant_rows);
   m.def("mx_quant_cols", &mx_quant_cols);
   m.def("gemm_mxfp8", &gemm_mxfp8);

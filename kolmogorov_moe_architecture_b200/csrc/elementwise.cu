@@ -490,6 +490,90 @@ __global__ void muon_apply_kernel(__nv_bfloat16* __restrict__ buf, const __nv_bf
 
 }  // namespace kmoe
 
+// ------------------------------------------------------------ int8 momentum (Muon8bit)
+// Block-wise absmax int8: q = rint(x / s * 127), s = max(|x| over the block, 1e-8); one CTA per block.
+// Elements past n (the padding of the last block) are written as 0.  Divisions are IEEE so that the
+// result matches the same formula evaluated by PyTorch.
+template <typename T>
+__device__ __forceinline__ float q8_load(const T* p, long long i);
+template <>
+__device__ __forceinline__ float q8_load<float>(const float* p, long long i) { return p[i]; }
+template <>
+__device__ __forceinline__ float q8_load<__nv_bfloat16>(const __nv_bfloat16* p, long long i) { return __bfloat162float(p[i]); }
+template <typename T>
+__device__ __forceinline__ void q8_store(T* p, long long i, float v);
+template <>
+__device__ __forceinline__ void q8_store<float>(float* p, long long i, float v) { p[i] = v; }
+template <>
+__device__ __forceinline__ void q8_store<__nv_bfloat16>(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16(v); }
+
+template <typename T>
+__global__ void q8_quant_kernel(const T* __restrict__ x, signed char* __restrict__ q, float* __restrict__ scales,
+                                long long n, int block) {
+  __shared__ float red[32];
+  const long long base = (long long)blockIdx.x * block;
+  float m = 0.f;
+  for (int i = threadIdx.x; i < block; i += blockDim.x) {
+    const long long j = base + i;
+    if (j < n) m = fmaxf(m, fabsf(q8_load<T>(x, j)));
+  }
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    v = warp_max(v);
+    if (threadIdx.x == 0) red[0] = fmaxf(v, 1e-8f);
+  }
+  __syncthreads();
+  const float s = red[0];
+  if (threadIdx.x == 0) scales[blockIdx.x] = s;
+  for (int i = threadIdx.x; i < block; i += blockDim.x) {
+    const long long j = base + i;
+    const float v = j < n ? q8_load<T>(x, j) : 0.f;
+    q[j] = (signed char)__float2int_rn(__fmul_rn(__fdiv_rn(v, s), 127.f));
+  }
+}
+
+// out = mu * dequant(q) + g   (the momentum update on the dequantised buffer), n elements
+template <typename T>
+__global__ void q8_momentum_kernel(const signed char* __restrict__ q, const float* __restrict__ scales,
+                                   const T* __restrict__ g, T* __restrict__ out, long long n, int block, float mu) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    // the stored buffer is rounded to the parameter's type before the update, as the eager path does
+    float d = __fmul_rn(__fdiv_rn((float)q[i], 127.f), scales[i / block]);
+    T tmp;
+    q8_store<T>(&tmp, 0, d);
+    d = q8_load<T>(&tmp, 0);
+    q8_store<T>(&tmp, 0, __fmul_rn(d, mu));
+    d = q8_load<T>(&tmp, 0);
+    q8_store<T>(out, i, d + q8_load<T>(g, i));
+  }
+}
+
+extern "C" int kmoe_q8_quant(const void* x, int is_bf16, signed char* q, float* scales, long long n, int block,
+                             cudaStream_t st) {
+  if (block < 32 || n <= 0) return -1;
+  const long long nb = (n + block - 1) / block;
+  if (is_bf16)
+    q8_quant_kernel<__nv_bfloat16><<<(unsigned)nb, 256, 0, st>>>((const __nv_bfloat16*)x, q, scales, n, block);
+  else
+    q8_quant_kernel<float><<<(unsigned)nb, 256, 0, st>>>((const float*)x, q, scales, n, block);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_q8_momentum(const signed char* q, const float* scales, const void* g, int is_bf16, void* out,
+                                long long n, int block, float mu, cudaStream_t st) {
+  if (block < 32 || n <= 0) return -1;
+  const int grid = grid_for(n, 256);
+  if (is_bf16)
+    q8_momentum_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(q, scales, (const __nv_bfloat16*)g, (__nv_bfloat16*)out, n,
+                                                            block, mu);
+  else
+    q8_momentum_kernel<float><<<grid, 256, 0, st>>>(q, scales, (const float*)g, (float*)out, n, block, mu);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 extern "C" int kmoe_muon_momentum(void* buf, const long long* grad_ptrs, float* sumsq, int n_mat, long long numel,
                                   float mu, cudaStream_t st) {
   if (numel % 8 || n_mat <= 0 || n_mat > 65535) return -1;

@@ -74,6 +74,14 @@ int kmoe_muon_momentum(void* buf, const long long* grad_ptrs, float* sumsq, int 
 int kmoe_muon_apply(void* buf, const void* ortho, const long long* grad_ptrs, const long long* param_ptrs, int n_mat,
                     long long numel, float lr, float mu, float wd, int nesterov, cudaStream_t st);
 
+// int8 momentum of Muon8bit: blocks of `block` elements, q = rint(x / s * 127) with s = max(absmax, 1e-8).
+// x / g / out are fp32 or bf16 (is_bf16); q holds ceil(n / block) * block bytes, scales one float per block.
+//   quant   : x -> (q, scales)
+//   momentum: out = mu * dequant(q, scales) + g
+int kmoe_q8_quant(const void* x, int is_bf16, signed char* q, float* scales, long long n, int block, cudaStream_t st);
+int kmoe_q8_momentum(const signed char* q, const float* scales, const void* g, int is_bf16, void* out, long long n,
+                     int block, float mu, cudaStream_t st);
+
 // ------------------------------------------------------------ MXFP8 (e4m3 + e8m0 1x32 block scales)
 // Scale factors live in 512-byte chunks, one per (128 operand rows, 128 reduction elements):
 //   chunk = (row / 128) * (K / 128) + k / 128,  byte = (row % 32) * 16 + ((row % 128) / 32) * 4 + (k % 128) / 32
@@ -154,6 +162,12 @@ int kmoe_scan_bwd(const void* u, const void* delta, const void* z, const float* 
 int kmoe_moe_max_rows(int n_assign, int E);
 int kmoe_moe_plan(const long long* idx, const unsigned char* keep, int n, int E, int max_rows, int expert_base,
                   int* pos, int* row_src, int* counts, int* offsets, int* tile_group, int* meta, cudaStream_t st);
+// keep[i] = assignment i is among the first `cap` of its expert in flat (token, slot) order
+int kmoe_moe_capacity_mask(const long long* idx, int n, int E, int cap, unsigned char* keep, cudaStream_t st);
+// greedy balanced top-k assignment, slot by slot (probs [T, E] fp32, taken [T, E] zeroed, counts [k + 1, E] zeroed,
+// sel [T, k] int64 out): see moe_balanced_slot_kernel
+int kmoe_moe_balanced_assign(const float* probs, unsigned char* taken, int* counts, long long* sel, int T, int E,
+                             int k, int cap, cudaStream_t st);
 int kmoe_moe_gather_rows(const void* src, const int* row_src, const float* assign_scale, const int* meta, void* dst,
                          int max_rows, int d, int div, cudaStream_t st);
 int kmoe_moe_combine(const void* Y, const int* pos, const float* w, void* out, int T, int k, int d, cudaStream_t st);

@@ -82,6 +82,70 @@ moe_plan_kernel(const long long* __restrict__ idx, const unsigned char* __restri
   }
 }
 
+// Capacity with drops for token choice: keep[i] = 1 iff assignment i is among the first `cap` assignments of its
+// expert in flat (token, slot) order.  Same single-block stable ranking as the plan kernel.
+__global__ void __launch_bounds__(PLAN_THREADS)
+moe_capacity_mask_kernel(const long long* __restrict__ idx, int n, int E, int cap, unsigned char* __restrict__ keep) {
+  extern __shared__ int sh[];     // hist[PLAN_THREADS][E]
+  int* hist = sh;
+  const int tid = threadIdx.x;
+  const int seg = (n + PLAN_THREADS - 1) / PLAN_THREADS;
+  const int lo = min(tid * seg, n), hi = min(lo + seg, n);
+  for (int e = 0; e < E; ++e) hist[tid * E + e] = 0;
+  for (int i = lo; i < hi; ++i) {
+    const int e = (int)idx[i];
+    if (e >= 0 && e < E) hist[tid * E + e]++;
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += PLAN_THREADS) {
+    int run = 0;
+    for (int t = 0; t < PLAN_THREADS; ++t) {
+      const int v = hist[t * E + e];
+      hist[t * E + e] = run;
+      run += v;
+    }
+  }
+  __syncthreads();
+  for (int i = lo; i < hi; ++i) {
+    const int e = (int)idx[i];
+    keep[i] = (e >= 0 && e < E && hist[tid * E + e]++ < cap) ? 1 : 0;
+  }
+}
+
+// One slot of the balanced token-choice assignment: every token takes its most probable expert among those it
+// has not used and that were not full (count >= cap) when the slot began; a token whose unused experts are all
+// full takes its most probable unused expert regardless.  One warp per token; ties go to the lower index.
+//   taken [T, E] uint8 (in/out), counts_in [E] (read), counts_out [E] (incremented), sel [T] int64
+__global__ void moe_balanced_slot_kernel(const float* __restrict__ probs, unsigned char* __restrict__ taken,
+                                         const int* __restrict__ counts_in, int* __restrict__ counts_out,
+                                         long long* __restrict__ sel, long long sel_stride, int T, int E, int cap) {
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < T; t += warps) {
+    float best = -INFINITY, fb = -INFINITY;
+    int bi = E, fi = E;
+    for (int e = lane; e < E; e += 32) {
+      if (taken[(size_t)t * E + e]) continue;
+      const float p = probs[(size_t)t * E + e];
+      if (p > fb) { fb = p; fi = e; }
+      if (counts_in[e] < cap && p > best) { best = p; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o), of = __shfl_xor_sync(0xffffffffu, fb, o);
+      const int obi = __shfl_xor_sync(0xffffffffu, bi, o), ofi = __shfl_xor_sync(0xffffffffu, fi, o);
+      if (ob > best || (ob == best && obi < bi)) { best = ob; bi = obi; }
+      if (of > fb || (of == fb && ofi < fi)) { fb = of; fi = ofi; }
+    }
+    const int pick = bi < E ? bi : (fi < E ? fi : 0);
+    if (lane == 0) {
+      sel[(size_t)t * sel_stride] = pick;
+      taken[(size_t)t * E + pick] = 1;
+      atomicAdd(&counts_out[pick], 1);
+    }
+  }
+}
+
 // dst[row] = scale(row) * src[row_src[row] / div]  (zero for padding rows), rows < meta[1].
 //   row_scale: optional fp32 per *assignment* multiplier (indexed by row_src), used by the
 //   backward of the combine: dY[row] = w[assignment] * dout[token].
@@ -200,6 +264,34 @@ extern "C" int kmoe_moe_plan(const long long* idx, const unsigned char* keep, in
   }
   moe_plan_kernel<<<1, PLAN_THREADS, smem, st>>>(idx, keep, n, E, max_rows, expert_base, pos, row_src, counts,
                                                  offsets, tile_group, meta);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_moe_capacity_mask(const long long* idx, int n, int E, int cap, unsigned char* keep,
+                                      cudaStream_t st) {
+  const size_t smem = (size_t)PLAN_THREADS * E * sizeof(int);
+  if (smem > 200 * 1024) return -1;
+  static size_t attr_set = 0;
+  if (smem > 48 * 1024 && smem > attr_set) {
+    if (cudaFuncSetAttribute(moe_capacity_mask_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return -3;
+    attr_set = smem;
+  }
+  moe_capacity_mask_kernel<<<1, PLAN_THREADS, smem, st>>>(idx, n, E, cap, keep);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// `counts` holds k + 1 rows of E ints, zeroed by the caller: row j = expert loads at the start of slot j.
+extern "C" int kmoe_moe_balanced_assign(const float* probs, unsigned char* taken, int* counts, long long* sel, int T,
+                                        int E, int k, int cap, cudaStream_t st) {
+  for (int j = 0; j < k; ++j) {
+    if (j > 0) cudaMemcpyAsync(counts + (size_t)(j + 1) * E, counts + (size_t)j * E, E * sizeof(int),
+                               cudaMemcpyDeviceToDevice, st);
+    // slot j reads row j and accumulates the loads after the slot into row j + 1 (which starts as a copy of row j)
+    moe_balanced_slot_kernel<<<148 * 4, 256, 0, st>>>(probs, taken, counts + (size_t)j * E,
+                                                      counts + (size_t)(j + 1) * E, sel + j, k, T, E, cap);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

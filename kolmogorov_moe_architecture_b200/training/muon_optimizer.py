@@ -225,7 +225,19 @@ class Muon8bit(Optimizer):
         self.use_8bit = use_8bit
 
     @staticmethod
+    def _on_kernels(t: torch.Tensor) -> bool:
+        """CUDA fp32 / bf16 tensors take the block-quantisation kernels (one pass each way) instead of the
+        pad / view / amax / round chain below."""
+        if not (t.is_cuda and t.dtype in (torch.float32, torch.bfloat16) and t.numel() > 0):
+            return False
+        from ..ops import ext_available
+        return ext_available()
+
+    @staticmethod
     def _quantize_to_8bit(t: torch.Tensor, block_size: int = 2048):
+        if Muon8bit._on_kernels(t):
+            q, scales = torch.ops.kmoe.q8_quant(t.contiguous(), block_size)
+            return q, scales, t.shape, t.numel()
         shape, flat = t.shape, t.flatten()
         n = flat.numel()
         if n % block_size:
@@ -268,6 +280,9 @@ class Muon8bit(Optimizer):
                 if group["use_8bit"]:
                     if "momentum_quantized" not in st:
                         buf = g.clone()
+                    elif self._on_kernels(g) and g.is_contiguous():
+                        # dequantise, decay and add the gradient in one pass
+                        buf = torch.ops.kmoe.q8_momentum(st["momentum_quantized"], st["momentum_scales"], g, mu)
                     else:
                         buf = self._dequantize_from_8bit(st["momentum_quantized"], st["momentum_scales"],
                                                          st["momentum_shape"], st["momentum_numel"]).to(g)

@@ -225,3 +225,114 @@ def test_param_sharded_plan_matches_replicated_2gpus(tmp_path):
                         "--master-addr", "127.0.0.1", "--master-port", "29585", str(f)],
                        env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "FSDP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+DEFAULT_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["KMOE_ROOT"])
+from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig, MoETransformer
+from kolmogorov_moe_architecture_b200.ops import cuda_ops
+from kolmogorov_moe_architecture_b200.parallel.zero import ShardedDataParallel
+from kolmogorov_moe_architecture_b200.training.engine import TrainEngine
+rank = int(os.environ["RANK"]); ws = int(os.environ["WORLD_SIZE"]); torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+cfg = AdvancedMoEConfig(vocab_size=512, d_model=128, n_layers=4, n_heads=2, n_kv_heads=1, head_dim=64, d_ff=256,
+                        d_ff_expert=128, n_experts=4, moe_layers=(1, 2), mamba_layers=(1,), max_seq_len=64,
+                        n_pred_tokens=2, aux_loss_weights=(1.0, 0.5), mamba_moe_mode="moe_ffn", dropout=0.0,
+                        attention_dropout=0.0, residual_dropout=0.0)
+out, used = {}, {}
+for transport in ("nccl", None):                      # None = what the benchmark runs: the library's own default
+    torch.manual_seed(0)
+    model = MoETransformer(cfg, verbose=False).cuda().to(torch.bfloat16)
+    dp = ShardedDataParallel(model, optimizer_kind="muon", lr=2e-3, adamw_lr=2e-3, transport=transport)
+    eng = TrainEngine(model, dp.optimizer, grad_clip=1.0, dp=dp)
+    g = torch.Generator().manual_seed(5 + rank)
+    for s in range(3):
+        eng.step(torch.randint(0, 512, (2, 64), generator=g).cuda())
+    cuda_ops.check_status()
+    out[transport] = torch.cat([p.detach().float().flatten() for p in model.parameters()])
+    used[transport] = (dp.transport, bool(getattr(dp, "_chunks", None)),
+                       int(dp.p2p.grad_mc != 0) if dp.transport == "p2p" else 0)
+err = (out["nccl"] - out[None]).abs().max().item()
+ref = out["nccl"].abs().max().item()
+mine = out[None].clone(); other = mine.clone(); dist.broadcast(other, 0)
+assert torch.equal(mine, other), "ranks diverged"
+assert err < 2e-2 * ref, (err, ref)
+if rank == 0: print("DEFAULT_OK", ws, err, used[None])
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.parametrize("n", [4, 8])
+def test_default_transport_matches_nccl_at_bench_rank_counts(tmp_path, n):
+    """The configuration the benchmark runs at 4 and 8 GPUs - no environment switches, so from 4 ranks the
+    switch's in-fabric reduction and the reduce-scatter overlapped with the backward pass - against the NCCL
+    transport: parameters after three steps agree, replicas are bit-identical."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    f = tmp_path / "default_worker.py"
+    f.write_text(DEFAULT_WORKER)
+    env = dict(os.environ, KMOE_ROOT=ROOT, KMOE_STRICT="1")
+    for k in ("KMOE_RS_OVERLAP", "KMOE_RS_CHUNKS", "KMOE_MULTIMEM", "NCCL_NVLS_ENABLE"):
+        env.pop(k, None)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", "29587", str(f)],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "DEFAULT_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("DEFAULT_OK")][0]
+    assert "'p2p', True, 1" in line, f"expected the peer transport with overlap and the multicast address: {line}"
+
+
+CURVE_WORKER = r'''
+import json, os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["KMOE_ROOT"])
+from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig, MoETransformer
+from kolmogorov_moe_architecture_b200.ops import cuda_ops
+from kolmogorov_moe_architecture_b200.parallel.zero import ShardedDataParallel
+from kolmogorov_moe_architecture_b200.training.engine import TrainEngine
+rank = int(os.environ["RANK"]); ws = int(os.environ["WORLD_SIZE"]); torch.cuda.set_device(rank)
+n = int(os.environ["KMOE_GLOBAL_RANKS"])              # the global batch is n micro-batches of 2 sequences
+if ws > 1:
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+cfg = AdvancedMoEConfig(vocab_size=512, d_model=128, n_layers=4, n_heads=2, n_kv_heads=1, head_dim=64, d_ff=256,
+                        d_ff_expert=128, n_experts=4, moe_layers=(1, 2), mamba_layers=(1,), max_seq_len=64,
+                        n_pred_tokens=2, aux_loss_weights=(1.0, 0.5), mamba_moe_mode="moe_ffn", dropout=0.0,
+                        attention_dropout=0.0, residual_dropout=0.0)
+torch.manual_seed(0)
+model = MoETransformer(cfg, verbose=False).cuda().to(torch.bfloat16)
+dp = ShardedDataParallel(model, optimizer_kind="muon", lr=2e-3, adamw_lr=2e-3)
+eng = TrainEngine(model, dp.optimizer, grad_clip=1.0, grad_accum=(n if ws == 1 else 1), dp=dp)
+g = torch.Generator().manual_seed(11)
+losses = []
+for s in range(5):
+    batch = torch.randint(0, 512, (2 * n, 64), generator=g)      # the same global batch in both runs
+    mine = batch if ws == 1 else batch[2 * rank: 2 * rank + 2]
+    l = eng.step(mine.cuda()).loss.detach().float().reshape(1)
+    if ws > 1:
+        dist.all_reduce(l); l /= ws
+    losses.append(float(l.item()))
+cuda_ops.check_status()
+if rank == 0: print("CURVE", json.dumps(losses))
+if ws > 1: dist.destroy_process_group()
+'''
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_loss_curve_one_gpu_equals_n_gpus(tmp_path, n):
+    """The same global batch, once as n accumulated micro-batches on one GPU and once as one micro-batch on
+    each of n GPUs: the loss curves agree step by step."""
+    import json
+    if not torch.cuda.is_available() or torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    f = tmp_path / "curve_worker.py"
+    f.write_text(CURVE_WORKER)
+    env = dict(os.environ, KMOE_ROOT=ROOT, KMOE_STRICT="1", KMOE_GLOBAL_RANKS=str(n))
+    curves = {}
+    for ranks in (1, n):
+        r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}",
+                            "--master-addr", "127.0.0.1", "--master-port", str(29589 + ranks), str(f)],
+                           env=env, capture_output=True, text=True, timeout=900)
+        assert r.returncode == 0 and "CURVE" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+        curves[ranks] = json.loads([l for l in r.stdout.splitlines() if l.startswith("CURVE")][0][6:])
+    for a, b in zip(curves[1], curves[n]):
+        assert abs(a - b) < 2e-2 * abs(a), (curves[1], curves[n])

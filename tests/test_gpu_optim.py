@@ -103,3 +103,45 @@ def test_barrier_wait_runs_out_and_reports_status():
     cuda_ops.check_status()                                       # cleared by the report
     x = torch.ones(1024, device="cuda")
     assert float((x * 2).sum()) == 2048.0                         # the context still works
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,block", [(5000, 2048), (4096, 2048), (100, 64)])
+def test_int8_momentum_kernels_equal_the_formulas(dtype, n, block):
+    """Block-wise absmax int8 quantisation of the Muon8bit momentum and the fused dequantise-decay-add pass
+    against the same formulas in plain PyTorch: identical int8 codes, scales and updated buffer."""
+    torch.manual_seed(0)
+    x = (torch.randn(n, device="cuda") * 3).to(dtype)
+    q, sc = torch.ops.kmoe.q8_quant(x, block)
+    flat = torch.nn.functional.pad(x.flatten(), (0, (-n) % block)).view(-1, block)
+    sc_ref = flat.abs().amax(dim=1, keepdim=True).clamp(min=1e-8).float()
+    q_ref = (flat.float() / sc_ref * 127).round().to(torch.int8)
+    assert torch.equal(sc, sc_ref) and torch.equal(q, q_ref)
+    g = torch.randn(n, device="cuda").to(dtype)
+    out = torch.ops.kmoe.q8_momentum(q, sc, g, 0.95)
+    ref = ((q_ref.float() / 127) * sc_ref).flatten()[:n].to(dtype)
+    ref.mul_(0.95).add_(g)
+    assert torch.equal(out, ref)
+
+
+def test_muon8bit_step_on_kernels_matches_eager_path(monkeypatch):
+    from kolmogorov_moe_architecture_b200.training import muon_optimizer as mo
+    torch.manual_seed(1)
+    shapes = [(128, 192), (64,), (3, 64, 128)]
+    res = {}
+    for kernels in (True, False):
+        ps = [torch.nn.Parameter((torch.randn(*s, device="cuda", generator=None) * 0.1).bfloat16()) for s in shapes]
+        torch.manual_seed(1)
+        for p in ps:
+            p.data.copy_((torch.randn_like(p, dtype=torch.float32) * 0.1).bfloat16())
+        if not kernels:
+            monkeypatch.setattr(mo.Muon8bit, "_on_kernels", staticmethod(lambda t: False))
+        opt = mo.Muon8bit(ps, lr=1e-2, block_size=256)
+        for step in range(3):
+            torch.manual_seed(10 + step)
+            for p in ps:
+                p.grad = torch.randn_like(p, dtype=torch.float32).bfloat16()
+            opt.step()
+        res[kernels] = [p.detach().float().clone() for p in ps]
+    for a, b in zip(res[True], res[False]):
+        assert torch.allclose(a, b, atol=1e-3, rtol=0), (a - b).abs().max()
