@@ -76,9 +76,16 @@ def build(force: bool = False, ptxas_v: bool = False, verbose: bool = True) -> s
             list(ex.map(lambda c: _run(c, quiet=not ptxas_v), jobs))
     if jobs or not os.path.exists(OUT):
         tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
-        _run([CXX, "-shared", "-o", OUT, *objs, f"-L{tlib}", "-lc10", "-ltorch_cpu", "-ltorch",
-              "-lc10_cuda", "-ltorch_cuda", "-L/usr/local/cuda/lib64", "-lcudart",
+        # The C++ runtime must be the process-wide shared one.  A toolchain whose search path only offers
+        # libstdc++.a would otherwise put a private copy of the runtime into the library; its stream / locale
+        # state is then not the one libtorch initialised, and the first formatted error message (TORCH_CHECK
+        # with a number in it) crashes instead of raising.  Hence: no implicit -lstdc++, the shared object by name.
+        _run([CXX, "-shared", "-nostdlib++", "-o", OUT, *objs, f"-L{tlib}", "-lc10", "-ltorch_cpu", "-ltorch",
+              "-lc10_cuda", "-ltorch_cuda", "-L/usr/local/cuda/lib64", "-lcudart", "-l:libstdc++.so.6", "-lm",
               f"-Wl,-rpath,{tlib}", "-Wl,-rpath,/usr/local/cuda/lib64"])
+        private = _run(["nm", "-D", "--defined-only", OUT], quiet=True).count("_ZNSt6locale5_Impl")
+        if private:
+            raise RuntimeError(f"{OUT} contains a private copy of the C++ runtime ({private} std::locale symbols)")
         if verbose:
             print(f"[build_ext] linked {OUT}")
     return OUT

@@ -705,7 +705,11 @@ void ep_move(const Tensor& slots, Tensor packed, const Tensor& meta_in, const Te
 
 }  // namespace
 
+// error-path self test: raises the same way a failed kernel entry point does (no device needed)
+void raise_check(int64_t code) { check((int)code, "self_test"); }
+
 TORCH_LIBRARY(kmoe, m) {
+  m.def("raise_check", &raise_check);
   m.def("gemm", &gemm);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

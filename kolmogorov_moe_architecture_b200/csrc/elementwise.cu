@@ -541,7 +541,8 @@ __global__ void q8_momentum_kernel(const signed char* __restrict__ q, const floa
                                    const T* __restrict__ g, T* __restrict__ out, long long n, int block, float mu) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     // the stored buffer is rounded to the parameter's type before the update, as the eager path does
-    float d = __fmul_rn(__fdiv_rn((float)q[i], 127.f), scales[i / block]);
+    // q / 127 as PyTorch evaluates a division by a host scalar: a multiplication by its reciprocal
+    float d = __fmul_rn(__fmul_rn((float)q[i], 1.0f / 127.0f), scales[i / block]);
     T tmp;
     q8_store<T>(&tmp, 0, d);
     d = q8_load<T>(&tmp, 0);

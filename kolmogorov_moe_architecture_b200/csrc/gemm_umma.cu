@@ -16,6 +16,8 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -920,7 +922,9 @@ extern "C" void kmoe_gemm_clear_tensormap_cache(void) {
 
 extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
   using namespace kmoe;
-  if (d->K % 8 != 0 || d->N % 8 != 0) return -1;
+  // 16-byte rows for TMA: the reduction length only matters for an operand whose rows run along it
+  if (d->N % 8 != 0) return -1;
+  if ((d->a_major == KMOE_MAJOR_K || d->b_major == KMOE_MAJOR_K) && d->K % 8 != 0) return -1;
   if (d->K <= 0 || d->M <= 0 || d->N <= 0) return -2;
   if (d->c_row_ptr != nullptr && (d->out_f32 || d->epilogue != KMOE_EPI_STORE)) return -3;
   if (d->k_split != 0 && (d->k_split % BK || d->k_split <= 0 || d->k_split >= d->K || d->B2 == nullptr ||

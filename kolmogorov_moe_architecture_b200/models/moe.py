@@ -43,27 +43,11 @@ class Router(nn.Module):
 
     @staticmethod
     def _balanced_topk_assignment(probs: torch.Tensor, top_k: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        """Greedy per-slot assignment under a global per-expert capacity of
-        ``(T * k) // E``: in slot j every token takes its best expert that was not
-        already full at the start of the slot and that it has not used
-        (reference: moe.py:353-421).  Runs without host synchronisation."""
-        T, E = probs.shape
-        cap = max((T * top_k) // E, 1)
-        counts = torch.zeros(E, dtype=torch.long, device=probs.device)
-        avail = probs.clone()
-        sel, wts = [], []
-        neg = float("-inf")
-        for _ in range(top_k):
-            masked = avail.masked_fill((counts >= cap)[None, :], neg)
-            best_p, best_e = masked.max(dim=-1)
-            fb_e = avail.argmax(dim=-1)
-            best_e = torch.where(best_p == neg, fb_e, best_e)
-            sel.append(best_e)
-            wts.append(probs.gather(1, best_e[:, None]).squeeze(1))
-            counts = counts + torch.bincount(best_e, minlength=E)
-            avail = avail.scatter(1, best_e[:, None], neg)
-        idx = torch.stack(sel, dim=1)
-        w = torch.stack(wts, dim=1)
+        """Greedy per-slot assignment under a global per-expert capacity of ``(T * k) // E`` (reference:
+        moe.py:353-421).  The indices come from ``ops.balanced_assign`` (one kernel per slot on CUDA, no host
+        synchronisation); the weights are gathered from ``probs`` here so they stay differentiable."""
+        idx = ops.balanced_assign(probs, top_k)
+        w = probs.gather(1, idx)
         return w / (w.sum(dim=-1, keepdim=True) + 1e-9), idx
 
     def forward(self, hidden_states: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
@@ -155,13 +139,12 @@ class GroupedExpertsExpertChoice(nn.Module):
     def forward(self, x: torch.Tensor, expert_weights: torch.Tensor, token_indices: torch.Tensor) -> torch.Tensor:
         B, S, d = x.shape
         _, E, C = token_indices.shape
+        if self.activation == "swiglu":
+            # grouped kernels: gather, batched SwiGLU GEMMs over the experts, deterministic weighted combine
+            return ops.expert_choice_swiglu(x, self.w1, self.w2, self.w3, expert_weights, token_indices)
         flat_idx = token_indices.reshape(B, E * C)
         xin = torch.gather(x, 1, flat_idx.unsqueeze(-1).expand(-1, -1, d)).view(B, E, C, d)
-        if self.activation == "swiglu":
-            h = ops.swiglu(torch.matmul(xin, self.w1), torch.matmul(xin, self.w2))
-            y = torch.matmul(h, self.w3)
-        else:
-            y = torch.matmul(F.silu(torch.matmul(xin, self.w1)), self.w2)
+        y = torch.matmul(F.silu(torch.matmul(xin, self.w1)), self.w2)
         y = (y * expert_weights.unsqueeze(-1).to(y.dtype)).view(B, E * C, d)
         out = torch.zeros_like(x)
         return out.scatter_add(1, flat_idx.unsqueeze(-1).expand(-1, -1, d), y)

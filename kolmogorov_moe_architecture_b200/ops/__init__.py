@@ -151,7 +151,32 @@ def expert_choice_route(logits, capacity):
 
 topk_softmax_route = eager.topk_softmax_route
 moe_aux_loss = eager.moe_aux_loss
-capacity_keep_mask = eager.capacity_keep_mask
+
+
+def capacity_keep_mask(idx, n_experts, capacity):
+    """Token-choice capacity with drops: the first ``capacity`` assignments of every expert are kept."""
+    if _use_cuda(idx):
+        from . import cuda_ops
+        return cuda_ops.capacity_keep_mask(idx, n_experts, capacity)
+    return eager.capacity_keep_mask(idx, n_experts, capacity)
+
+
+def balanced_assign(probs, top_k):
+    """Expert indices (T, k) of the greedy capacity-balanced token-choice assignment."""
+    if _use_cuda(probs):
+        from . import cuda_ops
+        return cuda_ops.balanced_assign(probs, top_k)
+    return eager.balanced_assign(probs, top_k)
+
+
+def expert_choice_swiglu(x, w1, w2, w3, wts, tok):
+    """Expert-choice expert FFN (x (B, S, d); wts, tok (B, E, C))."""
+    if _use_cuda(x):
+        from . import cuda_ops
+        return cuda_ops.expert_choice_swiglu(x, w1, w2, w3, wts, tok)
+    return eager.expert_choice_swiglu(x, w1, w2, w3, wts, tok)
+
+
 rope_tables = eager.rope_tables
 doc_start_from_ids = eager.doc_start_from_ids
 doc_start_to_mask = eager.doc_start_to_mask

@@ -507,6 +507,107 @@ def grouped_swiglu(x, w1, w2, w3, idx, weights, keep=None, moe_dtype="bf16"):
     return _GroupedSwiGLU.apply(x, w1.contiguous(), w2.contiguous(), w3.contiguous(), idx, weights, keep)
 
 
+class _ExpertChoiceSwiGLU(torch.autograd.Function):
+    """Expert-choice expert FFN on the grouped kernels.  Every expert takes the same number of rows (its ``C``
+    picks from each of the ``B`` sequences), so the experts are a batched GEMM over ``E`` groups of ``B * C``
+    rows.  A token can be picked by several experts; the slots are turned into the token-choice bookkeeping
+    with ``k = E`` (``pos[t, e]`` = row of token t at expert e, or -1), which makes gather, the weighted
+    combine and their backward the same deterministic kernels the token-choice path uses (no scatter-add,
+    no atomics).  Reference: moe_arch/model/moe.py:533-673 (gather + bmm + Triton scatter)."""
+
+    @staticmethod
+    def forward(ctx, x2, w1, w2, w3, wts, tok, S):
+        # x2 (B*S, d); wts, tok (B, E, C); w1, w2 (E, d, f); w3 (E, f, d)
+        T, d = x2.shape
+        B, E, C = tok.shape
+        f = w1.shape[2]
+        BC = B * C
+        dev = x2.device
+        t_glob = tok + (torch.arange(B, device=dev) * S).view(B, 1, 1)             # token row in x2
+        a = t_glob * E + torch.arange(E, device=dev).view(1, E, 1)                 # assignment id = t * E + e
+        a_rows = a.permute(1, 0, 2).reshape(-1)                                     # rows ordered (e, b, c)
+        row_src = a_rows.to(torch.int32)
+        pos = torch.full((T * E,), -1, dtype=torch.int32, device=dev)
+        pos[a_rows] = torch.arange(E * BC, dtype=torch.int32, device=dev)
+        wdense = torch.zeros(T * E, dtype=torch.float32, device=dev)
+        wdense[a_rows] = wts.permute(1, 0, 2).reshape(-1).float()
+        meta = torch.full((2,), E * BC, dtype=torch.int32, device=dev)          # [1] = live rows
+        Xg = K.moe_gather_rows(x2.contiguous(), row_src, None, meta, E)
+        H = torch.empty(E * BC, f, dtype=x2.dtype, device=dev)
+        G, U = torch.empty_like(H), torch.empty_like(H)
+        gemm(Xg, w1, H, B2=w2, G=G, U=U, mode=BATCHED, groups=E, epi=EPI_SWIGLU, M=BC, N=f, Kd=d, b_major=MAJ_MN,
+             lda=d, ldb=f, ldc=f, a_gs=BC * d, b_gs=d * f, c_gs=BC * f)
+        Y = torch.empty(E * BC, d, dtype=x2.dtype, device=dev)
+        gemm(H, w3, Y, mode=BATCHED, groups=E, M=BC, N=d, Kd=f, b_major=MAJ_MN, lda=f, ldb=d, ldc=d,
+             a_gs=BC * f, b_gs=f * d, c_gs=BC * d)
+        out = K.moe_combine(Y, pos, wdense, T, E)
+        _count(2)
+        ctx.save_for_backward(Xg, G, U, Y, w1, w2, w3, wdense, pos, row_src, meta, a)
+        ctx.dims = (T, d, E, f, BC)
+        ctx.wdtype = wts.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        Xg, G, U, Y, w1, w2, w3, wdense, pos, row_src, meta, a = ctx.saved_tensors
+        T, d, E, f, BC = ctx.dims
+        dout = dout.contiguous()
+        dY = K.moe_gather_rows(dout, row_src, wdense, meta, E)
+        dwts = K.moe_combine_dw(Y, dout, pos, E)[a].to(ctx.wdtype)                  # (B, E, C)
+        dH = torch.empty(E * BC, f, dtype=dout.dtype, device=dout.device)
+        gemm(dY, w3, dH, mode=BATCHED, groups=E, M=BC, N=f, Kd=d, lda=d, ldb=d, ldc=f,
+             a_gs=BC * d, b_gs=f * d, c_gs=BC * f)
+        dGU = K.swiglu_bwd_cat(G, U, dH, None)
+        dG, dU = dGU[:, :f], dGU[:, f:]
+        dXg = torch.empty(E * BC, d, dtype=dout.dtype, device=dout.device)
+        gemm(dGU, w1, dXg, B2=w2, mode=BATCHED, groups=E, M=BC, N=d, Kd=2 * f, k_split=f, lda=2 * f, ldb=f, ldc=d,
+             a_gs=BC * 2 * f, b_gs=d * f, c_gs=BC * d)
+        dx = K.moe_combine(dXg, pos, None, T, E)
+        H = K.swiglu_fwd(G, U, None)
+        sinks = [grad_sink(w) for w in (w1, w2, w3)]
+        dw1, dw2, dw3 = [s_[0] if s_ is not None else torch.empty_like(w) for s_, w in zip(sinks, (w1, w2, w3))]
+        common = dict(mode=BATCHED, groups=E, a_major=MAJ_MN, b_major=MAJ_MN, Kd=BC)
+        gemm(Xg, dG, dw1, M=d, N=f, lda=d, ldb=2 * f, ldc=f, a_gs=BC * d, b_gs=BC * 2 * f, c_gs=d * f, **common)
+        gemm(Xg, dU, dw2, M=d, N=f, lda=d, ldb=2 * f, ldc=f, a_gs=BC * d, b_gs=BC * 2 * f, c_gs=d * f, **common)
+        gemm(H, dY, dw3, M=f, N=d, lda=f, ldb=d, ldc=d, a_gs=BC * f, b_gs=BC * d, c_gs=f * d, **common)
+        _count(5)
+        for s_ in sinks:
+            if s_ is not None:
+                s_[1]()
+        dw1, dw2, dw3 = [None if s_ is not None else g for s_, g in zip(sinks, (dw1, dw2, dw3))]
+        return dx, dw1, dw2, dw3, dwts, None, None
+
+
+def expert_choice_swiglu(x, w1, w2, w3, wts, tok):
+    """x (B, S, d); wts, tok (B, E, C) from ``expert_choice_route``; returns (B, S, d)."""
+    B, S, d = x.shape
+    f = w1.shape[2]
+    ok = _bf16(x) and _bf16(w1) and d % 64 == 0 and f % 64 == 0 and tok.numel() > 0
+    if not ok:
+        _fallback("expert_choice_swiglu", f"dtype {x.dtype}/{w1.dtype} d={d} f={f}")
+        return eager.expert_choice_swiglu(x, w1, w2, w3, wts, tok)
+    out = _ExpertChoiceSwiGLU.apply(x.reshape(B * S, d), w1.contiguous(), w2.contiguous(), w3.contiguous(), wts,
+                                    tok, S)
+    return out.view(B, S, d)
+
+
+def capacity_keep_mask(idx, n_experts: int, capacity: int):
+    """First ``capacity`` assignments of each expert in (token, slot) order are kept (one kernel; no one-hot /
+    cumsum tensors of size assignments x experts)."""
+    if n_experts > 190:
+        return eager.capacity_keep_mask(idx, n_experts, capacity)
+    _count()
+    return K.moe_capacity_mask(idx.contiguous(), n_experts, int(capacity))
+
+
+def balanced_assign(probs, top_k: int):
+    """Expert indices (T, k) of the greedy balanced assignment (see ``eager.balanced_assign``)."""
+    T, E = probs.shape
+    cap = max((T * top_k) // E, 1)
+    _count(top_k)
+    return K.moe_balanced_assign(probs.detach().float().contiguous(), top_k, cap)
+
+
 # -------------------------------------------------------- routing decisions
 class _RouteTopK(torch.autograd.Function):
     """softmax over experts -> top-k -> renormalise, with the auxiliary loss
@@ -645,6 +746,20 @@ def mod_combine(res, proc, w, idx):
 
 
 # -------------------------------------------------------- LM head + MTP loss
+_HEAD_WEIGHTS: dict = {}
+
+
+def _head_weight_tensor(weights: tuple, device) -> torch.Tensor:
+    """The per-head loss weights on the device, created once: building a device tensor from Python numbers
+    is a pageable host-to-device copy, which blocks the host until the stream has drained."""
+    key = (weights, str(device))
+    t = _HEAD_WEIGHTS.get(key)
+    if t is None:
+        t = torch.tensor(list(weights), dtype=torch.float32).to(device)
+        _HEAD_WEIGHTS[key] = t
+    return t
+
+
 class _MTPLoss(torch.autograd.Function):
     """Per head: logits chunk = H W^T (tcgen05 GEMM) -> CE kernel writes d logits in place ->
     dH += dlogits W and dW = dlogits^T H.  Gradients are produced during forward (scaled
@@ -687,8 +802,7 @@ class _MTPLoss(torch.autograd.Function):
             per.append(loss_sum / n_valid)
             dWs.append(dW)
         per_t = torch.stack(per)
-        wt = torch.tensor(list(weights), dtype=torch.float32, device=hidden.device)
-        total = (per_t * wt).sum()
+        total = (per_t * _head_weight_tensor(tuple(float(w) for w in weights), hidden.device)).sum()
         ctx.shape = (B, S, d)
         ctx.n_heads = len(head_weights)
         saved = [dH if dH is not None else torch.empty(0, device=hidden.device)]

@@ -181,6 +181,40 @@ def expert_choice_route(logits: torch.Tensor, capacity: int):
     return w / (w.sum(dim=-1, keepdim=True) + 1e-9), tok
 
 
+def expert_choice_swiglu(x, w1, w2, w3, wts, tok):
+    """Expert-choice expert FFN: expert e applies SwiGLU to the C tokens it picked from every sequence and the
+    results are added back weighted (reference: moe.py:533-673).  x (B, S, d); wts, tok (B, E, C)."""
+    B, S, d = x.shape
+    _, E, C = tok.shape
+    flat_idx = tok.reshape(B, E * C)
+    xin = torch.gather(x, 1, flat_idx.unsqueeze(-1).expand(-1, -1, d)).view(B, E, C, d)
+    h = swiglu(torch.matmul(xin, w1), torch.matmul(xin, w2))
+    y = torch.matmul(h, w3)
+    y = (y * wts.unsqueeze(-1).to(y.dtype)).view(B, E * C, d)
+    return torch.zeros_like(x).scatter_add(1, flat_idx.unsqueeze(-1).expand(-1, -1, d), y)
+
+
+def balanced_assign(probs: torch.Tensor, top_k: int) -> torch.Tensor:
+    """Greedy per-slot assignment under a global per-expert capacity of ``(T * k) // E``: in slot j every token
+    takes its best expert that was not already full at the start of the slot and that it has not used; a
+    token with no such expert takes its best unused one (reference: moe.py:353-421).  Returns indices (T, k)."""
+    T, E = probs.shape
+    cap = max((T * top_k) // E, 1)
+    counts = torch.zeros(E, dtype=torch.long, device=probs.device)
+    avail = probs.detach().clone()
+    sel = []
+    neg = float("-inf")
+    for _ in range(top_k):
+        masked = avail.masked_fill((counts >= cap)[None, :], neg)
+        best_p, best_e = masked.max(dim=-1)
+        fb_e = avail.argmax(dim=-1)
+        best_e = torch.where(best_p == neg, fb_e, best_e)
+        sel.append(best_e)
+        counts = counts + torch.bincount(best_e, minlength=E)
+        avail = avail.scatter(1, best_e[:, None], neg)
+    return torch.stack(sel, dim=1)
+
+
 def capacity_keep_mask(idx: torch.Tensor, n_experts: int, capacity: int) -> torch.Tensor:
     """Drop policy for token-choice with capacity: for each expert keep the first
     ``capacity`` assignments in (token, slot) order; later ones are dropped and

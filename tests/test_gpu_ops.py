@@ -464,3 +464,47 @@ def test_dense_swiglu_fwd_bwd(T, d, f):
     assert _rel(y, yr) < 2e-2 and _rel(x.grad, xr.grad) < 2e-2
     for a, b in ((w1, r1), (w2, r2), (w3, r3)):
         assert _rel(a.grad, b.grad) < 2e-2
+
+
+@pytest.mark.parametrize("B,S,E,C,d,f", [(2, 64, 4, 20, 128, 192), (3, 96, 8, 12, 64, 64)])
+def test_expert_choice_swiglu_fwd_bwd(B, S, E, C, d, f):
+    """Expert-choice experts on the grouped kernels (batched GEMMs over the experts, deterministic combine)
+    against the gather / matmul / scatter-add definition in fp32; tokens picked by several experts included."""
+    ops, c, eager = _mods()
+    torch.manual_seed(3)
+    x = _bf(B, S, d, grad=True)
+    w1, w2 = _bf(E, d, f, scale=d ** -0.5, grad=True), _bf(E, d, f, scale=d ** -0.5, grad=True)
+    w3 = _bf(E, f, d, scale=f ** -0.5, grad=True)
+    logits = torch.randn(B, S, E, device="cuda")
+    wts, tok = eager.expert_choice_route(logits, C)
+    wts = wts.bfloat16().requires_grad_(True)
+    assert torch.bincount(tok.reshape(B, -1)[0], minlength=S).max() > 1      # some token has several experts
+    out = ops.expert_choice_swiglu(x, w1, w2, w3, wts, tok)
+    g = _bf(B, S, d)
+    out.backward(g)
+    c.check_status()
+    xr, a1, a2, a3, wr = [_f32_leaf(t) for t in (x, w1, w2, w3, wts)]
+    ref = eager.expert_choice_swiglu(xr, a1, a2, a3, wr, tok)
+    ref.backward(g.float())
+    assert _rel(out, ref) < 2e-2
+    for name, a, b in [("x", x, xr), ("w1", w1, a1), ("w2", w2, a2), ("w3", w3, a3), ("wts", wts, wr)]:
+        assert _rel(a.grad, b.grad) < 4e-2, name
+    out2 = ops.expert_choice_swiglu(x, w1, w2, w3, wts, tok)
+    assert torch.equal(out, out2), "the combine must be deterministic"
+
+
+@pytest.mark.parametrize("T,E,k,cap", [(1000, 8, 2, 130), (64, 4, 1, 3), (513, 16, 2, 10000)])
+def test_capacity_mask_and_balanced_assignment_kernels(T, E, k, cap):
+    """Device-side drop decision and balanced assignment against their PyTorch definitions (exact)."""
+    ops, c, eager = _mods()
+    torch.manual_seed(4)
+    logits = torch.randn(T, E, device="cuda")
+    logits[:, 1] += 1.0                                                      # a popular expert
+    idx = logits.topk(k, dim=-1).indices
+    keep = ops.capacity_keep_mask(idx, E, cap)
+    assert keep.dtype == torch.bool and torch.equal(keep, eager.capacity_keep_mask(idx, E, cap))
+    probs = torch.softmax(logits, -1)
+    got, want = ops.balanced_assign(probs, k), eager.balanced_assign(probs, k)
+    assert torch.equal(got, want)
+    counts = torch.bincount(got.reshape(-1), minlength=E)
+    assert counts.max() <= max((T * k) // E, 1) + T        # loose: fallback picks may exceed the capacity

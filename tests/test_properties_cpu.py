@@ -291,3 +291,15 @@ def test_mx_scale_chunk_layout_round_trip(rows, kchunks, seed):
             chunk = (r // 128) * kchunks + kg // 4
             sf[chunk * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + kg % 4] = int(exps[r, kg]) + 127
     assert torch.equal(decode_scale_chunks(sf, rows, K), exps.to(torch.int32))
+
+
+def test_extension_errors_raise_instead_of_crashing():
+    """A failed entry point of the compiled library surfaces as a Python exception with its formatted message.
+    (A library linked against a private copy of the C++ runtime crashes while formatting the number.)"""
+    import pytest
+    from kolmogorov_moe_architecture_b200.ops import loader
+    if not loader.ext_available():
+        pytest.skip("extension not built")
+    with pytest.raises(RuntimeError, match="kmoe::self_test failed with code -7"):
+        torch.ops.kmoe.raise_check(-7)
+    torch.ops.kmoe.raise_check(0)
