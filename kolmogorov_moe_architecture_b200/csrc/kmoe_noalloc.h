@@ -22,6 +22,12 @@
 //    part they use before reading it, so stale contents from an earlier call are never
 //    read; but two calls that overlap in time on the same device (different streams)
 //    race on it.  Serialise them.
+//  * Host threads: the function may be entered from several host threads only if they
+//    serialise their calls per device (which the shared scratch array demands anyway).  The
+//    cached device address is written without a lock; concurrent first calls would store
+//    the same value.
+//  * The return code comes from cudaGetLastError after the launches, so an error left
+//    pending by earlier unrelated work on the thread is reported as KMOE_NOALLOC_E_LAUNCH.
 //  * No cudaMalloc, cudaFree or allocating library routine is called, on any call.
 #pragma once
 #include <cuda_runtime.h>

@@ -45,6 +45,11 @@ def _case(fn, rows, d, seed):
     rel = lambda a, b: ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6)).item()
     assert rel(dx, dx_ref) < 2e-2
     assert rel(dw, dw_ref) < 2e-2
+    # and against the definition itself, evaluated in fp32 by autograd
+    xr, wr = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    (xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr).backward(dy.float())
+    assert rel(dx, xr.grad) < 2e-2
+    assert rel(dw, wr.grad) < 2e-2
 
 
 def test_noalloc_matches_regular_entry_point_on_two_calls():
@@ -52,6 +57,12 @@ def test_noalloc_matches_regular_entry_point_on_two_calls():
     _case(fn, 4096, 2048, seed=1)      # fills 64 partial rows of width 2048
     _case(fn, 300, 512, seed=2)        # smaller call right after: reuses the same scratch
     _case(fn, 4096, 2048, seed=3)
+
+
+def test_noalloc_at_the_size_limit_and_with_a_ragged_column_tail():
+    fn = _lib()
+    _case(fn, 520, 8192, seed=4)       # d at the stated maximum: every float of the 2 MiB scratch array is used
+    _case(fn, 64, 520, seed=5)         # d not a multiple of 256: the last column block is partly empty
 
 
 def test_noalloc_rejects_sizes_beyond_the_maximum():
