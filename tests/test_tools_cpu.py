@@ -182,3 +182,18 @@ def test_every_shipped_config_builds_a_model_on_the_meta_device():
     assert abs(n - 5.87e9) < 0.01e9
     acc = yaml.safe_load(open(os.path.join(ROOT, "configs", "fsdp_config.yaml")))
     assert acc["distributed_type"] == "FSDP" and acc["fsdp_config"]["fsdp_sharding_strategy"] == "FULL_SHARD"
+
+
+def test_hf_entrypoint_fsdp_settings():
+    """The shipped Accelerate-style FSDP file is consumed: a torchrun launch asks the HF Trainer for FULL_SHARD
+    over the transformer blocks, an Accelerate launch leaves FSDP to Accelerate, one process needs nothing."""
+    import train_production as tp
+    path = os.path.join(ROOT, "configs", "fsdp_config.yaml")
+    one = tp.fsdp_settings(path, env={})
+    assert one["distributed"] is False and one["hf_kwargs"] == {}
+    tr = tp.fsdp_settings(path, env={"WORLD_SIZE": "2"})
+    assert tr["distributed"] and tr["hf_kwargs"]["fsdp"] == "full_shard auto_wrap"
+    assert tr["hf_kwargs"]["fsdp_config"]["transformer_layer_cls_to_wrap"] == ["TransformerBlock"]
+    assert tr["hf_kwargs"]["fsdp_config"]["backward_prefetch"] == "backward_pre" and tr["cpu_offload"] is False
+    acc = tp.fsdp_settings(path, env={"WORLD_SIZE": "2", "ACCELERATE_USE_FSDP": "true"})
+    assert acc["accelerate_owns_fsdp"] and acc["hf_kwargs"] == {}

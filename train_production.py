@@ -6,6 +6,13 @@ The model is wrapped by ``MoEModelWrapper``; HF owns the loop, logging and ``che
 directories (``save_total_limit=3``); the optimizer is the hybrid Muon/AdamW or AdamW and the
 schedule the cosine-with-warm-up of this library.  ``mixed_precision.fp8: true`` selects the
 block-scaled fp8 expert GEMMs (``moe_dtype: mxfp8``) instead of the reference's torchao swap.
+
+Multi-GPU: launched by ``accelerate launch --config_file configs/fsdp_config.yaml`` Accelerate applies FSDP
+itself; launched by ``torchrun`` the script asks the HF Trainer for ``full_shard auto_wrap`` over
+``TransformerBlock`` (reference: train_production.py:518-529), taking prefetch / offload switches from
+``--fsdp_config`` (an Accelerate-style YAML such as ``configs/fsdp_config.yaml``).  Without ``accelerate``
+installed the same file selects this framework's own parameter-sharded plan (FULL_SHARD per block, AdamW on
+the shards, optional host offload) on the native loop.
 """
 import argparse
 import os
@@ -15,6 +22,34 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 
 
+def fsdp_settings(path, env=None):
+    """What an Accelerate-style FSDP file (``fsdp_config:`` block) asks for, in both vocabularies.
+
+    Returns ``{"distributed", "accelerate_owns_fsdp", "cpu_offload", "hf_kwargs"}``: ``hf_kwargs`` are the
+    ``TrainingArguments`` entries for a torchrun launch (empty when Accelerate applies FSDP itself or the job
+    has one process); ``cpu_offload`` is what the native parameter-sharded plan takes from the file."""
+    env = os.environ if env is None else env
+    world = int(env.get("WORLD_SIZE", "1") or 1)
+    fc = {}
+    if path:
+        import yaml
+        with open(path) as f:
+            fc = (yaml.safe_load(f) or {}).get("fsdp_config", {}) or {}
+    offload = bool(fc.get("fsdp_offload_params", False))
+    owns = str(env.get("ACCELERATE_USE_FSDP", "")).lower() in ("1", "true", "yes")
+    hf = {}
+    if world > 1 and not owns:
+        hf = {"fsdp": "full_shard auto_wrap" + (" offload" if offload else ""),
+              "fsdp_config": {"transformer_layer_cls_to_wrap": ["TransformerBlock"],
+                              "backward_prefetch": str(fc.get("fsdp_backward_prefetch", "BACKWARD_PRE")).lower(),
+                              "forward_prefetch": bool(fc.get("fsdp_forward_prefetch", True)),
+                              "use_orig_params": bool(fc.get("fsdp_use_orig_params", True)),
+                              "cpu_ram_efficient_loading": bool(fc.get("fsdp_cpu_ram_efficient_loading", True)),
+                              "sync_module_states": bool(fc.get("fsdp_sync_module_states", True)),
+                              "limit_all_gathers": bool(fc.get("fsdp_limit_all_gathers", True))}}
+    return {"distributed": world > 1, "accelerate_owns_fsdp": owns, "cpu_offload": offload, "hf_kwargs": hf}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", type=str, required=True)
@@ -22,17 +57,25 @@ def main(argv=None):
     ap.add_argument("--max_steps", type=int, default=None)
     ap.add_argument("--synthetic", action="store_true")
     ap.add_argument("--output_dir", type=str, default=None)
+    ap.add_argument("--fsdp_config", type=str, default=None,
+                    help="Accelerate-style FSDP settings (e.g. configs/fsdp_config.yaml) for multi-process runs")
     a = ap.parse_args(argv)
+    fs = fsdp_settings(a.fsdp_config)
     import importlib.util
     if importlib.util.find_spec("accelerate") is None:
         # HF Trainer cannot be constructed without `accelerate`; run the same recipe (hybrid optimizer,
         # cosine schedule with warm-up, checkpoint-N directories with the newest three kept) on the native loop.
         print("accelerate is not installed: running the HF recipe on the native training loop")
         from kolmogorov_moe_architecture_b200.training.runner import RunSpec, run_training
+        if fs["distributed"]:
+            print("multi-process run: FULL_SHARD per transformer block on this framework's parameter-sharded plan"
+                  + (" with host offload" if fs["cpu_offload"] else ""))
         return run_training(RunSpec(config_path=a.config, steps=a.max_steps, strict_config=True,
-                                    weights="fp32_autocast", optimizer_family="hybrid", checkpoint_format="C",
+                                    weights="bf16" if fs["distributed"] else "fp32_autocast",
+                                    optimizer_family="hybrid", checkpoint_format="C",
                                     checkpoint_dir=a.output_dir, resume=a.resume_from_checkpoint,
-                                    data_mode="synthetic" if a.synthetic else "streaming"))
+                                    data_mode="synthetic" if a.synthetic else "streaming",
+                                    shard_params=fs["distributed"], cpu_offload=fs["distributed"] and fs["cpu_offload"]))
     import torch
     from torch.utils.data import Dataset
     from transformers import TrainingArguments
@@ -74,7 +117,7 @@ def main(argv=None):
         learning_rate=tc["max_lr"], warmup_steps=min(tc["warmup_steps"], max(steps - 1, 0)),
         max_grad_norm=tc["gradient_clip_norm"], logging_steps=tc["log_interval"], save_steps=tc["save_interval"],
         save_total_limit=3, bf16=bool(mp.get("bf16", cuda)) and cuda, report_to=[], remove_unused_columns=False,
-        dataloader_num_workers=0, use_cpu=not cuda)
+        dataloader_num_workers=0, use_cpu=not cuda, **fs["hf_kwargs"])
     trainer = MoETrainer(oc, tc, tc["log_interval"], model=model, args=args, train_dataset=train_ds,
                          eval_dataset=eval_ds, callbacks=[TrueLoss(tc["gradient_accumulation_steps"])])
     try:
