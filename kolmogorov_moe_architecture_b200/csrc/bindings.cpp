@@ -106,6 +106,43 @@ std::tuple<Tensor, Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const T
   return {dx, dw};
 }
 
+// (sum, y, rstd): sum = x + addend (or x itself when addend is absent), y = rmsnorm(sum)
+std::tuple<Tensor, Tensor, Tensor> add_rmsnorm_fwd(const Tensor& x, const OptT& addend, const Tensor& w, double eps) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_bf16(x, "x"); need_bf16(w, "w");
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous());
+  const bool has = addend.has_value() && addend->defined();
+  if (has) { need_bf16(*addend, "addend"); TORCH_CHECK(addend->is_contiguous() && addend->sizes() == x.sizes()); }
+  const int d = x.size(-1);
+  const int rows = x.numel() / d;
+  Tensor y = at::empty_like(x);
+  Tensor sum = has ? at::empty_like(x) : x;
+  Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  check(kmoe_add_rmsnorm_fwd(x.data_ptr(), has ? addend->data_ptr() : nullptr, w.data_ptr(),
+                             has ? sum.data_ptr() : nullptr, y.data_ptr(), rstd.data_ptr<float>(), rows, d, (float)eps,
+                             cur_stream()), "add_rmsnorm_fwd");
+  return {sum, y, rstd};
+}
+
+// rmsnorm backward with the residual-branch gradient folded in: dx = norm term + dres
+std::tuple<Tensor, Tensor> rmsnorm_bwd_res(const Tensor& x, const Tensor& w, const Tensor& dy, const Tensor& rstd,
+                                           const OptT& dres) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_bf16(x, "x"); need_bf16(dy, "dy"); need_f32(rstd, "rstd");
+  TORCH_CHECK(x.is_contiguous() && dy.is_contiguous());
+  const bool has = dres.has_value() && dres->defined();
+  if (has) { need_bf16(*dres, "dres"); TORCH_CHECK(dres->is_contiguous() && dres->sizes() == x.sizes()); }
+  const int d = x.size(-1);
+  const int rows = x.numel() / d;
+  Tensor dx = at::empty_like(x);
+  Tensor dw = at::empty({d}, x.options().dtype(at::kFloat));
+  Tensor partial = at::empty({kmoe_rmsnorm_bwd_num_partials(rows), d}, x.options().dtype(at::kFloat));
+  check(kmoe_rmsnorm_bwd_res(x.data_ptr(), w.data_ptr(), dy.data_ptr(), rstd.data_ptr<float>(),
+                             has ? dres->data_ptr() : nullptr, dx.data_ptr(), nullptr, dw.data_ptr<float>(),
+                             partial.data_ptr<float>(), rows, d, cur_stream()), "rmsnorm_bwd_res");
+  return {dx, dw};
+}
+
 Tensor rowdot_fwd(const Tensor& x, const Tensor& w) {
   c10::cuda::CUDAGuard guard(x.device());
   need_bf16(x, "x"); need_bf16(w, "w");
@@ -504,24 +541,26 @@ std::tuple<Tensor, Tensor> mod_combine_bwd(const Tensor& dout, const Tensor& pro
 }
 
 // ------------------------------------------------------------- Muon elementwise passes
-void muon_momentum(Tensor buf, const Tensor& grad_ptrs, Tensor sumsq, double mu) {
+void muon_momentum(Tensor buf, const Tensor& grad_ptrs, Tensor sumsq, double mu, const OptT& gcoef) {
   c10::cuda::CUDAGuard guard(buf.device());
   need_bf16(buf, "buf"); need_f32(sumsq, "sumsq");
   TORCH_CHECK(buf.is_contiguous() && buf.dim() == 3 && grad_ptrs.scalar_type() == at::kLong &&
               grad_ptrs.numel() == buf.size(0) && sumsq.numel() == buf.size(0));
   check(kmoe_muon_momentum(buf.data_ptr(), (const long long*)grad_ptrs.data_ptr<int64_t>(), sumsq.data_ptr<float>(),
-                           (int)buf.size(0), buf.size(1) * buf.size(2), (float)mu, cur_stream()), "muon_momentum");
+                           (int)buf.size(0), buf.size(1) * buf.size(2), (float)mu, (const float*)ptr_or_null(gcoef),
+                           cur_stream()), "muon_momentum");
 }
 
 void muon_apply(Tensor buf, const Tensor& ortho, const Tensor& grad_ptrs, const Tensor& param_ptrs, double lr,
-                double mu, double wd, bool nesterov) {
+                double mu, double wd, bool nesterov, const OptT& gcoef) {
   c10::cuda::CUDAGuard guard(buf.device());
   need_bf16(buf, "buf"); need_bf16(ortho, "ortho");
   TORCH_CHECK(buf.is_contiguous() && ortho.is_contiguous() && buf.sizes() == ortho.sizes() && buf.dim() == 3);
   TORCH_CHECK(grad_ptrs.numel() == buf.size(0) && param_ptrs.numel() == buf.size(0));
   check(kmoe_muon_apply(buf.data_ptr(), ortho.data_ptr(), (const long long*)grad_ptrs.data_ptr<int64_t>(),
                         (const long long*)param_ptrs.data_ptr<int64_t>(), (int)buf.size(0), buf.size(1) * buf.size(2),
-                        (float)lr, (float)mu, (float)wd, nesterov ? 1 : 0, cur_stream()), "muon_apply");
+                        (float)lr, (float)mu, (float)wd, nesterov ? 1 : 0, (const float*)ptr_or_null(gcoef),
+                        cur_stream()), "muon_apply");
 }
 
 // int8 block-quantised momentum (Muon8bit): returns (q [blocks, block] int8, scales [blocks, 1] fp32)
@@ -713,6 +752,8 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("gemm", &gemm);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
+  m.def("rmsnorm_bwd_res", &rmsnorm_bwd_res);
   m.def("rope", &rope);
   m.def("rowdot_fwd", &rowdot_fwd);
   m.def("rowdot_bwd", &rowdot_bwd);

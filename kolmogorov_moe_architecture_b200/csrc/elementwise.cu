@@ -29,13 +29,30 @@ __device__ __forceinline__ uint4 pack8(const float* v) {
 
 // ------------------------------------------------------------------- RMSNorm
 // y = w * x * rsqrt(mean(x^2) + eps); optionally res_out = x (+ residual) is fused by the caller.
+// With `addend` the normalised row is h = bf16(x + addend), which is also written to `sum_out` (the residual
+// stream after the sequence mixer): residual add and pre-FFN norm in one pass.
 __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int d,
-                                   float eps) {
+                                   float eps, const __nv_bfloat16* __restrict__ addend,
+                                   __nv_bfloat16* __restrict__ sum_out) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
     const __nv_bfloat16* xr = x + (size_t)row * d;
+    if (addend != nullptr) {
+      const __nv_bfloat16* ar = addend + (size_t)row * d;
+      __nv_bfloat16* sr = sum_out + (size_t)row * d;
+      for (int c = lane * 8; c < d; c += 256) {
+        float v[8], a[8];
+        unpack8(*reinterpret_cast<const uint4*>(xr + c), v);
+        unpack8(*reinterpret_cast<const uint4*>(ar + c), a);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += a[i];
+        *reinterpret_cast<uint4*>(sr + c) = pack8(v);
+      }
+      __syncwarp();
+      xr = sr;                                   // each lane re-reads the columns it wrote itself
+    }
     float ss = 0.f;
     for (int c = lane * 8; c < d; c += 256) {
       float v[8];
@@ -59,9 +76,11 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
 }
 
 // dx = rstd * (w dy) - x * rstd^3 * mean(w dy x).  One warp per row.
+// `dres` (optional): gradient arriving through the residual branch that bypasses the norm; dx = norm term + dres.
 __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                    const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
-                                   __nv_bfloat16* __restrict__ dx, int rows, int d) {
+                                   __nv_bfloat16* __restrict__ dx, int rows, int d,
+                                   const __nv_bfloat16* __restrict__ dres = nullptr) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
@@ -87,6 +106,12 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __
       unpack8(*reinterpret_cast<const uint4*>(w + c), wv);
 #pragma unroll
       for (int i = 0; i < 8; ++i) o[i] = gv[i] * wv[i] * r - xv[i] * coef;
+      if (dres != nullptr) {
+        float rv[8];
+        unpack8(*reinterpret_cast<const uint4*>(dres + (size_t)row * d + c), rv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] += rv[i];
+      }
       *reinterpret_cast<uint4*>(dxr + c) = pack8(o);
     }
   }
@@ -292,15 +317,21 @@ static inline int grid_for(long long work, int block, int sms = 148) {
 
 using namespace kmoe;
 
-extern "C" int kmoe_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int d, float eps,
-                                cudaStream_t st) {
-  if (d % 8) return -1;
+extern "C" int kmoe_add_rmsnorm_fwd(const void* x, const void* addend, const void* w, void* sum_out, void* y,
+                                    float* rstd, int rows, int d, float eps, cudaStream_t st) {
+  if (d % 8 || (addend != nullptr) != (sum_out != nullptr)) return -1;
   const int block = 256, wpb = block / 32;
   int grid = (rows + wpb - 1) / wpb;
   if (grid > 148 * 8) grid = 148 * 8;
   rmsnorm_fwd_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
-                                             rstd, rows, d, eps);
+                                             rstd, rows, d, eps, (const __nv_bfloat16*)addend,
+                                             (__nv_bfloat16*)sum_out);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int d, float eps,
+                                cudaStream_t st) {
+  return kmoe_add_rmsnorm_fwd(x, nullptr, w, nullptr, y, rstd, rows, d, eps, st);
 }
 
 extern "C" int kmoe_rmsnorm_bwd_num_partials(int rows) {
@@ -311,12 +342,20 @@ extern "C" int kmoe_rmsnorm_bwd_num_partials(int rows) {
 // `partial` is scratch of kmoe_rmsnorm_bwd_num_partials(rows) * d floats.
 extern "C" int kmoe_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx,
                                 void* dw_bf16, float* dw_f32, float* partial, int rows, int d, cudaStream_t st) {
+  return kmoe_rmsnorm_bwd_res(x, w, dy, rstd, nullptr, dx, dw_bf16, dw_f32, partial, rows, d, st);
+}
+
+// dres (optional, bf16 [rows, d]): gradient of the residual branch, added to dx in the same pass.
+extern "C" int kmoe_rmsnorm_bwd_res(const void* x, const void* w, const void* dy, const float* rstd, const void* dres,
+                                    void* dx, void* dw_bf16, float* dw_f32, float* partial, int rows, int d,
+                                    cudaStream_t st) {
   if (d % 8) return -1;
   const int block = 256, wpb = block / 32;
   int grid = (rows + wpb - 1) / wpb;
   if (grid > 148 * 8) grid = 148 * 8;
   rmsnorm_bwd_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
-                                             (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, rows, d);
+                                             (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, rows, d,
+                                             (const __nv_bfloat16*)dres);
   const int parts = kmoe_rmsnorm_bwd_num_partials(rows);
   rmsnorm_dw_kernel<<<dim3((d + 255) / 256, parts), 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
                                                                   rstd, partial, rows, d);
@@ -422,8 +461,16 @@ extern "C" int kmoe_rmsnorm_bwd_noalloc(const void* x, const void* w, const void
 // (the orthogonalisation between them is the batched Newton-Schulz GEMM loop).  grid.y = matrix index.
 namespace kmoe {
 
+// gcoef (optional, device): the gradient is used as bf16(g * bf16(*gcoef)), i.e. as if the clip coefficient
+// had been multiplied into the bf16 gradient in memory beforehand (both Muon kernels apply it the same way)
+__device__ __forceinline__ float muon_gcoef(const float* gcoef) {
+  return gcoef != nullptr ? __bfloat162float(__float2bfloat16(*gcoef)) : 1.f;
+}
+
 __global__ void muon_momentum_kernel(__nv_bfloat16* __restrict__ buf, const long long* __restrict__ grad_ptrs,
-                                     float* __restrict__ sumsq, long long numel, float mu) {
+                                     float* __restrict__ sumsq, long long numel, float mu,
+                                     const float* __restrict__ gcoef) {
+  const float gc = muon_gcoef(gcoef);
   const int mi = blockIdx.y;
   __nv_bfloat16* b = buf + (long long)mi * numel;
   const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(grad_ptrs[mi]);
@@ -435,7 +482,10 @@ __global__ void muon_momentum_kernel(__nv_bfloat16* __restrict__ buf, const long
     unpack8(*(reinterpret_cast<const uint4*>(b) + i), bv);
     unpack8(*(reinterpret_cast<const uint4*>(g) + i), gv);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) bv[j] = mu * bv[j] + gv[j];
+    for (int j = 0; j < 8; ++j) {
+      const float gj = gcoef != nullptr ? __bfloat162float(__float2bfloat16(gv[j] * gc)) : gv[j];
+      bv[j] = mu * bv[j] + gj;
+    }
     const uint4 o = pack8(bv);
     *(reinterpret_cast<uint4*>(b) + i) = o;
     float rv[8];
@@ -456,7 +506,9 @@ __global__ void muon_momentum_kernel(__nv_bfloat16* __restrict__ buf, const long
 
 __global__ void muon_apply_kernel(__nv_bfloat16* __restrict__ buf, const __nv_bfloat16* __restrict__ ortho,
                                   const long long* __restrict__ grad_ptrs, const long long* __restrict__ param_ptrs,
-                                  long long numel, float lr, float mu, float wd, int nesterov) {
+                                  long long numel, float lr, float mu, float wd, int nesterov,
+                                  const float* __restrict__ gcoef) {
+  const float gc = muon_gcoef(gcoef);
   const int mi = blockIdx.y;
   __nv_bfloat16* b = buf + (long long)mi * numel;
   const __nv_bfloat16* o = ortho + (long long)mi * numel;
@@ -476,7 +528,8 @@ __global__ void muon_apply_kernel(__nv_bfloat16* __restrict__ buf, const __nv_bf
       for (int j = 0; j < 8; ++j) {
         // same rounding points as the unfused sequence: p*decay -> bf16, g + mu*o -> bf16, then the update
         const float pd = __bfloat162float(__float2bfloat16(pf[j] * decay));
-        const float up = __bfloat162float(__float2bfloat16(gf[j] + mu * of[j]));
+        const float gj = gcoef != nullptr ? __bfloat162float(__float2bfloat16(gf[j] * gc)) : gf[j];
+        const float up = __bfloat162float(__float2bfloat16(gj + mu * of[j]));
         pf[j] = pd - lr * up;
       }
     } else {
@@ -576,22 +629,23 @@ extern "C" int kmoe_q8_momentum(const signed char* q, const float* scales, const
 }
 
 extern "C" int kmoe_muon_momentum(void* buf, const long long* grad_ptrs, float* sumsq, int n_mat, long long numel,
-                                  float mu, cudaStream_t st) {
+                                  float mu, const float* gcoef, cudaStream_t st) {
   if (numel % 8 || n_mat <= 0 || n_mat > 65535) return -1;
   const long long per = (numel / 8 + 255) / 256;
   const long long cap = 2368 / n_mat > 64 ? 2368 / n_mat : 64;      // ~16 CTAs per SM over all matrices
   dim3 grid((unsigned)(per < cap ? per : cap), n_mat);
-  kmoe::muon_momentum_kernel<<<grid, 256, 0, st>>>((__nv_bfloat16*)buf, grad_ptrs, sumsq, numel, mu);
+  kmoe::muon_momentum_kernel<<<grid, 256, 0, st>>>((__nv_bfloat16*)buf, grad_ptrs, sumsq, numel, mu, gcoef);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 extern "C" int kmoe_muon_apply(void* buf, const void* ortho, const long long* grad_ptrs, const long long* param_ptrs,
-                               int n_mat, long long numel, float lr, float mu, float wd, int nesterov, cudaStream_t st) {
+                               int n_mat, long long numel, float lr, float mu, float wd, int nesterov,
+                               const float* gcoef, cudaStream_t st) {
   if (numel % 8 || n_mat <= 0 || n_mat > 65535) return -1;
   const long long per = (numel / 8 + 255) / 256;
   const long long cap = 2368 / n_mat > 64 ? 2368 / n_mat : 64;
   dim3 grid((unsigned)(per < cap ? per : cap), n_mat);
   kmoe::muon_apply_kernel<<<grid, 256, 0, st>>>((__nv_bfloat16*)buf, (const __nv_bfloat16*)ortho, grad_ptrs, param_ptrs,
-                                                numel, lr, mu, wd, nesterov);
+                                                numel, lr, mu, wd, nesterov, gcoef);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

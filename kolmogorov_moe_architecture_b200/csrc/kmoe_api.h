@@ -69,10 +69,12 @@ void kmoe_gemm_clear_tensormap_cache(void);
 // device arrays with the address of each matrix's gradient / parameter.
 //   momentum: buf = mu * buf + grad ; sumsq[i] += sum(buf_i^2)      (sumsq zeroed by the caller)
 //   apply   : param = param * (1 - lr * wd) - lr * (nesterov ? grad + mu * ortho : ortho) ; buf = ortho
+// gcoef (optional device float): the gradients are read as bf16(g * bf16(*gcoef)) - a clip coefficient applied on
+// the fly instead of by a pass over the gradients in memory.
 int kmoe_muon_momentum(void* buf, const long long* grad_ptrs, float* sumsq, int n_mat, long long numel, float mu,
-                       cudaStream_t st);
+                       const float* gcoef, cudaStream_t st);
 int kmoe_muon_apply(void* buf, const void* ortho, const long long* grad_ptrs, const long long* param_ptrs, int n_mat,
-                    long long numel, float lr, float mu, float wd, int nesterov, cudaStream_t st);
+                    long long numel, float lr, float mu, float wd, int nesterov, const float* gcoef, cudaStream_t st);
 
 // int8 momentum of Muon8bit: blocks of `block` elements, q = rint(x / s * 127) with s = max(absmax, 1e-8).
 // x / g / out are fp32 or bf16 (is_bf16); q holds ceil(n / block) * block bytes, scales one float per block.
@@ -120,6 +122,12 @@ void kmoe_mxfp8_clear_tensormap_cache(void);
 
 // ------------------------------------------------------------ row kernels (bf16 data, fp32 math)
 int kmoe_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int d, float eps, cudaStream_t st);
+/* residual add + norm in one pass: sum_out = x + addend, y = rmsnorm(sum_out) (addend / sum_out both or neither) */
+int kmoe_add_rmsnorm_fwd(const void* x, const void* addend, const void* w, void* sum_out, void* y, float* rstd,
+                         int rows, int d, float eps, cudaStream_t st);
+/* kmoe_rmsnorm_bwd plus the gradient of the residual branch (dres, bf16 [rows, d], optional) added into dx */
+int kmoe_rmsnorm_bwd_res(const void* x, const void* w, const void* dy, const float* rstd, const void* dres, void* dx,
+                         void* dw_bf16, float* dw_f32, float* partial, int rows, int d, cudaStream_t st);
 int kmoe_rmsnorm_bwd_num_partials(int rows);
 /* nn.Linear(d, 1): y[row] = x[row, :] . w ; backward gives dx (optional) and dw (bf16 and/or fp32). */
 int kmoe_rowdot_fwd(const void* x, const void* w, void* y, int rows, int d, cudaStream_t st);

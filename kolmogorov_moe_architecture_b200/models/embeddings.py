@@ -44,6 +44,15 @@ class RotaryPositionalEmbedding(nn.Module):
 
     def tables(self, seq_len: int, position_ids: Optional[torch.Tensor]):
         if position_ids is None:
+            if self.cos_cached.is_cuda:
+                # the kernel reads fp32 tables: convert the (possibly bf16-cast) buffers once, not on every call
+                key = (self.cos_cached.data_ptr(), self.cos_cached.dtype, seq_len)
+                hit = getattr(self, "_f32_tables", None)
+                if hit is None or hit[0] != key:
+                    hit = (key, self.cos_cached[:seq_len].float().contiguous(),
+                           self.sin_cached[:seq_len].float().contiguous())
+                    self._f32_tables = hit
+                return hit[1], hit[2]
             return self.cos_cached[:seq_len], self.sin_cached[:seq_len]
         return self.cos_cached[position_ids], self.sin_cached[position_ids]
 

@@ -47,6 +47,8 @@ class TransformerBlock(nn.Module):
         self.ffn_mod_router = MoDRouter(config) if self.use_mod else None
         self.residual_dropout = nn.Dropout(config.residual_dropout)
         self.aux_loss = 0.0
+        from .embeddings import RMSNorm
+        self._rms = isinstance(self.seq_norm, RMSNorm) and isinstance(self.ffn_norm, RMSNorm)
 
     def _ffn_with_mod(self, h: torch.Tensor, residual: torch.Tensor):
         """Kept tokens go through the FFN; their weighted outputs are added onto the residual stream
@@ -59,16 +61,25 @@ class TransformerBlock(nn.Module):
     def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
                 position_ids: Optional[torch.Tensor] = None, return_aux_loss: bool = False):
         aux = 0.0
-        h = self.seq_norm(hidden_states)
+        fused_norms = self._rms and hidden_states.is_cuda
+        if fused_norms:
+            # the residual stream passes through the norm op, which sums its two gradient paths in one kernel
+            hidden_states, h = ops.residual_rmsnorm(hidden_states, None, self.seq_norm.weight, self.seq_norm.eps)
+        else:
+            h = self.seq_norm(hidden_states)
         if self.use_mamba:
             mixed = self.seq_layer(h)
         else:
             mixed = self.seq_layer(h, attention_mask=attention_mask, position_ids=position_ids)
-        hidden_states = hidden_states + self.residual_dropout(mixed)
         if self.mixer_kind == "routing_mamba" and self.training:
             aux = aux + self.seq_layer.aux_loss
 
-        h = self.ffn_norm(hidden_states)
+        if fused_norms and self.residual_dropout.p == 0.0:
+            # residual add + pre-FFN norm in one pass
+            hidden_states, h = ops.residual_rmsnorm(hidden_states, mixed, self.ffn_norm.weight, self.ffn_norm.eps)
+        else:
+            hidden_states = hidden_states + self.residual_dropout(mixed)
+            h = self.ffn_norm(hidden_states)
         if self.use_mod and self.training and self.residual_dropout.p == 0.0:
             hidden_states, mod_aux = self._ffn_with_mod(h, hidden_states)
             aux = aux + mod_aux

@@ -49,6 +49,14 @@ def rmsnorm(x, weight, eps):
     return eager.rmsnorm(x, weight, eps)
 
 
+def residual_rmsnorm(x, addend, weight, eps):
+    """(h, y): h = x + addend (x itself when addend is None), y = rmsnorm(h); residual add and norm fused."""
+    if _use_cuda(x):
+        from . import cuda_ops
+        return cuda_ops.residual_rmsnorm(x, addend, weight, eps)
+    return eager.residual_rmsnorm(x, addend, weight, eps)
+
+
 def rope_apply(x, cos, sin):
     if _use_cuda(x):
         from . import cuda_ops

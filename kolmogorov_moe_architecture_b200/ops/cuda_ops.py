@@ -298,6 +298,41 @@ def rmsnorm(x, weight, eps):
     return _RMSNorm.apply(x, weight, eps)
 
 
+class _ResidualRMSNorm(torch.autograd.Function):
+    """(h, y) with h = x (+ addend) the residual stream and y = rmsnorm(h): the residual add, the norm and - in
+    backward - the sum of the two gradient paths that meet at h (through the norm and around it) in one kernel
+    each, instead of a norm kernel plus separate add kernels in both directions."""
+
+    @staticmethod
+    def forward(ctx, x, addend, w, eps):
+        xc = x.contiguous()
+        ac = addend.contiguous() if addend is not None else None
+        h, y, rstd = K.add_rmsnorm_fwd(xc, ac, w.contiguous(), eps)
+        _count()
+        ctx.save_for_backward(h, w, rstd)
+        ctx.has_addend = addend is not None
+        return h, y
+
+    @staticmethod
+    def backward(ctx, dh, dy):
+        h, w, rstd = ctx.saved_tensors
+        if dy is None:
+            return dh, (dh if ctx.has_addend else None), None, None
+        dres = dh.contiguous() if dh is not None else None
+        dx, dw = K.rmsnorm_bwd_res(h, w.contiguous(), dy.contiguous(), rstd, dres)
+        _count(2)
+        return dx, (dx if ctx.has_addend else None), dw.to(w.dtype), None
+
+
+def residual_rmsnorm(x, addend, weight, eps):
+    """Returns (h, y): h = x + addend (x itself when ``addend`` is None), y = rmsnorm(h).  Use h as the residual
+    stream from here on, so that its two gradient paths are summed inside the norm's backward kernel."""
+    if not (_bf16(x) and _bf16(weight) and x.shape[-1] % 8 == 0 and (addend is None or _bf16(addend))):
+        _fallback("residual_rmsnorm", f"dtype {x.dtype}/{weight.dtype}")
+        return eager.residual_rmsnorm(x, addend, weight, eps)
+    return _ResidualRMSNorm.apply(x, addend, weight, eps)
+
+
 # ---------------------------------------------------------------------- RoPE
 class _Rope(torch.autograd.Function):
     @staticmethod
@@ -771,7 +806,10 @@ class _MTPLoss(torch.autograd.Function):
         R = B * S
         h2 = hidden.reshape(R, d).contiguous()
         need_grad = ctx.needs_input_grad[0] or any(ctx.needs_input_grad[5:])
-        dH = torch.zeros_like(h2) if need_grad else None
+        # dH and dW are written by the first GEMM that contributes to them (beta = 0) and accumulated by the later
+        # ones, so neither needs a zero fill nor an addend read on its first use
+        dH = torch.empty_like(h2) if need_grad else None
+        dH_started = False
         dWs: List[Optional[torch.Tensor]] = []
         per = []
         for i, W in enumerate(head_weights):
@@ -787,7 +825,7 @@ class _MTPLoss(torch.autograd.Function):
             n_valid = (lab != ignore_index).sum().clamp(min=1).float()
             gscale = (float(weights[i]) / n_valid).reshape(1).contiguous()
             Wc = W.contiguous()
-            dW = torch.zeros_like(Wc) if need_grad else None
+            dW = torch.empty_like(Wc) if need_grad else None
             loss_sum = torch.zeros((), dtype=torch.float32, device=hidden.device)
             for r0 in range(0, R, chunk_rows):
                 r1 = min(R, r0 + chunk_rows)
@@ -797,10 +835,19 @@ class _MTPLoss(torch.autograd.Function):
                 _count()
                 loss_sum = loss_sum + rows.sum()
                 if need_grad:
-                    mm_nn(logits, Wc, out=dH[r0:r1], D=dH[r0:r1], beta=1.0)
-                    mm_tn(logits, hc, out=dW, D=dW, beta=1.0)
+                    if dH_started:
+                        mm_nn(logits, Wc, out=dH[r0:r1], D=dH[r0:r1], beta=1.0)
+                    else:
+                        mm_nn(logits, Wc, out=dH[r0:r1])
+                    if r0 > 0:
+                        mm_tn(logits, hc, out=dW, D=dW, beta=1.0)
+                    else:
+                        mm_tn(logits, hc, out=dW)
+            dH_started = dH_started or need_grad
             per.append(loss_sum / n_valid)
             dWs.append(dW)
+        if need_grad and not dH_started:
+            dH.zero_()
         per_t = torch.stack(per)
         total = (per_t * _head_weight_tensor(tuple(float(w) for w in weights), hidden.device)).sum()
         ctx.shape = (B, S, d)

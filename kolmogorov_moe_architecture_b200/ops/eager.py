@@ -14,6 +14,12 @@ import torch.nn.functional as F
 
 
 # ---------------------------------------------------------------- norm / rope
+def residual_rmsnorm(x, addend, weight, eps):
+    """(h, rmsnorm(h)) with h = x + addend (x when addend is None)."""
+    h = x if addend is None else x + addend
+    return h, rmsnorm(h, weight, eps)
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """w * x / sqrt(mean(x^2) + eps) (reference: moe_arch/model/embeddings.py:191-195)."""
     var = x.pow(2).mean(-1, keepdim=True)

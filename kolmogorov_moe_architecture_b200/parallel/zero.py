@@ -397,7 +397,11 @@ class ShardedDataParallel:
         else:
             lo = a0
         hi = a0 + self.used[self.rank]
-        if hi > lo:
+        if self.fused is not None and self.muon is not None and self.adamw is None:
+            # everything outside the fused AdamW range belongs to Muon, whose kernels take the coefficient as
+            # they read the gradients: no pass over the gradients in memory
+            self.muon.grad_coef = self._clip
+        elif hi > lo:
             self.flat_grad[lo:hi].mul_(coef.to(self.flat_grad.dtype))
 
     def finish(self) -> None:

@@ -144,6 +144,13 @@ class Muon(Optimizer):
             buckets = self._bucket_state(gi, mats) if (mats and backend != "qr") else []
             fused = [self._fused_ok(stacked, ps, standard) for stacked, ps, _ in buckets]
             in_fused = {id(p) for (b, ok) in zip(buckets, fused) if ok for p in b[1]}
+            # a pending gradient coefficient (global-norm clip): the fused kernels apply it while reading the
+            # gradient, everything else is scaled in memory
+            coef = getattr(self, "grad_coef", None)
+            if coef is not None:
+                rest = [p.grad for p in live if id(p) not in in_fused]
+                if rest:
+                    torch._foreach_mul_(rest, coef.reshape(()).to(rest[0].dtype))
             if wd != 0:
                 decay = [p for p in live if id(p) not in in_fused]      # fused buckets decay inside their kernel
                 if decay:
@@ -180,9 +187,9 @@ class Muon(Optimizer):
                     # the normalisation is folded into the first Newton-Schulz GEMMs
                     gp, pp = self._bucket_ptrs(stacked, ps)
                     sumsq = torch.zeros(stacked.shape[0], dtype=torch.float32, device=stacked.device)
-                    torch.ops.kmoe.muon_momentum(stacked, gp, sumsq, mu)
+                    torch.ops.kmoe.muon_momentum(stacked, gp, sumsq, mu, coef)
                     ortho = ops.newton_schulz(stacked, iters, sumsq=sumsq)
-                    torch.ops.kmoe.muon_apply(stacked, ortho.contiguous(), gp, pp, lr, mu, wd, bool(nesterov))
+                    torch.ops.kmoe.muon_apply(stacked, ortho.contiguous(), gp, pp, lr, mu, wd, bool(nesterov), coef)
                     from ..ops import cuda_ops
                     cuda_ops._count(2)
                     continue
@@ -197,6 +204,7 @@ class Muon(Optimizer):
                 stacked.copy_(ops.newton_schulz(stacked, iters))     # the orthogonal factor replaces the momentum
                 upd = torch._foreach_add(grads, views, alpha=mu) if nesterov else views
                 torch._foreach_add_(ps, upd, alpha=-lr)
+        self.grad_coef = None
         return loss
 
     @staticmethod

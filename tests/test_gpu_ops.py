@@ -508,3 +508,28 @@ def test_capacity_mask_and_balanced_assignment_kernels(T, E, k, cap):
     assert torch.equal(got, want)
     counts = torch.bincount(got.reshape(-1), minlength=E)
     assert counts.max() <= max((T * k) // E, 1) + T        # loose: fallback picks may exceed the capacity
+
+
+@pytest.mark.parametrize("with_addend", [False, True])
+def test_residual_rmsnorm_fwd_bwd(with_addend):
+    """Residual add + RMSNorm in one op; the residual stream h is used twice downstream (through the norm and
+    around it), and both gradient paths are summed inside the backward kernel."""
+    ops, c, eager = _mods()
+    x, w = _bf(3, 37, 512, grad=True), _bf(512, grad=True)
+    a = _bf(3, 37, 512, grad=True) if with_addend else None
+    h, y = ops.residual_rmsnorm(x, a, w, 1e-5)
+    g1, g2 = _bf(3, 37, 512), _bf(3, 37, 512)
+    ((h * g1).sum() + (y * g2).sum()).backward()
+    xr, wr = _f32_leaf(x), _f32_leaf(w)
+    ar = _f32_leaf(a) if with_addend else None
+    hr, yr = eager.residual_rmsnorm(xr, ar, wr, 1e-5)
+    ((hr * g1.float()).sum() + (yr * g2.float()).sum()).backward()
+    assert _rel(h, hr) < 1e-2 and _rel(y, yr) < 1e-2
+    assert _rel(x.grad, xr.grad) < 2e-2 and _rel(w.grad, wr.grad) < 2e-2
+    if with_addend:
+        assert _rel(a.grad, ar.grad) < 2e-2
+    # only the residual branch used downstream
+    x2 = x.detach().clone().requires_grad_(True)
+    h2, _ = ops.residual_rmsnorm(x2, None, w.detach(), 1e-5)
+    (h2 * g1).sum().backward()
+    assert _rel(x2.grad, g1) < 1e-6
