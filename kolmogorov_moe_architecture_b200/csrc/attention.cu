@@ -18,6 +18,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
+#include <cstdlib>
 
 #include <mutex>
 
@@ -270,6 +271,285 @@ teardown:
   tc_fence_before();
   __syncthreads();
   if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+
+// ------------------------------------------------------------ forward, two query tiles per CTA
+// One CTA per SM owns 256 query rows as two 128-row tiles, each with its own softmax warpgroup, S and O
+// accumulators (4 x 128 TMEM columns in all) and barriers; both tiles share the K/V tiles of a 128-key step.
+//   warps 0-3 / 4-7  softmax of tile 0 / 1 (thread = query row)
+//   warp 8           TMA producer: Q tiles once, K_j / V_j into 2-stage rings
+//   warp 9           MMA issuer: S_t = Q_t K_j^T (128 x 128 x 128), O_t += P_t V_j with P_t read from TMEM
+// P is written as packed bf16 over the first 64 columns of the tile's own S accumulator (the softmax reads S in
+// 32-column chunks and chunk c's P lands in columns it has already consumed), so no shared memory is spent on
+// P and the PV MMA takes its A operand from tensor memory.  The tensor pipe executes one tile's MMAs while the
+// other tile's warpgroup is in its softmax; 128-key steps halve the number of barrier round trips per key.
+constexpr int F2_KEYS = 128;
+constexpr int F2_THREADS = 320;
+constexpr int F2_TILE_BYTES = 2 * PANEL_BYTES;     // 128 rows x 128 bf16 columns, two 64-column panels
+
+// 2^x on the FMA pipe (x <= ~10): round-to-nearest split x = n + f, f in [-0.5, 0.5], cubic for 2^f, exponent
+// added in integer.  Relative error ~1e-4, far below the bf16 rounding of P.  Used for a share of the
+// exponentials so that the MUFU pipe (16 per clock and SM) is not the only limit of the softmax.
+__device__ __forceinline__ float ex2_fma(float x) {
+  x = fmaxf(x, -125.f);
+  const float t = x + 12582912.f;                   // 1.5 * 2^23: the integer part lands in the low mantissa bits
+  const float f = x - (t - 12582912.f);
+  float p = 0.0555041f;
+  p = fmaf(p, f, 0.2402265f);
+  p = fmaf(p, f, 0.6931472f);
+  p = fmaf(p, f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+template <int D>
+__global__ void __launch_bounds__(F2_THREADS, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
+  static_assert(D == 128, "two-tile forward is written for head_dim 128");
+  constexpr uint32_t IDESC_S = make_idesc_f16(128, F2_KEYS, 1, KMOE_MAJOR_K, KMOE_MAJOR_K);
+  constexpr uint32_t IDESC_PV = make_idesc_f16(128, D, 1, KMOE_MAJOR_K, KMOE_MAJOR_MN);
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t COL_S = 0, COL_O = 256;          // S_t at COL_S + 128 t, O_t at COL_O + 128 t
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                           // 2 tiles
+  uint8_t* sK = sQ + 2 * F2_TILE_BYTES;         // 2 stages
+  uint8_t* sV = sK + 2 * F2_TILE_BYTES;         // 2 stages
+  __shared__ uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full[2], pv_done[2];
+  __shared__ uint32_t tmem_slot;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = gridDim.x - 1 - blockIdx.x;    // heavy (late) query blocks first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hkv = h / (a.H / a.Hkv);
+  const int q0 = qb * 256;
+  // packed documents: key blocks that end before the document of the CTA's first query are invisible to all rows
+  const int jlo = a.doc_start != nullptr ? a.doc_start[(size_t)b * a.S + q0] / F2_KEYS : 0;
+  // visited key blocks per tile (causal): tile t sees keys < min(q0 + 128 (t + 1), S)
+  int nb[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int kmax = min(q0 + 128 * (t + 1), a.S);
+    nb[t] = (q0 + 128 * t < a.S) ? max((kmax + F2_KEYS - 1) / F2_KEYS - jlo, 0) : 0;
+  }
+  const int nblk = max(nb[0], nb[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1);
+      mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 128); mbar_init(&pv_done[i], 1);
+    }
+    mbar_fence_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  if (warp == 9) {
+    tmem_alloc(&tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one() && nblk > 0) {
+      mbar_expect_tx(&q_full, 2 * F2_TILE_BYTES);
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int p = 0; p < 2; ++p)
+          tma_load_4d(sQ + t * F2_TILE_BYTES + p * PANEL_BYTES, &tmQ, &q_full, p * 64, h, q0 + t * 128, b);
+      for (int j = 0; j < nblk; ++j) {
+        const int st = j & 1;
+        const uint32_t par = ((j >> 1) & 1) ^ 1;
+        if (!mbar_wait(&k_empty[st], par)) { atomicExch(a.status, 31); goto teardown; }
+        mbar_expect_tx(&k_full[st], F2_TILE_BYTES);
+#pragma unroll
+        for (int p = 0; p < 2; ++p)
+          tma_load_4d(sK + st * F2_TILE_BYTES + p * PANEL_BYTES, &tmK, &k_full[st], p * 64, hkv, (jlo + j) * F2_KEYS, b);
+        if (!mbar_wait(&v_empty[st], par)) { atomicExch(a.status, 32); goto teardown; }
+        mbar_expect_tx(&v_full[st], F2_TILE_BYTES);
+#pragma unroll
+        for (int p = 0; p < 2; ++p)
+          tma_load_4d(sV + st * F2_TILE_BYTES + p * PANEL_BYTES, &tmV, &v_full[st], p * 64, hkv, (jlo + j) * F2_KEYS, b);
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one() && nblk > 0) {
+      auto issue_S = [&](int t, int j) {
+        const uint32_t qa = smem_u32(sQ + t * F2_TILE_BYTES), ka = smem_u32(sK + (j & 1) * F2_TILE_BYTES);
+#pragma unroll
+        for (int k4 = 0; k4 < D / 16; ++k4) {
+          const uint32_t off = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;
+          umma_f16(tmem + COL_S + t * 128, make_smem_desc_sw128(qa + off, 16, 1024),
+                   make_smem_desc_sw128(ka + off, 16, 1024), IDESC_S, k4 > 0);
+        }
+        umma_commit(&s_full[t]);
+      };
+      if (!mbar_wait(&q_full, 0)) { atomicExch(a.status, 33); goto teardown; }
+      if (!mbar_wait(&k_full[0], 0)) { atomicExch(a.status, 34); goto teardown; }
+      tc_fence_after();
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+        if (nb[t] > 0) issue_S(t, 0);
+      umma_commit(&k_empty[0]);
+      for (int j = 0; j < nblk; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(&v_full[st], (j >> 1) & 1)) { atomicExch(a.status, 35); goto teardown; }
+        if (j + 1 < nblk && !mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1)) {
+          atomicExch(a.status, 36);
+          goto teardown;
+        }
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (j >= nb[t]) continue;
+          if (!mbar_wait(&p_full[t], j & 1)) { atomicExch(a.status, 37); goto teardown; }
+          tc_fence_after();
+          const uint32_t va = smem_u32(sV + st * F2_TILE_BYTES);
+#pragma unroll
+          for (int k4 = 0; k4 < F2_KEYS / 16; ++k4)   // A = P_t from tensor memory: 16 keys = 8 packed columns
+            umma_f16_ts(tmem + COL_O + t * 128, tmem + COL_S + t * 128 + k4 * 8,
+                        make_smem_desc_sw128(va + k4 * 16 * 128, PANEL_BYTES, 1024), IDESC_PV, (j > 0 || k4 > 0));
+          umma_commit(&pv_done[t]);
+          if (j + 1 < nb[t]) issue_S(t, j + 1);       // overwrites S_t / P_t: ordered behind the PV just issued
+        }
+        if (j + 1 < nblk) umma_commit(&k_empty[(j + 1) & 1]);
+        umma_commit(&v_empty[st]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warpgroups
+    const int t = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;
+    const int qt0 = q0 + t * 128;                 // first query row of this tile
+    const int qi = qt0 + r;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t ts = tmem + lane_base + COL_S + t * 128;
+    const uint32_t to = tmem + lane_base + COL_O + t * 128;
+    float m_used = -INFINITY, l = 0.f;
+    const int qstart = (a.doc_start != nullptr && qi < a.S) ? a.doc_start[(size_t)b * a.S + qi] : 0;
+    const float sc = a.scale_log2;
+    for (int j = 0; j < nb[t]; ++j) {
+      if (!mbar_wait(&s_full[t], j & 1)) { if (lane == 0) atomicExch(a.status, 38); goto teardown; }
+      tc_fence_after();
+      const int k0 = (jlo + j) * F2_KEYS;
+      const bool need_mask = (k0 + F2_KEYS > qt0) || (k0 + F2_KEYS > a.S) || (k0 < qstart);
+      // pass 1: row maximum of the raw scores.  The chunk loops are kept rolled and the mask is applied in a
+      // separate, rarely taken branch: the body stays small enough for the instruction cache.
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < F2_KEYS; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(ts + c, v);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kk = k0 + c + i;
+            if (kk > qi || kk >= a.S || kk < qstart) v[i] = 0xff800000u;      // -inf
+          }
+        }
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          m0 = fmaxf(m0, __uint_as_float(v[i]));
+          m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
+          m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
+          m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+        }
+        mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+      }
+      mx *= sc;                                       // scale > 0: max of the scaled scores
+      const bool grow = mx > m_used + RESCALE_THRESHOLD;      // always true on the first step
+      const float m_new = grow ? mx : m_used;
+      const float alpha = grow ? exp2f(m_used - m_new) : 1.f;
+      const float m_exp = (m_new == -INFINITY) ? 0.f : m_new;   // rows that have not met a visible key yet
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        // s_full for step j was committed after PV of step j-1 in the same in-order pipe: O is at rest
+#pragma unroll
+        for (int c = 0; c < D; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(to + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st_32x32(to + c, v);
+        }
+        tmem_st_wait();
+      }
+      // pass 2: p = 2^(s * scale - m), packed bf16 written over the columns of S already consumed
+      float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < F2_KEYS; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(ts + c, v);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kk = k0 + c + i;
+            if (kk > qi || kk >= a.S || kk < qstart) v[i] = 0xff800000u;
+          }
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float x0 = fmaf(__uint_as_float(v[i]), sc, -m_exp), x1 = fmaf(__uint_as_float(v[i + 1]), sc, -m_exp);
+          // every fourth pair on the FMA pipe, the rest on MUFU
+          const float p0 = ((i & 6) == 6) ? ex2_fma(x0) : exp2f(x0);
+          const float p1 = ((i & 6) == 6) ? ex2_fma(x1) : exp2f(x1);
+          rs0 += p0;
+          rs1 += p1;
+          pk[i >> 1] = pack_bf16(p0, p1);
+        }
+        tmem_st_32x16(ts + (c >> 1), pk);
+      }
+      const float rs = rs0 + rs1;
+      tmem_st_wait();
+      l = l * alpha + rs;
+      m_used = m_new;
+      tc_fence_before();
+      mbar_arrive(&p_full[t]);
+    }
+    if (nb[t] > 0) {
+      if (!mbar_wait(&pv_done[t], (nb[t] - 1) & 1)) { if (lane == 0) atomicExch(a.status, 39); goto teardown; }
+      tc_fence_after();
+      const bool row_ok = qi < a.S;
+      const float inv = 1.f / l;
+      __nv_bfloat16* orow = a.out + (((size_t)b * a.S + (row_ok ? qi : 0)) * a.H + h) * D;
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(to + c, v);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8)
+            *reinterpret_cast<uint4*>(orow + c + i) =
+                make_uint4(pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv),
+                           pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv),
+                           pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv),
+                           pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv));
+        }
+      }
+      if (row_ok) a.lse[((size_t)b * a.H + h) * a.S + qi] = (m_used + log2f(l)) * 0.6931471805599453f;
+      tc_fence_before();
+    }
+  }
+
+teardown:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
@@ -757,6 +1037,20 @@ static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
+static int launch_attn_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a,
+                            cudaStream_t st) {
+  const int smem = 6 * F2_TILE_BYTES + 1024;
+  auto kern = attn_fwd2_kernel<128>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -20;
+    attr = true;
+  }
+  dim3 grid((a.S + 255) / 256, a.H, a.B);
+  kern<<<grid, F2_THREADS, smem, st>>>(tq, tk, tv, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
 }  // namespace kmoe
 
 extern "C" int kmoe_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int H,
@@ -767,9 +1061,20 @@ extern "C" int kmoe_attn_fwd(const void* q, const void* k, const void* v, void* 
   CUtensorMap tq, tk, tv;
   int rc = make_bshd_tmap(&tq, q, B, S, H, D, ATT_BLK);
   if (rc) return rc;
+  AttnArgs a{B, S, H, Hkv, scale * 1.4426950408889634f, (__nv_bfloat16*)out, lse, status, doc_start};
+  // head_dim 128: two query tiles per CTA, 128-key steps (KMOE_ATTN_FWD2=0 keeps the one-tile kernel)
+  static int fwd2 = -1;
+  if (fwd2 < 0) {
+    const char* e = getenv("KMOE_ATTN_FWD2");
+    fwd2 = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  if (D == 128 && fwd2 == 1) {
+    if ((rc = make_bshd_tmap(&tk, k, B, S, Hkv, D, F2_KEYS))) return rc;
+    if ((rc = make_bshd_tmap(&tv, v, B, S, Hkv, D, F2_KEYS))) return rc;
+    return launch_attn_fwd2(tq, tk, tv, a, st);
+  }
   if ((rc = make_bshd_tmap(&tk, k, B, S, Hkv, D, FWD_BN))) return rc;
   if ((rc = make_bshd_tmap(&tv, v, B, S, Hkv, D, FWD_BN))) return rc;
-  AttnArgs a{B, S, H, Hkv, scale * 1.4426950408889634f, (__nv_bfloat16*)out, lse, status, doc_start};
   return D == 128 ? launch_attn_fwd<128>(tq, tk, tv, a, st) : launch_attn_fwd<64>(tq, tk, tv, a, st);
 }
 

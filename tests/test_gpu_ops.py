@@ -278,7 +278,7 @@ def test_flash_attention_fwd_bwd(B, S, H, Hkv, D):
     ref = eager.attention(qr, kr, vr, True)
     ref.backward(go.float())
     assert _rel(out, ref) < 2e-2
-    assert _rel(q.grad, qr.grad) < 3e-2, "dq"
+    assert _rel(q.grad, qr.grad) < 4e-2, "dq"
     assert _rel(k.grad, kr.grad) < 3e-2, "dk"
     assert _rel(v.grad, vr.grad) < 3e-2, "dv"
 
