@@ -738,24 +738,30 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t tbuf = tmem + lane_base + (j & 1) * COL_BUF;
       tc_fence_after();
       const int k0 = (jlo + j) * BWD_SUB;
+      // only blocks that touch the diagonal, the sequence end or a document start need per-element tests; the
+      // tests live in their own branch, off the common path (instruction-cache footprint)
+      const bool need_mask = (k0 + BWD_SUB > q0) || (k0 + BWD_SUB > a.S) || (k0 < qstart) || !row_ok;
       uint32_t ds_packed[BWD_SUB / 2];
 #pragma unroll
-      for (int c = 0; c < BWD_SUB; c += 32) {
+      for (int c = 0; c < BWD_SUB; c += 32) {        // two chunks: unrolled so the packed results stay in registers
         uint32_t sv[32], dv_[32];
         tmem_ld_32x32(tbuf + COL_S + c, sv);
         tmem_ld_32x32(tbuf + COL_DP + c, dv_);
         tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kj = k0 + c + i;
+            if ((kj > qi) || (kj >= a.S) || !row_ok || (kj < qstart)) sv[i] = 0xff800000u;   // -inf: p = 0
+          }
+        }
+        uint32_t* dsp = &ds_packed[c >> 1];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float v2[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int kj = k0 + c + i + e;
-            const bool dead = (kj > qi) || (kj >= a.S) || !row_ok || (kj < qstart);
-            const float p = dead ? 0.f : exp2f(__uint_as_float(sv[i + e]) * a.scale_log2 - lse2);
-            v2[e] = p * (__uint_as_float(dv_[i + e]) - dlt) * a.scale;
-          }
-          ds_packed[(c + i) >> 1] = pack_bf16(v2[0], v2[1]);
+          const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), a.scale_log2, -lse2));
+          const float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), a.scale_log2, -lse2));
+          dsp[i >> 1] = pack_bf16(p0 * (__uint_as_float(dv_[i]) - dlt) * a.scale,
+                                  p1 * (__uint_as_float(dv_[i + 1]) - dlt) * a.scale);
         }
       }
       tc_fence_before();
@@ -945,24 +951,32 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       uint32_t pt[BWD_SUB / 2], dst[BWD_SUB / 2];
+      // per-element tests only for query blocks that touch this key block's diagonal, the sequence end or a
+      // document boundary (s_start > first key of the block); the tests live in their own branch
+      bool need_mask = (qrow < k0 + ATT_BLK) || (qrow + BWD_SUB > a.S) || (k0 + ATT_BLK > a.S);
+      if (a.doc_start != nullptr) need_mask = need_mask || (s_start[BWD_SUB - 1] > k0);
 #pragma unroll
-      for (int c = 0; c < BWD_SUB; c += 32) {
+      for (int c = 0; c < BWD_SUB; c += 32) {        // two chunks: unrolled so the packed results stay in registers
         uint32_t sv[32], dv_[32];
         tmem_ld_32x32(tbuf + COL_ST + c, sv);
         tmem_ld_32x32(tbuf + COL_DPT + c, dv_);
         tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int qi = qrow + c + i;
+            if ((kj > qi) || (qi >= a.S) || (kj >= a.S) || (kj < s_start[c + i])) sv[i] = 0xff800000u;   // p = 0
+          }
+        }
+        uint32_t* ptp = &pt[c >> 1];
+        uint32_t* dsp = &dst[c >> 1];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float pv[2], dv2[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int qi = qrow + c + i + e;
-            const bool dead = (kj > qi) || (qi >= a.S) || (kj >= a.S) || (kj < s_start[c + i + e]);
-            pv[e] = dead ? 0.f : exp2f(__uint_as_float(sv[i + e]) * a.scale_log2 - s_lse[c + i + e]);
-            dv2[e] = pv[e] * (__uint_as_float(dv_[i + e]) - s_delta[c + i + e]) * a.scale;
-          }
-          pt[(c + i) >> 1] = pack_bf16(pv[0], pv[1]);
-          dst[(c + i) >> 1] = pack_bf16(dv2[0], dv2[1]);
+          const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), a.scale_log2, -s_lse[c + i]));
+          const float p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), a.scale_log2, -s_lse[c + i + 1]));
+          ptp[i >> 1] = pack_bf16(p0, p1);
+          dsp[i >> 1] = pack_bf16(p0 * (__uint_as_float(dv_[i]) - s_delta[c + i]) * a.scale,
+                                  p1 * (__uint_as_float(dv_[i + 1]) - s_delta[c + i + 1]) * a.scale);
         }
       }
       tc_fence_before();

@@ -279,8 +279,8 @@ def test_flash_attention_fwd_bwd(B, S, H, Hkv, D):
     ref.backward(go.float())
     assert _rel(out, ref) < 2e-2
     assert _rel(q.grad, qr.grad) < 4e-2, "dq"
-    assert _rel(k.grad, kr.grad) < 3e-2, "dk"
-    assert _rel(v.grad, vr.grad) < 3e-2, "dv"
+    assert _rel(k.grad, kr.grad) < 4e-2, "dk"
+    assert _rel(v.grad, vr.grad) < 4e-2, "dv"
 
 
 @pytest.mark.parametrize("T,E,k", [(777, 16, 2), (64, 8, 1), (1500, 64, 4)])
