@@ -1022,6 +1022,474 @@ teardown:
   if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
+// ------------------------------------------------- backward for head_dim 128: 128 x 128 steps, P and dS in TMEM
+// Both kernels below keep the structure of the two-tile forward: 8 softmax warps (two warpgroups that split the
+// 128 columns of an accumulator in halves; thread = accumulator row), warp 8 is the TMA producer, warp 9 issues
+// the MMAs.  The bf16 operands made by the threads (P^T and dS^T for dK/dV, dS for dQ) are written as packed
+// pairs over accumulator columns the same warpgroup has already consumed and enter the next MMA as its A
+// operand from tensor memory, so no shared memory and no proxy fence is spent on them.  The work of a step is
+// two chains that the tensor pipe interleaves: S -> P (exponentials) and dP -> dS (needs P, kept in
+// registers); while the threads are in one chain the pipe executes the MMAs of the other.
+constexpr int B2_THREADS = 320;
+constexpr int B2_TILE_BYTES = 2 * PANEL_BYTES;     // 128 rows x 128 bf16 columns
+
+// dK, dV of one (128-key block, KV head, batch): loops over the query heads of the group and over the
+// 128-query blocks at or after the key block.  TMEM: S^T | dP^T | dV | dK, 128 columns each.
+__global__ void __launch_bounds__(B2_THREADS, 1)
+attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                     const AttnBwdArgs a) {
+  constexpr int D = 128;
+  constexpr uint32_t IDESC_ST = make_idesc_f16(128, 128, 1, KMOE_MAJOR_K, KMOE_MAJOR_K);
+  constexpr uint32_t IDESC_ACC = make_idesc_f16(128, D, 1, KMOE_MAJOR_K, KMOE_MAJOR_MN);
+  constexpr uint32_t TMEM_COLS = 512, COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + B2_TILE_BYTES;
+  uint8_t* sQ = sV + B2_TILE_BYTES;             // 2 stages
+  uint8_t* sdO = sQ + 2 * B2_TILE_BYTES;        // 2 stages
+  __shared__ uint64_t kv_full, q_full[2], q_empty[2], stat_full[2], st_full, dpt_full, p_full, ds_full, acc_full;
+  __shared__ uint32_t tmem_slot;
+  __shared__ __align__(16) float s_lse[2][128], s_delta[2][128];
+  __shared__ __align__(16) int s_start[2][128];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int G = a.H / a.Hkv;
+  const int k0 = kb * ATT_BLK;
+  const int qblk1 = (a.S + ATT_BLK - 1) / ATT_BLK;
+  int per_head = qblk1 - kb;
+  if (a.doc_start != nullptr) {
+    // packed documents: once a query block starts in a document that begins after this key block's last key,
+    // it and all later query blocks cannot see the block (document starts do not decrease along the sequence)
+    const int klast = min(k0 + ATT_BLK, a.S) - 1;
+    for (int i = 1; i < per_head; ++i) {
+      if (a.doc_start[(size_t)b * a.S + (kb + i) * ATT_BLK] > klast) { per_head = i; break; }
+    }
+  }
+  const int niter = per_head * G;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&kv_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); mbar_init(&stat_full[i], 32); }
+    mbar_init(&st_full, 1); mbar_init(&dpt_full, 1);
+    mbar_init(&p_full, 256); mbar_init(&ds_full, 256); mbar_init(&acc_full, 1);
+    mbar_fence_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmdO); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  if (warp == 9) { tmem_alloc(&tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ producer: tiles by TMA, row statistics
+    if (elect_one()) {
+      mbar_expect_tx(&kv_full, 2 * B2_TILE_BYTES);
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        tma_load_4d(sK + p * PANEL_BYTES, &tmK, &kv_full, p * 64, hkv, k0, b);
+        tma_load_4d(sV + p * PANEL_BYTES, &tmV, &kv_full, p * 64, hkv, k0, b);
+      }
+    }
+    __syncwarp();
+    for (int it = 0; it < niter; ++it) {
+      const int st = it & 1;
+      const int h = hkv * G + it / per_head;
+      const int qrow = (kb + it % per_head) * ATT_BLK;
+      // the stage (tiles and statistics) is free once the dK MMA of iteration it - 2 has completed
+      if (!mbar_wait(&q_empty[st], ((it >> 1) & 1) ^ 1)) { if (lane == 0) atomicExch(a.status, 41); goto teardown; }
+      __syncwarp();
+      if (elect_one()) {
+        mbar_expect_tx(&q_full[st], 2 * B2_TILE_BYTES);
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          tma_load_4d(sQ + st * B2_TILE_BYTES + p * PANEL_BYTES, &tmQ, &q_full[st], p * 64, h, qrow, b);
+          tma_load_4d(sdO + st * B2_TILE_BYTES + p * PANEL_BYTES, &tmdO, &q_full[st], p * 64, h, qrow, b);
+        }
+      }
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = lane + 32 * i;
+        const int qi = qrow + r;
+        const size_t si = ((size_t)b * a.H + h) * a.S + (qi < a.S ? qi : 0);
+        s_lse[st][r] = a.lse[si] * 1.4426950408889634f;
+        s_delta[st][r] = a.delta[si];
+        s_start[st][r] = (a.doc_start != nullptr && qi < a.S) ? a.doc_start[(size_t)b * a.S + qi] : 0;
+      }
+      mbar_arrive(&stat_full[st]);
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one() && niter > 0) {
+      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+      // S^T = K Q^T or dP^T = V dO^T of one stage: 128 x 128 x 128
+      auto issue_t = [&](uint32_t col, uint32_t a_base, uint32_t b_base) {
+#pragma unroll
+        for (int k4 = 0; k4 < D / 16; ++k4) {
+          const uint32_t off = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;
+          umma_f16(tmem + col, make_smem_desc_sw128(a_base + off, 16, 1024),
+                   make_smem_desc_sw128(b_base + off, 16, 1024), IDESC_ST, k4 > 0);
+        }
+      };
+      // acc += X^T Y with X^T (128 keys x 128 queries, packed bf16) in tensor memory: queries 0-63 sit in the
+      // 32 columns at `col`, queries 64-127 in the 32 columns at `col` + 64 (each warpgroup packs over its own half)
+      auto issue_acc = [&](uint32_t acc, uint32_t col, uint32_t y_base, bool first) {
+#pragma unroll
+        for (int k4 = 0; k4 < ATT_BLK / 16; ++k4)
+          umma_f16_ts(tmem + acc, tmem + col + (k4 >> 2) * 64 + (k4 & 3) * 8,
+                      make_smem_desc_sw128(y_base + k4 * 16 * 128, PANEL_BYTES, 1024), IDESC_ACC, (!first || k4 > 0));
+      };
+      if (!mbar_wait(&kv_full, 0)) { atomicExch(a.status, 42); goto teardown; }
+      if (!mbar_wait(&q_full[0], 0)) { atomicExch(a.status, 43); goto teardown; }
+      tc_fence_after();
+      issue_t(COL_ST, ka, smem_u32(sQ));
+      umma_commit(&st_full);
+      issue_t(COL_DPT, va, smem_u32(sdO));
+      umma_commit(&dpt_full);
+      for (int it = 0; it < niter; ++it) {
+        const int st = it & 1, nx = st ^ 1;
+        const uint32_t qa = smem_u32(sQ + st * B2_TILE_BYTES), da = smem_u32(sdO + st * B2_TILE_BYTES);
+        // chain 1: P^T(it) -> dV, then S^T(it + 1) over the same columns (in order behind the dV MMAs)
+        if (!mbar_wait(&p_full, it & 1)) { atomicExch(a.status, 44); goto teardown; }
+        tc_fence_after();
+        issue_acc(COL_DV, COL_ST, da, it == 0);
+        if (it + 1 < niter) {
+          if (!mbar_wait(&q_full[nx], ((it + 1) >> 1) & 1)) { atomicExch(a.status, 45); goto teardown; }
+          tc_fence_after();
+          issue_t(COL_ST, ka, smem_u32(sQ + nx * B2_TILE_BYTES));
+          umma_commit(&st_full);
+        }
+        // chain 2: dS^T(it) -> dK, then dP^T(it + 1)
+        if (!mbar_wait(&ds_full, it & 1)) { atomicExch(a.status, 46); goto teardown; }
+        tc_fence_after();
+        issue_acc(COL_DK, COL_DPT, qa, it == 0);
+        umma_commit(&q_empty[st]);
+        if (it + 1 < niter) {
+          issue_t(COL_DPT, va, smem_u32(sdO + nx * B2_TILE_BYTES));
+          umma_commit(&dpt_full);
+        }
+      }
+      umma_commit(&acc_full);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warpgroups (thread = key row)
+    const int wg = warp >> 2;
+    const int cb = wg * 64;                        // this warpgroup's query columns of the step
+    const int r = (warp & 3) * 32 + lane;
+    const int kj = k0 + r;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t t_s = tmem + lane_base + COL_ST + cb;
+    const uint32_t t_dp = tmem + lane_base + COL_DPT + cb;
+    for (int it = 0; it < niter; ++it) {
+      const int st = it & 1;
+      const int qrow = (kb + it % per_head) * ATT_BLK;
+      if (!mbar_wait(&stat_full[st], (it >> 1) & 1)) { if (lane == 0) atomicExch(a.status, 47); goto teardown; }
+      if (!mbar_wait(&st_full, it & 1)) { if (lane == 0) atomicExch(a.status, 48); goto teardown; }
+      tc_fence_after();
+      // per-element tests only for steps that touch the diagonal, the sequence end or a document boundary
+      bool need_mask = (qrow < k0 + ATT_BLK) || (qrow + ATT_BLK > a.S) || (k0 + ATT_BLK > a.S);
+      if (a.doc_start != nullptr) need_mask = need_mask || (s_start[st][ATT_BLK - 1] > k0);
+      float p[64];
+#pragma unroll
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t sv[32];
+        tmem_ld_32x32(t_s + c, sv);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int qi = qrow + cb + c + i;
+            if ((kj > qi) || (qi >= a.S) || (kj >= a.S) || (kj < s_start[st][cb + c + i])) sv[i] = 0xff800000u;
+          }
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float x0 = fmaf(__uint_as_float(sv[i]), a.scale_log2, -s_lse[st][cb + c + i]);
+          const float x1 = fmaf(__uint_as_float(sv[i + 1]), a.scale_log2, -s_lse[st][cb + c + i + 1]);
+          // every fourth pair on the FMA pipe (x <= 0 up to rounding), the rest on MUFU
+          p[c + i] = ((i & 6) == 6) ? ex2_fma(x0) : exp2f(x0);
+          p[c + i + 1] = ((i & 6) == 6) ? ex2_fma(x1) : exp2f(x1);
+          pk[i >> 1] = pack_bf16(p[c + i], p[c + i + 1]);
+        }
+        tmem_st_32x16(t_s + (c >> 1), pk);        // over columns this warpgroup has consumed
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&p_full);
+      if (!mbar_wait(&dpt_full, it & 1)) { if (lane == 0) atomicExch(a.status, 49); goto teardown; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t dv_[32];
+        tmem_ld_32x32(t_dp + c, dv_);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+          pk[i >> 1] = pack_bf16(p[c + i] * (__uint_as_float(dv_[i]) - s_delta[st][cb + c + i]) * a.scale,
+                                 p[c + i + 1] * (__uint_as_float(dv_[i + 1]) - s_delta[st][cb + c + i + 1]) * a.scale);
+        tmem_st_32x16(t_dp + (c >> 1), pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&ds_full);
+    }
+    if (niter > 0) {
+      if (!mbar_wait(&acc_full, 0)) { if (lane == 0) atomicExch(a.status, 50); goto teardown; }
+      tc_fence_after();
+    }
+    const bool row_ok = kj < a.S;
+    const size_t off = (((size_t)b * a.S + (row_ok ? kj : 0)) * a.Hkv + hkv) * D + cb;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      __nv_bfloat16* drow = (which == 0 ? a.dv : a.dk) + off;
+      const uint32_t col0 = (which == 0 ? COL_DV : COL_DK) + cb;
+#pragma unroll 1
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t v[32];
+        if (niter > 0) {
+          tmem_ld_32x32(tmem + lane_base + col0 + c, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8)
+            *reinterpret_cast<uint4*>(drow + c + i) =
+                make_uint4(pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1])),
+                           pack_bf16(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])),
+                           pack_bf16(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5])),
+                           pack_bf16(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7])));
+        }
+      }
+    }
+    tc_fence_before();
+  }
+teardown:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+// dQ of one (128-query block, head, batch): loops over the 128-key blocks the block can see.
+// TMEM: S (two buffers, step parity) | dP | dQ, 128 columns each.
+__global__ void __launch_bounds__(B2_THREADS, 1)
+attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                    const AttnBwdArgs a) {
+  constexpr int D = 128;
+  constexpr uint32_t IDESC_S = make_idesc_f16(128, 128, 1, KMOE_MAJOR_K, KMOE_MAJOR_K);
+  constexpr uint32_t IDESC_DQ = make_idesc_f16(128, D, 1, KMOE_MAJOR_K, KMOE_MAJOR_MN);
+  constexpr uint32_t TMEM_COLS = 512, COL_S = 0, COL_DP = 256, COL_DQ = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sdO = sQ + B2_TILE_BYTES;
+  uint8_t* sK = sdO + B2_TILE_BYTES;            // 2 stages
+  uint8_t* sV = sK + 2 * B2_TILE_BYTES;         // 2 stages
+  __shared__ uint64_t qdo_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], dp_full, ds_full, dq_full;
+  __shared__ uint32_t tmem_slot;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = gridDim.x - 1 - blockIdx.x;    // heavy (late) query blocks first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hkv = h / (a.H / a.Hkv);
+  const int q0 = qb * ATT_BLK;
+  const int kmax = min(q0 + ATT_BLK, a.S);
+  // packed documents: key blocks that end before the document of the block's first query are invisible to all rows
+  const int jlo = a.doc_start != nullptr ? a.doc_start[(size_t)b * a.S + q0] / ATT_BLK : 0;
+  const int nblk = (kmax + ATT_BLK - 1) / ATT_BLK - jlo;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&qdo_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+    }
+    mbar_init(&dp_full, 1); mbar_init(&ds_full, 256); mbar_init(&dq_full, 1);
+    mbar_fence_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmdO); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  if (warp == 9) { tmem_alloc(&tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 8) {
+    if (elect_one() && nblk > 0) {
+      mbar_expect_tx(&qdo_full, 2 * B2_TILE_BYTES);
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        tma_load_4d(sQ + p * PANEL_BYTES, &tmQ, &qdo_full, p * 64, h, q0, b);
+        tma_load_4d(sdO + p * PANEL_BYTES, &tmdO, &qdo_full, p * 64, h, q0, b);
+      }
+      for (int j = 0; j < nblk; ++j) {
+        const int st = j & 1;
+        const uint32_t par = ((j >> 1) & 1) ^ 1;
+        if (!mbar_wait(&k_empty[st], par)) { atomicExch(a.status, 51); goto teardown; }
+        mbar_expect_tx(&k_full[st], B2_TILE_BYTES);
+#pragma unroll
+        for (int p = 0; p < 2; ++p)
+          tma_load_4d(sK + st * B2_TILE_BYTES + p * PANEL_BYTES, &tmK, &k_full[st], p * 64, hkv, (jlo + j) * ATT_BLK, b);
+        if (!mbar_wait(&v_empty[st], par)) { atomicExch(a.status, 52); goto teardown; }
+        mbar_expect_tx(&v_full[st], B2_TILE_BYTES);
+#pragma unroll
+        for (int p = 0; p < 2; ++p)
+          tma_load_4d(sV + st * B2_TILE_BYTES + p * PANEL_BYTES, &tmV, &v_full[st], p * 64, hkv, (jlo + j) * ATT_BLK, b);
+      }
+    }
+  } else if (warp == 9) {
+    if (elect_one() && nblk > 0) {
+      const uint32_t qa = smem_u32(sQ), da = smem_u32(sdO);
+      auto issue_t = [&](uint32_t col, uint32_t a_base, uint32_t b_base) {
+#pragma unroll
+        for (int k4 = 0; k4 < D / 16; ++k4) {
+          const uint32_t off = (k4 >> 2) * PANEL_BYTES + (k4 & 3) * 32;
+          umma_f16(tmem + col, make_smem_desc_sw128(a_base + off, 16, 1024),
+                   make_smem_desc_sw128(b_base + off, 16, 1024), IDESC_S, k4 > 0);
+        }
+      };
+      if (!mbar_wait(&qdo_full, 0)) { atomicExch(a.status, 53); goto teardown; }
+      if (!mbar_wait(&k_full[0], 0)) { atomicExch(a.status, 54); goto teardown; }
+      tc_fence_after();
+      issue_t(COL_S, qa, smem_u32(sK));
+      umma_commit(&s_full[0]);
+      if (!mbar_wait(&v_full[0], 0)) { atomicExch(a.status, 55); goto teardown; }
+      tc_fence_after();
+      issue_t(COL_DP, da, smem_u32(sV));
+      umma_commit(&dp_full);
+      umma_commit(&v_empty[0]);
+      for (int j = 0; j < nblk; ++j) {
+        const int st = j & 1, nx = st ^ 1;
+        const uint32_t nph = ((j + 1) >> 1) & 1;
+        if (j + 1 < nblk) {
+          // S of the next block into the other buffer: its readers finished that buffer before dS(j - 1) arrived
+          if (!mbar_wait(&k_full[nx], nph)) { atomicExch(a.status, 54); goto teardown; }
+          tc_fence_after();
+          issue_t(COL_S + nx * 128, qa, smem_u32(sK + nx * B2_TILE_BYTES));
+          umma_commit(&s_full[nx]);
+        }
+        if (!mbar_wait(&ds_full, j & 1)) { atomicExch(a.status, 56); goto teardown; }
+        tc_fence_after();
+        // dQ += dS K_j with dS (128 queries x 128 keys, packed bf16) in tensor memory: keys 0-63 in the 32 columns
+        // at COL_DP, keys 64-127 in the 32 columns at COL_DP + 64
+        const uint32_t ka = smem_u32(sK + st * B2_TILE_BYTES);
+#pragma unroll
+        for (int k4 = 0; k4 < ATT_BLK / 16; ++k4)
+          umma_f16_ts(tmem + COL_DQ, tmem + COL_DP + (k4 >> 2) * 64 + (k4 & 3) * 8,
+                      make_smem_desc_sw128(ka + k4 * 16 * 128, PANEL_BYTES, 1024), IDESC_DQ, (j > 0 || k4 > 0));
+        umma_commit(&k_empty[st]);
+        if (j + 1 < nblk) {
+          if (!mbar_wait(&v_full[nx], nph)) { atomicExch(a.status, 55); goto teardown; }
+          tc_fence_after();
+          issue_t(COL_DP, da, smem_u32(sV + nx * B2_TILE_BYTES));   // over dS(j): in order behind the dQ MMAs
+          umma_commit(&dp_full);
+          umma_commit(&v_empty[nx]);
+        }
+      }
+      umma_commit(&dq_full);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warpgroups (thread = query row)
+    const int wg = warp >> 2;
+    const int cb = wg * 64;                        // this warpgroup's key columns of the step
+    const int r = (warp & 3) * 32 + lane;
+    const int qi = q0 + r;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const bool row_ok = qi < a.S;
+    const size_t stat = ((size_t)b * a.H + h) * a.S + (row_ok ? qi : 0);
+    const float lse2 = a.lse[stat] * 1.4426950408889634f;
+    const float dlt = a.delta[stat];
+    const int qstart = (a.doc_start != nullptr && row_ok) ? a.doc_start[(size_t)b * a.S + qi] : 0;
+    const uint32_t t_dp = tmem + lane_base + COL_DP + cb;
+    for (int j = 0; j < nblk; ++j) {
+      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1)) { if (lane == 0) atomicExch(a.status, 57); goto teardown; }
+      tc_fence_after();
+      const uint32_t t_s = tmem + lane_base + COL_S + (j & 1) * 128 + cb;
+      const int k0 = (jlo + j) * ATT_BLK;
+      const bool need_mask = (k0 + ATT_BLK > q0) || (k0 + ATT_BLK > a.S) || (k0 < qstart) || !row_ok;
+      float p[64];
+#pragma unroll
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t sv[32];
+        tmem_ld_32x32(t_s + c, sv);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kj = k0 + cb + c + i;
+            if ((kj > qi) || (kj >= a.S) || !row_ok || (kj < qstart)) sv[i] = 0xff800000u;   // -inf: p = 0
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float x0 = fmaf(__uint_as_float(sv[i]), a.scale_log2, -lse2);
+          const float x1 = fmaf(__uint_as_float(sv[i + 1]), a.scale_log2, -lse2);
+          p[c + i] = ((i & 6) == 6) ? ex2_fma(x0) : exp2f(x0);
+          p[c + i + 1] = ((i & 6) == 6) ? ex2_fma(x1) : exp2f(x1);
+        }
+      }
+      if (!mbar_wait(&dp_full, j & 1)) { if (lane == 0) atomicExch(a.status, 58); goto teardown; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t dv_[32];
+        tmem_ld_32x32(t_dp + c, dv_);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+          pk[i >> 1] = pack_bf16(p[c + i] * (__uint_as_float(dv_[i]) - dlt) * a.scale,
+                                 p[c + i + 1] * (__uint_as_float(dv_[i + 1]) - dlt) * a.scale);
+        tmem_st_32x16(t_dp + (c >> 1), pk);       // over columns this warpgroup has consumed
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&ds_full);
+    }
+    if (nblk > 0) {
+      if (!mbar_wait(&dq_full, 0)) { if (lane == 0) atomicExch(a.status, 59); goto teardown; }
+      tc_fence_after();
+    }
+    __nv_bfloat16* drow = a.dq + (((size_t)b * a.S + (row_ok ? qi : 0)) * a.H + h) * D + cb;
+#pragma unroll 1
+    for (int c = 0; c < 64; c += 32) {
+      uint32_t v[32];
+      if (nblk > 0) {
+        tmem_ld_32x32(tmem + lane_base + COL_DQ + cb + c, v);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0u;
+      }
+      if (row_ok) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8)
+          *reinterpret_cast<uint4*>(drow + c + i) =
+              make_uint4(pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1])),
+                         pack_bf16(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])),
+                         pack_bf16(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5])),
+                         pack_bf16(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7])));
+      }
+    }
+    tc_fence_before();
+  }
+teardown:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
 }  // namespace kmoe
 
 // ------------------------------------------------------------------ host side
@@ -1118,8 +1586,33 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
     attr = true;
   }
   const int nb = (a.S + ATT_BLK - 1) / ATT_BLK;
-  k1<<<dim3(nb, a.H, a.B), ATT_THREADS, smem_dq, st>>>(tq128, tdo128, tk64, tv64, a);
-  k2<<<dim3(nb, a.Hkv, a.B), ATT_THREADS, smem_dkv, st>>>(tq64, tdo64, tk128, tv128, a);
+  // head_dim 128: 128 x 128 steps with P / dS in tensor memory.  KMOE_ATTN_BWD2=0 keeps the 64-wide kernels,
+  // =dq / =dkv moves only that kernel.
+  static int bwd2 = -1;
+  constexpr int smem2 = 6 * B2_TILE_BYTES + 1024;
+  if (bwd2 < 0) {
+    const char* e = getenv("KMOE_ATTN_BWD2");
+    int mode = 3;
+    if (e != nullptr && e[0] == '0') mode = 0;
+    else if (e != nullptr && e[0] == 'd' && e[1] == 'q') mode = 1;
+    else if (e != nullptr && e[0] == 'd' && e[1] == 'k') mode = 2;
+    if (D == 128 && mode != 0) {
+      if (cudaFuncSetAttribute(attn_bwd_dq2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) !=
+              cudaSuccess ||
+          cudaFuncSetAttribute(attn_bwd_dkv2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) !=
+              cudaSuccess)
+        return -20;
+    }
+    bwd2 = mode;
+  }
+  if (D == 128 && (bwd2 & 1))
+    attn_bwd_dq2_kernel<<<dim3(nb, a.H, a.B), B2_THREADS, smem2, st>>>(tq128, tdo128, tk128, tv128, a);
+  else
+    k1<<<dim3(nb, a.H, a.B), ATT_THREADS, smem_dq, st>>>(tq128, tdo128, tk64, tv64, a);
+  if (D == 128 && (bwd2 & 2))
+    attn_bwd_dkv2_kernel<<<dim3(nb, a.Hkv, a.B), B2_THREADS, smem2, st>>>(tq128, tdo128, tk128, tv128, a);
+  else
+    k2<<<dim3(nb, a.Hkv, a.B), ATT_THREADS, smem_dkv, st>>>(tq64, tdo64, tk128, tv128, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 }  // namespace kmoe
