@@ -324,8 +324,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __shared__ uint32_t tmem_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = gridDim.x - 1 - blockIdx.x;    // heavy (late) query blocks first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // the block index is the slowest grid dimension: all heavy (late) query blocks are scheduled before any lighter one
+  const int qb = gridDim.z - 1 - blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int hkv = h / (a.H / a.Hkv);
   const int q0 = qb * 256;
   // packed documents: key blocks that end before the document of the CTA's first query are invisible to all rows
@@ -443,76 +444,65 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after();
       const int k0 = (jlo + j) * F2_KEYS;
       const bool need_mask = (k0 + F2_KEYS > qt0) || (k0 + F2_KEYS > a.S) || (k0 < qstart);
-      // pass 1: row maximum of the raw scores.  The chunk loops are kept rolled and the mask is applied in a
-      // separate, rarely taken branch: the body stays small enough for the instruction cache.
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < F2_KEYS; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(ts + c, v);
-        tmem_ld_wait();
-        if (need_mask) {
+      // The whole row of scores (128 values) is read into registers once; the mask is applied in a separate,
+      // rarely taken branch.
+      uint32_t v[F2_KEYS];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kk = k0 + c + i;
-            if (kk > qi || kk >= a.S || kk < qstart) v[i] = 0xff800000u;      // -inf
-          }
-        }
-        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+      for (int c = 0; c < F2_KEYS; c += 32) tmem_ld_32x32(ts + c, *reinterpret_cast<uint32_t(*)[32]>(&v[c]));
+      tmem_ld_wait();
+      if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          m0 = fmaxf(m0, __uint_as_float(v[i]));
-          m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
-          m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
-          m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+        for (int i = 0; i < F2_KEYS; ++i) {
+          const int kk = k0 + i;
+          if (kk > qi || kk >= a.S || kk < qstart) v[i] = 0xff800000u;      // -inf
         }
-        mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
       }
-      mx *= sc;                                       // scale > 0: max of the scaled scores
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < F2_KEYS; i += 4) {
+        m0 = fmaxf(m0, __uint_as_float(v[i]));
+        m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
+        m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
+        m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+      }
+      const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * sc;      // scale > 0: max of the scaled scores
       const bool grow = mx > m_used + RESCALE_THRESHOLD;      // always true on the first step
       const float m_new = grow ? mx : m_used;
       const float alpha = grow ? exp2f(m_used - m_new) : 1.f;
       const float m_exp = (m_new == -INFINITY) ? 0.f : m_new;   // rows that have not met a visible key yet
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
         // s_full for step j was committed after PV of step j-1 in the same in-order pipe: O is at rest
-#pragma unroll
+#pragma unroll 1
         for (int c = 0; c < D; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(to + c, v);
+          uint32_t o[32];
+          tmem_ld_32x32(to + c, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-          tmem_st_32x32(to + c, v);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32(to + c, o);
         }
         tmem_st_wait();
       }
-      // pass 2: p = 2^(s * scale - m), packed bf16 written over the columns of S already consumed
-      float rs0 = 0.f, rs1 = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < F2_KEYS; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(ts + c, v);
-        tmem_ld_wait();
-        if (need_mask) {
+      // p = 2^(s * scale - m), packed bf16 written over the first 64 columns of S (all of S is in registers)
+      const uint64_t sc2 = pack_f32x2(sc, sc), nm2 = pack_f32x2(-m_exp, -m_exp);
+      uint64_t rsum = pack_f32x2(0.f, 0.f);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kk = k0 + c + i;
-            if (kk > qi || kk >= a.S || kk < qstart) v[i] = 0xff800000u;
-          }
-        }
+      for (int c = 0; c < F2_KEYS; c += 32) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float x0 = fmaf(__uint_as_float(v[i]), sc, -m_exp), x1 = fmaf(__uint_as_float(v[i + 1]), sc, -m_exp);
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[c + i]), __uint_as_float(v[c + i + 1])), sc2, nm2), x0, x1);
           // every fourth pair on the FMA pipe, the rest on MUFU
-          const float p0 = ((i & 6) == 6) ? ex2_fma(x0) : exp2f(x0);
-          const float p1 = ((i & 6) == 6) ? ex2_fma(x1) : exp2f(x1);
-          rs0 += p0;
-          rs1 += p1;
+          const float p0 = ((i & 6) == 6) ? ex2_fma(x0) : ex2_approx(x0);
+          const float p1 = ((i & 6) == 6) ? ex2_fma(x1) : ex2_approx(x1);
+          rsum = add_f32x2(rsum, pack_f32x2(p0, p1));
           pk[i >> 1] = pack_bf16(p0, p1);
         }
         tmem_st_32x16(ts + (c >> 1), pk);
       }
+      float rs0, rs1;
+      unpack_f32x2(rsum, rs0, rs1);
       const float rs = rs0 + rs1;
       tmem_st_wait();
       l = l * alpha + rs;
@@ -1032,6 +1022,7 @@ teardown:
 // registers); while the threads are in one chain the pipe executes the MMAs of the other.
 constexpr int B2_THREADS = 320;
 constexpr int B2_TILE_BYTES = 2 * PANEL_BYTES;     // 128 rows x 128 bf16 columns
+constexpr int DKV2_Q_STAGES = 2;                   // a third stage would not fit beside K, V, two dO stages and the statistics
 
 // dK, dV of one (128-key block, KV head, batch): loops over the query heads of the group and over the
 // 128-query blocks at or after the key block.  TMEM: S^T | dP^T | dV | dK, 128 columns each.
@@ -1040,6 +1031,7 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const AttnBwdArgs a) {
   constexpr int D = 128;
+  constexpr int NQ = DKV2_Q_STAGES;
   constexpr uint32_t IDESC_ST = make_idesc_f16(128, 128, 1, KMOE_MAJOR_K, KMOE_MAJOR_K);
   constexpr uint32_t IDESC_ACC = make_idesc_f16(128, D, 1, KMOE_MAJOR_K, KMOE_MAJOR_MN);
   constexpr uint32_t TMEM_COLS = 512, COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 384;
@@ -1048,15 +1040,19 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + B2_TILE_BYTES;
-  uint8_t* sQ = sV + B2_TILE_BYTES;             // 2 stages
-  uint8_t* sdO = sQ + 2 * B2_TILE_BYTES;        // 2 stages
-  __shared__ uint64_t kv_full, q_full[2], q_empty[2], stat_full[2], st_full, dpt_full, p_full, ds_full, acc_full;
+  // Q is held until the dK MMAs of its step, the last of the step;
+  // dO is released by the dV MMAs in mid-step.
+  uint8_t* sQ = sV + B2_TILE_BYTES;             // NQ stages (with the row statistics)
+  uint8_t* sdO = sQ + NQ * B2_TILE_BYTES;        // 2 stages
+  __shared__ uint64_t kv_full, q_full[NQ], q_empty[NQ], stat_full[NQ], do_full[2], do_empty[2];
+  __shared__ uint64_t st_full, dpt_full, p_full, ds_full, acc_full;
   __shared__ uint32_t tmem_slot;
-  __shared__ __align__(16) float s_lse[2][128], s_delta[2][128];
-  __shared__ __align__(16) int s_start[2][128];
+  __shared__ __align__(16) float s_lse[NQ][128], s_delta[NQ][128];   // -lse * log2(e), -delta * scale
+  __shared__ __align__(16) int s_start[NQ][128];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  // the key block is the slowest grid dimension: the heavy (early) key blocks of all heads are scheduled first
+  const int kb = blockIdx.z, hkv = blockIdx.x, b = blockIdx.y;
   const int G = a.H / a.Hkv;
   const int k0 = kb * ATT_BLK;
   const int qblk1 = (a.S + ATT_BLK - 1) / ATT_BLK;
@@ -1073,7 +1069,8 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(&kv_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); mbar_init(&stat_full[i], 32); }
+    for (int i = 0; i < NQ; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); mbar_init(&stat_full[i], 32); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&do_full[i], 1); mbar_init(&do_empty[i], 1); }
     mbar_init(&st_full, 1); mbar_init(&dpt_full, 1);
     mbar_init(&p_full, 256); mbar_init(&ds_full, 256); mbar_init(&acc_full, 1);
     mbar_fence_init();
@@ -1097,19 +1094,17 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     __syncwarp();
     for (int it = 0; it < niter; ++it) {
-      const int st = it & 1;
+      const int qs = it % NQ, os = it & 1;
       const int h = hkv * G + it / per_head;
       const int qrow = (kb + it % per_head) * ATT_BLK;
-      // the stage (tiles and statistics) is free once the dK MMA of iteration it - 2 has completed
-      if (!mbar_wait(&q_empty[st], ((it >> 1) & 1) ^ 1)) { if (lane == 0) atomicExch(a.status, 41); goto teardown; }
+      // the Q stage (tile and statistics) is free once the dK MMAs of step it - 3 have completed
+      if (!mbar_wait(&q_empty[qs], ((it / NQ) & 1) ^ 1)) { if (lane == 0) atomicExch(a.status, 41); goto teardown; }
       __syncwarp();
       if (elect_one()) {
-        mbar_expect_tx(&q_full[st], 2 * B2_TILE_BYTES);
+        mbar_expect_tx(&q_full[qs], B2_TILE_BYTES);
 #pragma unroll
-        for (int p = 0; p < 2; ++p) {
-          tma_load_4d(sQ + st * B2_TILE_BYTES + p * PANEL_BYTES, &tmQ, &q_full[st], p * 64, h, qrow, b);
-          tma_load_4d(sdO + st * B2_TILE_BYTES + p * PANEL_BYTES, &tmdO, &q_full[st], p * 64, h, qrow, b);
-        }
+        for (int p = 0; p < 2; ++p)
+          tma_load_4d(sQ + qs * B2_TILE_BYTES + p * PANEL_BYTES, &tmQ, &q_full[qs], p * 64, h, qrow, b);
       }
       __syncwarp();
 #pragma unroll
@@ -1117,11 +1112,21 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const int r = lane + 32 * i;
         const int qi = qrow + r;
         const size_t si = ((size_t)b * a.H + h) * a.S + (qi < a.S ? qi : 0);
-        s_lse[st][r] = a.lse[si] * 1.4426950408889634f;
-        s_delta[st][r] = a.delta[si];
-        s_start[st][r] = (a.doc_start != nullptr && qi < a.S) ? a.doc_start[(size_t)b * a.S + qi] : 0;
+        s_lse[qs][r] = -a.lse[si] * 1.4426950408889634f;       // the exponent is s * scale_log2 + this
+        s_delta[qs][r] = -a.delta[si] * a.scale;                // dS = P * (dP * scale + this)
+        s_start[qs][r] = (a.doc_start != nullptr && qi < a.S) ? a.doc_start[(size_t)b * a.S + qi] : 0;
       }
-      mbar_arrive(&stat_full[st]);
+      mbar_arrive(&stat_full[qs]);
+      // the dO stage is free once the dV MMAs of step it - 2 have completed
+      if (!mbar_wait(&do_empty[os], ((it >> 1) & 1) ^ 1)) { if (lane == 0) atomicExch(a.status, 40); goto teardown; }
+      __syncwarp();
+      if (elect_one()) {
+        mbar_expect_tx(&do_full[os], B2_TILE_BYTES);
+#pragma unroll
+        for (int p = 0; p < 2; ++p)
+          tma_load_4d(sdO + os * B2_TILE_BYTES + p * PANEL_BYTES, &tmdO, &do_full[os], p * 64, h, qrow, b);
+      }
+      __syncwarp();
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
@@ -1149,28 +1154,33 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_fence_after();
       issue_t(COL_ST, ka, smem_u32(sQ));
       umma_commit(&st_full);
+      if (!mbar_wait(&do_full[0], 0)) { atomicExch(a.status, 43); goto teardown; }
+      tc_fence_after();
       issue_t(COL_DPT, va, smem_u32(sdO));
       umma_commit(&dpt_full);
       for (int it = 0; it < niter; ++it) {
-        const int st = it & 1, nx = st ^ 1;
-        const uint32_t qa = smem_u32(sQ + st * B2_TILE_BYTES), da = smem_u32(sdO + st * B2_TILE_BYTES);
+        const int qs = it % NQ, qn = (it + 1) % NQ, os = it & 1, on = os ^ 1;
+        const uint32_t qa = smem_u32(sQ + qs * B2_TILE_BYTES), da = smem_u32(sdO + os * B2_TILE_BYTES);
         // chain 1: P^T(it) -> dV, then S^T(it + 1) over the same columns (in order behind the dV MMAs)
         if (!mbar_wait(&p_full, it & 1)) { atomicExch(a.status, 44); goto teardown; }
         tc_fence_after();
         issue_acc(COL_DV, COL_ST, da, it == 0);
+        umma_commit(&do_empty[os]);
         if (it + 1 < niter) {
-          if (!mbar_wait(&q_full[nx], ((it + 1) >> 1) & 1)) { atomicExch(a.status, 45); goto teardown; }
+          if (!mbar_wait(&q_full[qn], ((it + 1) / NQ) & 1)) { atomicExch(a.status, 45); goto teardown; }
           tc_fence_after();
-          issue_t(COL_ST, ka, smem_u32(sQ + nx * B2_TILE_BYTES));
+          issue_t(COL_ST, ka, smem_u32(sQ + qn * B2_TILE_BYTES));
           umma_commit(&st_full);
         }
         // chain 2: dS^T(it) -> dK, then dP^T(it + 1)
         if (!mbar_wait(&ds_full, it & 1)) { atomicExch(a.status, 46); goto teardown; }
         tc_fence_after();
         issue_acc(COL_DK, COL_DPT, qa, it == 0);
-        umma_commit(&q_empty[st]);
+        umma_commit(&q_empty[qs]);
         if (it + 1 < niter) {
-          issue_t(COL_DPT, va, smem_u32(sdO + nx * B2_TILE_BYTES));
+          if (!mbar_wait(&do_full[on], ((it + 1) >> 1) & 1)) { atomicExch(a.status, 45); goto teardown; }
+          tc_fence_after();
+          issue_t(COL_DPT, va, smem_u32(sdO + on * B2_TILE_BYTES));
           umma_commit(&dpt_full);
         }
       }
@@ -1185,56 +1195,63 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem + lane_base + COL_ST + cb;
     const uint32_t t_dp = tmem + lane_base + COL_DPT + cb;
+    const uint64_t sl2 = pack_f32x2(a.scale_log2, a.scale_log2), sc2 = pack_f32x2(a.scale, a.scale);
     for (int it = 0; it < niter; ++it) {
-      const int st = it & 1;
+      const int st = it % NQ;
       const int qrow = (kb + it % per_head) * ATT_BLK;
-      if (!mbar_wait(&stat_full[st], (it >> 1) & 1)) { if (lane == 0) atomicExch(a.status, 47); goto teardown; }
+      if (!mbar_wait(&stat_full[st], (it / NQ) & 1)) { if (lane == 0) atomicExch(a.status, 47); goto teardown; }
       if (!mbar_wait(&st_full, it & 1)) { if (lane == 0) atomicExch(a.status, 48); goto teardown; }
       tc_fence_after();
       // per-element tests only for steps that touch the diagonal, the sequence end or a document boundary
       bool need_mask = (qrow < k0 + ATT_BLK) || (qrow + ATT_BLK > a.S) || (k0 + ATT_BLK > a.S);
       if (a.doc_start != nullptr) need_mask = need_mask || (s_start[st][ATT_BLK - 1] > k0);
-      float p[64];
-#pragma unroll
-      for (int c = 0; c < 64; c += 32) {
-        uint32_t sv[32];
-        tmem_ld_32x32(t_s + c, sv);
+      uint64_t p2[32];                             // P of this thread's 64 queries, fp32 pairs
+      {
+        uint32_t sv[64];
+        tmem_ld_32x32(t_s, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+        tmem_ld_32x32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
         tmem_ld_wait();
         if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int qi = qrow + cb + c + i;
-            if ((kj > qi) || (qi >= a.S) || (kj >= a.S) || (kj < s_start[st][cb + c + i])) sv[i] = 0xff800000u;
+          for (int i = 0; i < 64; ++i) {
+            const int qi = qrow + cb + i;
+            if ((kj > qi) || (qi >= a.S) || (kj >= a.S) || (kj < s_start[st][cb + i])) sv[i] = 0xff800000u;  // p = 0
           }
         }
-        uint32_t pk[16];
+        uint32_t pk[32];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float x0 = fmaf(__uint_as_float(sv[i]), a.scale_log2, -s_lse[st][cb + c + i]);
-          const float x1 = fmaf(__uint_as_float(sv[i + 1]), a.scale_log2, -s_lse[st][cb + c + i + 1]);
-          // every fourth pair on the FMA pipe (x <= 0 up to rounding), the rest on MUFU
-          p[c + i] = ((i & 6) == 6) ? ex2_fma(x0) : exp2f(x0);
-          p[c + i + 1] = ((i & 6) == 6) ? ex2_fma(x1) : exp2f(x1);
-          pk[i >> 1] = pack_bf16(p[c + i], p[c + i + 1]);
+        for (int i = 0; i < 32; ++i) {
+          const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), sl2,
+                                       *reinterpret_cast<const uint64_t*>(&s_lse[st][cb + 2 * i]));
+          float x0, x1;
+          unpack_f32x2(x, x0, x1);
+          const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
+          p2[i] = pack_f32x2(e0, e1);
+          pk[i] = pack_bf16(e0, e1);
         }
-        tmem_st_32x16(t_s + (c >> 1), pk);        // over columns this warpgroup has consumed
+        tmem_st_32x32(t_s, pk);                     // over columns this warpgroup has consumed
       }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_full);
       if (!mbar_wait(&dpt_full, it & 1)) { if (lane == 0) atomicExch(a.status, 49); goto teardown; }
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 64; c += 32) {
-        uint32_t dv_[32];
-        tmem_ld_32x32(t_dp + c, dv_);
+      {
+        uint32_t dv_[64];
+        tmem_ld_32x32(t_dp, *reinterpret_cast<uint32_t(*)[32]>(&dv_[0]));
+        tmem_ld_32x32(t_dp + 32, *reinterpret_cast<uint32_t(*)[32]>(&dv_[32]));
         tmem_ld_wait();
-        uint32_t pk[16];
+        uint32_t pk[32];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2)
-          pk[i >> 1] = pack_bf16(p[c + i] * (__uint_as_float(dv_[i]) - s_delta[st][cb + c + i]) * a.scale,
-                                 p[c + i + 1] * (__uint_as_float(dv_[i + 1]) - s_delta[st][cb + c + i + 1]) * a.scale);
-        tmem_st_32x16(t_dp + (c >> 1), pk);
+        for (int i = 0; i < 32; ++i) {
+          // dS = P * (dP - delta) * scale = P * (dP * scale - delta * scale)
+          const uint64_t t = fma_f32x2(pack_f32x2(__uint_as_float(dv_[2 * i]), __uint_as_float(dv_[2 * i + 1])), sc2,
+                                       *reinterpret_cast<const uint64_t*>(&s_delta[st][cb + 2 * i]));
+          float d0, d1;
+          unpack_f32x2(mul_f32x2(p2[i], t), d0, d1);
+          pk[i] = pack_bf16(d0, d1);
+        }
+        tmem_st_32x32(t_dp, pk);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -1280,7 +1297,8 @@ teardown:
 }
 
 // dQ of one (128-query block, head, batch): loops over the 128-key blocks the block can see.
-// TMEM: S (two buffers, step parity) | dP | dQ, 128 columns each.
+// TMEM: S | dP (two buffers, step parity) | dQ, 128 columns each.  S and dP of step j + 1 are issued as soon as
+// the threads have read S of step j into registers, a whole thread phase ahead of their use.
 __global__ void __launch_bounds__(B2_THREADS, 1)
 attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -1288,20 +1306,21 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr int D = 128;
   constexpr uint32_t IDESC_S = make_idesc_f16(128, 128, 1, KMOE_MAJOR_K, KMOE_MAJOR_K);
   constexpr uint32_t IDESC_DQ = make_idesc_f16(128, D, 1, KMOE_MAJOR_K, KMOE_MAJOR_MN);
-  constexpr uint32_t TMEM_COLS = 512, COL_S = 0, COL_DP = 256, COL_DQ = 384;
+  constexpr uint32_t TMEM_COLS = 512, COL_S = 0, COL_DP = 128, COL_DQ = 384;   // dP buffer b at COL_DP + 128 b
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sdO = sQ + B2_TILE_BYTES;
-  uint8_t* sK = sdO + B2_TILE_BYTES;            // 2 stages
-  uint8_t* sV = sK + 2 * B2_TILE_BYTES;         // 2 stages
-  __shared__ uint64_t qdo_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], dp_full, ds_full, dq_full;
+  // K is held until the dQ MMAs of its step: a third stage lets the load of step j + 1 start a whole step ahead
+  uint8_t* sK = sdO + B2_TILE_BYTES;            // 3 stages
+  uint8_t* sV = sK + 3 * B2_TILE_BYTES;         // 2 stages
+  __shared__ uint64_t qdo_full, k_full[3], v_full[2], k_empty[3], v_empty[2], s_full, s_free, dp_full[2], ds_full, dq_full;
   __shared__ uint32_t tmem_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = gridDim.x - 1 - blockIdx.x;    // heavy (late) query blocks first
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int qb = gridDim.z - 1 - blockIdx.z;    // slowest grid dimension: heavy (late) query blocks first
+  const int h = blockIdx.x, b = blockIdx.y;
   const int hkv = h / (a.H / a.Hkv);
   const int q0 = qb * ATT_BLK;
   const int kmax = min(q0 + ATT_BLK, a.S);
@@ -1311,11 +1330,9 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(&qdo_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1);
-    }
-    mbar_init(&dp_full, 1); mbar_init(&ds_full, 256); mbar_init(&dq_full, 1);
+    for (int i = 0; i < 3; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); mbar_init(&dp_full[i], 1); }
+    mbar_init(&s_full, 1); mbar_init(&s_free, 256); mbar_init(&ds_full, 256); mbar_init(&dq_full, 1);
     mbar_fence_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmdO); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
   }
@@ -1334,14 +1351,13 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tma_load_4d(sdO + p * PANEL_BYTES, &tmdO, &qdo_full, p * 64, h, q0, b);
       }
       for (int j = 0; j < nblk; ++j) {
-        const int st = j & 1;
-        const uint32_t par = ((j >> 1) & 1) ^ 1;
-        if (!mbar_wait(&k_empty[st], par)) { atomicExch(a.status, 51); goto teardown; }
-        mbar_expect_tx(&k_full[st], B2_TILE_BYTES);
+        const int st = j & 1, ks = j % 3;
+        if (!mbar_wait(&k_empty[ks], ((j / 3) & 1) ^ 1)) { atomicExch(a.status, 51); goto teardown; }
+        mbar_expect_tx(&k_full[ks], B2_TILE_BYTES);
 #pragma unroll
         for (int p = 0; p < 2; ++p)
-          tma_load_4d(sK + st * B2_TILE_BYTES + p * PANEL_BYTES, &tmK, &k_full[st], p * 64, hkv, (jlo + j) * ATT_BLK, b);
-        if (!mbar_wait(&v_empty[st], par)) { atomicExch(a.status, 52); goto teardown; }
+          tma_load_4d(sK + ks * B2_TILE_BYTES + p * PANEL_BYTES, &tmK, &k_full[ks], p * 64, hkv, (jlo + j) * ATT_BLK, b);
+        if (!mbar_wait(&v_empty[st], ((j >> 1) & 1) ^ 1)) { atomicExch(a.status, 52); goto teardown; }
         mbar_expect_tx(&v_full[st], B2_TILE_BYTES);
 #pragma unroll
         for (int p = 0; p < 2; ++p)
@@ -1363,39 +1379,39 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (!mbar_wait(&k_full[0], 0)) { atomicExch(a.status, 54); goto teardown; }
       tc_fence_after();
       issue_t(COL_S, qa, smem_u32(sK));
-      umma_commit(&s_full[0]);
+      umma_commit(&s_full);
       if (!mbar_wait(&v_full[0], 0)) { atomicExch(a.status, 55); goto teardown; }
       tc_fence_after();
       issue_t(COL_DP, da, smem_u32(sV));
-      umma_commit(&dp_full);
+      umma_commit(&dp_full[0]);
       umma_commit(&v_empty[0]);
       for (int j = 0; j < nblk; ++j) {
-        const int st = j & 1, nx = st ^ 1;
-        const uint32_t nph = ((j + 1) >> 1) & 1;
+        const int st = j & 1, nx = st ^ 1, ks = j % 3, kn = (j + 1) % 3;
         if (j + 1 < nblk) {
-          // S of the next block into the other buffer: its readers finished that buffer before dS(j - 1) arrived
-          if (!mbar_wait(&k_full[nx], nph)) { atomicExch(a.status, 54); goto teardown; }
+          if (!mbar_wait(&k_full[kn], ((j + 1) / 3) & 1) || !mbar_wait(&v_full[nx], ((j + 1) >> 1) & 1)) {
+            atomicExch(a.status, 54);
+            goto teardown;
+          }
+          // S(j) is in the threads' registers: S(j + 1) may overwrite it.  dP(j + 1) goes to the other dP buffer,
+          // whose dS(j - 1) the dQ MMAs of step j - 1 (earlier in this pipe) have consumed.
+          if (!mbar_wait(&s_free, j & 1)) { atomicExch(a.status, 60); goto teardown; }
           tc_fence_after();
-          issue_t(COL_S + nx * 128, qa, smem_u32(sK + nx * B2_TILE_BYTES));
-          umma_commit(&s_full[nx]);
+          issue_t(COL_S, qa, smem_u32(sK + kn * B2_TILE_BYTES));
+          umma_commit(&s_full);
+          issue_t(COL_DP + nx * 128, da, smem_u32(sV + nx * B2_TILE_BYTES));
+          umma_commit(&dp_full[nx]);
+          umma_commit(&v_empty[nx]);
         }
         if (!mbar_wait(&ds_full, j & 1)) { atomicExch(a.status, 56); goto teardown; }
         tc_fence_after();
-        // dQ += dS K_j with dS (128 queries x 128 keys, packed bf16) in tensor memory: keys 0-63 in the 32 columns
-        // at COL_DP, keys 64-127 in the 32 columns at COL_DP + 64
-        const uint32_t ka = smem_u32(sK + st * B2_TILE_BYTES);
+        // dQ += dS K_j with dS (128 queries x 128 keys, packed bf16) in the step's dP buffer: keys 0-63 in its
+        // first 32 columns, keys 64-127 in the 32 columns from column 64
+        const uint32_t ka = smem_u32(sK + ks * B2_TILE_BYTES);
 #pragma unroll
         for (int k4 = 0; k4 < ATT_BLK / 16; ++k4)
-          umma_f16_ts(tmem + COL_DQ, tmem + COL_DP + (k4 >> 2) * 64 + (k4 & 3) * 8,
+          umma_f16_ts(tmem + COL_DQ, tmem + COL_DP + st * 128 + (k4 >> 2) * 64 + (k4 & 3) * 8,
                       make_smem_desc_sw128(ka + k4 * 16 * 128, PANEL_BYTES, 1024), IDESC_DQ, (j > 0 || k4 > 0));
-        umma_commit(&k_empty[st]);
-        if (j + 1 < nblk) {
-          if (!mbar_wait(&v_full[nx], nph)) { atomicExch(a.status, 55); goto teardown; }
-          tc_fence_after();
-          issue_t(COL_DP, da, smem_u32(sV + nx * B2_TILE_BYTES));   // over dS(j): in order behind the dQ MMAs
-          umma_commit(&dp_full);
-          umma_commit(&v_empty[nx]);
-        }
+        umma_commit(&k_empty[ks]);
       }
       umma_commit(&dq_full);
     }
@@ -1411,47 +1427,56 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const float lse2 = a.lse[stat] * 1.4426950408889634f;
     const float dlt = a.delta[stat];
     const int qstart = (a.doc_start != nullptr && row_ok) ? a.doc_start[(size_t)b * a.S + qi] : 0;
-    const uint32_t t_dp = tmem + lane_base + COL_DP + cb;
+    const uint32_t t_s = tmem + lane_base + COL_S + cb;
+    const uint64_t sl2 = pack_f32x2(a.scale_log2, a.scale_log2), nlse = pack_f32x2(-lse2, -lse2);
+    const uint64_t sc2 = pack_f32x2(a.scale, a.scale), nds = pack_f32x2(-dlt * a.scale, -dlt * a.scale);
     for (int j = 0; j < nblk; ++j) {
-      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1)) { if (lane == 0) atomicExch(a.status, 57); goto teardown; }
+      if (!mbar_wait(&s_full, j & 1)) { if (lane == 0) atomicExch(a.status, 57); goto teardown; }
       tc_fence_after();
-      const uint32_t t_s = tmem + lane_base + COL_S + (j & 1) * 128 + cb;
+      const uint32_t t_dp = tmem + lane_base + COL_DP + (j & 1) * 128 + cb;
       const int k0 = (jlo + j) * ATT_BLK;
       const bool need_mask = (k0 + ATT_BLK > q0) || (k0 + ATT_BLK > a.S) || (k0 < qstart) || !row_ok;
-      float p[64];
-#pragma unroll
-      for (int c = 0; c < 64; c += 32) {
-        uint32_t sv[32];
-        tmem_ld_32x32(t_s + c, sv);
+      uint64_t p2[32];                             // P of this thread's 64 keys, fp32 pairs
+      {
+        uint32_t sv[64];
+        tmem_ld_32x32(t_s, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+        tmem_ld_32x32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
         tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&s_free);                      // S is in registers: the next S may be issued
         if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kj = k0 + cb + c + i;
+          for (int i = 0; i < 64; ++i) {
+            const int kj = k0 + cb + i;
             if ((kj > qi) || (kj >= a.S) || !row_ok || (kj < qstart)) sv[i] = 0xff800000u;   // -inf: p = 0
           }
         }
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float x0 = fmaf(__uint_as_float(sv[i]), a.scale_log2, -lse2);
-          const float x1 = fmaf(__uint_as_float(sv[i + 1]), a.scale_log2, -lse2);
-          p[c + i] = ((i & 6) == 6) ? ex2_fma(x0) : exp2f(x0);
-          p[c + i + 1] = ((i & 6) == 6) ? ex2_fma(x1) : exp2f(x1);
+        for (int i = 0; i < 32; ++i) {
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), sl2, nlse),
+                       x0, x1);
+          p2[i] = pack_f32x2(ex2_approx(x0), ex2_approx(x1));
         }
       }
-      if (!mbar_wait(&dp_full, j & 1)) { if (lane == 0) atomicExch(a.status, 58); goto teardown; }
+      if (!mbar_wait(&dp_full[j & 1], (j >> 1) & 1)) { if (lane == 0) atomicExch(a.status, 58); goto teardown; }
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 64; c += 32) {
-        uint32_t dv_[32];
-        tmem_ld_32x32(t_dp + c, dv_);
+      {
+        uint32_t dv_[64];
+        tmem_ld_32x32(t_dp, *reinterpret_cast<uint32_t(*)[32]>(&dv_[0]));
+        tmem_ld_32x32(t_dp + 32, *reinterpret_cast<uint32_t(*)[32]>(&dv_[32]));
         tmem_ld_wait();
-        uint32_t pk[16];
+        uint32_t pk[32];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2)
-          pk[i >> 1] = pack_bf16(p[c + i] * (__uint_as_float(dv_[i]) - dlt) * a.scale,
-                                 p[c + i + 1] * (__uint_as_float(dv_[i + 1]) - dlt) * a.scale);
-        tmem_st_32x16(t_dp + (c >> 1), pk);       // over columns this warpgroup has consumed
+        for (int i = 0; i < 32; ++i) {
+          // dS = P * (dP - delta) * scale = P * (dP * scale - delta * scale)
+          const uint64_t t =
+              fma_f32x2(pack_f32x2(__uint_as_float(dv_[2 * i]), __uint_as_float(dv_[2 * i + 1])), sc2, nds);
+          float d0, d1;
+          unpack_f32x2(mul_f32x2(p2[i], t), d0, d1);
+          pk[i] = pack_bf16(d0, d1);
+        }
+        tmem_st_32x32(t_dp, pk);                    // over columns this warpgroup has consumed
       }
       tmem_st_wait();
       tc_fence_before();
@@ -1528,7 +1553,7 @@ static int launch_attn_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -20;
     attr = true;
   }
-  dim3 grid((a.S + 255) / 256, a.H, a.B);
+  dim3 grid(a.H, a.B, (a.S + 255) / 256);
   kern<<<grid, F2_THREADS, smem, st>>>(tq, tk, tv, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
@@ -1589,7 +1614,7 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
   // head_dim 128: 128 x 128 steps with P / dS in tensor memory.  KMOE_ATTN_BWD2=0 keeps the 64-wide kernels,
   // =dq / =dkv moves only that kernel.
   static int bwd2 = -1;
-  constexpr int smem2 = 6 * B2_TILE_BYTES + 1024;
+  constexpr int smem2 = 7 * B2_TILE_BYTES + 1024, smem_dkv2 = (4 + DKV2_Q_STAGES) * B2_TILE_BYTES + 1024;
   if (bwd2 < 0) {
     const char* e = getenv("KMOE_ATTN_BWD2");
     int mode = 3;
@@ -1599,18 +1624,18 @@ static int launch_attn_bwd(const void* q, const void* k, const void* v, const vo
     if (D == 128 && mode != 0) {
       if (cudaFuncSetAttribute(attn_bwd_dq2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) !=
               cudaSuccess ||
-          cudaFuncSetAttribute(attn_bwd_dkv2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) !=
+          cudaFuncSetAttribute(attn_bwd_dkv2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dkv2) !=
               cudaSuccess)
         return -20;
     }
     bwd2 = mode;
   }
   if (D == 128 && (bwd2 & 1))
-    attn_bwd_dq2_kernel<<<dim3(nb, a.H, a.B), B2_THREADS, smem2, st>>>(tq128, tdo128, tk128, tv128, a);
+    attn_bwd_dq2_kernel<<<dim3(a.H, a.B, nb), B2_THREADS, smem2, st>>>(tq128, tdo128, tk128, tv128, a);
   else
     k1<<<dim3(nb, a.H, a.B), ATT_THREADS, smem_dq, st>>>(tq128, tdo128, tk64, tv64, a);
   if (D == 128 && (bwd2 & 2))
-    attn_bwd_dkv2_kernel<<<dim3(nb, a.Hkv, a.B), B2_THREADS, smem2, st>>>(tq128, tdo128, tk128, tv128, a);
+    attn_bwd_dkv2_kernel<<<dim3(a.Hkv, a.B, nb), B2_THREADS, smem_dkv2, st>>>(tq128, tdo128, tk128, tv128, a);
   else
     k2<<<dim3(nb, a.Hkv, a.B), ATT_THREADS, smem_dkv, st>>>(tq64, tdo64, tk128, tv128, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;

