@@ -276,6 +276,38 @@ def bench_norm(rows):
     report(rows, "rmsnorm fwd+bwd 8192x2048", timeit(lambda: ops.rmsnorm(x, w, 1e-5).backward(go)), None, 5 * byt)
 
 
+def bench_modules(rows):
+    """Whole modules at the shapes of the reference-side table (``baseline/micro_reference.py``): the MoE layer
+    with its router, the MoD router and the Mamba block, forward + backward."""
+    from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig
+    from kolmogorov_moe_architecture_b200.models.moe import MoELayer
+    from kolmogorov_moe_architecture_b200.models.mod import MoDRouter
+    from kolmogorov_moe_architecture_b200.models.mamba import MambaBlock
+    cfg = AdvancedMoEConfig(d_model=2048, n_layers=2, n_heads=16, n_kv_heads=4, head_dim=128, vocab_size=50304,
+                            max_seq_len=2048, n_experts=16, moe_top_k=2, d_ff_expert=4096, moe_layers=(1,),
+                            mamba_enabled=True, mamba_layers=(0,), mod_enabled=True)
+    T, d, f, k = 16384, 2048, 4096, 2
+    x = torch.randn(8, T // 8, d, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    g = torch.randn_like(x)
+
+    def fb(mod, pick=lambda o: o):
+        def run():
+            o = mod(x)
+            pick(o).backward(g) if pick(o).shape == g.shape else pick(o).backward()
+            x.grad = None
+            mod.zero_grad(set_to_none=True)
+        return run
+    moe = MoELayer(cfg, 1).cuda().to(torch.bfloat16)
+    report(rows, f"MoELayer fwd+bwd, {T} tok x {d}, 16 experts d_ff {f}, top-{k}",
+           timeit(fb(moe, lambda o: o[0] if isinstance(o, tuple) else o)), 3 * (2.0 * T * k * d * f * 3))
+    del moe
+    mod = MoDRouter(cfg).cuda().to(torch.bfloat16)
+    report(rows, "MoDRouter fwd+bwd B=8 S=2048 d=2048",
+           timeit(fb(mod, lambda o: o[1].float().sum() + o[2].float().sum())))
+    mamba = MambaBlock(cfg).cuda().to(torch.bfloat16)
+    report(rows, "MambaBlock fwd+bwd B=8 S=2048 d=2048", timeit(fb(mamba)))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--which", default="gemm,moe,mxfp8,attn,scan,ce,norm,muon")
@@ -283,7 +315,7 @@ def main():
     a = ap.parse_args()
     rows = []
     table = {"gemm": bench_gemm, "moe": bench_moe, "mxfp8": bench_mxfp8, "attn": bench_attn, "attn_docs": bench_attn_docs, "scan": bench_scan, "ce": bench_ce,
-             "norm": bench_norm, "muon": bench_muon}
+             "norm": bench_norm, "muon": bench_muon, "modules": bench_modules}
     for k in a.which.split(","):
         table[k](rows)
     if a.out:

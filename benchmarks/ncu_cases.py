@@ -20,13 +20,14 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", required=True)
     ap.add_argument("--launches", type=int, default=4)
+    ap.add_argument("--shape", default=None, help="gemm case: M,N,K (default 8192,8192,2048)")
     a = ap.parse_args()
     from kolmogorov_moe_architecture_b200 import ops
     from kolmogorov_moe_architecture_b200.ops import cuda_ops as c, eager
     bf = lambda *s, sc=0.05: (torch.randn(*s, device="cuda") * sc).to(torch.bfloat16)
     n = a.launches
     if a.case == "gemm":
-        M, N, K = 8192, 8192, 2048
+        M, N, K = (int(v) for v in a.shape.split(",")) if a.shape else (8192, 8192, 2048)
         x, w = bf(M, K), bf(N, K)
         out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
         for _ in range(n):

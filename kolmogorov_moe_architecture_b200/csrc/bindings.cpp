@@ -174,6 +174,16 @@ std::tuple<Tensor, Tensor> rowdot_bwd(const Tensor& x, const Tensor& w, const Te
   return {need_dx ? dx : at::empty({0}, x.options()), dw};
 }
 
+void sum_partials(const Tensor& partial, Tensor out) {
+  c10::cuda::CUDAGuard guard(partial.device());
+  need_f32(partial, "partial"); need_bf16(out, "out");
+  TORCH_CHECK(partial.is_contiguous() && out.is_contiguous() && partial.dim() >= 2);
+  const int64_t n = out.numel();
+  TORCH_CHECK(partial.numel() == partial.size(0) * n && n % 4 == 0, "partial must be [parts, out.numel()]");
+  check(kmoe_sum_partials(partial.data_ptr<float>(), out.data_ptr(), (int)partial.size(0), n, cur_stream()),
+        "sum_partials");
+}
+
 Tensor rope(const Tensor& x, const Tensor& cs, const Tensor& sn, bool transpose) {
   c10::cuda::CUDAGuard guard(x.device());
   need_bf16(x, "x"); need_f32(cs, "cos"); need_f32(sn, "sin");
@@ -757,6 +767,7 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("rope", &rope);
   m.def("rowdot_fwd", &rowdot_fwd);
   m.def("rowdot_bwd", &rowdot_bwd);
+  m.def("sum_partials", &sum_partials);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("swiglu_bwd_cat", &swiglu_bwd_cat);

@@ -363,6 +363,28 @@ extern "C" int kmoe_rmsnorm_bwd_res(const void* x, const void* w, const void* dy
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
+// out[i] = sum over p of partial[p][i] (fp32 partial results of a split reduction) as bf16; four values per thread.
+__global__ void sum_partials_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int nparts,
+                                    long long n) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int p = 0; p < nparts; ++p) {
+    const float4 v = *reinterpret_cast<const float4*>(partial + (size_t)p * n + i);
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
+  uint2 o;
+  o.x = pack_bf16(s.x, s.y);
+  o.y = pack_bf16(s.z, s.w);
+  *reinterpret_cast<uint2*>(out + i) = o;
+}
+
+extern "C" int kmoe_sum_partials(const float* partial, void* out, int nparts, long long n, cudaStream_t st) {
+  if (n % 4 || nparts < 1) return -1;
+  sum_partials_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(partial, (__nv_bfloat16*)out, nparts, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 extern "C" int kmoe_rowdot_fwd(const void* x, const void* w, void* y, int rows, int d, cudaStream_t st) {
   if (d % 8) return -1;
   const int block = 256, wpb = block / 32;

@@ -616,7 +616,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
       ++it;
-      const bool staged = !swiglu && !args.out_f32;   // this path awaits the accumulator after prefetching D
+      const bool staged = !swiglu && !args.out_f32;   // this path awaits the accumulator itself
       if (!staged) {
         if (!mbar_wait(&tmem_full[acc], acc_ph)) {
           if (lane == 0) atomicExch(args.status, 14);
@@ -640,25 +640,10 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (!swiglu && !args.out_f32) {
         // bf16 output: a lane holds one row, so each 64-column slab is staged in shared memory and written
         // back with 8 lanes per row (four full 128-byte lines per store instruction).  The addend is read
-        // with the same pattern, and all of it before the accumulator is awaited, so its latency falls
-        // under the main loop of this tile instead of between the slabs.
+        // with the same pattern.
         __nv_bfloat16* Cb = reinterpret_cast<__nv_bfloat16*>(args.C);
         const __nv_bfloat16* Dp = reinterpret_cast<const __nv_bfloat16*>(args.D);
         constexpr int SLABS = BN / 64;
-        uint4 dpre[SLABS][8];
-        if (Dp != nullptr) {
-#pragma unroll
-          for (int sl = 0; sl < SLABS; ++sl) {
-#pragma unroll
-            for (int i8 = 0; i8 < 8; ++i8) {
-              const int grow = row0 + i8 * 4 + (lane >> 3);
-              const int gcol = t.n_tile * BN + sl * 64 + (lane & 7) * 8;
-              dpre[sl][i8] = (grow < args.M && gcol < args.N)
-                                 ? __ldg(reinterpret_cast<const uint4*>(Dp + goff + (long long)grow * args.ldd + gcol))
-                                 : make_uint4(0, 0, 0, 0);
-            }
-          }
-        }
         if (!mbar_wait(&tmem_full[acc], acc_ph)) {
           if (lane == 0) atomicExch(args.status, 14);
           goto teardown;
@@ -666,29 +651,42 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         tc_fence_after();
         // symmetric product: a tile strictly above the diagonal also writes its transpose
         const bool mirror = args.sym_upper && t.n_tile * BN >= (t.m_tile + 1) * PAIR_TM;
-#pragma unroll
+        const bool diag = args.diag_add != 0.f && t.n_tile * BN < row0 + 32 && (t.n_tile + 1) * BN > row0;
+        // the slab loop stays rolled: unrolled, the epilogue outgrows the instruction cache and every tile
+        // of a short-reduction product stalls on instruction fetch
+#pragma unroll 1
         for (int sl = 0; sl < SLABS; ++sl) {
           const int c = sl * 64;
           if (t.n_tile * BN + c >= args.N) break;
+          // the addend of this slab is requested first: its latency falls under the accumulator reads below
+          uint4 dpre[8];
+          if (Dp != nullptr) {
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t r[32];
-            if (have_acc) {
-              tmem_ld_32x32(t_row + c + h * 32, r);
-              tmem_ld_wait();
+            for (int i8 = 0; i8 < 8; ++i8) {
+              const int grow = row0 + i8 * 4 + (lane >> 3);
+              const int gcol = t.n_tile * BN + c + (lane & 7) * 8;
+              dpre[i8] = (grow < args.M && gcol < args.N)
+                             ? __ldg(reinterpret_cast<const uint4*>(Dp + goff + (long long)grow * args.ldd + gcol))
+                             : make_uint4(0, 0, 0, 0);
             }
+          }
+          uint32_t r[64];
+          if (have_acc) {
+            tmem_ld_32x32(t_row + c, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+            tmem_ld_32x32(t_row + c + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+            tmem_ld_wait();
+          }
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              float v[8];
+          for (int j = 0; j < 64; j += 8) {
+            float v[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] = have_acc ? __uint_as_float(r[j + i]) * scale : 0.f;
-              const int col0 = t.n_tile * BN + c + h * 32 + j;
-              if (args.diag_add != 0.f && row >= col0 && row < col0 + 8) {
+            for (int i = 0; i < 8; ++i) v[i] = have_acc ? __uint_as_float(r[j + i]) * scale : 0.f;
+            if (diag) {
+              const int col0 = t.n_tile * BN + c + j;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] += (col0 + i == row) ? args.diag_add : 0.f;
-              }
-              store8<__nv_bfloat16>(&stg[lane][h * 32 + j], v);
+              for (int i = 0; i < 8; ++i) v[i] += (col0 + i == row) ? args.diag_add : 0.f;
             }
+            store8<__nv_bfloat16>(&stg[lane][j], v);
           }
           __syncwarp();
 #pragma unroll
@@ -702,7 +700,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
               if (Dp != nullptr) {
                 float v[8];
                 const __nv_bfloat162* pv = reinterpret_cast<const __nv_bfloat162*>(&o);
-                const __nv_bfloat162* pd = reinterpret_cast<const __nv_bfloat162*>(&dpre[sl][i8]);
+                const __nv_bfloat162* pd = reinterpret_cast<const __nv_bfloat162*>(&dpre[i8]);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   const float2 f = __bfloat1622float2(pv[i]);
@@ -947,7 +945,11 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
   const int TM = pair ? PAIR_TM : BM;
   const long long tm_tiles = (d->M + TM - 1) / TM;
   const int units = pair ? sms / 2 : sms;       // CTAs or CTA pairs that run at once
-  const bool use256 = swiglu || (tm_tiles * n_tiles_256 * groups >= units && d->N >= 256);
+  // 256-wide tiles unless that would leave most of the machine idle.  A CTA pair on 256 x 128 tiles asks the L2
+  // for about 1.5x the bytes per FLOP of a 256 x 256 tile and runs at nearly the same time per reduction block,
+  // so two waves of narrow tiles are slower than one partly filled wave of wide ones.
+  const long long tiles256 = tm_tiles * n_tiles_256 * groups;
+  const bool use256 = swiglu || (d->N >= 256 && (pair ? 2 * tiles256 > units : tiles256 >= units));
   const int BN = use256 ? 256 : 128;
   const int b_box_rows = pair ? BN / 2 : (swiglu ? BN / 2 : BN);
 

@@ -129,6 +129,8 @@ int kmoe_add_rmsnorm_fwd(const void* x, const void* addend, const void* w, void*
 int kmoe_rmsnorm_bwd_res(const void* x, const void* w, const void* dy, const float* rstd, const void* dres, void* dx,
                          void* dw_bf16, float* dw_f32, float* partial, int rows, int d, cudaStream_t st);
 int kmoe_rmsnorm_bwd_num_partials(int rows);
+// out (bf16, n values) = sum of nparts fp32 vectors of n values stored back to back; n % 4 == 0
+int kmoe_sum_partials(const float* partial, void* out, int nparts, long long n, cudaStream_t st);
 /* nn.Linear(d, 1): y[row] = x[row, :] . w ; backward gives dx (optional) and dw (bf16 and/or fp32). */
 int kmoe_rowdot_fwd(const void* x, const void* w, void* y, int rows, int d, cudaStream_t st);
 int kmoe_rowdot_bwd(const void* x, const void* w, const void* dy, void* dx, void* dw_bf16, float* dw_f32,

@@ -260,6 +260,140 @@ __global__ void seq_topk_fwd_kernel(const float* __restrict__ scores, long long 
   for (int i = threadIdx.x; i < k; i += blockDim.x) w_out[(size_t)r * k + i] /= tot;
 }
 
+// Mode 0 without a sort: the k-th best key of the row is found by a 4-pass radix selection over
+// order-preserving 32-bit images of the scores (256-bin histograms in shared memory), then one block-wide
+// prefix count places the kept positions in ascending order.  Same result as the sorting kernel above: keys
+// compare by value descending and index ascending, so of the scores equal to the threshold the lowest
+// positions are kept.  (The images order -0.0 below +0.0.)
+__device__ __forceinline__ uint32_t score_key(float v) {
+  const uint32_t u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_score(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
+}
+
+__global__ void __launch_bounds__(1024)
+seq_topk_select_kernel(const float* __restrict__ scores, long long row_stride, long long col_stride, int rows_inner,
+                       long long outer_stride, int S, int k, long long* __restrict__ idx_out,
+                       float* __restrict__ w_out) {
+  extern __shared__ uint32_t ukey[];                 // [S]
+  __shared__ int hist[256];
+  __shared__ int warp_tot[32];
+  __shared__ float red[32];
+  __shared__ uint32_t s_prefix, s_top;
+  __shared__ int s_need;
+  const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const float* base = scores + (long long)(r / rows_inner) * outer_stride + (long long)(r % rows_inner) * row_stride;
+  uint32_t mxk = 0;
+  for (int i = tid; i < S; i += 1024) {
+    const uint32_t u = score_key(base[(long long)i * col_stride]);
+    ukey[i] = u;
+    mxk = max(mxk, u);
+  }
+  mxk = __reduce_max_sync(0xffffffffu, mxk);
+  if (lane == 0) warp_tot[wid] = (int)mxk;
+  if (tid == 0) { s_prefix = 0u; s_need = k; }
+  __syncthreads();
+  if (wid == 0) {
+    const uint32_t m = __reduce_max_sync(0xffffffffu, (uint32_t)warp_tot[lane]);
+    if (lane == 0) s_top = m;
+  }
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    if (tid < 256) hist[tid] = 0;
+    __syncthreads();
+    const uint32_t prefix = s_prefix;
+    const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+    for (int i = tid; i < S; i += 1024) {
+      const uint32_t u = ukey[i];
+      if ((u & mask) == prefix) atomicAdd(&hist[(u >> shift) & 255u], 1);
+    }
+    __syncthreads();
+    if (wid == 0) {
+      // lane L owns bins 8L .. 8L+7; the wanted key lies in the bin where the count from the top reaches `need`
+      int c[8], tot = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { c[j] = hist[8 * lane + j]; tot += c[j]; }
+      int suf = tot;                                 // sum over this and all higher lanes
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_down_sync(0xffffffffu, suf, o);
+        if (lane + o < 32) suf += t;
+      }
+      const int need = s_need;
+      int above = suf - tot;
+      if (above < need && need <= suf) {
+#pragma unroll
+        for (int j = 7; j >= 0; --j) {
+          if (above < need && above + c[j] >= need) {
+            s_prefix = prefix | ((uint32_t)(8 * lane + j) << shift);
+            s_need = need - above;
+            above = need;                            // taken: no lower bin matches
+          } else {
+            above += c[j];
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  const uint32_t thr = s_prefix;
+  const int need = s_need;                           // how many of the scores equal to the threshold are kept
+  // exclusive prefix counts (greater in the low half-word, equal in the high one) over contiguous chunks
+  const int per = (S + 1023) / 1024;
+  const int b0 = tid * per, b1 = min(b0 + per, S);
+  int packed = 0;
+  for (int i = b0; i < b1; ++i) {
+    const uint32_t u = ukey[i];
+    packed += (u > thr ? 1 : 0) + (u == thr ? 0x10000 : 0);
+  }
+  int inc = packed;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) warp_tot[wid] = inc;
+  __syncthreads();
+  if (wid == 0) {
+    const int w = warp_tot[lane];
+    int winc = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, winc, o);
+      if (lane >= o) winc += t;
+    }
+    warp_tot[lane] = winc - w;
+  }
+  __syncthreads();
+  const int excl = warp_tot[wid] + inc - packed;
+  int g = excl & 0xffff, e = excl >> 16;
+  const float top = key_score(s_top);
+  float den = 0.f;
+  for (int i = b0; i < b1; ++i) {
+    const uint32_t u = ukey[i];
+    const bool eq = u == thr;
+    if (u > thr || (eq && e < need)) {
+      const int o = g + min(e, need);
+      const float ex = __expf(key_score(u) - top);
+      idx_out[(size_t)r * k + o] = i;
+      w_out[(size_t)r * k + o] = ex;                 // normalised below
+      den += ex;
+    }
+    g += (u > thr) ? 1 : 0;
+    e += eq ? 1 : 0;
+  }
+  den = warp_sum(den);
+  if (lane == 0) red[wid] = den;
+  __threadfence_block();
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll 8
+  for (int i = 0; i < 32; ++i) tot += red[i];
+  for (int i = tid; i < k; i += 1024) w_out[(size_t)r * k + i] /= tot;
+}
+
 // mode 0: dscore[idx_j] = w_j (dw_j - sum_l w_l dw_l), zero elsewhere.
 // mode 1: p = softmax(row); w_j = p_j / (tot + eps); dp_j = (dw_j - sum_l dw_l w_l) / (tot + eps);
 //         dscore_t = p_t (dp_t - sum_j p_j dp_j)   (dp = 0 for tokens that were not picked)
@@ -349,7 +483,15 @@ extern "C" int kmoe_seq_topk_fwd(const float* scores, long long row_stride, long
   if (!attr_set) {
     if (cudaFuncSetAttribute(seq_topk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 8) != cudaSuccess)
       return -3;
+    if (cudaFuncSetAttribute(seq_topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 4) !=
+        cudaSuccess)
+      return -3;
     attr_set = true;
+  }
+  if (mode == 0) {      // kept positions in ascending order: selection instead of a sort
+    seq_topk_select_kernel<<<rows, 1024, (size_t)S * 4, st>>>(scores, row_stride, col_stride, rows_inner,
+                                                              outer_stride, S, k, idx, w);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }
   seq_topk_fwd_kernel<<<rows, 1024, smem, st>>>(scores, row_stride, col_stride, rows_inner, outer_stride, S, S2, k,
                                                 mode, idx, w, stat);

@@ -144,20 +144,57 @@ def _linear_ok(x2: torch.Tensor, w: torch.Tensor) -> bool:
             and x2.shape[0] % 8 == 0 and x2.shape[0] > 0)
 
 
+_SPLITK_RANGES: dict = {}
+
+
+def split_k_parts(out_f: int, in_f: int, T: int) -> int:
+    """Number of slices of the token dimension for a weight gradient whose (out_f, in_f) result is only a few
+    output tiles: with T in the thousands such a GEMM would keep a handful of SMs busy for its whole length.
+    Slices are at least 512 tokens long and aim at ~128 tiles in flight; 1 = no split."""
+    tiles = -(-out_f // 256) * -(-in_f // 256)
+    if tiles >= 48 or T < 2048 or os.environ.get("KMOE_SPLITK", "1") == "0":
+        return 1
+    return max(1, min(128 // tiles, T // 512, 32))
+
+
+def _split_k_ranges(T: int, parts: int, device):
+    key = (T, parts, device)
+    hit = _SPLITK_RANGES.get(key)
+    if hit is None:
+        step = -(-(-(-T // parts)) // 64) * 64            # slice length: a whole number of 64-row reduction blocks
+        begin = [min(i * step, T) for i in range(parts)]
+        length = [max(0, min(step, T - b)) for b in begin]
+        hit = (torch.tensor(begin, dtype=torch.int32, device=device),
+               torch.tensor(length, dtype=torch.int32, device=device))
+        _SPLITK_RANGES[key] = hit
+    return hit
+
+
 def _wgrad(dy: torch.Tensor, x2: torch.Tensor, w: torch.Tensor):
     """dW = dy^T x2 into the weight's slot of the flat gradient buffer when one is registered (returns None
-    then), else into a new tensor."""
+    then), else into a new tensor.  Narrow results (router and projection matrices of a few output tiles) are
+    computed as slices of the token dimension in one batched launch, fp32 partial results, and summed."""
     out_f, in_f = w.shape
     T = x2.shape[0]
     sink = grad_sink(w)
     dst = sink[0] if sink is not None else torch.empty_like(w)
+    parts = split_k_parts(out_f, in_f, T) if (out_f * in_f) % 4 == 0 and dst.is_contiguous() else 1
+    out, extra = dst, {}
+    if parts > 1:
+        kb, kl = _split_k_ranges(T, parts, dy.device)
+        out = torch.empty(parts, out_f, in_f, dtype=torch.float32, device=dy.device)
+        extra = dict(mode=BATCHED, groups=parts, k_begin=kb, k_len=kl, c_gs=out_f * in_f)
     if out_f % 64 == 0:
-        mm_tn(dy, x2, out=dst)
+        gemm(dy, x2, out, M=out_f, N=in_f, Kd=T, a_major=MAJ_MN, b_major=MAJ_MN, lda=dy.stride(0),
+             ldb=x2.stride(0), ldc=in_f if parts > 1 else dst.stride(0), **extra)
     else:
         # dy is too narrow to be read MN-major (rows of whole 64-element atoms): use its transpose, K-major
         dyT = dy.t().contiguous()
-        gemm(dyT, x2, dst, M=out_f, N=in_f, Kd=T, a_major=MAJ_K, b_major=MAJ_MN, lda=T, ldb=x2.stride(0),
-             ldc=dst.stride(0))
+        gemm(dyT, x2, out, M=out_f, N=in_f, Kd=T, a_major=MAJ_K, b_major=MAJ_MN, lda=T, ldb=x2.stride(0),
+             ldc=in_f if parts > 1 else dst.stride(0), **extra)
+    if parts > 1:
+        K.sum_partials(out, dst)
+        _count()
     if sink is not None:
         sink[1]()
         return None
