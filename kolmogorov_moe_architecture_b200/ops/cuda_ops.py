@@ -162,8 +162,8 @@ def _split_k_ranges(T: int, parts: int, device):
     hit = _SPLITK_RANGES.get(key)
     if hit is None:
         step = -(-(-(-T // parts)) // 64) * 64            # slice length: a whole number of 64-row reduction blocks
-        begin = [min(i * step, T) for i in range(parts)]
-        length = [max(0, min(step, T - b)) for b in begin]
+        begin = list(range(0, T, step))                   # rounding up may leave fewer slices than asked for
+        length = [min(step, T - b) for b in begin]
         hit = (torch.tensor(begin, dtype=torch.int32, device=device),
                torch.tensor(length, dtype=torch.int32, device=device))
         _SPLITK_RANGES[key] = hit
@@ -182,6 +182,7 @@ def _wgrad(dy: torch.Tensor, x2: torch.Tensor, w: torch.Tensor):
     out, extra = dst, {}
     if parts > 1:
         kb, kl = _split_k_ranges(T, parts, dy.device)
+        parts = kb.numel()
         out = torch.empty(parts, out_f, in_f, dtype=torch.float32, device=dy.device)
         extra = dict(mode=BATCHED, groups=parts, k_begin=kb, k_len=kl, c_gs=out_f * in_f)
     if out_f % 64 == 0:

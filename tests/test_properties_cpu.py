@@ -303,3 +303,25 @@ def test_extension_errors_raise_instead_of_crashing():
     with pytest.raises(RuntimeError, match="kmoe::self_test failed with code -7"):
         torch.ops.kmoe.raise_check(-7)
     torch.ops.kmoe.raise_check(0)
+
+
+@settings(max_examples=60, deadline=None)
+@given(out_f=st.sampled_from([8, 16, 40, 64, 128, 160, 512, 2048, 4096]),
+       in_f=st.sampled_from([64, 128, 512, 2048, 4096]),
+       T=st.integers(min_value=1, max_value=40000).map(lambda v: v * 8))
+def test_weight_gradient_token_slices_cover_every_token_once(out_f, in_f, T):
+    """The slices of a sliced weight gradient start on whole 64-row reduction blocks, do not overlap, and
+    together cover exactly the T tokens; large results and short sequences are not sliced."""
+    from kolmogorov_moe_architecture_b200.ops import cuda_ops as c
+    parts = c.split_k_parts(out_f, in_f, T)
+    assert 1 <= parts <= 32
+    tiles = -(-out_f // 256) * -(-in_f // 256)
+    if tiles >= 48 or T < 2048:
+        assert parts == 1
+        return
+    begin, length = (t.tolist() for t in c._split_k_ranges(T, parts, torch.device("cpu")))
+    assert 1 <= len(begin) <= parts and begin[0] == 0 and sum(length) == T
+    for i in range(len(begin)):
+        assert begin[i] % 64 == 0 and length[i] > 0
+        if i + 1 < len(begin):
+            assert begin[i] + length[i] == begin[i + 1]
