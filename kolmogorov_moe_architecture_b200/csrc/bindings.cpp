@@ -37,11 +37,17 @@ void gemm(const Tensor& A, const Tensor& B, const OptT& B2, Tensor C, const OptT
           int64_t b_major, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd, int64_t a_gs, int64_t b_gs,
           int64_t c_gs, const OptT& tile_group, const OptT& num_m_tiles, const OptT& k_begin, const OptT& k_len,
           double alpha, double beta, const OptT& row_scale, const OptT& row_ptr, const OptT& alpha_dev,
-          const OptT& beta_dev, bool sym_upper, double diag_add, int64_t k_split, Tensor status) {
+          const OptT& beta_dev, bool sym_upper, double diag_add, int64_t k_split, const OptT& D2, double beta2,
+          Tensor status) {
   c10::cuda::CUDAGuard guard(A.device());
   need_bf16(A, "A");
   need_bf16(B, "B");
   KmoeGemmDesc d{};
+  d.D2 = ptr_or_null(D2);
+  d.beta2 = (float)beta2;
+  if (D2.has_value() && D2->defined())
+    TORCH_CHECK(D2->scalar_type() == at::kBFloat16 && D.has_value() && D->defined() && D2->sizes() == D->sizes() &&
+                D2->strides() == D->strides(), "D2 must be a bf16 tensor laid out like D");
   d.A = A.data_ptr(); d.B = B.data_ptr(); d.B2 = ptr_or_null(B2); d.C = C.data_ptr();
   d.D = ptr_or_null(D); d.G_out = const_cast<void*>(ptr_or_null(G)); d.U_out = const_cast<void*>(ptr_or_null(U));
   d.mode = (int)mode; d.epilogue = (int)epilogue; d.M = (int)M; d.N = (int)N; d.K = (int)K; d.groups = (int)groups;

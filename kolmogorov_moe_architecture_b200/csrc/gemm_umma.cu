@@ -36,6 +36,7 @@ constexpr int NUM_THREADS = 192;
 struct GemmArgs {
   void* C;
   const void* D;
+  const void* D2;
   void* G_out;
   void* U_out;
   int mode, epilogue;
@@ -47,7 +48,7 @@ struct GemmArgs {
   const int* k_begin;
   const int* k_len;
   int out_f32;
-  float alpha, beta;
+  float alpha, beta, beta2;
   const float* row_scale;
   const float* alpha_dev;     // optional per-group multipliers of alpha / beta (BATCHED: index = group)
   const float* beta_dev;
@@ -652,6 +653,12 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         // symmetric product: a tile strictly above the diagonal also writes its transpose
         const bool mirror = args.sym_upper && t.n_tile * BN >= (t.m_tile + 1) * PAIR_TM;
         const bool diag = args.diag_add != 0.f && t.n_tile * BN < row0 + 32 && (t.n_tile + 1) * BN > row0;
+        // Addends of a symmetric product (and every second addend) are added before the slab is staged, each lane
+        // reading its own row, so that the mirrored tile is written from final values.
+        const __nv_bfloat16* D2p = reinterpret_cast<const __nv_bfloat16*>(args.D2);
+        const bool d_early = Dp != nullptr && (args.sym_upper || D2p != nullptr);
+        float beta2 = args.beta2;
+        if (args.beta_dev != nullptr) beta2 *= args.beta_dev[t.g_c];
         // the slab loop stays rolled: unrolled, the epilogue outgrows the instruction cache and every tile
         // of a short-reduction product stalls on instruction fetch
 #pragma unroll 1
@@ -660,16 +667,17 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if (t.n_tile * BN + c >= args.N) break;
           // the addend of this slab is requested first: its latency falls under the accumulator reads below
           uint4 dpre[8];
-          if (Dp != nullptr) {
+          auto load_addend = [&](const __nv_bfloat16* P) {      // 8 lanes per row: full 128-byte lines
 #pragma unroll
             for (int i8 = 0; i8 < 8; ++i8) {
               const int grow = row0 + i8 * 4 + (lane >> 3);
               const int gcol = t.n_tile * BN + c + (lane & 7) * 8;
               dpre[i8] = (grow < args.M && gcol < args.N)
-                             ? __ldg(reinterpret_cast<const uint4*>(Dp + goff + (long long)grow * args.ldd + gcol))
+                             ? __ldg(reinterpret_cast<const uint4*>(P + goff + (long long)grow * args.ldd + gcol))
                              : make_uint4(0, 0, 0, 0);
             }
-          }
+          };
+          if (Dp != nullptr) load_addend(Dp);
           uint32_t r[64];
           if (have_acc) {
             tmem_ld_32x32(t_row + c, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
@@ -677,17 +685,39 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             tmem_ld_wait();
           }
 #pragma unroll
-          for (int j = 0; j < 64; j += 8) {
-            float v[8];
+          for (int i = 0; i < 64; ++i) r[i] = have_acc ? __float_as_uint(__uint_as_float(r[i]) * scale) : 0u;
+          if (diag) {
+            const int col0 = t.n_tile * BN + c;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = have_acc ? __uint_as_float(r[j + i]) * scale : 0.f;
-            if (diag) {
-              const int col0 = t.n_tile * BN + c + j;
-#pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] += (col0 + i == row) ? args.diag_add : 0.f;
-            }
-            store8<__nv_bfloat16>(&stg[lane][j], v);
+            for (int i = 0; i < 64; ++i)
+              if (col0 + i == row) r[i] = __float_as_uint(__uint_as_float(r[i]) + args.diag_add);
           }
+          if (d_early) {
+            // the addends pass through the staging buffer to reach the lane that owns their row
+#pragma unroll 1
+            for (int pass = 0; pass < (D2p != nullptr ? 2 : 1); ++pass) {
+              const float bcoef = pass == 0 ? beta : beta2;
+              if (pass == 1) load_addend(D2p);
+#pragma unroll
+              for (int i8 = 0; i8 < 8; ++i8)
+                *reinterpret_cast<uint4*>(&stg[i8 * 4 + (lane >> 3)][(lane & 7) * 8]) = dpre[i8];
+              __syncwarp();
+#pragma unroll
+              for (int j8 = 0; j8 < 8; ++j8) {
+                const uint4 q4 = *reinterpret_cast<const uint4*>(&stg[lane][j8 * 8]);
+                const __nv_bfloat162* pq = reinterpret_cast<const __nv_bfloat162*>(&q4);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float2 f = __bfloat1622float2(pq[i]);
+                  r[j8 * 8 + 2 * i] = __float_as_uint(__uint_as_float(r[j8 * 8 + 2 * i]) + bcoef * f.x);
+                  r[j8 * 8 + 2 * i + 1] = __float_as_uint(__uint_as_float(r[j8 * 8 + 2 * i + 1]) + bcoef * f.y);
+                }
+              }
+              __syncwarp();
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 64; j += 8) store8<__nv_bfloat16>(&stg[lane][j], reinterpret_cast<const float*>(&r[j]));
           __syncwarp();
 #pragma unroll
           for (int i8 = 0; i8 < 8; ++i8) {
@@ -697,7 +727,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const int gcol = t.n_tile * BN + c + cc;
             if (grow < args.M && gcol < args.N) {
               uint4 o = *reinterpret_cast<const uint4*>(&stg[rr][cc]);
-              if (Dp != nullptr) {
+              if (Dp != nullptr && !d_early) {
                 float v[8];
                 const __nv_bfloat162* pv = reinterpret_cast<const __nv_bfloat162*>(&o);
                 const __nv_bfloat162* pd = reinterpret_cast<const __nv_bfloat162*>(&dpre[i8]);
@@ -954,7 +984,7 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
   const int b_box_rows = pair ? BN / 2 : (swiglu ? BN / 2 : BN);
 
   GemmArgs a;
-  a.C = d->C; a.D = d->D; a.G_out = d->G_out; a.U_out = d->U_out;
+  a.C = d->C; a.D = d->D; a.D2 = d->D2; a.beta2 = d->beta2; a.G_out = d->G_out; a.U_out = d->U_out;
   a.mode = d->mode; a.epilogue = d->epilogue;
   a.M = d->M; a.N = d->N; a.K = d->K; a.groups = d->groups;
   a.ldc = d->ldc; a.ldd = d->ldd ? d->ldd : d->ldc; a.c_gstride = d->c_gstride;
@@ -968,8 +998,10 @@ extern "C" int kmoe_gemm(const KmoeGemmDesc* d, cudaStream_t stream) {
   a.diag_add = d->diag_add;
   a.k_split = d->k_split;
   if (d->sym_upper && (d->M != d->N || swiglu || d->mode == KMOE_GEMM_GROUPED_M || d->out_f32 || d->N % 32 ||
-                       d->D != nullptr))
+                       (d->D != nullptr && !pair)))
     return -4;
+  // the second addend exists in the bf16 epilogue of the CTA-pair kernel only
+  if (d->D2 != nullptr && (!pair || swiglu || d->out_f32 || d->D == nullptr)) return -6;
 
   // The reduction extent seen by TMA: ragged batched GEMMs index a shared [sum K, rows] buffer.
   long long k_extent_a = d->K, k_extent_b = d->K;

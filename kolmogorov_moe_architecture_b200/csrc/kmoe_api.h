@@ -21,6 +21,7 @@ typedef struct KmoeGemmDesc {
   const void* B2;       // SWIGLU epilogue only: second weight (same layout as B)
   void* C;              // bf16 or fp32 output, row-major [M, N] (ldc)
   const void* D;        // optional addend with C's type and ldd
+  const void* D2;       // optional second addend (bf16 output, CTA-pair kernel): C = alpha A B + beta D + beta2 D2
   void* G_out;          // SWIGLU only, optional: pre-activation gate, [M, N] bf16 (ldc)
   void* U_out;          // SWIGLU only, optional: up projection
   int mode;             // KMOE_GEMM_*
@@ -38,7 +39,7 @@ typedef struct KmoeGemmDesc {
   const int* k_begin;
   const int* k_len;
   int out_f32;
-  float alpha, beta;
+  float alpha, beta, beta2;
   const float* row_scale;  // optional per-row multiplier applied to the product
   // optional (STORE epilogue): device array with the address of every output row, which may lie in a
   // peer GPU's memory; 0 skips the row.  Replaces C + row * ldc; D is still read at its usual place.
@@ -47,8 +48,8 @@ typedef struct KmoeGemmDesc {
   // multiplied by them, so scalars computed on the device (e.g. 1 / norm) need no separate pass.
   const float* alpha_dev;
   const float* beta_dev;
-  // C = A A^T style products (M == N, A and B the same operand, bf16 output, no addend): tiles entirely below
-  // the diagonal are not computed but mirrored from the upper part afterwards.
+  // Symmetric products (M == N, bf16 output; A A^T, or two commuting symmetric operands): tiles entirely below
+  // the diagonal are not computed but mirrored from the upper part.  Addends must be symmetric too.
   int sym_upper;
   // added to the elements on the main diagonal of every (group's) output after alpha is applied (STORE
   // epilogue, bf16 output): C = alpha * A B + diag_add * I, e.g. the 1.5 I - 0.5 X X^T factor of Newton-Schulz

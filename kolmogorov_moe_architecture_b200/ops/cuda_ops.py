@@ -84,17 +84,20 @@ def _count(n: int = 1):
 def gemm(A, B, C, *, M, N, Kd, mode=DENSE, epi=EPI_STORE, groups=1, a_major=MAJ_K, b_major=MAJ_K,
          lda, ldb, ldc, ldd=0, a_gs=0, b_gs=0, c_gs=0, B2=None, D=None, G=None, U=None,
          tile_group=None, num_m_tiles=None, k_begin=None, k_len=None, alpha=1.0, beta=0.0, row_scale=None,
-         row_ptr=None, alpha_dev=None, beta_dev=None, sym_upper=False, diag_add=0.0, k_split=0):
+         row_ptr=None, alpha_dev=None, beta_dev=None, sym_upper=False, diag_add=0.0, k_split=0, D2=None,
+         beta2=0.0):
     """``row_ptr`` (int64, one address per output row, 0 = skip) redirects each output row, e.g. into a
     peer GPU's buffer; ``C`` then only supplies the dtype.  ``alpha_dev`` / ``beta_dev`` (fp32, one entry
     per group of a batched GEMM) multiply alpha / beta with values that live on the device.  ``sym_upper``:
     the product is symmetric (A and B are the same operand, M == N): tiles below the diagonal are mirrored
     instead of computed.  ``diag_add`` is added to the main diagonal of the (bf16) result after ``alpha``.
     ``k_split`` > 0 (with ``B2``): the reduction is split, elements [0, k_split) multiply ``B`` and the rest
-    ``B2``: ``C = A[:, :k_split] B^T + A[:, k_split:] B2^T`` in one pass."""
+    ``B2``: ``C = A[:, :k_split] B^T + A[:, k_split:] B2^T`` in one pass.  ``D2`` / ``beta2``: a second addend
+    laid out like ``D`` (bf16 output): ``C = alpha A B + beta D + beta2 D2``; ``beta_dev`` scales both."""
     K.gemm(A, B, B2, C, D, G, U, mode, epi, M, N, Kd, groups, a_major, b_major, lda, ldb, ldc, ldd,
            a_gs, b_gs, c_gs, tile_group, num_m_tiles, k_begin, k_len, alpha, beta, row_scale, row_ptr,
-           alpha_dev, beta_dev, sym_upper, float(diag_add), int(k_split), status_tensor(A.device))
+           alpha_dev, beta_dev, sym_upper, float(diag_add), int(k_split), D2, float(beta2),
+           status_tensor(A.device))
     _count()
     return C
 
@@ -920,13 +923,67 @@ def mtp_cross_entropy(hidden, head_weights: Sequence[torch.Tensor], labels, weig
 
 # ------------------------------------------------------------ Newton-Schulz
 @torch.no_grad()
+def _newton_schulz_small_side(Y, s1, s2, iters, wide):
+    """The same five cubic steps carried out on the small side of the matrix.
+
+    With G = Y Y^T (g x g, g = the smaller dimension) every step is ``Y <- P Y`` with ``P = 1.5 I - 0.5 G``, and
+    all these factors are polynomials in the first G, so they commute: ``Y_k = Q_k Y_0`` with
+    ``Q_{k+1} = P_k Q_k`` and ``G_{k+1} = P_k^2 G_k``.  Only the first Gram product and the last ``Q Y_0`` touch
+    the long dimension; the steps in between are g x g products: 3 g^2 n + 12 g^3 FLOPs instead of 15 g^2 n.
+    In bf16 the factors must be held as deviations from their multiples of the identity - ``1.5 - 0.5 lambda``
+    rounds to 1.5 for the small eigenvalues that dominate a normalised gradient - so the stored matrices are
+    ``W = P - 1.5 I`` and ``V = Q - c I`` (c = 1.5^k):
+
+        W_0 = -0.5 s^2 Y Y^T                        V_1 = W_0
+        W'  = W (W (W + 3 I) + 2.25 I)              (two products, one addend each)
+        V'  = W' V + 1.5 V + c W'                   (one product, two addends)
+        Y_5 = s (V Y + c Y)
+
+    Every g x g product is symmetric: only the tiles that touch the upper triangle are computed.  Against the
+    step-by-step form in bf16 this is more accurate (Y is rounded once, not five times)."""
+    b, m, n = Y.shape
+    g = m if wide else n
+    kw = dict(mode=BATCHED, groups=b, M=g, N=g, Kd=g, lda=g, ldb=g, ldc=g, ldd=g, a_gs=g * g, b_gs=g * g,
+              c_gs=g * g, sym_upper=True)
+    new = lambda: torch.empty(b, g, g, dtype=torch.bfloat16, device=Y.device)
+    W, Wn, T1, Vn = new(), new(), new(), new()
+    ga = dict(alpha_dev=s2) if s2 is not None else {}
+    if wide:
+        gemm(Y, Y, W, mode=BATCHED, groups=b, M=m, N=m, Kd=n, lda=n, ldb=n, ldc=m, alpha=-0.5,
+             a_gs=m * n, b_gs=m * n, c_gs=m * m, sym_upper=True, **ga)
+    else:
+        gemm(Y, Y, W, mode=BATCHED, groups=b, M=n, N=n, Kd=m, a_major=MAJ_MN, b_major=MAJ_MN, lda=n, ldb=n,
+             ldc=n, alpha=-0.5, a_gs=m * n, b_gs=m * n, c_gs=n * n, sym_upper=True, **ga)
+    V, c = W, 1.5                                                 # Q_1 = P_0: V_1 is W_0 itself
+    for _ in range(iters - 1):
+        gemm(W, W, T1, D=W, beta=3.0, **kw)                       # T1 = W W + 3 W
+        gemm(W, T1, Wn, D=W, beta=2.25, **kw)                     # W' = W T1 + 2.25 W
+        gemm(Wn, V, Vn, D=V, beta=1.5, D2=Wn, beta2=c, **kw)      # V' = W' V + 1.5 V + c W'
+        old_w, old_v = W, V
+        W, V = Wn, Vn
+        Wn, Vn = old_w, (new() if old_v is old_w else old_v)      # the buffers just read are the next outputs
+        c *= 1.5
+    out = torch.empty_like(Y)
+    fa = dict(alpha_dev=s1, beta_dev=s1) if s1 is not None else {}
+    if wide:      # Y_out = s (V Y + c Y), Y read MN-major as the B operand
+        gemm(V, Y, out, D=Y, beta=c, mode=BATCHED, groups=b, M=m, N=n, Kd=m, b_major=MAJ_MN, lda=m, ldb=n,
+             ldc=n, ldd=n, a_gs=m * m, b_gs=m * n, c_gs=m * n, **fa)
+    else:         # Y_out = s (Y V + c Y), V symmetric: read K-major
+        gemm(Y, V, out, D=Y, beta=c, mode=BATCHED, groups=b, M=m, N=n, Kd=n, lda=n, ldb=n, ldc=n, ldd=n,
+             a_gs=m * n, b_gs=n * n, c_gs=m * n, **fa)
+    return out
+
+
 def newton_schulz(matrix: torch.Tensor, iters: int = 5, sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Batched cubic Newton-Schulz on the tcgen05 GEMM: per iteration one Gram product and
-    one product with the fused ``1.5 Y - 0.5 (G Y)`` epilogue.  bf16 operands, fp32 accumulation.
+    """Batched cubic Newton-Schulz on the tcgen05 GEMM, bf16 operands, fp32 accumulation.
+
+    Matrices whose long side is at least 1.25x the short one run the iteration on the short side
+    (``_newton_schulz_small_side``); the others run it step by step: per iteration one Gram product and one
+    product with the factor ``P = 1.5 I - 0.5 G`` that the Gram GEMM's epilogue emits.
 
     ``sumsq`` (fp32, one entry per matrix: its squared Frobenius norm, already on the device) removes the
-    normalisation passes: the first iteration runs on the unnormalised bf16 input and folds
-    ``s = 1 / (norm + 1e-7)`` into the GEMM epilogues (``P = 1.5 I - 0.5 s^2 X X^T``, ``Y1 = s P X``)."""
+    normalisation passes: the products run on the unnormalised bf16 input and ``s = 1 / (norm + 1e-7)`` is
+    folded into the GEMM epilogues."""
     squeeze = matrix.dim() == 2
     Y = matrix.unsqueeze(0) if squeeze else matrix
     b, m, n = Y.shape
@@ -942,10 +999,14 @@ def newton_schulz(matrix: torch.Tensor, iters: int = 5, sumsq: Optional[torch.Te
         Yf = Y.float()
         norms = Yf.reshape(b, -1).norm(dim=1).view(b, 1, 1)
         Ya = (Yf / (norms + 1e-7)).to(torch.bfloat16).contiguous()
-    Yb = torch.empty_like(Ya)
-    Yc = torch.empty_like(Ya) if s1 is not None else None        # never write into the caller's tensor
     wide = m <= n
     g = m if wide else n
+    if (iters >= 2 and 4 * max(m, n) >= 5 * g and g >= 256 and g % 64 == 0
+            and os.environ.get("KMOE_NS_SMALL_SIDE", "1") != "0"):
+        out = _newton_schulz_small_side(Ya, s1, s2, iters, wide).to(matrix.dtype)
+        return out.squeeze(0) if squeeze else out
+    Yb = torch.empty_like(Ya)
+    Yc = torch.empty_like(Ya) if s1 is not None else None        # never write into the caller's tensor
     Gm = torch.empty(b, g, g, dtype=torch.bfloat16, device=Y.device)
     # Y' = 1.5 Y - 0.5 G Y = (1.5 I - 0.5 G) Y: the Gram GEMM's epilogue emits P = 1.5 I - 0.5 G directly, so
     # the second product is a plain GEMM that reads no addend

@@ -230,14 +230,27 @@ def test_mtp_cross_entropy():
         assert _rel(a.grad, b.grad) < 4e-2
 
 
-@pytest.mark.parametrize("shape", [(256, 512), (512, 256), (3, 128, 320), (2, 320, 128)])
-def test_newton_schulz(shape):
+@pytest.mark.parametrize("shape", [(256, 512), (512, 256), (3, 128, 320), (2, 320, 128), (3, 256, 704),
+                                   (2, 704, 256), (2, 512, 512), (1, 512, 2048)])
+@pytest.mark.parametrize("with_sumsq", [False, True])
+def test_newton_schulz(shape, with_sumsq):
+    """Five cubic Newton-Schulz steps against the fp32 definition.  Shapes whose long side is at least 1.25x the
+    short one (and at least 256 on the short side) take the path that iterates on the short side; the others
+    the step-by-step path.  ``with_sumsq``: the norm comes in as a device scalar and is folded into the GEMMs."""
     ops, c, eager = _mods()
+    torch.manual_seed(13)
     m = torch.randn(*shape, device="cuda").to(torch.bfloat16)
-    out = ops.newton_schulz(m, 5)
+    if len(shape) == 3:
+        m[0, :4] *= 20.0                                   # a few dominant directions in one matrix of the stack
+    sumsq = None
+    if with_sumsq:
+        sumsq = m.float().reshape(1 if len(shape) == 2 else shape[0], -1).pow(2).sum(dim=-1)
+    out = ops.newton_schulz(m, 5, sumsq=sumsq)
     c.check_status()
     ref = eager.newton_schulz(m.float(), 5)
+    assert out.shape == m.shape and out.dtype == m.dtype
     assert _rel(out, ref) < 5e-2
+    assert ((out.float() - ref).norm() / ref.norm()).item() < 1e-2
 
 
 def test_model_step_bf16_matches_eager():
