@@ -944,7 +944,7 @@ def _newton_schulz_small_side(Y, s1, s2, iters, wide):
     b, m, n = Y.shape
     g = m if wide else n
     kw = dict(mode=BATCHED, groups=b, M=g, N=g, Kd=g, lda=g, ldb=g, ldc=g, ldd=g, a_gs=g * g, b_gs=g * g,
-              c_gs=g * g, sym_upper=True)
+              c_gs=g * g, sym_upper=os.environ.get("KMOE_NS_SYM", "1") != "0")
     new = lambda: torch.empty(b, g, g, dtype=torch.bfloat16, device=Y.device)
     W, Wn, T1, Vn = new(), new(), new(), new()
     ga = dict(alpha_dev=s2) if s2 is not None else {}
