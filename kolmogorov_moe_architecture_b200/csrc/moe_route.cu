@@ -26,27 +26,54 @@ constexpr int ROW_TILE = 128;
 //   meta[1] = live padded rows
 __global__ void __launch_bounds__(PLAN_THREADS)
 moe_plan_kernel(const long long* __restrict__ idx, const unsigned char* __restrict__ keep, int n, int E, int max_rows,
-                int expert_base, int* __restrict__ pos, int* __restrict__ row_src, int* __restrict__ counts,
-                int* __restrict__ offsets, int* __restrict__ tile_group, int* __restrict__ meta) {
-  extern __shared__ int sh[];     // hist[PLAN_THREADS][E] then off[E+1]
+                int expert_base, int stage_ids, int* __restrict__ pos, int* __restrict__ row_src,
+                int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ tile_group,
+                int* __restrict__ meta) {
+  // hist[PLAN_THREADS][ES] (ES = E rounded up to an odd number: threads of a warp hit different banks), then
+  // wtot[PLAN_THREADS / 32][E], off[E + 1], and, when they fit, the n local expert ids as 16-bit values
+  extern __shared__ int sh[];
+  const int ES = E | 1;
   int* hist = sh;
-  int* off = sh + PLAN_THREADS * E;
-  const int tid = threadIdx.x;
+  int* wtot = hist + PLAN_THREADS * ES;
+  int* off = wtot + (PLAN_THREADS / 32) * E;
+  unsigned short* eid = reinterpret_cast<unsigned short*>(off + E + 1);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int seg = (n + PLAN_THREADS - 1) / PLAN_THREADS;
   const int lo = min(tid * seg, n), hi = min(lo + seg, n);
-  for (int e = 0; e < E; ++e) hist[tid * E + e] = 0;
-  for (int i = tid; i < max_rows; i += PLAN_THREADS) row_src[i] = -1;
-  for (int i = lo; i < hi; ++i) {
+  auto local_expert = [&](int i) -> int {             // 0xffff: not routed to an expert of this plan
     const int e = (int)idx[i] - expert_base;
-    if (e >= 0 && e < E && (keep == nullptr || keep[i])) hist[tid * E + e]++;
+    return (e >= 0 && e < E && (keep == nullptr || keep[i])) ? e : 0xffff;
+  };
+  for (int e = 0; e < E; ++e) hist[tid * ES + e] = 0;
+  for (int i = tid; i < max_rows; i += PLAN_THREADS) row_src[i] = -1;
+  if (stage_ids) {
+    // coalesced read of the ids; the two passes below then walk each thread's contiguous segment in shared memory
+    for (int i = tid; i < n; i += PLAN_THREADS) eid[i] = (unsigned short)local_expert(i);
+    __syncthreads();
+  }
+  for (int i = lo; i < hi; ++i) {
+    const int e = stage_ids ? (int)eid[i] : local_expert(i);
+    if (e != 0xffff) hist[tid * ES + e]++;
   }
   __syncthreads();
-  // exclusive scan over threads, one expert per thread
+  // exclusive scan over the threads, per expert: shuffles inside a warp, then the warp totals
+  for (int e = 0; e < E; ++e) {
+    const int v = hist[tid * ES + e];
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += t;
+    }
+    hist[tid * ES + e] = inc - v;
+    if (lane == 31) wtot[warp * E + e] = inc;
+  }
+  __syncthreads();
   for (int e = tid; e < E; e += PLAN_THREADS) {
     int run = 0;
-    for (int t = 0; t < PLAN_THREADS; ++t) {
-      const int v = hist[t * E + e];
-      hist[t * E + e] = run;
+    for (int w = 0; w < PLAN_THREADS / 32; ++w) {
+      const int v = wtot[w * E + e];
+      wtot[w * E + e] = run;
       run += v;
     }
     counts[e] = run;
@@ -72,10 +99,10 @@ moe_plan_kernel(const long long* __restrict__ idx, const unsigned char* __restri
   }
   __syncthreads();
   for (int i = lo; i < hi; ++i) {
-    const int e = (int)idx[i] - expert_base;
+    const int e = stage_ids ? (int)eid[i] : local_expert(i);
     int p = -1;
-    if (e >= 0 && e < E && (keep == nullptr || keep[i])) {
-      p = off[e] + hist[tid * E + e]++;
+    if (e != 0xffff) {
+      p = off[e] + wtot[warp * E + e] + hist[tid * ES + e]++;
       if (p < max_rows) row_src[p] = i; else p = -1;
     }
     pos[i] = p;
@@ -254,16 +281,19 @@ extern "C" int kmoe_moe_max_rows(int n_assign, int E) {
 extern "C" int kmoe_moe_plan(const long long* idx, const unsigned char* keep, int n, int E, int max_rows,
                              int expert_base, int* pos, int* row_src, int* counts, int* offsets, int* tile_group,
                              int* meta, cudaStream_t st) {
-  const size_t smem = ((size_t)PLAN_THREADS * E + E + 1) * sizeof(int);
-  if (smem > 200 * 1024) return -1;
+  const size_t base = ((size_t)PLAN_THREADS * (E | 1) + (size_t)(PLAN_THREADS / 32) * E + E + 1) * sizeof(int);
+  if (base > 200 * 1024 || E >= 0xffff) return -1;
+  // the expert ids are staged in shared memory when they fit beside the histograms
+  const int stage_ids = base + (size_t)n * 2 <= 200 * 1024 ? 1 : 0;
+  const size_t smem = base + (stage_ids ? (size_t)n * 2 : 0);
   static size_t attr_set = 0;
   if (smem > 48 * 1024 && smem > attr_set) {
     if (cudaFuncSetAttribute(moe_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return -3;
     attr_set = smem;
   }
-  moe_plan_kernel<<<1, PLAN_THREADS, smem, st>>>(idx, keep, n, E, max_rows, expert_base, pos, row_src, counts,
-                                                 offsets, tile_group, meta);
+  moe_plan_kernel<<<1, PLAN_THREADS, smem, st>>>(idx, keep, n, E, max_rows, expert_base, stage_ids, pos, row_src,
+                                                 counts, offsets, tile_group, meta);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -274,12 +274,13 @@ class _DenseSwiGLU(torch.autograd.Function):
         G, U = torch.empty_like(H), torch.empty_like(H)
         gemm(x2, w1, H, B2=w2, G=G, U=U, epi=EPI_SWIGLU, M=T, N=f, Kd=d, lda=x2.stride(0), ldb=d, ldc=f)
         y = mm_nt(H, w3)
-        ctx.save_for_backward(x2, G, U, w1, w2, w3)
+        keep_h = os.environ.get("KMOE_MOE_KEEP_H", "1") != "0"      # else H is recomputed in the backward pass
+        ctx.save_for_backward(x2, G, U, w1, w2, w3, *((H,) if keep_h else ()))
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x2, G, U, w1, w2, w3 = ctx.saved_tensors
+        x2, G, U, w1, w2, w3, *kept = ctx.saved_tensors
         if not _rows_ok(dy):
             dy = dy.contiguous()
         dH = mm_nn(dy, w3)
@@ -293,8 +294,11 @@ class _DenseSwiGLU(torch.autograd.Function):
             # dx = dG W1 + dU W2 as one GEMM whose reduction runs over [dG | dU] and [W1 ; W2]
             dx = torch.empty(T, d, dtype=dy.dtype, device=dy.device)
             gemm(dGU, w1, dx, B2=w2, M=T, N=d, Kd=2 * f, k_split=f, b_major=MAJ_MN, lda=2 * f, ldb=d, ldc=d)
-        H = K.swiglu_fwd(G, U, None)
-        _count()
+        if kept:
+            H = kept[0]
+        else:
+            H = K.swiglu_fwd(G, U, None)
+            _count()
         dw1 = _wgrad(dG, x2, w1)
         dw2 = _wgrad(dU, x2, w2)
         dw3 = _wgrad(dy, H, w3)
@@ -528,14 +532,19 @@ class _GroupedSwiGLU(torch.autograd.Function):
         wf = weights.reshape(-1).float().contiguous()
         out = K.moe_combine(Y, pos, wf, T, k)
         _count(3)
-        ctx.save_for_backward(Xp, G, U, Y, w1, w2, w3, wf, pos, row_src, offsets, tile_group, meta)
+        # The hidden activations H are kept for the weight gradient of the down projection unless
+        # KMOE_MOE_KEEP_H=0 (then they are recomputed from G and U in the backward pass: one more kernel per
+        # layer, rows x f bf16 less memory held between the passes).
+        keep_h = os.environ.get("KMOE_MOE_KEEP_H", "1") != "0"
+        ctx.save_for_backward(Xp, G, U, Y, w1, w2, w3, wf, pos, row_src, offsets, tile_group, meta,
+                              *((H,) if keep_h else ()))
         ctx.dims = (T, d, E, f, k, max_rows)
         ctx.wdtype = weights.dtype
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        Xp, G, U, Y, w1, w2, w3, wf, pos, row_src, offsets, tile_group, meta = ctx.saved_tensors
+        Xp, G, U, Y, w1, w2, w3, wf, pos, row_src, offsets, tile_group, meta, *kept = ctx.saved_tensors
         T, d, E, f, k, max_rows = ctx.dims
         dout = dout.contiguous()
         nmt = meta[0:1]
@@ -554,7 +563,7 @@ class _GroupedSwiGLU(torch.autograd.Function):
         # weight gradients: per expert, reduction over that expert's (padded) row range
         kb = offsets[:E].contiguous()
         kl = (offsets[1:] - offsets[:E]).contiguous()
-        H = K.swiglu_fwd(G, U, meta[1:2])
+        H = kept[0] if kept else K.swiglu_fwd(G, U, meta[1:2])
         # weight gradients go straight to their place in the flat gradient buffer when one is registered
         sinks = [grad_sink(w) for w in (w1, w2, w3)]
         dw1, dw2, dw3 = [s[0] if s is not None else torch.empty_like(w) for s, w in zip(sinks, (w1, w2, w3))]
