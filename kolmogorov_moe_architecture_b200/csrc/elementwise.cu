@@ -75,6 +75,124 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
   }
 }
 
+// Register-resident variants for rows of NCH * 256 elements (NCH <= 8): a warp reads its row once (eight
+// elements per lane and 256-column chunk), so x / dy are not read a second time for the output pass, and the
+// backward also accumulates the weight gradient (column sums of dy * x * rstd over the rows a warp visits, then
+// over the block through shared memory): one pass over x and dy instead of three.
+template <int NCH>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                        __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, float eps,
+                        const __nv_bfloat16* __restrict__ addend, __nv_bfloat16* __restrict__ sum_out) {
+  constexpr int D = NCH * 256;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint4 wq[NCH];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) wq[j] = __ldg(reinterpret_cast<const uint4*>(w + j * 256 + lane * 8));
+  for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
+    const size_t base = (size_t)row * D + lane * 8;
+    uint4 xq[NCH];
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) xq[j] = *reinterpret_cast<const uint4*>(x + base + j * 256);
+    if (addend != nullptr) {
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        float v[8], a[8];
+        unpack8(xq[j], v);
+        unpack8(*reinterpret_cast<const uint4*>(addend + base + j * 256), a);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += a[i];
+        xq[j] = pack8(v);                          // the normalised row is the rounded sum, as stored
+        *reinterpret_cast<uint4*>(sum_out + base + j * 256) = xq[j];
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      float v[8];
+      unpack8(xq[j], v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / D + eps);
+    if (lane == 0 && rstd != nullptr) rstd[row] = r;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      float v[8], g[8];
+      unpack8(xq[j], v);
+      unpack8(wq[j], g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = v[i] * r * g[i];
+      *reinterpret_cast<uint4*>(y + base + j * 256) = pack8(v);
+    }
+  }
+}
+
+template <int NCH>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                        const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
+                        __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows,
+                        const __nv_bfloat16* __restrict__ dres) {
+  constexpr int D = NCH * 256;
+  __shared__ float sacc[D];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < D; i += 256) sacc[i] = 0.f;
+  __syncthreads();
+  const __nv_bfloat16* wl = w + lane * 8;          // re-read per row (first-level cache hits): saves 4 NCH registers
+  float acc[NCH * 8];
+#pragma unroll
+  for (int i = 0; i < NCH * 8; ++i) acc[i] = 0.f;
+  for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
+    const size_t base = (size_t)row * D + lane * 8;
+    uint4 xq[NCH], gq[NCH];
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      xq[j] = *reinterpret_cast<const uint4*>(x + base + j * 256);
+      gq[j] = *reinterpret_cast<const uint4*>(dy + base + j * 256);
+    }
+    const float r = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      float xv[8], gv[8], wv[8];
+      unpack8(xq[j], xv);
+      unpack8(gq[j], gv);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(wl + j * 256)), wv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        dot += gv[i] * wv[i] * xv[i];
+        acc[j * 8 + i] += gv[i] * xv[i] * r;
+      }
+    }
+    dot = warp_sum(dot);
+    const float coef = dot * r * r * r / D;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      float xv[8], gv[8], wv[8], o[8];
+      unpack8(xq[j], xv);
+      unpack8(gq[j], gv);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(wl + j * 256)), wv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = gv[i] * wv[i] * r - xv[i] * coef;
+      if (dres != nullptr) {
+        float rv[8];
+        unpack8(*reinterpret_cast<const uint4*>(dres + base + j * 256), rv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] += rv[i];
+      }
+      *reinterpret_cast<uint4*>(dx + base + j * 256) = pack8(o);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NCH; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) atomicAdd(&sacc[j * 256 + lane * 8 + i], acc[j * 8 + i]);
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += 256) partial[(size_t)blockIdx.x * D + i] = sacc[i];
+}
+
 // dx = rstd * (w dy) - x * rstd^3 * mean(w dy x).  One warp per row.
 // `dres` (optional): gradient arriving through the residual branch that bypasses the norm; dx = norm term + dres.
 __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
@@ -323,6 +441,19 @@ extern "C" int kmoe_add_rmsnorm_fwd(const void* x, const void* addend, const voi
   const int block = 256, wpb = block / 32;
   int grid = (rows + wpb - 1) / wpb;
   if (grid > 148 * 8) grid = 148 * 8;
+  if (rows > 0 && (d == 256 || d == 512 || d == 1024 || d == 2048)) {
+    const int g2 = grid > 148 * 4 ? 148 * 4 : grid;
+#define KMOE_FWD_ROWS(NCH)                                                                                        \
+  rmsnorm_fwd_rows_kernel<NCH><<<g2, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,              \
+                                                   (__nv_bfloat16*)y, rstd, rows, eps,                            \
+                                                   (const __nv_bfloat16*)addend, (__nv_bfloat16*)sum_out)
+    if (d == 2048) KMOE_FWD_ROWS(8);
+    else if (d == 1024) KMOE_FWD_ROWS(4);
+    else if (d == 512) KMOE_FWD_ROWS(2);
+    else KMOE_FWD_ROWS(1);
+#undef KMOE_FWD_ROWS
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   rmsnorm_fwd_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
                                              rstd, rows, d, eps, (const __nv_bfloat16*)addend,
                                              (__nv_bfloat16*)sum_out);
@@ -334,9 +465,11 @@ extern "C" int kmoe_rmsnorm_fwd(const void* x, const void* w, void* y, float* rs
   return kmoe_add_rmsnorm_fwd(x, nullptr, w, nullptr, y, rstd, rows, d, eps, st);
 }
 
+// Rows of fp32 partial column sums a backward pass may write: one per CTA of the register-resident kernel (eight
+// rows per CTA and sweep, at most two CTAs per SM).
 extern "C" int kmoe_rmsnorm_bwd_num_partials(int rows) {
-  int r = (rows + 63) / 64;
-  return r > 64 ? 64 : (r < 1 ? 1 : r);
+  int r = (rows + 7) / 8;
+  return r > 296 ? 296 : (r < 1 ? 1 : r);
 }
 
 // `partial` is scratch of kmoe_rmsnorm_bwd_num_partials(rows) * d floats.
@@ -353,6 +486,21 @@ extern "C" int kmoe_rmsnorm_bwd_res(const void* x, const void* w, const void* dy
   const int block = 256, wpb = block / 32;
   int grid = (rows + wpb - 1) / wpb;
   if (grid > 148 * 8) grid = 148 * 8;
+  if (rows > 0 && (d == 256 || d == 512 || d == 1024 || d == 2048)) {
+    // one pass: dx and the partial column sums of the weight gradient
+    const int g2 = kmoe_rmsnorm_bwd_num_partials(rows);
+#define KMOE_BWD_ROWS(NCH)                                                                                        \
+  rmsnorm_bwd_rows_kernel<NCH><<<g2, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,              \
+                                                   (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, partial,   \
+                                                   rows, (const __nv_bfloat16*)dres)
+    if (d == 2048) KMOE_BWD_ROWS(8);
+    else if (d == 1024) KMOE_BWD_ROWS(4);
+    else if (d == 512) KMOE_BWD_ROWS(2);
+    else KMOE_BWD_ROWS(1);
+#undef KMOE_BWD_ROWS
+    colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, (__nv_bfloat16*)dw_bf16, dw_f32, g2, d);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   rmsnorm_bwd_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
                                              (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, rows, d,
                                              (const __nv_bfloat16*)dres);

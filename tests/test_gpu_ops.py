@@ -31,11 +31,14 @@ def _f32_leaf(t):
     return t.detach().float().requires_grad_(True)
 
 
-def test_rmsnorm_fwd_bwd():
+@pytest.mark.parametrize("d", [512, 2048, 1024, 256, 384])
+def test_rmsnorm_fwd_bwd(d):
+    """Widths 256 / 512 / 1024 / 2048 run the register-resident kernels (one pass, weight gradient included),
+    384 the generic ones."""
     ops, c, eager = _mods()
-    x, w = _bf(37, 5, 512, grad=True), _bf(512, grad=True)
+    x, w = _bf(37, 5, d, grad=True), _bf(d, grad=True)
     y = ops.rmsnorm(x, w, 1e-5)
-    g = _bf(37, 5, 512)
+    g = _bf(37, 5, d)
     y.backward(g)
     xr, wr = _f32_leaf(x), _f32_leaf(w)
     yr = eager.rmsnorm(xr, wr, 1e-5)
@@ -534,14 +537,15 @@ def test_capacity_mask_and_balanced_assignment_kernels(T, E, k, cap):
 
 
 @pytest.mark.parametrize("with_addend", [False, True])
-def test_residual_rmsnorm_fwd_bwd(with_addend):
+@pytest.mark.parametrize("d", [512, 2048, 384])
+def test_residual_rmsnorm_fwd_bwd(with_addend, d):
     """Residual add + RMSNorm in one op; the residual stream h is used twice downstream (through the norm and
     around it), and both gradient paths are summed inside the backward kernel."""
     ops, c, eager = _mods()
-    x, w = _bf(3, 37, 512, grad=True), _bf(512, grad=True)
-    a = _bf(3, 37, 512, grad=True) if with_addend else None
+    x, w = _bf(3, 37, d, grad=True), _bf(d, grad=True)
+    a = _bf(3, 37, d, grad=True) if with_addend else None
     h, y = ops.residual_rmsnorm(x, a, w, 1e-5)
-    g1, g2 = _bf(3, 37, 512), _bf(3, 37, 512)
+    g1, g2 = _bf(3, 37, d), _bf(3, 37, d)
     ((h * g1).sum() + (y * g2).sum()).backward()
     xr, wr = _f32_leaf(x), _f32_leaf(w)
     ar = _f32_leaf(a) if with_addend else None
