@@ -180,6 +180,17 @@ std::tuple<Tensor, Tensor> rowdot_bwd(const Tensor& x, const Tensor& w, const Te
   return {need_dx ? dx : at::empty({0}, x.options()), dw};
 }
 
+Tensor sumsq(const Tensor& x) {
+  c10::cuda::CUDAGuard guard(x.device());
+  need_bf16(x, "x");
+  TORCH_CHECK(x.is_contiguous(), "x must be contiguous");
+  Tensor partial = at::empty({kmoe_sumsq_num_partials()}, x.options().dtype(at::kFloat));
+  Tensor out = at::empty({1}, x.options().dtype(at::kFloat));
+  check(kmoe_sumsq_bf16(x.data_ptr(), x.numel(), partial.data_ptr<float>(), out.data_ptr<float>(), cur_stream()),
+        "sumsq");
+  return out;
+}
+
 void sum_partials(const Tensor& partial, Tensor out) {
   c10::cuda::CUDAGuard guard(partial.device());
   need_f32(partial, "partial"); need_bf16(out, "out");
@@ -774,6 +785,7 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("rowdot_fwd", &rowdot_fwd);
   m.def("rowdot_bwd", &rowdot_bwd);
   m.def("sum_partials", &sum_partials);
+  m.def("sumsq", &sumsq);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("swiglu_bwd_cat", &swiglu_bwd_cat);

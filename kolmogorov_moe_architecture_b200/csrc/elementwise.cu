@@ -4,6 +4,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "kmoe_api.h"
 #include "ptx.cuh"
 
@@ -129,8 +131,8 @@ rmsnorm_fwd_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
   }
 }
 
-template <int NCH>
-__global__ void __launch_bounds__(256)
+template <int NCH, bool WITH_DW>
+__global__ void __launch_bounds__(256, WITH_DW ? 1 : 2)
 rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                         const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
                         __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows,
@@ -138,12 +140,14 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
   constexpr int D = NCH * 256;
   __shared__ float sacc[D];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < D; i += 256) sacc[i] = 0.f;
-  __syncthreads();
+  if (WITH_DW) {
+    for (int i = threadIdx.x; i < D; i += 256) sacc[i] = 0.f;
+    __syncthreads();
+  }
   const __nv_bfloat16* wl = w + lane * 8;          // re-read per row (first-level cache hits): saves 4 NCH registers
-  float acc[NCH * 8];
+  float acc[WITH_DW ? NCH * 8 : 1];
 #pragma unroll
-  for (int i = 0; i < NCH * 8; ++i) acc[i] = 0.f;
+  for (int i = 0; i < (WITH_DW ? NCH * 8 : 1); ++i) acc[i] = 0.f;
   for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
     const size_t base = (size_t)row * D + lane * 8;
     uint4 xq[NCH], gq[NCH];
@@ -163,7 +167,7 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         dot += gv[i] * wv[i] * xv[i];
-        acc[j * 8 + i] += gv[i] * xv[i] * r;
+        if (WITH_DW) acc[j * 8 + i] += gv[i] * xv[i] * r;
       }
     }
     dot = warp_sum(dot);
@@ -185,12 +189,14 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
       *reinterpret_cast<uint4*>(dx + base + j * 256) = pack8(o);
     }
   }
+  if (WITH_DW) {
 #pragma unroll
-  for (int j = 0; j < NCH; ++j)
+    for (int j = 0; j < NCH; ++j)
 #pragma unroll
-    for (int i = 0; i < 8; ++i) atomicAdd(&sacc[j * 256 + lane * 8 + i], acc[j * 8 + i]);
-  __syncthreads();
-  for (int i = threadIdx.x; i < D; i += 256) partial[(size_t)blockIdx.x * D + i] = sacc[i];
+      for (int i = 0; i < 8; ++i) atomicAdd(&sacc[j * 256 + lane * 8 + i], acc[j * 8 + i]);
+    __syncthreads();
+    for (int i = threadIdx.x; i < D; i += 256) partial[(size_t)blockIdx.x * D + i] = sacc[i];
+  }
 }
 
 // dx = rstd * (w dy) - x * rstd^3 * mean(w dy x).  One warp per row.
@@ -486,19 +492,37 @@ extern "C" int kmoe_rmsnorm_bwd_res(const void* x, const void* w, const void* dy
   const int block = 256, wpb = block / 32;
   int grid = (rows + wpb - 1) / wpb;
   if (grid > 148 * 8) grid = 148 * 8;
-  if (rows > 0 && (d == 256 || d == 512 || d == 1024 || d == 2048)) {
-    // one pass: dx and the partial column sums of the weight gradient
+  static int rows_mode = -1;      // KMOE_NORM_ROWS: 0 = generic kernels, 1 = one fused pass, 2 = register-resident dx + separate dw
+  if (rows_mode < 0) {
+    const char* e = getenv("KMOE_NORM_ROWS");
+    rows_mode = e != nullptr ? atoi(e) : 1;
+  }
+  if (rows_mode != 0 && rows > 0 && (d == 256 || d == 512 || d == 1024 || d == 2048)) {
     const int g2 = kmoe_rmsnorm_bwd_num_partials(rows);
+    const bool fused = rows_mode == 1;
 #define KMOE_BWD_ROWS(NCH)                                                                                        \
-  rmsnorm_bwd_rows_kernel<NCH><<<g2, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,              \
-                                                   (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, partial,   \
-                                                   rows, (const __nv_bfloat16*)dres)
+  do {                                                                                                            \
+    if (fused)                                                                                                    \
+      rmsnorm_bwd_rows_kernel<NCH, true><<<g2, 256, 0, st>>>(                                                     \
+          (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx,   \
+          partial, rows, (const __nv_bfloat16*)dres);                                                             \
+    else                                                                                                          \
+      rmsnorm_bwd_rows_kernel<NCH, false><<<grid > 148 * 4 ? 148 * 4 : grid, 256, 0, st>>>(                       \
+          (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx,   \
+          partial, rows, (const __nv_bfloat16*)dres);                                                             \
+  } while (0)
     if (d == 2048) KMOE_BWD_ROWS(8);
     else if (d == 1024) KMOE_BWD_ROWS(4);
     else if (d == 512) KMOE_BWD_ROWS(2);
     else KMOE_BWD_ROWS(1);
 #undef KMOE_BWD_ROWS
-    colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, (__nv_bfloat16*)dw_bf16, dw_f32, g2, d);
+    int parts = g2;
+    if (!fused) {
+      parts = g2 > 64 ? 64 : g2;
+      rmsnorm_dw_kernel<<<dim3((d + 255) / 256, parts), 256, 0, st>>>((const __nv_bfloat16*)x,
+                                                                      (const __nv_bfloat16*)dy, rstd, partial, rows, d);
+    }
+    colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, (__nv_bfloat16*)dw_bf16, dw_f32, parts, d);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }
   rmsnorm_bwd_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
@@ -525,6 +549,80 @@ __global__ void sum_partials_kernel(const float* __restrict__ partial, __nv_bflo
   o.x = pack_bf16(s.x, s.y);
   o.y = pack_bf16(s.z, s.w);
   *reinterpret_cast<uint2*>(out + i) = o;
+}
+
+// Sum of squares of n bf16 values in fp32 (the gradient norm of a flat buffer): block partial sums, then one
+// block adds them in a fixed order, so the result does not depend on scheduling.
+constexpr int SUMSQ_BLOCKS = 148 * 8;
+__global__ void __launch_bounds__(256)
+sumsq_partial_kernel(const __nv_bfloat16* __restrict__ x, long long n, float* __restrict__ partial) {
+  __shared__ float red[8];
+  const long long nvec = n / 8;
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (; i + 3 * stride < nvec; i += 4 * stride) {          // four independent 16-byte loads in flight
+    const uint4 a = __ldg(xv + i), b = __ldg(xv + i + stride), c = __ldg(xv + i + 2 * stride),
+                d = __ldg(xv + i + 3 * stride);
+    float v[8];
+    unpack8(a, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s0 += v[k] * v[k];
+    unpack8(b, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s1 += v[k] * v[k];
+    unpack8(c, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s2 += v[k] * v[k];
+    unpack8(d, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s3 += v[k] * v[k];
+  }
+  for (; i < nvec; i += stride) {
+    float v[8];
+    unpack8(__ldg(xv + i), v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s0 += v[k] * v[k];
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (int)(n - nvec * 8)) {   // tail of fewer than eight values
+    const float t = __bfloat162float(x[nvec * 8 + threadIdx.x]);
+    s1 += t * t;
+  }
+  float s = warp_sum((s0 + s1) + (s2 + s3));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w];
+    partial[blockIdx.x] = t;
+  }
+}
+__global__ void __launch_bounds__(256) sumsq_final_kernel(const float* __restrict__ partial, int nparts,
+                                                          float* __restrict__ out) {
+  __shared__ float red[8];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += 256) s += partial[i];
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w];
+    out[0] = t;
+  }
+}
+
+extern "C" int kmoe_sumsq_num_partials(void) { return SUMSQ_BLOCKS; }
+
+// x: n bf16 values, 16-byte aligned; partial: kmoe_sumsq_num_partials() floats of scratch; out: one float.
+extern "C" int kmoe_sumsq_bf16(const void* x, long long n, float* partial, float* out, cudaStream_t st) {
+  if (n < 0 || (reinterpret_cast<uintptr_t>(x) & 15)) return -1;
+  sumsq_partial_kernel<<<SUMSQ_BLOCKS, 256, 0, st>>>((const __nv_bfloat16*)x, n, partial);
+  sumsq_final_kernel<<<1, 256, 0, st>>>(partial, SUMSQ_BLOCKS, out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 extern "C" int kmoe_sum_partials(const float* partial, void* out, int nparts, long long n, cudaStream_t st) {

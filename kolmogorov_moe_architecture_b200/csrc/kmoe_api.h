@@ -130,6 +130,10 @@ int kmoe_add_rmsnorm_fwd(const void* x, const void* addend, const void* w, void*
 int kmoe_rmsnorm_bwd_res(const void* x, const void* w, const void* dy, const float* rstd, const void* dres, void* dx,
                          void* dw_bf16, float* dw_f32, float* partial, int rows, int d, cudaStream_t st);
 int kmoe_rmsnorm_bwd_num_partials(int rows);
+// sum of squares of n bf16 values (16-byte aligned) in fp32, summed in a fixed order; partial = scratch of
+// kmoe_sumsq_num_partials() floats
+int kmoe_sumsq_num_partials(void);
+int kmoe_sumsq_bf16(const void* x, long long n, float* partial, float* out, cudaStream_t st);
 // out (bf16, n values) = sum of nparts fp32 vectors of n values stored back to back; n % 4 == 0
 int kmoe_sum_partials(const float* partial, void* out, int nparts, long long n, cudaStream_t st);
 /* nn.Linear(d, 1): y[row] = x[row, :] . w ; backward gives dx (optional) and dw (bf16 and/or fp32). */

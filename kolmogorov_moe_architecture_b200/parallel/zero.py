@@ -384,8 +384,12 @@ class ShardedDataParallel:
     def owned_sq_norm(self) -> torch.Tensor:
         if getattr(self, "_sq_valid", False):
             return self._sq[0]
+        seg = self.own_slice(self.flat_grad)
+        if seg.is_cuda and seg.dtype == torch.bfloat16 and seg.data_ptr() % 16 == 0 and hasattr(torch.ops, "kmoe") \
+                and hasattr(torch.ops.kmoe, "sumsq"):
+            return torch.ops.kmoe.sumsq(seg)[0]              # one pass, fp32 accumulation, fixed summation order
         # fused fp32-accumulating reduction: no fp32 copy of the gradient segment is materialised
-        return torch.linalg.vector_norm(self.own_slice(self.flat_grad), dtype=torch.float32).pow(2)
+        return torch.linalg.vector_norm(seg, dtype=torch.float32).pow(2)
 
     def scale_owned(self, coef: torch.Tensor) -> None:
         """Apply the clip coefficient: the fused AdamW kernel reads it from the device; only

@@ -145,3 +145,17 @@ def test_muon8bit_step_on_kernels_matches_eager_path(monkeypatch):
         res[kernels] = [p.detach().float().clone() for p in ps]
     for a, b in zip(res[True], res[False]):
         assert torch.allclose(a, b, atol=1e-3, rtol=0), (a - b).abs().max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [7, 8, 4099, 3 * 2**20 + 5])
+def test_sum_of_squares_kernel(n):
+    """fp32 sum of squares of a bf16 buffer (the gradient norm of the flat buffer) against PyTorch in fp64; the
+    same call twice gives identical bits (fixed summation order)."""
+    import kolmogorov_moe_architecture_b200.ops.cuda_ops  # noqa: F401  (loads the extension)
+    torch.manual_seed(n)
+    x = (torch.randn(n, device="cuda") * 3).to(torch.bfloat16)
+    a, b = torch.ops.kmoe.sumsq(x), torch.ops.kmoe.sumsq(x)
+    ref = x.double().pow(2).sum()
+    assert torch.equal(a, b)
+    assert abs(a.item() - ref.item()) <= 1e-5 * ref.item()
