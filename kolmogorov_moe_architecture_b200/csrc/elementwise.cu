@@ -269,15 +269,34 @@ __global__ void rmsnorm_dw_kernel(const __nv_bfloat16* __restrict__ x, const __n
   if (blockIdx.x * 256 + col < d) partial[(size_t)blockIdx.y * d + blockIdx.x * 256 + col] = s_;
 }
 
-__global__ void colsum_partials_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out_bf16,
-                                       float* __restrict__ out_f32, int nparts, int d) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= d) return;
-  float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * d + c];
-  if (out_bf16 != nullptr) out_bf16[c] = __float2bfloat16(s);
-  if (out_f32 != nullptr) out_f32[c] = s;
+// Sum of `nparts` rows of partial column sums.  A block owns 32 columns; its eight warps take every eighth row
+// and the warp results are added in a fixed order.  Launch with colsum_grid(d) blocks of 256 threads.
+__global__ void __launch_bounds__(256)
+colsum_partials_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out_bf16,
+                       float* __restrict__ out_f32, int nparts, int d) {
+  __shared__ float red[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  float s0 = 0.f, s1 = 0.f;
+  if (c < d) {
+    int p = warp;
+    for (; p + 8 < nparts; p += 16) {
+      s0 += partial[(size_t)p * d + c];
+      s1 += partial[(size_t)(p + 8) * d + c];
+    }
+    if (p < nparts) s0 += partial[(size_t)p * d + c];
+  }
+  red[warp][lane] = s0 + s1;
+  __syncthreads();
+  if (warp == 0 && c < d) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += red[w][lane];
+    if (out_bf16 != nullptr) out_bf16[c] = __float2bfloat16(s);
+    if (out_f32 != nullptr) out_f32[c] = s;
+  }
 }
+static inline int colsum_grid(int d) { return (d + 31) / 32; }
 
 // ------------------------------------------------- Linear with one output column
 // y[row] = sum_c x[row, c] * w[c]   (the mixture-of-depths scorer and the last layer of its
@@ -522,7 +541,7 @@ extern "C" int kmoe_rmsnorm_bwd_res(const void* x, const void* w, const void* dy
       rmsnorm_dw_kernel<<<dim3((d + 255) / 256, parts), 256, 0, st>>>((const __nv_bfloat16*)x,
                                                                       (const __nv_bfloat16*)dy, rstd, partial, rows, d);
     }
-    colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, (__nv_bfloat16*)dw_bf16, dw_f32, parts, d);
+    colsum_partials_kernel<<<colsum_grid(d), 256, 0, st>>>(partial, (__nv_bfloat16*)dw_bf16, dw_f32, parts, d);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }
   rmsnorm_bwd_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
@@ -531,7 +550,7 @@ extern "C" int kmoe_rmsnorm_bwd_res(const void* x, const void* w, const void* dy
   const int parts = kmoe_rmsnorm_bwd_num_partials(rows);
   rmsnorm_dw_kernel<<<dim3((d + 255) / 256, parts), 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
                                                                   rstd, partial, rows, d);
-  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, (__nv_bfloat16*)dw_bf16, dw_f32, parts, d);
+  colsum_partials_kernel<<<colsum_grid(d), 256, 0, st>>>(partial, (__nv_bfloat16*)dw_bf16, dw_f32, parts, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -653,7 +672,7 @@ extern "C" int kmoe_rowdot_bwd(const void* x, const void* w, const void* dy, voi
   const int parts = kmoe_rmsnorm_bwd_num_partials(rows);
   rowdot_dw_kernel<<<dim3((d + 255) / 256, parts), 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
                                                                  partial, rows, d);
-  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, (__nv_bfloat16*)dw_bf16, dw_f32, parts, d);
+  colsum_partials_kernel<<<colsum_grid(d), 256, 0, st>>>(partial, (__nv_bfloat16*)dw_bf16, dw_f32, parts, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -721,7 +740,7 @@ extern "C" int kmoe_rmsnorm_bwd_noalloc(const void* x, const void* w, const void
   // left over from an earlier call is ever read and no clearing pass is needed
   rmsnorm_dw_kernel<<<dim3((d + 255) / 256, parts), 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
                                                                   rstd, partial, rows, d);
-  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(partial, nullptr, dw_f32, parts, d);
+  colsum_partials_kernel<<<colsum_grid(d), 256, 0, st>>>(partial, nullptr, dw_f32, parts, d);
   return cudaGetLastError() == cudaSuccess ? 0 : KMOE_NOALLOC_E_LAUNCH;
 }
 
