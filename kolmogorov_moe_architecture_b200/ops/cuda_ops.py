@@ -996,8 +996,20 @@ def newton_schulz(matrix: torch.Tensor, iters: int = 5, sumsq: Optional[torch.Te
     squeeze = matrix.dim() == 2
     Y = matrix.unsqueeze(0) if squeeze else matrix
     b, m, n = Y.shape
+    if (m == 1 or n == 1) and matrix.is_cuda:
+        # a vector: Y Y^T is the scalar |Y|^2 = 1 after the normalisation, every step multiplies by
+        # 1.5 - 0.5 |Y|^2 = 1, so the result is the normalised vector itself
+        Yf = Y.float()
+        out = (Yf / (Yf.reshape(b, -1).norm(dim=1).view(b, 1, 1) + 1e-7)).to(matrix.dtype)
+        return out.squeeze(0) if squeeze else out
+    if (m % 64 or n % 64) and min(m, n) >= 8 and matrix.dtype == torch.bfloat16:
+        # odd sizes (Mamba x_proj 160 x 4096, the 16 x 128 router of a small model): zero rows / columns stay zero
+        # through the iteration, so the matrix is padded to whole 64-element blocks and the result cut back
+        mp, np_ = -(-m // 64) * 64, -(-n // 64) * 64
+        padded = torch.nn.functional.pad(Y, (0, np_ - n, 0, mp - m))
+        out = newton_schulz(padded, iters, sumsq=sumsq)[:, :m, :n].contiguous()
+        return out.squeeze(0) if squeeze else out
     if m % 64 or n % 64:
-        # vectors and odd-sized matrices (e.g. the (1, d) MoD router) are negligible work
         return eager.newton_schulz(matrix, iters)
     s1 = s2 = None
     if sumsq is not None and matrix.dtype == torch.bfloat16 and Y.is_contiguous() and iters > 0:

@@ -234,16 +234,18 @@ def test_mtp_cross_entropy():
 
 
 @pytest.mark.parametrize("shape", [(256, 512), (512, 256), (3, 128, 320), (2, 320, 128), (3, 256, 704),
-                                   (2, 704, 256), (2, 512, 512), (1, 512, 2048)])
+                                   (2, 704, 256), (2, 512, 512), (1, 512, 2048), (4, 160, 1024), (3, 16, 128),
+                                   (5, 1, 256), (2, 192, 1)])
 @pytest.mark.parametrize("with_sumsq", [False, True])
 def test_newton_schulz(shape, with_sumsq):
     """Five cubic Newton-Schulz steps against the fp32 definition.  Shapes whose long side is at least 1.25x the
     short one (and at least 256 on the short side) take the path that iterates on the short side; the others
-    the step-by-step path.  ``with_sumsq``: the norm comes in as a device scalar and is folded into the GEMMs."""
+    the step-by-step path; sizes that are not multiples of 64 are zero-padded, vectors are only normalised.
+    ``with_sumsq``: the norm comes in as a device scalar and is folded into the GEMMs."""
     ops, c, eager = _mods()
     torch.manual_seed(13)
     m = torch.randn(*shape, device="cuda").to(torch.bfloat16)
-    if len(shape) == 3:
+    if len(shape) == 3 and min(shape[1:]) > 4:
         m[0, :4] *= 20.0                                   # a few dominant directions in one matrix of the stack
     sumsq = None
     if with_sumsq:
