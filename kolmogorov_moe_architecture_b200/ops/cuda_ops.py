@@ -906,6 +906,7 @@ class _MTPLoss(torch.autograd.Function):
         saved += [w if w is not None else torch.empty(0, device=hidden.device) for w in dWs]
         ctx.save_for_backward(*saved)
         ctx.need_grad = need_grad
+        ctx.heads = head_weights
         ctx.mark_non_differentiable(per_t)
         return total, per_t
 
@@ -915,7 +916,20 @@ class _MTPLoss(torch.autograd.Function):
         dH, dWs = saved[0], saved[1:]
         B, S, d = ctx.shape
         gh = (dH * g_total.to(dH.dtype)).view(B, S, d) if dH.numel() else None
-        gws = [(w * g_total.to(w.dtype)) if w.numel() else None for w in dWs]
+        gws = []
+        for W, w in zip(ctx.heads, dWs):
+            if not w.numel():
+                gws.append(None)
+                continue
+            sink = grad_sink(W) if W.is_contiguous() else None
+            if sink is not None:
+                # scaled straight into the weight's slot of the flat gradient buffer: one pass instead of a
+                # multiplication into a new tensor plus the copy into the buffer
+                torch.mul(w, g_total.to(w.dtype), out=sink[0])
+                sink[1]()
+                gws.append(None)
+            else:
+                gws.append(w * g_total.to(w.dtype))
         return (gh, None, None, None, None, *gws)
 
 
