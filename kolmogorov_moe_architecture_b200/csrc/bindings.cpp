@@ -542,6 +542,19 @@ Tensor rows_scatter(const Tensor& src, const Tensor& idx, int64_t S) {
   return out;
 }
 
+Tensor rows_scatter_rank1(const Tensor& src, const Tensor& idx, int64_t S, const Tensor& coef, const Tensor& wvec) {
+  c10::cuda::CUDAGuard guard(src.device());
+  need_bf16(src, "src"); need_bf16(coef, "coef"); need_bf16(wvec, "wvec"); check_idx(idx);
+  TORCH_CHECK(src.is_contiguous() && src.dim() == 3 && coef.is_contiguous() && wvec.is_contiguous());
+  const int B = src.size(0), k = src.size(1), d = src.size(2);
+  TORCH_CHECK(coef.numel() == (int64_t)B * S && wvec.numel() == d, "coef must hold B * S values, wvec d values");
+  Tensor out = at::empty({B, S, d}, src.options());
+  check(kmoe_rows_scatter_rank1(src.data_ptr(), (const long long*)idx.data_ptr<int64_t>(), coef.data_ptr(),
+                                wvec.data_ptr(), out.data_ptr(), B, (int)S, k, d, cur_stream()),
+        "rows_scatter_rank1");
+  return out;
+}
+
 Tensor mod_combine_fwd(const Tensor& res, const Tensor& proc, const Tensor& w, const Tensor& idx) {
   c10::cuda::CUDAGuard guard(res.device());
   need_bf16(res, "res"); need_bf16(proc, "proc"); need_f32(w, "w"); check_idx(idx);
@@ -808,6 +821,7 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("p2p_allgather", &p2p_allgather);
   m.def("rows_gather", &rows_gather);
   m.def("rows_scatter", &rows_scatter);
+  m.def("rows_scatter_rank1", &rows_scatter_rank1);
   m.def("mod_combine_fwd", &mod_combine_fwd);
   m.def("mod_combine_bwd", &mod_combine_bwd);
   m.def("muon_momentum", &muon_momentum);

@@ -37,19 +37,42 @@ __global__ void rows_gather_kernel(const __nv_bfloat16* __restrict__ src, const 
   }
 }
 
+// out[b, t, :] = src[b, slot(t), :] for kept positions, zero elsewhere; with `coef` / `wvec` the rank-one term
+// coef[b, t] * wvec[:] is added in the same pass (the gradient of a per-row dot product with wvec, i.e. of the
+// mixture-of-depths scorer, which reads the same rows).
 __global__ void rows_scatter_kernel(const __nv_bfloat16* __restrict__ src, const long long* __restrict__ idx,
-                                    __nv_bfloat16* __restrict__ out, int B, int S, int k, int d) {
+                                    __nv_bfloat16* __restrict__ out, int B, int S, int k, int d,
+                                    const __nv_bfloat16* __restrict__ coef = nullptr,
+                                    const __nv_bfloat16* __restrict__ wvec = nullptr) {
   const int vec = d / 8, lane = threadIdx.x & 31;
   const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
   for (long long r = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < (long long)B * S; r += warps) {
     const int b = (int)(r / S), t = (int)(r % S);
     const int j = find_slot(idx + (long long)b * k, k, t);
     uint4* o = reinterpret_cast<uint4*>(out + r * d);
-    if (j < 0) {
-      for (int v = lane; v < vec; v += 32) o[v] = make_uint4(0, 0, 0, 0);
-    } else {
-      const uint4* s = reinterpret_cast<const uint4*>(src + ((long long)b * k + j) * d);
-      for (int v = lane; v < vec; v += 32) o[v] = s[v];
+    const uint4* s = j < 0 ? nullptr : reinterpret_cast<const uint4*>(src + ((long long)b * k + j) * d);
+    if (coef == nullptr) {
+      if (j < 0) {
+        for (int v = lane; v < vec; v += 32) o[v] = make_uint4(0, 0, 0, 0);
+      } else {
+        for (int v = lane; v < vec; v += 32) o[v] = s[v];
+      }
+      continue;
+    }
+    const float c = __bfloat162float(coef[r]);
+    for (int v = lane; v < vec; v += 32) {
+      const uint4 wq = __ldg(reinterpret_cast<const uint4*>(wvec) + v);
+      const uint4 sq = j < 0 ? make_uint4(0, 0, 0, 0) : s[v];
+      const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&wq);
+      const __nv_bfloat162* ps = reinterpret_cast<const __nv_bfloat162*>(&sq);
+      uint4 oq;
+      __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&oq);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 fw = __bfloat1622float2(pw[i]), fs = __bfloat1622float2(ps[i]);
+        po[i] = __floats2bfloat162_rn(fs.x + c * fw.x, fs.y + c * fw.y);
+      }
+      o[v] = oq;
     }
   }
 }
@@ -152,6 +175,16 @@ extern "C" int kmoe_rows_scatter(const void* src, const long long* idx, void* ou
   if (B * (long long)S == 0) return 0;
   rows_scatter_kernel<<<grid_rows((long long)B * S), 256, 0, st>>>((const __nv_bfloat16*)src, idx, (__nv_bfloat16*)out,
                                                                    B, S, k, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int kmoe_rows_scatter_rank1(const void* src, const long long* idx, const void* coef, const void* wvec,
+                                       void* out, int B, int S, int k, int d, cudaStream_t st) {
+  if (d % 8 || coef == nullptr || wvec == nullptr) return -1;
+  if (B * (long long)S == 0) return 0;
+  rows_scatter_kernel<<<grid_rows((long long)B * S), 256, 0, st>>>(
+      (const __nv_bfloat16*)src, idx, (__nv_bfloat16*)out, B, S, k, d, (const __nv_bfloat16*)coef,
+      (const __nv_bfloat16*)wvec);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

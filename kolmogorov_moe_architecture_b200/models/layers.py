@@ -53,8 +53,7 @@ class TransformerBlock(nn.Module):
     def _ffn_with_mod(self, h: torch.Tensor, residual: torch.Tensor):
         """Kept tokens go through the FFN; their weighted outputs are added onto the residual stream
         (gather -> FFN -> residual + scatter(w * out), each a single pass)."""
-        sorted_idx, weights, _logits, _topk = self.ffn_mod_router(h)
-        picked = ops.mod_gather(h, sorted_idx)
+        picked, sorted_idx, weights = self.ffn_mod_router.route_and_gather(h)
         out = ops.mod_combine(residual, self.ffn(picked), weights, sorted_idx)
         return out, self.ffn_mod_router.aux_loss
 

@@ -33,6 +33,22 @@ class MoDRouter(nn.Module):
     def num_selected(self, seq_len: int) -> int:
         return max(1, min(seq_len, int(seq_len * self.capacity_factor)))
 
+    def _predictor_loss(self, hidden_states, topk_idx, like):
+        B, S, _ = hidden_states.shape
+        targets = torch.zeros(B, S, device=like.device, dtype=hidden_states.dtype)
+        targets.scatter_(1, topk_idx, 1.0)
+        aux_logits = self.aux_router(hidden_states.detach()).squeeze(-1)
+        return self.aux_loss_weight * F.binary_cross_entropy_with_logits(aux_logits, targets, reduction="mean")
+
+    def route_and_gather(self, hidden_states: torch.Tensor):
+        """``forward`` followed by the gather of the kept rows, as one op (one node of the autograd graph on the
+        GPU path): (kept rows (B, k, d), ascending indices, weights)."""
+        B, S, _ = hidden_states.shape
+        k = self.num_selected(S)
+        picked, sorted_idx, weights, logits = ops.mod_score_gather(hidden_states, self.router.weight, k)
+        self.aux_loss = self._predictor_loss(hidden_states, sorted_idx, logits) if self.training else 0.0
+        return picked, sorted_idx, weights
+
     def forward(self, hidden_states: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
         B, S, _ = hidden_states.shape
         if S == 0:
@@ -42,12 +58,5 @@ class MoDRouter(nn.Module):
         logits = self.router(hidden_states).squeeze(-1)
         k = self.num_selected(S)
         sorted_idx, weights, topk_idx = ops.mod_route(logits, k)
-        if self.training:
-            targets = torch.zeros(B, S, device=logits.device, dtype=hidden_states.dtype)
-            targets.scatter_(1, topk_idx, 1.0)
-            aux_logits = self.aux_router(hidden_states.detach()).squeeze(-1)
-            self.aux_loss = self.aux_loss_weight * F.binary_cross_entropy_with_logits(
-                aux_logits, targets, reduction="mean")
-        else:
-            self.aux_loss = 0.0
+        self.aux_loss = self._predictor_loss(hidden_states, topk_idx, logits) if self.training else 0.0
         return sorted_idx, weights, logits, topk_idx

@@ -9,6 +9,8 @@ from __future__ import annotations
 
 import os
 
+import torch
+
 from . import eager
 from .loader import ext_available, load_ext, require_ext  # noqa: F401
 
@@ -134,6 +136,18 @@ def mod_route(logits, k):
         from . import cuda_ops
         return cuda_ops.mod_route(logits, k)
     return eager.mod_route(logits, k)
+
+
+def mod_score_gather(h, w, k):
+    """Mixture-of-depths scorer ``h w^T``, per-sequence top-k with softmax weights and the gather of the kept
+    rows: (picked (B, k, d), ascending indices (B, k), weights (B, k), logits (B, S))."""
+    if (_use_cuda(h) and h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and h.shape[-1] % 8 == 0
+            and h.shape[1] <= 16384 and h.numel() > 0):
+        from . import cuda_ops
+        return cuda_ops.mod_score_gather(h, w, k)
+    logits = torch.nn.functional.linear(h, w).squeeze(-1)
+    idx, wts, _ = mod_route(logits, k)
+    return mod_gather(h, idx), idx, wts, logits
 
 
 def mod_gather(h, idx):

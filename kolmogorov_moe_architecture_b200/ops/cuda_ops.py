@@ -814,6 +814,67 @@ class _ModCombine(torch.autograd.Function):
         return g, dproc, dw.to(ctx.wdtype), None
 
 
+class _ModScoreGather(torch.autograd.Function):
+    """Mixture-of-depths scorer, top-k and row gather as one node of the graph: ``logits = h w``,
+    ``idx, weights = top-k / softmax(logits)``, ``picked = h[idx]``.  The hidden states feed both the scorer and
+    the gather; as one node their two gradients are formed by one kernel (scatter of the picked rows' gradient
+    plus the rank-one term ``dlogits w^T``) instead of two full-size tensors and an addition."""
+
+    @staticmethod
+    def forward(ctx, h, w, k):
+        B, S, d = h.shape
+        hc = h.contiguous()
+        h2 = hc.view(B * S, d)
+        wv = w.reshape(-1).contiguous()
+        logits = K.rowdot_fwd(h2, wv).view(B, S)
+        sf = logits.float()
+        idx, wts, stat = K.seq_topk_fwd(sf, S, 1, B, 0, B, S, k, 0)
+        picked = K.rows_gather(hc, idx)
+        _count(3)
+        ctx.save_for_backward(h2, wv, sf, idx, wts, stat)
+        ctx.w_param = w
+        ctx.meta = (B, S, d, k, w.shape)
+        ctx.mark_non_differentiable(idx)
+        ctx.set_materialize_grads(False)
+        return picked, idx, wts.to(h.dtype), logits
+
+    @staticmethod
+    def backward(ctx, d_picked, _didx, d_wts, d_logits):
+        h2, wv, sf, idx, wts, stat = ctx.saved_tensors
+        B, S, d, k, wshape = ctx.meta
+        dl = None
+        if d_wts is not None:
+            dl = K.seq_topk_bwd(sf, S, 1, B, 0, B, S, k, 0, idx, wts, d_wts.reshape(-1, k).float().contiguous(), stat)
+            _count()
+        if d_logits is not None:
+            dl = d_logits.float() if dl is None else dl + d_logits.float()
+        if d_picked is None:
+            d_picked = torch.zeros(B, k, d, dtype=h2.dtype, device=h2.device)
+        dw = None
+        if dl is None:
+            dh = K.rows_scatter(d_picked.contiguous(), idx, S)
+        else:
+            dlb = dl.to(h2.dtype).reshape(-1).contiguous()
+            dh = K.rows_scatter_rank1(d_picked.contiguous(), idx, S, dlb, wv)
+            if ctx.needs_input_grad[1]:
+                sink = grad_sink(ctx.w_param) if ctx.w_param.is_contiguous() else None
+                dst = sink[0].view(-1) if sink is not None else None
+                _dx, dwv = K.rowdot_bwd(h2, wv, dlb, False, dst)
+                _count(2)
+                if sink is not None:
+                    sink[1]()
+                else:
+                    dw = dwv.view(wshape)
+        _count()
+        return dh, dw, None
+
+
+def mod_score_gather(h, w, k):
+    """h (B, S, d), scorer weight w (1, d) -> (picked rows (B, k, d), ascending indices (B, k), softmax weights
+    (B, k), logits (B, S))."""
+    return _ModScoreGather.apply(h, w, k)
+
+
 def mod_gather(h, idx):
     """h (B, S, d), idx (B, k) ascending -> (B, k, d)."""
     if not _bf16(h) or h.shape[-1] % 8:

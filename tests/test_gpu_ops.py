@@ -562,3 +562,29 @@ def test_residual_rmsnorm_fwd_bwd(with_addend, d):
     h2, _ = ops.residual_rmsnorm(x2, None, w.detach(), 1e-5)
     (h2 * g1).sum().backward()
     assert _rel(x2.grad, g1) < 1e-6
+
+
+@pytest.mark.parametrize("B,S,d,k", [(2, 300, 256, 225), (3, 128, 512, 96)])
+def test_mod_score_gather_fwd_bwd(B, S, d, k):
+    """Scorer, top-k and gather of the kept rows as one op against the separate PyTorch definitions in fp32; the
+    hidden states get the scatter of the picked rows' gradient plus the scorer's rank-one term from one kernel."""
+    ops, c, eager = _mods()
+    torch.manual_seed(21)
+    h = _bf(B, S, d, grad=True)
+    w = _bf(1, d, scale=d ** -0.5, grad=True)
+    picked, idx, wts, logits = ops.mod_score_gather(h, w, k)
+    g1, g2 = _bf(B, k, d), torch.randn(B, k, device="cuda")
+    ((picked * g1).sum() + (wts.float() * g2).sum()).backward()
+    c.check_status()
+    hr, wr = _f32_leaf(h), _f32_leaf(w)
+    lr = F.linear(hr, wr).squeeze(-1)
+    # the kernel ranks the bf16-rounded logits: give the reference the same ranking
+    lq = lr.detach().to(torch.bfloat16).float()
+    idx_r, _, _ = eager.mod_route(lq, k)
+    assert torch.equal(idx, idx_r)
+    wts_r = torch.softmax(torch.gather(lr, 1, idx_r), dim=-1)
+    pr = eager.mod_gather(hr, idx_r)
+    ((pr * g1.float()).sum() + (wts_r * g2).sum()).backward()
+    assert torch.equal(picked.float(), pr.detach())
+    assert _rel(wts, wts_r) < 2e-2 and _rel(logits, lr) < 2e-2
+    assert _rel(h.grad, hr.grad) < 2e-2 and _rel(w.grad, wr.grad) < 3e-2
