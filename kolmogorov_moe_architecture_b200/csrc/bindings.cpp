@@ -555,6 +555,18 @@ Tensor rows_scatter_rank1(const Tensor& src, const Tensor& idx, int64_t S, const
   return out;
 }
 
+std::tuple<Tensor, Tensor> mod_bce(const Tensor& logits, const Tensor& idx) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  need_bf16(logits, "logits"); check_idx(idx);
+  TORCH_CHECK(logits.is_contiguous() && logits.dim() == 2 && idx.size(0) == logits.size(0));
+  Tensor loss = at::empty({1}, logits.options().dtype(at::kFloat));
+  Tensor dl = at::empty_like(logits);
+  check(kmoe_mod_bce(logits.data_ptr(), (const long long*)idx.data_ptr<int64_t>(), loss.data_ptr<float>(),
+                     dl.data_ptr(), (int)logits.size(0), (int)logits.size(1), (int)idx.size(1), cur_stream()),
+        "mod_bce");
+  return {loss, dl};
+}
+
 Tensor mod_combine_fwd(const Tensor& res, const Tensor& proc, const Tensor& w, const Tensor& idx) {
   c10::cuda::CUDAGuard guard(res.device());
   need_bf16(res, "res"); need_bf16(proc, "proc"); need_f32(w, "w"); check_idx(idx);
@@ -822,6 +834,7 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("rows_gather", &rows_gather);
   m.def("rows_scatter", &rows_scatter);
   m.def("rows_scatter_rank1", &rows_scatter_rank1);
+  m.def("mod_bce", &mod_bce);
   m.def("mod_combine_fwd", &mod_combine_fwd);
   m.def("mod_combine_bwd", &mod_combine_bwd);
   m.def("muon_momentum", &muon_momentum);

@@ -156,9 +156,43 @@ static int grid_rows(long long rows) {
   return (int)(want < 148 * 16 ? (want > 0 ? want : 1) : 148 * 16);
 }
 
+// Binary cross-entropy of the selection predictor: the target of position (b, t) is 1 iff t is among the kept
+// (ascending) indices of sequence b.  One CTA: loss = mean over B * S of softplus(x) - x * target, and
+// dlogits = (sigmoid(x) - target) / (B * S) for an upstream gradient of 1, summed in a fixed order.
+__global__ void __launch_bounds__(1024)
+mod_bce_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ idx, float* __restrict__ loss,
+               __nv_bfloat16* __restrict__ dlogits, int B, int S, int k) {
+  __shared__ float red[32];
+  const long long n = (long long)B * S;
+  const float inv = 1.f / (float)n;
+  float acc = 0.f;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+    const int b = (int)(i / S), t = (int)(i % S);
+    const float x = __bfloat162float(logits[i]);
+    const float tgt = find_slot(idx + (long long)b * k, k, t) >= 0 ? 1.f : 0.f;
+    acc += fmaxf(x, 0.f) - x * tgt + log1pf(__expf(-fabsf(x)));
+    dlogits[i] = __float2bfloat16((1.f / (1.f + __expf(-x)) - tgt) * inv);
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+    loss[0] = tot * inv;
+  }
+}
+
 }  // namespace kmoe
 
 using namespace kmoe;
+
+extern "C" int kmoe_mod_bce(const void* logits, const long long* idx, float* loss, void* dlogits, int B, int S, int k,
+                            cudaStream_t st) {
+  if (B * (long long)S == 0) return -1;
+  mod_bce_kernel<<<1, 1024, 0, st>>>((const __nv_bfloat16*)logits, idx, loss, (__nv_bfloat16*)dlogits, B, S, k);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 extern "C" int kmoe_rows_gather(const void* src, const long long* idx, void* out, int B, int S, int k, int d,
                                 cudaStream_t st) {

@@ -35,9 +35,14 @@ class GroupedQueryAttention(nn.Module):
     def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
                 position_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
         B, S, _ = hidden_states.shape
-        q = self.q_proj(hidden_states).view(B, S, self.n_heads, self.head_dim)
-        k = self.k_proj(hidden_states).view(B, S, self.n_kv_heads, self.head_dim)
-        v = self.v_proj(hidden_states).view(B, S, self.n_kv_heads, self.head_dim)
+        if self.q_proj.bias is None and self.k_proj.bias is None and self.v_proj.bias is None:
+            # the three projections of the same input as one autograd node: dx is accumulated inside the GEMMs
+            q, k, v = ops.linear_multi(hidden_states, [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight])
+        else:
+            q, k, v = self.q_proj(hidden_states), self.k_proj(hidden_states), self.v_proj(hidden_states)
+        q = q.view(B, S, self.n_heads, self.head_dim)
+        k = k.view(B, S, self.n_kv_heads, self.head_dim)
+        v = v.view(B, S, self.n_kv_heads, self.head_dim)
         q, k = self.rope(q, k, position_ids)
         if hasattr(attention_mask, "doc_start"):            # packed documents: boundaries, not a dense mask
             out = ops.attention(q, k, v, causal=True, dropout_p=self.attention_dropout, training=self.training,

@@ -34,11 +34,8 @@ class MoDRouter(nn.Module):
         return max(1, min(seq_len, int(seq_len * self.capacity_factor)))
 
     def _predictor_loss(self, hidden_states, topk_idx, like):
-        B, S, _ = hidden_states.shape
-        targets = torch.zeros(B, S, device=like.device, dtype=hidden_states.dtype)
-        targets.scatter_(1, topk_idx, 1.0)
         aux_logits = self.aux_router(hidden_states.detach()).squeeze(-1)
-        return self.aux_loss_weight * F.binary_cross_entropy_with_logits(aux_logits, targets, reduction="mean")
+        return self.aux_loss_weight * ops.mod_bce(aux_logits, topk_idx)
 
     def route_and_gather(self, hidden_states: torch.Tensor):
         """``forward`` followed by the gather of the kept rows, as one op (one node of the autograd graph on the

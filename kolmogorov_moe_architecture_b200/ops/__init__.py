@@ -35,6 +35,16 @@ def linear(x, weight, bias=None):
     return F.linear(x, weight, bias)
 
 
+def linear_multi(x, weights):
+    """Several bias-free projections of one input: ``[F.linear(x, w) for w in weights]``.  On the GPU path they
+    are one node of the autograd graph, so the input's gradient is accumulated inside the dgrad GEMMs."""
+    if _use_cuda(x):
+        from . import cuda_ops
+        return cuda_ops.linear_multi(x, weights)
+    import torch.nn.functional as F
+    return [F.linear(x, w) for w in weights]
+
+
 def dense_swiglu(x, w1, w2, w3):
     """``w3(silu(w1 x) * (w2 x))`` with ``nn.Linear``-layout weights (reference: moe_arch/model/ffn.py:44-64)."""
     if _use_cuda(x):
@@ -148,6 +158,16 @@ def mod_score_gather(h, w, k):
     logits = torch.nn.functional.linear(h, w).squeeze(-1)
     idx, wts, _ = mod_route(logits, k)
     return mod_gather(h, idx), idx, wts, logits
+
+
+def mod_bce(aux_logits, idx):
+    """Mean binary cross-entropy of (B, S) logits against "position is among the kept indices idx (B, k)"."""
+    if _use_cuda(aux_logits) and aux_logits.dtype == torch.bfloat16 and aux_logits.numel() > 0:
+        from . import cuda_ops
+        return cuda_ops.mod_bce(aux_logits, idx)
+    targets = torch.zeros_like(aux_logits)
+    targets.scatter_(1, idx, 1.0)
+    return torch.nn.functional.binary_cross_entropy_with_logits(aux_logits, targets, reduction="mean")
 
 
 def mod_gather(h, idx):

@@ -262,6 +262,49 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return y if bias is None else y + bias
 
 
+class _LinearMulti(torch.autograd.Function):
+    """Several bias-free projections of the same input as one node of the graph (the q / k / v projections of
+    an attention block): the input's gradient is accumulated by the dgrad GEMMs themselves (``beta = 1`` on the
+    second and later ones) instead of being formed as separate tensors that autograd then adds up."""
+
+    @staticmethod
+    def forward(ctx, x2, *ws):
+        ctx.save_for_backward(x2, *ws)
+        return tuple(mm_nt(x2, w) for w in ws)
+
+    @staticmethod
+    def backward(ctx, *dys):
+        x2, *ws = ctx.saved_tensors
+        dx = None
+        dws = []
+        for i, (dy, w) in enumerate(zip(dys, ws)):
+            if dy is None:
+                dws.append(None)
+                continue
+            if not _rows_ok(dy):
+                dy = dy.contiguous()
+            if ctx.needs_input_grad[0]:
+                if dx is None:
+                    dx = mm_nn(dy, w)
+                else:
+                    mm_nn(dy, w, out=dx, D=dx, beta=1.0)
+            dws.append(_wgrad(dy, x2, w) if ctx.needs_input_grad[1 + i] else None)
+        return (dx, *dws)
+
+
+def linear_multi(x: torch.Tensor, weights: Sequence[torch.Tensor]):
+    """``[F.linear(x, w) for w in weights]`` with one backward node (see ``_LinearMulti``)."""
+    in_f = weights[0].shape[1]
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, in_f)
+    if not _rows_ok(x2):
+        x2 = x2.contiguous()
+    if not all(_linear_ok(x2, w) and w.shape[0] % 64 == 0 for w in weights):
+        return [linear(x, w) for w in weights]
+    ys = _LinearMulti.apply(x2, *weights)
+    return [y.view(*lead, w.shape[0]) for y, w in zip(ys, weights)]
+
+
 class _DenseSwiGLU(torch.autograd.Function):
     """w3(silu(w1 x) * (w2 x)) with gate and up in one GEMM whose epilogue applies SwiGLU (one tile holds 128
     gate and 128 up columns), the same kernels the experts use with a single group."""
@@ -867,6 +910,28 @@ class _ModScoreGather(torch.autograd.Function):
                     dw = dwv.view(wshape)
         _count()
         return dh, dw, None
+
+
+class _ModBCE(torch.autograd.Function):
+    """Mean binary cross-entropy of the selection predictor against "this position was kept": targets are never
+    materialised, the gradient is produced with the loss."""
+
+    @staticmethod
+    def forward(ctx, logits, idx):
+        loss, dl = K.mod_bce(logits.contiguous(), idx)
+        _count()
+        ctx.save_for_backward(dl)
+        return loss[0]
+
+    @staticmethod
+    def backward(ctx, g):
+        (dl,) = ctx.saved_tensors
+        return dl * g.to(dl.dtype), None
+
+
+def mod_bce(logits, idx):
+    """logits (B, S) bf16, idx (B, k) ascending kept positions -> scalar fp32 loss."""
+    return _ModBCE.apply(logits, idx.contiguous())
 
 
 def mod_score_gather(h, w, k):

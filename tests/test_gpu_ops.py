@@ -588,3 +588,45 @@ def test_mod_score_gather_fwd_bwd(B, S, d, k):
     assert torch.equal(picked.float(), pr.detach())
     assert _rel(wts, wts_r) < 2e-2 and _rel(logits, lr) < 2e-2
     assert _rel(h.grad, hr.grad) < 2e-2 and _rel(w.grad, wr.grad) < 3e-2
+
+
+def test_linear_multi_fwd_bwd():
+    """q / k / v style projections of one input as one autograd node against three F.linear calls in fp32."""
+    ops, c, eager = _mods()
+    torch.manual_seed(5)
+    x = _bf(2, 100, 256, grad=True)
+    ws = [_bf(n, 256, scale=256 ** -0.5, grad=True) for n in (256, 64, 64)]
+    ys = ops.linear_multi(x, ws)
+    gs = [_bf(2, 100, n) for n in (256, 64, 64)]
+    sum((y * g).sum() for y, g in zip(ys, gs)).backward()
+    c.check_status()
+    xr, wrs = _f32_leaf(x), [_f32_leaf(w) for w in ws]
+    yrs = [F.linear(xr, w) for w in wrs]
+    sum((y * g.float()).sum() for y, g in zip(yrs, gs)).backward()
+    for y, yr in zip(ys, yrs):
+        assert _rel(y, yr) < 1e-2
+    assert _rel(x.grad, xr.grad) < 1e-2
+    for w, wr in zip(ws, wrs):
+        assert _rel(w.grad, wr.grad) < 1e-2
+    # only one of the outputs used downstream
+    x2 = x.detach().clone().requires_grad_(True)
+    y0, _, _ = ops.linear_multi(x2, [w.detach() for w in ws])
+    (y0 * gs[0]).sum().backward()
+    assert _rel(x2.grad, (gs[0].float() @ wrs[0].detach())) < 1e-2
+
+
+def test_mod_predictor_bce():
+    """Fused selection-predictor loss against zeros + scatter_ + binary_cross_entropy_with_logits in fp32."""
+    ops, c, eager = _mods()
+    torch.manual_seed(17)
+    B, S, k = 3, 333, 250
+    logits = (torch.randn(B, S, device="cuda") * 3).to(torch.bfloat16).requires_grad_(True)
+    idx = torch.stack([torch.randperm(S, device="cuda")[:k].sort().values for _ in range(B)])
+    loss = ops.mod_bce(logits, idx)
+    (loss * 2.5).backward()
+    lr = logits.detach().float().requires_grad_(True)
+    tgt = torch.zeros(B, S, device="cuda").scatter_(1, idx, 1.0)
+    ref = F.binary_cross_entropy_with_logits(lr, tgt, reduction="mean")
+    (ref * 2.5).backward()
+    assert abs(loss.item() - ref.item()) < 1e-4 * max(1.0, abs(ref.item()))
+    assert _rel(logits.grad, lr.grad) < 1e-2
