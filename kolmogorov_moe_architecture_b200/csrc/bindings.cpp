@@ -191,6 +191,14 @@ Tensor sumsq(const Tensor& x) {
   return out;
 }
 
+void scale_copy(const Tensor& src, Tensor dst, const Tensor& scale) {
+  c10::cuda::CUDAGuard guard(src.device());
+  need_bf16(src, "src"); need_bf16(dst, "dst"); need_f32(scale, "scale");
+  TORCH_CHECK(src.is_contiguous() && dst.is_contiguous() && src.numel() == dst.numel() && scale.numel() >= 1);
+  check(kmoe_scale_copy(src.data_ptr(), dst.data_ptr(), src.numel(), scale.data_ptr<float>(), cur_stream()),
+        "scale_copy");
+}
+
 void sum_partials(const Tensor& partial, Tensor out) {
   c10::cuda::CUDAGuard guard(partial.device());
   need_f32(partial, "partial"); need_bf16(out, "out");
@@ -811,6 +819,7 @@ TORCH_LIBRARY(kmoe, m) {
   m.def("rowdot_bwd", &rowdot_bwd);
   m.def("sum_partials", &sum_partials);
   m.def("sumsq", &sumsq);
+  m.def("scale_copy", &scale_copy);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("swiglu_bwd_cat", &swiglu_bwd_cat);

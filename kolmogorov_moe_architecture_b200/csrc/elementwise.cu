@@ -644,6 +644,32 @@ extern "C" int kmoe_sumsq_bf16(const void* x, long long n, float* partial, float
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
+// dst = bf16(src * *scale): a gradient computed for an upstream gradient of 1, rescaled on its way into the flat
+// gradient buffer.  16 bytes per thread and iteration.
+__global__ void __launch_bounds__(256)
+scale_copy_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n,
+                  const float* __restrict__ scale) {
+  const float sc = *scale;
+  const long long nvec = n / 8;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float v[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(src) + i), v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] *= sc;
+    reinterpret_cast<uint4*>(dst)[i] = pack8(v);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (int)(n - nvec * 8))
+    dst[nvec * 8 + threadIdx.x] = __float2bfloat16(__bfloat162float(src[nvec * 8 + threadIdx.x]) * sc);
+}
+
+extern "C" int kmoe_scale_copy(const void* src, void* dst, long long n, const float* scale, cudaStream_t st) {
+  if (n < 0 || ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15)) return -1;
+  if (n == 0) return 0;
+  scale_copy_kernel<<<148 * 8, 256, 0, st>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, n, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 extern "C" int kmoe_sum_partials(const float* partial, void* out, int nparts, long long n, cudaStream_t st) {
   if (n % 4 || nparts < 1) return -1;
   sum_partials_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(partial, (__nv_bfloat16*)out, nparts, n);

@@ -134,6 +134,8 @@ int kmoe_rmsnorm_bwd_num_partials(int rows);
 // kmoe_sumsq_num_partials() floats
 int kmoe_sumsq_num_partials(void);
 int kmoe_sumsq_bf16(const void* x, long long n, float* partial, float* out, cudaStream_t st);
+// dst = bf16(src * *scale) over n bf16 values (both 16-byte aligned; scale is a device float)
+int kmoe_scale_copy(const void* src, void* dst, long long n, const float* scale, cudaStream_t st);
 // out (bf16, n values) = sum of nparts fp32 vectors of n values stored back to back; n % 4 == 0
 int kmoe_sum_partials(const float* partial, void* out, int nparts, long long n, cudaStream_t st);
 /* nn.Linear(d, 1): y[row] = x[row, :] . w ; backward gives dx (optional) and dw (bf16 and/or fp32). */

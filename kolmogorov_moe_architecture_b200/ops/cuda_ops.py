@@ -879,7 +879,7 @@ class _ModScoreGather(torch.autograd.Function):
         ctx.meta = (B, S, d, k, w.shape)
         ctx.mark_non_differentiable(idx)
         ctx.set_materialize_grads(False)
-        return picked, idx, wts.to(h.dtype), logits
+        return picked, idx, wts, logits          # weights stay fp32: the combine kernel reads them as such
 
     @staticmethod
     def backward(ctx, d_picked, _didx, d_wts, d_logits):
@@ -1051,7 +1051,11 @@ class _MTPLoss(torch.autograd.Function):
             if sink is not None:
                 # scaled straight into the weight's slot of the flat gradient buffer: one pass instead of a
                 # multiplication into a new tensor plus the copy into the buffer
-                torch.mul(w, g_total.to(w.dtype), out=sink[0])
+                dst = sink[0]
+                if dst.is_contiguous() and dst.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+                    K.scale_copy(w, dst, g_total.reshape(1).float())
+                else:
+                    torch.mul(w, g_total.to(w.dtype), out=dst)
                 sink[1]()
                 gws.append(None)
             else:
