@@ -568,9 +568,12 @@ std::tuple<Tensor, Tensor> mod_bce(const Tensor& logits, const Tensor& idx) {
   need_bf16(logits, "logits"); check_idx(idx);
   TORCH_CHECK(logits.is_contiguous() && logits.dim() == 2 && idx.size(0) == logits.size(0));
   Tensor loss = at::empty({1}, logits.options().dtype(at::kFloat));
+  Tensor partial = at::empty({kmoe_mod_bce_num_partials((int)logits.size(0), (int)logits.size(1))},
+                             logits.options().dtype(at::kFloat));
   Tensor dl = at::empty_like(logits);
-  check(kmoe_mod_bce(logits.data_ptr(), (const long long*)idx.data_ptr<int64_t>(), loss.data_ptr<float>(),
-                     dl.data_ptr(), (int)logits.size(0), (int)logits.size(1), (int)idx.size(1), cur_stream()),
+  check(kmoe_mod_bce(logits.data_ptr(), (const long long*)idx.data_ptr<int64_t>(), partial.data_ptr<float>(),
+                     loss.data_ptr<float>(), dl.data_ptr(), (int)logits.size(0), (int)logits.size(1),
+                     (int)idx.size(1), cur_stream()),
         "mod_bce");
   return {loss, dl};
 }

@@ -259,9 +259,10 @@ int kmoe_seq_topk_bwd(const float* scores, long long row_stride, long long col_s
 int kmoe_rows_gather(const void* src, const long long* idx, void* out, int B, int S, int k, int d, cudaStream_t st);
 int kmoe_rows_scatter(const void* src, const long long* idx, void* out, int B, int S, int k, int d, cudaStream_t st);
 // mean binary cross-entropy of bf16 logits [B, S] against "position is among the ascending kept indices idx [B, k]";
-// dlogits (bf16 [B, S]) = gradient for an upstream gradient of 1
-int kmoe_mod_bce(const void* logits, const long long* idx, float* loss, void* dlogits, int B, int S, int k,
-                 cudaStream_t st);
+// dlogits (bf16 [B, S]) = gradient for an upstream gradient of 1; partial = scratch of kmoe_mod_bce_num_partials floats
+int kmoe_mod_bce_num_partials(int B, int S);
+int kmoe_mod_bce(const void* logits, const long long* idx, float* partial, float* loss, void* dlogits, int B, int S,
+                 int k, cudaStream_t st);
 // the same plus coef[b, t] * wvec[:] on every row (coef bf16 [B * S], wvec bf16 [d])
 int kmoe_rows_scatter_rank1(const void* src, const long long* idx, const void* coef, const void* wvec, void* out,
                             int B, int S, int k, int d, cudaStream_t st);

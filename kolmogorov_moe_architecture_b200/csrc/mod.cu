@@ -157,20 +157,22 @@ static int grid_rows(long long rows) {
 }
 
 // Binary cross-entropy of the selection predictor: the target of position (b, t) is 1 iff t is among the kept
-// (ascending) indices of sequence b.  One CTA: loss = mean over B * S of softplus(x) - x * target, and
-// dlogits = (sigmoid(x) - target) / (B * S) for an upstream gradient of 1, summed in a fixed order.
-__global__ void __launch_bounds__(1024)
-mod_bce_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ idx, float* __restrict__ loss,
-               __nv_bfloat16* __restrict__ dlogits, int B, int S, int k) {
-  __shared__ float red[32];
+// (ascending) indices of sequence b.  loss = mean over B * S of softplus(x) - x * target, and
+// dlogits = (sigmoid(x) - target) / (B * S) for an upstream gradient of 1.  Blocks of 256 positions write partial
+// sums, a second one-warp kernel adds them in a fixed order.
+__global__ void __launch_bounds__(256)
+mod_bce_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ idx,
+               float* __restrict__ partial, __nv_bfloat16* __restrict__ dlogits, int B, int S, int k) {
+  __shared__ float red[8];
   const long long n = (long long)B * S;
   const float inv = 1.f / (float)n;
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
   float acc = 0.f;
-  for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+  if (i < n) {
     const int b = (int)(i / S), t = (int)(i % S);
     const float x = __bfloat162float(logits[i]);
     const float tgt = find_slot(idx + (long long)b * k, k, t) >= 0 ? 1.f : 0.f;
-    acc += fmaxf(x, 0.f) - x * tgt + log1pf(__expf(-fabsf(x)));
+    acc = fmaxf(x, 0.f) - x * tgt + log1pf(__expf(-fabsf(x)));
     dlogits[i] = __float2bfloat16((1.f / (1.f + __expf(-x)) - tgt) * inv);
   }
   acc = warp_sum(acc);
@@ -178,19 +180,31 @@ mod_bce_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __rest
   __syncthreads();
   if (threadIdx.x == 0) {
     float tot = 0.f;
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
-    loss[0] = tot * inv;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    partial[blockIdx.x] = tot;
   }
+}
+__global__ void mod_bce_sum_kernel(const float* __restrict__ partial, int nparts, float inv, float* __restrict__ loss) {
+  float s = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += 32) s += partial[i];
+  s = warp_sum(s);
+  if (threadIdx.x == 0) loss[0] = s * inv;
 }
 
 }  // namespace kmoe
 
 using namespace kmoe;
 
-extern "C" int kmoe_mod_bce(const void* logits, const long long* idx, float* loss, void* dlogits, int B, int S, int k,
-                            cudaStream_t st) {
+extern "C" int kmoe_mod_bce_num_partials(int B, int S) { return (int)(((long long)B * S + 255) / 256); }
+
+// partial: scratch of kmoe_mod_bce_num_partials(B, S) floats
+extern "C" int kmoe_mod_bce(const void* logits, const long long* idx, float* partial, float* loss, void* dlogits, int B,
+                            int S, int k, cudaStream_t st) {
   if (B * (long long)S == 0) return -1;
-  mod_bce_kernel<<<1, 1024, 0, st>>>((const __nv_bfloat16*)logits, idx, loss, (__nv_bfloat16*)dlogits, B, S, k);
+  const int g = kmoe_mod_bce_num_partials(B, S);
+  mod_bce_kernel<<<g, 256, 0, st>>>((const __nv_bfloat16*)logits, idx, partial, (__nv_bfloat16*)dlogits, B, S, k);
+  mod_bce_sum_kernel<<<1, 32, 0, st>>>(partial, g, 1.f / (float)((long long)B * S), loss);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
