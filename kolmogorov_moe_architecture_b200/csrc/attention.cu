@@ -5,15 +5,20 @@
 // lse [B, H, S] fp32 (natural log).  Query head h reads KV head h / (H / Hkv) directly -
 // K and V are never expanded to H heads.
 //
-// Forward, one CTA per (128-query block, head, batch), two CTAs per SM, 64 keys per step:
-//   warp 4   TMA producer: Q once, then K_j / V_j into a 2-stage ring
-//   warp 5   MMA issuer:   S_j = Q K_j^T (double-buffered in TMEM), O += P_j V_j (O lives in TMEM)
-//   warps 0-3 (thread = query row): S_j from TMEM -> scale, causal mask, running max/sum,
-//            P_j as bf16 into swizzled smem (A operand of the PV MMA); O is rescaled in TMEM only
-//            when the row maximum grew by more than 2^8.
-// Backward is two kernels of the same structure: dQ (loop over KV blocks for a query
-// block) and dK/dV (loop over query blocks of all heads of the group for a KV block);
-// both recompute P from the saved lse, so no atomics and the result is deterministic.
+// head_dim 128 (the model's): 320-thread CTAs - eight softmax warps in two warpgroups, a TMA producer warp, an
+// MMA warp - and 128-key / 128-query steps.
+//   forward   attn_fwd2_kernel: two 128-query tiles per CTA, one per warpgroup; S = Q K^T in TMEM, the score row
+//             is read into registers once, P is written as packed bf16 over the S columns and feeds O += P V as
+//             the A operand from tensor memory; O is rescaled only when the row maximum grew by more than 2^8.
+//   backward  attn_bwd_dq2_kernel (loop over key blocks of a query block) and attn_bwd_dkv2_kernel (loop over
+//             the query heads of the group and their query blocks for a key block); both recompute P from the
+//             saved lse (no atomics, deterministic); the warpgroups split the 128 columns of an accumulator in
+//             halves; P^T / dS^T / dS are packed over consumed accumulator columns and enter the next MMA from
+//             tensor memory.
+// head_dim 64 keeps the earlier kernels (attn_fwd_kernel, attn_bwd_dq_kernel, attn_bwd_dkv_kernel): 192-thread
+// CTAs, one softmax warpgroup (thread = row), 64-wide steps, P / dS staged through swizzled shared memory.
+// In the head_dim-128 kernels the tile index is the slowest grid dimension, so the heavy tiles of all heads run
+// first.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -283,9 +288,9 @@ teardown:
 //   warps 0-3 / 4-7  softmax of tile 0 / 1 (thread = query row)
 //   warp 8           TMA producer: Q tiles once, K_j / V_j into 2-stage rings
 //   warp 9           MMA issuer: S_t = Q_t K_j^T (128 x 128 x 128), O_t += P_t V_j with P_t read from TMEM
-// P is written as packed bf16 over the first 64 columns of the tile's own S accumulator (the softmax reads S in
-// 32-column chunks and chunk c's P lands in columns it has already consumed), so no shared memory is spent on
-// P and the PV MMA takes its A operand from tensor memory.  The tensor pipe executes one tile's MMAs while the
+// P is written as packed bf16 over the first 64 columns of the tile's own S accumulator (the softmax has the whole
+// 128-value score row in registers by then), so no shared memory is spent on P and the PV MMA takes its A operand
+// from tensor memory.  The tensor pipe executes one tile's MMAs while the
 // other tile's warpgroup is in its softmax; 128-key steps halve the number of barrier round trips per key.
 constexpr int F2_KEYS = 128;
 constexpr int F2_THREADS = 320;
