@@ -325,3 +325,84 @@ def test_weight_gradient_token_slices_cover_every_token_once(out_f, in_f, T):
         assert begin[i] % 64 == 0 and length[i] > 0
         if i + 1 < len(begin):
             assert begin[i] + length[i] == begin[i + 1]
+
+
+def _score_key(v: float) -> int:
+    """Order-preserving 32-bit image of an fp32 score, as in the selection kernel."""
+    import struct
+    u = struct.unpack("<I", struct.pack("<f", v))[0]
+    return (~u & 0xFFFFFFFF) if (u & 0x80000000) else (u | 0x80000000)
+
+
+def _radix_select_keep(scores, k):
+    """Host restatement of the mixture-of-depths selection kernel: 4-pass radix selection of the k-th best key,
+    then keep everything above it and the lowest-indexed ``need`` of the ties."""
+    keys = [_score_key(float(v)) for v in scores]
+    prefix, need = 0, k
+    for p in range(4):
+        shift = 24 - 8 * p
+        mask = 0 if p == 0 else (0xFFFFFFFF << (shift + 8)) & 0xFFFFFFFF
+        hist = [0] * 256
+        for u in keys:
+            if (u & mask) == prefix:
+                hist[(u >> shift) & 255] += 1
+        above = 0
+        for b in range(255, -1, -1):
+            if above + hist[b] >= need:
+                prefix |= b << shift
+                need -= above
+                break
+            above += hist[b]
+    kept, ties = [], 0
+    for i, u in enumerate(keys):
+        if u > prefix or (u == prefix and ties < need):
+            kept.append(i)
+        if u == prefix:
+            ties += 1
+    return kept
+
+
+@settings(max_examples=60, deadline=None)
+@given(S=st.integers(min_value=2, max_value=300), frac=st.floats(min_value=0.05, max_value=1.0),
+       levels=st.integers(min_value=2, max_value=50), seed=st.integers(min_value=0, max_value=10**6))
+def test_radix_selection_equals_sorting_with_ties_to_the_lower_index(S, frac, levels, seed):
+    """The selection used on the GPU (no sort) keeps exactly the positions a stable descending sort keeps, also
+    when many scores are equal (few distinct levels) and for negative values."""
+    g = torch.Generator().manual_seed(seed)
+    scores = (torch.randint(0, levels, (S,), generator=g).float() - levels / 2) * 0.37
+    k = max(1, min(S, int(S * frac)))
+    kept = _radix_select_keep(scores.tolist(), k)
+    order = sorted(range(S), key=lambda i: (-float(scores[i]), i))[:k]
+    assert kept == sorted(order)
+    # (torch.topk, which the eager definition uses, leaves the order among equal scores unspecified; without ties
+    # the two agree)
+    distinct = torch.randperm(S, generator=g).float() * 0.01 - 1.0
+    idx, _, _ = eager.mod_route(distinct.unsqueeze(0), k)
+    assert idx[0].tolist() == _radix_select_keep(distinct.tolist(), k)
+
+
+@settings(max_examples=25, deadline=None)
+@given(m=st.sampled_from([8, 16, 24]), ratio=st.sampled_from([1.25, 2.0, 3.5]), tall=st.booleans(),
+       seed=st.integers(min_value=0, max_value=10**6))
+def test_newton_schulz_on_the_short_side_is_the_same_iteration(m, ratio, tall, seed):
+    """The identity behind the short-side form: with W = P - 1.5 I and V = Q - c I (c = 1.5^k),
+    W' = W (W (W + 3 I) + 2.25 I), V' = W' V + 1.5 V + c W' and Y_5 = V Y + c Y reproduce five steps of
+    Y <- 1.5 Y - 0.5 Y Y^T Y exactly (fp64 here)."""
+    torch.manual_seed(seed)
+    n = int(m * ratio)
+    Y0 = torch.randn(m, n, dtype=torch.float64)
+    if tall:
+        Y0 = Y0.t().contiguous()
+    ref = eager.newton_schulz(Y0, 5)
+    Y = Y0 / (Y0.norm() + 1e-7)
+    A = Y if not tall else Y.t()                     # iterate on the short side: A is (short, long)
+    I = torch.eye(A.shape[0], dtype=torch.float64)
+    W = -0.5 * (A @ A.t())
+    V, c = W.clone(), 1.5
+    for _ in range(4):
+        W = W @ (W @ (W + 3.0 * I) + 2.25 * I)
+        V = W @ V + 1.5 * V + c * W
+        c *= 1.5
+    out = V @ A + c * A
+    out = out if not tall else out.t()
+    assert torch.allclose(out, ref, rtol=1e-9, atol=1e-11)
