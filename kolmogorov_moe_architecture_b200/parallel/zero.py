@@ -217,11 +217,20 @@ class ShardedDataParallel:
         if not self._landing:
             return
         from ..ops import cuda_ops
+        # A parameter held by more than one module (tied embedding / output head) gets gradient from several nodes
+        # of the graph: it must go through autograd's accumulation, which calls the hooks once with the sum.  A
+        # direct write by the first op would mark it ready before the later contributions exist.
+        uses: Dict[int, int] = {}
+        for m in self.model.modules():
+            for q in m._parameters.values():
+                if q is not None:
+                    uses[id(q)] = uses.get(id(q), 0) + 1
         for (n, p) in self.named:
             self._views[id(p)] = p.grad
             p.grad = None
             p.register_post_accumulate_grad_hook(self._land)
-            cuda_ops.register_grad_sink(p, self._views[id(p)], self._sink_commit)
+            if uses.get(id(p), 1) == 1:
+                cuda_ops.register_grad_sink(p, self._views[id(p)], self._sink_commit)
 
     def _land(self, p) -> None:
         v = self._views[id(p)]
