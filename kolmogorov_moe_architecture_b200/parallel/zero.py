@@ -220,16 +220,12 @@ class ShardedDataParallel:
         # A parameter held by more than one module (tied embedding / output head) gets gradient from several nodes
         # of the graph: it must go through autograd's accumulation, which calls the hooks once with the sum.  A
         # direct write by the first op would mark it ready before the later contributions exist.
-        uses: Dict[int, int] = {}
-        for m in self.model.modules():
-            for q in m._parameters.values():
-                if q is not None:
-                    uses[id(q)] = uses.get(id(q), 0) + 1
+        shared = shared_parameter_ids(self.model)
         for (n, p) in self.named:
             self._views[id(p)] = p.grad
             p.grad = None
             p.register_post_accumulate_grad_hook(self._land)
-            if uses.get(id(p), 1) == 1:
+            if id(p) not in shared:
                 cuda_ops.register_grad_sink(p, self._views[id(p)], self._sink_commit)
 
     def _land(self, p) -> None:
@@ -486,6 +482,16 @@ class ShardedDataParallel:
             self.adamw.load_state_dict(sd["adamw"])
         if self.muon is not None and sd.get("muon") is not None:
             self.muon.load_state_dict(sd["muon"])
+
+
+def shared_parameter_ids(model: torch.nn.Module) -> set:
+    """``id`` of every parameter that more than one module of ``model`` holds (tied weights)."""
+    uses: Dict[int, int] = {}
+    for m in model.modules():
+        for q in m._parameters.values():
+            if q is not None:
+                uses[id(q)] = uses.get(id(q), 0) + 1
+    return {k for k, c in uses.items() if c > 1}
 
 
 class _PoolOptimizer:

@@ -204,3 +204,19 @@ def test_routing_mamba_batched_pass_equals_one_pass_per_expert():
     a, b = res[False], res[True]
     assert torch.allclose(a[0], b[0], atol=1e-5) and torch.allclose(a[1], b[1], atol=1e-5)
     assert set(a[2]) == set(b[2]) and all(torch.allclose(a[2][n], b[2][n], atol=1e-5) for n in a[2])
+
+
+def test_tied_parameters_are_found_for_the_gradient_landing():
+    """The embedding is tied to the first output head by default; the data-parallel plan must know, because such a
+    tensor gets gradient from two nodes of the graph and may not be marked ready by the first one."""
+    from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig, MoETransformer
+    from kolmogorov_moe_architecture_b200.parallel.zero import shared_parameter_ids
+    cfg = AdvancedMoEConfig(vocab_size=256, d_model=64, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=16, d_ff=128,
+                            d_ff_expert=64, n_experts=4, moe_layers=(1,), mamba_layers=(), max_seq_len=32,
+                            n_pred_tokens=2, aux_loss_weights=(1.0, 0.5))
+    model = MoETransformer(cfg, verbose=False)
+    shared = shared_parameter_ids(model)
+    names = [n for n, p in model.named_parameters() if id(p) in shared]
+    assert names == ["token_embedding.embedding.weight"]
+    assert model.lm_heads[0].weight is model.token_embedding.embedding.weight
+    assert id(model.lm_heads[1].weight) not in shared
