@@ -220,3 +220,29 @@ def test_tied_parameters_are_found_for_the_gradient_landing():
     assert names == ["token_embedding.embedding.weight"]
     assert model.lm_heads[0].weight is model.token_embedding.embedding.weight
     assert id(model.lm_heads[1].weight) not in shared
+
+
+def test_tied_embedding_gets_no_direct_gradient_destination():
+    """The gradient-landing set-up of the data-parallel plan (exercised here with a stand-in device type, no GPU
+    involved) registers a direct destination for every tensor except the tied embedding / first head."""
+    import types
+    from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig, MoETransformer
+    from kolmogorov_moe_architecture_b200.ops import cuda_ops
+    from kolmogorov_moe_architecture_b200.parallel.zero import ShardedDataParallel
+    cfg = AdvancedMoEConfig(vocab_size=256, d_model=64, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=16, d_ff=128,
+                            d_ff_expert=64, n_experts=4, moe_layers=(1,), mamba_layers=(), max_seq_len=32,
+                            n_pred_tokens=2, aux_loss_weights=(1.0, 0.5))
+    model = MoETransformer(cfg, verbose=False)
+    dp = ShardedDataParallel(model)
+    saved = dict(cuda_ops._GRAD_SINKS)
+    try:
+        cuda_ops._GRAD_SINKS.clear()
+        dp.device = types.SimpleNamespace(type="cuda")
+        dp._setup_grad_landing()
+        tied = model.token_embedding.embedding.weight
+        assert dp._landing and tied.data_ptr() not in cuda_ops._GRAD_SINKS
+        assert len(cuda_ops._GRAD_SINKS) == len(dp.named) - 1
+        assert all(p.grad is None for _, p in dp.named)
+    finally:
+        cuda_ops._GRAD_SINKS.clear()
+        cuda_ops._GRAD_SINKS.update(saved)
