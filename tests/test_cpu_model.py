@@ -246,3 +246,26 @@ def test_tied_embedding_gets_no_direct_gradient_destination():
     finally:
         cuda_ops._GRAD_SINKS.clear()
         cuda_ops._GRAD_SINKS.update(saved)
+
+
+def test_fused_op_entry_points_have_the_same_meaning_on_the_host():
+    """``ops.linear_multi``, ``ops.mod_score_gather`` and ``ops.mod_bce`` fall back to plain PyTorch here; the
+    definitions they fall back to are the ones the GPU kernels are tested against."""
+    import torch.nn.functional as F
+    from kolmogorov_moe_architecture_b200 import ops
+    from kolmogorov_moe_architecture_b200.ops import eager
+    torch.manual_seed(0)
+    x = torch.randn(2, 10, 16)
+    ws = [torch.randn(n, 16) for n in (16, 8, 8)]
+    for y, w in zip(ops.linear_multi(x, ws), ws):
+        assert torch.allclose(y, F.linear(x, w))
+    w = torch.randn(1, 16)
+    picked, idx, wts, logits = ops.mod_score_gather(x, w, 7)
+    ref_logits = F.linear(x, w).squeeze(-1)
+    ref_idx, ref_w, _ = eager.mod_route(ref_logits, 7)
+    assert torch.equal(idx, ref_idx) and torch.allclose(wts, ref_w) and torch.allclose(logits, ref_logits)
+    assert torch.equal(picked, eager.mod_gather(x, ref_idx))
+    assert (idx[:, 1:] > idx[:, :-1]).all() and torch.allclose(wts.sum(-1), torch.ones(2))
+    aux = torch.randn(2, 10)
+    tgt = torch.zeros(2, 10).scatter_(1, idx, 1.0)
+    assert torch.allclose(ops.mod_bce(aux, idx), F.binary_cross_entropy_with_logits(aux, tgt, reduction="mean"))
