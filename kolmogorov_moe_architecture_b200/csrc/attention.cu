@@ -1320,7 +1320,7 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   // K is held until the dQ MMAs of its step: a third stage lets the load of step j + 1 start a whole step ahead
   uint8_t* sK = sdO + B2_TILE_BYTES;            // 3 stages
   uint8_t* sV = sK + 3 * B2_TILE_BYTES;         // 2 stages
-  __shared__ uint64_t qdo_full, k_full[3], v_full[2], k_empty[3], v_empty[2], s_full, s_free, dp_full[2], ds_full, dq_full;
+  __shared__ uint64_t qdo_full, k_full[3], v_full[2], k_empty[3], v_empty[2], s_full, s_free, dp_full[2], ds_full[2], dq_full;
   __shared__ uint32_t tmem_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1336,8 +1336,10 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(&qdo_full, 1);
     for (int i = 0; i < 3; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); mbar_init(&dp_full[i], 1); }
-    mbar_init(&s_full, 1); mbar_init(&s_free, 256); mbar_init(&ds_full, 256); mbar_init(&dq_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); mbar_init(&dp_full[i], 1); mbar_init(&ds_full[i], 256);
+    }
+    mbar_init(&s_full, 1); mbar_init(&s_free, 256); mbar_init(&dq_full, 1);
     mbar_fence_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmdO); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
   }
@@ -1407,7 +1409,9 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           umma_commit(&dp_full[nx]);
           umma_commit(&v_empty[nx]);
         }
-        if (!mbar_wait(&ds_full, j & 1)) { atomicExch(a.status, 56); goto teardown; }
+        // one barrier per dP buffer: a thread may finish dS(j + 1) (it needs only s_free of step j, not this
+        // step's dQ MMAs) before a slower thread has arrived for dS(j), and the two must not share a phase
+        if (!mbar_wait(&ds_full[st], (j >> 1) & 1)) { atomicExch(a.status, 56); goto teardown; }
         tc_fence_after();
         // dQ += dS K_j with dS (128 queries x 128 keys, packed bf16) in the step's dP buffer: keys 0-63 in its
         // first 32 columns, keys 64-127 in the 32 columns from column 64
@@ -1485,7 +1489,7 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&ds_full);
+      mbar_arrive(&ds_full[j & 1]);
     }
     if (nblk > 0) {
       if (!mbar_wait(&dq_full, 0)) { if (lane == 0) atomicExch(a.status, 59); goto teardown; }
