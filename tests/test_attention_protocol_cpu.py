@@ -1,7 +1,7 @@
-"""Host model of the barrier protocols of the head_dim-128 attention backward kernels.
+"""Host model of the barrier protocols of the head_dim-128 attention kernels.
 
-The kernels (csrc/attention.cu: ``attn_bwd_dq2_kernel``, ``attn_bwd_dkv2_kernel``) are warp-specialised: a TMA
-producer, a single-thread MMA issuer and two softmax warpgroups hand shared-memory stages and tensor-memory regions
+The kernels (csrc/attention.cu: ``attn_fwd2_kernel``, ``attn_bwd_dq2_kernel``, ``attn_bwd_dkv2_kernel``) are warp-specialised: a TMA
+producer, a single-thread MMA issuer and eight softmax warps hand shared-memory stages and tensor-memory regions
 to one another through mbarriers that are waited on by phase parity.  This file restates each role's sequence of
 waits, arrivals, loads and MMAs, runs the roles under randomly chosen interleavings (loads and MMAs complete
 asynchronously, MMAs in issue order) and checks for every step count that
@@ -17,6 +17,8 @@ PyTorch (tests/test_gpu_ops.py).
 import random
 
 import pytest
+
+WARPS = range(8)      # softmax warps: warp w owns the 32 rows of quarter w % 4 in column half w // 4
 
 
 class Bar:
@@ -105,9 +107,9 @@ def run_dq2(nblk, seed, ds_barriers=2):
     qdo = Bar(1)
     k_full, k_empty = [Bar(1) for _ in range(3)], [Bar(1) for _ in range(3)]
     v_full, v_empty = [Bar(1) for _ in range(2)], [Bar(1) for _ in range(2)]
-    s_full, s_free, dq_full = Bar(1), Bar(2), Bar(1)
+    s_full, s_free, dq_full = Bar(1), Bar(8), Bar(1)
     dp_full = [Bar(1), Bar(1)]
-    ds_full = [Bar(2) for _ in range(ds_barriers)]
+    ds_full = [Bar(8) for _ in range(ds_barriers)]
     NB = ds_barriers
 
     def producer():
@@ -125,7 +127,7 @@ def run_dq2(nblk, seed, ds_barriers=2):
         m.mma([("QdO", ("QdO", 0)), (("K", 0), ("K", 0))], [("S", ("S", 0))])
         m.commit(s_full)
         yield ("wait", v_full[0], 0)
-        m.mma([("QdO", ("QdO", 0)), (("V", 0), ("V", 0))], [(("dP", 0, h), ("dP", 0)) for h in (0, 1)])
+        m.mma([("QdO", ("QdO", 0)), (("V", 0), ("V", 0))], [(("dP", 0, w), ("dP", 0)) for w in WARPS])
         m.commit(dp_full[0], v_empty[0])
         for j in range(nblk):
             st, nx, ks, kn = j & 1, (j & 1) ^ 1, j % 3, (j + 1) % 3
@@ -135,14 +137,14 @@ def run_dq2(nblk, seed, ds_barriers=2):
                 yield ("wait", s_free, j & 1)
                 m.mma([(("K", kn), ("K", j + 1))], [("S", ("S", j + 1))])
                 m.commit(s_full)
-                m.mma([(("V", nx), ("V", j + 1))], [(("dP", nx, h), ("dP", j + 1)) for h in (0, 1)])
+                m.mma([(("V", nx), ("V", j + 1))], [(("dP", nx, w), ("dP", j + 1)) for w in WARPS])
                 m.commit(dp_full[nx], v_empty[nx])
             yield ("wait", ds_full[j % NB], (j // NB) & 1)
-            m.mma([(("dP", st, 0), ("dS", j)), (("dP", st, 1), ("dS", j)), (("K", ks), ("K", j))], [("dQ", ("dQ", j))])
+            m.mma([(("dP", st, w), ("dS", j)) for w in WARPS] + [(("K", ks), ("K", j))], [("dQ", ("dQ", j))])
             m.commit(k_empty[ks])
         m.commit(dq_full)
 
-    def softmax(h):                                   # warpgroup h owns column half h of every accumulator
+    def softmax(h):                                   # warp h owns its rows and column half of every accumulator
         for j in range(nblk):
             yield ("wait", s_full, j & 1)
             m.read("S", ("S", j))
@@ -156,7 +158,7 @@ def run_dq2(nblk, seed, ds_barriers=2):
         yield ("wait", dq_full, 0)
         m.read("dQ", ("dQ", nblk - 1))
 
-    m.run([producer(), issuer(), softmax(0), softmax(1)])
+    m.run([producer(), issuer()] + [softmax(w) for w in WARPS])
 
 
 def run_dkv2(niter, seed, q_stages=2):
@@ -166,7 +168,7 @@ def run_dkv2(niter, seed, q_stages=2):
     kv = Bar(1)
     q_full, q_empty, stat_full = ([Bar(1) for _ in range(NQ)] for _ in range(3))
     do_full, do_empty = [Bar(1), Bar(1)], [Bar(1), Bar(1)]
-    st_full, dpt_full, p_full, ds_full, acc_full = Bar(1), Bar(1), Bar(2), Bar(2), Bar(1)
+    st_full, dpt_full, p_full, ds_full, acc_full = Bar(1), Bar(1), Bar(8), Bar(8), Bar(1)
 
     def producer():
         m.load("KV", ("KV", 0), kv)
@@ -182,30 +184,30 @@ def run_dkv2(niter, seed, q_stages=2):
     def issuer():
         yield ("wait", kv, 0)
         yield ("wait", q_full[0], 0)
-        m.mma([(("Q", 0), ("Q", 0))], [(("ST", h), ("ST", 0)) for h in (0, 1)])
+        m.mma([(("Q", 0), ("Q", 0))], [(("ST", w), ("ST", 0)) for w in WARPS])
         m.commit(st_full)
         yield ("wait", do_full[0], 0)
-        m.mma([(("dO", 0), ("dO", 0))], [(("DPT", h), ("DPT", 0)) for h in (0, 1)])
+        m.mma([(("dO", 0), ("dO", 0))], [(("DPT", w), ("DPT", 0)) for w in WARPS])
         m.commit(dpt_full)
         for it in range(niter):
             qs, qn, os_, on = it % NQ, (it + 1) % NQ, it & 1, (it & 1) ^ 1
             yield ("wait", p_full, it & 1)
-            m.mma([(("ST", 0), ("PT", it)), (("ST", 1), ("PT", it)), (("dO", os_), ("dO", it))], [("dV", ("dV", it))])
+            m.mma([(("ST", w), ("PT", it)) for w in WARPS] + [(("dO", os_), ("dO", it))], [("dV", ("dV", it))])
             m.commit(do_empty[os_])
             if it + 1 < niter:
                 yield ("wait", q_full[qn], ((it + 1) // NQ) & 1)
-                m.mma([(("Q", qn), ("Q", it + 1))], [(("ST", h), ("ST", it + 1)) for h in (0, 1)])
+                m.mma([(("Q", qn), ("Q", it + 1))], [(("ST", w), ("ST", it + 1)) for w in WARPS])
                 m.commit(st_full)
             yield ("wait", ds_full, it & 1)
-            m.mma([(("DPT", 0), ("dST", it)), (("DPT", 1), ("dST", it)), (("Q", qs), ("Q", it))], [("dK", ("dK", it))])
+            m.mma([(("DPT", w), ("dST", it)) for w in WARPS] + [(("Q", qs), ("Q", it))], [("dK", ("dK", it))])
             m.commit(q_empty[qs])
             if it + 1 < niter:
                 yield ("wait", do_full[on], ((it + 1) >> 1) & 1)
-                m.mma([(("dO", on), ("dO", it + 1))], [(("DPT", h), ("DPT", it + 1)) for h in (0, 1)])
+                m.mma([(("dO", on), ("dO", it + 1))], [(("DPT", w), ("DPT", it + 1)) for w in WARPS])
                 m.commit(dpt_full)
         m.commit(acc_full)
 
-    def softmax(h):                                   # warpgroup h owns column half h of S^T and dP^T
+    def softmax(h):                                   # warp h owns its rows and column half of S^T and dP^T
         for it in range(niter):
             qs = it % NQ
             yield ("wait", stat_full[qs], (it // NQ) & 1)
@@ -225,7 +227,77 @@ def run_dkv2(niter, seed, q_stages=2):
         m.read("dV", ("dV", niter - 1))
         m.read("dK", ("dK", niter - 1))
 
-    m.run([producer(), issuer(), softmax(0), softmax(1)])
+    m.run([producer(), issuer()] + [softmax(w) for w in WARPS])
+
+
+def run_fwd2(nb, seed):
+    """Forward, two 128-query tiles per CTA (``attn_fwd2_kernel``).  TMEM: S_0 | S_1 | O_0 | O_1; K and V: 2 stages
+    shared by the tiles.  ``nb[t]`` = key blocks tile t visits (tile 0 may visit fewer).  Warps 4t..4t+3 own tile t."""
+    m = Machine(seed)
+    nblk = max(nb)
+    q_full = Bar(1)
+    k_full, k_empty, v_full, v_empty = ([Bar(1), Bar(1)] for _ in range(4))
+    s_full, pv_done = [Bar(1), Bar(1)], [Bar(1), Bar(1)]
+    p_full = [Bar(4), Bar(4)]
+    tile_warps = lambda t: range(4 * t, 4 * t + 4)
+
+    def producer():
+        m.load("Q", ("Q", 0), q_full)
+        for j in range(nblk):
+            st, par = j & 1, ((j >> 1) & 1) ^ 1
+            yield ("wait", k_empty[st], par)
+            m.load(("K", st), ("K", j), k_full[st])
+            yield ("wait", v_empty[st], par)
+            m.load(("V", st), ("V", j), v_full[st])
+
+    def issue_s(t, j):
+        m.mma([("Q", ("Q", 0)), (("K", j & 1), ("K", j))], [(("S", w), ("S", j)) for w in tile_warps(t)])
+        m.commit(s_full[t])
+
+    def issuer():
+        yield ("wait", q_full, 0)
+        yield ("wait", k_full[0], 0)
+        for t in range(2):
+            if nb[t] > 0:
+                issue_s(t, 0)
+        m.commit(k_empty[0])
+        for j in range(nblk):
+            st = j & 1
+            yield ("wait", v_full[st], (j >> 1) & 1)
+            if j + 1 < nblk:
+                yield ("wait", k_full[(j + 1) & 1], ((j + 1) >> 1) & 1)
+            for t in range(2):
+                if j >= nb[t]:
+                    continue
+                yield ("wait", p_full[t], j & 1)
+                # O_t += P_t V_j: reads the rows the threads rescaled for this step, leaves O(j)
+                reads = [(("S", w), ("P", j)) for w in tile_warps(t)] + [(("V", st), ("V", j))]
+                reads += [(("O", w), ("O scaled", j)) for w in tile_warps(t)] if j > 0 else []
+                m.mma(reads, [(("O", w), ("O", j)) for w in tile_warps(t)])
+                m.commit(pv_done[t])
+                if j + 1 < nb[t]:
+                    issue_s(t, j + 1)
+            if j + 1 < nblk:
+                m.commit(k_empty[(j + 1) & 1])
+            m.commit(v_empty[st])
+
+    def softmax(w):
+        t = w // 4
+        for j in range(nb[t]):
+            yield ("wait", s_full[t], j & 1)
+            m.read(("S", w), ("S", j))
+            yield None
+            if j > 0:                              # rescale of O: PV(j - 1) must be complete, PV(j) not issued
+                m.read(("O", w), ("O", j - 1))
+                m.write(("O", w), ("O scaled", j))
+                yield None
+            m.write(("S", w), ("P", j))
+            p_full[t].arrive()
+        if nb[t] > 0:
+            yield ("wait", pv_done[t], (nb[t] - 1) & 1)
+            m.read(("O", w), ("O", nb[t] - 1))
+
+    m.run([producer(), issuer()] + [softmax(w) for w in WARPS])
 
 
 @pytest.mark.parametrize("nblk", list(range(1, 10)) + [16])
@@ -238,6 +310,15 @@ def test_dq_kernel_protocol_has_no_deadlock_and_no_stale_read(nblk):
 def test_dkv_kernel_protocol_has_no_deadlock_and_no_stale_read(niter):
     for seed in range(40):
         run_dkv2(niter, seed)
+
+
+@pytest.mark.parametrize("nb1", list(range(1, 10)) + [17])
+def test_forward_kernel_protocol_has_no_deadlock_and_no_stale_read(nb1):
+    for nb0 in sorted({max(nb1 - 1, 0), nb1}):     # tile 0 ends one key block earlier, or the sequence end cuts both
+        for seed in range(25):
+            run_fwd2((nb0, nb1), seed)
+    for seed in range(25):                         # the sequence ends inside tile 0: tile 1 has no rows
+        run_fwd2((nb1, 0), seed)
 
 
 def test_one_ds_barrier_for_two_dp_buffers_would_mix_phases():
