@@ -1,18 +1,20 @@
-"""Host model of the barrier protocols of the head_dim-128 attention kernels.
+"""Host model of the barrier protocols of the warp-specialised kernels.
 
-The kernels (csrc/attention.cu: ``attn_fwd2_kernel``, ``attn_bwd_dq2_kernel``, ``attn_bwd_dkv2_kernel``) are warp-specialised: a TMA
-producer, a single-thread MMA issuer and eight softmax warps hand shared-memory stages and tensor-memory regions
-to one another through mbarriers that are waited on by phase parity.  This file restates each role's sequence of
-waits, arrivals, loads and MMAs, runs the roles under randomly chosen interleavings (loads and MMAs complete
+The attention kernels (csrc/attention.cu: ``attn_fwd2_kernel``, ``attn_bwd_dq2_kernel``, ``attn_bwd_dkv2_kernel`` and
+the 64-key-wide ``attn_fwd_kernel``, ``attn_bwd_dq_kernel``, ``attn_bwd_dkv_kernel``) and the persistent GEMMs
+(csrc/gemm_umma.cu: ``umma_gemm_kernel``, ``umma_gemm_pair_kernel``) are warp-specialised: a TMA producer, a
+single-thread MMA issuer and softmax / epilogue warps hand shared-memory stages and tensor-memory regions to one
+another through mbarriers that are waited on by phase parity.  This file restates each role's sequence of waits,
+arrivals, loads and MMAs, runs the roles under randomly chosen interleavings (loads and MMAs complete
 asynchronously, MMAs in issue order) and checks for every step count that
 
 * nothing deadlocks (a parity wait that can never be satisfied would show up as one), and
 * every read sees the data it is meant to see: each write tags its buffer with (what, step), each read asserts
-  the tag - an MMA that overwrites S before the threads have read it, or a load that lands in a stage an MMA
-  still needs, fails the assertion.
+  the tag - an MMA that overwrites S before the threads have read it, a load that lands in a stage an MMA still
+  needs, or a barrier phase completed by arrivals that belong to two different steps, fails the assertion.
 
 It is a model of the protocol, not of the arithmetic; the kernels themselves are tested on the GPU against fp32
-PyTorch (tests/test_gpu_ops.py).
+PyTorch (tests/test_gpu_ops.py, tests/test_gpu_gemm.py).
 """
 import random
 
@@ -300,6 +302,235 @@ def run_fwd2(nb, seed):
     m.run([producer(), issuer()] + [softmax(w) for w in WARPS])
 
 
+# ---------------------------------------------------------------- the 64-key-wide kernels (head_dim 64 path)
+W4 = range(4)         # these kernels have four softmax warps (thread = accumulator row)
+
+
+def run_fwd64(nblk, seed):
+    """``attn_fwd_kernel``: TMEM S x 2 | O; K, V: 2 stages; P goes through one shared-memory panel."""
+    m = Machine(seed)
+    q_full, p_full, pv_full = Bar(1), Bar(4), Bar(1)
+    k_full, k_empty, v_full, v_empty, s_full = ([Bar(1), Bar(1)] for _ in range(5))
+    s_free = [Bar(4), Bar(4)]
+
+    def producer():
+        m.load("Q", ("Q", 0), q_full)
+        for j in range(nblk):
+            st, par = j & 1, ((j >> 1) & 1) ^ 1
+            yield ("wait", k_empty[st], par)
+            m.load(("K", st), ("K", j), k_full[st])
+            yield ("wait", v_empty[st], par)
+            m.load(("V", st), ("V", j), v_full[st])
+
+    def issue_s(j):
+        st = j & 1
+        yield ("wait", k_full[st], (j >> 1) & 1)
+        yield ("wait", s_free[st], ((j >> 1) & 1) ^ 1)
+        m.mma([("Q", ("Q", 0)), (("K", st), ("K", j))], [(("S", st, w), ("S", j)) for w in W4])
+        m.commit(s_full[st], k_empty[st])
+
+    def issuer():
+        yield ("wait", q_full, 0)
+        yield from issue_s(0)
+        for j in range(nblk):
+            if j + 1 < nblk:
+                yield from issue_s(j + 1)
+            st = j & 1
+            yield ("wait", v_full[st], (j >> 1) & 1)
+            yield ("wait", p_full, j & 1)
+            reads = [(("P", w), ("P", j)) for w in W4] + [(("V", st), ("V", j))]
+            reads += [(("O", w), ("O scaled", j)) for w in W4] if j > 0 else []
+            m.mma(reads, [(("O", w), ("O", j)) for w in W4])
+            m.commit(pv_full, v_empty[st])
+
+    def softmax(w):
+        for j in range(nblk):
+            st = j & 1
+            yield ("wait", s_full[st], (j >> 1) & 1)
+            m.read(("S", st, w), ("S", j))
+            s_free[st].arrive()
+            yield None
+            if j > 0:
+                yield ("wait", pv_full, (j - 1) & 1)
+                m.read(("O", w), ("O", j - 1))
+                m.write(("O", w), ("O scaled", j))
+                yield None
+            m.write(("P", w), ("P", j))             # the panel PV(j - 1) read: free since pv_full
+            p_full.arrive()
+        yield ("wait", pv_full, (nblk - 1) & 1)
+        m.read(("O", w), ("O", nblk - 1))
+
+    m.run([producer(), issuer()] + [softmax(w) for w in W4])
+
+
+def run_dq64(nblk, seed):
+    """``attn_bwd_dq_kernel``: TMEM (S | dP) x 2 | dQ; K, V: 2 stages; dS goes through one shared-memory panel
+    that ``ds_free`` hands back after the step's dQ MMAs."""
+    m = Machine(seed)
+    qdo, ds_full, ds_free, dq_full = Bar(1), Bar(4), Bar(1), Bar(1)
+    k_full, k_empty, v_full, v_empty, sdp_full = ([Bar(1), Bar(1)] for _ in range(5))
+
+    def producer():
+        m.load("QdO", ("QdO", 0), qdo)
+        for j in range(nblk):
+            st, par = j & 1, ((j >> 1) & 1) ^ 1
+            yield ("wait", k_empty[st], par)
+            m.load(("K", st), ("K", j), k_full[st])
+            yield ("wait", v_empty[st], par)
+            m.load(("V", st), ("V", j), v_full[st])
+
+    def issue_sdp(j):
+        st, ph = j & 1, (j >> 1) & 1
+        yield ("wait", k_full[st], ph)
+        yield ("wait", v_full[st], ph)
+        m.mma([("QdO", ("QdO", 0)), (("K", st), ("K", j)), (("V", st), ("V", j))],
+              [(("SdP", st, w), ("SdP", j)) for w in W4])
+        m.commit(sdp_full[st], v_empty[st])
+
+    def issuer():
+        yield ("wait", qdo, 0)
+        yield from issue_sdp(0)
+        for j in range(nblk):
+            st = j & 1
+            if j + 1 < nblk:
+                yield from issue_sdp(j + 1)
+            yield ("wait", ds_full, j & 1)
+            m.mma([(("dS", w), ("dS", j)) for w in W4] + [(("K", st), ("K", j))], [("dQ", ("dQ", j))])
+            m.commit(ds_free, k_empty[st])
+        m.commit(dq_full)
+
+    def softmax(w):
+        for j in range(nblk):
+            yield ("wait", sdp_full[j & 1], (j >> 1) & 1)
+            m.read(("SdP", j & 1, w), ("SdP", j))
+            yield None
+            yield ("wait", ds_free, (j & 1) ^ 1)
+            m.write(("dS", w), ("dS", j))
+            ds_full.arrive()
+        yield ("wait", dq_full, 0)
+        m.read("dQ", ("dQ", nblk - 1))
+
+    m.run([producer(), issuer()] + [softmax(w) for w in W4])
+
+
+def run_dkv64(niter, seed):
+    """``attn_bwd_dkv_kernel``: TMEM (S^T | dP^T) x 2 | dV | dK; Q / dO: 2 stages; P^T and dS^T go through
+    shared-memory panels that ``pds_free`` hands back; the threads stage the row statistics themselves between
+    two CTA-local barriers of the four warps."""
+    m = Machine(seed)
+    kv, pds_full, pds_free, acc_full = Bar(1), Bar(4), Bar(1), Bar(1)
+    q_full, q_empty, st_full = ([Bar(1), Bar(1)] for _ in range(3))
+    sync = [Bar(4) for _ in range(2 * niter)]          # bar.sync 1, 128: one single-use barrier per use
+
+    def producer():
+        m.load("KV", ("KV", 0), kv)
+        for it in range(niter):
+            st = it & 1
+            yield ("wait", q_empty[st], ((it >> 1) & 1) ^ 1)
+            m.load(("QdO", st), ("QdO", it), q_full[st])
+
+    def issue_st(it):
+        st = it & 1
+        yield ("wait", q_full[st], (it >> 1) & 1)
+        m.mma([("KV", ("KV", 0)), (("QdO", st), ("QdO", it))], [(("ST", st, w), ("ST", it)) for w in W4])
+        m.commit(st_full[st])
+
+    def issuer():
+        yield ("wait", kv, 0)
+        yield from issue_st(0)
+        for it in range(niter):
+            st = it & 1
+            if it + 1 < niter:
+                yield from issue_st(it + 1)
+            yield ("wait", pds_full, it & 1)
+            m.mma([(("PdS", w), ("PdS", it)) for w in W4] + [(("QdO", st), ("QdO", it))], [("dKV", ("dKV", it))])
+            m.commit(pds_free, q_empty[st])
+        m.commit(acc_full)
+
+    def softmax(w):
+        for it in range(niter):
+            yield ("wait", st_full[it & 1], (it >> 1) & 1)
+            sync[2 * it].arrive()
+            yield ("wait", sync[2 * it], 0)
+            if w < 2:                                  # rows 0-63 stage the statistics of the step's 64 queries
+                m.write(("stat", w), ("stat", it))
+            sync[2 * it + 1].arrive()
+            yield ("wait", sync[2 * it + 1], 0)
+            m.read(("ST", it & 1, w), ("ST", it))
+            m.read(("stat", 0), ("stat", it))
+            yield None
+            m.read(("stat", 1), ("stat", it))
+            yield ("wait", pds_free, (it & 1) ^ 1)
+            m.write(("PdS", w), ("PdS", it))
+            pds_full.arrive()
+        yield ("wait", acc_full, 0)
+        m.read("dKV", ("dKV", niter - 1))
+
+    m.run([producer(), issuer()] + [softmax(w) for w in W4])
+
+
+# ---------------------------------------------------------------- persistent GEMMs (csrc/gemm_umma.cu)
+def run_gemm(k_blocks, stages, seed, ctas=1):
+    """``umma_gemm_kernel`` (ctas=1) and ``umma_gemm_pair_kernel`` (ctas=2) for the tiles one CTA (pair) works
+    through: ``k_blocks[i]`` reduction blocks for tile i (0 = a group without rows in a batched product: the
+    epilogue writes zeros / the addend and the issuer arrives by itself).  Ring of ``stages`` shared-memory
+    stages, two accumulators, four epilogue warps per CTA.  In the pair the ``full`` and ``tmem_empty`` barriers
+    live in the leader, ``empty`` and ``tmem_full`` exist in both CTAs and get the leader's commits."""
+    m = Machine(seed)
+    C = range(ctas)
+    full = [Bar(1 + ctas) for _ in range(stages)]         # the leader's expect_tx + one load group per CTA
+    empty = [[Bar(1) for _ in range(stages)] for _ in C]
+    tmem_full = [[Bar(1), Bar(1)] for _ in C]
+    tmem_empty = [Bar(4 * ctas), Bar(4 * ctas)]
+
+    def producer(c):
+        s, ph, n = 0, 0, 0
+        for i, kb_n in enumerate(k_blocks):
+            for kb in range(kb_n):
+                yield ("wait", empty[c][s], ph ^ 1)
+                if c == 0:
+                    full[s].arrive()                      # arrive.expect_tx
+                m.load(("stage", c, s), ("AB", n), full[s])
+                n += 1
+                s += 1
+                if s == stages:
+                    s, ph = 0, ph ^ 1
+
+    def issuer():
+        s, ph, n = 0, 0, 0
+        for i, kb_n in enumerate(k_blocks):
+            acc, acc_ph = i & 1, (i >> 1) & 1
+            yield ("wait", tmem_empty[acc], acc_ph ^ 1)
+            for kb in range(kb_n):
+                yield ("wait", full[s], ph)
+                reads = [(("stage", c, s), ("AB", n)) for c in C]
+                if kb > 0:
+                    reads += [(("acc", c, acc, w), ("acc", i, kb - 1)) for c in C for w in W4]
+                m.mma(reads, [(("acc", c, acc, w), ("acc", i, kb)) for c in C for w in W4])
+                m.commit(*[empty[c][s] for c in C])
+                n += 1
+                s += 1
+                if s == stages:
+                    s, ph = 0, ph ^ 1
+            if kb_n > 0:
+                m.commit(*[tmem_full[c][acc] for c in C])
+            else:
+                for c in C:
+                    tmem_full[c][acc].arrive()
+
+    def epilogue(c, w):
+        for i, kb_n in enumerate(k_blocks):
+            acc, acc_ph = i & 1, (i >> 1) & 1
+            yield ("wait", tmem_full[c][acc], acc_ph)
+            if kb_n > 0:
+                m.read(("acc", c, acc, w), ("acc", i, kb_n - 1))
+                yield None
+                m.read(("acc", c, acc, w), ("acc", i, kb_n - 1))      # later slabs of the same tile
+            tmem_empty[acc].arrive()
+
+    m.run([producer(c) for c in C] + [issuer()] + [epilogue(c, w) for c in C for w in W4])
+
+
 @pytest.mark.parametrize("nblk", list(range(1, 10)) + [16])
 def test_dq_kernel_protocol_has_no_deadlock_and_no_stale_read(nblk):
     for seed in range(40):
@@ -319,6 +550,25 @@ def test_forward_kernel_protocol_has_no_deadlock_and_no_stale_read(nb1):
             run_fwd2((nb0, nb1), seed)
     for seed in range(25):                         # the sequence ends inside tile 0: tile 1 has no rows
         run_fwd2((nb1, 0), seed)
+
+
+@pytest.mark.parametrize("n", list(range(1, 8)) + [12, 33])
+def test_the_64_wide_kernels_have_no_deadlock_and_no_stale_read(n):
+    for seed in range(25):
+        run_fwd64(n, seed)
+        run_dq64(n, seed)
+        run_dkv64(n, seed)
+
+
+@pytest.mark.parametrize("ctas", [1, 2])
+@pytest.mark.parametrize("stages", [2, 4, 6])
+def test_gemm_ring_and_accumulator_hand_off(ctas, stages):
+    rng = random.Random(stages * 10 + ctas)
+    shapes = [[1], [3], [1, 1, 1, 1, 1], [2, 0, 5, 0, 0, 1], [0], [0, 0, 0], [32, 2, 32], [7] * 9]
+    shapes += [[rng.choice([0, 1, 2, 3, 9]) for _ in range(rng.randint(1, 8))] for _ in range(6)]
+    for kbs in shapes:
+        for seed in range(12):
+            run_gemm(kbs, stages, seed, ctas=ctas)
 
 
 def test_one_ds_barrier_for_two_dp_buffers_would_mix_phases():
