@@ -3,7 +3,9 @@
 Every function here takes the CUDA kernel path for CUDA tensors and the
 plain-PyTorch definition in :mod:`.eager` for CPU tensors.  On a CUDA tensor
 the compiled extension is mandatory: a missing ``_C`` library raises instead
-of silently falling back, unless ``KMOE_ALLOW_EAGER=1`` is set.
+of silently falling back, unless ``KMOE_ALLOW_EAGER=1`` is set.  With ``KMOE_CHECK_INPUTS=1`` the data-dependent
+inputs (expert ids, labels, kept positions, document starts) are validated before
+the launch (:mod:`.checks`).
 """
 from __future__ import annotations
 
@@ -11,7 +13,7 @@ import os
 
 import torch
 
-from . import eager
+from . import checks, eager
 from .loader import ext_available, load_ext, require_ext  # noqa: F401
 
 
@@ -86,6 +88,8 @@ def swiglu(gate, up):
 def attention(q, k, v, causal=True, attn_mask=None, dropout_p=0.0, training=False, doc_start=None):
     """``doc_start`` (B, S): packed-document boundaries (see ``eager.doc_start_from_ids``); on CUDA the flash
     kernels apply them directly, elsewhere they become an additive mask."""
+    if doc_start is not None and checks.enabled():
+        checks.doc_start(doc_start)
     if attn_mask is None and not (dropout_p > 0.0 and training) and _use_cuda(q):
         from . import cuda_ops
         return cuda_ops.attention(q, k, v, causal, doc_start)
@@ -112,6 +116,10 @@ def selective_scan(u, delta, A, Bm, Cm, D, z, delta_bias, delta_softplus=True):
 def grouped_swiglu(x, w1, w2, w3, idx, weights, keep=None, moe_dtype="bf16"):
     if x.shape[0] == 0:
         return x * 0
+    if checks.enabled():
+        checks.expert_indices(idx, w1.shape[0], top_k_distinct=False)
+        checks.routing_weights(weights)
+        checks.keep_mask(keep, idx)
     if _use_cuda(x):
         from . import cuda_ops
         return cuda_ops.grouped_swiglu(x, w1, w2, w3, idx, weights, keep, moe_dtype)
@@ -119,6 +127,8 @@ def grouped_swiglu(x, w1, w2, w3, idx, weights, keep=None, moe_dtype="bf16"):
 
 
 def mtp_cross_entropy(hidden, head_weights, labels, weights, ignore_index=-100):
+    if checks.enabled():
+        checks.labels(labels, head_weights[0].shape[0], ignore_index)
     if _use_cuda(hidden):
         from . import cuda_ops
         return cuda_ops.mtp_cross_entropy(hidden, head_weights, labels, weights, ignore_index)
@@ -162,6 +172,8 @@ def mod_score_gather(h, w, k):
 
 def mod_bce(aux_logits, idx):
     """Mean binary cross-entropy of (B, S) logits against "position is among the kept indices idx (B, k)"."""
+    if checks.enabled():
+        checks.kept_rows(idx, aux_logits.shape[1])
     if _use_cuda(aux_logits) and aux_logits.dtype == torch.bfloat16 and aux_logits.numel() > 0:
         from . import cuda_ops
         return cuda_ops.mod_bce(aux_logits, idx)
@@ -171,6 +183,8 @@ def mod_bce(aux_logits, idx):
 
 
 def mod_gather(h, idx):
+    if checks.enabled():
+        checks.kept_rows(idx, h.shape[1])
     if _use_cuda(h):
         from . import cuda_ops
         return cuda_ops.mod_gather(h, idx)
@@ -178,6 +192,9 @@ def mod_gather(h, idx):
 
 
 def mod_combine(res, proc, w, idx):
+    if checks.enabled():
+        checks.kept_rows(idx, res.shape[1])
+        checks.routing_weights(w, "mixture-of-depths weights")
     if _use_cuda(res):
         from . import cuda_ops
         return cuda_ops.mod_combine(res, proc, w, idx)
@@ -197,6 +214,8 @@ moe_aux_loss = eager.moe_aux_loss
 
 def capacity_keep_mask(idx, n_experts, capacity):
     """Token-choice capacity with drops: the first ``capacity`` assignments of every expert are kept."""
+    if checks.enabled():
+        checks.index_range(idx, n_experts, "expert index")
     if _use_cuda(idx):
         from . import cuda_ops
         return cuda_ops.capacity_keep_mask(idx, n_experts, capacity)
@@ -213,6 +232,9 @@ def balanced_assign(probs, top_k):
 
 def expert_choice_swiglu(x, w1, w2, w3, wts, tok):
     """Expert-choice expert FFN (x (B, S, d); wts, tok (B, E, C))."""
+    if checks.enabled():
+        checks.distinct_rows(tok, x.shape[1], "expert-choice token index")
+        checks.routing_weights(wts, "expert-choice weights")
     if _use_cuda(x):
         from . import cuda_ops
         return cuda_ops.expert_choice_swiglu(x, w1, w2, w3, wts, tok)

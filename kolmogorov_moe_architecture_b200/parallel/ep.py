@@ -53,6 +53,11 @@ def expert_parallel_ffn(x: torch.Tensor, idx: torch.Tensor, weights: torch.Tenso
                         n_experts: int, group=None, keep: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x (T, d); idx, weights (T, k) with global expert ids; ``local_experts(x, ids, w, keep)``
     evaluates this rank's experts.  Returns (T, d)."""
+    from ..ops import checks
+    if checks.enabled():
+        checks.index_range(idx, n_experts, "expert index")
+        checks.routing_weights(weights)
+        checks.keep_mask(keep, idx)
     ws = dist.get_world_size(group)
     T, d = x.shape
     k = idx.shape[1]

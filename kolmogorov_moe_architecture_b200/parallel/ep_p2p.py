@@ -329,6 +329,11 @@ def expert_parallel_ffn_fused(x, idx, weights, w1, w2, w3, n_experts: int, group
     ``slot_cap``: upper bound on the assignments one rank sends to one expert (the capacity when ``keep``
     enforces one); it sizes the receive slots and the expert-side buffers, which default to the worst case T.
     ``moe_dtype="mxfp8"`` runs the expert GEMMs block-scaled in fp8 (d and f multiples of 128)."""
+    from ..ops import checks
+    if checks.enabled():
+        checks.expert_indices(idx, n_experts)          # distinct per token: a source sends an expert at most T rows
+        checks.routing_weights(weights)
+        checks.keep_mask(keep, idx)
     T, d = x.shape
     cap = None if slot_cap is None else min(int(slot_cap), T)
     buf = get_buffers(T, idx.shape[1], d, n_experts, x.dtype, x.device, group, cap)

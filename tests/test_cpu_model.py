@@ -269,3 +269,32 @@ def test_fused_op_entry_points_have_the_same_meaning_on_the_host():
     aux = torch.randn(2, 10)
     tgt = torch.zeros(2, 10).scatter_(1, idx, 1.0)
     assert torch.allclose(ops.mod_bce(aux, idx), F.binary_cross_entropy_with_logits(aux, tgt, reduction="mean"))
+
+
+@pytest.mark.parametrize("kw", [dict(mamba_moe_mode="moe_ffn"), dict(mamba_moe_mode="routing_mamba"),
+                                dict(moe_routing="expert_choice", mamba_layers=()),
+                                dict(moe_balanced_routing=True, mamba_layers=()),
+                                dict(moe_drop_tokens=True, moe_capacity_factor=1.0, mamba_layers=())])
+def test_input_validation_mode_accepts_what_the_model_itself_produces(kw, monkeypatch):
+    """``KMOE_CHECK_INPUTS=1`` validates every data-dependent kernel input; the model's own routers, the
+    mixture-of-depths selection, the loss labels and packed-document starts must all pass it, and the result must
+    not change."""
+    from kolmogorov_moe_architecture_b200.data import PackedDocs
+    torch.manual_seed(1)
+    m = kmoe.MoETransformer(_tiny(**kw), verbose=False)
+    m.train()
+    ids = torch.randint(0, 200, (2, 32))
+    labels = ids.clone()
+    labels[0, :5] = -100
+    pd = PackedDocs(doc_ids=torch.tensor([[0] * 7 + [1] * 25, [2] * 32]))
+    torch.manual_seed(2)
+    ref = m(ids, labels=labels, attention_mask=pd, return_logits=False)["loss"]
+    monkeypatch.setenv("KMOE_CHECK_INPUTS", "1")
+    torch.manual_seed(2)
+    out = m(ids, labels=labels, attention_mask=pd, return_logits=False)["loss"]
+    out.backward()
+    assert torch.equal(out, ref)
+    bad = labels.clone()
+    bad[1, 3] = 200
+    with pytest.raises(IndexError, match="labels: value 200"):
+        m(ids, labels=bad, return_logits=False)

@@ -2,6 +2,7 @@
 against - checked on generated shapes and values."""
 import math
 
+import pytest
 import torch
 from hypothesis import given, settings, strategies as st
 
@@ -406,3 +407,83 @@ def test_newton_schulz_on_the_short_side_is_the_same_iteration(m, ratio, tall, s
     out = V @ A + c * A
     out = out if not tall else out.t()
     assert torch.allclose(out, ref, rtol=1e-9, atol=1e-11)
+
+
+# ---------------------------------------------------------------- opt-in validation of data-dependent inputs
+def test_input_checks_name_the_first_offending_element(monkeypatch):
+    from kolmogorov_moe_architecture_b200 import ops
+    from kolmogorov_moe_architecture_b200.ops import checks
+    monkeypatch.setenv("KMOE_CHECK_INPUTS", "1")
+    assert checks.enabled()
+    g = torch.Generator().manual_seed(0)
+    T, d, f, E, k = 12, 16, 24, 4, 2
+    x = torch.randn(T, d, generator=g)
+    w1, w2, w3 = torch.randn(E, d, f, generator=g), torch.randn(E, d, f, generator=g), torch.randn(E, f, d, generator=g)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)])
+    wts = torch.softmax(torch.randn(T, k, generator=g), -1)
+    ops.grouped_swiglu(x, w1, w2, w3, idx, wts)                       # valid input passes
+    bad = idx.clone()
+    bad[5, 1] = E
+    with pytest.raises(IndexError, match=r"value 4 at position \(5, 1\) is outside \[0, 4\)"):
+        ops.grouped_swiglu(x, w1, w2, w3, bad, wts)
+    nanw = wts.clone()
+    nanw[3, 0] = float("nan")
+    with pytest.raises(ValueError, match=r"non-finite value at position \(3, 0\)"):
+        ops.grouped_swiglu(x, w1, w2, w3, idx, nanw)
+    with pytest.raises(ValueError, match="keep mask has 5 elements for 24 assignments"):
+        ops.grouped_swiglu(x, w1, w2, w3, idx, wts, keep=torch.ones(5, dtype=torch.bool))
+    dup = idx.clone()
+    dup[7] = 2
+    with pytest.raises(ValueError, match="token 7 is assigned to expert 2 twice"):
+        checks.expert_indices(dup, E)
+    checks.expert_indices(dup, E, top_k_distinct=False)
+
+    # labels of the loss head
+    V, B, S = 32, 2, 9
+    hidden = torch.randn(B, S, d, generator=g)
+    heads = [torch.randn(V, d, generator=g) for _ in range(2)]
+    lab = torch.randint(0, V, (B, S), generator=g)
+    lab[0, 2] = -100
+    ops.mtp_cross_entropy(hidden, heads, lab, [0.7, 0.3])
+    lab[1, 4] = V + 3
+    with pytest.raises(IndexError, match=r"labels: value 35 at position \(1, 4\) is neither -100 nor in \[0, 32\)"):
+        ops.mtp_cross_entropy(hidden, heads, lab, [0.7, 0.3])
+
+    # mixture-of-depths positions: in range and strictly ascending
+    h = torch.randn(B, S, d, generator=g)
+    kept = torch.tensor([[0, 3, 4, 8], [1, 2, 5, 6]])
+    ops.mod_gather(h, kept)
+    with pytest.raises(IndexError, match=r"value 9 at position \(0, 3\) is outside \[0, 9\)"):
+        ops.mod_gather(h, torch.tensor([[0, 3, 4, 9], [1, 2, 5, 6]]))
+    with pytest.raises(ValueError, match=r"not strictly ascending at position \(1, 1\) \(5 is followed by 5\)"):
+        ops.mod_gather(h, torch.tensor([[0, 3, 4, 8], [1, 5, 5, 6]]))
+    with pytest.raises(ValueError, match="expected an integer tensor"):
+        checks.kept_rows(kept.float(), S)
+
+    # expert-choice: an expert takes a token at most once
+    tok = torch.tensor([[[0, 1, 2], [3, 4, 5]], [[6, 7, 8], [1, 1, 0]]])
+    with pytest.raises(ValueError, match=r"row 1 is selected twice in group \(1, 1\)"):
+        checks.distinct_rows(tok, S, "expert-choice token index")
+
+    # packed documents
+    ds = torch.tensor([[0, 0, 0, 3, 3, 5], [0, 1, 1, 1, 4, 4]])
+    checks.doc_start(ds)
+    with pytest.raises(IndexError, match=r"value 4 at position \(0, 3\) is outside \[0, 3\]"):
+        checks.doc_start(torch.tensor([[0, 0, 0, 4, 4, 5]]))
+    with pytest.raises(ValueError, match=r"decreases after position \(0, 3\) \(3 -> 2\)"):
+        checks.doc_start(torch.tensor([[0, 0, 0, 3, 2, 5]]))
+    q = torch.randn(1, 6, 2, 8, generator=g)
+    with pytest.raises(ValueError, match="decreases"):
+        ops.attention(q, q, q, doc_start=torch.tensor([[0, 0, 0, 3, 2, 5]]))
+
+
+def test_input_checks_are_off_by_default(monkeypatch):
+    from kolmogorov_moe_architecture_b200 import ops
+    from kolmogorov_moe_architecture_b200.ops import checks
+    monkeypatch.delenv("KMOE_CHECK_INPUTS", raising=False)
+    assert not checks.enabled()
+    # no validation pass runs: a float index tensor, which the checks reject, reaches the op itself
+    h = torch.randn(1, 4, 8)
+    with pytest.raises(Exception) as e:
+        ops.mod_gather(h, torch.tensor([[0.0, 1.0]]))
+    assert "expected an integer tensor" not in str(e.value)
