@@ -158,10 +158,12 @@ class PackedDocs:
             self.doc_start = doc_start
         else:
             # start positions from outside: a start is neither negative nor after its own position (the
-            # attention kernels index key blocks with it)
+            # attention kernels index key blocks with it), and starts never move backwards along a sequence
+            # (the kernels skip the key blocks before the start of a tile's first query for the whole tile)
             ds = doc_start.to(torch.int32)
             pos = torch.arange(ds.shape[-1], device=ds.device, dtype=torch.int32)
-            self.doc_start = torch.minimum(ds.clamp(min=0), pos.expand_as(ds))
+            ds = torch.minimum(ds.clamp(min=0), pos.expand_as(ds))
+            self.doc_start = torch.cummax(ds, dim=-1).values
 
     @property
     def device(self):

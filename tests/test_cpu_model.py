@@ -177,7 +177,9 @@ def test_packed_docs_sanitises_start_positions_given_from_outside():
     from kolmogorov_moe_architecture_b200.data import PackedDocs
     ds = torch.tensor([[0, 0, 5, -3, 4, 9]])
     p = PackedDocs(doc_start=ds)
-    assert p.doc_start.dtype == torch.int32 and p.doc_start.tolist() == [[0, 0, 2, 0, 4, 5]]
+    assert p.doc_start.dtype == torch.int32 and p.doc_start.tolist() == [[0, 0, 2, 2, 4, 5]]
+    from kolmogorov_moe_architecture_b200.ops import checks
+    checks.doc_start(p.doc_start)                      # what the validation mode demands of document starts
     assert p.to("cpu").doc_start.tolist() == p.doc_start.tolist() and len(p.chunk(1)) == 1
     ids = torch.tensor([[7, 7, 8, 8, 8, 9]])
     assert PackedDocs(doc_ids=ids).doc_start.tolist() == [[0, 0, 2, 2, 2, 5]]
