@@ -95,6 +95,16 @@ class MoETransformer(nn.Module):
     def forward(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
                 position_ids: Optional[torch.Tensor] = None, labels: Optional[torch.Tensor] = None,
                 return_logits: bool = True) -> Dict[str, torch.Tensor]:
+        from ..ops import checks
+        if checks.enabled():       # out-of-range ids would otherwise end in a device-side assertion of the lookup
+            checks.index_range(input_ids, self.config.vocab_size, "input_ids")
+            if labels is not None:
+                checks.labels(labels, self.config.vocab_size)
+            if position_ids is not None:
+                checks.index_range(position_ids, self.config.max_seq_len, "position_ids")
+            elif input_ids.shape[1] > self.config.max_seq_len:
+                raise IndexError(f"sequence length {input_ids.shape[1]} exceeds max_seq_len "
+                                 f"{self.config.max_seq_len} (the rotary tables end there)")
         hidden, aux = self.forward_hidden(input_ids, attention_mask, position_ids)
         if hasattr(attention_mask, "doc_start") or (attention_mask is not None and attention_mask.dim() == 4):
             attention_mask = None                           # attention structure, not a padding mask for the loss

@@ -300,3 +300,13 @@ def test_input_validation_mode_accepts_what_the_model_itself_produces(kw, monkey
     bad[1, 3] = 200
     with pytest.raises(IndexError, match="labels: value 200"):
         m(ids, labels=bad, return_logits=False)
+    with pytest.raises(IndexError, match="labels: value 200"):
+        m(ids, labels=bad)                                  # the path through materialised logits as well
+    toks = ids.clone()
+    toks[0, 9] = 200
+    with pytest.raises(IndexError, match=r"input_ids: value 200 at position \(0, 9\) is outside \[0, 200\)"):
+        m(toks)
+    with pytest.raises(IndexError, match="exceeds max_seq_len 32"):
+        m(torch.zeros(1, 33, dtype=torch.long))
+    with pytest.raises(IndexError, match="position_ids: value 32"):
+        m(ids, position_ids=torch.arange(1, 33).expand(2, 32))
