@@ -66,25 +66,34 @@ class Machine:
         roles = [[r, None] for r in roles]
         for r in roles:
             r[1] = next(r[0], "done")
+        # uneven speeds: every other seed makes some roles, the tensor pipe or the loads very slow or very fast,
+        # so that one warp can run a whole step ahead of another
+        skew = self.rng.random() < 0.5
+        speed = lambda: self.rng.choice([0.02, 0.2, 1.0, 1.0, 5.0, 50.0]) if skew else 1.0
+        w_role = [speed() for _ in roles]
+        w_pipe, w_load = speed(), speed()
         steps = 0
         while True:
             steps += 1
             assert steps < 200000, "model did not terminate"
-            choices = []
+            choices, weights = [], []
             for i, (gen, st) in enumerate(roles):
                 if st == "done":
                     continue
                 if st is None or (st[0] == "wait" and st[1].passed(st[2])):
                     choices.append(("role", i))
+                    weights.append(w_role[i])
             if self.pipe:
                 choices.append(("pipe", 0))
+                weights.append(w_pipe)
             for i in range(len(self.loads)):
                 choices.append(("load", i))
+                weights.append(w_load)
             if not choices:
                 assert all(st == "done" for _, st in roles), \
                     "deadlock: " + str([st for _, st in roles if st != "done"][0][2:])
                 return
-            kind, i = self.rng.choice(choices)
+            kind, i = self.rng.choices(choices, weights)[0]
             if kind == "role":
                 roles[i][1] = next(roles[i][0], "done")
             elif kind == "pipe":
