@@ -266,6 +266,7 @@ class ShardedDataParallel:
         self._chunks: List[List[Tuple[int, int]]] = []
         self._chunk_of: Dict[int, int] = {}
         self._pending: List[int] = []
+        self._ready_seen: set = set()
         self._launched = 0
         self._rs_stream = None
         # measured at 2 GPUs the overlap costs more than the 4 ms it hides, so it is on from 4 ranks
@@ -314,6 +315,15 @@ class ShardedDataParallel:
         g = self._chunk_of.get(id(p))
         if g is None:
             return
+        if id(p) in self._ready_seen:
+            # A group is reduced as soon as its last tensor is complete; a tensor that is completed twice (a
+            # second backward pass without set_sync(False) before it, or a weight that two nodes of the graph
+            # write, the first of them directly into the flat buffer) would let its group go early.
+            name = next((n for n, q in self.named if q is p), "?")
+            raise RuntimeError(f"gradient of {name} was marked complete twice in one step: accumulate "
+                               f"micro-batches under set_sync(False), and keep weights that several modules "
+                               f"use out of the direct gradient destinations")
+        self._ready_seen.add(id(p))
         self._pending[g] -= 1
         while self._launched < len(self._chunks) and self._pending[self._launched] <= 0:
             self._launch_chunk(self._launched)
@@ -455,6 +465,7 @@ class ShardedDataParallel:
         if self._chunks:                                  # re-arm the overlapped reduction for the next backward
             self._sq.zero_()
             self._pending = list(self._group_sizes)
+            self._ready_seen.clear()
             self._launched = 0
 
     def reduce_clip_and_step(self, optimizer=None, max_norm: Optional[float] = 1.0) -> torch.Tensor:

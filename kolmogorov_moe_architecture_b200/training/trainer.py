@@ -67,6 +67,9 @@ class Trainer:
             batch = next(batches)
             ids = batch["input_ids"].to(self.device, non_blocking=True)
             labels = batch["labels"].to(self.device, non_blocking=True)
+            if getattr(self.engine, "dp", None) is not None:
+                # gradients are reduced over the ranks only with the micro-batch that completes the step
+                self.engine.dp.set_sync((self.global_step + 1) % ga == 0)
             out = self.engine._forward_backward_scaled(ids, labels, batch.get("attention_mask"), ga)
             for k, v in (("loss", out["loss"]), ("lm", out["lm_loss"]), ("aux", out["aux_loss"])):
                 v = v.detach().float() if torch.is_tensor(v) else torch.tensor(float(v), device=self.device)
