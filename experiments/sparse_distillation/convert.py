@@ -68,9 +68,20 @@ def infer_layer_dims(state: Dict[str, torch.Tensor]):
 
 
 def convert_to_sparse(model: nn.Module, distilled_path: Optional[str] = None, trainer=None,
-                      random_init: bool = False) -> SparseModelWrapper:
+                      random_init: bool = False, layer_config_path: Optional[str] = None,
+                      device=None) -> SparseModelWrapper:
     """Build the sparse model from a ``SparseDistillationTrainer`` or from its ``save()`` file.
-    ``random_init=True`` keeps the architecture but re-initialises the experts (a control)."""
+    ``random_init=True`` keeps the architecture but re-initialises the experts (a control).
+    ``layer_config_path``: the per-layer file of ``generate_config``; expert counts and widths always come from
+    the saved weights' shapes, the file supplies each layer's ``top_k`` (and must agree with the shapes).
+    ``device``: where the model goes first (default: where it is)."""
+    if device is not None:
+        model.to(device)
+    per_layer = {}
+    if layer_config_path:
+        import json
+        per_layer = json.load(open(layer_config_path))
+        per_layer = per_layer.get("layers", per_layer)
     if trainer is not None:
         layers = {k: v for k, v in trainer.get_moe_layers().items()}
     else:
@@ -80,6 +91,12 @@ def convert_to_sparse(model: nn.Module, distilled_path: Optional[str] = None, tr
         for k, sd in ck["layers"].items():
             E, d, f = infer_layer_dims(sd)
             top_k = ck.get("dims", {}).get(k, (d, f, E, cfg.moe_top_k))[3]
+            lc = per_layer.get(str(k), {})
+            if lc:
+                if int(lc.get("n_experts", E)) != E or int(lc.get("d_ff_expert", f)) != f:
+                    raise ValueError(f"layer {k}: the layer configuration says {lc.get('n_experts')} experts of width "
+                                     f"{lc.get('d_ff_expert')}, the checkpoint holds {E} of width {f}")
+                top_k = int(lc.get("top_k", top_k))
             layer = MoEDistillationLayer(d, f, cfg, n_experts=E, top_k=top_k)
             layer.load_state_dict(sd)
             layers[k] = layer

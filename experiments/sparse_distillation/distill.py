@@ -139,6 +139,9 @@ class MoEDistillationLayer(nn.Module):
             self.experts = GroupedExperts(self.n_experts, d_model, d_ff_expert)
         self._last_router_logits: Optional[torch.Tensor] = None
         self._last_expert_counts: Optional[torch.Tensor] = None
+        # token choice under a per-expert capacity of T k / E (greedy, slot by slot): keeps every expert in use
+        # while fine-tuning (reference: finetune_eval.py:812-826 switches it on, moe.py:353-421 defines it)
+        self.balanced_routing = False
 
     def get_router_logits(self, x: torch.Tensor) -> torch.Tensor:
         logits = self.router(x)
@@ -160,7 +163,13 @@ class MoEDistillationLayer(nn.Module):
             self._last_expert_counts = torch.full((self.n_experts,), cap * x3.shape[0], device=x.device)
         else:
             probs = F.softmax(logits, dim=-1)
-            w, idx = torch.topk(probs, self.top_k, dim=-1)
+            if self.balanced_routing:
+                from kolmogorov_moe_architecture_b200 import ops
+                idx = ops.balanced_assign(probs.reshape(-1, self.n_experts).float(), self.top_k).view(
+                    *probs.shape[:-1], self.top_k)
+                w = probs.gather(-1, idx)
+            else:
+                w, idx = torch.topk(probs, self.top_k, dim=-1)
             w = w / w.sum(-1, keepdim=True)
             flat = x3.reshape(-1, self.d_model)
             out = self.experts(flat, idx.reshape(-1, self.top_k), w.reshape(-1, self.top_k)).view_as(x3)
@@ -253,8 +262,17 @@ def balanced_topk_targets(scores: torch.Tensor, k: int, max_prob: float, tempera
     return (1 - balance) * t + balance / E
 
 
+def _ids_of_batch(b) -> torch.Tensor:
+    """Token ids of a batch given as a tensor, a tuple whose first entry is one, or a dict with ``input_ids``."""
+    if isinstance(b, dict):
+        return b.get("input_ids", b.get("tokens"))
+    return b[0] if isinstance(b, (list, tuple)) else b
+
+
 class SparseDistillationTrainer:
-    def __init__(self, model: nn.Module, config: DistillationConfig, device: str = "cpu"):
+    def __init__(self, model: nn.Module = None, config: DistillationConfig = None, device: str = "cpu",
+                 dense_model: nn.Module = None):
+        model = dense_model if model is None else model          # the reference's keyword for the teacher
         self.model, self.cfg, self.device = model, config, torch.device(device)
         self.ffn = find_ffn_modules(model)
         assert self.ffn, "no FFN modules found in the model"
@@ -348,8 +366,18 @@ class SparseDistillationTrainer:
         return parts
 
     # ------------------------------------------------------------------- modes
-    def distill(self, batches=None, steps: Optional[int] = None) -> Dict[int, List[float]]:
-        """Dispatch on the configuration.  ``batches``: iterable of input-id tensors (real-data modes)."""
+    def distill(self, batches=None, steps: Optional[int] = None, epochs: int = 1, max_steps: Optional[int] = None,
+                dataloader=None) -> Dict[int, List[float]]:
+        """Dispatch on the configuration.  ``batches`` (or ``dataloader``, the reference's name for it): iterable of
+        input-id tensors or of dicts with ``input_ids``, walked ``epochs`` times in the real-data modes;
+        ``steps`` / ``max_steps`` bound the number of updates (reference: distill.py:929-1094)."""
+        batches = dataloader if batches is None else batches
+        steps = max_steps if steps is None else steps
+        if batches is not None and epochs > 1:
+            once = list(batches)
+            batches = [b for _ in range(epochs) for b in once]
+        if batches is not None:
+            batches = [_ids_of_batch(b) for b in batches]
         if self.cfg.dynamic_experts:
             return self._distill_dynamic(steps or self.cfg.data_free_steps)
         if self.cfg.empirical_routing:
@@ -464,7 +492,7 @@ class SparseDistillationTrainer:
             opt.zero_grad(set_to_none=True)
             loss.backward()
             opt.step()
-            last = float(loss)
+            last = float(loss.detach())
         return last
 
     def _distill_data_free(self, steps: int) -> Dict[int, List[float]]:
@@ -567,7 +595,12 @@ class SparseDistillationTrainer:
 
     # -------------------------------------------------------------- evaluation
     @torch.no_grad()
-    def evaluate(self, n_batches: int = 4) -> Dict[int, Dict[str, float]]:
+    def evaluate(self, n_batches: int = 4, batches=None, max_batches: int = 100) -> Dict[int, Dict[str, float]]:
+        """Per layer: MSE, cosine similarity and relative MSE of the MoE layer against the dense FFN - on what the
+        FFN sees when the model runs on ``batches`` (token ids; reference: distill.py:2849-2922) or, without
+        batches, on ``n_batches`` random unit-norm inputs."""
+        if batches is not None:
+            return self._evaluate_on_data(batches, max_batches)
         out = {}
         for i in range(len(self.ffn)):
             layer = self.moe_layers[str(i)].to(self.device).eval()
@@ -580,6 +613,30 @@ class SparseDistillationTrainer:
             out[i] = {"mse": mse / n_batches, "cosine": cos / n_batches,
                       "rel_mse": (mse / n_batches) / max(float(y.pow(2).mean()), 1e-12)}
         return out
+
+    @torch.no_grad()
+    def _evaluate_on_data(self, batches, max_batches: int) -> Dict[int, Dict[str, float]]:
+        n = 0
+        acc = {i: [0.0, 0.0, 0.0] for i in range(len(self.ffn))}
+        dev = next(self.model.parameters()).device
+        self.model.eval()
+        for b in batches:
+            if n >= max_batches:
+                break
+            with FFNActivationCache(self.model) as cache:
+                self.model(_ids_of_batch(b).to(dev))
+            for i in range(len(self.ffn)):
+                layer = self.moe_layers[str(i)].to(self.device).eval()
+                x, y = cache.inputs[i].to(self.device), cache.outputs[i].to(self.device).float()
+                s = layer(x).float()
+                acc[i][0] += float(F.mse_loss(s, y))
+                acc[i][1] += float(F.cosine_similarity(s.reshape(-1, self.d_model), y.reshape(-1, self.d_model),
+                                                       dim=-1).mean())
+                acc[i][2] += float(y.pow(2).mean())
+            n += 1
+        n = max(n, 1)
+        return {i: {"mse": a[0] / n, "cosine": a[1] / n, "rel_mse": (a[0] / n) / max(a[2] / n, 1e-12)}
+                for i, a in acc.items()}
 
     def save(self, path: str):
         torch.save({"layers": {k: v.state_dict() for k, v in self.moe_layers.items()}, "config": asdict(self.cfg),

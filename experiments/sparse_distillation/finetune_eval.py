@@ -240,7 +240,7 @@ def finetune(wrapper: SparseModelWrapper, batches: Iterable, steps: int, lr: flo
              lb_weight: float = 0.01, z_weight: float = 0.001, moe_only: bool = True, out_dir: Optional[str] = None,
              eval_batches=None, logits_of=None, eval_every: Optional[int] = None, lr_schedule: bool = False,
              resume: Optional[str] = None, pad_token_id: Optional[int] = None, max_grad_norm: float = 1.0,
-             log_every: int = 0) -> Dict[str, object]:
+             log_every: int = 0, use_8bit_adam: bool = False) -> Dict[str, object]:
     """Language-model fine-tuning of the converted model: cross-entropy plus the routers' auxiliary losses,
     gradient clipping, constant LR or cosine decay to 10 %, evaluation every ``eval_every`` steps with
     ``latest_checkpoint.pt`` (with optimizer state, for ``resume``) and ``best_checkpoint.pt`` under
@@ -248,7 +248,15 @@ def finetune(wrapper: SparseModelWrapper, batches: Iterable, steps: int, lr: flo
     if moe_only:
         freeze_all_but_moe(wrapper)
     params = [p for p in wrapper.model.parameters() if p.requires_grad]
-    opt = torch.optim.AdamW(params, lr=lr, weight_decay=0.0)
+    opt, opt_name = None, "adamw"
+    if use_8bit_adam:                            # the reference's default when bitsandbytes is importable
+        try:
+            import bitsandbytes as bnb
+            opt, opt_name = bnb.optim.Adam8bit(params, lr=lr), "adam8bit"
+        except Exception:
+            opt = None
+    if opt is None:
+        opt = torch.optim.AdamW(params, lr=lr, weight_decay=0.0)
     start = load_finetuned(wrapper, resume, opt) if resume else 0
     eval_every = eval_every or max(steps // 4, 1)
     best, last = float("inf"), 0.0
@@ -288,21 +296,16 @@ def finetune(wrapper: SparseModelWrapper, batches: Iterable, steps: int, lr: flo
                 best = ppl
                 if out_dir:
                     _save(os.path.join(out_dir, "best_checkpoint.pt"), wrapper, opt, s + 1, ppl, False)
-    return {"final_loss": last, "best_ppl": best, "history": history}
+    return {"final_loss": last, "best_ppl": best, "history": history, "optimizer": opt_name}
 
 
 def _token_batches(a, vocab: int, n: int, seed: int):
-    """Batches of token ids: a ``.bin`` file of uint16 ids when ``--data`` names one, otherwise random ids
-    from a seed (there is no dataset download in this script)."""
-    g = torch.Generator().manual_seed(seed)
-    if a.data:
-        import numpy as np
-        arr = np.memmap(a.data, dtype=np.uint16, mode="r")
-        n_seq = (len(arr) - 1) // a.seq_len
-        pick = torch.randperm(n_seq, generator=g)[: n * a.batch_size].tolist()
-        rows = [torch.from_numpy(np.asarray(arr[i * a.seq_len: (i + 1) * a.seq_len], dtype=np.int64)) for i in pick]
-        return [torch.stack(rows[i: i + a.batch_size]).to(a.device) for i in range(0, len(rows) - a.batch_size + 1, a.batch_size)]
-    return [torch.randint(0, vocab, (a.batch_size, a.seq_len), generator=g).to(a.device) for _ in range(n)]
+    """``n`` batches of token ids: the tokenised data set when it can be loaded, else the uint16 file ``--data``
+    names, else random ids from a seed.  Returns (batches, source, pad id)."""
+    from .data import load_token_batches
+    return load_token_batches(a.model, vocab, dataset=a.dataset, dataset_config=a.dataset_config, data_file=a.data,
+                              max_samples=a.max_samples, seq_len=a.seq_len, batch_size=a.batch_size, n_batches=n,
+                              seed=seed, device=a.device)
 
 
 def main(argv=None):
@@ -310,6 +313,9 @@ def main(argv=None):
 
         python -m experiments.sparse_distillation.finetune_eval --model toy --checkpoint out/distilled_moe.pt \\
             [--eval_only] [--compare_dense] [--random_init] [--moe_only] [--lr_schedule] [--resume latest.pt]
+
+    Every argument of the reference's script (Experiments/sparse_distillation/finetune_eval.py:696-770) is
+    accepted under the same name.
     """
     import argparse
     import copy
@@ -318,10 +324,24 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description="fine-tune and evaluate a sparse (distilled) model")
     ap.add_argument("--model", default="toy", help="'toy' or a local Hugging Face model directory")
     ap.add_argument("--checkpoint", required=True, help="file written by SparseDistillationTrainer.save")
-    ap.add_argument("--data", default=None, help="uint16 token file; random tokens when absent")
+    ap.add_argument("--layer_config", default=None, help="layer_config.json with per-layer n_experts / d_ff_expert / top_k")
+    ap.add_argument("--dtype", default="float32", choices=["float32", "float16", "bfloat16"])
+    ap.add_argument("--dataset", default="wikitext")
+    ap.add_argument("--dataset_config", default="wikitext-2-raw-v1")
+    ap.add_argument("--max_samples", type=int, default=20000)
+    ap.add_argument("--data", default=None, help="uint16 token file used when the data set cannot be loaded; "
+                    "random tokens when absent as well")
     ap.add_argument("--seq_len", type=int, default=64)
     ap.add_argument("--batch_size", type=int, default=4)
+    ap.add_argument("--epochs", type=int, default=1)
     ap.add_argument("--max_steps", type=int, default=100)
+    ap.add_argument("--no_8bit_adam", action="store_true",
+                    help="plain AdamW even where bitsandbytes' 8-bit Adam could be imported")
+    ap.add_argument("--balanced-routing", "--balanced_routing", dest="balanced_routing", action="store_true",
+                    help="token choice under a per-expert capacity, to keep every expert in use")
+    ap.add_argument("--compile", action="store_true", help="torch.compile the model before training")
+    ap.add_argument("--compile_mode", default="max-autotune",
+                    choices=["default", "reduce-overhead", "max-autotune", "max-autotune-no-cudagraphs"])
     ap.add_argument("--eval_every", type=int, default=None)
     ap.add_argument("--eval_batches", type=int, default=8)
     ap.add_argument("--lr", type=float, default=1e-4)
@@ -337,29 +357,44 @@ def main(argv=None):
     ap.add_argument("--output", default=None)
     ap.add_argument("--device", default="cpu")
     a = ap.parse_args(argv)
+    dtype = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}[a.dtype]
     if a.model == "toy":
         from .example_usage import ToyLM
         torch.manual_seed(0)
-        model, vocab = ToyLM(), 256
+        model, vocab = ToyLM().to(dtype), 256
     else:
         from transformers import AutoModelForCausalLM
-        model = AutoModelForCausalLM.from_pretrained(a.model, local_files_only=True)
+        model = AutoModelForCausalLM.from_pretrained(a.model, torch_dtype=dtype)
         vocab = model.config.vocab_size
     model.to(a.device)
     dense = copy.deepcopy(model).eval() if a.compare_dense else None
-    wrapper = convert_to_sparse(model, distilled_path=a.checkpoint, random_init=a.random_init)
+    wrapper = convert_to_sparse(model, distilled_path=a.checkpoint, random_init=a.random_init,
+                                layer_config_path=a.layer_config)
+    balanced = 0
+    if a.balanced_routing:
+        for layer in wrapper.moe_modules().values():
+            if hasattr(layer, "balanced_routing") and getattr(layer, "routing", "") == "token_choice":
+                layer.balanced_routing = True
+                balanced += 1
     if a.load_finetuned:
         load_finetuned(wrapper, a.load_finetuned)
-    train_b = _token_batches(a, vocab, max(a.max_steps, 1), seed=1)
-    eval_b = _token_batches(a, vocab, a.eval_batches, seed=2)
-    report: Dict[str, object] = {"parameters": wrapper.count_parameters()}
+    if a.compile:
+        try:
+            wrapper.model = torch.compile(wrapper.model, mode=a.compile_mode, fullgraph=False)
+        except Exception as e:
+            print(f"torch.compile failed ({type(e).__name__}: {e}); continuing without it")
+    train_b, source, pad = _token_batches(a, vocab, max(a.max_steps, 1), seed=1)
+    eval_b, _, _ = _token_batches(a, vocab, a.eval_batches, seed=2)
+    a.max_steps = min(a.max_steps, max(a.epochs, 1) * max(len(train_b), 1))
+    report: Dict[str, object] = {"parameters": wrapper.count_parameters(), "data": source,
+                                 "balanced_routing_layers": balanced}
     report["ppl_before"] = compute_perplexity(wrapper, eval_b, accumulate_routing=True)
     report["routing_before"] = compute_routing_stats_accumulated(wrapper, verbose=False)["aggregate"]
     if not a.eval_only:
         report["finetune"] = finetune(wrapper, train_b, a.max_steps, lr=a.lr, lb_weight=a.load_balance_weight,
                                       z_weight=a.z_loss_weight, moe_only=a.moe_only, out_dir=a.output,
                                       eval_batches=eval_b, eval_every=a.eval_every, lr_schedule=a.lr_schedule,
-                                      resume=a.resume)
+                                      resume=a.resume, pad_token_id=pad, use_8bit_adam=not a.no_8bit_adam)
         report["ppl_after"] = compute_perplexity(wrapper, eval_b, accumulate_routing=True)
         report["routing_after"] = compute_routing_stats_accumulated(wrapper, verbose=False)["aggregate"]
     if dense is not None:

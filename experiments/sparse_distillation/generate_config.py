@@ -68,24 +68,37 @@ def compute_layer_config(analysis: Dict, target_expansion_ratio: float = 3.0, ta
 
 
 def main(argv=None):
+    """``python -m experiments.sparse_distillation.generate_config out/cluster_analysis.json [--expansion_ratio 3]
+    [--active_ratio 0.25] [--min_experts 4] [--min_top_k 1] [--max_top_k 8] [--output out/layer_config.json]``
+    (the reference's arguments; the output defaults to ``layer_config.json`` beside the analysis)."""
     ap = argparse.ArgumentParser(description="per-layer MoE configuration from a cluster analysis")
-    ap.add_argument("--analysis", required=True)
-    ap.add_argument("--output", required=True)
-    ap.add_argument("--d-ff-dense", type=int, default=None,
+    ap.add_argument("analysis_path", nargs="?", default=None, help="cluster_analysis.json of example_usage --analyze_clusters")
+    ap.add_argument("--analysis", default=None, help="the same, as an option")
+    ap.add_argument("--output", default=None)
+    ap.add_argument("--d-ff-dense", "--d_ff_dense", dest="d_ff_dense", type=int, default=None,
                     help="needed for an analysis of the form {layer: {k: quality}}; a file with d_model / d_ff / layers brings its own")
-    ap.add_argument("--expansion", type=float, default=None)
-    ap.add_argument("--active-ratio", type=float, default=0.25)
-    ap.add_argument("--min-experts", type=int, default=4)
-    ap.add_argument("--max-top-k", type=int, default=8)
+    ap.add_argument("--expansion_ratio", "--expansion", dest="expansion", type=float, default=None,
+                    help="target n_experts * d_ff_expert / d_ff_dense (default 3.0)")
+    ap.add_argument("--active_ratio", "--active-ratio", dest="active_ratio", type=float, default=0.25,
+                    help="target top_k * d_ff_expert / d_ff_dense")
+    ap.add_argument("--min_experts", "--min-experts", dest="min_experts", type=int, default=4)
+    ap.add_argument("--min_top_k", "--min-top-k", dest="min_top_k", type=int, default=1)
+    ap.add_argument("--max_top_k", "--max-top-k", dest="max_top_k", type=int, default=8)
     a = ap.parse_args(argv)
-    data = json.load(open(a.analysis))
+    path = a.analysis_path or a.analysis
+    if path is None:
+        ap.error("the analysis file is required")
+    out = a.output or (path.replace("cluster_analysis.json", "layer_config.json") if path.endswith("cluster_analysis.json")
+                       else path + ".layer_config.json")
+    data = json.load(open(path))
     if "layers" in data and "d_ff" in data:
-        cfg = compute_layer_config(data, a.expansion or 3.0, a.active_ratio, a.min_experts, 1, a.max_top_k)
+        cfg = compute_layer_config(data, a.expansion or 3.0, a.active_ratio, a.min_experts, a.min_top_k, a.max_top_k)
     else:
         assert a.d_ff_dense, "--d-ff-dense is required for this analysis format"
         cfg = generate(data, a.d_ff_dense, a.expansion or 2.0, a.active_ratio)
         print(json.dumps(cfg, indent=2))
-    json.dump(cfg, open(a.output, "w"), indent=2)
+    json.dump(cfg, open(out, "w"), indent=2)
+    print(f"saved {out}")
     return cfg
 
 

@@ -1,4 +1,5 @@
 """Sparse distillation pipeline on a toy transformer (CPU)."""
+import pytest
 import torch
 
 from experiments.sparse_distillation.convert import convert_to_sparse
@@ -178,3 +179,86 @@ def test_compute_layer_config_holds_the_ratios(tmp_path):
     f.write_text(json.dumps(analysis))
     out = main(["--analysis", str(f), "--output", str(tmp_path / "o.json")])
     assert json.load(open(tmp_path / "o.json"))["layers"] == out["layers"]
+
+
+def test_command_lines_take_the_reference_arguments(tmp_path, capsys):
+    """analyse clusters -> per-layer configuration -> distil with it -> fine-tune / evaluate, each step driven through
+    its command line with the argument names of the reference's scripts
+    (Experiments/sparse_distillation/{example_usage,generate_config,finetune_eval}.py)."""
+    import json
+    from experiments.sparse_distillation import example_usage as eu, finetune_eval as fe, generate_config as gc
+    out = str(tmp_path / "o")
+    # every flag of the reference's example_usage parses, and lands in the configuration
+    a = eu.build_parser().parse_args(
+        "--model toy --dtype float32 --dataset wikitext --dataset_config wikitext-2-raw-v1 --max_samples 64 "
+        "--seq_len 32 --batch_size 2 --n_experts 6 --moe_top_k 3 --capacity_factor 1.5 --d_ff_expert 0.5 "
+        "--routing token_choice --epochs 2 --lr 3e-4 --max_steps 7 --sequential --no_data_free --data_free_steps 9 "
+        "--data_free_batch_size 3 --data_free_seq_len 48 --no_compile --no_load_balance --load_balance_weight 0.02 "
+        "--no_z_loss --z_loss_weight 0.002 --no_supervised_routing --cluster_samples 500 --router_train_steps 11 "
+        "--empirical_routing --empirical_eval_interval 5 --empirical_temperature 0.2 --empirical_entropy_weight 0.03 "
+        "--no_curriculum --curriculum_warmup_steps 50 --curriculum_initial_balance 0.8 --curriculum_final_balance 0.2 "
+        "--no_gradient_routing --gradient_routing_exact --router_mlp --router_hidden_dim 32 --router_n_layers 3 "
+        "--dynamic --reallocate_every 4 --growth_factor 1.5 --shrink_factor 0.7 --min_d_ff 16 --max_d_ff 512 "
+        f"--output {out} --device cpu".split())
+    c = eu.config_from_args(a)
+    assert (c.n_experts, c.moe_top_k, c.moe_capacity_factor, c.d_ff_expert, c.learning_rate) == (6, 3, 1.5, 0.5, 3e-4)
+    assert c.sequential_layers and not c.data_free and (c.data_free_steps, c.data_free_batch_size) == (9, 3)
+    assert not c.use_load_balancing and c.load_balancing_weight == 0.02 and not c.use_z_loss and c.z_loss_weight == 0.002
+    assert not c.supervised_routing and c.cluster_samples == 500 and c.router_train_steps == 11
+    assert c.empirical_routing and c.empirical_eval_interval == 5 and c.empirical_temperature == 0.2
+    assert not c.curriculum_routing and c.curriculum_warmup_steps == 50 and c.curriculum_final_balance == 0.2
+    assert not c.gradient_routing and not c.gradient_routing_fast
+    assert c.router_mlp and (c.router_hidden_dim, c.router_n_layers) == (32, 3)
+    assert c.dynamic_experts and (c.reallocate_every_n_steps, c.growth_factor, c.min_d_ff, c.max_d_ff) == (4, 1.5, 16, 512)
+    assert eu.parse_expert_width("2048") == 2048 and eu.parse_expert_width("0.075") == 0.075
+    assert eu.parse_expert_width(None) is None and eu.parse_expert_width("auto") is None
+    # 1. cluster analysis (stops after writing the file)
+    _, sparse, analysis = eu.main(["--analyze_clusters", "--steps", "4", "--k_values", "2,4", "--output", out])
+    assert sparse is None and set(analysis["layers"]) == {"0", "1"} and analysis["d_ff"] == 256
+    # 2. per-layer configuration, positional path, default output beside it
+    cfg = gc.main([out + "/cluster_analysis.json", "--expansion_ratio", "2", "--active_ratio", "0.5", "--min_experts",
+                   "2", "--min_top_k", "1", "--max_top_k", "4"])
+    saved = json.load(open(out + "/layer_config.json"))
+    assert saved["layers"] == cfg["layers"] and abs(cfg["stats"]["actual_expansion_ratio"] - 2.0) < 1e-6
+    # 3. distillation with that configuration, on token batches, two epochs
+    tr, sparse, ev = eu.main(["--layer_config", out + "/layer_config.json", "--no_data_free", "--max_steps", "6",
+                              "--epochs", "2", "--steps", "6", "--output", out])
+    for i, lc in cfg["layers"].items():
+        layer = tr.moe_layers[i]
+        assert (layer.n_experts, layer.d_ff, layer.top_k) == (lc["n_experts"], lc["d_ff_expert"], lc["top_k"])
+    assert set(ev) == {0, 1} and all(0 < v["rel_mse"] < 2 for v in ev.values())
+    assert (tmp_path / "o" / "distilled_moe_layers.pt").exists() and (tmp_path / "o" / "sparse_model.pt").exists()
+    # 4. fine-tune / evaluate with the reference's switches
+    rep = fe.main(["--model", "toy", "--checkpoint", out + "/distilled_moe_layers.pt", "--layer_config",
+                   out + "/layer_config.json", "--dtype", "float32", "--dataset", "wikitext", "--dataset_config",
+                   "wikitext-2-raw-v1", "--max_samples", "32", "--epochs", "1", "--max_steps", "4", "--eval_every", "2",
+                   "--eval_batches", "2", "--seq_len", "16", "--batch_size", "2", "--balanced-routing", "--no_8bit_adam",
+                   "--moe_only", "--load_balance_weight", "0.01", "--z_loss_weight", "0.001", "--device", "cpu"])
+    assert rep["balanced_routing_layers"] == 2 and rep["data"] == "random" and rep["finetune"]["optimizer"] == "adamw"
+    capsys.readouterr()
+    # a layer configuration that contradicts the checkpoint is refused
+    bad = json.load(open(out + "/layer_config.json"))
+    bad["layers"]["0"]["n_experts"] += 1
+    json.dump(bad, open(out + "/bad.json", "w"))
+    with pytest.raises(ValueError, match="layer 0: the layer configuration says"):
+        fe.main(["--checkpoint", out + "/distilled_moe_layers.pt", "--layer_config", out + "/bad.json", "--eval_only"])
+
+
+def test_balanced_routing_brings_unused_experts_into_use():
+    """Two experts that every token prefers: plain top-2 leaves the other two without a token; with the capacity of
+    T k / E checked at the start of each slot (the reference's rule, moe.py:353-421), whichever of the two is full
+    after the first slot is closed in the second, and its tokens go to the idle experts."""
+    from experiments.sparse_distillation.distill import MoEDistillationLayer
+    torch.manual_seed(0)
+    layer = MoEDistillationLayer(32, 16, _cfg(), n_experts=4, top_k=2)
+    with torch.no_grad():
+        layer.expert_bias[0] = 8.0
+        layer.expert_bias[1] = 8.0
+    x = torch.randn(2, 24, 32)
+    layer(x)
+    free = layer._last_expert_counts.clone()
+    layer.balanced_routing = True
+    out = layer(x)
+    bal = layer._last_expert_counts
+    assert free.tolist() == [48, 48, 0, 0]
+    assert int(bal.sum()) == 96 and int((bal == 0).sum()) == 0 and out.shape == x.shape
