@@ -68,10 +68,12 @@ def lint_config(cfg) -> list:
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", required=True)
+    ap.add_argument("--config", default="configs/production_training.yaml")
     ap.add_argument("--checkpoint", default=None)
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--batches", type=int, default=4)
+    ap.add_argument("--batch-size", type=int, default=1)
+    ap.add_argument("--seq-len", type=int, default=512)
     a = ap.parse_args(argv)
     from eval.evaluate_perplexity import load_model
     from kolmogorov_moe_architecture_b200.utils.fault import gradient_census
@@ -79,7 +81,7 @@ def main(argv=None):
     an = RouterAnalyzer(model)
     model.train()
     for _ in range(a.batches):
-        ids = torch.randint(0, cfg.vocab_size, (2, min(128, cfg.max_seq_len)), device=a.device)
+        ids = torch.randint(0, cfg.vocab_size, (a.batch_size, min(a.seq_len, cfg.max_seq_len)), device=a.device)
         model.zero_grad(set_to_none=True)
         model(ids, labels=ids, return_logits=False)["loss"].backward()
     rep = an.report()

@@ -311,7 +311,7 @@ def _token_batches(a, vocab: int, n: int, seed: int):
 def main(argv=None):
     """Fine-tune and/or evaluate a distilled checkpoint:
 
-        python -m experiments.sparse_distillation.finetune_eval --model toy --checkpoint out/distilled_moe.pt \\
+        python -m experiments.sparse_distillation.finetune_eval --model toy --checkpoint out/distilled_moe_layers.pt \\
             [--eval_only] [--compare_dense] [--random_init] [--moe_only] [--lr_schedule] [--resume latest.pt]
 
     Every argument of the reference's script (Experiments/sparse_distillation/finetune_eval.py:696-770) is

@@ -47,6 +47,9 @@ def test_diagnose_training_reports_every_section(tiny):
     from tools import diagnose_training as dt
     rep = dt.main(["--checkpoint", tiny["checkpoint"], "--config", tiny["config"], "--device", "cpu", "--synthetic",
                    "--eval-batches", "2"])
+    quick = dt.main(["--checkpoint", tiny["checkpoint"], "--config", tiny["config"], "--device", "cpu", "--gpu", "0",
+                     "--skip-eval", "--skip-generation"])
+    assert "evaluation" not in quick and "gradients" in quick
     assert set(rep) >= {"router", "routing_in_model", "movement", "trainability", "evaluation", "gradients", "findings"}
     assert rep["trainability"]["trainable"] == rep["trainability"]["total"]
     assert abs(rep["evaluation"]["lm_loss"] - rep["evaluation"]["uniform_loss"]) < 1.0   # untrained model
@@ -99,6 +102,14 @@ def test_param_calculator_matches_the_model(tiny):
     assert pc.format_params(5.87e9) == "5.87B" and pc.format_params(1500) == "1.50K"
     found = pc.design(5e9, 1.5e9, tol=0.3, limit=3)
     assert isinstance(found, list)
+    # the reference's manual options: experts in every layer, totals equal to the instantiated model
+    rep = pc.main(["--vocab-size", "1000", "--d-model", "256", "--n-layers", "4", "--n-heads", "2", "--n-kv-heads", "1",
+                   "--head-dim", "128", "--d-ff", "512", "--d-ff-expert", "256", "--n-experts", "4", "--top-k", "2",
+                   "--all-moe", "--world", "2"])
+    bd = rep["breakdown"]
+    assert bd["experts"] == 4 * 4 * 3 * 256 * 256 and bd["dense_ffn"] == 0 and bd["mamba"] == 0 and bd["mod_router"] == 0
+    assert bd["embedding"] == 1000 * 256
+    assert isinstance(pc.main(["--design", "--target-total", "5", "--target-active", "1.5"]), list)
 
 
 def test_plateau_memory_debug_and_active_param_tools(tiny, capsys):
@@ -108,7 +119,7 @@ def test_plateau_memory_debug_and_active_param_tools(tiny, capsys):
     import diagnose_memory
     import diagnose_plateau
     rep = diagnose_plateau.main(["--config", tiny["config"], "--checkpoint", tiny["checkpoint"], "--device", "cpu",
-                                 "--batches", "2"])
+                                 "--batches", "2", "--batch-size", "1", "--seq-len", "16"])
     assert rep, "router hooks recorded nothing"
     rows = check_memory.main(["--config", tiny["config"], "--seq-len", "32"])
     assert [r[0] for r in rows][:2] == ["start", "model"] and len(rows) >= 6
@@ -130,7 +141,9 @@ def test_expert_choice_scatter_benchmark_variants_agree():
     a = bec.scatter_loop(torch.zeros(B, S, d), w_out, idx)
     b = bec.scatter_vectorised(torch.zeros(B, S, d), w_out, idx)
     assert torch.allclose(a, b, atol=1e-6)
-    bec.main(["--device", "cpu"])
+    times = bec.main(["--device", "cpu", "--batch-size", "2", "--seq-len", "64", "--d-model", "32", "--n-experts", "4",
+                      "--capacity-factor", "1.25", "--warmup", "1", "--iters", "3"])
+    assert set(times) == {"loop", "scatter_add"} and all(t > 0 for t in times.values())
 
 
 def test_bench_clock_sampler_parses_nvidia_smi_lines_and_flags():

@@ -152,11 +152,16 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--checkpoint", default=None)
     ap.add_argument("--config", required=True)
-    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--device", default=None, help="default: cuda:<--gpu> when a GPU is present, else cpu")
+    ap.add_argument("--gpu", type=int, default=0, help="GPU index (the reference's way of naming the device)")
     ap.add_argument("--synthetic", action="store_true")
     ap.add_argument("--data", default=None, help="uint16 token file for the evaluation pass")
     ap.add_argument("--eval-batches", type=int, default=8)
+    ap.add_argument("--skip-eval", action="store_true", help="no evaluation pass")
+    ap.add_argument("--skip-generation", action="store_true", help="no greedy sample")
     a = ap.parse_args(argv)
+    if a.device is None:
+        a.device = f"cuda:{a.gpu}" if torch.cuda.is_available() else "cpu"
     from eval.evaluate_perplexity import load_model
     from kolmogorov_moe_architecture_b200.utils.fault import check_router_collapse
     model, cfg = load_model(a.checkpoint, a.config, a.device, dtype=torch.float32 if a.device == "cpu" else torch.bfloat16)
@@ -171,15 +176,21 @@ def main(argv=None):
     print("[movement] least moved:", sorted(mv.items(), key=lambda kv: kv[1])[:5])
     tr = trainability(model)
     print(f"[trainable] {tr['trainable']:,} of {tr['total']:,}; frozen tensors: {len(tr['frozen_tensors'])}")
-    ev = run_evaluation(model, cfg, a.eval_batches, a.device, None if a.synthetic else a.data)
-    print(f"[eval] {ev['source']}: loss {ev['lm_loss']:.4f} (uniform {ev['uniform_loss']:.4f}) ppl {ev['perplexity']:.1f}")
+    ev = None
+    if not a.skip_eval:
+        ev = run_evaluation(model, cfg, a.eval_batches, a.device, None if a.synthetic else a.data)
+        print(f"[eval] {ev['source']}: loss {ev['lm_loss']:.4f} (uniform {ev['uniform_loss']:.4f}) "
+              f"ppl {ev['perplexity']:.1f}")
     ids = torch.randint(0, cfg.vocab_size, (2, min(64, cfg.max_seq_len)), device=a.device)
     grads = gradient_flow(model, ids)
     for k, v in grads.items():
         print(f"[grad] {k}: {v}")
-    print("[sample]", greedy_sample(model, ids[:1, :8], 12)[0].tolist())
+    if not a.skip_generation:
+        print("[sample]", greedy_sample(model, ids[:1, :8], 12)[0].tolist())
     report = {"router": stats, "collapsed": collapsed, "routing_in_model": in_model, "movement": mv,
-              "trainability": tr, "evaluation": ev, "gradients": grads}
+              "trainability": tr, "gradients": grads}
+    if ev is not None:
+        report["evaluation"] = ev
     report["findings"] = findings(report)
     for line in report["findings"]:
         print("[finding]", line)

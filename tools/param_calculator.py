@@ -2,7 +2,8 @@
 ``tools/param_calculator.py``).
 
     python tools/param_calculator.py --config configs/training_4.5b.yaml
-    python tools/param_calculator.py --design --target-total 5e9 --target-active 1.5e9
+    python tools/param_calculator.py --d-model 1024 --n-layers 18 --n-experts 16 --top-k 2 [--all-moe]
+    python tools/param_calculator.py --design --target-total 5 --target-active 1.5       # billions
 
 ``analyze`` gives exact totals by component (from an instantiated model on the meta device, so a
 7B model costs no memory), the active-parameter count, and training-memory estimates for the
@@ -128,19 +129,63 @@ def design(target_total: float, target_active: float, tol: float = 0.1, limit: i
     return sorted(out, key=lambda r: abs(r["total_b"] * 1e9 - target_total))[:limit]
 
 
-if __name__ == "__main__":
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--config", default=None)
+def config_from_flags(a):
+    """The model the manual options describe (reference: tools/param_calculator.py:343-358): attention and experts
+    in every layer, no Mamba, no mixture-of-depths.  In the reference a manual configuration has experts in all
+    layers with or without ``--all-moe`` (its layer list defaults to "all"); the flag is accepted and means the same
+    here."""
+    from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig
+    L = a.n_layers
+    moe = tuple(range(L))
+    return AdvancedMoEConfig(vocab_size=a.vocab_size, d_model=a.d_model, n_layers=L, n_heads=a.n_heads,
+                             n_kv_heads=a.n_kv_heads, head_dim=a.head_dim, d_ff=a.d_ff, d_ff_expert=a.d_ff_expert,
+                             n_experts=a.n_experts, moe_top_k=a.top_k, moe_layers=moe, mamba_enabled=False,
+                             mamba_layers=(), mod_enabled=False)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description="parameter and memory report of a model configuration")
+    ap.add_argument("--config", default=None, help="YAML configuration")
     ap.add_argument("--world", type=int, default=8)
-    ap.add_argument("--design", action="store_true")
-    ap.add_argument("--target-total", type=float, default=5e9)
-    ap.add_argument("--target-active", type=float, default=1.5e9)
-    a = ap.parse_args()
+    manual = ap.add_argument_group("manual configuration (used when any of them is given and --config is not)")
+    manual.add_argument("--vocab-size", type=int, default=None)
+    manual.add_argument("--d-model", type=int, default=None)
+    manual.add_argument("--n-layers", type=int, default=None)
+    manual.add_argument("--n-heads", type=int, default=None)
+    manual.add_argument("--n-kv-heads", type=int, default=None)
+    manual.add_argument("--head-dim", type=int, default=None)
+    manual.add_argument("--d-ff", type=int, default=None)
+    manual.add_argument("--d-ff-expert", type=int, default=None)
+    manual.add_argument("--n-experts", type=int, default=None)
+    manual.add_argument("--top-k", type=int, default=None)
+    manual.add_argument("--all-moe", action="store_true", help="experts in every layer (already the rule for a manual configuration)")
+    ap.add_argument("--design", action="store_true", help="search configurations near the targets")
+    ap.add_argument("--target-total", type=float, default=5.0,
+                    help="total parameters, in billions (values above 1000 are taken as a plain count)")
+    ap.add_argument("--target-active", type=float, default=1.5, help="active parameters, same unit")
+    a = ap.parse_args(argv)
     if a.design:
-        for r in design(a.target_total, a.target_active):
+        to_count = lambda v: v if v > 1000 else v * 1e9
+        found = design(to_count(a.target_total), to_count(a.target_active))
+        for r in found:
             print(r)
+        return found
+    from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig
+    from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml, model_config_tolerant
+    defaults = dict(vocab_size=32000, d_model=1024, n_layers=18, n_heads=8, n_kv_heads=4, head_dim=128, d_ff=4096,
+                    d_ff_expert=2048, n_experts=16, top_k=2)                 # the reference's manual defaults
+    given = a.all_moe or any(getattr(a, k) is not None for k in defaults)
+    if a.config:
+        cfg = model_config_tolerant(load_yaml(a.config))
+    elif given:
+        for k, v in defaults.items():
+            if getattr(a, k) is None:
+                setattr(a, k, v)
+        cfg = config_from_flags(a)
     else:
-        from kolmogorov_moe_architecture_b200 import AdvancedMoEConfig
-        from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml, model_config_tolerant
-        cfg = model_config_tolerant(load_yaml(a.config)) if a.config else AdvancedMoEConfig()
-        print_report(cfg, a.world)
+        cfg = AdvancedMoEConfig()
+    return print_report(cfg, a.world)
+
+
+if __name__ == "__main__":
+    main()

@@ -115,7 +115,10 @@ if __name__ == "__main__":
     ap.add_argument("--checkpoint", required=True)
     ap.add_argument("--config", required=True)
     ap.add_argument("--output", required=True)
-    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--device", default=None, help="default: cuda:<--gpu> when a GPU is present, else cpu")
+    ap.add_argument("--gpu", type=int, default=0, help="GPU index (the reference's way of naming the device)")
     ap.add_argument("--entropy-threshold", type=float, default=0.85)
     a = ap.parse_args()
+    if a.device is None:
+        a.device = f"cuda:{a.gpu}" if torch.cuda.is_available() else "cpu"
     reallocate_experts(a.checkpoint, a.config, a.output, a.device, a.entropy_threshold)
