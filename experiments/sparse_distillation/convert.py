@@ -53,6 +53,31 @@ class SparseModelWrapper(nn.Module):
                           "entropy": float(-(u * torch.log(u + 1e-10)).sum() / torch.log(torch.tensor(float(len(u)))))}
         return out
 
+    # the reference's view of the same object (Experiments/sparse_distillation/convert.py:80-143)
+    @property
+    def base_model(self) -> nn.Module:
+        return self.model
+
+    @property
+    def moe_layers(self) -> nn.ModuleDict:
+        """The MoE layers keyed by layer index (a view: the modules live inside ``model``)."""
+        return nn.ModuleDict({str(i): m for i, m in self.moe_modules().items()})
+
+    @property
+    def n_experts(self) -> int:
+        """Experts per layer (of the first MoE layer; layers may differ under a per-layer configuration)."""
+        return next(iter(self.moe_modules().values())).n_experts
+
+    def get_active_parameters(self, top_k: Optional[int] = None) -> int:
+        """Parameters a token touches: everything outside the experts, plus ``top_k`` of each layer's experts
+        (each layer's own ``top_k`` when none is given)."""
+        total = sum(p.numel() for p in self.model.parameters())
+        idle = 0.0
+        for m in self.moe_modules().values():
+            k = min(top_k if top_k is not None else m.top_k, m.n_experts)
+            idle += sum(p.numel() for p in m.experts.parameters()) * (1.0 - k / m.n_experts)
+        return int(total - idle)
+
     def count_parameters(self) -> Dict[str, int]:
         total = sum(p.numel() for p in self.model.parameters())
         expert = sum(p.numel() for m in self.moe_modules().values() for p in m.experts.parameters())
@@ -67,14 +92,17 @@ def infer_layer_dims(state: Dict[str, torch.Tensor]):
     return w1.shape[0], w1.shape[1], w1.shape[2]
 
 
-def convert_to_sparse(model: nn.Module, distilled_path: Optional[str] = None, trainer=None,
+def convert_to_sparse(model: nn.Module = None, distilled_path: Optional[str] = None, trainer=None,
                       random_init: bool = False, layer_config_path: Optional[str] = None,
-                      device=None) -> SparseModelWrapper:
+                      device=None, dense_model: nn.Module = None,
+                      distillation_checkpoint: Optional[str] = None) -> SparseModelWrapper:
     """Build the sparse model from a ``SparseDistillationTrainer`` or from its ``save()`` file.
     ``random_init=True`` keeps the architecture but re-initialises the experts (a control).
     ``layer_config_path``: the per-layer file of ``generate_config``; expert counts and widths always come from
     the saved weights' shapes, the file supplies each layer's ``top_k`` (and must agree with the shapes).
     ``device``: where the model goes first (default: where it is)."""
+    model = dense_model if model is None else model                      # the reference's keyword names
+    distilled_path = distillation_checkpoint if distilled_path is None else distilled_path
     if device is not None:
         model.to(device)
     per_layer = {}

@@ -334,20 +334,20 @@ class SparseDistillationTrainer:
 
     def compute_loss(self, student: torch.Tensor, teacher: torch.Tensor, aux: Dict) -> Tuple[torch.Tensor, Dict[str, float]]:
         mse = F.mse_loss(student.float(), teacher.float())
-        loss, parts = mse, {"mse": float(mse)}
+        loss, parts = mse, {"mse": float(mse.detach())}
         if self.cfg.use_cosine_loss:
             cos = 1 - F.cosine_similarity(student.float().reshape(-1, student.shape[-1]),
                                           teacher.float().reshape(-1, teacher.shape[-1]), dim=-1).mean()
             loss = loss + self.cfg.cosine_loss_weight * cos
-            parts["cos"] = float(cos)
+            parts["cos"] = float(cos.detach())
         if self.cfg.use_load_balancing and self.cfg.moe_routing == "token_choice":
             lb = self.compute_load_balancing_loss(aux["router_logits"], aux["expert_counts"])
             loss = loss + self.cfg.load_balancing_weight * lb
-            parts["lb"] = float(lb)
+            parts["lb"] = float(lb.detach())
         if self.cfg.use_z_loss:
             z = self.compute_z_loss(aux["router_logits"])
             loss = loss + self.cfg.z_loss_weight * z
-            parts["z"] = float(z)
+            parts["z"] = float(z.detach())
         return loss, parts
 
     def train_step(self, i: int, x: torch.Tensor, target: torch.Tensor) -> Dict[str, float]:
@@ -362,7 +362,7 @@ class SparseDistillationTrainer:
         for g in opt.param_groups:
             g["lr"] = lr
         opt.step()
-        parts["loss"] = float(loss)
+        parts["loss"] = float(loss.detach())
         return parts
 
     # ------------------------------------------------------------------- modes
@@ -551,7 +551,7 @@ class SparseDistillationTrainer:
                 total.backward()
                 torch.nn.utils.clip_grad_norm_(layer.parameters(), c.max_grad_norm)
                 opt.step()
-                hist[i].append(float(loss))
+                hist[i].append(float(loss.detach()))
         return hist
 
     def _distill_dynamic(self, steps: int) -> Dict[int, List[float]]:
@@ -580,7 +580,7 @@ class SparseDistillationTrainer:
                 opt.zero_grad(set_to_none=True)
                 loss.backward()
                 opt.step()
-                hist[i].append(float(loss))
+                hist[i].append(float(loss.detach()))
                 pe = torch.zeros(base.n_experts, device=x.device).index_add_(0, idx[:, 0], per_tok.detach())
                 cnt = torch.bincount(idx[:, 0], minlength=base.n_experts)
                 tracker.update(pe / cnt.clamp(min=1), cnt)

@@ -186,6 +186,35 @@ def compare_dense(dense_model, wrapper: SparseModelWrapper, batches, logits_of=N
     return {"dense_ppl": d, "sparse_ppl": s_, "ratio": s_ / d if d > 0 else float("inf")}
 
 
+def compute_load_balancing_loss(router_logits: torch.Tensor, expert_counts: torch.Tensor) -> torch.Tensor:
+    """E * sum_e f_e P_e: f = share of the assignments each expert received, P = mean routing probability."""
+    E = router_logits.shape[-1]
+    P = F.softmax(router_logits.reshape(-1, E).float(), -1).mean(0)
+    f = expert_counts.float() / expert_counts.sum().clamp(min=1)
+    return E * (f * P).sum()
+
+
+def compute_z_loss(router_logits: torch.Tensor) -> torch.Tensor:
+    """Mean squared log-sum-exp of the router logits."""
+    return torch.logsumexp(router_logits.reshape(-1, router_logits.shape[-1]).float(), -1).pow(2).mean()
+
+
+def freeze_non_moe_layers(model, moe_only: bool = False):
+    """The parameters to train: all of them, or with ``moe_only`` the experts, routers and norms (the rest is
+    frozen) - the name rule of the reference (finetune_eval.py:467-495).  ``freeze_all_but_moe`` is the stricter
+    form used by this file's ``finetune``: MoE layers only, found by module, not by name."""
+    if not moe_only:
+        return list(model.parameters())
+    keep = []
+    for name, p in model.named_parameters():
+        low = name.lower()
+        on = "experts" in low or "router" in low or "expert_bias" in low or "norm" in low or "ln" in low
+        p.requires_grad_(on)
+        if on:
+            keep.append(p)
+    return keep
+
+
 def freeze_all_but_moe(wrapper: SparseModelWrapper) -> int:
     for p in wrapper.model.parameters():
         p.requires_grad_(False)
@@ -207,11 +236,9 @@ def aux_losses(wrapper: SparseModelWrapper, lb_weight: float, z_weight: float) -
             continue
         t = 0.0
         if lb_weight > 0 and c is not None and m.routing == "token_choice":
-            E = rl.shape[-1]
-            P = F.softmax(rl.reshape(-1, E).float(), -1).mean(0)
-            t = t + lb_weight * E * ((c.float() / c.sum().clamp(min=1)) * P).sum()
+            t = t + lb_weight * compute_load_balancing_loss(rl, c)
         if z_weight > 0:
-            t = t + z_weight * torch.logsumexp(rl.float(), -1).pow(2).mean()
+            t = t + z_weight * compute_z_loss(rl)
         if torch.is_tensor(t):
             total = t if total is None else total + t
     return total if total is not None else torch.zeros((), device=next(wrapper.model.parameters()).device)

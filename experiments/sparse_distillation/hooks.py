@@ -6,6 +6,7 @@ FFN modules are discovered by name: the last path component is one of ``mlp``, `
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional, Tuple
 
 import torch
@@ -14,11 +15,23 @@ import torch.nn as nn
 FFN_NAMES = ("mlp", "ffn", "feed_forward", "ff")
 
 
-def find_ffn_modules(model: nn.Module, names=FFN_NAMES) -> List[Tuple[str, nn.Module]]:
+@dataclass
+class FFNActivation:
+    """Input and output of one FFN layer for the last forward pass, (batch, seq, d_model) each."""
+    layer_idx: int
+    input: torch.Tensor
+    output: torch.Tensor
+
+
+def find_ffn_modules(model: nn.Module, names=FFN_NAMES,
+                     layer_filter: Optional[Callable[[str, nn.Module], bool]] = None) -> List[Tuple[str, nn.Module]]:
+    """(path, module) of every feed-forward block, outermost match only.  ``layer_filter(name, module)`` replaces
+    the name rule when given."""
     found = []
     for name, mod in model.named_modules():
         leaf = name.split(".")[-1].lower()
-        if leaf in names and not any(name.startswith(p + ".") for p, _ in found):
+        hit = layer_filter(name, mod) if layer_filter is not None else leaf in names
+        if name and hit and not any(name.startswith(p + ".") for p, _ in found):
             found.append((name, mod))
     return found
 
@@ -27,9 +40,10 @@ class FFNActivationCache:
     """``with FFNActivationCache(model) as cache: model(x)`` then ``cache.inputs[i]`` / ``cache.outputs[i]``
     hold the (detached) activations of FFN layer i for the last forward."""
 
-    def __init__(self, model: nn.Module, layers: Optional[List[int]] = None, detach: bool = True, to_cpu: bool = False):
+    def __init__(self, model: nn.Module, layers: Optional[List[int]] = None, detach: bool = True, to_cpu: bool = False,
+                 layer_filter: Optional[Callable[[str, nn.Module], bool]] = None):
         self.model, self.detach, self.to_cpu = model, detach, to_cpu
-        self.ffn = find_ffn_modules(model)
+        self.ffn = find_ffn_modules(model, layer_filter=layer_filter)
         self.layers = list(range(len(self.ffn))) if layers is None else layers
         self.inputs: Dict[int, torch.Tensor] = {}
         self.outputs: Dict[int, torch.Tensor] = {}
@@ -63,6 +77,23 @@ class FFNActivationCache:
         self.inputs.clear()
         self.outputs.clear()
 
+    # the reference's names for the same operations (Experiments/sparse_distillation/hooks.py:108-158)
+    @property
+    def layer_indices(self) -> List[int]:
+        return list(self.layers)
+
+    def register_hooks(self):
+        return self.register()
+
+    def remove_hooks(self):
+        self.remove()
+
+    def get_activations(self) -> Dict[int, FFNActivation]:
+        return {i: FFNActivation(i, self.inputs[i], self.outputs[i]) for i in sorted(self.inputs) if i in self.outputs}
+
+    def get_layer_activation(self, layer_idx: int) -> Optional[FFNActivation]:
+        return self.get_activations().get(layer_idx)
+
     __enter__ = register
 
     def __exit__(self, *exc):
@@ -71,21 +102,66 @@ class FFNActivationCache:
 
 
 class StreamingFFNExtractor:
-    """Calls ``fn(layer_idx, ffn_input, ffn_output)`` during the forward pass instead of storing
-    activations, so only one layer's tensors are alive at a time."""
+    """Activations without keeping them around, in two forms.
 
-    def __init__(self, model: nn.Module, fn: Callable[[int, torch.Tensor, torch.Tensor], None]):
-        self.ffn = find_ffn_modules(model)
-        self.fn = fn
+    Pull (the reference's form, hooks.py:171-243): ``StreamingFFNExtractor(model).extract(input_ids)`` runs one
+    forward pass of the (evaluation-mode) model and returns ``{layer: FFNActivation}`` for that batch only.
+
+    Push: ``with StreamingFFNExtractor(model, fn): model(x)`` calls ``fn(layer, ffn_input, ffn_output)`` as each
+    layer runs, so only one layer's tensors are alive at a time."""
+
+    def __init__(self, model: nn.Module, fn: Optional[Callable[[int, torch.Tensor, torch.Tensor], None]] = None,
+                 **cache_kwargs):
+        self.model, self.fn = model, fn
+        self._handles = []
+        if fn is None:
+            self.cache = FFNActivationCache(model, **cache_kwargs)
+            self.cache.register_hooks()
+            self.ffn = self.cache.ffn
+            model.eval()
+        else:
+            self.cache = None
+            self.ffn = find_ffn_modules(model, layer_filter=cache_kwargs.get("layer_filter"))
+
+    @torch.no_grad()
+    def extract(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
+                **kwargs) -> Dict[int, FFNActivation]:
+        assert self.cache is not None, "extract() belongs to the form without a callback"
+        self.cache.clear()
+        if attention_mask is not None:
+            kwargs["attention_mask"] = attention_mask
+        self.model(input_ids, **kwargs)
+        return self.cache.get_activations()
+
+    @property
+    def n_layers(self) -> int:
+        return len(self.ffn)
+
+    @property
+    def layer_indices(self) -> List[int]:
+        return self.cache.layer_indices if self.cache is not None else list(range(len(self.ffn)))
+
+    def close(self) -> None:
+        if self.cache is not None:
+            self.cache.remove_hooks()
+        for h in self._handles:
+            h.remove()
         self._handles = []
 
     def __enter__(self):
-        for i, (_, mod) in enumerate(self.ffn):
-            self._handles.append(mod.register_forward_hook(
-                lambda m, inp, out, i=i: self.fn(i, inp[0].detach(), (out[0] if isinstance(out, tuple) else out).detach())))
+        if self.fn is not None:
+            for i, (_, mod) in enumerate(self.ffn):
+                self._handles.append(mod.register_forward_hook(
+                    lambda m, inp, out, i=i: self.fn(i, inp[0].detach(),
+                                                     (out[0] if isinstance(out, tuple) else out).detach())))
         return self
 
     def __exit__(self, *exc):
-        for h in self._handles:
-            h.remove()
+        self.close()
         return False
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

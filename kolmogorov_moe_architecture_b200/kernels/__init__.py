@@ -47,9 +47,25 @@ def grouped_swiglu_forward(sorted_inputs, W1, W2, W3, sorted_expert_ids, seg_sta
     return grouped_swiglu_forward_pytorch(sorted_inputs, W1, W2, W3, sorted_expert_ids, seg_starts, seg_ends)
 
 
-class GroupedSwiGLUFunction:
-    """Kept for callers that used ``GroupedSwiGLUFunction.apply``."""
+class GroupedSwiGLUFunction(torch.autograd.Function):
+    """``GroupedSwiGLUFunction.apply(sorted_inputs, W1, W2, W3, sorted_expert_ids, seg_starts, seg_ends)`` for
+    callers of the reference's autograd wrapper (moe_arch/kernels/__init__.py:140-225, whose backward is a Python
+    loop of seven matmuls per expert).  Forward and backward both run the differentiable grouped path of
+    ``grouped_swiglu_with_grad``: the forward records that path's own graph, the backward asks it for the gradients
+    of the inputs and the three weight stacks."""
 
     @staticmethod
-    def apply(sorted_inputs, W1, W2, W3, sorted_expert_ids, seg_starts=None, seg_ends=None):
-        return grouped_swiglu_with_grad(sorted_inputs, W1, W2, W3, sorted_expert_ids, seg_starts, seg_ends)
+    def forward(ctx, sorted_inputs, W1, W2, W3, sorted_expert_ids, seg_starts=None, seg_ends=None):
+        with torch.enable_grad():
+            leaves = [t.detach().requires_grad_(t.requires_grad) for t in (sorted_inputs, W1, W2, W3)]
+            out = grouped_swiglu_with_grad(*leaves, sorted_expert_ids)
+        ctx.leaves, ctx.out = leaves, out
+        return out.detach()
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        need = [t for t in ctx.leaves if t.requires_grad]
+        got = iter(torch.autograd.grad(ctx.out, need, grad_out) if need else ())
+        grads = [next(got) if t.requires_grad else None for t in ctx.leaves]
+        ctx.leaves = ctx.out = None
+        return (*grads, None, None, None)

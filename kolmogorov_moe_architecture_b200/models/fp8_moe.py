@@ -82,3 +82,33 @@ class FP8MoELayer(nn.Module):
         if self.training:
             self.aux_loss = eager.moe_aux_loss(logits, idx, self.n_experts, 0.01, 0.0)
         return self.experts(flat, idx, w.to(flat.dtype)).view(shape)
+
+
+def benchmark_fp8_vs_bf16(n_experts: int = 16, d_model: int = 1024, d_ff: int = 2048, n_tokens: int = 8192,
+                          top_k: int = 2, n_iters: int = 20, device=None):
+    """Block-scaled fp8 experts against the same experts in bf16, forward and forward + backward (reference:
+    moe_arch/model/fp8_moe.py:341-394, whose fp8 path is simulated in bf16).  Needs a GPU with the library loaded;
+    returns the milliseconds per call, or None where fp8 is unavailable."""
+    from ._bench import default_device, report, routed_inputs, time_ms
+    from .sparse_moe import SparseGroupedExpertsPyTorch
+    device = device or default_device()
+    if not (str(device).startswith("cuda") and is_fp8_available()):
+        print("block-scaled fp8 needs a GPU with this library's kernels: nothing to compare")
+        return None
+    x, idx, w = routed_inputs(n_tokens, d_model, n_experts, top_k, device, torch.bfloat16)
+    bf16 = SparseGroupedExpertsPyTorch(n_experts, d_model, d_ff).to(device).bfloat16()
+    fp8 = FP8GroupedExperts(n_experts, d_model, d_ff).to(device).bfloat16()
+    with torch.no_grad():
+        for a, b in zip(fp8.parameters(), bf16.parameters()):
+            a.copy_(b)
+    times = {}
+    for name, mod in (("bf16", bf16), ("mxfp8", fp8)):
+        with torch.no_grad():
+            times[f"{name} forward"] = time_ms(lambda: mod(x, idx, w), device, iters=n_iters)
+        xs = x.detach().requires_grad_(True)
+        times[f"{name} forward+backward"] = time_ms(lambda: mod(xs, idx, w).sum().backward(), device, iters=n_iters)
+    with torch.no_grad():
+        rel = float((fp8(x, idx, w).float() - bf16(x, idx, w).float()).norm() / bf16(x, idx, w).float().norm())
+    print(f"relative difference of the outputs: {rel:.4f}")
+    return report(f"{n_experts} experts, d_model {d_model}, d_ff {d_ff}, {n_tokens} tokens, top-{top_k}", times,
+                  "bf16 forward")

@@ -52,3 +52,24 @@ class FusedSparseMoE(nn.Module):
         if self.training:
             self.aux_loss = ops.moe_aux_loss(logits, idx, self.n_experts, 0.01, 0.001)
         return ops.grouped_swiglu(flat, self.w1, self.w2, self.w3, idx, w).view(shape)
+
+
+def benchmark_fused_vs_original(d_model: int = 512, d_ff: int = 1024, n_experts: int = 16, top_k: int = 2,
+                                batch: int = 2, seq_len: int = 1024, n_iters: int = 20, device=None):
+    """``FusedSparseMoE`` against ``MoELayer`` at the reference's shape (moe_arch/model/fused_moe.py:448-496):
+    forward time of both on the same input."""
+    from ..config import AdvancedMoEConfig
+    from ._bench import default_device, report, time_ms
+    from .moe import MoELayer
+    device = device or default_device()
+    dtype = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
+    cfg = AdvancedMoEConfig(d_model=d_model, d_ff_expert=d_ff, n_experts=n_experts, moe_top_k=top_k, n_layers=4,
+                            n_heads=max(d_model // 64, 1), n_kv_heads=max(d_model // 128, 1), head_dim=64,
+                            moe_layers=(0,), mamba_enabled=False, mamba_layers=(), vocab_size=1000)
+    original = MoELayer(cfg, layer_idx=0).to(device).to(dtype).eval()
+    fused = FusedSparseMoE(d_model, d_ff, n_experts, top_k).to(device).to(dtype).eval()
+    x = torch.randn(batch, seq_len, d_model, generator=torch.Generator().manual_seed(0)).to(device=device, dtype=dtype)
+    with torch.no_grad():
+        times = {"MoELayer": time_ms(lambda: original(x), device, iters=n_iters),
+                 "FusedSparseMoE": time_ms(lambda: fused(x), device, iters=n_iters)}
+    return report(f"{n_experts} experts, d_model {d_model}, d_ff {d_ff}, {batch} x {seq_len} tokens", times, "MoELayer")

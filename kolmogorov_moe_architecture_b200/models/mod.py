@@ -57,3 +57,29 @@ class MoDRouter(nn.Module):
         sorted_idx, weights, topk_idx = ops.mod_route(logits, k)
         self.aux_loss = self._predictor_loss(hidden_states, topk_idx, logits) if self.training else 0.0
         return sorted_idx, weights, logits, topk_idx
+
+
+class MoDLayer(nn.Module):
+    """Any layer under mixture-of-depths routing: the router keeps ``k`` positions per sequence, only those go
+    through ``layer_module`` and come back weighted by the router; the other positions pass unchanged
+    (``out = x`` there, ``out = x + w * layer(x_kept)`` at kept positions - the rule ``TransformerBlock`` applies to
+    its FFN half).  In the reference this wrapper is stale (it unpacks three of the router's four results and
+    overwrites the kept rows instead of adding to them, moe_arch/model/mod.py:174-234); this one follows the block's
+    rule and exposes the router's auxiliary loss as ``aux_loss``.  At evaluation the layer runs on every position,
+    as in the block."""
+
+    def __init__(self, config, layer_module: nn.Module):
+        super().__init__()
+        self.config = config
+        self.layer = layer_module
+        self.router = MoDRouter(config)
+        self.aux_loss = 0.0
+
+    def forward(self, hidden_states: torch.Tensor, **layer_kwargs) -> torch.Tensor:
+        if not self.training:
+            self.aux_loss = 0.0
+            return hidden_states + self.layer(hidden_states, **layer_kwargs)
+        picked, idx, weights = self.router.route_and_gather(hidden_states)
+        self.aux_loss = self.router.aux_loss
+        processed = self.layer(picked, **layer_kwargs)
+        return ops.mod_combine(hidden_states, processed, weights, idx)

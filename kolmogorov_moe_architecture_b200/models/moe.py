@@ -259,3 +259,17 @@ class MoELayer(nn.Module):
         if self.last_drop_count is not None:
             out["dropped"] = float(self.last_drop_count)
         return out
+
+
+class Expert(nn.Module):
+    """One expert as a module of its own: ``ExpertFFN(d_model, d_ff_expert)`` on (n_tokens, d_model) rows
+    (reference: moe_arch/model/moe.py:297-324).  The layers of this framework keep their experts stacked in
+    ``GroupedExperts``; this class is for code that builds or inspects a single expert."""
+
+    def __init__(self, config):
+        super().__init__()
+        from .ffn import ExpertFFN
+        self.expert_ffn = ExpertFFN(config.d_model, config.d_ff_expert, config.ffn_activation, config.dropout)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.expert_ffn(x)

@@ -139,3 +139,29 @@ class ExpertParallelMoE(nn.Module):
         out = expert_parallel_ffn(xf, idx, w, self.local_experts, self.n_experts,
                                   self.process_group, keep=keep)
         return out.reshape(B, S, d)
+
+
+def benchmark_sparse_vs_batched(n_experts: int = 64, d_model: int = 2048, d_ff: int = 1536, n_tokens: int = 8192,
+                                top_k: int = 2, n_iters: int = 20, device=None):
+    """``SparseGroupedExpertsPyTorch`` against ``BatchedMoEOptimized`` with the same weights: agreement of the
+    outputs and forward time (reference: moe_arch/model/sparse_moe.py:694-789, at d_ff 1524; 1536 here: the
+    kernels take widths that are multiples of 64).  In this framework both names run the grouped kernel, so the
+    figures also show that the two entry points cost the same."""
+    import torch
+    from ._bench import default_device, report, routed_inputs, time_ms
+    from .triton_moe import BatchedMoEOptimized
+    device = device or default_device()
+    dtype = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
+    x, idx, w = routed_inputs(n_tokens, d_model, n_experts, top_k, device, dtype)
+    sparse = SparseGroupedExpertsPyTorch(n_experts, d_model, d_ff).to(device).to(dtype)
+    batched = BatchedMoEOptimized(n_experts, d_model, d_ff).to(device).to(dtype)
+    with torch.no_grad():
+        for a, b in zip(batched.parameters(), sparse.parameters()):
+            a.copy_(b)
+        diff = float((sparse(x, idx, w).float() - batched(x, idx, w).float()).abs().max())
+        times = {"batched": time_ms(lambda: batched(x, idx, w), device, iters=n_iters),
+                 "sparse": time_ms(lambda: sparse(x, idx, w), device, iters=n_iters)}
+    print(f"max |sparse - batched| = {diff:.6f}")
+    times = report(f"{n_experts} experts, d_model {d_model}, d_ff {d_ff}, {n_tokens} tokens, top-{top_k}", times, "batched")
+    times["max_diff"] = diff
+    return times

@@ -35,3 +35,30 @@ class BatchedMoE(GroupedExperts):
 
 class BatchedMoEOptimized(GroupedExperts):
     pass
+
+
+def benchmark_moe_implementations(n_experts: int = 110, d_model: int = 2048, d_ff: int = 1024, n_tokens: int = 16384,
+                                  top_k: int = 2, n_iters: int = 20, device=None):
+    """Forward time of the four expert classes of this module on one routed batch, and their agreement (reference:
+    moe_arch/model/triton_moe.py:709-799, where they are four different implementations; here they share the
+    grouped kernel and differ in name only, which the equal times show)."""
+    import torch
+    from ._bench import default_device, report, routed_inputs, time_ms
+    device = device or default_device()
+    dtype = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
+    x, idx, w = routed_inputs(n_tokens, d_model, n_experts, top_k, device, dtype)
+    mods = {c.__name__: c(n_experts, d_model, d_ff).to(device).to(dtype)
+            for c in (BatchedMoE, BatchedMoEOptimized, TritonGroupedExperts, TritonGroupedExpertsFused)}
+    base = mods["BatchedMoE"]
+    times, diffs = {}, {}
+    with torch.no_grad():
+        ref = base(x, idx, w).float()
+        for name, m in mods.items():
+            for a, b in zip(m.parameters(), base.parameters()):
+                a.copy_(b)
+            diffs[name] = float((m(x, idx, w).float() - ref).abs().max())
+            times[name] = time_ms(lambda m=m: m(x, idx, w), device, iters=n_iters)
+    print("max |difference| to BatchedMoE:", {k: round(v, 6) for k, v in diffs.items()})
+    times = report(f"{n_experts} experts, d_model {d_model}, d_ff {d_ff}, {n_tokens} tokens, top-{top_k}", times, "BatchedMoE")
+    times["max_diff"] = max(diffs.values())
+    return times

@@ -222,3 +222,68 @@ def test_block_annotations_open_a_range_per_block_and_direction():
     ann.remove()
     model(ids, labels=ids, return_logits=False)["loss"].backward()
     assert ann.events == {"forward": 3 * L, "backward": L}
+
+
+def test_module_level_benchmarks_and_single_modules_of_the_reference_api():
+    """``moe_arch.model.*`` exposes, beside the layer classes, one benchmark function per variant module, the
+    ``MoDLayer`` wrapper and the single ``Expert``; ``moe_arch.kernels`` has its benchmark harness and build
+    helpers.  All of them run on the CPU at small sizes."""
+    import torch
+    from moe_arch.kernels.benchmark import benchmark, create_test_data, verify_correctness
+    from moe_arch.kernels.setup import get_cuda_arch_flags, get_gpu_arch
+    from moe_arch.model.config import AdvancedMoEConfig
+    from moe_arch.model.fp8_moe import benchmark_fp8_vs_bf16
+    from moe_arch.model.fused_moe import benchmark_fused_vs_original
+    from moe_arch.model.mod import MoDLayer
+    from moe_arch.model.moe import Expert
+    from moe_arch.model.sparse_moe import benchmark_sparse_vs_batched
+    from moe_arch.model.triton_moe import benchmark_moe_implementations
+    kw = dict(n_experts=4, d_model=32, d_ff=64, n_tokens=48, top_k=2, n_iters=1, device="cpu")
+    t = benchmark_sparse_vs_batched(**kw)
+    assert t["max_diff"] < 1e-5 and t["sparse"] > 0 and t["batched"] > 0
+    t = benchmark_moe_implementations(**kw)
+    assert t["max_diff"] < 1e-5 and {"BatchedMoE", "TritonGroupedExpertsFused"} <= set(t)
+    t = benchmark_fused_vs_original(d_model=64, d_ff=64, n_experts=4, top_k=2, batch=2, seq_len=8, n_iters=1, device="cpu")
+    assert set(t) == {"MoELayer", "FusedSparseMoE"}
+    assert benchmark_fp8_vs_bf16(device="cpu") is None            # block-scaled fp8 exists on the GPU only
+    data = create_test_data(4, 32, 64, 40, 2, device="cpu")
+    assert data[0].shape == (80, 32) and bool((data[4][1:] >= data[4][:-1]).all()) and int(data[6][-1]) == 80
+    assert verify_correctness(*data) and benchmark(*data, n_warmup=1, n_iters=1)["pytorch_ms"] > 0
+    assert get_cuda_arch_flags() == ["-gencode", "arch=compute_100a,code=sm_100a"] and get_gpu_arch() is None
+    # MoDLayer: kept positions get x + w * layer(x), the others pass unchanged; evaluation runs every position
+    cfg = AdvancedMoEConfig(vocab_size=100, d_model=32, n_layers=2, n_heads=2, n_kv_heads=1, head_dim=16, d_ff=64,
+                            d_ff_expert=32, n_experts=4, moe_layers=(1,), mamba_layers=(), max_seq_len=16,
+                            mod_capacity_factor=0.5, dropout=0.0, device="cpu", dtype="float32")
+    torch.manual_seed(0)
+    layer = MoDLayer(cfg, torch.nn.Linear(32, 32))
+    x = torch.randn(2, 16, 32)
+    layer.train()
+    y = layer(x)
+    idx, w, _, _ = layer.router(x)
+    changed = (y != x).any(-1)
+    assert changed.sum(1).tolist() == [8, 8] and torch.equal(changed.nonzero()[:, 1].view(2, 8), idx)
+    want = x[0, idx[0]] + w[0, :, None] * layer.layer(x[0, idx[0]])
+    assert torch.allclose(y[0, idx[0]], want, atol=1e-6) and torch.is_tensor(layer.aux_loss)
+    layer.eval()
+    assert torch.allclose(layer(x), x + layer.layer(x)) and layer.aux_loss == 0.0
+    e = Expert(cfg)
+    assert e(torch.randn(5, 32)).shape == (5, 32) and {n for n, _ in e.named_parameters()} == {
+        "expert_ffn.ffn.w1.weight", "expert_ffn.ffn.w2.weight", "expert_ffn.ffn.w3.weight"}
+
+
+def test_grouped_swiglu_function_matches_the_differentiable_path():
+    import torch
+    from moe_arch.kernels import GroupedSwiGLUFunction, grouped_swiglu_with_grad
+    from moe_arch.kernels.benchmark import create_test_data
+    x, w1, w2, w3, ids, s0, s1 = create_test_data(3, 16, 32, 20, 2, device="cpu")
+    a = [t.clone().requires_grad_(True) for t in (x, w1, w2, w3)]
+    b = [t.clone().requires_grad_(True) for t in (x, w1, w2, w3)]
+    ya = GroupedSwiGLUFunction.apply(*a, ids, s0, s1)
+    yb = grouped_swiglu_with_grad(*b, ids)
+    g = torch.randn_like(ya)
+    ya.backward(g)
+    yb.backward(g)
+    assert torch.allclose(ya, yb, atol=1e-6)
+    assert all(torch.allclose(p.grad, q.grad, atol=1e-6) for p, q in zip(a, b))
+    frozen = GroupedSwiGLUFunction.apply(x.clone().requires_grad_(True), w1, w2, w3, ids)      # weights without gradients
+    frozen.sum().backward()

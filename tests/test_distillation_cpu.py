@@ -262,3 +262,57 @@ def test_balanced_routing_brings_unused_experts_into_use():
     bal = layer._last_expert_counts
     assert free.tolist() == [48, 48, 0, 0]
     assert int(bal.sum()) == 96 and int((bal == 0).sum()) == 0 and out.shape == x.shape
+
+
+def test_reference_names_of_hooks_wrapper_and_helpers():
+    """The reference's spellings work: ``Experiments.sparse_distillation`` import path, ``register_hooks`` /
+    ``get_activations`` / ``FFNActivation``, ``StreamingFFNExtractor.extract``, ``SparseModelWrapper.base_model`` /
+    ``moe_layers`` / ``n_experts`` / ``get_active_parameters``, the loss helpers and ``freeze_non_moe_layers``."""
+    import Experiments.sparse_distillation as ES
+    from Experiments.sparse_distillation.finetune_eval import (compute_load_balancing_loss, compute_z_loss,
+                                                               freeze_non_moe_layers)
+    from Experiments.sparse_distillation.hooks import FFNActivation, StreamingFFNExtractor
+    assert ES.SparseDistillationTrainer is SparseDistillationTrainer and ES.FFNActivationCache is FFNActivationCache
+    torch.manual_seed(0)
+    m = ToyLM().eval()
+    ids = torch.randint(0, 256, (2, 12))
+    cache = FFNActivationCache(m)
+    cache.register_hooks()
+    with torch.no_grad():
+        m(ids)
+    acts = cache.get_activations()
+    cache.remove_hooks()
+    assert cache.layer_indices == [0, 1] and set(acts) == {0, 1} and isinstance(acts[0], FFNActivation)
+    with torch.no_grad():
+        assert torch.allclose(m.blocks[1].mlp(acts[1].input), acts[1].output, atol=1e-6)
+    assert cache.get_layer_activation(1).layer_idx == 1 and cache.get_layer_activation(7) is None
+    only_first = FFNActivationCache(m, layer_filter=lambda name, mod: name == "blocks.0.mlp")
+    assert [n for n, _ in only_first.ffn] == ["blocks.0.mlp"]
+    ex = StreamingFFNExtractor(m)
+    got = ex.extract(ids)
+    assert ex.n_layers == 2 and ex.layer_indices == [0, 1] and torch.equal(got[0].input, acts[0].input)
+    ex.close()
+    with torch.no_grad():
+        m(ids)                                   # hooks are gone: nothing is recorded any more
+    seen = []
+    with StreamingFFNExtractor(m, lambda i, x, y: seen.append((i, tuple(x.shape)))):
+        with torch.no_grad():
+            m(ids)
+    assert seen == [(0, (2, 12, 64)), (1, (2, 12, 64))]
+    tr = SparseDistillationTrainer(dense_model=m, config=_cfg(), device="cpu")
+    wrapper = convert_to_sparse(dense_model=m, trainer=tr)
+    assert wrapper.base_model is m and wrapper.n_experts == _cfg().n_experts
+    assert set(wrapper.moe_layers.keys()) == {"0", "1"} and len(list(wrapper.parameters())) == len(list(m.parameters()))
+    total = sum(p.numel() for p in m.parameters())
+    experts = sum(p.numel() for l in wrapper.moe_layers.values() for p in l.experts.parameters())
+    k, E = _cfg().moe_top_k, _cfg().n_experts
+    assert wrapper.get_active_parameters() == int(total - experts * (1 - k / E))
+    assert wrapper.get_active_parameters(top_k=E) == total
+    logits, counts = torch.zeros(6, 4), torch.tensor([3, 3, 3, 3])
+    assert abs(float(compute_load_balancing_loss(logits, counts)) - 1.0) < 1e-6      # uniform: E * sum (1/E)(1/E) = 1
+    assert abs(float(compute_z_loss(logits)) - torch.log(torch.tensor(4.0)).pow(2).item()) < 1e-6
+    kept = freeze_non_moe_layers(wrapper, moe_only=True)
+    names = {n for n, p in wrapper.named_parameters() if p.requires_grad}
+    assert kept and all(("experts" in n or "router" in n or "expert_bias" in n or "norm" in n) for n in names)
+    assert not any(n.endswith("emb.weight") or n.endswith("head.weight") for n in names)
+    assert len(freeze_non_moe_layers(wrapper, moe_only=False)) == len(list(wrapper.parameters()))
