@@ -24,6 +24,15 @@ def main(argv=None):
     else:
         cfg = {"3b": kmoe.get_3b_config, "5b": kmoe.get_5b_config, "test": kmoe.get_test_config,
                "bench": kmoe.get_bench_5b_config}[a.preset]()
+    return analyze_config(cfg, a.config or a.preset)
+
+
+def analyze_config(cfg, name: str = ""):
+    """Totals, active parameters and the per-layer-kind breakdown of one configuration (counted on a meta-device
+    instance); prints the report and returns the counts."""
+    import kolmogorov_moe_architecture_b200 as kmoe
+    if name:
+        print(f"== {name}")
     with torch.device("meta"):
         m = kmoe.MoETransformer(cfg, verbose=False)
     c = m.count_parameters()

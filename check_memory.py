@@ -53,5 +53,21 @@ def main(argv=None):
     return rows
 
 
+# ---- names of the reference's script, for code that imports them from here
+def load_config(path):
+    """The YAML file as a dict."""
+    from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml
+    return load_yaml(path)
+
+
+def print_memory(step, label):
+    """One line with the allocated / reserved / peak GiB at this point; returns the row."""
+    rows = []
+    snapshot(f"{step}:{label}", rows)
+    tag, alloc, reserved, peak = rows[0]
+    print(f"[{tag}] allocated {alloc:.2f} GiB  reserved {reserved:.2f} GiB  peak {peak:.2f} GiB")
+    return rows[0]
+
+
 if __name__ == "__main__":
     main()

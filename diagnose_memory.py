@@ -132,5 +132,22 @@ def main(argv=None):
     return {"growth_mb_per_step": slope * 1000, "leak": leaking, "containers": found, "opt_steps": len(after_opt)}
 
 
+# ---- names of the reference's script, for code that imports them from here
+def load_config(path):
+    """The YAML file as a dict."""
+    from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml
+    return load_yaml(path)
+
+
+def get_mem():
+    """(allocated, reserved) in GB."""
+    a, r, _ = mem()
+    return a, r
+
+
+def print_mem(label, prev_alloc=None):
+    return show(label, prev_alloc)
+
+
 if __name__ == "__main__":
     main()

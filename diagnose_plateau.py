@@ -34,7 +34,7 @@ class RouterAnalyzer:
                 E = logits.shape[-1]
                 c = torch.bincount(idx.flatten(), minlength=E).float().cpu()
                 s["counts"] = c if s["counts"] is None else s["counts"] + c
-                s["max_prob"] += float(torch.softmax(logits.float(), -1).max(-1).values.mean())
+                s["max_prob"] += float(torch.softmax(logits.detach().float(), -1).max(-1).values.mean())
         return fn
 
     def report(self):
@@ -93,6 +93,32 @@ def main(argv=None):
     for note in lint_config(cfg):
         print("config:", note)
     return rep
+
+
+# ---- names of the reference's script, for code that imports them from here
+def load_config(path):
+    """The YAML file as a dict."""
+    from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml
+    return load_yaml(path)
+
+
+def create_model_from_config(config_dict):
+    """(model, model configuration) from a configuration dict (its ``model:`` section, read with defaults)."""
+    from kolmogorov_moe_architecture_b200 import MoETransformer
+    from kolmogorov_moe_architecture_b200.utils.config_io import model_config_tolerant
+    cfg = model_config_tolerant(config_dict)
+    return MoETransformer(cfg, verbose=False), cfg
+
+
+def analyze_gradients(model):
+    """Gradient statistics per parameter group after a backward pass."""
+    from kolmogorov_moe_architecture_b200.utils.fault import gradient_census
+    return gradient_census(model)
+
+
+RouterAnalyzer.register_hooks = lambda self: self          # the hooks are registered by the constructor
+RouterAnalyzer.remove_hooks = RouterAnalyzer.close
+RouterAnalyzer.get_stats = RouterAnalyzer.report
 
 
 if __name__ == "__main__":

@@ -152,5 +152,19 @@ def main(argv=None):
     return results
 
 
+# ---- names of the reference's script, for code that imports them from here
+def load_config(path):
+    """The YAML file as a dict."""
+    from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml
+    return load_yaml(path)
+
+
+def load_model_from_checkpoint(checkpoint_path, config_path, device="cuda"):
+    """(model, model configuration) with the checkpoint's weights, in evaluation mode."""
+    model, cfg = load_model(checkpoint_path, config_path, device,
+                            dtype=torch.bfloat16 if str(device).startswith("cuda") else torch.float32)
+    return model.eval(), cfg
+
+
 if __name__ == "__main__":
     main()

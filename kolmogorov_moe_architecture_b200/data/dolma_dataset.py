@@ -295,3 +295,7 @@ class ThreadedPrefetcher(PinnedPrefetcher):
 
     def __next__(self):
         return self._to_device(super().__next__())
+
+    def stop(self):
+        """End the producer thread and drop what it has staged (the reference's name for ``close``)."""
+        self.close()

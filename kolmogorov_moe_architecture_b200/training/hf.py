@@ -80,3 +80,74 @@ def make_hf_classes():
             return (out["loss"], out) if return_outputs else out["loss"]
 
     return MoETrainer, TrueLossLoggingCallback
+
+
+class OnTheFlyDataCollator:
+    """Collator for raw-text examples: tokenises ``example["text"]`` per batch (truncated and padded to
+    ``max_length``) and sets ``labels = input_ids``, padding positions masked with -100 so they are not scored
+    (reference: train_production.py:76-104, which scores the padding as well)."""
+
+    def __init__(self, tokenizer, max_length: int):
+        self.tokenizer, self.max_length = tokenizer, max_length
+
+    def __call__(self, examples):
+        batch = self.tokenizer([e["text"] for e in examples], truncation=True, max_length=self.max_length,
+                               padding="max_length", return_tensors="pt")
+        batch = dict(batch)
+        labels = batch["input_ids"].clone()
+        if "attention_mask" in batch:
+            labels = labels.masked_fill(batch["attention_mask"] == 0, -100)
+        batch["labels"] = labels
+        return batch
+
+
+def load_and_prepare_dataset(config: dict, tokenizer, split: str = "train"):
+    """The ``data:`` section's data set for the HF loop: raw text rows for on-the-fly tokenisation
+    (``data.tokenize_on_fly``) or rows tokenised up front to at most ``model.max_seq_len`` tokens, empty documents
+    dropped, limited to ``data.max_examples``; a streaming data set is collected into memory first.  Without the
+    ``datasets`` package or network access: a synthetic data set of random token rows, announced on stdout."""
+    data = config.get("data") or {}
+    max_len = int((config.get("model") or {}).get("max_seq_len", 2048))
+    max_examples = data.get("max_examples")
+    streaming = bool(data.get("use_streaming", False))
+    on_fly = bool(data.get("tokenize_on_fly", False))
+    try:
+        import os
+        if os.environ.get("HF_HUB_OFFLINE") == "1" or os.environ.get("KMOE_OFFLINE") == "1":
+            raise RuntimeError("offline")
+        from datasets import Dataset, load_dataset
+        ds = load_dataset(data["dataset_name"], name=data.get("dataset_config"), split=split, streaming=streaming)
+    except Exception as e:
+        print(f"[data] {data.get('dataset_name')} unavailable ({type(e).__name__}); synthetic rows instead")
+        return SyntheticRows(int((config.get("model") or {}).get("vocab_size", 50257)), max_len, int(max_examples or 1024))
+    if streaming:
+        rows = []
+        for ex in ds:
+            if ex.get("text", "").strip():
+                rows.append(ex)
+            if max_examples and len(rows) >= max_examples:
+                break
+        ds = Dataset.from_list(rows)
+    else:
+        if max_examples:
+            ds = ds.select(range(min(int(max_examples), len(ds))))
+        ds = ds.filter(lambda ex: ex.get("text", "").strip() != "")
+    if on_fly:
+        return ds
+    tok = ds.map(lambda ex: tokenizer(ex["text"], truncation=True, max_length=max_len, padding=False), batched=True,
+                 remove_columns=ds.column_names)
+    return tok.filter(lambda ex: len(ex["input_ids"]) > 0)
+
+
+class SyntheticRows(torch.utils.data.Dataset):
+    """Random token rows with ``labels = input_ids`` (what the loaders fall back to without a data set)."""
+
+    def __init__(self, vocab_size: int, seq_len: int, n: int, seed: int = 1234):
+        g = torch.Generator().manual_seed(seed)
+        self.rows = torch.randint(1, vocab_size, (n, seq_len), generator=g)
+
+    def __len__(self):
+        return self.rows.shape[0]
+
+    def __getitem__(self, i):
+        return {"input_ids": self.rows[i], "labels": self.rows[i].clone()}

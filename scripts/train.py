@@ -10,6 +10,8 @@ import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
+from kolmogorov_moe_architecture_b200.training.script_api import load_config  # noqa: E402,F401
+
 
 def main(argv=None):
     ap = argparse.ArgumentParser()

@@ -318,3 +318,149 @@ def test_debug_mode_profile_phases_and_token_weighting(tiny_cfg, capsys):
     plain, weighted = _records(os.path.join(base, "a.jsonl")), _records(os.path.join(base, "b.jsonl"))
     assert weighted[1]["loss"] != pytest.approx(plain[1]["loss"], rel=1e-6)
     assert abs(weighted[1]["loss"] - plain[1]["lm_loss"]) < 1.0      # still a next-token loss near ln(vocab)
+
+
+def test_script_level_helpers_of_the_reference_work_on_this_framework(tmp_path, monkeypatch):
+    """Code that imports the helpers the reference's scripts define (``from train_distributed import
+    create_model, wrap_model_with_fsdp, create_optimizer, create_scheduler, train_step`` and so on) keeps
+    working: a few steps under the parameter-sharded plan and under a plain optimizer, schedule landmarks,
+    checkpoints, diagnostics, token weights, timing."""
+    import math
+    import yaml
+    monkeypatch.setenv("KMOE_OFFLINE", "1")
+    import train as t1
+    import train_custom as tc
+    import train_distributed as td
+    cfg = {"model": dict(vocab_size=128, d_model=32, n_layers=2, n_heads=2, n_kv_heads=1, head_dim=16, d_ff=64,
+                         d_ff_expert=32, n_experts=4, moe_top_k=2, moe_layers=[1], mamba_enabled=False,
+                         mamba_layers=[], mod_enabled=False, max_seq_len=16, n_pred_tokens=2,
+                         aux_loss_weights=[1.0, 0.5], moe_implementation="batched"),
+           "training": dict(max_lr=1e-2, warmup_steps=2, min_lr_ratio=0.1, batch_size=2),
+           "optimizer": dict(type="adamw", weight_decay=0.1), "data": dict(tokenizer_name="gpt2")}
+    path = tmp_path / "c.yaml"
+    path.write_text(yaml.safe_dump(cfg))
+    assert td.load_config(str(path))["model"]["d_model"] == 32 and t1.load_config(str(path)) == td.load_config(str(path))
+    rank, world, local = td.setup_distributed()
+    assert (rank, world, local) == (0, 1, 0) and tc.is_main_process()
+    torch.manual_seed(0)
+    model, mcfg = td.create_model(cfg, rank, world)
+    assert mcfg.d_model == 32 and sum(p.numel() for p in model.parameters()) > 0
+    loader = td.create_dataloader(cfg, td.load_tokenizer(cfg), 16, 2, rank, world)
+    batch = next(iter(loader))
+    assert batch["input_ids"].shape == (2, 16) and torch.equal(batch["input_ids"], batch["labels"])
+    # plain optimizer: decay / no-decay groups, warm-up then cosine to the floor
+    opt = td.create_optimizer(model, cfg)
+    assert [g["weight_decay"] for g in opt.param_groups] == [0.1, 0.0]
+    no_decay = {id(p) for p in opt.param_groups[1]["params"]}
+    assert all(("norm" in n or "embedding" in n or "bias" in n) == (id(p) in no_decay) for n, p in model.named_parameters())
+    sched = td.create_scheduler(opt, cfg, total_steps=10)
+    lrs = []
+    losses = []
+    for step in range(10):
+        lrs.append(sched.get_last_lr()[0])
+        m = td.train_step(model, batch, opt, sched, grad_clip=1.0, accumulation_steps=2, step=step, debug=(step == 1))
+        losses.append(m["loss"])
+    assert lrs[0] == 0.0 and lrs[1] == 0.0 and lrs[2] == pytest.approx(5e-3)        # two calls per optimizer step
+    assert sched.last_step == 5 and sched.factor(10) == pytest.approx(0.1) and sched.factor(2) == pytest.approx(1.0)
+    assert losses[-1] < losses[0] and "grad_norm" in m
+    stats = td.collect_router_stats(model, batch)
+    assert stats and all(0.0 <= s["entropy"] <= 1.0 for s in stats.values())
+    census = td.check_parameter_gradients(model, 0, 0)
+    assert "census" in census and "flow" in census
+    # the same calls with the model under the parameter-sharded plan (one rank: the shard is the whole unit)
+    torch.manual_seed(0)
+    m2, _ = td.create_model(cfg, 0, 1)
+    m2 = td.wrap_model_with_fsdp(m2, 0, use_bf16=False, cpu_offload=False, activation_checkpointing=False)
+    opt2 = td.create_optimizer(m2, cfg)
+    assert opt2 is m2._kmoe_plan.optimizer and opt2.param_groups[0]["lr"] == 1e-2
+    sched2 = td.create_scheduler(opt2, cfg, total_steps=8)
+    first = last = None
+    for step in range(8):
+        out = td.train_step(m2, batch, opt2, sched2, grad_clip=1.0, accumulation_steps=1, step=step)
+        first = out["loss"] if first is None else first
+        last = out["loss"]
+    assert last < first and sched2.last_step == 8
+    # checkpoints in train_custom's directory layout, for both kinds of model
+    d = tc.save_checkpoint(model, opt, sched, 5, checkpoint_dir=str(tmp_path / "ck"))
+    assert sorted(os.listdir(d)) == ["model.pt", "optimizer.pt", "training_state.pt"]
+    before = {k: v.clone() for k, v in model.state_dict().items()}
+    with torch.no_grad():
+        next(model.parameters()).add_(1.0)
+    assert tc.load_checkpoint(model, opt, sched, d) == 5
+    assert all(torch.equal(v, model.state_dict()[k]) for k, v in before.items())
+    d2 = tc.save_checkpoint(m2, opt2, sched2, 8, checkpoint_dir=str(tmp_path / "ck2"))
+    full = torch.load(os.path.join(d2, "model.pt"))
+    assert set(full) == set(model.state_dict()) and tc.load_checkpoint(m2, opt2, sched2, d2) == 8
+    assert set(t1.get_model_state_dict(m2)) == set(full)
+    # train.py's single-file checkpoint and cache path
+    st = {"model": model, "optimizer": opt, "step": 7, "epoch": 0, "data_idx": 3, "losses": [1.0, 0.5],
+          "total_tokens": 99, "config_path": str(path), "checkpoint_saved": False}
+    assert t1.save_checkpoint(st, str(tmp_path / "b" / "checkpoint-7.pt"), reason="test") and st["checkpoint_saved"]
+    ck = torch.load(tmp_path / "b" / "checkpoint-7.pt", weights_only=False)
+    assert ck["step"] == 7 and ck["data_idx"] == 3 and "model_state_dict" in ck
+    assert not t1.save_checkpoint({"model": None}, str(tmp_path / "none.pt"))
+    p1, p2 = t1.get_cache_path("a/b", 128, 1000, True), t1.get_cache_path("a/b", 256, 1000, True)
+    assert p1 != p2 and p1.endswith(".pt") and "packed" in p1
+    stats_, collapsed, summary = t1.check_router_collapse_fast(model, "cpu", 0.7)
+    assert isinstance(summary, str) and isinstance(collapsed, list)
+    # token weights, weighted loss, evaluation, timing, scheduler with absolute rates, prefetcher, configuration
+    w = tc.compute_token_weights(8, 0.5)
+    assert w.mean().item() == pytest.approx(1.0) and w[-1] > w[0] and torch.equal(tc.compute_token_weights(4, 0), torch.ones(4))
+    model.eval()
+    plain, met = tc.compute_loss(model, batch)
+    weighted, _ = tc.compute_loss(model, batch, tc.compute_token_weights(16, 0.0))
+    assert met["ppl"] == pytest.approx(math.exp(float(plain)), rel=1e-4)
+    with torch.no_grad():
+        out = model(batch["input_ids"], labels=batch["labels"])
+        ce = torch.nn.functional.cross_entropy(out["logits"][:, :-1].reshape(-1, 128), batch["labels"][:, 1:].reshape(-1))
+    assert float(weighted) == pytest.approx(float(ce), rel=1e-5)          # uniform weights: the first head's loss
+    ev = tc.evaluate(model, [batch, batch], max_batches=1)
+    assert ev["batches"] == 1 and ev["ppl"] == pytest.approx(math.exp(ev["loss"]))
+    ts = tc.TimingStats()
+    ts.update(data=0.1, forward=0.3)
+    ts.update("forward", 0.1)
+    assert ts.counts == {"data": 1, "forward": 2} and "forward" in ts.summary()
+    s3 = tc.CosineWarmupScheduler(torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=1.0), 2, 10, max_lr=0.5, min_lr=0.05)
+    for _ in range(10):
+        s3.step()
+    assert s3.get_lr()[0] == pytest.approx(0.05)
+    assert [b["input_ids"].shape for b in tc.CUDAPrefetcher([batch, batch], "cpu")] == [(2, 16), (2, 16)]
+    tcfg = tc.TrainConfig.from_yaml(str(path))
+    assert tcfg.learning_rate == 1e-2 and tcfg.min_lr == pytest.approx(1e-3) and tcfg.max_seq_len == 16
+    assert tcfg.model["d_model"] == 32 and tcfg.optimizer == "adamw" and tcfg.weight_decay == 0.1
+    td.cleanup_distributed()
+
+
+def test_names_of_the_hugging_face_scripts(monkeypatch):
+    """``train_production`` (and its two variants) expose the wrapper, the collator, the data set loader and -
+    built on first use - the Trainer subclasses under the reference's names."""
+    monkeypatch.setenv("KMOE_OFFLINE", "1")
+    import train_fineweb_working as tfw
+    import train_production as tp
+    from scripts import train_hf
+    assert tfw.SimpleModelWrapper is tp.MoEModelWrapper and train_hf.MoEModelWrapper is tp.MoEModelWrapper
+    trainer_cls, cb_cls = tp.MoETrainer, tp.TrueLossLoggingCallback
+    assert trainer_cls.__name__ == "MoETrainer" and tfw.MuonTrainer.__name__ == "MoETrainer"
+    logs = {"loss": 8.0}
+    cb_cls(4).on_log(None, None, None, logs=logs)
+    assert logs["true_loss"] == 2.0 and logs["accumulated_loss"] == 8.0
+
+    class Tok:
+        def __call__(self, texts, truncation=True, max_length=8, padding="max_length", return_tensors=None):
+            texts = [texts] if isinstance(texts, str) else texts
+            rows = [[ord(c) % 50 + 1 for c in t][:max_length] for t in texts]
+            if padding == "max_length":
+                mask = [[1] * len(r) + [0] * (max_length - len(r)) for r in rows]
+                rows = [r + [0] * (max_length - len(r)) for r in rows]
+                return {"input_ids": torch.tensor(rows), "attention_mask": torch.tensor(mask)}
+            return {"input_ids": rows}
+
+    batch = tp.OnTheFlyDataCollator(Tok(), 8)([{"text": "abc"}, {"text": "a much longer text"}])
+    assert batch["input_ids"].shape == (2, 8) and batch["labels"][0].tolist()[3:] == [-100] * 5
+    assert torch.equal(batch["labels"][1], batch["input_ids"][1])
+    ds = tp.load_and_prepare_dataset({"data": {"dataset_name": "wikitext", "max_examples": 6},
+                                      "model": {"max_seq_len": 12, "vocab_size": 64}}, Tok())
+    assert len(ds) == 6 and ds[0]["input_ids"].shape == (12,) and int(ds[0]["input_ids"].max()) < 64
+    assert tfw.tokenize_function({"text": ["hello"]}, Tok(), 4)["input_ids"] == [[ord(c) % 50 + 1 for c in "hell"]]
+    with pytest.raises(AttributeError):
+        tp.no_such_name

@@ -210,3 +210,63 @@ def test_hf_entrypoint_fsdp_settings():
     assert tr["hf_kwargs"]["fsdp_config"]["backward_prefetch"] == "backward_pre" and tr["cpu_offload"] is False
     acc = tp.fsdp_settings(path, env={"WORLD_SIZE": "2", "ACCELERATE_USE_FSDP": "true"})
     assert acc["accelerate_owns_fsdp"] and acc["hf_kwargs"] == {}
+
+
+def test_tools_expose_the_reference_helper_names(tiny, capsys):
+    """Helper functions that the reference's tools define at module level exist here under the same names and do
+    the same job."""
+    import analyze_active_params
+    import check_memory
+    import debug_training
+    import diagnose_memory
+    import diagnose_plateau
+    from eval import evaluate_perplexity as ev
+    from tools import benchmark_expert_choice as bec, diagnose_training as dt, param_calculator as pc, reallocate_experts as re_
+    raw = diagnose_plateau.load_config(tiny["config"])
+    assert raw == ev.load_config(tiny["config"]) == check_memory.load_config(tiny["config"]) == diagnose_memory.load_config(tiny["config"])
+    model, cfg = diagnose_plateau.create_model_from_config(raw)
+    assert cfg.d_model == raw["model"]["d_model"] and re_.create_model_config(raw).d_model == cfg.d_model
+    assert dt.create_model_config(raw).n_layers == cfg.n_layers
+    an = diagnose_plateau.RouterAnalyzer(model)
+    assert an.register_hooks() is an
+    ids = torch.randint(0, cfg.vocab_size, (2, 16))
+    model.train()
+    model(ids, labels=ids, return_logits=False)["loss"].backward()
+    assert an.get_stats() and diagnose_plateau.analyze_gradients(model)
+    an.remove_hooks()
+    assert check_memory.print_memory(3, "after forward")[0] == "3:after forward"
+    assert diagnose_memory.get_mem() == (0.0, 0.0) and diagnose_memory.print_mem("x", 0.0) == 0.0
+    assert debug_training.analyze_checkpoint(tiny["checkpoint"])["non_finite"] == []
+    c = analyze_active_params.analyze_config(cfg, "tiny")
+    assert c["total"] == sum(p.numel() for p in model.parameters())
+    loaded, lcfg = ev.load_model_from_checkpoint(tiny["checkpoint"], tiny["config"], "cpu")
+    assert not loaded.training and lcfg.d_model == cfg.d_model
+    trained, tcfg = dt.load_checkpoint(tiny["checkpoint"], tiny["config"], "cpu")
+    fresh = dt.create_fresh_model(tcfg, "cpu")
+    mv = dt.analyze_parameter_movement(trained, fresh)
+    assert mv and max(mv.values()) < 1e-6                       # the checkpoint is the seed-0 initialisation
+    with torch.no_grad():
+        next(trained.parameters()).add_(1.0)
+    assert max(dt.analyze_parameter_movement(trained, fresh).values()) > 0.1
+    assert dt.analyze_trainability(trained)["trainable"] == dt.analyze_trainability(trained)["total"]
+    assert len(dt.test_generation(trained, tcfg, "cpu", prompt_len=4, new_tokens=3)) == 7
+    assert dt.check_gradient_flow(trained, tcfg, "cpu")
+    # the plain attention + MoE calculator against a model of that shape
+    mp = pc.ModelParams(vocab_size=500, d_model=64, n_layers=4, n_heads=2, n_kv_heads=1, head_dim=32, d_ff=128,
+                        d_ff_expert=64, n_experts=4, moe_top_k=2, moe_layers=[1, 3], tie_embeddings=True)
+    r = pc.calculate_params(mp)
+    import kolmogorov_moe_architecture_b200 as kmoe
+    twin = kmoe.MoETransformer(kmoe.AdvancedMoEConfig(
+        vocab_size=500, d_model=64, n_layers=4, n_heads=2, n_kv_heads=1, head_dim=32, d_ff=128, d_ff_expert=64,
+        n_experts=4, moe_top_k=2, moe_layers=(1, 3), mamba_enabled=False, mamba_layers=(), mod_enabled=False,
+        n_pred_tokens=1, aux_loss_weights=(1.0,), max_seq_len=16), verbose=False)
+    assert r["total_params"] == sum(p.numel() for p in twin.parameters())
+    assert r["n_moe_layers"] == 2 and r["active_params"] == r["total_params"] - r["expert_params"] / 2
+    assert pc.print_report(r, mp) is r
+    assert pc.load_config(tiny["config"]).d_model == cfg.d_model
+    best = pc.design_model(0.1, 0.05, vocab_size=32000)
+    assert best is None or isinstance(best, pc.ModelParams)
+    assert bec.original_scatter_add is bec.scatter_loop and bec.vectorized_scatter_add is bec.scatter_vectorised
+    w, idx = torch.randn(1, 2, 3, 4), torch.tensor([[[0, 1, 2], [2, 3, 4]]])
+    assert bec.benchmark_fn(bec.vectorized_scatter_add, torch.zeros(1, 6, 4), w, idx, warmup=1, iters=2) > 0
+    capsys.readouterr()

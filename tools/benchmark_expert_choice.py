@@ -70,6 +70,16 @@ def time_fn(fn, out_like, w_out, idx, warmup: int, iters: int) -> float:
     return (time.perf_counter() - t0) / max(iters, 1) * 1e3
 
 
+# the reference's names for the two PyTorch forms and the timer
+original_scatter_add = scatter_loop
+vectorized_scatter_add = scatter_vectorised
+
+
+def benchmark_fn(fn, output, weighted_outputs, token_indices, warmup: int = 10, iters: int = 100) -> float:
+    """Milliseconds per call of ``fn(zeros_like(output), weighted_outputs, token_indices)``."""
+    return time_fn(fn, output, weighted_outputs, token_indices, warmup, iters)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description="expert-choice combine: loop, scatter_add, kernel")
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu", choices=["cuda", "cpu"])

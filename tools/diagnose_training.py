@@ -197,5 +197,66 @@ def main(argv=None):
     return report
 
 
+# ---- names of the reference's tool, for code that imports them from here
+def create_model_config(config_dict):
+    """``AdvancedMoEConfig`` from a YAML dict (its ``model:`` section, read with defaults)."""
+    from kolmogorov_moe_architecture_b200.utils.config_io import model_config_tolerant
+    return model_config_tolerant(config_dict)
+
+
+def load_checkpoint(checkpoint_path, config_path, device="cpu"):
+    """(model with the checkpoint's weights, model configuration)."""
+    from eval.evaluate_perplexity import load_model
+    return load_model(checkpoint_path, config_path, device,
+                      dtype=torch.float32 if str(device) == "cpu" else torch.bfloat16)
+
+
+def create_fresh_model(config, device="cpu", seed: int = 0):
+    """A newly initialised model of the same configuration (seeded: the comparison is against the seed's values)."""
+    from kolmogorov_moe_architecture_b200 import MoETransformer
+    torch.manual_seed(seed)
+    return MoETransformer(config, verbose=False).to(device)
+
+
+def analyze_parameter_movement(trained_model, fresh_model=None, device="cpu") -> dict:
+    """Relative distance of every component of the trained model from a fresh initialisation (the given one, or
+    one built from the model's own configuration and seed 0)."""
+    if fresh_model is None:
+        return parameter_movement(trained_model, trained_model.config)
+    fresh = dict(fresh_model.named_parameters())
+    out = {}
+    for name, p in trained_model.named_parameters():
+        q = fresh.get(name)
+        if q is not None and q.shape == p.shape:
+            key = ".".join(name.split(".")[:3])
+            d = float((p.detach().float() - q.detach().float().to(p.device)).norm())
+            n = float(q.detach().float().norm()) + 1e-12
+            prev = out.get(key, (0.0, 0.0))
+            out[key] = (prev[0] + d * d, prev[1] + n * n)
+    return {k: (a ** 0.5) / (b ** 0.5) for k, (a, b) in out.items()}
+
+
+def analyze_trainability(model) -> dict:
+    return trainability(model)
+
+
+def test_generation(model, config, device="cpu", prompt_len: int = 8, new_tokens: int = 12):
+    """Greedy continuation of a random prompt; returns the token ids (no tokenizer is needed to see whether the
+    model repeats one token or produces a spread)."""
+    ids = torch.randint(0, config.vocab_size, (1, prompt_len), device=device)
+    out = greedy_sample(model, ids, new_tokens)[0].tolist()
+    print("[sample]", out, "- distinct new tokens:", len(set(out[prompt_len:])))
+    return out
+
+
+test_generation.__test__ = False          # a tool function, not a test case
+
+
+def check_gradient_flow(model, config, device="cpu", batch: int = 2) -> dict:
+    """One forward-backward pass on random tokens; gradient statistics per parameter group."""
+    ids = torch.randint(0, config.vocab_size, (batch, min(64, config.max_seq_len)), device=device)
+    return gradient_flow(model, ids)
+
+
 if __name__ == "__main__":
     main()

@@ -88,7 +88,22 @@ def breakdown(cfg) -> dict:
     return out
 
 
-def print_report(cfg, world: int = 8, micro_batch: int = 4, optimizer: str = "muon") -> dict:
+def print_report(cfg, world=8, micro_batch: int = 4, optimizer: str = "muon") -> dict:
+    """Report of a model configuration (``print_report(cfg, world)``), or - in the reference's call form
+    ``print_report(params, model_params)`` - of a ``calculate_params`` result for a ``ModelParams``."""
+    if isinstance(cfg, dict) and isinstance(world, ModelParams):
+        params, mp = cfg, world
+        print("=" * 64)
+        print(f"  vocab {mp.vocab_size:,}  d_model {mp.d_model}  layers {mp.n_layers} "
+              f"({params['n_moe_layers']} MoE, {params['n_dense_layers']} dense)  experts {mp.n_experts} x "
+              f"d_ff {mp.d_ff_expert}, top-{mp.moe_top_k}")
+        for k in ("embedding_params", "lm_head_params", "attention_params", "norm_params", "dense_ffn_params",
+                  "router_params", "expert_params"):
+            print(f"  {k[:-7]:12s} {format_params(params[k]):>10s}  {100 * params[k] / max(params['total_params'], 1):5.1f} %")
+        print(f"  {'total':12s} {format_params(params['total_params']):>10s}")
+        print(f"  {'active':12s} {format_params(params['active_params']):>10s}  sparsity {100 * params['sparsity']:.1f} %")
+        print("=" * 64)
+        return params
     r, b = analyze(cfg, world, micro_batch, optimizer), breakdown(cfg)
     n_moe = len([i for i in range(cfg.n_layers) if i in set(cfg.moe_layers)]) if cfg.moe_layers is not None else cfg.n_layers
     print("=" * 64)
@@ -127,6 +142,82 @@ def design(target_total: float, target_active: float, tol: float = 0.1, limit: i
             out.append({"d_model": d, "n_layers": L, "n_experts": E, "d_ff_expert": cfg.d_ff_expert,
                         "total_b": est / 1e9, "active_b": active / 1e9})
     return sorted(out, key=lambda r: abs(r["total_b"] * 1e9 - target_total))[:limit]
+
+
+# ---- the reference's plain attention + MoE calculator (tools/param_calculator.py:19-236), for code that imports it
+from dataclasses import dataclass                                             # noqa: E402
+from typing import List, Optional                                             # noqa: E402
+
+
+@dataclass
+class ModelParams:
+    """Sizes of an attention + SwiGLU / MoE transformer without Mamba, mixture-of-depths or extra heads."""
+    vocab_size: int = 32000
+    d_model: int = 1024
+    n_layers: int = 18
+    n_heads: int = 8
+    n_kv_heads: int = 4
+    head_dim: int = 128
+    d_ff: int = 4096
+    d_ff_expert: int = 2048
+    n_experts: int = 16
+    moe_top_k: int = 2
+    moe_layers: Optional[List[int]] = None          # None = every layer
+    tie_embeddings: bool = False
+
+
+def calculate_params(cfg: ModelParams) -> dict:
+    """Analytic totals of a ``ModelParams`` model: q/k/v/o projections, two norms per layer and a final one, a
+    three-matrix SwiGLU in the dense layers, a d -> 128 -> E router MLP and E three-matrix experts in the MoE
+    layers.  Active = everything but the experts, plus ``moe_top_k / n_experts`` of the experts."""
+    L, d = cfg.n_layers, cfg.d_model
+    moe = set(range(L)) if cfg.moe_layers is None else set(cfg.moe_layers)
+    n_moe, n_dense = len(moe), L - len(moe)
+    emb = cfg.vocab_size * d
+    head = 0 if cfg.tie_embeddings else cfg.vocab_size * d
+    attn = 2 * d * cfg.n_heads * cfg.head_dim + 2 * d * cfg.n_kv_heads * cfg.head_dim
+    norms = 2 * d * L + d
+    dense = 3 * d * cfg.d_ff * n_dense
+    router = (d * 128 + 128 * cfg.n_experts) * n_moe
+    per_expert = 3 * d * cfg.d_ff_expert
+    experts = per_expert * cfg.n_experts * n_moe
+    total = emb + head + attn * L + norms + dense + router + experts
+    active = total - experts + experts * cfg.moe_top_k / max(cfg.n_experts, 1)
+    return {"total_params": total, "active_params": active, "sparsity": 1.0 - active / total if total else 0.0,
+            "embedding_params": emb, "lm_head_params": head, "attention_params": attn * L, "norm_params": norms,
+            "dense_ffn_params": dense, "router_params": router, "expert_params": experts,
+            "attention_per_layer": attn, "expert_ffn_per_expert": per_expert,
+            "experts_per_layer": per_expert * cfg.n_experts, "n_moe_layers": n_moe, "n_dense_layers": n_dense,
+            "moe_top_k": cfg.moe_top_k, "n_experts": cfg.n_experts}
+
+
+def load_config(path: str) -> ModelParams:
+    """``ModelParams`` from the ``model:`` section of a YAML file (the reference's defaults for missing keys)."""
+    from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml
+    m = load_yaml(path).get("model") or {}
+    d = ModelParams()
+    return ModelParams(**{k: m.get(k, getattr(d, k)) for k in d.__dataclass_fields__})
+
+
+def design_model(target_total: float, target_active: float, vocab_size: int = 32000) -> Optional[ModelParams]:
+    """Grid search over (d_model, n_layers, n_experts, expert width) for the plain MoE model closest to the targets
+    (in billions of parameters); None when nothing comes within 15 %."""
+    best, best_err = None, 0.15
+    for d, L, E, f in itertools.product((512, 768, 1024, 1536, 2048, 2560, 3072, 4096), (8, 12, 16, 18, 24, 32, 40),
+                                        (8, 16, 32, 64), (512, 1024, 1536, 2048, 2816, 4096)):
+        cfg = ModelParams(vocab_size=vocab_size, d_model=d, n_layers=L, n_heads=max(d // 128, 1),
+                          n_kv_heads=max(d // 512, 1), head_dim=128, d_ff=4 * d, d_ff_expert=f, n_experts=E)
+        r = calculate_params(cfg)
+        err = max(abs(r["total_params"] / 1e9 - target_total) / target_total,
+                  abs(r["active_params"] / 1e9 - target_active) / target_active)
+        if err < best_err:
+            best, best_err = cfg, err
+    if best is not None:
+        r = calculate_params(best)
+        print(f"closest: {best}  total {format_params(r['total_params'])}  active {format_params(r['active_params'])}")
+    else:
+        print("no configuration within 15 % of the targets")
+    return best
 
 
 def config_from_flags(a):

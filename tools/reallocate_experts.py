@@ -110,15 +110,25 @@ def reallocate_experts(checkpoint_path: str, config_path: str, output_path: str,
     return info
 
 
-if __name__ == "__main__":
-    ap = argparse.ArgumentParser()
+def create_model_config(config_dict):
+    """``AdvancedMoEConfig`` from a YAML dict (its ``model:`` section, read with the tolerant loader's defaults)."""
+    from kolmogorov_moe_architecture_b200.utils.config_io import model_config_tolerant
+    return model_config_tolerant(config_dict)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description="copy experts from healthy to collapsed layers, reset the routers")
     ap.add_argument("--checkpoint", required=True)
     ap.add_argument("--config", required=True)
     ap.add_argument("--output", required=True)
     ap.add_argument("--device", default=None, help="default: cuda:<--gpu> when a GPU is present, else cpu")
     ap.add_argument("--gpu", type=int, default=0, help="GPU index (the reference's way of naming the device)")
     ap.add_argument("--entropy-threshold", type=float, default=0.85)
-    a = ap.parse_args()
+    a = ap.parse_args(argv)
     if a.device is None:
         a.device = f"cuda:{a.gpu}" if torch.cuda.is_available() else "cpu"
-    reallocate_experts(a.checkpoint, a.config, a.output, a.device, a.entropy_threshold)
+    return reallocate_experts(a.checkpoint, a.config, a.output, a.device, a.entropy_threshold)
+
+
+if __name__ == "__main__":
+    main()

@@ -13,6 +13,11 @@ import os
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+# helpers that the reference's script defines at module level and other code imports from it
+from kolmogorov_moe_architecture_b200.training.script_api import (  # noqa: E402,F401
+    check_router_collapse_fast, get_cache_path, get_dataloader, get_model_state_dict, load_config, signal_handler)
+from kolmogorov_moe_architecture_b200.training.script_api import save_state_checkpoint as save_checkpoint  # noqa: E402,F401
 os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 
 

@@ -15,6 +15,30 @@ import sys
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
+# helpers that the reference's script defines at module level and other code imports from it
+from kolmogorov_moe_architecture_b200.data.dolma_dataset import ThreadedPrefetcher  # noqa: E402,F401
+from kolmogorov_moe_architecture_b200.training.script_api import (  # noqa: E402,F401
+    CosineWarmupScheduler, CUDAPrefetcher, PackedSequenceDataset, StandardDataset, TimingStats, TrainConfig,
+    cleanup_distributed, compute_loss, compute_token_weights, create_dataloader, evaluate, is_main_process,
+    load_checkpoint, print_rank0, save_checkpoint, setup_distributed, setup_fsdp)
+
+
+def train(config):
+    """Train from a ``TrainConfig`` (reference: train_custom.py:944-1295): the configuration's YAML file drives the
+    run, its fields override the file's step count, batch size, checkpoint directory and loss weighting."""
+    from kolmogorov_moe_architecture_b200.training.runner import RunSpec, run_training
+    assert config.config_path, "TrainConfig.from_yaml(path) records the file the run is built from"
+    spec = RunSpec(config_path=config.config_path, steps=config.max_steps, batch_size=config.batch_size,
+                   strict_config=True, weights="bf16" if config.dtype == "bfloat16" else "fp32_autocast",
+                   optimizer_family="muon8bit_all" if config.optimizer == "muon" else "adamw", checkpoint_format="C",
+                   checkpoint_dir=config.checkpoint_dir,
+                   data_mode="packed" if config.pack_sequences else "streaming",
+                   document_mask=bool(config.use_document_attention_mask), wandb=bool(config.use_wandb),
+                   profile=bool(config.profile), compile=bool(config.compile),
+                   token_weight_decay=config.token_weight_decay if config.use_token_weights or config.token_weight_decay
+                   else 0.0)
+    return run_training(spec)
+
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description="Custom MoE Training Script")

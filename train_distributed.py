@@ -17,6 +17,12 @@ import sys
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
+# helpers that the reference's launcher defines at module level and other code imports from it
+from kolmogorov_moe_architecture_b200.training.script_api import (  # noqa: E402,F401
+    PackedSequenceDataset, check_parameter_gradients, cleanup_distributed, collect_router_stats, create_dataloader,
+    create_model, create_optimizer, create_scheduler, load_config, load_tokenizer, print_debug_stats,
+    setup_distributed, train_step, wrap_model_with_fsdp)
+
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description="Distributed MoE Training")

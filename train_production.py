@@ -19,6 +19,20 @@ import os
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+# names the reference's script defines at module level; the two Trainer subclasses need ``transformers`` and are
+# built on first use
+from kolmogorov_moe_architecture_b200.training.hf import (MoEModelWrapper, OnTheFlyDataCollator,  # noqa: E402,F401
+                                                          load_and_prepare_dataset)
+from kolmogorov_moe_architecture_b200.training.script_api import load_config  # noqa: E402,F401
+
+
+def __getattr__(name):
+    if name in ("MoETrainer", "TrueLossLoggingCallback"):
+        from kolmogorov_moe_architecture_b200.training.hf import make_hf_classes
+        trainer, callback = make_hf_classes()
+        return trainer if name == "MoETrainer" else callback
+    raise AttributeError(name)
 os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 
 
