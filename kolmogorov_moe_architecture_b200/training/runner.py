@@ -329,7 +329,11 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
     if spec.checkpoint_format == "B":
         cdir = os.path.join(cdir, os.path.splitext(os.path.basename(spec.config_path))[0])
     save_every = spec.save_interval if spec.save_interval is not None else train_cfg["save_interval"]
-    logger = MetricLogger(spec.jsonl, spec.wandb, spec.wandb_project, spec.wandb_run, y, rank=rank)
+    wb = y.get("wandb") or {}                  # the YAML's ``wandb:`` section: enabled / project / entity / run_name
+    hf = y.get("huggingface") or {}
+    logger = MetricLogger(spec.jsonl, spec.wandb or bool(wb.get("enabled", False)) or bool(hf.get("use_wandb", False)),
+                          wb.get("project", spec.wandb_project), spec.wandb_run or wb.get("run_name"), y,
+                          tensorboard_dir=hf.get("logging_dir"), rank=rank, entity=wb.get("entity"))
     timer = PhaseTimer(enabled=spec.profile, device=device)
     if spec.profile:
         engine.timer = timer                   # forward / backward / optimizer next to data / step

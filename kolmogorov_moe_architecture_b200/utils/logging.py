@@ -15,7 +15,7 @@ from typing import Any, Dict, Optional
 class MetricLogger:
     def __init__(self, jsonl_path: Optional[str] = None, use_wandb: bool = False, project: str = "moe-architecture",
                  run_name: Optional[str] = None, config: Optional[dict] = None, tensorboard_dir: Optional[str] = None,
-                 rank: int = 0):
+                 rank: int = 0, entity: Optional[str] = None):
         self.rank = rank
         self.f = None
         self.wandb = None
@@ -28,7 +28,7 @@ class MetricLogger:
         if use_wandb:
             try:
                 import wandb
-                wandb.init(project=project, name=run_name, config=config)
+                wandb.init(project=project, name=run_name, config=config, **({'entity': entity} if entity else {}))
                 self.wandb = wandb
             except Exception as e:
                 print(f"Warning: Could not initialize W&B: {e}")

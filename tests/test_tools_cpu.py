@@ -210,6 +210,20 @@ def test_hf_entrypoint_fsdp_settings():
     assert tr["hf_kwargs"]["fsdp_config"]["backward_prefetch"] == "backward_pre" and tr["cpu_offload"] is False
     acc = tp.fsdp_settings(path, env={"WORLD_SIZE": "2", "ACCELERATE_USE_FSDP": "true"})
     assert acc["accelerate_owns_fsdp"] and acc["hf_kwargs"] == {}
+    assert tr["sharding_strategy"] == "full_shard" and tr["sharded_state_dict"]
+    assert tr["hf_kwargs"]["fsdp_config"]["state_dict_type"] == "SHARDED_STATE_DICT"
+    # other strategies, wrap policies and offload in the file change the request accordingly
+    import tempfile
+    import yaml
+    with tempfile.NamedTemporaryFile("w", suffix=".yaml", delete=False) as f:
+        yaml.safe_dump({"fsdp_config": {"fsdp_sharding_strategy": "SHARD_GRAD_OP", "fsdp_auto_wrap_policy": "SIZE_BASED_WRAP",
+                                        "fsdp_min_num_params": 5000, "fsdp_offload_params": True,
+                                        "fsdp_state_dict_type": "FULL_STATE_DICT"}}, f)
+    alt = tp.fsdp_settings(f.name, env={"WORLD_SIZE": "4"})
+    os.unlink(f.name)
+    assert alt["hf_kwargs"]["fsdp"] == "shard_grad_op auto_wrap offload" and alt["cpu_offload"]
+    assert alt["hf_kwargs"]["fsdp_config"]["min_num_params"] == 5000 and not alt["sharded_state_dict"]
+    assert "transformer_layer_cls_to_wrap" not in alt["hf_kwargs"]["fsdp_config"]
 
 
 def test_tools_expose_the_reference_helper_names(tiny, capsys):

@@ -51,17 +51,25 @@ def fsdp_settings(path, env=None):
             fc = (yaml.safe_load(f) or {}).get("fsdp_config", {}) or {}
     offload = bool(fc.get("fsdp_offload_params", False))
     owns = str(env.get("ACCELERATE_USE_FSDP", "")).lower() in ("1", "true", "yes")
+    # sharding strategy and wrap policy in the words of ``TrainingArguments.fsdp``
+    strategy = {"FULL_SHARD": "full_shard", "SHARD_GRAD_OP": "shard_grad_op", "HYBRID_SHARD": "hybrid_shard",
+                "NO_SHARD": "no_shard"}.get(str(fc.get("fsdp_sharding_strategy", "FULL_SHARD")).upper(), "full_shard")
+    by_layer = str(fc.get("fsdp_auto_wrap_policy", "TRANSFORMER_BASED_WRAP")).upper() == "TRANSFORMER_BASED_WRAP"
     hf = {}
     if world > 1 and not owns:
-        hf = {"fsdp": "full_shard auto_wrap" + (" offload" if offload else ""),
-              "fsdp_config": {"transformer_layer_cls_to_wrap": ["TransformerBlock"],
+        hf = {"fsdp": strategy + " auto_wrap" + (" offload" if offload else ""),
+              "fsdp_config": {**({"transformer_layer_cls_to_wrap": ["TransformerBlock"]} if by_layer
+                                 else {"min_num_params": int(fc.get("fsdp_min_num_params", 1e8))}),
+                              "state_dict_type": str(fc.get("fsdp_state_dict_type", "SHARDED_STATE_DICT")),
                               "backward_prefetch": str(fc.get("fsdp_backward_prefetch", "BACKWARD_PRE")).lower(),
                               "forward_prefetch": bool(fc.get("fsdp_forward_prefetch", True)),
                               "use_orig_params": bool(fc.get("fsdp_use_orig_params", True)),
                               "cpu_ram_efficient_loading": bool(fc.get("fsdp_cpu_ram_efficient_loading", True)),
                               "sync_module_states": bool(fc.get("fsdp_sync_module_states", True)),
                               "limit_all_gathers": bool(fc.get("fsdp_limit_all_gathers", True))}}
-    return {"distributed": world > 1, "accelerate_owns_fsdp": owns, "cpu_offload": offload, "hf_kwargs": hf}
+    return {"distributed": world > 1, "accelerate_owns_fsdp": owns, "cpu_offload": offload, "hf_kwargs": hf,
+            "sharding_strategy": strategy, "sharded_state_dict": "SHARDED" in str(fc.get("fsdp_state_dict_type",
+                                                                                        "SHARDED_STATE_DICT")).upper()}
 
 
 def main(argv=None):
@@ -125,13 +133,31 @@ def main(argv=None):
     steps = a.max_steps or max(1, tc["total_tokens"] // (tc["batch_size"] * cfg.max_seq_len *
                                                           tc["gradient_accumulation_steps"]))
     cuda = torch.cuda.is_available()
+    hfc, wb, evc = y.get("huggingface") or {}, y.get("wandb") or {}, y.get("evaluation") or {}
+    report = ["wandb"] if (wb.get("enabled") or hfc.get("use_wandb")) else []
+    if report:
+        os.environ.setdefault("WANDB_PROJECT", str(wb.get("project", "moe-training")))
+        if wb.get("entity"):
+            os.environ.setdefault("WANDB_ENTITY", str(wb["entity"]))
+    if hfc.get("logging_dir"):
+        report.append("tensorboard")
+    extra = {}
+    if evc.get("enabled") and eval_ds is not None:
+        # evaluation.eval_steps batches every evaluation.eval_interval steps (training.eval_interval as fallback)
+        n_eval = int(evc.get("eval_steps", 100)) * tc["batch_size"]
+        eval_ds = torch.utils.data.Subset(eval_ds, range(min(n_eval, len(eval_ds))))
+        extra = {"eval_strategy": "steps", "eval_steps": int(evc.get("eval_interval", tc.get("eval_interval", 500)))}
+    else:
+        eval_ds = None
     args = TrainingArguments(
         output_dir=a.output_dir or tc["checkpoint_dir"], max_steps=steps,
         per_device_train_batch_size=tc["batch_size"], gradient_accumulation_steps=tc["gradient_accumulation_steps"],
         learning_rate=tc["max_lr"], warmup_steps=min(tc["warmup_steps"], max(steps - 1, 0)),
         max_grad_norm=tc["gradient_clip_norm"], logging_steps=tc["log_interval"], save_steps=tc["save_interval"],
-        save_total_limit=3, bf16=bool(mp.get("bf16", cuda)) and cuda, report_to=[], remove_unused_columns=False,
-        dataloader_num_workers=0, use_cpu=not cuda, **fs["hf_kwargs"])
+        save_total_limit=int(hfc.get("save_total_limit", 3)), bf16=bool(mp.get("bf16", cuda)) and cuda,
+        report_to=report, run_name=wb.get("run_name"), logging_dir=hfc.get("logging_dir"),
+        seed=int(hfc.get("seed", 42)), remove_unused_columns=False,
+        dataloader_num_workers=0, use_cpu=not cuda, **extra, **fs["hf_kwargs"])
     trainer = MoETrainer(oc, tc, tc["log_interval"], model=model, args=args, train_dataset=train_ds,
                          eval_dataset=eval_ds, callbacks=[TrueLoss(tc["gradient_accumulation_steps"])])
     try:
