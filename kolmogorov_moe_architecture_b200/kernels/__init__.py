@@ -63,9 +63,9 @@ class GroupedSwiGLUFunction(torch.autograd.Function):
         return out.detach()
 
     @staticmethod
-    def backward(ctx, grad_out):
+    def backward(ctx, grad_output):
         need = [t for t in ctx.leaves if t.requires_grad]
-        got = iter(torch.autograd.grad(ctx.out, need, grad_out) if need else ())
+        got = iter(torch.autograd.grad(ctx.out, need, grad_output) if need else ())
         grads = [next(got) if t.requires_grad else None for t in ctx.leaves]
         ctx.leaves = ctx.out = None
         return (*grads, None, None, None)

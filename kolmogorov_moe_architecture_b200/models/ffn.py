@@ -46,9 +46,12 @@ def get_ffn_module(d_model: int, d_ff: int, activation: str = "swiglu", dropout:
 class ExpertFFN(nn.Module):
     """A single stand-alone expert (kept for API parity, ffn.py:136-162)."""
 
-    def __init__(self, d_model: int, d_ff: int, activation: str = "swiglu", dropout: float = 0.0):
+    def __init__(self, d_model: int, d_ff: int = None, activation: str = "swiglu", dropout: float = 0.0,
+                 d_ff_expert: int = None):
         super().__init__()
-        self.ffn = get_ffn_module(d_model, d_ff, activation, dropout)
+        width = d_ff_expert if d_ff is None else d_ff          # ``d_ff_expert``: the reference's keyword
+        assert width is not None, "the expert width is required"
+        self.ffn = get_ffn_module(d_model, width, activation, dropout)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.ffn(x)

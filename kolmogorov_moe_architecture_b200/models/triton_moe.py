@@ -9,16 +9,24 @@ import torch
 from .moe import GroupedExperts
 
 
-def sort_tokens_by_expert(expert_indices: torch.Tensor, n_experts: int):
-    """Stable sort of the flat (token, slot) assignments by expert.
-    Returns (sorted_token_idx, sorted_expert_ids, sort_order, seg_starts, seg_ends)."""
+def sort_tokens_by_expert(expert_indices: torch.Tensor, expert_weights=None, n_experts: int = None):
+    """Stable sort of the flat (token, slot) assignments by expert (reference: triton_moe.py:160-198).
+
+    ``sort_tokens_by_expert(expert_indices, expert_weights, n_experts)`` returns
+    (sorted_token_indices, sorted_expert_ids, sorted_weights, segment_starts, segment_ends).
+    Called without weights - ``sort_tokens_by_expert(expert_indices, n_experts)`` - the third result is the sort
+    order itself (flat assignment index of every sorted position), from which any per-assignment tensor can be
+    brought into the same order."""
+    if n_experts is None and not torch.is_tensor(expert_weights):
+        expert_weights, n_experts = None, expert_weights
     T, k = expert_indices.shape
     flat = expert_indices.reshape(-1)
     order = torch.argsort(flat, stable=True)
     tok = torch.arange(T, device=flat.device).repeat_interleave(k)[order]
     counts = torch.bincount(flat, minlength=n_experts)
     ends = torch.cumsum(counts, 0)
-    return tok, flat[order], order, ends - counts, ends
+    third = order if expert_weights is None else expert_weights.reshape(-1)[order]
+    return tok, flat[order], third, ends - counts, ends
 
 
 class TritonGroupedExperts(GroupedExperts):

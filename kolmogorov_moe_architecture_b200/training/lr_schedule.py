@@ -56,9 +56,9 @@ class CosineScheduleWithWarmup:
                 "max_steps": self.max_steps, "max_lr": self.max_lr, "min_lr": self.min_lr,
                 "warmup_init_lr": self.warmup_init_lr}
 
-    def load_state_dict(self, sd: dict) -> None:
+    def load_state_dict(self, state_dict: dict) -> None:
         for k in ("current_step", "warmup_steps", "max_steps", "max_lr", "min_lr", "warmup_init_lr"):
-            setattr(self, k, sd[k])
+            setattr(self, k, state_dict[k])
 
 
 def get_lr_scheduler(optimizer, total_tokens: int, batch_size: int, seq_len: int,

@@ -287,3 +287,18 @@ def test_grouped_swiglu_function_matches_the_differentiable_path():
     assert all(torch.allclose(p.grad, q.grad, atol=1e-6) for p, q in zip(a, b))
     frozen = GroupedSwiGLUFunction.apply(x.clone().requires_grad_(True), w1, w2, w3, ids)      # weights without gradients
     frozen.sum().backward()
+
+
+def test_keyword_names_of_the_reference_are_accepted():
+    import torch
+    from moe_arch.model.ffn import ExpertFFN
+    from moe_arch.model.triton_moe import sort_tokens_by_expert
+    e = ExpertFFN(d_model=16, d_ff_expert=32)
+    assert e(torch.randn(3, 16)).shape == (3, 16)
+    idx = torch.tensor([[2, 0], [1, 2], [0, 1]])
+    w = torch.tensor([[0.6, 0.4], [0.7, 0.3], [0.5, 0.5]])
+    tok, ids, sw, s0, s1 = sort_tokens_by_expert(expert_indices=idx, expert_weights=w, n_experts=3)
+    assert ids.tolist() == [0, 0, 1, 1, 2, 2] and tok.tolist() == [0, 2, 1, 2, 0, 1]
+    assert torch.allclose(sw, torch.tensor([0.4, 0.5, 0.7, 0.5, 0.6, 0.3])) and s0.tolist() == [0, 2, 4] and s1.tolist() == [2, 4, 6]
+    _, _, order, _, _ = sort_tokens_by_expert(idx, 3)
+    assert torch.equal(w.reshape(-1)[order], sw)
