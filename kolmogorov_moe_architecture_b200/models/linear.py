@@ -13,6 +13,30 @@ import torch.nn as nn
 from .. import ops
 
 
+import contextlib
+import threading
+
+_state = threading.local()
+
+
+@contextlib.contextmanager
+def deferred_init():
+    """Inside this block ``Linear`` layers are created without ``nn.Linear``'s default initialisation: the caller
+    initialises every one of them afterwards (``MoETransformer`` applies normal(0, init_std) to all Linear
+    weights and zeros the biases), so drawing the default values first is one wasted pass over every weight."""
+    prev = getattr(_state, "defer", False)
+    _state.defer = True
+    try:
+        yield
+    finally:
+        _state.defer = prev
+
+
 class Linear(nn.Linear):
+    def reset_parameters(self) -> None:
+        if not getattr(_state, "defer", False):
+            super().reset_parameters()
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.linear(x, self.weight, self.bias)
+

@@ -31,11 +31,13 @@ class MoETransformer(nn.Module):
         super().__init__()
         self.config = config
         self.gradient_checkpointing = False
-        self.token_embedding = TokenEmbedding(config)
-        self.layers = nn.ModuleList([TransformerBlock(config, i) for i in range(config.n_layers)])
-        self.final_norm = get_norm_layer(config)
-        self.lm_heads = nn.ModuleList([Linear(config.d_model, config.vocab_size, bias=False)
-                                       for _ in range(config.n_pred_tokens)])
+        from .linear import deferred_init
+        with deferred_init():                    # every Linear is initialised by ``_init_weights`` below
+            self.token_embedding = TokenEmbedding(config)
+            self.layers = nn.ModuleList([TransformerBlock(config, i) for i in range(config.n_layers)])
+            self.final_norm = get_norm_layer(config)
+            self.lm_heads = nn.ModuleList([Linear(config.d_model, config.vocab_size, bias=False)
+                                           for _ in range(config.n_pred_tokens)])
         self.tie_word_embeddings = getattr(config, "tie_word_embeddings", True)
         if self.tie_word_embeddings:
             self.lm_heads[0].weight = self.token_embedding.embedding.weight
