@@ -22,9 +22,21 @@ def _set_submodule(root: nn.Module, path: str, new: nn.Module) -> None:
         setattr(parent, parts[-1], new)
 
 
-def replace_ffn_with_moe(model: nn.Module, moe_layers: Dict[str, nn.Module]) -> nn.Module:
-    for i, (name, _) in enumerate(find_ffn_modules(model)):
-        if str(i) in moe_layers:
+def replace_ffn_with_moe(model: nn.Module, moe_layers, layer_indices=None, ffn_name_pattern: Optional[str] = None,
+                         inplace: bool = True) -> nn.Module:
+    """Put ``moe_layers[str(i)]`` (a dict or ``nn.ModuleDict`` keyed by layer index) in the place of the i-th
+    feed-forward block.  ``layer_indices`` restricts the replacement to those layers; ``ffn_name_pattern`` names the
+    attribute of the blocks (``"mlp"``, ``"ffn"``, ...) when the default name rule should not decide;
+    ``inplace=False`` works on a deep copy (reference: convert.py:18-77, which copies by default; here the default
+    is in place, because the copy of a multi-billion-parameter model is rarely wanted)."""
+    if not inplace:
+        import copy
+        model = copy.deepcopy(model)
+    names = (ffn_name_pattern,) if ffn_name_pattern else None
+    found = find_ffn_modules(model, names=names) if names else find_ffn_modules(model)
+    wanted = None if layer_indices is None else {int(i) for i in layer_indices}
+    for i, (name, _) in enumerate(found):
+        if str(i) in moe_layers and (wanted is None or i in wanted):
             _set_submodule(model, name, moe_layers[str(i)])
     return model
 
@@ -32,9 +44,21 @@ def replace_ffn_with_moe(model: nn.Module, moe_layers: Dict[str, nn.Module]) -> 
 class SparseModelWrapper(nn.Module):
     """The converted model plus helpers: routing statistics of the last forward and parameter counts."""
 
-    def __init__(self, model: nn.Module, moe_paths: Dict[int, str]):
+    def __init__(self, model: nn.Module = None, moe_paths: Dict[int, str] = None, base_model: nn.Module = None,
+                 moe_layers=None, layer_indices=None):
+        """``SparseModelWrapper(model, {layer: path of its MoE module})``, or in the reference's form
+        ``SparseModelWrapper(base_model, moe_layers, layer_indices)`` with the MoE layers already in the model: the
+        paths are then found by identity."""
         super().__init__()
-        self.model, self.moe_paths = model, moe_paths
+        model = base_model if model is None else model
+        if moe_paths is not None and not all(isinstance(v, str) for v in dict(moe_paths).values()):
+            moe_layers, moe_paths = moe_paths, None            # second positional was the reference's moe_layers
+        if moe_paths is None:
+            where = {id(m): n for n, m in model.named_modules()}
+            items = moe_layers.items() if moe_layers is not None else []
+            moe_paths = {int(k): where[id(m)] for k, m in items if id(m) in where
+                         and (layer_indices is None or int(k) in {int(i) for i in layer_indices})}
+        self.model, self.moe_paths = model, dict(moe_paths)
 
     def forward(self, *a, **kw):
         return self.model(*a, **kw)

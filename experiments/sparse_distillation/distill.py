@@ -125,8 +125,26 @@ def _dense_ffn_weights(ffn: nn.Module):
 class MoEDistillationLayer(nn.Module):
     """Router (+ optional learnable per-expert logit bias) and stacked experts."""
 
-    def __init__(self, d_model: int, d_ff_expert: int, cfg: DistillationConfig, n_experts=None, top_k=None):
+    def __init__(self, d_model: int, d_ff_expert: int = None, cfg=None, n_experts=None, top_k=None, *,
+                 d_ff: int = None, capacity_factor: float = None, routing_type: str = None, mlp_router: bool = None,
+                 router_hidden_dim: int = None, router_n_layers: int = None, use_expert_bias: bool = None):
+        """``MoEDistillationLayer(d_model, d_ff_expert, config[, n_experts, top_k])``, or with the settings spelled
+        out as in the reference (distill.py:253): ``MoEDistillationLayer(d_model, d_ff, n_experts,
+        capacity_factor=..., routing_type=..., mlp_router=..., router_hidden_dim=..., router_n_layers=...,
+        use_expert_bias=...)`` - a configuration is then made from the defaults and these values."""
         super().__init__()
+        if isinstance(cfg, int):                             # third positional is the expert count
+            n_experts, cfg = cfg, None
+        d_ff_expert = d_ff if d_ff_expert is None else d_ff_expert
+        if cfg is None:
+            cfg = DistillationConfig(moe_routing=routing_type or "expert_choice")
+        over = {k: v for k, v in dict(moe_capacity_factor=capacity_factor, moe_routing=routing_type,
+                                      router_mlp=mlp_router, router_hidden_dim=router_hidden_dim,
+                                      router_n_layers=router_n_layers, use_expert_bias=use_expert_bias).items()
+                if v is not None}
+        if over:
+            import dataclasses
+            cfg = dataclasses.replace(cfg, **over)
         self.cfg, self.d_model, self.d_ff = cfg, d_model, d_ff_expert
         self.n_experts, self.top_k = n_experts or cfg.n_experts, top_k or cfg.moe_top_k
         self.routing = cfg.moe_routing
@@ -271,10 +289,11 @@ def _ids_of_batch(b) -> torch.Tensor:
 
 class SparseDistillationTrainer:
     def __init__(self, model: nn.Module = None, config: DistillationConfig = None, device: str = "cpu",
-                 dense_model: nn.Module = None):
+                 dense_model: nn.Module = None, layer_filter=None):
         model = dense_model if model is None else model          # the reference's keyword for the teacher
+        config = DistillationConfig() if config is None else config
         self.model, self.cfg, self.device = model, config, torch.device(device)
-        self.ffn = find_ffn_modules(model)
+        self.ffn = find_ffn_modules(model, layer_filter=layer_filter)
         assert self.ffn, "no FFN modules found in the model"
         self.d_model, self.d_ff_dense, self.dtype = self._infer_dimensions()
         self.layer_cfg = json.load(open(config.layer_config_path)) if config.layer_config_path else {}
@@ -322,17 +341,23 @@ class SparseDistillationTrainer:
 
     # ------------------------------------------------------------------ losses
     @staticmethod
-    def compute_load_balancing_loss(logits: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
+    def compute_load_balancing_loss(router_logits: torch.Tensor, expert_counts: torch.Tensor) -> torch.Tensor:
+        logits, counts = router_logits, expert_counts
         E = logits.shape[-1]
         P = F.softmax(logits.reshape(-1, E).float(), -1).mean(0)
         f = counts.float() / counts.sum().clamp(min=1)
         return E * (f * P).sum()
 
     @staticmethod
-    def compute_z_loss(logits: torch.Tensor) -> torch.Tensor:
-        return torch.logsumexp(logits.float(), dim=-1).pow(2).mean()
+    def compute_z_loss(router_logits: torch.Tensor) -> torch.Tensor:
+        return torch.logsumexp(router_logits.float(), dim=-1).pow(2).mean()
 
-    def compute_loss(self, student: torch.Tensor, teacher: torch.Tensor, aux: Dict) -> Tuple[torch.Tensor, Dict[str, float]]:
+    def compute_loss(self, moe_output: torch.Tensor, target: torch.Tensor, aux_info: Optional[Dict] = None,
+                     return_metrics: bool = False):
+        """MSE (+ cosine, load-balance and z terms as configured) of the MoE output against the dense FFN's.
+        Returns the loss, or (loss, {"mse", "cos", "lb", "z"}) with ``return_metrics``."""
+        student, teacher, aux = moe_output, target, aux_info
+        have_aux = aux is not None and aux.get("router_logits") is not None
         mse = F.mse_loss(student.float(), teacher.float())
         loss, parts = mse, {"mse": float(mse.detach())}
         if self.cfg.use_cosine_loss:
@@ -340,21 +365,32 @@ class SparseDistillationTrainer:
                                           teacher.float().reshape(-1, teacher.shape[-1]), dim=-1).mean()
             loss = loss + self.cfg.cosine_loss_weight * cos
             parts["cos"] = float(cos.detach())
-        if self.cfg.use_load_balancing and self.cfg.moe_routing == "token_choice":
+        if have_aux and self.cfg.use_load_balancing and self.cfg.moe_routing == "token_choice":
             lb = self.compute_load_balancing_loss(aux["router_logits"], aux["expert_counts"])
             loss = loss + self.cfg.load_balancing_weight * lb
             parts["lb"] = float(lb.detach())
-        if self.cfg.use_z_loss:
+        if have_aux and self.cfg.use_z_loss:
             z = self.compute_z_loss(aux["router_logits"])
             loss = loss + self.cfg.z_loss_weight * z
             parts["z"] = float(z.detach())
-        return loss, parts
+        return (loss, parts) if return_metrics else loss
 
-    def train_step(self, i: int, x: torch.Tensor, target: torch.Tensor) -> Dict[str, float]:
+    def train_step(self, i, x: torch.Tensor = None, target: torch.Tensor = None, return_metrics: bool = False):
+        """One update of layer ``i`` on (FFN input, FFN output): returns the loss parts of that layer.  In the
+        reference's form, ``train_step(activations)`` with ``{layer: FFNActivation}`` from a forward pass of the
+        dense model, every layer in the dict gets one update and the result is ``{layer: loss}`` (the parts
+        instead of the loss with ``return_metrics``)."""
+        if isinstance(i, dict):
+            out = {}
+            for k, act in i.items():
+                parts = self.train_step(int(k), act.input, act.output)
+                out[int(k)] = parts if return_metrics else parts["loss"]
+            self.step_count += 1
+            return out
         layer = self.moe_layers[str(i)].to(self.device).train()
         opt = self._get_optimizer(i)
         out, aux = layer(x.to(self.device), return_aux=True)
-        loss, parts = self.compute_loss(out, target.to(self.device), aux)
+        loss, parts = self.compute_loss(out, target.to(self.device), aux, return_metrics=True)
         opt.zero_grad(set_to_none=True)
         loss.backward()
         torch.nn.utils.clip_grad_norm_(layer.parameters(), self.cfg.max_grad_norm)
@@ -472,7 +508,25 @@ class SparseDistillationTrainer:
         assign, cent = kmeans(Y, n_clusters, spherical=True)
         return X, Y, assign, cent
 
-    def analyze_cluster_quality(self, i: int, ks=(4, 8, 16), batches=None) -> Dict[int, Dict[str, float]]:
+    def analyze_cluster_quality(self, i=None, ks=(4, 8, 16), batches=None, outputs: torch.Tensor = None,
+                                k_values=None) -> Dict[int, Dict[str, float]]:
+        """Cluster quality of layer ``i``'s FFN outputs for each cluster count in ``ks``.  In the reference's form,
+        ``analyze_cluster_quality(outputs, k_values)``, the (N, d_model) outputs are given directly
+        (distill.py:1394-1536)."""
+        if torch.is_tensor(i):
+            outputs, i = i, None
+            if not isinstance(ks, tuple) or ks != (4, 8, 16):
+                k_values = ks if k_values is None else k_values
+        if outputs is not None:
+            res = {}
+            Y = outputs.reshape(-1, outputs.shape[-1]).float()
+            for k in (k_values or range(4, 65, 2)):
+                if k > Y.shape[0]:
+                    break
+                assign, cent = kmeans(Y, int(k), spherical=True)
+                res[int(k)] = cluster_quality(F.normalize(Y, dim=-1), assign, cent)
+            return res
+        ks = k_values if k_values is not None else ks
         out = {}
         batches = list(batches) if batches is not None else None
         for k in ks:
@@ -542,7 +596,7 @@ class SparseDistillationTrainer:
                                                     temp, bal)
                     xt = x
                 out, aux = layer(x, return_aux=True)
-                loss, parts = self.compute_loss(out, y, aux)
+                loss, parts = self.compute_loss(out, y, aux, return_metrics=True)
                 logp = F.log_softmax(layer.get_router_logits(xt.detach()).reshape(-1, layer.n_experts).float(), -1)
                 kl = F.kl_div(logp, targets, reduction="batchmean")
                 ent = -(logp.exp() * logp).sum(-1).mean()
@@ -595,12 +649,16 @@ class SparseDistillationTrainer:
 
     # -------------------------------------------------------------- evaluation
     @torch.no_grad()
-    def evaluate(self, n_batches: int = 4, batches=None, max_batches: int = 100) -> Dict[int, Dict[str, float]]:
+    def evaluate(self, n_batches=4, batches=None, max_batches: Optional[int] = 100,
+                 dataloader=None) -> Dict[int, Dict[str, float]]:
         """Per layer: MSE, cosine similarity and relative MSE of the MoE layer against the dense FFN - on what the
         FFN sees when the model runs on ``batches`` (token ids; reference: distill.py:2849-2922) or, without
         batches, on ``n_batches`` random unit-norm inputs."""
+        if not isinstance(n_batches, int):                       # evaluate(dataloader, max_batches): the reference's form
+            batches, n_batches = n_batches, 4
+        batches = dataloader if batches is None else batches
         if batches is not None:
-            return self._evaluate_on_data(batches, max_batches)
+            return self._evaluate_on_data(batches, max_batches if max_batches is not None else 10 ** 9)
         out = {}
         for i in range(len(self.ffn)):
             layer = self.moe_layers[str(i)].to(self.device).eval()

@@ -40,8 +40,19 @@ class ExpertStats:
 class DynamicExpertLayer(nn.Module):
     """SwiGLU experts with per-expert hidden width ``d_ffs[e]``; token-choice forward."""
 
-    def __init__(self, d_model: int, d_ffs: List[int]):
+    def __init__(self, d_model: int = None, d_ffs: List[int] = None, d_ff_per_expert: List[int] = None,
+                 activation: str = "swiglu", n_experts: int = None):
+        """``DynamicExpertLayer(d_model, [f_0, f_1, ...])``, or in the reference's order
+        ``DynamicExpertLayer(n_experts, d_model, d_ff_per_expert)`` (dynamic_experts.py:61)."""
         super().__init__()
+        if d_ff_per_expert is not None and not isinstance(d_ffs, (list, tuple)):
+            # reference order: the first positional is the expert count, the second the model width
+            first, second = d_model, d_ffs
+            if n_experts is None and second is not None:
+                n_experts, d_model = first, second
+            d_ffs = d_ff_per_expert
+        assert activation == "swiglu", "dynamic experts are SwiGLU experts"
+        assert n_experts is None or n_experts == len(d_ffs), "one width per expert"
         self.d_model, self.d_ffs = d_model, list(d_ffs)
         self.w1 = nn.ParameterList([nn.Parameter(torch.randn(d_model, f) * d_model ** -0.5) for f in d_ffs])
         self.w2 = nn.ParameterList([nn.Parameter(torch.randn(d_model, f) * d_model ** -0.5) for f in d_ffs])
@@ -57,8 +68,12 @@ class DynamicExpertLayer(nn.Module):
     def forward_expert(self, x: torch.Tensor, expert_idx: int) -> torch.Tensor:
         return self.expert(expert_idx, x)
 
-    def get_expert_params(self, e: int) -> int:
-        return 3 * self.d_model * self.d_ffs[e]
+    @property
+    def d_ff_per_expert(self) -> List[int]:
+        return self.d_ffs
+
+    def get_expert_params(self, expert_idx: int) -> int:
+        return 3 * self.d_model * self.d_ffs[expert_idx]
 
     def get_total_params(self) -> int:
         return sum(self.get_expert_params(e) for e in range(self.n_experts))
@@ -72,7 +87,22 @@ class DynamicExpertLayer(nn.Module):
         u = usage.float().cpu()
         return float(top_k * (sizes * u / u.sum().clamp(min=1e-12)).sum())
 
-    def forward(self, x: torch.Tensor, idx: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, idx: torch.Tensor = None, weights: torch.Tensor = None, *,
+                expert_weights: torch.Tensor = None, token_indices: torch.Tensor = None):
+        """Token choice: ``forward(x (T, d), idx (T, k), weights (T, k))`` -> (T, d).
+        Expert choice (the reference's form, dynamic_experts.py:108-146): ``forward(x (B, S, d), expert_weights
+        (B, E, C), token_indices (B, E, C))`` -> (output (B, S, d), {expert: its (B, C, d) outputs})."""
+        if expert_weights is not None or (x.dim() == 3 and idx is not None and idx.is_floating_point()):
+            ew = expert_weights if expert_weights is not None else idx
+            ti = token_indices if token_indices is not None else weights
+            out = torch.zeros_like(x)
+            per_expert = {}
+            for e in range(self.n_experts):
+                gi = ti[:, e, :].unsqueeze(-1).expand(-1, -1, x.shape[-1])
+                y = self.expert(e, torch.gather(x, 1, gi))
+                per_expert[e] = y
+                out = out.scatter_add(1, gi, y * ew[:, e, :].unsqueeze(-1).to(y.dtype))
+            return out, per_expert
         out = torch.zeros_like(x)
         for e in range(self.n_experts):
             tok, slot = (idx == e).nonzero(as_tuple=True)
@@ -81,9 +111,10 @@ class DynamicExpertLayer(nn.Module):
         return out
 
 
-def interpolate_expert_weights(w1, w2, w3, new_f: int):
+def interpolate_expert_weights(old_w1, old_w2, old_w3, new_d_ff: int):
     """Resize one expert's hidden width.  Growing interpolates the hidden axis linearly; shrinking
-    keeps the ``new_f`` hidden units with the largest L2 importance ||w1_j|| ||w2_j|| ||w3_j||."""
+    keeps the ``new_d_ff`` hidden units with the largest L2 importance ||w1_j|| ||w2_j|| ||w3_j||."""
+    w1, w2, w3, new_f = old_w1, old_w2, old_w3, new_d_ff
     f = w1.shape[1]
     if new_f == f:
         return w1, w2, w3
@@ -141,7 +172,7 @@ class DynamicExpertTracker:
         """``expert_outputs[e]`` / ``targets[e]``: (n_e, d_model) rows routed to expert e and what they should be."""
         for e, out in expert_outputs.items():
             if e in targets and out.numel():
-                self.expert_stats[e].total_loss += float(F.mse_loss(out.float(), targets[e].float(), reduction="sum"))
+                self.expert_stats[e].total_loss += float(F.mse_loss(out.detach().float(), targets[e].float(), reduction="sum"))
                 self.expert_stats[e].token_count += out.shape[0]
         self.step_count += 1
 
@@ -203,9 +234,15 @@ def print_active_params_report(layers: Dict[int, DynamicExpertLayer], top_k: int
 
 
 @torch.no_grad()
-def reallocate_expert_layer(layer: DynamicExpertLayer, plan: Dict[int, int]) -> DynamicExpertLayer:
+def reallocate_expert_layer(layer: DynamicExpertLayer, plan=None, device=None, new_d_ff=None) -> DynamicExpertLayer:
+    """Resize the experts of ``layer`` in place.  ``plan``: {expert: new width}; a list of one width per expert
+    (the reference's ``new_d_ff``, dynamic_experts.py:375-418) is taken as a plan for every expert.  ``device``
+    moves the layer there afterwards."""
+    plan = new_d_ff if plan is None else plan
+    if isinstance(plan, (list, tuple)):
+        plan = {e: int(f) for e, f in enumerate(plan) if int(f) != layer.d_ffs[e]}
     for e, f in plan.items():
         a, b, c = interpolate_expert_weights(layer.w1[e].data, layer.w2[e].data, layer.w3[e].data, f)
         layer.w1[e], layer.w2[e], layer.w3[e] = nn.Parameter(a.contiguous()), nn.Parameter(b.contiguous()), nn.Parameter(c.contiguous())
         layer.d_ffs[e] = f
-    return layer
+    return layer.to(device) if device is not None else layer

@@ -140,11 +140,16 @@ def _ids_of(batch):
 
 
 @torch.no_grad()
-def compute_perplexity(model, batches: Iterable, logits_of=None, pad_token_id: Optional[int] = None,
-                       max_batches: Optional[int] = None, accumulate_routing: bool = False) -> float:
+def compute_perplexity(model, batches: Iterable = None, logits_of=None, pad_token_id: Optional[int] = None,
+                       max_batches: Optional[int] = None, accumulate_routing: bool = False, dataloader=None,
+                       device=None) -> float:
     """Token-weighted next-token perplexity.  Positions whose target is ``pad_token_id`` do not count;
     ``accumulate_routing`` (model = ``SparseModelWrapper``) folds every batch's expert counts into the
-    layers' running totals (reference: finetune_eval.py:388-464)."""
+    layers' running totals (reference: finetune_eval.py:388-464).  The reference's call form
+    ``compute_perplexity(model, dataloader, device, ...)`` works too: batches are moved to ``device``."""
+    batches = dataloader if batches is None else batches
+    if logits_of is not None and not callable(logits_of):        # third positional is a device
+        device, logits_of = logits_of, None
     tot, n = 0.0, 0
     was_training = getattr(model, "training", False)
     model.eval()
@@ -154,6 +159,8 @@ def compute_perplexity(model, batches: Iterable, logits_of=None, pad_token_id: O
         if max_batches is not None and bi >= max_batches:
             break
         ids = _ids_of(batch)
+        if device is not None:
+            ids = ids.to(device)
         logits = _logits(model(ids), logits_of)
         tgt = ids[:, 1:].reshape(-1)
         if pad_token_id is not None:
@@ -263,15 +270,59 @@ def load_finetuned(wrapper: SparseModelWrapper, path: str, optimizer=None) -> in
     return int(ck.get("step", 0))
 
 
-def finetune(wrapper: SparseModelWrapper, batches: Iterable, steps: int, lr: float = 1e-5,
-             lb_weight: float = 0.01, z_weight: float = 0.001, moe_only: bool = True, out_dir: Optional[str] = None,
-             eval_batches=None, logits_of=None, eval_every: Optional[int] = None, lr_schedule: bool = False,
-             resume: Optional[str] = None, pad_token_id: Optional[int] = None, max_grad_norm: float = 1.0,
-             log_every: int = 0, use_8bit_adam: bool = False) -> Dict[str, object]:
+_REF_ORDER = ("model", "train_dataloader", "eval_dataloader", "device", "epochs", "lr", "eval_every", "max_steps",
+              "use_8bit_adam", "pad_token_id", "moe_only", "load_balance_weight", "z_loss_weight", "resume_checkpoint",
+              "save_dir", "use_lr_schedule")
+_OWN_ORDER = ("wrapper", "batches", "steps", "lr", "lb_weight", "z_weight", "moe_only", "out_dir", "eval_batches",
+              "logits_of", "eval_every", "lr_schedule", "resume", "pad_token_id", "max_grad_norm", "log_every",
+              "use_8bit_adam")
+
+
+def finetune(*args, **kwargs) -> Dict[str, object]:
+    """Fine-tune a converted model; see ``_finetune`` for the arguments.  Positional arguments are read in this
+    file's order ``(wrapper, batches, steps, lr, ...)`` when the third one is a step count (or absent), and in the
+    reference's order ``(model, train_dataloader, eval_dataloader, device, epochs, lr, ...)`` otherwise."""
+    order = _REF_ORDER if len(args) >= 3 and not isinstance(args[2], int) else _OWN_ORDER
+    for name, value in zip(order, args):
+        if name in kwargs:
+            raise TypeError(f"finetune() got multiple values for argument '{name}'")
+        kwargs[name] = value
+    return _finetune(**kwargs)
+
+
+def _finetune(wrapper: SparseModelWrapper = None, batches: Iterable = None, steps=None, lr: float = 1e-5,
+             lb_weight: Optional[float] = None, z_weight: Optional[float] = None, moe_only: bool = True,
+             out_dir: Optional[str] = None, eval_batches=None, logits_of=None, eval_every: Optional[int] = None,
+             lr_schedule: bool = False, resume: Optional[str] = None, pad_token_id: Optional[int] = None,
+             max_grad_norm: float = 1.0, log_every: int = 0, use_8bit_adam: bool = False, *,
+             model=None, train_dataloader=None, eval_dataloader=None, device=None, epochs: int = 1,
+             max_steps: Optional[int] = None, load_balance_weight: Optional[float] = None,
+             z_loss_weight: Optional[float] = None, resume_checkpoint: Optional[str] = None,
+             save_dir: Optional[str] = None, use_lr_schedule: Optional[bool] = None) -> Dict[str, object]:
     """Language-model fine-tuning of the converted model: cross-entropy plus the routers' auxiliary losses,
     gradient clipping, constant LR or cosine decay to 10 %, evaluation every ``eval_every`` steps with
     ``latest_checkpoint.pt`` (with optimizer state, for ``resume``) and ``best_checkpoint.pt`` under
-    ``out_dir`` (reference: finetune_eval.py:498-693)."""
+    ``out_dir`` (reference: finetune_eval.py:498-693).
+
+    The keyword names of the reference are accepted as well (``model``, ``train_dataloader``, ``eval_dataloader``,
+    ``device``, ``epochs``, ``max_steps``, ``load_balance_weight``, ``z_loss_weight``, ``resume_checkpoint``,
+    ``save_dir``, ``use_lr_schedule``)."""
+    wrapper = model if wrapper is None else wrapper
+    batches = train_dataloader if batches is None else batches
+    eval_batches = eval_dataloader if eval_batches is None else eval_batches
+    lb_weight = (0.01 if load_balance_weight is None else load_balance_weight) if lb_weight is None else lb_weight
+    z_weight = (0.001 if z_loss_weight is None else z_loss_weight) if z_weight is None else z_weight
+    resume = resume_checkpoint if resume is None else resume
+    out_dir = save_dir if out_dir is None else out_dir
+    lr_schedule = lr_schedule if use_lr_schedule is None else use_lr_schedule
+    if device is not None:
+        wrapper.to(device)
+        batches = [_to_device(b, device) for b in batches]
+        eval_batches = [_to_device(b, device) for b in eval_batches] if eval_batches is not None else None
+    if steps is None:
+        n = len(batches) if hasattr(batches, "__len__") else None
+        steps = max_steps if n is None else min(max_steps or epochs * n, epochs * n)
+        assert steps is not None, "give steps / max_steps for a data source without a length"
     if moe_only:
         freeze_all_but_moe(wrapper)
     params = [p for p in wrapper.model.parameters() if p.requires_grad]
@@ -324,6 +375,12 @@ def finetune(wrapper: SparseModelWrapper, batches: Iterable, steps: int, lr: flo
                 if out_dir:
                     _save(os.path.join(out_dir, "best_checkpoint.pt"), wrapper, opt, s + 1, ppl, False)
     return {"final_loss": last, "best_ppl": best, "history": history, "optimizer": opt_name}
+
+
+def _to_device(batch, device):
+    if isinstance(batch, dict):
+        return {k: (v.to(device) if torch.is_tensor(v) else v) for k, v in batch.items()}
+    return batch.to(device) if torch.is_tensor(batch) else batch
 
 
 def _token_batches(a, vocab: int, n: int, seed: int):

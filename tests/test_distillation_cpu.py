@@ -316,3 +316,74 @@ def test_reference_names_of_hooks_wrapper_and_helpers():
     assert kept and all(("experts" in n or "router" in n or "expert_bias" in n or "norm" in n) for n in names)
     assert not any(n.endswith("emb.weight") or n.endswith("head.weight") for n in names)
     assert len(freeze_non_moe_layers(wrapper, moe_only=False)) == len(list(wrapper.parameters()))
+
+
+def test_call_forms_of_the_reference_are_accepted():
+    """Constructors and functions of the package can be called the way the reference's are: argument order,
+    keyword names, and what comes back."""
+    from experiments.sparse_distillation import finetune_eval as fe
+    from experiments.sparse_distillation.convert import SparseModelWrapper, replace_ffn_with_moe
+    from experiments.sparse_distillation.dynamic_experts import DynamicExpertLayer
+    from experiments.sparse_distillation.hooks import StreamingFFNExtractor
+    torch.manual_seed(0)
+    # layer with its settings spelled out
+    layer = MoEDistillationLayer(32, 16, 4, capacity_factor=2.0, routing_type="token_choice", mlp_router=True,
+                                 router_hidden_dim=8, router_n_layers=2, use_expert_bias=False)
+    assert (layer.n_experts, layer.d_ff, layer.routing) == (4, 16, "token_choice") and layer.expert_bias is None
+    assert layer.cfg.moe_capacity_factor == 2.0 and layer(torch.randn(2, 5, 32)).shape == (2, 5, 32)
+    assert MoEDistillationLayer(d_model=32, d_ff=16, n_experts=4).routing == "expert_choice"
+    # trainer: default configuration, layer filter, loss with and without metrics, a step on activations
+    m = ToyLM().eval()
+    tr = SparseDistillationTrainer(dense_model=m, config=_cfg(), device="cpu",
+                                   layer_filter=lambda name, mod: name.endswith("mlp"))
+    assert len(tr.ffn) == 2 and SparseDistillationTrainer(dense_model=ToyLM()).cfg.n_experts == 16
+    x = torch.randn(2, 6, 64)
+    y = tr._teacher(0, x)
+    out, aux = tr.moe_layers["0"](x, return_aux=True)
+    loss = tr.compute_loss(moe_output=out, target=y, aux_info=aux)
+    loss2, metrics = tr.compute_loss(out, y, aux, return_metrics=True)
+    assert torch.is_tensor(loss) and torch.equal(loss, loss2) and "mse" in metrics
+    assert float(tr.compute_loss(out, y)) > 0                              # no routing information: MSE (+ cosine)
+    assert float(tr.compute_load_balancing_loss(router_logits=aux["router_logits"], expert_counts=aux["expert_counts"])) > 0
+    assert float(tr.compute_z_loss(router_logits=aux["router_logits"])) >= 0
+    ids = torch.randint(0, 256, (2, 10))
+    acts = StreamingFFNExtractor(m).extract(ids)
+    step = tr.train_step(acts)
+    assert set(step) == {0, 1} and all(isinstance(v, float) for v in step.values())
+    assert "mse" in tr.train_step(acts, return_metrics=True)[0]
+    q = tr.analyze_cluster_quality(acts[0].output, [2, 3])
+    assert set(q) == {2, 3} and "balance" in q[2]
+    assert set(tr.evaluate([ids, ids], max_batches=1)) == {0, 1} and set(tr.evaluate(dataloader=[{"input_ids": ids}])) == {0, 1}
+    # conversion: the reference's argument order and keyword names
+    wrapper = SparseModelWrapper(base_model=replace_ffn_with_moe(m, tr.get_moe_layers(), layer_indices=[0, 1],
+                                                                 ffn_name_pattern="mlp", inplace=True),
+                                 moe_layers=tr.get_moe_layers(), layer_indices=[0, 1])
+    assert wrapper.moe_paths == {0: "blocks.0.mlp", 1: "blocks.1.mlp"}
+    copy_ = replace_ffn_with_moe(ToyLM(), tr.get_moe_layers(), [0], inplace=False)
+    assert type(copy_.blocks[0].mlp).__name__ == "MoEDistillationLayer" and type(copy_.blocks[1].mlp).__name__ != "MoEDistillationLayer"
+    # perplexity and fine-tuning with data loaders, a device and the reference's keywords
+    batches = [{"input_ids": torch.randint(0, 256, (2, 12))} for _ in range(3)]
+    p1 = fe.compute_perplexity(wrapper, batches, "cpu", pad_token_id=None, max_batches=2, accumulate_routing=True)
+    assert p1 == fe.compute_perplexity(model=wrapper, dataloader=batches, device="cpu", max_batches=2)
+    rep = fe.finetune(wrapper, batches, batches[:1], "cpu", epochs=2, lr=1e-3, eval_every=3, max_steps=5,
+                      use_8bit_adam=False, moe_only=True, load_balance_weight=0.01, z_loss_weight=0.001,
+                      use_lr_schedule=True)
+    assert rep["history"][-1]["step"] == 5 and rep["optimizer"] == "adamw"
+    rep2 = fe.finetune(model=wrapper, train_dataloader=batches, eval_dataloader=batches[:1], device="cpu", epochs=1)
+    assert rep2["history"][-1]["step"] == 3
+    # dynamic experts in the reference's argument order and its expert-choice forward
+    dyn = DynamicExpertLayer(3, 16, [8, 16, 24])
+    assert dyn.n_experts == 3 and dyn.d_model == 16 and dyn.d_ff_per_expert == [8, 16, 24]
+    assert dyn.get_expert_params(expert_idx=2) == 3 * 16 * 24
+    xb = torch.randn(2, 7, 16)
+    ti = torch.stack([torch.stack([torch.randperm(7)[:3] for _ in range(3)]) for _ in range(2)])
+    ew = torch.rand(2, 3, 3)
+    yb, per = dyn(xb, ew, ti)
+    want = torch.zeros_like(xb)
+    for b in range(2):
+        for e in range(3):
+            want[b].index_add_(0, ti[b, e], dyn.expert(e, xb[b, ti[b, e]]) * ew[b, e].unsqueeze(1))
+    assert torch.allclose(yb, want, atol=1e-5) and per[1].shape == (2, 3, 16)
+    a, b_, c = interpolate_expert_weights(old_w1=dyn.w1[0].data, old_w2=dyn.w2[0].data, old_w3=dyn.w3[0].data, new_d_ff=12)
+    assert a.shape == (16, 12) and c.shape == (12, 16)
+    assert reallocate_expert_layer(dyn, new_d_ff=[8, 32, 24], device="cpu").d_ffs == [8, 32, 24]

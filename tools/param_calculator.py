@@ -169,7 +169,10 @@ class ModelParams:
 def calculate_params(cfg: ModelParams) -> dict:
     """Analytic totals of a ``ModelParams`` model: q/k/v/o projections, two norms per layer and a final one, a
     three-matrix SwiGLU in the dense layers, a d -> 128 -> E router MLP and E three-matrix experts in the MoE
-    layers.  Active = everything but the experts, plus ``moe_top_k / n_experts`` of the experts."""
+    layers.  Active = everything but the experts, plus ``moe_top_k / n_experts`` of the experts.  (The reference's
+    function counts one d x E matrix per router; its models, like the ones here, have the two-matrix router, so
+    this count equals what an instantiated model holds - router_params and the totals differ from the
+    reference's by that amount.)"""
     L, d = cfg.n_layers, cfg.d_model
     moe = set(range(L)) if cfg.moe_layers is None else set(cfg.moe_layers)
     n_moe, n_dense = len(moe), L - len(moe)
