@@ -375,11 +375,13 @@ class SparseDistillationTrainer:
             parts["z"] = float(z.detach())
         return (loss, parts) if return_metrics else loss
 
-    def train_step(self, i, x: torch.Tensor = None, target: torch.Tensor = None, return_metrics: bool = False):
+    def train_step(self, i=None, x: torch.Tensor = None, target: torch.Tensor = None, return_metrics: bool = False,
+                   activations=None):
         """One update of layer ``i`` on (FFN input, FFN output): returns the loss parts of that layer.  In the
         reference's form, ``train_step(activations)`` with ``{layer: FFNActivation}`` from a forward pass of the
         dense model, every layer in the dict gets one update and the result is ``{layer: loss}`` (the parts
         instead of the loss with ``return_metrics``)."""
+        i = activations if i is None else i
         if isinstance(i, dict):
             out = {}
             for k, act in i.items():

@@ -350,7 +350,7 @@ def test_call_forms_of_the_reference_are_accepted():
     acts = StreamingFFNExtractor(m).extract(ids)
     step = tr.train_step(acts)
     assert set(step) == {0, 1} and all(isinstance(v, float) for v in step.values())
-    assert "mse" in tr.train_step(acts, return_metrics=True)[0]
+    assert "mse" in tr.train_step(activations=acts, return_metrics=True)[0]
     q = tr.analyze_cluster_quality(acts[0].output, [2, 3])
     assert set(q) == {2, 3} and "balance" in q[2]
     assert set(tr.evaluate([ids, ids], max_batches=1)) == {0, 1} and set(tr.evaluate(dataloader=[{"input_ids": ids}])) == {0, 1}
