@@ -27,9 +27,10 @@ def main(argv=None):
     return analyze_config(cfg, a.config or a.preset)
 
 
-def analyze_config(cfg, name: str = ""):
+def analyze_config(config, name: str = ""):
     """Totals, active parameters and the per-layer-kind breakdown of one configuration (counted on a meta-device
     instance); prints the report and returns the counts."""
+    cfg = config
     import kolmogorov_moe_architecture_b200 as kmoe
     if name:
         print(f"== {name}")

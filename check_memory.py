@@ -54,10 +54,10 @@ def main(argv=None):
 
 
 # ---- names of the reference's script, for code that imports them from here
-def load_config(path):
+def load_config(path=None, config_path=None):
     """The YAML file as a dict."""
     from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml
-    return load_yaml(path)
+    return load_yaml(config_path if path is None else path)
 
 
 def print_memory(step, label):

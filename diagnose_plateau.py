@@ -96,10 +96,10 @@ def main(argv=None):
 
 
 # ---- names of the reference's script, for code that imports them from here
-def load_config(path):
+def load_config(path=None, config_path=None):
     """The YAML file as a dict."""
     from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml
-    return load_yaml(path)
+    return load_yaml(config_path if path is None else path)
 
 
 def create_model_from_config(config_dict):
@@ -116,7 +116,7 @@ def analyze_gradients(model):
     return gradient_census(model)
 
 
-RouterAnalyzer.register_hooks = lambda self: self          # the hooks are registered by the constructor
+RouterAnalyzer.register_hooks = lambda self, model=None, n_experts=None: self    # registered by the constructor
 RouterAnalyzer.remove_hooks = RouterAnalyzer.close
 RouterAnalyzer.get_stats = RouterAnalyzer.report
 

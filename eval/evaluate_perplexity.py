@@ -47,7 +47,8 @@ def windows(tokens: List[int], seq_len: int, stride: int) -> List[torch.Tensor]:
     return [torch.tensor(tokens[i:i + seq_len], dtype=torch.long) for i in range(0, len(tokens) - seq_len, stride)]
 
 
-def prepare_eval_data(ds: EvalDataset, tokenizer, target_tokens=3_000_000, seq_len=2048, stride=512):
+def prepare_eval_data(dataset_config: EvalDataset, tokenizer, target_tokens=3_000_000, seq_len=2048, stride=512):
+    ds = dataset_config
     try:
         from datasets import load_dataset
         args = (ds.hf_name, ds.hf_config) if ds.hf_config else (ds.hf_name,)
@@ -153,10 +154,10 @@ def main(argv=None):
 
 
 # ---- names of the reference's script, for code that imports them from here
-def load_config(path):
+def load_config(path=None, config_path=None):
     """The YAML file as a dict."""
     from kolmogorov_moe_architecture_b200.utils.config_io import load_yaml
-    return load_yaml(path)
+    return load_yaml(config_path if path is None else path)
 
 
 def load_model_from_checkpoint(checkpoint_path, config_path, device="cuda"):

@@ -28,9 +28,9 @@ from ..utils.config_io import load_yaml, model_config_tolerant
 
 
 # ----------------------------------------------------------------------------------------- configuration, ranks
-def load_config(path: str) -> Dict[str, Any]:
-    """The YAML file as a dict."""
-    return load_yaml(path)
+def load_config(path: str = None, config_path: str = None) -> Dict[str, Any]:
+    """The YAML file as a dict (``config_path``: the keyword some of the reference's scripts use)."""
+    return load_yaml(config_path if path is None else path)
 
 
 def setup_distributed() -> Tuple[int, int, int]:
@@ -258,8 +258,9 @@ def create_scheduler(optimizer, config: Dict[str, Any], total_steps: int) -> War
 class CosineWarmupScheduler(WarmupCosine):
     """train_custom.py's scheduler: absolute ``max_lr`` / ``min_lr`` instead of a ratio."""
 
-    def __init__(self, optimizer, warmup_steps: int, total_steps: int, max_lr: Optional[float] = None,
-                 min_lr: Optional[float] = None):
+    def __init__(self, optimizer, warmup_steps: int, max_steps: int = None, max_lr: Optional[float] = None,
+                 min_lr: Optional[float] = None, total_steps: int = None):
+        total_steps = max_steps if total_steps is None else total_steps
         if max_lr is not None:
             for g in optimizer.param_groups:
                 g["lr"] = max_lr
@@ -436,8 +437,8 @@ class CUDAPrefetcher:
     """Iterates a loader one batch ahead: the next batch's host-to-device copy runs on a side stream while the
     current one is in use.  On a machine without a GPU it is the loader itself."""
 
-    def __init__(self, loader: Iterable, device=None):
-        self.loader = loader
+    def __init__(self, dataloader: Iterable, device=None):
+        self.loader = dataloader
         self.device = torch.device(device) if device is not None else _device_of(0)
         self.stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
 

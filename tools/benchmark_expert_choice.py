@@ -24,7 +24,8 @@ import torch
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-def scatter_loop(out, w_out, idx):
+def scatter_loop(output, weighted_outputs, token_indices):
+    out, w_out, idx = output, weighted_outputs, token_indices
     B, E, C, d = w_out.shape
     for b in range(B):
         for e in range(E):
@@ -32,7 +33,8 @@ def scatter_loop(out, w_out, idx):
     return out
 
 
-def scatter_vectorised(out, w_out, idx):
+def scatter_vectorised(output, weighted_outputs, token_indices):
+    out, w_out, idx = output, weighted_outputs, token_indices
     B, E, C, d = w_out.shape
     return out.scatter_add(1, idx.reshape(B, E * C, 1).expand(-1, -1, d), w_out.reshape(B, E * C, d))
 

@@ -43,8 +43,9 @@ def gradient_flow(model, ids) -> dict:
     return gradient_census(model)
 
 
-def calculate_gini(values) -> float:
+def calculate_gini(array) -> float:
     """Gini coefficient of non-negative values (0 = all equal, -> 1 = one holds everything)."""
+    values = array
     v = torch.as_tensor(values, dtype=torch.float64).flatten().clamp(min=0).sort().values
     n, tot = v.numel(), float(v.sum())
     if n == 0 or tot == 0:
@@ -86,11 +87,12 @@ def analyze_router_collapse(model, n_samples: int = 8, seq_len: int = 64, device
 
 
 @torch.no_grad()
-def run_evaluation(model, cfg, n_batches: int = 8, device: str = "cpu", data: str = None, batch_size: int = 2,
-                   seq_len: int = None) -> dict:
+def run_evaluation(model, config=None, n_batches: int = 8, device: str = "cpu", data: str = None, batch_size: int = 2,
+                   seq_len: int = None, cfg=None) -> dict:
     """Mean loss / perplexity of head 0 (next token) and of the full multi-token objective over batches from a
     uint16 token file, or over random tokens when there is none - where a trained model should sit near
     ln(vocab) and a broken one far above (reference: tools/diagnose_training.py:354-467)."""
+    cfg = config if cfg is None else cfg
     import math
     import numpy as np
     S = seq_len or min(256, cfg.max_seq_len)

@@ -34,8 +34,11 @@ def _gini(x: torch.Tensor) -> float:
 
 
 @torch.no_grad()
-def analyze_router_entropy(model, n_samples: int = 50, seq_len: int = 256, generator=None) -> Tuple[Dict, int, int]:
+def analyze_router_entropy(model, n_samples: int = 50, seq_len: int = 256, device=None,
+                           generator=None) -> Tuple[Dict, int, int]:
     base = getattr(model, "_orig_mod", model)
+    if device is not None:
+        base.to(device)
     was_training = base.training
     base.eval()
     dev = next(base.parameters()).device
