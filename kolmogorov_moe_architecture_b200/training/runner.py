@@ -333,7 +333,7 @@ def run_training(spec: RunSpec) -> Dict[str, Any]:
     hf = y.get("huggingface") or {}
     logger = MetricLogger(spec.jsonl, spec.wandb or bool(wb.get("enabled", False)) or bool(hf.get("use_wandb", False)),
                           wb.get("project", spec.wandb_project), spec.wandb_run or wb.get("run_name"), y,
-                          tensorboard_dir=hf.get("logging_dir"), rank=rank, entity=wb.get("entity"))
+                          rank=rank, entity=wb.get("entity"))
     timer = PhaseTimer(enabled=spec.profile, device=device)
     if spec.profile:
         engine.timer = timer                   # forward / backward / optimizer next to data / step
