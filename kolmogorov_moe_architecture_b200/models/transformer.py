@@ -207,6 +207,7 @@ class MoETransformer(nn.Module):
             "moe_layers": moe_p, "standard_layers": std_p, "n_moe_layers": n_moe,
             "n_standard_layers": n_std, "n_mamba_layers": n_mamba, "n_attention_layers": n_attn,
             "final_norm": _numel(self.final_norm), "lm_heads": _numel(self.lm_heads),
+            "lm_head": _numel(self.lm_heads),          # the single-head name older callers (and the reference's tests) use
             "total": total, "total_billions": total / 1e9, "active": active,
             "active_billions": active / 1e9, "sparsity": 1.0 - active / max(total, 1),
         }

@@ -6,9 +6,10 @@ tests are skipped where there is none.  Each script is started in a child proces
 ``moe_arch`` first, so that the script's own ``sys.path`` entry for its tree no longer decides what ``moe_arch``
 is.  A script passes when it exits 0, prints its check marks and no failure mark.
 
-Not run: the scripts that build multi-billion-parameter models on the host (``test_3b_config.py``,
-``tests/test_phase1_mvp.py`` and its siblings print a key the reference itself lacks and stop there, on the
-reference as well as here), and the ones that need a data set from the hub.
+Not run: ``test_3b_config.py`` (builds a 14-billion-parameter model on the host), ``tests/test_phase2_moe.py`` and
+``tests/test_phase3_complete.py`` (they use an older interface and stop at the same line on the reference itself:
+``layer.ffn.router`` of a dense layer, three results from the four-result MoD router), and the scripts that need
+a data set from the hub.
 """
 import os
 import subprocess
@@ -37,6 +38,10 @@ RUNNER = (
     ("test_muon_with_model.py", 6),              # hybrid optimizer on the whole model, a few steps
     ("verify_routing_mamba_fix.py", 8),          # RoutingMamba where a layer is both Mamba and MoE
     ("tests/test_phase4_training.py", 20),       # tokenizer, data, schedule, Muon, trainer, checkpoint, pipeline
+    # shapes, loss, gradients, generation and an 8-layer cut of the 5B preset: two minutes on a CPU, so only with
+    # KMOE_SLOW_TESTS=1 (the script reads ``count_parameters()["lm_head"]``, which the reference itself lacks)
+    pytest.param("tests/test_phase1_mvp.py", 10,
+                 marks=pytest.mark.skipif(os.environ.get("KMOE_SLOW_TESTS") != "1", reason="slow: KMOE_SLOW_TESTS=1")),
 ])
 def test_reference_script_passes_on_this_framework(script, min_checks, tmp_path):
     path = os.path.join(SRC, script)
