@@ -111,20 +111,31 @@ class DynamicExpertLayer(nn.Module):
         return out
 
 
-def interpolate_expert_weights(old_w1, old_w2, old_w3, new_d_ff: int):
-    """Resize one expert's hidden width.  Growing interpolates the hidden axis linearly; shrinking
-    keeps the ``new_d_ff`` hidden units with the largest L2 importance ||w1_j|| ||w2_j|| ||w3_j||."""
+def interpolate_expert_weights(old_w1, old_w2, old_w3, new_d_ff: int, importance: str = "sum",
+                               rescale: str = "sqrt"):
+    """Resize one expert's hidden width (reference: dynamic_experts.py:166-238; the defaults are its rules).
+
+    Growing interpolates the hidden axis linearly and rescales the down projection.  The hidden units of a trained
+    expert are not ordered, so neighbours are close to independent and the output - a sum over the units - grows
+    like the square root of their number: ``rescale="sqrt"`` multiplies w3 by ``sqrt(old / new)`` (on random
+    weights the output norm then stays within 10-35 % of the original).  ``rescale="exact"`` multiplies by
+    ``old / new``, which is right only for weights that vary smoothly along the hidden axis.
+
+    Shrinking keeps the ``new_d_ff`` most important hidden units in their original order.  The importance of unit j
+    is ``||w1_j|| + ||w2_j|| + ||w3_j||`` (``importance="sum"``) or the product of the three norms
+    (``"product"``: the size of the unit's contribution to the output)."""
     w1, w2, w3, new_f = old_w1, old_w2, old_w3, new_d_ff
     f = w1.shape[1]
     if new_f == f:
         return w1, w2, w3
     if new_f < f:
-        imp = w1.norm(dim=0) * w2.norm(dim=0) * w3.norm(dim=1)
+        n1, n2, n3 = w1.norm(dim=0), w2.norm(dim=0), w3.norm(dim=1)
+        imp = n1 * n2 * n3 if importance == "product" else n1 + n2 + n3
         keep = torch.topk(imp, new_f).indices.sort().values
         return w1[:, keep], w2[:, keep], w3[keep]
     up = lambda t: F.interpolate(t.unsqueeze(0), size=new_f, mode="linear", align_corners=True).squeeze(0)
-    scale = (f / new_f) ** 0.5
-    return up(w1), up(w2), up(w3.t()).t() * scale * scale
+    scale = f / new_f if rescale == "exact" else (f / new_f) ** 0.5
+    return up(w1), up(w2), up(w3.t()).t() * scale
 
 
 class DynamicExpertTracker:
