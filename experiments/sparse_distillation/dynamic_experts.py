@@ -145,8 +145,9 @@ class DynamicExpertTracker:
     dynamic_experts.py:241-345 - rank by mean loss, grow the worst, shrink the best, optionally rescale all
     widths so the layer's parameter count stays put)."""
 
-    def __init__(self, n_experts: int, momentum: float = 0.99, initial_d_ff: Optional[int] = None,
-                 d_model: Optional[int] = None, config: Optional[DynamicExpertConfig] = None):
+    def __init__(self, n_experts: int, initial_d_ff: Optional[int] = None, d_model: Optional[int] = None,
+                 config: Optional[DynamicExpertConfig] = None, momentum: float = 0.99):
+        # positional order of the reference: (n_experts, initial_d_ff, d_model, config)
         self.n_experts, self.d_model = n_experts, d_model
         self.config = config or DynamicExpertConfig()
         self.loss = torch.zeros(n_experts)
@@ -195,7 +196,11 @@ class DynamicExpertTracker:
         return self.step_count > 0 and self.step_count % self.config.reallocate_every_n_steps == 0
 
     def compute_reallocation(self) -> Dict[int, int]:
-        """New width for every expert (unchanged ones included)."""
+        """New width for every expert (unchanged ones included): the ``top_k_grow`` experts with the highest mean
+        loss grow, the ``top_k_shrink`` with the lowest shrink.  With ``maintain_param_budget`` all widths are then
+        scaled by ``before / after`` - parameters are linear in the width, so the layer's size really stays what
+        it was (the reference scales by the square root of that ratio, dynamic_experts.py:327-340, which leaves
+        the budget off by the other square root).  Widths are rounded down to multiples of ``round_to``."""
         c = self.config
         rnd = lambda f: max(c.round_to, int(f) // c.round_to * c.round_to)
         ranked = sorted(self.expert_stats.values(), key=lambda s: s.avg_loss, reverse=True)
