@@ -54,3 +54,23 @@ def test_reference_script_passes_on_this_framework(script, min_checks, tmp_path)
     assert r.returncode == 0, tail
     assert r.stdout.count("✓") >= min_checks, tail
     assert "✗" not in r.stdout and "Traceback" not in r.stdout, tail
+
+
+def test_layer_configuration_equals_the_reference_s_committed_sample(capsys):
+    """The reference ships a cluster analysis and the per-layer configuration its generator made from it
+    (``sparse_distillation_output/``): this framework's generator gives the same layers and the same totals."""
+    import json
+    from experiments.sparse_distillation.generate_config import compute_layer_config
+    d = os.path.join(SRC, "sparse_distillation_output")
+    if not os.path.isfile(os.path.join(d, "layer_config.json")):
+        pytest.skip("no sample output in the reference tree")
+    analysis = json.load(open(os.path.join(d, "cluster_analysis.json")))
+    gold = json.load(open(os.path.join(d, "layer_config.json")))
+    ours = compute_layer_config(analysis, gold["target_expansion_ratio"], gold["target_active_ratio"], gold["min_experts"])
+    capsys.readouterr()
+    assert set(ours["layers"]) == set(gold["layers"]) and len(gold["layers"]) > 0
+    for k, g in gold["layers"].items():
+        assert {x: ours["layers"][k][x] for x in ("n_experts", "d_ff_expert", "top_k")} == \
+               {x: g[x] for x in ("n_experts", "d_ff_expert", "top_k")}, k
+    for k, v in gold["stats"].items():
+        assert ours["stats"][k] == pytest.approx(v), k
