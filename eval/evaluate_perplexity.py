@@ -98,19 +98,34 @@ def load_model(checkpoint: Optional[str], config_path: str, device: str, dtype=t
 
 
 def write_reports(results: Dict[str, Dict], meta: Dict, out_md: str):
+    """Markdown table plus a JSON file beside it, in the layout of the reference's committed results
+    (eval/results.md, eval/results_2000step.json): ``{"checkpoint", "config", "settings": {"tokens_per_dataset",
+    "seq_len", "stride"}, "results": {dataset: {"perplexity", "loss", "num_tokens", ...}}}`` and, in addition,
+    ``"average_perplexity"`` and the full ``"meta"``.  A data set that could not be loaded is listed as N/A."""
     os.makedirs(os.path.dirname(os.path.abspath(out_md)), exist_ok=True)
-    good = [r["perplexity"] for r in results.values() if r["num_tokens"] > 0 and math.isfinite(r["perplexity"])]
+    ok = lambda r: r.get("num_tokens", 0) > 0 and math.isfinite(r.get("perplexity", float("nan")))
+    good = [r["perplexity"] for r in results.values() if ok(r)]
     avg = sum(good) / len(good) if good else float("nan")
     with open(out_md, "w") as f:
-        f.write("# Perplexity evaluation\n\n")
+        f.write("# Perplexity Evaluation Results\n\n## Settings\n\n")
+        labels = {"checkpoint": "Checkpoint", "config": "Config", "device": "Device",
+                  "tokens_per_dataset": "Tokens per dataset", "seq_len": "Sequence length", "stride": "Stride"}
         for k, v in meta.items():
-            f.write(f"- {k}: {v}\n")
-        f.write("\n| dataset | perplexity | loss | tokens | seconds |\n|---|---|---|---|---|\n")
+            shown = f"{v:,}" if isinstance(v, int) and k == "tokens_per_dataset" else (f"`{v}`" if isinstance(v, str) else v)
+            f.write(f"- **{labels.get(k, k)}**: {shown}\n")
+        f.write("\n## Results\n\n| Dataset | Perplexity | Loss | Tokens | Time (s) |\n"
+                "|---------|------------|------|--------|----------|\n")
         for name, r in results.items():
-            f.write(f"| {name} | {r['perplexity']:.2f} | {r['loss']:.4f} | {r['num_tokens']:,} | {r.get('seconds', 0):.1f} |\n")
-        f.write(f"\n**average perplexity: {avg:.2f}**\n")
+            if ok(r):
+                f.write(f"| {name} | {r['perplexity']:.2f} | {r['loss']:.4f} | {r['num_tokens']:,} | "
+                        f"{r.get('seconds', 0):.1f} |\n")
+            else:
+                f.write(f"| {name} | N/A | N/A | - | - | *Could not load data* |\n")
+        f.write(f"| **Average** | **{avg:.2f}** | - | - | - |\n")
     with open(os.path.splitext(out_md)[0] + ".json", "w") as f:
-        json.dump({"meta": meta, "results": results, "average_perplexity": avg}, f, indent=2)
+        json.dump({"checkpoint": meta.get("checkpoint"), "config": meta.get("config"),
+                   "settings": {k: meta.get(k) for k in ("tokens_per_dataset", "seq_len", "stride")},
+                   "results": results, "average_perplexity": avg, "meta": meta}, f, indent=2)
     return avg
 
 
@@ -147,8 +162,8 @@ def main(argv=None):
             t0 = time.time()
             results[ds.name] = compute_perplexity(model, seqs, a.batch_size, a.device)
             results[ds.name]["seconds"] = time.time() - t0
-    avg = write_reports(results, {"checkpoint": a.checkpoint, "config": a.config, "seq_len": seq_len,
-                                  "stride": a.stride, "tokens_per_dataset": a.tokens}, a.output)
+    avg = write_reports(results, {"checkpoint": a.checkpoint, "config": a.config, "device": str(a.device),
+                                  "tokens_per_dataset": a.tokens, "seq_len": seq_len, "stride": a.stride}, a.output)
     print(f"average perplexity {avg:.2f} -> {a.output}")
     return results
 

@@ -38,6 +38,15 @@ def test_evaluate_perplexity_synthetic(tiny):
     res = json.load(open(out.replace(".md", ".json")))
     text = json.dumps(res)
     assert "perplexity" in text
+    # the layout of the reference's committed results: checkpoint / config / settings / results[dataset]
+    assert {"checkpoint", "config", "settings", "results"} <= set(res)
+    assert res["settings"] == {"tokens_per_dataset": 2000, "seq_len": 32, "stride": 16}
+    assert {"perplexity", "loss"} <= set(res["results"]["synthetic"])
+    md = open(out).read()
+    assert "| Dataset | Perplexity | Loss | Tokens | Time (s) |" in md and "| **Average** |" in md
+    ev.write_reports({"wikipedia": {"perplexity": float("nan"), "loss": float("nan"), "num_tokens": 0}},
+                     {"checkpoint": "c.pt", "config": "c.yaml"}, out)
+    assert "| wikipedia | N/A | N/A | - | - | *Could not load data* |" in open(out).read()
     # strided windows cover the stream with the requested overlap
     w = ev.windows(list(range(100)), 32, 16)
     assert all(len(x) == 32 for x in w) and w[1][0] == 16
