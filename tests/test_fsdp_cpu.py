@@ -239,3 +239,51 @@ def _recompute_worker(rank, world, tmp):
 
 def test_fsdp_with_activation_recomputation(tmp_path):
     run_ranks(_recompute_worker, 2, str(tmp_path))
+
+
+def _script_api_worker(rank, world, tmp):
+    """The reference's launcher spelled with its own helper names, on two ranks: every rank builds the model,
+    shards it, steps on its own batches, and the two ranks end with the same full state dict and checkpoint."""
+    import torch.distributed as dist
+    import yaml
+    os.environ["KMOE_OFFLINE"] = "1"
+    import train_custom as tc
+    import train_distributed as td
+    cfg = {"model": dict(vocab_size=128, d_model=32, n_layers=2, n_heads=2, n_kv_heads=1, head_dim=16, d_ff=64,
+                         d_ff_expert=32, n_experts=4, moe_top_k=2, moe_layers=[1], mamba_enabled=False,
+                         mamba_layers=[], mod_enabled=False, max_seq_len=16, n_pred_tokens=1,
+                         aux_loss_weights=[1.0], moe_implementation="batched"),
+           "training": dict(max_lr=5e-3, warmup_steps=1, min_lr_ratio=0.1), "optimizer": dict(weight_decay=0.01)}
+    r, w, _ = td.setup_distributed()                   # the group exists already: ranks are read from it
+    assert (r, w) == (rank, world)
+    torch.manual_seed(0)
+    model, _ = td.create_model(cfg, r, w)
+    model = td.wrap_model_with_fsdp(model, r, use_bf16=False, activation_checkpointing=False)
+    opt = td.create_optimizer(model, cfg)
+    sched = td.create_scheduler(opt, cfg, total_steps=6)
+    loader = iter(td.create_dataloader(cfg, td.load_tokenizer(cfg), 16, 2, r, w))
+    first = next(loader)
+    other = [torch.empty_like(first["input_ids"]) for _ in range(w)]
+    dist.all_gather(other, first["input_ids"])
+    assert not torch.equal(other[0], other[1]), "ranks must see different rows"
+    losses = []
+    batch = first
+    for step in range(6):
+        losses.append(td.train_step(model, batch, opt, sched, grad_clip=1.0, accumulation_steps=1, step=step)["loss"])
+    assert losses[-1] < losses[0]
+    import train as single_gpu_script
+    full = single_gpu_script.get_model_state_dict(model)          # gathers the sharded model in full
+    flat = torch.cat([v.reshape(-1).float() for _, v in sorted(full.items())])
+    both = [torch.empty_like(flat) for _ in range(w)]
+    dist.all_gather(both, flat)
+    assert torch.equal(both[0], both[1]), "ranks hold different parameters after the same steps"
+    d = tc.save_checkpoint(model, opt, sched, 6, checkpoint_dir=os.path.join(tmp, "ck"))
+    dist.barrier()
+    ck = os.path.join(tmp, "ck", "checkpoint-6")
+    assert (d == ck) if r == 0 else (d is None)
+    assert sorted(os.listdir(ck)) == ["model.pt", "optimizer.pt", "training_state.pt"]
+    assert tc.load_checkpoint(model, opt, sched, ck) == 6
+
+
+def test_reference_launcher_helpers_on_two_ranks(tmp_path):
+    run_ranks(_script_api_worker, 2, str(tmp_path))
