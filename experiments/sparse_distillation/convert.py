@@ -137,10 +137,14 @@ def convert_to_sparse(model: nn.Module = None, distilled_path: Optional[str] = N
     if trainer is not None:
         layers = {k: v for k, v in trainer.get_moe_layers().items()}
     else:
+        from .distill import checkpoint_config, checkpoint_layers, load_layer_state
         ck = torch.load(distilled_path, map_location="cpu", weights_only=False)
-        cfg = DistillationConfig(**ck["config"])
+        cfg = checkpoint_config(ck)
+        if any(k.startswith("router.mlp.") for sd in checkpoint_layers(ck).values() for k in sd) and not cfg.router_mlp:
+            import dataclasses
+            cfg = dataclasses.replace(cfg, router_mlp=True)
         layers = {}
-        for k, sd in ck["layers"].items():
+        for k, sd in checkpoint_layers(ck).items():
             E, d, f = infer_layer_dims(sd)
             top_k = ck.get("dims", {}).get(k, (d, f, E, cfg.moe_top_k))[3]
             lc = per_layer.get(str(k), {})
@@ -150,7 +154,7 @@ def convert_to_sparse(model: nn.Module = None, distilled_path: Optional[str] = N
                                      f"{lc.get('d_ff_expert')}, the checkpoint holds {E} of width {f}")
                 top_k = int(lc.get("top_k", top_k))
             layer = MoEDistillationLayer(d, f, cfg, n_experts=E, top_k=top_k)
-            layer.load_state_dict(sd)
+            load_layer_state(layer, sd)
             layers[k] = layer
     if random_init:
         for layer in layers.values():

@@ -99,17 +99,21 @@ class DistillationConfig:
 
 
 class MLPRouter(nn.Module):
+    """Router with ``n_layers`` linear layers (with biases) and GELU between them; parameters ``mlp.{0,2,...}``
+    (reference: distill.py:212-243)."""
+
     def __init__(self, d_model: int, n_experts: int, hidden_dim: int = 256, n_layers: int = 2):
         super().__init__()
+        self.d_model, self.n_experts = d_model, n_experts
         dims = [d_model] + [hidden_dim] * (n_layers - 1)
         layers: List[nn.Module] = []
         for a, b in zip(dims[:-1], dims[1:]):
-            layers += [nn.Linear(a, b, bias=False), nn.SiLU()]
-        layers.append(nn.Linear(dims[-1], n_experts, bias=False))
-        self.net = nn.Sequential(*layers)
+            layers += [nn.Linear(a, b), nn.GELU()]
+        layers.append(nn.Linear(dims[-1], n_experts))
+        self.mlp = nn.Sequential(*layers)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.net(x)
+        return self.mlp(x)
 
 
 def _dense_ffn_weights(ffn: nn.Module):
@@ -148,8 +152,16 @@ class MoEDistillationLayer(nn.Module):
         self.cfg, self.d_model, self.d_ff = cfg, d_model, d_ff_expert
         self.n_experts, self.top_k = n_experts or cfg.n_experts, top_k or cfg.moe_top_k
         self.routing = cfg.moe_routing
-        self.router = (MLPRouter(d_model, self.n_experts, cfg.router_hidden_dim, cfg.router_n_layers)
-                       if cfg.router_mlp else nn.Linear(d_model, self.n_experts, bias=False))
+        # The router is the model family's own: a d -> 128 -> E network without biases (``Router`` for token choice,
+        # ``ExpertChoiceRouter`` for expert choice; parameters ``router.router.{0,2}.weight``, the keys of the
+        # reference's distillation checkpoints), or the deeper ``MLPRouter`` when asked for.  Only its logits are
+        # used here: selection, bias and weights are this layer's business.
+        if cfg.router_mlp:
+            self.router = MLPRouter(d_model, self.n_experts, cfg.router_hidden_dim, cfg.router_n_layers)
+        else:
+            mini = AdvancedMoEConfig(d_model=d_model, n_experts=self.n_experts, d_ff_expert=d_ff_expert,
+                                     moe_capacity_factor=cfg.moe_capacity_factor, moe_top_k=min(self.top_k, self.n_experts))
+            self.router = ExpertChoiceRouter(mini) if self.routing == "expert_choice" else Router(mini)
         self.expert_bias = nn.Parameter(torch.zeros(self.n_experts)) if cfg.use_expert_bias else None
         if self.routing == "expert_choice":
             self.experts = GroupedExpertsExpertChoice(self.n_experts, d_model, d_ff_expert)
@@ -161,8 +173,12 @@ class MoEDistillationLayer(nn.Module):
         # while fine-tuning (reference: finetune_eval.py:812-826 switches it on, moe.py:353-421 defines it)
         self.balanced_routing = False
 
+    def router_net(self) -> nn.Module:
+        """The network that maps hidden states to expert logits."""
+        return self.router if isinstance(self.router, MLPRouter) else self.router.router
+
     def get_router_logits(self, x: torch.Tensor) -> torch.Tensor:
-        logits = self.router(x)
+        logits = self.router_net()(x)
         return logits + self.expert_bias if self.expert_bias is not None else logits
 
     def forward(self, x: torch.Tensor, return_aux: bool = False):
@@ -278,6 +294,34 @@ def balanced_topk_targets(scores: torch.Tensor, k: int, max_prob: float, tempera
     t = t / t.sum(-1, keepdim=True)
     E = scores.shape[-1]
     return (1 - balance) * t + balance / E
+
+
+def checkpoint_layers(ck: Dict) -> Dict[str, Dict[str, torch.Tensor]]:
+    """Per-layer state dicts of a distillation checkpoint: this file's layout (``{"layers": {i: state}}``) or the
+    reference's (``{"moe_layers": {"<i>.<key>": tensor}}``, distill.py:2924-2950)."""
+    if "layers" in ck:
+        return {str(k): v for k, v in ck["layers"].items()}
+    out: Dict[str, Dict[str, torch.Tensor]] = {}
+    for key, t in ck["moe_layers"].items():
+        i, rest = key.split(".", 1)
+        out.setdefault(i, {})[rest] = t
+    return out
+
+
+def checkpoint_config(ck: Dict) -> "DistillationConfig":
+    """The configuration stored in a checkpoint: a dict of fields (this file's layout) or the object itself."""
+    c = ck.get("config")
+    if isinstance(c, dict):
+        known = {f for f in DistillationConfig.__dataclass_fields__}
+        return DistillationConfig(**{k: v for k, v in c.items() if k in known})
+    return c if c is not None else DistillationConfig()
+
+
+def load_layer_state(layer: nn.Module, state: Dict[str, torch.Tensor]) -> None:
+    """Load one layer.  Keys of a helper module the reference keeps beside an MLP router (``_base_router.*``, its
+    routing logic; unused weights) are ignored; everything else must match."""
+    state = {k: v for k, v in state.items() if not k.startswith("_base_router.")}
+    layer.load_state_dict(state)
 
 
 def _ids_of_batch(b) -> torch.Tensor:
@@ -619,7 +663,7 @@ class SparseDistillationTrainer:
             with torch.no_grad():
                 for e in range(base.n_experts):
                     dyn.w1[e].copy_(base.experts.w1[e]); dyn.w2[e].copy_(base.experts.w2[e]); dyn.w3[e].copy_(base.experts.w3[e])
-            router = base.router.to(self.device)
+            router = base.router_net().to(self.device)
             tracker = DynamicExpertTracker(base.n_experts)
             make_opt = lambda: torch.optim.AdamW(list(dyn.parameters()) + list(router.parameters()), lr=c.learning_rate)
             opt = make_opt()
@@ -704,6 +748,6 @@ class SparseDistillationTrainer:
 
     def load(self, path: str):
         ck = torch.load(path, map_location="cpu", weights_only=False)
-        for k, sd in ck["layers"].items():
-            self.moe_layers[k].load_state_dict(sd)
+        for k, sd in checkpoint_layers(ck).items():
+            load_layer_state(self.moe_layers[k], sd)
         return ck

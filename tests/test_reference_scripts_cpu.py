@@ -74,3 +74,50 @@ def test_layer_configuration_equals_the_reference_s_committed_sample(capsys):
                {x: g[x] for x in ("n_experts", "d_ff_expert", "top_k")}, k
     for k, v in gold["stats"].items():
         assert ours["stats"][k] == pytest.approx(v), k
+
+
+MAKE_REFERENCE_CHECKPOINT = r"""
+import sys, torch
+sys.path.insert(0, {src!r})
+from Experiments.sparse_distillation import distill as ref_distill      # imported before this repository is on
+import moe_arch                                                         # the path: the reference's own code
+from Experiments.sparse_distillation.distill import DistillationConfig, SparseDistillationTrainer
+assert ref_distill.__file__.startswith({src!r}) and moe_arch.__file__.startswith({src!r})
+sys.path.insert(1, {root!r})
+from experiments.sparse_distillation.example_usage import ToyLM          # only the toy teacher comes from this repo
+torch.manual_seed(0)
+m = ToyLM().eval()
+cfg = DistillationConfig(n_experts=4, moe_top_k=2, moe_routing={routing!r}, d_ff_expert=64, data_free=True,
+                         data_free_steps=3, data_free_batch_size=2, data_free_seq_len=16, use_compile=False,
+                         supervised_routing=False, log_interval=1000, router_mlp={mlp!r})
+tr = SparseDistillationTrainer(dense_model=m, config=cfg, device="cpu")
+tr.distill()
+tr.save({out!r} + "/distilled.pt")
+torch.save(m.state_dict(), {out!r} + "/teacher.pt")
+x = torch.randn(2, 16, 64)
+with torch.no_grad():
+    torch.save({{"x": x, "y0": tr.moe_layers["0"](x), "y1": tr.moe_layers["1"](x)}}, {out!r} + "/io.pt")
+"""
+
+
+@pytest.mark.parametrize("routing,mlp", [("token_choice", False), ("expert_choice", False), ("token_choice", True)])
+def test_distillation_checkpoint_of_the_reference_loads_and_computes_the_same(routing, mlp, tmp_path):
+    """A checkpoint written by the reference's own ``SparseDistillationTrainer`` (run in a child process on its
+    code) is read by ``convert_to_sparse`` here, and the converted layers map the same input to the same output."""
+    import torch
+    from experiments.sparse_distillation.convert import convert_to_sparse
+    from experiments.sparse_distillation.example_usage import ToyLM
+    code = MAKE_REFERENCE_CHECKPOINT.format(src=SRC, root=ROOT, out=str(tmp_path), routing=routing, mlp=mlp)
+    env = dict(os.environ, MOE_DISABLE_COMPILE="1", CUDA_VISIBLE_DEVICES="", HF_HUB_OFFLINE="1")
+    r = subprocess.run([sys.executable, "-c", code], cwd=str(tmp_path), env=env, stdout=subprocess.PIPE,
+                       stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:]
+    m = ToyLM().eval()
+    m.load_state_dict(torch.load(tmp_path / "teacher.pt"))
+    wrapper = convert_to_sparse(dense_model=m, distillation_checkpoint=str(tmp_path / "distilled.pt"), device="cpu")
+    io = torch.load(tmp_path / "io.pt")
+    layers = wrapper.moe_layers
+    assert layers["0"].routing == routing and layers["0"].n_experts == 4 and layers["0"].d_ff == 64
+    with torch.no_grad():
+        for k in ("0", "1"):
+            assert torch.allclose(layers[k](io["x"]), io["y" + k], atol=1e-6), (routing, mlp, k)
