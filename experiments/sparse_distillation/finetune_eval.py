@@ -252,22 +252,32 @@ def aux_losses(wrapper: SparseModelWrapper, lb_weight: float, z_weight: float) -
 
 
 def _save(path: str, wrapper: SparseModelWrapper, opt, step: int, ppl: float, with_optimizer: bool) -> None:
+    """``moe_layers`` (flat ``"<layer>.<key>"`` state dict), ``global_step``, ``best_ppl`` and
+    ``optimizer_state_dict`` are the reference's keys (finetune_eval.py:656-681); ``model`` adds the rest of the
+    model, which fine-tuning without ``moe_only`` changes too."""
     os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
-    moe = {str(i): m.state_dict() for i, m in wrapper.moe_modules().items()}
-    ck = {"model": wrapper.model.state_dict(), "moe_layers": moe, "step": step, "ppl": ppl}
+    ck = {"model": wrapper.model.state_dict(), "moe_layers": wrapper.moe_layers.state_dict(), "step": step,
+          "global_step": step, "ppl": ppl, "best_ppl": ppl}
     if with_optimizer:
-        ck["optimizer"] = opt.state_dict()
+        ck["optimizer_state_dict"] = opt.state_dict()
     torch.save(ck, path)
 
 
 def load_finetuned(wrapper: SparseModelWrapper, path: str, optimizer=None) -> int:
-    """Load weights saved by ``finetune`` (and the optimizer state when one is passed: resume).  Returns
-    the step the file was written at."""
+    """Load weights saved by ``finetune`` here or by the reference's (MoE layers only), and the optimizer state
+    when one is passed (resume).  Returns the step the file was written at."""
+    from .distill import checkpoint_layers, load_layer_state
     ck = torch.load(path, map_location="cpu", weights_only=False)
-    wrapper.model.load_state_dict(ck["model"])
-    if optimizer is not None and "optimizer" in ck:
-        optimizer.load_state_dict(ck["optimizer"])
-    return int(ck.get("step", 0))
+    if "model" in ck:
+        wrapper.model.load_state_dict(ck["model"])
+    elif ck.get("moe_layers") is not None:
+        mods = wrapper.moe_modules()
+        for k, sd in checkpoint_layers({"moe_layers": ck["moe_layers"]}).items():
+            load_layer_state(mods[int(k)], sd)
+    opt_state = ck.get("optimizer_state_dict", ck.get("optimizer"))
+    if optimizer is not None and opt_state is not None:
+        optimizer.load_state_dict(opt_state)
+    return int(ck.get("step", ck.get("global_step", 0)))
 
 
 _REF_ORDER = ("model", "train_dataloader", "eval_dataloader", "device", "epochs", "lr", "eval_every", "max_steps",

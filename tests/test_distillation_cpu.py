@@ -387,3 +387,24 @@ def test_call_forms_of_the_reference_are_accepted():
     a, b_, c = interpolate_expert_weights(old_w1=dyn.w1[0].data, old_w2=dyn.w2[0].data, old_w3=dyn.w3[0].data, new_d_ff=12)
     assert a.shape == (16, 12) and c.shape == (12, 16)
     assert reallocate_expert_layer(dyn, new_d_ff=[8, 32, 24], device="cpu").d_ffs == [8, 32, 24]
+
+
+def test_finetune_checkpoints_carry_the_reference_keys_and_its_files_load(tmp_path):
+    from experiments.sparse_distillation import finetune_eval as fe
+    torch.manual_seed(0)
+    m = ToyLM().eval()
+    tr = SparseDistillationTrainer(m, _cfg(), device="cpu")
+    wrapper = convert_to_sparse(m, trainer=tr)
+    batches = [torch.randint(0, 256, (2, 12)) for _ in range(2)]
+    fe.finetune(wrapper, batches, 2, lr=1e-3, out_dir=str(tmp_path), eval_batches=batches[:1], eval_every=1)
+    ck = torch.load(tmp_path / "latest_checkpoint.pt", weights_only=False)
+    assert {"moe_layers", "global_step", "best_ppl", "optimizer_state_dict"} <= set(ck)
+    assert "0.experts.w1" in ck["moe_layers"] and ck["global_step"] == 2
+    # a file with the reference's keys only (no "model") restores the MoE layers
+    only_moe = {k: ck[k] for k in ("moe_layers", "global_step", "best_ppl")}
+    torch.save(only_moe, tmp_path / "ref_style.pt")
+    before = wrapper.moe_layers["0"].experts.w1.detach().clone()
+    with torch.no_grad():
+        wrapper.moe_layers["0"].experts.w1.add_(1.0)
+    assert fe.load_finetuned(wrapper, str(tmp_path / "ref_style.pt")) == 2
+    assert torch.equal(wrapper.moe_layers["0"].experts.w1, before)
