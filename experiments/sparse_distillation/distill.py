@@ -743,8 +743,16 @@ class SparseDistillationTrainer:
                 for i, a in acc.items()}
 
     def save(self, path: str):
+        """``layers`` / ``dims`` / ``config`` (a plain dict) are what this package reads back; ``moe_layers`` (flat
+        ``"<layer>.<key>"`` state dict), ``d_model``, ``d_ff``, ``layer_indices``, ``layer_dimensions``,
+        ``global_step`` and ``layer_config`` are the reference's keys for the same content (distill.py:2924-2950)."""
         torch.save({"layers": {k: v.state_dict() for k, v in self.moe_layers.items()}, "config": asdict(self.cfg),
-                    "dims": {k: (v.d_model, v.d_ff, v.n_experts, v.top_k) for k, v in self.moe_layers.items()}}, path)
+                    "dims": {k: (v.d_model, v.d_ff, v.n_experts, v.top_k) for k, v in self.moe_layers.items()},
+                    "moe_layers": self.moe_layers.state_dict(), "d_model": self.d_model, "d_ff": self.d_ff_dense,
+                    "dtype": str(self.dtype), "layer_indices": [int(k) for k in self.moe_layers],
+                    "layer_dimensions": {int(k): {"n_experts": v.n_experts, "d_ff": v.d_ff}
+                                         for k, v in self.moe_layers.items()},
+                    "global_step": self.step_count, "layer_config": self.layer_cfg or None}, path)
 
     def load(self, path: str):
         ck = torch.load(path, map_location="cpu", weights_only=False)
