@@ -3,6 +3,11 @@ transformer (counterpart of the reference's ``Experiments/sparse_distillation/ho
 
 FFN modules are discovered by name: the last path component is one of ``mlp``, ``ffn``,
 ``feed_forward``, ``ff`` (HF LLaMA/GPT-style models and this framework's blocks all match).
+
+Layers are numbered in the order they are found, 0 .. n-1.  The reference numbers a layer by the first number in
+its module path (``model.layers.5.mlp`` -> 5, hooks.py:98-106); the two agree whenever every block of the model has
+a feed-forward module, which is what its checkpoints' layer keys assume.  With a ``layer_filter`` that keeps only
+some blocks the numbers differ: here the kept layers are renumbered.
 """
 from __future__ import annotations
 
