@@ -7,7 +7,7 @@ from typing import Dict, Optional
 import torch
 import torch.nn as nn
 
-from .distill import DistillationConfig, MoEDistillationLayer
+from .distill import MoEDistillationLayer
 from .hooks import find_ffn_modules
 
 

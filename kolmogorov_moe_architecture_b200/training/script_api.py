@@ -14,7 +14,6 @@ from __future__ import annotations
 import hashlib
 import math
 import os
-import time
 from dataclasses import dataclass, field, fields
 from typing import Any, Dict, Iterable, Iterator, List, Optional, Tuple
 
