@@ -29,7 +29,8 @@ def _layer_stats(counts: torch.Tensor) -> Dict[str, object]:
     meaningful = int((u > 0.1 / E).sum())                            # at least a tenth of the uniform share
     return {"n_experts": E, "total_tokens": int(tot), "expert_counts": counts.tolist(), "expert_fracs": u.tolist(),
             "entropy": ent, "normalized_entropy": ent / math.log(E) if E > 1 else 0.0, "gini": gini,
-            "min_frac": float(u.min()), "max_frac": float(u.max()), "imbalance": float(u.max() * E),
+            "max_entropy": math.log(E), "min_frac": float(u.min()), "max_frac": float(u.max()),
+            "imbalance": float(u.max() * E), "imbalance_ratio": float(u.max() / (u.min() + 1e-10)),
             "active_experts": int((counts > 0).sum()), "meaningful_experts": meaningful,
             "collapsed": meaningful < 0.5 * E}
 
@@ -41,8 +42,11 @@ def _summarise(per_layer: Dict[int, Dict[str, object]], verbose: bool) -> Dict[s
         ne = [s["normalized_entropy"] for s in live.values()]
         agg = {"mean_normalized_entropy": sum(ne) / len(ne), "min_normalized_entropy": min(ne),
                "worst_max_frac": max(s["max_frac"] for s in live.values()),
+               "worst_min_frac": min(s["min_frac"] for s in live.values()),
                "mean_active_experts": sum(s["active_experts"] for s in live.values()) / len(live),
+               "mean_active_expert_frac": sum(s["active_experts"] / s["n_experts"] for s in live.values()) / len(live),
                "collapsed_layers": [i for i, s in live.items() if s["collapsed"]]}
+        agg["n_collapsed"] = len(agg["collapsed_layers"])
     if verbose:
         for i, s in sorted(live.items()):
             flag = "  COLLAPSED" if s["collapsed"] else ""

@@ -408,3 +408,36 @@ def test_finetune_checkpoints_carry_the_reference_keys_and_its_files_load(tmp_pa
         wrapper.moe_layers["0"].experts.w1.add_(1.0)
     assert fe.load_finetuned(wrapper, str(tmp_path / "ref_style.pt")) == 2
     assert torch.equal(wrapper.moe_layers["0"].experts.w1, before)
+
+
+def test_routing_statistics_have_the_reference_keys_and_values():
+    """Golden figures: the reference's ``compute_routing_stats`` on the same three count vectors
+    (reference: Experiments/sparse_distillation/finetune_eval.py:67-209)."""
+    from experiments.sparse_distillation import finetune_eval as fe
+
+    class Layer(torch.nn.Module):
+        def __init__(self, counts):
+            super().__init__()
+            self._last_expert_counts = torch.tensor(counts, dtype=torch.float)
+            self.n_experts = len(counts)
+
+    layers = torch.nn.ModuleDict({"0": Layer([10, 10, 0, 0]), "1": Layer([5, 5, 5, 5]), "2": Layer([97, 1, 1, 1])})
+    r = fe.compute_routing_stats(layers, verbose=False)
+    golden = {
+        0: dict(total_tokens=20, entropy=0.6931471825, max_entropy=1.3862943611, normalized_entropy=0.5, min_frac=0.0,
+                max_frac=0.5, imbalance_ratio=5e9, active_experts=2, meaningful_experts=2, collapsed=False),
+        1: dict(total_tokens=20, entropy=1.3862943649, normalized_entropy=1.0, min_frac=0.25, max_frac=0.25,
+                imbalance_ratio=1.0, active_experts=4, meaningful_experts=4, collapsed=False),
+        2: dict(total_tokens=100, entropy=0.1677004993, normalized_entropy=0.1209703393, min_frac=0.01, max_frac=0.97,
+                imbalance_ratio=97.0, active_experts=4, meaningful_experts=1, collapsed=True),
+    }
+    for i, want in golden.items():
+        got = r["per_layer"][i]
+        for k, v in want.items():
+            assert got[k] == pytest.approx(v, rel=1e-5, abs=1e-7), (i, k, got[k], v)
+    agg = r["aggregate"]
+    assert agg["mean_normalized_entropy"] == pytest.approx(0.5403234478, rel=1e-5)
+    assert agg["min_normalized_entropy"] == pytest.approx(0.1209703393, rel=1e-5)
+    assert agg["mean_active_expert_frac"] == pytest.approx(10 / 12)
+    assert agg["worst_min_frac"] == 0.0 and agg["worst_max_frac"] == pytest.approx(0.97)
+    assert agg["collapsed_layers"] == [2] and agg["n_collapsed"] == 1
