@@ -441,3 +441,19 @@ def test_routing_statistics_have_the_reference_keys_and_values():
     assert agg["mean_active_expert_frac"] == pytest.approx(10 / 12)
     assert agg["worst_min_frac"] == 0.0 and agg["worst_max_frac"] == pytest.approx(0.97)
     assert agg["collapsed_layers"] == [2] and agg["n_collapsed"] == 1
+
+
+def test_the_guide_snippet_runs_as_written(tmp_path, monkeypatch):
+    """The Python example of the package's user guide is executed verbatim (in a scratch directory)."""
+    import os
+    import re
+    here = os.path.dirname(os.path.abspath(__file__))
+    guide = os.path.join(here, "..", "experiments", "sparse_distillation", "README.md")
+    code = re.search(r"```python\n(.*?)```", open(guide).read(), re.S).group(1)
+    monkeypatch.chdir(tmp_path)
+    torch.manual_seed(0)
+    scope = {}
+    exec(compile(code, "guide-snippet", "exec"), scope)
+    assert scope["logits"].shape == (2, 16, 256)
+    assert os.path.exists(tmp_path / "distilled.pt")
+    assert set(scope["quality"]) == {0, 1} and set(scope["sparse"].count_parameters()) >= {"total", "active"}
