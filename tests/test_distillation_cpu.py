@@ -457,3 +457,18 @@ def test_the_guide_snippet_runs_as_written(tmp_path, monkeypatch):
     assert scope["logits"].shape == (2, 16, 256)
     assert os.path.exists(tmp_path / "distilled.pt")
     assert set(scope["quality"]) == {0, 1} and set(scope["sparse"].count_parameters()) >= {"total", "active"}
+
+
+def test_finetuning_auxiliary_losses_match_the_reference_figures():
+    """Golden figures: the reference's ``compute_load_balancing_loss`` / ``compute_z_loss`` on the same seeded
+    logits (reference: Experiments/sparse_distillation/finetune_eval.py:28-64)."""
+    from experiments.sparse_distillation import finetune_eval as fe
+    torch.manual_seed(0)
+    golden = [(1.071408748626709, 12.736410140991211), (1.010005235671997, 10.339591979980469),
+              (1.4494478702545166, 23.843008041381836)]
+    for shape, (lb, z) in zip(((2, 16, 8), (64, 4), (3, 5, 16)), golden):
+        lg = torch.randn(*shape) * 2
+        E = shape[-1]
+        cnt = torch.bincount(lg.reshape(-1, E).topk(2, -1).indices.reshape(-1), minlength=E).float()
+        assert float(fe.compute_load_balancing_loss(lg, cnt)) == pytest.approx(lb, rel=1e-5)
+        assert float(fe.compute_z_loss(lg)) == pytest.approx(z, rel=1e-5)
